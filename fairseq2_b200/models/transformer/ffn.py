@@ -1,0 +1,125 @@
+"""Feed-forward networks (cf. fairseq2 ``models/transformer/ffn.py``:
+standard :43, Dauphin :135, GLU :229).
+
+``GLUFeedForwardNetwork`` runs gate and up projections as ONE GEMM whenever
+their weights are adjacent in memory and applies ``silu(gate) * up`` with the
+fused SwiGLU kernel.
+"""
+from __future__ import annotations
+
+from abc import ABC, abstractmethod
+from typing import Callable
+
+import torch
+from torch import Tensor
+from torch.nn import Dropout, Module, ReLU, SiLU
+
+from fairseq2_b200.gang import Gangs
+from fairseq2_b200.models.transformer.multihead_attention import merged_linear
+from fairseq2_b200.nn.normalization import LayerNorm
+from fairseq2_b200.nn.projection import ColumnShardedLinear, Linear, Projection, RowShardedLinear
+from fairseq2_b200.ops.activation import swiglu
+from fairseq2_b200.typing import DataType, Device
+
+
+class FeedForwardNetwork(Module, ABC):
+    def __init__(self, model_dim: int) -> None:
+        super().__init__()
+        self.model_dim = model_dim
+
+    @abstractmethod
+    def forward(self, seqs: Tensor) -> Tensor: ...
+
+
+def _col(gangs: Gangs | None, i: int, o: int, bias: bool, init_fn, device, dtype) -> Projection:  # type: ignore[no-untyped-def]
+    if gangs is not None and gangs.tp.size > 1:
+        return ColumnShardedLinear(gangs.tp, i, o, bias, gather_output=False, init_fn=init_fn, device=device,
+                                   dtype=dtype)
+    return Linear(i, o, bias, init_fn=init_fn, device=device, dtype=dtype)
+
+
+def _row(gangs: Gangs | None, i: int, o: int, bias: bool, init_fn, device, dtype) -> Projection:  # type: ignore[no-untyped-def]
+    if gangs is not None and gangs.tp.size > 1:
+        return RowShardedLinear(gangs.tp, i, o, bias, scatter_input=False, init_fn=init_fn, device=device,
+                                dtype=dtype)
+    return Linear(i, o, bias, init_fn=init_fn, device=device, dtype=dtype)
+
+
+class StandardFeedForwardNetwork(FeedForwardNetwork):
+    def __init__(self, model_dim: int, inner_dim: int, bias: bool, *, inner_activation: Module | None = None,
+                 inner_dropout_p: float = 0.0, inner_layer_norm: LayerNorm | None = None,
+                 proj_init_fn: Callable[[Linear], None] | None = None, gangs: Gangs | None = None,
+                 device: Device | None = None, dtype: DataType | None = None) -> None:
+        super().__init__(model_dim)
+        self.inner_proj = _col(gangs, model_dim, inner_dim, bias, proj_init_fn, device, dtype)
+        self.inner_activation = inner_activation if inner_activation is not None else ReLU()
+        self.inner_dropout = Dropout(inner_dropout_p) if inner_dropout_p > 0.0 else None
+        self.inner_layer_norm = inner_layer_norm
+        self.output_proj = _row(gangs, inner_dim, model_dim, bias, proj_init_fn, device, dtype)
+
+    def forward(self, seqs: Tensor) -> Tensor:
+        seqs = self.inner_activation(self.inner_proj(seqs))
+        if self.inner_layer_norm is not None:
+            seqs = self.inner_layer_norm(seqs)
+        if self.inner_dropout is not None:
+            seqs = self.inner_dropout(seqs)
+        return self.output_proj(seqs)
+
+
+class DauphinFeedForwardNetwork(FeedForwardNetwork):
+    """GLU of Dauphin et al.: one projection to ``2·inner``, ``a * sigmoid(b)``."""
+
+    def __init__(self, model_dim: int, inner_dim: int, bias: bool, *, inner_activation: Module | None = None,
+                 inner_dropout_p: float = 0.0, device: Device | None = None, dtype: DataType | None = None) -> None:
+        super().__init__(model_dim)
+        self.inner_proj = Linear(model_dim, inner_dim * 2, bias, device=device, dtype=dtype)
+        self.inner_activation = inner_activation if inner_activation is not None else torch.nn.Sigmoid()
+        self.inner_dropout = Dropout(inner_dropout_p) if inner_dropout_p > 0.0 else None
+        self.output_proj = Linear(inner_dim, model_dim, bias, device=device, dtype=dtype)
+
+    def forward(self, seqs: Tensor) -> Tensor:
+        a, b = self.inner_proj(seqs).chunk(2, dim=-1)
+        seqs = a * self.inner_activation(b)
+        if self.inner_dropout is not None:
+            seqs = self.inner_dropout(seqs)
+        return self.output_proj(seqs)
+
+
+class GLUFeedForwardNetwork(FeedForwardNetwork):
+    """``output_proj(act(gate_proj(x)) * inner_proj(x))`` (SwiGLU by default).
+
+    ``inner_dim`` is scaled by ``inner_dim_scale`` (2/3 in LLaMA) and rounded up
+    to a multiple of ``inner_dim_to_multiple``.
+    """
+
+    def __init__(self, model_dim: int, inner_dim: int, bias: bool, *, gate_activation: Module | None = None,
+                 inner_dim_scale: float = 2 / 3, inner_dim_to_multiple: int = 1, inner_dropout_p: float = 0.0,
+                 proj_init_fn: Callable[[Linear], None] | None = None, gangs: Gangs | None = None,
+                 device: Device | None = None, dtype: DataType | None = None) -> None:
+        super().__init__(model_dim)
+        self.inner_dim_scale, self.inner_dim_to_multiple = inner_dim_scale, inner_dim_to_multiple
+        if inner_dim_scale != 1.0:
+            inner_dim = int(inner_dim * inner_dim_scale)
+        if inner_dim_to_multiple != 1:
+            inner_dim = inner_dim_to_multiple * ((inner_dim + inner_dim_to_multiple - 1) // inner_dim_to_multiple)
+        self.inner_dim = inner_dim
+        self.gate_proj = _col(gangs, model_dim, inner_dim, bias, proj_init_fn, device, dtype)
+        self.gate_activation = gate_activation if gate_activation is not None else SiLU()
+        self.inner_proj = _col(gangs, model_dim, inner_dim, bias, proj_init_fn, device, dtype)
+        self.inner_dropout = Dropout(inner_dropout_p) if inner_dropout_p > 0.0 else None
+        self.output_proj = _row(gangs, inner_dim, model_dim, bias, proj_init_fn, device, dtype)
+
+    def forward(self, seqs: Tensor) -> Tensor:
+        h = None
+        if isinstance(self.gate_activation, SiLU):
+            gu = merged_linear(seqs, [self.gate_proj, self.inner_proj])
+            if gu is not None:
+                h = swiglu(gu)
+        if h is None:
+            h = self.gate_activation(self.gate_proj(seqs)) * self.inner_proj(seqs)
+        if self.inner_dropout is not None:
+            h = self.inner_dropout(h)
+        return self.output_proj(h)
+
+    def extra_repr(self) -> str:
+        return f"model_dim={self.model_dim}, inner_dim={self.inner_dim}"

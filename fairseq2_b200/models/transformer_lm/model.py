@@ -1,0 +1,61 @@
+"""Decoder-only language model (cf. fairseq2 ``models/transformer_lm/model.py:25-215``).
+
+With ``targets`` the output projection and the cross-entropy run as the fused,
+chunked kernel pipeline of ``ops.cross_entropy`` -- the full ``[T, V]`` logits
+are never resident -- unless logits are requested or label smoothing is on.
+"""
+from __future__ import annotations
+
+from typing import Literal
+
+from torch import Tensor
+
+from fairseq2_b200.models.clm import CausalLM
+from fairseq2_b200.models.transformer.frontend import TransformerFrontend
+from fairseq2_b200.models.transformer_lm.decoder import TransformerLMDecoder
+from fairseq2_b200.nn.batch_layout import BatchLayout
+from fairseq2_b200.nn.functional import cross_entropy
+from fairseq2_b200.nn.incremental_state import IncrementalStateBag
+from fairseq2_b200.nn.projection import Linear, Projection, TiedProjection
+from fairseq2_b200.ops.cross_entropy import fused_linear_cross_entropy
+
+
+class TransformerLM(CausalLM):
+    def __init__(self, model_dim: int, decoder_frontend: TransformerFrontend, decoder: TransformerLMDecoder,
+                 final_proj: Projection, pad_idx: int | None, max_seq_len: int) -> None:
+        super().__init__(max_seq_len)
+        self.model_dim = model_dim
+        self.decoder_frontend, self.decoder, self.final_proj = decoder_frontend, decoder, final_proj
+        self.pad_idx = pad_idx
+
+    def forward(self, seqs, seqs_layout, targets=None, *, state_bag=None, label_smoothing=0.0, target_mask=None,
+                reduction="sum", return_logits=False):  # type: ignore[override]
+        seqs, seqs_layout = self.decoder_frontend(seqs, seqs_layout, state_bag=state_bag)
+        out = self.decoder(seqs, seqs_layout, state_bag=state_bag)
+        del seqs
+        if targets is None:
+            return self.final_proj(out)
+        if not return_logits:
+            return self.compute_fused_loss(out, targets, label_smoothing=label_smoothing, target_mask=target_mask,
+                                           reduction=reduction)
+        logits = self.final_proj(out)
+        loss = self.compute_loss(logits, targets, label_smoothing=label_smoothing, target_mask=target_mask,
+                                 reduction=reduction)
+        return loss, logits
+
+    def compute_loss(self, logits: Tensor, targets: Tensor, *, label_smoothing: float = 0.0,
+                     target_mask: Tensor | None = None, reduction: Literal["sum", "mean"] = "sum") -> Tensor:
+        return cross_entropy(logits, targets, self.pad_idx, label_smoothing=label_smoothing, target_mask=target_mask,
+                             reduction=reduction)
+
+    def compute_fused_loss(self, decoder_output: Tensor, targets: Tensor, *, label_smoothing: float = 0.0,
+                           target_mask: Tensor | None = None, reduction: Literal["sum", "mean"] = "sum") -> Tensor:
+        fp = self.final_proj
+        if label_smoothing == 0.0 and isinstance(fp, (Linear, TiedProjection)) and fp.bias is None:
+            return fused_linear_cross_entropy(decoder_output, fp.weight, targets, target_mask=target_mask,
+                                              pad_idx=self.pad_idx, reduction=reduction)
+        return self.compute_loss(fp(decoder_output), targets, label_smoothing=label_smoothing,
+                                 target_mask=target_mask, reduction=reduction)
+
+    def extra_repr(self) -> str:
+        return f"model_dim={self.model_dim}, pad_idx={self.pad_idx}, max_seq_len={self.max_seq_len}"
