@@ -1,0 +1,38 @@
+// Parameters and host entry points of the varlen GQA attention kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+
+namespace fs2 {
+
+struct AttnParams {
+    // [tokens, heads, D] views; *_tstride is the token stride in elements, heads are D apart.
+    const __nv_bfloat16* q;
+    const __nv_bfloat16* k;
+    const __nv_bfloat16* v;
+    __nv_bfloat16* o;
+    const __nv_bfloat16* dout;
+    __nv_bfloat16* dq;
+    __nv_bfloat16* dk;
+    __nv_bfloat16* dv;
+    float* lse;    // [H, total_q]
+    float* delta;  // [H, total_q]
+    size_t q_tstride, k_tstride, v_tstride, o_tstride, do_tstride, dq_tstride, dk_tstride, dv_tstride;
+    const int* q_begins;
+    const int* q_lens;
+    const int* k_begins;
+    const int* k_lens;
+    int num_seqs, total_q, max_q, max_k;
+    int H, Hkv, D;
+    int causal;
+    float scale;
+};
+
+// Return nullptr on success, else a static error string.
+const char* attn_forward(const AttnParams& p, cudaStream_t st);
+const char* attn_backward(const AttnParams& p, cudaStream_t st);
+
+}  // namespace fs2

@@ -1,0 +1,425 @@
+// Python bindings of the sm_100a kernels (module fairseq2_b200._C).
+//
+// Every entry point validates shapes/dtypes/alignment on the host, launches on
+// the current CUDA stream of the tensor's device and never synchronises.
+
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <optional>
+#include <tuple>
+#include <vector>
+
+#include "attention.h"
+#include "elementwise.h"
+#include "gemm_tcgen05.h"
+
+namespace {
+
+using at::Tensor;
+
+int num_sms(const Tensor& t) { return at::cuda::getDeviceProperties(t.get_device())->multiProcessorCount; }
+
+cudaStream_t stream_of(const Tensor& t) { return at::cuda::getCurrentCUDAStream(t.get_device()).stream(); }
+
+bool is_bf16(const Tensor& t) { return t.scalar_type() == at::kBFloat16; }
+
+bool aligned16(const Tensor& t) { return reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0; }
+
+// ---------------------------------------------------------------- status word
+// One pinned, host-mapped int per process. Kernels store a non-zero code when a
+// bounded wait gives up; the host can poll it without touching the stream.
+int* g_status_host = nullptr;
+int* g_status_dev = nullptr;
+
+int* status_dev_ptr() {
+    if (g_status_host == nullptr) {
+        TORCH_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&g_status_host), sizeof(int), cudaHostAllocMapped) ==
+                        cudaSuccess,
+                    "cudaHostAlloc for the kernel status word failed");
+        *g_status_host = 0;
+        TORCH_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&g_status_dev), g_status_host, 0) ==
+                        cudaSuccess,
+                    "cudaHostGetDevicePointer for the kernel status word failed");
+    }
+    return g_status_dev;
+}
+
+int read_status() { return g_status_host ? *reinterpret_cast<volatile int*>(g_status_host) : 0; }
+
+void reset_status() {
+    if (g_status_host) *reinterpret_cast<volatile int*>(g_status_host) = 0;
+}
+
+void check_status() {
+    const int s = read_status();
+    if (s != 0) {
+        reset_status();
+        TORCH_CHECK(false, "a fairseq2_b200 kernel gave up on a bounded wait (code ", s & 0xff, ", site ", s >> 8, ")");
+    }
+}
+
+// ----------------------------------------------------------------------- GEMM
+void gemm_bf16(const Tensor& a, const Tensor& b, Tensor& out, bool a_mn, bool b_mn, bool accumulate) {
+    TORCH_CHECK(a.is_cuda() && b.is_cuda() && out.is_cuda(), "gemm_bf16: tensors must be on a CUDA device");
+    TORCH_CHECK(is_bf16(a) && is_bf16(b), "gemm_bf16: operands must be bfloat16");
+    TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && out.dim() == 2, "gemm_bf16: operands must be 2-D");
+    TORCH_CHECK(a.is_contiguous() && b.is_contiguous() && out.is_contiguous(), "gemm_bf16: operands must be contiguous");
+    const int64_t M = a_mn ? a.size(1) : a.size(0);
+    const int64_t K = a_mn ? a.size(0) : a.size(1);
+    const int64_t N = b_mn ? b.size(1) : b.size(0);
+    const int64_t Kb = b_mn ? b.size(0) : b.size(1);
+    TORCH_CHECK(K == Kb, "gemm_bf16: reduction dims differ (", K, " vs ", Kb, ")");
+    TORCH_CHECK(out.size(0) == M && out.size(1) == N, "gemm_bf16: out must be [", M, ", ", N, "]");
+    const bool f32 = out.scalar_type() == at::kFloat;
+    TORCH_CHECK(f32 || is_bf16(out), "gemm_bf16: out must be bfloat16 or float32");
+    TORCH_CHECK(a.size(1) % 8 == 0 && b.size(1) % 8 == 0 && N % 8 == 0,
+                "gemm_bf16: row pitches must be multiples of 16 bytes");
+    TORCH_CHECK(aligned16(a) && aligned16(b) && aligned16(out), "gemm_bf16: base pointers must be 16-byte aligned");
+    TORCH_CHECK(M > 0 && N > 0 && K > 0 && M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31),
+                "gemm_bf16: bad problem size");
+    check_status();
+    c10::cuda::CUDAGuard guard(a.device());
+    // Tensor maps are encoded through the driver API, which needs the primary
+    // context bound to the calling thread. Autograd worker threads may not have
+    // issued a runtime call yet, so bind it explicitly (a no-op when current).
+    TORCH_CHECK(cudaSetDevice(a.get_device()) == cudaSuccess, "gemm_bf16: cudaSetDevice failed");
+    const char* err = fs2::gemm_bf16_tcgen05(a.data_ptr(), b.data_ptr(), out.data_ptr(), static_cast<int>(M),
+                                             static_cast<int>(N), static_cast<int>(K), a_mn, b_mn, f32, accumulate,
+                                             status_dev_ptr(), num_sms(a), stream_of(a));
+    TORCH_CHECK(err == nullptr, "gemm_bf16: ", err);
+}
+
+// ---------------------------------------------------------------------- norms
+std::tuple<Tensor, Tensor> rms_norm_fwd(const Tensor& x, const Tensor& w, double eps) {
+    TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous() && w.is_contiguous(), "rms_norm_fwd: bad input");
+    TORCH_CHECK(x.scalar_type() == w.scalar_type() && (is_bf16(x) || x.scalar_type() == at::kFloat),
+                "rms_norm_fwd: dtype must be bf16 or fp32 and match the weight");
+    const int rows = static_cast<int>(x.size(0)), D = static_cast<int>(x.size(1));
+    TORCH_CHECK(D % 8 == 0 && D <= 65536 && w.numel() == D && aligned16(x) && aligned16(w), "rms_norm_fwd: bad dim");
+    c10::cuda::CUDAGuard guard(x.device());
+    Tensor y = at::empty_like(x);
+    Tensor rstd = at::empty({rows}, x.options().dtype(at::kFloat));
+    if (rows > 0)
+        fs2::rms_norm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr<float>(), rows, D,
+                          static_cast<float>(eps), is_bf16(x), num_sms(x), stream_of(x));
+    return {y, rstd};
+}
+
+std::tuple<Tensor, Tensor> rms_norm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd) {
+    TORCH_CHECK(dy.is_cuda() && dy.is_contiguous() && x.is_contiguous() && dy.sizes() == x.sizes(),
+                "rms_norm_bwd: bad input");
+    TORCH_CHECK(dy.scalar_type() == x.scalar_type(), "rms_norm_bwd: dtype mismatch");
+    const int rows = static_cast<int>(x.size(0)), D = static_cast<int>(x.size(1));
+    c10::cuda::CUDAGuard guard(x.device());
+    Tensor dx = at::empty_like(x);
+    Tensor dw = at::zeros({D}, x.options().dtype(at::kFloat));
+    if (rows > 0) {
+        const int grid = fs2::norm_bwd_grid(rows, num_sms(x));
+        Tensor part = at::empty({grid, D}, x.options().dtype(at::kFloat));
+        fs2::rms_norm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(),
+                          part.data_ptr<float>(), dw.data_ptr<float>(), rows, D, is_bf16(x), num_sms(x),
+                          stream_of(x));
+    }
+    return {dx, dw};
+}
+
+std::tuple<Tensor, Tensor, Tensor> layer_norm_fwd(const Tensor& x, const Tensor& w, const Tensor& b, double eps) {
+    TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous() && w.is_contiguous() && b.is_contiguous(),
+                "layer_norm_fwd: bad input");
+    TORCH_CHECK(x.scalar_type() == w.scalar_type() && x.scalar_type() == b.scalar_type() &&
+                    (is_bf16(x) || x.scalar_type() == at::kFloat),
+                "layer_norm_fwd: dtype must be bf16 or fp32 and match weight/bias");
+    const int rows = static_cast<int>(x.size(0)), D = static_cast<int>(x.size(1));
+    TORCH_CHECK(D % 8 == 0 && D <= 65536 && w.numel() == D && b.numel() == D && aligned16(x) && aligned16(w) &&
+                    aligned16(b),
+                "layer_norm_fwd: bad dim");
+    c10::cuda::CUDAGuard guard(x.device());
+    Tensor y = at::empty_like(x);
+    Tensor mean = at::empty({rows}, x.options().dtype(at::kFloat));
+    Tensor rstd = at::empty({rows}, x.options().dtype(at::kFloat));
+    if (rows > 0)
+        fs2::layer_norm_fwd(x.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), mean.data_ptr<float>(),
+                            rstd.data_ptr<float>(), rows, D, static_cast<float>(eps), is_bf16(x), num_sms(x),
+                            stream_of(x));
+    return {y, mean, rstd};
+}
+
+std::tuple<Tensor, Tensor, Tensor> layer_norm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w,
+                                                  const Tensor& mean, const Tensor& rstd) {
+    TORCH_CHECK(dy.is_cuda() && dy.is_contiguous() && x.is_contiguous() && dy.sizes() == x.sizes(),
+                "layer_norm_bwd: bad input");
+    const int rows = static_cast<int>(x.size(0)), D = static_cast<int>(x.size(1));
+    c10::cuda::CUDAGuard guard(x.device());
+    Tensor dx = at::empty_like(x);
+    Tensor dw = at::zeros({D}, x.options().dtype(at::kFloat));
+    Tensor db = at::zeros({D}, x.options().dtype(at::kFloat));
+    if (rows > 0) {
+        const int grid = fs2::norm_bwd_grid(rows, num_sms(x));
+        Tensor part = at::empty({2, grid, D}, x.options().dtype(at::kFloat));
+        fs2::layer_norm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), mean.data_ptr<float>(),
+                            rstd.data_ptr<float>(), dx.data_ptr(), part[0].data_ptr<float>(),
+                            part[1].data_ptr<float>(), dw.data_ptr<float>(), db.data_ptr<float>(), rows, D,
+                            is_bf16(x), num_sms(x), stream_of(x));
+    }
+    return {dx, dw, db};
+}
+
+// --------------------------------------------------------------------- SwiGLU
+Tensor swiglu_fwd(const Tensor& gu) {
+    TORCH_CHECK(gu.is_cuda() && is_bf16(gu) && gu.dim() == 2 && gu.is_contiguous() && gu.size(1) % 16 == 0 &&
+                    aligned16(gu),
+                "swiglu_fwd: expects contiguous bf16 [rows, 2F] with F % 8 == 0");
+    const int64_t rows = gu.size(0), F = gu.size(1) / 2;
+    c10::cuda::CUDAGuard guard(gu.device());
+    Tensor y = at::empty({rows, F}, gu.options());
+    if (rows > 0)
+        fs2::swiglu_fwd(gu.data_ptr(), y.data_ptr(), static_cast<size_t>(rows), static_cast<int>(F), num_sms(gu),
+                        stream_of(gu));
+    return y;
+}
+
+Tensor swiglu_bwd(const Tensor& dy, const Tensor& gu) {
+    TORCH_CHECK(dy.is_cuda() && is_bf16(dy) && dy.is_contiguous() && gu.is_contiguous() && dy.dim() == 2 &&
+                    gu.size(0) == dy.size(0) && gu.size(1) == 2 * dy.size(1),
+                "swiglu_bwd: bad input");
+    c10::cuda::CUDAGuard guard(gu.device());
+    Tensor dgu = at::empty_like(gu);
+    if (gu.size(0) > 0)
+        fs2::swiglu_bwd(dy.data_ptr(), gu.data_ptr(), dgu.data_ptr(), static_cast<size_t>(gu.size(0)),
+                        static_cast<int>(dy.size(1)), num_sms(gu), stream_of(gu));
+    return dgu;
+}
+
+// ----------------------------------------------------------------------- RoPE
+void rope_inplace(Tensor x, const Tensor& freqs, const Tensor& pos, bool inverse) {
+    TORCH_CHECK(x.is_cuda() && is_bf16(x) && x.dim() == 3 && x.stride(2) == 1, "rope_inplace: x must be bf16 [T, heads, D]");
+    TORCH_CHECK(freqs.is_cuda() && freqs.scalar_type() == at::kFloat && freqs.is_contiguous() && freqs.dim() == 3 &&
+                    freqs.size(1) * 2 == x.size(2) && freqs.size(2) == 2,
+                "rope_inplace: freqs must be fp32 [L, D/2, 2]");
+    TORCH_CHECK(pos.is_cuda() && pos.scalar_type() == at::kInt && pos.is_contiguous() && pos.numel() == x.size(0),
+                "rope_inplace: positions must be int32 [T]");
+    const int D = static_cast<int>(x.size(2));
+    TORCH_CHECK(D % 8 == 0 && x.stride(0) % 8 == 0 && x.stride(1) % 8 == 0 && aligned16(x), "rope_inplace: alignment");
+    c10::cuda::CUDAGuard guard(x.device());
+    fs2::rope_inplace(x.data_ptr(), freqs.data_ptr<float>(), pos.data_ptr<int>(), static_cast<size_t>(x.size(0)),
+                      static_cast<int>(x.size(1)), D, static_cast<size_t>(x.stride(0)),
+                      static_cast<size_t>(x.stride(1)), static_cast<int>(freqs.size(0)), inverse, num_sms(x),
+                      stream_of(x));
+}
+
+// -------------------------------------------------------------- cross-entropy
+void ce_fwd_bwd_inplace(Tensor logits, const Tensor& targets, const std::optional<Tensor>& mask, int64_t pad_idx,
+                        Tensor loss) {
+    TORCH_CHECK(logits.is_cuda() && is_bf16(logits) && logits.dim() == 2 && logits.is_contiguous() &&
+                    logits.size(1) % 8 == 0 && aligned16(logits),
+                "ce_fwd_bwd_inplace: logits must be contiguous bf16 [rows, V], V % 8 == 0");
+    TORCH_CHECK(targets.scalar_type() == at::kLong && targets.is_contiguous() && targets.numel() == logits.size(0),
+                "ce_fwd_bwd_inplace: targets must be int64 [rows]");
+    TORCH_CHECK(loss.scalar_type() == at::kFloat && loss.numel() == 1, "ce_fwd_bwd_inplace: loss must be an fp32 scalar");
+    const float* mptr = nullptr;
+    if (mask.has_value()) {
+        TORCH_CHECK(mask->scalar_type() == at::kFloat && mask->is_contiguous() && mask->numel() == logits.size(0),
+                    "ce_fwd_bwd_inplace: mask must be fp32 [rows]");
+        mptr = mask->data_ptr<float>();
+    }
+    const int rows = static_cast<int>(logits.size(0));
+    if (rows == 0) return;
+    c10::cuda::CUDAGuard guard(logits.device());
+    Tensor row_loss = at::empty({rows}, logits.options().dtype(at::kFloat));
+    fs2::ce_fwd_bwd(logits.data_ptr(), reinterpret_cast<const long long*>(targets.data_ptr<int64_t>()), mptr,
+                    row_loss.data_ptr<float>(), rows, static_cast<int>(logits.size(1)), static_cast<int>(pad_idx),
+                    stream_of(logits));
+    loss.add_(row_loss.sum());
+}
+
+// ------------------------------------------------------------------ attention
+fs2::AttnParams make_attn_params(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& qb, const Tensor& ql,
+                                 const Tensor& kb, const Tensor& kl, int64_t max_q, int64_t max_k, bool causal,
+                                 double scale) {
+    auto check_view = [](const Tensor& t, const char* name) {
+        TORCH_CHECK(t.is_cuda() && is_bf16(t) && t.dim() == 3, name, " must be a bf16 [T, heads, D] CUDA tensor");
+        TORCH_CHECK(t.stride(2) == 1 && t.stride(1) == t.size(2), name, " must have contiguous heads");
+        TORCH_CHECK(t.stride(0) % 8 == 0 && aligned16(t), name, " must be 16-byte aligned");
+    };
+    check_view(q, "q");
+    check_view(k, "k");
+    check_view(v, "v");
+    TORCH_CHECK(k.sizes() == v.sizes() && q.size(2) == k.size(2), "attention: shape mismatch");
+    TORCH_CHECK(q.size(1) % k.size(1) == 0, "attention: H must be a multiple of Hkv");
+    for (const Tensor* t : {&qb, &ql, &kb, &kl})
+        TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kInt && t->dim() == 1 && t->stride(0) == 1,
+                    "attention: sequence offsets/lengths must be int32 CUDA vectors");
+    TORCH_CHECK(qb.numel() == ql.numel() && kb.numel() == kl.numel() && qb.numel() == kb.numel(),
+                "attention: inconsistent number of sequences");
+    fs2::AttnParams p{};
+    p.q = static_cast<const __nv_bfloat16*>(q.data_ptr());
+    p.k = static_cast<const __nv_bfloat16*>(k.data_ptr());
+    p.v = static_cast<const __nv_bfloat16*>(v.data_ptr());
+    p.q_tstride = q.stride(0);
+    p.k_tstride = k.stride(0);
+    p.v_tstride = v.stride(0);
+    p.q_begins = qb.data_ptr<int>();
+    p.q_lens = ql.data_ptr<int>();
+    p.k_begins = kb.data_ptr<int>();
+    p.k_lens = kl.data_ptr<int>();
+    p.num_seqs = static_cast<int>(qb.numel());
+    p.total_q = static_cast<int>(q.size(0));
+    p.max_q = static_cast<int>(max_q);
+    p.max_k = static_cast<int>(max_k);
+    p.H = static_cast<int>(q.size(1));
+    p.Hkv = static_cast<int>(k.size(1));
+    p.D = static_cast<int>(q.size(2));
+    p.causal = causal ? 1 : 0;
+    p.scale = static_cast<float>(scale);
+    return p;
+}
+
+std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& qb,
+                                    const Tensor& ql, const Tensor& kb, const Tensor& kl, int64_t max_q,
+                                    int64_t max_k, bool causal, double scale) {
+    fs2::AttnParams p = make_attn_params(q, k, v, qb, ql, kb, kl, max_q, max_k, causal, scale);
+    c10::cuda::CUDAGuard guard(q.device());
+    // rows that belong to no sequence (padding) stay zero
+    Tensor out = at::zeros({q.size(0), q.size(1), q.size(2)}, q.options());
+    Tensor lse = at::full({q.size(1), q.size(0)}, -INFINITY, q.options().dtype(at::kFloat));
+    p.o = static_cast<__nv_bfloat16*>(out.data_ptr());
+    p.o_tstride = out.stride(0);
+    p.lse = lse.data_ptr<float>();
+    const char* err = fs2::attn_forward(p, stream_of(q));
+    TORCH_CHECK(err == nullptr, "attn_fwd: ", err);
+    return {out, lse};
+}
+
+void attn_bwd_out(const Tensor& dout, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out,
+                  const Tensor& lse, const Tensor& qb, const Tensor& ql, const Tensor& kb, const Tensor& kl,
+                  int64_t max_q, int64_t max_k, bool causal, double scale, Tensor dq, Tensor dk, Tensor dv) {
+    fs2::AttnParams p = make_attn_params(q, k, v, qb, ql, kb, kl, max_q, max_k, causal, scale);
+    auto check_view = [](const Tensor& t, const Tensor& like, const char* name) {
+        TORCH_CHECK(t.is_cuda() && is_bf16(t) && t.sizes() == like.sizes() && t.stride(2) == 1 &&
+                        t.stride(1) == t.size(2) && t.stride(0) % 8 == 0 && aligned16(t),
+                    name, " has a bad layout");
+    };
+    check_view(dout, q, "dout");
+    check_view(out, q, "out");
+    check_view(dq, q, "dq");
+    check_view(dk, k, "dk");
+    check_view(dv, v, "dv");
+    c10::cuda::CUDAGuard guard(q.device());
+    Tensor delta = at::empty({q.size(1), q.size(0)}, q.options().dtype(at::kFloat));
+    p.o = static_cast<__nv_bfloat16*>(out.data_ptr());
+    p.o_tstride = out.stride(0);
+    p.dout = static_cast<const __nv_bfloat16*>(dout.data_ptr());
+    p.do_tstride = dout.stride(0);
+    p.dq = static_cast<__nv_bfloat16*>(dq.data_ptr());
+    p.dk = static_cast<__nv_bfloat16*>(dk.data_ptr());
+    p.dv = static_cast<__nv_bfloat16*>(dv.data_ptr());
+    p.dq_tstride = dq.stride(0);
+    p.dk_tstride = dk.stride(0);
+    p.dv_tstride = dv.stride(0);
+    p.lse = lse.data_ptr<float>();
+    p.delta = delta.data_ptr<float>();
+    const char* err = fs2::attn_backward(p, stream_of(q));
+    TORCH_CHECK(err == nullptr, "attn_bwd: ", err);
+}
+
+std::tuple<Tensor, Tensor, Tensor> attn_bwd(const Tensor& dout, const Tensor& q, const Tensor& k, const Tensor& v,
+                                            const Tensor& out, const Tensor& lse, const Tensor& qb, const Tensor& ql,
+                                            const Tensor& kb, const Tensor& kl, int64_t max_q, int64_t max_k,
+                                            bool causal, double scale) {
+    // tokens outside every sequence (padding) receive zero gradients
+    Tensor dq = at::zeros({q.size(0), q.size(1), q.size(2)}, q.options());
+    Tensor dk = at::zeros({k.size(0), k.size(1), k.size(2)}, k.options());
+    Tensor dv = at::zeros({v.size(0), v.size(1), v.size(2)}, v.options());
+    attn_bwd_out(dout, q, k, v, out, lse, qb, ql, kb, kl, max_q, max_k, causal, scale, dq, dk, dv);
+    return {dq, dk, dv};
+}
+
+// ------------------------------------------------------------------ optimizer
+void multi_tensor_adamw(const std::vector<Tensor>& masters, const std::vector<Tensor>& grads,
+                        const std::vector<Tensor>& ms, const std::vector<Tensor>& vs, const std::vector<Tensor>& lows,
+                        double lr, double beta1, double beta2, double eps, double wd, int64_t step,
+                        const std::optional<Tensor>& grad_scale) {
+    const size_t n = masters.size();
+    TORCH_CHECK(grads.size() == n && ms.size() == n && vs.size() == n && lows.size() == n,
+                "multi_tensor_adamw: list sizes differ");
+    const float* gs = nullptr;
+    if (grad_scale.has_value()) {
+        TORCH_CHECK(grad_scale->is_cuda() && grad_scale->scalar_type() == at::kFloat && grad_scale->numel() == 1,
+                    "multi_tensor_adamw: grad_scale must be an fp32 device scalar");
+        gs = grad_scale->data_ptr<float>();
+    }
+    for (size_t i = 0; i < n; ++i) {
+        const Tensor& p = masters[i];
+        const Tensor& g = grads[i];
+        TORCH_CHECK(p.is_cuda() && p.scalar_type() == at::kFloat && p.is_contiguous(), "multi_tensor_adamw: master weights must be contiguous fp32");
+        TORCH_CHECK(ms[i].scalar_type() == at::kFloat && vs[i].scalar_type() == at::kFloat && ms[i].is_contiguous() &&
+                        vs[i].is_contiguous() && ms[i].numel() == p.numel() && vs[i].numel() == p.numel(),
+                    "multi_tensor_adamw: optimizer state must be contiguous fp32 of the parameter's size");
+        TORCH_CHECK(g.is_contiguous() && g.numel() == p.numel() && (is_bf16(g) || g.scalar_type() == at::kFloat),
+                    "multi_tensor_adamw: gradients must be contiguous bf16/fp32");
+        void* low = nullptr;
+        if (lows[i].numel() > 0) {
+            TORCH_CHECK(is_bf16(lows[i]) && lows[i].is_contiguous() && lows[i].numel() == p.numel() && aligned16(lows[i]),
+                        "multi_tensor_adamw: low-precision copies must be contiguous bf16");
+            low = lows[i].data_ptr();
+        }
+        TORCH_CHECK(aligned16(p) && aligned16(g) && aligned16(ms[i]) && aligned16(vs[i]),
+                    "multi_tensor_adamw: tensors must be 16-byte aligned");
+        c10::cuda::CUDAGuard guard(p.device());
+        fs2::adamw(p.data_ptr<float>(), g.data_ptr(), is_bf16(g), ms[i].data_ptr<float>(), vs[i].data_ptr<float>(), low,
+                   static_cast<size_t>(p.numel()), static_cast<float>(lr), static_cast<float>(beta1),
+                   static_cast<float>(beta2), static_cast<float>(eps), static_cast<float>(wd), static_cast<int>(step),
+                   gs, num_sms(p), stream_of(p));
+    }
+}
+
+Tensor multi_tensor_l2_norm_sq(const std::vector<Tensor>& ts) {
+    TORCH_CHECK(!ts.empty(), "multi_tensor_l2_norm_sq: empty list");
+    c10::cuda::CUDAGuard guard(ts[0].device());
+    Tensor out = at::zeros({}, ts[0].options().dtype(at::kFloat));
+    for (const Tensor& t : ts) {
+        TORCH_CHECK(t.is_cuda() && t.is_contiguous() && (is_bf16(t) || t.scalar_type() == at::kFloat) && aligned16(t),
+                    "multi_tensor_l2_norm_sq: tensors must be contiguous, 16-byte aligned bf16/fp32");
+        fs2::l2_norm_sq(t.data_ptr(), is_bf16(t), static_cast<size_t>(t.numel()), out.data_ptr<float>(), num_sms(t),
+                        stream_of(t));
+    }
+    return out;
+}
+
+void multi_tensor_scale(const std::vector<Tensor>& ts, const Tensor& scale) {
+    TORCH_CHECK(scale.is_cuda() && scale.scalar_type() == at::kFloat && scale.numel() == 1,
+                "multi_tensor_scale: scale must be an fp32 device scalar");
+    for (const Tensor& t : ts) {
+        TORCH_CHECK(t.is_cuda() && t.is_contiguous() && (is_bf16(t) || t.scalar_type() == at::kFloat) && aligned16(t),
+                    "multi_tensor_scale: tensors must be contiguous, 16-byte aligned bf16/fp32");
+        c10::cuda::CUDAGuard guard(t.device());
+        fs2::scale_inplace(t.data_ptr(), is_bf16(t), static_cast<size_t>(t.numel()), scale.data_ptr<float>(),
+                           num_sms(t), stream_of(t));
+    }
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.doc() = "fairseq2_b200 sm_100a kernels";
+    m.def("gemm_bf16", &gemm_bf16);
+    m.def("rms_norm_fwd", &rms_norm_fwd);
+    m.def("rms_norm_bwd", &rms_norm_bwd);
+    m.def("layer_norm_fwd", &layer_norm_fwd);
+    m.def("layer_norm_bwd", &layer_norm_bwd);
+    m.def("swiglu_fwd", &swiglu_fwd);
+    m.def("swiglu_bwd", &swiglu_bwd);
+    m.def("rope_inplace", &rope_inplace);
+    m.def("ce_fwd_bwd_inplace", &ce_fwd_bwd_inplace);
+    m.def("attn_fwd", &attn_fwd);
+    m.def("attn_bwd", &attn_bwd);
+    m.def("attn_bwd_out", &attn_bwd_out);
+    m.def("multi_tensor_adamw", &multi_tensor_adamw);
+    m.def("multi_tensor_l2_norm_sq", &multi_tensor_l2_norm_sq);
+    m.def("multi_tensor_scale", &multi_tensor_scale);
+    m.def("check_status", &check_status, "Raises if a kernel recorded a bounded-wait failure.");
+    m.def("read_status", &read_status);
+    m.def("reset_status", &reset_status);
+}

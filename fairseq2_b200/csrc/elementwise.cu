@@ -1,0 +1,625 @@
+// Bandwidth-bound kernels: RMSNorm / LayerNorm (fwd + bwd), SwiGLU, rotary
+// encoding, masked cross-entropy (loss + in-place logit gradient), AdamW,
+// L2 norm and scaling. All use 16-byte vector accesses and fp32 arithmetic.
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "common.cuh"
+#include "elementwise.h"
+
+namespace fs2 {
+
+namespace {
+
+constexpr int MAX_VPT = 8;  // upper bound on vectors of 8 elements cached per thread
+
+inline int norm_block(int D) {
+    int nvec = D / 8;
+    int threads = ((nvec + 31) / 32) * 32;
+    if (threads > 1024) threads = 1024;
+    if (threads < 32) threads = 32;
+    return threads;
+}
+
+// ------------------------------------------------------------------- RMSNorm
+template <typename T, int VPT>
+__global__ void rms_norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
+                                    float* __restrict__ rstd, int rows, int D, float eps) {
+    __shared__ float scratch[32];
+    const int nvec = D / 8;
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const T* xr = x + static_cast<size_t>(row) * D;
+        T* yr = y + static_cast<size_t>(row) * D;
+        float cache[VPT][8];
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int v = threadIdx.x + j * blockDim.x;
+            if (v < nvec) {
+                load8(xr, static_cast<size_t>(v) * 8, cache[j]);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) ss += cache[j][e] * cache[j][e];
+            }
+        }
+        ss = block_sum(ss, scratch);
+        const float r = rsqrtf(ss / D + eps);
+        if (threadIdx.x == 0) rstd[row] = r;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int v = threadIdx.x + j * blockDim.x;
+            if (v < nvec) {
+                float wv[8], o[8];
+                load8(w, static_cast<size_t>(v) * 8, wv);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    // match the reference: normalise in fp32, round to the
+                    // activation dtype, then scale by the weight
+                    float n = cache[j][e] * r;
+                    if constexpr (sizeof(T) == 2) n = __bfloat162float(__float2bfloat16_rn(n));
+                    o[e] = n * wv[e];
+                }
+                store8(yr, static_cast<size_t>(v) * 8, o);
+            }
+        }
+    }
+}
+
+// dx = rstd * (g - xhat * mean(g * xhat)), g = dy * w, xhat = x * rstd
+// dw partial per block: sum over its rows of dy * xhat
+template <typename T, int VPT>
+__global__ void rms_norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
+                                    const float* __restrict__ rstd, T* __restrict__ dx, float* __restrict__ dw_part,
+                                    int rows, int D) {
+    __shared__ float scratch[32];
+    const int nvec = D / 8;
+    float dwacc[VPT][8];
+    float wv[VPT][8];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int v = threadIdx.x + j * blockDim.x;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dwacc[j][e] = 0.f;
+        if (v < nvec) load8(w, static_cast<size_t>(v) * 8, wv[j]);
+    }
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const size_t off = static_cast<size_t>(row) * D;
+        const float r = rstd[row];
+        float g[VPT][8], xh[VPT][8];
+        float dot = 0.f;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int v = threadIdx.x + j * blockDim.x;
+            if (v < nvec) {
+                float dyv[8], xv[8];
+                load8(dy + off, static_cast<size_t>(v) * 8, dyv);
+                load8(x + off, static_cast<size_t>(v) * 8, xv);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    xh[j][e] = xv[e] * r;
+                    g[j][e] = dyv[e] * wv[j][e];
+                    dot += g[j][e] * xh[j][e];
+                    dwacc[j][e] += dyv[e] * xh[j][e];
+                }
+            }
+        }
+        dot = block_sum(dot, scratch);
+        const float m = dot / D;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int v = threadIdx.x + j * blockDim.x;
+            if (v < nvec) {
+                float o[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = r * (g[j][e] - xh[j][e] * m);
+                store8(dx + off, static_cast<size_t>(v) * 8, o);
+            }
+        }
+    }
+    float* part = dw_part + static_cast<size_t>(blockIdx.x) * D;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int v = threadIdx.x + j * blockDim.x;
+        if (v < nvec) store8(part, static_cast<size_t>(v) * 8, dwacc[j]);
+    }
+}
+
+// out[d] = sum_p part[p, d]
+__global__ void reduce_partials_kernel(const float* __restrict__ part, float* __restrict__ out, int P, int D) {
+    const int d = blockIdx.x * blockDim.x + threadIdx.x;
+    if (d >= D) return;
+    float s = 0.f;
+    for (int p = 0; p < P; ++p) s += part[static_cast<size_t>(p) * D + d];
+    out[d] = s;
+}
+
+// ----------------------------------------------------------------- LayerNorm
+template <typename T, int VPT>
+__global__ void layer_norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ b,
+                                      T* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd, int rows,
+                                      int D, float eps) {
+    __shared__ float scratch[32];
+    const int nvec = D / 8;
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const size_t off = static_cast<size_t>(row) * D;
+        float cache[VPT][8];
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int v = threadIdx.x + j * blockDim.x;
+            if (v < nvec) {
+                load8(x + off, static_cast<size_t>(v) * 8, cache[j]);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) s += cache[j][e];
+            }
+        }
+        const float mu = block_sum(s, scratch) / D;
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int v = threadIdx.x + j * blockDim.x;
+            if (v < nvec) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float d = cache[j][e] - mu;
+                    ss += d * d;
+                }
+            }
+        }
+        const float r = rsqrtf(block_sum(ss, scratch) / D + eps);
+        if (threadIdx.x == 0) {
+            mean[row] = mu;
+            rstd[row] = r;
+        }
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int v = threadIdx.x + j * blockDim.x;
+            if (v < nvec) {
+                float wv[8], bv[8], o[8];
+                load8(w, static_cast<size_t>(v) * 8, wv);
+                load8(b, static_cast<size_t>(v) * 8, bv);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = (cache[j][e] - mu) * r * wv[e] + bv[e];
+                store8(y + off, static_cast<size_t>(v) * 8, o);
+            }
+        }
+    }
+}
+
+// dx = rstd * (g - mean(g) - xhat * mean(g * xhat)); dw += dy * xhat; db += dy
+template <typename T, int VPT>
+__global__ void layer_norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
+                                      const float* __restrict__ mean, const float* __restrict__ rstd,
+                                      T* __restrict__ dx, float* __restrict__ dw_part, float* __restrict__ db_part,
+                                      int rows, int D) {
+    __shared__ float scratch[32];
+    const int nvec = D / 8;
+    float dwacc[VPT][8], dbacc[VPT][8], wv[VPT][8];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int v = threadIdx.x + j * blockDim.x;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dwacc[j][e] = dbacc[j][e] = 0.f;
+        if (v < nvec) load8(w, static_cast<size_t>(v) * 8, wv[j]);
+    }
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const size_t off = static_cast<size_t>(row) * D;
+        const float mu = mean[row], r = rstd[row];
+        float g[VPT][8], xh[VPT][8];
+        float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int v = threadIdx.x + j * blockDim.x;
+            if (v < nvec) {
+                float dyv[8], xv[8];
+                load8(dy + off, static_cast<size_t>(v) * 8, dyv);
+                load8(x + off, static_cast<size_t>(v) * 8, xv);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    xh[j][e] = (xv[e] - mu) * r;
+                    g[j][e] = dyv[e] * wv[j][e];
+                    s1 += g[j][e];
+                    s2 += g[j][e] * xh[j][e];
+                    dwacc[j][e] += dyv[e] * xh[j][e];
+                    dbacc[j][e] += dyv[e];
+                }
+            }
+        }
+        s1 = block_sum(s1, scratch) / D;
+        s2 = block_sum(s2, scratch) / D;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int v = threadIdx.x + j * blockDim.x;
+            if (v < nvec) {
+                float o[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = r * (g[j][e] - s1 - xh[j][e] * s2);
+                store8(dx + off, static_cast<size_t>(v) * 8, o);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int v = threadIdx.x + j * blockDim.x;
+        if (v < nvec) {
+            store8(dw_part + static_cast<size_t>(blockIdx.x) * D, static_cast<size_t>(v) * 8, dwacc[j]);
+            store8(db_part + static_cast<size_t>(blockIdx.x) * D, static_cast<size_t>(v) * 8, dbacc[j]);
+        }
+    }
+}
+
+// -------------------------------------------------------------------- SwiGLU
+// gate_up: [rows, 2F] (gate | up); y: [rows, F]
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ y, size_t rows,
+                                  int F) {
+    const size_t nvec_row = F / 8;
+    const size_t total = rows * nvec_row;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t row = i / nvec_row, v = i - row * nvec_row;
+        float g[8], u[8], o[8];
+        load8(gu + row * 2 * F, v * 8, g);
+        load8(gu + row * 2 * F + F, v * 8, u);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float s = g[e] / (1.f + __expf(-g[e]));
+            o[e] = s * u[e];
+        }
+        store8(y + row * F, v * 8, o);
+    }
+}
+
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ gu,
+                                  __nv_bfloat16* __restrict__ dgu, size_t rows, int F) {
+    const size_t nvec_row = F / 8;
+    const size_t total = rows * nvec_row;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t row = i / nvec_row, v = i - row * nvec_row;
+        float g[8], u[8], d[8], dg[8], du[8];
+        load8(gu + row * 2 * F, v * 8, g);
+        load8(gu + row * 2 * F + F, v * 8, u);
+        load8(dy + row * F, v * 8, d);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float sig = 1.f / (1.f + __expf(-g[e]));
+            const float silu = g[e] * sig;
+            du[e] = d[e] * silu;
+            dg[e] = d[e] * u[e] * (sig + silu * (1.f - sig));
+        }
+        store8(dgu + row * 2 * F, v * 8, dg);
+        store8(dgu + row * 2 * F + F, v * 8, du);
+    }
+}
+
+// ---------------------------------------------------------------------- RoPE
+// x: [tokens, heads, D] with token stride `tstride` and head stride `hstride`
+// (elements). freqs: [L, D/2, 2] (cos, sin) fp32. pos[t] < 0 -> untouched.
+__global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ freqs,
+                            const int* __restrict__ pos, size_t tokens, int heads, int D, size_t tstride,
+                            size_t hstride, int max_pos, float sign) {
+    const int vec_per_head = D / 8;
+    const size_t total = tokens * heads * vec_per_head;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int v = static_cast<int>(i % vec_per_head);
+        const size_t th = i / vec_per_head;
+        const int h = static_cast<int>(th % heads);
+        const size_t t = th / heads;
+        const int p = pos[t];
+        if (p < 0 || p >= max_pos) continue;
+        __nv_bfloat16* ptr = x + t * tstride + static_cast<size_t>(h) * hstride;
+        float f[8], cs[8], o[8];
+        load8(ptr, static_cast<size_t>(v) * 8, f);
+        load8(freqs + (static_cast<size_t>(p) * (D / 2)) * 2, static_cast<size_t>(v) * 8, cs);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float c = cs[2 * e], s = cs[2 * e + 1] * sign;
+            const float a = f[2 * e], b = f[2 * e + 1];
+            o[2 * e] = a * c - b * s;
+            o[2 * e + 1] = a * s + b * c;
+        }
+        store8(ptr, static_cast<size_t>(v) * 8, o);
+    }
+}
+
+// ------------------------------------------------------------- cross-entropy
+// One block per row. logits (bf16, [rows, V]) are overwritten with
+// (softmax - onehot) * mask[row]; row_loss[row] = (lse - logit[target]) * mask.
+__global__ void ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ targets,
+                                  const float* __restrict__ mask, float* __restrict__ row_loss, int V, int pad_idx) {
+    __shared__ float scratch[32];
+    const size_t row = blockIdx.x;
+    __nv_bfloat16* lr = logits + row * static_cast<size_t>(V);
+    const long long tgt = targets[row];
+    float mk = mask ? mask[row] : 1.f;
+    if (tgt == pad_idx || tgt < 0 || tgt >= V) mk = 0.f;
+    const int nvec = V / 8;
+    if (mk == 0.f) {
+        const float zf[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        const bf16x8 z = pack8(zf);
+        for (int v = threadIdx.x; v < nvec; v += blockDim.x) *reinterpret_cast<bf16x8*>(lr + static_cast<size_t>(v) * 8) = z;
+        if (threadIdx.x == 0) row_loss[row] = 0.f;
+        return;
+    }
+    float mx = -INFINITY, sum = 0.f;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+        float f[8];
+        load8(lr, static_cast<size_t>(v) * 8, f);
+        float lm = f[0];
+#pragma unroll
+        for (int e = 1; e < 8; ++e) lm = fmaxf(lm, f[e]);
+        const float nm = fmaxf(mx, lm);
+        float acc = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc += __expf(f[e] - nm);
+        sum = sum * __expf(mx - nm) + acc;
+        mx = nm;
+    }
+    const float gmx = block_max(mx, scratch);
+    sum = (mx == -INFINITY) ? 0.f : sum * __expf(mx - gmx);
+    const float gsum = block_sum(sum, scratch);
+    const float lse = gmx + logf(gsum);
+    const float tl = __bfloat162float(lr[tgt]);
+    __syncthreads();  // everyone has read the target logit before it is overwritten
+    if (threadIdx.x == 0) row_loss[row] = (lse - tl) * mk;
+    const int tv = static_cast<int>(tgt / 8), te = static_cast<int>(tgt % 8);
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+        float f[8], o[8];
+        load8(lr, static_cast<size_t>(v) * 8, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = __expf(f[e] - lse) * mk;
+        if (v == tv) o[te] -= mk;
+        store8(lr, static_cast<size_t>(v) * 8, o);
+    }
+}
+
+// --------------------------------------------------------------------- AdamW
+template <typename G>
+__global__ void adamw_kernel(float* __restrict__ p, const G* __restrict__ g, float* __restrict__ m,
+                             float* __restrict__ v, __nv_bfloat16* __restrict__ low, size_t n, float lr, float beta1,
+                             float beta2, float eps, float wd, float bc1, float bc2_sqrt,
+                             const float* __restrict__ grad_scale) {
+    const float gs = grad_scale ? *grad_scale : 1.f;
+    const size_t nvec = n / 8;
+    const float step_size = lr / bc1;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < nvec;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        float pv[8], gv[8], mv[8], vv[8];
+        load8(p, i * 8, pv);
+        load8(g, i * 8, gv);
+        load8(m, i * 8, mv);
+        load8(v, i * 8, vv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float gr = gv[e] * gs;
+            pv[e] *= (1.f - lr * wd);
+            mv[e] = beta1 * mv[e] + (1.f - beta1) * gr;
+            vv[e] = beta2 * vv[e] + (1.f - beta2) * gr * gr;
+            const float denom = sqrtf(vv[e]) / bc2_sqrt + eps;
+            pv[e] -= step_size * mv[e] / denom;
+        }
+        store8(p, i * 8, pv);
+        store8(m, i * 8, mv);
+        store8(v, i * 8, vv);
+        if (low) store8(low, i * 8, pv);
+    }
+    // tail (n not a multiple of 8)
+    if (blockIdx.x == 0) {
+        for (size_t i = nvec * 8 + threadIdx.x; i < n; i += blockDim.x) {
+            float gr;
+            if constexpr (sizeof(G) == 2) gr = __bfloat162float(g[i]) * gs;
+            else gr = g[i] * gs;
+            float pv = p[i] * (1.f - lr * wd);
+            const float mv = beta1 * m[i] + (1.f - beta1) * gr;
+            const float vv = beta2 * v[i] + (1.f - beta2) * gr * gr;
+            pv -= step_size * mv / (sqrtf(vv) / bc2_sqrt + eps);
+            p[i] = pv;
+            m[i] = mv;
+            v[i] = vv;
+            if (low) low[i] = __float2bfloat16_rn(pv);
+        }
+    }
+}
+
+template <typename T>
+__global__ void l2_norm_sq_kernel(const T* __restrict__ x, size_t n, float* __restrict__ out) {
+    __shared__ float scratch[32];
+    const size_t nvec = n / 8;
+    float acc = 0.f;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < nvec;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        float f[8];
+        load8(x, i * 8, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc += f[e] * f[e];
+    }
+    if (blockIdx.x == 0) {
+        for (size_t i = nvec * 8 + threadIdx.x; i < n; i += blockDim.x) {
+            float f;
+            if constexpr (sizeof(T) == 2) f = __bfloat162float(x[i]);
+            else f = x[i];
+            acc += f * f;
+        }
+    }
+    acc = block_sum(acc, scratch);
+    if (threadIdx.x == 0) atomicAdd(out, acc);
+}
+
+template <typename T>
+__global__ void scale_kernel(T* __restrict__ x, size_t n, const float* __restrict__ scale) {
+    const float s = *scale;
+    const size_t nvec = n / 8;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < nvec;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        float f[8];
+        load8(x, i * 8, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] *= s;
+        store8(x, i * 8, f);
+    }
+    if (blockIdx.x == 0) {
+        for (size_t i = nvec * 8 + threadIdx.x; i < n; i += blockDim.x) {
+            if constexpr (sizeof(T) == 2) x[i] = __float2bfloat16_rn(__bfloat162float(x[i]) * s);
+            else x[i] = x[i] * s;
+        }
+    }
+}
+
+inline int norm_vpt(int D, int threads) {
+    const int nvec = D / 8;
+    const int need = (nvec + threads - 1) / threads;
+    return need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
+}
+
+#define FS2_VPT_DISPATCH(VPT_VALUE, ...)                   \
+    switch (VPT_VALUE) {                                   \
+        case 1: { constexpr int VPT = 1; __VA_ARGS__; break; } \
+        case 2: { constexpr int VPT = 2; __VA_ARGS__; break; } \
+        case 4: { constexpr int VPT = 4; __VA_ARGS__; break; } \
+        default: { constexpr int VPT = 8; __VA_ARGS__; break; } \
+    }
+
+inline int stream_grid(size_t work_items, int threads, int num_sms) {
+    size_t blocks = (work_items + threads - 1) / threads;
+    const size_t cap = static_cast<size_t>(num_sms) * 8;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return static_cast<int>(blocks);
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------ launchers
+int norm_bwd_grid(int rows, int num_sms) {
+    int g = num_sms * 2;
+    return rows < g ? rows : g;
+}
+
+void rms_norm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int D, float eps, bool bf16,
+                  int num_sms, cudaStream_t st) {
+    const int threads = norm_block(D);
+    const int grid = rows < num_sms * 16 ? rows : num_sms * 16;
+    FS2_VPT_DISPATCH(norm_vpt(D, threads),
+        if (bf16)
+            rms_norm_fwd_kernel<__nv_bfloat16, VPT><<<grid, threads, 0, st>>>(
+                static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+                static_cast<__nv_bfloat16*>(y), rstd, rows, D, eps);
+        else
+            rms_norm_fwd_kernel<float, VPT><<<grid, threads, 0, st>>>(
+                static_cast<const float*>(x), static_cast<const float*>(w), static_cast<float*>(y), rstd, rows, D,
+                eps))
+}
+
+void rms_norm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw_part,
+                  float* dw, int rows, int D, bool bf16, int num_sms, cudaStream_t st) {
+    const int threads = norm_block(D);
+    const int grid = norm_bwd_grid(rows, num_sms);
+    FS2_VPT_DISPATCH(norm_vpt(D, threads),
+        if (bf16)
+            rms_norm_bwd_kernel<__nv_bfloat16, VPT><<<grid, threads, 0, st>>>(
+                static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
+                static_cast<const __nv_bfloat16*>(w), rstd, static_cast<__nv_bfloat16*>(dx), dw_part, rows, D);
+        else
+            rms_norm_bwd_kernel<float, VPT><<<grid, threads, 0, st>>>(
+                static_cast<const float*>(dy), static_cast<const float*>(x), static_cast<const float*>(w), rstd,
+                static_cast<float*>(dx), dw_part, rows, D))
+    reduce_partials_kernel<<<(D + 255) / 256, 256, 0, st>>>(dw_part, dw, grid, D);
+}
+
+void layer_norm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int rows, int D,
+                    float eps, bool bf16, int num_sms, cudaStream_t st) {
+    const int threads = norm_block(D);
+    const int grid = rows < num_sms * 16 ? rows : num_sms * 16;
+    FS2_VPT_DISPATCH(norm_vpt(D, threads),
+        if (bf16)
+            layer_norm_fwd_kernel<__nv_bfloat16, VPT><<<grid, threads, 0, st>>>(
+                static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+                static_cast<const __nv_bfloat16*>(b), static_cast<__nv_bfloat16*>(y), mean, rstd, rows, D, eps);
+        else
+            layer_norm_fwd_kernel<float, VPT><<<grid, threads, 0, st>>>(
+                static_cast<const float*>(x), static_cast<const float*>(w), static_cast<const float*>(b),
+                static_cast<float*>(y), mean, rstd, rows, D, eps))
+}
+
+void layer_norm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx,
+                    float* dw_part, float* db_part, float* dw, float* db, int rows, int D, bool bf16, int num_sms,
+                    cudaStream_t st) {
+    const int threads = norm_block(D);
+    const int grid = norm_bwd_grid(rows, num_sms);
+    FS2_VPT_DISPATCH(norm_vpt(D, threads),
+        if (bf16)
+            layer_norm_bwd_kernel<__nv_bfloat16, VPT><<<grid, threads, 0, st>>>(
+                static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
+                static_cast<const __nv_bfloat16*>(w), mean, rstd, static_cast<__nv_bfloat16*>(dx), dw_part, db_part,
+                rows, D);
+        else
+            layer_norm_bwd_kernel<float, VPT><<<grid, threads, 0, st>>>(
+                static_cast<const float*>(dy), static_cast<const float*>(x), static_cast<const float*>(w), mean,
+                rstd, static_cast<float*>(dx), dw_part, db_part, rows, D))
+    reduce_partials_kernel<<<(D + 255) / 256, 256, 0, st>>>(dw_part, dw, grid, D);
+    reduce_partials_kernel<<<(D + 255) / 256, 256, 0, st>>>(db_part, db, grid, D);
+}
+
+void swiglu_fwd(const void* gu, void* y, size_t rows, int F, int num_sms, cudaStream_t st) {
+    const size_t work = rows * (F / 8);
+    swiglu_fwd_kernel<<<stream_grid(work, 256, num_sms), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(gu),
+                                                                        static_cast<__nv_bfloat16*>(y), rows, F);
+}
+
+void swiglu_bwd(const void* dy, const void* gu, void* dgu, size_t rows, int F, int num_sms, cudaStream_t st) {
+    const size_t work = rows * (F / 8);
+    swiglu_bwd_kernel<<<stream_grid(work, 256, num_sms), 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(gu),
+        static_cast<__nv_bfloat16*>(dgu), rows, F);
+}
+
+void rope_inplace(void* x, const float* freqs, const int* pos, size_t tokens, int heads, int D, size_t tstride,
+                  size_t hstride, int max_pos, bool inverse, int num_sms, cudaStream_t st) {
+    const size_t work = tokens * heads * (D / 8);
+    if (work == 0) return;
+    rope_kernel<<<stream_grid(work, 256, num_sms), 256, 0, st>>>(static_cast<__nv_bfloat16*>(x), freqs, pos, tokens,
+                                                                  heads, D, tstride, hstride, max_pos,
+                                                                  inverse ? -1.f : 1.f);
+}
+
+void ce_fwd_bwd(void* logits, const long long* targets, const float* mask, float* row_loss, int rows, int V,
+                int pad_idx, cudaStream_t st) {
+    if (rows == 0) return;
+    ce_fwd_bwd_kernel<<<rows, 1024, 0, st>>>(static_cast<__nv_bfloat16*>(logits), targets, mask, row_loss, V,
+                                             pad_idx);
+}
+
+void adamw(float* p, const void* g, bool g_bf16, float* m, float* v, void* low, size_t n, float lr, float beta1,
+           float beta2, float eps, float wd, int step, const float* grad_scale, int num_sms, cudaStream_t st) {
+    if (n == 0) return;
+    const float bc1 = 1.f - powf(beta1, static_cast<float>(step));
+    const float bc2 = 1.f - powf(beta2, static_cast<float>(step));
+    const int grid = stream_grid(n / 8 + 1, 256, num_sms);
+    if (g_bf16)
+        adamw_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p, static_cast<const __nv_bfloat16*>(g), m, v,
+                                                          static_cast<__nv_bfloat16*>(low), n, lr, beta1, beta2, eps,
+                                                          wd, bc1, sqrtf(bc2), grad_scale);
+    else
+        adamw_kernel<float><<<grid, 256, 0, st>>>(p, static_cast<const float*>(g), m, v,
+                                                  static_cast<__nv_bfloat16*>(low), n, lr, beta1, beta2, eps, wd, bc1,
+                                                  sqrtf(bc2), grad_scale);
+}
+
+void l2_norm_sq(const void* x, bool bf16, size_t n, float* out, int num_sms, cudaStream_t st) {
+    if (n == 0) return;
+    const int grid = stream_grid(n / 8 + 1, 512, num_sms);
+    if (bf16) l2_norm_sq_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>(static_cast<const __nv_bfloat16*>(x), n, out);
+    else l2_norm_sq_kernel<float><<<grid, 512, 0, st>>>(static_cast<const float*>(x), n, out);
+}
+
+void scale_inplace(void* x, bool bf16, size_t n, const float* scale, int num_sms, cudaStream_t st) {
+    if (n == 0) return;
+    const int grid = stream_grid(n / 8 + 1, 256, num_sms);
+    if (bf16) scale_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<__nv_bfloat16*>(x), n, scale);
+    else scale_kernel<float><<<grid, 256, 0, st>>>(static_cast<float*>(x), n, scale);
+}
+
+}  // namespace fs2

@@ -1,0 +1,32 @@
+// Host launchers of the bandwidth-bound kernels in elementwise.cu.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+
+namespace fs2 {
+
+int norm_bwd_grid(int rows, int num_sms);
+
+void rms_norm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int D, float eps, bool bf16,
+                  int num_sms, cudaStream_t st);
+void rms_norm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw_part,
+                  float* dw, int rows, int D, bool bf16, int num_sms, cudaStream_t st);
+void layer_norm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int rows, int D,
+                    float eps, bool bf16, int num_sms, cudaStream_t st);
+void layer_norm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx,
+                    float* dw_part, float* db_part, float* dw, float* db, int rows, int D, bool bf16, int num_sms,
+                    cudaStream_t st);
+void swiglu_fwd(const void* gu, void* y, size_t rows, int F, int num_sms, cudaStream_t st);
+void swiglu_bwd(const void* dy, const void* gu, void* dgu, size_t rows, int F, int num_sms, cudaStream_t st);
+void rope_inplace(void* x, const float* freqs, const int* pos, size_t tokens, int heads, int D, size_t tstride,
+                  size_t hstride, int max_pos, bool inverse, int num_sms, cudaStream_t st);
+void ce_fwd_bwd(void* logits, const long long* targets, const float* mask, float* row_loss, int rows, int V,
+                int pad_idx, cudaStream_t st);
+void adamw(float* p, const void* g, bool g_bf16, float* m, float* v, void* low, size_t n, float lr, float beta1,
+           float beta2, float eps, float wd, int step, const float* grad_scale, int num_sms, cudaStream_t st);
+void l2_norm_sq(const void* x, bool bf16, size_t n, float* out, int num_sms, cudaStream_t st);
+void scale_inplace(void* x, bool bf16, size_t n, const float* scale, int num_sms, cudaStream_t st);
+
+}  // namespace fs2

@@ -1,0 +1,417 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a:
+//
+//   TMA (cp.async.bulk.tensor) -> 128B-swizzled shared memory -> tcgen05.mma
+//   (operands from smem descriptors, fp32 accumulators in TMEM) -> tcgen05.ld
+//   -> swizzled staging tile -> TMA store (or TMA reduce-add for accumulation).
+//
+// One CTA per SM, 192 threads:
+//   warp 0      : TMA producer (one elected lane)
+//   warp 1      : TMEM allocator + MMA issuer (one elected lane)
+//   warps 2..5  : epilogue; warp w owns TMEM lanes [32*(w%4), 32*(w%4)+32)
+//
+// CTA tile 128x256, K block 64 (one 128-byte swizzle row), 4 smem stages
+// (48 KB each) and a double-buffered accumulator (2 x 256 TMEM columns), so the
+// epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Operand layouts. C[M,N] = A * B^T with
+//   K-major A  : memory [M, K] row-major          (a_mn = false)
+//   MN-major A : memory [K, M] row-major          (a_mn = true)
+//   K-major B  : memory [N, K] row-major          (b_mn = false)
+//   MN-major B : memory [K, N] row-major          (b_mn = true)
+// which covers forward (x W^T), dgrad (dy W) and wgrad (dy^T x) of a linear
+// layer without a transpose pass.
+//
+// Every barrier wait is bounded (2 s); a wait that gives up records a code in
+// a host-visible status word, raises a CTA-wide abort flag, and all roles fall
+// through to the common teardown that frees TMEM.
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+
+#include "common.cuh"
+#include "gemm_tcgen05.h"
+
+namespace fs2 {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;            // 16 KB
+constexpr int B_BYTES = BN * BK * 2;            // 32 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;  // 48 KB
+constexpr int EPI_BYTES = 128 * 128;            // 128 rows x 128 B
+constexpr int MN_BLOCK_BYTES = 64 * 128;        // one [64 k-rows][64 mn] TMA box
+constexpr int BAR_BYTES = 256;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * EPI_BYTES + BAR_BYTES + 1024;
+constexpr int TMEM_COLS = 512;
+constexpr int NUM_THREADS = 192;
+constexpr int GROUP_M = 16;
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
+
+static_assert(SMEM_BYTES <= 232448, "shared memory budget of one CTA exceeded");
+
+__device__ __forceinline__ uint32_t make_idesc(bool a_mn, bool b_mn) {
+    uint32_t d = 0;
+    d |= 1u << 4;                         // D format: f32
+    d |= 1u << 7;                         // A format: bf16
+    d |= 1u << 10;                        // B format: bf16
+    d |= (a_mn ? 1u : 0u) << 15;          // A major: 0 = K, 1 = MN
+    d |= (b_mn ? 1u : 0u) << 16;          // B major
+    d |= static_cast<uint32_t>(BN >> 3) << 17;
+    d |= static_cast<uint32_t>(BM >> 4) << 24;
+    return d;
+}
+
+// Named barrier over the 128 epilogue threads that also ORs a predicate.
+__device__ __forceinline__ bool epi_bar_or(bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        "setp.ne.u32 p, %1, 0;\n\t"
+        "barrier.cta.red.or.pred q, 1, 128, p;\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t"
+        "}"
+        : "=r"(r)
+        : "r"(static_cast<uint32_t>(pred))
+        : "memory");
+    return r != 0;
+}
+
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("barrier.cta.sync 1, 128;" ::: "memory"); }
+
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_tile, int& n_tile) {
+    const int per_group = GROUP_M * num_n;
+    const int g = t / per_group;
+    const int first_m = g * GROUP_M;
+    const int gsize = min(GROUP_M, num_m - first_m);
+    const int r = t - g * per_group;
+    m_tile = first_m + r % gsize;
+    n_tile = r / gsize;
+}
+
+template <bool A_MN, bool B_MN, bool OUT_F32>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+            const __grid_constant__ CUtensorMap tma_c, int M, int N, int K, int accumulate, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* smem = smem_raw + (base - raw);
+
+    const uint32_t epi_base = base + STAGES * STAGE_BYTES;
+    uint8_t* bar_ptr = smem + STAGES * STAGE_BYTES + 2 * EPI_BYTES;
+    const uint32_t bar_base = smem_u32(bar_ptr);
+    // barrier slots (8 B each): full[4] empty[4] tmem_full[2] tmem_empty[2]
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_ptr + 8 * (2 * STAGES + 4));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_ptr + 8 * (2 * STAGES + 4) + 8);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    const int num_m = (M + BM - 1) / BM;
+    const int num_n = (N + BN - 1) / BN;
+    const int num_tiles = num_m * num_n;
+    const int num_kb = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 128);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tmap(&tma_a);
+        prefetch_tmap(&tma_b);
+        prefetch_tmap(&tma_c);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                int mt, nt;
+                tile_coords(t, num_m, num_n, mt, nt);
+                const int m0 = mt * BM, n0 = nt * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
+                        if (!*abort_flag) report_status(status, kStatusTimeout | (1 << 8));
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t a_s = base + stage * STAGE_BYTES;
+                    const uint32_t b_s = a_s + A_BYTES;
+                    const uint32_t fb = full_bar(stage);
+                    mbar_arrive_expect_tx(fb, STAGE_BYTES);
+                    const int k0 = kb * BK;
+                    if constexpr (!A_MN) {
+                        tma_load_2d(a_s, &tma_a, fb, k0, m0);
+                    } else {
+#pragma unroll
+                        for (int h = 0; h < BM / 64; ++h) tma_load_2d(a_s + h * MN_BLOCK_BYTES, &tma_a, fb, m0 + h * 64, k0);
+                    }
+                    if constexpr (!B_MN) {
+                        tma_load_2d(b_s, &tma_b, fb, k0, n0);
+                    } else {
+#pragma unroll
+                        for (int h = 0; h < BN / 64; ++h) tma_load_2d(b_s + h * MN_BLOCK_BYTES, &tma_b, fb, n0 + h * 64, k0);
+                    }
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc(A_MN, B_MN);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                if (!mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
+                    if (!*abort_flag) report_status(status, kStatusTimeout | (2 << 8));
+                    *abort_flag = 1;
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait_bounded(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
+                        if (!*abort_flag) report_status(status, kStatusTimeout | (3 << 8));
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const uint32_t a_s = base + stage * STAGE_BYTES;
+                    const uint32_t b_s = a_s + A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        uint64_t da, db;
+                        if constexpr (!A_MN) da = make_smem_desc(a_s + k * UMMA_K * 2, 16, 1024);
+                        else da = make_smem_desc(a_s + k * UMMA_K * 128, MN_BLOCK_BYTES, 1024);
+                        if constexpr (!B_MN) db = make_smem_desc(b_s + k * UMMA_K * 2, 16, 1024);
+                        else db = make_smem_desc(b_s + k * UMMA_K * 128, MN_BLOCK_BYTES, 1024);
+                        umma_bf16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(empty_bar(stage));
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                umma_commit(tfull_bar(acc));
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1u;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue
+        const int q = warp & 3;                       // TMEM lane quadrant of this warp
+        const int row = q * 32 + lane;                // row inside the CTA tile
+        const bool leader = (threadIdx.x == 64);      // first epilogue thread issues the stores
+        constexpr int CHUNK_COLS = OUT_F32 ? 32 : 64;
+        constexpr int NCHUNK = BN / CHUNK_COLS;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        int buf = 0;
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+            int mt, nt;
+            tile_coords(t, num_m, num_n, mt, nt);
+            const int m0 = mt * BM, n0 = nt * BN;
+            const bool got = mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS);
+            if (epi_bar_or(!got)) {
+                if (leader && !*abort_flag) report_status(status, kStatusTimeout | (4 << 8));
+                *abort_flag = 1;
+                break;
+            }
+            tcgen05_fence_after();
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
+#pragma unroll 1
+            for (int c = 0; c < NCHUNK; ++c) {
+                const int col0 = c * CHUNK_COLS;
+                if (n0 + col0 >= N) break;  // uniform over the CTA
+                if (leader) tma_wait_group_read<1>();
+                epi_bar_sync();
+                const uint32_t sbuf = epi_base + buf * EPI_BYTES;
+                const uint32_t srow = sbuf + row * 128;
+                if constexpr (OUT_F32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(t_row + col0, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const uint32_t dst = srow + (((j ^ (row & 7)) & 7) << 4);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v[4 * j]),
+                                     "r"(v[4 * j + 1]), "r"(v[4 * j + 2]), "r"(v[4 * j + 3])
+                                     : "memory");
+                    }
+                } else {
+                    uint32_t v[64];
+                    tmem_ld_32x32(t_row + col0, v);
+                    tmem_ld_32x32(t_row + col0 + 32, v + 32);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        uint32_t p[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[8 * j + 2 * e]),
+                                                                      __uint_as_float(v[8 * j + 2 * e + 1]));
+                            p[e] = *reinterpret_cast<uint32_t*>(&h);
+                        }
+                        const uint32_t dst = srow + (((j ^ (row & 7)) & 7) << 4);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(p[0]), "r"(p[1]),
+                                     "r"(p[2]), "r"(p[3])
+                                     : "memory");
+                    }
+                }
+                fence_proxy_async_smem();
+                epi_bar_sync();
+                if (leader) {
+                    if (accumulate) tma_reduce_add_2d(&tma_c, sbuf, n0 + col0, m0);
+                    else tma_store_2d(&tma_c, sbuf, n0 + col0, m0);
+                    tma_commit_group();
+                }
+                buf ^= 1;
+            }
+            tcgen05_fence_before();
+            mbar_arrive(tempty_bar(acc));
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1u;
+        }
+        if (leader) tma_wait_group<0>();
+    }
+
+    // -------------------------------------------------------------- teardown
+    __syncthreads();
+    if (*abort_flag) {
+        // Give copies that were already in flight time to land before the CTA retires.
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+        __syncthreads();
+    }
+    tcgen05_fence_after();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------- host side
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode_fn() {
+    static EncodeFn fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres);
+        if (e != cudaSuccess || p == nullptr) return nullptr;
+        fn = reinterpret_cast<EncodeFn>(p);
+    }
+    return fn;
+}
+
+// 2-D row-major tensor [rows, cols] of `elem_bytes` elements; box [box_rows, box_cols].
+thread_local char g_tmap_err[256];
+
+bool make_tmap(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt, int elem_bytes, uint64_t rows, uint64_t cols,
+               uint32_t box_rows, uint32_t box_cols) {
+    EncodeFn fn = get_encode_fn();
+    if (fn == nullptr) {
+        snprintf(g_tmap_err, sizeof(g_tmap_err), "cuTensorMapEncodeTiled entry point not found");
+        return false;
+    }
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * static_cast<uint64_t>(elem_bytes)};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(m, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        snprintf(g_tmap_err, sizeof(g_tmap_err),
+                 "cuTensorMapEncodeTiled failed with CUresult %d (ptr %p, rows %llu, cols %llu, elem %d B, box %ux%u)",
+                 static_cast<int>(r), ptr, static_cast<unsigned long long>(rows),
+                 static_cast<unsigned long long>(cols), elem_bytes, box_rows, box_cols);
+        return false;
+    }
+    return true;
+}
+
+template <bool A_MN, bool B_MN, bool OUT_F32>
+cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, int M, int N, int K,
+                   int accumulate, int* status, int num_sms, cudaStream_t stream) {
+    auto kern = gemm_kernel<A_MN, B_MN, OUT_F32>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    const int num_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int grid = num_tiles < num_sms ? num_tiles : num_sms;
+    kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tc, M, N, K, accumulate, status);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+const char* gemm_bf16_tcgen05(const void* a, const void* b, void* c, int M, int N, int K, bool a_mn, bool b_mn,
+                              bool out_f32, bool accumulate, int* status, int num_sms, cudaStream_t stream) {
+    CUtensorMap ta, tb, tc;
+    bool ok = true;
+    g_tmap_err[0] = 0;
+    if (!a_mn) ok = ok && make_tmap(&ta, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, BM, BK);
+    else ok = ok && make_tmap(&ta, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, BK, 64);
+    if (!b_mn) ok = ok && make_tmap(&tb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, BN, BK);
+    else ok = ok && make_tmap(&tb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, BK, 64);
+    if (out_f32) ok = ok && make_tmap(&tc, c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, M, N, 128, 32);
+    else ok = ok && make_tmap(&tc, c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, 128, 64);
+    if (!ok) return g_tmap_err;
+    cudaError_t e;
+    const int acc = accumulate ? 1 : 0;
+#define FS2_LAUNCH(AM, BMN, F32) e = launch<AM, BMN, F32>(ta, tb, tc, M, N, K, acc, status, num_sms, stream)
+    if (!a_mn && !b_mn) { if (out_f32) FS2_LAUNCH(false, false, true); else FS2_LAUNCH(false, false, false); }
+    else if (!a_mn && b_mn) { if (out_f32) FS2_LAUNCH(false, true, true); else FS2_LAUNCH(false, true, false); }
+    else if (a_mn && !b_mn) { if (out_f32) FS2_LAUNCH(true, false, true); else FS2_LAUNCH(true, false, false); }
+    else { if (out_f32) FS2_LAUNCH(true, true, true); else FS2_LAUNCH(true, true, false); }
+#undef FS2_LAUNCH
+    if (e != cudaSuccess) return cudaGetErrorString(e);
+    return nullptr;
+}
+
+}  // namespace fs2

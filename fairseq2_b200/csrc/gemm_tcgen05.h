@@ -1,0 +1,16 @@
+// Host entry point of the tcgen05 bf16 GEMM (see gemm_tcgen05.cu).
+#pragma once
+
+#include <cuda_runtime.h>
+
+namespace fs2 {
+
+// C[M,N] (+)= A * B^T. `a` is [M,K] (or [K,M] when a_mn), `b` is [N,K] (or
+// [K,N] when b_mn), `c` is bf16 or fp32 [M,N]; all row-major, 16-byte aligned
+// bases and row pitches. `status` points to host-mapped memory that receives a
+// non-zero code if a bounded wait inside the kernel gave up.
+// Returns nullptr on success, else a static error string.
+const char* gemm_bf16_tcgen05(const void* a, const void* b, void* c, int M, int N, int K, bool a_mn, bool b_mn,
+                              bool out_f32, bool accumulate, int* status, int num_sms, cudaStream_t stream);
+
+}  // namespace fs2

@@ -80,8 +80,10 @@ class _QKVRopeAttnFn(torch.autograd.Function):
     def forward(ctx, qkv, freqs, positions, begins, lens, max_len, causal, scale, H, Hkv):  # type: ignore[override]
         ext = require_ext()
         if freqs is not None:
+            # The producer of `qkv` (the merged projection) does not need its own
+            # output in backward, so rotating it in place is safe; the raw kernel
+            # call bypasses autograd's version counters by construction.
             ext.rope_inplace(qkv[:, : H + Hkv], freqs, positions, False)
-            ctx.mark_dirty(qkv)
         q, k, v = qkv[:, :H], qkv[:, H:H + Hkv], qkv[:, H + Hkv:]
         out, lse = ext.attn_fwd(q, k, v, begins, lens, begins, lens, max_len, max_len, causal, scale)
         ctx.save_for_backward(qkv, out, lse, begins, lens, freqs, positions)

@@ -1,0 +1,280 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 formulation of
+the same op (the oracle lives next to each op as ``*_reference``)."""
+from __future__ import annotations
+
+import math
+
+import pytest
+import torch
+
+from fairseq2_b200.ops import require_ext
+from fairseq2_b200.ops.activation import swiglu, swiglu_reference
+from fairseq2_b200.ops.attention import attention_reference, qkv_rope_attention, varlen_attention
+from fairseq2_b200.ops.cross_entropy import cross_entropy_reference, fused_linear_cross_entropy
+from fairseq2_b200.ops.gemm import gemm, gemm_reference, linear
+from fairseq2_b200.ops.norm import layer_norm, rms_norm, rms_norm_reference
+from fairseq2_b200.ops.optim import (adamw_reference, multi_tensor_adamw, multi_tensor_l2_norm_sq,
+                                     multi_tensor_scale)
+from fairseq2_b200.ops.rope import apply_rope, rope_reference
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _rel_err(a: torch.Tensor, b: torch.Tensor) -> float:
+    a, b = a.float(), b.float()
+    return float((a - b).norm() / b.norm().clamp(min=1e-12))
+
+
+@pytest.fixture(autouse=True)
+def _status():
+    ext = require_ext()
+    ext.reset_status()
+    yield
+    torch.cuda.synchronize()
+    assert ext.read_status() == 0, f"kernel status word = {ext.read_status():#x}"
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 256), (200, 264, 72), (1024, 1536, 1024), (16, 24, 40)])
+def test_gemm_layouts(a_mn: bool, b_mn: bool, shape: tuple[int, int, int]) -> None:
+    M, N, K = shape
+    torch.manual_seed(0)
+    a = torch.randn((K, M) if a_mn else (M, K), device=DEV, dtype=torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), device=DEV, dtype=torch.bfloat16)
+    ref = gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+    out = torch.empty((M, N), device=DEV, dtype=torch.bfloat16)
+    require_ext().gemm_bf16(a, b, out, a_mn, b_mn, False)
+    assert _rel_err(out, ref) < 5e-3
+    out32 = torch.empty((M, N), device=DEV, dtype=torch.float32)
+    require_ext().gemm_bf16(a, b, out32, a_mn, b_mn, False)
+    assert _rel_err(out32, ref) < 1e-4
+
+
+def test_gemm_accumulate() -> None:
+    torch.manual_seed(1)
+    M, N, K = 384, 520, 320
+    a = torch.randn((M, K), device=DEV, dtype=torch.bfloat16)
+    b = torch.randn((N, K), device=DEV, dtype=torch.bfloat16)
+    base = torch.randn((M, N), device=DEV, dtype=torch.float32)
+    out = base.clone()
+    require_ext().gemm_bf16(a, b, out, False, False, True)
+    ref = base + gemm_reference(a, b, out_dtype=torch.float32)
+    assert _rel_err(out, ref) < 1e-4
+    outb = base.to(torch.bfloat16)
+    require_ext().gemm_bf16(a, b, outb, False, False, True)
+    assert _rel_err(outb, ref) < 1e-2
+
+
+def test_gemm_large_persistent() -> None:
+    """More tiles than SMs: exercises the persistent loop, both accumulators and every stage phase."""
+    torch.manual_seed(2)
+    M, N, K = 4096, 4096, 2048
+    a = torch.randn((M, K), device=DEV, dtype=torch.bfloat16)
+    b = torch.randn((N, K), device=DEV, dtype=torch.bfloat16)
+    out = gemm(a, b)
+    ref = torch.matmul(a, b.t())
+    assert _rel_err(out, ref) < 5e-3
+
+
+def test_linear_autograd() -> None:
+    torch.manual_seed(3)
+    x = torch.randn((4, 96, 256), device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = torch.randn((384, 256), device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y = linear(x, w)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_(True)
+    wr = w.detach().float().requires_grad_(True)
+    yr = torch.nn.functional.linear(xr, wr)
+    yr.backward(g.float())
+    assert _rel_err(y, yr) < 5e-3
+    assert _rel_err(x.grad, xr.grad) < 5e-3
+    assert _rel_err(w.grad, wr.grad) < 5e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rows,D", [(7, 64), (300, 4096), (33, 1024), (5, 8192)])
+def test_rms_norm(dtype: torch.dtype, rows: int, D: int) -> None:
+    torch.manual_seed(4)
+    x = torch.randn((rows, D), device=DEV, dtype=dtype, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(D, device=DEV)).to(dtype).requires_grad_(True)
+    y = rms_norm(x, (D,), w, 1e-5)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    yr = rms_norm_reference(xr, wr, 1e-5)
+    yr.backward(g.float())
+    tol = 1e-2 if dtype == torch.bfloat16 else 1e-5
+    assert _rel_err(y, yr) < tol
+    assert _rel_err(x.grad, xr.grad) < tol
+    assert _rel_err(w.grad, wr.grad) < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_layer_norm(dtype: torch.dtype) -> None:
+    torch.manual_seed(5)
+    rows, D = 130, 1024
+    x = torch.randn((rows, D), device=DEV, dtype=dtype, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(D, device=DEV)).to(dtype).requires_grad_(True)
+    b = (0.1 * torch.randn(D, device=DEV)).to(dtype).requires_grad_(True)
+    y = layer_norm(x, (D,), w, b, 1e-5)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr, br = (t.detach().float().requires_grad_(True) for t in (x, w, b))
+    yr = torch.nn.functional.layer_norm(xr, (D,), wr, br, 1e-5)
+    yr.backward(g.float())
+    tol = 1e-2 if dtype == torch.bfloat16 else 1e-5
+    assert _rel_err(y, yr) < tol
+    assert _rel_err(x.grad, xr.grad) < tol
+    assert _rel_err(w.grad, wr.grad) < tol
+    assert _rel_err(b.grad, br.grad) < tol
+
+
+def test_swiglu() -> None:
+    torch.manual_seed(6)
+    gu = torch.randn((77, 2 * 1024), device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y = swiglu(gu)
+    g = torch.randn_like(y)
+    y.backward(g)
+    gr = gu.detach().float().requires_grad_(True)
+    yr = swiglu_reference(gr)
+    yr.backward(g.float())
+    assert _rel_err(y, yr) < 1e-2
+    assert _rel_err(gu.grad, gr.grad) < 1e-2
+
+
+def _freqs(L: int, D: int, theta: float = 10000.0) -> torch.Tensor:
+    inv = 1.0 / (theta ** (torch.arange(0, D, 2, device=DEV, dtype=torch.float32) / D))
+    ang = torch.outer(torch.arange(L, device=DEV, dtype=torch.float32), inv)
+    return torch.stack((ang.cos(), ang.sin()), dim=-1).contiguous()
+
+
+def test_rope() -> None:
+    torch.manual_seed(7)
+    T, H, D = 50, 6, 128
+    x = torch.randn((T, H, D), device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    pos = torch.arange(T, device=DEV, dtype=torch.int32) % 23
+    pos[-3:] = -1
+    f = _freqs(64, D)
+    y = apply_rope(x, f, pos)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_(True)
+    yr = rope_reference(xr, f, pos)
+    yr.backward(g.float())
+    assert _rel_err(y, yr) < 1e-2
+    assert _rel_err(x.grad, xr.grad) < 1e-2
+
+
+def _seqs(lens: list[int]):
+    b = [0]
+    for l in lens:
+        b.append(b[-1] + l)
+    return (torch.tensor(b[:-1], device=DEV, dtype=torch.int32), torch.tensor(lens, device=DEV, dtype=torch.int32))
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("D,H,Hkv", [(128, 8, 2), (64, 4, 4)])
+@pytest.mark.parametrize("lens", [[5], [64, 128], [1, 37, 200, 130], [300, 77]])
+def test_attention_fwd_bwd(causal: bool, D: int, H: int, Hkv: int, lens: list[int]) -> None:
+    torch.manual_seed(8)
+    T = sum(lens)
+    q = torch.randn((T, H, D), device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn((T, Hkv, D), device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn((T, Hkv, D), device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    b, l = _seqs(lens)
+    out = varlen_attention(q, k, v, b, l, b, l, max(lens), max(lens), causal=causal)
+    g = torch.randn_like(out)
+    out.backward(g)
+    qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    ref = attention_reference(qr, kr, vr, b, l, b, l, causal)
+    ref.backward(g.float())
+    assert _rel_err(out, ref) < 1e-2
+    assert _rel_err(q.grad, qr.grad) < 2e-2
+    assert _rel_err(k.grad, kr.grad) < 2e-2
+    assert _rel_err(v.grad, vr.grad) < 2e-2
+
+
+def test_attention_cross_lengths() -> None:
+    """Lk > Lq (prefill against a cache): bottom-right aligned causal mask."""
+    torch.manual_seed(9)
+    H, Hkv, D = 4, 2, 128
+    ql, kl = [3, 70], [40, 133]
+    q = torch.randn((sum(ql), H, D), device=DEV, dtype=torch.bfloat16)
+    k = torch.randn((sum(kl), Hkv, D), device=DEV, dtype=torch.bfloat16)
+    v = torch.randn((sum(kl), Hkv, D), device=DEV, dtype=torch.bfloat16)
+    qb, qlt = _seqs(ql)
+    kb, klt = _seqs(kl)
+    out = varlen_attention(q, k, v, qb, qlt, kb, klt, max(ql), max(kl), causal=True)
+    ref = attention_reference(q.float(), k.float(), v.float(), qb, qlt, kb, klt, True)
+    assert _rel_err(out, ref) < 1e-2
+
+
+def test_qkv_rope_attention_fused() -> None:
+    torch.manual_seed(10)
+    H, Hkv, D = 8, 2, 128
+    lens = [100, 28, 129]
+    T = sum(lens)
+    qkv = torch.randn((T, H + 2 * Hkv, D), device=DEV, dtype=torch.bfloat16)
+    b, l = _seqs(lens)
+    pos = torch.cat([torch.arange(n, device=DEV, dtype=torch.int32) for n in lens])
+    f = _freqs(256, D)
+    leaf = qkv.clone().requires_grad_(True)
+    out = qkv_rope_attention(leaf * 1.0, f, pos, b, l, max(lens), num_heads=H, num_kv_heads=Hkv, causal=True)
+    g = torch.randn_like(out)
+    out.backward(g)
+    ref_leaf = qkv.detach().float().requires_grad_(True)
+    qr = rope_reference(ref_leaf[:, :H], f, pos)
+    kr = rope_reference(ref_leaf[:, H:H + Hkv], f, pos)
+    ref = attention_reference(qr, kr, ref_leaf[:, H + Hkv:], b, l, b, l, True)
+    ref.backward(g.float())
+    assert _rel_err(out, ref) < 1e-2
+    assert _rel_err(leaf.grad, ref_leaf.grad) < 2e-2
+
+
+def test_fused_linear_cross_entropy() -> None:
+    torch.manual_seed(11)
+    T, D, V = 300, 256, 1024
+    h = (0.5 * torch.randn((T, D), device=DEV)).to(torch.bfloat16).requires_grad_(True)
+    w = (0.05 * torch.randn((V, D), device=DEV)).to(torch.bfloat16).requires_grad_(True)
+    t = torch.randint(0, V, (T,), device=DEV)
+    t[5] = 7
+    mask = (torch.rand(T, device=DEV) > 0.3)
+    loss = fused_linear_cross_entropy(h, w, t, target_mask=mask, pad_idx=7, reduction="sum", chunk_size=128)
+    (loss * 0.5).backward()
+    hr, wr = h.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    lr = cross_entropy_reference(torch.nn.functional.linear(hr, wr), t, 7, target_mask=mask, reduction="sum")
+    (lr * 0.5).backward()
+    assert abs(float(loss) - float(lr)) / abs(float(lr)) < 5e-3
+    assert _rel_err(h.grad, hr.grad) < 2e-2
+    assert _rel_err(w.grad, wr.grad) < 2e-2
+
+
+@pytest.mark.parametrize("gdtype", [torch.bfloat16, torch.float32])
+def test_adamw_and_norm(gdtype: torch.dtype) -> None:
+    torch.manual_seed(12)
+    n = 100_003 - 3  # multiple of 8 keeps the flat views aligned
+    p = torch.randn(n, device=DEV)
+    g = torch.randn(n, device=DEV).to(gdtype)
+    m = torch.zeros(n, device=DEV)
+    v = torch.zeros(n, device=DEV)
+    low = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    pr, mr, vr = p.clone(), m.clone(), v.clone()
+    scale = torch.tensor(0.5, device=DEV)
+    for step in (1, 2, 3):
+        multi_tensor_adamw([p], [g], [m], [v], [low], lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1,
+                           step=step, grad_scale=scale)
+        adamw_reference(pr, g, mr, vr, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step,
+                        grad_scale=0.5)
+    assert _rel_err(p, pr) < 1e-5
+    assert _rel_err(m, mr) < 1e-5
+    assert _rel_err(v, vr) < 1e-5
+    assert _rel_err(low, pr) < 5e-3
+    nsq = multi_tensor_l2_norm_sq([g, p])
+    ref = g.float().pow(2).sum() + p.pow(2).sum()
+    assert abs(float(nsq) - float(ref)) / float(ref) < 1e-4
+    gc = g.clone()
+    multi_tensor_scale([gc], scale)
+    assert _rel_err(gc, g.float() * 0.5) < 5e-3
