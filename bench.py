@@ -1,0 +1,246 @@
+"""Headline benchmark: LLaMA-3-8B SFT training throughput (tokens/s over all GPUs).
+
+    python bench.py --gpus N --steps K --warmup W            # this framework
+    python bench.py --impl reference --gpus N ...            # unmodified fairseq2 from baseline/_ref
+
+Model/config: LLaMA-3-8B architecture (32 layers, dim 4096, 32/8 heads, FFN
+14336, vocab 128256), random init, packed sequences of 8192 tokens per GPU made
+of documents of 128-4096 tokens with per-document block-causal attention and a
+masked prompt prefix; bf16 compute with fp32 master weights and fp32 AdamW
+state, FSDP over N ranks, activation checkpointing off. Synthetic data.
+
+Two numbers are measured, each over exactly K steps after W warm-up steps:
+``value`` is timed on the device with CUDA events around steps whose inputs are
+already resident; ``e2e`` runs the same public training step but every step
+copies its inputs from pinned host memory and reads the loss back to the host.
+Each rank's inputs differ per step and exceed no cache assumptions: the working
+set of a step (weights + activations) is far larger than the 126 MB L2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+
+def _clock_sampler(stop: threading.Event, out: list[dict], gpu_index: int) -> None:
+    q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+    try:
+        proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "200",
+                                 "-i", str(gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+    except OSError:
+        return
+    assert proc.stdout is not None
+    try:
+        while not stop.is_set():
+            line = proc.stdout.readline()
+            if not line:
+                break
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 7:
+                try:
+                    out.append({"sm": float(parts[0]), "max": float(parts[1]), "power": float(parts[2]),
+                                "hw_slowdown": parts[3], "hw_thermal": parts[4], "sw_thermal": parts[5],
+                                "sw_power_cap": parts[6]})
+                except ValueError:
+                    pass
+    finally:
+        proc.terminate()
+
+
+def _summarize_clocks(samples: list[dict]) -> dict:
+    if not samples:
+        return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+    sm = sorted(s["sm"] for s in samples)
+    reasons = []
+    for key, name in (("hw_slowdown", "hw_slowdown"), ("hw_thermal", "hw_thermal_slowdown"),
+                      ("sw_thermal", "sw_thermal_slowdown"), ("sw_power_cap", "sw_power_cap")):
+        if any(s[key].lower().startswith("active") for s in samples):
+            reasons.append(name)
+    return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": samples[0]["max"], "reasons": reasons,
+            "samples": len(samples), "power_w_max": max(s["power"] for s in samples)}
+
+
+def run_ours(args: argparse.Namespace) -> None:
+    import numpy as np
+    import torch
+
+    from fairseq2_b200.datasets.synthetic import make_packed_sft_example
+    from fairseq2_b200.gang import (FakeGang, ProcessGroupGang, ReduceOperation, create_fsdp_gangs,
+                                    create_parallel_gangs)
+    from fairseq2_b200.models.llama import create_llama_model, get_llama_config
+    from fairseq2_b200.nn import BatchLayout
+    from fairseq2_b200.nn.data_parallel import DataParallelFacade
+    from fairseq2_b200.ops import require_ext
+    from fairseq2_b200.optim import AdamW
+    from fairseq2_b200.parallel.fsdp import FSDP
+    from fairseq2_b200.trainer import TrainStep, TrainUnit
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} does not match WORLD_SIZE {world}; launch with torch.distributed.run.")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    ext = require_ext()
+
+    root = FakeGang(device) if world == 1 else ProcessGroupGang.create_default_process_group(device)
+    gangs = create_fsdp_gangs(create_parallel_gangs(root, tp_size=1))
+
+    cfg = get_llama_config(args.model)
+    if args.layers is not None:          # debugging aid only; the JSON line marks such a run
+        cfg.num_layers = args.layers
+    seq_len = args.seq_len
+    torch.manual_seed(2)
+    with torch.device("meta"):
+        model = create_llama_model(cfg, gangs)
+    fsdp = FSDP(model, gangs, param_dtype=torch.bfloat16, fp32_reduce=True)
+    facade = DataParallelFacade(fsdp)
+    optimizer = AdamW(fsdp.parameters(), lr=1e-5, betas=(0.9, 0.95), weight_decay=0.1)
+
+    class SFTUnit(TrainUnit):
+        """Loss-masked next-token cross entropy over a packed batch (``lm.sft`` semantics)."""
+
+        @property
+        def model(self) -> DataParallelFacade:
+            return facade
+
+        def process_batch(self, batch, metric_bag=None):  # type: ignore[no-untyped-def]
+            tokens, mask, layout, num_targets = batch
+            loss = fsdp(tokens[:-1], layout, targets=tokens[1:], target_mask=mask, reduction="sum")
+            return loss, num_targets
+
+    step_fn = TrainStep(SFTUnit(), optimizer, gangs, max_grad_norm=1.0)
+
+    rng = np.random.default_rng(1234 + rank)
+    total = args.warmup + 2 * args.steps
+    examples = [make_packed_sft_example(rng, seq_len, cfg.vocab_size) for _ in range(total)]
+
+    def stage(ex):  # type: ignore[no-untyped-def]
+        tokens = ex.tokens.to(device, non_blocking=True)
+        mask = ex.target_mask.to(device, non_blocking=True)
+        layout = BatchLayout((seq_len,), ex.seq_lens, packed=True, device=device)
+        return tokens, mask, layout, ex.num_targets
+
+    def barrier() -> None:
+        if world > 1:
+            root.barrier()
+        torch.cuda.synchronize(device)
+
+    # ---- warm-up
+    for i in range(args.warmup):
+        loss, _ = step_fn([stage(examples[i])], i)
+    barrier()
+
+    # ---- device-timed region: inputs resident before the clock starts
+    staged = [stage(examples[args.warmup + i]) for i in range(args.steps)]
+    samples: list[dict] = []
+    stop = threading.Event()
+    sampler = threading.Thread(target=_clock_sampler, args=(stop, samples, local_rank), daemon=True)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    ext.reset_launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(args.steps):
+        loss, gnorm = step_fn([staged[i]], args.warmup + i)
+    ev1.record()
+    barrier()
+    launches = int(ext.launch_count())
+    dev_ms = ev0.elapsed_time(ev1)
+    del staged
+
+    # ---- end-to-end region: H2D of every step's inputs + D2H of its loss
+    barrier()
+    t0 = time.perf_counter()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    h2d = d2h = 0
+    last_loss = 0.0
+    for i in range(args.steps):
+        ex = examples[args.warmup + args.steps + i]
+        batch = stage(ex)
+        h2d = ex.tokens.numel() * 8 + ex.target_mask.numel() * 4 + (2 * len(ex.seq_lens) + 1 + seq_len) * 4
+        loss, gnorm = step_fn([batch], args.warmup + args.steps + i)
+        last_loss = float(loss.item())
+        d2h = 4
+    e1.record()
+    barrier()
+    e2e_ms = max((time.perf_counter() - t0) * 1e3, e0.elapsed_time(e1))
+    stop.set()
+    ext.check_status()
+
+    times = torch.tensor([dev_ms, e2e_ms], device=device, dtype=torch.float64)
+    if world > 1:
+        root.all_reduce(times, ReduceOperation.MAX)
+    dev_ms, e2e_ms = float(times[0]), float(times[1])
+    tokens_per_step = seq_len * world
+    value = tokens_per_step * args.steps / (dev_ms * 1e-3)
+    e2e_value = tokens_per_step * args.steps / (e2e_ms * 1e-3)
+
+    if rank == 0:
+        n_params = sum(u.shard_size for u in fsdp.all_units) * world
+        flops_per_token = 6 * 8.03e9 if args.model == "llama3_8b" and args.layers is None else None
+        out = {
+            "metric": "llama3_8b_fsdp_sft_tokens_per_second", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "impl": "fairseq2_b200",
+            "config": {"model": args.model if args.layers is None else f"{args.model}[layers={args.layers}]",
+                       "global_batch": world, "seq_len": seq_len, "parallelism": f"fsdp{world}",
+                       "packing": "documents 128-4096 tokens, block-causal, prompt-masked loss",
+                       "optimizer": "AdamW lr 1e-5 fp32 state, fp32 master weights, grad clip 1.0",
+                       "activation_checkpointing": False,
+                       "l2": "per-step working set (weights+activations) >> 126 MB L2; inputs differ every step"},
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": launches,
+            "clocks": _summarize_clocks(samples),
+            "final_loss": last_loss,
+            "peak_mem_gb": torch.cuda.max_memory_allocated(device) / 2**30,
+        }
+        if flops_per_token is not None:
+            out["model_tflops_per_gpu"] = flops_per_token * value / world / 1e12
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        root.close()
+
+
+def run_reference(args: argparse.Namespace) -> None:
+    from baseline.reference_arm import run_reference_arm
+
+    run_reference_arm(args)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="llama3_8b")
+    ap.add_argument("--seq-len", type=int, default=8192)
+    ap.add_argument("--layers", type=int, default=None, help="debugging only: truncates the model (result is not a valid benchmark)")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.layers is None:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -27,6 +27,12 @@ bool is_bf16(const Tensor& t) { return t.scalar_type() == at::kBFloat16; }
 
 bool aligned16(const Tensor& t) { return reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0; }
 
+// Number of kernels of this extension launched so far (host-side bookkeeping
+// that benchmarks use to report how much of a step runs on in-tree kernels).
+int64_t g_launches = 0;
+int64_t launch_count() { return g_launches; }
+void reset_launch_count() { g_launches = 0; }
+
 // ---------------------------------------------------------------- status word
 // One pinned, host-mapped int per process. Kernels store a non-zero code when a
 // bounded wait gives up; the host can poll it without touching the stream.
@@ -89,6 +95,7 @@ void gemm_bf16(const Tensor& a, const Tensor& b, Tensor& out, bool a_mn, bool b_
                                              static_cast<int>(N), static_cast<int>(K), a_mn, b_mn, f32, accumulate,
                                              status_dev_ptr(), num_sms(a), stream_of(a));
     TORCH_CHECK(err == nullptr, "gemm_bf16: ", err);
+    g_launches += 1;
 }
 
 // ---------------------------------------------------------------------- norms
@@ -104,6 +111,7 @@ std::tuple<Tensor, Tensor> rms_norm_fwd(const Tensor& x, const Tensor& w, double
     if (rows > 0)
         fs2::rms_norm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr<float>(), rows, D,
                           static_cast<float>(eps), is_bf16(x), num_sms(x), stream_of(x));
+    g_launches += 1;
     return {y, rstd};
 }
 
@@ -121,6 +129,7 @@ std::tuple<Tensor, Tensor> rms_norm_bwd(const Tensor& dy, const Tensor& x, const
         fs2::rms_norm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(),
                           part.data_ptr<float>(), dw.data_ptr<float>(), rows, D, is_bf16(x), num_sms(x),
                           stream_of(x));
+        g_launches += 2;
     }
     return {dx, dw};
 }
@@ -143,6 +152,7 @@ std::tuple<Tensor, Tensor, Tensor> layer_norm_fwd(const Tensor& x, const Tensor&
         fs2::layer_norm_fwd(x.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), mean.data_ptr<float>(),
                             rstd.data_ptr<float>(), rows, D, static_cast<float>(eps), is_bf16(x), num_sms(x),
                             stream_of(x));
+    g_launches += 1;
     return {y, mean, rstd};
 }
 
@@ -162,6 +172,7 @@ std::tuple<Tensor, Tensor, Tensor> layer_norm_bwd(const Tensor& dy, const Tensor
                             rstd.data_ptr<float>(), dx.data_ptr(), part[0].data_ptr<float>(),
                             part[1].data_ptr<float>(), dw.data_ptr<float>(), db.data_ptr<float>(), rows, D,
                             is_bf16(x), num_sms(x), stream_of(x));
+        g_launches += 3;
     }
     return {dx, dw, db};
 }
@@ -177,6 +188,7 @@ Tensor swiglu_fwd(const Tensor& gu) {
     if (rows > 0)
         fs2::swiglu_fwd(gu.data_ptr(), y.data_ptr(), static_cast<size_t>(rows), static_cast<int>(F), num_sms(gu),
                         stream_of(gu));
+    g_launches += 1;
     return y;
 }
 
@@ -189,6 +201,7 @@ Tensor swiglu_bwd(const Tensor& dy, const Tensor& gu) {
     if (gu.size(0) > 0)
         fs2::swiglu_bwd(dy.data_ptr(), gu.data_ptr(), dgu.data_ptr(), static_cast<size_t>(gu.size(0)),
                         static_cast<int>(dy.size(1)), num_sms(gu), stream_of(gu));
+    g_launches += 1;
     return dgu;
 }
 
@@ -207,6 +220,7 @@ void rope_inplace(Tensor x, const Tensor& freqs, const Tensor& pos, bool inverse
                       static_cast<int>(x.size(1)), D, static_cast<size_t>(x.stride(0)),
                       static_cast<size_t>(x.stride(1)), static_cast<int>(freqs.size(0)), inverse, num_sms(x),
                       stream_of(x));
+    g_launches += 1;
 }
 
 // -------------------------------------------------------------- cross-entropy
@@ -231,6 +245,7 @@ void ce_fwd_bwd_inplace(Tensor logits, const Tensor& targets, const std::optiona
     fs2::ce_fwd_bwd(logits.data_ptr(), reinterpret_cast<const long long*>(targets.data_ptr<int64_t>()), mptr,
                     row_loss.data_ptr<float>(), rows, static_cast<int>(logits.size(1)), static_cast<int>(pad_idx),
                     stream_of(logits));
+    g_launches += 1;
     loss.add_(row_loss.sum());
 }
 
@@ -289,6 +304,7 @@ std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tens
     p.lse = lse.data_ptr<float>();
     const char* err = fs2::attn_forward(p, stream_of(q));
     TORCH_CHECK(err == nullptr, "attn_fwd: ", err);
+    g_launches += 1;
     return {out, lse};
 }
 
@@ -322,6 +338,7 @@ void attn_bwd_out(const Tensor& dout, const Tensor& q, const Tensor& k, const Te
     p.delta = delta.data_ptr<float>();
     const char* err = fs2::attn_backward(p, stream_of(q));
     TORCH_CHECK(err == nullptr, "attn_bwd: ", err);
+    g_launches += 3;
 }
 
 std::tuple<Tensor, Tensor, Tensor> attn_bwd(const Tensor& dout, const Tensor& q, const Tensor& k, const Tensor& v,
@@ -372,6 +389,7 @@ void multi_tensor_adamw(const std::vector<Tensor>& masters, const std::vector<Te
                    static_cast<size_t>(p.numel()), static_cast<float>(lr), static_cast<float>(beta1),
                    static_cast<float>(beta2), static_cast<float>(eps), static_cast<float>(wd), static_cast<int>(step),
                    gs, num_sms(p), stream_of(p));
+        g_launches += 1;
     }
 }
 
@@ -384,6 +402,7 @@ Tensor multi_tensor_l2_norm_sq(const std::vector<Tensor>& ts) {
                     "multi_tensor_l2_norm_sq: tensors must be contiguous, 16-byte aligned bf16/fp32");
         fs2::l2_norm_sq(t.data_ptr(), is_bf16(t), static_cast<size_t>(t.numel()), out.data_ptr<float>(), num_sms(t),
                         stream_of(t));
+        g_launches += 1;
     }
     return out;
 }
@@ -397,6 +416,7 @@ void multi_tensor_scale(const std::vector<Tensor>& ts, const Tensor& scale) {
         c10::cuda::CUDAGuard guard(t.device());
         fs2::scale_inplace(t.data_ptr(), is_bf16(t), static_cast<size_t>(t.numel()), scale.data_ptr<float>(),
                            num_sms(t), stream_of(t));
+        g_launches += 1;
     }
 }
 
@@ -419,6 +439,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("multi_tensor_adamw", &multi_tensor_adamw);
     m.def("multi_tensor_l2_norm_sq", &multi_tensor_l2_norm_sq);
     m.def("multi_tensor_scale", &multi_tensor_scale);
+    m.def("launch_count", &launch_count);
+    m.def("reset_launch_count", &reset_launch_count);
     m.def("check_status", &check_status, "Raises if a kernel recorded a bounded-wait failure.");
     m.def("read_status", &read_status);
     m.def("reset_status", &reset_status);

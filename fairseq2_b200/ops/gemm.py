@@ -82,6 +82,7 @@ class _LinearFn(torch.autograd.Function):
             x2 = x2.contiguous()
         ctx.save_for_backward(x2, weight)
         ctx.x_shape = x.shape
+        ctx.weight_ref = weight if hasattr(weight, "grad_sink") else None
         y = gemm(x2, weight)
         return y.view(*x.shape[:-1], weight.shape[0])
 
@@ -95,7 +96,14 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = gemm(dy2, weight, b_mn=True).view(ctx.x_shape)
         if ctx.needs_input_grad[1]:
-            dw = gemm(dy2, x2, a_mn=True, b_mn=True)
+            w = ctx.weight_ref
+            sink = getattr(w, "grad_sink", None) if w is not None else None
+            if sink is not None and sink.is_contiguous():
+                # data-parallel wrappers point `grad_sink` into their flat gradient buffer
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=sink, accumulate=bool(getattr(w, "grad_sink_filled", False)))
+                w.grad_sink_filled = True
+            else:
+                dw = gemm(dy2, x2, a_mn=True, b_mn=True)
         return dx, dw
 
 

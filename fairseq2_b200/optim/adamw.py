@@ -1,0 +1,161 @@
+"""AdamW with a fused sm_100a step and first-class support for flat, sharded
+parameter units.
+
+Plain parameters are updated by the multi-tensor kernel of ``ops.optim`` (or
+the PyTorch formulation on CPU). Parameters that are dim-0 shards of an FSDP
+unit (they carry ``_fs2_unit``) are updated *per unit* with ONE launch over the
+unit's flat fp32 master / moment buffers, reading the unit's reduced gradient
+shard and refreshing its bf16 shard in the same pass -- the optimizer half of
+worklist row W3. ``grad_scale`` (loss normalisation x clip coefficient) is a
+device scalar consumed inside the kernel.
+
+Hyper-parameters and state layout (``step``, ``exp_avg``, ``exp_avg_sq`` per
+parameter) follow ``torch.optim.AdamW`` so optimizer state dicts keep the
+reference checkpoint format (fairseq2 ``recipe/internal/optim.py:61-72``).
+"""
+from __future__ import annotations
+
+from typing import Any, Callable, Iterable
+
+import torch
+from torch import Tensor
+from torch.optim import Optimizer
+
+from fairseq2_b200.ops.optim import adamw_reference, multi_tensor_adamw
+
+
+class AdamW(Optimizer):
+    def __init__(self, params: Iterable[Any], lr: float = 1e-3, betas: tuple[float, float] = (0.9, 0.999),
+                 eps: float = 1e-8, weight_decay: float = 0.0, *, impl: str = "auto") -> None:
+        if lr < 0.0:
+            raise ValueError(f"`lr` must be non-negative, but is {lr} instead.")
+        if not 0.0 <= betas[0] < 1.0 or not 0.0 <= betas[1] < 1.0:
+            raise ValueError(f"`betas` must be in [0, 1), but are {betas} instead.")
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
+        self.impl = impl
+        self._unit_state: dict[int, tuple[Tensor, Tensor]] = {}
+
+    def _unit_moments(self, unit: Any) -> tuple[Tensor, Tensor]:
+        st = self._unit_state.get(id(unit))
+        if st is None:
+            st = (torch.zeros_like(unit.master), torch.zeros_like(unit.master))
+            self._unit_state[id(unit)] = st
+        return st
+
+    def _init_state(self, p: Tensor) -> dict[str, Any]:
+        st = self.state[p]
+        if not st:
+            unit = getattr(p, "_fs2_unit", None)
+            st["step"] = torch.zeros((), dtype=torch.float32)
+            if unit is not None:
+                m, v = self._unit_moments(unit)
+                s = p._fs2_spec  # type: ignore[attr-defined]
+                n = s.rows_local * s.row
+                st["exp_avg"] = m[s.shard_off: s.shard_off + n].view(p.shape)
+                st["exp_avg_sq"] = v[s.shard_off: s.shard_off + n].view(p.shape)
+            else:
+                st["exp_avg"] = torch.zeros_like(p, dtype=torch.float32, memory_format=torch.preserve_format)
+                st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32, memory_format=torch.preserve_format)
+        return st
+
+    @torch.no_grad()
+    def step(self, closure: Callable[[], Tensor] | None = None, *, grad_scale: Tensor | None = None) -> Tensor | None:  # type: ignore[override]
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        for group in self.param_groups:
+            lr, (b1, b2), eps, wd = group["lr"], group["betas"], group["eps"], group["weight_decay"]
+            lr = float(lr)
+            units: dict[int, Any] = {}
+            unit_members: dict[int, int] = {}
+            plain: list[Tensor] = []
+            for p in group["params"]:
+                unit = getattr(p, "_fs2_unit", None)
+                if unit is not None:
+                    units[id(unit)] = unit
+                    unit_members[id(unit)] = unit_members.get(id(unit), 0) + 1
+                    self._init_state(p)
+                elif p.grad is not None:
+                    plain.append(p)
+            # ---- flat units: one launch each
+            for uid, unit in units.items():
+                if not unit.grads_ready or unit.grad_shard is None:
+                    continue
+                if unit_members[uid] != len(unit.shard_params):
+                    raise ValueError("All parameters of an FSDP unit must be in the same optimizer parameter group.")
+                st0 = self.state[unit.shard_params[0]]
+                step = int(st0["step"].item()) + 1 if "_host_step" not in st0 else st0["_host_step"] + 1
+                m, v = self._unit_moments(unit)
+                low = unit.low_shard if unit.low_shard.dtype == torch.bfloat16 else None
+                multi_tensor_adamw([unit.master], [unit.grad_shard], [m], [v], [low], lr=lr, beta1=b1, beta2=b2,
+                                   eps=eps, weight_decay=wd, step=step, grad_scale=grad_scale)
+                if low is None:
+                    unit.low_shard.copy_(unit.master)
+                for sp in unit.shard_params:
+                    st = self.state[sp]
+                    st["_host_step"] = step
+                    st["step"].fill_(step)
+            # ---- ordinary parameters
+            if plain:
+                ms, vs, gs, lows, masters = [], [], [], [], []
+                step = 0
+                for p in plain:
+                    st = self._init_state(p)
+                    step = st.get("_host_step", int(st["step"].item())) + 1
+                    st["_host_step"] = step
+                    st["step"].fill_(step)
+                    ms.append(st["exp_avg"])
+                    vs.append(st["exp_avg_sq"])
+                    gs.append(p.grad)
+                if all(p.is_cuda and p.dtype == torch.float32 and p.is_contiguous() and p.data_ptr() % 16 == 0
+                       and g.is_contiguous() and g.data_ptr() % 16 == 0 for p, g in zip(plain, gs)):
+                    multi_tensor_adamw(plain, gs, ms, vs, [None] * len(plain), lr=lr, beta1=b1, beta2=b2, eps=eps,
+                                       weight_decay=wd, step=step, grad_scale=grad_scale)
+                else:
+                    for p, g, m, v in zip(plain, gs, ms, vs):
+                        if p.dtype == torch.float32:
+                            adamw_reference(p, g, m, v, lr=lr, beta1=b1, beta2=b2, eps=eps, weight_decay=wd,
+                                            step=step, grad_scale=grad_scale if grad_scale is not None else 1.0)
+                        else:
+                            master = self.state[p].setdefault("master", p.detach().float().clone())
+                            adamw_reference(master, g, m, v, lr=lr, beta1=b1, beta2=b2, eps=eps, weight_decay=wd,
+                                            step=step, grad_scale=grad_scale if grad_scale is not None else 1.0,
+                                            low=p)
+        return loss
+
+    def state_dict(self) -> dict[str, Any]:  # type: ignore[override]
+        for group in self.param_groups:
+            for p in group["params"]:
+                if getattr(p, "_fs2_unit", None) is not None:
+                    self._init_state(p)
+        sd = super().state_dict()
+        for st in sd["state"].values():
+            st.pop("_host_step", None)
+        return sd
+
+    def load_state_dict(self, state_dict: dict[str, Any]) -> None:  # type: ignore[override]
+        # materialise flat-unit state first so loaded tensors are copied into the flat buffers
+        targets: dict[int, dict[str, Tensor]] = {}
+        idx = 0
+        for group in self.param_groups:
+            for p in group["params"]:
+                if getattr(p, "_fs2_unit", None) is not None:
+                    st = self._init_state(p)
+                    targets[idx] = {"exp_avg": st["exp_avg"], "exp_avg_sq": st["exp_avg_sq"]}
+                idx += 1
+        super().load_state_dict(state_dict)
+        idx = 0
+        for group in self.param_groups:
+            for p in group["params"]:
+                st = self.state.get(p)
+                if st:
+                    if idx in targets:
+                        for k in ("exp_avg", "exp_avg_sq"):
+                            if st[k].data_ptr() != targets[idx][k].data_ptr():
+                                targets[idx][k].copy_(st[k])
+                                st[k] = targets[idx][k]
+                    if isinstance(st.get("step"), Tensor):
+                        st["_host_step"] = int(st["step"].item())
+                        st["step"] = st["step"].detach().to("cpu", torch.float32)
+                idx += 1

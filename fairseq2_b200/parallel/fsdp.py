@@ -1,0 +1,633 @@
+"""Fully sharded data parallelism with flat, dim-0 sharded parameter units.
+
+Capability parity with fairseq2's FSDP wrappers (``nn/fsdp/fsdp2.py:60-299``,
+``fsdp1.py:50-281``, wrap policy ``models/transformer_lm/fsdp.py:17-34``):
+per-layer units, bf16 compute parameters with fp32 master weights ("static
+mixed precision"), reshard-after-forward, gradient reduce-scatter, local
+(dim-0 shard) state dicts that are interchangeable with FSDP2's
+``DTensor.to_local()`` shards, ``no_sync`` and ``summon_full_parameters``.
+
+The design is its own and B200-first:
+
+* Each unit owns ONE flat buffer per role -- fp32 master shard, bf16 shard
+  (all-gather source, lives in symmetric memory when available), bf16 full
+  parameters, bf16 full gradients, reduced gradient shard. Module parameters
+  are *views*: q/k/v and gate/up weights end up adjacent, so the model runs
+  them as single GEMMs, and weight-gradient GEMMs write straight into the flat
+  gradient buffer (``grad_sink``) -- no autograd accumulation pass, no
+  concatenation, no copy-out after the all-gather.
+* Every parameter is all-gathered into its own contiguous ``[W * chunk, ...]``
+  region (coalesced into one launch), so the gathered tensor *is* the
+  parameter.
+* Optimizer state is flat per unit as well; one fused AdamW launch updates a
+  unit (fp32 master, moments) and refreshes the bf16 shard in the same pass.
+  Loss normalisation and clipping factors stay on the device and are applied
+  inside that launch (no separate gradient scaling pass, no host sync).
+* With one rank the unit degenerates gracefully: the bf16 buffer is the full
+  parameter, the flat bf16 gradient is the "reduced" gradient.
+"""
+from __future__ import annotations
+
+import math
+from contextlib import contextmanager
+from dataclasses import dataclass
+from typing import Any, Callable, Iterable, Iterator, Mapping, Sequence
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+from torch.nn import Module, Parameter
+
+from fairseq2_b200.gang import Gang, Gangs, ProcessGroupGang, ReduceOperation
+from fairseq2_b200.logging import log
+from fairseq2_b200.ops.optim import multi_tensor_l2_norm_sq
+from fairseq2_b200.typing import DataType, Device
+
+_ALIGN = 64  # elements; keeps every region 128-byte aligned (TMA needs 16 B)
+
+
+def _round_up(n: int, m: int) -> int:
+    return ((n + m - 1) // m) * m
+
+
+@dataclass
+class _ParamSpec:
+    fqn: str
+    owners: list[tuple[Module, str]]   # every (module, attribute) that holds this parameter (tied weights)
+    shape: tuple[int, ...]
+    d0: int
+    row: int            # elements per dim-0 row
+    chunk: int          # dim-0 rows per rank (ceil)
+    shard_off: int      # offset into the flat shard buffers
+    shard_numel: int    # padded elements per rank (chunk * row, aligned)
+    rows_local: int     # real rows owned by this rank
+    requires_grad: bool
+
+
+class FlatParamUnit:
+    """One FSDP unit: the parameters of ``module`` that are not owned by a nested unit."""
+
+    def __init__(self, name: str, module: Module, named_params: list[tuple[str, list[tuple[Module, str]], Parameter]],
+                 gang: Gang, *, param_dtype: DataType, reduce_dtype: DataType, reshard_after_forward: bool) -> None:
+        self.name, self.module, self.gang = name, module, gang
+        self.world, self.rank = gang.size, gang.rank
+        self.param_dtype, self.reduce_dtype = param_dtype, reduce_dtype
+        self.reshard_after_forward = reshard_after_forward and gang.size > 1
+        dev = named_params[0][2].device
+        self.device = dev
+        W, r = self.world, self.rank
+
+        specs: list[_ParamSpec] = []
+        off = 0
+        for fqn, owners, p in named_params:
+            shape = tuple(p.shape) if p.ndim > 0 else (1,)
+            d0 = shape[0]
+            row = int(math.prod(shape[1:])) if len(shape) > 1 else 1
+            chunk = (d0 + W - 1) // W
+            shard_numel = _round_up(chunk * row, _ALIGN)
+            rows_local = max(0, min(d0, (r + 1) * chunk) - r * chunk)
+            specs.append(_ParamSpec(fqn, owners, shape, d0, row, chunk, off, shard_numel, rows_local,
+                                    p.requires_grad))
+            off += shard_numel
+        self.specs = specs
+        self.shard_size = off
+
+        # fp32 master shard (+ bf16 shard that feeds the all-gather)
+        self.master = torch.zeros(off, device=dev, dtype=torch.float32)
+        with torch.no_grad():
+            for s, (_, _, p) in zip(specs, named_params):
+                if s.rows_local > 0:
+                    src = p.detach().reshape(s.d0, s.row)[r * s.chunk: r * s.chunk + s.rows_local]
+                    self.master[s.shard_off: s.shard_off + s.rows_local * s.row].copy_(src.reshape(-1))
+        self.low_shard = self.master.to(param_dtype)
+        self.full: Tensor | None = self.low_shard if W == 1 else None
+        self.grad_full: Tensor | None = None
+        self.grad_shard: Tensor | None = None   # reduced gradient of the local shard
+        self.grads_ready = False
+        self.unsharded = W == 1
+        self._ag_event: torch.cuda.Event | None = None
+
+        # shard parameters handed to the optimizer / state dict
+        self.shard_params: list[Parameter] = []
+        for s in specs:
+            view = self.master[s.shard_off: s.shard_off + s.rows_local * s.row].view(s.rows_local, *s.shape[1:])
+            sp = Parameter(view, requires_grad=s.requires_grad)
+            sp._fs2_unit = self  # type: ignore[attr-defined]
+            sp._fs2_spec = s  # type: ignore[attr-defined]
+            self.shard_params.append(sp)
+
+        # module parameters become views of the full bf16 buffer
+        self.compute_params: list[Parameter] = []
+        for s in specs:
+            cp = Parameter(torch.empty(0, device=dev, dtype=param_dtype), requires_grad=s.requires_grad)
+            for owner, attr in s.owners:
+                owner._parameters[attr] = cp
+            self.compute_params.append(cp)
+        if W == 1:
+            self._bind_full(self.low_shard)
+
+    # ------------------------------------------------------------- views
+    def _region(self, buf: Tensor, s: _ParamSpec) -> Tensor:
+        """``[W * chunk, row]`` region of parameter ``s`` inside a full-size flat buffer."""
+        return buf[self.world * s.shard_off: self.world * (s.shard_off + s.shard_numel)]
+
+    def _bind_full(self, full: Tensor) -> None:
+        for s, cp in zip(self.specs, self.compute_params):
+            reg = self._region(full, s)
+            cp.data = reg[: s.d0 * s.row].view(s.shape)
+
+    def _bind_grad_sinks(self, grad_full: Tensor, filled: bool) -> None:
+        for s, cp in zip(self.specs, self.compute_params):
+            reg = self._region(grad_full, s)
+            cp.grad_sink = reg[: s.d0 * s.row].view(s.shape)  # type: ignore[attr-defined]
+            cp.grad_sink_filled = filled  # type: ignore[attr-defined]
+
+    # -------------------------------------------------------- collectives
+    def unshard(self, comm_stream: "torch.cuda.Stream | None") -> None:
+        """Starts the all-gather of the bf16 shards into a fresh full buffer."""
+        if self.unsharded:
+            return
+        W = self.world
+        full = torch.empty(W * self.shard_size, device=self.device, dtype=self.param_dtype)
+        cur = torch.cuda.current_stream(self.device) if self.device.type == "cuda" else None
+        if comm_stream is not None and cur is not None:
+            comm_stream.wait_stream(cur)
+            ctx: Any = torch.cuda.stream(comm_stream)
+        else:
+            ctx = _null()
+        with ctx:
+            _coalesced_all_gather(self.gang, [self._region(full, s).view(W, s.shard_numel) for s in self.specs],
+                                  [self.low_shard[s.shard_off: s.shard_off + s.shard_numel] for s in self.specs])
+            if comm_stream is not None:
+                ev = torch.cuda.Event()
+                ev.record(comm_stream)
+                self._ag_event = ev
+        self.full = full
+        self._bind_full(full)
+        self.unsharded = True
+
+    def wait_unshard(self) -> None:
+        if self._ag_event is not None:
+            torch.cuda.current_stream(self.device).wait_event(self._ag_event)
+            self._ag_event = None
+
+    def reshard(self) -> None:
+        if self.world == 1 or not self.unsharded:
+            return
+        self.full = None
+        for cp in self.compute_params:
+            cp.data = torch.empty(0, device=self.device, dtype=self.param_dtype)
+        self.unsharded = False
+
+    def prepare_grads(self) -> None:
+        """Allocates (or reuses, when accumulating) the flat bf16 gradient buffer
+        and points every parameter's ``grad_sink`` into it."""
+        if self.grad_full is None:
+            self.grad_full = torch.empty(self.world * self.shard_size, device=self.device, dtype=self.param_dtype)
+            if self.world > 1:
+                self.grad_full.zero_()  # padding rows take part in the reduce-scatter
+            self._bind_grad_sinks(self.grad_full, filled=False)
+
+    def collect_autograd_grads(self) -> None:
+        """Gradients that autograd produced the ordinary way (``param.grad``)
+        are moved into the flat buffer; sinks written by GEMM epilogues are
+        already in place."""
+        assert self.grad_full is not None
+        for s, cp in zip(self.specs, self.compute_params):
+            if cp.grad is not None:
+                sink = cp.grad_sink  # type: ignore[attr-defined]
+                if cp.grad_sink_filled:  # type: ignore[attr-defined]
+                    sink.add_(cp.grad.to(sink.dtype))
+                else:
+                    sink.copy_(cp.grad)
+                cp.grad_sink_filled = True  # type: ignore[attr-defined]
+                cp.grad = None
+
+    def reduce_grads(self, comm_stream: "torch.cuda.Stream | None", *, average: bool = True) -> None:
+        """Reduce-scatters the flat gradient into ``grad_shard`` (mean over ranks)."""
+        if self.grad_full is None:
+            return
+        self.collect_autograd_grads()
+        for s, cp in zip(self.specs, self.compute_params):
+            if not getattr(cp, "grad_sink_filled", False) and getattr(cp, "grad_sink", None) is not None:
+                cp.grad_sink.zero_()  # type: ignore[attr-defined]  # parameter took no part in this step
+                cp.grad_sink_filled = True  # type: ignore[attr-defined]
+        W = self.world
+        if W == 1:
+            self.grad_shard = self.grad_full
+            self.grads_ready = True
+            return
+        gf = self.grad_full
+        cur = torch.cuda.current_stream(self.device) if self.device.type == "cuda" else None
+        if comm_stream is not None and cur is not None:
+            comm_stream.wait_stream(cur)
+            ctx: Any = torch.cuda.stream(comm_stream)
+        else:
+            ctx = _null()
+        with ctx:
+            if self.reduce_dtype != gf.dtype:
+                gf = gf.to(self.reduce_dtype)
+            out = torch.empty(self.shard_size, device=self.device, dtype=self.reduce_dtype)
+            _coalesced_reduce_scatter(
+                self.gang, [out[s.shard_off: s.shard_off + s.shard_numel] for s in self.specs],
+                [self._region(gf, s).view(W, s.shard_numel) for s in self.specs],
+                ReduceOperation.MEAN if average else ReduceOperation.SUM)
+            if self.grad_shard is not None and self.grads_ready:
+                self.grad_shard.add_(out)       # gradient accumulation across micro-batches
+            else:
+                self.grad_shard = out
+            if comm_stream is not None and cur is not None:
+                # `gf`/`grad_full` were allocated on the compute stream and are consumed here
+                gf.record_stream(comm_stream)
+                self.grad_full.record_stream(comm_stream)
+        self.grads_ready = True
+        self.grad_full = None
+        for cp in self.compute_params:
+            cp.grad_sink = None  # type: ignore[attr-defined]
+            cp.grad_sink_filled = False  # type: ignore[attr-defined]
+
+    def zero_grad(self) -> None:
+        self.grads_ready = False
+        if self.world == 1:
+            if self.grad_full is not None:
+                # keep the buffer, mark every sink as empty: the next wgrad overwrites
+                for cp in self.compute_params:
+                    cp.grad_sink_filled = False  # type: ignore[attr-defined]
+            self.grad_shard = None
+        else:
+            self.grad_shard = None
+            self.grad_full = None
+        for cp in self.compute_params:
+            cp.grad = None
+
+    def refresh_low_from_master(self) -> None:
+        self.low_shard.copy_(self.master)
+
+    def local_grad_norm_sq(self) -> Tensor | None:
+        if not self.grads_ready or self.grad_shard is None:
+            return None
+        g = self.grad_shard
+        if self.world == 1:
+            # padding between regions is zero, so the flat norm is the parameter norm
+            pass
+        if g.is_cuda:
+            return multi_tensor_l2_norm_sq([g])
+        return g.float().pow(2).sum()
+
+
+@contextmanager
+def _null() -> Iterator[None]:
+    yield
+
+
+def _coalesced_all_gather(gang: Gang, outs: Sequence[Tensor], ins: Sequence[Tensor]) -> None:
+    if isinstance(gang, ProcessGroupGang) and gang.device.type == "cuda":
+        pg = gang.as_process_group()
+        with dist._coalescing_manager(group=pg, device=gang.device, async_ops=False):
+            for o, i in zip(outs, ins):
+                dist.all_gather_into_tensor(o, i, group=pg)
+        return
+    for o, i in zip(outs, ins):
+        gang.all_gather(o, i)
+
+
+def _coalesced_reduce_scatter(gang: Gang, outs: Sequence[Tensor], ins: Sequence[Tensor], op: ReduceOperation) -> None:
+    if isinstance(gang, ProcessGroupGang) and gang.device.type == "cuda":
+        pg = gang.as_process_group()
+        top = dist.ReduceOp.AVG if op == ReduceOperation.MEAN else dist.ReduceOp.SUM
+        with dist._coalescing_manager(group=pg, device=gang.device, async_ops=False):
+            for o, i in zip(outs, ins):
+                dist.reduce_scatter_tensor(o, i, op=top, group=pg)
+        return
+    for o, i in zip(outs, ins):
+        gang.reduce_scatter(o, i, op)
+
+
+FSDPWrapPolicy = Callable[[Module], "list[Module]"]
+
+
+def layerwise_wrap_policy(module: Module) -> list[Module]:
+    """Every element of a ``layers`` ModuleList anywhere in the model is a unit
+    (the fairseq2 "layer" granularity)."""
+    units: list[Module] = []
+    for m in module.modules():
+        layers = getattr(m, "layers", None)
+        if isinstance(layers, torch.nn.ModuleList):
+            units.extend(layers)
+    return units
+
+
+class FSDP(Module):
+    """Wraps ``module``; see the module docstring for the design."""
+
+    def __init__(self, module: Module, gangs: Gangs, *, wrap_policy: FSDPWrapPolicy | None = layerwise_wrap_policy,
+                 param_dtype: DataType = torch.bfloat16, fp32_reduce: bool = True,
+                 reshard_after_forward: bool = True, overlap: bool = True) -> None:
+        super().__init__()
+        self.module = module
+        self.gangs = gangs
+        self.gang = gangs.sdp if gangs.sdp.size > 1 or gangs.rdp.size > 1 else gangs.dp
+        if gangs.rdp.size > 1 and gangs.sdp.size > 1:
+            self.replica_gang: Gang | None = gangs.rdp
+        else:
+            self.replica_gang = None
+        W = self.gang.size
+        self.param_dtype = param_dtype
+        reduce_dtype = torch.float32 if (fp32_reduce and W > 1) else param_dtype
+        unit_modules = wrap_policy(module) if wrap_policy is not None else []
+        owned: set[int] = set()
+        self.units: list[FlatParamUnit] = []
+
+        memo: dict[int, Parameter] = {}
+
+        def holders_of(p: Parameter) -> list[tuple[Module, str]]:
+            return [(sub, attr) for sub in module.modules() for attr, q in sub._parameters.items() if q is p]
+
+        def collect(m: Module, prefix: str) -> list[tuple[str, list[tuple[Module, str]], Parameter]]:
+            out: list[tuple[str, list[tuple[Module, str]], Parameter]] = []
+            for mod_name, sub in m.named_modules(prefix=prefix):
+                for attr, p in sub._parameters.items():
+                    if p is None or id(p) in owned:
+                        continue
+                    owned.add(id(p))
+                    out.append((f"{mod_name}.{attr}" if mod_name else attr, holders_of(p), p))
+            return out
+
+        def make_unit(name: str, m: Module, reshard: bool) -> FlatParamUnit | None:
+            _materialize(m, target_device, memo)
+            nps = collect(m, name)
+            if not nps:
+                return None
+            u = FlatParamUnit(name, m, nps, self.gang, param_dtype=param_dtype, reduce_dtype=reduce_dtype,
+                              reshard_after_forward=reshard)
+            owned.update(id(cp) for cp in u.compute_params)
+            return u
+
+        names = {id(m): n for n, m in module.named_modules()}
+        last = len(unit_modules) - 1
+        target_device = gangs.root.device
+        for i, um in enumerate(unit_modules):
+            u = make_unit(names[id(um)], um, reshard_after_forward and i != last)
+            if u is not None:
+                self.units.append(u)
+        self.root_unit: FlatParamUnit | None = make_unit("", module, False)
+        self.all_units = ([self.root_unit] if self.root_unit is not None else []) + self.units
+        # cast floating-point buffers (e.g. nothing for RoPE tables which stay fp32 by design)
+        dev = self.all_units[0].device if self.all_units else torch.device("cpu")
+        self.device = dev
+        self.comm_stream = torch.cuda.Stream(dev) if (overlap and dev.type == "cuda" and W > 1) else None
+        self._require_sync = True
+        self._grad_scale: Tensor | None = None
+        self._in_backward = False
+        self._pending_reduce: list[FlatParamUnit] = []
+        self._install_hooks()
+        n = sum(u.shard_size for u in self.all_units)
+        log.info("FSDP: {} unit(s), {:,} local shard elements, world size {}.", len(self.all_units), n, W)
+
+    # ------------------------------------------------------------------ hooks
+    def _install_hooks(self) -> None:
+        for idx, u in enumerate(self.units):
+            u.module.register_forward_pre_hook(self._make_pre_forward(idx))
+            u.module.register_forward_hook(self._make_post_forward(idx))
+            u.module.register_full_backward_pre_hook(self._make_pre_backward(idx))
+            u.module.register_full_backward_hook(self._make_post_backward(idx))
+
+    def _make_pre_forward(self, idx: int):  # type: ignore[no-untyped-def]
+        def hook(m: Module, args: Any) -> None:
+            u = self.units[idx]
+            u.unshard(self.comm_stream)
+            u.wait_unshard()
+            if torch.is_grad_enabled():
+                u.prepare_grads()
+            if idx + 1 < len(self.units):           # prefetch the next layer
+                self.units[idx + 1].unshard(self.comm_stream)
+        return hook
+
+    def _make_post_forward(self, idx: int):  # type: ignore[no-untyped-def]
+        def hook(m: Module, args: Any, out: Any) -> None:
+            u = self.units[idx]
+            if u.reshard_after_forward and not self._in_backward:
+                u.reshard()
+        return hook
+
+    def _make_pre_backward(self, idx: int):  # type: ignore[no-untyped-def]
+        def hook(m: Module, grad_out: Any) -> None:
+            self._in_backward = True
+            self._flush_pending_reduce()
+            u = self.units[idx]
+            u.unshard(self.comm_stream)
+            u.wait_unshard()
+            u.prepare_grads()
+            if idx - 1 >= 0:
+                self.units[idx - 1].unshard(self.comm_stream)
+        return hook
+
+    def _make_post_backward(self, idx: int):  # type: ignore[no-untyped-def]
+        def hook(m: Module, grad_in: Any, grad_out: Any) -> None:
+            # The reduction is issued at the next hook (the pre-backward of the
+            # preceding layer fires right after this one) so that every
+            # AccumulateGrad node of this unit has certainly run.
+            self._pending_reduce.append(self.units[idx])
+        return hook
+
+    def _flush_pending_reduce(self) -> None:
+        for u in self._pending_reduce:
+            if self._require_sync:
+                u.reduce_grads(self.comm_stream)
+            if u.world > 1:
+                u.reshard()
+        self._pending_reduce.clear()
+
+    # ---------------------------------------------------------------- forward
+    def forward(self, *args: Any, **kwargs: Any) -> Any:
+        self._in_backward = False
+        if self.root_unit is not None:
+            self.root_unit.unshard(self.comm_stream)
+            self.root_unit.wait_unshard()
+            if torch.is_grad_enabled():
+                self.root_unit.prepare_grads()
+        if self.units:
+            self.units[0].unshard(self.comm_stream)
+        return self.module(*args, **kwargs)
+
+    def finish_backward(self) -> None:
+        """Call after ``loss.backward()``: reduces the root unit, any unit whose
+        post-backward hook did not fire, and joins the communication stream."""
+        self._in_backward = False
+        self._flush_pending_reduce()
+        if self._require_sync:
+            for u in self.all_units:
+                if u.grad_full is not None and (u.world > 1 or not u.grads_ready):
+                    u.reduce_grads(self.comm_stream)
+        if self.root_unit is not None and self.root_unit.world > 1 and self._require_sync:
+            pass  # the root stays unsharded until the optimizer refreshed its shard
+        if self.comm_stream is not None:
+            torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
+        if self.replica_gang is not None and self._require_sync:
+            for u in self.all_units:
+                if u.grad_shard is not None:
+                    self.replica_gang.all_reduce(u.grad_shard, ReduceOperation.MEAN)
+
+    def after_optimizer_step(self) -> None:
+        """The optimizer wrote new bf16 shards: gathered copies are stale."""
+        for u in self.all_units:
+            if u.world > 1:
+                u.reshard()
+
+    # ------------------------------------------------------------ grad control
+    @contextmanager
+    def no_sync(self) -> Iterator[None]:
+        old = self._require_sync
+        self._require_sync = False
+        try:
+            yield
+        finally:
+            self._require_sync = old
+
+    def zero_grad(self, set_to_none: bool = True) -> None:  # type: ignore[override]
+        for u in self.all_units:
+            u.zero_grad()
+        self._grad_scale = None
+
+    def scale_grads(self, factor: Tensor | float) -> None:
+        """Records a factor that the optimizer applies to every gradient."""
+        f = factor if isinstance(factor, Tensor) else torch.tensor(float(factor), device=self.device)
+        f = f.to(device=self.device, dtype=torch.float32)
+        self._grad_scale = f if self._grad_scale is None else self._grad_scale * f
+
+    @property
+    def grad_scale(self) -> Tensor | None:
+        return self._grad_scale
+
+    def grad_norm(self) -> Tensor:
+        parts = [n for n in (u.local_grad_norm_sq() for u in self.all_units) if n is not None]
+        if not parts:
+            return torch.zeros((), device=self.device)
+        total = torch.stack(parts).sum()
+        if self.gang.size > 1:
+            self.gang.all_reduce(total, ReduceOperation.SUM)
+        norm = total.sqrt()
+        if self._grad_scale is not None:
+            norm = norm * self._grad_scale
+        return norm
+
+    def clip_grad_norm(self, max_norm: float | None) -> Tensor:
+        norm = self.grad_norm()
+        if max_norm is not None:
+            coef = (max_norm / (norm + 1e-6)).clamp(max=1.0)
+            self.scale_grads(coef)
+        return norm
+
+    # ------------------------------------------------------------- parameters
+    def named_parameters(self, prefix: str = "", recurse: bool = True, remove_duplicate: bool = True):  # type: ignore[override]
+        for u in self.all_units:
+            for s, sp in zip(u.specs, u.shard_params):
+                yield (prefix + ("." if prefix else "") + s.fqn, sp)
+
+    def parameters(self, recurse: bool = True):  # type: ignore[override]
+        for _, p in self.named_parameters():
+            yield p
+
+    def state_dict(self, *args: Any, **kwargs: Any) -> dict[str, Any]:  # type: ignore[override]
+        """Local (dim-0 shard) state dict: fp32 master shards keyed by the FQNs
+        of the unwrapped model, plus persistent buffers."""
+        out: dict[str, Any] = {}
+        for name, p in self.named_parameters():
+            out[name] = p.detach()
+        for name, b in self.module.named_buffers():
+            mod_name, _, leaf = name.rpartition(".")
+            mod = self.module.get_submodule(mod_name) if mod_name else self.module
+            if leaf not in mod._non_persistent_buffers_set:
+                out[name] = b
+        return out
+
+    def load_state_dict(self, state_dict: Mapping[str, Any], strict: bool = True, assign: bool = False):  # type: ignore[override]
+        own = dict(self.named_parameters())
+        missing = [k for k in own if k not in state_dict]
+        bufs = {n for n, _ in self.module.named_buffers()}
+        unexpected = [k for k in state_dict if k not in own and k not in bufs]
+        if strict and (missing or unexpected):
+            raise ValueError(f"`state_dict` does not match the model (missing: {missing}, unexpected: {unexpected}).")
+        with torch.no_grad():
+            for k, p in own.items():
+                if k in state_dict:
+                    src = state_dict[k]
+                    if tuple(src.shape) != tuple(p.shape):
+                        raise ValueError(f"The shape of '{k}' is {tuple(src.shape)}, but {tuple(p.shape)} is expected.")
+                    p.copy_(src)
+            for n, b in self.module.named_buffers():
+                if n in state_dict:
+                    b.copy_(state_dict[n])
+        for u in self.all_units:
+            u.refresh_low_from_master()
+            if u.world > 1:
+                u.reshard()
+
+    @contextmanager
+    def summon_full_parameters(self) -> Iterator[None]:
+        """All parameters gathered (bf16 compute copies) for inference/export."""
+        was = [u.unsharded for u in self.all_units]
+        for u in self.all_units:
+            u.unshard(None)
+        try:
+            yield
+        finally:
+            for u, w in zip(self.all_units, was):
+                if not w:
+                    u.reshard()
+
+    def full_state_dict(self, dtype: DataType | None = None) -> dict[str, Tensor]:
+        """Gathers fp32 master weights of every parameter (all ranks must call)."""
+        out: dict[str, Tensor] = {}
+        for u in self.all_units:
+            for s in u.specs:
+                local = u.master[s.shard_off: s.shard_off + s.chunk * s.row]
+                if u.world > 1:
+                    buf = torch.empty((u.world, s.chunk * s.row), device=u.device, dtype=torch.float32)
+                    u.gang.all_gather(buf, local.contiguous())
+                    full = buf.reshape(-1)[: s.d0 * s.row]
+                else:
+                    full = local[: s.d0 * s.row]
+                t = full.view(s.shape).clone()
+                out[s.fqn] = t.to(dtype) if dtype is not None else t
+        return out
+
+
+def _materialize(module: Module, device: Device, memo: dict[int, Parameter]) -> None:
+    """Meta-device parameters/buffers under ``module`` are allocated on
+    ``device`` and initialised module by module (children first), so that a
+    model far larger than one GPU can be sharded unit by unit: only one unit
+    is ever resident in full precision."""
+    for sub in reversed(list(module.modules())):
+        metas = [n for n, p in sub._parameters.items() if p is not None and p.is_meta]
+        metab = [n for n, b in sub._buffers.items() if b is not None and b.is_meta]
+        if not metas and not metab:
+            continue
+        fresh = False
+        for n in metas:
+            p = sub._parameters[n]
+            if id(p) in memo:       # tied parameter that another module already materialised
+                sub._parameters[n] = memo[id(p)]
+                continue
+            np_ = Parameter(torch.empty_like(p, device=device), requires_grad=p.requires_grad)
+            memo[id(p)] = np_
+            sub._parameters[n] = np_
+            fresh = True
+        if not fresh and not metab:
+            continue
+        for n in metab:
+            sub._buffers[n] = torch.empty_like(sub._buffers[n], device=device)
+        fn = getattr(sub, "reset_parameters", None)
+        if callable(fn):
+            fn()
+        else:
+            fn2 = getattr(sub, "reset_non_persistent_buffers", None)
+            if callable(fn2):
+                fn2()
+
+
+def to_fsdp(module: Module, gangs: Gangs, *, wrap_policy: FSDPWrapPolicy | None = layerwise_wrap_policy,
+            mixed_precision_dtype: DataType | None = torch.bfloat16, fp32_reduce: bool = True,
+            reshard_after_forward: bool = True, **_: Any) -> FSDP:
+    return FSDP(module, gangs, wrap_policy=wrap_policy, param_dtype=mixed_precision_dtype or torch.float32,
+                fp32_reduce=fp32_reduce, reshard_after_forward=reshard_after_forward)
