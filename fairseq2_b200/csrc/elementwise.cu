@@ -623,3 +623,89 @@ void scale_inplace(void* x, bool bf16, size_t n, const float* scale, int num_sms
 }
 
 }  // namespace fs2
+
+// ---------------------------------------------------------------------------
+// Allocation-free RMSNorm backward (declared and documented in no_alloc.h).
+// Same kernels as `rms_norm_bwd` above; only the home of the per-block partial
+// sums differs: a fixed __device__ array instead of a caller-provided buffer.
+// ---------------------------------------------------------------------------
+#include <mutex>
+
+#include "no_alloc.h"
+
+namespace fs2 {
+namespace {
+
+static __device__ __align__(256) float g_no_alloc_scratch[FS2_NO_ALLOC_MAX_BLOCKS * FS2_NO_ALLOC_MAX_DIM];
+
+constexpr int kMaxDevices = 64;
+float* g_no_alloc_ptr[kMaxDevices] = {};
+std::mutex g_no_alloc_mutex;
+thread_local const char* g_no_alloc_error = "";
+
+// Device address of the scratch array on the current device. In host code the
+// array's name is only a handle, never an address a kernel may dereference.
+float* no_alloc_scratch_ptr() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        g_no_alloc_error = "cudaGetDevice failed or device ordinal out of range";
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lock(g_no_alloc_mutex);
+    if (g_no_alloc_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_no_alloc_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            g_no_alloc_error = "cudaGetSymbolAddress failed for the static scratch array";
+            return nullptr;
+        }
+        g_no_alloc_ptr[dev] = static_cast<float*>(p);
+    }
+    return g_no_alloc_ptr[dev];
+}
+
+}  // namespace
+}  // namespace fs2
+
+extern "C" const char* fs2_no_alloc_last_error() { return fs2::g_no_alloc_error; }
+
+extern "C" int fs2_rms_norm_bwd_no_alloc(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
+                                         float* dw, int rows, int D, int is_bf16, cudaStream_t stream) {
+    using namespace fs2;
+    if (rows < 1) {
+        g_no_alloc_error = "rows must be >= 1";
+        return 1;
+    }
+    if (D < 8 || D % 8 != 0 || D > FS2_NO_ALLOC_MAX_DIM) {
+        g_no_alloc_error = "D must be a multiple of 8 and at most FS2_NO_ALLOC_MAX_DIM (8192)";
+        return 2;
+    }
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(x) |
+                           reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(dx) |
+                           reinterpret_cast<uintptr_t>(dw);
+    if (dy == nullptr || x == nullptr || w == nullptr || rstd == nullptr || dx == nullptr || dw == nullptr ||
+        (bits & 15u) != 0) {
+        g_no_alloc_error = "all pointers must be non-null and 16-byte aligned";
+        return 3;
+    }
+    float* scratch = no_alloc_scratch_ptr();
+    if (scratch == nullptr) return 4;
+    const int threads = norm_block(D);
+    const int grid = rows < FS2_NO_ALLOC_MAX_BLOCKS ? rows : FS2_NO_ALLOC_MAX_BLOCKS;
+    FS2_VPT_DISPATCH(norm_vpt(D, threads),
+        if (is_bf16)
+            rms_norm_bwd_kernel<__nv_bfloat16, VPT><<<grid, threads, 0, stream>>>(
+                static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
+                static_cast<const __nv_bfloat16*>(w), rstd, static_cast<__nv_bfloat16*>(dx), scratch, rows, D);
+        else
+            rms_norm_bwd_kernel<float, VPT><<<grid, threads, 0, stream>>>(
+                static_cast<const float*>(dy), static_cast<const float*>(x), static_cast<const float*>(w), rstd,
+                static_cast<float*>(dx), scratch, rows, D))
+    reduce_partials_kernel<<<(D + 255) / 256, 256, 0, stream>>>(scratch, dw, grid, D);
+    if (cudaGetLastError() != cudaSuccess) {
+        g_no_alloc_error = "kernel launch failed";
+        return 5;
+    }
+    g_no_alloc_error = "";
+    return 0;
+}
