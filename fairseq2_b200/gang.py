@@ -364,7 +364,8 @@ class ProcessGroupGang(Gang):
             raise ValueError("`output_tensor` must be contiguous.")
         if output_tensor.shape[0] != self._size or output_tensor.shape[1:] != input_tensor.shape:
             raise ValueError(f"`output_tensor` must have shape [{self._size}, *input_tensor.shape].")
-        self._run(dist.all_gather_into_tensor, output_tensor, input_tensor.contiguous(), group=self._pg)
+        self._run(dist.all_gather_into_tensor, output_tensor.view(-1), input_tensor.contiguous().view(-1),
+                  group=self._pg)
 
     def all_gather_to_list(self, output_tensors: list[Tensor], input_tensor: Tensor) -> None:
         if len(output_tensors) != self._size:
@@ -381,7 +382,8 @@ class ProcessGroupGang(Gang):
             output_tensor.copy_(tmp[self._rank])
             return
         top = dist.ReduceOp.AVG if op == ReduceOperation.MEAN else _TORCH_OPS[op]
-        self._run(dist.reduce_scatter_tensor, output_tensor, input_tensor.contiguous(), top, group=self._pg)
+        self._run(dist.reduce_scatter_tensor, output_tensor.view(-1), input_tensor.contiguous().view(-1), top,
+                  group=self._pg)
 
     def all_to_all(self, output_tensor: Tensor, input_tensor: Tensor,
                    output_split_sizes: Sequence[int] | None = None,
