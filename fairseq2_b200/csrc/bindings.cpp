@@ -12,6 +12,7 @@
 #include <vector>
 
 #include "attention.h"
+#include "comm.h"
 #include "elementwise.h"
 #include "gemm_tcgen05.h"
 
@@ -420,6 +421,128 @@ void multi_tensor_scale(const std::vector<Tensor>& ts, const Tensor& scale) {
     }
 }
 
+// ------------------------------------------------------- symmetric-memory comm
+fs2::CommPeers make_peers(const std::vector<int64_t>& ptrs, int64_t rank, double wait_limit_s) {
+    TORCH_CHECK(!ptrs.empty() && ptrs.size() <= static_cast<size_t>(fs2::kCommMaxRanks),
+                "comm: between 1 and ", fs2::kCommMaxRanks, " ranks are supported");
+    TORCH_CHECK(rank >= 0 && rank < static_cast<int64_t>(ptrs.size()), "comm: bad rank");
+    fs2::CommPeers p{};
+    for (size_t i = 0; i < ptrs.size(); ++i) {
+        TORCH_CHECK(ptrs[i] != 0 && ptrs[i] % 16 == 0, "comm: peer base pointers must be non-null and 16-byte aligned");
+        p.base[i] = reinterpret_cast<void*>(ptrs[i]);
+    }
+    p.world = static_cast<int>(ptrs.size());
+    p.rank = static_cast<int>(rank);
+    p.wait_limit_ns = static_cast<unsigned long long>(wait_limit_s * 1e9);
+    return p;
+}
+
+fs2::CommSegments make_segments(const std::vector<int64_t>& offs, const std::vector<int64_t>& numels) {
+    TORCH_CHECK(offs.size() == numels.size() && !offs.empty() &&
+                    offs.size() <= static_cast<size_t>(fs2::kCommMaxSegments),
+                "comm: between 1 and ", fs2::kCommMaxSegments, " segments are supported");
+    fs2::CommSegments s{};
+    s.count = static_cast<int>(offs.size());
+    for (size_t i = 0; i < offs.size(); ++i) {
+        TORCH_CHECK(offs[i] % 8 == 0 && numels[i] % 8 == 0, "comm: segments must be multiples of 8 elements");
+        TORCH_CHECK(i == 0 || offs[i] == offs[i - 1] + numels[i - 1], "comm: segments must tile the shard buffer");
+        s.off[i] = offs[i];
+        s.numel[i] = numels[i];
+    }
+    return s;
+}
+
+void comm_barrier(const std::vector<int64_t>& ptrs, int64_t rank, int64_t slot, int64_t epoch, int64_t device,
+                  double wait_limit_s) {
+    c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+    fs2::comm_barrier(make_peers(ptrs, rank, wait_limit_s), static_cast<int>(slot), static_cast<uint32_t>(epoch),
+                      status_dev_ptr(), at::cuda::getCurrentCUDAStream(device).stream());
+    g_launches += 1;
+}
+
+void comm_signal(const std::vector<int64_t>& ptrs, int64_t rank, int64_t slot, int64_t epoch, int64_t device) {
+    c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+    fs2::comm_signal(make_peers(ptrs, rank, 1.0), static_cast<int>(slot), static_cast<uint32_t>(epoch),
+                     at::cuda::getCurrentCUDAStream(device).stream());
+    g_launches += 1;
+}
+
+void comm_allgather_segments(const std::vector<int64_t>& ptrs, int64_t rank, const std::vector<int64_t>& offs,
+                             const std::vector<int64_t>& numels, int64_t shard_byte_off, Tensor full, int64_t slot,
+                             int64_t epoch, int64_t blocks, double wait_limit_s) {
+    TORCH_CHECK(full.is_cuda() && full.is_contiguous() && full.element_size() == 2 && aligned16(full),
+                "comm_allgather_segments: `full` must be a contiguous 2-byte CUDA tensor");
+    const int64_t shard_numel = offs.back() + numels.back();
+    TORCH_CHECK(full.numel() == shard_numel * static_cast<int64_t>(ptrs.size()),
+                "comm_allgather_segments: `full` must hold world x shard elements");
+    TORCH_CHECK(shard_byte_off % 16 == 0, "comm_allgather_segments: unaligned shard offset");
+    c10::cuda::CUDAGuard guard(full.device());
+    fs2::comm_allgather_segments(make_peers(ptrs, rank, wait_limit_s), make_segments(offs, numels), shard_byte_off,
+                                 full.data_ptr(), shard_numel, static_cast<int>(slot), static_cast<uint32_t>(epoch),
+                                 static_cast<int>(blocks), status_dev_ptr(), stream_of(full));
+    g_launches += 1;
+}
+
+void comm_reducescatter_segments(const std::vector<int64_t>& ptrs, int64_t rank, const std::vector<int64_t>& offs,
+                                 const std::vector<int64_t>& numels, int64_t full_byte_off, Tensor out, double scale,
+                                 bool accumulate, int64_t slot, int64_t epoch, int64_t blocks, double wait_limit_s) {
+    const int64_t shard_numel = offs.back() + numels.back();
+    TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.numel() == shard_numel && aligned16(out) &&
+                    (out.scalar_type() == at::kFloat || is_bf16(out)),
+                "comm_reducescatter_segments: `out` must be a contiguous fp32/bf16 shard-sized CUDA tensor");
+    TORCH_CHECK(full_byte_off % 16 == 0, "comm_reducescatter_segments: unaligned offset");
+    c10::cuda::CUDAGuard guard(out.device());
+    fs2::comm_reducescatter_segments(make_peers(ptrs, rank, wait_limit_s), make_segments(offs, numels),
+                                     full_byte_off, out.data_ptr(), out.scalar_type() == at::kFloat, shard_numel,
+                                     static_cast<float>(scale), accumulate, static_cast<int>(slot),
+                                     static_cast<uint32_t>(epoch), static_cast<int>(blocks), status_dev_ptr(),
+                                     stream_of(out));
+    g_launches += 1;
+}
+
+void comm_allreduce_f32(const std::vector<int64_t>& ptrs, int64_t rank, int64_t byte_off, Tensor out, int64_t op,
+                        int64_t slot, int64_t epoch, double wait_limit_s) {
+    TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.scalar_type() == at::kFloat,
+                "comm_allreduce_f32: `out` must be a contiguous fp32 CUDA tensor");
+    TORCH_CHECK(byte_off % 16 == 0 && op >= 0 && op <= 4, "comm_allreduce_f32: bad argument");
+    c10::cuda::CUDAGuard guard(out.device());
+    const int64_t n = out.numel();
+    const int blocks = static_cast<int>(std::min<int64_t>(std::max<int64_t>((n + 255) / 256, 1), 64));
+    fs2::comm_allreduce_f32(make_peers(ptrs, rank, wait_limit_s), byte_off, out.data_ptr<float>(), n,
+                            static_cast<int>(op), static_cast<int>(slot), static_cast<uint32_t>(epoch), blocks,
+                            status_dev_ptr(), stream_of(out));
+    g_launches += 1;
+}
+
+void comm_pull(const std::vector<int64_t>& ptrs, int64_t rank, int64_t src_rank, int64_t byte_off, Tensor dst,
+               int64_t slot, int64_t epoch, double wait_limit_s) {
+    TORCH_CHECK(dst.is_cuda() && dst.is_contiguous() && aligned16(dst) && (dst.numel() * dst.element_size()) % 16 == 0,
+                "comm_pull: `dst` must be contiguous, 16-byte aligned and a multiple of 16 bytes");
+    TORCH_CHECK(src_rank >= 0 && src_rank < static_cast<int64_t>(ptrs.size()) && byte_off % 16 == 0, "comm_pull: bad argument");
+    c10::cuda::CUDAGuard guard(dst.device());
+    const int64_t bytes = dst.numel() * dst.element_size();
+    const int blocks = static_cast<int>(std::min<int64_t>(std::max<int64_t>(bytes / (512 * 16 * 4), 1), 32));
+    fs2::comm_pull(make_peers(ptrs, rank, wait_limit_s), static_cast<int>(src_rank), byte_off, dst.data_ptr(), bytes,
+                   static_cast<int>(slot), static_cast<uint32_t>(epoch), blocks, status_dev_ptr(), stream_of(dst));
+    g_launches += 1;
+}
+
+void comm_alltoall(const std::vector<int64_t>& ptrs, int64_t rank, int64_t byte_off, Tensor dst,
+                   const Tensor& send_offs, int64_t slot, int64_t epoch, double wait_limit_s) {
+    TORCH_CHECK(dst.is_cuda() && dst.is_contiguous(), "comm_alltoall: `dst` must be a contiguous CUDA tensor");
+    const int64_t W = static_cast<int64_t>(ptrs.size());
+    TORCH_CHECK(send_offs.is_cuda() && send_offs.scalar_type() == at::kLong && send_offs.is_contiguous() &&
+                    send_offs.numel() == W * (W + 1),
+                "comm_alltoall: `send_offs` must be an int64 [W, W + 1] CUDA tensor");
+    c10::cuda::CUDAGuard guard(dst.device());
+    const int64_t row = dst.dim() > 1 ? dst.numel() / std::max<int64_t>(dst.size(0), 1) : 1;
+    fs2::comm_alltoall(make_peers(ptrs, rank, wait_limit_s), byte_off, dst.data_ptr(),
+                       reinterpret_cast<const long long*>(send_offs.data_ptr<int64_t>()),
+                       static_cast<int>(row * dst.element_size()), static_cast<int>(slot),
+                       static_cast<uint32_t>(epoch), 8, status_dev_ptr(), stream_of(dst));
+    g_launches += 1;
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -439,6 +562,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("multi_tensor_adamw", &multi_tensor_adamw);
     m.def("multi_tensor_l2_norm_sq", &multi_tensor_l2_norm_sq);
     m.def("multi_tensor_scale", &multi_tensor_scale);
+    m.def("comm_barrier", &comm_barrier);
+    m.def("comm_signal", &comm_signal);
+    m.def("comm_allgather_segments", &comm_allgather_segments);
+    m.def("comm_reducescatter_segments", &comm_reducescatter_segments);
+    m.def("comm_allreduce_f32", &comm_allreduce_f32);
+    m.def("comm_pull", &comm_pull);
+    m.def("comm_alltoall", &comm_alltoall);
     m.def("launch_count", &launch_count);
     m.def("reset_launch_count", &reset_launch_count);
     m.def("check_status", &check_status, "Raises if a kernel recorded a bounded-wait failure.");

@@ -1,0 +1,335 @@
+// Collective kernels over symmetric (peer-mapped) memory for one NVSwitch box.
+//
+// Every rank maps the same arena of every peer into its address space; the
+// kernels move data with plain 16-byte peer loads/stores over NVLink -- no TMA,
+// no library call. They use no shared memory and few registers, so their CTAs
+// co-reside with the persistent GEMM CTAs instead of displacing them.
+//
+// Synchronisation is by monotonically increasing flags ("epochs") that live in
+// the first bytes of each rank's arena. A rank signals by storing the epoch
+// into slot [slot * MAX_RANKS + its_rank] of every peer's flag area; a rank
+// waits by polling its own flag area. Every wait is bounded: after the time
+// limit the kernel stores a code into the host-mapped status word and returns
+// without touching peer data, so the context stays usable.
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "comm.h"
+#include "common.cuh"
+
+namespace fs2 {
+
+namespace {
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// 16-byte load that bypasses L1 (peer data changes between epochs).
+__device__ __forceinline__ uint4 ld_peer16(const void* p) {
+    uint4 v;
+    asm volatile("ld.relaxed.sys.global.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p)
+                 : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void st16(void* p, uint4 v) {
+    asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+
+// Thread 0 of the block signals (optionally) and waits until every peer's flag
+// in `slot` reached `epoch`; returns false for the whole block on time-out.
+__device__ __forceinline__ bool signal_and_wait(const CommPeers& peers, int slot, uint32_t epoch, bool do_signal,
+                                                int* status, int site) {
+    __shared__ int ok_flag;
+    if (threadIdx.x == 0) {
+        int ok = 1;
+        if (do_signal && blockIdx.x == 0) {
+            __threadfence_system();
+            for (int r = 0; r < peers.world; ++r) {
+                uint32_t* f = reinterpret_cast<uint32_t*>(peers.base[r]) + slot * kCommMaxRanks + peers.rank;
+                st_release_sys(f, epoch);
+            }
+        }
+        const uint32_t* mine = reinterpret_cast<const uint32_t*>(peers.base[peers.rank]) + slot * kCommMaxRanks;
+        const uint64_t t0 = global_timer_ns();
+        for (int r = 0; r < peers.world && ok; ++r) {
+            uint32_t spins = 0;
+            // epochs only grow; compare with wrap-around safe arithmetic
+            while (static_cast<int32_t>(ld_acquire_sys(mine + r) - epoch) < 0) {
+                if ((++spins & 255u) == 0 && global_timer_ns() - t0 > peers.wait_limit_ns) {
+                    ok = 0;
+                    report_status(status, kStatusTimeout | (site << 8));
+                    break;
+                }
+            }
+        }
+        ok_flag = ok;
+    }
+    __syncthreads();
+    return ok_flag != 0;
+}
+
+// ---------------------------------------------------------------------------
+__global__ void barrier_kernel(CommPeers peers, int slot, uint32_t epoch, int* status) {
+    signal_and_wait(peers, slot, epoch, true, status, 16);
+}
+
+__global__ void signal_kernel(CommPeers peers, int slot, uint32_t epoch) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        __threadfence_system();
+        for (int r = 0; r < peers.world; ++r) {
+            uint32_t* f = reinterpret_cast<uint32_t*>(peers.base[r]) + slot * kCommMaxRanks + peers.rank;
+            st_release_sys(f, epoch);
+        }
+    }
+}
+
+// Segment table: parameter `s` owns [off, off + numel) of every rank's shard
+// buffer and the region [W * off, W * (off + numel)) of a full buffer, rank r's
+// slice starting at W * off + r * numel.
+
+// All-gather: full[W*off_s + r*numel_s + i] = peer_r.shard[off_s + i]. 2-byte elements.
+// grid = (blocks, W); blockIdx.y selects the source rank (rotated so that ranks start on
+// different peers). Each thread keeps AG_UNROLL independent 16-byte peer loads in flight:
+// NVLink latency x bandwidth needs megabytes outstanding per GPU.
+constexpr int AG_UNROLL = 8;
+
+__global__ void __launch_bounds__(512) allgather_segments_kernel(
+    CommPeers peers, CommSegments segs, long long shard_byte_off, __nv_bfloat16* __restrict__ full,
+    long long shard_numel, int slot, uint32_t epoch, int* status) {
+    if (epoch != 0 && !signal_and_wait(peers, slot, epoch, false, status, 17)) return;
+    const int W = peers.world;
+    const int r = (peers.rank + blockIdx.y) % W;
+    const __nv_bfloat16* src =
+        reinterpret_cast<const __nv_bfloat16*>(reinterpret_cast<const char*>(peers.base[r]) + shard_byte_off);
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (int s = 0; s < segs.count; ++s) {
+        const long long off = segs.off[s];
+        const long long nvec = segs.numel[s] / 8;
+        const __nv_bfloat16* sp = src + off;
+        __nv_bfloat16* dp = full + W * off + r * segs.numel[s];
+        for (long long v0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v0 < nvec;
+             v0 += stride * AG_UNROLL) {
+            uint4 buf[AG_UNROLL];
+#pragma unroll
+            for (int u = 0; u < AG_UNROLL; ++u) {
+                const long long v = v0 + u * stride;
+                if (v < nvec) buf[u] = ld_peer16(sp + v * 8);
+            }
+#pragma unroll
+            for (int u = 0; u < AG_UNROLL; ++u) {
+                const long long v = v0 + u * stride;
+                if (v < nvec) st16(dp + v * 8, buf[u]);
+            }
+        }
+    }
+}
+
+// Reduce-scatter: out[off_s + i] = scale * sum_r peer_r.full[W*off_s + rank*numel_s + i]; bf16 in,
+// fp32 accumulate. All W peer loads of RS_UNROLL vectors are issued before the first use.
+constexpr int RS_UNROLL = 2;
+
+template <typename OutT, int W>
+__device__ __forceinline__ void reducescatter_body(const CommPeers& peers, const CommSegments& segs,
+                                                   long long full_byte_off, OutT* __restrict__ out, float scale,
+                                                   int accumulate) {
+    const __nv_bfloat16* srcs[W];
+#pragma unroll
+    for (int k = 0; k < W; ++k) {
+        const int r = (peers.rank + k) % W;
+        srcs[k] = reinterpret_cast<const __nv_bfloat16*>(reinterpret_cast<const char*>(peers.base[r]) + full_byte_off);
+    }
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (int s = 0; s < segs.count; ++s) {
+        const long long off = segs.off[s];
+        const long long nvec = segs.numel[s] / 8;
+        const long long src_base = W * off + peers.rank * segs.numel[s];
+        for (long long v0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v0 < nvec;
+             v0 += stride * RS_UNROLL) {
+            uint4 raw[RS_UNROLL][W];
+#pragma unroll
+            for (int u = 0; u < RS_UNROLL; ++u) {
+                const long long v = v0 + u * stride;
+                if (v < nvec) {
+#pragma unroll
+                    for (int k = 0; k < W; ++k) raw[u][k] = ld_peer16(srcs[k] + src_base + v * 8);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < RS_UNROLL; ++u) {
+                const long long v = v0 + u * stride;
+                if (v >= nvec) continue;
+                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int k = 0; k < W; ++k) {
+                    bf16x8 p;
+                    *reinterpret_cast<uint4*>(&p) = raw[u][k];
+                    float f[8];
+                    unpack8(p, f);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc[e] += f[e];
+                }
+                const size_t j = static_cast<size_t>(off + v * 8);
+                if (accumulate) {
+                    float prev[8];
+                    load8(out, j, prev);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc[e] = acc[e] * scale + prev[e];
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc[e] *= scale;
+                }
+                store8(out, j, acc);
+            }
+        }
+    }
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(512) reducescatter_segments_kernel(
+    CommPeers peers, CommSegments segs, long long full_byte_off, OutT* __restrict__ out, long long shard_numel,
+    float scale, int accumulate, int slot, uint32_t epoch, int* status) {
+    if (!signal_and_wait(peers, slot, epoch, true, status, 18)) return;
+    switch (peers.world) {
+        case 1: reducescatter_body<OutT, 1>(peers, segs, full_byte_off, out, scale, accumulate); break;
+        case 2: reducescatter_body<OutT, 2>(peers, segs, full_byte_off, out, scale, accumulate); break;
+        case 3: reducescatter_body<OutT, 3>(peers, segs, full_byte_off, out, scale, accumulate); break;
+        case 4: reducescatter_body<OutT, 4>(peers, segs, full_byte_off, out, scale, accumulate); break;
+        case 5: reducescatter_body<OutT, 5>(peers, segs, full_byte_off, out, scale, accumulate); break;
+        case 6: reducescatter_body<OutT, 6>(peers, segs, full_byte_off, out, scale, accumulate); break;
+        case 7: reducescatter_body<OutT, 7>(peers, segs, full_byte_off, out, scale, accumulate); break;
+        default: reducescatter_body<OutT, 8>(peers, segs, full_byte_off, out, scale, accumulate); break;
+    }
+}
+
+// One-shot all-reduce of `numel` fp32 values staged at `byte_off` of every arena.
+// op: 0 sum, 1 mean, 2 product, 3 min, 4 max.
+__global__ void allreduce_f32_kernel(CommPeers peers, long long byte_off, float* __restrict__ out, long long numel,
+                                     int op, int slot, uint32_t epoch, int* status) {
+    if (!signal_and_wait(peers, slot, epoch, true, status, 19)) return;
+    const int W = peers.world;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < numel;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        float acc = 0.f;
+        for (int r = 0; r < W; ++r) {
+            const float* src = reinterpret_cast<const float*>(reinterpret_cast<const char*>(peers.base[r]) + byte_off);
+            float v;
+            asm volatile("ld.relaxed.sys.global.L1::no_allocate.f32 %0, [%1];" : "=f"(v) : "l"(src + i) : "memory");
+            if (r == 0) acc = v;
+            else if (op <= 1) acc += v;
+            else if (op == 2) acc *= v;
+            else if (op == 3) acc = fminf(acc, v);
+            else acc = fmaxf(acc, v);
+        }
+        if (op == 1) acc /= W;
+        out[i] = acc;
+    }
+}
+
+// Pull copy: dst[i] = peer_src.arena[byte_off + i] for `bytes` bytes (multiple of 16).
+__global__ void pull_kernel(CommPeers peers, int src_rank, long long byte_off, char* __restrict__ dst,
+                            long long bytes, int slot, uint32_t epoch, int* status) {
+    if (!signal_and_wait(peers, slot, epoch, true, status, 20)) return;
+    const char* src = reinterpret_cast<const char*>(peers.base[src_rank]) + byte_off;
+    const long long nvec = bytes / 16;
+    for (long long v = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v < nvec;
+         v += static_cast<long long>(gridDim.x) * blockDim.x)
+        st16(dst + v * 16, ld_peer16(src + v * 16));
+}
+
+// All-to-all with equal or variable splits, pull based. Every rank staged its
+// send buffer at `byte_off`; `send_offs` ([W, W+1] int64 element offsets, row r =
+// rank r's prefix sums over destinations) is replicated on every rank.
+__global__ void alltoall_kernel(CommPeers peers, long long byte_off, char* __restrict__ dst,
+                                const long long* __restrict__ send_offs, int elem_bytes, int slot, uint32_t epoch,
+                                int* status) {
+    if (!signal_and_wait(peers, slot, epoch, true, status, 21)) return;
+    const int W = peers.world;
+    const int src_rank = blockIdx.y;
+    long long dst_elem = 0;
+    for (int r = 0; r < src_rank; ++r)
+        dst_elem += send_offs[r * (W + 1) + peers.rank + 1] - send_offs[r * (W + 1) + peers.rank];
+    const long long beg = send_offs[src_rank * (W + 1) + peers.rank];
+    const long long end = send_offs[src_rank * (W + 1) + peers.rank + 1];
+    const char* src = reinterpret_cast<const char*>(peers.base[src_rank]) + byte_off + beg * elem_bytes;
+    char* out = dst + dst_elem * elem_bytes;
+    const long long bytes = (end - beg) * elem_bytes;
+    const bool vec_ok = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+    if (vec_ok) {
+        const long long nvec = bytes / 16;
+        for (long long v = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v < nvec;
+             v += static_cast<long long>(gridDim.x) * blockDim.x)
+            st16(out + v * 16, ld_peer16(src + v * 16));
+        for (long long b = nvec * 16 + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; b < bytes;
+             b += static_cast<long long>(gridDim.x) * blockDim.x)
+            out[b] = src[b];
+    } else {
+        for (long long b = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; b < bytes;
+             b += static_cast<long long>(gridDim.x) * blockDim.x)
+            out[b] = src[b];
+    }
+}
+
+}  // namespace
+
+void comm_barrier(const CommPeers& peers, int slot, uint32_t epoch, int* status, cudaStream_t st) {
+    barrier_kernel<<<1, 32, 0, st>>>(peers, slot, epoch, status);
+}
+
+void comm_signal(const CommPeers& peers, int slot, uint32_t epoch, cudaStream_t st) {
+    signal_kernel<<<1, 32, 0, st>>>(peers, slot, epoch);
+}
+
+void comm_allgather_segments(const CommPeers& peers, const CommSegments& segs, long long shard_byte_off, void* full,
+                             long long shard_numel, int slot, uint32_t epoch, int blocks, int* status,
+                             cudaStream_t st) {
+    dim3 grid(blocks, peers.world);
+    allgather_segments_kernel<<<grid, 512, 0, st>>>(peers, segs, shard_byte_off, static_cast<__nv_bfloat16*>(full),
+                                                    shard_numel, slot, epoch, status);
+}
+
+void comm_reducescatter_segments(const CommPeers& peers, const CommSegments& segs, long long full_byte_off, void* out,
+                                 bool out_f32, long long shard_numel, float scale, bool accumulate, int slot,
+                                 uint32_t epoch, int blocks, int* status, cudaStream_t st) {
+    if (out_f32)
+        reducescatter_segments_kernel<float><<<blocks, 512, 0, st>>>(peers, segs, full_byte_off,
+                                                                     static_cast<float*>(out), shard_numel, scale,
+                                                                     accumulate ? 1 : 0, slot, epoch, status);
+    else
+        reducescatter_segments_kernel<__nv_bfloat16><<<blocks, 512, 0, st>>>(
+            peers, segs, full_byte_off, static_cast<__nv_bfloat16*>(out), shard_numel, scale, accumulate ? 1 : 0,
+            slot, epoch, status);
+}
+
+void comm_allreduce_f32(const CommPeers& peers, long long byte_off, float* out, long long numel, int op, int slot,
+                        uint32_t epoch, int blocks, int* status, cudaStream_t st) {
+    allreduce_f32_kernel<<<blocks, 256, 0, st>>>(peers, byte_off, out, numel, op, slot, epoch, status);
+}
+
+void comm_pull(const CommPeers& peers, int src_rank, long long byte_off, void* dst, long long bytes, int slot,
+               uint32_t epoch, int blocks, int* status, cudaStream_t st) {
+    pull_kernel<<<blocks, 512, 0, st>>>(peers, src_rank, byte_off, static_cast<char*>(dst), bytes, slot, epoch,
+                                        status);
+}
+
+void comm_alltoall(const CommPeers& peers, long long byte_off, void* dst, const long long* send_offs, int elem_bytes,
+                   int slot, uint32_t epoch, int blocks, int* status, cudaStream_t st) {
+    dim3 grid(blocks, peers.world);
+    alltoall_kernel<<<grid, 512, 0, st>>>(peers, byte_off, static_cast<char*>(dst), send_offs, elem_bytes, slot,
+                                          epoch, status);
+}
+
+}  // namespace fs2

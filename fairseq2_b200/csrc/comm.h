@@ -1,0 +1,42 @@
+// Host launchers of the symmetric-memory collective kernels (comm.cu).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace fs2 {
+
+constexpr int kCommMaxRanks = 8;       // one NVSwitch box
+constexpr int kCommMaxSegments = 32;
+constexpr int kCommFlagBytes = 64 * 1024;  // flag area at the start of every arena
+
+struct CommPeers {
+    void* base[kCommMaxRanks];  // arena base of every rank, mapped into this process
+    int world;
+    int rank;
+    unsigned long long wait_limit_ns;
+};
+
+struct CommSegments {
+    int count;
+    long long off[kCommMaxSegments];    // element offset of the segment in a rank's shard buffer
+    long long numel[kCommMaxSegments];  // elements per rank
+};
+
+void comm_barrier(const CommPeers& peers, int slot, uint32_t epoch, int* status, cudaStream_t st);
+void comm_signal(const CommPeers& peers, int slot, uint32_t epoch, cudaStream_t st);
+void comm_allgather_segments(const CommPeers& peers, const CommSegments& segs, long long shard_byte_off, void* full,
+                             long long shard_numel, int slot, uint32_t epoch, int blocks, int* status,
+                             cudaStream_t st);
+void comm_reducescatter_segments(const CommPeers& peers, const CommSegments& segs, long long full_byte_off, void* out,
+                                 bool out_f32, long long shard_numel, float scale, bool accumulate, int slot,
+                                 uint32_t epoch, int blocks, int* status, cudaStream_t st);
+void comm_allreduce_f32(const CommPeers& peers, long long byte_off, float* out, long long numel, int op, int slot,
+                        uint32_t epoch, int blocks, int* status, cudaStream_t st);
+void comm_pull(const CommPeers& peers, int src_rank, long long byte_off, void* dst, long long bytes, int slot,
+               uint32_t epoch, int blocks, int* status, cudaStream_t st);
+void comm_alltoall(const CommPeers& peers, long long byte_off, void* dst, const long long* send_offs, int elem_bytes,
+                   int slot, uint32_t epoch, int blocks, int* status, cudaStream_t st);
+
+}  // namespace fs2

@@ -106,6 +106,7 @@ class FlatParamUnit:
         self.grads_ready = False
         self.unsharded = W == 1
         self._ag_event: torch.cuda.Event | None = None
+        self.arena: Any = None
 
         # shard parameters handed to the optimizer / state dict
         self.shard_params: list[Parameter] = []
@@ -126,6 +127,22 @@ class FlatParamUnit:
         if W == 1:
             self._bind_full(self.low_shard)
 
+    # ------------------------------------------------------------- arena
+    def attach_arena(self, arena: Any, slot: int) -> None:
+        """Moves the bf16 shard and the flat gradient buffer into the symmetric
+        arena so that peers can pull them directly over NVLink."""
+        self.arena = arena
+        self.slot = slot
+        self.low_off, low = arena.alloc_tensor(self.shard_size, self.param_dtype)
+        low.copy_(self.low_shard)
+        self.low_shard = low
+        self.grad_off, gf = arena.alloc_tensor(self.world * self.shard_size, self.param_dtype)
+        self.grad_full = gf
+        self._bind_grad_sinks(gf, filled=False)
+        self.seg_offs = [s.shard_off for s in self.specs]
+        self.seg_numels = [s.shard_numel for s in self.specs]
+        self.rs_epoch = 0
+
     # ------------------------------------------------------------- views
     def _region(self, buf: Tensor, s: _ParamSpec) -> Tensor:
         """``[W * chunk, row]`` region of parameter ``s`` inside a full-size flat buffer."""
@@ -143,7 +160,7 @@ class FlatParamUnit:
             cp.grad_sink_filled = filled  # type: ignore[attr-defined]
 
     # -------------------------------------------------------- collectives
-    def unshard(self, comm_stream: "torch.cuda.Stream | None") -> None:
+    def unshard(self, comm_stream: "torch.cuda.Stream | None", param_epoch: int = 0) -> None:
         """Starts the all-gather of the bf16 shards into a fresh full buffer."""
         if self.unsharded:
             return
@@ -156,8 +173,14 @@ class FlatParamUnit:
         else:
             ctx = _null()
         with ctx:
-            _coalesced_all_gather(self.gang, [self._region(full, s).view(W, s.shard_numel) for s in self.specs],
-                                  [self.low_shard[s.shard_off: s.shard_off + s.shard_numel] for s in self.specs])
+            if self.arena is not None:
+                a = self.arena
+                ag_blocks = max(32 // W, 4)
+                a.ext.comm_allgather_segments(a.peer_ptrs, a.rank, self.seg_offs, self.seg_numels, self.low_off, full,
+                                              1, param_epoch, ag_blocks, a.wait_limit_s)
+            else:
+                _coalesced_all_gather(self.gang, [self._region(full, s).view(W, s.shard_numel) for s in self.specs],
+                                      [self.low_shard[s.shard_off: s.shard_off + s.shard_numel] for s in self.specs])
             if comm_stream is not None:
                 ev = torch.cuda.Event()
                 ev.record(comm_stream)
@@ -182,7 +205,7 @@ class FlatParamUnit:
     def prepare_grads(self) -> None:
         """Allocates (or reuses, when accumulating) the flat bf16 gradient buffer
         and points every parameter's ``grad_sink`` into it."""
-        if self.grad_full is None:
+        if self.grad_full is None and self.arena is None:
             self.grad_full = torch.empty(self.world * self.shard_size, device=self.device, dtype=self.param_dtype)
             if self.world > 1:
                 self.grad_full.zero_()  # padding rows take part in the reduce-scatter
@@ -224,6 +247,21 @@ class FlatParamUnit:
             ctx: Any = torch.cuda.stream(comm_stream)
         else:
             ctx = _null()
+        if self.arena is not None:
+            # bf16 gradients are pulled from every peer and summed in fp32 by one kernel
+            a = self.arena
+            with ctx:
+                acc = self.grad_shard is not None and self.grads_ready
+                if not acc:
+                    self.grad_shard = torch.empty(self.shard_size, device=self.device, dtype=torch.float32)
+                self.rs_epoch += 1
+                a.ext.comm_reducescatter_segments(a.peer_ptrs, a.rank, self.seg_offs, self.seg_numels, self.grad_off,
+                                                  self.grad_shard, (1.0 / W) if average else 1.0, acc, 2 + self.slot,
+                                                  self.rs_epoch, 48, a.wait_limit_s)
+            self.grads_ready = True
+            for cp in self.compute_params:
+                cp.grad_sink_filled = False  # type: ignore[attr-defined]
+            return
         with ctx:
             if self.reduce_dtype != gf.dtype:
                 gf = gf.to(self.reduce_dtype)
@@ -254,6 +292,10 @@ class FlatParamUnit:
                 for cp in self.compute_params:
                     cp.grad_sink_filled = False  # type: ignore[attr-defined]
             self.grad_shard = None
+        elif self.arena is not None:
+            self.grad_shard = None
+            for cp in self.compute_params:
+                cp.grad_sink_filled = False  # type: ignore[attr-defined]
         else:
             self.grad_shard = None
             self.grad_full = None
@@ -322,7 +364,7 @@ class FSDP(Module):
 
     def __init__(self, module: Module, gangs: Gangs, *, wrap_policy: FSDPWrapPolicy | None = layerwise_wrap_policy,
                  param_dtype: DataType = torch.bfloat16, fp32_reduce: bool = True,
-                 reshard_after_forward: bool = True, overlap: bool = True) -> None:
+                 reshard_after_forward: bool = True, overlap: bool = True, comm: str = "auto") -> None:
         super().__init__()
         self.module = module
         self.gangs = gangs
@@ -380,6 +422,28 @@ class FSDP(Module):
         self._grad_scale: Tensor | None = None
         self._in_backward = False
         self._pending_reduce: list[FlatParamUnit] = []
+        self.param_epoch = 0
+        self.arena: Any = None
+        if comm not in ("auto", "symm", "nccl"):
+            raise ValueError(f"`comm` must be 'auto', 'symm' or 'nccl', but is '{comm}' instead.")
+        if W > 1 and comm != "nccl" and param_dtype == torch.bfloat16:
+            from fairseq2_b200.parallel.symm import SymmetricArena, symmetric_memory_available
+
+            if symmetric_memory_available(self.gang):
+                need = sum((1 + W) * u.shard_size * 2 + 1024 for u in self.all_units) + (1 << 20)
+                try:
+                    self.arena = SymmetricArena(self.gang, need)  # type: ignore[arg-type]
+                    for i, u in enumerate(self.all_units):
+                        u.attach_arena(self.arena, i)
+                    torch.cuda.synchronize(dev)
+                    self.gang.barrier()
+                except Exception as ex:  # noqa: BLE001
+                    if comm == "symm":
+                        raise
+                    log.warning("Symmetric memory is not usable ({}); FSDP falls back to NCCL collectives.", ex)
+                    self.arena = None
+            elif comm == "symm":
+                raise RuntimeError("Symmetric-memory communication was requested but is not available.")
         self._install_hooks()
         n = sum(u.shard_size for u in self.all_units)
         log.info("FSDP: {} unit(s), {:,} local shard elements, world size {}.", len(self.all_units), n, W)
@@ -395,12 +459,12 @@ class FSDP(Module):
     def _make_pre_forward(self, idx: int):  # type: ignore[no-untyped-def]
         def hook(m: Module, args: Any) -> None:
             u = self.units[idx]
-            u.unshard(self.comm_stream)
+            u.unshard(self.comm_stream, self.param_epoch)
             u.wait_unshard()
             if torch.is_grad_enabled():
                 u.prepare_grads()
             if idx + 1 < len(self.units):           # prefetch the next layer
-                self.units[idx + 1].unshard(self.comm_stream)
+                self.units[idx + 1].unshard(self.comm_stream, self.param_epoch)
         return hook
 
     def _make_post_forward(self, idx: int):  # type: ignore[no-untyped-def]
@@ -415,11 +479,11 @@ class FSDP(Module):
             self._in_backward = True
             self._flush_pending_reduce()
             u = self.units[idx]
-            u.unshard(self.comm_stream)
+            u.unshard(self.comm_stream, self.param_epoch)
             u.wait_unshard()
             u.prepare_grads()
             if idx - 1 >= 0:
-                self.units[idx - 1].unshard(self.comm_stream)
+                self.units[idx - 1].unshard(self.comm_stream, self.param_epoch)
         return hook
 
     def _make_post_backward(self, idx: int):  # type: ignore[no-untyped-def]
@@ -442,12 +506,12 @@ class FSDP(Module):
     def forward(self, *args: Any, **kwargs: Any) -> Any:
         self._in_backward = False
         if self.root_unit is not None:
-            self.root_unit.unshard(self.comm_stream)
+            self.root_unit.unshard(self.comm_stream, self.param_epoch)
             self.root_unit.wait_unshard()
             if torch.is_grad_enabled():
                 self.root_unit.prepare_grads()
         if self.units:
-            self.units[0].unshard(self.comm_stream)
+            self.units[0].unshard(self.comm_stream, self.param_epoch)
         return self.module(*args, **kwargs)
 
     def finish_backward(self) -> None:
@@ -469,10 +533,16 @@ class FSDP(Module):
                     self.replica_gang.all_reduce(u.grad_shard, ReduceOperation.MEAN)
 
     def after_optimizer_step(self) -> None:
-        """The optimizer wrote new bf16 shards: gathered copies are stale."""
+        """The optimizer wrote new bf16 shards: gathered copies are stale. With the
+        symmetric arena this is also the one synchronisation point of a step:
+        every rank announces "my shards of step N are written" and the next
+        all-gathers wait for all peers' announcements."""
         for u in self.all_units:
             if u.world > 1:
                 u.reshard()
+        if self.arena is not None:
+            self.param_epoch += 1
+            self.arena.signal(1, self.param_epoch)
 
     # ------------------------------------------------------------ grad control
     @contextmanager
@@ -562,13 +632,16 @@ class FSDP(Module):
             u.refresh_low_from_master()
             if u.world > 1:
                 u.reshard()
+        if self.arena is not None:
+            torch.cuda.synchronize(self.device)
+            self.gang.barrier()
 
     @contextmanager
     def summon_full_parameters(self) -> Iterator[None]:
         """All parameters gathered (bf16 compute copies) for inference/export."""
         was = [u.unsharded for u in self.all_units]
         for u in self.all_units:
-            u.unshard(None)
+            u.unshard(None, self.param_epoch)
         try:
             yield
         finally:

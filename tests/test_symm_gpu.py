@@ -1,0 +1,127 @@
+"""Symmetric-memory collectives and the zero-copy FSDP path on 2+ GPUs,
+checked against closed-form expectations and against the NCCL path."""
+from __future__ import annotations
+
+import os
+
+import pytest
+import torch
+
+from tests.dist_utils import run_distributed
+
+pytestmark = pytest.mark.gpu
+
+
+def _need_gpus(n: int) -> None:
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+
+
+def _collectives_worker(rank: int, world: int):
+    from fairseq2_b200.gang import ProcessGroupGang, ReduceOperation
+    from fairseq2_b200.parallel.symm import SymmGang
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    base = ProcessGroupGang.create_default_process_group(dev)
+    g = SymmGang(base, staging_bytes=8 << 20)
+    out = {}
+    t = torch.full((1000,), float(rank + 1), device=dev)
+    g.all_reduce(t, ReduceOperation.SUM)
+    out["sum"] = float(t[0]), float(t[-1])
+    t = torch.full((7,), float(rank + 1), device=dev, dtype=torch.bfloat16)
+    g.all_reduce(t, ReduceOperation.MAX)
+    out["max"] = float(t[0])
+    inp = torch.arange(10, device=dev, dtype=torch.int64) + 100 * rank
+    ag = torch.empty((world, 10), device=dev, dtype=torch.int64)
+    g.all_gather(ag, inp)
+    out["ag"] = ag.cpu().tolist()
+    b = torch.full((33,), float(rank), device=dev)
+    g.broadcast(b, source_rank=world - 1)
+    out["bcast"] = float(b[0])
+    rs_in = torch.stack([torch.full((16,), float(rank * 10 + j), device=dev) for j in range(world)])
+    rs_out = torch.empty(16, device=dev)
+    g.reduce_scatter(rs_out, rs_in, ReduceOperation.SUM)
+    out["rs"] = float(rs_out[0])
+    # variable all-to-all: rank r sends (r + j + 1) rows to rank j
+    isz = [rank + j + 1 for j in range(world)]
+    osz = [j + rank + 1 for j in range(world)]
+    send = torch.cat([torch.full((n, 4), float(rank * 100 + j), device=dev) for j, n in enumerate(isz)])
+    recv = torch.empty((sum(osz), 4), device=dev)
+    g.all_to_all(recv, send, osz, isz)
+    out["a2a"] = [float(x[0, 0]) for x in recv.split(osz)]
+    g.barrier()
+    torch.cuda.synchronize()
+    g.arena.ext.check_status()
+    g.close()
+    return out
+
+
+def test_symm_gang_collectives() -> None:
+    _need_gpus(2)
+    world = 2
+    res = run_distributed(_collectives_worker, world)
+    for rank, r in enumerate(res):
+        assert r["sum"] == (3.0, 3.0)
+        assert r["max"] == 2.0
+        assert r["ag"] == [[i + 100 * q for i in range(10)] for q in range(world)]
+        assert r["bcast"] == float(world - 1)
+        assert r["rs"] == sum(q * 10 + rank for q in range(world))
+        assert r["a2a"] == [float(q * 100 + rank) for q in range(world)]
+
+
+def _fsdp_worker(rank: int, world: int, comm: str):
+    import numpy as np
+
+    from fairseq2_b200.datasets.synthetic import make_packed_sft_example
+    from fairseq2_b200.gang import ProcessGroupGang, create_fsdp_gangs, create_parallel_gangs
+    from fairseq2_b200.models.llama import LLaMAConfig, create_llama_model
+    from fairseq2_b200.nn import BatchLayout
+    from fairseq2_b200.ops import require_ext
+    from fairseq2_b200.optim import AdamW
+    from fairseq2_b200.parallel.fsdp import FSDP
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    root = ProcessGroupGang.create_default_process_group(dev)
+    gangs = create_fsdp_gangs(create_parallel_gangs(root))
+    cfg = LLaMAConfig(model_dim=512, max_seq_len=2048, vocab_size=4096, num_layers=3, num_attn_heads=4,
+                      num_key_value_heads=2, ffn_inner_dim=1408, ffn_inner_dim_scale=1.0,
+                      ffn_inner_dim_multiple_of=1, rope_theta=500000.0, shard_embed_dim=False)
+    torch.manual_seed(0)
+    with torch.device("meta"):
+        model = create_llama_model(cfg, gangs)
+    fsdp = FSDP(model, gangs, param_dtype=torch.bfloat16, comm=comm, fp32_reduce=True)
+    assert (fsdp.arena is not None) == (comm == "symm")
+    opt = AdamW(fsdp.parameters(), lr=1e-3)
+    rng = np.random.default_rng(5 + rank)
+    losses = []
+    for _ in range(3):
+        ex = make_packed_sft_example(rng, 1024, cfg.vocab_size, doc_len_range=(64, 512))
+        tokens, mask = ex.tokens.to(dev), ex.target_mask.to(dev)
+        layout = BatchLayout((1024,), ex.seq_lens, packed=True, device=dev)
+        fsdp.zero_grad()
+        loss = fsdp(tokens[:-1], layout, targets=tokens[1:], target_mask=mask)
+        loss.backward()
+        fsdp.finish_backward()
+        fsdp.scale_grads(1.0 / 1024)
+        gn = fsdp.clip_grad_norm(1.0)
+        opt.step(grad_scale=fsdp.grad_scale)
+        fsdp.after_optimizer_step()
+        losses.append((float(loss), float(gn)))
+    torch.cuda.synchronize()
+    require_ext().check_status()
+    root.close()
+    return losses
+
+
+def test_fsdp_symm_matches_nccl() -> None:
+    _need_gpus(2)
+    a = run_distributed(_fsdp_worker, 2, "symm")
+    b = run_distributed(_fsdp_worker, 2, "nccl")
+    for ra, rb in zip(a, b):
+        for (la, ga), (lb, gb) in zip(ra, rb):
+            assert abs(la - lb) / abs(lb) < 2e-2
+            assert abs(ga - gb) / abs(gb) < 5e-2
