@@ -107,6 +107,7 @@ class FlatParamUnit:
         self.unsharded = W == 1
         self._ag_event: torch.cuda.Event | None = None
         self.arena: Any = None
+        self.needs_reduce = False   # gradients were (or may have been) produced since the last reduction
 
         # shard parameters handed to the optimizer / state dict
         self.shard_params: list[Parameter] = []
@@ -205,6 +206,7 @@ class FlatParamUnit:
     def prepare_grads(self) -> None:
         """Allocates (or reuses, when accumulating) the flat bf16 gradient buffer
         and points every parameter's ``grad_sink`` into it."""
+        self.needs_reduce = True
         if self.grad_full is None and self.arena is None:
             self.grad_full = torch.empty(self.world * self.shard_size, device=self.device, dtype=self.param_dtype)
             if self.world > 1:
@@ -228,8 +230,9 @@ class FlatParamUnit:
 
     def reduce_grads(self, comm_stream: "torch.cuda.Stream | None", *, average: bool = True) -> None:
         """Reduce-scatters the flat gradient into ``grad_shard`` (mean over ranks)."""
-        if self.grad_full is None:
+        if self.grad_full is None or not self.needs_reduce:
             return
+        self.needs_reduce = False
         self.collect_autograd_grads()
         for s, cp in zip(self.specs, self.compute_params):
             if not getattr(cp, "grad_sink_filled", False) and getattr(cp, "grad_sink", None) is not None:
@@ -521,7 +524,7 @@ class FSDP(Module):
         self._flush_pending_reduce()
         if self._require_sync:
             for u in self.all_units:
-                if u.grad_full is not None and (u.world > 1 or not u.grads_ready):
+                if u.needs_reduce:
                     u.reduce_grads(self.comm_stream)
         if self.root_unit is not None and self.root_unit.world > 1 and self._require_sync:
             pass  # the root stays unsharded until the optimizer refreshed its shard
