@@ -66,7 +66,7 @@ def build_data(verbose: bool = False, force: bool = False) -> Path | None:
     build_dir = CSRC / "_build" / "data"
     build_dir.mkdir(parents=True, exist_ok=True)
     cpp_extension.load(name="_data", sources=[str(s) for s in sources],
-                       extra_cflags=["-O2", "-std=c++17", "-pthread"], extra_ldflags=["-pthread"],
+                       extra_cflags=["-O2", "-std=c++17", "-pthread"], extra_ldflags=["-pthread", "-lz"],
                        build_directory=str(build_dir), verbose=verbose, is_python_module=False, with_cuda=False)
     shutil.copy2(build_dir / "_data.so", target)
     return target

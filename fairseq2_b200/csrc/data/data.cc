@@ -45,7 +45,7 @@ MemoryBlock MemoryBlock::map_file(const std::string& path) {
     void* addr = ::mmap(nullptr, n, PROT_READ, MAP_PRIVATE, fd, 0);
     ::close(fd);
     if (addr == MAP_FAILED) throw ByteStreamError("The file '" + path + "' cannot be memory mapped.");
-    auto m = std::make_shared<Mapping>(Mapping{addr, n});
+    std::shared_ptr<Mapping> m(new Mapping{addr, n});  // built in place: a temporary would unmap on destruction
     return MemoryBlock(std::shared_ptr<const void>(m, addr), static_cast<const uint8_t*>(addr), n);
 }
 
@@ -115,11 +115,7 @@ Data data_from_py(py::handle h) {
     if (THPVariable_Check(h.ptr())) return Data(THPVariable_Unpack(h.ptr()));
     if (py::isinstance<MemoryBlock>(h)) return Data(h.cast<MemoryBlock>());
     if (py::isinstance<py::list>(h) || py::isinstance<py::tuple>(h)) {
-        const bool is_tuple = py::isinstance<py::tuple>(h);
-        if (is_tuple) {
-            // tuples stay opaque Python objects (their identity matters to user code), except
-            // that a tuple of plain values is converted for the native ops that index into it
-        }
+        // tuples are converted like lists so that native ops can index into them
         DataList out;
         auto seq = py::reinterpret_borrow<py::sequence>(h);
         out.reserve(py::len(seq));

@@ -217,18 +217,20 @@ public:
 using DataSourceFactory = std::function<std::unique_ptr<DataSource>()>;
 
 // ------------------------------------------------------------ DataPipeline
+// A DataPipeline is a cheap-to-copy handle: copies refer to the same underlying
+// source and position (like the Python object they are exposed as).
 class DataPipeline {
 public:
-    DataPipeline() = default;
-    explicit DataPipeline(DataSourceFactory f) : factory_(std::move(f)) {}
+    DataPipeline() : s_(std::make_shared<State>()) {}
+    explicit DataPipeline(DataSourceFactory f) : s_(std::make_shared<State>()) { s_->factory = std::move(f); }
 
     std::optional<Data> next();
     void reset(bool reset_rng = false);
     void record_position(Tape& t, bool strict = true) const;
     void reload_position(Tape& t, bool strict = true);
-    bool is_broken() const noexcept { return broken_; }
+    bool is_broken() const noexcept { return s_->broken; }
     Finitude finitude() const;
-    void set_max_num_warnings(size_t n) { max_num_warnings_ = n; }
+    void set_max_num_warnings(size_t n) { s_->max_num_warnings = n; }
 
     // static factories
     static class DataPipelineBuilder constant(Data example, std::optional<std::string> key);
@@ -244,20 +246,17 @@ public:
     void ensure_initialized() const;
 
 private:
+    struct State {
+        DataSourceFactory factory;
+        std::unique_ptr<DataSource> source;
+        bool broken = false;
+        size_t max_num_warnings = 0;
+        size_t warning_count = 0;
+    };
     void check_broken() const {
-        if (broken_) throw DataPipelineError("The data pipeline is broken by a previous operation and cannot be used.");
+        if (s_->broken) throw DataPipelineError("The data pipeline is broken by a previous operation and cannot be used.");
     }
-
-    DataSourceFactory factory_;
-    mutable std::unique_ptr<DataSource> source_;
-    mutable bool broken_ = false;
-    size_t max_num_warnings_ = 0;
-    size_t warning_count_ = 0;
-    mutable std::optional<Data> last_failed_;
-
-public:
-    std::optional<Data> last_failed_example() const { return last_failed_; }
-    void set_last_failed(Data d) const { last_failed_ = std::move(d); }
+    std::shared_ptr<State> s_;
 };
 
 // Python callables wrapped for use from worker threads.

@@ -1,0 +1,593 @@
+// Element selectors, collater, file/text/zip sources, file mapper and text
+// converters of the native data pipeline runtime.
+#include <dirent.h>
+#include <fnmatch.h>
+#include <sys/stat.h>
+#include <zlib.h>
+
+#include <algorithm>
+#include <cctype>
+#include <cstring>
+#include <fstream>
+#include <list>
+#include <map>
+#include <mutex>
+
+#include "extras.h"
+
+namespace fs2d {
+
+// ============================================================ element selector
+// Path mini-language: "a.b[0]", "[*].audio.data", several paths separated by ','.
+namespace {
+
+struct PathStep {
+    enum Kind { Key, Index, Wildcard } kind;
+    std::string key;
+    size_t index = 0;
+};
+
+std::vector<PathStep> parse_path(const std::string& s) {
+    std::vector<PathStep> out;
+    size_t i = 0;
+    auto fail = [&]() -> void {
+        throw std::invalid_argument("`selector` must be a well-formatted element path, but is '" + s + "' instead.");
+    };
+    if (s.empty()) fail();
+    while (i < s.size()) {
+        if (s[i] == '[') {
+            size_t j = s.find(']', i);
+            if (j == std::string::npos) fail();
+            std::string inner = s.substr(i + 1, j - i - 1);
+            if (inner == "*") {
+                out.push_back({PathStep::Wildcard, "", 0});
+            } else {
+                if (inner.empty() || !std::all_of(inner.begin(), inner.end(), ::isdigit)) fail();
+                out.push_back({PathStep::Index, "", static_cast<size_t>(std::stoull(inner))});
+            }
+            i = j + 1;
+            if (i < s.size() && s[i] == '.') {
+                ++i;
+                if (i >= s.size()) fail();
+            }
+        } else {
+            size_t j = i;
+            while (j < s.size() && s[j] != '.' && s[j] != '[') ++j;
+            if (j == i) fail();
+            out.push_back({PathStep::Key, s.substr(i, j - i), 0});
+            i = j;
+            if (i < s.size() && s[i] == '.') {
+                ++i;
+                if (i >= s.size() || s[i] == '.' ) fail();
+            }
+        }
+    }
+    return out;
+}
+
+std::vector<std::vector<PathStep>> parse_selector(const std::string& s) {
+    std::vector<std::vector<PathStep>> out;
+    size_t start = 0;
+    while (true) {
+        size_t c = s.find(',', start);
+        std::string part = s.substr(start, c == std::string::npos ? std::string::npos : c - start);
+        size_t a = part.find_first_not_of(' ');
+        size_t b = part.find_last_not_of(' ');
+        if (a == std::string::npos) throw std::invalid_argument("`selector` must not contain empty paths.");
+        out.push_back(parse_path(part.substr(a, b - a + 1)));
+        if (c == std::string::npos) break;
+        start = c + 1;
+    }
+    return out;
+}
+
+void visit_path(Data& d, const std::vector<PathStep>& path, size_t pos, const std::function<void(Data&)>& fn,
+                const std::string& sel) {
+    if (pos == path.size()) {
+        fn(d);
+        return;
+    }
+    const PathStep& st = path[pos];
+    auto missing = [&]() {
+        throw std::invalid_argument("The input data does not have an element at path '" + sel + "'.");
+    };
+    if (st.kind == PathStep::Key) {
+        Data* e = d.find(st.key);
+        if (e == nullptr) missing();
+        visit_path(*e, path, pos + 1, fn, sel);
+    } else if (st.kind == PathStep::Index) {
+        if (!d.is_list() || st.index >= d.as_list().size()) missing();
+        visit_path(d.as_list()[st.index], path, pos + 1, fn, sel);
+    } else {
+        if (!d.is_list()) missing();
+        for (auto& e : d.as_list()) visit_path(e, path, pos + 1, fn, sel);
+    }
+}
+
+}  // namespace
+
+Data apply_selected(Data&& d, const std::optional<std::string>& selector, const MapFn& fn) {
+    if (!selector) return fn(std::move(d));
+    Data copy = d.deep_copy();  // containers are shared; never mutate the caller's view
+    for (const auto& path : parse_selector(*selector))
+        visit_path(copy, path, 0, [&](Data& e) { e = fn(std::move(e)); }, *selector);
+    return copy;
+}
+
+const Data& select_single(const Data& d, const std::optional<std::string>& selector) {
+    if (!selector) return d;
+    const Data* found = nullptr;
+    auto paths = parse_selector(*selector);
+    visit_path(const_cast<Data&>(d), paths[0], 0, [&](Data& e) { found = &e; }, *selector);
+    if (found == nullptr) throw std::invalid_argument("The input data does not have an element at path '" + *selector + "'.");
+    return *found;
+}
+
+// ==================================================================== collater
+namespace {
+
+Data collate_tensors(const std::vector<at::Tensor>& ts, const std::optional<int64_t>& pad_value, int64_t pad_to_multiple,
+                     const std::string& path) {
+    if (!pad_value) {
+        for (const auto& t : ts)
+            if (t.sizes() != ts[0].sizes())
+                throw std::invalid_argument("The tensors at path '" + path +
+                                            "' in the bucket must all have the same shape when no padding value is set.");
+        return Data(at::stack(ts));
+    }
+    int64_t max_len = 0;
+    for (const auto& t : ts) {
+        if (t.dim() == 0) throw std::invalid_argument("Zero-dimensional tensors at path '" + path + "' cannot be padded.");
+        max_len = std::max<int64_t>(max_len, t.size(0));
+    }
+    if (pad_to_multiple > 1) max_len = ((max_len + pad_to_multiple - 1) / pad_to_multiple) * pad_to_multiple;
+    std::vector<int64_t> shape = ts[0].sizes().vec();
+    shape[0] = max_len;
+    shape.insert(shape.begin(), static_cast<int64_t>(ts.size()));
+    at::Tensor out = at::full(shape, *pad_value, ts[0].options());
+    std::vector<int64_t> lens;
+    bool ragged = false;
+    for (size_t i = 0; i < ts.size(); ++i) {
+        const int64_t n = ts[i].size(0);
+        lens.push_back(n);
+        if (n != max_len) ragged = true;
+        out[static_cast<int64_t>(i)].narrow(0, 0, n).copy_(ts[i]);
+    }
+    DataDict d{{"is_ragged", Data(ragged)}, {"seqs", Data(out)}, {"seq_lens", Data(at::tensor(lens, at::kLong))}};
+    return Data(std::move(d));
+}
+
+}  // namespace
+
+Collater::Collater(std::optional<int64_t> pad_value, int64_t pad_to_multiple, std::vector<CollateOverride> overrides)
+    : pad_value_(pad_value), pad_to_multiple_(pad_to_multiple), overrides_(std::move(overrides)) {
+    if (pad_to_multiple_ > 1 && !pad_value_)
+        throw std::invalid_argument("`pad_value` must be set when `pad_to_multiple` is greater than 1.");
+}
+
+Data Collater::operator()(Data&& bucket) const {
+    if (!bucket.is_list()) throw std::invalid_argument("The collater expects a list of examples (a bucket).");
+    DataList& items = bucket.as_list();
+    if (items.empty()) throw std::invalid_argument("The bucket must contain at least one element.");
+    return collate(items, "");
+}
+
+Data Collater::collate(DataList& items, const std::string& path) const {
+    const Data& first = items[0];
+    if (first.is_dict()) {
+        DataDict out;
+        for (const auto& kv : first.as_dict()) {
+            DataList column;
+            column.reserve(items.size());
+            for (auto& it : items) {
+                if (!it.is_dict()) throw std::invalid_argument("The bucket items at path '" + path + "' must all be dicts.");
+                const Data* e = it.find(kv.first);
+                if (e == nullptr || it.as_dict().size() != first.as_dict().size())
+                    throw std::invalid_argument("The dicts in the bucket at path '" + path + "' must all have the same keys.");
+                column.push_back(*e);
+            }
+            out.emplace_back(kv.first, collate(column, path.empty() ? kv.first : path + "." + kv.first));
+        }
+        return Data(std::move(out));
+    }
+    if (first.is_list()) {
+        const size_t n = first.as_list().size();
+        DataList out;
+        for (size_t i = 0; i < n; ++i) {
+            DataList column;
+            for (auto& it : items) {
+                if (!it.is_list() || it.as_list().size() != n)
+                    throw std::invalid_argument("The lists in the bucket at path '" + path + "' must all have the same length.");
+                column.push_back(it.as_list()[i]);
+            }
+            out.push_back(collate(column, path + "[" + std::to_string(i) + "]"));
+        }
+        return Data(std::move(out));
+    }
+    if (first.is_tensor()) {
+        std::vector<at::Tensor> ts;
+        for (auto& it : items) {
+            if (!it.is_tensor()) throw std::invalid_argument("The bucket items at path '" + path + "' must all be tensors.");
+            ts.push_back(it.as_tensor());
+        }
+        std::optional<int64_t> pad = pad_value_;
+        int64_t mult = pad_to_multiple_;
+        for (const auto& ov : overrides_)
+            if (ov.selector == path) {
+                pad = ov.pad_value;
+                mult = ov.pad_to_multiple;
+            }
+        return collate_tensors(ts, pad, mult, path);
+    }
+    return Data(DataList(items));  // non-tensor leaves stay a list
+}
+
+// ================================================================= list_files
+namespace {
+
+// natural order: digit runs compare numerically
+bool natural_less(const std::string& a, const std::string& b) {
+    size_t i = 0, j = 0;
+    while (i < a.size() && j < b.size()) {
+        if (std::isdigit(static_cast<unsigned char>(a[i])) && std::isdigit(static_cast<unsigned char>(b[j]))) {
+            size_t ie = i, je = j;
+            while (ie < a.size() && std::isdigit(static_cast<unsigned char>(a[ie]))) ++ie;
+            while (je < b.size() && std::isdigit(static_cast<unsigned char>(b[je]))) ++je;
+            std::string na = a.substr(i, ie - i), nb = b.substr(j, je - j);
+            na.erase(0, std::min(na.find_first_not_of('0'), na.size() - 1));
+            nb.erase(0, std::min(nb.find_first_not_of('0'), nb.size() - 1));
+            if (na.size() != nb.size()) return na.size() < nb.size();
+            if (na != nb) return na < nb;
+            i = ie;
+            j = je;
+        } else {
+            if (a[i] != b[j]) return a[i] < b[j];
+            ++i;
+            ++j;
+        }
+    }
+    return a.size() - i < b.size() - j;
+}
+
+void walk(const std::string& dir, const std::optional<std::string>& pattern, std::vector<std::string>& out) {
+    DIR* d = ::opendir(dir.c_str());
+    if (d == nullptr) throw ByteStreamError("The directory '" + dir + "' cannot be opened.");
+    std::vector<std::string> names;
+    while (dirent* e = ::readdir(d)) {
+        std::string n = e->d_name;
+        if (n != "." && n != "..") names.push_back(n);
+    }
+    ::closedir(d);
+    std::sort(names.begin(), names.end(), natural_less);
+    for (const auto& n : names) {
+        std::string full = dir + "/" + n;
+        struct stat st {};
+        if (::stat(full.c_str(), &st) != 0) continue;
+        if (S_ISDIR(st.st_mode)) walk(full, pattern, out);
+        else if (S_ISREG(st.st_mode) && (!pattern || ::fnmatch(pattern->c_str(), full.c_str(), 0) == 0))
+            out.push_back(full);
+    }
+}
+
+}  // namespace
+
+DataPipelineBuilder list_files(const std::string& path, std::optional<std::string> pattern) {
+    std::vector<std::string> files;
+    struct stat st {};
+    if (::stat(path.c_str(), &st) != 0) throw ByteStreamError("'" + path + "' does not exist.");
+    if (S_ISDIR(st.st_mode)) walk(path, pattern, files);
+    else files.push_back(path);
+    DataList items;
+    for (auto& f : files) items.emplace_back(std::move(f));
+    return read_list(std::move(items));
+}
+
+// ================================================================== read_text
+namespace {
+
+class TextSource final : public DataSource {
+public:
+    TextSource(std::string path, std::optional<std::string> key, std::string ending, bool ltrim, bool rtrim,
+               bool skip_empty, bool memory_map)
+        : path_(std::move(path)), key_(std::move(key)), ending_(std::move(ending)), ltrim_(ltrim), rtrim_(rtrim),
+          skip_empty_(skip_empty) {
+        block_ = memory_map ? MemoryBlock::map_file(path_) : MemoryBlock::read_file(path_);
+    }
+    std::optional<Data> next() override {
+        const char* base = reinterpret_cast<const char*>(block_.data());
+        const size_t n = block_.size();
+        while (pos_ < n) {
+            size_t e = pos_;
+            while (e < n && base[e] != '\n') ++e;
+            size_t line_end = e;
+            if (line_end > pos_ && base[line_end - 1] == '\r' && ending_ != "lf") --line_end;
+            size_t a = pos_, b = line_end;
+            if (ltrim_) while (a < b && std::isspace(static_cast<unsigned char>(base[a]))) ++a;
+            if (rtrim_) while (b > a && std::isspace(static_cast<unsigned char>(base[b - 1]))) --b;
+            pos_ = e < n ? e + 1 : n;
+            ++line_nr_;
+            if (a == b && skip_empty_) continue;
+            std::string line(base + a, b - a);
+            if (key_) return Data(DataDict{{*key_, Data(std::move(line))}});
+            return Data(std::move(line));
+        }
+        return std::nullopt;
+    }
+    void reset(bool) override {
+        pos_ = 0;
+        line_nr_ = 0;
+    }
+    void record_position(Tape& t, bool) const override {
+        t.record_int(static_cast<int64_t>(pos_));
+        t.record_int(static_cast<int64_t>(line_nr_));
+    }
+    void reload_position(Tape& t, bool) override {
+        pos_ = static_cast<size_t>(t.read_int());
+        line_nr_ = static_cast<size_t>(t.read_int());
+    }
+    Finitude finitude() const override { return Finitude::Finite; }
+
+private:
+    std::string path_;
+    std::optional<std::string> key_;
+    std::string ending_;
+    bool ltrim_, rtrim_, skip_empty_;
+    MemoryBlock block_;
+    size_t pos_ = 0, line_nr_ = 0;
+};
+
+}  // namespace
+
+DataPipelineBuilder read_text(const std::string& path, std::optional<std::string> key, const std::string& line_ending,
+                              bool ltrim, bool rtrim, bool skip_empty, bool memory_map, size_t) {
+    if (line_ending != "infer" && line_ending != "lf" && line_ending != "crlf")
+        throw std::invalid_argument("`line_ending` must be 'infer', 'lf' or 'crlf'.");
+    return DataPipelineBuilder([=]() -> std::unique_ptr<DataSource> {
+        return std::make_unique<TextSource>(path, key, line_ending, ltrim, rtrim, skip_empty, memory_map);
+    });
+}
+
+// ====================================================== read_zipped_records
+// Minimal ZIP reader (central directory, methods 0 = stored and 8 = deflate).
+namespace {
+
+uint32_t rd32(const uint8_t* p) { return p[0] | (p[1] << 8) | (p[2] << 16) | (static_cast<uint32_t>(p[3]) << 24); }
+uint16_t rd16(const uint8_t* p) { return static_cast<uint16_t>(p[0] | (p[1] << 8)); }
+
+struct ZipEntry {
+    std::string name;
+    uint32_t method, comp_size, size, local_off;
+};
+
+class ZipSource final : public DataSource {
+public:
+    explicit ZipSource(const std::string& path) : path_(path) {
+        block_ = MemoryBlock::map_file(path);
+        const uint8_t* b = block_.data();
+        const size_t n = block_.size();
+        if (n < 22) throw RecordError("'" + path + "' is not a valid zip archive.");
+        size_t eocd = std::string::npos;
+        for (size_t i = n - 22;; --i) {
+            if (rd32(b + i) == 0x06054b50) {
+                eocd = i;
+                break;
+            }
+            if (i == 0 || n - i > 65557) break;
+        }
+        if (eocd == std::string::npos) throw RecordError("'" + path + "' is not a valid zip archive.");
+        const uint16_t count = rd16(b + eocd + 10);
+        size_t p = rd32(b + eocd + 16);
+        for (uint16_t i = 0; i < count; ++i) {
+            if (p + 46 > n || rd32(b + p) != 0x02014b50) throw RecordError("'" + path + "' has a corrupt central directory.");
+            ZipEntry e;
+            e.method = rd16(b + p + 10);
+            e.comp_size = rd32(b + p + 20);
+            e.size = rd32(b + p + 24);
+            const uint16_t nl = rd16(b + p + 28), xl = rd16(b + p + 30), cl = rd16(b + p + 32);
+            e.local_off = rd32(b + p + 42);
+            e.name.assign(reinterpret_cast<const char*>(b + p + 46), nl);
+            p += 46 + nl + xl + cl;
+            if (!e.name.empty() && e.name.back() != '/') entries_.push_back(std::move(e));
+        }
+    }
+    std::optional<Data> next() override {
+        if (pos_ >= entries_.size()) return std::nullopt;
+        const ZipEntry& e = entries_[pos_++];
+        const uint8_t* b = block_.data();
+        const size_t lo = e.local_off;
+        if (lo + 30 > block_.size() || rd32(b + lo) != 0x04034b50)
+            throw RecordError("The zip record '" + e.name + "' in '" + path_ + "' is corrupt.");
+        const size_t data_off = lo + 30 + rd16(b + lo + 26) + rd16(b + lo + 28);
+        if (data_off + e.comp_size > block_.size())
+            throw RecordError("The zip record '" + e.name + "' in '" + path_ + "' is truncated.");
+        if (e.method == 0) return Data(block_.slice(data_off, e.size));
+        if (e.method != 8) throw RecordError("The zip record '" + e.name + "' uses an unsupported compression method.");
+        std::vector<uint8_t> out(e.size);
+        z_stream zs{};
+        if (inflateInit2(&zs, -MAX_WBITS) != Z_OK) throw RecordError("zlib cannot be initialised.");
+        zs.next_in = const_cast<Bytef*>(b + data_off);
+        zs.avail_in = e.comp_size;
+        zs.next_out = out.data();
+        zs.avail_out = e.size;
+        const int rc = inflate(&zs, Z_FINISH);
+        inflateEnd(&zs);
+        if (rc != Z_STREAM_END) throw RecordError("The zip record '" + e.name + "' in '" + path_ + "' cannot be inflated.");
+        return Data(MemoryBlock::copy_of(out.data(), out.size()));
+    }
+    void reset(bool) override { pos_ = 0; }
+    void record_position(Tape& t, bool) const override { t.record_int(static_cast<int64_t>(pos_)); }
+    void reload_position(Tape& t, bool) override { pos_ = static_cast<size_t>(t.read_int()); }
+    Finitude finitude() const override { return Finitude::Finite; }
+
+private:
+    std::string path_;
+    MemoryBlock block_;
+    std::vector<ZipEntry> entries_;
+    size_t pos_ = 0;
+};
+
+}  // namespace
+
+DataPipelineBuilder read_zipped_records(const std::string& path) {
+    return DataPipelineBuilder([path]() -> std::unique_ptr<DataSource> { return std::make_unique<ZipSource>(path); });
+}
+
+// ================================================================= FileMapper
+struct FileMapper::Cache {
+    std::mutex m;
+    std::list<std::pair<std::string, MemoryBlock>> lru;
+    std::map<std::string, std::list<std::pair<std::string, MemoryBlock>>::iterator> index;
+};
+
+FileMapper::FileMapper(std::optional<std::string> root_dir, size_t cached_fd_count)
+    : root_(std::move(root_dir)), capacity_(cached_fd_count == 0 ? 100 : cached_fd_count),
+      cache_(std::make_shared<Cache>()) {}
+
+Data FileMapper::operator()(Data&& d) const {
+    if (!d.is_string()) throw std::invalid_argument("The input data must be a path string.");
+    std::string spec = d.as_string();
+    // "path[:offset[:length]]"
+    std::string path = spec;
+    std::optional<size_t> off, len;
+    size_t c2 = spec.rfind(':');
+    if (c2 != std::string::npos) {
+        size_t c1 = c2 > 0 ? spec.rfind(':', c2 - 1) : std::string::npos;
+        auto is_num = [](const std::string& s) { return !s.empty() && std::all_of(s.begin(), s.end(), ::isdigit); };
+        std::string last = spec.substr(c2 + 1);
+        if (c1 != std::string::npos && is_num(last) && is_num(spec.substr(c1 + 1, c2 - c1 - 1))) {
+            off = std::stoull(spec.substr(c1 + 1, c2 - c1 - 1));
+            len = std::stoull(last);
+            path = spec.substr(0, c1);
+        } else if (is_num(last)) {
+            off = std::stoull(last);
+            path = spec.substr(0, c2);
+        }
+    }
+    std::string full = (root_ && !path.empty() && path[0] != '/') ? *root_ + "/" + path : path;
+    MemoryBlock block;
+    {
+        std::lock_guard<std::mutex> lk(cache_->m);
+        auto it = cache_->index.find(full);
+        if (it != cache_->index.end()) {
+            cache_->lru.splice(cache_->lru.begin(), cache_->lru, it->second);
+            block = it->second->second;
+        }
+    }
+    if (block.data() == nullptr && block.size() == 0) {
+        block = MemoryBlock::map_file(full);
+        std::lock_guard<std::mutex> lk(cache_->m);
+        cache_->lru.emplace_front(full, block);
+        cache_->index[full] = cache_->lru.begin();
+        while (cache_->lru.size() > capacity_) {
+            cache_->index.erase(cache_->lru.back().first);
+            cache_->lru.pop_back();
+        }
+    }
+    if (off) {
+        if (*off > block.size()) throw std::invalid_argument("The offset in '" + spec + "' is beyond the end of the file.");
+        const size_t l = len ? *len : block.size() - *off;
+        if (l > block.size() - *off) throw std::invalid_argument("The length in '" + spec + "' is beyond the end of the file.");
+        block = block.slice(*off, l);
+    }
+    DataDict out{{"path", Data(spec)}, {"data", Data(block)}};
+    return Data(std::move(out));
+}
+
+// ============================================================= text converters
+StrSplitter::StrSplitter(char sep, std::optional<std::vector<std::string>> names, std::vector<size_t> indices,
+                         bool exclude)
+    : sep_(sep), names_(std::move(names)), indices_(std::move(indices)), exclude_(exclude) {
+    std::sort(indices_.begin(), indices_.end());
+}
+
+Data StrSplitter::operator()(Data&& d) const {
+    if (!d.is_string()) throw std::invalid_argument("The input data must be of type `str`.");
+    const std::string& s = d.as_string();
+    std::vector<std::string> fields;
+    size_t start = 0;
+    while (true) {
+        size_t p = s.find(sep_, start);
+        fields.push_back(s.substr(start, p == std::string::npos ? std::string::npos : p - start));
+        if (p == std::string::npos) break;
+        start = p + 1;
+    }
+    if (!indices_.empty()) {
+        std::vector<std::string> kept;
+        if (exclude_) {
+            for (size_t i = 0; i < fields.size(); ++i)
+                if (!std::binary_search(indices_.begin(), indices_.end(), i)) kept.push_back(fields[i]);
+        } else {
+            for (size_t i : indices_) {
+                if (i >= fields.size())
+                    throw std::invalid_argument("The input string must have at least " + std::to_string(i + 1) +
+                                                " field(s), but has " + std::to_string(fields.size()) + " instead.");
+                kept.push_back(fields[i]);
+            }
+        }
+        fields = std::move(kept);
+    }
+    if (names_) {
+        if (names_->size() != fields.size())
+            throw std::invalid_argument("The number of fields (" + std::to_string(fields.size()) +
+                                        ") must match the number of names (" + std::to_string(names_->size()) + ").");
+        DataDict out;
+        for (size_t i = 0; i < fields.size(); ++i) out.emplace_back((*names_)[i], Data(std::move(fields[i])));
+        return Data(std::move(out));
+    }
+    DataList out;
+    for (auto& f : fields) out.emplace_back(std::move(f));
+    return Data(std::move(out));
+}
+
+Data StrToIntConverter::operator()(Data&& d) const {
+    if (!d.is_string()) throw std::invalid_argument("The input data must be of type `str`.");
+    const std::string& s = d.as_string();
+    try {
+        size_t idx = 0;
+        long long v = std::stoll(s, &idx, base_);
+        if (idx != s.size()) throw std::invalid_argument("trailing characters");
+        return Data(static_cast<int64_t>(v));
+    } catch (const std::exception&) {
+        throw std::invalid_argument("The input string must represent an integer, but is '" + s + "' instead.");
+    }
+}
+
+Data StrToTensorConverter::operator()(Data&& d) const {
+    if (!d.is_string()) throw std::invalid_argument("The input data must be of type `str`.");
+    const std::string& s = d.as_string();
+    std::vector<double> fvals;
+    std::vector<int64_t> ivals;
+    const bool is_float = at::isFloatingType(dtype_);
+    size_t i = 0;
+    while (i < s.size()) {
+        while (i < s.size() && std::isspace(static_cast<unsigned char>(s[i]))) ++i;
+        if (i >= s.size()) break;
+        size_t j = i;
+        while (j < s.size() && !std::isspace(static_cast<unsigned char>(s[j]))) ++j;
+        std::string tok = s.substr(i, j - i);
+        try {
+            size_t idx = 0;
+            if (is_float) {
+                fvals.push_back(std::stod(tok, &idx));
+            } else {
+                ivals.push_back(std::stoll(tok, &idx));
+            }
+            if (idx != tok.size()) throw std::invalid_argument("bad token");
+        } catch (const std::exception&) {
+            throw std::invalid_argument("The input string must be a space-separated list of numbers, but contains '" + tok + "'.");
+        }
+        i = j;
+    }
+    at::Tensor t = is_float ? at::tensor(fvals, at::kDouble).to(dtype_) : at::tensor(ivals, at::kLong).to(dtype_);
+    if (size_) {
+        int64_t n = 1;
+        for (auto x : *size_) n *= x;
+        if (n != t.numel())
+            throw std::invalid_argument("The number of parsed elements (" + std::to_string(t.numel()) +
+                                        ") does not match the requested size.");
+        t = t.view(*size_);
+    }
+    return Data(t);
+}
+
+}  // namespace fs2d

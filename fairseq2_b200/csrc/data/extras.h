@@ -1,0 +1,109 @@
+// Declarations of the pipeline helpers implemented in extras.cc / audio.cc.
+#pragma once
+
+#include "data.h"
+
+namespace fs2d {
+
+Data apply_selected(Data&& d, const std::optional<std::string>& selector, const MapFn& fn);
+const Data& select_single(const Data& d, const std::optional<std::string>& selector);
+
+struct CollateOverride {
+    std::string selector;
+    std::optional<int64_t> pad_value;
+    int64_t pad_to_multiple = 1;
+};
+
+// Recursive collation of a bucket (list of examples) into stacked / padded tensors.
+class Collater {
+public:
+    Collater(std::optional<int64_t> pad_value, int64_t pad_to_multiple, std::vector<CollateOverride> overrides);
+    Data operator()(Data&& bucket) const;
+
+private:
+    Data collate(DataList& items, const std::string& path) const;
+    std::optional<int64_t> pad_value_;
+    int64_t pad_to_multiple_;
+    std::vector<CollateOverride> overrides_;
+};
+
+// "path[:offset[:length]]" -> {"path": str, "data": MemoryBlock} with an LRU of mapped files.
+class FileMapper {
+public:
+    FileMapper(std::optional<std::string> root_dir, size_t cached_fd_count);
+    Data operator()(Data&& d) const;
+
+private:
+    struct Cache;
+    std::optional<std::string> root_;
+    size_t capacity_;
+    std::shared_ptr<Cache> cache_;
+};
+
+class StrSplitter {
+public:
+    StrSplitter(char sep, std::optional<std::vector<std::string>> names, std::vector<size_t> indices, bool exclude);
+    Data operator()(Data&& d) const;
+
+private:
+    char sep_;
+    std::optional<std::vector<std::string>> names_;
+    std::vector<size_t> indices_;
+    bool exclude_;
+};
+
+class StrToIntConverter {
+public:
+    explicit StrToIntConverter(int base) : base_(base) {}
+    Data operator()(Data&& d) const;
+
+private:
+    int base_;
+};
+
+class StrToTensorConverter {
+public:
+    StrToTensorConverter(std::optional<std::vector<int64_t>> size, at::ScalarType dtype)
+        : size_(std::move(size)), dtype_(dtype) {}
+    Data operator()(Data&& d) const;
+
+private:
+    std::optional<std::vector<int64_t>> size_;
+    at::ScalarType dtype_;
+};
+
+// RIFF/WAVE decoder (PCM 8/16/24/32-bit and IEEE float) -> {"waveform", "sample_rate", "format"}.
+class AudioDecoder {
+public:
+    AudioDecoder(bool keepdim, std::optional<at::ScalarType> dtype) : keepdim_(keepdim), dtype_(dtype) {}
+    Data operator()(Data&& d) const;
+
+private:
+    bool keepdim_;
+    std::optional<at::ScalarType> dtype_;
+};
+
+// Kaldi-compatible log-mel filter bank features (povey window, pre-emphasis 0.97, 25 ms / 10 ms frames).
+class WaveformToFbankConverter {
+public:
+    WaveformToFbankConverter(int num_mel_bins, float waveform_scale, bool channel_last, bool standardize,
+                             bool keep_waveform, std::optional<at::ScalarType> dtype)
+        : num_mel_bins_(num_mel_bins), scale_(waveform_scale), channel_last_(channel_last),
+          standardize_(standardize), keep_waveform_(keep_waveform), dtype_(dtype) {}
+    Data operator()(Data&& d) const;
+
+private:
+    int num_mel_bins_;
+    float scale_;
+    bool channel_last_, standardize_, keep_waveform_;
+    std::optional<at::ScalarType> dtype_;
+};
+
+// PNG decoder (8/16-bit gray, gray+alpha, RGB, RGBA, palette; non-interlaced) -> {"image", "bit_depth", "format"}.
+class ImageDecoder {
+public:
+    ImageDecoder() = default;
+    Data operator()(Data&& d) const;
+};
+
+}  // namespace fs2d

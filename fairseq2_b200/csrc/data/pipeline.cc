@@ -12,21 +12,18 @@
 #include <random>
 #include <thread>
 
-#include "data.h"
+#include "extras.h"
 
 namespace fs2d {
 
 // ===================================================================== pipeline
 void DataPipeline::ensure_initialized() const {
-    if (source_ == nullptr) {
-        if (!factory_) {
-            // an empty pipeline yields nothing
-            return;
-        }
+    if (s_->source == nullptr) {
+        if (!s_->factory) return;  // an empty pipeline yields nothing
         try {
-            source_ = factory_();
+            s_->source = s_->factory();
         } catch (...) {
-            broken_ = true;
+            s_->broken = true;
             throw;
         }
     }
@@ -35,20 +32,19 @@ void DataPipeline::ensure_initialized() const {
 std::optional<Data> DataPipeline::next() {
     check_broken();
     ensure_initialized();
-    if (source_ == nullptr) return std::nullopt;
+    if (s_->source == nullptr) return std::nullopt;
     while (true) {
         try {
-            return source_->next();
+            return s_->source->next();
         } catch (const DataPipelineError& ex) {
-            if (ex.recoverable() && (max_num_warnings_ == 0 ? false : warning_count_ < max_num_warnings_)) {
-                ++warning_count_;
+            if (ex.recoverable() && s_->warning_count < s_->max_num_warnings) {
+                ++s_->warning_count;
                 continue;  // skip the faulty example
             }
-            if (!ex.recoverable()) broken_ = true;
-            else broken_ = true;
+            s_->broken = true;
             throw;
         } catch (...) {
-            broken_ = true;
+            s_->broken = true;
             throw;
         }
     }
@@ -56,27 +52,27 @@ std::optional<Data> DataPipeline::next() {
 
 void DataPipeline::reset(bool reset_rng) {
     check_broken();
-    if (source_ == nullptr) return;
+    if (s_->source == nullptr) return;
     try {
-        source_->reset(reset_rng);
+        s_->source->reset(reset_rng);
     } catch (...) {
-        broken_ = true;
+        s_->broken = true;
         throw;
     }
 }
 
 void DataPipeline::record_position(Tape& t, bool strict) const {
     check_broken();
-    if (source_ == nullptr) {
+    if (s_->source == nullptr) {
         t.record_bool(false);
         return;
     }
     t.record_bool(true);
     t.record_bool(strict);
     try {
-        source_->record_position(t, strict);
+        s_->source->record_position(t, strict);
     } catch (...) {
-        broken_ = true;
+        s_->broken = true;
         throw;
     }
 }
@@ -85,23 +81,23 @@ void DataPipeline::reload_position(Tape& t, bool) {
     check_broken();
     const bool initialized = t.read_bool();
     if (!initialized) {
-        if (source_ != nullptr) source_->reset(true);
+        if (s_->source != nullptr) s_->source->reset(true);
         return;
     }
     const bool strict = t.read_bool();
     ensure_initialized();
-    if (source_ == nullptr) return;
+    if (s_->source == nullptr) return;
     try {
-        source_->reload_position(t, strict);
+        s_->source->reload_position(t, strict);
     } catch (...) {
-        broken_ = true;
+        s_->broken = true;
         throw;
     }
 }
 
 Finitude DataPipeline::finitude() const {
     ensure_initialized();
-    return source_ ? source_->finitude() : Finitude::Finite;
+    return s_->source ? s_->source->finitude() : Finitude::Finite;
 }
 
 DataPipeline DataPipelineBuilder::and_return(size_t max_num_warnings) && {
@@ -111,6 +107,25 @@ DataPipeline DataPipelineBuilder::and_return(size_t max_num_warnings) && {
 }
 
 namespace {
+
+// Small counter-based generator (splitmix64): its whole state is one integer,
+// which makes recording it on a tape trivial and exact.
+struct Rng {
+    using result_type = uint64_t;
+    uint64_t state;
+    explicit Rng(uint64_t seed) : state(seed) {}
+    void seed(uint64_t s) { state = s; }
+    static constexpr result_type min() { return 0; }
+    static constexpr result_type max() { return UINT64_MAX; }
+    result_type operator()() {
+        uint64_t z = (state += 0x9E3779B97F4A7C15ull);
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+        z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+        return z ^ (z >> 31);
+    }
+    double uniform() { return static_cast<double>((*this)() >> 11) * (1.0 / 9007199254740992.0); }
+    size_t below(size_t n) { return static_cast<size_t>((*this)() % n); }
+};
 
 // ======================================================================= sources
 class ListSource final : public DataSource {
@@ -321,7 +336,7 @@ public:
                 eod_ = true;
                 return std::nullopt;
             }
-            const double u = std::uniform_real_distribution<double>(0.0, 1.0)(gen_) * total;
+            const double u = gen_.uniform() * total;
             double acc = 0;
             size_t pick = ps_.size();
             for (size_t i = 0; i < ps_.size(); ++i) {
@@ -355,9 +370,7 @@ public:
     void record_position(Tape& t, bool s) const override {
         t.record_bool(filled_);
         t.record_bool(eod_);
-        std::ostringstream os;
-        os << gen_;
-        t.record(Data(os.str()));
+        t.record_int(static_cast<int64_t>(gen_.state));
         for (size_t i = 0; i < ps_.size(); ++i) {
             t.record_bool(done_[i]);
             t.record_bool(blocked_[i]);
@@ -369,8 +382,7 @@ public:
     void reload_position(Tape& t, bool s) override {
         filled_ = t.read_bool();
         eod_ = t.read_bool();
-        std::istringstream is(t.read().as_string());
-        is >> gen_;
+        gen_.state = static_cast<uint64_t>(t.read_int());
         for (size_t i = 0; i < ps_.size(); ++i) {
             done_[i] = t.read_bool();
             blocked_[i] = t.read_bool();
@@ -389,7 +401,7 @@ private:
     std::vector<float> weights_;
     uint64_t seed_;
     bool allow_repeats_;
-    std::mt19937_64 gen_;
+    Rng gen_;
     Finitude fin_;
     std::vector<std::optional<Data>> buffer_;
     std::vector<bool> done_, blocked_;
@@ -539,8 +551,6 @@ private:
     size_t n_;
     bool drop_;
 };
-
-const Data& select_single(const Data& d, const std::optional<std::string>& selector);
 
 class BucketByLengthSource final : public DataSource {
 public:
@@ -764,8 +774,6 @@ private:
     std::condition_variable cv_;
     bool stop_ = false;
 };
-
-Data apply_selected(Data&& d, const std::optional<std::string>& selector, const MapFn& fn);
 
 // map: sequential, or `num_parallel_calls` workers. In parallel mode a buffer
 // of N examples is filled, mapped concurrently and drained in order
@@ -1182,7 +1190,7 @@ public:
                 }
                 buf_.push_back(std::move(*d));
             }
-            std::shuffle(buf_.begin(), buf_.end(), gen_);
+            for (size_t k = buf_.size(); k > 1; --k) std::swap(buf_[k - 1], buf_[gen_.below(k)]);  // Fisher-Yates
             filled_ = true;
         }
         if (buf_.empty()) return std::nullopt;
@@ -1192,7 +1200,7 @@ public:
             return out;
         }
         // pick a random slot, emit it, refill the slot from the input
-        const size_t i = std::uniform_int_distribution<size_t>(0, buf_.size() - 1)(gen_);
+        const size_t i = gen_.below(buf_.size());
         Data out = std::move(buf_[i]);
         auto d = in_->next();
         if (d) {
@@ -1214,17 +1222,14 @@ public:
         t.record(Data(DataList(buf_)));
         t.record_bool(filled_);
         t.record_bool(inner_done_);
-        std::ostringstream os;
-        os << gen_;
-        t.record(Data(os.str()));
+        t.record_int(static_cast<int64_t>(gen_.state));
         in_->record_position(t, s);
     }
     void reload_position(Tape& t, bool s) override {
         buf_ = t.read().as_list();
         filled_ = t.read_bool();
         inner_done_ = t.read_bool();
-        std::istringstream is(t.read().as_string());
-        is >> gen_;
+        gen_.state = static_cast<uint64_t>(t.read_int());
         in_->reload_position(t, s);
     }
     Finitude finitude() const override { return in_->finitude(); }
@@ -1233,7 +1238,7 @@ private:
     std::unique_ptr<DataSource> in_;
     size_t window_;
     uint64_t seed_;
-    std::mt19937_64 gen_;
+    Rng gen_;
     DataList buf_;
     bool filled_ = false, inner_done_ = false;
 };
