@@ -415,6 +415,7 @@ class Trainer(Task):
         if self._publish_every is not None and self._step_nr % self._publish_every != 0:
             self._publish_metrics()
         if self._ckpt is not None and (self._ckpt_every is not None or self._ckpt_every_epochs is not None):
+            self._ckpt.maybe_complete_save_operation(blocking=True)
             last = self._ckpt.maybe_get_last_step_number()
             if last != self._step_nr and self._step_nr > 0:
                 self._save_checkpoint(blocking=True)

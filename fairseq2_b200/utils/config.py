@@ -98,7 +98,7 @@ class ConfigProcessor:
 
 def parse_config_overrides(pairs: Sequence[str]) -> dict[str, object]:
     """``["a.b=1", "c=[1,2]"]`` -> nested dict, values parsed as YAML scalars."""
-    import yaml
+    from fairseq2_b200.utils.yaml import YamlError, parse_yaml_value
 
     out: dict[str, object] = {}
     for item in pairs:
@@ -106,8 +106,8 @@ def parse_config_overrides(pairs: Sequence[str]) -> dict[str, object]:
             raise ValueError(f"A config override must be of the form key=value, but is '{item}' instead.")
         key, raw = item.split("=", 1)
         try:
-            val = yaml.safe_load(raw)
-        except yaml.YAMLError as ex:
+            val = parse_yaml_value(raw)
+        except YamlError as ex:
             raise ValueError(f"The value of '{key}' is not valid YAML: {ex}") from None
         cur = out
         parts = key.strip().split(".")

@@ -73,6 +73,11 @@ class ValueConverter:
             for a in get_args(t):
                 if obj == a and type(obj) is type(a):
                     return obj
+            if isinstance(obj, bool):
+                # YAML 1.1 reads a bare `on`/`off`/`yes`/`no` as a boolean
+                for word in (("on", "yes", "true") if obj else ("off", "no", "false")):
+                    if word in get_args(t):
+                        return word
             raise StructureError(
                 f"`{path or 'obj'}` must be one of {list(get_args(t))}, but is `{obj!r}` instead.")
         if origin in (list, typing.List, typing.Sequence, typing.MutableSequence) or t is list:

@@ -4,6 +4,8 @@ from __future__ import annotations
 from pathlib import Path
 from typing import IO, Any
 
+import re
+
 import yaml
 
 
@@ -11,13 +13,30 @@ class YamlError(Exception):
     pass
 
 
+class _Loader(yaml.SafeLoader):
+    """Safe loader that also reads ``1e-3`` / ``3E5`` (no dot) as floats, as YAML 1.2 does."""
+
+
+_Loader.add_implicit_resolver(
+    "tag:yaml.org,2002:float",
+    re.compile(r"^[-+]?(?:[0-9][0-9_]*)(?:\.[0-9_]*)?[eE][-+]?[0-9]+$"),
+    list("-+0123456789"))
+
+
+def parse_yaml_value(text: str) -> Any:
+    try:
+        return yaml.load(text, Loader=_Loader)
+    except yaml.YAMLError as ex:
+        raise YamlError(f"The YAML value cannot be parsed: {ex}") from ex
+
+
 def load_yaml(source: Path | IO[str] | str) -> list[Any]:
     """Loads every document of a (possibly multi-document) YAML source."""
     try:
         if isinstance(source, Path):
             with source.open("r", encoding="utf-8") as fp:
-                return [d for d in yaml.safe_load_all(fp)]
-        return [d for d in yaml.safe_load_all(source)]
+                return [d for d in yaml.load_all(fp, Loader=_Loader)]
+        return [d for d in yaml.load_all(source, Loader=_Loader)]
     except yaml.YAMLError as ex:
         raise YamlError(f"The YAML source cannot be parsed: {ex}") from ex
 

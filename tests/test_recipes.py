@@ -1,0 +1,68 @@
+"""End-to-end recipe runs on CPU with the tiny LLaMA and the byte-level tokenizer."""
+import json
+from pathlib import Path
+
+import pytest
+import torch
+
+from fairseq2_b200.recipe.cli import main
+
+
+def _write_sft_data(root: Path, n: int = 64) -> Path:
+    d = root / "data"
+    (d / "train").mkdir(parents=True)
+    (d / "valid").mkdir(parents=True)
+    for split in ("train", "valid"):
+        with open(d / split / "part0.jsonl", "w") as fp:
+            for i in range(n if split == "train" else 8):
+                fp.write(json.dumps({"id": i, "src": f"Q: what is {i} plus {i}? ", "tgt": f"A: {2 * i}."}) + "\n")
+    return d
+
+
+def _sft_args(tmp_path: Path, data: Path, extra: list[str]) -> list[str]:
+    src = f"[{{path: {data}, split: train}}]"
+    vsrc = f"[{{path: {data}, split: valid}}]"
+    return [str(tmp_path / "out"), "--no-sweep-dir", "--no-exit-on-error", "--config",
+            "model.name=null", "model.family=llama", "model.arch=tiny", "tokenizer.name=char_tokenizer",
+            f"dataset.config_overrides={{sources: {{train: {src}, valid: {vsrc}}}}}",
+            "dataset.max_seq_len=128", "dataset.max_num_tokens=256", "dataset.valid_split=valid",
+            "trainer.mixed_precision.mode=off", "optimizer.config.lr=1e-3",
+            "lr_scheduler.config.num_warmup_steps=1", "regime.validate_every_n_steps=2",
+            "regime.checkpoint_every_n_steps=2", "regime.publish_metrics_every_n_steps=1",
+            "regime.export_hugging_face=false", "common.metric_recorders.jsonl=true", *extra]
+
+
+@pytest.mark.parametrize("packed", [True, False])
+def test_lm_sft_recipe_end_to_end(tmp_path: Path, packed: bool) -> None:
+    from recipes.lm.sft.recipe import LMSFTRecipe
+
+    data = _write_sft_data(tmp_path)
+    args = _sft_args(tmp_path, data, ["regime.num_steps=4", f"dataset.packed={str(packed).lower()}"])
+    assert main(LMSFTRecipe(), args) == 0
+    out = tmp_path / "out"
+    assert (out / "config.yaml").exists()
+    assert (out / "logs" / "rank_0.log").exists()
+    assert (out / "checkpoints" / "step_4").is_dir()
+    lines = [json.loads(l) for l in open(out / "metrics" / "train.jsonl")]
+    assert len(lines) == 4 and all("NLL Loss" in l for l in lines)
+    assert lines[-1]["NLL Loss"] < lines[0]["NLL Loss"]
+    assert (out / "metrics" / "valid.jsonl").exists()
+    # resume: two more steps continue from step 4
+    args = _sft_args(tmp_path, data, ["regime.num_steps=6", f"dataset.packed={str(packed).lower()}"])
+    assert main(LMSFTRecipe(), args) == 0
+    lines = [json.loads(l) for l in open(out / "metrics" / "train.jsonl")]
+    assert [l["Step"] for l in lines][-2:] == [5, 6]
+
+
+def test_dump_config(capsys: pytest.CaptureFixture[str]) -> None:
+    from recipes.lm.sft.recipe import LMSFTRecipe
+
+    assert main(LMSFTRecipe(), ["--dump-config", "--config", "regime.num_steps=7"]) == 0
+    out = capsys.readouterr().out
+    assert "num_steps: 7" in out and "data_parallelism: fsdp" in out
+
+
+def test_bad_config_exit_code() -> None:
+    from recipes.lm.sft.recipe import LMSFTRecipe
+
+    assert main(LMSFTRecipe(), ["--dump-config", "--config", "regime.num_stepz=7"]) != 0
