@@ -13,3 +13,23 @@ register_model_family(ModelFamily(
     name=LLAMA_FAMILY, kls=TransformerLM, config_kls=LLaMAConfig, factory=create_llama_model,
     state_dict_converter=convert_llama_state_dict, fsdp_wrap_policy=layerwise_wrap_policy,
     layerwise_ac_applier=apply_layerwise_ac, hg_exporter=export_llama_to_hg))
+
+
+def _register_lm_families() -> None:
+    from fairseq2_b200.models.mistral import (MISTRAL_FAMILY, MistralConfig, convert_mistral_state_dict,
+                                              create_mistral_model, export_mistral_to_hg)
+    from fairseq2_b200.models.olmo import (OLMO_FAMILY, OLMOConfig, convert_olmo_state_dict, create_olmo_model,
+                                           export_olmo_to_hg)
+    from fairseq2_b200.models.qwen import (QWEN_FAMILY, QwenConfig, convert_qwen_state_dict, create_qwen_model,
+                                           export_qwen_to_hg)
+
+    for name, cfg, factory, conv, exp in (
+            (MISTRAL_FAMILY, MistralConfig, create_mistral_model, convert_mistral_state_dict, export_mistral_to_hg),
+            (QWEN_FAMILY, QwenConfig, create_qwen_model, convert_qwen_state_dict, export_qwen_to_hg),
+            (OLMO_FAMILY, OLMOConfig, create_olmo_model, convert_olmo_state_dict, export_olmo_to_hg)):
+        register_model_family(ModelFamily(
+            name=name, kls=TransformerLM, config_kls=cfg, factory=factory, state_dict_converter=conv,
+            fsdp_wrap_policy=layerwise_wrap_policy, layerwise_ac_applier=apply_layerwise_ac, hg_exporter=exp))
+
+
+_register_lm_families()

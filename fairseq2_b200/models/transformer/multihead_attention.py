@@ -16,6 +16,7 @@ import torch
 from torch import Tensor
 from torch.nn import Module, Parameter
 
+from fairseq2_b200.error import NotSupportedError
 from fairseq2_b200.gang import Gangs
 from fairseq2_b200.models.transformer.attention_bias import AttentionBiasCache
 from fairseq2_b200.models.transformer.sdpa import SDPA
@@ -261,7 +262,7 @@ class StandardMultiheadAttention(MultiheadAttention):
                  pos_encoder: PositionEncoder | None = None, output_proj: Projection | None = None,
                  output_proj_init_fn: Callable[[Linear], None] | None = None, bias: bool = True,
                  output_proj_bias: bool | None = None, state_factory: Callable[..., AttentionState] | None = None,
-                 gangs: Gangs | None = None, device: Device | None = None, dtype: DataType | None = None) -> None:
+                 qk_norm_over_heads: bool = False, gangs: Gangs | None = None, device: Device | None = None, dtype: DataType | None = None) -> None:
         super().__init__(model_dim, num_heads)
         nkv = num_key_value_heads if num_key_value_heads is not None else num_heads
         if num_heads % nkv:
@@ -284,6 +285,10 @@ class StandardMultiheadAttention(MultiheadAttention):
         self.k_proj = k_proj if k_proj is not None else col(kv_dim, nkv * hd)
         self.v_proj = v_proj if v_proj is not None else col(kv_dim, nkv * hd)
         self.q_norm, self.k_norm = q_norm, k_norm
+        # OLMo-2 style: q/k norms span the whole projection (all heads) rather than one head
+        self.qk_norm_over_heads = qk_norm_over_heads
+        if qk_norm_over_heads and tp is not None:
+            raise NotSupportedError("`qk_norm_over_heads` is not supported when tensor parallelism is enabled.")
         if pos_encoder is not None and pos_encoder.encoding_dim != hd:
             raise ValueError(f"`pos_encoder.encoding_dim` must equal the head dimension ({hd}).")
         self.pos_encoder = pos_encoder
@@ -315,8 +320,11 @@ class StandardMultiheadAttention(MultiheadAttention):
                     return self.output_proj(fused)
                 q, k, v = qkv[..., :H, :], qkv[..., H:H + Hkv, :], qkv[..., H + Hkv:, :]
         if q is None:
-            q = self.q_proj(seqs).unflatten(-1, (H, D))
-            if self.q_norm is not None:
+            q = self.q_proj(seqs)
+            if self.q_norm is not None and self.qk_norm_over_heads:
+                q = self.q_norm(q)
+            q = q.unflatten(-1, (H, D))
+            if self.q_norm is not None and not self.qk_norm_over_heads:
                 q = self.q_norm(q)
         if self.pos_encoder is not None:
             q = self.pos_encoder(q, seqs_layout, state_bag=state_bag)
@@ -327,9 +335,12 @@ class StandardMultiheadAttention(MultiheadAttention):
             k, v = state_bag.maybe_get_state(self, AttentionState).get()  # type: ignore[union-attr]
         else:
             if k is None:
-                k = self.k_proj(keys).unflatten(-1, (Hkv, D))
+                k = self.k_proj(keys)
+                if self.k_norm is not None and self.qk_norm_over_heads:
+                    k = self.k_norm(k)
+                k = k.unflatten(-1, (Hkv, D))
                 v = self.v_proj(values).unflatten(-1, (Hkv, D))
-                if self.k_norm is not None:
+                if self.k_norm is not None and not self.qk_norm_over_heads:
                     k = self.k_norm(k)
             if self.pos_encoder is not None:
                 k = self.pos_encoder(k, keys_layout, state_bag=state_bag)

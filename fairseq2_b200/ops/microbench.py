@@ -1,0 +1,188 @@
+"""Per-kernel micro-benchmarks on one GPU.
+
+    python -m fairseq2_b200.ops.microbench gemm --m 8192 --n 6144 --k 4096
+    python -m fairseq2_b200.ops.microbench attention --tokens 8192 --seq-len 8192
+    python -m fairseq2_b200.ops.microbench all
+
+Every case warms up, flushes L2 (a 256 MiB write) between timed iterations,
+times with CUDA events on the launching stream and prints one JSON line with
+the median time and the achieved TFLOP/s or GB/s. ``--iters 1 --warmup 0`` makes
+a case small enough for a profiler capture of a single launch.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+from typing import Any, Callable
+
+import torch
+
+from fairseq2_b200.ops._ext import require_ext
+
+_DEV = "cuda"
+
+
+def _time(fn: Callable[[], Any], iters: int, warmup: int) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=_DEV)
+    ts = []
+    for _ in range(iters):
+        flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def _emit(case: str, ms: float, *, flops: float | None = None, nbytes: float | None = None, **kw: Any) -> None:
+    r: dict[str, Any] = {"case": case, "ms": round(ms, 4), **kw}
+    if flops is not None:
+        r["tflops"] = round(flops / ms / 1e9, 1)
+    if nbytes is not None:
+        r["gbs"] = round(nbytes / ms / 1e6, 1)
+    r["status"] = require_ext().read_status()
+    print(json.dumps(r), flush=True)
+
+
+def bench_gemm(a: argparse.Namespace) -> None:
+    ext = require_ext()
+    M, N, K = a.m, a.n, a.k
+    x = torch.randn((K, M) if a.a_mn else (M, K), device=_DEV, dtype=torch.bfloat16)
+    w = torch.randn((K, N) if a.b_mn else (N, K), device=_DEV, dtype=torch.bfloat16)
+    out = torch.empty((M, N), device=_DEV, dtype=torch.bfloat16)
+    ms = _time(lambda: ext.gemm_bf16(x, w, out, a.a_mn, a.b_mn, False), a.iters, a.warmup)
+    r: dict[str, Any] = {}
+    if a.compare:
+        A, B = (x.t() if a.a_mn else x), (w if a.b_mn else w.t())
+        ref = torch.matmul(A, B)
+        r["rel_err"] = float((out.float() - ref.float()).norm() / ref.float().norm())
+        r["ms_cublas"] = round(_time(lambda: torch.matmul(A, B, out=ref), a.iters, a.warmup), 4)
+    _emit("gemm", ms, flops=2.0 * M * N * K, M=M, N=N, K=K, a_mn=a.a_mn, b_mn=a.b_mn, **r)
+
+
+def _attn_inputs(a: argparse.Namespace):  # type: ignore[no-untyped-def]
+    T, S, H, Hkv, D = a.tokens, a.seq_len, a.heads, a.kv_heads, a.head_dim
+    nseq = T // S
+    qkv = torch.randn(T, H + 2 * Hkv, D, device=_DEV, dtype=torch.bfloat16)
+    begins = torch.arange(nseq, device=_DEV, dtype=torch.int32) * S
+    lens = torch.full((nseq,), S, device=_DEV, dtype=torch.int32)
+    return qkv, begins, lens
+
+
+def bench_attention(a: argparse.Namespace) -> None:
+    ext = require_ext()
+    T, S, H, Hkv, D = a.tokens, a.seq_len, a.heads, a.kv_heads, a.head_dim
+    qkv, begins, lens = _attn_inputs(a)
+    q, k, v = qkv[:, :H], qkv[:, H:H + Hkv], qkv[:, H + Hkv:]
+    scale = 1.0 / math.sqrt(D)
+    fl_fwd = 4.0 * (T // S) * H * D * S * S / 2      # causal: half of the score matrix
+    out, lse = ext.attn_fwd(q, k, v, begins, lens, begins, lens, S, S, True, scale)
+    ms = _time(lambda: ext.attn_fwd(q, k, v, begins, lens, begins, lens, S, S, True, scale), a.iters, a.warmup)
+    _emit("attention_fwd", ms, flops=fl_fwd, tokens=T, seq_len=S, heads=H, kv_heads=Hkv, head_dim=D)
+    dout = torch.randn_like(out)
+    dqkv = torch.empty_like(qkv)
+
+    def bwd() -> None:
+        ext.attn_bwd_out(dout, q, k, v, out, lse, begins, lens, begins, lens, S, S, True, scale, dqkv[:, :H],
+                         dqkv[:, H:H + Hkv], dqkv[:, H + Hkv:])
+
+    ms = _time(bwd, a.iters, a.warmup)
+    _emit("attention_bwd", ms, flops=2.5 * fl_fwd, tokens=T, seq_len=S, heads=H, kv_heads=Hkv, head_dim=D)
+
+
+def bench_norm(a: argparse.Namespace) -> None:
+    from fairseq2_b200.ops.norm import rms_norm
+
+    T, Dm = a.tokens, a.dim
+    x = torch.randn(T, Dm, device=_DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = torch.ones(Dm, device=_DEV, dtype=torch.bfloat16, requires_grad=True)
+    ms = _time(lambda: rms_norm(x.detach(), (Dm,), w.detach(), 1e-5), a.iters, a.warmup)
+    _emit("rms_norm_fwd", ms, nbytes=2.0 * T * Dm * 2, tokens=T, dim=Dm)
+    y = rms_norm(x, (Dm,), w, 1e-5)
+    g = torch.randn_like(y)
+    ms = _time(lambda: torch.autograd.grad(y, (x, w), g, retain_graph=True), a.iters, a.warmup)
+    _emit("rms_norm_bwd", ms, nbytes=3.0 * T * Dm * 2, tokens=T, dim=Dm)
+
+
+def bench_swiglu(a: argparse.Namespace) -> None:
+    from fairseq2_b200.ops.activation import swiglu
+
+    T, F = a.tokens, a.ffn_dim
+    gu = torch.randn(T, 2 * F, device=_DEV, dtype=torch.bfloat16)
+    ms = _time(lambda: swiglu(gu), a.iters, a.warmup)
+    _emit("swiglu_fwd", ms, nbytes=3.0 * T * F * 2, tokens=T, ffn_dim=F)
+
+
+def bench_adamw(a: argparse.Namespace) -> None:
+    from fairseq2_b200.ops.optim import multi_tensor_adamw
+
+    n = a.numel
+    p = torch.randn(n, device=_DEV)
+    g = torch.randn(n, device=_DEV)
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    low = torch.empty(n, device=_DEV, dtype=torch.bfloat16)
+
+    def run() -> None:
+        multi_tensor_adamw([p], [g], [m], [v], [low], step=1, lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8,
+                           weight_decay=0.1)
+
+    ms = _time(run, a.iters, a.warmup)
+    _emit("adamw", ms, nbytes=n * (4 * 4 + 3 * 4 + 2.0), numel=n)
+
+
+def bench_ce(a: argparse.Namespace) -> None:
+    from fairseq2_b200.ops.cross_entropy import fused_linear_cross_entropy
+
+    T, Dm, V = a.tokens, a.dim, a.vocab
+    h = torch.randn(T, Dm, device=_DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(V, Dm, device=_DEV, dtype=torch.bfloat16) * 0.02).requires_grad_()
+    t = torch.randint(0, V, (T,), device=_DEV)
+
+    def run() -> None:
+        loss = fused_linear_cross_entropy(h, w, t)
+        loss.backward()
+        h.grad = w.grad = None
+
+    ms = _time(run, a.iters, a.warmup)
+    _emit("fused_linear_ce_fwd_bwd", ms, flops=6.0 * T * Dm * V, tokens=T, dim=Dm, vocab=V)
+
+
+_CASES = {"gemm": bench_gemm, "attention": bench_attention, "norm": bench_norm, "swiglu": bench_swiglu,
+          "adamw": bench_adamw, "ce": bench_ce}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("case", choices=[*_CASES, "all"])
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=6144)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--a-mn", action="store_true", help="A is stored [K, M]")
+    ap.add_argument("--b-mn", action="store_true", help="B is stored [K, N]")
+    ap.add_argument("--compare", action="store_true", help="also time torch.matmul and report the relative error")
+    ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--seq-len", type=int, default=8192)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--dim", type=int, default=4096)
+    ap.add_argument("--ffn-dim", type=int, default=14336)
+    ap.add_argument("--vocab", type=int, default=128256)
+    ap.add_argument("--numel", type=int, default=1 << 28)
+    a = ap.parse_args()
+    torch.manual_seed(0)
+    for name in (_CASES if a.case == "all" else [a.case]):
+        _CASES[name](a)
+
+
+if __name__ == "__main__":
+    main()

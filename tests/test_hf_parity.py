@@ -1,0 +1,90 @@
+"""Logit parity of the LM families against Hugging Face ``transformers`` reference
+implementations with random weights (CPU, fp32)."""
+import pytest
+import torch
+
+from fairseq2_b200.gang import create_fake_gangs
+from fairseq2_b200.models.family import get_model_family
+from fairseq2_b200.nn.batch_layout import BatchLayout
+
+transformers = pytest.importorskip("transformers")
+
+
+def _ours(family: str, config, hf_model):  # type: ignore[no-untyped-def]
+    fam = get_model_family(family)
+    g = create_fake_gangs(torch.device("cpu"))
+    model = fam.create_new_model(config, g)
+    sd = fam.state_dict_converter({k: v.clone() for k, v in hf_model.state_dict().items()}, config)
+    missing, unexpected = model.load_state_dict(sd, strict=False)
+    assert not unexpected, unexpected
+    assert all("final_proj" in k for k in missing), missing
+    return model.eval()
+
+
+def _check(model, hf_model, vocab: int, atol: float = 2e-4) -> None:  # type: ignore[no-untyped-def]
+    torch.manual_seed(0)
+    x = torch.randint(1, vocab, (2, 48))
+    with torch.no_grad():
+        ref = hf_model(x).logits
+        out = model(x, BatchLayout((2, 48), [48, 48]))
+    assert torch.allclose(out, ref, atol=atol, rtol=1e-3), float((out - ref).abs().max())
+
+
+def test_llama_matches_hf() -> None:
+    from fairseq2_b200.models.llama import LLaMAConfig
+
+    hc = transformers.LlamaConfig(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                                  num_key_value_heads=2, vocab_size=512, max_position_embeddings=256,
+                                  rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False)
+    hf = transformers.LlamaForCausalLM(hc).eval()
+    c = LLaMAConfig(model_dim=128, max_seq_len=256, vocab_size=512, num_layers=2, num_attn_heads=4,
+                    num_key_value_heads=2, ffn_inner_dim=256, ffn_inner_dim_scale=1.0, ffn_inner_dim_multiple_of=1)
+    _check(_ours("llama", c, hf), hf, 512)
+
+
+def test_mistral_matches_hf() -> None:
+    from fairseq2_b200.models.mistral import MistralConfig
+
+    hc = transformers.MistralConfig(hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                                    num_attention_heads=4, num_key_value_heads=2, vocab_size=512,
+                                    max_position_embeddings=256, sliding_window=16, rope_theta=10000.0,
+                                    rms_norm_eps=1e-5, attn_implementation="eager")
+    hf = transformers.MistralForCausalLM(hc).eval()
+    c = MistralConfig(model_dim=128, max_seq_len=256, vocab_size=512, attn_window_len=16, num_layers=2,
+                      num_attn_heads=4, num_key_value_heads=2, ffn_inner_dim=256)
+    _check(_ours("mistral", c, hf), hf, 512)
+
+
+@pytest.mark.parametrize("v3", [False, True])
+def test_qwen_matches_hf(v3: bool) -> None:
+    from fairseq2_b200.models.qwen import QwenConfig
+
+    kw = dict(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=2, vocab_size=512, max_position_embeddings=256, rope_theta=1e6, rms_norm_eps=1e-6,
+              tie_word_embeddings=True)
+    if v3:
+        hf = transformers.Qwen3ForCausalLM(transformers.Qwen3Config(head_dim=64, **kw)).eval()
+    else:
+        hf = transformers.Qwen2ForCausalLM(transformers.Qwen2Config(**kw)).eval()
+    for n, p in hf.named_parameters():   # biases and norm weights are not random by default
+        if p.ndim == 1:
+            torch.nn.init.normal_(p, mean=1.0 if "norm" in n else 0.0, std=0.1)
+    c = QwenConfig(model_dim=128, max_seq_len=256, vocab_size=512, tied_embeddings=True, num_layers=2,
+                   num_attn_heads=4, num_key_value_heads=2, head_dim=64 if v3 else None, qkv_proj_bias=not v3,
+                   q_norm=v3, k_norm=v3, ffn_inner_dim=256)
+    _check(_ours("qwen", c, hf), hf, 512)
+
+
+def test_olmo2_matches_hf() -> None:
+    from fairseq2_b200.models.olmo import OLMOConfig
+
+    hc = transformers.Olmo2Config(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                                  num_key_value_heads=2, vocab_size=512, max_position_embeddings=256,
+                                  rope_theta=500000.0, rms_norm_eps=1e-6, pad_token_id=0, tie_word_embeddings=False)
+    hf = transformers.Olmo2ForCausalLM(hc).eval()
+    for n, p in hf.named_parameters():
+        if p.ndim == 1:
+            torch.nn.init.normal_(p, mean=1.0, std=0.1)
+    c = OLMOConfig(model_dim=128, max_seq_len=256, vocab_size=512, pad_idx=0, num_layers=2, num_attn_heads=4,
+                   num_key_value_heads=2, ffn_inner_dim=256)
+    _check(_ours("olmo", c, hf), hf, 512)
