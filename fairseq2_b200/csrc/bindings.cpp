@@ -15,6 +15,7 @@
 #include "comm.h"
 #include "elementwise.h"
 #include "gemm_tcgen05.h"
+#include "generation.h"
 
 namespace {
 
@@ -222,6 +223,61 @@ void rope_inplace(Tensor x, const Tensor& freqs, const Tensor& pos, bool inverse
                       static_cast<size_t>(x.stride(1)), static_cast<int>(freqs.size(0)), inverse, num_sms(x),
                       stream_of(x));
     g_launches += 1;
+}
+
+// ----------------------------------------------------------------- generation
+void ngram_repeat_block(const Tensor& seqs, Tensor probs, int64_t n, double ban_value) {
+    TORCH_CHECK(seqs.is_cuda() && seqs.scalar_type() == at::kLong && seqs.dim() == 2 && seqs.is_contiguous(),
+                "ngram_repeat_block: seqs must be contiguous int64 [N, S]");
+    TORCH_CHECK(probs.is_cuda() && probs.scalar_type() == at::kFloat && probs.dim() == 2 && probs.is_contiguous() &&
+                    probs.size(0) == seqs.size(0),
+                "ngram_repeat_block: probs must be contiguous fp32 [N, V]");
+    TORCH_CHECK(n >= 1, "ngram_repeat_block: n must be positive");
+    c10::cuda::CUDAGuard guard(probs.device());
+    if (seqs.size(1) < n || seqs.size(0) == 0) return;
+    fs2::ngram_repeat_block(reinterpret_cast<const long long*>(seqs.data_ptr<int64_t>()), probs.data_ptr<float>(),
+                            static_cast<int>(seqs.size(0)), static_cast<int>(seqs.size(1)),
+                            static_cast<int>(probs.size(1)), static_cast<int>(n), static_cast<float>(ban_value),
+                            stream_of(probs));
+    g_launches += 1;
+}
+
+Tensor sample_top_p_top_k(const Tensor& probs, const Tensor& uniform, double p, int64_t k) {
+    TORCH_CHECK(probs.is_cuda() && probs.scalar_type() == at::kFloat && probs.dim() == 2 && probs.is_contiguous(),
+                "sample_top_p_top_k: probs must be contiguous fp32 [N, V]");
+    TORCH_CHECK(uniform.is_cuda() && uniform.scalar_type() == at::kFloat && uniform.is_contiguous() &&
+                    uniform.numel() == probs.size(0),
+                "sample_top_p_top_k: uniform must be fp32 [N]");
+    TORCH_CHECK(p > 0.0 && k >= 0, "sample_top_p_top_k: p must be in (0, 1] and k non-negative");
+    c10::cuda::CUDAGuard guard(probs.device());
+    Tensor out = at::empty({probs.size(0)}, probs.options().dtype(at::kLong));
+    if (probs.size(0) == 0) return out;
+    fs2::sample_top_p_top_k(probs.data_ptr<float>(), uniform.data_ptr<float>(),
+                            reinterpret_cast<long long*>(out.data_ptr<int64_t>()), static_cast<int>(probs.size(0)),
+                            static_cast<int>(probs.size(1)), static_cast<float>(p), static_cast<int>(k),
+                            stream_of(probs));
+    g_launches += 1;
+    return out;
+}
+
+std::tuple<Tensor, Tensor> beam_topk(const Tensor& lprobs, const Tensor& beam_scores, int64_t k) {
+    TORCH_CHECK(lprobs.is_cuda() && lprobs.scalar_type() == at::kFloat && lprobs.dim() == 3 && lprobs.is_contiguous(),
+                "beam_topk: lprobs must be contiguous fp32 [N, beams, V]");
+    TORCH_CHECK(beam_scores.is_cuda() && beam_scores.scalar_type() == at::kFloat && beam_scores.is_contiguous() &&
+                    beam_scores.dim() == 2 && beam_scores.size(0) == lprobs.size(0) &&
+                    beam_scores.size(1) == lprobs.size(1),
+                "beam_topk: beam_scores must be contiguous fp32 [N, beams]");
+    TORCH_CHECK(k >= 1 && k <= 32 && k <= lprobs.size(1) * lprobs.size(2), "beam_topk: k must be in [1, 32]");
+    c10::cuda::CUDAGuard guard(lprobs.device());
+    Tensor scores = at::empty({lprobs.size(0), k}, lprobs.options());
+    Tensor idx = at::empty({lprobs.size(0), k}, lprobs.options().dtype(at::kLong));
+    if (lprobs.size(0) == 0) return {scores, idx};
+    fs2::beam_topk(lprobs.data_ptr<float>(), beam_scores.data_ptr<float>(), scores.data_ptr<float>(),
+                   reinterpret_cast<long long*>(idx.data_ptr<int64_t>()), static_cast<int>(lprobs.size(0)),
+                   static_cast<int>(lprobs.size(1)), static_cast<int>(lprobs.size(2)), static_cast<int>(k),
+                   stream_of(lprobs));
+    g_launches += 1;
+    return {scores, idx};
 }
 
 // -------------------------------------------------------------- cross-entropy
@@ -569,6 +625,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("comm_allreduce_f32", &comm_allreduce_f32);
     m.def("comm_pull", &comm_pull);
     m.def("comm_alltoall", &comm_alltoall);
+    m.def("ngram_repeat_block", &ngram_repeat_block);
+    m.def("sample_top_p_top_k", &sample_top_p_top_k);
+    m.def("beam_topk", &beam_topk);
     m.def("launch_count", &launch_count);
     m.def("reset_launch_count", &reset_launch_count);
     m.def("check_status", &check_status, "Raises if a kernel recorded a bounded-wait failure.");

@@ -185,10 +185,13 @@ class BeamSearchAlgorithm(ABC):
 
 class StandardBeamSearchAlgorithm(BeamSearchAlgorithm):
     def step(self, beam_size: int, lprobs: Tensor, scores: Tensor) -> tuple[Tensor, Tensor, Tensor]:
+        from fairseq2_b200.ops.sampling import beam_topk
+
         V = lprobs.shape[-1]
-        cand = (lprobs + scores.unsqueeze(-1)).view(-1)
-        k = min(2 * beam_size, cand.numel() - 1) if cand.numel() > 1 else 1
-        top, idx = torch.topk(cand, k)
+        n = lprobs.numel()
+        k = min(2 * beam_size, n - 1) if n > 1 else 1
+        top, idx = beam_topk(lprobs.unsqueeze(0).float(), scores.unsqueeze(0).float(), k)
+        top, idx = top[0].to(lprobs.dtype), idx[0]
         return idx // V, idx % V, top
 
 

@@ -31,5 +31,12 @@ def _register_lm_families() -> None:
             name=name, kls=TransformerLM, config_kls=cfg, factory=factory, state_dict_converter=conv,
             fsdp_wrap_policy=layerwise_wrap_policy, layerwise_ac_applier=apply_layerwise_ac, hg_exporter=exp))
 
+    from fairseq2_b200.models.llama4 import LLAMA4_FAMILY, Llama4Config, convert_llama4_state_dict, create_llama4_model
+
+    register_model_family(ModelFamily(
+        name=LLAMA4_FAMILY, kls=TransformerLM, config_kls=Llama4Config, factory=create_llama4_model,
+        state_dict_converter=convert_llama4_state_dict, fsdp_wrap_policy=layerwise_wrap_policy,
+        layerwise_ac_applier=apply_layerwise_ac))
+
 
 _register_lm_families()

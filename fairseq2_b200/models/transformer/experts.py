@@ -1,0 +1,157 @@
+"""Mixture-of-experts feed-forward network (cf. fairseq2 ``models/transformer/experts.py:85-369``,
+``models/llama4/moe.py:24-157``).
+
+The reference feeds EVERY token to EVERY expert with the non-selected ones
+multiplied by ``sigmoid(-inf) = 0``, i.e. ``num_experts`` times the needed
+FLOPs. Here tokens are dispatched sparsely: rows are permuted so that each
+expert's tokens are contiguous, every expert runs one GEMM over exactly its
+rows, and the results are combined with an index-add. Because the experts are
+bias-free GLU networks, ``expert(0) = 0`` and the two formulations agree.
+"""
+from __future__ import annotations
+
+import math
+from abc import ABC, abstractmethod
+
+import torch
+from torch import Tensor
+from torch.nn import Module, Parameter, SiLU
+
+from fairseq2_b200.gang import Gang
+from fairseq2_b200.models.transformer.ffn import FeedForwardNetwork, GLUFeedForwardNetwork
+from fairseq2_b200.ops.grouped_gemm import grouped_mm
+from fairseq2_b200.ops.tensor_parallel import reduce
+from fairseq2_b200.typing import DataType, Device
+
+
+class ExpertNetwork(Module, ABC):
+    def __init__(self, num_experts: int, model_dim: int, inner_dim: int) -> None:
+        super().__init__()
+        self.num_experts, self.model_dim, self.inner_dim = num_experts, model_dim, inner_dim
+
+    @abstractmethod
+    def forward(self, x: Tensor, group_sizes: list[int]) -> Tensor:
+        """``x``: ``[R, model_dim]`` rows sorted by expert, ``group_sizes[e]`` rows for expert ``e``."""
+
+    @property
+    def num_local_experts(self) -> int:
+        return self.num_experts
+
+
+class GroupedExpertNetwork(ExpertNetwork):
+    """All experts' GLU weights stacked: ``gate_proj``/``inner_proj`` ``[E, D, F]``, ``output_proj`` ``[E, F, D]``."""
+
+    def __init__(self, num_experts: int, model_dim: int, inner_dim: int, *, activation: Module | None = None,
+                 device: Device | None = None, dtype: DataType | None = None) -> None:
+        super().__init__(num_experts, model_dim, inner_dim)
+        kw = {"device": device, "dtype": dtype}
+        self.gate_proj = Parameter(torch.empty((num_experts, model_dim, inner_dim), **kw))
+        self.inner_proj = Parameter(torch.empty((num_experts, model_dim, inner_dim), **kw))
+        self.output_proj = Parameter(torch.empty((num_experts, inner_dim, model_dim), **kw))
+        self.activation = activation if activation is not None else SiLU()
+        self.reset_parameters()
+
+    def reset_parameters(self) -> None:
+        for w in (self.gate_proj, self.inner_proj, self.output_proj):
+            if w.device.type != "meta":
+                torch.nn.init.trunc_normal_(w, std=w.shape[1] ** -0.5, a=-3 * w.shape[1] ** -0.5, b=3 * w.shape[1] ** -0.5)
+
+    def forward(self, x: Tensor, group_sizes: list[int]) -> Tensor:
+        h = self.activation(grouped_mm(x, self.gate_proj, group_sizes)) * grouped_mm(x, self.inner_proj, group_sizes)
+        return grouped_mm(h, self.output_proj, group_sizes)
+
+
+class TPShardedExpertNetwork(ExpertNetwork):
+    """Every expert's inner dimension is split over the tensor-parallel gang; the caller reduces the output."""
+
+    def __init__(self, gang: Gang, num_experts: int, model_dim: int, inner_dim: int, *,
+                 activation: Module | None = None, device: Device | None = None, dtype: DataType | None = None) -> None:
+        super().__init__(num_experts, model_dim, inner_dim)
+        if inner_dim % gang.size:
+            raise ValueError(f"`inner_dim` ({inner_dim}) must be a multiple of the gang size ({gang.size}).")
+        self.gang = gang
+        f = inner_dim // gang.size
+        kw = {"device": device, "dtype": dtype}
+        self.gate_proj = Parameter(torch.empty((num_experts, model_dim, f), **kw))
+        self.inner_proj = Parameter(torch.empty((num_experts, model_dim, f), **kw))
+        self.output_proj = Parameter(torch.empty((num_experts, f, model_dim), **kw))
+        self.activation = activation if activation is not None else SiLU()
+        GroupedExpertNetwork.reset_parameters(self)  # type: ignore[arg-type]
+
+    @staticmethod
+    def from_grouped_expert_network(net: GroupedExpertNetwork, gang: Gang) -> "TPShardedExpertNetwork":
+        out = TPShardedExpertNetwork(gang, net.num_experts, net.model_dim, net.inner_dim, activation=net.activation,
+                                     device=net.gate_proj.device, dtype=net.gate_proj.dtype)
+        f, r = net.inner_dim // gang.size, gang.rank
+        with torch.no_grad():
+            out.gate_proj.copy_(net.gate_proj[:, :, r * f:(r + 1) * f])
+            out.inner_proj.copy_(net.inner_proj[:, :, r * f:(r + 1) * f])
+            out.output_proj.copy_(net.output_proj[:, r * f:(r + 1) * f, :])
+        return out
+
+    def forward(self, x: Tensor, group_sizes: list[int]) -> Tensor:
+        h = self.activation(grouped_mm(x, self.gate_proj, group_sizes)) * grouped_mm(x, self.inner_proj, group_sizes)
+        return grouped_mm(h, self.output_proj, group_sizes)
+
+
+def route_tokens(logits: Tensor, top_k: int) -> tuple[Tensor, Tensor, Tensor, list[int]]:
+    """Token-choice routing. Returns ``(token_idx [R], expert_scores [R], order, group_sizes)`` where the ``R = T·k``
+    routed rows are sorted by expert; ``expert_scores`` is ``sigmoid`` of the selected logits."""
+    T, E = logits.shape
+    scores, experts = torch.topk(logits, top_k, dim=1)                   # [T, k]
+    flat_e = experts.reshape(-1)
+    order = torch.argsort(flat_e, stable=True)                           # rows grouped by expert
+    token_idx = order // top_k
+    sizes = torch.bincount(flat_e, minlength=E).tolist()
+    return token_idx, torch.sigmoid(scores.reshape(-1)[order].float()), order, sizes
+
+
+class MoE(FeedForwardNetwork):
+    """Top-k routed experts plus an optional always-on shared expert (LLaMA-4)."""
+
+    def __init__(self, model_dim: int, inner_dim: int, use_shared_expert: bool, num_experts: int,
+                 capacity_factor: float, top_k: int, *, moe_activation: Module | None = None,
+                 inner_dim_scale: float = 2 / 3, inner_dim_to_multiple: int = 1, auto_scale: bool = True,
+                 tp_gang: Gang | None = None, device: Device | None = None, dtype: DataType | None = None) -> None:
+        super().__init__(model_dim)
+        if inner_dim_scale != 1.0:
+            inner_dim = int(inner_dim * inner_dim_scale)
+        if auto_scale:
+            # keep the activated parameter count equal to that of a dense layer
+            inner_dim = int(inner_dim / (capacity_factor + int(use_shared_expert)))
+        if inner_dim_to_multiple != 1:
+            inner_dim = inner_dim_to_multiple * ((inner_dim + inner_dim_to_multiple - 1) // inner_dim_to_multiple)
+        self.inner_dim, self.num_experts, self.top_k = inner_dim, num_experts, top_k
+        self.tp_gang = tp_gang if tp_gang is not None and tp_gang.size > 1 else None
+        self.shared_expert: GLUFeedForwardNetwork | None = None
+        if use_shared_expert:
+            self.shared_expert = GLUFeedForwardNetwork(model_dim, inner_dim, bias=False, inner_dim_scale=1.0,
+                                                       device=device, dtype=dtype)
+        self.router = Parameter(torch.empty((model_dim, num_experts), device=device, dtype=dtype))
+        if self.tp_gang is not None:
+            self.experts: ExpertNetwork = TPShardedExpertNetwork(self.tp_gang, num_experts, model_dim, inner_dim,
+                                                                 activation=moe_activation, device=device, dtype=dtype)
+        else:
+            self.experts = GroupedExpertNetwork(num_experts, model_dim, inner_dim, activation=moe_activation,
+                                                device=device, dtype=dtype)
+        self.reset_parameters()
+
+    def reset_parameters(self) -> None:
+        if self.router.device.type != "meta":
+            torch.nn.init.trunc_normal_(self.router, std=self.model_dim ** -0.5)
+
+    def forward(self, seqs: Tensor) -> Tensor:
+        x = seqs.reshape(-1, self.model_dim)
+        logits = x @ self.router
+        token_idx, scores, _, sizes = route_tokens(logits, self.top_k)
+        routed_in = x.index_select(0, token_idx) * scores.to(x.dtype).unsqueeze(1)
+        routed_out = self.experts(routed_in, sizes)
+        out = self.shared_expert(x) if self.shared_expert is not None else torch.zeros_like(x)
+        out = out.index_add(0, token_idx, routed_out)
+        if self.tp_gang is not None:
+            out = reduce(out, self.tp_gang)
+        return out.view(seqs.shape)
+
+    def extra_repr(self) -> str:
+        return (f"model_dim={self.model_dim}, inner_dim={self.inner_dim}, num_experts={self.num_experts}, "
+                f"top_k={self.top_k}")

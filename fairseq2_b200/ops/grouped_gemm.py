@@ -1,0 +1,64 @@
+"""Grouped GEMM over row groups (mixture-of-experts feed-forward).
+
+``grouped_mm(x, w, group_sizes)``: ``x`` is ``[T, K]`` with rows sorted by
+group, ``w`` is ``[G, K, N]``; rows of group ``g`` are multiplied by ``w[g]``.
+On CUDA each group is one tcgen05 GEMM launch writing straight into its row
+slice of the output (and, in backward, into its slice of ``dx`` / its page of
+``dw``), so nothing is concatenated or copied.
+"""
+from __future__ import annotations
+
+from typing import Sequence
+
+import torch
+from torch import Tensor
+
+from fairseq2_b200.ops.gemm import gemm
+
+
+def grouped_mm_reference(x: Tensor, w: Tensor, group_sizes: Sequence[int]) -> Tensor:
+    out = x.new_empty((x.shape[0], w.shape[2]))
+    s = 0
+    for g, n in enumerate(group_sizes):
+        out[s:s + n] = (x[s:s + n].float() @ w[g].float()).to(x.dtype)
+        s += n
+    return out
+
+
+class _GroupedMM(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x: Tensor, w: Tensor, group_sizes: tuple[int, ...]) -> Tensor:  # type: ignore[override]
+        x = x.contiguous()
+        y = x.new_empty((x.shape[0], w.shape[2]))
+        s = 0
+        for g, n in enumerate(group_sizes):
+            if n:
+                gemm(x[s:s + n], w[g], b_mn=True, out=y[s:s + n])
+            s += n
+        ctx.save_for_backward(x, w)
+        ctx.group_sizes = group_sizes
+        return y
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):  # type: ignore[override]
+        x, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = torch.empty_like(x) if ctx.needs_input_grad[0] else None
+        dw = torch.zeros_like(w) if ctx.needs_input_grad[1] else None
+        s = 0
+        for g, n in enumerate(ctx.group_sizes):
+            if n:
+                if dx is not None:
+                    gemm(dy[s:s + n], w[g], out=dx[s:s + n])                    # dy · w[g]ᵀ
+                if dw is not None:
+                    gemm(x[s:s + n], dy[s:s + n], a_mn=True, b_mn=True, out=dw[g])  # xᵀ · dy
+            s += n
+        return dx, dw, None
+
+
+def grouped_mm(x: Tensor, w: Tensor, group_sizes: Sequence[int]) -> Tensor:
+    if sum(group_sizes) != x.shape[0]:
+        raise ValueError(f"`group_sizes` must sum to the number of rows of `x` ({x.shape[0]}).")
+    if len(group_sizes) != w.shape[0]:
+        raise ValueError(f"`group_sizes` must have one entry per group of `w` ({w.shape[0]}).")
+    return _GroupedMM.apply(x, w, tuple(int(n) for n in group_sizes))

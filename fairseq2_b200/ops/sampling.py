@@ -1,5 +1,5 @@
-"""Generation-step operators -- worklist row W15: n-gram repeat blocking,
-top-p / top-k sampling and beam top-k. The CUDA kernels live in
+"""Generation-step operators: n-gram repeat blocking, top-p / top-k sampling
+and beam-search candidate selection. The CUDA kernels live in
 ``csrc/generation.cu``; the PyTorch formulations below are the CPU path and
 the oracles.
 
@@ -13,7 +13,7 @@ from __future__ import annotations
 import torch
 from torch import Tensor
 
-from fairseq2_b200.ops._ext import get_ext, use_kernels
+from fairseq2_b200.ops._ext import require_ext, use_kernels
 
 
 def ngram_repeat_block_reference(seqs: Tensor, probs: Tensor, n: int, ban_value: float) -> None:
@@ -34,10 +34,8 @@ def ngram_repeat_block_reference(seqs: Tensor, probs: Tensor, n: int, ban_value:
 
 def ngram_repeat_block(seqs: Tensor, probs: Tensor, n: int, ban_value: float) -> None:
     if use_kernels(seqs, probs) and probs.dtype == torch.float32 and probs.is_contiguous():
-        ext = get_ext()
-        if hasattr(ext, "ngram_repeat_block"):
-            ext.ngram_repeat_block(seqs.contiguous(), probs, n, ban_value)
-            return
+        require_ext().ngram_repeat_block(seqs.contiguous(), probs, n, ban_value)
+        return
     ngram_repeat_block_reference(seqs, probs, n, ban_value)
 
 
@@ -69,11 +67,25 @@ def sample_top_p_top_k(probs: Tensor, *, p: float = 1.0, k: int = 0, generator: 
     CDF of the kept entries with one uniform random number per row.
     """
     if use_kernels(probs) and probs.dtype == torch.float32 and probs.is_contiguous():
-        ext = get_ext()
-        if hasattr(ext, "sample_top_p_top_k"):
-            if uniform is None:
-                uniform = torch.rand(probs.shape[0], device=probs.device, generator=generator)
-            return ext.sample_top_p_top_k(probs, uniform, float(p), int(k))
+        if uniform is None:
+            uniform = torch.rand(probs.shape[0], device=probs.device, generator=generator)
+        return require_ext().sample_top_p_top_k(probs, uniform, float(p), int(k))
     if k > 0:
         return top_k_sample_reference(probs, k, generator)
     return top_p_sample_reference(probs, p, generator)
+
+
+def beam_topk_reference(lprobs: Tensor, beam_scores: Tensor, k: int) -> tuple[Tensor, Tensor]:
+    """``lprobs``: ``[N, beams, V]``, ``beam_scores``: ``[N, beams]`` -> top ``k`` of the summed scores over the
+    flattened ``beams*V`` candidates, as ``(scores [N, k], flat indices [N, k])``."""
+    cand = (lprobs + beam_scores.unsqueeze(-1)).flatten(1)
+    return torch.topk(cand, k, dim=-1)
+
+
+def beam_topk(lprobs: Tensor, beam_scores: Tensor, k: int) -> tuple[Tensor, Tensor]:
+    """Adds the running beam scores and selects the best ``k`` continuations in one kernel, without
+    materialising the ``[N, beams*V]`` sum."""
+    if (use_kernels(lprobs) and lprobs.dtype == torch.float32 and lprobs.is_contiguous() and k <= 32
+            and beam_scores.dtype == torch.float32):
+        return require_ext().beam_topk(lprobs, beam_scores.contiguous(), k)
+    return beam_topk_reference(lprobs, beam_scores, k)

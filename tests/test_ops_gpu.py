@@ -278,3 +278,76 @@ def test_adamw_and_norm(gdtype: torch.dtype) -> None:
     gc = g.clone()
     multi_tensor_scale([gc], scale)
     assert _rel_err(gc, g.float() * 0.5) < 5e-3
+
+
+# ------------------------------------------------------------------ generation kernels
+@pytest.mark.gpu
+@pytest.mark.parametrize("n", [1, 2, 3, 4])
+def test_ngram_repeat_block_kernel(n: int) -> None:
+    from fairseq2_b200.ops.sampling import ngram_repeat_block, ngram_repeat_block_reference
+
+    torch.manual_seed(n)
+    seqs = torch.randint(0, 6, (9, 37), device="cuda")
+    probs = torch.rand(9, 50, device="cuda")
+    ref = probs.clone()
+    ngram_repeat_block_reference(seqs, ref, n, 0.0)
+    ngram_repeat_block(seqs, probs, n, 0.0)
+    assert torch.equal(probs, ref)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("V", [1000, 32000, 128256])
+def test_sample_kernel_support_matches_reference(V: int) -> None:
+    """Every sampled token must lie in the reference's kept set, and extreme uniforms must hit its ends."""
+    from fairseq2_b200.ops.sampling import sample_top_p_top_k
+
+    torch.manual_seed(0)
+    N = 16
+    probs = torch.softmax(torch.randn(N, V, device="cuda") * 3, dim=-1)
+    for p, k in ((0.9, 0), (0.5, 0), (1.0, 10), (1.0, 1), (0.7, 50)):
+        sp, si = torch.sort(probs, dim=-1, descending=True)
+        keep = torch.ones_like(sp, dtype=torch.bool)
+        if p < 1.0:
+            keep &= (torch.cumsum(sp, -1) - sp) <= p
+        if k > 0:
+            keep &= torch.arange(V, device="cuda")[None, :] < k
+        kept = torch.zeros_like(keep).scatter(1, si, keep)
+        for _ in range(4):
+            u = torch.rand(N, device="cuda")
+            tok = sample_top_p_top_k(probs, p=p, k=k, uniform=u)
+            assert bool(kept.gather(1, tok[:, None]).all()), (p, k)
+        # u -> 0 picks the first kept index, u -> 1 the last
+        first = kept.float().argmax(dim=1)
+        last = V - 1 - kept.flip(1).float().argmax(dim=1)
+        assert torch.equal(sample_top_p_top_k(probs, p=p, k=k, uniform=torch.zeros(N, device="cuda")), first)
+        assert torch.equal(sample_top_p_top_k(probs, p=p, k=k, uniform=torch.ones(N, device="cuda")), last)
+
+
+@pytest.mark.gpu
+def test_sample_kernel_distribution() -> None:
+    from fairseq2_b200.ops.sampling import sample_top_p_top_k
+
+    torch.manual_seed(1)
+    V, draws = 64, 40000
+    base = torch.softmax(torch.randn(V, device="cuda"), dim=-1)
+    probs = base.expand(draws, V).contiguous()
+    tok = sample_top_p_top_k(probs, p=0.8, k=0, uniform=torch.rand(draws, device="cuda"))
+    sp, si = torch.sort(base, descending=True)
+    keep = (torch.cumsum(sp, 0) - sp) <= 0.8
+    expect = torch.zeros(V, device="cuda").scatter(0, si, sp * keep)
+    expect = expect / expect.sum()
+    freq = torch.bincount(tok, minlength=V).float() / draws
+    assert float((freq - expect).abs().max()) < 0.01
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("beams,V,k", [(1, 1000, 2), (4, 32000, 8), (5, 128256, 10)])
+def test_beam_topk_kernel(beams: int, V: int, k: int) -> None:
+    from fairseq2_b200.ops.sampling import beam_topk, beam_topk_reference
+
+    torch.manual_seed(0)
+    lp = torch.log_softmax(torch.randn(3, beams, V, device="cuda"), dim=-1)
+    sc = torch.randn(3, beams, device="cuda")
+    s, i = beam_topk(lp, sc, k)
+    rs, ri = beam_topk_reference(lp, sc, k)
+    assert torch.allclose(s, rs) and torch.equal(i, ri)
