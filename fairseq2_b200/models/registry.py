@@ -40,3 +40,28 @@ def _register_lm_families() -> None:
 
 
 _register_lm_families()
+
+
+def _encoder_wrap_policy(module):  # type: ignore[no-untyped-def]
+    """One FSDP unit per encoder layer (speech encoders keep the front end in the root unit)."""
+    enc = getattr(module, "encoder", None)
+    return list(enc.layers) if enc is not None and hasattr(enc, "layers") else []
+
+
+def _register_speech_families() -> None:
+    from fairseq2_b200.models.wav2vec2 import (WAV2VEC2_FAMILY, Wav2Vec2Config, Wav2Vec2Model,
+                                               convert_wav2vec2_asr_state_dict, convert_wav2vec2_state_dict,
+                                               create_wav2vec2_model)
+    from fairseq2_b200.models.wav2vec2.asr import (WAV2VEC2_ASR_FAMILY, Wav2Vec2AsrConfig, Wav2Vec2AsrModel,
+                                                   create_wav2vec2_asr_model)
+
+    register_model_family(ModelFamily(
+        name=WAV2VEC2_FAMILY, kls=Wav2Vec2Model, config_kls=Wav2Vec2Config, factory=create_wav2vec2_model,
+        state_dict_converter=convert_wav2vec2_state_dict, fsdp_wrap_policy=_encoder_wrap_policy, supports_meta=False))
+    register_model_family(ModelFamily(
+        name=WAV2VEC2_ASR_FAMILY, kls=Wav2Vec2AsrModel, config_kls=Wav2Vec2AsrConfig,
+        factory=create_wav2vec2_asr_model, state_dict_converter=convert_wav2vec2_asr_state_dict,
+        fsdp_wrap_policy=_encoder_wrap_policy, supports_meta=False))
+
+
+_register_speech_families()

@@ -1,0 +1,84 @@
+"""Convolutional position encoders of wav2vec 2.0 (cf. fairseq2 ``models/wav2vec2/position_encoder.py:32-289``)."""
+from __future__ import annotations
+
+import torch
+from torch import Tensor
+from torch.nn import GELU, Conv1d, Module, Sequential
+from torch.nn.utils.parametrizations import weight_norm
+
+from fairseq2_b200.nn.batch_layout import BatchLayout
+from fairseq2_b200.nn.incremental_state import IncrementalStateBag
+from fairseq2_b200.nn.normalization import StandardLayerNorm
+from fairseq2_b200.nn.position_encoder import PositionEncoder
+from fairseq2_b200.nn.utils.mask import apply_mask
+from fairseq2_b200.typing import DataType, Device
+
+
+class Wav2Vec2PositionalConv1d(Conv1d):
+    def reset_parameters(self) -> None:
+        if self.weight.device.type == "meta":
+            return
+        model_dim, kernel_size = self.in_channels, self.kernel_size[0]
+        std = (4.0 / (kernel_size * model_dim)) ** 0.5
+        torch.nn.init.normal_(self.weight, mean=0.0, std=std)
+        if self.bias is not None:
+            torch.nn.init.zeros_(self.bias)
+
+
+def _zero_padding(seqs: Tensor, layout: BatchLayout) -> Tensor:
+    if not layout.padded:
+        return seqs
+    return apply_mask(seqs, layout.position_indices >= 0)
+
+
+class Wav2Vec2PositionEncoder(PositionEncoder):
+    """``x + GELU(grouped_conv(x))`` with a weight-normalised, same-padded convolution."""
+
+    def __init__(self, model_dim: int, kernel_size: int, num_groups: int, *, device: Device | None = None,
+                 dtype: DataType | None = None) -> None:
+        super().__init__(model_dim)
+        conv = Wav2Vec2PositionalConv1d(model_dim, model_dim, kernel_size, padding=kernel_size // 2, groups=num_groups,
+                                        device=device, dtype=dtype)
+        self.conv = weight_norm(conv, dim=2)
+        self.remove_pad = kernel_size % 2 == 0
+        self.activation = GELU()
+
+    def forward(self, seqs: Tensor, seqs_layout: BatchLayout, *, state_bag: IncrementalStateBag | None = None) -> Tensor:
+        if state_bag is not None:
+            raise ValueError("`Wav2Vec2PositionEncoder` does not support incremental decoding.")
+        seqs = _zero_padding(seqs, seqs_layout)      # padding must not leak into the convolution
+        enc = self.conv(seqs.transpose(1, 2))
+        if self.remove_pad:
+            enc = enc[:, :, :-1]
+        return seqs + self.activation(enc).transpose(1, 2)
+
+
+class Wav2Vec2StackedPositionEncoder(PositionEncoder):
+    """``depth`` smaller grouped convolutions, each followed by a parameter-free layer norm and GELU."""
+
+    def __init__(self, model_dim: int, kernel_size: int, num_groups: int, num_layers: int, *,
+                 device: Device | None = None, dtype: DataType | None = None) -> None:
+        super().__init__(model_dim)
+        k = max(3, kernel_size // num_layers)
+        self.layers = Sequential(*[_StackedLayer(model_dim, k, num_groups, device, dtype) for _ in range(num_layers)])
+
+    def forward(self, seqs: Tensor, seqs_layout: BatchLayout, *, state_bag: IncrementalStateBag | None = None) -> Tensor:
+        if state_bag is not None:
+            raise ValueError("`Wav2Vec2StackedPositionEncoder` does not support incremental decoding.")
+        seqs = _zero_padding(seqs, seqs_layout)
+        return seqs + self.layers(seqs.transpose(1, 2)).transpose(1, 2)
+
+
+class _StackedLayer(Module):
+    def __init__(self, model_dim: int, kernel_size: int, num_groups: int, device: Device | None,
+                 dtype: DataType | None) -> None:
+        super().__init__()
+        self.conv = Conv1d(model_dim, model_dim, kernel_size, padding="same", groups=num_groups, device=device,
+                           dtype=dtype)
+        self.layer_norm = StandardLayerNorm(model_dim, bias=False, elementwise_affine=False)
+        self.activation = GELU()
+
+    def forward(self, x: Tensor) -> Tensor:
+        x = self.conv(x)
+        x = self.layer_norm(x.transpose(1, 2)).transpose(1, 2)
+        return self.activation(x)

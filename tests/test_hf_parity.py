@@ -88,3 +88,32 @@ def test_olmo2_matches_hf() -> None:
     c = OLMOConfig(model_dim=128, max_seq_len=256, vocab_size=512, pad_idx=0, num_layers=2, num_attn_heads=4,
                    num_key_value_heads=2, ffn_inner_dim=256)
     _check(_ours("olmo", c, hf), hf, 512)
+
+
+@pytest.mark.parametrize("stable", [False, True])
+def test_wav2vec2_asr_matches_hf(stable: bool) -> None:
+    from fairseq2_b200.models.transformer.norm_order import TransformerNormOrder
+    from fairseq2_b200.models.wav2vec2 import Wav2Vec2EncoderConfig
+    from fairseq2_b200.models.wav2vec2.asr import Wav2Vec2AsrConfig
+
+    hc = transformers.Wav2Vec2Config(
+        vocab_size=16, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, intermediate_size=128,
+        conv_dim=(32, 32, 32), conv_stride=(5, 2, 2), conv_kernel=(10, 3, 2), conv_bias=stable,
+        feat_extract_norm="layer" if stable else "group", do_stable_layer_norm=stable, num_conv_pos_embeddings=16,
+        num_conv_pos_embedding_groups=4, hidden_dropout=0.0, attention_dropout=0.0, activation_dropout=0.0,
+        feat_proj_dropout=0.0, final_dropout=0.0, layerdrop=0.0, mask_time_prob=0.0)
+    hf = transformers.Wav2Vec2ForCTC(hc).eval()
+    e = Wav2Vec2EncoderConfig(
+        model_dim=64, max_seq_len=512, feature_dim=32, feature_extractor_layer_descs=[(32, 10, 5), (32, 3, 2), (32, 2, 2)],
+        feature_extractor_bias=stable, feature_extractor_layer_norm_convs=stable, pos_conv_kernel_size=16,
+        num_pos_conv_groups=4, num_encoder_layers=2, num_encoder_attn_heads=4, ffn_inner_dim=128, dropout_p=0.0,
+        attn_dropout_p=0.0, layer_drop_p=0.0, norm_order=TransformerNormOrder.PRE if stable else TransformerNormOrder.POST)
+    c = Wav2Vec2AsrConfig(encoder_config=e, target_vocab_size=16, use_masking=False)
+    model = _ours("wav2vec2_asr", c, hf)
+    torch.manual_seed(0)
+    x = torch.randn(2, 3000)
+    with torch.no_grad():
+        ref = hf(x).logits
+        out, layout = model(x, BatchLayout((2, 3000), [3000, 3000]))
+    assert layout.seq_lens == [ref.shape[1]] * 2
+    assert torch.allclose(out, ref, atol=2e-4, rtol=1e-3), float((out - ref).abs().max())
