@@ -25,7 +25,7 @@ struct AttnParams {
     const int* q_lens;
     const int* k_begins;
     const int* k_lens;
-    int num_seqs, total_q, max_q, max_k;
+    int num_seqs, total_q, total_k, max_q, max_k;
     int H, Hkv, D;
     int causal;
     float scale;
@@ -34,5 +34,8 @@ struct AttnParams {
 // Return nullptr on success, else a static error string.
 const char* attn_forward(const AttnParams& p, cudaStream_t st);
 const char* attn_backward(const AttnParams& p, cudaStream_t st);
+
+// tcgen05/TMEM path (head_dim 128); `status` is the host-mapped status word for bounded waits.
+const char* attn_forward_tc(const AttnParams& p, int* status, cudaStream_t st);
 
 }  // namespace fs2

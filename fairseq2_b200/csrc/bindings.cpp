@@ -7,7 +7,9 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <cstdlib>
 #include <optional>
+#include <string>
 #include <tuple>
 #include <vector>
 
@@ -338,6 +340,7 @@ fs2::AttnParams make_attn_params(const Tensor& q, const Tensor& k, const Tensor&
     p.k_lens = kl.data_ptr<int>();
     p.num_seqs = static_cast<int>(qb.numel());
     p.total_q = static_cast<int>(q.size(0));
+    p.total_k = static_cast<int>(k.size(0));
     p.max_q = static_cast<int>(max_q);
     p.max_k = static_cast<int>(max_k);
     p.H = static_cast<int>(q.size(1));
@@ -359,7 +362,13 @@ std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tens
     p.o = static_cast<__nv_bfloat16*>(out.data_ptr());
     p.o_tstride = out.stride(0);
     p.lse = lse.data_ptr<float>();
-    const char* err = fs2::attn_forward(p, stream_of(q));
+    // head_dim 128 runs on the tcgen05/TMEM kernel; FAIRSEQ2_B200_ATTN=mma selects the mma.sync kernel instead
+    static const bool use_tc = []() {
+        const char* e = std::getenv("FAIRSEQ2_B200_ATTN");
+        return e == nullptr || std::string(e) != "mma";
+    }();
+    const char* err = (use_tc && p.D == 128) ? fs2::attn_forward_tc(p, status_dev_ptr(), stream_of(q))
+                                             : fs2::attn_forward(p, stream_of(q));
     TORCH_CHECK(err == nullptr, "attn_fwd: ", err);
     g_launches += 1;
     return {out, lse};

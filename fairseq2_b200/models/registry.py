@@ -63,5 +63,30 @@ def _register_speech_families() -> None:
         factory=create_wav2vec2_asr_model, state_dict_converter=convert_wav2vec2_asr_state_dict,
         fsdp_wrap_policy=_encoder_wrap_policy, supports_meta=False))
 
+    from fairseq2_b200.models.nllb import NLLB_FAMILY, NllbConfig, convert_nllb_state_dict, create_nllb_model
+    from fairseq2_b200.models.s2t_transformer import (S2T_CONFORMER_FAMILY, S2T_TRANSFORMER_FAMILY, S2TConformerConfig,
+                                                      S2TTransformerConfig, convert_s2t_state_dict,
+                                                      create_s2t_conformer_model, create_s2t_transformer_model)
+    from fairseq2_b200.models.transformer.model import TransformerModel
+    from fairseq2_b200.models.w2vbert import W2VBERT_FAMILY, W2VBertConfig, W2VBertModel, create_w2vbert_model
+
+    def enc_dec_policy(module):  # type: ignore[no-untyped-def]
+        return list(module.encoder.layers) + list(module.decoder.layers)
+
+    register_model_family(ModelFamily(
+        name=NLLB_FAMILY, kls=TransformerModel, config_kls=NllbConfig, factory=create_nllb_model,
+        state_dict_converter=convert_nllb_state_dict, fsdp_wrap_policy=enc_dec_policy, supports_meta=False))
+    register_model_family(ModelFamily(
+        name=S2T_TRANSFORMER_FAMILY, kls=TransformerModel, config_kls=S2TTransformerConfig,
+        factory=create_s2t_transformer_model, state_dict_converter=convert_s2t_state_dict,
+        fsdp_wrap_policy=enc_dec_policy, supports_meta=False))
+    register_model_family(ModelFamily(
+        name=S2T_CONFORMER_FAMILY, kls=TransformerModel, config_kls=S2TConformerConfig,
+        factory=create_s2t_conformer_model, state_dict_converter=convert_s2t_state_dict,
+        fsdp_wrap_policy=enc_dec_policy, supports_meta=False))
+    register_model_family(ModelFamily(
+        name=W2VBERT_FAMILY, kls=W2VBertModel, config_kls=W2VBertConfig, factory=create_w2vbert_model,
+        fsdp_wrap_policy=lambda m: list(m.w2v2_model.encoder.layers), supports_meta=False))
+
 
 _register_speech_families()

@@ -47,4 +47,14 @@ def compute_row_mask(shape: tuple[int, int], span_len: int, max_mask_prob: float
     mask = torch.zeros((num_rows, max_row_len), device=dev, dtype=torch.bool)
     mask.scatter_(1, idx.clamp(max=max_row_len - 1), True)
     valid = torch.arange(max_row_len, device=dev).view(1, -1) < row_lens.view(-1, 1)
-    return mask & valid
+    mask &= valid
+    # Overlapping spans leave rows with different numbers of masked elements. Consumers gather the masked
+    # elements into a dense (rows, count) tensor, so surplus elements are unmasked at random: every masked
+    # element draws a key and only the `min count` smallest keys of a row stay masked.
+    counts = mask.sum(dim=1)
+    keep = int(counts.min())
+    if keep < int(counts.max()):
+        keys = torch.rand(mask.shape, device=dev, generator=generator).masked_fill_(~mask, 2.0)
+        kth = keys.kthvalue(keep, dim=1, keepdim=True).values if keep > 0 else keys.new_full((num_rows, 1), -1.0)
+        mask &= keys <= kth
+    return mask

@@ -197,6 +197,25 @@ def test_attention_fwd_bwd(causal: bool, D: int, H: int, Hkv: int, lens: list[in
     assert _rel_err(v.grad, vr.grad) < 2e-2
 
 
+@pytest.mark.parametrize("causal", [True, False])
+def test_attention_long_sequences(causal: bool) -> None:
+    """Many key/value tiles per query tile: exercises the ring phases of the tcgen05 forward kernel."""
+    torch.manual_seed(12)
+    H, Hkv, D = 4, 2, 128
+    lens = [1500, 700, 129, 1]
+    T = sum(lens)
+    q = torch.randn((T, H, D), device=DEV, dtype=torch.bfloat16)
+    k = torch.randn((T, Hkv, D), device=DEV, dtype=torch.bfloat16)
+    v = torch.randn((T, Hkv, D), device=DEV, dtype=torch.bfloat16)
+    b, l = _seqs(lens)
+    out = varlen_attention(q, k, v, b, l, b, l, max(lens), max(lens), causal=causal)
+    ref = attention_reference(q.float(), k.float(), v.float(), b, l, b, l, causal)
+    assert _rel_err(out, ref) < 1e-2
+    from fairseq2_b200.ops._ext import require_ext
+
+    assert require_ext().read_status() == 0
+
+
 def test_attention_cross_lengths() -> None:
     """Lk > Lq (prefill against a cache): bottom-right aligned causal mask."""
     torch.manual_seed(9)
