@@ -1,6 +1,8 @@
 """Registers the built-in model families."""
 from __future__ import annotations
 
+from torch.nn import Module
+
 from fairseq2_b200.models.family import ModelFamily, register_model_family
 from fairseq2_b200.models.llama.config import LLAMA_FAMILY, LLaMAConfig
 from fairseq2_b200.models.llama.factory import create_llama_model
@@ -90,3 +92,40 @@ def _register_speech_families() -> None:
 
 
 _register_speech_families()
+
+
+def _register_vision_families() -> None:
+    from fairseq2_b200.models.jepa import (JEPA_CLASSIFIER_FAMILY, JEPA_FAMILY, JepaClassifierConfig,
+                                           JepaClassifierModel, JepaConfig, JepaModel, convert_jepa_state_dict,
+                                           create_jepa_classifier_model, create_jepa_model)
+
+    register_model_family(ModelFamily(
+        name=JEPA_FAMILY, kls=JepaModel, config_kls=JepaConfig, factory=create_jepa_model,
+        state_dict_converter=convert_jepa_state_dict, fsdp_wrap_policy=_encoder_wrap_policy, supports_meta=False))
+    register_model_family(ModelFamily(
+        name=JEPA_CLASSIFIER_FAMILY, kls=JepaClassifierModel, config_kls=JepaClassifierConfig,
+        factory=create_jepa_classifier_model, fsdp_wrap_policy=_encoder_wrap_policy, supports_meta=False))
+
+
+_register_vision_families()
+
+
+def _register_hg_family() -> None:
+    from fairseq2_b200.models.hg import HG_FAMILY, HuggingFaceModelConfig, create_hg_model
+
+    def hg_policy(module):  # type: ignore[no-untyped-def]
+        """FSDP units: the repeated decoder/encoder blocks of the wrapped model (largest ModuleList)."""
+        import torch
+
+        best = []
+        for m in module.modules():
+            if isinstance(m, torch.nn.ModuleList) and len(m) > len(best):
+                best = list(m)
+        return best
+
+    register_model_family(ModelFamily(
+        name=HG_FAMILY, kls=Module, config_kls=HuggingFaceModelConfig, factory=create_hg_model,
+        fsdp_wrap_policy=hg_policy, supports_meta=False))
+
+
+_register_hg_family()

@@ -101,3 +101,45 @@ def test_wav2vec2_ssl_asr_and_w2vbert() -> None:
     loss, out = wb(fb, fl)
     loss.aggregate.backward()
     assert out.bert_logits.shape[1:] == (16, 1) and out.bert_targets.shape[0] == out.bert_logits.shape[0]
+
+
+def test_jepa_and_classifier() -> None:
+    torch.manual_seed(0)
+    g = _gangs()
+    fam = get_model_family("jepa")
+    model = fam.create_new_model(fam.get_arch_config("test"), g)
+    x, xl = torch.randn(2, 3, 32, 32), BatchLayout((2, 3), [3, 3])
+    y, yl = model(x, xl)
+    assert y.shape == (2, 16, 64) and yl.seq_lens == [16, 16]
+    fam = get_model_family("jepa_classifier")
+    clf = fam.create_new_model(fam.get_arch_config("test"), g)
+    out = clf(x, xl)
+    out.sum().backward()
+    assert out.shape == (2, 10)
+
+
+def test_jepa_checkpoint_conversion_splits_fused_qkv() -> None:
+    from fairseq2_b200.models.jepa import JepaConfig, convert_jepa_state_dict
+
+    sd = {"encoder": {"module.backbone.blocks.0.attn.qkv.weight": torch.randn(192, 64),
+                      "module.backbone.blocks.0.attn.proj.bias": torch.randn(64),
+                      "module.backbone.pos_embed": torch.randn(1, 16, 64),
+                      "module.backbone.patch_embed.proj.weight": torch.randn(64, 3, 8, 8)}}
+    out = convert_jepa_state_dict(sd, JepaConfig())
+    assert set(out) == {"encoder.layers.0.self_attn.q_proj.weight", "encoder.layers.0.self_attn.k_proj.weight",
+                        "encoder.layers.0.self_attn.v_proj.weight", "encoder.layers.0.self_attn.output_proj.bias",
+                        "encoder_frontend.patch_feature_extractor.conv.weight"}
+
+
+def test_hg_adapter_wraps_causal_lm() -> None:
+    transformers = pytest.importorskip("transformers")
+    from fairseq2_b200.models.hg import HgCausalLMAdapter, HuggingFaceModelConfig, create_hg_model
+
+    hc = transformers.GPT2Config(n_layer=2, n_head=2, n_embd=64, vocab_size=300, n_positions=128)
+    model = create_hg_model(HuggingFaceModelConfig(hf_name="unused", model_type="causal_lm", random_init=True),
+                            hf_config=hc)
+    assert isinstance(model, HgCausalLMAdapter) and model.max_seq_len == 128
+    x, layout = torch.randint(0, 300, (2, 10)), BatchLayout((2, 10), [10, 6])
+    loss = model(x, layout, targets=x.roll(-1, 1))
+    loss.backward()
+    assert model(x, layout).shape == (2, 10, 300) and hasattr(model, "generate")
