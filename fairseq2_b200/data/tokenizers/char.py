@@ -32,7 +32,7 @@ class _Enc(TokenEncoder):
 
 class _Dec(TokenDecoder):
     def __call__(self, token_indices: Tensor) -> str:
-        bs = bytes(int(i) - _OFFSET for i in token_indices.tolist() if int(i) >= _OFFSET)
+        bs = bytes(int(i) - _OFFSET for i in token_indices.tolist() if _OFFSET <= int(i) < _OFFSET + 256)
         return bs.decode("utf-8", errors="replace")
 
     def decode_from_tokens(self, tokens: Sequence[str]) -> str:

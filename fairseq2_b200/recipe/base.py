@@ -382,6 +382,65 @@ class RecipeContext:
         return TorchProfiler(ps.skip_n_steps, ps.wait_n_steps, ps.num_warmup_steps, ps.num_active_steps, ps.repeat,
                              self.output_dir / "tb", self.gangs.root.rank)
 
+    # -------------------------------------------------------------- generation
+    def create_seq_generator(self, model: RecipeModel | Module, tokenizer: Any,
+                             section_name: str = "seq_generator") -> Any:
+        """Builds the sampling or beam-search generator described by ``config.<section_name>``."""
+        from fairseq2_b200.generation import (BeamSearchSequenceGenerator, SamplingSequenceGenerator,
+                                              StandardBeamSearchAlgorithm, TopKSampler, TopPSampler)
+        from fairseq2_b200.recipe.config import BeamSearchConfig, SamplingConfig, SequenceGeneratorSection
+        from fairseq2_b200.utils.structured import structure
+
+        section = getattr(self.config, section_name, None) or SequenceGeneratorSection()
+        module = model.module if isinstance(model, RecipeModel) else model
+        vi = tokenizer.vocab_info
+        if vi.eos_idx is None:
+            raise ValueError("The tokenizer must define an end-of-sequence symbol for generation.")
+        if section.name == "sampling":
+            sc: SamplingConfig = structure(dict(section.config), SamplingConfig)
+            if sc.sampler.name == "top-p":
+                sampler: Any = TopPSampler(float(sc.sampler.config.get("p", 0.9)))
+            elif sc.sampler.name == "top-k":
+                sampler = TopKSampler(int(sc.sampler.config.get("k", 1)))
+            else:
+                raise ValueError(f"'{sc.sampler.name}' is not a known sampler (top-p, top-k).")
+            return SamplingSequenceGenerator(
+                module, vi.eos_idx, vi.pad_idx, sampler, num_gens=sc.num_gens, min_gen_len=sc.min_gen_len,
+                max_gen_len=sc.max_gen_len, max_seq_len=sc.max_seq_len, echo_prompt=sc.echo_prompt,
+                compute_scores=sc.compute_scores, normalize_scores=sc.normalize_scores, temperature=sc.temperature,
+                unk_penalty=sc.unk_penalty, len_penalty=sc.len_penalty, prefill_chunk_size=sc.prefill_chunk_size,
+                decode_capacity_increment=sc.decode_capacity_increment, unk_idx=vi.unk_idx)
+        if section.name == "beam_search":
+            bc: BeamSearchConfig = structure(dict(section.config), BeamSearchConfig)
+            if bc.algorithm != "standard":
+                raise ValueError(f"'{bc.algorithm}' is not a known beam search algorithm (standard).")
+            return BeamSearchSequenceGenerator(
+                module, vi.eos_idx, vi.pad_idx, StandardBeamSearchAlgorithm(), beam_size=bc.beam_size,
+                min_gen_len=bc.min_gen_len, max_gen_len=bc.max_gen_len, max_seq_len=bc.max_seq_len,
+                echo_prompt=bc.echo_prompt, normalize_scores=bc.normalize_scores, temperature=bc.temperature,
+                unk_penalty=bc.unk_penalty, len_penalty=bc.len_penalty, prefill_chunk_size=bc.prefill_chunk_size,
+                decode_capacity_increment=bc.decode_capacity_increment, unk_idx=vi.unk_idx)
+        raise ValueError(f"'{section.name}' is not a known sequence generator (sampling, beam_search).")
+
+    def _eval_kwargs(self, section_name: str) -> dict[str, Any]:
+        from fairseq2_b200.recipe.config import MixedPrecisionSection
+
+        section = getattr(self.config, section_name, None)
+        mp = section.mixed_precision if section is not None else MixedPrecisionSection(mode="off")
+        return {"amp": mp.mode == "auto" and self.device.type == "cuda", "amp_dtype": mp.dtype,
+                "metric_recorder": self.create_metric_recorder(),
+                "device_stat_tracker": create_device_stat_tracker(self.device), "seed": self.common.seed}
+
+    def create_evaluator(self, units: Any, data_readers: Any) -> Task:
+        from fairseq2_b200.evaluator import Evaluator
+
+        return Evaluator(list(units), list(data_readers), self.gangs, **self._eval_kwargs("evaluator"))
+
+    def create_generator(self, unit: Any, data_reader: Any) -> Task:
+        from fairseq2_b200.evaluator import Generator
+
+        return Generator(unit, data_reader, self.gangs, **self._eval_kwargs("generator"))
+
     # ----------------------------------------------------------------- trainer
     def create_trainer(self, unit: TrainUnit[Any], data_reader: Any, validator: Validator | None = None, *,
                        optimizer: Optimizer | None = None, hg_exporter: Any | None = None) -> Trainer:

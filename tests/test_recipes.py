@@ -66,3 +66,43 @@ def test_bad_config_exit_code() -> None:
     from recipes.lm.sft.recipe import LMSFTRecipe
 
     assert main(LMSFTRecipe(), ["--dump-config", "--config", "regime.num_stepz=7"]) != 0
+
+
+def test_lm_train_recipe(tmp_path: Path) -> None:
+    from recipes.lm.train.recipe import LMTrainRecipe
+
+    d = tmp_path / "corpus"
+    d.mkdir()
+    with open(d / "shard0.jsonl", "w") as fp:
+        for i in range(200):
+            fp.write(json.dumps({"text": f"document {i}: " + "the quick brown fox jumps over the lazy dog. " * (1 + i % 5)}) + "\n")
+    args = [str(tmp_path / "out"), "--no-sweep-dir", "--no-exit-on-error", "--config", "model.arch=tiny",
+            "tokenizer.name=char_tokenizer", f"dataset.config_overrides={{sources: [{{path: {d}}}]}}",
+            "dataset.max_seq_len=128", "dataset.max_num_tokens=512", "trainer.mixed_precision.mode=off",
+            "optimizer.config.lr=1e-3", "lr_scheduler.config.num_warmup_steps=1", "regime.num_steps=4",
+            "regime.checkpoint_every_n_steps=4", "regime.publish_metrics_every_n_steps=1",
+            "common.metric_recorders.jsonl=true"]
+    assert main(LMTrainRecipe(), args) == 0
+    lines = [json.loads(l) for l in open(tmp_path / "out" / "metrics" / "train.jsonl")]
+    assert len(lines) == 4 and lines[-1]["NLL Loss"] < lines[0]["NLL Loss"]
+    assert all(l["Number of Elements"] == 512 for l in lines)       # packed buffers are always full
+
+
+def test_lm_generate_recipe(tmp_path: Path) -> None:
+    from recipes.lm.generate.recipe import LMGenerateRecipe
+
+    prompts = tmp_path / "prompts.jsonl"
+    with open(prompts, "w") as fp:
+        for i in range(5):
+            fp.write(json.dumps({"id": f"p{i}", "prompt": f"Question {i}?"}) + "\n")
+    for gen in ("sampling", "beam_search"):
+        out = tmp_path / gen
+        args = [str(out), "--no-sweep-dir", "--no-exit-on-error", "--config", "model.name=null", "model.family=llama",
+                "model.arch=tiny", "model.dtype=float32", "tokenizer.name=char_tokenizer",
+                f"dataset.config_overrides={{path: {prompts}}}", "dataset.batch_size=2",
+                f"seq_generator.name={gen}", "seq_generator.config={max_gen_len: 8}"]
+        assert main(LMGenerateRecipe(), args) == 0
+        rows = [json.loads(l) for l in open(out / "output" / "rank_0.jsonl")]
+        assert [r["id"] for r in rows] == [f"p{i}" for i in range(5)]
+        assert all(1 <= len(r["token_indices"]) <= 8 + 20 for r in rows)
+        assert "<<<<< RESPONSE >>>>>" in (out / "output" / "rank_0.txt").read_text()
