@@ -646,6 +646,17 @@ const char* attn_forward(const AttnParams& p, cudaStream_t st) {
     return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
 
+const char* attn_delta(const AttnParams& p, cudaStream_t st) {
+    if (p.num_seqs == 0 || p.total_q == 0) return nullptr;
+    const size_t warps = static_cast<size_t>(p.total_q) * p.H;
+    const int dgrid = static_cast<int>((warps * 32 + 255) / 256);
+    if (p.D == 128) attn_delta_kernel<128><<<dgrid, 256, 0, st>>>(p);
+    else if (p.D == 64) attn_delta_kernel<64><<<dgrid, 256, 0, st>>>(p);
+    else return "attention: head_dim must be 64 or 128";
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+}
+
 const char* attn_backward(const AttnParams& p, cudaStream_t st) {
     if (p.num_seqs == 0 || p.total_q == 0) return nullptr;
     cudaError_t e;

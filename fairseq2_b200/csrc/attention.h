@@ -37,5 +37,9 @@ const char* attn_backward(const AttnParams& p, cudaStream_t st);
 
 // tcgen05/TMEM path (head_dim 128); `status` is the host-mapped status word for bounded waits.
 const char* attn_forward_tc(const AttnParams& p, int* status, cudaStream_t st);
+const char* attn_backward_tc(const AttnParams& p, int* status, cudaStream_t st);
+
+// delta[h, t] = sum_d dO[t, h, d] * O[t, h, d] (first step of both backward paths)
+const char* attn_delta(const AttnParams& p, cudaStream_t st);
 
 }  // namespace fs2

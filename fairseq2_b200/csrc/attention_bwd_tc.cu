@@ -1,0 +1,576 @@
+// Flash-attention backward on the 5th-generation tensor cores (sm_100a), head_dim 128.
+//
+// Two deterministic kernels (no atomics), both built like the forward kernel: TMA -> 128B-swizzled
+// shared memory -> tcgen05.mma with accumulators in TMEM -> tcgen05.ld; 192 threads = TMA producer
+// warp, MMA issuer warp, four compute warps whose thread t owns TMEM lane t.
+//
+// dQ kernel: a CTA owns 128 query rows of one head. Q and dO stay resident; per 64-row K/V tile the
+//   issuer computes S = Q K^T and dP = dO V^T into a double-buffered TMEM pair, the compute warps
+//   turn them into dS = P * (dP - delta) (P = exp2(S * scale - lse)) as a bf16 A-operand tile in
+//   shared memory, and dQ += dS K accumulates in TMEM (K read as an MN-major B operand).
+//
+// dK/dV kernel: a CTA owns 128 key/value rows of one KV head. K and V stay resident; it walks the
+//   query heads of the group and their 64-row query tiles, computing S^T = K Q^T and dP^T = V dO^T,
+//   then P^T and dS^T as bf16 tiles, and dV += P^T dO, dK += dS^T Q accumulate in TMEM over the
+//   whole walk (Q and dO read as MN-major B operands).
+//
+// The softmax scale is applied once to the dQ / dK accumulators in the epilogue.
+// Every barrier wait is bounded; a wait that gives up records a code in the host-visible status
+// word, raises a CTA-wide abort flag and every role falls through to the teardown that frees TMEM.
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "attention.h"
+#include "attention_tc.cuh"
+#include "common.cuh"
+
+namespace fs2 {
+
+namespace {
+
+using namespace tc;
+
+constexpr int HD = 128;
+constexpr int BOX128 = 128 * 64 * 2;     // [128 rows][64 cols] bf16 box
+constexpr int BOX64 = 64 * 64 * 2;       // [64 rows][64 cols] bf16 box
+constexpr int BIG_TILE = 2 * BOX128;     // [128][128]
+constexpr int SMALL_TILE = 2 * BOX64;    // [64][128]
+constexpr int OPER_TILE = 128 * 64 * 2;  // thread-written [128][64] A operand
+constexpr int BWD_THREADS = 192;
+constexpr uint32_t BWD_TMEM_COLS = 512;
+
+// shared memory: two resident [128][128] tiles, two stages of two [64][128] tiles, operand tiles
+constexpr int OFF_RES0 = 0;
+constexpr int OFF_RES1 = OFF_RES0 + BIG_TILE;
+constexpr int OFF_STG = OFF_RES1 + BIG_TILE;              // stage s: [first small tile][second small tile]
+constexpr int OFF_OPER = OFF_STG + 2 * 2 * SMALL_TILE;    // dQ kernel: dS[2]; dK/dV kernel: {P^T, dS^T}[2]
+constexpr int OFF_VEC = OFF_OPER + 4 * OPER_TILE;         // lse/delta staging (dK/dV kernel): [4 warps][2 bufs][2][64] floats
+constexpr int OFF_BAR = OFF_VEC + 4 * 2 * 2 * 64 * 4;
+constexpr int BWD_SMEM_BYTES = OFF_BAR + 256 + 1024;
+static_assert(BWD_SMEM_BYTES <= 232448, "shared memory budget of one CTA exceeded");
+
+enum : int {
+    B_RES_FULL = 0,
+    B_STG_FULL = 1,    // [2]
+    B_STG_EMPTY = 3,   // [2]
+    B_ACC_FULL = 5,    // [2] score pair in TMEM ready
+    B_ACC_EMPTY = 7,   // [2] score pair consumed
+    B_OP_FULL = 9,     // [2] operand tile(s) written
+    B_OP_EMPTY = 11,   // [2] operand tile(s) consumed by the MMA
+    B_DONE = 13,
+    B_NUM = 14
+};
+
+struct Ctx {
+    uint32_t base;
+    uint32_t bar_base;
+    uint32_t tmem_base;
+    volatile int* abort_flag;
+    int* status;
+    __device__ __forceinline__ uint32_t bar(int slot) const { return bar_base + 8u * static_cast<uint32_t>(slot); }
+    __device__ __forceinline__ bool wait(int slot, uint32_t parity) const {
+        return mbar_wait_bounded(bar(slot), parity, abort_flag, WAIT_NS);
+    }
+    __device__ __forceinline__ void fail(int code) const {
+        if (!*abort_flag) report_status(status, kStatusTimeout | (code << 8));
+        *abort_flag = 1;
+    }
+};
+
+__device__ __forceinline__ void bwd_setup(Ctx& c, uint8_t* smem_raw, int* status, int op_full_count) {
+    const uint32_t raw = smem_u32(smem_raw);
+    c.base = (raw + 1023u) & ~1023u;
+    uint8_t* smem = smem_raw + (c.base - raw);
+    uint8_t* bar_ptr = smem + OFF_BAR;
+    c.bar_base = smem_u32(bar_ptr);
+    c.status = status;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_ptr + 8 * B_NUM);
+    c.abort_flag = reinterpret_cast<volatile int*>(bar_ptr + 8 * B_NUM + 8);
+    const int warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) {
+        mbar_init(c.bar(B_RES_FULL), 1);
+        mbar_init(c.bar(B_DONE), 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(c.bar(B_STG_FULL + s), 1);
+            mbar_init(c.bar(B_STG_EMPTY + s), 1);
+            mbar_init(c.bar(B_ACC_FULL + s), 1);
+            mbar_init(c.bar(B_ACC_EMPTY + s), 128);
+            mbar_init(c.bar(B_OP_FULL + s), op_full_count);
+            mbar_init(c.bar(B_OP_EMPTY + s), 1);
+        }
+        *c.abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), BWD_TMEM_COLS);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    c.tmem_base = *tmem_slot;
+}
+
+__device__ __forceinline__ void bwd_teardown(const Ctx& c) {
+    __syncthreads();
+    if (*c.abort_flag) {
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+        __syncthreads();
+    }
+    tcgen05_fence_after();
+    if ((threadIdx.x >> 5) == 1) tmem_dealloc(c.tmem_base, BWD_TMEM_COLS);
+}
+
+// D[128 x 64] = A[128 x 128 (K-major, two 64-col boxes of 128 rows)] * B[64 x 128 (K-major, two boxes of 64 rows)]^T
+__device__ __forceinline__ void mma_scores(uint32_t d_tmem, uint32_t a_s, uint32_t b_s, uint32_t idesc) {
+#pragma unroll
+    for (int k = 0; k < HD / 16; ++k) {
+        const uint64_t da = make_smem_desc(a_s + (k >> 2) * BOX128 + (k & 3) * 32, 16, 1024);
+        const uint64_t db = make_smem_desc(b_s + (k >> 2) * BOX64 + (k & 3) * 32, 16, 1024);
+        umma_bf16(d_tmem, da, db, idesc, k > 0 ? 1u : 0u);
+    }
+}
+
+// D[128 x 128] (+)= A[128 x 64 (K-major operand tile)] * B[64 x 128 (row-major [64][128] tile read MN-major)]
+__device__ __forceinline__ void mma_accum(uint32_t d_tmem, uint32_t a_s, uint32_t b_s, uint32_t idesc, bool first) {
+#pragma unroll
+    for (int k = 0; k < 64 / 16; ++k) {
+        const uint64_t da = make_smem_desc(a_s + k * 32, 16, 1024);
+        const uint64_t db = make_smem_desc(b_s + k * 16 * 128, BOX64, 1024);
+        umma_bf16(d_tmem, da, db, idesc, (first && k == 0) ? 0u : 1u);
+    }
+}
+
+// Epilogue: TMEM accumulator [128 lanes][128 cols] * mul -> bf16 row in global memory.
+__device__ __forceinline__ void store_acc_row(uint32_t t_lane_col, float mul, __nv_bfloat16* dst, bool valid) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_lane_col + c * 32, v);
+        tmem_ld_wait();
+        if (valid) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                uint4 w;
+                w.x = pack2_bf16(__uint_as_float(v[8 * g]) * mul, __uint_as_float(v[8 * g + 1]) * mul);
+                w.y = pack2_bf16(__uint_as_float(v[8 * g + 2]) * mul, __uint_as_float(v[8 * g + 3]) * mul);
+                w.z = pack2_bf16(__uint_as_float(v[8 * g + 4]) * mul, __uint_as_float(v[8 * g + 5]) * mul);
+                w.w = pack2_bf16(__uint_as_float(v[8 * g + 6]) * mul, __uint_as_float(v[8 * g + 7]) * mul);
+                *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = w;
+            }
+        }
+    }
+}
+
+// ============================================================================ dQ kernel
+// grid (q tiles of 128, seqs, H)
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_do,
+                      const __grid_constant__ CUtensorMap tma_k, const __grid_constant__ CUtensorMap tma_v,
+                      const AttnParams p, int* status) {
+    const int seq = blockIdx.y, h = blockIdx.z;
+    const int q_len = p.q_lens[seq], k_len = p.k_lens[seq];
+    const int qblk = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
+    const int q0 = qblk * 128;
+    if (q0 >= q_len) return;
+    const int q_begin = p.q_begins[seq], k_begin = p.k_begins[seq];
+    const int shift = k_len - q_len;
+    const int q_last = min(q0 + 128, q_len) - 1;
+    const int kv_hi = p.causal ? min(k_len, q_last + shift + 1) : k_len;
+    const int n_iter = kv_hi > 0 ? (kv_hi + 63) / 64 : 0;
+    const int kvh = h / (p.H / p.Hkv);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (n_iter == 0) {
+        // no visible key: the gradient of these query rows is zero
+        if (warp >= 2) {
+            const int row = (warp & 3) * 32 + lane;
+            if (q0 + row < q_len) {
+                __nv_bfloat16* dst = p.dq + static_cast<size_t>(q_begin + q0 + row) * p.dq_tstride + static_cast<size_t>(h) * HD;
+                for (int c = 0; c < HD / 8; ++c) *reinterpret_cast<uint4*>(dst + 8 * c) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        return;
+    }
+
+    extern __shared__ uint8_t smem_raw[];
+    Ctx c;
+    bwd_setup(c, smem_raw, status, 128);
+    if (threadIdx.x == 0) {
+        prefetch_tmap(&tma_q);
+        prefetch_tmap(&tma_do);
+        prefetch_tmap(&tma_k);
+        prefetch_tmap(&tma_v);
+    }
+    const uint32_t q_s = c.base + OFF_RES0, do_s = c.base + OFF_RES1;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const uint32_t rb = c.bar(B_RES_FULL);
+            mbar_arrive_expect_tx(rb, 2 * BIG_TILE);
+            tma_load_2d(q_s, &tma_q, rb, h * HD, q_begin + q0);
+            tma_load_2d(q_s + BOX128, &tma_q, rb, h * HD + 64, q_begin + q0);
+            tma_load_2d(do_s, &tma_do, rb, h * HD, q_begin + q0);
+            tma_load_2d(do_s + BOX128, &tma_do, rb, h * HD + 64, q_begin + q0);
+            for (int i = 0; i < n_iter; ++i) {
+                const int st = i & 1;
+                const uint32_t ph = static_cast<uint32_t>(i >> 1) & 1u;
+                if (!c.wait(B_STG_EMPTY + st, ph ^ 1u)) {
+                    c.fail(0x41);
+                    break;
+                }
+                const uint32_t fb = c.bar(B_STG_FULL + st);
+                const uint32_t k_s = c.base + OFF_STG + st * 2 * SMALL_TILE, v_s = k_s + SMALL_TILE;
+                const int row = k_begin + i * 64;
+                mbar_arrive_expect_tx(fb, 2 * SMALL_TILE);
+                tma_load_2d(k_s, &tma_k, fb, kvh * HD, row);
+                tma_load_2d(k_s + BOX64, &tma_k, fb, kvh * HD + 64, row);
+                tma_load_2d(v_s, &tma_v, fb, kvh * HD, row);
+                tma_load_2d(v_s + BOX64, &tma_v, fb, kvh * HD + 64, row);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t id_s = make_idesc_bf16(128, 64, false);
+            const uint32_t id_acc = make_idesc_bf16(128, 128, true);
+            bool ok = c.wait(B_RES_FULL, 0u);
+            if (!ok) c.fail(0x42);
+            auto accumulate = [&](int j) -> bool {     // dQ += dS_j K_j
+                const int b = j & 1;
+                const uint32_t ph = static_cast<uint32_t>(j >> 1) & 1u;
+                if (!c.wait(B_OP_FULL + b, ph)) return false;
+                tcgen05_fence_after();
+                const uint32_t k_s = c.base + OFF_STG + b * 2 * SMALL_TILE;
+                mma_accum(c.tmem_base + 256u, c.base + OFF_OPER + b * OPER_TILE, k_s, id_acc, j == 0);
+                umma_commit(c.bar(B_OP_EMPTY + b));
+                umma_commit(c.bar(B_STG_EMPTY + b));
+                return true;
+            };
+            for (int i = 0; i < n_iter && ok; ++i) {
+                const int b = i & 1;
+                const uint32_t ph = static_cast<uint32_t>(i >> 1) & 1u;
+                ok = c.wait(B_STG_FULL + b, ph) && c.wait(B_ACC_EMPTY + b, ph ^ 1u);
+                if (!ok) {
+                    c.fail(0x43);
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t k_s = c.base + OFF_STG + b * 2 * SMALL_TILE, v_s = k_s + SMALL_TILE;
+                mma_scores(c.tmem_base + static_cast<uint32_t>(b * 128), q_s, k_s, id_s);        // S
+                mma_scores(c.tmem_base + static_cast<uint32_t>(b * 128 + 64), do_s, v_s, id_s);  // dP
+                umma_commit(c.bar(B_ACC_FULL + b));
+                if (i > 0 && !accumulate(i - 1)) {
+                    c.fail(0x44);
+                    ok = false;
+                }
+            }
+            if (ok && !accumulate(n_iter - 1)) {
+                c.fail(0x45);
+                ok = false;
+            }
+            if (ok) umma_commit(c.bar(B_DONE));
+        }
+    } else {
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;
+        const int q_row = q0 + row;
+        const bool row_ok = q_row < q_len;
+        const uint32_t t_lane = c.tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+        const float sl2 = p.scale * LOG2E;
+        const size_t stat_idx = static_cast<size_t>(h) * p.total_q + q_begin + q_row;
+        const float neg_lse2 = row_ok ? -p.lse[stat_idx] * LOG2E : -INFINITY;   // -inf -> probability 0
+        const float delta = row_ok ? p.delta[stat_idx] : 0.f;
+        const int lim = p.causal ? min(k_len - 1, q_row + shift) : k_len - 1;
+        bool ok = true;
+        for (int i = 0; i < n_iter; ++i) {
+            const int b = i & 1;
+            const uint32_t ph = static_cast<uint32_t>(i >> 1) & 1u;
+            const int kv0 = i * 64;
+            if (!warp_wait(c.bar(B_ACC_FULL + b), ph, c.abort_flag) ||
+                !warp_wait(c.bar(B_OP_EMPTY + b), ph ^ 1u, c.abort_flag)) {
+                ok = false;
+                break;
+            }
+            tcgen05_fence_after();
+            const int rel = lim - kv0;
+            const uint32_t t_s = t_lane + static_cast<uint32_t>(b * 128);
+            const uint32_t ds_tile = c.base + OFF_OPER + b * OPER_TILE;
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+                uint32_t s[32], dp[32];
+                tmem_ld_32x32(t_s + cc * 32, s);
+                tmem_ld_32x32(t_s + 64 + cc * 32, dp);
+                tmem_ld_wait();
+                float e[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const float pr = ex2_approx(fmaf(__uint_as_float(s[j]), sl2, neg_lse2));
+                    const float ds = pr * (__uint_as_float(dp[j]) - delta);
+                    e[j] = (cc * 32 + j <= rel) ? ds : 0.f;
+                }
+#pragma unroll
+                for (int g = 0; g < 4; ++g) st_swizzled_chunk(ds_tile, row, static_cast<uint32_t>(cc * 4 + g), e + 8 * g);
+            }
+            tcgen05_fence_before();
+            mbar_arrive(c.bar(B_ACC_EMPTY + b));
+            fence_proxy_async_smem();
+            mbar_arrive(c.bar(B_OP_FULL + b));
+        }
+        if (ok) ok = warp_wait(c.bar(B_DONE), 0u, c.abort_flag);
+        if (!ok) {
+            if (lane == 0) c.fail(0x46);
+        } else {
+            tcgen05_fence_after();
+            __nv_bfloat16* dst = p.dq + static_cast<size_t>(q_begin + q_row) * p.dq_tstride + static_cast<size_t>(h) * HD;
+            store_acc_row(t_lane + 256u, p.scale, dst, row_ok);
+        }
+    }
+    bwd_teardown(c);
+}
+
+// ========================================================================= dK/dV kernel
+// grid (kv tiles of 128, seqs, Hkv)
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_do,
+                       const __grid_constant__ CUtensorMap tma_k, const __grid_constant__ CUtensorMap tma_v,
+                       const AttnParams p, int* status) {
+    const int seq = blockIdx.y, kvh = blockIdx.z;
+    const int q_len = p.q_lens[seq], k_len = p.k_lens[seq];
+    const int kv0 = static_cast<int>(blockIdx.x) * 128;
+    if (kv0 >= k_len) return;
+    const int q_begin = p.q_begins[seq], k_begin = p.k_begins[seq];
+    const int shift = k_len - q_len;
+    const int G = p.H / p.Hkv;
+    // first query row that can see this tile (causal: q + shift >= kv0), rounded down to a 64-row tile
+    const int q_lo = p.causal ? max(0, kv0 - shift) : 0;
+    const int jt_lo = q_lo / 64;
+    const int jt_hi = (q_len + 63) / 64;
+    const int per_head = max(0, jt_hi - jt_lo);
+    const int n_iter = per_head * G;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (n_iter == 0) {
+        // no query sees these keys: zero gradients
+        if (warp >= 2) {
+            const int row = (warp & 3) * 32 + lane;
+            if (kv0 + row < k_len) {
+                const size_t t = static_cast<size_t>(k_begin + kv0 + row);
+                __nv_bfloat16* dk = p.dk + t * p.dk_tstride + static_cast<size_t>(kvh) * HD;
+                __nv_bfloat16* dv = p.dv + t * p.dv_tstride + static_cast<size_t>(kvh) * HD;
+                for (int c = 0; c < HD / 8; ++c) {
+                    *reinterpret_cast<uint4*>(dk + 8 * c) = make_uint4(0, 0, 0, 0);
+                    *reinterpret_cast<uint4*>(dv + 8 * c) = make_uint4(0, 0, 0, 0);
+                }
+            }
+        }
+        return;
+    }
+
+    extern __shared__ uint8_t smem_raw[];
+    Ctx c;
+    bwd_setup(c, smem_raw, status, 128);
+    if (threadIdx.x == 0) {
+        prefetch_tmap(&tma_q);
+        prefetch_tmap(&tma_do);
+        prefetch_tmap(&tma_k);
+        prefetch_tmap(&tma_v);
+    }
+    const uint32_t k_s = c.base + OFF_RES0, v_s = c.base + OFF_RES1;
+    float* vec = reinterpret_cast<float*>(smem_raw + (c.base - smem_u32(smem_raw)) + OFF_VEC);
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const uint32_t rb = c.bar(B_RES_FULL);
+            mbar_arrive_expect_tx(rb, 2 * BIG_TILE);
+            tma_load_2d(k_s, &tma_k, rb, kvh * HD, k_begin + kv0);
+            tma_load_2d(k_s + BOX128, &tma_k, rb, kvh * HD + 64, k_begin + kv0);
+            tma_load_2d(v_s, &tma_v, rb, kvh * HD, k_begin + kv0);
+            tma_load_2d(v_s + BOX128, &tma_v, rb, kvh * HD + 64, k_begin + kv0);
+            for (int i = 0; i < n_iter; ++i) {
+                const int st = i & 1;
+                const uint32_t ph = static_cast<uint32_t>(i >> 1) & 1u;
+                const int h = kvh * G + i / per_head;
+                const int row = q_begin + (jt_lo + i % per_head) * 64;
+                if (!c.wait(B_STG_EMPTY + st, ph ^ 1u)) {
+                    c.fail(0x51);
+                    break;
+                }
+                const uint32_t fb = c.bar(B_STG_FULL + st);
+                const uint32_t q_s = c.base + OFF_STG + st * 2 * SMALL_TILE, do_s = q_s + SMALL_TILE;
+                mbar_arrive_expect_tx(fb, 2 * SMALL_TILE);
+                tma_load_2d(q_s, &tma_q, fb, h * HD, row);
+                tma_load_2d(q_s + BOX64, &tma_q, fb, h * HD + 64, row);
+                tma_load_2d(do_s, &tma_do, fb, h * HD, row);
+                tma_load_2d(do_s + BOX64, &tma_do, fb, h * HD + 64, row);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t id_s = make_idesc_bf16(128, 64, false);
+            const uint32_t id_acc = make_idesc_bf16(128, 128, true);
+            bool ok = c.wait(B_RES_FULL, 0u);
+            if (!ok) c.fail(0x52);
+            auto accumulate = [&](int j) -> bool {     // dV += P^T dO_j ; dK += dS^T Q_j
+                const int b = j & 1;
+                const uint32_t ph = static_cast<uint32_t>(j >> 1) & 1u;
+                if (!c.wait(B_OP_FULL + b, ph)) return false;
+                tcgen05_fence_after();
+                const uint32_t q_s = c.base + OFF_STG + b * 2 * SMALL_TILE, do_s = q_s + SMALL_TILE;
+                const uint32_t pt_s = c.base + OFF_OPER + b * 2 * OPER_TILE, dst_s = pt_s + OPER_TILE;
+                mma_accum(c.tmem_base + 256u, pt_s, do_s, id_acc, j == 0);
+                mma_accum(c.tmem_base + 384u, dst_s, q_s, id_acc, j == 0);
+                umma_commit(c.bar(B_OP_EMPTY + b));
+                umma_commit(c.bar(B_STG_EMPTY + b));
+                return true;
+            };
+            for (int i = 0; i < n_iter && ok; ++i) {
+                const int b = i & 1;
+                const uint32_t ph = static_cast<uint32_t>(i >> 1) & 1u;
+                ok = c.wait(B_STG_FULL + b, ph) && c.wait(B_ACC_EMPTY + b, ph ^ 1u);
+                if (!ok) {
+                    c.fail(0x53);
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t q_s = c.base + OFF_STG + b * 2 * SMALL_TILE, do_s = q_s + SMALL_TILE;
+                mma_scores(c.tmem_base + static_cast<uint32_t>(b * 128), k_s, q_s, id_s);         // S^T
+                mma_scores(c.tmem_base + static_cast<uint32_t>(b * 128 + 64), v_s, do_s, id_s);   // dP^T
+                umma_commit(c.bar(B_ACC_FULL + b));
+                if (i > 0 && !accumulate(i - 1)) {
+                    c.fail(0x54);
+                    ok = false;
+                }
+            }
+            if (ok && !accumulate(n_iter - 1)) {
+                c.fail(0x55);
+                ok = false;
+            }
+            if (ok) umma_commit(c.bar(B_DONE));
+        }
+    } else {
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;          // key/value row inside the tile
+        const int kv_row = kv0 + row;
+        const bool row_ok = kv_row < k_len;
+        const uint32_t t_lane = c.tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+        const float sl2 = p.scale * LOG2E;
+        bool ok = true;
+        for (int i = 0; i < n_iter; ++i) {
+            const int b = i & 1;
+            const uint32_t ph = static_cast<uint32_t>(i >> 1) & 1u;
+            const int h = kvh * G + i / per_head;
+            const int qt0 = (jt_lo + i % per_head) * 64;
+            // Every warp stages its own copy of -lse * log2(e) and delta of the 64 query rows of this tile, so
+            // that only a warp-level sync is needed (a CTA-wide named barrier could block after an abort).
+            float* nl = vec + ((quad * 2 + b) * 2) * 64;
+            float* dl = nl + 64;
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const int j = lane + 32 * r;
+                const int q = qt0 + j;
+                const size_t idx = static_cast<size_t>(h) * p.total_q + q_begin + q;
+                nl[j] = (q < q_len) ? -p.lse[idx] * LOG2E : -INFINITY;   // -inf -> probability 0
+                dl[j] = (q < q_len) ? p.delta[idx] : 0.f;
+            }
+            __syncwarp();
+            if (!warp_wait(c.bar(B_ACC_FULL + b), ph, c.abort_flag) ||
+                !warp_wait(c.bar(B_OP_EMPTY + b), ph ^ 1u, c.abort_flag)) {
+                ok = false;
+                break;
+            }
+            tcgen05_fence_after();
+            // query column j (row qt0 + j) sees key kv_row iff kv_row <= qt0 + j + shift
+            const int jmin = p.causal ? kv_row - shift - qt0 : 0;     // columns below jmin are masked
+            const uint32_t t_s = t_lane + static_cast<uint32_t>(b * 128);
+            const uint32_t pt_tile = c.base + OFF_OPER + b * 2 * OPER_TILE, dst_tile = pt_tile + OPER_TILE;
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+                uint32_t s[32], dp[32];
+                tmem_ld_32x32(t_s + cc * 32, s);
+                tmem_ld_32x32(t_s + 64 + cc * 32, dp);
+                tmem_ld_wait();
+                float pe[32], de[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int col = cc * 32 + j;
+                    float pr = ex2_approx(fmaf(__uint_as_float(s[j]), sl2, nl[col]));
+                    float ds = pr * (__uint_as_float(dp[j]) - dl[col]);
+                    const bool live = row_ok && col >= jmin;
+                    pe[j] = live ? pr : 0.f;
+                    de[j] = live ? ds : 0.f;
+                }
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    st_swizzled_chunk(pt_tile, row, static_cast<uint32_t>(cc * 4 + g), pe + 8 * g);
+                    st_swizzled_chunk(dst_tile, row, static_cast<uint32_t>(cc * 4 + g), de + 8 * g);
+                }
+            }
+            tcgen05_fence_before();
+            mbar_arrive(c.bar(B_ACC_EMPTY + b));
+            fence_proxy_async_smem();
+            mbar_arrive(c.bar(B_OP_FULL + b));
+        }
+        if (ok) ok = warp_wait(c.bar(B_DONE), 0u, c.abort_flag);
+        if (!ok) {
+            if (lane == 0) c.fail(0x56);
+        } else {
+            tcgen05_fence_after();
+            const size_t t = static_cast<size_t>(k_begin + kv_row);
+            store_acc_row(t_lane + 256u, 1.0f, p.dv + t * p.dv_tstride + static_cast<size_t>(kvh) * HD, row_ok);
+            store_acc_row(t_lane + 384u, p.scale, p.dk + t * p.dk_tstride + static_cast<size_t>(kvh) * HD, row_ok);
+        }
+    }
+    bwd_teardown(c);
+}
+
+}  // namespace
+
+// delta = rowsum(dO * O); defined with the mma.sync kernels
+const char* attn_delta(const AttnParams& p, cudaStream_t st);
+
+const char* attn_backward_tc(const AttnParams& p, int* status, cudaStream_t st) {
+    if (p.num_seqs == 0 || p.total_q == 0) return nullptr;
+    if (p.D != HD) return "attn_backward_tc: head_dim must be 128";
+    const size_t strides[] = {p.q_tstride, p.k_tstride, p.v_tstride, p.do_tstride, p.dq_tstride, p.dk_tstride, p.dv_tstride};
+    for (size_t s : strides)
+        if (s % 8) return "attn_backward_tc: row pitches must be multiples of 16 bytes";
+    const void* ptrs[] = {p.q, p.k, p.v, p.dout, p.dq, p.dk, p.dv};
+    for (const void* ptr : ptrs)
+        if (reinterpret_cast<uintptr_t>(ptr) % 16) return "attn_backward_tc: operands must be 16-byte aligned";
+    const char* err = attn_delta(p, st);
+    if (err != nullptr) return err;
+    const uint64_t qcols = static_cast<uint64_t>(p.H) * HD, kcols = static_cast<uint64_t>(p.Hkv) * HD;
+    CUtensorMap q128, do128, k64, v64, q64, do64, k128, v128;
+    if (!make_view_tmap(&q128, p.q, p.total_q, qcols, p.q_tstride, 128) ||
+        !make_view_tmap(&do128, p.dout, p.total_q, qcols, p.do_tstride, 128) ||
+        !make_view_tmap(&k64, p.k, p.total_k, kcols, p.k_tstride, 64) ||
+        !make_view_tmap(&v64, p.v, p.total_k, kcols, p.v_tstride, 64) ||
+        !make_view_tmap(&q64, p.q, p.total_q, qcols, p.q_tstride, 64) ||
+        !make_view_tmap(&do64, p.dout, p.total_q, qcols, p.do_tstride, 64) ||
+        !make_view_tmap(&k128, p.k, p.total_k, kcols, p.k_tstride, 128) ||
+        !make_view_tmap(&v128, p.v, p.total_k, kcols, p.v_tstride, 128))
+        return tmap_error();
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_bwd_dq_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             BWD_SMEM_BYTES);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(attn_bwd_dkv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     BWD_SMEM_BYTES);
+        if (e != cudaSuccess) return cudaGetErrorString(e);
+        configured = true;
+    }
+    const dim3 grid_kv((p.max_k + 127) / 128, p.num_seqs, p.Hkv);
+    const dim3 grid_q((p.max_q + 127) / 128, p.num_seqs, p.H);
+    attn_bwd_dkv_tc_kernel<<<grid_kv, BWD_THREADS, BWD_SMEM_BYTES, st>>>(q64, do64, k128, v128, p, status);
+    attn_bwd_dq_tc_kernel<<<grid_q, BWD_THREADS, BWD_SMEM_BYTES, st>>>(q128, do128, k64, v64, p, status);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+}
+
+}  // namespace fs2

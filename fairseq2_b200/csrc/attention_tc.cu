@@ -32,11 +32,14 @@
 #include <cstdio>
 
 #include "attention.h"
+#include "attention_tc.cuh"
 #include "common.cuh"
 
 namespace fs2 {
 
 namespace {
+
+using namespace tc;
 
 constexpr int TQ = 128;                      // query rows per CTA
 constexpr int TK = 128;                      // key/value rows per iteration
@@ -73,34 +76,6 @@ enum : int {
     NUM_BARS = 19
 };
 
-__device__ __forceinline__ uint32_t idesc_128x128(bool b_mn) {
-    uint32_t d = 0;
-    d |= 1u << 4;                                  // D: f32
-    d |= 1u << 7;                                  // A: bf16
-    d |= 1u << 10;                                 // B: bf16
-    d |= (b_mn ? 1u : 0u) << 16;                   // B major: 0 = K, 1 = MN
-    d |= static_cast<uint32_t>(128 >> 3) << 17;    // N
-    d |= static_cast<uint32_t>(128 >> 4) << 24;    // M
-    return d;
-}
-
-__device__ __forceinline__ float ex2_approx(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-
-__device__ __forceinline__ uint32_t pack2_bf16(float a, float b) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&h);
-}
-
-// Warp-uniform bounded wait for the softmax warps: every lane must take the same branch
-// because the TMEM loads that follow are warp-collective.
-__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    const bool got = mbar_wait_bounded(bar, parity, abort_flag, WAIT_LIMIT_NS);
-    return __all_sync(0xffffffffu, got);
-}
 
 __global__ void __launch_bounds__(TC_THREADS, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
@@ -195,8 +170,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     } else if (warp == 1) {
         // -------------------------------------------------------------- MMA issuer
         if (lane == 0) {
-            const uint32_t idesc_s = idesc_128x128(false);
-            const uint32_t idesc_pv = idesc_128x128(true);
+            const uint32_t idesc_s = make_idesc_bf16(128, 128, false);
+            const uint32_t idesc_pv = make_idesc_bf16(128, 128, true);
             bool ok = mbar_wait_bounded(bar(BAR_Q_FULL), 0u, abort_flag, WAIT_LIMIT_NS);
             if (!ok) {
                 if (!*abort_flag) report_status(status, kStatusTimeout | (0x21 << 8));
@@ -394,52 +369,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
 
 }  // namespace
 
-// ------------------------------------------------------------------ host side
-namespace {
-
-using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeFn encode_fn() {
-    static EncodeFn fn = nullptr;
-    if (fn == nullptr) {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess)
-            return nullptr;
-        fn = reinterpret_cast<EncodeFn>(ptr);
-    }
-    return fn;
-}
-
-thread_local char g_err[256];
-
-// [rows, cols] bf16 view whose rows are `row_stride` elements apart; box = [128 rows][64 cols].
-bool make_view_tmap(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t cols, uint64_t row_stride) {
-    EncodeFn fn = encode_fn();
-    if (fn == nullptr) {
-        snprintf(g_err, sizeof(g_err), "cuTensorMapEncodeTiled entry point not found");
-        return false;
-    }
-    cuuint64_t dims[2] = {cols, rows};
-    cuuint64_t strides[1] = {row_stride * 2};
-    cuuint32_t box[2] = {64, 128};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        snprintf(g_err, sizeof(g_err), "cuTensorMapEncodeTiled failed with CUresult %d (rows %llu, cols %llu, stride %llu)",
-                 static_cast<int>(r), static_cast<unsigned long long>(rows), static_cast<unsigned long long>(cols),
-                 static_cast<unsigned long long>(row_stride));
-        return false;
-    }
-    return true;
-}
-
-}  // namespace
-
 const char* attn_forward_tc(const AttnParams& p, int* status, cudaStream_t st) {
     if (p.num_seqs == 0 || p.total_q == 0) return nullptr;
     if (p.D != HD) return "attn_forward_tc: head_dim must be 128";
@@ -448,11 +377,10 @@ const char* attn_forward_tc(const AttnParams& p, int* status, cudaStream_t st) {
         reinterpret_cast<uintptr_t>(p.v) % 16 || reinterpret_cast<uintptr_t>(p.o) % 16)
         return "attn_forward_tc: operands must be 16-byte aligned with 16-byte aligned row pitch";
     CUtensorMap tq, tk, tv;
-    g_err[0] = 0;
-    if (!make_view_tmap(&tq, p.q, p.total_q, static_cast<uint64_t>(p.H) * HD, p.q_tstride) ||
-        !make_view_tmap(&tk, p.k, p.total_k, static_cast<uint64_t>(p.Hkv) * HD, p.k_tstride) ||
-        !make_view_tmap(&tv, p.v, p.total_k, static_cast<uint64_t>(p.Hkv) * HD, p.v_tstride))
-        return g_err;
+    if (!make_view_tmap(&tq, p.q, p.total_q, static_cast<uint64_t>(p.H) * HD, p.q_tstride, 128) ||
+        !make_view_tmap(&tk, p.k, p.total_k, static_cast<uint64_t>(p.Hkv) * HD, p.k_tstride, 128) ||
+        !make_view_tmap(&tv, p.v, p.total_k, static_cast<uint64_t>(p.Hkv) * HD, p.v_tstride, 128))
+        return tmap_error();
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -402,7 +402,12 @@ void attn_bwd_out(const Tensor& dout, const Tensor& q, const Tensor& k, const Te
     p.dv_tstride = dv.stride(0);
     p.lse = lse.data_ptr<float>();
     p.delta = delta.data_ptr<float>();
-    const char* err = fs2::attn_backward(p, stream_of(q));
+    static const bool use_tc = []() {
+        const char* e = std::getenv("FAIRSEQ2_B200_ATTN");
+        return e == nullptr || (std::string(e) != "mma" && std::string(e) != "mma_bwd");
+    }();
+    const char* err = (use_tc && p.D == 128) ? fs2::attn_backward_tc(p, status_dev_ptr(), stream_of(q))
+                                             : fs2::attn_backward(p, stream_of(q));
     TORCH_CHECK(err == nullptr, "attn_bwd: ", err);
     g_launches += 3;
 }

@@ -393,7 +393,8 @@ class StandardMultiheadAttention(MultiheadAttention):
             freqs, pos = pe.freqs, layout.position_indices_i32.reshape(-1)
         out = qkv_rope_attention(flat, freqs, pos, layout.seq_begin_indices_pt[:-1], layout.seq_lens_pt,
                                  layout.max_seq_len, num_heads=H, num_kv_heads=Hkv,
-                                 causal=isinstance(bias, CausalAttentionBias))
+                                 causal=isinstance(bias, CausalAttentionBias),
+                                 has_padding=layout.padded or sum(layout.seq_lens) < flat.shape[0])
         out = out.flatten(-2, -1)
         if not layout.packed:
             out = out.view(*qkv.shape[:2], H * self.head_dim)

@@ -77,7 +77,7 @@ class _QKVRopeAttnFn(torch.autograd.Function):
     projection's dgrad/wgrad GEMMs consume it without a concat."""
 
     @staticmethod
-    def forward(ctx, qkv, freqs, positions, begins, lens, max_len, causal, scale, H, Hkv):  # type: ignore[override]
+    def forward(ctx, qkv, freqs, positions, begins, lens, max_len, causal, scale, H, Hkv, has_padding):  # type: ignore[override]
         ext = require_ext()
         if freqs is not None:
             # The producer of `qkv` (the merged projection) does not need its own
@@ -87,27 +87,29 @@ class _QKVRopeAttnFn(torch.autograd.Function):
         q, k, v = qkv[:, :H], qkv[:, H:H + Hkv], qkv[:, H + Hkv:]
         out, lse = ext.attn_fwd(q, k, v, begins, lens, begins, lens, max_len, max_len, causal, scale)
         ctx.save_for_backward(qkv, out, lse, begins, lens, freqs, positions)
-        ctx.meta = (max_len, causal, scale, H, Hkv)
+        ctx.meta = (max_len, causal, scale, H, Hkv, has_padding)
         return out
 
     @staticmethod
     def backward(ctx, dout):  # type: ignore[override]
         ext = require_ext()
         qkv, out, lse, begins, lens, freqs, positions = ctx.saved_tensors
-        max_len, causal, scale, H, Hkv = ctx.meta
+        max_len, causal, scale, H, Hkv, has_padding = ctx.meta
         q, k, v = qkv[:, :H], qkv[:, H:H + Hkv], qkv[:, H + Hkv:]
-        dqkv = torch.empty_like(qkv)
+        # rows outside every sequence are never written by the kernels: they must read as zero gradients
+        dqkv = torch.zeros_like(qkv) if has_padding else torch.empty_like(qkv)
         ext.attn_bwd_out(dout.contiguous(), q, k, v, out, lse, begins, lens, begins, lens, max_len, max_len, causal,
                          scale, dqkv[:, :H], dqkv[:, H:H + Hkv], dqkv[:, H + Hkv:])
         if freqs is not None:
             ext.rope_inplace(dqkv[:, : H + Hkv], freqs, positions, True)
-        return dqkv, None, None, None, None, None, None, None, None, None
+        return dqkv, None, None, None, None, None, None, None, None, None, None
 
 
 def qkv_rope_attention(qkv: Tensor, freqs: Tensor | None, positions: Tensor | None, begins: Tensor, lens: Tensor,
                        max_len: int, *, num_heads: int, num_kv_heads: int, causal: bool = True,
-                       scale: float | None = None) -> Tensor:
+                       scale: float | None = None, has_padding: bool = True) -> Tensor:
     """``qkv``: contiguous bf16 ``[T, H + 2·Hkv, D]`` (modified in place). Returns ``[T, H, D]``."""
     D = qkv.shape[-1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    return _QKVRopeAttnFn.apply(qkv, freqs, positions, begins, lens, max_len, causal, scale, num_heads, num_kv_heads)
+    return _QKVRopeAttnFn.apply(qkv, freqs, positions, begins, lens, max_len, causal, scale, num_heads, num_kv_heads,
+                                has_padding)
