@@ -451,6 +451,10 @@ class RecipeContext:
             raise ValueError("`bootstrap_model()` must be called before `create_trainer()`.")
         optimizer = optimizer or self.create_optimizer(model)
         sched = self.create_lr_scheduler(optimizer)
+        if hg_exporter is None and regime.export_hugging_face and model.family.hg_exporter is not None:
+            from fairseq2_b200.checkpoint.hg import OutOfProcHuggingFaceExporter
+
+            hg_exporter = OutOfProcHuggingFaceExporter(self.checkpoint_dir, self.gangs)
         gangs = self.gangs
         if ts.mixed_precision.mode != "off" and ts.mixed_precision.dtype == torch.float16:
             init, mn = ts.fp16_loss_scale

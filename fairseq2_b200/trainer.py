@@ -256,6 +256,8 @@ class Trainer(Task):
             self._recorder.close()
         if self._ckpt is not None:
             self._ckpt.close()
+        if self._hg_exporter is not None:
+            self._hg_exporter.complete_pending_export_operations(blocking=True)
         self._validator.close()
 
     def run(self) -> None:

@@ -106,3 +106,34 @@ def test_lm_generate_recipe(tmp_path: Path) -> None:
         assert [r["id"] for r in rows] == [f"p{i}" for i in range(5)]
         assert all(1 <= len(r["token_indices"]) <= 8 + 20 for r in rows)
         assert "<<<<< RESPONSE >>>>>" in (out / "output" / "rank_0.txt").read_text()
+
+
+def test_sft_recipe_exports_hugging_face_checkpoint(tmp_path: Path) -> None:
+    """The out-of-process exporter writes ``step_N/hg`` which loads into ``transformers`` with equal logits."""
+    transformers = pytest.importorskip("transformers")
+    from recipes.lm.sft.recipe import LMSFTRecipe
+
+    data = _write_sft_data(tmp_path, 16)
+    args = [a for a in _sft_args(tmp_path, data, ["regime.num_steps=2", "dataset.packed=true"])
+            if a != "regime.export_hugging_face=false"] + ["regime.export_hugging_face=true",
+                                                           "regime.save_model_only=false"]
+    assert main(LMSFTRecipe(), args) == 0
+    hg = tmp_path / "out" / "checkpoints" / "step_2" / "hg"
+    assert (hg / "config.json").exists() and (hg / "model.safetensors").exists(), \
+        (tmp_path / "out" / "checkpoints" / "step_2" / "hg.stderr").read_text()
+    hf = transformers.AutoModelForCausalLM.from_pretrained(hg, torch_dtype=torch.float32).eval()
+
+    from fairseq2_b200.gang import create_fake_gangs
+    from fairseq2_b200.models.family import get_model_family
+    from fairseq2_b200.nn.batch_layout import BatchLayout
+
+    fam = get_model_family("llama")
+    cfg = fam.get_arch_config("tiny")
+    g = create_fake_gangs(torch.device("cpu"))
+    ours = fam.create_new_model(cfg, g)
+    fam.load_into(ours, tmp_path / "out" / "checkpoints" / "step_2" / "model", cfg, g)
+    x = torch.randint(1, 300, (1, 12))
+    with torch.no_grad():
+        a = ours.eval()(x, BatchLayout((1, 12), [12]))
+        b = hf(x).logits
+    assert torch.allclose(a, b, atol=5e-2), float((a - b).abs().max())
