@@ -43,26 +43,36 @@ constexpr int OPER_TILE = 128 * 64 * 2;  // thread-written [128][64] A operand
 constexpr int BWD_THREADS = 192;
 constexpr uint32_t BWD_TMEM_COLS = 512;
 
-// shared memory: two resident [128][128] tiles, two stages of two [64][128] tiles, operand tiles
+// Shared memory: two resident [128][128] tiles, a ring of stages (each two [64][128] tiles), operand tiles.
+// A stage is released only after the accumulating MMA that reads it has completed, so the ring must be deep
+// enough for the TMA loads to run ahead of that point.
+constexpr int STAGE_BYTES = 2 * SMALL_TILE;
 constexpr int OFF_RES0 = 0;
 constexpr int OFF_RES1 = OFF_RES0 + BIG_TILE;
-constexpr int OFF_STG = OFF_RES1 + BIG_TILE;              // stage s: [first small tile][second small tile]
-constexpr int OFF_OPER = OFF_STG + 2 * 2 * SMALL_TILE;    // dQ kernel: dS[2]; dK/dV kernel: {P^T, dS^T}[2]
-constexpr int OFF_VEC = OFF_OPER + 4 * OPER_TILE;         // lse/delta staging (dK/dV kernel): [4 warps][2 bufs][2][64] floats
-constexpr int OFF_BAR = OFF_VEC + 4 * 2 * 2 * 64 * 4;
-constexpr int BWD_SMEM_BYTES = OFF_BAR + 256 + 1024;
-static_assert(BWD_SMEM_BYTES <= 232448, "shared memory budget of one CTA exceeded");
+constexpr int OFF_STG = OFF_RES1 + BIG_TILE;
+// dQ kernel: 4 stages, dS double-buffered
+constexpr int DQ_NSTG = 4, DQ_NOP = 2;
+constexpr int DQ_OFF_OPER = OFF_STG + DQ_NSTG * STAGE_BYTES;
+constexpr int DQ_OFF_BAR = DQ_OFF_OPER + DQ_NOP * OPER_TILE;
+constexpr int DQ_SMEM_BYTES = DQ_OFF_BAR + 256 + 1024;
+// dK/dV kernel: 3 stages, one {P^T, dS^T} pair, per-warp lse/delta staging [4 warps][2 bufs][2][64] floats
+constexpr int KV_NSTG = 3, KV_NOP = 1;
+constexpr int KV_OFF_OPER = OFF_STG + KV_NSTG * STAGE_BYTES;
+constexpr int KV_OFF_VEC = KV_OFF_OPER + KV_NOP * 2 * OPER_TILE;
+constexpr int KV_OFF_BAR = KV_OFF_VEC + 4 * 2 * 2 * 64 * 4;
+constexpr int KV_SMEM_BYTES = KV_OFF_BAR + 256 + 1024;
+static_assert(DQ_SMEM_BYTES <= 232448 && KV_SMEM_BYTES <= 232448, "shared memory budget of one CTA exceeded");
 
 enum : int {
     B_RES_FULL = 0,
-    B_STG_FULL = 1,    // [2]
-    B_STG_EMPTY = 3,   // [2]
-    B_ACC_FULL = 5,    // [2] score pair in TMEM ready
-    B_ACC_EMPTY = 7,   // [2] score pair consumed
-    B_OP_FULL = 9,     // [2] operand tile(s) written
-    B_OP_EMPTY = 11,   // [2] operand tile(s) consumed by the MMA
-    B_DONE = 13,
-    B_NUM = 14
+    B_STG_FULL = 1,    // [4]
+    B_STG_EMPTY = 5,   // [4]
+    B_ACC_FULL = 9,    // [2] score pair in TMEM ready
+    B_ACC_EMPTY = 11,  // [2] score pair consumed
+    B_OP_FULL = 13,    // [2] operand tile(s) written
+    B_OP_EMPTY = 15,   // [2] operand tile(s) consumed by the MMA
+    B_DONE = 17,
+    B_NUM = 18
 };
 
 struct Ctx {
@@ -81,11 +91,11 @@ struct Ctx {
     }
 };
 
-__device__ __forceinline__ void bwd_setup(Ctx& c, uint8_t* smem_raw, int* status, int op_full_count) {
+__device__ __forceinline__ void bwd_setup(Ctx& c, uint8_t* smem_raw, int* status, int off_bar) {
     const uint32_t raw = smem_u32(smem_raw);
     c.base = (raw + 1023u) & ~1023u;
     uint8_t* smem = smem_raw + (c.base - raw);
-    uint8_t* bar_ptr = smem + OFF_BAR;
+    uint8_t* bar_ptr = smem + off_bar;
     c.bar_base = smem_u32(bar_ptr);
     c.status = status;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_ptr + 8 * B_NUM);
@@ -94,12 +104,14 @@ __device__ __forceinline__ void bwd_setup(Ctx& c, uint8_t* smem_raw, int* status
     if (threadIdx.x == 0) {
         mbar_init(c.bar(B_RES_FULL), 1);
         mbar_init(c.bar(B_DONE), 1);
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < 4; ++s) {
             mbar_init(c.bar(B_STG_FULL + s), 1);
             mbar_init(c.bar(B_STG_EMPTY + s), 1);
+        }
+        for (int s = 0; s < 2; ++s) {
             mbar_init(c.bar(B_ACC_FULL + s), 1);
             mbar_init(c.bar(B_ACC_EMPTY + s), 128);
-            mbar_init(c.bar(B_OP_FULL + s), op_full_count);
+            mbar_init(c.bar(B_OP_FULL + s), 128);
             mbar_init(c.bar(B_OP_EMPTY + s), 1);
         }
         *c.abort_flag = 0;
@@ -200,7 +212,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_co
 
     extern __shared__ uint8_t smem_raw[];
     Ctx c;
-    bwd_setup(c, smem_raw, status, 128);
+    bwd_setup(c, smem_raw, status, DQ_OFF_BAR);
     if (threadIdx.x == 0) {
         prefetch_tmap(&tma_q);
         prefetch_tmap(&tma_do);
@@ -218,14 +230,14 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_co
             tma_load_2d(do_s, &tma_do, rb, h * HD, q_begin + q0);
             tma_load_2d(do_s + BOX128, &tma_do, rb, h * HD + 64, q_begin + q0);
             for (int i = 0; i < n_iter; ++i) {
-                const int st = i & 1;
-                const uint32_t ph = static_cast<uint32_t>(i >> 1) & 1u;
+                const int st = i % DQ_NSTG;
+                const uint32_t ph = static_cast<uint32_t>(i / DQ_NSTG) & 1u;
                 if (!c.wait(B_STG_EMPTY + st, ph ^ 1u)) {
                     c.fail(0x41);
                     break;
                 }
                 const uint32_t fb = c.bar(B_STG_FULL + st);
-                const uint32_t k_s = c.base + OFF_STG + st * 2 * SMALL_TILE, v_s = k_s + SMALL_TILE;
+                const uint32_t k_s = c.base + OFF_STG + st * STAGE_BYTES, v_s = k_s + SMALL_TILE;
                 const int row = k_begin + i * 64;
                 mbar_arrive_expect_tx(fb, 2 * SMALL_TILE);
                 tma_load_2d(k_s, &tma_k, fb, kvh * HD, row);
@@ -241,26 +253,25 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_co
             bool ok = c.wait(B_RES_FULL, 0u);
             if (!ok) c.fail(0x42);
             auto accumulate = [&](int j) -> bool {     // dQ += dS_j K_j
-                const int b = j & 1;
-                const uint32_t ph = static_cast<uint32_t>(j >> 1) & 1u;
-                if (!c.wait(B_OP_FULL + b, ph)) return false;
+                const int ob = j % DQ_NOP, st = j % DQ_NSTG;
+                if (!c.wait(B_OP_FULL + ob, static_cast<uint32_t>(j / DQ_NOP) & 1u)) return false;
                 tcgen05_fence_after();
-                const uint32_t k_s = c.base + OFF_STG + b * 2 * SMALL_TILE;
-                mma_accum(c.tmem_base + 256u, c.base + OFF_OPER + b * OPER_TILE, k_s, id_acc, j == 0);
-                umma_commit(c.bar(B_OP_EMPTY + b));
-                umma_commit(c.bar(B_STG_EMPTY + b));
+                const uint32_t k_s = c.base + OFF_STG + st * STAGE_BYTES;
+                mma_accum(c.tmem_base + 256u, c.base + DQ_OFF_OPER + ob * OPER_TILE, k_s, id_acc, j == 0);
+                umma_commit(c.bar(B_OP_EMPTY + ob));
+                umma_commit(c.bar(B_STG_EMPTY + st));
                 return true;
             };
             for (int i = 0; i < n_iter && ok; ++i) {
-                const int b = i & 1;
+                const int b = i & 1, st = i % DQ_NSTG;
                 const uint32_t ph = static_cast<uint32_t>(i >> 1) & 1u;
-                ok = c.wait(B_STG_FULL + b, ph) && c.wait(B_ACC_EMPTY + b, ph ^ 1u);
+                ok = c.wait(B_STG_FULL + st, static_cast<uint32_t>(i / DQ_NSTG) & 1u) && c.wait(B_ACC_EMPTY + b, ph ^ 1u);
                 if (!ok) {
                     c.fail(0x43);
                     break;
                 }
                 tcgen05_fence_after();
-                const uint32_t k_s = c.base + OFF_STG + b * 2 * SMALL_TILE, v_s = k_s + SMALL_TILE;
+                const uint32_t k_s = c.base + OFF_STG + st * STAGE_BYTES, v_s = k_s + SMALL_TILE;
                 mma_scores(c.tmem_base + static_cast<uint32_t>(b * 128), q_s, k_s, id_s);        // S
                 mma_scores(c.tmem_base + static_cast<uint32_t>(b * 128 + 64), do_s, v_s, id_s);  // dP
                 umma_commit(c.bar(B_ACC_FULL + b));
@@ -291,15 +302,16 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_co
             const int b = i & 1;
             const uint32_t ph = static_cast<uint32_t>(i >> 1) & 1u;
             const int kv0 = i * 64;
+            const int ob = i % DQ_NOP;
             if (!warp_wait(c.bar(B_ACC_FULL + b), ph, c.abort_flag) ||
-                !warp_wait(c.bar(B_OP_EMPTY + b), ph ^ 1u, c.abort_flag)) {
+                !warp_wait(c.bar(B_OP_EMPTY + ob), (static_cast<uint32_t>(i / DQ_NOP) & 1u) ^ 1u, c.abort_flag)) {
                 ok = false;
                 break;
             }
             tcgen05_fence_after();
             const int rel = lim - kv0;
             const uint32_t t_s = t_lane + static_cast<uint32_t>(b * 128);
-            const uint32_t ds_tile = c.base + OFF_OPER + b * OPER_TILE;
+            const uint32_t ds_tile = c.base + DQ_OFF_OPER + ob * OPER_TILE;
 #pragma unroll
             for (int cc = 0; cc < 2; ++cc) {
                 uint32_t s[32], dp[32];
@@ -319,7 +331,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_co
             tcgen05_fence_before();
             mbar_arrive(c.bar(B_ACC_EMPTY + b));
             fence_proxy_async_smem();
-            mbar_arrive(c.bar(B_OP_FULL + b));
+            mbar_arrive(c.bar(B_OP_FULL + ob));
         }
         if (ok) ok = warp_wait(c.bar(B_DONE), 0u, c.abort_flag);
         if (!ok) {
@@ -373,7 +385,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
 
     extern __shared__ uint8_t smem_raw[];
     Ctx c;
-    bwd_setup(c, smem_raw, status, 128);
+    bwd_setup(c, smem_raw, status, KV_OFF_BAR);
     if (threadIdx.x == 0) {
         prefetch_tmap(&tma_q);
         prefetch_tmap(&tma_do);
@@ -381,7 +393,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
         prefetch_tmap(&tma_v);
     }
     const uint32_t k_s = c.base + OFF_RES0, v_s = c.base + OFF_RES1;
-    float* vec = reinterpret_cast<float*>(smem_raw + (c.base - smem_u32(smem_raw)) + OFF_VEC);
+    float* vec = reinterpret_cast<float*>(smem_raw + (c.base - smem_u32(smem_raw)) + KV_OFF_VEC);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -392,8 +404,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
             tma_load_2d(v_s, &tma_v, rb, kvh * HD, k_begin + kv0);
             tma_load_2d(v_s + BOX128, &tma_v, rb, kvh * HD + 64, k_begin + kv0);
             for (int i = 0; i < n_iter; ++i) {
-                const int st = i & 1;
-                const uint32_t ph = static_cast<uint32_t>(i >> 1) & 1u;
+                const int st = i % KV_NSTG;
+                const uint32_t ph = static_cast<uint32_t>(i / KV_NSTG) & 1u;
                 const int h = kvh * G + i / per_head;
                 const int row = q_begin + (jt_lo + i % per_head) * 64;
                 if (!c.wait(B_STG_EMPTY + st, ph ^ 1u)) {
@@ -401,7 +413,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
                     break;
                 }
                 const uint32_t fb = c.bar(B_STG_FULL + st);
-                const uint32_t q_s = c.base + OFF_STG + st * 2 * SMALL_TILE, do_s = q_s + SMALL_TILE;
+                const uint32_t q_s = c.base + OFF_STG + st * STAGE_BYTES, do_s = q_s + SMALL_TILE;
                 mbar_arrive_expect_tx(fb, 2 * SMALL_TILE);
                 tma_load_2d(q_s, &tma_q, fb, h * HD, row);
                 tma_load_2d(q_s + BOX64, &tma_q, fb, h * HD + 64, row);
@@ -416,28 +428,27 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
             bool ok = c.wait(B_RES_FULL, 0u);
             if (!ok) c.fail(0x52);
             auto accumulate = [&](int j) -> bool {     // dV += P^T dO_j ; dK += dS^T Q_j
-                const int b = j & 1;
-                const uint32_t ph = static_cast<uint32_t>(j >> 1) & 1u;
-                if (!c.wait(B_OP_FULL + b, ph)) return false;
+                const int ob = j % KV_NOP, st = j % KV_NSTG;
+                if (!c.wait(B_OP_FULL + ob, static_cast<uint32_t>(j / KV_NOP) & 1u)) return false;
                 tcgen05_fence_after();
-                const uint32_t q_s = c.base + OFF_STG + b * 2 * SMALL_TILE, do_s = q_s + SMALL_TILE;
-                const uint32_t pt_s = c.base + OFF_OPER + b * 2 * OPER_TILE, dst_s = pt_s + OPER_TILE;
+                const uint32_t q_s = c.base + OFF_STG + st * STAGE_BYTES, do_s = q_s + SMALL_TILE;
+                const uint32_t pt_s = c.base + KV_OFF_OPER + ob * 2 * OPER_TILE, dst_s = pt_s + OPER_TILE;
                 mma_accum(c.tmem_base + 256u, pt_s, do_s, id_acc, j == 0);
                 mma_accum(c.tmem_base + 384u, dst_s, q_s, id_acc, j == 0);
-                umma_commit(c.bar(B_OP_EMPTY + b));
-                umma_commit(c.bar(B_STG_EMPTY + b));
+                umma_commit(c.bar(B_OP_EMPTY + ob));
+                umma_commit(c.bar(B_STG_EMPTY + st));
                 return true;
             };
             for (int i = 0; i < n_iter && ok; ++i) {
-                const int b = i & 1;
+                const int b = i & 1, st = i % KV_NSTG;
                 const uint32_t ph = static_cast<uint32_t>(i >> 1) & 1u;
-                ok = c.wait(B_STG_FULL + b, ph) && c.wait(B_ACC_EMPTY + b, ph ^ 1u);
+                ok = c.wait(B_STG_FULL + st, static_cast<uint32_t>(i / KV_NSTG) & 1u) && c.wait(B_ACC_EMPTY + b, ph ^ 1u);
                 if (!ok) {
                     c.fail(0x53);
                     break;
                 }
                 tcgen05_fence_after();
-                const uint32_t q_s = c.base + OFF_STG + b * 2 * SMALL_TILE, do_s = q_s + SMALL_TILE;
+                const uint32_t q_s = c.base + OFF_STG + st * STAGE_BYTES, do_s = q_s + SMALL_TILE;
                 mma_scores(c.tmem_base + static_cast<uint32_t>(b * 128), k_s, q_s, id_s);         // S^T
                 mma_scores(c.tmem_base + static_cast<uint32_t>(b * 128 + 64), v_s, do_s, id_s);   // dP^T
                 umma_commit(c.bar(B_ACC_FULL + b));
@@ -478,8 +489,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
                 dl[j] = (q < q_len) ? p.delta[idx] : 0.f;
             }
             __syncwarp();
-            if (!warp_wait(c.bar(B_ACC_FULL + b), ph, c.abort_flag) ||
-                !warp_wait(c.bar(B_OP_EMPTY + b), ph ^ 1u, c.abort_flag)) {
+            const int ob = i % KV_NOP;
+            if (!warp_wait(c.bar(B_ACC_FULL + b), ph, c.abort_flag)) {
                 ok = false;
                 break;
             }
@@ -487,7 +498,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
             // query column j (row qt0 + j) sees key kv_row iff kv_row <= qt0 + j + shift
             const int jmin = p.causal ? kv_row - shift - qt0 : 0;     // columns below jmin are masked
             const uint32_t t_s = t_lane + static_cast<uint32_t>(b * 128);
-            const uint32_t pt_tile = c.base + OFF_OPER + b * 2 * OPER_TILE, dst_tile = pt_tile + OPER_TILE;
+            const uint32_t pt_tile = c.base + KV_OFF_OPER + ob * 2 * OPER_TILE, dst_tile = pt_tile + OPER_TILE;
 #pragma unroll
             for (int cc = 0; cc < 2; ++cc) {
                 uint32_t s[32], dp[32];
@@ -504,16 +515,25 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
                     pe[j] = live ? pr : 0.f;
                     de[j] = live ? ds : 0.f;
                 }
+                if (cc == 0) {
+                    // the single operand pair is still being read by the MMA of the previous tile until this fires;
+                    // the math above already overlapped with it
+                    if (!warp_wait(c.bar(B_OP_EMPTY + ob), (static_cast<uint32_t>(i / KV_NOP) & 1u) ^ 1u, c.abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                }
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
                     st_swizzled_chunk(pt_tile, row, static_cast<uint32_t>(cc * 4 + g), pe + 8 * g);
                     st_swizzled_chunk(dst_tile, row, static_cast<uint32_t>(cc * 4 + g), de + 8 * g);
                 }
             }
+            if (!ok) break;
             tcgen05_fence_before();
             mbar_arrive(c.bar(B_ACC_EMPTY + b));
             fence_proxy_async_smem();
-            mbar_arrive(c.bar(B_OP_FULL + b));
+            mbar_arrive(c.bar(B_OP_FULL + ob));
         }
         if (ok) ok = warp_wait(c.bar(B_DONE), 0u, c.abort_flag);
         if (!ok) {
@@ -558,17 +578,17 @@ const char* attn_backward_tc(const AttnParams& p, int* status, cudaStream_t st) 
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_bwd_dq_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             BWD_SMEM_BYTES);
+                                             DQ_SMEM_BYTES);
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(attn_bwd_dkv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     BWD_SMEM_BYTES);
+                                     KV_SMEM_BYTES);
         if (e != cudaSuccess) return cudaGetErrorString(e);
         configured = true;
     }
     const dim3 grid_kv((p.max_k + 127) / 128, p.num_seqs, p.Hkv);
     const dim3 grid_q((p.max_q + 127) / 128, p.num_seqs, p.H);
-    attn_bwd_dkv_tc_kernel<<<grid_kv, BWD_THREADS, BWD_SMEM_BYTES, st>>>(q64, do64, k128, v128, p, status);
-    attn_bwd_dq_tc_kernel<<<grid_q, BWD_THREADS, BWD_SMEM_BYTES, st>>>(q128, do128, k64, v64, p, status);
+    attn_bwd_dkv_tc_kernel<<<grid_kv, BWD_THREADS, KV_SMEM_BYTES, st>>>(q64, do64, k128, v128, p, status);
+    attn_bwd_dq_tc_kernel<<<grid_q, BWD_THREADS, DQ_SMEM_BYTES, st>>>(q128, do128, k64, v64, p, status);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }

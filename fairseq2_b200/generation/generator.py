@@ -13,7 +13,7 @@ from __future__ import annotations
 
 from abc import ABC, abstractmethod
 from dataclasses import dataclass, field
-from typing import Sequence
+from typing import Any, Sequence
 
 import torch
 from torch import Tensor
@@ -41,6 +41,27 @@ class SequenceGeneratorOutput:
 class SequenceGenerator(ABC):
     def __init__(self, model: CausalLM, eos_idx: int, pad_idx: int | None = None) -> None:
         self.model, self.eos_idx, self.pad_idx = model, eos_idx, pad_idx
+        self._step_hooks: dict[int, Any] = {}
+
+    def register_step_hook(self, hook: Any) -> Any:
+        """``hook(prompt_indices, seqs, step_scores, prefill)`` runs after every decoding step with the indices of
+        the prompts still being generated and their sequences so far. The returned handle is a context manager
+        that removes the hook on exit (or via ``remove()``)."""
+        key = max(self._step_hooks, default=-1) + 1
+        self._step_hooks[key] = hook
+        hooks = self._step_hooks
+
+        class _Handle:
+            def remove(self) -> None:
+                hooks.pop(key, None)
+
+            def __enter__(self) -> "_Handle":
+                return self
+
+            def __exit__(self, *exc: object) -> None:
+                self.remove()
+
+        return _Handle()
 
     @abstractmethod
     def __call__(self, prompt_seqs: Tensor, prompt_layout: BatchLayout) -> SequenceGeneratorOutput: ...
@@ -145,6 +166,10 @@ class SamplingSequenceGenerator(SequenceGenerator):
             seqs[active, nxt] = tok
             if step_scores is not None:
                 step_scores[active, nxt] = torch.log(probs.gather(1, tok.unsqueeze(1)).squeeze(1).clamp(min=1e-30))
+            if self._step_hooks:
+                ss = step_scores[active, :nxt + 1] if step_scores is not None else None
+                for hook in self._step_hooks.values():
+                    hook(active // self.num_gens, seqs[active, :nxt + 1], ss, False)
             done = (tok == self.eos_idx) & ~in_prompt
             if done.any():
                 rows = active[done]

@@ -137,3 +137,45 @@ def test_sft_recipe_exports_hugging_face_checkpoint(tmp_path: Path) -> None:
         a = ours.eval()(x, BatchLayout((1, 12), [12]))
         b = hf(x).logits
     assert torch.allclose(a, b, atol=5e-2), float((a - b).abs().max())
+
+
+def test_chatbot_program_streams_reply() -> None:
+    from fairseq2_b200.data.tokenizers import CharTokenizer
+    from fairseq2_b200.gang import FakeGang, create_fake_gangs
+    from fairseq2_b200.generation import SamplingSequenceGenerator, TopKSampler
+    from fairseq2_b200.models.family import get_model_family
+    from recipes.chatbot.chatbot import LLaMADialogEncoder, Message, MistralDialogEncoder, StandardChatbot
+    from recipes.chatbot.program import ChatbotProgram, ProgramView
+
+    torch.manual_seed(0)
+    dev = torch.device("cpu")
+    tok = CharTokenizer()
+    fam = get_model_family("llama")
+    model = fam.create_new_model(fam.get_arch_config("tiny"), create_fake_gangs(dev)).eval()
+    vi = tok.vocab_info
+    gen = SamplingSequenceGenerator(model, vi.eos_idx, vi.pad_idx, TopKSampler(1), max_gen_len=6)
+    enc = LLaMADialogEncoder(tok, dev)
+    ids = enc.encode([Message("system", "be brief"), Message("user", "hi"), Message("bot", "hello"), Message("user", "bye?")])
+    assert ids[0] == vi.bos_idx and (ids == vi.eos_idx).sum() == 1
+    assert not MistralDialogEncoder(tok, dev).supports_system_prompt
+
+    class View(ProgramView):
+        def __init__(self) -> None:
+            self.inputs, self.pieces = iter(["hi there", "bye"]), []
+
+        def input_system_prompt(self) -> str:
+            return ""
+
+        def input_message(self) -> str:
+            return next(self.inputs)
+
+        def print_reply(self, message: str) -> None:
+            self.pieces.append(("reply", message))
+
+        def print_reply_piece(self, piece: str) -> None:
+            self.pieces.append(("piece", piece))
+
+    view = View()
+    bot = StandardChatbot(gen, enc, tok.create_decoder(skip_special_tokens=True))
+    ChatbotProgram(view, bot, gen, tok, FakeGang(device=dev), enc).run()
+    assert ("reply", "Bye!\n") in view.pieces and ("piece", "\n") in view.pieces
