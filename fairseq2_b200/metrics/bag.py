@@ -109,5 +109,12 @@ def sync_and_compute_metrics(bag: MetricBag | Sequence[MetricBag], gang: Gang | 
     if gang is not None and gang.rank != 0:
         return None
     names = [n for n, _ in items]
-    vals = torch.stack([m.compute_from(states[n]).to(torch.float64) for n, m in items]).cpu().tolist()  # one D2H
-    return dict(zip(names, vals))
+    outs = [m.compute_from(states[n]).to(torch.float64).reshape(-1) for n, m in items]
+    flat = torch.cat([o.to(outs[0].device) for o in outs]).cpu().tolist()  # one D2H
+    result: dict[str, Any] = {}
+    off = 0
+    for n, o in zip(names, outs):
+        k = o.numel()
+        result[n] = flat[off] if k == 1 else flat[off: off + k]   # multi-valued metrics (e.g. UER + WER) stay lists
+        off += k
+    return result

@@ -179,3 +179,55 @@ def test_chatbot_program_streams_reply() -> None:
     bot = StandardChatbot(gen, enc, tok.create_decoder(skip_special_tokens=True))
     ChatbotProgram(view, bot, gen, tok, FakeGang(device=dev), enc).run()
     assert ("reply", "Bye!\n") in view.pieces and ("piece", "\n") in view.pieces
+
+
+def _write_speech_data(root: Path, n: int = 12) -> Path:
+    import struct
+
+    audio = root / "audio"
+    audio.mkdir(parents=True)
+    man = root / "manifest"
+    man.mkdir()
+    g = torch.Generator().manual_seed(0)
+    for split, count in (("train", n), ("valid", 4)):
+        rows, texts = [], []
+        for i in range(count):
+            num = 3000 + 250 * i
+            t = torch.arange(num) / 16000
+            wav = (0.3 * torch.sin(2 * torch.pi * (200 + 40 * i) * t) + 0.05 * torch.randn(num, generator=g))
+            pcm = (wav.clamp(-1, 1) * 32767).to(torch.int16).numpy().tobytes()
+            name = f"{split}_{i}.wav"
+            with open(audio / name, "wb") as fp:
+                fp.write(b"RIFF" + struct.pack("<I", 36 + len(pcm)) + b"WAVEfmt " +
+                         struct.pack("<IHHIIHH", 16, 1, 1, 16000, 32000, 2, 16) + b"data" +
+                         struct.pack("<I", len(pcm)) + pcm)
+            rows.append(f"{name}\t{num}")
+            texts.append("ab ba"[: 3 + i % 3])
+        (man / f"{split}.tsv").write_text(str(audio) + "\n" + "\n".join(rows) + "\n")
+        (man / f"{split}.wrd").write_text("\n".join(texts) + "\n")
+    return man
+
+
+def test_wav2vec2_ssl_and_asr_recipes(tmp_path: Path) -> None:
+    from recipes.wav2vec2.asr.recipe import Wav2Vec2AsrRecipe
+    from recipes.wav2vec2.ssl.recipe import Wav2Vec2SslRecipe
+
+    man = _write_speech_data(tmp_path)
+    common = ["--no-sweep-dir", "--no-exit-on-error", "--config", "model.arch=tiny",
+              f"dataset.config_overrides={{path: {man}}}", "dataset.min_audio_len=1000", "dataset.max_audio_len=8000",
+              "dataset.max_num_elements=16000", "dataset.npc=1", "trainer.mixed_precision.mode=off",
+              "regime.num_steps=3", "regime.validate_every_n_steps=3", "regime.checkpoint_every_n_steps=3",
+              "regime.publish_metrics_every_n_steps=1", "common.metric_recorders.jsonl=true"]
+    out = tmp_path / "ssl"
+    assert main(Wav2Vec2SslRecipe(), [str(out), *common, "lr_scheduler.config.num_warmup_steps=1",
+                                      "optimizer.config.lr=1e-4"]) == 0
+    rows = [json.loads(l) for l in open(out / "metrics" / "train.jsonl")]
+    assert len(rows) == 3
+    assert (out / "metrics" / "valid.jsonl").exists() and (out / "checkpoints" / "step_3").is_dir()
+
+    out = tmp_path / "asr"
+    assert main(Wav2Vec2AsrRecipe(), [str(out), *common, "tokenizer.name=char_tokenizer",
+                                      "model.config_overrides={target_vocab_size: 300}",
+                                      "trainer.freeze_encoder_for_n_steps=1", "regime.validate_after_n_steps=0"]) == 0
+    valid = [json.loads(l) for l in open(out / "metrics" / "valid.jsonl")]
+    assert valid and any("wer" in k.lower() for k in valid[-1])
