@@ -1,5 +1,6 @@
 """End-to-end recipe runs on CPU with the tiny LLaMA and the byte-level tokenizer."""
 import json
+import math
 from pathlib import Path
 
 import pytest
@@ -231,3 +232,24 @@ def test_wav2vec2_ssl_and_asr_recipes(tmp_path: Path) -> None:
                                       "trainer.freeze_encoder_for_n_steps=1", "regime.validate_after_n_steps=0"]) == 0
     valid = [json.loads(l) for l in open(out / "metrics" / "valid.jsonl")]
     assert valid and any("wer" in k.lower() for k in valid[-1])
+
+
+def test_lm_dpo_recipe(tmp_path: Path) -> None:
+    from recipes.lm.dpo.recipe import LMDPORecipe
+
+    data = tmp_path / "pref.jsonl"
+    with open(data, "w") as fp:
+        for i in range(32):
+            fp.write(json.dumps({"src": f"Is {i} even? ", "tgt_chosen": "yes" if i % 2 == 0 else "no",
+                                 "tgt_rejected": "no" if i % 2 == 0 else "yes"}) + "\n")
+    args = [str(tmp_path / "out"), "--no-sweep-dir", "--no-exit-on-error", "--config", "model.name=null",
+            "model.family=llama", "model.arch=tiny", "reference_model.name=null", "reference_model.family=llama",
+            "reference_model.arch=tiny", "reference_model.dtype=float32", "tokenizer.name=char_tokenizer",
+            f"dataset.config_overrides={{path: {data}}}", "dataset.batch_size=4", "dataset.max_seq_len=64",
+            "trainer.mixed_precision.mode=off", "optimizer.config.lr=1e-4", "lr_scheduler.config.num_warmup_steps=1",
+            "criterion.beta=0.5", "criterion.nll_scale=0.1", "regime.num_steps=4",
+            "regime.checkpoint_every_n_steps=4", "regime.publish_metrics_every_n_steps=1",
+            "common.metric_recorders.jsonl=true"]
+    assert main(LMDPORecipe(), args) == 0
+    rows = [json.loads(l) for l in open(tmp_path / "out" / "metrics" / "train.jsonl")]
+    assert len(rows) == 4 and all(math.isfinite(r["dpo_loss"]) for r in rows)
