@@ -102,6 +102,32 @@ void gemm_bf16(const Tensor& a, const Tensor& b, Tensor& out, bool a_mn, bool b_
     g_launches += 1;
 }
 
+// C = a[M,K] * b[N,K]^T summed over ranks and scattered by rows: rank r receives rows [r*rpr, (r+1)*rpr) of the sum
+// in its fp32 [rpr, N] buffer at `out_byte_off` of its symmetric arena (`ptrs` are the arenas' base addresses).
+void gemm_reduce_scatter(const Tensor& a, const Tensor& b, const std::vector<int64_t>& ptrs, int64_t out_byte_off,
+                         int64_t rows_per_rank) {
+    TORCH_CHECK(a.is_cuda() && b.is_cuda() && is_bf16(a) && is_bf16(b) && a.dim() == 2 && b.dim() == 2 &&
+                    a.is_contiguous() && b.is_contiguous() && a.size(1) == b.size(1),
+                "gemm_reduce_scatter: a [M,K] and b [N,K] must be contiguous bf16 CUDA matrices");
+    TORCH_CHECK(a.size(1) % 8 == 0 && aligned16(a) && aligned16(b) && out_byte_off % 16 == 0,
+                "gemm_reduce_scatter: alignment");
+    TORCH_CHECK(!ptrs.empty() && ptrs.size() <= 8, "gemm_reduce_scatter: between 1 and 8 ranks are supported");
+    float* outs[8];
+    for (size_t i = 0; i < ptrs.size(); ++i) {
+        TORCH_CHECK(ptrs[i] != 0, "gemm_reduce_scatter: null peer pointer");
+        outs[i] = reinterpret_cast<float*>(ptrs[i] + out_byte_off);
+    }
+    check_status();
+    c10::cuda::CUDAGuard guard(a.device());
+    TORCH_CHECK(cudaSetDevice(a.get_device()) == cudaSuccess, "gemm_reduce_scatter: cudaSetDevice failed");
+    const char* err = fs2::gemm_reduce_scatter_bf16_tcgen05(
+        a.data_ptr(), b.data_ptr(), outs, static_cast<int>(ptrs.size()), static_cast<int>(rows_per_rank),
+        static_cast<int>(a.size(0)), static_cast<int>(b.size(0)), static_cast<int>(a.size(1)), status_dev_ptr(),
+        num_sms(a), stream_of(a));
+    TORCH_CHECK(err == nullptr, "gemm_reduce_scatter: ", err);
+    g_launches += 1;
+}
+
 // ---------------------------------------------------------------------- norms
 std::tuple<Tensor, Tensor> rms_norm_fwd(const Tensor& x, const Tensor& w, double eps) {
     TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous() && w.is_contiguous(), "rms_norm_fwd: bad input");
@@ -618,6 +644,7 @@ void comm_alltoall(const std::vector<int64_t>& ptrs, int64_t rank, int64_t byte_
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.doc() = "fairseq2_b200 sm_100a kernels";
     m.def("gemm_bf16", &gemm_bf16);
+    m.def("gemm_reduce_scatter", &gemm_reduce_scatter);
     m.def("rms_norm_fwd", &rms_norm_fwd);
     m.def("rms_norm_bwd", &rms_norm_bwd);
     m.def("layer_norm_fwd", &layer_norm_fwd);

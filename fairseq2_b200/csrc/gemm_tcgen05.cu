@@ -98,10 +98,22 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_
     n_tile = r / gsize;
 }
 
-template <bool A_MN, bool B_MN, bool OUT_F32>
+// Destination of the fused reduce-scatter epilogue: row block r of C (rows [r * rows_per_rank, (r + 1) *
+// rows_per_rank)) is summed into `out[r]`, an fp32 [rows_per_rank, N] buffer in rank r's memory that this GPU
+// reaches through a peer mapping.
+struct PeerOut {
+    float* out[8];
+    int rows_per_rank;
+};
+
+// PEER_RED: instead of storing C locally, every fp32 tile is reduced (red.global.add) straight into the memory of
+// the rank that owns its rows, so a row-parallel GEMM and the reduce-scatter that follows it are one kernel and the
+// NVLink traffic of tile i overlaps the tensor-core work of tile i + 1.
+template <bool A_MN, bool B_MN, bool OUT_F32, bool PEER_RED = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-            const __grid_constant__ CUtensorMap tma_c, int M, int N, int K, int accumulate, int* status) {
+            const __grid_constant__ CUtensorMap tma_c, int M, int N, int K, int accumulate, int* status,
+            const PeerOut po) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -265,7 +277,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
             for (int c = 0; c < NCHUNK; ++c) {
                 const int col0 = c * CHUNK_COLS;
                 if (n0 + col0 >= N) break;  // uniform over the CTA
-                if (leader) tma_wait_group_read<1>();
+                if constexpr (!PEER_RED) {
+                    if (leader) tma_wait_group_read<1>();
+                }
                 epi_bar_sync();
                 const uint32_t sbuf = epi_base + buf * EPI_BYTES;
                 const uint32_t srow = sbuf + row * 128;
@@ -300,12 +314,36 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
                                      : "memory");
                     }
                 }
-                fence_proxy_async_smem();
-                epi_bar_sync();
-                if (leader) {
-                    if (accumulate) tma_reduce_add_2d(&tma_c, sbuf, n0 + col0, m0);
-                    else tma_store_2d(&tma_c, sbuf, n0 + col0, m0);
-                    tma_commit_group();
+                if constexpr (PEER_RED) {
+                    static_assert(!PEER_RED || OUT_F32, "the fused reduce-scatter epilogue accumulates in fp32");
+                    epi_bar_sync();
+                    // 128 threads sweep the staged [128 rows][32 fp32] chunk: 8 threads cover one 128-byte row
+                    // segment, so every red instruction of a warp touches four full 128-byte lines of the owner
+                    const int e = static_cast<int>(threadIdx.x) - 64;
+                    const int j = e & 7;
+#pragma unroll
+                    for (int it = 0; it < 8; ++it) {
+                        const int r = it * 16 + (e >> 3);
+                        const int grow = m0 + r, gcol = n0 + col0 + j * 4;
+                        if (grow < M && gcol < N) {
+                            float4 v;
+                            const uint32_t src = sbuf + r * 128 + (((j ^ (r & 7)) & 7) << 4);
+                            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                         : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(src));
+                            const int owner = grow / po.rows_per_rank;
+                            float* dst = po.out[owner] + static_cast<size_t>(grow - owner * po.rows_per_rank) * N + gcol;
+                            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                                         ::"l"(dst), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+                        }
+                    }
+                } else {
+                    fence_proxy_async_smem();
+                    epi_bar_sync();
+                    if (leader) {
+                        if (accumulate) tma_reduce_add_2d(&tma_c, sbuf, n0 + col0, m0);
+                        else tma_store_2d(&tma_c, sbuf, n0 + col0, m0);
+                        tma_commit_group();
+                    }
                 }
                 buf ^= 1;
             }
@@ -314,7 +352,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1u;
         }
-        if (leader) tma_wait_group<0>();
+        if constexpr (!PEER_RED) {
+            if (leader) tma_wait_group<0>();
+        }
     }
 
     // -------------------------------------------------------------- teardown
@@ -384,7 +424,7 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
     }
     const int num_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int grid = num_tiles < num_sms ? num_tiles : num_sms;
-    kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tc, M, N, K, accumulate, status);
+    kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tc, M, N, K, accumulate, status, PeerOut{});
     return cudaGetLastError();
 }
 
@@ -412,6 +452,34 @@ const char* gemm_bf16_tcgen05(const void* a, const void* b, void* c, int M, int 
 #undef FS2_LAUNCH
     if (e != cudaSuccess) return cudaGetErrorString(e);
     return nullptr;
+}
+
+const char* gemm_reduce_scatter_bf16_tcgen05(const void* a, const void* b, float* const* peer_out, int world,
+                                             int rows_per_rank, int M, int N, int K, int* status, int num_sms,
+                                             cudaStream_t stream) {
+    if (world < 1 || world > 8) return "gemm_reduce_scatter: between 1 and 8 ranks are supported";
+    if (rows_per_rank <= 0 || rows_per_rank * world < M) return "gemm_reduce_scatter: rows_per_rank * world must cover M";
+    if (N % 4) return "gemm_reduce_scatter: N must be a multiple of 4";
+    CUtensorMap ta, tb;
+    g_tmap_err[0] = 0;
+    if (!make_tmap(&ta, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, BM, BK) ||
+        !make_tmap(&tb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, BN, BK))
+        return g_tmap_err;
+    PeerOut po{};
+    for (int r = 0; r < world; ++r) po.out[r] = peer_out[r];
+    po.rows_per_rank = rows_per_rank;
+    auto kern = gemm_kernel<false, false, true, true>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return cudaGetErrorString(e);
+        configured = true;
+    }
+    const int num_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int grid = num_tiles < num_sms ? num_tiles : num_sms;
+    kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, ta, M, N, K, 0, status, po);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
 
 }  // namespace fs2

@@ -13,4 +13,11 @@ namespace fs2 {
 const char* gemm_bf16_tcgen05(const void* a, const void* b, void* c, int M, int N, int K, bool a_mn, bool b_mn,
                               bool out_f32, bool accumulate, int* status, int num_sms, cudaStream_t stream);
 
+// Row-parallel GEMM fused with its reduce-scatter: C = A[M,K] * B[N,K]^T is never stored locally; every fp32
+// tile is added into `peer_out[r]` ([rows_per_rank, N] fp32 in rank r's memory, zeroed beforehand), where r owns
+// the tile's rows. The caller brackets the launch with cross-rank barriers (buffers zeroed / all adds landed).
+const char* gemm_reduce_scatter_bf16_tcgen05(const void* a, const void* b, float* const* peer_out, int world,
+                                             int rows_per_rank, int M, int N, int K, int* status, int num_sms,
+                                             cudaStream_t stream);
+
 }  // namespace fs2

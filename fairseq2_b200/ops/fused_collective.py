@@ -1,0 +1,61 @@
+"""Compute + collective fused into one kernel over NVLink peer memory.
+
+``FusedGemmReduceScatter`` is the row-parallel linear layer of tensor parallelism with a sequence-parallel
+output: every rank multiplies its slice of the activations by its slice of the weight and the partial products
+must be summed over ranks, rank ``r`` keeping rows ``[r·M/W, (r+1)·M/W)``. Instead of a GEMM followed by a
+reduce-scatter, the tcgen05 GEMM's epilogue adds every fp32 accumulator tile straight into the memory of the
+rank that owns its rows (``red.global.add.v4.f32`` through the peer mapping), so the NVLink transfer of tile
+``i`` overlaps the tensor-core work of tile ``i + 1`` and the full ``[M, N]`` partial product never exists.
+
+The destination buffers live in a symmetric arena and alternate between two slots: a slot is zeroed one call
+ahead, so each call needs a single cross-rank barrier (after the kernel, when all additions have landed).
+"""
+from __future__ import annotations
+
+import torch
+from torch import Tensor
+
+from fairseq2_b200.parallel.symm import SymmetricArena
+
+
+def gemm_reduce_scatter_reference(x_parts: list[Tensor], w_parts: list[Tensor], rank: int) -> Tensor:
+    """fp32 oracle: ``sum_r x_r @ w_rᵀ`` restricted to the rows that ``rank`` owns."""
+    full = sum(x.float() @ w.float().t() for x, w in zip(x_parts, w_parts))
+    rows = full.shape[0] // len(x_parts)
+    return full[rank * rows:(rank + 1) * rows]
+
+
+class FusedGemmReduceScatter:
+    #: barrier slot inside the arena's flag page reserved for this operator family
+    SLOT = 40
+
+    def __init__(self, arena: SymmetricArena, max_rows_per_rank: int, out_dim: int) -> None:
+        self.arena = arena
+        self.max_rows, self.out_dim = max_rows_per_rank, out_dim
+        self._slots = [arena.alloc_tensor(max_rows_per_rank * out_dim, torch.float32) for _ in range(2)]
+        self._which = 0
+        self._epoch = 0
+        for _, buf in self._slots:
+            buf.zero_()
+        # every rank's slots are zero before anyone adds into them
+        self._epoch += 1
+        arena.barrier(self.SLOT, self._epoch)
+
+    def __call__(self, x: Tensor, weight: Tensor) -> Tensor:
+        """``x``: bf16 ``[M, K_local]``, ``weight``: bf16 ``[N, K_local]`` -> fp32 ``[M / world, N]`` (a view into
+        the arena that stays valid until the call after the next one)."""
+        arena = self.arena
+        M, N = x.shape[0], weight.shape[0]
+        if M % arena.world:
+            raise ValueError(f"The number of rows ({M}) must be a multiple of the world size ({arena.world}).")
+        rows = M // arena.world
+        if rows > self.max_rows or N != self.out_dim:
+            raise ValueError("The operands exceed the shapes this operator was created for.")
+        off, buf = self._slots[self._which]
+        nxt_off, nxt = self._slots[self._which ^ 1]
+        self._which ^= 1
+        arena.ext.gemm_reduce_scatter(x.contiguous(), weight.contiguous(), arena.peer_ptrs, off, rows)
+        nxt.zero_()                       # the other slot is free again: its last reader ran before this call
+        self._epoch += 1
+        arena.barrier(self.SLOT, self._epoch)   # all ranks' additions have landed (and their next slots are zero)
+        return buf[: rows * N].view(rows, N)

@@ -125,3 +125,35 @@ def test_fsdp_symm_matches_nccl() -> None:
         for (la, ga), (lb, gb) in zip(ra, rb):
             assert abs(la - lb) / abs(lb) < 2e-2
             assert abs(ga - gb) / abs(gb) < 5e-2
+
+
+def _gemm_rs_worker(rank: int, world: int):
+    from fairseq2_b200.gang import ProcessGroupGang
+    from fairseq2_b200.ops.fused_collective import FusedGemmReduceScatter, gemm_reduce_scatter_reference
+    from fairseq2_b200.parallel.symm import SymmetricArena
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    base = ProcessGroupGang.create_default_process_group(dev)
+    M, N, Kl = 1024, 768, 512
+    arena = SymmetricArena(base, 4 * (M // world) * N * 4 + (1 << 20))
+    op = FusedGemmReduceScatter(arena, M // world, N)
+    errs = []
+    for it in range(3):                                   # three calls exercise both buffer slots
+        gen = torch.Generator(device="cpu").manual_seed(100 + it)
+        xs = [torch.randn(M, Kl, generator=gen).to(torch.bfloat16) for _ in range(world)]
+        ws = [(torch.randn(N, Kl, generator=gen) * 0.05).to(torch.bfloat16) for _ in range(world)]
+        out = op(xs[rank].to(dev), ws[rank].to(dev))
+        ref = gemm_reduce_scatter_reference(xs, ws, rank).to(dev)
+        errs.append(float((out - ref).norm() / ref.norm()))
+    torch.cuda.synchronize()
+    arena.ext.check_status()
+    base.close()
+    return errs
+
+
+def test_fused_gemm_reduce_scatter() -> None:
+    _need_gpus(2)
+    for errs in run_distributed(_gemm_rs_worker, 2):
+        assert all(e < 1e-2 for e in errs), errs
