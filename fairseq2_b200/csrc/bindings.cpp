@@ -596,6 +596,34 @@ void comm_reducescatter_segments(const std::vector<int64_t>& ptrs, int64_t rank,
     g_launches += 1;
 }
 
+void comm_reducescatter_adamw(const std::vector<int64_t>& ptrs, int64_t rank, const std::vector<int64_t>& offs,
+                              const std::vector<int64_t>& numels, int64_t full_byte_off, Tensor master, Tensor m,
+                              Tensor v, const std::optional<Tensor>& low, double scale, double lr, double beta1,
+                              double beta2, double eps, double wd, int64_t step, int64_t slot, int64_t epoch,
+                              int64_t blocks, double wait_limit_s) {
+    const int64_t shard_numel = offs.back() + numels.back();
+    for (const Tensor* t : {&master, &m, &v})
+        TORCH_CHECK(t->is_cuda() && t->is_contiguous() && t->scalar_type() == at::kFloat &&
+                        t->numel() == shard_numel && aligned16(*t),
+                    "comm_reducescatter_adamw: master/m/v must be contiguous fp32 shard-sized CUDA tensors");
+    void* lowp = nullptr;
+    if (low.has_value()) {
+        TORCH_CHECK(low->is_cuda() && low->is_contiguous() && is_bf16(*low) && low->numel() == shard_numel &&
+                        aligned16(*low),
+                    "comm_reducescatter_adamw: `low` must be a contiguous bf16 shard-sized CUDA tensor");
+        lowp = low->data_ptr();
+    }
+    TORCH_CHECK(full_byte_off % 16 == 0 && step >= 1, "comm_reducescatter_adamw: bad argument");
+    c10::cuda::CUDAGuard guard(master.device());
+    fs2::comm_reducescatter_adamw(make_peers(ptrs, rank, wait_limit_s), make_segments(offs, numels), full_byte_off,
+                                  master.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), lowp,
+                                  static_cast<float>(scale), static_cast<float>(lr), static_cast<float>(beta1),
+                                  static_cast<float>(beta2), static_cast<float>(eps), static_cast<float>(wd),
+                                  static_cast<int>(step), static_cast<int>(slot), static_cast<uint32_t>(epoch),
+                                  static_cast<int>(blocks), status_dev_ptr(), stream_of(master));
+    g_launches += 1;
+}
+
 void comm_allreduce_f32(const std::vector<int64_t>& ptrs, int64_t rank, int64_t byte_off, Tensor out, int64_t op,
                         int64_t slot, int64_t epoch, double wait_limit_s) {
     TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.scalar_type() == at::kFloat,
@@ -607,6 +635,22 @@ void comm_allreduce_f32(const std::vector<int64_t>& ptrs, int64_t rank, int64_t 
     fs2::comm_allreduce_f32(make_peers(ptrs, rank, wait_limit_s), byte_off, out.data_ptr<float>(), n,
                             static_cast<int>(op), static_cast<int>(slot), static_cast<uint32_t>(epoch), blocks,
                             status_dev_ptr(), stream_of(out));
+    g_launches += 1;
+}
+
+void comm_allreduce_inplace(const std::vector<int64_t>& ptrs, int64_t rank, int64_t byte_off, int64_t numel, bool f32,
+                            double scale, int64_t slot_in, int64_t slot_mid, int64_t epoch, int64_t counter_byte_off,
+                            int64_t device, int64_t blocks, double wait_limit_s) {
+    const int64_t per = f32 ? 4 : 8;
+    TORCH_CHECK(byte_off % 16 == 0 && numel % per == 0 && numel > 0, "comm_allreduce_inplace: the bucket must be a "
+                "whole number of 16-byte vectors at a 16-byte aligned offset");
+    TORCH_CHECK(counter_byte_off % 4 == 0 && blocks >= 1 && blocks <= 148, "comm_allreduce_inplace: bad argument");
+    c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+    auto* counter = reinterpret_cast<unsigned int*>(ptrs[static_cast<size_t>(rank)] + counter_byte_off);
+    fs2::comm_allreduce_inplace(make_peers(ptrs, rank, wait_limit_s), byte_off, numel, f32, static_cast<float>(scale),
+                                static_cast<int>(slot_in), static_cast<int>(slot_mid), static_cast<uint32_t>(epoch),
+                                counter, static_cast<int>(blocks), status_dev_ptr(),
+                                at::cuda::getCurrentCUDAStream(static_cast<c10::DeviceIndex>(device)).stream());
     g_launches += 1;
 }
 
@@ -663,7 +707,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("comm_signal", &comm_signal);
     m.def("comm_allgather_segments", &comm_allgather_segments);
     m.def("comm_reducescatter_segments", &comm_reducescatter_segments);
+    m.def("comm_reducescatter_adamw", &comm_reducescatter_adamw);
     m.def("comm_allreduce_f32", &comm_allreduce_f32);
+    m.def("comm_allreduce_inplace", &comm_allreduce_inplace);
     m.def("comm_pull", &comm_pull);
     m.def("comm_alltoall", &comm_alltoall);
     m.def("ngram_repeat_block", &ngram_repeat_block);

@@ -15,6 +15,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <cmath>
 #include <cstdint>
 
 #include "comm.h"
@@ -142,10 +143,52 @@ __global__ void __launch_bounds__(512) allgather_segments_kernel(
 // fp32 accumulate. All W peer loads of RS_UNROLL vectors are issued before the first use.
 constexpr int RS_UNROLL = 2;
 
-template <typename OutT, int W>
+// What happens to a reduced (and scaled) vector of 8 gradients at shard element index j.
+template <typename OutT>
+struct StoreSink {
+    OutT* out;
+    int accumulate;
+    __device__ __forceinline__ void operator()(size_t j, float* acc) const {
+        if (accumulate) {
+            float prev[8];
+            load8(out, j, prev);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] += prev[e];
+        }
+        store8(out, j, acc);
+    }
+};
+
+// AdamW applied to the freshly reduced gradient while it is still in registers: the fp32 gradient shard is never
+// written to (or re-read from) memory.
+struct AdamWSink {
+    float* p;
+    float* m;
+    float* v;
+    __nv_bfloat16* low;   // bf16 copy of the updated parameters (may be null)
+    float lr, beta1, beta2, eps, wd, step_size, bc2_sqrt;
+    __device__ __forceinline__ void operator()(size_t j, float* g) const {
+        float pv[8], mv[8], vv[8];
+        load8(p, j, pv);
+        load8(m, j, mv);
+        load8(v, j, vv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            pv[e] *= (1.f - lr * wd);
+            mv[e] = beta1 * mv[e] + (1.f - beta1) * g[e];
+            vv[e] = beta2 * vv[e] + (1.f - beta2) * g[e] * g[e];
+            pv[e] -= step_size * mv[e] / (sqrtf(vv[e]) / bc2_sqrt + eps);
+        }
+        store8(p, j, pv);
+        store8(m, j, mv);
+        store8(v, j, vv);
+        if (low) store8(low, j, pv);
+    }
+};
+
+template <typename Sink, int W>
 __device__ __forceinline__ void reducescatter_body(const CommPeers& peers, const CommSegments& segs,
-                                                   long long full_byte_off, OutT* __restrict__ out, float scale,
-                                                   int accumulate) {
+                                                   long long full_byte_off, const Sink& sink, float scale) {
     const __nv_bfloat16* srcs[W];
 #pragma unroll
     for (int k = 0; k < W; ++k) {
@@ -183,18 +226,26 @@ __device__ __forceinline__ void reducescatter_body(const CommPeers& peers, const
                     for (int e = 0; e < 8; ++e) acc[e] += f[e];
                 }
                 const size_t j = static_cast<size_t>(off + v * 8);
-                if (accumulate) {
-                    float prev[8];
-                    load8(out, j, prev);
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) acc[e] = acc[e] * scale + prev[e];
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) acc[e] *= scale;
-                }
-                store8(out, j, acc);
+                for (int e = 0; e < 8; ++e) acc[e] *= scale;
+                sink(j, acc);
             }
         }
+    }
+}
+
+template <typename Sink>
+__device__ __forceinline__ void reducescatter_dispatch(const CommPeers& peers, const CommSegments& segs,
+                                                       long long full_byte_off, const Sink& sink, float scale) {
+    switch (peers.world) {
+        case 1: reducescatter_body<Sink, 1>(peers, segs, full_byte_off, sink, scale); break;
+        case 2: reducescatter_body<Sink, 2>(peers, segs, full_byte_off, sink, scale); break;
+        case 3: reducescatter_body<Sink, 3>(peers, segs, full_byte_off, sink, scale); break;
+        case 4: reducescatter_body<Sink, 4>(peers, segs, full_byte_off, sink, scale); break;
+        case 5: reducescatter_body<Sink, 5>(peers, segs, full_byte_off, sink, scale); break;
+        case 6: reducescatter_body<Sink, 6>(peers, segs, full_byte_off, sink, scale); break;
+        case 7: reducescatter_body<Sink, 7>(peers, segs, full_byte_off, sink, scale); break;
+        default: reducescatter_body<Sink, 8>(peers, segs, full_byte_off, sink, scale); break;
     }
 }
 
@@ -203,16 +254,15 @@ __global__ void __launch_bounds__(512) reducescatter_segments_kernel(
     CommPeers peers, CommSegments segs, long long full_byte_off, OutT* __restrict__ out, long long shard_numel,
     float scale, int accumulate, int slot, uint32_t epoch, int* status) {
     if (!signal_and_wait(peers, slot, epoch, true, status, 18)) return;
-    switch (peers.world) {
-        case 1: reducescatter_body<OutT, 1>(peers, segs, full_byte_off, out, scale, accumulate); break;
-        case 2: reducescatter_body<OutT, 2>(peers, segs, full_byte_off, out, scale, accumulate); break;
-        case 3: reducescatter_body<OutT, 3>(peers, segs, full_byte_off, out, scale, accumulate); break;
-        case 4: reducescatter_body<OutT, 4>(peers, segs, full_byte_off, out, scale, accumulate); break;
-        case 5: reducescatter_body<OutT, 5>(peers, segs, full_byte_off, out, scale, accumulate); break;
-        case 6: reducescatter_body<OutT, 6>(peers, segs, full_byte_off, out, scale, accumulate); break;
-        case 7: reducescatter_body<OutT, 7>(peers, segs, full_byte_off, out, scale, accumulate); break;
-        default: reducescatter_body<OutT, 8>(peers, segs, full_byte_off, out, scale, accumulate); break;
-    }
+    reducescatter_dispatch(peers, segs, full_byte_off, StoreSink<OutT>{out, accumulate}, scale);
+}
+
+// Reduce-scatter fused with the optimizer step of the local shard (no gradient clipping between the two).
+__global__ void __launch_bounds__(512) reducescatter_adamw_kernel(CommPeers peers, CommSegments segs,
+                                                                  long long full_byte_off, AdamWSink sink, float scale,
+                                                                  int slot, uint32_t epoch, int* status) {
+    if (!signal_and_wait(peers, slot, epoch, true, status, 24)) return;
+    reducescatter_dispatch(peers, segs, full_byte_off, sink, scale);
 }
 
 // One-shot all-reduce of `numel` fp32 values staged at `byte_off` of every arena.
@@ -236,6 +286,110 @@ __global__ void allreduce_f32_kernel(CommPeers peers, long long byte_off, float*
         }
         if (op == 1) acc /= W;
         out[i] = acc;
+    }
+}
+
+// In-place two-shot all-reduce (+ scale) of a bucket that lives at `byte_off` of every arena.
+//   phase 1: this rank sums slice `rank` of every peer's bucket (fp32 accumulation), scales it and writes it
+//            back into its own bucket;
+//   phase 2: once every peer has published its reduced slice, the other slices are pulled over NVLink.
+// Every element crosses NVLink twice per rank ((W-1)/W in, (W-1)/W out), the minimum for an all-reduce, and the
+// averaging factor of data parallelism is applied on the way instead of by a separate pass over the gradients.
+// `counter` (device memory, zero between launches) detects the last CTA of phase 1.
+template <typename T, int W>
+__device__ __forceinline__ void allreduce_phase1(const CommPeers& peers, long long byte_off, long long chunk,
+                                                 long long numel, float scale) {
+    constexpr int PER = 16 / sizeof(T);
+    const long long beg = peers.rank * chunk;
+    const long long end = beg + chunk < numel ? beg + chunk : numel;
+    const long long nvec = end > beg ? (end - beg) / PER : 0;
+    char* mine = reinterpret_cast<char*>(peers.base[peers.rank]) + byte_off + beg * sizeof(T);
+    for (long long v = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v < nvec;
+         v += static_cast<long long>(gridDim.x) * blockDim.x) {
+        uint4 in[W];
+#pragma unroll
+        for (int r = 0; r < W; ++r) {
+            const int src = (peers.rank + r) % W;     // start on different peers
+            in[r] = ld_peer16(reinterpret_cast<const char*>(peers.base[src]) + byte_off + beg * sizeof(T) + v * 16);
+        }
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll
+        for (int r = 0; r < W; ++r) {
+            if constexpr (sizeof(T) == 2) {
+                float f[8];
+                unpack8(*reinterpret_cast<const bf16x8*>(&in[r]), f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] += f[i];
+            } else {
+                const float* f = reinterpret_cast<const float*>(&in[r]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[i] += f[i];
+            }
+        }
+        uint4 out;
+        if constexpr (sizeof(T) == 2) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] *= scale;
+            bf16x8 pk = pack8(acc);
+            out = *reinterpret_cast<uint4*>(&pk);
+        } else {
+            float* f = reinterpret_cast<float*>(&out);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) f[i] = acc[i] * scale;
+        }
+        st16(mine + v * 16, out);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(512) allreduce_inplace_kernel(CommPeers peers, long long byte_off, long long numel,
+                                                                float scale, int slot_in, int slot_mid,
+                                                                uint32_t epoch, unsigned int* counter, int* status) {
+    if (!signal_and_wait(peers, slot_in, epoch, true, status, 22)) return;
+    constexpr int PER = 16 / sizeof(T);
+    const int W = peers.world;
+    // slices are multiples of one 16-byte vector; `numel` itself is a multiple of PER (host-checked)
+    long long chunk = (numel + W - 1) / W;
+    chunk = (chunk + PER - 1) / PER * PER;
+    switch (W) {
+        case 1: allreduce_phase1<T, 1>(peers, byte_off, chunk, numel, scale); break;
+        case 2: allreduce_phase1<T, 2>(peers, byte_off, chunk, numel, scale); break;
+        case 3: allreduce_phase1<T, 3>(peers, byte_off, chunk, numel, scale); break;
+        case 4: allreduce_phase1<T, 4>(peers, byte_off, chunk, numel, scale); break;
+        case 5: allreduce_phase1<T, 5>(peers, byte_off, chunk, numel, scale); break;
+        case 6: allreduce_phase1<T, 6>(peers, byte_off, chunk, numel, scale); break;
+        case 7: allreduce_phase1<T, 7>(peers, byte_off, chunk, numel, scale); break;
+        default: allreduce_phase1<T, 8>(peers, byte_off, chunk, numel, scale); break;
+    }
+    // the last CTA to finish phase 1 publishes "my slice is reduced" to every peer
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        const unsigned int prev = atomicAdd(counter, 1u);
+        if (prev == gridDim.x - 1) {
+            *counter = 0;
+            __threadfence_system();
+            for (int r = 0; r < W; ++r) {
+                uint32_t* f = reinterpret_cast<uint32_t*>(peers.base[r]) + slot_mid * kCommMaxRanks + peers.rank;
+                st_release_sys(f, epoch);
+            }
+        }
+    }
+    if (!signal_and_wait(peers, slot_mid, epoch, false, status, 23)) return;
+    // phase 2: pull the reduced slices of the peers
+    char* mine = reinterpret_cast<char*>(peers.base[peers.rank]) + byte_off;
+    for (int r = 1; r < W; ++r) {
+        const int src = (peers.rank + r) % W;
+        const long long beg = src * chunk;
+        const long long end = beg + chunk < numel ? beg + chunk : numel;
+        const long long nvec = end > beg ? (end - beg) / PER : 0;
+        const char* from = reinterpret_cast<const char*>(peers.base[src]) + byte_off + beg * sizeof(T);
+        char* to = mine + beg * sizeof(T);
+        for (long long v = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v < nvec;
+             v += static_cast<long long>(gridDim.x) * blockDim.x)
+            st16(to + v * 16, ld_peer16(from + v * 16));
     }
 }
 
@@ -330,6 +484,35 @@ void comm_alltoall(const CommPeers& peers, long long byte_off, void* dst, const 
     dim3 grid(blocks, peers.world);
     alltoall_kernel<<<grid, 512, 0, st>>>(peers, byte_off, static_cast<char*>(dst), send_offs, elem_bytes, slot,
                                           epoch, status);
+}
+
+void comm_reducescatter_adamw(const CommPeers& peers, const CommSegments& segs, long long full_byte_off, float* p,
+                              float* m, float* v, void* low, float scale, float lr, float beta1, float beta2, float eps,
+                              float wd, int step, int slot, uint32_t epoch, int blocks, int* status, cudaStream_t st) {
+    AdamWSink sink{};
+    sink.p = p;
+    sink.m = m;
+    sink.v = v;
+    sink.low = static_cast<__nv_bfloat16*>(low);
+    sink.lr = lr;
+    sink.beta1 = beta1;
+    sink.beta2 = beta2;
+    sink.eps = eps;
+    sink.wd = wd;
+    sink.step_size = lr / (1.f - powf(beta1, static_cast<float>(step)));
+    sink.bc2_sqrt = sqrtf(1.f - powf(beta2, static_cast<float>(step)));
+    reducescatter_adamw_kernel<<<blocks, 512, 0, st>>>(peers, segs, full_byte_off, sink, scale, slot, epoch, status);
+}
+
+void comm_allreduce_inplace(const CommPeers& peers, long long byte_off, long long numel, bool f32, float scale,
+                            int slot_in, int slot_mid, uint32_t epoch, unsigned int* counter, int blocks, int* status,
+                            cudaStream_t st) {
+    if (f32)
+        allreduce_inplace_kernel<float><<<blocks, 512, 0, st>>>(peers, byte_off, numel, scale, slot_in, slot_mid, epoch,
+                                                                counter, status);
+    else
+        allreduce_inplace_kernel<__nv_bfloat16><<<blocks, 512, 0, st>>>(peers, byte_off, numel, scale, slot_in,
+                                                                        slot_mid, epoch, counter, status);
 }
 
 }  // namespace fs2

@@ -39,4 +39,16 @@ void comm_pull(const CommPeers& peers, int src_rank, long long byte_off, void* d
 void comm_alltoall(const CommPeers& peers, long long byte_off, void* dst, const long long* send_offs, int elem_bytes,
                    int slot, uint32_t epoch, int blocks, int* status, cudaStream_t st);
 
+// Reduce-scatter of bf16 gradients fused with the AdamW step of the local fp32 shard (`p`, `m`, `v`: shard-sized
+// fp32; `low`: optional bf16 copy of the updated parameters). `step` is the 1-based step count.
+void comm_reducescatter_adamw(const CommPeers& peers, const CommSegments& segs, long long full_byte_off, float* p,
+                              float* m, float* v, void* low, float scale, float lr, float beta1, float beta2, float eps,
+                              float wd, int step, int slot, uint32_t epoch, int blocks, int* status, cudaStream_t st);
+
+// In-place all-reduce (sum * scale) of `numel` bf16/fp32 elements at `byte_off` of every arena; `counter` is a zeroed
+// device word; at most `blocks` <= number of SMs CTAs.
+void comm_allreduce_inplace(const CommPeers& peers, long long byte_off, long long numel, bool f32, float scale,
+                            int slot_in, int slot_mid, uint32_t epoch, unsigned int* counter, int blocks, int* status,
+                            cudaStream_t st);
+
 }  // namespace fs2

@@ -1,5 +1,5 @@
 """Distributed data parallelism with flat gradient buckets (cf. fairseq2
-``nn/ddp.py:30-152``; worklist row W4).
+``nn/ddp.py:30-152``).
 
 Parameters keep their dtype and stay replicated. Gradients of each bucket live
 in one flat buffer (``param.grad`` are views); as soon as the last gradient of
@@ -8,6 +8,11 @@ stream, so communication overlaps the rest of the backward pass. The 1/size
 factor is not applied here (``normalize_grads`` semantics of the reference's
 custom comm hook, ``nn/ddp.py:141-152``): the caller scales by the global
 number of targets afterwards.
+
+On one NVSwitch box (``comm="symm"``, the default when available) the buckets
+are allocated inside a symmetric arena and reduced IN PLACE by the in-tree
+two-shot all-reduce kernel, which applies the averaging factor while the data
+moves: no staging copy, no library call and no separate scaling pass.
 """
 from __future__ import annotations
 
@@ -23,11 +28,22 @@ from fairseq2_b200.nn.utils.module import broadcast_module
 
 
 class _Bucket:
-    def __init__(self, params: list[torch.nn.Parameter]) -> None:
+    def __init__(self, params: list[torch.nn.Parameter], arena: Any | None = None, index: int = 0) -> None:
         self.params = params
         n = sum(p.numel() for p in params)
         p0 = params[0]
-        self.flat = torch.zeros(n, device=p0.device, dtype=p0.dtype)
+        self.index = index
+        self.numel = n
+        self.byte_off = -1
+        if arena is not None:
+            per = 16 // p0.element_size()
+            padded = (n + per - 1) // per * per              # whole 16-byte vectors
+            self.byte_off, raw = arena.alloc_tensor(padded, p0.dtype)
+            raw.zero_()
+            self.flat = raw[:n]
+            self.padded = padded
+        else:
+            self.flat = torch.zeros(n, device=p0.device, dtype=p0.dtype)
         self.views: list[Tensor] = []
         off = 0
         for p in params:
@@ -38,8 +54,11 @@ class _Bucket:
 
 
 class DDP(Module):
+    #: first flag slot used by the bucket all-reduces (two slots per bucket)
+    SLOT_BASE = 64
+
     def __init__(self, module: Module, gangs: Gangs, *, bucket_bytes: int = 64 * 1024 * 1024,
-                 broadcast_parameters: bool = True, average: bool = True) -> None:
+                 broadcast_parameters: bool = True, average: bool = True, comm: str = "auto") -> None:
         super().__init__()
         self.module = module
         self.gang: Gang = gangs.rdp if gangs.rdp.size > 1 else gangs.dp
@@ -52,23 +71,56 @@ class DDP(Module):
         self.device = dev
         self.comm_stream = torch.cuda.Stream(dev) if dev.type == "cuda" and self.gang.size > 1 else None
         # buckets in reverse registration order ~ order in which gradients become ready
-        self.buckets: list[_Bucket] = []
+        groups: list[list[torch.nn.Parameter]] = []
         cur: list[torch.nn.Parameter] = []
         size = 0
         for p in reversed(params):
             nbytes = p.numel() * p.element_size()
             if cur and (size + nbytes > bucket_bytes or p.dtype != cur[0].dtype):
-                self.buckets.append(_Bucket(cur))
+                groups.append(cur)
                 cur, size = [], 0
             cur.append(p)
             size += nbytes
         if cur:
-            self.buckets.append(_Bucket(cur))
+            groups.append(cur)
+        self.arena = self._maybe_create_arena(groups, comm)
+        self._epoch = 0
+        self._counter_off = -1
+        if self.arena is not None:
+            self._counter_off, c = self.arena.alloc(4 * len(groups), align=16)
+            c.zero_()
+        self.buckets: list[_Bucket] = [_Bucket(g, self.arena, i) for i, g in enumerate(groups)]
+        if self.arena is not None:
+            torch.cuda.synchronize(dev)
+            self.gang.barrier()
         self._bucket_of: dict[int, tuple[_Bucket, int]] = {}
         for b in self.buckets:
             for i, p in enumerate(b.params):
                 self._bucket_of[id(p)] = (b, i)
                 p.register_post_accumulate_grad_hook(self._on_grad)
+
+    def _maybe_create_arena(self, groups: list[list[torch.nn.Parameter]], comm: str) -> Any | None:
+        if comm not in ("auto", "symm", "nccl"):
+            raise ValueError(f"`comm` must be 'auto', 'symm' or 'nccl', but is '{comm}' instead.")
+        from fairseq2_b200.gang import ProcessGroupGang
+
+        usable = (self.device.type == "cuda" and self.gang.size > 1 and self.gang.size <= 8
+                  and isinstance(self.gang, ProcessGroupGang)
+                  and all(g[0].dtype in (torch.float32, torch.bfloat16) for g in groups))
+        if comm == "nccl" or not usable:
+            if comm == "symm":
+                raise RuntimeError("The symmetric-memory all-reduce needs 2 to 8 CUDA ranks of one process group and "
+                                   "fp32/bf16 parameters.")
+            return None
+        try:
+            from fairseq2_b200.parallel.symm import SymmetricArena
+
+            total = sum(sum(p.numel() * p.element_size() for p in g) + 512 for g in groups) + 4096
+            return SymmetricArena(self.gang, total)
+        except Exception:  # noqa: BLE001 - peer access unavailable: fall back to the process group
+            if comm == "symm":
+                raise
+            return None
 
     def forward(self, *a: Any, **kw: Any) -> Any:
         return self.module(*a, **kw)
@@ -85,6 +137,9 @@ class DDP(Module):
     def _reduce(self, b: _Bucket) -> None:
         if self.gang.size == 1:
             return
+        if self.arena is not None:
+            self._reduce_symm(b)
+            return
         op = ReduceOperation.MEAN if self.average else ReduceOperation.SUM
         if self.comm_stream is not None:
             self.comm_stream.wait_stream(torch.cuda.current_stream(self.device))
@@ -92,6 +147,23 @@ class DDP(Module):
                 self.gang.all_reduce(b.flat, op)
         else:
             self.gang.all_reduce(b.flat, op)
+
+    def _reduce_symm(self, b: _Bucket) -> None:
+        a = self.arena
+        assert a is not None and self.comm_stream is not None
+        # every bucket is reduced once per step, in the same order on every rank: the step counter is the epoch
+        epoch = self._step_epoch
+        scale = 1.0 / self.gang.size if self.average else 1.0
+        blocks = max(1, min(64, b.padded * b.flat.element_size() // (512 * 16 * 4)))
+        self.comm_stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(self.comm_stream):
+            a.ext.comm_allreduce_inplace(a.peer_ptrs, a.rank, b.byte_off, b.padded, b.flat.dtype == torch.float32,
+                                         scale, self.SLOT_BASE + 2 * b.index, self.SLOT_BASE + 2 * b.index + 1, epoch,
+                                         self._counter_off + 4 * b.index, a.device_index, blocks, a.wait_limit_s)
+
+    @property
+    def _step_epoch(self) -> int:
+        return self._epoch + 1
 
     def finish_backward(self) -> None:
         for b in self.buckets:
@@ -103,6 +175,8 @@ class DDP(Module):
                         p.grad = b.views[i]
                 self._reduce(b)
             b.pending = len(b.params)
+        if self._require_sync:
+            self._epoch += 1
         if self.comm_stream is not None:
             torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
 

@@ -157,3 +157,93 @@ def test_fused_gemm_reduce_scatter() -> None:
     _need_gpus(2)
     for errs in run_distributed(_gemm_rs_worker, 2):
         assert all(e < 1e-2 for e in errs), errs
+
+
+def _ddp_symm_worker(rank: int, world: int):
+    from fairseq2_b200.gang import ProcessGroupGang, create_parallel_gangs
+    from fairseq2_b200.parallel.ddp import DDP
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    base = ProcessGroupGang.create_default_process_group(dev)
+    gangs = create_parallel_gangs(base)
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(64, 257), torch.nn.ReLU(), torch.nn.Linear(257, 33)).to(dev)
+    ddp = DDP(model, gangs, bucket_bytes=32 * 1024, comm="symm", average=True)
+    assert ddp.arena is not None and len(ddp.buckets) >= 2
+    out = []
+    for step in range(3):
+        gen = torch.Generator().manual_seed(1000 * step + rank)
+        x = torch.randn(16, 64, generator=gen).to(dev)
+        ddp.zero_grad()
+        ddp(x).square().sum().backward()
+        ddp.finish_backward()
+        torch.cuda.synchronize()
+        # oracle: average of the per-rank gradients computed locally from every rank's input
+        ref = [torch.zeros_like(p) for p in model.parameters()]
+        for r in range(world):
+            g2 = torch.Generator().manual_seed(1000 * step + r)
+            xr = torch.randn(16, 64, generator=g2).to(dev)
+            grads = torch.autograd.grad(model(xr).square().sum(), list(model.parameters()))
+            for a, g in zip(ref, grads):
+                a += g / world
+        out.append(max(float((p.grad - a).abs().max() / a.abs().max().clamp(min=1e-6))
+                       for p, a in zip(model.parameters(), ref)))
+    ddp.arena.ext.check_status()
+    base.close()
+    return out
+
+
+def test_ddp_symmetric_allreduce() -> None:
+    _need_gpus(2)
+    for errs in run_distributed(_ddp_symm_worker, 2):
+        assert all(e < 1e-5 for e in errs), errs
+
+
+def _rs_adamw_worker(rank: int, world: int):
+    from fairseq2_b200.gang import ProcessGroupGang
+    from fairseq2_b200.ops.optim import multi_tensor_adamw
+    from fairseq2_b200.parallel.symm import SymmetricArena
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    base = ProcessGroupGang.create_default_process_group(dev)
+    n = 8 * 1024 + 64                       # shard elements (two segments)
+    segs_off, segs_n = [0, 8 * 1024], [8 * 1024, 64]
+    arena = SymmetricArena(base, 2 * world * n + (1 << 16))
+    goff, full = arena.alloc_tensor(world * n, torch.bfloat16)
+    gen = torch.Generator().manual_seed(7 + rank)
+    full.copy_((torch.randn(world * n, generator=gen) * 0.1).to(torch.bfloat16))
+    hp = dict(lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1)
+    torch.manual_seed(3)
+    master0 = torch.randn(n, device=dev)
+    errs = []
+    # unfused: reduce-scatter into an fp32 shard, then the AdamW kernel
+    m1, mm1, vv1 = master0.clone(), torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+    low1 = torch.empty(n, device=dev, dtype=torch.bfloat16)
+    gshard = torch.empty(n, device=dev)
+    arena.ext.comm_reducescatter_segments(arena.peer_ptrs, rank, segs_off, segs_n, goff, gshard, 1.0 / world, False,
+                                          10, 1, 8, 5.0)
+    multi_tensor_adamw([m1], [gshard], [mm1], [vv1], [low1], step=1, **hp)
+    # fused
+    m2, mm2, vv2 = master0.clone(), torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+    low2 = torch.empty(n, device=dev, dtype=torch.bfloat16)
+    arena.ext.comm_reducescatter_adamw(arena.peer_ptrs, rank, segs_off, segs_n, goff, m2, mm2, vv2, low2, 1.0 / world,
+                                       hp["lr"], hp["beta1"], hp["beta2"], hp["eps"], hp["weight_decay"], 1, 11, 1, 8,
+                                       5.0)
+    torch.cuda.synchronize()
+    for a, b in ((m1, m2), (mm1, mm2), (vv1, vv2), (low1.float(), low2.float())):
+        errs.append(float((a - b).abs().max()))
+    arena.barrier(12, 1)
+    torch.cuda.synchronize()
+    arena.ext.check_status()
+    base.close()
+    return errs
+
+
+def test_fused_reduce_scatter_adamw_matches_two_kernels() -> None:
+    _need_gpus(2)
+    for errs in run_distributed(_rs_adamw_worker, 2):
+        assert all(e < 1e-6 for e in errs), errs
