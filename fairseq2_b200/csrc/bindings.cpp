@@ -128,6 +128,39 @@ void gemm_reduce_scatter(const Tensor& a, const Tensor& b, const std::vector<int
     g_launches += 1;
 }
 
+// out[M,N] = A * B^T with one operand assembled from the ranks' row shards inside the kernel. The shards sit at
+// `shard_byte_off` of every arena, the local scratch for the assembled operand at `gathered_byte_off` of this
+// rank's arena, the per-block flags at `flags_byte_off`.
+void gemm_allgather(const std::vector<int64_t>& ptrs, int64_t rank, int64_t shard_byte_off, int64_t rows_per_rank,
+                    const Tensor& other, int64_t gathered_byte_off, int64_t flags_byte_off, int64_t epoch,
+                    bool gather_b, Tensor out, int64_t ncopy) {
+    TORCH_CHECK(other.is_cuda() && is_bf16(other) && other.dim() == 2 && other.is_contiguous() && aligned16(other),
+                "gemm_allgather: the local operand must be a contiguous bf16 CUDA matrix");
+    TORCH_CHECK(out.is_cuda() && is_bf16(out) && out.dim() == 2 && out.is_contiguous() && aligned16(out),
+                "gemm_allgather: `out` must be a contiguous bf16 CUDA matrix");
+    const int64_t world = static_cast<int64_t>(ptrs.size());
+    TORCH_CHECK(world >= 1 && world <= 8 && rank >= 0 && rank < world, "gemm_allgather: bad world/rank");
+    const int64_t K = other.size(1);
+    const int64_t M = gather_b ? other.size(0) : rows_per_rank * world;
+    const int64_t N = gather_b ? rows_per_rank * world : other.size(0);
+    TORCH_CHECK(out.size(0) == M && out.size(1) == N && K % 8 == 0 && N % 8 == 0, "gemm_allgather: shape mismatch");
+    TORCH_CHECK(shard_byte_off % 16 == 0 && gathered_byte_off % 1024 == 0 && flags_byte_off % 4 == 0,
+                "gemm_allgather: unaligned arena offsets");
+    const void* shards[8];
+    for (int64_t r = 0; r < world; ++r) shards[r] = reinterpret_cast<const void*>(ptrs[static_cast<size_t>(r)] + shard_byte_off);
+    const int64_t mine = ptrs[static_cast<size_t>(rank)];
+    check_status();
+    c10::cuda::CUDAGuard guard(other.device());
+    TORCH_CHECK(cudaSetDevice(other.get_device()) == cudaSuccess, "gemm_allgather: cudaSetDevice failed");
+    const char* err = fs2::gemm_allgather_bf16_tcgen05(
+        shards, static_cast<int>(world), static_cast<int>(rank), static_cast<int>(rows_per_rank), other.data_ptr(),
+        reinterpret_cast<void*>(mine + gathered_byte_off), reinterpret_cast<unsigned int*>(mine + flags_byte_off),
+        static_cast<unsigned int>(epoch), gather_b, out.data_ptr(), static_cast<int>(M), static_cast<int>(N),
+        static_cast<int>(K), static_cast<int>(ncopy), status_dev_ptr(), num_sms(other), stream_of(other));
+    TORCH_CHECK(err == nullptr, "gemm_allgather: ", err);
+    g_launches += 1;
+}
+
 // ---------------------------------------------------------------------- norms
 std::tuple<Tensor, Tensor> rms_norm_fwd(const Tensor& x, const Tensor& w, double eps) {
     TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous() && w.is_contiguous(), "rms_norm_fwd: bad input");
@@ -689,6 +722,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.doc() = "fairseq2_b200 sm_100a kernels";
     m.def("gemm_bf16", &gemm_bf16);
     m.def("gemm_reduce_scatter", &gemm_reduce_scatter);
+    m.def("gemm_allgather", &gemm_allgather);
     m.def("rms_norm_fwd", &rms_norm_fwd);
     m.def("rms_norm_bwd", &rms_norm_bwd);
     m.def("layer_norm_fwd", &layer_norm_fwd);

@@ -88,6 +88,24 @@ __device__ __forceinline__ bool epi_bar_or(bool pred) {
 
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("barrier.cta.sync 1, 128;" ::: "memory"); }
 
+// Tile order of the fused all-gather: blocks of the gathered operand are visited in arrival order (own shard,
+// then the peers in ring order) and every block is used for all tiles that need it before moving on.
+template <int GATHER>
+__device__ __forceinline__ void gather_tile_coords(int t, int num_m, int num_n, int rank, int world, int per_rank,
+                                                   int& m_tile, int& n_tile, int& gblock) {
+    if constexpr (GATHER == 1) {
+        const int idx = t / num_n;
+        m_tile = ((rank + idx / per_rank) % world) * per_rank + idx % per_rank;
+        n_tile = t % num_n;
+        gblock = m_tile;
+    } else {
+        const int idx = t / num_m;
+        n_tile = ((rank + idx / per_rank) % world) * per_rank + idx % per_rank;
+        m_tile = t % num_m;
+        gblock = n_tile;
+    }
+}
+
 __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_tile, int& n_tile) {
     const int per_group = GROUP_M * num_n;
     const int g = t / per_group;
@@ -106,14 +124,74 @@ struct PeerOut {
     int rows_per_rank;
 };
 
+// Arguments of the fused all-gather: the gathered operand (A when GATHER == 1, B when GATHER == 2) is assembled in
+// `dst` from the `world` row shards `src[r]` (peer mappings) by the first `ncopy` CTAs of the grid while the other
+// CTAs compute. `flags[b]` reaches `epoch` once block b (BM rows of A / BN rows of B) has landed.
+struct GatherArgs {
+    const void* src[8];
+    void* dst;
+    unsigned int* flags;
+    unsigned int epoch;
+    int ncopy;
+    int rows_per_rank;
+    int rank;
+    int world;
+    long long row_bytes;
+};
+
 // PEER_RED: instead of storing C locally, every fp32 tile is reduced (red.global.add) straight into the memory of
 // the rank that owns its rows, so a row-parallel GEMM and the reduce-scatter that follows it are one kernel and the
 // NVLink traffic of tile i overlaps the tensor-core work of tile i + 1.
-template <bool A_MN, bool B_MN, bool OUT_F32, bool PEER_RED = false>
+//
+// GATHER: all-gather of one operand fused into the GEMM. Copier CTAs pull the peers' shards over NVLink exactly
+// once into local memory, block by block in the order in which the compute CTAs consume them (own shard first),
+// and publish a flag per block; a compute CTA's TMA producer waits for the flag of the block its tile needs, so
+// the GEMM starts on local data immediately and the remaining transfers hide behind tensor-core work.
+template <bool A_MN, bool B_MN, bool OUT_F32, bool PEER_RED = false, int GATHER = 0>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
             const __grid_constant__ CUtensorMap tma_c, int M, int N, int K, int accumulate, int* status,
-            const PeerOut po) {
+            const PeerOut po, const GatherArgs ga) {
+    constexpr int GBLK = GATHER == 2 ? BN : BM;          // rows of the gathered operand per flag
+    if constexpr (GATHER != 0) {
+        if (static_cast<int>(blockIdx.x) < ga.ncopy) {
+            const int per_rank = ga.rows_per_rank / GBLK;
+            const int total = per_rank * ga.world;
+            const long long blk_bytes = static_cast<long long>(GBLK) * ga.row_bytes;
+            for (int i = blockIdx.x; i < total; i += ga.ncopy) {
+                const int src_rank = (ga.rank + i / per_rank) % ga.world;
+                const int bi = i % per_rank;
+                const int gblock = src_rank * per_rank + bi;
+                const char* from = static_cast<const char*>(ga.src[src_rank]) + bi * blk_bytes;
+                char* to = static_cast<char*>(ga.dst) + gblock * blk_bytes;
+                const long long nvec = blk_bytes / 16;
+                for (long long v0 = threadIdx.x; v0 < nvec; v0 += NUM_THREADS * 4) {
+                    uint4 buf[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const long long v = v0 + u * NUM_THREADS;
+                        if (v < nvec)
+                            asm volatile("ld.relaxed.sys.global.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                         : "=r"(buf[u].x), "=r"(buf[u].y), "=r"(buf[u].z), "=r"(buf[u].w)
+                                         : "l"(from + v * 16) : "memory");
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const long long v = v0 + u * NUM_THREADS;
+                        if (v < nvec) *reinterpret_cast<uint4*>(to + v * 16) = buf[u];
+                    }
+                }
+                __threadfence();
+                __syncthreads();
+                if (threadIdx.x == 0)
+                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(ga.flags + gblock), "r"(ga.epoch) : "memory");
+            }
+            return;
+        }
+    }
+    const int ncopy = GATHER != 0 ? ga.ncopy : 0;
+    const int first_tile = static_cast<int>(blockIdx.x) - ncopy;
+    const int tile_stride = static_cast<int>(gridDim.x) - ncopy;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -168,9 +246,30 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            for (int t = first_tile; t < num_tiles && ok; t += tile_stride) {
                 int mt, nt;
-                tile_coords(t, num_m, num_n, mt, nt);
+                if constexpr (GATHER != 0) {
+                    int gblock;
+                    gather_tile_coords<GATHER>(t, num_m, num_n, ga.rank, ga.world, ga.rows_per_rank / GBLK, mt, nt, gblock);
+                    // wait until the copier CTAs have landed this block of the gathered operand
+                    const uint64_t t0 = global_timer_ns();
+                    uint32_t seen, spins = 0;
+                    while (true) {
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(ga.flags + gblock) : "memory");
+                        if (static_cast<int32_t>(seen - ga.epoch) >= 0) break;
+                        if ((++spins & 63u) == 0 && (*abort_flag || global_timer_ns() - t0 > WAIT_LIMIT_NS)) {
+                            if (!*abort_flag) report_status(status, kStatusTimeout | (5 << 8));
+                            *abort_flag = 1;
+                            ok = false;
+                            break;
+                        }
+                    }
+                    if (!ok) break;
+                    fence_proxy_async_smem();
+                    asm volatile("fence.proxy.async.global;" ::: "memory");   // generic-proxy copies -> TMA reads
+                } else {
+                    tile_coords(t, num_m, num_n, mt, nt);
+                }
                 const int m0 = mt * BM, n0 = nt * BN;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
@@ -212,7 +311,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            for (int t = first_tile; t < num_tiles && ok; t += tile_stride) {
                 if (!mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
                     if (!*abort_flag) report_status(status, kStatusTimeout | (2 << 8));
                     *abort_flag = 1;
@@ -261,9 +360,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         int acc = 0;
         uint32_t acc_phase = 0;
         int buf = 0;
-        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        for (int t = first_tile; t < num_tiles; t += tile_stride) {
             int mt, nt;
-            tile_coords(t, num_m, num_n, mt, nt);
+            if constexpr (GATHER != 0) {
+                int gblock;
+                gather_tile_coords<GATHER>(t, num_m, num_n, ga.rank, ga.world, ga.rows_per_rank / GBLK, mt, nt, gblock);
+            } else {
+                tile_coords(t, num_m, num_n, mt, nt);
+            }
             const int m0 = mt * BM, n0 = nt * BN;
             const bool got = mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS);
             if (epi_bar_or(!got)) {
@@ -424,7 +528,7 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
     }
     const int num_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int grid = num_tiles < num_sms ? num_tiles : num_sms;
-    kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tc, M, N, K, accumulate, status, PeerOut{});
+    kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tc, M, N, K, accumulate, status, PeerOut{}, GatherArgs{});
     return cudaGetLastError();
 }
 
@@ -454,6 +558,63 @@ const char* gemm_bf16_tcgen05(const void* a, const void* b, void* c, int M, int 
     return nullptr;
 }
 
+// C[M,N] (bf16) = A * B^T where one operand is the concatenation of `world` row shards that live on the peers.
+// gather_b = false: A = concat_r a_shards[r] ([rows_per_rank, K] each), B = `other` [N, K] is local;
+// gather_b = true : B = concat_r b_shards[r], A = `other` [M, K] is local.
+// `gathered` is local scratch for the assembled operand, `flags` one zero-initialised word per block.
+const char* gemm_allgather_bf16_tcgen05(const void* const* shards, int world, int rank, int rows_per_rank,
+                                        const void* other, void* gathered, unsigned int* flags, unsigned int epoch,
+                                        bool gather_b, void* c, int M, int N, int K, int ncopy, int* status,
+                                        int num_sms, cudaStream_t stream) {
+    if (world < 1 || world > 8) return "gemm_allgather: between 1 and 8 ranks are supported";
+    const int blk = gather_b ? BN : BM;
+    if (rows_per_rank % blk) return "gemm_allgather: the shard height must be a multiple of the tile height";
+    if ((gather_b ? N : M) != rows_per_rank * world) return "gemm_allgather: shards do not add up to the operand";
+    CUtensorMap ta, tb, tc;
+    g_tmap_err[0] = 0;
+    if (!make_tmap(&ta, gather_b ? other : gathered, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, BM, BK) ||
+        !make_tmap(&tb, gather_b ? gathered : other, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, BN, BK) ||
+        !make_tmap(&tc, c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, 128, 64))
+        return g_tmap_err;
+    GatherArgs ga{};
+    for (int r = 0; r < world; ++r) ga.src[r] = shards[r];
+    ga.dst = gathered;
+    ga.flags = flags;
+    ga.epoch = epoch;
+    ga.rows_per_rank = rows_per_rank;
+    ga.rank = rank;
+    ga.world = world;
+    ga.row_bytes = static_cast<long long>(K) * 2;
+    const int num_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    if (ncopy < 1) ncopy = 1;
+    if (ncopy > num_sms / 4) ncopy = num_sms / 4;
+    ga.ncopy = ncopy;
+    int grid = num_tiles + ncopy;
+    if (grid > num_sms) grid = num_sms;            // every CTA must be resident: compute CTAs wait on copier CTAs
+    cudaError_t e;
+    if (!gather_b) {
+        auto kern = gemm_kernel<false, false, false, false, 1>;
+        static bool configured = false;
+        if (!configured) {
+            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+            if (e != cudaSuccess) return cudaGetErrorString(e);
+            configured = true;
+        }
+        kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tc, M, N, K, 0, status, PeerOut{}, ga);
+    } else {
+        auto kern = gemm_kernel<false, false, false, false, 2>;
+        static bool configured = false;
+        if (!configured) {
+            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+            if (e != cudaSuccess) return cudaGetErrorString(e);
+            configured = true;
+        }
+        kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tc, M, N, K, 0, status, PeerOut{}, ga);
+    }
+    e = cudaGetLastError();
+    return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+}
+
 const char* gemm_reduce_scatter_bf16_tcgen05(const void* a, const void* b, float* const* peer_out, int world,
                                              int rows_per_rank, int M, int N, int K, int* status, int num_sms,
                                              cudaStream_t stream) {
@@ -477,7 +638,7 @@ const char* gemm_reduce_scatter_bf16_tcgen05(const void* a, const void* b, float
     }
     const int num_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int grid = num_tiles < num_sms ? num_tiles : num_sms;
-    kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, ta, M, N, K, 0, status, po);
+    kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, ta, M, N, K, 0, status, po, GatherArgs{});
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }

@@ -59,3 +59,56 @@ class FusedGemmReduceScatter:
         self._epoch += 1
         arena.barrier(self.SLOT, self._epoch)   # all ranks' additions have landed (and their next slots are zero)
         return buf[: rows * N].view(rows, N)
+
+
+class FusedAllGatherGemm:
+    """All-gather of one GEMM operand fused into the tcgen05 GEMM.
+
+    ``gather="a"`` is the column-parallel linear layer with a sequence-parallel input: every rank holds
+    ``[M / W, K]`` rows of the activations and ``[N_local, K]`` of the weight; ``gather="b"`` is the FSDP
+    unshard: every rank holds ``[N / W, K]`` rows of the weight and all of the activations.
+
+    A few CTAs of the GEMM grid copy the peers' shards over NVLink into local memory -- each byte crosses once,
+    own shard first, then the peers in ring order -- and raise one flag per tile-height block; the TMA producers
+    of the compute CTAs wait for the flag of the block they need. The GEMM therefore starts at once on local data
+    and the remaining transfers overlap tensor-core work inside the same kernel.
+
+    Usage: write the local shard into ``self.shard`` (a view into the symmetric arena), then call the operator.
+    """
+
+    SLOT = 42
+
+    def __init__(self, arena: SymmetricArena, rows_per_rank: int, k: int, *, gather: str = "a",
+                 num_copy_ctas: int = 8) -> None:
+        if gather not in ("a", "b"):
+            raise ValueError("`gather` must be 'a' or 'b'.")
+        blk = 256 if gather == "b" else 128
+        if rows_per_rank % blk:
+            raise ValueError(f"`rows_per_rank` must be a multiple of {blk} for gather='{gather}'.")
+        self.arena, self.rows, self.k, self.gather_b = arena, rows_per_rank, k, gather == "b"
+        self.ncopy = num_copy_ctas
+        self._shard_off, self.shard = arena.alloc_tensor(rows_per_rank * k, torch.bfloat16)
+        self.shard = self.shard.view(rows_per_rank, k)
+        self._gathered_off, _ = arena.alloc(arena.world * rows_per_rank * k * 2, align=1024)
+        nblocks = arena.world * rows_per_rank // blk
+        self._flags_off, flags = arena.alloc(4 * nblocks, align=16)
+        flags.zero_()
+        self._epoch = 0
+        self._bar_epoch = 0
+
+    def __call__(self, other: Tensor, out: Tensor | None = None) -> Tensor:
+        a = self.arena
+        W = a.world
+        if self.gather_b:
+            M, N = other.shape[0], self.rows * W
+        else:
+            M, N = self.rows * W, other.shape[0]
+        if out is None:
+            out = torch.empty((M, N), device=other.device, dtype=torch.bfloat16)
+        # every rank has written its shard (and finished reading the shards of the previous call)
+        self._bar_epoch += 1
+        a.barrier(self.SLOT, self._bar_epoch)
+        self._epoch += 1
+        a.ext.gemm_allgather(a.peer_ptrs, a.rank, self._shard_off, self.rows, other.contiguous(), self._gathered_off,
+                             self._flags_off, self._epoch, self.gather_b, out, self.ncopy)
+        return out

@@ -247,3 +247,38 @@ def test_fused_reduce_scatter_adamw_matches_two_kernels() -> None:
     _need_gpus(2)
     for errs in run_distributed(_rs_adamw_worker, 2):
         assert all(e < 1e-6 for e in errs), errs
+
+
+def _ag_gemm_worker(rank: int, world: int):
+    from fairseq2_b200.gang import ProcessGroupGang
+    from fairseq2_b200.ops.fused_collective import FusedAllGatherGemm
+    from fairseq2_b200.parallel.symm import SymmetricArena
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    base = ProcessGroupGang.create_default_process_group(dev)
+    arena = SymmetricArena(base, 64 << 20)
+    errs = []
+    for gather, rows, other_rows, K in (("a", 512, 768, 1024), ("b", 512, 640, 1024)):
+        op = FusedAllGatherGemm(arena, rows, K, gather=gather, num_copy_ctas=4)
+        for it in range(2):
+            gen = torch.Generator().manual_seed(50 + it)
+            shards = [(torch.randn(rows, K, generator=gen) * 0.5).to(torch.bfloat16) for _ in range(world)]
+            other = (torch.randn(other_rows, K, generator=gen) * 0.1).to(torch.bfloat16)
+            op.shard.copy_(shards[rank])
+            out = op(other.to(dev))
+            full = torch.cat(shards).float().to(dev)
+            ref = other.float().to(dev) @ full.t() if gather == "b" else full @ other.float().to(dev).t()
+            errs.append(float((out.float() - ref).norm() / ref.norm()))
+    arena.barrier(13, 1)
+    torch.cuda.synchronize()
+    arena.ext.check_status()
+    base.close()
+    return errs
+
+
+def test_fused_allgather_gemm() -> None:
+    _need_gpus(2)
+    for errs in run_distributed(_ag_gemm_worker, 2):
+        assert all(e < 1e-2 for e in errs), errs
