@@ -14,6 +14,8 @@ reductions sum/mean).
 """
 from __future__ import annotations
 
+from typing import Any
+
 import torch
 import torch.nn.functional as F
 from torch import Tensor
@@ -116,3 +118,87 @@ def fused_linear_cross_entropy(h: Tensor, weight: Tensor, targets: Tensor, *, ta
         return loss
     logits = F.linear(h2, weight)
     return cross_entropy_reference(logits, t, pad_idx, target_mask=m, reduction=reduction)
+
+
+class _VocabParallelLinearCE(torch.autograd.Function):
+    """Output projection + cross entropy with the vocabulary split over a tensor-parallel gang.
+
+    Per chunk of rows every rank computes its ``[rows, V/W]`` slice of the logits and three per-row scalars -- the
+    local maximum, the local sum of exponentials and the target logit if the target falls into its slice -- which
+    are combined with one MAX and one SUM all-reduce of ``[rows]`` / ``[rows, 2]`` values. Neither the full logits
+    nor the full vocabulary ever exist on one rank; gradients are produced in the same pass and scaled by the
+    upstream gradient in backward (``dh`` is summed over the gang there, since every rank holds a partial)."""
+
+    @staticmethod
+    def forward(ctx, h: Tensor, weight: Tensor, targets: Tensor, mask: Tensor | None, pad_idx: int, chunk: int,
+                gang: Any) -> Tensor:  # type: ignore[override]
+        from fairseq2_b200.gang import ReduceOperation
+
+        T, D = h.shape
+        Vl = weight.shape[0]
+        lo = gang.rank * Vl
+        loss = torch.zeros((), dtype=torch.float32, device=h.device)
+        need_dh, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        dh = torch.empty_like(h) if need_dh else None
+        dw = torch.zeros((Vl, D), dtype=torch.float32, device=h.device) if need_dw else None
+        for s in range(0, T, chunk):
+            e = min(s + chunk, T)
+            hc, tc = h[s:e], targets[s:e]
+            logits = gemm(hc, weight, out_dtype=torch.float32) if hc.is_cuda else hc.float() @ weight.float().t()
+            logits = logits.float()
+            row_w = torch.ones(e - s, device=h.device) if mask is None else mask[s:e].float()
+            if pad_idx >= 0:
+                row_w = row_w * (tc != pad_idx)
+            mx = logits.max(dim=1).values
+            gang.all_reduce(mx, ReduceOperation.MAX)
+            ex = torch.exp(logits - mx.unsqueeze(1))
+            local = (tc >= lo) & (tc < lo + Vl)
+            idx = (tc - lo).clamp(0, Vl - 1)
+            stats = torch.stack([ex.sum(dim=1), torch.where(local, logits.gather(1, idx.unsqueeze(1)).squeeze(1),
+                                                            torch.zeros_like(mx))], dim=1)
+            gang.all_reduce(stats, ReduceOperation.SUM)
+            loss += ((torch.log(stats[:, 0]) + mx - stats[:, 1]) * row_w).sum()
+            if need_dh or need_dw:
+                p = ex / stats[:, :1]
+                p[torch.arange(e - s, device=h.device)[local], idx[local]] -= 1.0
+                g = (p * row_w.unsqueeze(1)).to(h.dtype)
+                if need_dh:
+                    dh[s:e] = gemm(g, weight, b_mn=True) if g.is_cuda and g.dtype == torch.bfloat16 else \
+                        (g.float() @ weight.float()).to(h.dtype)
+                if need_dw:
+                    dw += g.float().t() @ hc.float()
+        ctx.save_for_backward(dh, dw)
+        ctx.gang, ctx.wdtype = gang, weight.dtype
+        return loss
+
+    @staticmethod
+    def backward(ctx, g: Tensor):  # type: ignore[override]
+        from fairseq2_b200.gang import ReduceOperation
+
+        dh, dw = ctx.saved_tensors
+        gdh = gdw = None
+        if dh is not None:
+            gdh = dh.mul_(g.to(dh.dtype))
+            ctx.gang.all_reduce(gdh, ReduceOperation.SUM)     # every rank contributed its vocabulary slice
+        if dw is not None:
+            gdw = (dw * g).to(ctx.wdtype)
+        return gdh, gdw, None, None, None, None, None
+
+
+def vocab_parallel_linear_cross_entropy(h: Tensor, weight_shard: Tensor, targets: Tensor, gang: Any, *,
+                                        target_mask: Tensor | None = None, pad_idx: int | None = None,
+                                        reduction: str = "sum", chunk_size: int = 4096) -> Tensor:
+    """``cross_entropy(h @ concat_r(weight_shard_r)ᵀ, targets)`` where rank ``r`` of ``gang`` holds rows
+    ``[r·V/W, (r+1)·V/W)`` of the output projection. Returns the same fp32 scalar on every rank."""
+    h2 = h.reshape(-1, h.shape[-1]).contiguous()
+    t = targets.reshape(-1).contiguous()
+    m = target_mask.reshape(-1).float() if target_mask is not None else None
+    loss = _VocabParallelLinearCE.apply(h2, weight_shard, t, m, -100 if pad_idx is None else pad_idx, chunk_size,
+                                        gang)
+    if reduction == "mean":
+        denom = m.sum() if m is not None else ((t != pad_idx).sum() if pad_idx is not None
+                                               else torch.tensor(float(t.numel()), device=h.device))
+        loss = loss / denom.clamp(min=1)
+    elif reduction != "sum":
+        raise ValueError(f"`reduction` must be 'sum' or 'mean', but is '{reduction}' instead.")
+    return loss
