@@ -18,6 +18,7 @@
 #include "elementwise.h"
 #include "gemm_tcgen05.h"
 #include "generation.h"
+#include "moe.h"
 
 namespace {
 
@@ -283,6 +284,71 @@ void rope_inplace(Tensor x, const Tensor& freqs, const Tensor& pos, bool inverse
                       static_cast<int>(x.size(1)), D, static_cast<size_t>(x.stride(0)),
                       static_cast<size_t>(x.stride(1)), static_cast<int>(freqs.size(0)), inverse, num_sms(x),
                       stream_of(x));
+    g_launches += 1;
+}
+
+// ------------------------------------------------------------------------ MoE
+// logits [T, E] -> (expert_ids [T, k] int32, gates [T, k] fp32, counts [E] int32, prob_sum [E] fp32 or empty)
+std::tuple<Tensor, Tensor, Tensor, Tensor> moe_route(const Tensor& logits, int64_t k, bool softmax_gate,
+                                                     bool with_prob_sum) {
+    TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.is_contiguous() &&
+                    (is_bf16(logits) || logits.scalar_type() == at::kFloat),
+                "moe_route: logits must be a contiguous bf16/fp32 [T, E] CUDA tensor");
+    const int64_t T = logits.size(0), E = logits.size(1);
+    TORCH_CHECK(E >= 1 && E <= 256 && k >= 1 && k <= 8 && k <= E, "moe_route: up to 256 experts and top-8 are supported");
+    c10::cuda::CUDAGuard guard(logits.device());
+    auto iopt = logits.options().dtype(at::kInt);
+    auto fopt = logits.options().dtype(at::kFloat);
+    Tensor ids = at::empty({T, k}, iopt), gates = at::empty({T, k}, fopt), counts = at::zeros({E}, iopt);
+    Tensor prob_sum = with_prob_sum ? at::zeros({E}, fopt) : at::empty({0}, fopt);
+    fs2::moe_route(logits.data_ptr(), is_bf16(logits), static_cast<int>(T), static_cast<int>(E), static_cast<int>(k),
+                   softmax_gate, ids.data_ptr<int>(), gates.data_ptr<float>(), counts.data_ptr<int>(),
+                   with_prob_sum ? prob_sum.data_ptr<float>() : nullptr, stream_of(logits));
+    g_launches += 1;
+    return {ids, gates, counts, prob_sum};
+}
+
+// x [T, D] bf16 -> (routed [T*k, D] bf16 in expert order, src_row [T*k] int32, inv [T, k] int32, offsets [E+1] int32)
+std::tuple<Tensor, Tensor, Tensor, Tensor> moe_dispatch(const Tensor& x, const Tensor& expert_ids, const Tensor& gates,
+                                                        const Tensor& counts, bool scale_by_gate) {
+    TORCH_CHECK(x.is_cuda() && is_bf16(x) && x.dim() == 2 && x.is_contiguous() && x.size(1) % 8 == 0 && aligned16(x),
+                "moe_dispatch: x must be a contiguous bf16 [T, D] CUDA tensor with D % 8 == 0");
+    TORCH_CHECK(expert_ids.scalar_type() == at::kInt && expert_ids.is_contiguous() && expert_ids.dim() == 2 &&
+                    expert_ids.size(0) == x.size(0) && gates.scalar_type() == at::kFloat && gates.is_contiguous() &&
+                    gates.sizes() == expert_ids.sizes() && counts.scalar_type() == at::kInt && counts.is_contiguous(),
+                "moe_dispatch: bad routing tensors");
+    const int64_t T = x.size(0), D = x.size(1), k = expert_ids.size(1), E = counts.numel();
+    c10::cuda::CUDAGuard guard(x.device());
+    auto iopt = x.options().dtype(at::kInt);
+    Tensor offsets = at::empty({E + 1}, iopt), cursor = at::empty({E}, iopt);
+    Tensor routed = at::empty({T * k, D}, x.options()), src_row = at::empty({T * k}, iopt), inv = at::empty({T, k}, iopt);
+    fs2::moe_offsets(counts.data_ptr<int>(), offsets.data_ptr<int>(), cursor.data_ptr<int>(), static_cast<int>(E),
+                     stream_of(x));
+    fs2::moe_dispatch(x.data_ptr(), expert_ids.data_ptr<int>(), gates.data_ptr<float>(), offsets.data_ptr<int>(),
+                      cursor.data_ptr<int>(), routed.data_ptr(), src_row.data_ptr<int>(), inv.data_ptr<int>(),
+                      static_cast<int>(T), static_cast<int>(k), static_cast<int>(D), scale_by_gate, stream_of(x));
+    g_launches += 2;
+    return {routed, src_row, inv, offsets};
+}
+
+// y[t] (+)= sum_j gate[t, j] * routed[inv[t, j]]
+void moe_combine(const Tensor& routed, const Tensor& inv, const std::optional<Tensor>& gates, Tensor y,
+                 bool accumulate) {
+    TORCH_CHECK(routed.is_cuda() && is_bf16(routed) && routed.dim() == 2 && routed.is_contiguous() && is_bf16(y) &&
+                    y.is_contiguous() && y.dim() == 2 && y.size(1) == routed.size(1) && y.size(1) % 8 == 0 &&
+                    aligned16(routed) && aligned16(y),
+                "moe_combine: routed/y must be contiguous bf16 matrices with D % 8 == 0");
+    TORCH_CHECK(inv.scalar_type() == at::kInt && inv.is_contiguous() && inv.dim() == 2 && inv.size(0) == y.size(0),
+                "moe_combine: inv must be int32 [T, k]");
+    const float* gp = nullptr;
+    if (gates.has_value()) {
+        TORCH_CHECK(gates->scalar_type() == at::kFloat && gates->is_contiguous() && gates->sizes() == inv.sizes(),
+                    "moe_combine: gates must be fp32 [T, k]");
+        gp = gates->data_ptr<float>();
+    }
+    c10::cuda::CUDAGuard guard(y.device());
+    fs2::moe_combine(routed.data_ptr(), inv.data_ptr<int>(), gp, y.data_ptr(), static_cast<int>(y.size(0)),
+                     static_cast<int>(inv.size(1)), static_cast<int>(y.size(1)), accumulate, stream_of(y));
     g_launches += 1;
 }
 
@@ -746,6 +812,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("comm_allreduce_inplace", &comm_allreduce_inplace);
     m.def("comm_pull", &comm_pull);
     m.def("comm_alltoall", &comm_alltoall);
+    m.def("moe_route", &moe_route);
+    m.def("moe_dispatch", &moe_dispatch);
+    m.def("moe_combine", &moe_combine);
     m.def("ngram_repeat_block", &ngram_repeat_block);
     m.def("sample_top_p_top_k", &sample_top_p_top_k);
     m.def("beam_topk", &beam_topk);

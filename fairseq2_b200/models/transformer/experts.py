@@ -143,6 +143,18 @@ class MoE(FeedForwardNetwork):
     def forward(self, seqs: Tensor) -> Tensor:
         x = seqs.reshape(-1, self.model_dim)
         logits = x @ self.router
+        from fairseq2_b200.ops import moe as moe_ops
+
+        if moe_ops.moe_kernels_available(x, logits):
+            # fused top-k gate + histogram, gather/scale into expert order, experts, gather back per token
+            ids, gates, counts = moe_ops.moe_route(logits, self.top_k)
+            routed_in, src_row, inv = moe_ops.moe_dispatch(x, gates, ids, counts)
+            routed_out = self.experts(routed_in, counts.tolist())
+            base = self.shared_expert(x) if self.shared_expert is not None else None
+            out = moe_ops.moe_combine(routed_out, inv, src_row, base)
+            if self.tp_gang is not None:
+                out = reduce(out, self.tp_gang)
+            return out.view(seqs.shape)
         token_idx, scores, _, sizes = route_tokens(logits, self.top_k)
         routed_in = x.index_select(0, token_idx) * scores.to(x.dtype).unsqueeze(1)
         routed_out = self.experts(routed_in, sizes)

@@ -8,6 +8,8 @@ from __future__ import annotations
 
 import importlib.util
 import os
+from contextlib import contextmanager
+from typing import Iterator
 import sys
 from pathlib import Path
 from types import ModuleType
@@ -69,13 +71,28 @@ def require_ext() -> ModuleType:
             f"{ex}") from ex
 
 
+_kernels_on = True
+
+
+@contextmanager
+def kernels_enabled(value: bool) -> Iterator[None]:
+    """Temporarily routes CUDA tensors through the PyTorch formulations (``value=False``); used by tests that
+    compare a kernel path with its oracle on the same device."""
+    global _kernels_on
+    old, _kernels_on = _kernels_on, value
+    try:
+        yield
+    finally:
+        _kernels_on = old
+
+
 def use_kernels(*tensors: object) -> bool:
     """True when the op must run on the native kernels (any CUDA tensor input)."""
     import torch
 
     for t in tensors:
         if isinstance(t, torch.Tensor) and t.is_cuda:
-            if os.environ.get("FAIRSEQ2_B200_FORCE_TORCH") == "1":
+            if not _kernels_on or os.environ.get("FAIRSEQ2_B200_FORCE_TORCH") == "1":
                 return False
             return True
     return False

@@ -38,8 +38,7 @@ class FusedGemmReduceScatter:
         for _, buf in self._slots:
             buf.zero_()
         # every rank's slots are zero before anyone adds into them
-        self._epoch += 1
-        arena.barrier(self.SLOT, self._epoch)
+        arena.barrier_next(self.SLOT)
 
     def __call__(self, x: Tensor, weight: Tensor) -> Tensor:
         """``x``: bf16 ``[M, K_local]``, ``weight``: bf16 ``[N, K_local]`` -> fp32 ``[M / world, N]`` (a view into
@@ -56,8 +55,7 @@ class FusedGemmReduceScatter:
         self._which ^= 1
         arena.ext.gemm_reduce_scatter(x.contiguous(), weight.contiguous(), arena.peer_ptrs, off, rows)
         nxt.zero_()                       # the other slot is free again: its last reader ran before this call
-        self._epoch += 1
-        arena.barrier(self.SLOT, self._epoch)   # all ranks' additions have landed (and their next slots are zero)
+        arena.barrier_next(self.SLOT)     # all ranks' additions have landed (and their next slots are zero)
         return buf[: rows * N].view(rows, N)
 
 
@@ -106,9 +104,10 @@ class FusedAllGatherGemm:
         if out is None:
             out = torch.empty((M, N), device=other.device, dtype=torch.bfloat16)
         # every rank has written its shard (and finished reading the shards of the previous call)
-        self._bar_epoch += 1
-        a.barrier(self.SLOT, self._bar_epoch)
+        a.barrier_next(self.SLOT)
         self._epoch += 1
         a.ext.gemm_allgather(a.peer_ptrs, a.rank, self._shard_off, self.rows, other.contiguous(), self._gathered_off,
                              self._flags_off, self._epoch, self.gather_b, out, self.ncopy)
+        # nobody may overwrite its shard for the next call while a slower peer is still copying it
+        a.barrier_next(self.SLOT)
         return out

@@ -100,6 +100,13 @@ class SymmetricArena:
     def signal(self, slot: int, epoch: int) -> None:
         self.ext.comm_signal(self.peer_ptrs, self.rank, slot, epoch, self.device_index)
 
+    def barrier_next(self, slot: int) -> None:
+        """Barrier on ``slot`` with the arena-wide next epoch of that slot, so that several operators may share
+        a slot (epochs only grow; a repeated epoch would let a barrier pass without synchronising)."""
+        epochs = self.__dict__.setdefault("_slot_epochs", {})
+        epochs[slot] = epochs.get(slot, 0) + 1
+        self.barrier(slot, epochs[slot])
+
     def next_generic_epoch(self) -> int:
         self._generic_epoch += 1
         return self._generic_epoch

@@ -370,3 +370,39 @@ def test_beam_topk_kernel(beams: int, V: int, k: int) -> None:
     s, i = beam_topk(lp, sc, k)
     rs, ri = beam_topk_reference(lp, sc, k)
     assert torch.allclose(s, rs) and torch.equal(i, ri)
+
+
+# ------------------------------------------------------------------------- MoE kernels
+@pytest.mark.gpu
+@pytest.mark.parametrize("E,k,softmax", [(16, 1, False), (128, 2, True), (8, 2, False)])
+def test_moe_route_kernel(E: int, k: int, softmax: bool) -> None:
+    from fairseq2_b200.ops.moe import moe_route, moe_route_reference
+
+    torch.manual_seed(0)
+    logits = torch.randn(777, E, device="cuda", dtype=torch.bfloat16)
+    ids, gates, counts = moe_route(logits, k, softmax)
+    rids, rgates, rcounts = moe_route_reference(logits, k, softmax)
+    assert torch.equal(ids.long(), rids) and torch.equal(counts.long(), rcounts)
+    assert torch.allclose(gates, rgates, atol=1e-5)
+
+
+@pytest.mark.gpu
+def test_moe_layer_kernels_match_reference_path() -> None:
+    """The fused dispatch/combine path against the index_select/index_add formulation, forward and backward."""
+    from fairseq2_b200.models.transformer.experts import MoE
+    from fairseq2_b200.ops import _ext
+
+    torch.manual_seed(0)
+    moe = MoE(256, 512, True, 8, 1.0, 2, inner_dim_scale=1.0).to("cuda", torch.bfloat16)
+    x = torch.randn(300, 256, device="cuda", dtype=torch.bfloat16)
+    outs = []
+    for kernels in (True, False):
+        xi = x.clone().requires_grad_(True)
+        moe.zero_grad()
+        with _ext.kernels_enabled(kernels):
+            y = moe(xi)
+            (y.float() ** 2).sum().backward()
+        outs.append((y.detach().float(), xi.grad.float(), moe.router.grad.float().clone(),
+                     moe.experts.gate_proj.grad.float().clone()))
+    for a, b in zip(*outs):
+        assert float((a - b).norm() / b.norm().clamp(min=1e-6)) < 3e-2
