@@ -5,7 +5,7 @@ lists of ``num_accumulate`` batches and keep data-parallel ranks in step.
 (the default for training), ``UNTIL_LAST`` keeps going with empty lists until
 the last one finishes (evaluation). The per-step count exchange runs on a CPU
 (gloo) side gang when one is given so the hot loop never blocks on a device
-read-back (worklist collective C13)."""
+read-back."""
 from __future__ import annotations
 
 from abc import ABC, abstractmethod

@@ -4,7 +4,7 @@ synchronisation (cf. fairseq2 ``metrics/bag.py:26-145``).
 ``begin_updates``/``commit_updates``/``rollback_updates`` let the trainer drop
 the metric updates of a step that is retried after an fp16 overflow.
 ``sync_and_compute_metrics`` packs all metric states into one fp64 vector per
-reduction kind and all-reduces it once (worklist collective C14)."""
+reduction kind and all-reduces it once."""
 from __future__ import annotations
 
 from copy import deepcopy

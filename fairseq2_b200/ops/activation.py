@@ -1,4 +1,4 @@
-"""SwiGLU gating ``silu(gate) * up`` -- worklist row W11.
+"""SwiGLU gating ``silu(gate) * up``.
 
 The merged gate|up projection writes one ``[T, 2F]`` buffer; the kernel reads
 both halves with 16-byte loads and writes ``[T, F]``. Backward recomputes

@@ -1,4 +1,4 @@
-"""Variable-length (packed or padded) causal GQA attention -- worklist row W9.
+"""Variable-length (packed or padded) causal GQA attention.
 
 Sequences are described by begin offsets and lengths into the flattened token
 axis, so packed batches (block-causal per document) and padded batches share

@@ -1,4 +1,4 @@
-"""Output projection fused with masked cross-entropy -- worklist row W8.
+"""Output projection fused with masked cross-entropy.
 
 ``fused_linear_cross_entropy`` never materialises the ``[T, V]`` logits of the
 whole batch: tokens are processed in chunks; per chunk the tcgen05 GEMM writes

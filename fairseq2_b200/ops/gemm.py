@@ -1,4 +1,4 @@
-"""Dense bf16 GEMM on tcgen05/TMEM -- worklist row W1.
+"""Dense bf16 GEMM on tcgen05/TMEM.
 
 ``gemm(a, b, a_mn=, b_mn=)`` computes ``C[M, N] = A · Bᵀ`` where, with the
 default *K-major* operands, ``a`` is ``[M, K]`` and ``b`` is ``[N, K]`` (the

@@ -1,4 +1,4 @@
-"""RMSNorm / LayerNorm (forward and backward) -- worklist rows W10.
+"""RMSNorm / LayerNorm (forward and backward).
 
 CUDA: one block per row group, fp32 statistics, 16-byte vector loads, the
 backward produces dx in one pass and per-block partial dw that a second tiny

@@ -1,4 +1,4 @@
-"""Multi-tensor AdamW and gradient-norm kernels -- worklist rows W17 / K10.
+"""Multi-tensor AdamW and gradient-norm kernels.
 
 One launch updates a whole list of tensors: fp32 master weights, ``exp_avg``,
 ``exp_avg_sq`` are read and written once, the gradient (bf16 or fp32) is read

@@ -1,4 +1,4 @@
-"""Rotary position encoding on interleaved pairs -- part of worklist row W9.
+"""Rotary position encoding on interleaved pairs.
 
 ``x[..., 2i], x[..., 2i+1]`` is rotated by the angle ``pos * theta_i``. The
 kernel rotates q and k heads in place right after the QKV projection, reading

@@ -5,8 +5,8 @@ Plain parameters are updated by the multi-tensor kernel of ``ops.optim`` (or
 the PyTorch formulation on CPU). Parameters that are dim-0 shards of an FSDP
 unit (they carry ``_fs2_unit``) are updated *per unit* with ONE launch over the
 unit's flat fp32 master / moment buffers, reading the unit's reduced gradient
-shard and refreshing its bf16 shard in the same pass -- the optimizer half of
-worklist row W3. ``grad_scale`` (loss normalisation x clip coefficient) is a
+shard and refreshing its bf16 shard in the same pass: the optimizer half of
+the fused reduce-scatter + update. ``grad_scale`` (loss normalisation x clip coefficient) is a
 device scalar consumed inside the kernel.
 
 Hyper-parameters and state layout (``step``, ``exp_avg``, ``exp_avg_sq`` per

@@ -1,4 +1,4 @@
-"""Symmetric-memory communication for one NVSwitch box (worklist row W16).
+"""Symmetric-memory communication for one NVSwitch box.
 
 ``SymmetricArena`` allocates one buffer per rank through
 ``torch.distributed._symmetric_memory`` (CUDA VMM allocation + handle exchange
