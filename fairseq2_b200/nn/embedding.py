@@ -140,9 +140,28 @@ class ShardedEmbedding(Embedding):
         with torch.no_grad():
             self.weight.copy_(full.weight[:, self.gang.rank * c:(self.gang.rank + 1) * c])
 
+    @staticmethod
+    def from_embedding(embed: StandardEmbedding, gang: Gang) -> "ShardedEmbedding":
+        m = ShardedEmbedding(gang, embed.num_embeddings, embed.embed_dim, embed.pad_idx, init_fn=embed.init_fn,
+                             device=torch.device("meta"), dtype=embed.weight.dtype)
+        m.to_empty(device=embed.weight.device)
+        c = m.sharded_embed_dim
+        with torch.no_grad():
+            m.weight.copy_(embed.weight[:, gang.rank * c:(gang.rank + 1) * c])
+        return m
+
     def forward(self, x: Tensor) -> Tensor:
         y = F.embedding(x, self.weight, self.pad_idx)
         return gather(y, self.gang, dim=-1)
+
+    def to_embedding(self, device: Device | None = None) -> StandardEmbedding:
+        w = gather(self.weight.detach(), self.gang, dim=1)
+        e = StandardEmbedding(self.num_embeddings, self.embed_dim, self.pad_idx, device=torch.device("meta"),
+                              dtype=self.weight.dtype)
+        e.to_empty(device=device or self.weight.device)
+        with torch.no_grad():
+            e.weight.copy_(w)
+        return e
 
     def get_shard_dims(self) -> list[tuple[Parameter, int]]:
         return [(self.weight, 1)]
