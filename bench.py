@@ -71,6 +71,34 @@ def _summarize_clocks(samples: list[dict]) -> dict:
             "samples": len(samples), "power_w_max": max(s["power"] for s in samples)}
 
 
+def _trace_steps(args: argparse.Namespace, step_fn, batches, rank: int, record: bool) -> None:  # type: ignore[no-untyped-def]
+    """Kernel timeline of two more steps (outside every timed region): one JSON row per kernel with stream, start
+    and duration in microseconds, for overlap analysis of the compute and communication streams."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    if not record:                       # the other ranks only take part in the collectives
+        for i, b in enumerate(batches):
+            step_fn([b], 10_000 + i)
+        torch.cuda.synchronize()
+        return
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for i, b in enumerate(batches):
+            step_fn([b], 10_000 + i)
+        torch.cuda.synchronize()
+    raw = f"{args.trace}.rank{rank}.raw.json"
+    os.makedirs(os.path.dirname(os.path.abspath(raw)), exist_ok=True)
+    prof.export_chrome_trace(raw)
+    with open(raw) as fp:
+        events = json.load(fp)["traceEvents"]
+    os.remove(raw)
+    rows = [{"name": e["name"][:96], "ts": e["ts"], "dur": e["dur"], "stream": e.get("args", {}).get("stream")}
+            for e in events if e.get("cat") in ("kernel", "gpu_memcpy", "gpu_memset")]
+    path = f"{args.trace}.rank{rank}.json"
+    with open(path, "w") as fp:
+        json.dump(rows, fp)
+
+
 def run_ours(args: argparse.Namespace) -> None:
     import numpy as np
     import torch
@@ -182,6 +210,11 @@ def run_ours(args: argparse.Namespace) -> None:
     stop.set()
     ext.check_status()
 
+    if args.trace:
+        _trace_steps(args, step_fn, [stage(examples[args.warmup + i]) for i in range(2)], rank,
+                     record=rank == 0 or args.trace_all_ranks)
+        barrier()
+
     times = torch.tensor([dev_ms, e2e_ms], device=device, dtype=torch.float64)
     if world > 1:
         root.all_reduce(times, ReduceOperation.MAX)
@@ -232,6 +265,9 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="llama3_8b")
     ap.add_argument("--seq-len", type=int, default=8192)
+    ap.add_argument("--trace", default=None, metavar="PREFIX",
+                    help="after the timed regions, write a kernel timeline of two steps to PREFIX.rankN.json")
+    ap.add_argument("--trace-all-ranks", action="store_true")
     ap.add_argument("--layers", type=int, default=None, help="debugging only: truncates the model (result is not a valid benchmark)")
     args = ap.parse_args()
     if args.warmup < 3 and args.layers is None:

@@ -1,0 +1,241 @@
+"""Device-timed microbenchmarks of the peer-memory collectives and the fused compute+collective kernels.
+
+Run one process per GPU::
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        -m fairseq2_b200.parallel.commbench [--cases all] [--iters 10]
+
+Every case is timed with CUDA events on the launching stream after warm-up, a barrier on both sides, and reported as
+the MAX over ranks. Rank 0 prints one JSON line per case with the achieved rate and its fraction of the roofline
+
+    target = max(FLOPs / measured GEMM peak, bytes that must cross NVLink per GPU / link bandwidth)
+
+(and local HBM bytes / measured copy bandwidth where that is the larger term), where the link bandwidth defaults to the measured peer-copy figure of 770 GB/s per direction per GPU. For each case
+the NCCL (or NCCL + separate kernel) formulation of the same work is timed next to it.
+
+The shapes are the ones a LLaMA-3-8B layer produces: an FSDP unit of 218 M bf16 parameters; the row-parallel
+``[8192, 14336/W] x [4096, 14336/W]`` and column-parallel ``[8192, 4096] x [14336/W, 4096]`` feed-forward GEMMs.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+from collections.abc import Callable
+
+import torch
+import torch.distributed as dist
+
+
+def _time(fn: Callable[[], None], barrier: Callable[[], None], iters: int, warmup: int = 3) -> float:
+    for _ in range(warmup):
+        fn()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    barrier()
+    ms = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda", dtype=torch.float64)
+    dist.all_reduce(ms, dist.ReduceOp.MAX)
+    return float(ms)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--cases", default="all")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--unit-params", type=int, default=218_112_000, help="parameters of one FSDP unit")
+    ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--link-gbs", type=float, default=770.0)
+    ap.add_argument("--gemm-tflops", type=float, default=None, help="defaults to MEASURED_PEAKS.json or 1590")
+    args = ap.parse_args()
+
+    from fairseq2_b200.gang import ProcessGroupGang
+    from fairseq2_b200.ops.fused_collective import FusedAllGatherGemm, FusedGemmReduceScatter
+    from fairseq2_b200.ops.gemm import gemm as gemm_nt
+    from fairseq2_b200.ops.optim import multi_tensor_adamw
+    from fairseq2_b200.parallel.symm import SymmetricArena
+
+    rank, W = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
+    torch.cuda.set_device(dev)
+    base = ProcessGroupGang.create_default_process_group(dev)
+    pg = base.as_process_group()
+    peak = args.gemm_tflops
+    if peak is None:
+        try:
+            with open(os.path.join(os.path.dirname(__file__), "..", "..", "MEASURED_PEAKS.json")) as fp:
+                peak = float(json.load(fp)["bf16_tflops"])
+        except (OSError, KeyError, ValueError):
+            peak = 1590.0
+    link = args.link_gbs * 1e9
+    hbm = 6.5e12
+    try:
+        with open(os.path.join(os.path.dirname(__file__), "..", "..", "MEASURED_PEAKS.json")) as fp:
+            hbm = float(json.load(fp)["hbm_gbs"]) * 1e9
+    except (OSError, KeyError, ValueError):
+        pass
+    cases = args.cases.split(",")
+    want = lambda c: "all" in cases or c in cases  # noqa: E731
+
+    n = (args.unit_params // W + 2047) // 2048 * 2048            # shard elements
+    T = args.tokens
+    arena_bytes = ((W + 1) * n * 2 + (128 << 20) + 2 * (T // W) * 4096 * 4 + (T // W + T) * 4096 * 2
+                   + (14336 // W + 14336) * 4096 * 2 + (64 << 20))
+    arena = SymmetricArena(base, arena_bytes)
+    ext = arena.ext
+    epoch = {"v": 0}
+
+    def barrier() -> None:
+        arena.barrier_next(0)
+        torch.cuda.synchronize()
+
+    def emit(case: str, ms: float, *, nvlink_bytes: float = 0.0, flops: float = 0.0, hbm_bytes: float = 0.0,
+             baseline_ms: float | None = None, **extra: object) -> None:
+        if rank != 0:
+            return
+        target_ms = max(flops / (peak * 1e12), nvlink_bytes / link, hbm_bytes / hbm) * 1e3
+        row = {"case": case, "world": W, "ms": round(ms, 4), "target_ms": round(target_ms, 4),
+               "frac_of_roofline": round(target_ms / ms, 3) if ms > 0 else None}
+        if nvlink_bytes:
+            row["nvlink_gbs_per_gpu"] = round(nvlink_bytes / ms / 1e6, 1)
+        if flops:
+            row["tflops"] = round(flops / ms / 1e9, 1)
+        if baseline_ms is not None:
+            row["nccl_formulation_ms"] = round(baseline_ms, 4)
+        row.update(extra)
+        print(json.dumps(row), flush=True)
+
+    segs_off, segs_n = [0], [n]
+    shard_off, shard = arena.alloc_tensor(n, torch.bfloat16)
+    grad_off, grad_full = arena.alloc_tensor(W * n, torch.bfloat16)
+    shard.normal_()
+    grad_full.normal_(std=0.01)
+    full = torch.empty(W * n, device=dev, dtype=torch.bfloat16)
+    peer_bytes = (W - 1) * n * 2                                  # received (AG) or read (RS) over NVLink per GPU
+
+    if want("allgather"):
+        for blocks in (max(32 // W, 4), 16):
+            def ag() -> None:
+                epoch["v"] += 1
+                ext.comm_allgather_segments(arena.peer_ptrs, rank, segs_off, segs_n, shard_off, full, 1, 0, blocks,
+                                            arena.wait_limit_s)
+            ms = _time(ag, barrier, args.iters)
+            nccl = _time(lambda: dist.all_gather_into_tensor(full, shard, group=pg), barrier, args.iters)
+            emit("fsdp_unit_allgather", ms, nvlink_bytes=peer_bytes, baseline_ms=nccl, blocks_per_peer=blocks,
+                 mbytes=round(W * n * 2 / 1e6, 1))
+
+    if want("reducescatter"):
+        gshard = torch.empty(n, device=dev, dtype=torch.float32)
+        rs_epoch = {"v": 0}
+
+        def rs() -> None:
+            rs_epoch["v"] += 1
+            ext.comm_reducescatter_segments(arena.peer_ptrs, rank, segs_off, segs_n, grad_off, gshard, 1.0 / W, False, 3,
+                                            rs_epoch["v"], 48, arena.wait_limit_s)
+        ms = _time(rs, barrier, args.iters)
+        out16 = torch.empty(n, device=dev, dtype=torch.bfloat16)
+        nccl = _time(lambda: dist.reduce_scatter_tensor(out16, grad_full, op=dist.ReduceOp.AVG, group=pg), barrier,
+                     args.iters)
+        emit("fsdp_unit_reducescatter_fp32acc", ms, nvlink_bytes=peer_bytes, baseline_ms=nccl)
+
+        master, m, v = torch.randn(n, device=dev), torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+        low = torch.empty(n, device=dev, dtype=torch.bfloat16)
+        hp = dict(lr=1e-5, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1)
+        fe = {"v": 0}
+
+        def rs_adamw() -> None:
+            fe["v"] += 1
+            ext.comm_reducescatter_adamw(arena.peer_ptrs, rank, segs_off, segs_n, grad_off, master, m, v, low, 1.0 / W,
+                                         hp["lr"], hp["beta1"], hp["beta2"], hp["eps"], hp["weight_decay"], fe["v"], 4,
+                                         fe["v"], 96, arena.wait_limit_s)
+
+        def rs_then_adamw() -> None:
+            rs()
+            multi_tensor_adamw([master], [gshard], [m], [v], [low], step=max(rs_epoch["v"], 1), **hp)
+
+        ms_f = _time(rs_adamw, barrier, args.iters)
+        ms_u = _time(rs_then_adamw, barrier, args.iters)
+        # local HBM traffic of the optimizer half: p, m, v read + written (fp32) and the bf16 copy written
+        emit("fsdp_unit_reducescatter_adamw_fused", ms_f, nvlink_bytes=peer_bytes, hbm_bytes=n * (24 + 2 + 2),
+             baseline_ms=ms_u, note="baseline = our reduce-scatter kernel + our AdamW kernel")
+
+    if want("allreduce"):
+        numel = 64 * 1024 * 1024                                  # 128 MB of bf16, a DDP-scale bucket
+        off, bucket = arena.alloc_tensor(numel, torch.bfloat16)
+        coff, counter = arena.alloc(64, align=64)
+        counter.zero_()
+        bucket.normal_(std=0.01)
+        ae = {"v": 0}
+
+        def ar() -> None:
+            ae["v"] += 1
+            ext.comm_allreduce_inplace(arena.peer_ptrs, rank, off, numel, False, 1.0 / W, 5, 6, ae["v"], coff,
+                                       arena.device_index, 64, arena.wait_limit_s)
+        ms = _time(ar, barrier, args.iters)
+        ref = torch.empty(numel, device=dev, dtype=torch.bfloat16).normal_(std=0.01)
+        nccl = _time(lambda: dist.all_reduce(ref, op=dist.ReduceOp.AVG, group=pg), barrier, args.iters)
+        emit("ddp_bucket_allreduce_inplace_128MB", ms, nvlink_bytes=2 * (W - 1) / W * numel * 2, baseline_ms=nccl)
+
+    K_ffn, D = 14336, 4096
+    if want("gemm_rs") and K_ffn % W == 0 and T % (W * 128) == 0:
+        kl = K_ffn // W
+        x = torch.randn(T, kl, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(D, kl, device=dev, dtype=torch.bfloat16) * 0.02
+        op = FusedGemmReduceScatter(arena, T // W, D)
+        ms = _time(lambda: op(x, w), barrier, args.iters)
+        out = torch.empty(T // W, D, device=dev, dtype=torch.bfloat16)
+
+        def unfused() -> None:
+            y = gemm_nt(x, w)
+            dist.reduce_scatter_tensor(out, y, group=pg)
+        nccl = _time(unfused, barrier, args.iters)
+        gemm_only = _time(lambda: gemm_nt(x, w), barrier, args.iters)
+        emit("tp_row_gemm_reducescatter_fused", ms, flops=2.0 * T * kl * D, nvlink_bytes=(W - 1) / W * T * D * 4,
+             baseline_ms=nccl, gemm_alone_ms=round(gemm_only, 4),
+             note="fused path reduces in fp32 (4 B/element on the wire); baseline = our GEMM + NCCL bf16 reduce-scatter")
+
+    if want("ag_gemm") and K_ffn % W == 0 and (T // W) % 128 == 0:
+        nl = K_ffn // W
+        w = torch.randn(nl, D, device=dev, dtype=torch.bfloat16) * 0.02
+        op_a = FusedAllGatherGemm(arena, T // W, D, gather="a")
+        op_a.shard.normal_()
+        ms = _time(lambda: op_a(w), barrier, args.iters)
+        xs = op_a.shard.clone()
+        xg = torch.empty(T, D, device=dev, dtype=torch.bfloat16)
+
+        def unfused_a() -> None:
+            dist.all_gather_into_tensor(xg, xs, group=pg)
+            gemm_nt(xg, w)
+        nccl = _time(unfused_a, barrier, args.iters)
+        gemm_only = _time(lambda: gemm_nt(xg, w), barrier, args.iters)
+        emit("tp_column_allgather_gemm_fused", ms, flops=2.0 * T * D * nl, nvlink_bytes=(W - 1) / W * T * D * 2,
+             baseline_ms=nccl, gemm_alone_ms=round(gemm_only, 4))
+
+    if want("ag_gemm") and (K_ffn // W) % 256 == 0:
+        rows = K_ffn // W                                          # FSDP unshard of the [14336, 4096] up-projection
+        op_b = FusedAllGatherGemm(arena, rows, D, gather="b")
+        op_b.shard.normal_(std=0.02)
+        x = torch.randn(T, D, device=dev, dtype=torch.bfloat16)
+        ms = _time(lambda: op_b(x), barrier, args.iters)
+        ws = op_b.shard.clone()
+        wg = torch.empty(K_ffn, D, device=dev, dtype=torch.bfloat16)
+
+        def unfused_b() -> None:
+            dist.all_gather_into_tensor(wg, ws, group=pg)
+            gemm_nt(x, wg)
+        nccl = _time(unfused_b, barrier, args.iters)
+        gemm_only = _time(lambda: gemm_nt(x, wg), barrier, args.iters)
+        emit("fsdp_unshard_allgather_gemm_fused", ms, flops=2.0 * T * D * K_ffn, nvlink_bytes=(W - 1) / W * K_ffn * D * 2,
+             baseline_ms=nccl, gemm_alone_ms=round(gemm_only, 4))
+
+    barrier()
+    ext.check_status()
+    base.close()
+
+
+if __name__ == "__main__":
+    main()
