@@ -678,6 +678,37 @@ void comm_allgather_segments(const std::vector<int64_t>& ptrs, int64_t rank, con
     g_launches += 1;
 }
 
+// All-gather of the same segment layout through the copy engines: one peer-to-peer cudaMemcpyAsync per
+// (peer, segment), peers visited in ring order starting after this rank so that no GPU is read by everyone at
+// once. No SM takes part, so the GEMMs that run next to it on the compute stream keep all of them.
+void comm_allgather_copy(const std::vector<int64_t>& ptrs, int64_t rank, const std::vector<int64_t>& offs,
+                         const std::vector<int64_t>& numels, int64_t shard_byte_off, Tensor full, int64_t slot,
+                         int64_t epoch, double wait_limit_s) {
+    TORCH_CHECK(full.is_cuda() && full.is_contiguous() && full.element_size() == 2 && aligned16(full),
+                "comm_allgather_copy: `full` must be a contiguous 2-byte CUDA tensor");
+    TORCH_CHECK(offs.size() == numels.size() && !offs.empty(), "comm_allgather_copy: bad segment table");
+    const int64_t W = static_cast<int64_t>(ptrs.size());
+    const int64_t shard_numel = offs.back() + numels.back();
+    TORCH_CHECK(full.numel() == shard_numel * W, "comm_allgather_copy: `full` must hold world x shard elements");
+    c10::cuda::CUDAGuard guard(full.device());
+    cudaStream_t st = stream_of(full);
+    if (epoch != 0) {
+        fs2::comm_wait(make_peers(ptrs, rank, wait_limit_s), static_cast<int>(slot), static_cast<uint32_t>(epoch),
+                       status_dev_ptr(), st);
+        g_launches += 1;
+    }
+    char* dst = static_cast<char*>(full.data_ptr());
+    for (int64_t k = 1; k <= W; ++k) {
+        const int64_t r = (rank + k) % W;                       // own shard last: it needs no link
+        const char* src = reinterpret_cast<const char*>(ptrs[static_cast<size_t>(r)]) + shard_byte_off;
+        for (size_t i = 0; i < offs.size(); ++i) {
+            const size_t bytes = static_cast<size_t>(numels[i]) * 2;
+            C10_CUDA_CHECK(cudaMemcpyAsync(dst + (W * offs[i] + r * numels[i]) * 2, src + offs[i] * 2, bytes,
+                                           cudaMemcpyDeviceToDevice, st));
+        }
+    }
+}
+
 void comm_reducescatter_segments(const std::vector<int64_t>& ptrs, int64_t rank, const std::vector<int64_t>& offs,
                                  const std::vector<int64_t>& numels, int64_t full_byte_off, Tensor out, double scale,
                                  bool accumulate, int64_t slot, int64_t epoch, int64_t blocks, double wait_limit_s) {
@@ -806,6 +837,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("comm_barrier", &comm_barrier);
     m.def("comm_signal", &comm_signal);
     m.def("comm_allgather_segments", &comm_allgather_segments);
+    m.def("comm_allgather_copy", &comm_allgather_copy);
     m.def("comm_reducescatter_segments", &comm_reducescatter_segments);
     m.def("comm_reducescatter_adamw", &comm_reducescatter_adamw);
     m.def("comm_allreduce_f32", &comm_allreduce_f32);

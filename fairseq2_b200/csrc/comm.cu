@@ -88,6 +88,10 @@ __global__ void barrier_kernel(CommPeers peers, int slot, uint32_t epoch, int* s
     signal_and_wait(peers, slot, epoch, true, status, 16);
 }
 
+__global__ void wait_kernel(CommPeers peers, int slot, uint32_t epoch, int* status) {
+    signal_and_wait(peers, slot, epoch, false, status, 19);
+}
+
 __global__ void signal_kernel(CommPeers peers, int slot, uint32_t epoch) {
     if (threadIdx.x == 0 && blockIdx.x == 0) {
         __threadfence_system();
@@ -441,6 +445,10 @@ __global__ void alltoall_kernel(CommPeers peers, long long byte_off, char* __res
 
 void comm_barrier(const CommPeers& peers, int slot, uint32_t epoch, int* status, cudaStream_t st) {
     barrier_kernel<<<1, 32, 0, st>>>(peers, slot, epoch, status);
+}
+
+void comm_wait(const CommPeers& peers, int slot, uint32_t epoch, int* status, cudaStream_t st) {
+    wait_kernel<<<1, 32, 0, st>>>(peers, slot, epoch, status);
 }
 
 void comm_signal(const CommPeers& peers, int slot, uint32_t epoch, cudaStream_t st) {

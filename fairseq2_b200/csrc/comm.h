@@ -26,6 +26,8 @@ struct CommSegments {
 
 void comm_barrier(const CommPeers& peers, int slot, uint32_t epoch, int* status, cudaStream_t st);
 void comm_signal(const CommPeers& peers, int slot, uint32_t epoch, cudaStream_t st);
+// Waits (bounded) until every peer's flag in `slot` has reached `epoch`, without signalling.
+void comm_wait(const CommPeers& peers, int slot, uint32_t epoch, int* status, cudaStream_t st);
 void comm_allgather_segments(const CommPeers& peers, const CommSegments& segs, long long shard_byte_off, void* full,
                              long long shard_numel, int slot, uint32_t epoch, int blocks, int* status,
                              cudaStream_t st);

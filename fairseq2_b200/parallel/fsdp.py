@@ -29,6 +29,7 @@ The design is its own and B200-first:
 from __future__ import annotations
 
 import math
+import os
 from contextlib import contextmanager
 from dataclasses import dataclass
 from typing import Any, Callable, Iterable, Iterator, Mapping, Sequence
@@ -129,6 +130,11 @@ class FlatParamUnit:
             self._bind_full(self.low_shard)
 
     # ------------------------------------------------------------- arena
+    #: "copy": all-gather through the copy engines (no SM); "kernel": the load/store kernel
+    allgather_engine = "kernel"
+    #: thread blocks of the reduce-scatter kernel
+    rs_blocks = 48
+
     def attach_arena(self, arena: Any, slot: int) -> None:
         """Moves the bf16 shard and the flat gradient buffer into the symmetric
         arena so that peers can pull them directly over NVLink."""
@@ -176,9 +182,13 @@ class FlatParamUnit:
         with ctx:
             if self.arena is not None:
                 a = self.arena
-                ag_blocks = max(32 // W, 4)
-                a.ext.comm_allgather_segments(a.peer_ptrs, a.rank, self.seg_offs, self.seg_numels, self.low_off, full,
-                                              1, param_epoch, ag_blocks, a.wait_limit_s)
+                if self.allgather_engine == "copy":
+                    a.ext.comm_allgather_copy(a.peer_ptrs, a.rank, self.seg_offs, self.seg_numels, self.low_off, full,
+                                              1, param_epoch, a.wait_limit_s)
+                else:
+                    ag_blocks = max(32 // W, 4)
+                    a.ext.comm_allgather_segments(a.peer_ptrs, a.rank, self.seg_offs, self.seg_numels, self.low_off,
+                                                  full, 1, param_epoch, ag_blocks, a.wait_limit_s)
             else:
                 _coalesced_all_gather(self.gang, [self._region(full, s).view(W, s.shard_numel) for s in self.specs],
                                       [self.low_shard[s.shard_off: s.shard_off + s.shard_numel] for s in self.specs])
@@ -260,7 +270,7 @@ class FlatParamUnit:
                 self.rs_epoch += 1
                 a.ext.comm_reducescatter_segments(a.peer_ptrs, a.rank, self.seg_offs, self.seg_numels, self.grad_off,
                                                   self.grad_shard, (1.0 / W) if average else 1.0, acc, 2 + self.slot,
-                                                  self.rs_epoch, 48, a.wait_limit_s)
+                                                  self.rs_epoch, self.rs_blocks, a.wait_limit_s)
             self.grads_ready = True
             for cp in self.compute_params:
                 cp.grad_sink_filled = False  # type: ignore[attr-defined]
@@ -367,7 +377,8 @@ class FSDP(Module):
 
     def __init__(self, module: Module, gangs: Gangs, *, wrap_policy: FSDPWrapPolicy | None = layerwise_wrap_policy,
                  param_dtype: DataType = torch.bfloat16, fp32_reduce: bool = True,
-                 reshard_after_forward: bool = True, overlap: bool = True, comm: str = "auto") -> None:
+                 reshard_after_forward: bool = True, overlap: bool = True, comm: str = "auto",
+                 allgather: str = "kernel", rs_blocks: int = 48) -> None:
         super().__init__()
         self.module = module
         self.gangs = gangs
@@ -436,8 +447,13 @@ class FSDP(Module):
                 need = sum((1 + W) * u.shard_size * 2 + 1024 for u in self.all_units) + (1 << 20)
                 try:
                     self.arena = SymmetricArena(self.gang, need)  # type: ignore[arg-type]
+                    engine = os.environ.get("FAIRSEQ2_B200_FSDP_ALLGATHER", allgather)
+                    if engine not in ("copy", "kernel"):
+                        raise ValueError(f"`allgather` must be 'copy' or 'kernel', but is '{engine}' instead.")
                     for i, u in enumerate(self.all_units):
                         u.attach_arena(self.arena, i)
+                        u.allgather_engine = engine
+                        u.rs_blocks = int(os.environ.get("FAIRSEQ2_B200_FSDP_RS_BLOCKS", rs_blocks))
                     torch.cuda.synchronize(dev)
                     self.gang.barrier()
                 except Exception as ex:  # noqa: BLE001
