@@ -118,6 +118,7 @@ void gemm_reduce_scatter(const Tensor& a, const Tensor& b, const std::vector<int
         TORCH_CHECK(ptrs[i] != 0, "gemm_reduce_scatter: null peer pointer");
         outs[i] = reinterpret_cast<float*>(ptrs[i] + out_byte_off);
     }
+    TORCH_CHECK(b.size(0) % 4 == 0, "gemm_reduce_scatter: N must be a multiple of 4");
     check_status();
     c10::cuda::CUDAGuard guard(a.device());
     TORCH_CHECK(cudaSetDevice(a.get_device()) == cudaSuccess, "gemm_reduce_scatter: cudaSetDevice failed");
@@ -126,6 +127,46 @@ void gemm_reduce_scatter(const Tensor& a, const Tensor& b, const std::vector<int
         static_cast<int>(a.size(0)), static_cast<int>(b.size(0)), static_cast<int>(a.size(1)), status_dev_ptr(),
         num_sms(a), stream_of(a));
     TORCH_CHECK(err == nullptr, "gemm_reduce_scatter: ", err);
+    g_launches += 1;
+}
+
+// bf16 scatter form of the fused row-parallel GEMM: tile rows owned by rank r land in slice `rank` of the
+// [world, rows_per_rank, N] bf16 buffer at `slices_byte_off` of rank r's arena.
+void gemm_scatter(const Tensor& a, const Tensor& b, const std::vector<int64_t>& ptrs, int64_t rank,
+                  int64_t slices_byte_off, int64_t rows_per_rank) {
+    TORCH_CHECK(a.is_cuda() && b.is_cuda() && is_bf16(a) && is_bf16(b) && a.dim() == 2 && b.dim() == 2 &&
+                    a.is_contiguous() && b.is_contiguous() && a.size(1) == b.size(1),
+                "gemm_scatter: a [M,K] and b [N,K] must be contiguous bf16 CUDA matrices");
+    TORCH_CHECK(a.size(1) % 8 == 0 && b.size(0) % 8 == 0 && aligned16(a) && aligned16(b) && slices_byte_off % 16 == 0,
+                "gemm_scatter: alignment");
+    TORCH_CHECK(!ptrs.empty() && ptrs.size() <= 8 && rank >= 0 && rank < static_cast<int64_t>(ptrs.size()),
+                "gemm_scatter: between 1 and 8 ranks are supported");
+    void* outs[8];
+    for (size_t i = 0; i < ptrs.size(); ++i) {
+        TORCH_CHECK(ptrs[i] != 0, "gemm_scatter: null peer pointer");
+        outs[i] = reinterpret_cast<void*>(ptrs[i] + slices_byte_off);
+    }
+    check_status();
+    c10::cuda::CUDAGuard guard(a.device());
+    const char* err = fs2::gemm_scatter_bf16_tcgen05(
+        a.data_ptr(), b.data_ptr(), outs, static_cast<int>(ptrs.size()), static_cast<int>(rank),
+        static_cast<int>(rows_per_rank), static_cast<int>(a.size(0)), static_cast<int>(b.size(0)),
+        static_cast<int>(a.size(1)), status_dev_ptr(), num_sms(a), stream_of(a));
+    TORCH_CHECK(err == nullptr, "gemm_scatter: ", err);
+    g_launches += 1;
+}
+
+// out[i] = sum_w slices[w, i] in fp32; `slices` is [W, n] bf16, `out` is [n] bf16 or fp32.
+void reduce_slices(const Tensor& slices, Tensor out) {
+    TORCH_CHECK(slices.is_cuda() && is_bf16(slices) && slices.is_contiguous() && slices.dim() >= 2 && aligned16(slices),
+                "reduce_slices: `slices` must be a contiguous bf16 CUDA tensor [W, ...]");
+    const int64_t W = slices.size(0), n = slices.numel() / W;
+    TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.numel() == n && aligned16(out) && n % 8 == 0 &&
+                    (is_bf16(out) || out.scalar_type() == at::kFloat) && W >= 1 && W <= 8,
+                "reduce_slices: `out` must be a contiguous bf16/fp32 CUDA tensor of one slice (multiple of 8 elements)");
+    c10::cuda::CUDAGuard guard(out.device());
+    fs2::comm_reduce_slices(slices.data_ptr(), static_cast<int>(W), n, out.data_ptr(), out.scalar_type() == at::kFloat,
+                            stream_of(out));
     g_launches += 1;
 }
 
@@ -726,6 +767,46 @@ void comm_reducescatter_segments(const std::vector<int64_t>& ptrs, int64_t rank,
     g_launches += 1;
 }
 
+// Reduce-scatter whose NVLink half runs on the copy engines: after the barrier that says every rank's gradients of
+// this unit are final, the peers' slices of the local shard are copied into `staging` ([W - 1, shard] bf16, local
+// memory), then one short kernel sums them with the own slice in fp32. The SMs are busy for a local-memory pass only.
+void comm_reducescatter_copy(const std::vector<int64_t>& ptrs, int64_t rank, const std::vector<int64_t>& offs,
+                             const std::vector<int64_t>& numels, int64_t full_byte_off, Tensor staging, Tensor out,
+                             double scale, bool accumulate, int64_t slot, int64_t epoch, int64_t blocks,
+                             double wait_limit_s) {
+    const int64_t W = static_cast<int64_t>(ptrs.size());
+    const int64_t shard_numel = offs.back() + numels.back();
+    TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.numel() == shard_numel && aligned16(out) &&
+                    (out.scalar_type() == at::kFloat || is_bf16(out)),
+                "comm_reducescatter_copy: `out` must be a contiguous fp32/bf16 shard-sized CUDA tensor");
+    TORCH_CHECK(staging.is_cuda() && staging.is_contiguous() && is_bf16(staging) && aligned16(staging) &&
+                    staging.numel() >= (W - 1) * shard_numel,
+                "comm_reducescatter_copy: `staging` must be a contiguous bf16 CUDA tensor of (world - 1) shards");
+    TORCH_CHECK(full_byte_off % 16 == 0, "comm_reducescatter_copy: unaligned offset");
+    c10::cuda::CUDAGuard guard(out.device());
+    cudaStream_t st = stream_of(out);
+    const auto peers = make_peers(ptrs, rank, wait_limit_s);
+    const auto segs = make_segments(offs, numels);
+    fs2::comm_barrier(peers, static_cast<int>(slot), static_cast<uint32_t>(epoch), status_dev_ptr(), st);
+    char* stage = static_cast<char*>(staging.data_ptr());
+    const void* staged[8];
+    for (int64_t k = 1; k < W; ++k) {
+        const int64_t r = (rank + k) % W;
+        const char* src = reinterpret_cast<const char*>(ptrs[static_cast<size_t>(r)]) + full_byte_off;
+        char* dst = stage + (k - 1) * shard_numel * 2;
+        staged[k - 1] = dst;
+        for (size_t i = 0; i < offs.size(); ++i) {
+            C10_CUDA_CHECK(cudaMemcpyAsync(dst + offs[i] * 2, src + (W * offs[i] + rank * numels[i]) * 2,
+                                           static_cast<size_t>(numels[i]) * 2, cudaMemcpyDeviceToDevice, st));
+        }
+    }
+    const char* own = reinterpret_cast<const char*>(ptrs[static_cast<size_t>(rank)]) + full_byte_off;
+    fs2::comm_reduce_staged(own, staged, static_cast<int>(W - 1), segs, static_cast<int>(rank), static_cast<int>(W),
+                            out.data_ptr(), out.scalar_type() == at::kFloat, static_cast<float>(scale), accumulate,
+                            static_cast<int>(blocks), st);
+    g_launches += 2;
+}
+
 void comm_reducescatter_adamw(const std::vector<int64_t>& ptrs, int64_t rank, const std::vector<int64_t>& offs,
                               const std::vector<int64_t>& numels, int64_t full_byte_off, Tensor master, Tensor m,
                               Tensor v, const std::optional<Tensor>& low, double scale, double lr, double beta1,
@@ -820,6 +901,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("gemm_bf16", &gemm_bf16);
     m.def("gemm_reduce_scatter", &gemm_reduce_scatter);
     m.def("gemm_allgather", &gemm_allgather);
+    m.def("gemm_scatter", &gemm_scatter);
+    m.def("reduce_slices", &reduce_slices);
     m.def("rms_norm_fwd", &rms_norm_fwd);
     m.def("rms_norm_bwd", &rms_norm_bwd);
     m.def("layer_norm_fwd", &layer_norm_fwd);
@@ -839,6 +922,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("comm_allgather_segments", &comm_allgather_segments);
     m.def("comm_allgather_copy", &comm_allgather_copy);
     m.def("comm_reducescatter_segments", &comm_reducescatter_segments);
+    m.def("comm_reducescatter_copy", &comm_reducescatter_copy);
     m.def("comm_reducescatter_adamw", &comm_reducescatter_adamw);
     m.def("comm_allreduce_f32", &comm_allreduce_f32);
     m.def("comm_allreduce_inplace", &comm_allreduce_inplace);

@@ -269,6 +269,58 @@ __global__ void __launch_bounds__(512) reducescatter_adamw_kernel(CommPeers peer
     reducescatter_dispatch(peers, segs, full_byte_off, sink, scale);
 }
 
+// Second half of the copy-engine reduce-scatter: the peers' slices of this rank's shard have been copied into local
+// staging buffers (shard layout), the own slice still sits in the local full-gradient buffer. Sums own + staged in
+// ring order (the order of the load/store kernel above, so both paths give the same bits) from local memory only.
+struct StagedSlices {
+    const __nv_bfloat16* p[kCommMaxRanks];
+    int count;
+};
+
+template <typename OutT>
+__global__ void __launch_bounds__(512) reduce_staged_kernel(const __nv_bfloat16* __restrict__ own_full,
+                                                            StagedSlices staged, CommSegments segs, int rank, int world,
+                                                            OutT* __restrict__ out, float scale, int accumulate) {
+    const StoreSink<OutT> sink{out, accumulate};
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (int s = 0; s < segs.count; ++s) {
+        const long long off = segs.off[s];
+        const long long nvec = segs.numel[s] / 8;
+        const __nv_bfloat16* own = own_full + world * off + rank * segs.numel[s];
+        for (long long v = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v < nvec; v += stride) {
+            float acc[8];
+            load8(own, static_cast<size_t>(v * 8), acc);
+            for (int k = 0; k < staged.count; ++k) {
+                float f[8];
+                load8(staged.p[k] + off, static_cast<size_t>(v * 8), f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[e] += f[e];
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] *= scale;
+            sink(static_cast<size_t>(off + v * 8), acc);
+        }
+    }
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(256) reduce_slices_kernel(const __nv_bfloat16* __restrict__ slices, int world,
+                                                            long long n, OutT* __restrict__ out) {
+    const long long nvec = n / 8;
+    for (long long v = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v < nvec;
+         v += static_cast<long long>(gridDim.x) * blockDim.x) {
+        float acc[8];
+        load8(slices, static_cast<size_t>(v * 8), acc);
+        for (int w = 1; w < world; ++w) {
+            float f[8];
+            load8(slices + w * n, static_cast<size_t>(v * 8), f);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] += f[e];
+        }
+        store8(out, static_cast<size_t>(v * 8), acc);
+    }
+}
+
 // One-shot all-reduce of `numel` fp32 values staged at `byte_off` of every arena.
 // op: 0 sum, 1 mean, 2 product, 3 min, 4 max.
 __global__ void allreduce_f32_kernel(CommPeers peers, long long byte_off, float* __restrict__ out, long long numel,
@@ -510,6 +562,31 @@ void comm_reducescatter_adamw(const CommPeers& peers, const CommSegments& segs, 
     sink.step_size = lr / (1.f - powf(beta1, static_cast<float>(step)));
     sink.bc2_sqrt = sqrtf(1.f - powf(beta2, static_cast<float>(step)));
     reducescatter_adamw_kernel<<<blocks, 512, 0, st>>>(peers, segs, full_byte_off, sink, scale, slot, epoch, status);
+}
+
+void comm_reduce_slices(const void* slices, int world, long long n, void* out, bool out_f32, cudaStream_t st) {
+    const long long nvec = n / 8;
+    const int blocks = static_cast<int>(nvec / 256 < 1 ? 1 : (nvec / 256 > 1184 ? 1184 : nvec / 256));
+    if (out_f32)
+        reduce_slices_kernel<float><<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(slices), world, n,
+                                                            static_cast<float*>(out));
+    else
+        reduce_slices_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(slices), world, n,
+                                                                    static_cast<__nv_bfloat16*>(out));
+}
+
+void comm_reduce_staged(const void* own_full, const void* const* staged, int count, const CommSegments& segs, int rank,
+                        int world, void* out, bool out_f32, float scale, bool accumulate, int blocks, cudaStream_t st) {
+    StagedSlices sl;
+    sl.count = count;
+    for (int k = 0; k < count; ++k) sl.p[k] = static_cast<const __nv_bfloat16*>(staged[k]);
+    if (out_f32)
+        reduce_staged_kernel<float><<<blocks, 512, 0, st>>>(static_cast<const __nv_bfloat16*>(own_full), sl, segs, rank,
+                                                            world, static_cast<float*>(out), scale, accumulate ? 1 : 0);
+    else
+        reduce_staged_kernel<__nv_bfloat16><<<blocks, 512, 0, st>>>(static_cast<const __nv_bfloat16*>(own_full), sl,
+                                                                    segs, rank, world, static_cast<__nv_bfloat16*>(out),
+                                                                    scale, accumulate ? 1 : 0);
 }
 
 void comm_allreduce_inplace(const CommPeers& peers, long long byte_off, long long numel, bool f32, float scale,

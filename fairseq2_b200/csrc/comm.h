@@ -26,6 +26,11 @@ struct CommSegments {
 
 void comm_barrier(const CommPeers& peers, int slot, uint32_t epoch, int* status, cudaStream_t st);
 void comm_signal(const CommPeers& peers, int slot, uint32_t epoch, cudaStream_t st);
+// out[i] = sum over w < world of slices[w * n + i] (bf16 in, fp32 sum, bf16 or fp32 out); n a multiple of 8.
+void comm_reduce_slices(const void* slices, int world, long long n, void* out, bool out_f32, cudaStream_t st);
+// out[off_s + i] = scale * (own_full[W * off_s + rank * numel_s + i] + sum_k staged[k][off_s + i]); local memory only.
+void comm_reduce_staged(const void* own_full, const void* const* staged, int count, const CommSegments& segs, int rank,
+                        int world, void* out, bool out_f32, float scale, bool accumulate, int blocks, cudaStream_t st);
 // Waits (bounded) until every peer's flag in `slot` has reached `epoch`, without signalling.
 void comm_wait(const CommPeers& peers, int slot, uint32_t epoch, int* status, cudaStream_t st);
 void comm_allgather_segments(const CommPeers& peers, const CommSegments& segs, long long shard_byte_off, void* full,

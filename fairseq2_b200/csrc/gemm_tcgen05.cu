@@ -120,8 +120,9 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_
 // rows_per_rank)) is summed into `out[r]`, an fp32 [rows_per_rank, N] buffer in rank r's memory that this GPU
 // reaches through a peer mapping.
 struct PeerOut {
-    float* out[8];
+    void* out[8];
     int rows_per_rank;
+    int slice;          // bf16 scatter mode: index of this rank's slice inside every owner's [world, rows, N] buffer
 };
 
 // Arguments of the fused all-gather: the gathered operand (A when GATHER == 1, B when GATHER == 2) is assembled in
@@ -139,9 +140,12 @@ struct GatherArgs {
     long long row_bytes;
 };
 
-// PEER_RED: instead of storing C locally, every fp32 tile is reduced (red.global.add) straight into the memory of
-// the rank that owns its rows, so a row-parallel GEMM and the reduce-scatter that follows it are one kernel and the
-// NVLink traffic of tile i overlaps the tensor-core work of tile i + 1.
+// PEER_RED: instead of storing C locally, every tile goes straight into the memory of the rank that owns its rows,
+// so a row-parallel GEMM and the reduce-scatter that follows it are one kernel and the NVLink traffic of tile i
+// overlaps the tensor-core work of tile i + 1. Two forms: with OUT_F32 the fp32 tile is summed in place in the
+// owner's [rows, N] buffer (red.global.add); without it the tile is rounded to bf16 and written with plain 16-byte
+// stores into this rank's slice of the owner's [world, rows, N] buffer, and the owner sums the slices afterwards
+// (half the bytes on the wire, no atomics, a deterministic sum).
 //
 // GATHER: all-gather of one operand fused into the GEMM. Copier CTAs pull the peers' shards over NVLink exactly
 // once into local memory, block by block in the order in which the compute CTAs consume them (own shard first),
@@ -155,36 +159,79 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
     constexpr int GBLK = GATHER == 2 ? BN : BM;          // rows of the gathered operand per flag
     if constexpr (GATHER != 0) {
         if (static_cast<int>(blockIdx.x) < ga.ncopy) {
+            // Copier CTA: one thread moves its blocks with bulk copies, peer memory -> shared memory -> local
+            // memory, COPY_BUFS chunks of COPY_CHUNK bytes in flight, so no registers stage the data and ~200 KB
+            // per copier CTA are outstanding on NVLink.
+            if (threadIdx.x != 0) return;
+            extern __shared__ uint8_t copier_smem[];
+            const uint32_t craw = smem_u32(copier_smem);
+            const uint32_t cbase = (craw + 1023u) & ~1023u;
+            constexpr uint32_t COPY_CHUNK = 32768;
+            constexpr int COPY_BUFS = STAGES * STAGE_BYTES / COPY_CHUNK;
+            const uint32_t cbar = cbase + STAGES * STAGE_BYTES + 2 * EPI_BYTES;
+            for (int b = 0; b < COPY_BUFS; ++b) mbar_init(cbar + 8 * b, 1);
+            fence_barrier_init();
             const int per_rank = ga.rows_per_rank / GBLK;
             const int total = per_rank * ga.world;
             const long long blk_bytes = static_cast<long long>(GBLK) * ga.row_bytes;
-            for (int i = blockIdx.x; i < total; i += ga.ncopy) {
+            const int nch = static_cast<int>((blk_bytes + COPY_CHUNK - 1) / COPY_CHUNK);
+            const int my_blocks = (total - static_cast<int>(blockIdx.x) + ga.ncopy - 1) / ga.ncopy;
+            const long long total_chunks = static_cast<long long>(my_blocks) * nch;
+            int abort_local = 0;
+            bool failed = false;
+            // chunk c -> (source, destination, bytes, block, last chunk of its block?)
+            auto locate = [&](long long c, const char*& from, char*& to, uint32_t& bytes, int& gblock, bool& last) {
+                const int i = static_cast<int>(blockIdx.x) + static_cast<int>(c / nch) * ga.ncopy;
+                const int k = static_cast<int>(c % nch);
                 const int src_rank = (ga.rank + i / per_rank) % ga.world;
                 const int bi = i % per_rank;
-                const int gblock = src_rank * per_rank + bi;
-                const char* from = static_cast<const char*>(ga.src[src_rank]) + bi * blk_bytes;
-                char* to = static_cast<char*>(ga.dst) + gblock * blk_bytes;
-                const long long nvec = blk_bytes / 16;
-                for (long long v0 = threadIdx.x; v0 < nvec; v0 += NUM_THREADS * 4) {
-                    uint4 buf[4];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const long long v = v0 + u * NUM_THREADS;
-                        if (v < nvec)
-                            asm volatile("ld.relaxed.sys.global.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
-                                         : "=r"(buf[u].x), "=r"(buf[u].y), "=r"(buf[u].z), "=r"(buf[u].w)
-                                         : "l"(from + v * 16) : "memory");
-                    }
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const long long v = v0 + u * NUM_THREADS;
-                        if (v < nvec) *reinterpret_cast<uint4*>(to + v * 16) = buf[u];
-                    }
+                gblock = src_rank * per_rank + bi;
+                const long long off = static_cast<long long>(k) * COPY_CHUNK;
+                from = static_cast<const char*>(ga.src[src_rank]) + bi * blk_bytes + off;
+                to = static_cast<char*>(ga.dst) + gblock * blk_bytes + off;
+                bytes = static_cast<uint32_t>(min(static_cast<long long>(COPY_CHUNK), blk_bytes - off));
+                last = k == nch - 1;
+            };
+            auto issue_load = [&](long long c) {
+                const char* from; char* to; uint32_t bytes; int gblock; bool last;
+                locate(c, from, to, bytes, gblock, last);
+                const int slot = static_cast<int>(c % COPY_BUFS);
+                mbar_arrive_expect_tx(cbar + 8 * slot, bytes);
+                bulk_load(cbase + slot * COPY_CHUNK, from, bytes, cbar + 8 * slot);
+            };
+            long long issued = 0;
+            for (; issued < total_chunks && issued < COPY_BUFS; ++issued) issue_load(issued);
+            long long c = 0;
+            for (; c < total_chunks; ++c) {
+                const int slot = static_cast<int>(c % COPY_BUFS);
+                if (!mbar_wait_bounded(cbar + 8 * slot, static_cast<uint32_t>((c / COPY_BUFS) & 1), &abort_local,
+                                       WAIT_LIMIT_NS)) {
+                    report_status(status, 0x71);
+                    failed = true;
+                    break;
                 }
-                __threadfence();
-                __syncthreads();
-                if (threadIdx.x == 0)
+                const char* from; char* to; uint32_t bytes; int gblock; bool last;
+                locate(c, from, to, bytes, gblock, last);
+                bulk_store(to, cbase + slot * COPY_CHUNK, bytes);
+                tma_commit_group();
+                if (last) {
+                    tma_wait_group<0>();                                   // the whole block has landed
+                    asm volatile("fence.proxy.async.global;" ::: "memory");
+                    __threadfence();
                     asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(ga.flags + gblock), "r"(ga.epoch) : "memory");
+                }
+                if (issued < total_chunks) {
+                    tma_wait_group_read<0>();                              // the store has read this buffer
+                    issue_load(issued);
+                    ++issued;
+                }
+            }
+            tma_wait_group<0>();
+            if (failed) {
+                // loads still in flight target this CTA's shared memory: give each a bounded chance to land
+                for (long long d = c + 1; d < issued; ++d)
+                    mbar_wait_bounded(cbar + 8 * static_cast<int>(d % COPY_BUFS),
+                                      static_cast<uint32_t>((d / COPY_BUFS) & 1), &abort_local, WAIT_LIMIT_NS);
             }
             return;
         }
@@ -419,25 +466,36 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
                     }
                 }
                 if constexpr (PEER_RED) {
-                    static_assert(!PEER_RED || OUT_F32, "the fused reduce-scatter epilogue accumulates in fp32");
                     epi_bar_sync();
-                    // 128 threads sweep the staged [128 rows][32 fp32] chunk: 8 threads cover one 128-byte row
-                    // segment, so every red instruction of a warp touches four full 128-byte lines of the owner
+                    // 128 threads sweep the staged [128 rows][128 bytes] chunk: 8 threads cover one 128-byte row
+                    // segment, so every instruction of a warp touches four full 128-byte lines of the owner
                     const int e = static_cast<int>(threadIdx.x) - 64;
                     const int j = e & 7;
+                    constexpr int PER16 = OUT_F32 ? 4 : 8;              // elements per 16-byte piece
 #pragma unroll
                     for (int it = 0; it < 8; ++it) {
                         const int r = it * 16 + (e >> 3);
-                        const int grow = m0 + r, gcol = n0 + col0 + j * 4;
+                        const int grow = m0 + r, gcol = n0 + col0 + j * PER16;
                         if (grow < M && gcol < N) {
-                            float4 v;
                             const uint32_t src = sbuf + r * 128 + (((j ^ (r & 7)) & 7) << 4);
-                            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                                         : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(src));
                             const int owner = grow / po.rows_per_rank;
-                            float* dst = po.out[owner] + static_cast<size_t>(grow - owner * po.rows_per_rank) * N + gcol;
-                            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
-                                         ::"l"(dst), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+                            const size_t lrow = static_cast<size_t>(grow - owner * po.rows_per_rank);
+                            if constexpr (OUT_F32) {
+                                float4 v;
+                                asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                             : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(src));
+                                float* dst = static_cast<float*>(po.out[owner]) + lrow * N + gcol;
+                                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                                             ::"l"(dst), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+                            } else {
+                                uint4 v;
+                                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                                             : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(src));
+                                __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(po.out[owner]) +
+                                    (static_cast<size_t>(po.slice) * po.rows_per_rank + lrow) * N + gcol;
+                                asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};"
+                                             ::"l"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+                            }
                         }
                     }
                 } else {
@@ -630,6 +688,35 @@ const char* gemm_reduce_scatter_bf16_tcgen05(const void* a, const void* b, float
     for (int r = 0; r < world; ++r) po.out[r] = peer_out[r];
     po.rows_per_rank = rows_per_rank;
     auto kern = gemm_kernel<false, false, true, true>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return cudaGetErrorString(e);
+        configured = true;
+    }
+    const int num_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int grid = num_tiles < num_sms ? num_tiles : num_sms;
+    kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, ta, M, N, K, 0, status, po, GatherArgs{});
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+}
+
+const char* gemm_scatter_bf16_tcgen05(const void* a, const void* b, void* const* peer_slices, int world, int rank,
+                                      int rows_per_rank, int M, int N, int K, int* status, int num_sms,
+                                      cudaStream_t stream) {
+    if (world < 1 || world > 8 || rank < 0 || rank >= world) return "gemm_scatter: between 1 and 8 ranks are supported";
+    if (rows_per_rank <= 0 || rows_per_rank * world < M) return "gemm_scatter: rows_per_rank * world must cover M";
+    if (N % 8) return "gemm_scatter: N must be a multiple of 8";
+    CUtensorMap ta, tb;
+    g_tmap_err[0] = 0;
+    if (!make_tmap(&ta, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, BM, BK) ||
+        !make_tmap(&tb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, BN, BK))
+        return g_tmap_err;
+    PeerOut po{};
+    for (int r = 0; r < world; ++r) po.out[r] = peer_slices[r];
+    po.rows_per_rank = rows_per_rank;
+    po.slice = rank;
+    auto kern = gemm_kernel<false, false, false, true>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);

@@ -28,4 +28,10 @@ const char* gemm_reduce_scatter_bf16_tcgen05(const void* a, const void* b, float
                                              int rows_per_rank, int M, int N, int K, int* status, int num_sms,
                                              cudaStream_t stream);
 
+// Same GEMM, bf16 scatter form: the tile is rounded to bf16 and stored into slice `rank` of `peer_slices[r]`
+// ([world, rows_per_rank, N] bf16 in rank r's memory). After a cross-rank barrier the owner sums its `world` slices.
+const char* gemm_scatter_bf16_tcgen05(const void* a, const void* b, void* const* peer_slices, int world, int rank,
+                                      int rows_per_rank, int M, int N, int K, int* status, int num_sms,
+                                      cudaStream_t stream);
+
 }  // namespace fs2

@@ -26,23 +26,39 @@ def gemm_reduce_scatter_reference(x_parts: list[Tensor], w_parts: list[Tensor], 
 
 
 class FusedGemmReduceScatter:
+    """Row-parallel linear layer fused with its reduce-scatter: ``out[rank] = (sum_r x_r @ w_r^T)[rows of rank]``.
+
+    The GEMM epilogue sends every output tile over NVLink to the rank that owns its rows while the next tile is on
+    the tensor cores. ``mode="scatter"`` (default): tiles are rounded to bf16 and written with plain stores into this
+    rank's slice of the owner's ``[world, rows, N]`` buffer; after a barrier the owner sums its slices in fp32 (the
+    numerics of a bf16 reduce-scatter, deterministic, 2 bytes per element on the wire). ``mode="red"``: fp32 tiles
+    are summed in place in the owner's buffer with ``red.global.add`` (no rounding of the partial products, 4 bytes
+    per element, summation order not fixed).
+    """
+
     #: barrier slot inside the arena's flag page reserved for this operator family
     SLOT = 40
 
-    def __init__(self, arena: SymmetricArena, max_rows_per_rank: int, out_dim: int) -> None:
-        self.arena = arena
+    def __init__(self, arena: SymmetricArena, max_rows_per_rank: int, out_dim: int, *, mode: str = "scatter",
+                 out_dtype: torch.dtype = torch.bfloat16) -> None:
+        if mode not in ("scatter", "red"):
+            raise ValueError(f"`mode` must be 'scatter' or 'red', but is '{mode}' instead.")
+        self.arena, self.mode, self.out_dtype = arena, mode, out_dtype
         self.max_rows, self.out_dim = max_rows_per_rank, out_dim
-        self._slots = [arena.alloc_tensor(max_rows_per_rank * out_dim, torch.float32) for _ in range(2)]
         self._which = 0
-        self._epoch = 0
-        for _, buf in self._slots:
-            buf.zero_()
-        # every rank's slots are zero before anyone adds into them
-        arena.barrier_next(self.SLOT)
+        if mode == "red":
+            self._slots = [arena.alloc_tensor(max_rows_per_rank * out_dim, torch.float32) for _ in range(2)]
+            for _, buf in self._slots:
+                buf.zero_()
+            # every rank's slots are zero before anyone adds into them
+            arena.barrier_next(self.SLOT)
+        else:
+            self._slots = [arena.alloc_tensor(arena.world * max_rows_per_rank * out_dim, torch.bfloat16)
+                           for _ in range(2)]
 
     def __call__(self, x: Tensor, weight: Tensor) -> Tensor:
-        """``x``: bf16 ``[M, K_local]``, ``weight``: bf16 ``[N, K_local]`` -> fp32 ``[M / world, N]`` (a view into
-        the arena that stays valid until the call after the next one)."""
+        """``x``: bf16 ``[M, K_local]``, ``weight``: bf16 ``[N, K_local]`` -> ``[M / world, N]``. In "red" mode the
+        result is an fp32 view into the arena that stays valid until the call after the next one."""
         arena = self.arena
         M, N = x.shape[0], weight.shape[0]
         if M % arena.world:
@@ -53,10 +69,18 @@ class FusedGemmReduceScatter:
         off, buf = self._slots[self._which]
         nxt_off, nxt = self._slots[self._which ^ 1]
         self._which ^= 1
-        arena.ext.gemm_reduce_scatter(x.contiguous(), weight.contiguous(), arena.peer_ptrs, off, rows)
-        nxt.zero_()                       # the other slot is free again: its last reader ran before this call
-        arena.barrier_next(self.SLOT)     # all ranks' additions have landed (and their next slots are zero)
-        return buf[: rows * N].view(rows, N)
+        if self.mode == "red":
+            arena.ext.gemm_reduce_scatter(x.contiguous(), weight.contiguous(), arena.peer_ptrs, off, rows)
+            nxt.zero_()                       # the other slot is free again: its last reader ran before this call
+            arena.barrier_next(self.SLOT)     # all ranks' additions have landed (and their next slots are zero)
+            return buf[: rows * N].view(rows, N)
+        # two slots alternate: a rank passes the barrier of call k + 1 only after its own sum of call k, so the
+        # slot written by call k + 2 is no longer being read by anyone
+        arena.ext.gemm_scatter(x.contiguous(), weight.contiguous(), arena.peer_ptrs, arena.rank, off, rows)
+        arena.barrier_next(self.SLOT)         # every rank's tiles for my rows have landed
+        out = torch.empty((rows, N), device=x.device, dtype=self.out_dtype)
+        arena.ext.reduce_slices(buf[: arena.world * rows * N].view(arena.world, rows * N), out)
+        return out
 
 
 class FusedAllGatherGemm:

@@ -83,7 +83,7 @@ def main() -> None:
 
     n = (args.unit_params // W + 2047) // 2048 * 2048            # shard elements
     T = args.tokens
-    arena_bytes = ((W + 1) * n * 2 + (128 << 20) + 2 * (T // W) * 4096 * 4 + (T // W + T) * 4096 * 2
+    arena_bytes = ((W + 1) * n * 2 + (128 << 20) + 2 * (T // W) * 4096 * 4 + 2 * T * 4096 * 2 + (T // W + T) * 4096 * 2
                    + (14336 // W + 14336) * 4096 * 2 + (64 << 20))
     arena = SymmetricArena(base, arena_bytes)
     ext = arena.ext
@@ -185,8 +185,10 @@ def main() -> None:
         kl = K_ffn // W
         x = torch.randn(T, kl, device=dev, dtype=torch.bfloat16)
         w = torch.randn(D, kl, device=dev, dtype=torch.bfloat16) * 0.02
-        op = FusedGemmReduceScatter(arena, T // W, D)
+        op = FusedGemmReduceScatter(arena, T // W, D, mode="red")
         ms = _time(lambda: op(x, w), barrier, args.iters)
+        op_s = FusedGemmReduceScatter(arena, T // W, D, mode="scatter")
+        ms_s = _time(lambda: op_s(x, w), barrier, args.iters)
         out = torch.empty(T // W, D, device=dev, dtype=torch.bfloat16)
 
         def unfused() -> None:
@@ -194,9 +196,12 @@ def main() -> None:
             dist.reduce_scatter_tensor(out, y, group=pg)
         nccl = _time(unfused, barrier, args.iters)
         gemm_only = _time(lambda: gemm_nt(x, w), barrier, args.iters)
-        emit("tp_row_gemm_reducescatter_fused", ms, flops=2.0 * T * kl * D, nvlink_bytes=(W - 1) / W * T * D * 4,
+        emit("tp_row_gemm_reducescatter_fused_red_f32", ms, flops=2.0 * T * kl * D, nvlink_bytes=(W - 1) / W * T * D * 4,
              baseline_ms=nccl, gemm_alone_ms=round(gemm_only, 4),
-             note="fused path reduces in fp32 (4 B/element on the wire); baseline = our GEMM + NCCL bf16 reduce-scatter")
+             note="fp32 red.global.add (4 B/element on the wire); baseline = our GEMM + NCCL bf16 reduce-scatter")
+        emit("tp_row_gemm_reducescatter_fused_scatter_bf16", ms_s, flops=2.0 * T * kl * D,
+             nvlink_bytes=(W - 1) / W * T * D * 2, baseline_ms=nccl, gemm_alone_ms=round(gemm_only, 4),
+             note="bf16 tiles stored into the owner's slices + local sum; baseline = our GEMM + NCCL bf16 reduce-scatter")
 
     if want("ag_gemm") and K_ffn % W == 0 and (T // W) % 128 == 0:
         nl = K_ffn // W

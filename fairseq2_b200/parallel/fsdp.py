@@ -134,6 +134,9 @@ class FlatParamUnit:
     allgather_engine = "kernel"
     #: thread blocks of the reduce-scatter kernel
     rs_blocks = 48
+    #: local bf16 buffer of (world - 1) shards shared by all units: when set, the NVLink half of the reduce-scatter
+    #: runs on the copy engines and only the final sum runs on SMs
+    rs_staging: Tensor | None = None
 
     def attach_arena(self, arena: Any, slot: int) -> None:
         """Moves the bf16 shard and the flat gradient buffer into the symmetric
@@ -268,9 +271,15 @@ class FlatParamUnit:
                 if not acc:
                     self.grad_shard = torch.empty(self.shard_size, device=self.device, dtype=torch.float32)
                 self.rs_epoch += 1
-                a.ext.comm_reducescatter_segments(a.peer_ptrs, a.rank, self.seg_offs, self.seg_numels, self.grad_off,
-                                                  self.grad_shard, (1.0 / W) if average else 1.0, acc, 2 + self.slot,
-                                                  self.rs_epoch, self.rs_blocks, a.wait_limit_s)
+                if self.rs_staging is not None:
+                    a.ext.comm_reducescatter_copy(a.peer_ptrs, a.rank, self.seg_offs, self.seg_numels, self.grad_off,
+                                                  self.rs_staging, self.grad_shard, (1.0 / W) if average else 1.0, acc,
+                                                  2 + self.slot, self.rs_epoch, 4 * self.rs_blocks, a.wait_limit_s)
+                else:
+                    a.ext.comm_reducescatter_segments(a.peer_ptrs, a.rank, self.seg_offs, self.seg_numels,
+                                                      self.grad_off, self.grad_shard, (1.0 / W) if average else 1.0,
+                                                      acc, 2 + self.slot, self.rs_epoch, self.rs_blocks,
+                                                      a.wait_limit_s)
             self.grads_ready = True
             for cp in self.compute_params:
                 cp.grad_sink_filled = False  # type: ignore[attr-defined]
@@ -378,7 +387,7 @@ class FSDP(Module):
     def __init__(self, module: Module, gangs: Gangs, *, wrap_policy: FSDPWrapPolicy | None = layerwise_wrap_policy,
                  param_dtype: DataType = torch.bfloat16, fp32_reduce: bool = True,
                  reshard_after_forward: bool = True, overlap: bool = True, comm: str = "auto",
-                 allgather: str = "kernel", rs_blocks: int = 48) -> None:
+                 allgather: str = "copy", reducescatter: str = "kernel", rs_blocks: int = 48) -> None:
         super().__init__()
         self.module = module
         self.gangs = gangs
@@ -454,6 +463,11 @@ class FSDP(Module):
                         u.attach_arena(self.arena, i)
                         u.allgather_engine = engine
                         u.rs_blocks = int(os.environ.get("FAIRSEQ2_B200_FSDP_RS_BLOCKS", rs_blocks))
+                    if os.environ.get("FAIRSEQ2_B200_FSDP_REDUCESCATTER", reducescatter) == "copy":
+                        biggest = max(u.shard_size for u in self.all_units)
+                        staging = torch.empty((W - 1) * biggest, device=dev, dtype=torch.bfloat16)
+                        for u in self.all_units:
+                            u.rs_staging = staging
                     torch.cuda.synchronize(dev)
                     self.gang.barrier()
                 except Exception as ex:  # noqa: BLE001

@@ -137,16 +137,17 @@ def _gemm_rs_worker(rank: int, world: int):
     torch.cuda.set_device(dev)
     base = ProcessGroupGang.create_default_process_group(dev)
     M, N, Kl = 1024, 768, 512
-    arena = SymmetricArena(base, 4 * (M // world) * N * 4 + (1 << 20))
-    op = FusedGemmReduceScatter(arena, M // world, N)
+    arena = SymmetricArena(base, 8 * M * N * 4 + (1 << 20))
     errs = []
-    for it in range(3):                                   # three calls exercise both buffer slots
-        gen = torch.Generator(device="cpu").manual_seed(100 + it)
-        xs = [torch.randn(M, Kl, generator=gen).to(torch.bfloat16) for _ in range(world)]
-        ws = [(torch.randn(N, Kl, generator=gen) * 0.05).to(torch.bfloat16) for _ in range(world)]
-        out = op(xs[rank].to(dev), ws[rank].to(dev))
-        ref = gemm_reduce_scatter_reference(xs, ws, rank).to(dev)
-        errs.append(float((out - ref).norm() / ref.norm()))
+    for mode in ("red", "scatter"):
+        op = FusedGemmReduceScatter(arena, M // world, N, mode=mode)
+        for it in range(3):                                   # three calls exercise both buffer slots
+            gen = torch.Generator(device="cpu").manual_seed(100 + it)
+            xs = [torch.randn(M, Kl, generator=gen).to(torch.bfloat16) for _ in range(world)]
+            ws = [(torch.randn(N, Kl, generator=gen) * 0.05).to(torch.bfloat16) for _ in range(world)]
+            out = op(xs[rank].to(dev), ws[rank].to(dev))
+            ref = gemm_reduce_scatter_reference(xs, ws, rank).to(dev)
+            errs.append(float((out.float() - ref).norm() / ref.norm()))
     torch.cuda.synchronize()
     arena.ext.check_status()
     base.close()
@@ -282,3 +283,40 @@ def test_fused_allgather_gemm() -> None:
     _need_gpus(2)
     for errs in run_distributed(_ag_gemm_worker, 2):
         assert all(e < 1e-2 for e in errs), errs
+
+
+def _missing_peer_worker(rank: int, world: int):
+    """Rank 1 withholds its signal for one barrier: rank 0's wait runs out after 0.3 s, the kernel records a status
+    and returns, the host raises, and the context stays usable for a later barrier that everyone joins."""
+    from fairseq2_b200.gang import ProcessGroupGang
+    from fairseq2_b200.parallel.symm import SymmetricArena
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    base = ProcessGroupGang.create_default_process_group(dev)
+    arena = SymmetricArena(base, 1 << 20, wait_limit_s=0.3)
+    arena.barrier(20, 1)                       # everyone joins: passes
+    torch.cuda.synchronize()
+    arena.ext.check_status()
+    detected = False
+    if rank == 0:
+        arena.barrier(21, 1)                   # nobody else signals slot 21
+        torch.cuda.synchronize()
+        try:
+            arena.ext.check_status()
+        except RuntimeError as ex:
+            detected = "bounded wait" in str(ex)
+    base.barrier()                             # host-side rendezvous between the two phases
+    arena.barrier(22, 1)                       # the GPU context still works on both ranks
+    probe = torch.ones(4, device=dev).sum().item()
+    torch.cuda.synchronize()
+    arena.ext.check_status()
+    base.close()
+    return detected, probe
+
+
+def test_bounded_wait_reports_missing_peer() -> None:
+    _need_gpus(2)
+    results = run_distributed(_missing_peer_worker, 2)
+    assert results[0] == (True, 4.0) and results[1] == (False, 4.0)
