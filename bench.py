@@ -133,7 +133,8 @@ def run_ours(args: argparse.Namespace) -> None:
     torch.manual_seed(2)
     with torch.device("meta"):
         model = create_llama_model(cfg, gangs)
-    fsdp = FSDP(model, gangs, param_dtype=torch.bfloat16, fp32_reduce=True)
+    fsdp = FSDP(model, gangs, param_dtype=torch.bfloat16, fp32_reduce=True,
+                reshard_after_forward=bool(args.reshard_after_forward))
     facade = DataParallelFacade(fsdp)
     optimizer = AdamW(fsdp.parameters(), lr=1e-5, betas=(0.9, 0.95), weight_decay=0.1)
 
@@ -235,7 +236,7 @@ def run_ours(args: argparse.Namespace) -> None:
                        "global_batch": world, "seq_len": seq_len, "parallelism": f"fsdp{world}",
                        "packing": "documents 128-4096 tokens, block-causal, prompt-masked loss",
                        "optimizer": "AdamW lr 1e-5 fp32 state, fp32 master weights, grad clip 1.0",
-                       "activation_checkpointing": False,
+                       "activation_checkpointing": False, "reshard_after_forward": bool(args.reshard_after_forward),
                        "l2": "per-step working set (weights+activations) >> 126 MB L2; inputs differ every step"},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -265,6 +266,8 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="llama3_8b")
     ap.add_argument("--seq-len", type=int, default=8192)
+    ap.add_argument("--reshard-after-forward", type=int, default=1, choices=[0, 1],
+                    help="0 keeps the gathered bf16 weights between forward and backward (one all-gather per step)")
     ap.add_argument("--trace", default=None, metavar="PREFIX",
                     help="after the timed regions, write a kernel timeline of two steps to PREFIX.rankN.json")
     ap.add_argument("--trace-all-ranks", action="store_true")

@@ -188,8 +188,13 @@ void gemm_allgather(const std::vector<int64_t>& ptrs, int64_t rank, int64_t shar
     TORCH_CHECK(out.size(0) == M && out.size(1) == N && K % 8 == 0 && N % 8 == 0, "gemm_allgather: shape mismatch");
     TORCH_CHECK(shard_byte_off % 16 == 0 && gathered_byte_off % 1024 == 0 && flags_byte_off % 4 == 0,
                 "gemm_allgather: unaligned arena offsets");
+    // a negative shard offset means: rank r keeps its shard at slice r of its own gathered buffer
+    const bool inplace = shard_byte_off < 0;
     const void* shards[8];
-    for (int64_t r = 0; r < world; ++r) shards[r] = reinterpret_cast<const void*>(ptrs[static_cast<size_t>(r)] + shard_byte_off);
+    for (int64_t r = 0; r < world; ++r) {
+        const int64_t off = inplace ? gathered_byte_off + r * rows_per_rank * K * 2 : shard_byte_off;
+        shards[r] = reinterpret_cast<const void*>(ptrs[static_cast<size_t>(r)] + off);
+    }
     const int64_t mine = ptrs[static_cast<size_t>(rank)];
     check_status();
     c10::cuda::CUDAGuard guard(other.device());
@@ -198,7 +203,7 @@ void gemm_allgather(const std::vector<int64_t>& ptrs, int64_t rank, int64_t shar
         shards, static_cast<int>(world), static_cast<int>(rank), static_cast<int>(rows_per_rank), other.data_ptr(),
         reinterpret_cast<void*>(mine + gathered_byte_off), reinterpret_cast<unsigned int*>(mine + flags_byte_off),
         static_cast<unsigned int>(epoch), gather_b, out.data_ptr(), static_cast<int>(M), static_cast<int>(N),
-        static_cast<int>(K), static_cast<int>(ncopy), status_dev_ptr(), num_sms(other), stream_of(other));
+        static_cast<int>(K), static_cast<int>(ncopy), inplace, status_dev_ptr(), num_sms(other), stream_of(other));
     TORCH_CHECK(err == nullptr, "gemm_allgather: ", err);
     g_launches += 1;
 }
@@ -370,6 +375,88 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> moe_dispatch(const Tensor& x, const T
                       static_cast<int>(T), static_cast<int>(k), static_cast<int>(D), scale_by_gate, stream_of(x));
     g_launches += 2;
     return {routed, src_row, inv, offsets};
+}
+
+fs2::CommPeers make_peers(const std::vector<int64_t>& ptrs, int64_t rank, double wait_limit_s);
+
+// Expert-parallel routing over the symmetric arena; see moe.h for the protocol.
+std::tuple<Tensor, Tensor, Tensor, Tensor> moe_ep_layout(const std::vector<int64_t>& ptrs, int64_t rank,
+                                                         const Tensor& counts, int64_t table_byte_off, int64_t slot,
+                                                         int64_t epoch, double wait_limit_s) {
+    const int64_t W = static_cast<int64_t>(ptrs.size()), E = counts.numel();
+    TORCH_CHECK(counts.is_cuda() && counts.scalar_type() == at::kInt && counts.is_contiguous() && E % W == 0 && E <= 256,
+                "moe_ep_layout: counts must be an int32 CUDA vector whose length is a multiple of the world size");
+    TORCH_CHECK(table_byte_off % 16 == 0, "moe_ep_layout: unaligned table offset");
+    c10::cuda::CUDAGuard guard(counts.device());
+    auto iopt = counts.options();
+    Tensor send_base = at::empty({E}, iopt), cursor = at::empty({E}, iopt), group_sizes = at::empty({E / W}, iopt),
+           total = at::empty({1}, iopt);
+    fs2::moe_ep_layout(make_peers(ptrs, rank, wait_limit_s), counts.data_ptr<int>(), table_byte_off, static_cast<int>(E),
+                       send_base.data_ptr<int>(), cursor.data_ptr<int>(), group_sizes.data_ptr<int>(),
+                       total.data_ptr<int>(), static_cast<int>(slot), static_cast<uint32_t>(epoch), status_dev_ptr(),
+                       stream_of(counts));
+    g_launches += 1;
+    return {send_base, cursor, group_sizes, total};
+}
+
+void moe_ep_push(const std::vector<int64_t>& ptrs, int64_t rank, const Tensor& x, const std::optional<Tensor>& expert_ids,
+                 const std::optional<Tensor>& gates, const std::optional<Tensor>& send_base,
+                 const std::optional<Tensor>& cursor, int64_t inbox_byte_off, Tensor dest, int64_t E, int64_t cap) {
+    TORCH_CHECK(x.is_cuda() && is_bf16(x) && x.dim() == 2 && x.is_contiguous() && x.size(1) % 8 == 0 && aligned16(x),
+                "moe_ep_push: x must be a contiguous bf16 [T, D] CUDA tensor with D % 8 == 0");
+    TORCH_CHECK(dest.scalar_type() == at::kInt && dest.is_contiguous() && dest.dim() == 2 && dest.size(0) == x.size(0),
+                "moe_ep_push: dest must be int32 [T, k]");
+    const bool assign = expert_ids.has_value();
+    if (assign) {
+        TORCH_CHECK(send_base.has_value() && cursor.has_value() && expert_ids->scalar_type() == at::kInt &&
+                        expert_ids->is_contiguous() && expert_ids->sizes() == dest.sizes() &&
+                        send_base->numel() == E && cursor->numel() == E,
+                    "moe_ep_push: bad routing tensors");
+    }
+    const float* gp = nullptr;
+    if (gates.has_value()) {
+        TORCH_CHECK(gates->scalar_type() == at::kFloat && gates->is_contiguous() && gates->sizes() == dest.sizes(),
+                    "moe_ep_push: gates must be fp32 [T, k]");
+        gp = gates->data_ptr<float>();
+    }
+    TORCH_CHECK(inbox_byte_off % 16 == 0 && cap > 0 && E % static_cast<int64_t>(ptrs.size()) == 0, "moe_ep_push: bad arguments");
+    c10::cuda::CUDAGuard guard(x.device());
+    fs2::moe_ep_push(make_peers(ptrs, rank, 1.0), x.data_ptr(), assign ? expert_ids->data_ptr<int>() : nullptr, gp,
+                     assign ? send_base->data_ptr<int>() : nullptr, assign ? cursor->data_ptr<int>() : nullptr,
+                     inbox_byte_off, dest.data_ptr<int>(), static_cast<int>(x.size(0)), static_cast<int>(dest.size(1)),
+                     static_cast<int>(x.size(1)), static_cast<int>(E), static_cast<int>(cap), assign, stream_of(x));
+    g_launches += 1;
+}
+
+void moe_ep_pull(const std::vector<int64_t>& ptrs, int64_t rank, int64_t outbox_byte_off, const Tensor& dest,
+                 const std::optional<Tensor>& gates, Tensor y, const std::optional<Tensor>& x,
+                 const std::optional<Tensor>& dgate, int64_t cap, bool accumulate) {
+    TORCH_CHECK(y.is_cuda() && is_bf16(y) && y.dim() == 2 && y.is_contiguous() && y.size(1) % 8 == 0 && aligned16(y),
+                "moe_ep_pull: y must be a contiguous bf16 [T, D] CUDA tensor with D % 8 == 0");
+    TORCH_CHECK(dest.scalar_type() == at::kInt && dest.is_contiguous() && dest.dim() == 2 && dest.size(0) == y.size(0) &&
+                    dest.size(1) <= 8,
+                "moe_ep_pull: dest must be int32 [T, k <= 8]");
+    const float* gp = nullptr;
+    if (gates.has_value()) {
+        TORCH_CHECK(gates->scalar_type() == at::kFloat && gates->is_contiguous() && gates->sizes() == dest.sizes(),
+                    "moe_ep_pull: gates must be fp32 [T, k]");
+        gp = gates->data_ptr<float>();
+    }
+    const void* xp = nullptr;
+    float* dgp = nullptr;
+    if (x.has_value()) {
+        TORCH_CHECK(dgate.has_value() && is_bf16(*x) && x->is_contiguous() && x->sizes() == y.sizes() &&
+                        dgate->scalar_type() == at::kFloat && dgate->is_contiguous() && dgate->sizes() == dest.sizes(),
+                    "moe_ep_pull: x must match y and dgate must be fp32 [T, k]");
+        xp = x->data_ptr();
+        dgp = dgate->data_ptr<float>();
+    }
+    TORCH_CHECK(outbox_byte_off % 16 == 0 && cap > 0, "moe_ep_pull: bad arguments");
+    c10::cuda::CUDAGuard guard(y.device());
+    fs2::moe_ep_pull(make_peers(ptrs, rank, 1.0), outbox_byte_off, dest.data_ptr<int>(), gp, y.data_ptr(), xp, dgp,
+                     static_cast<int>(y.size(0)), static_cast<int>(dest.size(1)), static_cast<int>(y.size(1)),
+                     static_cast<int>(cap), accumulate, stream_of(y));
+    g_launches += 1;
 }
 
 // y[t] (+)= sum_j gate[t, j] * routed[inv[t, j]]
@@ -931,6 +1018,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("moe_route", &moe_route);
     m.def("moe_dispatch", &moe_dispatch);
     m.def("moe_combine", &moe_combine);
+    m.def("moe_ep_layout", &moe_ep_layout);
+    m.def("moe_ep_push", &moe_ep_push);
+    m.def("moe_ep_pull", &moe_ep_pull);
     m.def("ngram_repeat_block", &ngram_repeat_block);
     m.def("sample_top_p_top_k", &sample_top_p_top_k);
     m.def("beam_topk", &beam_topk);

@@ -138,6 +138,7 @@ struct GatherArgs {
     int rank;
     int world;
     long long row_bytes;
+    int inplace;        // the own shard already sits at its place in `dst`: only the peers' shards are copied
 };
 
 // PEER_RED: instead of storing C locally, every tile goes straight into the memory of the rank that owns its rows,
@@ -175,13 +176,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
             const int total = per_rank * ga.world;
             const long long blk_bytes = static_cast<long long>(GBLK) * ga.row_bytes;
             const int nch = static_cast<int>((blk_bytes + COPY_CHUNK - 1) / COPY_CHUNK);
-            const int my_blocks = (total - static_cast<int>(blockIdx.x) + ga.ncopy - 1) / ga.ncopy;
+            const int first = ga.inplace ? per_rank : 0;      // arrival order starts with the own shard
+            if (ga.inplace && blockIdx.x == 0) {
+                for (int b = 0; b < per_rank; ++b)
+                    asm volatile("st.release.gpu.global.u32 [%0], %1;"
+                                 ::"l"(ga.flags + ga.rank * per_rank + b), "r"(ga.epoch) : "memory");
+            }
+            const int mine = total - first - static_cast<int>(blockIdx.x);
+            const int my_blocks = mine > 0 ? (mine + ga.ncopy - 1) / ga.ncopy : 0;
             const long long total_chunks = static_cast<long long>(my_blocks) * nch;
             int abort_local = 0;
             bool failed = false;
             // chunk c -> (source, destination, bytes, block, last chunk of its block?)
             auto locate = [&](long long c, const char*& from, char*& to, uint32_t& bytes, int& gblock, bool& last) {
-                const int i = static_cast<int>(blockIdx.x) + static_cast<int>(c / nch) * ga.ncopy;
+                const int i = first + static_cast<int>(blockIdx.x) + static_cast<int>(c / nch) * ga.ncopy;
                 const int k = static_cast<int>(c % nch);
                 const int src_rank = (ga.rank + i / per_rank) % ga.world;
                 const int bi = i % per_rank;
@@ -622,8 +630,8 @@ const char* gemm_bf16_tcgen05(const void* a, const void* b, void* c, int M, int 
 // `gathered` is local scratch for the assembled operand, `flags` one zero-initialised word per block.
 const char* gemm_allgather_bf16_tcgen05(const void* const* shards, int world, int rank, int rows_per_rank,
                                         const void* other, void* gathered, unsigned int* flags, unsigned int epoch,
-                                        bool gather_b, void* c, int M, int N, int K, int ncopy, int* status,
-                                        int num_sms, cudaStream_t stream) {
+                                        bool gather_b, void* c, int M, int N, int K, int ncopy, bool inplace,
+                                        int* status, int num_sms, cudaStream_t stream) {
     if (world < 1 || world > 8) return "gemm_allgather: between 1 and 8 ranks are supported";
     const int blk = gather_b ? BN : BM;
     if (rows_per_rank % blk) return "gemm_allgather: the shard height must be a multiple of the tile height";
@@ -643,6 +651,7 @@ const char* gemm_allgather_bf16_tcgen05(const void* const* shards, int world, in
     ga.rank = rank;
     ga.world = world;
     ga.row_bytes = static_cast<long long>(K) * 2;
+    ga.inplace = inplace ? 1 : 0;
     const int num_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     if (ncopy < 1) ncopy = 1;
     if (ncopy > num_sms / 4) ncopy = num_sms / 4;

@@ -18,8 +18,8 @@ const char* gemm_bf16_tcgen05(const void* a, const void* b, void* c, int M, int 
 // (zero before the first call; `epoch` must grow by one per call), `ncopy` the number of CTAs that move data.
 const char* gemm_allgather_bf16_tcgen05(const void* const* shards, int world, int rank, int rows_per_rank,
                                         const void* other, void* gathered, unsigned int* flags, unsigned int epoch,
-                                        bool gather_b, void* c, int M, int N, int K, int ncopy, int* status,
-                                        int num_sms, cudaStream_t stream);
+                                        bool gather_b, void* c, int M, int N, int K, int ncopy, bool inplace,
+                                        int* status, int num_sms, cudaStream_t stream);
 
 // Row-parallel GEMM fused with its reduce-scatter: C = A[M,K] * B[N,K]^T is never stored locally; every fp32
 // tile is added into `peer_out[r]` ([rows_per_rank, N] fp32 in rank r's memory, zeroed beforehand), where r owns

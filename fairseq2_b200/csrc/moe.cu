@@ -6,6 +6,7 @@
 #include <cfloat>
 #include <cstdint>
 
+#include "comm_dev.cuh"
 #include "common.cuh"
 #include "moe.h"
 
@@ -168,6 +169,158 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* _
     }
 }
 
+// ------------------------------------------------------------------ expert parallelism over peer memory
+//
+// W ranks, E experts, rank r owns experts [r * El, (r + 1) * El). The all-to-alls of the classic formulation are
+// folded into the routing kernels: dispatch STORES each token row straight into the owning rank's inbox, combine
+// LOADS each token's expert outputs straight from the owners' outboxes. Row positions are agreed on without a
+// second exchange: every rank publishes its per-expert counts to everyone, after which each rank can compute the
+// layout of every inbox (rows ordered by expert, then by source rank, then by arrival).
+
+// One block. Publishes counts[E] into row `rank` of every peer's [W, E] table, waits (bounded) until all rows of
+// the own table arrived, then derives
+//   send_base[e]  : first inbox row (at the owner of e) of this rank's rows for expert e
+//   group_sizes[i]: rows that local expert i receives from all ranks;  total[0] = their sum
+//   cursor[e] = 0
+__global__ void __launch_bounds__(256) moe_ep_layout_kernel(CommPeers peers, const int* __restrict__ counts,
+                                                            long long table_byte_off, int E, int El,
+                                                            int* __restrict__ send_base, int* __restrict__ cursor,
+                                                            int* __restrict__ group_sizes, int* __restrict__ total,
+                                                            int slot, uint32_t epoch, int* status) {
+    const int W = peers.world;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        const int c = counts[e];
+        for (int r = 0; r < W; ++r) {
+            int* tbl = reinterpret_cast<int*>(static_cast<char*>(peers.base[r]) + table_byte_off);
+            tbl[peers.rank * E + e] = c;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (!signal_and_wait(peers, slot, epoch, true, status, 40)) return;
+    const volatile int* tbl = reinterpret_cast<const volatile int*>(static_cast<char*>(peers.base[peers.rank]) + table_byte_off);
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        const int owner_first = (e / El) * El;
+        int base = 0;
+        for (int e2 = owner_first; e2 < e; ++e2)
+            for (int s = 0; s < W; ++s) base += tbl[s * E + e2];
+        for (int s = 0; s < peers.rank; ++s) base += tbl[s * E + e];
+        send_base[e] = base;
+        cursor[e] = 0;
+    }
+    for (int i = threadIdx.x; i < El; i += blockDim.x) {
+        int n = 0;
+        for (int s = 0; s < W; ++s) n += tbl[s * E + peers.rank * El + i];
+        group_sizes[i] = n;
+    }
+    if (threadIdx.x == 0) {
+        int n = 0;
+        for (int i = 0; i < El; ++i)
+            for (int s = 0; s < W; ++s) n += tbl[s * E + peers.rank * El + i];
+        total[0] = n;
+    }
+}
+
+// One warp per (token, choice): stores x[t] (* gate) into row `dest[t, j] % cap` of the inbox of rank
+// `dest[t, j] / cap`. With `assign` the destination is chosen here (send_base + arrival order) and recorded in
+// `dest`; without it the rows go where an earlier call put them (used by the backward of combine).
+__global__ void __launch_bounds__(256) moe_ep_push_kernel(CommPeers peers, const __nv_bfloat16* __restrict__ x,
+                                                          const int* __restrict__ expert_ids,
+                                                          const float* __restrict__ gates,
+                                                          const int* __restrict__ send_base, int* __restrict__ cursor,
+                                                          long long inbox_byte_off, int* __restrict__ dest, int rows,
+                                                          int k, int D, int El, int cap, int assign) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= rows) return;
+    const int t = warp / k;
+    int d = 0;
+    if (lane == 0) {
+        if (assign) {
+            const int e = expert_ids[warp];
+            const int row = send_base[e] + atomicAdd(&cursor[e], 1);
+            d = row < cap ? (e / El) * cap + row : -1;          // a full inbox drops the row (combine reads zero)
+            dest[warp] = d;
+        } else {
+            d = dest[warp];
+        }
+    }
+    d = __shfl_sync(0xffffffffu, d, 0);
+    if (d < 0) return;
+    const float g = gates ? gates[warp] : 1.f;
+    const __nv_bfloat16* src = x + static_cast<size_t>(t) * D;
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(peers.base[d / cap]) + inbox_byte_off) +
+                         static_cast<size_t>(d % cap) * D;
+    for (int c = lane * 8; c < D; c += 256) {
+        float f[8];
+        load8(src, c, f);
+        if (gates) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] *= g;
+        }
+        const bf16x8 p = pack8(f);
+        st16(dst + c, *reinterpret_cast<const uint4*>(&p));
+    }
+}
+
+// One warp per token: y[t] (+)= sum_j gate[t, j] * outbox(dest[t, j]) with 16-byte peer loads. If `x` is given,
+// dgate[t, j] = <outbox row, x[t]> is produced as well (the gradient of a gate that scaled the pushed row).
+__global__ void __launch_bounds__(256) moe_ep_pull_kernel(CommPeers peers, long long outbox_byte_off,
+                                                          const int* __restrict__ dest,
+                                                          const float* __restrict__ gates,
+                                                          __nv_bfloat16* __restrict__ y,
+                                                          const __nv_bfloat16* __restrict__ x,
+                                                          float* __restrict__ dgate, int T_, int k, int D, int cap,
+                                                          int accumulate) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= T_) return;
+    __nv_bfloat16* dst = y + static_cast<size_t>(warp) * D;
+    float dots[MAX_K];
+#pragma unroll
+    for (int j = 0; j < MAX_K; ++j) dots[j] = 0.f;
+    for (int c = lane * 8; c < D; c += 256) {
+        float acc[8];
+        if (accumulate) load8(dst, c, acc);
+        else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+        }
+        float xv[8];
+        if (x) load8(x + static_cast<size_t>(warp) * D, c, xv);
+#pragma unroll
+        for (int j = 0; j < MAX_K; ++j) {
+            if (j >= k) break;
+            const int d = dest[warp * k + j];
+            if (d < 0) continue;
+            const __nv_bfloat16* src =
+                reinterpret_cast<const __nv_bfloat16*>(static_cast<const char*>(peers.base[d / cap]) + outbox_byte_off) +
+                static_cast<size_t>(d % cap) * D;
+            const uint4 raw = ld_peer16(src + c);
+            bf16x8 p;
+            *reinterpret_cast<uint4*>(&p) = raw;
+            float f[8];
+            unpack8(p, f);
+            const float g = gates ? gates[warp * k + j] : 1.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] += g * f[i];
+            if (x) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) dots[j] += f[i] * xv[i];
+            }
+        }
+        store8(dst, c, acc);
+    }
+    if (x && dgate) {
+#pragma unroll
+        for (int j = 0; j < MAX_K; ++j) {
+            if (j >= k) break;
+            const float s = warp_sum(dots[j]);
+            if (lane == 0) dgate[warp * k + j] = s;
+        }
+    }
+}
+
 }  // namespace
 
 void moe_route(const void* logits, bool bf16, int T, int E, int k, bool softmax_gate, int* expert_ids, float* gates,
@@ -203,6 +356,32 @@ void moe_combine(const void* routed, const int* inv, const float* slot_gates, vo
     const int blocks = (T * 32 + 255) / 256;
     moe_combine_kernel<<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(routed), inv, slot_gates,
                                                static_cast<__nv_bfloat16*>(y), T, k, D, accumulate ? 1 : 0);
+}
+
+void moe_ep_layout(const CommPeers& peers, const int* counts, long long table_byte_off, int E, int* send_base,
+                   int* cursor, int* group_sizes, int* total, int slot, uint32_t epoch, int* status, cudaStream_t st) {
+    moe_ep_layout_kernel<<<1, 256, 0, st>>>(peers, counts, table_byte_off, E, E / peers.world, send_base, cursor,
+                                            group_sizes, total, slot, epoch, status);
+}
+
+void moe_ep_push(const CommPeers& peers, const void* x, const int* expert_ids, const float* gates, const int* send_base,
+                 int* cursor, long long inbox_byte_off, int* dest, int T, int k, int D, int E, int cap, bool assign,
+                 cudaStream_t st) {
+    const int rows = T * k;
+    if (rows == 0) return;
+    const int blocks = (rows * 32 + 255) / 256;
+    moe_ep_push_kernel<<<blocks, 256, 0, st>>>(peers, static_cast<const __nv_bfloat16*>(x), expert_ids, gates, send_base,
+                                               cursor, inbox_byte_off, dest, rows, k, D, E / peers.world, cap,
+                                               assign ? 1 : 0);
+}
+
+void moe_ep_pull(const CommPeers& peers, long long outbox_byte_off, const int* dest, const float* gates, void* y,
+                 const void* x, float* dgate, int T, int k, int D, int cap, bool accumulate, cudaStream_t st) {
+    if (T == 0) return;
+    const int blocks = (T * 32 + 255) / 256;
+    moe_ep_pull_kernel<<<blocks, 256, 0, st>>>(peers, outbox_byte_off, dest, gates, static_cast<__nv_bfloat16*>(y),
+                                               static_cast<const __nv_bfloat16*>(x), dgate, T, k, D, cap,
+                                               accumulate ? 1 : 0);
 }
 
 }  // namespace fs2

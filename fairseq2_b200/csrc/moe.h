@@ -3,6 +3,10 @@
 
 #include <cuda_runtime.h>
 
+#include <cstdint>
+
+#include "comm.h"
+
 namespace fs2 {
 
 // Per token: top-k of `logits` [T, E] (bf16 or fp32), gate = sigmoid(logit) or softmax over the selected k;
@@ -23,5 +27,23 @@ void moe_dispatch(const void* x, const int* expert_ids, const float* gates, cons
 // as a gather per token through inv[t, j] = p. bf16 in/out, fp32 accumulation.
 void moe_combine(const void* routed, const int* inv, const float* slot_gates, void* y, int T, int k, int D,
                  bool accumulate, cudaStream_t st);
+
+// Expert parallelism over peer memory (rank r owns experts [r * E / W, (r + 1) * E / W)).
+//
+// moe_ep_layout: one block; publishes counts[E] to every peer's [W, E] table at `table_byte_off`, waits (bounded,
+// epoch flag `slot`) for all rows, then fills send_base[E], cursor[E] = 0, group_sizes[E / W], total[1].
+void moe_ep_layout(const CommPeers& peers, const int* counts, long long table_byte_off, int E, int* send_base,
+                   int* cursor, int* group_sizes, int* total, int slot, uint32_t epoch, int* status, cudaStream_t st);
+
+// moe_ep_push: row (t, j) of x [T, D] (* gate if given) is stored into the inbox (at `inbox_byte_off`, `cap` rows of
+// D bf16) of the rank owning its expert. `assign`: positions are taken from send_base/cursor and written to
+// dest[t, j] = owner * cap + row (-1 if the inbox is full); otherwise dest is read.
+void moe_ep_push(const CommPeers& peers, const void* x, const int* expert_ids, const float* gates, const int* send_base,
+                 int* cursor, long long inbox_byte_off, int* dest, int T, int k, int D, int E, int cap, bool assign,
+                 cudaStream_t st);
+
+// moe_ep_pull: y[t] (+)= sum_j gate[t, j] * outbox row dest[t, j] (peer loads); optionally dgate[t, j] = <row, x[t]>.
+void moe_ep_pull(const CommPeers& peers, long long outbox_byte_off, const int* dest, const float* gates, void* y,
+                 const void* x, float* dgate, int T, int k, int D, int cap, bool accumulate, cudaStream_t st);
 
 }  // namespace fs2

@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import math
 from abc import ABC, abstractmethod
+from typing import Any
 
 import torch
 from torch import Tensor
@@ -112,7 +113,11 @@ class MoE(FeedForwardNetwork):
     def __init__(self, model_dim: int, inner_dim: int, use_shared_expert: bool, num_experts: int,
                  capacity_factor: float, top_k: int, *, moe_activation: Module | None = None,
                  inner_dim_scale: float = 2 / 3, inner_dim_to_multiple: int = 1, auto_scale: bool = True,
-                 tp_gang: Gang | None = None, device: Device | None = None, dtype: DataType | None = None) -> None:
+                 tp_gang: Gang | None = None, ep: Any | None = None, device: Device | None = None,
+                 dtype: DataType | None = None) -> None:
+        """``ep``: an ``ops.moe_ep.ExpertParallelExchange``. When given, this rank holds only its
+        ``num_experts / ep.arena.world`` experts and tokens travel to the owning rank inside the dispatch kernel and
+        back inside the combine kernel; the router and the shared expert stay replicated."""
         super().__init__(model_dim)
         if inner_dim_scale != 1.0:
             inner_dim = int(inner_dim * inner_dim_scale)
@@ -128,9 +133,17 @@ class MoE(FeedForwardNetwork):
             self.shared_expert = GLUFeedForwardNetwork(model_dim, inner_dim, bias=False, inner_dim_scale=1.0,
                                                        device=device, dtype=dtype)
         self.router = Parameter(torch.empty((model_dim, num_experts), device=device, dtype=dtype))
-        if self.tp_gang is not None:
-            self.experts: ExpertNetwork = TPShardedExpertNetwork(self.tp_gang, num_experts, model_dim, inner_dim,
-                                                                 activation=moe_activation, device=device, dtype=dtype)
+        self.ep = ep
+        if ep is not None:
+            if self.tp_gang is not None:
+                raise ValueError("Expert parallelism and tensor-parallel experts are mutually exclusive.")
+            if ep.num_experts != num_experts or ep.model_dim != model_dim:
+                raise ValueError("`ep` was created for a different number of experts or model dimension.")
+            self.experts: ExpertNetwork = GroupedExpertNetwork(ep.num_local_experts, model_dim, inner_dim,
+                                                               activation=moe_activation, device=device, dtype=dtype)
+        elif self.tp_gang is not None:
+            self.experts = TPShardedExpertNetwork(self.tp_gang, num_experts, model_dim, inner_dim,
+                                                  activation=moe_activation, device=device, dtype=dtype)
         else:
             self.experts = GroupedExpertNetwork(num_experts, model_dim, inner_dim, activation=moe_activation,
                                                 device=device, dtype=dtype)
@@ -145,6 +158,14 @@ class MoE(FeedForwardNetwork):
         logits = x @ self.router
         from fairseq2_b200.ops import moe as moe_ops
 
+        if self.ep is not None:
+            if not moe_ops.moe_kernels_available(x, logits):
+                raise RuntimeError("Expert parallelism needs the CUDA routing kernels (bf16 activations on a GPU).")
+            ids, gates, counts = moe_ops.moe_route(logits, self.top_k)
+            rows, dest, group_sizes = self.ep.dispatch(x, ids, counts, gates=gates)
+            rows_out = self.experts(rows, group_sizes.tolist())
+            base = self.shared_expert(x) if self.shared_expert is not None else None
+            return self.ep.combine(rows_out, dest, x.shape[0], base=base).view(seqs.shape)
         if moe_ops.moe_kernels_available(x, logits):
             # fused top-k gate + histogram, gather/scale into expert order, experts, gather back per token
             ids, gates, counts = moe_ops.moe_route(logits, self.top_k)

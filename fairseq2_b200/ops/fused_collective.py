@@ -91,7 +91,7 @@ class FusedAllGatherGemm:
     unshard: every rank holds ``[N / W, K]`` rows of the weight and all of the activations.
 
     A few CTAs of the GEMM grid copy the peers' shards over NVLink into local memory -- each byte crosses once,
-    own shard first, then the peers in ring order -- and raise one flag per tile-height block; the TMA producers
+    own shard (already in place) first, then the peers in ring order -- and raise one flag per tile-height block; the TMA producers
     of the compute CTAs wait for the flag of the block they need. The GEMM therefore starts at once on local data
     and the remaining transfers overlap tensor-core work inside the same kernel.
 
@@ -109,9 +109,10 @@ class FusedAllGatherGemm:
             raise ValueError(f"`rows_per_rank` must be a multiple of {blk} for gather='{gather}'.")
         self.arena, self.rows, self.k, self.gather_b = arena, rows_per_rank, k, gather == "b"
         self.ncopy = num_copy_ctas
-        self._shard_off, self.shard = arena.alloc_tensor(rows_per_rank * k, torch.bfloat16)
-        self.shard = self.shard.view(rows_per_rank, k)
-        self._gathered_off, _ = arena.alloc(arena.world * rows_per_rank * k * 2, align=1024)
+        # the own shard lives at its final place inside the gathered operand, so it is never copied
+        self._gathered_off, gathered = arena.alloc(arena.world * rows_per_rank * k * 2, align=1024)
+        self.shard = gathered.view(torch.bfloat16).view(arena.world, rows_per_rank, k)[arena.rank]
+        self._shard_off = -16
         nblocks = arena.world * rows_per_rank // blk
         self._flags_off, flags = arena.alloc(4 * nblocks, align=16)
         flags.zero_()

@@ -23,6 +23,14 @@ The design is its own and B200-first:
   unit (fp32 master, moments) and refreshes the bf16 shard in the same pass.
   Loss normalisation and clipping factors stay on the device and are applied
   inside that launch (no separate gradient scaling pass, no host sync).
+* Inside one NVSwitch box the collectives run over a symmetric-memory arena without NCCL. By default the
+  bytes move on the copy engines (``allgather="copy"``, ``reducescatter="copy"``): peer-to-peer copies of the
+  peers' shards (all-gather) or of the peers' slices of the local gradient shard into a staging buffer followed
+  by one short local fp32 sum (reduce-scatter), ordered by epoch flags that tiny kernels signal and wait on
+  with bounded spins. No SM is occupied while data is on the wire, which matters because the persistent GEMMs
+  assign tiles to SMs statically: a co-resident load/store kernel slows whole GEMMs, not just its own SMs
+  (measured on 4 GPUs: 432 ms/step with load/store kernels, 406 ms with copy engines). ``"kernel"`` selects
+  the load/store kernels, which are the better choice for small units where launch latency dominates.
 * With one rank the unit degenerates gracefully: the bf16 buffer is the full
   parameter, the flat bf16 gradient is the "reduced" gradient.
 """
@@ -387,7 +395,7 @@ class FSDP(Module):
     def __init__(self, module: Module, gangs: Gangs, *, wrap_policy: FSDPWrapPolicy | None = layerwise_wrap_policy,
                  param_dtype: DataType = torch.bfloat16, fp32_reduce: bool = True,
                  reshard_after_forward: bool = True, overlap: bool = True, comm: str = "auto",
-                 allgather: str = "copy", reducescatter: str = "kernel", rs_blocks: int = 48) -> None:
+                 allgather: str = "copy", reducescatter: str = "copy", rs_blocks: int = 48) -> None:
         super().__init__()
         self.module = module
         self.gangs = gangs

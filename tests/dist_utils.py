@@ -39,11 +39,18 @@ def run_distributed(fn: Callable[..., Any], world: int, *args: Any, timeout: flo
     errors: list[str] = []
     try:
         for _ in range(world):
-            rank, status, payload = out.get(timeout=timeout)
+            try:
+                rank, status, payload = out.get(timeout=timeout)
+            except Exception:  # noqa: BLE001 - queue.Empty: a rank never reported
+                missing = sorted(set(range(world)) - set(results) - {int(e.split("]")[0][6:]) for e in errors})
+                errors.append(f"rank(s) {missing} did not report within {timeout} s")
+                break
             if status == "ok":
                 results[rank] = payload
             else:
                 errors.append(f"[rank {rank}] {payload}")
+                if world > 1:
+                    timeout = min(timeout, 20.0)    # the others are probably stuck waiting for the failed rank
     finally:
         for p in procs:
             p.join(timeout=10)
