@@ -19,6 +19,7 @@
 #include "gemm_tcgen05.h"
 #include "generation.h"
 #include "moe.h"
+#include "wav2vec2.h"
 
 namespace {
 
@@ -127,6 +128,36 @@ void gemm_reduce_scatter(const Tensor& a, const Tensor& b, const std::vector<int
         static_cast<int>(a.size(0)), static_cast<int>(b.size(0)), static_cast<int>(a.size(1)), status_dev_ptr(),
         num_sms(a), stream_of(a));
     TORCH_CHECK(err == nullptr, "gemm_reduce_scatter: ", err);
+    g_launches += 1;
+}
+
+// GEMM over strided views of flat bf16 storage. Each operand is (storage, rows in memory, row pitch in elements);
+// logical shapes: A [M, K] (or [K, M] if a_mn), B [N, K] (or [K, N] if b_mn), out [M, N] bf16/fp32.
+void gemm_bf16_view(const Tensor& a, int64_t a_rows, int64_t lda, bool a_mn, const Tensor& b, int64_t b_rows, int64_t ldb,
+                    bool b_mn, Tensor out, int64_t c_rows, int64_t ldc, int64_t M, int64_t N, int64_t K,
+                    bool accumulate) {
+    TORCH_CHECK(a.is_cuda() && b.is_cuda() && out.is_cuda() && is_bf16(a) && is_bf16(b) && a.is_contiguous() &&
+                    b.is_contiguous() && out.is_contiguous() && aligned16(a) && aligned16(b) && aligned16(out),
+                "gemm_bf16_view: operands must be contiguous, 16-byte aligned CUDA storage (bf16 inputs)");
+    const bool f32 = out.scalar_type() == at::kFloat;
+    TORCH_CHECK(f32 || is_bf16(out), "gemm_bf16_view: out must be bfloat16 or float32");
+    const int64_t a_cols = a_mn ? M : K, b_cols = b_mn ? N : K;
+    const int64_t esz_c = f32 ? 4 : 2;
+    TORCH_CHECK(M > 0 && N > 0 && K > 0 && lda > 0 && ldb > 0 && ldc > 0 && a_rows > 0 && b_rows > 0 && c_rows > 0,
+                "gemm_bf16_view: sizes must be positive");
+    TORCH_CHECK((lda * 2) % 16 == 0 && (ldb * 2) % 16 == 0 && (ldc * esz_c) % 16 == 0 &&
+                    ((a_mn && b_mn) || K % 8 == 0) && (a_mn ? M % 8 == 0 : true) && (b_mn ? N % 8 == 0 : true) && (N * esz_c) % 16 == 0,
+                "gemm_bf16_view: row pitches and row lengths must be multiples of 16 bytes");
+    TORCH_CHECK((a_rows - 1) * lda + a_cols <= a.numel() && (b_rows - 1) * ldb + b_cols <= b.numel() &&
+                    (c_rows - 1) * ldc + N <= out.numel(),
+                "gemm_bf16_view: a view reaches beyond its storage");
+    check_status();
+    c10::cuda::CUDAGuard guard(a.device());
+    TORCH_CHECK(cudaSetDevice(a.get_device()) == cudaSuccess, "gemm_bf16_view: cudaSetDevice failed");
+    const char* err = fs2::gemm_bf16_tcgen05_view(a.data_ptr(), lda, a_rows, b.data_ptr(), ldb, b_rows, out.data_ptr(), ldc,
+                                                  c_rows, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K),
+                                                  a_mn, b_mn, f32, accumulate, status_dev_ptr(), num_sms(a), stream_of(a));
+    TORCH_CHECK(err == nullptr, "gemm_bf16_view: ", err);
     g_launches += 1;
 }
 
@@ -244,7 +275,9 @@ std::tuple<Tensor, Tensor> rms_norm_bwd(const Tensor& dy, const Tensor& x, const
     return {dx, dw};
 }
 
-std::tuple<Tensor, Tensor, Tensor> layer_norm_fwd(const Tensor& x, const Tensor& w, const Tensor& b, double eps) {
+std::tuple<Tensor, Tensor, Tensor> layer_norm_fwd(const Tensor& x, const Tensor& w, const Tensor& b, double eps,
+                                                  bool gelu) {
+    TORCH_CHECK(!gelu || is_bf16(x), "layer_norm_fwd: the fused GELU needs bf16");
     TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous() && w.is_contiguous() && b.is_contiguous(),
                 "layer_norm_fwd: bad input");
     TORCH_CHECK(x.scalar_type() == w.scalar_type() && x.scalar_type() == b.scalar_type() &&
@@ -261,13 +294,17 @@ std::tuple<Tensor, Tensor, Tensor> layer_norm_fwd(const Tensor& x, const Tensor&
     if (rows > 0)
         fs2::layer_norm_fwd(x.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), mean.data_ptr<float>(),
                             rstd.data_ptr<float>(), rows, D, static_cast<float>(eps), is_bf16(x), num_sms(x),
-                            stream_of(x));
+                            stream_of(x), gelu);
     g_launches += 1;
     return {y, mean, rstd};
 }
 
 std::tuple<Tensor, Tensor, Tensor> layer_norm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w,
-                                                  const Tensor& mean, const Tensor& rstd) {
+                                                  const Tensor& mean, const Tensor& rstd,
+                                                  const std::optional<Tensor>& b_for_gelu) {
+    TORCH_CHECK(!b_for_gelu.has_value() || (is_bf16(x) && is_bf16(*b_for_gelu) && b_for_gelu->is_contiguous() &&
+                                            b_for_gelu->numel() == x.size(1)),
+                "layer_norm_bwd: the fused GELU needs bf16 and the bias");
     TORCH_CHECK(dy.is_cuda() && dy.is_contiguous() && x.is_contiguous() && dy.sizes() == x.sizes(),
                 "layer_norm_bwd: bad input");
     const int rows = static_cast<int>(x.size(0)), D = static_cast<int>(x.size(1));
@@ -281,7 +318,8 @@ std::tuple<Tensor, Tensor, Tensor> layer_norm_bwd(const Tensor& dy, const Tensor
         fs2::layer_norm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), mean.data_ptr<float>(),
                             rstd.data_ptr<float>(), dx.data_ptr(), part[0].data_ptr<float>(),
                             part[1].data_ptr<float>(), dw.data_ptr<float>(), db.data_ptr<float>(), rows, D,
-                            is_bf16(x), num_sms(x), stream_of(x));
+                            is_bf16(x), num_sms(x), stream_of(x),
+                            b_for_gelu.has_value() ? b_for_gelu->data_ptr() : nullptr);
         g_launches += 3;
     }
     return {dx, dw, db};
@@ -375,6 +413,98 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> moe_dispatch(const Tensor& x, const T
                       static_cast<int>(T), static_cast<int>(k), static_cast<int>(D), scale_by_gate, stream_of(x));
     g_launches += 2;
     return {routed, src_row, inv, offsets};
+}
+
+// ------------------------------------------------------------------ wav2vec 2.0 objective
+// returns (logits [P, K + 1] fp32, lse [P] fp32, loss_sum [1] fp32)
+std::tuple<Tensor, Tensor, Tensor> w2v_contrastive_fwd(const Tensor& x, const Tensor& tgt, const Tensor& distractors,
+                                                       double temp) {
+    TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous() && tgt.is_contiguous() && tgt.sizes() == x.sizes() &&
+                    x.scalar_type() == tgt.scalar_type() && (is_bf16(x) || x.scalar_type() == at::kFloat),
+                "w2v_contrastive_fwd: x and targets must be contiguous [P, M] bf16/fp32 CUDA tensors");
+    TORCH_CHECK(distractors.scalar_type() == at::kInt && distractors.is_contiguous() && distractors.dim() == 2 &&
+                    distractors.size(0) == x.size(0) && x.size(1) <= 1024,
+                "w2v_contrastive_fwd: distractors must be int32 [P, K]; feature dim <= 1024");
+    const int64_t P = x.size(0), M = x.size(1), K = distractors.size(1);
+    c10::cuda::CUDAGuard guard(x.device());
+    auto fopt = x.options().dtype(at::kFloat);
+    Tensor logits = at::empty({P, K + 1}, fopt), lse = at::empty({P}, fopt), loss = at::zeros({1}, fopt);
+    fs2::w2v_contrastive_fwd(x.data_ptr(), tgt.data_ptr(), is_bf16(x), distractors.data_ptr<int>(), static_cast<int>(P),
+                             static_cast<int>(K), static_cast<int>(M), static_cast<float>(temp),
+                             logits.data_ptr<float>(), lse.data_ptr<float>(), loss.data_ptr<float>(), stream_of(x));
+    g_launches += 1;
+    return {logits, lse, loss};
+}
+
+// returns (dx [P, M] fp32, dtgt [P, M] fp32)
+std::tuple<Tensor, Tensor> w2v_contrastive_bwd(const Tensor& x, const Tensor& tgt, const Tensor& distractors,
+                                               const Tensor& logits, const Tensor& lse, const Tensor& scale,
+                                               double temp) {
+    const int64_t P = x.size(0), M = x.size(1), K = distractors.size(1);
+    TORCH_CHECK(scale.is_cuda() && scale.scalar_type() == at::kFloat && scale.numel() == 1 && logits.is_contiguous() &&
+                    lse.is_contiguous() && logits.numel() == P * (K + 1) && lse.numel() == P,
+                "w2v_contrastive_bwd: bad saved tensors");
+    c10::cuda::CUDAGuard guard(x.device());
+    auto fopt = x.options().dtype(at::kFloat);
+    Tensor dx = at::empty({P, M}, fopt), dtgt = at::zeros({P, M}, fopt);
+    fs2::w2v_contrastive_bwd(x.data_ptr(), tgt.data_ptr(), is_bf16(x), distractors.data_ptr<int>(),
+                             logits.data_ptr<float>(), lse.data_ptr<float>(), scale.data_ptr<float>(),
+                             static_cast<int>(P), static_cast<int>(K), static_cast<int>(M), static_cast<float>(temp),
+                             dx.data_ptr<float>(), dtgt.data_ptr<float>(), stream_of(x));
+    g_launches += 1;
+    return {dx, dtgt};
+}
+
+// returns (q [R, E], hard_idx [R], sel [R], prob_sum [G, V], hard_count [G, V], y_soft [R, V] or empty)
+std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor, Tensor> w2v_quantize_fwd(const Tensor& logits,
+                                                                            const std::optional<Tensor>& noise,
+                                                                            const Tensor& entries, int64_t G, double tau,
+                                                                            bool training, bool keep_soft) {
+    TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.is_contiguous() && entries.is_contiguous() &&
+                    entries.dim() == 2 && logits.scalar_type() == entries.scalar_type() &&
+                    (is_bf16(logits) || logits.scalar_type() == at::kFloat),
+                "w2v_quantize_fwd: logits [R, V] and entries [G * V, E] must be contiguous bf16/fp32 CUDA tensors");
+    const int64_t R = logits.size(0), V = logits.size(1), E = entries.size(1);
+    TORCH_CHECK(G >= 1 && R % G == 0 && entries.size(0) == G * V && V <= 512, "w2v_quantize_fwd: bad shapes");
+    const float* np = nullptr;
+    if (noise.has_value()) {
+        TORCH_CHECK(noise->scalar_type() == at::kFloat && noise->is_contiguous() && noise->sizes() == logits.sizes(),
+                    "w2v_quantize_fwd: noise must be fp32 [R, V]");
+        np = noise->data_ptr<float>();
+    }
+    c10::cuda::CUDAGuard guard(logits.device());
+    auto fopt = logits.options().dtype(at::kFloat);
+    auto iopt = logits.options().dtype(at::kInt);
+    Tensor q = at::empty({R, E}, logits.options()), hard_idx = at::empty({R}, iopt), sel = at::empty({R}, iopt);
+    Tensor prob_sum = at::zeros({G, V}, fopt), hard_count = at::zeros({G, V}, fopt);
+    Tensor y_soft = (training && keep_soft) ? at::empty({R, V}, fopt) : at::empty({0}, fopt);
+    fs2::w2v_quantize_fwd(logits.data_ptr(), np, entries.data_ptr(), is_bf16(logits), static_cast<int>(R),
+                          static_cast<int>(G), static_cast<int>(V), static_cast<int>(E), static_cast<float>(tau), training,
+                          hard_idx.data_ptr<int>(), sel.data_ptr<int>(), prob_sum.data_ptr<float>(),
+                          hard_count.data_ptr<float>(), y_soft.numel() ? y_soft.data_ptr<float>() : nullptr, q.data_ptr(),
+                          stream_of(logits));
+    g_launches += 1;
+    return {q, hard_idx, sel, prob_sum, hard_count, y_soft};
+}
+
+// returns (dlogits [R, V] fp32, dentries [G * V, E] fp32)
+std::tuple<Tensor, Tensor> w2v_quantize_bwd(const Tensor& dq, const Tensor& entries, const Tensor& y_soft,
+                                            const Tensor& sel, int64_t G, double tau) {
+    TORCH_CHECK(dq.is_cuda() && dq.is_contiguous() && dq.dim() == 2 && entries.is_contiguous() &&
+                    dq.scalar_type() == entries.scalar_type() && y_soft.scalar_type() == at::kFloat &&
+                    y_soft.is_contiguous() && sel.scalar_type() == at::kInt,
+                "w2v_quantize_bwd: bad tensors");
+    const int64_t R = dq.size(0), E = dq.size(1), V = y_soft.size(1);
+    TORCH_CHECK(entries.size(0) == G * V && entries.size(1) == E && y_soft.size(0) == R && sel.numel() == R,
+                "w2v_quantize_bwd: bad shapes");
+    c10::cuda::CUDAGuard guard(dq.device());
+    auto fopt = dq.options().dtype(at::kFloat);
+    Tensor dlogits = at::empty({R, V}, fopt), dentries = at::zeros({G * V, E}, fopt);
+    fs2::w2v_quantize_bwd(dq.data_ptr(), entries.data_ptr(), is_bf16(dq), y_soft.data_ptr<float>(), sel.data_ptr<int>(),
+                          static_cast<int>(R), static_cast<int>(G), static_cast<int>(V), static_cast<int>(E),
+                          static_cast<float>(tau), dlogits.data_ptr<float>(), dentries.data_ptr<float>(), stream_of(dq));
+    g_launches += 1;
+    return {dlogits, dentries};
 }
 
 fs2::CommPeers make_peers(const std::vector<int64_t>& ptrs, int64_t rank, double wait_limit_s);
@@ -987,13 +1117,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.doc() = "fairseq2_b200 sm_100a kernels";
     m.def("gemm_bf16", &gemm_bf16);
     m.def("gemm_reduce_scatter", &gemm_reduce_scatter);
+    m.def("gemm_bf16_view", &gemm_bf16_view);
     m.def("gemm_allgather", &gemm_allgather);
     m.def("gemm_scatter", &gemm_scatter);
     m.def("reduce_slices", &reduce_slices);
     m.def("rms_norm_fwd", &rms_norm_fwd);
     m.def("rms_norm_bwd", &rms_norm_bwd);
-    m.def("layer_norm_fwd", &layer_norm_fwd);
-    m.def("layer_norm_bwd", &layer_norm_bwd);
+    m.def("layer_norm_fwd", &layer_norm_fwd, py::arg("x"), py::arg("w"), py::arg("b"), py::arg("eps"),
+          py::arg("gelu") = false);
+    m.def("layer_norm_bwd", &layer_norm_bwd, py::arg("dy"), py::arg("x"), py::arg("w"), py::arg("mean"),
+          py::arg("rstd"), py::arg("b_for_gelu") = std::nullopt);
     m.def("swiglu_fwd", &swiglu_fwd);
     m.def("swiglu_bwd", &swiglu_bwd);
     m.def("rope_inplace", &rope_inplace);
@@ -1018,6 +1151,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("moe_route", &moe_route);
     m.def("moe_dispatch", &moe_dispatch);
     m.def("moe_combine", &moe_combine);
+    m.def("w2v_contrastive_fwd", &w2v_contrastive_fwd);
+    m.def("w2v_contrastive_bwd", &w2v_contrastive_bwd);
+    m.def("w2v_quantize_fwd", &w2v_quantize_fwd);
+    m.def("w2v_quantize_bwd", &w2v_quantize_bwd);
     m.def("moe_ep_layout", &moe_ep_layout);
     m.def("moe_ep_push", &moe_ep_push);
     m.def("moe_ep_pull", &moe_ep_pull);

@@ -136,7 +136,15 @@ __global__ void reduce_partials_kernel(const float* __restrict__ part, float* __
 }
 
 // ----------------------------------------------------------------- LayerNorm
-template <typename T, int VPT>
+__device__ __forceinline__ float gelu_exact(float n) { return 0.5f * n * (1.f + erff(n * 0.70710678118654752f)); }
+
+__device__ __forceinline__ float gelu_exact_grad(float n) {
+    return 0.5f * (1.f + erff(n * 0.70710678118654752f)) + n * 0.39894228040143268f * __expf(-0.5f * n * n);
+}
+
+// GELU = true applies the exact (erf) GELU to the normalised row in the same pass: the convolutional feature
+// encoders of speech models are conv -> LayerNorm over channels -> GELU on channels-last rows.
+template <typename T, int VPT, bool GELU = false>
 __global__ void layer_norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ b,
                                       T* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd, int rows,
                                       int D, float eps) {
@@ -181,7 +189,10 @@ __global__ void layer_norm_fwd_kernel(const T* __restrict__ x, const T* __restri
                 load8(w, static_cast<size_t>(v) * 8, wv);
                 load8(b, static_cast<size_t>(v) * 8, bv);
 #pragma unroll
-                for (int e = 0; e < 8; ++e) o[e] = (cache[j][e] - mu) * r * wv[e] + bv[e];
+                for (int e = 0; e < 8; ++e) {
+                    o[e] = (cache[j][e] - mu) * r * wv[e] + bv[e];
+                    if constexpr (GELU) o[e] = gelu_exact(o[e]);
+                }
                 store8(y + off, static_cast<size_t>(v) * 8, o);
             }
         }
@@ -189,20 +200,24 @@ __global__ void layer_norm_fwd_kernel(const T* __restrict__ x, const T* __restri
 }
 
 // dx = rstd * (g - mean(g) - xhat * mean(g * xhat)); dw += dy * xhat; db += dy
-template <typename T, int VPT>
+template <typename T, int VPT, bool GELU = false>
 __global__ void layer_norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
-                                      const float* __restrict__ mean, const float* __restrict__ rstd,
+                                      const T* __restrict__ b, const float* __restrict__ mean,
+                                      const float* __restrict__ rstd,
                                       T* __restrict__ dx, float* __restrict__ dw_part, float* __restrict__ db_part,
                                       int rows, int D) {
     __shared__ float scratch[32];
     const int nvec = D / 8;
-    float dwacc[VPT][8], dbacc[VPT][8], wv[VPT][8];
+    float dwacc[VPT][8], dbacc[VPT][8], wv[VPT][8], bv[GELU ? VPT : 1][8];
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
         const int v = threadIdx.x + j * blockDim.x;
 #pragma unroll
         for (int e = 0; e < 8; ++e) dwacc[j][e] = dbacc[j][e] = 0.f;
-        if (v < nvec) load8(w, static_cast<size_t>(v) * 8, wv[j]);
+        if (v < nvec) {
+            load8(w, static_cast<size_t>(v) * 8, wv[j]);
+            if constexpr (GELU) load8(b, static_cast<size_t>(v) * 8, bv[j]);
+        }
     }
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
         const size_t off = static_cast<size_t>(row) * D;
@@ -219,6 +234,7 @@ __global__ void layer_norm_bwd_kernel(const T* __restrict__ dy, const T* __restr
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
                     xh[j][e] = (xv[e] - mu) * r;
+                    if constexpr (GELU) dyv[e] *= gelu_exact_grad(xh[j][e] * wv[j][e] + bv[j][e]);
                     g[j][e] = dyv[e] * wv[j][e];
                     s1 += g[j][e];
                     s2 += g[j][e] * xh[j][e];
@@ -530,9 +546,16 @@ void rms_norm_bwd(const void* dy, const void* x, const void* w, const float* rst
 }
 
 void layer_norm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int rows, int D,
-                    float eps, bool bf16, int num_sms, cudaStream_t st) {
+                    float eps, bool bf16, int num_sms, cudaStream_t st, bool gelu) {
     const int threads = norm_block(D);
     const int grid = rows < num_sms * 16 ? rows : num_sms * 16;
+    if (gelu) {        // bf16 only
+        FS2_VPT_DISPATCH(norm_vpt(D, threads),
+            (layer_norm_fwd_kernel<__nv_bfloat16, VPT, true><<<grid, threads, 0, st>>>(
+                static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+                static_cast<const __nv_bfloat16*>(b), static_cast<__nv_bfloat16*>(y), mean, rstd, rows, D, eps)))
+        return;
+    }
     FS2_VPT_DISPATCH(norm_vpt(D, threads),
         if (bf16)
             layer_norm_fwd_kernel<__nv_bfloat16, VPT><<<grid, threads, 0, st>>>(
@@ -546,19 +569,27 @@ void layer_norm_fwd(const void* x, const void* w, const void* b, void* y, float*
 
 void layer_norm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx,
                     float* dw_part, float* db_part, float* dw, float* db, int rows, int D, bool bf16, int num_sms,
-                    cudaStream_t st) {
+                    cudaStream_t st, const void* b_for_gelu) {
     const int threads = norm_block(D);
     const int grid = norm_bwd_grid(rows, num_sms);
+    if (b_for_gelu != nullptr) {        // bf16 only: dy is the gradient of gelu(layer_norm(x))
+        FS2_VPT_DISPATCH(norm_vpt(D, threads),
+            (layer_norm_bwd_kernel<__nv_bfloat16, VPT, true><<<grid, threads, 0, st>>>(
+                static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
+                static_cast<const __nv_bfloat16*>(w), static_cast<const __nv_bfloat16*>(b_for_gelu), mean, rstd,
+                static_cast<__nv_bfloat16*>(dx), dw_part, db_part, rows, D)))
+    } else {
     FS2_VPT_DISPATCH(norm_vpt(D, threads),
         if (bf16)
             layer_norm_bwd_kernel<__nv_bfloat16, VPT><<<grid, threads, 0, st>>>(
                 static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
-                static_cast<const __nv_bfloat16*>(w), mean, rstd, static_cast<__nv_bfloat16*>(dx), dw_part, db_part,
-                rows, D);
+                static_cast<const __nv_bfloat16*>(w), nullptr, mean, rstd, static_cast<__nv_bfloat16*>(dx), dw_part,
+                db_part, rows, D);
         else
             layer_norm_bwd_kernel<float, VPT><<<grid, threads, 0, st>>>(
-                static_cast<const float*>(dy), static_cast<const float*>(x), static_cast<const float*>(w), mean,
-                rstd, static_cast<float*>(dx), dw_part, db_part, rows, D))
+                static_cast<const float*>(dy), static_cast<const float*>(x), static_cast<const float*>(w), nullptr,
+                mean, rstd, static_cast<float*>(dx), dw_part, db_part, rows, D))
+    }
     reduce_partials_kernel<<<(D + 255) / 256, 256, 0, st>>>(dw_part, dw, grid, D);
     reduce_partials_kernel<<<(D + 255) / 256, 256, 0, st>>>(db_part, db, grid, D);
 }

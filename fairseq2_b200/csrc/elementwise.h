@@ -13,11 +13,13 @@ void rms_norm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, 
                   int num_sms, cudaStream_t st);
 void rms_norm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw_part,
                   float* dw, int rows, int D, bool bf16, int num_sms, cudaStream_t st);
+// `gelu` (bf16 only): y = gelu(layer_norm(x)) in one pass; the backward then takes the bias as `b_for_gelu` to
+// rebuild the pre-activation and treats `dy` as the gradient of the GELU output.
 void layer_norm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int rows, int D,
-                    float eps, bool bf16, int num_sms, cudaStream_t st);
+                    float eps, bool bf16, int num_sms, cudaStream_t st, bool gelu = false);
 void layer_norm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx,
                     float* dw_part, float* db_part, float* dw, float* db, int rows, int D, bool bf16, int num_sms,
-                    cudaStream_t st);
+                    cudaStream_t st, const void* b_for_gelu = nullptr);
 void swiglu_fwd(const void* gu, void* y, size_t rows, int F, int num_sms, cudaStream_t st);
 void swiglu_bwd(const void* dy, const void* gu, void* dgu, size_t rows, int F, int num_sms, cudaStream_t st);
 void rope_inplace(void* x, const float* freqs, const int* pos, size_t tokens, int heads, int D, size_t tstride,

@@ -559,15 +559,18 @@ EncodeFn get_encode_fn() {
 // 2-D row-major tensor [rows, cols] of `elem_bytes` elements; box [box_rows, box_cols].
 thread_local char g_tmap_err[256];
 
+// `ld` is the distance between consecutive rows in elements (0 = `cols`, a dense matrix). It may be SMALLER than
+// `cols`: rows then overlap in memory, which is how a strided convolution over a channels-last signal becomes a GEMM
+// without materialising the patches.
 bool make_tmap(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt, int elem_bytes, uint64_t rows, uint64_t cols,
-               uint32_t box_rows, uint32_t box_cols) {
+               uint32_t box_rows, uint32_t box_cols, uint64_t ld = 0) {
     EncodeFn fn = get_encode_fn();
     if (fn == nullptr) {
         snprintf(g_tmap_err, sizeof(g_tmap_err), "cuTensorMapEncodeTiled entry point not found");
         return false;
     }
     cuuint64_t dims[2] = {cols, rows};
-    cuuint64_t strides[1] = {cols * static_cast<uint64_t>(elem_bytes)};
+    cuuint64_t strides[1] = {(ld ? ld : cols) * static_cast<uint64_t>(elem_bytes)};
     cuuint32_t box[2] = {box_cols, box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(m, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -602,15 +605,26 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
 
 const char* gemm_bf16_tcgen05(const void* a, const void* b, void* c, int M, int N, int K, bool a_mn, bool b_mn,
                               bool out_f32, bool accumulate, int* status, int num_sms, cudaStream_t stream) {
+    return gemm_bf16_tcgen05_view(a, 0, 0, b, 0, 0, c, 0, 0, M, N, K, a_mn, b_mn, out_f32, accumulate, status, num_sms,
+                                  stream);
+}
+
+const char* gemm_bf16_tcgen05_view(const void* a, long long lda, long long a_rows, const void* b, long long ldb,
+                                   long long b_rows, void* c, long long ldc, long long c_rows, int M, int N, int K,
+                                   bool a_mn, bool b_mn, bool out_f32, bool accumulate, int* status, int num_sms,
+                                   cudaStream_t stream) {
     CUtensorMap ta, tb, tc;
     bool ok = true;
     g_tmap_err[0] = 0;
-    if (!a_mn) ok = ok && make_tmap(&ta, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, BM, BK);
-    else ok = ok && make_tmap(&ta, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, BK, 64);
-    if (!b_mn) ok = ok && make_tmap(&tb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, BN, BK);
-    else ok = ok && make_tmap(&tb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, BK, 64);
-    if (out_f32) ok = ok && make_tmap(&tc, c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, M, N, 128, 32);
-    else ok = ok && make_tmap(&tc, c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, 128, 64);
+    // `*_rows` (0 = all) is the number of rows that exist in memory; tiles beyond it read zeros / are not written
+    const uint64_t ar = a_rows ? a_rows : (a_mn ? K : M), br = b_rows ? b_rows : (b_mn ? K : N);
+    const uint64_t cr = c_rows ? c_rows : M;
+    if (!a_mn) ok = ok && make_tmap(&ta, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ar, K, BM, BK, lda);
+    else ok = ok && make_tmap(&ta, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ar, M, BK, 64, lda);
+    if (!b_mn) ok = ok && make_tmap(&tb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, br, K, BN, BK, ldb);
+    else ok = ok && make_tmap(&tb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, br, N, BK, 64, ldb);
+    if (out_f32) ok = ok && make_tmap(&tc, c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, cr, N, 128, 32, ldc);
+    else ok = ok && make_tmap(&tc, c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, cr, N, 128, 64, ldc);
     if (!ok) return g_tmap_err;
     cudaError_t e;
     const int acc = accumulate ? 1 : 0;

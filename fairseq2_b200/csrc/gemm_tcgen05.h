@@ -13,6 +13,16 @@ namespace fs2 {
 const char* gemm_bf16_tcgen05(const void* a, const void* b, void* c, int M, int N, int K, bool a_mn, bool b_mn,
                               bool out_f32, bool accumulate, int* status, int num_sms, cudaStream_t stream);
 
+// The same GEMM over strided views: `lda`/`ldb`/`ldc` are row pitches in elements (0 = dense) and may be smaller
+// than the row length, so that rows overlap in memory (a strided 1-D convolution over a channels-last signal is
+// A[r, :] = x[r * stride * C : r * stride * C + k * C]). `a_rows`/`b_rows`/`c_rows` (0 = all) give the number of
+// rows that exist in memory: tiles beyond them read zeros and are not written. With `accumulate` the output tile is
+// added (TMA reduce-add), which also sums rows of C that overlap.
+const char* gemm_bf16_tcgen05_view(const void* a, long long lda, long long a_rows, const void* b, long long ldb,
+                                   long long b_rows, void* c, long long ldc, long long c_rows, int M, int N, int K,
+                                   bool a_mn, bool b_mn, bool out_f32, bool accumulate, int* status, int num_sms,
+                                   cudaStream_t stream);
+
 // GEMM fused with the all-gather of one operand (see gemm_tcgen05.cu): `shards[r]` is rank r's [rows_per_rank, K]
 // bf16 shard (peer mapping), `gathered` local scratch for the whole operand, `flags` one word per tile-height block
 // (zero before the first call; `epoch` must grow by one per call), `ncopy` the number of CTAs that move data.

@@ -38,6 +38,8 @@ class Wav2Vec2Output:
     encoder_output: Tensor
     encoder_output_layout: BatchLayout
     raw_features: Tensor
+    contrastive_loss: Tensor | None = None
+    """Summed cross entropy of ``logits`` against index 0, produced together with the logits by the fused kernel."""
 
 
 @dataclass
@@ -88,19 +90,31 @@ class Wav2Vec2Model(Module):
         seqs = self.final_proj(Wav2Vec2Masker.extract_masked_elements(f.seqs, f.temporal_mask))
         q = self.quantizer(f.targets)
         targets = self.final_target_proj(q.quantized_vectors)
-        logits = self._compute_logits(seqs, targets, self._sample_distractors(targets))
-        n, s = logits.shape[:2]
-        return Wav2Vec2Output(logits, targets, n * s, f.temporal_mask, q, f.seqs, f.seqs_layout, f.raw)
+        n, s, m = targets.shape
+        from fairseq2_b200.ops.wav2vec2 import contrastive_logits_and_loss
+
+        # logits and loss in one pass over index-given distractors; the [N, S, K, M] gather is never built
+        idx = self._sample_distractor_indices(n, s, targets.device)
+        logits, loss = contrastive_logits_and_loss(seqs.reshape(n * s, m), targets.reshape(n * s, m),
+                                                   idx.view(n * s, -1), self.logit_temp)
+        return Wav2Vec2Output(logits.view(n, s, -1), targets, n * s, f.temporal_mask, q, f.seqs, f.seqs_layout, f.raw,
+                              contrastive_loss=loss)
+
+    def _sample_distractor_indices(self, n: int, s: int, dev: torch.device) -> Tensor:
+        """For every masked step, the rows (in the flattened ``[N * S, M]`` targets) of ``num_distractors`` other
+        masked steps of the same utterance."""
+        own = torch.arange(s, device=dev).repeat_interleave(self.num_distractors)
+        rnd = torch.randint(0, max(s - 1, 1), (n, s * self.num_distractors), device=dev)
+        rnd = rnd + (rnd >= own)                                      # skip the step itself
+        if s == 1:
+            rnd = torch.zeros_like(rnd)
+        rnd = rnd + torch.arange(n, device=dev).unsqueeze(1) * s
+        return rnd.view(n, s, self.num_distractors).to(torch.int32)
 
     def _sample_distractors(self, targets: Tensor) -> Tensor:
-        """For every masked step, ``num_distractors`` other masked steps of the same utterance."""
         n, s, m = targets.shape
-        dev = targets.device
-        own = torch.arange(s, device=dev).repeat_interleave(self.num_distractors)
-        rnd = torch.randint(0, s - 1, (n, s * self.num_distractors), device=dev)
-        rnd = rnd + (rnd >= own)                                      # skip the step itself
-        rnd = rnd + torch.arange(n, device=dev).unsqueeze(1) * s
-        return targets.reshape(-1, m)[rnd.view(-1)].view(n, s, self.num_distractors, m)
+        idx = self._sample_distractor_indices(n, s, targets.device)
+        return targets.reshape(-1, m)[idx.view(-1).long()].view(n, s, self.num_distractors, m)
 
     def _compute_logits(self, seqs: Tensor, targets: Tensor, distractors: Tensor) -> Tensor:
         seqs, targets = seqs.unsqueeze(2), targets.unsqueeze(2)
@@ -117,8 +131,11 @@ class Wav2Vec2Model(Module):
                      features_penalty_weight: float = 10.0) -> Wav2Vec2Loss:
         logits = output.logits
         n, s, c = logits.shape
-        flat = logits.transpose(0, 1).reshape(-1, c).float()
-        contrastive = cross_entropy(flat, flat.new_zeros((n * s,), dtype=torch.int64), reduction="sum")
+        if output.contrastive_loss is not None:
+            contrastive = output.contrastive_loss
+        else:
+            flat = logits.transpose(0, 1).reshape(-1, c).float()
+            contrastive = cross_entropy(flat, flat.new_zeros((n * s,), dtype=torch.int64), reduction="sum")
         entries = self.quantizer.num_codebooks * self.quantizer.num_codebook_entries  # type: ignore[attr-defined]
         diversity = (entries - output.quantizer_output.prob_perplexity) / entries * (n * s)
         penalty = output.raw_features.float().pow(2).mean() * (n * s)

@@ -7,7 +7,6 @@ from dataclasses import dataclass
 import torch
 from torch import Tensor
 from torch.nn import Module, Parameter
-from torch.nn.functional import gumbel_softmax
 
 from fairseq2_b200.nn.projection import Linear
 from fairseq2_b200.typing import DataType, Device
@@ -73,23 +72,20 @@ class GumbelVectorQuantizer(VectorQuantizer):
         temp = self._current_temperature()
         bsz, tsz, fsz = x.shape
         G, V = self.num_codebooks, self.num_codebook_entries
-        x = self.entry_proj(x.reshape(-1, fsz)).view(bsz * tsz * G, V)
-        k = x.argmax(dim=-1, keepdim=True)
-        hard = torch.zeros_like(x, dtype=torch.float32).scatter_(-1, k, 1.0).view(bsz * tsz, G, V)
-        hard_probs = hard.mean(dim=0)
+        logits = self.entry_proj(x.reshape(-1, fsz)).view(bsz * tsz * G, V)
+        from fairseq2_b200.ops.wav2vec2 import gumbel_quantize, sample_gumbel_noise
+
+        # one kernel: arg-max codes, soft probabilities, straight-through Gumbel sample and the code-book LOOKUP of
+        # the selected entry (the dense formulation multiplies a [frames, G*V, 1] one-hot with the whole code book)
+        noise = sample_gumbel_noise(tuple(logits.shape), logits.device) if self.training else None
+        q, sel, prob_sum, hard_count = gumbel_quantize(logits, noise, self.entries.view(G * V, -1), G, temp, self.training)
+        frames = max(bsz * tsz, 1)
+        hard_probs = hard_count / frames
         code_perplexity = torch.exp(-torch.sum(hard_probs * torch.log(hard_probs + 1e-7), dim=-1)).sum()
-        avg_probs = torch.softmax(x.view(bsz * tsz, G, V).float(), dim=-1).mean(dim=0)
+        avg_probs = prob_sum / frames
         prob_perplexity = torch.exp(-torch.sum(avg_probs * torch.log(avg_probs + 1e-7), dim=-1)).sum()
-        if self.training:
-            x = gumbel_softmax(x.float(), tau=temp, hard=True).type_as(x)
-        else:
-            x = hard.view(bsz * tsz * G, V).type_as(x)
-        x = x.view(bsz * tsz, -1)
-        cb = x
-        # (T, G·V, 1) * (1, G·V, E) summed over V within each codebook
-        q = (x.unsqueeze(-1) * self.entries).view(bsz * tsz, G, V, -1).sum(dim=-2)
-        q = q.view(bsz, tsz, -1)
-        return VectorQuantizerOutput(q, cb, G, V, code_perplexity, prob_perplexity, temp)
+        cb = torch.nn.functional.one_hot(sel.long().view(bsz * tsz, G), V).to(logits.dtype).view(bsz * tsz, G * V)
+        return VectorQuantizerOutput(q.view(bsz, tsz, -1), cb, G, V, code_perplexity, prob_perplexity, temp)
 
     def _current_temperature(self) -> float:
         temp = max(self.max_temp * self.temp_decay ** int(self.num_updates), self.min_temp)

@@ -1,0 +1,91 @@
+"""Strided 1-D convolution over channels-last signals as a tcgen05 GEMM on overlapping-row views.
+
+For ``x`` ``[B, L, C]`` (contiguous) and a kernel of width ``k`` and stride ``s`` with ``L % s == 0``, row ``r`` of the
+patch matrix is ``x.flatten()[r * s * C : r * s * C + k * C]`` -- consecutive rows overlap in memory. A TMA tensor map
+with row pitch ``s * C`` describes exactly that matrix, so the convolution is ONE GEMM ``patches @ W2^T`` with
+``W2 = weight.permute(0, 2, 1).reshape(C_out, k * C)`` and no im2col buffer. The backward uses the same views:
+
+* weight gradient ``dW2 = dY^T @ patches`` (both operands MN-major views),
+* input gradient: ``dY @ W2`` has the shape of the patch matrix; the GEMM epilogue reduce-adds it through the same
+  overlapping-row tensor map into a zeroed ``dx``, which sums the overlapping taps (col2im without a buffer).
+
+The output has ``L / s`` rows per batch element ("virtual length"): row ``t`` is a true convolution output iff
+``t * s + k <= valid_len``; the remaining rows at the end of each batch element mix in the next element's samples (or
+zeros at the very end) and must be dropped by the caller -- stacks of such layers drop them once at the end, since a
+valid row of layer ``i + 1`` only ever reads valid rows of layer ``i``.
+
+Replaces cuDNN ``Conv1d`` + two transposes per layer in the wav2vec2 feature extractor
+(fairseq2 ``models/wav2vec2/feature_extractor.py:28-270``) for the layers with 8-element-aligned channel counts.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+from torch import Tensor
+
+from fairseq2_b200.ops._ext import require_ext, use_kernels
+
+
+def conv1d_cl_reference(x: Tensor, weight: Tensor, bias: Tensor | None, stride: int) -> Tensor:
+    """fp32 oracle with the same virtual-length convention (invalid tail rows are zero-padded convolutions)."""
+    B, L, C = x.shape
+    k = weight.shape[2]
+    xp = F.pad(x.float().transpose(1, 2), (0, k))                 # tail rows read zeros here, neighbours in the kernel
+    y = F.conv1d(xp, weight.float(), None if bias is None else bias.float(), stride=stride)
+    return y[:, :, : L // stride].transpose(1, 2)
+
+
+def conv1d_cl_supported(x: Tensor, weight: Tensor, stride: int) -> bool:
+    C_out, C, k = weight.shape
+    return (use_kernels(x, weight) and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 3
+            and x.shape[2] == C and C % 8 == 0 and C_out % 8 == 0 and x.shape[1] % stride == 0 and k >= stride
+            and x.shape[0] * x.shape[1] * C >= k * C)
+
+
+class _Conv1dCL(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x: Tensor, weight: Tensor, stride: int) -> Tensor:  # type: ignore[override]
+        ext = require_ext()
+        B, L, C = x.shape
+        C_out, _, k = weight.shape
+        x = x.contiguous()
+        w2 = weight.permute(0, 2, 1).reshape(C_out, k * C).contiguous()
+        R = B * L // stride                                       # rows of the (virtual) patch matrix
+        rows_ok = (B * L * C - k * C) // (stride * C) + 1         # rows that lie fully inside the storage
+        y = torch.empty((R, C_out), device=x.device, dtype=x.dtype)
+        ext.gemm_bf16_view(x, min(rows_ok, R), stride * C, False, w2, C_out, k * C, False, y, R, C_out, R, C_out, k * C,
+                           False)
+        ctx.save_for_backward(x, w2)
+        ctx.meta = (B, L, C, C_out, k, stride, R, min(rows_ok, R))
+        return y.view(B, L // stride, C_out)
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):  # type: ignore[override]
+        ext = require_ext()
+        x, w2 = ctx.saved_tensors
+        B, L, C, C_out, k, stride, R, rows_ok = ctx.meta
+        dy2 = dy.reshape(R, C_out).contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[1]:
+            # dW2 [C_out, k*C] = dY^T [C_out, R] @ patches [R, k*C]; rows of the patch view beyond rows_ok read zeros
+            dw2 = torch.empty((C_out, k * C), device=x.device, dtype=torch.float32)
+            ext.gemm_bf16_view(dy2, R, C_out, True, x, rows_ok, stride * C, True, dw2, C_out, k * C, C_out, k * C, R,
+                               False)
+            dw = dw2.view(C_out, k, C).permute(0, 2, 1).to(w2.dtype)
+        if ctx.needs_input_grad[0]:
+            # d patches [R, k*C] = dY [R, C_out] @ W2 [C_out, k*C], reduce-added through the overlapping-row view
+            dxf = torch.zeros((B * L, C), device=x.device, dtype=torch.float32)
+            ext.gemm_bf16_view(dy2, R, C_out, False, w2, C_out, k * C, True, dxf, rows_ok, stride * C, R, k * C, C_out,
+                               True)
+            dx = dxf.view(B, L, C).to(x.dtype)
+        return dx, dw, None
+
+
+def conv1d_channels_last(x: Tensor, weight: Tensor, bias: Tensor | None, stride: int) -> Tensor:
+    """``x`` ``[B, L, C_in]``, ``weight`` ``[C_out, C_in, k]`` (the ``torch.nn.Conv1d`` layout) -> ``[B, L / stride,
+    C_out]`` in the virtual-length convention of the module docstring."""
+    if conv1d_cl_supported(x, weight, stride):
+        y = _Conv1dCL.apply(x, weight, stride)
+        return y if bias is None else y + bias
+    return conv1d_cl_reference(x, weight, bias, stride).to(x.dtype)

@@ -16,7 +16,14 @@ def _free_port() -> int:
         return int(s.getsockname()[1])
 
 
-def _entry(rank: int, world: int, port: int, fn: Callable[..., Any], args: tuple[Any, ...], out: Any) -> None:
+def _entry(rank: int, world: int, port: int, fn: Callable[..., Any], args: tuple[Any, ...], out: Any,
+           dump_after: float = 0.0) -> None:
+    if dump_after > 0:
+        import faulthandler
+        import sys
+
+        faulthandler.enable(file=sys.stderr)                                         # a crashing rank says where
+        faulthandler.dump_traceback_later(dump_after, exit=False, file=sys.stderr)   # where is a stuck rank?
     os.environ.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "RANK": str(rank),
                        "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank), "LOCAL_WORLD_SIZE": str(world)})
     torch.set_num_threads(2)
@@ -32,7 +39,7 @@ def run_distributed(fn: Callable[..., Any], world: int, *args: Any, timeout: flo
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, out)) for r in range(world)]
+    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, out, 0.6 * timeout)) for r in range(world)]
     for p in procs:
         p.start()
     results: dict[int, Any] = {}

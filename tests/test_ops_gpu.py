@@ -412,3 +412,94 @@ def test_moe_layer_kernels_match_reference_path() -> None:
                      moe.experts.gate_proj.grad.float().clone()))
     for a, b in zip(*outs):
         assert float((a - b).norm() / b.norm().clamp(min=1e-6)) < 3e-2
+
+
+# ------------------------------------------------------------------- speech feature encoder kernels
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,L,C,C_out,k,s", [(3, 640, 512, 512, 3, 2), (2, 250, 64, 128, 2, 2), (1, 96, 8, 8, 10, 4)])
+def test_conv1d_channels_last_view_gemm(B: int, L: int, C: int, C_out: int, k: int, s: int) -> None:
+    from fairseq2_b200.ops.conv import conv1d_channels_last, conv1d_cl_reference, conv1d_cl_supported
+
+    torch.manual_seed(0)
+    x = torch.randn(B, L, C, device="cuda", dtype=torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(C_out, C, k, device="cuda") * (C * k) ** -0.5).to(torch.bfloat16).requires_grad_(True)
+    b = torch.randn(C_out, device="cuda", dtype=torch.bfloat16)
+    assert conv1d_cl_supported(x, w, s)
+    T_out = (L - k) // s + 1                                   # rows that are true convolution outputs
+    y = conv1d_channels_last(x, w, b, s)
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    ref = conv1d_cl_reference(xr, wr, b.float(), s)
+    assert y.shape == (B, L // s, C_out)
+    assert _rel_err(y[:, :T_out].float(), ref[:, :T_out]) < 1e-2
+    g = torch.randn(B, T_out, C_out, device="cuda", dtype=torch.bfloat16)
+    y[:, :T_out].backward(g)                                   # the invalid tail rows receive zero gradient
+    ref[:, :T_out].backward(g.float())
+    assert _rel_err(w.grad.float(), wr.grad) < 1.5e-2
+    assert _rel_err(x.grad.float(), xr.grad) < 1.5e-2
+
+
+@pytest.mark.gpu
+def test_layer_norm_gelu_fused() -> None:
+    from fairseq2_b200.ops.norm import layer_norm_gelu
+
+    torch.manual_seed(0)
+    x = torch.randn(1000, 512, device="cuda", dtype=torch.bfloat16).requires_grad_(True)
+    w = (1 + 0.1 * torch.randn(512, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    b = (0.1 * torch.randn(512, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    y = layer_norm_gelu(x, w, b, 1e-5)
+    xr, wr, br = (t.detach().float().requires_grad_(True) for t in (x, w, b))
+    ref = torch.nn.functional.gelu(torch.nn.functional.layer_norm(xr, (512,), wr, br, 1e-5))
+    assert _rel_err(y.float(), ref) < 1e-2
+    g = torch.randn_like(y)
+    y.backward(g)
+    ref.backward(g.float())
+    assert _rel_err(x.grad.float(), xr.grad) < 1.5e-2
+    assert _rel_err(w.grad.float(), wr.grad) < 1.5e-2 and _rel_err(b.grad.float(), br.grad) < 1.5e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_wav2vec2_contrastive_kernel(dtype: torch.dtype) -> None:
+    from fairseq2_b200.ops.wav2vec2 import contrastive_logits_and_loss, contrastive_reference
+
+    torch.manual_seed(0)
+    P, K, M = 333, 100, 256
+    x = torch.randn(P, M, device="cuda").to(dtype).requires_grad_(True)
+    t = torch.randn(P, M, device="cuda").to(dtype)
+    t[7] = t[3]                                                # a distractor identical to a target must give -inf
+    t = t.requires_grad_(True)
+    d = torch.randint(0, P, (P, K), device="cuda", dtype=torch.int32)
+    d[3, 5] = 7
+    logits, loss = contrastive_logits_and_loss(x, t, d, 0.1)
+    xr, tr = x.detach().float().requires_grad_(True), t.detach().float().requires_grad_(True)
+    rlogits, rloss = contrastive_reference(xr, tr, d, 0.1)
+    assert torch.isinf(logits[3, 6]) and torch.isinf(rlogits[3, 6])
+    fin = torch.isfinite(rlogits)
+    assert torch.equal(fin, torch.isfinite(logits))
+    assert torch.allclose(logits[fin], rlogits[fin], atol=2e-3)
+    assert abs(float(loss) - float(rloss)) / float(rloss) < 1e-3
+    (loss * 0.5).backward()
+    (rloss * 0.5).backward()
+    assert _rel_err(x.grad.float(), xr.grad) < 1e-2 and _rel_err(t.grad.float(), tr.grad) < 1e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("training", [True, False])
+def test_wav2vec2_gumbel_quantizer_kernel(training: bool) -> None:
+    from fairseq2_b200.ops.wav2vec2 import gumbel_quantize, gumbel_quantize_reference, sample_gumbel_noise
+
+    torch.manual_seed(0)
+    frames, G, V, E = 257, 2, 320, 128
+    logits = torch.randn(frames * G, V, device="cuda").requires_grad_(True)
+    entries = torch.rand(G * V, E, device="cuda").requires_grad_(True)
+    noise = sample_gumbel_noise((frames * G, V), logits.device) if training else None
+    q, sel, prob_sum, hard = gumbel_quantize(logits, noise, entries, G, 1.7, training)
+    lr, er = logits.detach().clone().requires_grad_(True), entries.detach().clone().requires_grad_(True)
+    rq, rsel, rprob, rhard = gumbel_quantize_reference(lr, noise, er, G, 1.7, training)
+    assert torch.equal(sel.long(), rsel) and torch.allclose(hard, rhard) and torch.allclose(prob_sum, rprob, atol=1e-4)
+    assert torch.allclose(q, rq, atol=1e-5)
+    if training:
+        w = torch.randn_like(q)
+        (q * w).sum().backward()
+        (rq * w).sum().backward()
+        assert _rel_err(logits.grad, lr.grad) < 1e-3 and _rel_err(entries.grad, er.grad) < 1e-3

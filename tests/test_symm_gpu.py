@@ -3,6 +3,7 @@ checked against closed-form expectations and against the NCCL path."""
 from __future__ import annotations
 
 import os
+import sys
 
 import pytest
 import torch
@@ -296,9 +297,11 @@ def _missing_peer_worker(rank: int, world: int):
     torch.cuda.set_device(dev)
     base = ProcessGroupGang.create_default_process_group(dev)
     arena = SymmetricArena(base, 1 << 20, wait_limit_s=0.3)
+    print(f"[missing-peer rank {rank}] arena ready", file=sys.stderr, flush=True)
     arena.barrier(20, 1)                       # everyone joins: passes
     torch.cuda.synchronize()
     arena.ext.check_status()
+    print(f"[missing-peer rank {rank}] first barrier passed", file=sys.stderr, flush=True)
     detected = ""
     if rank == 0:
         arena.barrier(21, 1)                   # nobody else signals slot 21
@@ -307,18 +310,21 @@ def _missing_peer_worker(rank: int, world: int):
             arena.ext.check_status()
         except Exception as ex:  # noqa: BLE001
             detected = str(ex)
+    print(f"[missing-peer rank {rank}] after the withheld barrier", file=sys.stderr, flush=True)
     arena.wait_limit_s = 20.0                  # rank 1 gets here 0.3 s before rank 0
     arena.barrier(22, 1)                       # the GPU context still works on both ranks
     probe = torch.ones(4, device=dev).sum().item()
     torch.cuda.synchronize()
     arena.ext.check_status()
+    print(f"[missing-peer rank {rank}] closing", file=sys.stderr, flush=True)
     base.close()
+    print(f"[missing-peer rank {rank}] closed", file=sys.stderr, flush=True)
     return detected, probe
 
 
 def test_bounded_wait_reports_missing_peer() -> None:
     _need_gpus(2)
-    results = run_distributed(_missing_peer_worker, 2, timeout=90.0)
+    results = run_distributed(_missing_peer_worker, 2, timeout=60.0)
     assert "bounded wait" in results[0][0] and results[0][1] == 4.0 and results[1] == ("", 4.0)
 
 
