@@ -106,13 +106,59 @@ class Wav2Vec2FeatureExtractor(SequenceFeatureExtractor):
         if seqs_layout.packed:
             raise ValueError("`seqs` must not be a packed batch.")
         x = seqs.unsqueeze(1) if self.num_channels == 1 and seqs.ndim == 2 else seqs.transpose(1, 2)
-        for layer in self.layers:
-            x = layer(x)
-        if self.training and self.grad_scale != 1.0:
-            x = scale_gradient(x, self.grad_scale)
-        x = x.transpose(1, 2)                        # (N, S_out, C)
+        if self._channels_last_ok(x):
+            x = self._forward_channels_last(x)
+            if self.training and self.grad_scale != 1.0:
+                x = scale_gradient(x, self.grad_scale)
+        else:
+            for layer in self.layers:
+                x = layer(x)
+            if self.training and self.grad_scale != 1.0:
+                x = scale_gradient(x, self.grad_scale)
+            x = x.transpose(1, 2)                    # (N, S_out, C)
         lens = self._contract_seq_lens(seqs_layout.seq_lens)
         return x, BatchLayout(tuple(x.shape[:2]), lens, device=x.device)
+
+    def _channels_last_ok(self, x: Tensor) -> bool:
+        from fairseq2_b200.ops._ext import use_kernels
+
+        if not (use_kernels(x) and x.dtype == torch.bfloat16 and len(self.layers) > 1):
+            return False
+        first = self.layers[0]
+        if first.conv.weight.dtype != torch.bfloat16 or first.conv.out_channels % 8:
+            return False
+        return all(layer.conv.out_channels % 8 == 0 and layer.conv.kernel_size[0] >= layer.conv.stride[0]
+                   and layer.group_norm is None for layer in self.layers[1:])
+
+    def _forward_channels_last(self, x: Tensor) -> Tensor:
+        """The first convolution (few input channels) runs as usual; from then on activations stay channels-last
+        ``(N, S, C)`` and every strided convolution is one tcgen05 GEMM over an overlapping-row view, followed by
+        one fused LayerNorm+GELU kernel. Time steps are padded once so that every stride divides evenly; rows
+        past the true output length are meaningless and cut off at the end."""
+        from fairseq2_b200.ops.conv import conv1d_channels_last
+        from fairseq2_b200.ops.norm import layer_norm_gelu
+
+        valid = x.shape[-1]
+        x = self.layers[0](x)                        # (N, C, S1)
+        valid = (valid - self.layers[0].conv.kernel_size[0]) // self.layers[0].conv.stride[0] + 1
+        total_stride = 1
+        for layer in self.layers[1:]:
+            total_stride *= layer.conv.stride[0]
+        pad = (-x.shape[-1]) % total_stride
+        x = x.transpose(1, 2)
+        x = torch.nn.functional.pad(x, (0, 0, 0, pad)) if pad else x.contiguous()
+        for layer in self.layers[1:]:
+            k, s = layer.conv.kernel_size[0], layer.conv.stride[0]
+            x = conv1d_channels_last(x, layer.conv.weight, layer.conv.bias, s)
+            valid = (valid - k) // s + 1
+            if layer.dropout is not None:
+                x = layer.dropout(x)
+            if layer.layer_norm is not None:
+                ln = layer.layer_norm
+                x = layer_norm_gelu(x, ln.weight, ln.bias, ln.eps)
+            else:
+                x = torch.nn.functional.gelu(x)
+        return x[:, :valid]
 
     def _contract_seq_lens(self, seq_lens: Sequence[int]) -> list[int]:
         out = list(seq_lens)

@@ -503,3 +503,32 @@ def test_wav2vec2_gumbel_quantizer_kernel(training: bool) -> None:
         (q * w).sum().backward()
         (rq * w).sum().backward()
         assert _rel_err(logits.grad, lr.grad) < 1e-3 and _rel_err(entries.grad, er.grad) < 1e-3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("layer_norm", [True, False])
+def test_wav2vec2_feature_extractor_channels_last_path(layer_norm: bool) -> None:
+    """The GEMM-on-views path of the feature extractor against the Conv1d path, forward and weight gradients."""
+    from fairseq2_b200.models.wav2vec2.feature_extractor import Wav2Vec2FeatureExtractor
+    from fairseq2_b200.nn import BatchLayout
+    from fairseq2_b200.ops import _ext
+
+    torch.manual_seed(0)
+    descs = [(64, 10, 5), (64, 3, 2), (64, 3, 2), (64, 2, 2)]
+    fe = Wav2Vec2FeatureExtractor(descs, bias=layer_norm, layer_norm=layer_norm).to("cuda", torch.bfloat16)
+    wave = torch.randn(3, 4000, device="cuda", dtype=torch.bfloat16)
+    layout = BatchLayout((3, 4000), [4000, 3300, 2801], device=wave.device)
+    outs, grads = [], []
+    for fast in (True, False):
+        fe.zero_grad()
+        with _ext.kernels_enabled(fast):
+            assert fe._channels_last_ok(wave.unsqueeze(1)) == fast
+            y, y_layout = fe(wave, layout)
+        g = torch.randn(y.shape, device="cuda", dtype=torch.bfloat16, generator=torch.Generator("cuda").manual_seed(1))
+        (y.float() * g.float()).sum().backward()
+        outs.append(y.float())
+        grads.append([p.grad.float().clone() for p in fe.parameters()])
+    assert outs[0].shape == outs[1].shape and list(y_layout.seq_lens) == fe._contract_seq_lens([4000, 3300, 2801])
+    assert _rel_err(outs[0], outs[1]) < 3e-2
+    for a, b in zip(grads[0], grads[1]):
+        assert _rel_err(a, b) < 6e-2
