@@ -28,6 +28,7 @@ struct AttnParams {
     int num_seqs, total_q, total_k, max_q, max_k;
     int H, Hkv, D;
     int causal;
+    int window;    // > 0 (causal only): query i sees keys j with i + shift - window < j <= i + shift; 0 = no limit
     float scale;
 };
 

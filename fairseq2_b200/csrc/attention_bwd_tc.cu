@@ -194,7 +194,9 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_co
     const int shift = k_len - q_len;
     const int q_last = min(q0 + 128, q_len) - 1;
     const int kv_hi = p.causal ? min(k_len, q_last + shift + 1) : k_len;
-    const int n_iter = kv_hi > 0 ? (kv_hi + 63) / 64 : 0;
+    const bool windowed = p.causal && p.window > 0;
+    const int it0 = windowed ? max(0, q0 + shift - p.window + 1) / 64 : 0;     // first key tile inside the window
+    const int n_iter = kv_hi > 0 ? max(0, (kv_hi + 63) / 64 - it0) : 0;
     const int kvh = h / (p.H / p.Hkv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -238,7 +240,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_co
                 }
                 const uint32_t fb = c.bar(B_STG_FULL + st);
                 const uint32_t k_s = c.base + OFF_STG + st * STAGE_BYTES, v_s = k_s + SMALL_TILE;
-                const int row = k_begin + i * 64;
+                const int row = k_begin + (it0 + i) * 64;
                 mbar_arrive_expect_tx(fb, 2 * SMALL_TILE);
                 tma_load_2d(k_s, &tma_k, fb, kvh * HD, row);
                 tma_load_2d(k_s + BOX64, &tma_k, fb, kvh * HD + 64, row);
@@ -297,11 +299,12 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_co
         const float neg_lse2 = row_ok ? -p.lse[stat_idx] * LOG2E : -INFINITY;   // -inf -> probability 0
         const float delta = row_ok ? p.delta[stat_idx] : 0.f;
         const int lim = p.causal ? min(k_len - 1, q_row + shift) : k_len - 1;
+        const int lo = windowed ? q_row + shift - p.window + 1 : -(1 << 30);
         bool ok = true;
         for (int i = 0; i < n_iter; ++i) {
             const int b = i & 1;
             const uint32_t ph = static_cast<uint32_t>(i >> 1) & 1u;
-            const int kv0 = i * 64;
+            const int kv0 = (it0 + i) * 64;
             const int ob = i % DQ_NOP;
             if (!warp_wait(c.bar(B_ACC_FULL + b), ph, c.abort_flag) ||
                 !warp_wait(c.bar(B_OP_EMPTY + ob), (static_cast<uint32_t>(i / DQ_NOP) & 1u) ^ 1u, c.abort_flag)) {
@@ -309,7 +312,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_co
                 break;
             }
             tcgen05_fence_after();
-            const int rel = lim - kv0;
+            const int rel = lim - kv0, rel_lo = lo - kv0;
             const uint32_t t_s = t_lane + static_cast<uint32_t>(b * 128);
             const uint32_t ds_tile = c.base + DQ_OFF_OPER + ob * OPER_TILE;
 #pragma unroll
@@ -323,7 +326,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_co
                 for (int j = 0; j < 32; ++j) {
                     const float pr = ex2_approx(fmaf(__uint_as_float(s[j]), sl2, neg_lse2));
                     const float ds = pr * (__uint_as_float(dp[j]) - delta);
-                    e[j] = (cc * 32 + j <= rel) ? ds : 0.f;
+                    e[j] = (cc * 32 + j <= rel && cc * 32 + j >= rel_lo) ? ds : 0.f;
                 }
 #pragma unroll
                 for (int g = 0; g < 4; ++g) st_swizzled_chunk(ds_tile, row, static_cast<uint32_t>(cc * 4 + g), e + 8 * g);
@@ -361,7 +364,11 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
     // first query row that can see this tile (causal: q + shift >= kv0), rounded down to a 64-row tile
     const int q_lo = p.causal ? max(0, kv0 - shift) : 0;
     const int jt_lo = q_lo / 64;
-    const int jt_hi = (q_len + 63) / 64;
+    // sliding window: query rows beyond q_hi no longer see the last key of this tile
+    const bool windowed = p.causal && p.window > 0;
+    const int kv_last = min(kv0 + 128, k_len) - 1;
+    const int q_hi = windowed ? min(q_len, kv_last - shift + p.window) : q_len;     // exclusive
+    const int jt_hi = (q_hi + 63) / 64;
     const int per_head = max(0, jt_hi - jt_lo);
     const int n_iter = per_head * G;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -497,6 +504,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
             tcgen05_fence_after();
             // query column j (row qt0 + j) sees key kv_row iff kv_row <= qt0 + j + shift
             const int jmin = p.causal ? kv_row - shift - qt0 : 0;     // columns below jmin are masked
+            const int jmax = windowed ? kv_row - shift + p.window - 1 - qt0 : (1 << 30);   // and above jmax
             const uint32_t t_s = t_lane + static_cast<uint32_t>(b * 128);
             const uint32_t pt_tile = c.base + KV_OFF_OPER + ob * 2 * OPER_TILE, dst_tile = pt_tile + OPER_TILE;
 #pragma unroll
@@ -511,7 +519,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
                     const int col = cc * 32 + j;
                     float pr = ex2_approx(fmaf(__uint_as_float(s[j]), sl2, nl[col]));
                     float ds = pr * (__uint_as_float(dp[j]) - dl[col]);
-                    const bool live = row_ok && col >= jmin;
+                    const bool live = row_ok && col >= jmin && col <= jmax;
                     pe[j] = live ? pr : 0.f;
                     de[j] = live ? ds : 0.f;
                 }

@@ -92,7 +92,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     const int q_last = min(q0 + TQ, q_len) - 1;
     const int kv_hi = p.causal ? min(k_len, q_last + shift + 1) : k_len;
     if (kv_hi <= 0) return;                                // nothing to attend to: output stays zero
-    const int n_iter = (kv_hi + TK - 1) / TK;
+    // sliding window: the first key any row of this tile can see, rounded down to a key tile
+    const bool windowed = p.causal && p.window > 0;
+    const int it0 = windowed ? max(0, q0 + shift - p.window + 1) / TK : 0;
+    const int n_iter = (kv_hi + TK - 1) / TK - it0;
+    if (n_iter <= 0) return;
     const int kvh = h / (p.H / p.Hkv);
 
     extern __shared__ uint8_t smem_raw[];
@@ -146,7 +150,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
             for (int i = 0; i < n_iter; ++i) {
                 const int st = i & 1;
                 const uint32_t ph = static_cast<uint32_t>(i >> 1) & 1u;
-                const int row = k_begin + i * TK;
+                const int row = k_begin + (it0 + i) * TK;
                 if (!mbar_wait_bounded(bar(BAR_K_EMPTY + st), ph ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
                     if (!*abort_flag) report_status(status, kStatusTimeout | (0x11 << 8));
                     *abort_flag = 1;
@@ -239,6 +243,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
         const float sl2 = p.scale * LOG2E_F;
         const int lim = p.causal ? min(k_len - 1, q_row + shift) : k_len - 1;   // last visible key of this row
+        const int lo = windowed ? q_row + shift - p.window + 1 : -(1 << 30);    // first visible key of this row
         float m = -INFINITY, l = 0.f, alpha_prev = 1.f;
         float o[HD];
 #pragma unroll
@@ -266,14 +271,16 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         for (int i = 0; i < n_iter; ++i) {
             const int b = i & 1;
             const uint32_t ph = static_cast<uint32_t>(i >> 1) & 1u;
-            const int kv0 = i * TK;
+            const int kv0 = (it0 + i) * TK;
             if (!warp_wait(bar(BAR_S_FULL + b), ph, abort_flag)) {
                 ok = false;
                 break;
             }
             tcgen05_fence_after();
-            const bool need_mask = (kv0 + TK > k_len) || (p.causal && kv0 + TK - 1 > q0 + shift);
+            const bool need_mask = (kv0 + TK > k_len) || (p.causal && kv0 + TK - 1 > q0 + shift) ||
+                                   (windowed && q_last + shift - p.window + 1 > kv0);
             const int rel = lim - kv0;                 // columns > rel are masked
+            const int rel_lo = lo - kv0;               // columns < rel_lo are masked (sliding window)
             const uint32_t t_s = t_lane + static_cast<uint32_t>(b * 128);
             // pass 1: row maximum
             float mx = -INFINITY;
@@ -285,7 +292,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
                 if (need_mask) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
-                        if (c * 32 + j <= rel) mx = fmaxf(mx, __uint_as_float(v[j]));
+                        if (c * 32 + j <= rel && c * 32 + j >= rel_lo) mx = fmaxf(mx, __uint_as_float(v[j]));
                 } else {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(v[j]));
@@ -307,7 +314,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     float pr = ex2_approx(fmaf(__uint_as_float(v[j]), sl2, neg_ms));
-                    if (need_mask && c * 32 + j > rel) pr = 0.f;
+                    if (need_mask && (c * 32 + j > rel || c * 32 + j < rel_lo)) pr = 0.f;
                     e[j] = pr;
                     rowsum += pr;
                 }

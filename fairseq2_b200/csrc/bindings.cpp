@@ -736,8 +736,11 @@ fs2::AttnParams make_attn_params(const Tensor& q, const Tensor& k, const Tensor&
 
 std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& qb,
                                     const Tensor& ql, const Tensor& kb, const Tensor& kl, int64_t max_q,
-                                    int64_t max_k, bool causal, double scale) {
+                                    int64_t max_k, bool causal, double scale, int64_t window) {
     fs2::AttnParams p = make_attn_params(q, k, v, qb, ql, kb, kl, max_q, max_k, causal, scale);
+    TORCH_CHECK(window >= 0 && (window == 0 || (causal && p.D == 128)),
+                "attn_fwd: a sliding window needs causal attention with head_dim 128");
+    p.window = static_cast<int>(window);
     c10::cuda::CUDAGuard guard(q.device());
     // rows that belong to no sequence (padding) stay zero
     Tensor out = at::zeros({q.size(0), q.size(1), q.size(2)}, q.options());
@@ -750,8 +753,8 @@ std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tens
         const char* e = std::getenv("FAIRSEQ2_B200_ATTN");
         return e == nullptr || std::string(e) != "mma";
     }();
-    const char* err = (use_tc && p.D == 128) ? fs2::attn_forward_tc(p, status_dev_ptr(), stream_of(q))
-                                             : fs2::attn_forward(p, stream_of(q));
+    const char* err = ((use_tc || p.window > 0) && p.D == 128) ? fs2::attn_forward_tc(p, status_dev_ptr(), stream_of(q))
+                                                               : fs2::attn_forward(p, stream_of(q));
     TORCH_CHECK(err == nullptr, "attn_fwd: ", err);
     g_launches += 1;
     return {out, lse};
@@ -759,8 +762,12 @@ std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tens
 
 void attn_bwd_out(const Tensor& dout, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out,
                   const Tensor& lse, const Tensor& qb, const Tensor& ql, const Tensor& kb, const Tensor& kl,
-                  int64_t max_q, int64_t max_k, bool causal, double scale, Tensor dq, Tensor dk, Tensor dv) {
+                  int64_t max_q, int64_t max_k, bool causal, double scale, Tensor dq, Tensor dk, Tensor dv,
+                  int64_t window) {
     fs2::AttnParams p = make_attn_params(q, k, v, qb, ql, kb, kl, max_q, max_k, causal, scale);
+    TORCH_CHECK(window >= 0 && (window == 0 || (causal && p.D == 128)),
+                "attn_bwd: a sliding window needs causal attention with head_dim 128");
+    p.window = static_cast<int>(window);
     auto check_view = [](const Tensor& t, const Tensor& like, const char* name) {
         TORCH_CHECK(t.is_cuda() && is_bf16(t) && t.sizes() == like.sizes() && t.stride(2) == 1 &&
                         t.stride(1) == t.size(2) && t.stride(0) % 8 == 0 && aligned16(t),
@@ -789,8 +796,8 @@ void attn_bwd_out(const Tensor& dout, const Tensor& q, const Tensor& k, const Te
         const char* e = std::getenv("FAIRSEQ2_B200_ATTN");
         return e == nullptr || (std::string(e) != "mma" && std::string(e) != "mma_bwd");
     }();
-    const char* err = (use_tc && p.D == 128) ? fs2::attn_backward_tc(p, status_dev_ptr(), stream_of(q))
-                                             : fs2::attn_backward(p, stream_of(q));
+    const char* err = ((use_tc || p.window > 0) && p.D == 128) ? fs2::attn_backward_tc(p, status_dev_ptr(), stream_of(q))
+                                                               : fs2::attn_backward(p, stream_of(q));
     TORCH_CHECK(err == nullptr, "attn_bwd: ", err);
     g_launches += 3;
 }
@@ -798,12 +805,12 @@ void attn_bwd_out(const Tensor& dout, const Tensor& q, const Tensor& k, const Te
 std::tuple<Tensor, Tensor, Tensor> attn_bwd(const Tensor& dout, const Tensor& q, const Tensor& k, const Tensor& v,
                                             const Tensor& out, const Tensor& lse, const Tensor& qb, const Tensor& ql,
                                             const Tensor& kb, const Tensor& kl, int64_t max_q, int64_t max_k,
-                                            bool causal, double scale) {
+                                            bool causal, double scale, int64_t window) {
     // tokens outside every sequence (padding) receive zero gradients
     Tensor dq = at::zeros({q.size(0), q.size(1), q.size(2)}, q.options());
     Tensor dk = at::zeros({k.size(0), k.size(1), k.size(2)}, k.options());
     Tensor dv = at::zeros({v.size(0), v.size(1), v.size(2)}, v.options());
-    attn_bwd_out(dout, q, k, v, out, lse, qb, ql, kb, kl, max_q, max_k, causal, scale, dq, dk, dv);
+    attn_bwd_out(dout, q, k, v, out, lse, qb, ql, kb, kl, max_q, max_k, causal, scale, dq, dk, dv, window);
     return {dq, dk, dv};
 }
 

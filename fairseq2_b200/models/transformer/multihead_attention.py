@@ -375,7 +375,10 @@ class StandardMultiheadAttention(MultiheadAttention):
         if state_bag is not None or self._attn_weight_hooks or not isinstance(self.sdpa, VarlenSDPA):
             return None
         bias = self.sdpa.bias
-        if not isinstance(bias, (CausalAttentionBias, IdentityBias)) or getattr(bias, "attn_window_len", None):
+        if not isinstance(bias, (CausalAttentionBias, IdentityBias)):
+            return None
+        window = getattr(bias, "attn_window_len", None)
+        if window and self.head_dim != 128:        # the sliding window lives in the tcgen05 kernels only
             return None
         if self.training and self.sdpa.dropout_p > 0.0:
             return None
@@ -394,7 +397,7 @@ class StandardMultiheadAttention(MultiheadAttention):
         out = qkv_rope_attention(flat, freqs, pos, layout.seq_begin_indices_pt[:-1], layout.seq_lens_pt,
                                  layout.max_seq_len, num_heads=H, num_kv_heads=Hkv,
                                  causal=isinstance(bias, CausalAttentionBias),
-                                 has_padding=layout.padded or sum(layout.seq_lens) < flat.shape[0])
+                                 has_padding=layout.padded or sum(layout.seq_lens) < flat.shape[0], window=window)
         out = out.flatten(-2, -1)
         if not layout.packed:
             out = out.view(*qkv.shape[:2], H * self.head_dim)

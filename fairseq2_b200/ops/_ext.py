@@ -50,7 +50,30 @@ def get_ext() -> ModuleType:
         except ImportError as ex:
             _err = str(ex)
             raise
+        _install_status_check(_ext)
     return _ext
+
+
+class KernelWaitTimeout(RuntimeError):
+    """A kernel gave up on a bounded wait (a peer never signalled, a copy never landed) and returned early."""
+
+    def __init__(self, code: int, site: int) -> None:
+        super().__init__(f"a fairseq2_b200 kernel gave up on a bounded wait (code {code}, site {site})")
+        self.code, self.site = code, site
+
+
+def _install_status_check(mod: ModuleType) -> None:
+    """``ext.check_status()`` is evaluated in Python: it reads the host-mapped status word, clears it and raises
+    ``KernelWaitTimeout``. The error therefore never travels through C++ unwinding of a process whose GPU peers may
+    already be gone."""
+
+    def check_status() -> None:
+        status = int(mod.read_status())
+        if status != 0:
+            mod.reset_status()
+            raise KernelWaitTimeout(status & 0xFF, status >> 8)
+
+    mod.check_status = check_status  # type: ignore[attr-defined]
 
 
 def ext_available() -> bool:

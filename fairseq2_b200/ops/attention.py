@@ -43,20 +43,21 @@ def attention_reference(q: Tensor, k: Tensor, v: Tensor, q_begins: Tensor, q_len
 
 class _AttnFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, q_begins, q_lens, k_begins, k_lens, max_q, max_k, causal, scale):  # type: ignore[override]
+    def forward(ctx, q, k, v, q_begins, q_lens, k_begins, k_lens, max_q, max_k, causal, scale, window):  # type: ignore[override]
         ext = require_ext()
-        out, lse = ext.attn_fwd(q, k, v, q_begins, q_lens, k_begins, k_lens, max_q, max_k, causal, scale)
+        out, lse = ext.attn_fwd(q, k, v, q_begins, q_lens, k_begins, k_lens, max_q, max_k, causal, scale, window)
         ctx.save_for_backward(q, k, v, out, lse, q_begins, q_lens, k_begins, k_lens)
-        ctx.meta = (max_q, max_k, causal, scale)
+        ctx.meta = (max_q, max_k, causal, scale, window)
         return out
 
     @staticmethod
     def backward(ctx, dout):  # type: ignore[override]
         ext = require_ext()
         q, k, v, out, lse, qb, ql, kb, kl = ctx.saved_tensors
-        max_q, max_k, causal, scale = ctx.meta
-        dq, dk, dv = ext.attn_bwd(dout.contiguous(), q, k, v, out, lse, qb, ql, kb, kl, max_q, max_k, causal, scale)
-        return dq, dk, dv, None, None, None, None, None, None, None, None
+        max_q, max_k, causal, scale, window = ctx.meta
+        dq, dk, dv = ext.attn_bwd(dout.contiguous(), q, k, v, out, lse, qb, ql, kb, kl, max_q, max_k, causal, scale,
+                                  window)
+        return dq, dk, dv, None, None, None, None, None, None, None, None, None
 
 
 def varlen_attention(q: Tensor, k: Tensor, v: Tensor, q_begins: Tensor, q_lens: Tensor, k_begins: Tensor,
@@ -64,9 +65,11 @@ def varlen_attention(q: Tensor, k: Tensor, v: Tensor, q_begins: Tensor, q_lens: 
                      window: int | None = None) -> Tensor:
     D = q.shape[-1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    if (use_kernels(q) and q.dtype == torch.bfloat16 and D in (64, 128) and window is None
+    windowed = window is not None and window > 0
+    if (use_kernels(q) and q.dtype == torch.bfloat16 and D in (64, 128) and (not windowed or (causal and D == 128))
             and q.is_contiguous() and k.is_contiguous() and v.is_contiguous()):
-        return _AttnFn.apply(q, k, v, q_begins, q_lens, k_begins, k_lens, max_q, max_k, causal, scale)
+        return _AttnFn.apply(q, k, v, q_begins, q_lens, k_begins, k_lens, max_q, max_k, causal, scale,
+                             window if windowed else 0)
     return attention_reference(q, k, v, q_begins, q_lens, k_begins, k_lens, causal, scale, window)
 
 
@@ -77,7 +80,7 @@ class _QKVRopeAttnFn(torch.autograd.Function):
     projection's dgrad/wgrad GEMMs consume it without a concat."""
 
     @staticmethod
-    def forward(ctx, qkv, freqs, positions, begins, lens, max_len, causal, scale, H, Hkv, has_padding):  # type: ignore[override]
+    def forward(ctx, qkv, freqs, positions, begins, lens, max_len, causal, scale, H, Hkv, has_padding, window=0):  # type: ignore[override]
         ext = require_ext()
         if freqs is not None:
             # The producer of `qkv` (the merged projection) does not need its own
@@ -85,31 +88,32 @@ class _QKVRopeAttnFn(torch.autograd.Function):
             # call bypasses autograd's version counters by construction.
             ext.rope_inplace(qkv[:, : H + Hkv], freqs, positions, False)
         q, k, v = qkv[:, :H], qkv[:, H:H + Hkv], qkv[:, H + Hkv:]
-        out, lse = ext.attn_fwd(q, k, v, begins, lens, begins, lens, max_len, max_len, causal, scale)
+        out, lse = ext.attn_fwd(q, k, v, begins, lens, begins, lens, max_len, max_len, causal, scale, window)
         ctx.save_for_backward(qkv, out, lse, begins, lens, freqs, positions)
-        ctx.meta = (max_len, causal, scale, H, Hkv, has_padding)
+        ctx.meta = (max_len, causal, scale, H, Hkv, has_padding, window)
         return out
 
     @staticmethod
     def backward(ctx, dout):  # type: ignore[override]
         ext = require_ext()
         qkv, out, lse, begins, lens, freqs, positions = ctx.saved_tensors
-        max_len, causal, scale, H, Hkv, has_padding = ctx.meta
+        max_len, causal, scale, H, Hkv, has_padding, window = ctx.meta
         q, k, v = qkv[:, :H], qkv[:, H:H + Hkv], qkv[:, H + Hkv:]
         # rows outside every sequence are never written by the kernels: they must read as zero gradients
         dqkv = torch.zeros_like(qkv) if has_padding else torch.empty_like(qkv)
         ext.attn_bwd_out(dout.contiguous(), q, k, v, out, lse, begins, lens, begins, lens, max_len, max_len, causal,
-                         scale, dqkv[:, :H], dqkv[:, H:H + Hkv], dqkv[:, H + Hkv:])
+                         scale, dqkv[:, :H], dqkv[:, H:H + Hkv], dqkv[:, H + Hkv:], window)
         if freqs is not None:
             ext.rope_inplace(dqkv[:, : H + Hkv], freqs, positions, True)
-        return dqkv, None, None, None, None, None, None, None, None, None, None
+        return dqkv, None, None, None, None, None, None, None, None, None, None, None
 
 
 def qkv_rope_attention(qkv: Tensor, freqs: Tensor | None, positions: Tensor | None, begins: Tensor, lens: Tensor,
                        max_len: int, *, num_heads: int, num_kv_heads: int, causal: bool = True,
-                       scale: float | None = None, has_padding: bool = True) -> Tensor:
-    """``qkv``: contiguous bf16 ``[T, H + 2·Hkv, D]`` (modified in place). Returns ``[T, H, D]``."""
+                       scale: float | None = None, has_padding: bool = True, window: int | None = None) -> Tensor:
+    """``qkv``: contiguous bf16 ``[T, H + 2·Hkv, D]`` (modified in place). Returns ``[T, H, D]``. ``window``
+    (causal, head_dim 128 only): every query sees at most that many most recent keys, itself included."""
     D = qkv.shape[-1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     return _QKVRopeAttnFn.apply(qkv, freqs, positions, begins, lens, max_len, causal, scale, num_heads, num_kv_heads,
-                                has_padding)
+                                has_padding, window or 0)

@@ -83,15 +83,15 @@ def bench_attention(a: argparse.Namespace) -> None:
     q, k, v = qkv[:, :H], qkv[:, H:H + Hkv], qkv[:, H + Hkv:]
     scale = 1.0 / math.sqrt(D)
     fl_fwd = 4.0 * (T // S) * H * D * S * S / 2      # causal: half of the score matrix
-    out, lse = ext.attn_fwd(q, k, v, begins, lens, begins, lens, S, S, True, scale)
-    ms = _time(lambda: ext.attn_fwd(q, k, v, begins, lens, begins, lens, S, S, True, scale), a.iters, a.warmup)
+    out, lse = ext.attn_fwd(q, k, v, begins, lens, begins, lens, S, S, True, scale, 0)
+    ms = _time(lambda: ext.attn_fwd(q, k, v, begins, lens, begins, lens, S, S, True, scale, 0), a.iters, a.warmup)
     _emit("attention_fwd", ms, flops=fl_fwd, tokens=T, seq_len=S, heads=H, kv_heads=Hkv, head_dim=D)
     dout = torch.randn_like(out)
     dqkv = torch.empty_like(qkv)
 
     def bwd() -> None:
         ext.attn_bwd_out(dout, q, k, v, out, lse, begins, lens, begins, lens, S, S, True, scale, dqkv[:, :H],
-                         dqkv[:, H:H + Hkv], dqkv[:, H + Hkv:])
+                         dqkv[:, H:H + Hkv], dqkv[:, H + Hkv:], 0)
 
     ms = _time(bwd, a.iters, a.warmup)
     _emit("attention_bwd", ms, flops=2.5 * fl_fwd, tokens=T, seq_len=S, heads=H, kv_heads=Hkv, head_dim=D)

@@ -111,4 +111,4 @@ def gumbel_quantize(logits: Tensor, noise: Tensor | None, entries: Tensor, G: in
 
 def sample_gumbel_noise(shape: tuple[int, ...], device: torch.device, generator: torch.Generator | None = None) -> Tensor:
     u = torch.rand(shape, device=device, generator=generator).clamp_(1e-10, 1.0)
-    return -torch.log(-torch.log(u).clamp_(min=1e-10))
+    return -torch.log((-torch.log(u)).clamp_(min=1e-10))

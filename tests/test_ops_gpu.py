@@ -216,6 +216,33 @@ def test_attention_long_sequences(causal: bool) -> None:
     assert require_ext().read_status() == 0
 
 
+@pytest.mark.parametrize("window", [1, 50, 128, 300, 5000])
+def test_attention_sliding_window(window: int) -> None:
+    """Causal attention restricted to the `window` most recent keys (tcgen05 kernels, head_dim 128): key tiles
+    before the window are skipped, the tile at its edge is masked; forward and all three gradients."""
+    torch.manual_seed(21)
+    H, Hkv, D = 4, 2, 128
+    lens = [700, 129, 1, 333]
+    T = sum(lens)
+    q = torch.randn((T, H, D), device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn((T, Hkv, D), device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn((T, Hkv, D), device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    b, l = _seqs(lens)
+    out = varlen_attention(q, k, v, b, l, b, l, max(lens), max(lens), causal=True, window=window)
+    g = torch.randn_like(out)
+    out.backward(g)
+    qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    ref = attention_reference(qr, kr, vr, b, l, b, l, True, None, window)
+    ref.backward(g.float())
+    assert _rel_err(out, ref) < 1e-2
+    assert _rel_err(q.grad, qr.grad) < 2e-2
+    assert _rel_err(k.grad, kr.grad) < 2e-2
+    assert _rel_err(v.grad, vr.grad) < 2e-2
+    from fairseq2_b200.ops._ext import require_ext
+
+    assert require_ext().read_status() == 0
+
+
 def test_attention_cross_lengths() -> None:
     """Lk > Lq (prefill against a cache): bottom-right aligned causal mask."""
     torch.manual_seed(9)
@@ -497,12 +524,14 @@ def test_wav2vec2_gumbel_quantizer_kernel(training: bool) -> None:
     lr, er = logits.detach().clone().requires_grad_(True), entries.detach().clone().requires_grad_(True)
     rq, rsel, rprob, rhard = gumbel_quantize_reference(lr, noise, er, G, 1.7, training)
     assert torch.equal(sel.long(), rsel) and torch.allclose(hard, rhard) and torch.allclose(prob_sum, rprob, atol=1e-4)
-    assert torch.allclose(q, rq, atol=1e-5)
+    rows = torch.arange(frames * G, device="cuda")
+    assert torch.equal(q, entries.detach().view(G, V, E)[rows % G, sel.long()])      # an exact code-book lookup
+    assert torch.allclose(q, rq, atol=2e-3)                # the dense oracle may run its contraction in TF32
     if training:
         w = torch.randn_like(q)
         (q * w).sum().backward()
         (rq * w).sum().backward()
-        assert _rel_err(logits.grad, lr.grad) < 1e-3 and _rel_err(entries.grad, er.grad) < 1e-3
+        assert _rel_err(logits.grad, lr.grad) < 5e-3 and _rel_err(entries.grad, er.grad) < 5e-3
 
 
 @pytest.mark.gpu
