@@ -77,6 +77,9 @@ enum : int {
 };
 
 
+// WINDOWED compiles the sliding-window bounds in; the plain instantiation keeps the softmax loop free of them (the
+// softmax warps are the bottleneck of this kernel: one extra instruction per score costs several percent).
+template <bool WINDOWED>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                    const __grid_constant__ CUtensorMap tma_v, const AttnParams p, int* status) {
@@ -93,7 +96,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     const int kv_hi = p.causal ? min(k_len, q_last + shift + 1) : k_len;
     if (kv_hi <= 0) return;                                // nothing to attend to: output stays zero
     // sliding window: the first key any row of this tile can see, rounded down to a key tile
-    const bool windowed = p.causal && p.window > 0;
+    constexpr bool windowed = WINDOWED;
     const int it0 = windowed ? max(0, q0 + shift - p.window + 1) / TK : 0;
     const int n_iter = (kv_hi + TK - 1) / TK - it0;
     if (n_iter <= 0) return;
@@ -292,7 +295,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
                 if (need_mask) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
-                        if (c * 32 + j <= rel && c * 32 + j >= rel_lo) mx = fmaxf(mx, __uint_as_float(v[j]));
+                        if (c * 32 + j <= rel && (!WINDOWED || c * 32 + j >= rel_lo)) mx = fmaxf(mx, __uint_as_float(v[j]));
                 } else {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(v[j]));
@@ -314,7 +317,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     float pr = ex2_approx(fmaf(__uint_as_float(v[j]), sl2, neg_ms));
-                    if (need_mask && (c * 32 + j > rel || c * 32 + j < rel_lo)) pr = 0.f;
+                    if (need_mask && (c * 32 + j > rel || (WINDOWED && c * 32 + j < rel_lo))) pr = 0.f;
                     e[j] = pr;
                     rowsum += pr;
                 }
@@ -390,13 +393,19 @@ const char* attn_forward_tc(const AttnParams& p, int* status, cudaStream_t st) {
         return tmap_error();
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(attn_fwd_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              TC_SMEM_BYTES);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(attn_fwd_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     TC_SMEM_BYTES);
         if (e != cudaSuccess) return cudaGetErrorString(e);
         configured = true;
     }
     const dim3 grid((p.max_q + TQ - 1) / TQ, p.num_seqs, p.H);
-    attn_fwd_tc_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, st>>>(tq, tk, tv, p, status);
+    if (p.causal && p.window > 0)
+        attn_fwd_tc_kernel<true><<<grid, TC_THREADS, TC_SMEM_BYTES, st>>>(tq, tk, tv, p, status);
+    else
+        attn_fwd_tc_kernel<false><<<grid, TC_THREADS, TC_SMEM_BYTES, st>>>(tq, tk, tv, p, status);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }

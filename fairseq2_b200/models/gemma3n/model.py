@@ -1,0 +1,280 @@
+"""Gemma 3n text decoder: AltUp (alternating updates over ``altup_num_inputs`` hidden streams), LAuReL low-rank
+residuals, per-layer input embeddings, local/global attention with two RoPE bases, query/key/value RMS norms,
+key/value sharing across the last layers, Gaussian top-k activation sparsity and final logit soft-capping
+(cf. fairseq2 ``models/gemma3n/{altup,decoder_layer,decoder,frontend,model}.py``).
+"""
+from __future__ import annotations
+
+import math
+from typing import Literal
+
+import torch
+import torch.nn.functional as F
+from torch import Tensor
+from torch.nn import Module, ModuleList, Parameter
+
+from fairseq2_b200.models.gemma3n.config import Gemma3nConfig, is_global_layer, kv_source_layer
+from fairseq2_b200.nn import BatchLayout
+from fairseq2_b200.nn.functional import cross_entropy
+from fairseq2_b200.nn.normalization import RMSNorm
+from fairseq2_b200.nn.projection import Linear
+from fairseq2_b200.ops.attention import varlen_attention
+from fairseq2_b200.typing import DataType, Device
+
+
+def _rms(x: Tensor, eps: float) -> Tensor:
+    """Scale-free RMS normalisation in fp32."""
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).type_as(x)
+
+
+class AltUp(Module):
+    """Predict-and-correct mixing of the hidden streams around a layer that only transforms the active one."""
+
+    def __init__(self, cfg: Gemma3nConfig, device: Device | None, dtype: DataType | None) -> None:
+        super().__init__()
+        n, d = cfg.altup_num_inputs, cfg.model_dim
+        kw = {"device": device, "dtype": dtype}
+        self.n, self.active, self.clip = n, cfg.altup_active_idx, cfg.altup_coef_clip
+        self.correct_output_scale = Parameter(torch.zeros(d, **kw))
+        self.correction_coefs = Linear(n, n, bias=False, **kw)
+        self.prediction_coefs = Linear(n, n * n, bias=False, **kw)
+        self.modality_router = Linear(d, n, bias=False, **kw)
+        self.router_norm = RMSNorm(d, bias=False, eps=cfg.rms_norm_eps, **kw)
+        self.router_input_scale = 1.0 / d
+
+    def _modalities(self, x: Tensor) -> Tensor:
+        return torch.tanh(self.modality_router(self.router_norm(x) * self.router_input_scale).float()).type_as(x)
+
+    def _clipped(self, w: Tensor) -> Tensor:
+        return w.clamp(-self.clip, self.clip) if (self.training and self.clip is not None) else w
+
+    def predict(self, streams: Tensor) -> Tensor:
+        """``streams``: ``[n, ..., D]`` -> predictions of the same shape."""
+        m = self._modalities(streams[self.active])                                    # [..., n]
+        coefs = F.linear(m, self._clipped(self.prediction_coefs.weight))              # [..., n*n]
+        coefs = coefs.reshape(*m.shape[:-1], self.n, self.n).transpose(-1, -2)
+        x = streams.movedim(0, -1)                                                     # [..., D, n]
+        pred = torch.matmul(x, coefs).movedim(-1, 0)
+        return (pred + streams).contiguous().type_as(streams)
+
+    def correct(self, predictions: Tensor, activated: Tensor) -> Tensor:
+        m = self._modalities(activated)
+        innovation = activated - predictions[self.active]
+        coefs = F.linear(m, self._clipped(self.correction_coefs.weight)) + 1.0         # [..., n]
+        coefs = coefs.movedim(-1, 0).unsqueeze(-1)
+        return (innovation.unsqueeze(0) * coefs + predictions).contiguous().type_as(activated)
+
+    def scale_corrected_output(self, x: Tensor) -> Tensor:
+        return (x.type_as(self.correct_output_scale) * self.correct_output_scale).type_as(x)
+
+
+class Laurel(Module):
+    """``x + norm(right(left(x)))`` with a rank-``laurel_rank`` bottleneck."""
+
+    def __init__(self, cfg: Gemma3nConfig, device: Device | None, dtype: DataType | None) -> None:
+        super().__init__()
+        kw = {"device": device, "dtype": dtype}
+        self.linear_left = Linear(cfg.model_dim, cfg.laurel_rank, bias=False, **kw)
+        self.linear_right = Linear(cfg.laurel_rank, cfg.model_dim, bias=False, **kw)
+        self.post_laurel_norm = RMSNorm(cfg.model_dim, bias=False, eps=cfg.rms_norm_eps, **kw)
+
+    def forward(self, x: Tensor) -> Tensor:
+        return x + self.post_laurel_norm(self.linear_right(self.linear_left(x)))
+
+
+class Gemma3nFFN(Module):
+    def __init__(self, cfg: Gemma3nConfig, sparsity: float, device: Device | None, dtype: DataType | None) -> None:
+        super().__init__()
+        kw = {"device": device, "dtype": dtype}
+        self.gate_proj = Linear(cfg.model_dim, cfg.ffn_inner_dim, bias=False, **kw)
+        self.up_proj = Linear(cfg.model_dim, cfg.ffn_inner_dim, bias=False, **kw)
+        self.down_proj = Linear(cfg.ffn_inner_dim, cfg.model_dim, bias=False, **kw)
+        self.sparsity = sparsity
+        # standard-normal quantile of the target sparsity: entries below mean + z * std are zeroed
+        self.std_multiplier = math.sqrt(2.0) * float(torch.erfinv(torch.tensor(2.0 * sparsity - 1.0))) if sparsity > 0 else 0.0
+
+    def forward(self, x: Tensor) -> Tensor:
+        gate = self.gate_proj(x)
+        if self.sparsity > 0.0:
+            mean = gate.mean(dim=-1, keepdim=True)
+            std = gate.std(dim=-1, keepdim=True, unbiased=False)
+            gate = F.relu(gate - (mean + std * self.std_multiplier))
+        return self.down_proj(F.gelu(gate, approximate="tanh") * self.up_proj(x))
+
+
+def _rope_half(x: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
+    """Half-rotation RoPE: ``x`` ``[T, H, D]``, ``cos``/``sin`` ``[T, D]``."""
+    d = x.shape[-1] // 2
+    rot = torch.cat((-x[..., d:], x[..., :d]), dim=-1)
+    return x * cos.unsqueeze(1) + rot * sin.unsqueeze(1)
+
+
+class Gemma3nAttention(Module):
+    def __init__(self, cfg: Gemma3nConfig, layer_idx: int, device: Device | None, dtype: DataType | None) -> None:
+        super().__init__()
+        kw = {"device": device, "dtype": dtype}
+        H, Hkv, D = cfg.num_attn_heads, cfg.num_key_value_heads, cfg.head_dim
+        self.H, self.Hkv, self.D, self.eps = H, Hkv, D, cfg.rms_norm_eps
+        self.is_global = is_global_layer(layer_idx, cfg.num_layers)
+        self.window = None if self.is_global else cfg.sliding_window
+        self.kv_source = kv_source_layer(layer_idx, cfg.num_layers, cfg.num_kv_shared_layers)
+        self.q_proj = Linear(cfg.model_dim, H * D, bias=False, **kw)
+        self.k_proj = Linear(cfg.model_dim, Hkv * D, bias=False, **kw)
+        self.v_proj = Linear(cfg.model_dim, Hkv * D, bias=False, **kw)
+        self.o_proj = Linear(H * D, cfg.model_dim, bias=False, **kw)
+        self.q_norm = RMSNorm(D, bias=False, eps=cfg.rms_norm_eps, **kw)
+        self.k_norm = RMSNorm(D, bias=False, eps=cfg.rms_norm_eps, **kw)
+
+    def forward(self, x: Tensor, cos: Tensor, sin: Tensor, layout: BatchLayout, begins: Tensor, lens: Tensor,
+                shared_kv: dict[int, tuple[Tensor, Tensor]], layer_idx: int) -> Tensor:
+        """``x``: ``[T, D_model]`` (tokens of all sequences, flattened)."""
+        T = x.shape[0]
+        q = _rope_half(self.q_norm(self.q_proj(x).view(T, self.H, self.D)), cos, sin)
+        if self.kv_source is not None and self.kv_source in shared_kv:
+            k, v = shared_kv[self.kv_source]
+        else:
+            k = _rope_half(self.k_norm(self.k_proj(x).view(T, self.Hkv, self.D)), cos, sin)
+            v = _rms(self.v_proj(x).view(T, self.Hkv, self.D), self.eps)
+            shared_kv[layer_idx] = (k, v)
+        out = varlen_attention(q.contiguous(), k.contiguous(), v.contiguous(), begins, lens, begins, lens,
+                               layout.max_seq_len, layout.max_seq_len, causal=True, scale=1.0, window=self.window)
+        return self.o_proj(out.reshape(T, self.H * self.D))
+
+
+class Gemma3nDecoderLayer(Module):
+    def __init__(self, cfg: Gemma3nConfig, layer_idx: int, device: Device | None, dtype: DataType | None) -> None:
+        super().__init__()
+        kw = {"device": device, "dtype": dtype}
+        d, p = cfg.model_dim, cfg.hidden_size_per_layer_input
+        self.layer_idx, self.active, self.correct_scale = layer_idx, cfg.altup_active_idx, cfg.altup_correct_scale
+        self.self_attn = Gemma3nAttention(cfg, layer_idx, device, dtype)
+        self.mlp = Gemma3nFFN(cfg, cfg.activation_sparsity if layer_idx < cfg.num_sparse_layers else 0.0, device, dtype)
+        norm = lambda: RMSNorm(d, bias=False, eps=cfg.rms_norm_eps, **kw)  # noqa: E731
+        self.input_layernorm, self.post_attention_layernorm = norm(), norm()
+        self.pre_feedforward_layernorm, self.post_feedforward_layernorm = norm(), norm()
+        self.altup = AltUp(cfg, device, dtype)
+        self.laurel = Laurel(cfg, device, dtype)
+        self.per_layer_input_gate = Linear(d, p, bias=False, **kw)
+        self.per_layer_projection = Linear(p, d, bias=False, **kw)
+        self.post_per_layer_input_norm = norm()
+
+    def forward(self, streams: Tensor, per_layer_input: Tensor, cos: Tensor, sin: Tensor, layout: BatchLayout,
+                begins: Tensor, lens: Tensor, shared_kv: dict[int, tuple[Tensor, Tensor]]) -> Tensor:
+        predictions = self.altup.predict(streams)
+        active = predictions[self.active]
+        normed = self.input_layernorm(active)
+        laurel = self.laurel(normed)
+        attn = self.post_attention_layernorm(self.self_attn(normed, cos, sin, layout, begins, lens, shared_kv,
+                                                            self.layer_idx))
+        attn_laurel = (active + attn + laurel) / math.sqrt(2.0)
+        ffn = self.post_feedforward_layernorm(self.mlp(self.pre_feedforward_layernorm(attn_laurel)))
+        corrected = self.altup.correct(predictions, attn_laurel + ffn)
+        first = corrected[self.active].clone()
+        if self.correct_scale:
+            first = self.altup.scale_corrected_output(first)
+        first = F.gelu(self.per_layer_input_gate(first), approximate="tanh") * per_layer_input
+        first = self.post_per_layer_input_norm(self.per_layer_projection(first))
+        return torch.cat([corrected[:1], corrected[1:] + first], dim=0)
+
+
+class Gemma3nModel(Module):
+    """Decoder-only LM with the ``TransformerLM`` calling convention: ``forward(seqs, layout, targets=None, ...)``."""
+
+    def __init__(self, cfg: Gemma3nConfig, *, device: Device | None = None, dtype: DataType | None = None) -> None:
+        super().__init__()
+        kw = {"device": device, "dtype": dtype}
+        self.cfg = cfg
+        self.model_dim, self.pad_idx, self.max_seq_len = cfg.model_dim, cfg.pad_idx, cfg.max_seq_len
+        d, L, p = cfg.model_dim, cfg.num_layers, cfg.hidden_size_per_layer_input
+        self.embed_tokens = torch.nn.Embedding(cfg.vocab_size, d, padding_idx=cfg.pad_idx, **kw)
+        self.embed_tokens_per_layer = torch.nn.Embedding(cfg.vocab_size_per_layer_input, L * p, padding_idx=cfg.pad_idx, **kw)
+        self.per_layer_model_projection = Linear(d, L * p, bias=False, **kw)
+        self.per_layer_projection_norm = RMSNorm(p, bias=False, eps=cfg.rms_norm_eps, **kw)
+        self.altup_projections = ModuleList([Linear(d, d, bias=False, **kw) for _ in range(1, cfg.altup_num_inputs)])
+        self.altup_unembed_projections = ModuleList([Linear(d, d, bias=False, **kw) for _ in range(1, cfg.altup_num_inputs)])
+        self.layers = ModuleList([Gemma3nDecoderLayer(cfg, i, device, dtype) for i in range(L)])
+        self.norm = RMSNorm(d, bias=False, eps=cfg.rms_norm_eps, **kw)
+        self.lm_head: Linear | None = None if cfg.tied_embeddings else Linear(d, cfg.vocab_size, bias=False, **kw)
+        self.reset_parameters()
+
+    def reset_parameters(self) -> None:
+        for emb in (self.embed_tokens, self.embed_tokens_per_layer):
+            if emb.weight.device.type != "meta":
+                torch.nn.init.normal_(emb.weight, std=self.cfg.init_std)
+                if emb.padding_idx is not None:
+                    with torch.no_grad():
+                        emb.weight[emb.padding_idx].zero_()
+
+    # ------------------------------------------------------------------ pieces
+    def _rope_tables(self, positions: Tensor, theta: float, dtype: torch.dtype) -> tuple[Tensor, Tensor]:
+        D = self.cfg.head_dim
+        inv = 1.0 / (theta ** (torch.arange(0, D, 2, device=positions.device, dtype=torch.float32) / D))
+        ang = positions.float().unsqueeze(-1) * inv
+        emb = torch.cat((ang, ang), dim=-1)
+        return emb.cos().to(dtype), emb.sin().to(dtype)
+
+    def _per_layer_inputs(self, ids: Tensor, embeds: Tensor) -> Tensor:
+        cfg = self.cfg
+        L, p = cfg.num_layers, cfg.hidden_size_per_layer_input
+        proj = (self.per_layer_model_projection(embeds) * cfg.model_dim ** -0.5).view(-1, L, p)
+        proj = self.per_layer_projection_norm(proj)
+        in_vocab = ids < cfg.vocab_size_per_layer_input
+        tok = self.embed_tokens_per_layer(torch.where(in_vocab, ids, torch.zeros_like(ids))) * p ** 0.5
+        tok = tok.view(-1, L, p) * in_vocab.view(-1, 1, 1)
+        return (proj + tok.type_as(proj)) * (2.0 ** -0.5)
+
+    @staticmethod
+    def _match_magnitude(x: Tensor, target: Tensor) -> Tensor:
+        mag = torch.sqrt(torch.clamp(x.pow(2).mean(-1, keepdim=True), min=1e-5))
+        return x * target / mag
+
+    def decode(self, seqs: Tensor, layout: BatchLayout) -> Tensor:
+        """Token ids ``[N, S]`` or packed ``[T]`` -> final hidden states of the same leading shape."""
+        cfg = self.cfg
+        shape = seqs.shape
+        ids = seqs.reshape(-1)
+        T = ids.shape[0]
+        if layout.packed:
+            begins, lens = layout.seq_begin_indices_pt[:-1], layout.seq_lens_pt
+        else:
+            S = shape[1]
+            lens = layout.seq_lens_pt
+            begins = (torch.arange(shape[0], device=ids.device, dtype=torch.int32) * S)
+        positions = layout.position_indices.reshape(-1).clamp(min=0)
+        x0 = self.embed_tokens(ids) * cfg.model_dim ** 0.5
+        per_layer = self._per_layer_inputs(ids, x0)
+        target = x0.pow(2).mean(-1, keepdim=True) ** 0.5
+        streams = torch.stack([x0] + [self._match_magnitude(proj(x0), target) for proj in self.altup_projections])
+        cos_l, sin_l = self._rope_tables(positions, cfg.rope_theta, x0.dtype)
+        cos_g, sin_g = self._rope_tables(positions, cfg.rope_theta_global, x0.dtype)
+        shared_kv: dict[int, tuple[Tensor, Tensor]] = {}
+        for i, layer in enumerate(self.layers):
+            cos, sin = (cos_g, sin_g) if layer.self_attn.is_global else (cos_l, sin_l)
+            streams = layer(streams, per_layer[:, i], cos, sin, layout, begins, lens, shared_kv)
+        target = streams[0].pow(2).mean(-1, keepdim=True) ** 0.5
+        outs = [streams[0]] + [self._match_magnitude(proj(streams[i + 1]), target)
+                               for i, proj in enumerate(self.altup_unembed_projections)]
+        h = self.norm(torch.stack(outs).mean(dim=0))
+        del T
+        return h.view(*shape, cfg.model_dim)
+
+    def project(self, h: Tensor) -> Tensor:
+        w = self.embed_tokens.weight if self.lm_head is None else self.lm_head.weight
+        logits = F.linear(h, w)
+        cap = self.cfg.final_logit_soft_cap
+        if cap:
+            logits = torch.tanh(logits.float() / cap).mul(cap).type_as(logits)
+        return logits
+
+    def forward(self, seqs: Tensor, seqs_layout: BatchLayout, targets: Tensor | None = None, *, state_bag: object = None,
+                label_smoothing: float = 0.0, target_mask: Tensor | None = None,
+                reduction: Literal["sum", "mean"] = "sum", return_logits: bool = False):  # type: ignore[no-untyped-def]
+        if state_bag is not None:
+            raise NotImplementedError("Incremental decoding is not implemented for Gemma 3n.")
+        logits = self.project(self.decode(seqs, seqs_layout))
+        if targets is None:
+            return logits
+        loss = cross_entropy(logits, targets, self.pad_idx, label_smoothing=label_smoothing, target_mask=target_mask,
+                             reduction=reduction)
+        return (loss, logits) if return_logits else loss

@@ -41,6 +41,15 @@ def _register_lm_families() -> None:
         layerwise_ac_applier=apply_layerwise_ac))
 
 
+    from fairseq2_b200.models.gemma3n import (GEMMA3N_FAMILY, Gemma3nConfig, Gemma3nModel, convert_gemma3n_state_dict,
+                                              create_gemma3n_model, export_gemma3n_to_hg, gemma3n_wrap_policy)
+
+    register_model_family(ModelFamily(
+        name=GEMMA3N_FAMILY, kls=Gemma3nModel, config_kls=Gemma3nConfig, factory=create_gemma3n_model,
+        state_dict_converter=convert_gemma3n_state_dict, fsdp_wrap_policy=gemma3n_wrap_policy,
+        hg_exporter=export_gemma3n_to_hg))
+
+
 _register_lm_families()
 
 

@@ -117,3 +117,49 @@ def test_wav2vec2_asr_matches_hf(stable: bool) -> None:
         out, layout = model(x, BatchLayout((2, 3000), [3000, 3000]))
     assert layout.seq_lens == [ref.shape[1]] * 2
     assert torch.allclose(out, ref, atol=2e-4, rtol=1e-3), float((out - ref).abs().max())
+
+
+@pytest.mark.parametrize("shared", [0, 2])
+def test_gemma3n_text_logits_match_hf(shared: int) -> None:
+    """AltUp, LAuReL, per-layer inputs, local/global attention with two RoPE bases, activation sparsity, soft-cap;
+    with ``shared`` > 0 the last layers reuse earlier keys/values (Hugging Face does so when its cache is on)."""
+    from dataclasses import replace
+
+    from transformers.models.gemma3n import Gemma3nForCausalLM, Gemma3nTextConfig
+
+    from fairseq2_b200.models.gemma3n import convert_gemma3n_state_dict, create_gemma3n_model, export_gemma3n_to_hg
+    from fairseq2_b200.models.gemma3n.config import gemma3n_tiny
+
+    torch.manual_seed(0)
+    cfg = replace(gemma3n_tiny(), num_kv_shared_layers=shared, num_layers=8 if shared else 6)
+    _, hg = export_gemma3n_to_hg({}, cfg)
+    for key in ("architectures", "model_type"):
+        hg.pop(key)
+    hf = Gemma3nForCausalLM(Gemma3nTextConfig(**hg, attn_implementation="eager")).eval()
+    with torch.no_grad():
+        for name, p in hf.named_parameters():
+            if "correct_output_scale" in name:
+                p.normal_(std=0.5)                       # zero-initialised upstream: would hide the AltUp scale
+            elif "norm" in name and p.dim() == 1:
+                p.add_(0.1 * torch.randn_like(p))
+    model = create_gemma3n_model(cfg).eval()
+    missing, unexpected = model.load_state_dict(convert_gemma3n_state_dict(hf.state_dict(), cfg), strict=False)
+    assert not missing and not unexpected
+    ids = torch.randint(1, cfg.vocab_size, (2, 20))
+    lens = [20, 13]
+    mask = torch.zeros(2, 20, dtype=torch.long)
+    for i, n in enumerate(lens):
+        mask[i, :n] = 1
+    with torch.no_grad():
+        ref = hf(input_ids=ids, attention_mask=mask, use_cache=shared > 0).logits
+        out = model(ids, BatchLayout((2, 20), lens))
+    for i, n in enumerate(lens):
+        assert torch.allclose(out[i, :n], ref[i, :n], atol=2e-4), float((out[i, :n] - ref[i, :n]).abs().max())
+    # packed batch: the same two sequences back to back
+    packed = torch.cat([ids[0, :20], ids[1, :13]])
+    with torch.no_grad():
+        pk = model(packed, BatchLayout((33,), lens, packed=True))
+    assert torch.allclose(pk[:20], out[0, :20], atol=2e-4) and torch.allclose(pk[20:], out[1, :13], atol=2e-4)
+    # round trip of the exporter
+    sd, _ = export_gemma3n_to_hg(model.state_dict(), cfg)
+    assert set(sd) == {k for k in hf.state_dict() if k != "lm_head.weight"}

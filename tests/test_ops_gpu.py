@@ -235,8 +235,11 @@ def test_attention_sliding_window(window: int) -> None:
     ref = attention_reference(qr, kr, vr, b, l, b, l, True, None, window)
     ref.backward(g.float())
     assert _rel_err(out, ref) < 1e-2
-    assert _rel_err(q.grad, qr.grad) < 2e-2
-    assert _rel_err(k.grad, kr.grad) < 2e-2
+    if window > 1:
+        assert _rel_err(q.grad, qr.grad) < 2e-2
+        assert _rel_err(k.grad, kr.grad) < 2e-2
+    else:       # a softmax over one key is constant: dq and dk vanish
+        assert float(q.grad.float().abs().max()) < 1e-4 and float(k.grad.float().abs().max()) < 1e-4
     assert _rel_err(v.grad, vr.grad) < 2e-2
     from fairseq2_b200.ops._ext import require_ext
 
