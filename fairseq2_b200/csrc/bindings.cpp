@@ -1089,6 +1089,23 @@ void comm_allreduce_inplace(const std::vector<int64_t>& ptrs, int64_t rank, int6
     g_launches += 1;
 }
 
+void comm_allreduce_multimem(const std::vector<int64_t>& ptrs, int64_t rank, int64_t multicast_ptr, int64_t byte_off,
+                             int64_t numel, bool f32, double scale, int64_t slot_in, int64_t slot_out, int64_t epoch,
+                             int64_t counter_byte_off, int64_t device, int64_t blocks, double wait_limit_s) {
+    const int64_t per = f32 ? 4 : 8;
+    TORCH_CHECK(multicast_ptr != 0, "comm_allreduce_multimem: the arena has no multicast mapping");
+    TORCH_CHECK(byte_off % 16 == 0 && numel > 0 && numel % per == 0 && counter_byte_off % 4 == 0 && blocks > 0,
+                "comm_allreduce_multimem: the buffer must be 16-byte aligned and a multiple of 16 bytes");
+    c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+    auto* counter = reinterpret_cast<unsigned int*>(ptrs[static_cast<size_t>(rank)] + counter_byte_off);
+    fs2::comm_allreduce_multimem(make_peers(ptrs, rank, wait_limit_s), reinterpret_cast<void*>(multicast_ptr), byte_off,
+                                 numel, f32, static_cast<float>(scale), static_cast<int>(slot_in),
+                                 static_cast<int>(slot_out), static_cast<uint32_t>(epoch), counter,
+                                 static_cast<int>(blocks), status_dev_ptr(),
+                                 at::cuda::getCurrentCUDAStream(static_cast<c10::DeviceIndex>(device)).stream());
+    g_launches += 1;
+}
+
 void comm_pull(const std::vector<int64_t>& ptrs, int64_t rank, int64_t src_rank, int64_t byte_off, Tensor dst,
                int64_t slot, int64_t epoch, double wait_limit_s) {
     TORCH_CHECK(dst.is_cuda() && dst.is_contiguous() && aligned16(dst) && (dst.numel() * dst.element_size()) % 16 == 0,
@@ -1153,6 +1170,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("comm_reducescatter_adamw", &comm_reducescatter_adamw);
     m.def("comm_allreduce_f32", &comm_allreduce_f32);
     m.def("comm_allreduce_inplace", &comm_allreduce_inplace);
+    m.def("comm_allreduce_multimem", &comm_allreduce_multimem);
     m.def("comm_pull", &comm_pull);
     m.def("comm_alltoall", &comm_alltoall);
     m.def("moe_route", &moe_route);

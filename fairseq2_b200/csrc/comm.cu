@@ -392,6 +392,65 @@ __global__ void __launch_bounds__(512) allreduce_inplace_kernel(CommPeers peers,
     }
 }
 
+// In-place all-reduce through the NVSwitch multicast mapping of the arena (NVLS): every rank owns 1/W of the buffer,
+// reads it with multimem.ld_reduce -- the switch fetches the W copies and returns their sum, accumulated in fp32 --
+// scales it and writes it back with multimem.st, which the switch delivers to all W copies. Each GPU therefore moves
+// 1/W of the buffer in and 1/W out instead of (W-1)/W each way, and issues 1/W of the loads.
+template <typename T>
+__global__ void __launch_bounds__(512) allreduce_multimem_kernel(CommPeers peers, char* mc_base, long long byte_off,
+                                                                 long long numel, float scale, int slot_in, int slot_out,
+                                                                 uint32_t epoch, unsigned int* counter, int* status) {
+    if (!signal_and_wait(peers, slot_in, epoch, true, status, 26)) return;
+    constexpr int PER = 16 / sizeof(T);
+    const int W = peers.world;
+    const long long nvec = numel / PER;
+    const long long per_rank = (nvec + W - 1) / W;
+    const long long beg = peers.rank * per_rank;
+    const long long end = beg + per_rank < nvec ? beg + per_rank : nvec;
+    char* mc = mc_base + byte_off;
+    for (long long v = beg + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v < end;
+         v += static_cast<long long>(gridDim.x) * blockDim.x) {
+        char* addr = mc + v * 16;
+        if constexpr (sizeof(T) == 4) {
+            float a, b, c, d;
+            asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                         : "=f"(a), "=f"(b), "=f"(c), "=f"(d) : "l"(addr) : "memory");
+            a *= scale; b *= scale; c *= scale; d *= scale;
+            asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                         ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+        } else {
+            uint4 r;
+            asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(addr) : "memory");
+            bf16x8 p;
+            *reinterpret_cast<uint4*>(&p) = r;
+            float f[8];
+            unpack8(p, f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] *= scale;
+            p = pack8(f);
+            r = *reinterpret_cast<uint4*>(&p);
+            asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};"
+                         ::"l"(addr), "r"(r.x), "r"(r.y), "r"(r.z), "r"(r.w) : "memory");
+        }
+    }
+    // the last CTA to finish tells every peer that this rank's slice has been written everywhere
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        const unsigned int prev = atomicAdd(counter, 1u);
+        if (prev == gridDim.x - 1) {
+            *counter = 0;
+            __threadfence_system();
+            for (int r = 0; r < W; ++r) {
+                uint32_t* f = reinterpret_cast<uint32_t*>(peers.base[r]) + slot_out * kCommMaxRanks + peers.rank;
+                st_release_sys(f, epoch);
+            }
+        }
+    }
+    signal_and_wait(peers, slot_out, epoch, false, status, 27);
+}
+
 // Pull copy: dst[i] = peer_src.arena[byte_off + i] for `bytes` bytes (multiple of 16).
 __global__ void pull_kernel(CommPeers peers, int src_rank, long long byte_off, char* __restrict__ dst,
                             long long bytes, int slot, uint32_t epoch, int* status) {
@@ -530,6 +589,18 @@ void comm_reduce_staged(const void* own_full, const void* const* staged, int cou
         reduce_staged_kernel<__nv_bfloat16><<<blocks, 512, 0, st>>>(static_cast<const __nv_bfloat16*>(own_full), sl,
                                                                     segs, rank, world, static_cast<__nv_bfloat16*>(out),
                                                                     scale, accumulate ? 1 : 0);
+}
+
+void comm_allreduce_multimem(const CommPeers& peers, void* multicast_base, long long byte_off, long long numel, bool f32,
+                             float scale, int slot_in, int slot_out, uint32_t epoch, unsigned int* counter, int blocks,
+                             int* status, cudaStream_t st) {
+    char* mc = static_cast<char*>(multicast_base);
+    if (f32)
+        allreduce_multimem_kernel<float><<<blocks, 512, 0, st>>>(peers, mc, byte_off, numel, scale, slot_in, slot_out,
+                                                                 epoch, counter, status);
+    else
+        allreduce_multimem_kernel<__nv_bfloat16><<<blocks, 512, 0, st>>>(peers, mc, byte_off, numel, scale, slot_in,
+                                                                         slot_out, epoch, counter, status);
 }
 
 void comm_allreduce_inplace(const CommPeers& peers, long long byte_off, long long numel, bool f32, float scale,

@@ -26,6 +26,12 @@ struct CommSegments {
 
 void comm_barrier(const CommPeers& peers, int slot, uint32_t epoch, int* status, cudaStream_t st);
 void comm_signal(const CommPeers& peers, int slot, uint32_t epoch, cudaStream_t st);
+// In-place sum (times `scale`) of the `numel` elements (bf16 or fp32, a multiple of 16 bytes) at `byte_off` of every
+// arena, through the NVSwitch multicast mapping `multicast_base` of the arena (multimem.ld_reduce / multimem.st).
+// `counter` is a zero-initialised word in local memory; `slot_in` / `slot_out` are two epoch-flag slots.
+void comm_allreduce_multimem(const CommPeers& peers, void* multicast_base, long long byte_off, long long numel, bool f32,
+                             float scale, int slot_in, int slot_out, uint32_t epoch, unsigned int* counter, int blocks,
+                             int* status, cudaStream_t st);
 // out[i] = sum over w < world of slices[w * n + i] (bf16 in, fp32 sum, bf16 or fp32 out); n a multiple of 8.
 void comm_reduce_slices(const void* slices, int world, long long n, void* out, bool out_f32, cudaStream_t st);
 // out[off_s + i] = scale * (own_full[W * off_s + rank * numel_s + i] + sum_k staged[k][off_s + i]); local memory only.

@@ -154,7 +154,53 @@ def bench_ce(a: argparse.Namespace) -> None:
     _emit("fused_linear_ce_fwd_bwd", ms, flops=6.0 * T * Dm * V, tokens=T, dim=Dm, vocab=V)
 
 
-_CASES = {"gemm": bench_gemm, "attention": bench_attention, "norm": bench_norm, "swiglu": bench_swiglu,
+def bench_conv(a: argparse.Namespace) -> None:
+    """One strided feature-encoder convolution (wav2vec 2.0 layers 2-5: 512 -> 512 channels, k=3, s=2) as a GEMM over
+    overlapping-row views vs cuDNN ``conv1d`` on the channels-first layout, forward and backward; then the fused
+    LayerNorm+GELU kernel vs the two PyTorch ops."""
+    import torch.nn.functional as F
+
+    from fairseq2_b200.ops.conv import conv1d_channels_last
+    from fairseq2_b200.ops.norm import layer_norm_gelu
+
+    B, L, C, k, s = 32, 8192, 512, 3, 2
+    x = torch.randn(B, L, C, device=_DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(C, C, k, device=_DEV) * (C * k) ** -0.5).to(torch.bfloat16).requires_grad_(True)
+    fl = 2.0 * B * (L // s) * C * C * k
+    y = conv1d_channels_last(x, w, None, s)
+    g = torch.randn_like(y)
+    ms = _time(lambda: conv1d_channels_last(x, w, None, s), a.iters, a.warmup)
+    _emit("conv1d_view_gemm_fwd", ms, flops=fl, batch=B, length=L, channels=C, kernel=k, stride=s)
+
+    def ours_fb() -> None:
+        x.grad = w.grad = None
+        conv1d_channels_last(x, w, None, s).backward(g)
+
+    ms = _time(ours_fb, a.iters, a.warmup)
+    _emit("conv1d_view_gemm_fwd_bwd", ms, flops=3 * fl)
+    xc = x.detach().transpose(1, 2).contiguous().requires_grad_(True)
+    wc = w.detach().clone().requires_grad_(True)
+    yc = F.conv1d(xc, wc, stride=s)
+    gc = torch.randn_like(yc)
+    ms = _time(lambda: F.conv1d(xc, wc, stride=s), a.iters, a.warmup)
+    _emit("conv1d_cudnn_fwd", ms, flops=fl)
+
+    def cudnn_fb() -> None:
+        xc.grad = wc.grad = None
+        F.conv1d(xc, wc, stride=s).backward(gc)
+
+    ms = _time(cudnn_fb, a.iters, a.warmup)
+    _emit("conv1d_cudnn_fwd_bwd", ms, flops=3 * fl)
+    rows = B * (L // s)
+    h = torch.randn(rows, C, device=_DEV, dtype=torch.bfloat16)
+    lw, lb = torch.ones(C, device=_DEV, dtype=torch.bfloat16), torch.zeros(C, device=_DEV, dtype=torch.bfloat16)
+    ms = _time(lambda: layer_norm_gelu(h, lw, lb, 1e-5), a.iters, a.warmup)
+    _emit("layer_norm_gelu_fused_fwd", ms, nbytes=2.0 * rows * C * 2)
+    ms = _time(lambda: F.gelu(F.layer_norm(h, (C,), lw, lb, 1e-5)), a.iters, a.warmup)
+    _emit("layer_norm_then_gelu_torch_fwd", ms, nbytes=2.0 * rows * C * 2)
+
+
+_CASES = {"conv": bench_conv, "gemm": bench_gemm, "attention": bench_attention, "norm": bench_norm, "swiglu": bench_swiglu,
           "adamw": bench_adamw, "ce": bench_ce}
 
 

@@ -179,6 +179,17 @@ def main() -> None:
         ref = torch.empty(numel, device=dev, dtype=torch.bfloat16).normal_(std=0.01)
         nccl = _time(lambda: dist.all_reduce(ref, op=dist.ReduceOp.AVG, group=pg), barrier, args.iters)
         emit("ddp_bucket_allreduce_inplace_128MB", ms, nvlink_bytes=2 * (W - 1) / W * numel * 2, baseline_ms=nccl)
+        if arena.multicast_ptr:
+            me = {"v": 0}
+
+            def ar_mm() -> None:
+                me["v"] += 1
+                ext.comm_allreduce_multimem(arena.peer_ptrs, rank, arena.multicast_ptr, off, numel, False, 1.0 / W, 7, 8,
+                                            me["v"], coff, arena.device_index, 64, arena.wait_limit_s)
+            ms = _time(ar_mm, barrier, args.iters)
+            # through the switch every GPU sends and receives the whole buffer once (1/W reduced in, 1/W broadcast
+            # out, and serves the other ranks' reads of its copy)
+            emit("ddp_bucket_allreduce_multimem_128MB", ms, nvlink_bytes=numel * 2, baseline_ms=nccl)
 
     K_ffn, D = 14336, 4096
     if want("gemm_rs") and K_ffn % W == 0 and T % (W * 128) == 0:

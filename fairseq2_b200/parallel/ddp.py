@@ -58,8 +58,15 @@ class DDP(Module):
     SLOT_BASE = 64
 
     def __init__(self, module: Module, gangs: Gangs, *, bucket_bytes: int = 64 * 1024 * 1024,
-                 broadcast_parameters: bool = True, average: bool = True, comm: str = "auto") -> None:
+                 broadcast_parameters: bool = True, average: bool = True, comm: str = "auto",
+                 allreduce: str = "auto") -> None:
+        """``allreduce`` picks the kernel of the symmetric-memory path: "multimem" reduces inside the NVSwitch
+        (``multimem.ld_reduce`` / ``multimem.st`` on the multicast mapping of the arena), "p2p" is the two-shot
+        kernel on plain peer loads and stores and what "auto" selects."""
         super().__init__()
+        if allreduce not in ("auto", "multimem", "p2p"):
+            raise ValueError(f"`allreduce` must be 'auto', 'multimem' or 'p2p', but is '{allreduce}' instead.")
+        self._allreduce = allreduce
         self.module = module
         self.gang: Gang = gangs.rdp if gangs.rdp.size > 1 else gangs.dp
         self.average = average
@@ -155,11 +162,16 @@ class DDP(Module):
         epoch = self._step_epoch
         scale = 1.0 / self.gang.size if self.average else 1.0
         blocks = max(1, min(64, b.padded * b.flat.element_size() // (512 * 16 * 4)))
+        use_mm = self._allreduce == "multimem"          # "auto" stays on plain peer loads/stores
+        if use_mm and a.multicast_ptr == 0:
+            raise RuntimeError("The symmetric arena has no NVSwitch multicast mapping; use allreduce='p2p'.")
         self.comm_stream.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(self.comm_stream):
-            a.ext.comm_allreduce_inplace(a.peer_ptrs, a.rank, b.byte_off, b.padded, b.flat.dtype == torch.float32,
-                                         scale, self.SLOT_BASE + 2 * b.index, self.SLOT_BASE + 2 * b.index + 1, epoch,
-                                         self._counter_off + 4 * b.index, a.device_index, blocks, a.wait_limit_s)
+            fn = a.ext.comm_allreduce_multimem if use_mm else a.ext.comm_allreduce_inplace
+            args = (a.multicast_ptr,) if use_mm else ()
+            fn(a.peer_ptrs, a.rank, *args, b.byte_off, b.padded, b.flat.dtype == torch.float32, scale,
+               self.SLOT_BASE + 2 * b.index, self.SLOT_BASE + 2 * b.index + 1, epoch, self._counter_off + 4 * b.index,
+               a.device_index, blocks, a.wait_limit_s)
 
     @property
     def _step_epoch(self) -> int:

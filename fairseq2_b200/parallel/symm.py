@@ -70,6 +70,9 @@ class SymmetricArena:
         self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
         self.handle = symm_mem.rendezvous(self.buf, pg.group_name)
         self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        # NVSwitch multicast mapping of the same buffer (0 where the fabric does not offer one): one address whose
+        # loads can be reduced and whose stores are replicated inside the switch (``multimem.*`` instructions)
+        self.multicast_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
         self.nbytes = nbytes
         self._top = FLAG_BYTES
         self.buf.zero_()

@@ -161,7 +161,7 @@ def test_fused_gemm_reduce_scatter() -> None:
         assert all(e < 1e-2 for e in errs), errs
 
 
-def _ddp_symm_worker(rank: int, world: int):
+def _ddp_symm_worker(rank: int, world: int, allreduce: str = "p2p"):
     from fairseq2_b200.gang import ProcessGroupGang, create_parallel_gangs
     from fairseq2_b200.parallel.ddp import DDP
 
@@ -172,8 +172,11 @@ def _ddp_symm_worker(rank: int, world: int):
     gangs = create_parallel_gangs(base)
     torch.manual_seed(0)
     model = torch.nn.Sequential(torch.nn.Linear(64, 257), torch.nn.ReLU(), torch.nn.Linear(257, 33)).to(dev)
-    ddp = DDP(model, gangs, bucket_bytes=32 * 1024, comm="symm", average=True)
+    ddp = DDP(model, gangs, bucket_bytes=32 * 1024, comm="symm", average=True, allreduce=allreduce)
     assert ddp.arena is not None and len(ddp.buckets) >= 2
+    if allreduce == "multimem" and ddp.arena.multicast_ptr == 0:
+        base.close()
+        return []                              # no NVSwitch multicast on this box
     out = []
     for step in range(3):
         gen = torch.Generator().manual_seed(1000 * step + rank)
@@ -197,9 +200,10 @@ def _ddp_symm_worker(rank: int, world: int):
     return out
 
 
-def test_ddp_symmetric_allreduce() -> None:
+@pytest.mark.parametrize("allreduce", ["p2p", "multimem"])
+def test_ddp_symmetric_allreduce(allreduce: str) -> None:
     _need_gpus(2)
-    for errs in run_distributed(_ddp_symm_worker, 2):
+    for errs in run_distributed(_ddp_symm_worker, 2, allreduce):
         assert all(e < 1e-5 for e in errs), errs
 
 
