@@ -147,15 +147,311 @@ Data WaveformToFbankConverter::operator()(Data&& d) const {
     return Data(std::move(out));
 }
 
+// ------------------------------------------------------------------ baseline JPEG
+// Sequential (baseline / extended) DCT JPEG with Huffman coding: 8-bit samples, 1 or 3 components, any sampling
+// factors up to 2x2 (4:4:4, 4:2:2, 4:2:0), restart intervals. Progressive and arithmetic-coded files are rejected.
+namespace {
+
+struct JpegHuff {
+    uint8_t bits[17] = {0};
+    uint8_t vals[256] = {0};
+    int mincode[17] = {0}, maxcode[18] = {0}, valptr[17] = {0};
+    bool present = false;
+    void build() {
+        int code = 0, k = 0;
+        for (int l = 1; l <= 16; ++l) {
+            valptr[l] = k;
+            mincode[l] = code;
+            code += bits[l];
+            k += bits[l];
+            maxcode[l] = bits[l] ? code - 1 : -1;
+            code <<= 1;
+        }
+        maxcode[17] = 0x7fffffff;
+        present = true;
+    }
+};
+
+struct JpegBits {
+    const uint8_t* p;
+    const uint8_t* end;
+    uint32_t acc = 0;
+    int cnt = 0;
+    int get_bit() {
+        if (cnt == 0) {
+            uint8_t b = p < end ? *p++ : 0;
+            if (b == 0xFF) {
+                const uint8_t b2 = p < end ? *p : 0;
+                if (b2 == 0) ++p;                 // stuffed zero
+                else { --p; b = 0; }              // a marker: feed zeros, the caller resynchronises
+            }
+            acc = b;
+            cnt = 8;
+        }
+        --cnt;
+        return (acc >> cnt) & 1;
+    }
+    int get_bits(int n) {
+        int v = 0;
+        for (int i = 0; i < n; ++i) v = (v << 1) | get_bit();
+        return v;
+    }
+    void reset() { cnt = 0; }
+};
+
+int jpeg_decode_symbol(JpegBits& br, const JpegHuff& h) {
+    int code = 0;
+    for (int l = 1; l <= 16; ++l) {
+        code = (code << 1) | br.get_bit();
+        if (h.maxcode[l] >= 0 && code <= h.maxcode[l] && code >= h.mincode[l])
+            return h.vals[h.valptr[l] + code - h.mincode[l]];
+    }
+    throw std::invalid_argument("The JPEG entropy-coded data is corrupt.");
+}
+
+int jpeg_extend(int v, int t) { return t == 0 ? 0 : (v < (1 << (t - 1)) ? v - (1 << t) + 1 : v); }
+
+const int kZigzag[64] = {0,  1,  8,  16, 9,  2,  3,  10, 17, 24, 32, 25, 18, 11, 4,  5,  12, 19, 26, 33, 40, 48,
+                         41, 34, 27, 20, 13, 6,  7,  14, 21, 28, 35, 42, 49, 56, 57, 50, 43, 36, 29, 22, 15, 23,
+                         30, 37, 44, 51, 58, 59, 52, 45, 38, 31, 39, 46, 53, 60, 61, 54, 47, 55, 62, 63};
+
+void jpeg_idct8x8(const float* in, uint8_t* out, int out_stride) {
+    static float c[8][8];
+    static bool init = false;
+    if (!init) {
+        for (int x = 0; x < 8; ++x)
+            for (int u = 0; u < 8; ++u)
+                c[x][u] = (u == 0 ? 0.35355339059f : 0.5f) * std::cos((2 * x + 1) * u * 3.14159265358979323846 / 16.0);
+        init = true;
+    }
+    float tmp[64];
+    for (int y = 0; y < 8; ++y)          // rows
+        for (int x = 0; x < 8; ++x) {
+            float s = 0.f;
+            for (int u = 0; u < 8; ++u) s += c[x][u] * in[y * 8 + u];
+            tmp[y * 8 + x] = s;
+        }
+    for (int x = 0; x < 8; ++x)          // columns
+        for (int y = 0; y < 8; ++y) {
+            float s = 0.f;
+            for (int v = 0; v < 8; ++v) s += c[y][v] * tmp[v * 8 + x];
+            const int val = static_cast<int>(std::lround(s + 128.f));
+            out[y * out_stride + x] = static_cast<uint8_t>(val < 0 ? 0 : (val > 255 ? 255 : val));
+        }
+}
+
+struct JpegComp {
+    int id = 0, h = 1, v = 1, tq = 0, td = 0, ta = 0, pred = 0;
+    int bw = 0, bh = 0;                  // plane size in pixels (multiple of 8 * sampling)
+    std::vector<uint8_t> plane;
+};
+
+at::Tensor decode_jpeg(const uint8_t* b, size_t n) {
+    auto be16 = [&](size_t p) { return (static_cast<int>(b[p]) << 8) | b[p + 1]; };
+    float qt[4][64] = {};
+    bool qt_present[4] = {false, false, false, false};
+    JpegHuff dc[4], ac[4];
+    std::vector<JpegComp> comps;
+    int width = 0, height = 0, restart = 0, hmax = 1, vmax = 1;
+    size_t p = 2;
+    bool got_frame = false;
+    while (p + 4 <= n) {
+        if (b[p] != 0xFF) throw std::invalid_argument("The JPEG marker stream is corrupt.");
+        while (p < n && b[p] == 0xFF) ++p;
+        const uint8_t m = b[p++];
+        if (m == 0xD8 || (m >= 0xD0 && m <= 0xD7) || m == 0x01) continue;
+        if (m == 0xD9) break;
+        if (p + 2 > n) break;
+        const size_t len = static_cast<size_t>(be16(p));
+        if (len < 2 || p + len > n) throw std::invalid_argument("The JPEG file is truncated.");
+        const size_t seg = p + 2, seg_end = p + len;
+        if (m == 0xDB) {                                            // DQT
+            size_t q = seg;
+            while (q < seg_end) {
+                const int pq = b[q] >> 4, tq = b[q] & 15;
+                ++q;
+                if (tq > 3) throw std::invalid_argument("The JPEG quantization table index is invalid.");
+                for (int i = 0; i < 64; ++i) {
+                    qt[tq][kZigzag[i]] = pq ? static_cast<float>(be16(q)) : static_cast<float>(b[q]);
+                    q += pq ? 2 : 1;
+                }
+                qt_present[tq] = true;
+            }
+        } else if (m == 0xC4) {                                     // DHT
+            size_t q = seg;
+            while (q < seg_end) {
+                const int tc = b[q] >> 4, th = b[q] & 15;
+                ++q;
+                if (th > 3 || tc > 1) throw std::invalid_argument("The JPEG Huffman table index is invalid.");
+                JpegHuff& h = tc ? ac[th] : dc[th];
+                int total = 0;
+                for (int l = 1; l <= 16; ++l) {
+                    h.bits[l] = b[q++];
+                    total += h.bits[l];
+                }
+                if (total > 256 || q + total > seg_end) throw std::invalid_argument("The JPEG Huffman table is corrupt.");
+                for (int i = 0; i < total; ++i) h.vals[i] = b[q++];
+                h.build();
+            }
+        } else if (m == 0xC0 || m == 0xC1) {                        // SOF0 / SOF1
+            if (b[seg] != 8) throw std::invalid_argument("Only 8-bit JPEG files are supported.");
+            height = be16(seg + 1);
+            width = be16(seg + 3);
+            const int nc = b[seg + 5];
+            if ((nc != 1 && nc != 3) || width <= 0 || height <= 0)
+                throw std::invalid_argument("Only grayscale and three-component JPEG files are supported.");
+            comps.resize(nc);
+            for (int i = 0; i < nc; ++i) {
+                comps[i].id = b[seg + 6 + 3 * i];
+                comps[i].h = b[seg + 7 + 3 * i] >> 4;
+                comps[i].v = b[seg + 7 + 3 * i] & 15;
+                comps[i].tq = b[seg + 8 + 3 * i];
+                if (comps[i].h < 1 || comps[i].h > 2 || comps[i].v < 1 || comps[i].v > 2 || comps[i].tq > 3)
+                    throw std::invalid_argument("The JPEG sampling factors are not supported.");
+                hmax = std::max(hmax, comps[i].h);
+                vmax = std::max(vmax, comps[i].v);
+            }
+            got_frame = true;
+        } else if (m == 0xC2 || (m >= 0xC5 && m <= 0xCF && m != 0xC8 && m != 0xCC)) {
+            throw std::invalid_argument("Progressive, lossless and arithmetic-coded JPEG files are not supported.");
+        } else if (m == 0xDD) {                                     // DRI
+            restart = be16(seg);
+        } else if (m == 0xDA) {                                     // SOS: the entropy-coded scan follows
+            if (!got_frame) throw std::invalid_argument("The JPEG file has no frame header before its scan.");
+            const int ns = b[seg];
+            if (ns != static_cast<int>(comps.size()))
+                throw std::invalid_argument("Only single-scan (interleaved) JPEG files are supported.");
+            for (int i = 0; i < ns; ++i) {
+                const int cid = b[seg + 1 + 2 * i];
+                for (auto& c : comps)
+                    if (c.id == cid) {
+                        c.td = b[seg + 2 + 2 * i] >> 4;
+                        c.ta = b[seg + 2 + 2 * i] & 15;
+                    }
+            }
+            const int mcu_w = 8 * hmax, mcu_h = 8 * vmax;
+            const int mcus_x = (width + mcu_w - 1) / mcu_w, mcus_y = (height + mcu_h - 1) / mcu_h;
+            for (auto& c : comps) {
+                if (!qt_present[c.tq] || !dc[c.td].present || !ac[c.ta].present)
+                    throw std::invalid_argument("The JPEG scan refers to a table that was not defined.");
+                c.bw = mcus_x * c.h * 8;
+                c.bh = mcus_y * c.v * 8;
+                c.plane.assign(static_cast<size_t>(c.bw) * c.bh, 0);
+                c.pred = 0;
+            }
+            JpegBits br{b + seg_end, b + n};
+            int until_restart = restart;
+            for (int my = 0; my < mcus_y; ++my)
+                for (int mx = 0; mx < mcus_x; ++mx) {
+                    if (restart && until_restart == 0) {
+                        br.reset();
+                        while (br.p + 1 < br.end && !(br.p[0] == 0xFF && br.p[1] >= 0xD0 && br.p[1] <= 0xD7)) ++br.p;
+                        br.p += 2;
+                        for (auto& c : comps) c.pred = 0;
+                        until_restart = restart;
+                    }
+                    for (auto& c : comps)
+                        for (int by = 0; by < c.v; ++by)
+                            for (int bx = 0; bx < c.h; ++bx) {
+                                float blk[64] = {0};
+                                const int t = jpeg_decode_symbol(br, dc[c.td]);
+                                if (t > 11) throw std::invalid_argument("The JPEG entropy-coded data is corrupt.");
+                                c.pred += jpeg_extend(br.get_bits(t), t);
+                                blk[0] = c.pred * qt[c.tq][0];
+                                for (int k = 1; k < 64;) {
+                                    const int rs = jpeg_decode_symbol(br, ac[c.ta]);
+                                    const int r = rs >> 4, sz = rs & 15;
+                                    if (sz == 0) {
+                                        if (r == 15) { k += 16; continue; }
+                                        break;
+                                    }
+                                    k += r;
+                                    if (k > 63) throw std::invalid_argument("The JPEG entropy-coded data is corrupt.");
+                                    const int z = kZigzag[k];
+                                    blk[z] = jpeg_extend(br.get_bits(sz), sz) * qt[c.tq][z];
+                                    ++k;
+                                }
+                                const int px = (mx * c.h + bx) * 8, py = (my * c.v + by) * 8;
+                                jpeg_idct8x8(blk, c.plane.data() + static_cast<size_t>(py) * c.bw + px, c.bw);
+                            }
+                    if (restart) --until_restart;
+                }
+            // chroma upsampling with the triangle filter ("3/4 near + 1/4 far", separable) on the valid part of each
+            // plane, then colour conversion
+            const int nc = static_cast<int>(comps.size());
+            at::Tensor out = at::empty({height, width, nc}, at::kByte);
+            uint8_t* o = out.data_ptr<uint8_t>();
+            std::vector<std::vector<uint8_t>> full(nc);
+            for (int ci = 0; ci < nc; ++ci) {
+                const JpegComp& c = comps[ci];
+                const int fx = hmax / c.h, fy = vmax / c.v;
+                const int cw = (width * c.h + hmax - 1) / hmax, ch = (height * c.v + vmax - 1) / vmax;
+                std::vector<uint8_t>& f = full[ci];
+                f.resize(static_cast<size_t>(width) * height);
+                auto at_ = [&](int x, int y) {
+                    x = x < 0 ? 0 : (x >= cw ? cw - 1 : x);
+                    y = y < 0 ? 0 : (y >= ch ? ch - 1 : y);
+                    return static_cast<int>(c.plane[static_cast<size_t>(y) * c.bw + x]);
+                };
+                for (int y = 0; y < height; ++y)
+                    for (int x = 0; x < width; ++x) {
+                        int val;
+                        if (fx == 1 && fy == 1) {
+                            val = at_(x, y);
+                        } else if (fx == 2 && fy == 1) {
+                            const int i = x >> 1;
+                            val = (x & 1) ? (3 * at_(i, y) + at_(i + 1, y) + 2) >> 2 : (3 * at_(i, y) + at_(i - 1, y) + 1) >> 2;
+                        } else if (fx == 1 && fy == 2) {
+                            const int j = y >> 1;
+                            val = (y & 1) ? (3 * at_(x, j) + at_(x, j + 1) + 2) >> 2 : (3 * at_(x, j) + at_(x, j - 1) + 1) >> 2;
+                        } else {
+                            const int i = x >> 1, j = y >> 1, jf = (y & 1) ? j + 1 : j - 1;
+                            auto colsum = [&](int xi) { return 3 * at_(xi, j) + at_(xi, jf); };
+                            val = (x & 1) ? (3 * colsum(i) + colsum(i + 1) + 7) >> 4 : (3 * colsum(i) + colsum(i - 1) + 8) >> 4;
+                        }
+                        f[static_cast<size_t>(y) * width + x] = static_cast<uint8_t>(val);
+                    }
+            }
+            auto sample = [&](int ci, int x, int y) { return static_cast<int>(full[ci][static_cast<size_t>(y) * width + x]); };
+            auto clamp8 = [](float v) { const int i = static_cast<int>(std::lround(v)); return static_cast<uint8_t>(i < 0 ? 0 : (i > 255 ? 255 : i)); };
+            for (int y = 0; y < height; ++y)
+                for (int x = 0; x < width; ++x) {
+                    uint8_t* px = o + (static_cast<size_t>(y) * width + x) * nc;
+                    if (nc == 1) {
+                        px[0] = static_cast<uint8_t>(sample(0, x, y));
+                    } else {
+                        const float Y = static_cast<float>(sample(0, x, y));
+                        const float cb = static_cast<float>(sample(1, x, y)) - 128.f;
+                        const float cr = static_cast<float>(sample(2, x, y)) - 128.f;
+                        px[0] = clamp8(Y + 1.402f * cr);
+                        px[1] = clamp8(Y - 0.344136f * cb - 0.714136f * cr);
+                        px[2] = clamp8(Y + 1.772f * cb);
+                    }
+                }
+            return out;
+        }
+        p = seg_end;
+    }
+    throw std::invalid_argument("The JPEG file has no image scan.");
+}
+
+}  // namespace
+
 // ================================================================== ImageDecoder
 Data ImageDecoder::operator()(Data&& d) const {
     if (!d.is_memory_block()) throw std::invalid_argument("The input data must be of type `MemoryBlock`.");
     const MemoryBlock& mb = d.as_memory_block();
     const uint8_t* b = mb.data();
     const size_t n = mb.size();
+    if (n >= 4 && b[0] == 0xFF && b[1] == 0xD8) {
+        at::Tensor img = decode_jpeg(b, n);
+        const double channels = static_cast<double>(img.size(2));
+        DataDict res{{"bit_depth", Data(8.0)}, {"format", Data(channels)}, {"image", Data(img)}};
+        return Data(std::move(res));
+    }
     static const uint8_t sig[8] = {0x89, 'P', 'N', 'G', 0x0D, 0x0A, 0x1A, 0x0A};
     if (n < 8 || std::memcmp(b, sig, 8) != 0)
-        throw std::invalid_argument("The input image is not a PNG file (JPEG decoding is not available in this build).");
+        throw std::invalid_argument("The input image is neither a PNG nor a JPEG file.");
     size_t p = 8;
     uint32_t width = 0, height = 0;
     int depth = 0, color = 0, interlace = 0;

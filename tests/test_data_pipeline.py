@@ -277,3 +277,34 @@ def test_create_bucket_sizes() -> None:
     sizes = create_bucket_sizes(max_num_elements=16, max_seq_len=8, min_seq_len=2)
     assert sizes[-1] == (2, 8) and all(b * s <= 16 for b, s in sizes)
     assert [s for _, s in sizes] == sorted(s for _, s in sizes)
+
+
+def test_image_decoder_jpeg_matches_libjpeg() -> None:
+    """Baseline JPEG (grayscale, 4:4:4, 4:2:2, 4:2:0, restart markers) decoded by the native runtime vs Pillow."""
+    import io
+
+    import numpy as np
+
+    PIL = pytest.importorskip("PIL.Image")
+    from fairseq2_b200.data.data_pipeline import MemoryBlock
+    from fairseq2_b200.data.image import ImageDecoder
+
+    y, x = np.mgrid[0:67, 0:93]
+    rgb = np.stack([(x * 2 + y) % 256, (x + y * 3) % 256, (x * y // 7) % 256], -1).astype(np.uint8)
+    rgb = (0.5 * rgb + 0.5 * np.roll(rgb, 3, 0)).astype(np.uint8)
+    dec = ImageDecoder()
+    cases = [("RGB", {"subsampling": 0}), ("RGB", {"subsampling": 1}), ("RGB", {"subsampling": 2}), ("L", {}),
+             ("RGB", {"subsampling": 2, "restart_marker_rows": 1})]
+    for mode, kw in cases:
+        im = PIL.fromarray(rgb if mode == "RGB" else rgb[..., 0])
+        buf = io.BytesIO()
+        im.save(buf, format="JPEG", quality=90, **kw)
+        data = buf.getvalue()
+        out = dec(MemoryBlock(data))
+        ref = np.asarray(PIL.open(io.BytesIO(data)).convert(mode))
+        ref = ref if ref.ndim == 3 else ref[..., None]
+        got = out["image"].numpy()
+        assert got.shape == ref.shape and out["bit_depth"] == 8.0
+        assert np.abs(got.astype(int) - ref.astype(int)).max() <= 4, (mode, kw)
+    with pytest.raises(Exception):
+        dec(MemoryBlock(b"\xff\xd8\xff\xc2\x00\x0b\x08\x00\x10\x00\x10\x01\x01\x11\x00"))      # progressive
