@@ -164,11 +164,12 @@ void gemm_bf16_view(const Tensor& a, int64_t a_rows, int64_t lda, bool a_mn, con
 // bf16 scatter form of the fused row-parallel GEMM: tile rows owned by rank r land in slice `rank` of the
 // [world, rows_per_rank, N] bf16 buffer at `slices_byte_off` of rank r's arena.
 void gemm_scatter(const Tensor& a, const Tensor& b, const std::vector<int64_t>& ptrs, int64_t rank,
-                  int64_t slices_byte_off, int64_t rows_per_rank) {
+                  int64_t slices_byte_off, int64_t rows_per_rank, bool b_mn) {
     TORCH_CHECK(a.is_cuda() && b.is_cuda() && is_bf16(a) && is_bf16(b) && a.dim() == 2 && b.dim() == 2 &&
-                    a.is_contiguous() && b.is_contiguous() && a.size(1) == b.size(1),
-                "gemm_scatter: a [M,K] and b [N,K] must be contiguous bf16 CUDA matrices");
-    TORCH_CHECK(a.size(1) % 8 == 0 && b.size(0) % 8 == 0 && aligned16(a) && aligned16(b) && slices_byte_off % 16 == 0,
+                    a.is_contiguous() && b.is_contiguous() && a.size(1) == b.size(b_mn ? 0 : 1),
+                "gemm_scatter: a [M,K] and b [N,K] (or [K,N] with b_mn) must be contiguous bf16 CUDA matrices");
+    TORCH_CHECK(a.size(1) % 8 == 0 && b.size(0) % 8 == 0 && b.size(1) % 8 == 0 && aligned16(a) && aligned16(b) &&
+                    slices_byte_off % 16 == 0,
                 "gemm_scatter: alignment");
     TORCH_CHECK(!ptrs.empty() && ptrs.size() <= 8 && rank >= 0 && rank < static_cast<int64_t>(ptrs.size()),
                 "gemm_scatter: between 1 and 8 ranks are supported");
@@ -180,8 +181,8 @@ void gemm_scatter(const Tensor& a, const Tensor& b, const std::vector<int64_t>& 
     check_status();
     c10::cuda::CUDAGuard guard(a.device());
     const char* err = fs2::gemm_scatter_bf16_tcgen05(
-        a.data_ptr(), b.data_ptr(), outs, static_cast<int>(ptrs.size()), static_cast<int>(rank),
-        static_cast<int>(rows_per_rank), static_cast<int>(a.size(0)), static_cast<int>(b.size(0)),
+        a.data_ptr(), b.data_ptr(), b_mn, outs, static_cast<int>(ptrs.size()), static_cast<int>(rank),
+        static_cast<int>(rows_per_rank), static_cast<int>(a.size(0)), static_cast<int>(b.size(b_mn ? 1 : 0)),
         static_cast<int>(a.size(1)), status_dev_ptr(), num_sms(a), stream_of(a));
     TORCH_CHECK(err == nullptr, "gemm_scatter: ", err);
     g_launches += 1;
@@ -206,16 +207,17 @@ void reduce_slices(const Tensor& slices, Tensor out) {
 // rank's arena, the per-block flags at `flags_byte_off`.
 void gemm_allgather(const std::vector<int64_t>& ptrs, int64_t rank, int64_t shard_byte_off, int64_t rows_per_rank,
                     const Tensor& other, int64_t gathered_byte_off, int64_t flags_byte_off, int64_t epoch,
-                    bool gather_b, Tensor out, int64_t ncopy) {
+                    bool gather_b, Tensor out, int64_t ncopy, bool other_mn) {
+    TORCH_CHECK(!(other_mn && gather_b), "gemm_allgather: an MN-major local operand needs gather of A");
     TORCH_CHECK(other.is_cuda() && is_bf16(other) && other.dim() == 2 && other.is_contiguous() && aligned16(other),
                 "gemm_allgather: the local operand must be a contiguous bf16 CUDA matrix");
     TORCH_CHECK(out.is_cuda() && is_bf16(out) && out.dim() == 2 && out.is_contiguous() && aligned16(out),
                 "gemm_allgather: `out` must be a contiguous bf16 CUDA matrix");
     const int64_t world = static_cast<int64_t>(ptrs.size());
     TORCH_CHECK(world >= 1 && world <= 8 && rank >= 0 && rank < world, "gemm_allgather: bad world/rank");
-    const int64_t K = other.size(1);
+    const int64_t K = other_mn ? other.size(0) : other.size(1);
     const int64_t M = gather_b ? other.size(0) : rows_per_rank * world;
-    const int64_t N = gather_b ? rows_per_rank * world : other.size(0);
+    const int64_t N = gather_b ? rows_per_rank * world : (other_mn ? other.size(1) : other.size(0));
     TORCH_CHECK(out.size(0) == M && out.size(1) == N && K % 8 == 0 && N % 8 == 0, "gemm_allgather: shape mismatch");
     TORCH_CHECK(shard_byte_off % 16 == 0 && gathered_byte_off % 1024 == 0 && flags_byte_off % 4 == 0,
                 "gemm_allgather: unaligned arena offsets");
@@ -234,7 +236,8 @@ void gemm_allgather(const std::vector<int64_t>& ptrs, int64_t rank, int64_t shar
         shards, static_cast<int>(world), static_cast<int>(rank), static_cast<int>(rows_per_rank), other.data_ptr(),
         reinterpret_cast<void*>(mine + gathered_byte_off), reinterpret_cast<unsigned int*>(mine + flags_byte_off),
         static_cast<unsigned int>(epoch), gather_b, out.data_ptr(), static_cast<int>(M), static_cast<int>(N),
-        static_cast<int>(K), static_cast<int>(ncopy), inplace, status_dev_ptr(), num_sms(other), stream_of(other));
+        static_cast<int>(K), static_cast<int>(ncopy), inplace, status_dev_ptr(), num_sms(other), stream_of(other),
+        other_mn);
     TORCH_CHECK(err == nullptr, "gemm_allgather: ", err);
     g_launches += 1;
 }

@@ -645,15 +645,17 @@ const char* gemm_bf16_tcgen05_view(const void* a, long long lda, long long a_row
 const char* gemm_allgather_bf16_tcgen05(const void* const* shards, int world, int rank, int rows_per_rank,
                                         const void* other, void* gathered, unsigned int* flags, unsigned int epoch,
                                         bool gather_b, void* c, int M, int N, int K, int ncopy, bool inplace,
-                                        int* status, int num_sms, cudaStream_t stream) {
+                                        int* status, int num_sms, cudaStream_t stream, bool other_mn) {
     if (world < 1 || world > 8) return "gemm_allgather: between 1 and 8 ranks are supported";
+    if (other_mn && gather_b) return "gemm_allgather: an MN-major local operand is only supported when A is gathered";
     const int blk = gather_b ? BN : BM;
     if (rows_per_rank % blk) return "gemm_allgather: the shard height must be a multiple of the tile height";
     if ((gather_b ? N : M) != rows_per_rank * world) return "gemm_allgather: shards do not add up to the operand";
     CUtensorMap ta, tb, tc;
     g_tmap_err[0] = 0;
     if (!make_tmap(&ta, gather_b ? other : gathered, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, BM, BK) ||
-        !make_tmap(&tb, gather_b ? gathered : other, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, BN, BK) ||
+        !(other_mn ? make_tmap(&tb, other, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, BK, 64)
+                   : make_tmap(&tb, gather_b ? gathered : other, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, BN, BK)) ||
         !make_tmap(&tc, c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, 128, 64))
         return g_tmap_err;
     GatherArgs ga{};
@@ -673,7 +675,16 @@ const char* gemm_allgather_bf16_tcgen05(const void* const* shards, int world, in
     int grid = num_tiles + ncopy;
     if (grid > num_sms) grid = num_sms;            // every CTA must be resident: compute CTAs wait on copier CTAs
     cudaError_t e;
-    if (!gather_b) {
+    if (!gather_b && other_mn) {
+        auto kern = gemm_kernel<false, true, false, false, 1>;
+        static bool configured = false;
+        if (!configured) {
+            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+            if (e != cudaSuccess) return cudaGetErrorString(e);
+            configured = true;
+        }
+        kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tc, M, N, K, 0, status, PeerOut{}, ga);
+    } else if (!gather_b) {
         auto kern = gemm_kernel<false, false, false, false, 1>;
         static bool configured = false;
         if (!configured) {
@@ -724,8 +735,8 @@ const char* gemm_reduce_scatter_bf16_tcgen05(const void* a, const void* b, float
     return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
 
-const char* gemm_scatter_bf16_tcgen05(const void* a, const void* b, void* const* peer_slices, int world, int rank,
-                                      int rows_per_rank, int M, int N, int K, int* status, int num_sms,
+const char* gemm_scatter_bf16_tcgen05(const void* a, const void* b, bool b_mn, void* const* peer_slices, int world,
+                                      int rank, int rows_per_rank, int M, int N, int K, int* status, int num_sms,
                                       cudaStream_t stream) {
     if (world < 1 || world > 8 || rank < 0 || rank >= world) return "gemm_scatter: between 1 and 8 ranks are supported";
     if (rows_per_rank <= 0 || rows_per_rank * world < M) return "gemm_scatter: rows_per_rank * world must cover M";
@@ -733,22 +744,31 @@ const char* gemm_scatter_bf16_tcgen05(const void* a, const void* b, void* const*
     CUtensorMap ta, tb;
     g_tmap_err[0] = 0;
     if (!make_tmap(&ta, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, BM, BK) ||
-        !make_tmap(&tb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, BN, BK))
+        !(b_mn ? make_tmap(&tb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, BK, 64)
+               : make_tmap(&tb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, BN, BK)))
         return g_tmap_err;
     PeerOut po{};
     for (int r = 0; r < world; ++r) po.out[r] = peer_slices[r];
     po.rows_per_rank = rows_per_rank;
     po.slice = rank;
-    auto kern = gemm_kernel<false, false, false, true>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_kernel<false, false, false, true>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(gemm_kernel<false, true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     SMEM_BYTES);
         if (e != cudaSuccess) return cudaGetErrorString(e);
         configured = true;
     }
     const int num_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int grid = num_tiles < num_sms ? num_tiles : num_sms;
-    kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, ta, M, N, K, 0, status, po, GatherArgs{});
+    if (b_mn)
+        gemm_kernel<false, true, false, true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, ta, M, N, K, 0, status,
+                                                                                          po, GatherArgs{});
+    else
+        gemm_kernel<false, false, false, true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, ta, M, N, K, 0, status,
+                                                                                           po, GatherArgs{});
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }

@@ -29,7 +29,7 @@ const char* gemm_bf16_tcgen05_view(const void* a, long long lda, long long a_row
 const char* gemm_allgather_bf16_tcgen05(const void* const* shards, int world, int rank, int rows_per_rank,
                                         const void* other, void* gathered, unsigned int* flags, unsigned int epoch,
                                         bool gather_b, void* c, int M, int N, int K, int ncopy, bool inplace,
-                                        int* status, int num_sms, cudaStream_t stream);
+                                        int* status, int num_sms, cudaStream_t stream, bool other_mn = false);
 
 // Row-parallel GEMM fused with its reduce-scatter: C = A[M,K] * B[N,K]^T is never stored locally; every fp32
 // tile is added into `peer_out[r]` ([rows_per_rank, N] fp32 in rank r's memory, zeroed beforehand), where r owns
@@ -40,8 +40,9 @@ const char* gemm_reduce_scatter_bf16_tcgen05(const void* a, const void* b, float
 
 // Same GEMM, bf16 scatter form: the tile is rounded to bf16 and stored into slice `rank` of `peer_slices[r]`
 // ([world, rows_per_rank, N] bf16 in rank r's memory). After a cross-rank barrier the owner sums its `world` slices.
-const char* gemm_scatter_bf16_tcgen05(const void* a, const void* b, void* const* peer_slices, int world, int rank,
-                                      int rows_per_rank, int M, int N, int K, int* status, int num_sms,
+// `b_mn`: B is given as [K, N] row-major (e.g. a weight used untransposed in a backward pass).
+const char* gemm_scatter_bf16_tcgen05(const void* a, const void* b, bool b_mn, void* const* peer_slices, int world,
+                                      int rank, int rows_per_rank, int M, int N, int K, int* status, int num_sms,
                                       cudaStream_t stream);
 
 }  // namespace fs2

@@ -15,6 +15,7 @@ from __future__ import annotations
 import torch
 from torch import Tensor
 
+from fairseq2_b200.ops.gemm import gemm
 from fairseq2_b200.parallel.symm import SymmetricArena
 
 
@@ -56,11 +57,14 @@ class FusedGemmReduceScatter:
             self._slots = [arena.alloc_tensor(arena.world * max_rows_per_rank * out_dim, torch.bfloat16)
                            for _ in range(2)]
 
-    def __call__(self, x: Tensor, weight: Tensor) -> Tensor:
-        """``x``: bf16 ``[M, K_local]``, ``weight``: bf16 ``[N, K_local]`` -> ``[M / world, N]``. In "red" mode the
-        result is an fp32 view into the arena that stays valid until the call after the next one."""
+    def __call__(self, x: Tensor, weight: Tensor, *, weight_kn: bool = False) -> Tensor:
+        """``x``: bf16 ``[M, K_local]``, ``weight``: bf16 ``[N, K_local]`` (or ``[K_local, N]`` with ``weight_kn``,
+        "scatter" mode only) -> ``[M / world, N]``. In "red" mode the result is an fp32 view into the arena that
+        stays valid until the call after the next one."""
         arena = self.arena
-        M, N = x.shape[0], weight.shape[0]
+        if weight_kn and self.mode != "scatter":
+            raise ValueError("`weight_kn` needs mode='scatter'.")
+        M, N = x.shape[0], weight.shape[1 if weight_kn else 0]
         if M % arena.world:
             raise ValueError(f"The number of rows ({M}) must be a multiple of the world size ({arena.world}).")
         rows = M // arena.world
@@ -76,7 +80,7 @@ class FusedGemmReduceScatter:
             return buf[: rows * N].view(rows, N)
         # two slots alternate: a rank passes the barrier of call k + 1 only after its own sum of call k, so the
         # slot written by call k + 2 is no longer being read by anyone
-        arena.ext.gemm_scatter(x.contiguous(), weight.contiguous(), arena.peer_ptrs, arena.rank, off, rows)
+        arena.ext.gemm_scatter(x.contiguous(), weight.contiguous(), arena.peer_ptrs, arena.rank, off, rows, weight_kn)
         arena.barrier_next(self.SLOT)         # every rank's tiles for my rows have landed
         out = torch.empty((rows, N), device=x.device, dtype=self.out_dtype)
         arena.ext.reduce_slices(buf[: arena.world * rows * N].view(arena.world, rows * N), out)
@@ -119,20 +123,114 @@ class FusedAllGatherGemm:
         self._epoch = 0
         self._bar_epoch = 0
 
-    def __call__(self, other: Tensor, out: Tensor | None = None) -> Tensor:
+    @property
+    def gathered(self) -> Tensor:
+        """The assembled operand ``[world * rows, k]`` (valid after a call until the shard is rewritten)."""
+        a = self.arena
+        n = a.world * self.rows * self.k * 2
+        return a.buf[self._gathered_off: self._gathered_off + n].view(torch.bfloat16).view(a.world * self.rows, self.k)
+
+    def __call__(self, other: Tensor, out: Tensor | None = None, *, other_kn: bool = False) -> Tensor:
+        """``other``: the local operand ``[N, k]`` (gather="a"; ``[k, N]`` with ``other_kn``) or ``[M, k]``
+        (gather="b")."""
         a = self.arena
         W = a.world
         if self.gather_b:
             M, N = other.shape[0], self.rows * W
         else:
-            M, N = self.rows * W, other.shape[0]
+            M, N = self.rows * W, other.shape[1 if other_kn else 0]
         if out is None:
             out = torch.empty((M, N), device=other.device, dtype=torch.bfloat16)
         # every rank has written its shard (and finished reading the shards of the previous call)
         a.barrier_next(self.SLOT)
         self._epoch += 1
         a.ext.gemm_allgather(a.peer_ptrs, a.rank, self._shard_off, self.rows, other.contiguous(), self._gathered_off,
-                             self._flags_off, self._epoch, self.gather_b, out, self.ncopy)
+                             self._flags_off, self._epoch, self.gather_b, out, self.ncopy, other_kn)
         # nobody may overwrite its shard for the next call while a slower peer is still copying it
         a.barrier_next(self.SLOT)
         return out
+
+
+class _ColumnSP(torch.autograd.Function):
+    """``y [T, F_local] = all_gather(x_shard) @ w^T``; backward reduce-scatters ``dy @ w`` back to the token shard."""
+
+    @staticmethod
+    def forward(ctx, x_shard: Tensor, weight: Tensor, sp: "SequenceParallelLinears") -> Tensor:  # type: ignore[override]
+        sp.ag.shard.copy_(x_shard)
+        y = sp.ag(weight)
+        ctx.save_for_backward(x_shard, weight)
+        ctx.sp = sp
+        return y
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):  # type: ignore[override]
+        x_shard, weight = ctx.saved_tensors
+        sp: SequenceParallelLinears = ctx.sp
+        dy = dy.contiguous()
+        dx_shard = sp.rs(dy, weight, weight_kn=True)                 # [T / W, D] = reduce_scatter(dy @ w)
+        dw = None
+        if ctx.needs_input_grad[1]:
+            x_full = sp.all_gather_tokens(x_shard)
+            dw = gemm(dy, x_full, a_mn=True, b_mn=True)              # [F_local, D] = dy^T @ x
+        return dx_shard, dw, None
+
+
+class _RowSP(torch.autograd.Function):
+    """``y_shard [T / W, D] = reduce_scatter(h @ w^T)``; backward all-gathers ``dy_shard`` inside the dgrad GEMM."""
+
+    @staticmethod
+    def forward(ctx, h: Tensor, weight: Tensor, sp: "SequenceParallelLinears") -> Tensor:  # type: ignore[override]
+        y = sp.rs(h, weight)
+        ctx.save_for_backward(h, weight)
+        ctx.sp = sp
+        return y
+
+    @staticmethod
+    def backward(ctx, dy_shard: Tensor):  # type: ignore[override]
+        h, weight = ctx.saved_tensors
+        sp: SequenceParallelLinears = ctx.sp
+        sp.ag.shard.copy_(dy_shard)
+        dh = sp.ag(weight, other_kn=True)                            # [T, F_local] = all_gather(dy) @ w
+        dw = None
+        if ctx.needs_input_grad[1]:
+            dw = gemm(sp.ag.gathered, h, a_mn=True, b_mn=True)       # [D, F_local] = dy^T @ h (dy just gathered)
+        return dh, dw, None
+
+
+class SequenceParallelLinears:
+    """Megatron-style tensor parallelism with sequence-parallel activations, every collective fused into a GEMM.
+
+    Activations between blocks are sharded by tokens (``[T / W, D]`` per rank). ``column(x_shard, w)`` is the
+    column-parallel projection (``w``: ``[F / W, D]``): the all-gather of the tokens runs inside the tcgen05 GEMM.
+    ``row(h, w)`` is the row-parallel projection (``w``: ``[D, F / W]``): the GEMM epilogue scatters its tiles to the
+    ranks that own the rows and the result comes back token-sharded. The backward passes use the same two kernels
+    with the roles swapped, so a feed-forward block costs four fused launches and no stand-alone collective except
+    the token all-gather for the column weight gradient. One instance serves all layers of a model with the same
+    ``tokens_per_rank`` and ``model_dim`` (the reference has no sequence-parallel mode:
+    fairseq2 ``ops/tensor_parallel.py:18-140``, ``nn/projection.py:127-626``).
+    """
+
+    def __init__(self, arena: SymmetricArena, tokens_per_rank: int, model_dim: int) -> None:
+        self.arena = arena
+        self.tokens_per_rank, self.model_dim = tokens_per_rank, model_dim
+        self.ag = FusedAllGatherGemm(arena, tokens_per_rank, model_dim, gather="a")
+        self.rs = FusedGemmReduceScatter(arena, tokens_per_rank, model_dim, mode="scatter")
+        self._gather_off, buf = arena.alloc(tokens_per_rank * model_dim * 2, align=16)
+        self._gather_src = buf.view(torch.bfloat16).view(tokens_per_rank, model_dim)
+        self._epoch = 0
+
+    def all_gather_tokens(self, x_shard: Tensor) -> Tensor:
+        a = self.arena
+        self._gather_src.copy_(x_shard)
+        n = self.tokens_per_rank * self.model_dim
+        full = torch.empty(a.world * n, device=x_shard.device, dtype=torch.bfloat16)
+        a.barrier_next(FusedAllGatherGemm.SLOT)                      # every rank has staged its shard
+        a.ext.comm_allgather_segments(a.peer_ptrs, a.rank, [0], [n], self._gather_off, full, 1, 0, 8, a.wait_limit_s)
+        a.barrier_next(FusedAllGatherGemm.SLOT)                      # nobody restages while a peer still reads
+        return full.view(a.world * self.tokens_per_rank, self.model_dim)
+
+    def column(self, x_shard: Tensor, weight: Tensor) -> Tensor:
+        return _ColumnSP.apply(x_shard, weight, self)
+
+    def row(self, h: Tensor, weight: Tensor) -> Tensor:
+        return _RowSP.apply(h, weight, self)

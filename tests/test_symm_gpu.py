@@ -389,3 +389,54 @@ def test_moe_expert_parallel_matches_single_rank() -> None:
     _need_gpus(2)
     for errs in run_distributed(_moe_ep_worker, 2):
         assert all(e < 3e-2 for e in errs), errs
+
+
+def _sp_mlp_worker(rank: int, world: int):
+    """Sequence-parallel tensor-parallel MLP (column -> GELU -> row) built from the fused kernels vs the same MLP on
+    one rank: outputs for this rank's tokens, input gradient, both weight-gradient shards."""
+    from fairseq2_b200.gang import ProcessGroupGang
+    from fairseq2_b200.ops.fused_collective import SequenceParallelLinears
+    from fairseq2_b200.parallel.symm import SymmetricArena
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    base = ProcessGroupGang.create_default_process_group(dev)
+    Tl, D, F = 256, 256, 1024
+    arena = SymmetricArena(base, 16 << 20)
+    sp = SequenceParallelLinears(arena, Tl, D)
+    gen = torch.Generator().manual_seed(3)
+    w1 = (torch.randn(F, D, generator=gen) * D ** -0.5).to(dev, torch.bfloat16)
+    w2 = (torch.randn(D, F, generator=gen) * F ** -0.5).to(dev, torch.bfloat16)
+    Fl = F // world
+    w1_l = w1[rank * Fl:(rank + 1) * Fl].clone().requires_grad_(True)          # column shard [F / W, D]
+    w2_l = w2[:, rank * Fl:(rank + 1) * Fl].clone().contiguous().requires_grad_(True)   # row shard [D, F / W]
+    errs = []
+    for step in range(2):
+        x = torch.randn(world * Tl, D, generator=torch.Generator().manual_seed(10 + step)).to(dev, torch.bfloat16)
+        g = torch.randn(world * Tl, D, generator=torch.Generator().manual_seed(20 + step)).to(dev, torch.bfloat16)
+        xs = x[rank * Tl:(rank + 1) * Tl].clone().requires_grad_(True)
+        w1_l.grad = w2_l.grad = None
+        y = sp.row(torch.nn.functional.gelu(sp.column(xs, w1_l)), w2_l)
+        y.backward(g[rank * Tl:(rank + 1) * Tl])
+        xr = x.float().requires_grad_(True)
+        w1r, w2r = w1.float().requires_grad_(True), w2.float().requires_grad_(True)
+        yr = torch.nn.functional.gelu(xr @ w1r.t()) @ w2r.t()
+        yr.backward(g.float())
+
+        def rel(a, b):
+            return float((a.float() - b).norm() / b.norm().clamp(min=1e-6))
+
+        sl = slice(rank * Tl, (rank + 1) * Tl)
+        errs += [rel(y, yr[sl].detach()), rel(xs.grad, xr.grad[sl]), rel(w1_l.grad, w1r.grad[rank * Fl:(rank + 1) * Fl]),
+                 rel(w2_l.grad, w2r.grad[:, rank * Fl:(rank + 1) * Fl])]
+    torch.cuda.synchronize()
+    arena.ext.check_status()
+    base.close()
+    return errs
+
+
+def test_sequence_parallel_mlp_from_fused_kernels() -> None:
+    _need_gpus(2)
+    for errs in run_distributed(_sp_mlp_worker, 2):
+        assert all(e < 3e-2 for e in errs), errs
