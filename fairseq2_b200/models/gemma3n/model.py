@@ -16,6 +16,7 @@ from torch.nn import Module, ModuleList, Parameter
 from fairseq2_b200.models.gemma3n.config import Gemma3nConfig, is_global_layer, kv_source_layer
 from fairseq2_b200.nn import BatchLayout
 from fairseq2_b200.nn.functional import cross_entropy
+from fairseq2_b200.nn.incremental_state import IncrementalState, IncrementalStateBag
 from fairseq2_b200.nn.normalization import RMSNorm
 from fairseq2_b200.nn.projection import Linear
 from fairseq2_b200.ops.attention import varlen_attention
@@ -110,6 +111,41 @@ def _rope_half(x: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
     return x * cos.unsqueeze(1) + rot * sin.unsqueeze(1)
 
 
+class _KVState(IncrementalState):
+    """Keys and values of one layer for all steps so far: ``[N, L, Hkv, D]``."""
+
+    def __init__(self, k: Tensor, v: Tensor) -> None:
+        self.k, self.v = k, v
+
+    def append(self, k: Tensor, v: Tensor) -> None:
+        self.k, self.v = torch.cat([self.k, k], dim=1), torch.cat([self.v, v], dim=1)
+
+    def reorder(self, new_order: Tensor) -> None:
+        self.k, self.v = self.k.index_select(0, new_order), self.v.index_select(0, new_order)
+
+    def size_bytes(self) -> int:
+        return 2 * self.k.numel() * self.k.element_size()
+
+    def capacity_bytes(self) -> int:
+        return self.size_bytes()
+
+
+class _AttnGeometry:
+    """Flattened-token geometry of one forward call: where each sequence's queries and keys start and how long they
+    are. Without a state bag keys = queries; with one, keys also cover the cached steps."""
+
+    def __init__(self, q_begins: Tensor, q_lens: Tensor, max_q: int, batch: int | None, steps: int | None) -> None:
+        self.q_begins, self.q_lens, self.max_q = q_begins, q_lens, max_q
+        self.k_begins, self.k_lens, self.max_k = q_begins, q_lens, max_q
+        self.batch, self.steps = batch, steps          # set in incremental mode: tokens are [batch, steps]
+
+    def with_cache_len(self, total: int, device: torch.device) -> None:
+        assert self.batch is not None
+        self.k_begins = torch.arange(self.batch, device=device, dtype=torch.int32) * total
+        self.k_lens = torch.full((self.batch,), total, device=device, dtype=torch.int32)
+        self.max_k = total
+
+
 class Gemma3nAttention(Module):
     def __init__(self, cfg: Gemma3nConfig, layer_idx: int, device: Device | None, dtype: DataType | None) -> None:
         super().__init__()
@@ -126,8 +162,9 @@ class Gemma3nAttention(Module):
         self.q_norm = RMSNorm(D, bias=False, eps=cfg.rms_norm_eps, **kw)
         self.k_norm = RMSNorm(D, bias=False, eps=cfg.rms_norm_eps, **kw)
 
-    def forward(self, x: Tensor, cos: Tensor, sin: Tensor, layout: BatchLayout, begins: Tensor, lens: Tensor,
-                shared_kv: dict[int, tuple[Tensor, Tensor]], layer_idx: int) -> Tensor:
+    def forward(self, x: Tensor, cos: Tensor, sin: Tensor, geo: _AttnGeometry,
+                shared_kv: dict[int, tuple[Tensor, Tensor]], layer_idx: int,
+                state_bag: IncrementalStateBag | None = None) -> Tensor:
         """``x``: ``[T, D_model]`` (tokens of all sequences, flattened)."""
         T = x.shape[0]
         q = _rope_half(self.q_norm(self.q_proj(x).view(T, self.H, self.D)), cos, sin)
@@ -136,9 +173,21 @@ class Gemma3nAttention(Module):
         else:
             k = _rope_half(self.k_norm(self.k_proj(x).view(T, self.Hkv, self.D)), cos, sin)
             v = _rms(self.v_proj(x).view(T, self.Hkv, self.D), self.eps)
+            if state_bag is not None:
+                # keys/values of the earlier steps come from the cache; the new ones are appended
+                kb, vb = k.view(geo.batch, geo.steps, self.Hkv, self.D), v.view(geo.batch, geo.steps, self.Hkv, self.D)
+                state = state_bag.maybe_get_state(self, _KVState)
+                if state is None:
+                    state = _KVState(kb, vb)
+                    state_bag.set_state(self, state)
+                else:
+                    state.append(kb, vb)
+                k, v = state.k.reshape(-1, self.Hkv, self.D), state.v.reshape(-1, self.Hkv, self.D)
             shared_kv[layer_idx] = (k, v)
-        out = varlen_attention(q.contiguous(), k.contiguous(), v.contiguous(), begins, lens, begins, lens,
-                               layout.max_seq_len, layout.max_seq_len, causal=True, scale=1.0, window=self.window)
+        if state_bag is not None:
+            geo.with_cache_len(k.shape[0] // geo.batch, x.device)
+        out = varlen_attention(q.contiguous(), k.contiguous(), v.contiguous(), geo.q_begins, geo.q_lens, geo.k_begins,
+                               geo.k_lens, geo.max_q, geo.max_k, causal=True, scale=1.0, window=self.window)
         return self.o_proj(out.reshape(T, self.H * self.D))
 
 
@@ -159,14 +208,14 @@ class Gemma3nDecoderLayer(Module):
         self.per_layer_projection = Linear(p, d, bias=False, **kw)
         self.post_per_layer_input_norm = norm()
 
-    def forward(self, streams: Tensor, per_layer_input: Tensor, cos: Tensor, sin: Tensor, layout: BatchLayout,
-                begins: Tensor, lens: Tensor, shared_kv: dict[int, tuple[Tensor, Tensor]]) -> Tensor:
+    def forward(self, streams: Tensor, per_layer_input: Tensor, cos: Tensor, sin: Tensor, geo: _AttnGeometry,
+                shared_kv: dict[int, tuple[Tensor, Tensor]], state_bag: IncrementalStateBag | None = None) -> Tensor:
         predictions = self.altup.predict(streams)
         active = predictions[self.active]
         normed = self.input_layernorm(active)
         laurel = self.laurel(normed)
-        attn = self.post_attention_layernorm(self.self_attn(normed, cos, sin, layout, begins, lens, shared_kv,
-                                                            self.layer_idx))
+        attn = self.post_attention_layernorm(self.self_attn(normed, cos, sin, geo, shared_kv, self.layer_idx,
+                                                            state_bag))
         attn_laurel = (active + attn + laurel) / math.sqrt(2.0)
         ffn = self.post_feedforward_layernorm(self.mlp(self.pre_feedforward_layernorm(attn_laurel)))
         corrected = self.altup.correct(predictions, attn_laurel + ffn)
@@ -229,19 +278,24 @@ class Gemma3nModel(Module):
         mag = torch.sqrt(torch.clamp(x.pow(2).mean(-1, keepdim=True), min=1e-5))
         return x * target / mag
 
-    def decode(self, seqs: Tensor, layout: BatchLayout) -> Tensor:
-        """Token ids ``[N, S]`` or packed ``[T]`` -> final hidden states of the same leading shape."""
+    def decode(self, seqs: Tensor, layout: BatchLayout, state_bag: IncrementalStateBag | None = None) -> Tensor:
+        """Token ids ``[N, S]`` or packed ``[T]`` -> final hidden states of the same leading shape. With a state bag
+        ``seqs`` holds the next ``S`` steps of every sequence (unpadded) and attention also covers the cached steps."""
         cfg = self.cfg
         shape = seqs.shape
         ids = seqs.reshape(-1)
         T = ids.shape[0]
         if layout.packed:
-            begins, lens = layout.seq_begin_indices_pt[:-1], layout.seq_lens_pt
+            if state_bag is not None:
+                raise ValueError("Incremental decoding needs an unpacked batch.")
+            geo = _AttnGeometry(layout.seq_begin_indices_pt[:-1], layout.seq_lens_pt, layout.max_seq_len, None, None)
         else:
             S = shape[1]
-            lens = layout.seq_lens_pt
             begins = (torch.arange(shape[0], device=ids.device, dtype=torch.int32) * S)
+            geo = _AttnGeometry(begins, layout.seq_lens_pt, layout.max_seq_len, shape[0], S)
         positions = layout.position_indices.reshape(-1).clamp(min=0)
+        if state_bag is not None:
+            positions = positions + state_bag.step_nr
         x0 = self.embed_tokens(ids) * cfg.model_dim ** 0.5
         per_layer = self._per_layer_inputs(ids, x0)
         target = x0.pow(2).mean(-1, keepdim=True) ** 0.5
@@ -251,7 +305,7 @@ class Gemma3nModel(Module):
         shared_kv: dict[int, tuple[Tensor, Tensor]] = {}
         for i, layer in enumerate(self.layers):
             cos, sin = (cos_g, sin_g) if layer.self_attn.is_global else (cos_l, sin_l)
-            streams = layer(streams, per_layer[:, i], cos, sin, layout, begins, lens, shared_kv)
+            streams = layer(streams, per_layer[:, i], cos, sin, geo, shared_kv, state_bag)
         target = streams[0].pow(2).mean(-1, keepdim=True) ** 0.5
         outs = [streams[0]] + [self._match_magnitude(proj(streams[i + 1]), target)
                                for i, proj in enumerate(self.altup_unembed_projections)]
@@ -267,12 +321,11 @@ class Gemma3nModel(Module):
             logits = torch.tanh(logits.float() / cap).mul(cap).type_as(logits)
         return logits
 
-    def forward(self, seqs: Tensor, seqs_layout: BatchLayout, targets: Tensor | None = None, *, state_bag: object = None,
+    def forward(self, seqs: Tensor, seqs_layout: BatchLayout, targets: Tensor | None = None, *,
+                state_bag: IncrementalStateBag | None = None,
                 label_smoothing: float = 0.0, target_mask: Tensor | None = None,
                 reduction: Literal["sum", "mean"] = "sum", return_logits: bool = False):  # type: ignore[no-untyped-def]
-        if state_bag is not None:
-            raise NotImplementedError("Incremental decoding is not implemented for Gemma 3n.")
-        logits = self.project(self.decode(seqs, seqs_layout))
+        logits = self.project(self.decode(seqs, seqs_layout, state_bag))
         if targets is None:
             return logits
         loss = cross_entropy(logits, targets, self.pad_idx, label_smoothing=label_smoothing, target_mask=target_mask,

@@ -163,3 +163,31 @@ def test_gemma3n_text_logits_match_hf(shared: int) -> None:
     # round trip of the exporter
     sd, _ = export_gemma3n_to_hg(model.state_dict(), cfg)
     assert set(sd) == {k for k in hf.state_dict() if k != "lm_head.weight"}
+
+
+def test_gemma3n_incremental_decoding_matches_full_forward() -> None:
+    """Prefill + single steps through the KV cache (incl. KV-sharing layers and the sliding window) reproduce the
+    logits of one full forward; the sampling generator runs on the model."""
+    from dataclasses import replace
+
+    from fairseq2_b200.generation import SamplingSequenceGenerator
+    from fairseq2_b200.models.gemma3n import create_gemma3n_model
+    from fairseq2_b200.models.gemma3n.config import gemma3n_tiny
+    from fairseq2_b200.nn.incremental_state import IncrementalStateBag
+
+    torch.manual_seed(0)
+    cfg = replace(gemma3n_tiny(), num_kv_shared_layers=2, num_layers=8)
+    model = create_gemma3n_model(cfg).eval()
+    ids = torch.randint(1, cfg.vocab_size, (2, 20))
+    with torch.no_grad():
+        full = model(ids, BatchLayout((2, 20), [20, 20]))
+        bag = IncrementalStateBag(64)
+        outs = [model(ids[:, :11], BatchLayout.of(ids[:, :11]), state_bag=bag)]
+        bag.increment_step_nr(11)
+        for t in range(11, 20):
+            outs.append(model(ids[:, t:t + 1], BatchLayout.of(ids[:, t:t + 1]), state_bag=bag))
+            bag.increment_step_nr(1)
+    assert torch.allclose(torch.cat(outs, dim=1), full, atol=1e-4)
+    gen = SamplingSequenceGenerator(model, eos_idx=2, pad_idx=0, max_gen_len=6)
+    out = gen(ids[:, :5], BatchLayout((2, 5), [5, 4]))
+    assert len(out.hypotheses) == 2 and all(len(h[0].seq) >= 5 for h in out.hypotheses)
