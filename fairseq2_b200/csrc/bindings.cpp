@@ -135,7 +135,7 @@ void gemm_reduce_scatter(const Tensor& a, const Tensor& b, const std::vector<int
 // logical shapes: A [M, K] (or [K, M] if a_mn), B [N, K] (or [K, N] if b_mn), out [M, N] bf16/fp32.
 void gemm_bf16_view(const Tensor& a, int64_t a_rows, int64_t lda, bool a_mn, const Tensor& b, int64_t b_rows, int64_t ldb,
                     bool b_mn, Tensor out, int64_t c_rows, int64_t ldc, int64_t M, int64_t N, int64_t K,
-                    bool accumulate) {
+                    bool accumulate, int64_t k_splits) {
     TORCH_CHECK(a.is_cuda() && b.is_cuda() && out.is_cuda() && is_bf16(a) && is_bf16(b) && a.is_contiguous() &&
                     b.is_contiguous() && out.is_contiguous() && aligned16(a) && aligned16(b) && aligned16(out),
                 "gemm_bf16_view: operands must be contiguous, 16-byte aligned CUDA storage (bf16 inputs)");
@@ -156,7 +156,8 @@ void gemm_bf16_view(const Tensor& a, int64_t a_rows, int64_t lda, bool a_mn, con
     TORCH_CHECK(cudaSetDevice(a.get_device()) == cudaSuccess, "gemm_bf16_view: cudaSetDevice failed");
     const char* err = fs2::gemm_bf16_tcgen05_view(a.data_ptr(), lda, a_rows, b.data_ptr(), ldb, b_rows, out.data_ptr(), ldc,
                                                   c_rows, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K),
-                                                  a_mn, b_mn, f32, accumulate, status_dev_ptr(), num_sms(a), stream_of(a));
+                                                  a_mn, b_mn, f32, accumulate, status_dev_ptr(), num_sms(a), stream_of(a),
+                                                  static_cast<int>(k_splits));
     TORCH_CHECK(err == nullptr, "gemm_bf16_view: ", err);
     g_launches += 1;
 }

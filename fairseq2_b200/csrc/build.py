@@ -63,10 +63,20 @@ def build_data(verbose: bool = False, force: bool = False) -> Path | None:
     target = PKG / "_data.so"
     if not force and not _newer(sources, target):
         return target
-    build_dir = CSRC / "_build" / "data"
+    # FAIRSEQ2_B200_SANITIZE=address|undefined|thread builds the data runtime with that sanitizer into
+    # _data_<kind>.so (load it with LD_PRELOAD of the sanitizer runtime); the regular build is untouched
+    sanitize = os.environ.get("FAIRSEQ2_B200_SANITIZE", "")
+    if sanitize and sanitize not in ("address", "undefined", "thread"):
+        raise ValueError(f"FAIRSEQ2_B200_SANITIZE must be address, undefined or thread, but is '{sanitize}'.")
+    cflags, ldflags, tag = ["-O2", "-std=c++17", "-pthread"], ["-pthread", "-lz"], "data"
+    if sanitize:
+        cflags += [f"-fsanitize={sanitize}", "-fno-omit-frame-pointer", "-g"]
+        ldflags += [f"-fsanitize={sanitize}"]
+        tag = f"data_{sanitize}"
+        target = PKG / f"_data_{sanitize}.so"
+    build_dir = CSRC / "_build" / tag
     build_dir.mkdir(parents=True, exist_ok=True)
-    cpp_extension.load(name="_data", sources=[str(s) for s in sources],
-                       extra_cflags=["-O2", "-std=c++17", "-pthread"], extra_ldflags=["-pthread", "-lz"],
+    cpp_extension.load(name="_data", sources=[str(s) for s in sources], extra_cflags=cflags, extra_ldflags=ldflags,
                        build_directory=str(build_dir), verbose=verbose, is_python_module=False, with_cuda=False)
     shutil.copy2(build_dir / "_data.so", target)
     return target

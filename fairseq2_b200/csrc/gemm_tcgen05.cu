@@ -139,7 +139,43 @@ struct GatherArgs {
     int world;
     long long row_bytes;
     int inplace;        // the own shard already sits at its place in `dst`: only the peers' shards are copied
+    // Grouped (mixture-of-experts) modes, MODE 3 and 4; all tables live in device memory, nothing is read on the host
+    const int* tile_row0;      // MODE 3: first row of m-tile i in the expert-sorted, 128-row padded activation buffer
+    const int* tile_expert;    // MODE 3: expert of m-tile i
+    const int* num_m_tiles;    // MODE 3: number of valid m-tiles
+    const int* group_offsets;  // MODE 4: padded row offset of every expert, [experts + 1], multiples of 128
+    int group_rows_b;          // MODE 3: rows one expert occupies in B's tensor map
+    int experts;               // MODE 4
 };
+
+// Tile of a grouped GEMM (MODE 3: per-expert row blocks times a per-expert weight; MODE 4: per-expert weight gradient).
+struct GroupedTile {
+    int m0, n0, b_row_add, c_row0, kb_begin, kb_end;
+};
+
+template <int MODE>
+__device__ __forceinline__ GroupedTile grouped_tile(int t, int num_m, int num_n, int M, const GatherArgs& ga) {
+    GroupedTile g;
+    if constexpr (MODE == 3) {
+        const int mi = t / num_n;
+        g.m0 = ga.tile_row0[mi];
+        g.n0 = (t % num_n) * BN;
+        g.b_row_add = ga.tile_expert[mi] * ga.group_rows_b;
+        g.c_row0 = g.m0;
+        g.kb_begin = 0;
+        g.kb_end = -1;                   // caller substitutes the full K range
+    } else {
+        const int per = num_m * num_n;
+        const int e = t / per, r = t % per;
+        g.m0 = (r / num_n) * BM;
+        g.n0 = (r % num_n) * BN;
+        g.b_row_add = 0;
+        g.c_row0 = e * M + g.m0;
+        g.kb_begin = ga.group_offsets[e] / BK;
+        g.kb_end = ga.group_offsets[e + 1] / BK;
+    }
+    return g;
+}
 
 // PEER_RED: instead of storing C locally, every tile goes straight into the memory of the rank that owns its rows,
 // so a row-parallel GEMM and the reduce-scatter that follows it are one kernel and the NVLink traffic of tile i
@@ -155,10 +191,13 @@ struct GatherArgs {
 template <bool A_MN, bool B_MN, bool OUT_F32, bool PEER_RED = false, int GATHER = 0>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-            const __grid_constant__ CUtensorMap tma_c, int M, int N, int K, int accumulate, int* status,
+            const __grid_constant__ CUtensorMap tma_c, int M, int N, int K, int accumulate_and_splits, int* status,
             const PeerOut po, const GatherArgs ga) {
+    int accumulate = accumulate_and_splits;
+    constexpr bool kGather = GATHER == 1 || GATHER == 2;  // GATHER 3 / 4 are the grouped (MoE) modes
+    constexpr int GROUPED = GATHER == 3 ? 1 : (GATHER == 4 ? 2 : 0);
     constexpr int GBLK = GATHER == 2 ? BN : BM;          // rows of the gathered operand per flag
-    if constexpr (GATHER != 0) {
+    if constexpr (kGather) {
         if (static_cast<int>(blockIdx.x) < ga.ncopy) {
             // Copier CTA: one thread moves its blocks with bulk copies, peer memory -> shared memory -> local
             // memory, COPY_BUFS chunks of COPY_CHUNK bytes in flight, so no registers stage the data and ~200 KB
@@ -244,7 +283,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
             return;
         }
     }
-    const int ncopy = GATHER != 0 ? ga.ncopy : 0;
+    const int ncopy = kGather ? ga.ncopy : 0;
     const int first_tile = static_cast<int>(blockIdx.x) - ncopy;
     const int tile_stride = static_cast<int>(gridDim.x) - ncopy;
     extern __shared__ uint8_t smem_raw[];
@@ -266,10 +305,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
-    const int num_m = (M + BM - 1) / BM;
+    const int num_m = GROUPED == 1 ? *ga.num_m_tiles : (M + BM - 1) / BM;
     const int num_n = (N + BN - 1) / BN;
-    const int num_tiles = num_m * num_n;
-    const int num_kb = (K + BK - 1) / BK;
+    // split-K: `accumulate` carries the number of K splits in its bits 8 and up (0/1 = none). Tile t then covers
+    // output tile t % (num_m * num_n) over the K range of split t / (num_m * num_n) and is reduce-added into C.
+    const int k_splits = (accumulate >> 8) > 1 ? (accumulate >> 8) : 1;
+    accumulate &= 1;
+    const int num_mn = num_m * num_n;
+    const int num_tiles = GROUPED == 2 ? num_mn * ga.experts : num_mn * k_splits;
+    const int num_kb_total = (K + BK - 1) / BK;
+    const int kb_per_split = (num_kb_total + k_splits - 1) / k_splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -302,8 +347,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
             uint32_t phase = 0;
             bool ok = true;
             for (int t = first_tile; t < num_tiles && ok; t += tile_stride) {
-                int mt, nt;
-                if constexpr (GATHER != 0) {
+                int mt = 0, nt = 0;
+                GroupedTile gt{};
+                if constexpr (GROUPED != 0) {
+                    gt = grouped_tile<GATHER>(t, num_m, num_n, M, ga);
+                } else if constexpr (kGather) {
                     int gblock;
                     gather_tile_coords<GATHER>(t, num_m, num_n, ga.rank, ga.world, ga.rows_per_rank / GBLK, mt, nt, gblock);
                     // wait until the copier CTAs have landed this block of the gathered operand
@@ -323,10 +371,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
                     fence_proxy_async_smem();
                     asm volatile("fence.proxy.async.global;" ::: "memory");   // generic-proxy copies -> TMA reads
                 } else {
-                    tile_coords(t, num_m, num_n, mt, nt);
+                    tile_coords(t % num_mn, num_m, num_n, mt, nt);
                 }
-                const int m0 = mt * BM, n0 = nt * BN;
-                for (int kb = 0; kb < num_kb; ++kb) {
+                const int m0 = GROUPED != 0 ? gt.m0 : mt * BM, n0 = GROUPED != 0 ? gt.n0 : nt * BN;
+                const int b_add = GROUPED != 0 ? gt.b_row_add : 0;
+                int kb_begin = (t / num_mn) * kb_per_split;
+                int kb_end = min(num_kb_total, kb_begin + kb_per_split);
+                if constexpr (GROUPED == 1) { kb_begin = 0; kb_end = num_kb_total; }
+                if constexpr (GROUPED == 2) { kb_begin = gt.kb_begin; kb_end = gt.kb_end; }
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
                         if (!*abort_flag) report_status(status, kStatusTimeout | (1 << 8));
                         *abort_flag = 1;
@@ -345,10 +398,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
                         for (int h = 0; h < BM / 64; ++h) tma_load_2d(a_s + h * MN_BLOCK_BYTES, &tma_a, fb, m0 + h * 64, k0);
                     }
                     if constexpr (!B_MN) {
-                        tma_load_2d(b_s, &tma_b, fb, k0, n0);
+                        tma_load_2d(b_s, &tma_b, fb, k0, n0 + b_add);
                     } else {
 #pragma unroll
-                        for (int h = 0; h < BN / 64; ++h) tma_load_2d(b_s + h * MN_BLOCK_BYTES, &tma_b, fb, n0 + h * 64, k0);
+                        for (int h = 0; h < BN / 64; ++h)
+                            tma_load_2d(b_s + h * MN_BLOCK_BYTES, &tma_b, fb, n0 + h * 64, k0 + b_add);
                     }
                     if (++stage == STAGES) {
                         stage = 0;
@@ -374,7 +428,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
                 }
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-                for (int kb = 0; kb < num_kb; ++kb) {
+                int kb_begin = (t / num_mn) * kb_per_split;
+                int kb_end = min(num_kb_total, kb_begin + kb_per_split);
+                if constexpr (GROUPED == 1) { kb_begin = 0; kb_end = num_kb_total; }
+                if constexpr (GROUPED == 2) {
+                    const GroupedTile gt = grouped_tile<GATHER>(t, num_m, num_n, M, ga);
+                    kb_begin = gt.kb_begin;
+                    kb_end = gt.kb_end;
+                }
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     if (!mbar_wait_bounded(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
                         if (!*abort_flag) report_status(status, kStatusTimeout | (3 << 8));
                         *abort_flag = 1;
@@ -391,7 +453,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
                         else da = make_smem_desc(a_s + k * UMMA_K * 128, MN_BLOCK_BYTES, 1024);
                         if constexpr (!B_MN) db = make_smem_desc(b_s + k * UMMA_K * 2, 16, 1024);
                         else db = make_smem_desc(b_s + k * UMMA_K * 128, MN_BLOCK_BYTES, 1024);
-                        umma_bf16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        umma_bf16(d_tmem, da, db, idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
                     }
                     umma_commit(empty_bar(stage));
                     if (++stage == STAGES) {
@@ -416,14 +478,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         uint32_t acc_phase = 0;
         int buf = 0;
         for (int t = first_tile; t < num_tiles; t += tile_stride) {
-            int mt, nt;
-            if constexpr (GATHER != 0) {
+            int mt = 0, nt = 0;
+            GroupedTile gt{};
+            if constexpr (GROUPED != 0) {
+                gt = grouped_tile<GATHER>(t, num_m, num_n, M, ga);
+            } else if constexpr (kGather) {
                 int gblock;
                 gather_tile_coords<GATHER>(t, num_m, num_n, ga.rank, ga.world, ga.rows_per_rank / GBLK, mt, nt, gblock);
             } else {
-                tile_coords(t, num_m, num_n, mt, nt);
+                tile_coords(t % num_mn, num_m, num_n, mt, nt);
             }
-            const int m0 = mt * BM, n0 = nt * BN;
+            const int m0 = GROUPED != 0 ? gt.c_row0 : mt * BM, n0 = GROUPED != 0 ? gt.n0 : nt * BN;
             const bool got = mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS);
             if (epi_bar_or(!got)) {
                 if (leader && !*abort_flag) report_status(status, kStatusTimeout | (4 << 8));
@@ -587,7 +652,7 @@ bool make_tmap(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt, int elem
 
 template <bool A_MN, bool B_MN, bool OUT_F32>
 cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, int M, int N, int K,
-                   int accumulate, int* status, int num_sms, cudaStream_t stream) {
+                   int accumulate, int* status, int num_sms, cudaStream_t stream, int k_splits = 1) {
     auto kern = gemm_kernel<A_MN, B_MN, OUT_F32>;
     static bool configured = false;
     if (!configured) {
@@ -595,9 +660,17 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    const int num_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int num_kb = (K + BK - 1) / BK;
+    if (k_splits > num_kb) k_splits = num_kb;
+    if (k_splits > 1) {                       // no empty splits: ceil(num_kb / ceil(num_kb / splits))
+        const int per = (num_kb + k_splits - 1) / k_splits;
+        k_splits = (num_kb + per - 1) / per;
+    }
+    if (k_splits < 1) k_splits = 1;
+    const int num_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * k_splits;
     const int grid = num_tiles < num_sms ? num_tiles : num_sms;
-    kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tc, M, N, K, accumulate, status, PeerOut{}, GatherArgs{});
+    kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tc, M, N, K, (accumulate & 1) | (k_splits << 8), status,
+                                                    PeerOut{}, GatherArgs{});
     return cudaGetLastError();
 }
 
@@ -606,13 +679,14 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
 const char* gemm_bf16_tcgen05(const void* a, const void* b, void* c, int M, int N, int K, bool a_mn, bool b_mn,
                               bool out_f32, bool accumulate, int* status, int num_sms, cudaStream_t stream) {
     return gemm_bf16_tcgen05_view(a, 0, 0, b, 0, 0, c, 0, 0, M, N, K, a_mn, b_mn, out_f32, accumulate, status, num_sms,
-                                  stream);
+                                  stream, 1);
 }
 
 const char* gemm_bf16_tcgen05_view(const void* a, long long lda, long long a_rows, const void* b, long long ldb,
                                    long long b_rows, void* c, long long ldc, long long c_rows, int M, int N, int K,
                                    bool a_mn, bool b_mn, bool out_f32, bool accumulate, int* status, int num_sms,
-                                   cudaStream_t stream) {
+                                   cudaStream_t stream, int k_splits) {
+    if (k_splits > 1 && !accumulate) return "gemm: split-K needs accumulate (a zeroed or meaningful output)";
     CUtensorMap ta, tb, tc;
     bool ok = true;
     g_tmap_err[0] = 0;
@@ -628,7 +702,7 @@ const char* gemm_bf16_tcgen05_view(const void* a, long long lda, long long a_row
     if (!ok) return g_tmap_err;
     cudaError_t e;
     const int acc = accumulate ? 1 : 0;
-#define FS2_LAUNCH(AM, BMN, F32) e = launch<AM, BMN, F32>(ta, tb, tc, M, N, K, acc, status, num_sms, stream)
+#define FS2_LAUNCH(AM, BMN, F32) e = launch<AM, BMN, F32>(ta, tb, tc, M, N, K, acc, status, num_sms, stream, k_splits)
     if (!a_mn && !b_mn) { if (out_f32) FS2_LAUNCH(false, false, true); else FS2_LAUNCH(false, false, false); }
     else if (!a_mn && b_mn) { if (out_f32) FS2_LAUNCH(false, true, true); else FS2_LAUNCH(false, true, false); }
     else if (a_mn && !b_mn) { if (out_f32) FS2_LAUNCH(true, false, true); else FS2_LAUNCH(true, false, false); }
@@ -731,6 +805,90 @@ const char* gemm_reduce_scatter_bf16_tcgen05(const void* a, const void* b, float
     const int num_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int grid = num_tiles < num_sms ? num_tiles : num_sms;
     kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, ta, M, N, K, 0, status, po, GatherArgs{});
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+}
+
+// Grouped GEMM for mixture-of-experts layers in ONE launch, with every size that depends on the routing read from
+// device memory. `a` is the expert-sorted activation buffer [rows_cap, K] whose per-expert row ranges are padded to
+// multiples of 128 (padding rows are zero); m-tile i covers rows [tile_row0[i], +128) and belongs to expert
+// tile_expert[i]; `b` holds all experts' weights, [E, N, K] (K-major) or [E, K, N] (`b_mn`); c = [rows_cap, N] bf16.
+const char* gemm_grouped_bf16_tcgen05(const void* a, const void* b, void* c, int rows_cap, int N, int K, bool b_mn,
+                                      int experts, const int* tile_row0, const int* tile_expert,
+                                      const int* num_m_tiles, int max_m_tiles, int* status, int num_sms,
+                                      cudaStream_t stream) {
+    if (rows_cap <= 0 || N <= 0 || K <= 0 || experts <= 0 || max_m_tiles <= 0) return "gemm_grouped: bad sizes";
+    CUtensorMap ta, tb, tc;
+    g_tmap_err[0] = 0;
+    if (!make_tmap(&ta, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_cap, K, BM, BK) ||
+        !(b_mn ? make_tmap(&tb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, static_cast<uint64_t>(experts) * K, N, BK, 64)
+               : make_tmap(&tb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, static_cast<uint64_t>(experts) * N, K, BN, BK)) ||
+        !make_tmap(&tc, c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_cap, N, 128, 64))
+        return g_tmap_err;
+    GatherArgs ga{};
+    ga.tile_row0 = tile_row0;
+    ga.tile_expert = tile_expert;
+    ga.num_m_tiles = num_m_tiles;
+    ga.group_rows_b = b_mn ? K : N;
+    ga.experts = experts;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_kernel<false, false, false, false, 3>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(gemm_kernel<false, true, false, false, 3>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return cudaGetErrorString(e);
+        configured = true;
+    }
+    const long long max_tiles = static_cast<long long>(max_m_tiles) * ((N + BN - 1) / BN);
+    const int grid = max_tiles < num_sms ? static_cast<int>(max_tiles) : num_sms;
+    if (b_mn)
+        gemm_kernel<false, true, false, false, 3><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(
+            ta, tb, tc, rows_cap, N, K, 0, status, PeerOut{}, ga);
+    else
+        gemm_kernel<false, false, false, false, 3><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(
+            ta, tb, tc, rows_cap, N, K, 0, status, PeerOut{}, ga);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+}
+
+// Weight gradients of all experts in one launch: dw[e] [M, N] = x[rows of e]^T @ dy[rows of e], the row range of
+// expert e being [offsets[e], offsets[e + 1]) (device array, multiples of 128, never empty). x: [rows, M], dy: [rows, N].
+const char* gemm_grouped_wgrad_bf16_tcgen05(const void* x, const void* dy, void* dw, bool out_f32, int rows, int M,
+                                            int N, int experts, const int* offsets, int* status, int num_sms,
+                                            cudaStream_t stream) {
+    if (rows <= 0 || M <= 0 || N <= 0 || experts <= 0) return "gemm_grouped_wgrad: bad sizes";
+    if (M % BM) return "gemm_grouped_wgrad: the per-expert output height must be a multiple of 128";
+    CUtensorMap ta, tb, tc;
+    g_tmap_err[0] = 0;
+    const uint64_t crow = static_cast<uint64_t>(experts) * M;
+    if (!make_tmap(&ta, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, M, BK, 64) ||
+        !make_tmap(&tb, dy, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, N, BK, 64) ||
+        !(out_f32 ? make_tmap(&tc, dw, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, crow, N, 128, 32)
+                  : make_tmap(&tc, dw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, crow, N, 128, 64)))
+        return g_tmap_err;
+    GatherArgs ga{};
+    ga.group_offsets = offsets;
+    ga.experts = experts;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_kernel<true, true, false, false, 4>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(gemm_kernel<true, true, true, false, 4>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return cudaGetErrorString(e);
+        configured = true;
+    }
+    const long long tiles = static_cast<long long>(experts) * (M / BM) * ((N + BN - 1) / BN);
+    const int grid = tiles < num_sms ? static_cast<int>(tiles) : num_sms;
+    if (out_f32)
+        gemm_kernel<true, true, true, false, 4><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tc, M, N, rows, 0,
+                                                                                           status, PeerOut{}, ga);
+    else
+        gemm_kernel<true, true, false, false, 4><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tc, M, N, rows, 0,
+                                                                                            status, PeerOut{}, ga);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }

@@ -17,11 +17,13 @@ const char* gemm_bf16_tcgen05(const void* a, const void* b, void* c, int M, int 
 // than the row length, so that rows overlap in memory (a strided 1-D convolution over a channels-last signal is
 // A[r, :] = x[r * stride * C : r * stride * C + k * C]). `a_rows`/`b_rows`/`c_rows` (0 = all) give the number of
 // rows that exist in memory: tiles beyond them read zeros and are not written. With `accumulate` the output tile is
-// added (TMA reduce-add), which also sums rows of C that overlap.
+// added (TMA reduce-add), which also sums rows of C that overlap. `k_splits` > 1 (needs `accumulate`) cuts the
+// reduction dimension into that many ranges handled by different CTAs: for long-K, small-output products such as the
+// weight gradient of a convolution.
 const char* gemm_bf16_tcgen05_view(const void* a, long long lda, long long a_rows, const void* b, long long ldb,
                                    long long b_rows, void* c, long long ldc, long long c_rows, int M, int N, int K,
                                    bool a_mn, bool b_mn, bool out_f32, bool accumulate, int* status, int num_sms,
-                                   cudaStream_t stream);
+                                   cudaStream_t stream, int k_splits = 1);
 
 // GEMM fused with the all-gather of one operand (see gemm_tcgen05.cu): `shards[r]` is rank r's [rows_per_rank, K]
 // bf16 shard (peer mapping), `gathered` local scratch for the whole operand, `flags` one word per tile-height block
@@ -44,5 +46,14 @@ const char* gemm_reduce_scatter_bf16_tcgen05(const void* a, const void* b, float
 const char* gemm_scatter_bf16_tcgen05(const void* a, const void* b, bool b_mn, void* const* peer_slices, int world,
                                       int rank, int rows_per_rank, int M, int N, int K, int* status, int num_sms,
                                       cudaStream_t stream);
+
+// Grouped (mixture-of-experts) GEMMs with device-resident routing tables; see gemm_tcgen05.cu.
+const char* gemm_grouped_bf16_tcgen05(const void* a, const void* b, void* c, int rows_cap, int N, int K, bool b_mn,
+                                      int experts, const int* tile_row0, const int* tile_expert,
+                                      const int* num_m_tiles, int max_m_tiles, int* status, int num_sms,
+                                      cudaStream_t stream);
+const char* gemm_grouped_wgrad_bf16_tcgen05(const void* x, const void* dy, void* dw, bool out_f32, int rows, int M,
+                                            int N, int experts, const int* offsets, int* status, int num_sms,
+                                            cudaStream_t stream);
 
 }  // namespace fs2

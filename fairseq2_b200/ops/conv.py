@@ -55,7 +55,7 @@ class _Conv1dCL(torch.autograd.Function):
         rows_ok = (B * L * C - k * C) // (stride * C) + 1         # rows that lie fully inside the storage
         y = torch.empty((R, C_out), device=x.device, dtype=x.dtype)
         ext.gemm_bf16_view(x, min(rows_ok, R), stride * C, False, w2, C_out, k * C, False, y, R, C_out, R, C_out, k * C,
-                           False)
+                           False, 1)
         ctx.save_for_backward(x, w2)
         ctx.meta = (B, L, C, C_out, k, stride, R, min(rows_ok, R))
         return y.view(B, L // stride, C_out)
@@ -69,16 +69,20 @@ class _Conv1dCL(torch.autograd.Function):
         dx = dw = None
         if ctx.needs_input_grad[1]:
             # dW2 [C_out, k*C] = dY^T [C_out, R] @ patches [R, k*C]; rows of the patch view beyond rows_ok read zeros
-            dw2 = torch.empty((C_out, k * C), device=x.device, dtype=torch.float32)
+            # a long reduction (all output positions) into a small matrix: split K so that every SM has a tile
+            tiles = ((C_out + 127) // 128) * ((k * C + 255) // 256)
+            splits = max(1, min(R // 2048, (2 * 148 + tiles - 1) // tiles))
+            dw2 = torch.zeros((C_out, k * C), device=x.device, dtype=torch.float32)
             ext.gemm_bf16_view(dy2, R, C_out, True, x, rows_ok, stride * C, True, dw2, C_out, k * C, C_out, k * C, R,
-                               False)
+                               True, splits)
             dw = dw2.view(C_out, k, C).permute(0, 2, 1).to(w2.dtype)
         if ctx.needs_input_grad[0]:
             # d patches [R, k*C] = dY [R, C_out] @ W2 [C_out, k*C], reduce-added through the overlapping-row view
-            dxf = torch.zeros((B * L, C), device=x.device, dtype=torch.float32)
-            ext.gemm_bf16_view(dy2, R, C_out, False, w2, C_out, k * C, True, dxf, rows_ok, stride * C, R, k * C, C_out,
-                               True)
-            dx = dxf.view(B, L, C).to(x.dtype)
+            # overlapping taps add at most ceil(k / stride) bf16 partial sums per element
+            dx2 = torch.zeros((B * L, C), device=x.device, dtype=x.dtype)
+            ext.gemm_bf16_view(dy2, R, C_out, False, w2, C_out, k * C, True, dx2, rows_ok, stride * C, R, k * C, C_out,
+                               True, 1)
+            dx = dx2.view(B, L, C)
         return dx, dw, None
 
 
