@@ -593,6 +593,87 @@ void moe_ep_pull(const std::vector<int64_t>& ptrs, int64_t rank, int64_t outbox_
     g_launches += 1;
 }
 
+// Dispatch into the 128-row padded, expert-sorted layout of the single-launch grouped GEMM. Nothing is read back
+// to the host: the buffer is sized for the worst case (T * k + 128 * E rows) and the tile tables stay on the device.
+// returns (routed [cap, D] (padding rows zero), src_row [cap] (-1 on padding rows), inv [T, k], offsets [E + 1],
+//          tile_row0 [cap / 128], tile_expert [cap / 128], num_tiles [1])
+std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor> moe_dispatch_padded(const Tensor& x,
+                                                                                   const Tensor& expert_ids,
+                                                                                   const Tensor& gates,
+                                                                                   const Tensor& counts,
+                                                                                   bool scale_by_gate) {
+    TORCH_CHECK(x.is_cuda() && is_bf16(x) && x.dim() == 2 && x.is_contiguous() && x.size(1) % 8 == 0 && aligned16(x),
+                "moe_dispatch_padded: x must be a contiguous bf16 [T, D] CUDA tensor with D % 8 == 0");
+    TORCH_CHECK(expert_ids.scalar_type() == at::kInt && expert_ids.is_contiguous() && expert_ids.dim() == 2 &&
+                    expert_ids.size(0) == x.size(0) && gates.scalar_type() == at::kFloat && gates.is_contiguous() &&
+                    gates.sizes() == expert_ids.sizes() && counts.scalar_type() == at::kInt && counts.is_contiguous(),
+                "moe_dispatch_padded: bad routing tensors");
+    const int64_t T = x.size(0), D = x.size(1), k = expert_ids.size(1), E = counts.numel();
+    TORCH_CHECK(E >= 1 && E <= 256, "moe_dispatch_padded: up to 256 experts are supported");
+    const int64_t cap = (T * k + 127) / 128 * 128 + 128 * E;
+    c10::cuda::CUDAGuard guard(x.device());
+    auto iopt = x.options().dtype(at::kInt);
+    Tensor offsets = at::empty({E + 1}, iopt), cursor = at::empty({E}, iopt);
+    Tensor tile_row0 = at::empty({cap / 128}, iopt), tile_expert = at::empty({cap / 128}, iopt);
+    Tensor num_tiles = at::empty({1}, iopt);
+    Tensor routed = at::zeros({cap, D}, x.options()), src_row = at::full({cap}, -1, iopt), inv = at::empty({T, k}, iopt);
+    fs2::moe_grouped_layout(counts.data_ptr<int>(), static_cast<int>(E), offsets.data_ptr<int>(), cursor.data_ptr<int>(),
+                            tile_row0.data_ptr<int>(), tile_expert.data_ptr<int>(), num_tiles.data_ptr<int>(),
+                            stream_of(x));
+    fs2::moe_dispatch(x.data_ptr(), expert_ids.data_ptr<int>(), gates.data_ptr<float>(), offsets.data_ptr<int>(),
+                      cursor.data_ptr<int>(), routed.data_ptr(), src_row.data_ptr<int>(), inv.data_ptr<int>(),
+                      static_cast<int>(T), static_cast<int>(k), static_cast<int>(D), scale_by_gate, stream_of(x));
+    g_launches += 2;
+    return {routed, src_row, inv, offsets, tile_row0, tile_expert, num_tiles};
+}
+
+// y [cap, N] = grouped(x [cap, K], w): w is [E, K, N] (`w_kn`) or [E, N, K]; one launch, no host-side sizes.
+Tensor grouped_gemm(const Tensor& x, const Tensor& w, bool w_kn, const Tensor& tile_row0, const Tensor& tile_expert,
+                    const Tensor& num_tiles) {
+    TORCH_CHECK(x.is_cuda() && is_bf16(x) && x.dim() == 2 && x.is_contiguous() && aligned16(x) && is_bf16(w) &&
+                    w.dim() == 3 && w.is_contiguous() && aligned16(w),
+                "grouped_gemm: x [rows, K] and w [E, ., .] must be contiguous bf16 CUDA tensors");
+    const int64_t rows = x.size(0), K = x.size(1), E = w.size(0);
+    const int64_t N = w_kn ? w.size(2) : w.size(1);
+    TORCH_CHECK((w_kn ? w.size(1) : w.size(2)) == K && K % 8 == 0 && N % 8 == 0 && rows % 128 == 0,
+                "grouped_gemm: shape mismatch (K, N multiples of 8; rows a multiple of 128)");
+    TORCH_CHECK(tile_row0.scalar_type() == at::kInt && tile_expert.scalar_type() == at::kInt &&
+                    num_tiles.scalar_type() == at::kInt && tile_row0.numel() >= rows / 128 &&
+                    tile_expert.numel() >= rows / 128 && num_tiles.numel() == 1,
+                "grouped_gemm: bad tile tables");
+    check_status();
+    c10::cuda::CUDAGuard guard(x.device());
+    Tensor y = at::empty({rows, N}, x.options());
+    const char* err = fs2::gemm_grouped_bf16_tcgen05(
+        x.data_ptr(), w.data_ptr(), y.data_ptr(), static_cast<int>(rows), static_cast<int>(N), static_cast<int>(K), w_kn,
+        static_cast<int>(E), tile_row0.data_ptr<int>(), tile_expert.data_ptr<int>(), num_tiles.data_ptr<int>(),
+        static_cast<int>(rows / 128), status_dev_ptr(), num_sms(x), stream_of(x));
+    TORCH_CHECK(err == nullptr, "grouped_gemm: ", err);
+    g_launches += 1;
+    return y;
+}
+
+// dw [E, M, N] (fp32) = per-expert x^T @ dy over the padded row ranges given by offsets [E + 1].
+Tensor grouped_gemm_wgrad(const Tensor& x, const Tensor& dy, const Tensor& offsets) {
+    TORCH_CHECK(x.is_cuda() && is_bf16(x) && is_bf16(dy) && x.dim() == 2 && dy.dim() == 2 && x.is_contiguous() &&
+                    dy.is_contiguous() && x.size(0) == dy.size(0) && aligned16(x) && aligned16(dy),
+                "grouped_gemm_wgrad: x [rows, M] and dy [rows, N] must be contiguous bf16 CUDA matrices");
+    const int64_t rows = x.size(0), M = x.size(1), N = dy.size(1), E = offsets.numel() - 1;
+    TORCH_CHECK(offsets.scalar_type() == at::kInt && E >= 1 && M % 128 == 0 && N % 8 == 0,
+                "grouped_gemm_wgrad: offsets must be int32 [E + 1]; M a multiple of 128, N of 8");
+    check_status();
+    c10::cuda::CUDAGuard guard(x.device());
+    Tensor dw = at::empty({E, M, N}, x.options().dtype(at::kFloat));
+    const char* err = fs2::gemm_grouped_wgrad_bf16_tcgen05(x.data_ptr(), dy.data_ptr(), dw.data_ptr(), true,
+                                                           static_cast<int>(rows), static_cast<int>(M),
+                                                           static_cast<int>(N), static_cast<int>(E),
+                                                           offsets.data_ptr<int>(), status_dev_ptr(), num_sms(x),
+                                                           stream_of(x));
+    TORCH_CHECK(err == nullptr, "grouped_gemm_wgrad: ", err);
+    g_launches += 1;
+    return dw;
+}
+
 // y[t] (+)= sum_j gate[t, j] * routed[inv[t, j]]
 void moe_combine(const Tensor& routed, const Tensor& inv, const std::optional<Tensor>& gates, Tensor y,
                  bool accumulate) {
@@ -1180,6 +1261,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("moe_route", &moe_route);
     m.def("moe_dispatch", &moe_dispatch);
     m.def("moe_combine", &moe_combine);
+    m.def("moe_dispatch_padded", &moe_dispatch_padded);
+    m.def("grouped_gemm", &grouped_gemm);
+    m.def("grouped_gemm_wgrad", &grouped_gemm_wgrad);
     m.def("w2v_contrastive_fwd", &w2v_contrastive_fwd);
     m.def("w2v_contrastive_bwd", &w2v_contrastive_bwd);
     m.def("w2v_quantize_fwd", &w2v_quantize_fwd);

@@ -108,6 +108,31 @@ __global__ void moe_offsets_kernel(const int* __restrict__ counts, int* __restri
     }
 }
 
+// Layout of the expert-sorted activation buffer for the grouped GEMM: every expert's row range is padded to a
+// multiple of 128 rows (at least 128, so no expert is empty), offsets[e] is its first row, tile_row0/tile_expert list
+// the 128-row tiles in order, num_tiles[0] their count. One block; E <= 256.
+__global__ void moe_grouped_layout_kernel(const int* __restrict__ counts, int E, int* __restrict__ offsets,
+                                          int* __restrict__ cursor, int* __restrict__ tile_row0,
+                                          int* __restrict__ tile_expert, int* __restrict__ num_tiles) {
+    if (threadIdx.x == 0) {
+        int row = 0, tile = 0;
+        for (int e = 0; e < E; ++e) {
+            offsets[e] = row;
+            cursor[e] = 0;
+            int padded = (counts[e] + 127) / 128 * 128;
+            if (padded == 0) padded = 128;
+            for (int r = 0; r < padded; r += 128) {
+                tile_row0[tile] = row + r;
+                tile_expert[tile] = e;
+                ++tile;
+            }
+            row += padded;
+        }
+        offsets[E] = row;
+        num_tiles[0] = tile;
+    }
+}
+
 __global__ void __launch_bounds__(256) moe_dispatch_kernel(const __nv_bfloat16* __restrict__ x,
                                                            const int* __restrict__ expert_ids,
                                                            const float* __restrict__ gates,
@@ -338,6 +363,11 @@ void moe_route(const void* logits, bool bf16, int T, int E, int k, bool softmax_
 
 void moe_offsets(const int* counts, int* offsets, int* cursor, int E, cudaStream_t st) {
     moe_offsets_kernel<<<1, 32, 0, st>>>(counts, offsets, cursor, E);
+}
+
+void moe_grouped_layout(const int* counts, int E, int* offsets, int* cursor, int* tile_row0, int* tile_expert,
+                        int* num_tiles, cudaStream_t st) {
+    moe_grouped_layout_kernel<<<1, 32, 0, st>>>(counts, E, offsets, cursor, tile_row0, tile_expert, num_tiles);
 }
 
 void moe_dispatch(const void* x, const int* expert_ids, const float* gates, const int* offsets, int* cursor, void* out,

@@ -18,6 +18,12 @@ void moe_route(const void* logits, bool bf16, int T, int E, int k, bool softmax_
 // offsets[e] = exclusive prefix sum of counts; cursor[e] = 0. One block.
 void moe_offsets(const int* counts, int* offsets, int* cursor, int E, cudaStream_t st);
 
+// Padded layout for the single-launch grouped GEMM: offsets[E + 1] (row ranges padded to multiples of 128, never
+// empty), cursor[E] = 0, the list of 128-row tiles (tile_row0, tile_expert; at most rows / 128 + E entries) and their
+// number. One block.
+void moe_grouped_layout(const int* counts, int E, int* offsets, int* cursor, int* tile_row0, int* tile_expert,
+                        int* num_tiles, cudaStream_t st);
+
 // Dispatch: row (t, j) goes to slot p = offsets[e] + (arrival order within e); out[p, :] = x[t, :] * gate,
 // src_row[p] = t, inv[t*k + j] = p. bf16 rows of D elements (D % 8 == 0).
 void moe_dispatch(const void* x, const int* expert_ids, const float* gates, const int* offsets, int* cursor,

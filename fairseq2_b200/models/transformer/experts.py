@@ -20,7 +20,7 @@ from torch.nn import Module, Parameter, SiLU
 
 from fairseq2_b200.gang import Gang
 from fairseq2_b200.models.transformer.ffn import FeedForwardNetwork, GLUFeedForwardNetwork
-from fairseq2_b200.ops.grouped_gemm import grouped_mm
+from fairseq2_b200.ops.grouped_gemm import grouped_mm, grouped_mm_device, grouped_mm_device_supported
 from fairseq2_b200.ops.tensor_parallel import reduce
 from fairseq2_b200.typing import DataType, Device
 
@@ -60,6 +60,14 @@ class GroupedExpertNetwork(ExpertNetwork):
     def forward(self, x: Tensor, group_sizes: list[int]) -> Tensor:
         h = self.activation(grouped_mm(x, self.gate_proj, group_sizes)) * grouped_mm(x, self.inner_proj, group_sizes)
         return grouped_mm(h, self.output_proj, group_sizes)
+
+    def supports_padded_layout(self, x: Tensor) -> bool:
+        return all(grouped_mm_device_supported(x, w) for w in (self.gate_proj, self.inner_proj, self.output_proj))
+
+    def forward_padded(self, x: Tensor, layout: tuple[Tensor, Tensor, Tensor, Tensor]) -> Tensor:
+        """``x`` in the 128-row padded expert-sorted layout: three single-launch grouped GEMMs, no host-side sizes."""
+        h = self.activation(grouped_mm_device(x, self.gate_proj, layout)) * grouped_mm_device(x, self.inner_proj, layout)
+        return grouped_mm_device(h, self.output_proj, layout)
 
 
 class TPShardedExpertNetwork(ExpertNetwork):
@@ -169,8 +177,13 @@ class MoE(FeedForwardNetwork):
         if moe_ops.moe_kernels_available(x, logits):
             # fused top-k gate + histogram, gather/scale into expert order, experts, gather back per token
             ids, gates, counts = moe_ops.moe_route(logits, self.top_k)
-            routed_in, src_row, inv = moe_ops.moe_dispatch(x, gates, ids, counts)
-            routed_out = self.experts(routed_in, counts.tolist())
+            if isinstance(self.experts, GroupedExpertNetwork) and self.experts.supports_padded_layout(x):
+                # padded layout + device-resident tile tables: the CPU never waits for the routing result
+                routed_in, src_row, inv, layout = moe_ops.moe_dispatch_padded(x, gates, ids, counts)
+                routed_out = self.experts.forward_padded(routed_in, layout)
+            else:
+                routed_in, src_row, inv = moe_ops.moe_dispatch(x, gates, ids, counts)
+                routed_out = self.experts(routed_in, counts.tolist())
             base = self.shared_expert(x) if self.shared_expert is not None else None
             out = moe_ops.moe_combine(routed_out, inv, src_row, base)
             if self.tp_gang is not None:

@@ -62,3 +62,45 @@ def grouped_mm(x: Tensor, w: Tensor, group_sizes: Sequence[int]) -> Tensor:
     if len(group_sizes) != w.shape[0]:
         raise ValueError(f"`group_sizes` must have one entry per group of `w` ({w.shape[0]}).")
     return _GroupedMM.apply(x, w, tuple(int(n) for n in group_sizes))
+
+
+class _GroupedMMDevice(torch.autograd.Function):
+    """Single-launch grouped GEMM over the 128-row padded layout; all routing-dependent sizes stay on the device."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, w: Tensor, offsets: Tensor, tile_row0: Tensor, tile_expert: Tensor,  # type: ignore[override]
+                num_tiles: Tensor) -> Tensor:
+        from fairseq2_b200.ops._ext import require_ext
+
+        y = require_ext().grouped_gemm(x.contiguous(), w, True, tile_row0, tile_expert, num_tiles)
+        ctx.save_for_backward(x, w, offsets, tile_row0, tile_expert, num_tiles)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):  # type: ignore[override]
+        from fairseq2_b200.ops._ext import require_ext
+
+        ext = require_ext()
+        x, w, offsets, tile_row0, tile_expert, num_tiles = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = ext.grouped_gemm(dy, w, False, tile_row0, tile_expert, num_tiles)      # dy @ w[e]^T: w read as [E, K, N] K-major
+        if ctx.needs_input_grad[1]:
+            dw = ext.grouped_gemm_wgrad(x.contiguous(), dy, offsets).to(w.dtype)          # [E, K, N]
+        return dx, dw, None, None, None, None
+
+
+def grouped_mm_device_supported(x: Tensor, w: Tensor) -> bool:
+    from fairseq2_b200.ops._ext import use_kernels
+
+    return (use_kernels(x, w) and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.dim() == 3
+            and w.shape[1] % 128 == 0 and w.shape[2] % 128 == 0 and w.is_contiguous())
+
+
+def grouped_mm_device(x: Tensor, w: Tensor, layout: tuple[Tensor, Tensor, Tensor, Tensor]) -> Tensor:
+    """``x``: ``[rows, K]`` in the padded expert-sorted layout produced by ``ops.moe.moe_dispatch_padded`` (``layout`` =
+    ``(offsets, tile_row0, tile_expert, num_tiles)``), ``w``: ``[E, K, N]`` -> ``[rows, N]``. One kernel launch per
+    GEMM, no device-to-host copy of the group sizes."""
+    offsets, tile_row0, tile_expert, num_tiles = layout
+    return _GroupedMMDevice.apply(x, w, offsets, tile_row0, tile_expert, num_tiles)

@@ -42,6 +42,32 @@ class _Dispatch(torch.autograd.Function):
         return dx, dgates, None, None
 
 
+class _DispatchPadded(torch.autograd.Function):
+    """``_Dispatch`` into the 128-row padded layout of the single-launch grouped GEMM (padding rows are zero)."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, gates: Tensor, expert_ids: Tensor, counts: Tensor):  # type: ignore[override]
+        ext = require_ext()
+        routed, src_row, inv, offsets, tile_row0, tile_expert, num_tiles = ext.moe_dispatch_padded(
+            x, expert_ids, gates, counts, True)
+        ctx.save_for_backward(x, gates, src_row, inv)
+        ctx.mark_non_differentiable(src_row, inv, offsets, tile_row0, tile_expert, num_tiles)
+        return routed, src_row, inv, offsets, tile_row0, tile_expert, num_tiles
+
+    @staticmethod
+    def backward(ctx, d_routed: Tensor, *_: Tensor):  # type: ignore[override]
+        ext = require_ext()
+        x, gates, src_row, inv = ctx.saved_tensors
+        d_routed = d_routed.contiguous()
+        dx = torch.empty_like(x)
+        ext.moe_combine(d_routed, inv, gates, dx, False)
+        live = src_row >= 0
+        xr = x.index_select(0, src_row.clamp(min=0).long())
+        dslot = (d_routed.float() * xr.float()).sum(dim=1) * live
+        dgates = dslot[inv.long()]
+        return dx, dgates, None, None
+
+
 class _Combine(torch.autograd.Function):
     """``y[t] = base[t] + sum_j routed[inv[t, j]]``."""
 
@@ -60,7 +86,9 @@ class _Combine(torch.autograd.Function):
     def backward(ctx, dy: Tensor):  # type: ignore[override]
         inv, src_row = ctx.saved_tensors
         dy = dy.contiguous()
-        d_routed = dy.index_select(0, src_row.long())
+        d_routed = dy.index_select(0, src_row.clamp(min=0).long())
+        if bool((src_row.numel() > 0)):
+            d_routed = d_routed * (src_row >= 0).unsqueeze(1).to(d_routed.dtype)    # padding rows of the padded layout
         return d_routed, None, None, (dy if ctx.has_base else None)
 
 
@@ -85,6 +113,16 @@ def moe_dispatch(x: Tensor, gates: Tensor, expert_ids: Tensor, counts: Tensor) -
     routed, src_row, inv, _ = _Dispatch.apply(x.contiguous(), gates.float().contiguous(), expert_ids.contiguous(),
                                               counts.contiguous())
     return routed, src_row, inv
+
+
+def moe_dispatch_padded(x: Tensor, gates: Tensor, expert_ids: Tensor, counts: Tensor
+                        ) -> tuple[Tensor, Tensor, Tensor, tuple[Tensor, Tensor, Tensor, Tensor]]:
+    """Like ``moe_dispatch`` but into a buffer whose per-expert row ranges are padded to multiples of 128 rows, with
+    the tile tables the single-launch grouped GEMM needs. Returns ``(routed, src_row, inv, layout)``; nothing is
+    copied to the host."""
+    routed, src_row, inv, offsets, tile_row0, tile_expert, num_tiles = _DispatchPadded.apply(
+        x.contiguous(), gates.float().contiguous(), expert_ids.contiguous(), counts.contiguous())
+    return routed, src_row, inv, (offsets, tile_row0, tile_expert, num_tiles)
 
 
 def moe_combine(routed: Tensor, inv: Tensor, src_row: Tensor, base: Tensor | None = None) -> Tensor:
