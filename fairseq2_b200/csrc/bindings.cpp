@@ -643,7 +643,8 @@ Tensor grouped_gemm(const Tensor& x, const Tensor& w, bool w_kn, const Tensor& t
                 "grouped_gemm: bad tile tables");
     check_status();
     c10::cuda::CUDAGuard guard(x.device());
-    Tensor y = at::empty({rows, N}, x.options());
+    // rows past the last tile (the buffer is sized for the worst case) are never written by the kernel
+    Tensor y = at::zeros({rows, N}, x.options());
     const char* err = fs2::gemm_grouped_bf16_tcgen05(
         x.data_ptr(), w.data_ptr(), y.data_ptr(), static_cast<int>(rows), static_cast<int>(N), static_cast<int>(K), w_kn,
         static_cast<int>(E), tile_row0.data_ptr<int>(), tile_expert.data_ptr<int>(), num_tiles.data_ptr<int>(),
