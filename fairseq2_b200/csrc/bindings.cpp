@@ -329,6 +329,38 @@ std::tuple<Tensor, Tensor, Tensor> layer_norm_bwd(const Tensor& dy, const Tensor
     return {dx, dw, db};
 }
 
+// ------------------------------------------------------- vocabulary-parallel embedding
+Tensor embed_vocab_parallel_fwd(const Tensor& ids, const Tensor& table, int64_t lo, double scale) {
+    TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous() && table.is_cuda() &&
+                    is_bf16(table) && table.dim() == 2 && table.is_contiguous() && table.size(1) % 8 == 0 &&
+                    aligned16(table),
+                "embed_vocab_parallel_fwd: ids must be int64, the table shard a contiguous bf16 [rows, D] with D % 8 == 0");
+    c10::cuda::CUDAGuard guard(table.device());
+    auto shape = ids.sizes().vec();
+    shape.push_back(table.size(1));
+    Tensor out = at::empty(shape, table.options());
+    fs2::embed_vocab_parallel_fwd(ids.data_ptr<int64_t>() ? reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()) : nullptr,
+                                  table.data_ptr(), out.data_ptr(), static_cast<size_t>(ids.numel()),
+                                  static_cast<int>(table.size(1)), lo, table.size(0), static_cast<float>(scale),
+                                  stream_of(table));
+    g_launches += 1;
+    return out;
+}
+
+Tensor embed_vocab_parallel_bwd(const Tensor& ids, const Tensor& dout, int64_t rows, int64_t lo, double scale) {
+    TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous() && dout.is_cuda() &&
+                    is_bf16(dout) && dout.is_contiguous() && dout.size(-1) % 8 == 0 && aligned16(dout) &&
+                    dout.numel() == ids.numel() * dout.size(-1),
+                "embed_vocab_parallel_bwd: bad tensors");
+    c10::cuda::CUDAGuard guard(dout.device());
+    Tensor dtable = at::zeros({rows, dout.size(-1)}, dout.options().dtype(at::kFloat));
+    fs2::embed_vocab_parallel_bwd(reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()), dout.data_ptr(),
+                                  dtable.data_ptr<float>(), static_cast<size_t>(ids.numel()),
+                                  static_cast<int>(dout.size(-1)), lo, rows, static_cast<float>(scale), stream_of(dout));
+    g_launches += 1;
+    return dtable;
+}
+
 // --------------------------------------------------------------------- SwiGLU
 Tensor swiglu_fwd(const Tensor& gu) {
     TORCH_CHECK(gu.is_cuda() && is_bf16(gu) && gu.dim() == 2 && gu.is_contiguous() && gu.size(1) % 16 == 0 &&
@@ -1262,6 +1294,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("moe_route", &moe_route);
     m.def("moe_dispatch", &moe_dispatch);
     m.def("moe_combine", &moe_combine);
+    m.def("embed_vocab_parallel_fwd", &embed_vocab_parallel_fwd);
+    m.def("embed_vocab_parallel_bwd", &embed_vocab_parallel_bwd);
     m.def("moe_dispatch_padded", &moe_dispatch_padded);
     m.def("grouped_gemm", &grouped_gemm);
     m.def("grouped_gemm_wgrad", &grouped_gemm_wgrad);

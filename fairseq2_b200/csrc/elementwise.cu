@@ -341,6 +341,49 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restri
     }
 }
 
+// ------------------------------------------------------ vocabulary-parallel embedding
+// This rank holds rows [lo, lo + rows) of the table. out[t] = table[ids[t] - lo] for ids in range, else 0 (the other
+// ranks contribute those rows; the sum over ranks is the lookup). One warp per token.
+__global__ void __launch_bounds__(256) embed_vocab_parallel_fwd_kernel(const long long* __restrict__ ids,
+                                                                       const __nv_bfloat16* __restrict__ table,
+                                                                       __nv_bfloat16* __restrict__ out, size_t tokens,
+                                                                       int D, long long lo, long long rows, float scale) {
+    const size_t t = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (t >= tokens) return;
+    const long long r = ids[t] - lo;
+    const bool mine = r >= 0 && r < rows;
+    for (int c = lane * 8; c < D; c += 256) {
+        float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (mine) {
+            load8(table + static_cast<size_t>(r) * D, c, f);
+            if (scale != 1.f) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] *= scale;
+            }
+        }
+        store8(out + t * D, c, f);
+    }
+}
+
+// dtable[ids[t] - lo] += scale * dout[t] for ids in range (fp32 accumulation buffer, atomics: tokens repeat).
+__global__ void __launch_bounds__(256) embed_vocab_parallel_bwd_kernel(const long long* __restrict__ ids,
+                                                                       const __nv_bfloat16* __restrict__ dout,
+                                                                       float* __restrict__ dtable, size_t tokens, int D,
+                                                                       long long lo, long long rows, float scale) {
+    const size_t t = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (t >= tokens) return;
+    const long long r = ids[t] - lo;
+    if (r < 0 || r >= rows) return;
+    for (int c = lane * 8; c < D; c += 256) {
+        float f[8];
+        load8(dout + t * D, c, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) atomicAdd(dtable + static_cast<size_t>(r) * D + c + e, f[e] * scale);
+    }
+}
+
 // ------------------------------------------------------------- cross-entropy
 // One block per row. logits (bf16, [rows, V]) are overwritten with
 // (softmax - onehot) * mask[row]; row_loss[row] = (lse - logit[target]) * mask.
@@ -614,6 +657,22 @@ void rope_inplace(void* x, const float* freqs, const int* pos, size_t tokens, in
     rope_kernel<<<stream_grid(work, 256, num_sms), 256, 0, st>>>(static_cast<__nv_bfloat16*>(x), freqs, pos, tokens,
                                                                   heads, D, tstride, hstride, max_pos,
                                                                   inverse ? -1.f : 1.f);
+}
+
+void embed_vocab_parallel_fwd(const long long* ids, const void* table, void* out, size_t tokens, int D, long long lo,
+                              long long rows, float scale, cudaStream_t st) {
+    if (tokens == 0) return;
+    const unsigned blocks = static_cast<unsigned>((tokens * 32 + 255) / 256);
+    embed_vocab_parallel_fwd_kernel<<<blocks, 256, 0, st>>>(ids, static_cast<const __nv_bfloat16*>(table),
+                                                            static_cast<__nv_bfloat16*>(out), tokens, D, lo, rows, scale);
+}
+
+void embed_vocab_parallel_bwd(const long long* ids, const void* dout, float* dtable, size_t tokens, int D, long long lo,
+                              long long rows, float scale, cudaStream_t st) {
+    if (tokens == 0) return;
+    const unsigned blocks = static_cast<unsigned>((tokens * 32 + 255) / 256);
+    embed_vocab_parallel_bwd_kernel<<<blocks, 256, 0, st>>>(ids, static_cast<const __nv_bfloat16*>(dout), dtable, tokens,
+                                                            D, lo, rows, scale);
 }
 
 void ce_fwd_bwd(void* logits, const long long* targets, const float* mask, float* row_loss, int rows, int V,

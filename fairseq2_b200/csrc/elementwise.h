@@ -20,6 +20,12 @@ void layer_norm_fwd(const void* x, const void* w, const void* b, void* y, float*
 void layer_norm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx,
                     float* dw_part, float* db_part, float* dw, float* db, int rows, int D, bool bf16, int num_sms,
                     cudaStream_t st, const void* b_for_gelu = nullptr);
+// Vocabulary-parallel embedding shard [rows, D] covering ids [lo, lo + rows): forward writes the row (times `scale`)
+// or zeros; backward accumulates `scale * dout` into an fp32 [rows, D] buffer. D a multiple of 8.
+void embed_vocab_parallel_fwd(const long long* ids, const void* table, void* out, size_t tokens, int D, long long lo,
+                              long long rows, float scale, cudaStream_t st);
+void embed_vocab_parallel_bwd(const long long* ids, const void* dout, float* dtable, size_t tokens, int D, long long lo,
+                              long long rows, float scale, cudaStream_t st);
 void swiglu_fwd(const void* gu, void* y, size_t rows, int F, int num_sms, cudaStream_t st);
 void swiglu_bwd(const void* dy, const void* gu, void* dgu, size_t rows, int F, int num_sms, cudaStream_t st);
 void rope_inplace(void* x, const float* freqs, const int* pos, size_t tokens, int heads, int D, size_t tstride,

@@ -91,12 +91,9 @@ class VocabShardedEmbedding(Embedding):
         return m
 
     def forward(self, x: Tensor) -> Tensor:
-        lo = self.gang.rank * self.sharded_num_embeddings
-        hi = lo + self.sharded_num_embeddings
-        oob = (x < lo) | (x >= hi)
-        local = (x - lo).masked_fill(oob, 0)
-        y = F.embedding(local, self.weight)
-        y = y.masked_fill(oob.unsqueeze(-1), 0.0)
+        from fairseq2_b200.ops.embedding import embed_vocab_parallel
+
+        y = embed_vocab_parallel(x, self.weight, self.gang.rank * self.sharded_num_embeddings)
         return reduce(y, self.gang)
 
     def to_embedding(self, device: Device | None = None) -> StandardEmbedding:

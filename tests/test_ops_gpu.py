@@ -603,3 +603,21 @@ def test_grouped_gemm_single_launch_padded_layout() -> None:
     for j in range(k):
         dxr += gates[:, j:j + 1] * rr.grad[inv[:, j].long()]
     assert _rel_err(xin.grad.float(), dxr) < 1.5e-2
+
+
+@pytest.mark.gpu
+def test_embed_vocab_parallel_kernel() -> None:
+    from fairseq2_b200.ops.embedding import embed_vocab_parallel, embed_vocab_parallel_reference
+
+    torch.manual_seed(0)
+    V, D, lo = 1000, 256, 250
+    shard = torch.randn(250, D, device="cuda", dtype=torch.bfloat16).requires_grad_(True)
+    ids = torch.randint(0, V, (7, 123), device="cuda")
+    out = embed_vocab_parallel(ids, shard, lo)
+    sr = shard.detach().float().requires_grad_(True)
+    ref = embed_vocab_parallel_reference(ids, sr, lo)
+    assert torch.equal(out.float(), ref.detach())
+    g = torch.randn_like(out)
+    out.backward(g)
+    ref.backward(g.float())
+    assert _rel_err(shard.grad.float(), sr.grad) < 1e-2
