@@ -81,10 +81,12 @@ def main() -> None:
     cases = args.cases.split(",")
     want = lambda c: "all" in cases or c in cases  # noqa: E731
 
+    want_tp = "all" in cases or "tp_mlp" in cases
     n = (args.unit_params // W + 2047) // 2048 * 2048            # shard elements
     T = args.tokens
     arena_bytes = ((W + 1) * n * 2 + (128 << 20) + 2 * (T // W) * 4096 * 4 + 2 * T * 4096 * 2 + 3 * (T + 64) * 4096 * 2
-                   + 3 * (14336 + 64) * 4096 * 2 + (64 << 20))
+                   + 3 * (14336 + 64) * 4096 * 2 + (64 << 20)
+                   + ((3 * T + 2 * (T // W)) * 8192 * 2 + (64 << 20) if want_tp else 0))
     arena = SymmetricArena(base, arena_bytes)
     ext = arena.ext
     epoch = {"v": 0}
@@ -257,6 +259,57 @@ def main() -> None:
         gemm_only = _time(lambda: gemm_nt(x, wg), barrier, args.iters)
         emit("fsdp_unshard_allgather_gemm_fused", ms, flops=2.0 * T * D * K_ffn, nvlink_bytes=(W - 1) / W * K_ffn * D * 2,
              baseline_ms=nccl, gemm_alone_ms=round(gemm_only, 4), copier_ctas=ncopy_b)
+
+    if want("tp_mlp") and T % (W * 128) == 0:
+        # LLaMA-3-70B feed-forward block under tensor parallelism: D = 8192, F = 28672 / W per rank, T tokens.
+        # ours: token-sharded activations, all-gather inside the column GEMM, reduce-scatter inside the row GEMM,
+        # same kernels with swapped roles in the backward pass. baseline: the Megatron formulation the reference
+        # uses (replicated activations, GEMMs + one NCCL all-reduce forward and one backward), our GEMM kernel.
+        from fairseq2_b200.ops.fused_collective import SequenceParallelLinears
+
+        D2, F2 = 8192, 28672
+        if F2 % W == 0 and (F2 // W) % 8 == 0:
+            Fl, Tl = F2 // W, T // W
+            sp = SequenceParallelLinears(arena, Tl, D2)
+            w1 = (torch.randn(Fl, D2, device=dev) * D2 ** -0.5).to(torch.bfloat16).requires_grad_(True)
+            w2 = (torch.randn(D2, Fl, device=dev) * F2 ** -0.5).to(torch.bfloat16).requires_grad_(True)
+            xs = torch.randn(Tl, D2, device=dev, dtype=torch.bfloat16, requires_grad=True)
+            gs = torch.randn(Tl, D2, device=dev, dtype=torch.bfloat16)
+
+            def ours() -> None:
+                xs.grad = w1.grad = w2.grad = None
+                y = sp.row(torch.nn.functional.gelu(sp.column(xs, w1)), w2)
+                y.backward(gs)
+
+            xf = torch.randn(T, D2, device=dev, dtype=torch.bfloat16, requires_grad=True)
+            gf = torch.randn(T, D2, device=dev, dtype=torch.bfloat16)
+
+            class _AllReduceBwd(torch.autograd.Function):          # identity forward, all-reduce backward
+                @staticmethod
+                def forward(ctx, t):  # type: ignore[no-untyped-def]
+                    return t
+
+                @staticmethod
+                def backward(ctx, g):  # type: ignore[no-untyped-def]
+                    g = g.contiguous()
+                    dist.all_reduce(g, group=pg)
+                    return g
+
+            from fairseq2_b200.ops.gemm import linear as k_linear
+
+            def megatron() -> None:
+                xf.grad = w1.grad = w2.grad = None
+                h = torch.nn.functional.gelu(k_linear(_AllReduceBwd.apply(xf), w1))
+                y = k_linear(h, w2)
+                dist.all_reduce(y, group=pg)
+                y.backward(gf)
+
+            ms = _time(ours, barrier, args.iters)
+            base_ms = _time(megatron, barrier, args.iters)
+            flops = 3 * 2 * 2.0 * T * D2 * Fl                     # two GEMMs, forward + dgrad + wgrad
+            emit("tp_mlp_70b_fwd_bwd_sequence_parallel_fused", ms, flops=flops,
+                 nvlink_bytes=4 * (W - 1) / W * T * D2 * 2, baseline_ms=base_ms, tokens=T, model_dim=D2, inner_dim=F2,
+                 note="baseline = replicated activations, same GEMM kernel, NCCL all-reduce forward and backward")
 
     barrier()
     ext.check_status()
