@@ -1,5 +1,4 @@
-"""Gemma 3n configuration (cf. fairseq2 ``models/gemma3n/config.py:27-274``). Text decoder; the audio tower
-(USM conformer) is not part of this package yet."""
+"""Gemma 3n configuration: text decoder and audio tower (cf. fairseq2 ``models/gemma3n/config.py:27-274``)."""
 from __future__ import annotations
 
 from dataclasses import dataclass
@@ -7,6 +6,32 @@ from dataclasses import dataclass
 from fairseq2_b200.runtime.config_registry import ConfigRegistrar
 
 GEMMA3N_FAMILY = "gemma3n"
+
+
+@dataclass(kw_only=True)
+class Gemma3nAudioConfig:
+    """Audio tower (Universal-Speech-Model conformer); defaults are the E2B/E4B tower
+    (cf. fairseq2 ``models/gemma3n/config.py:27-92``)."""
+
+    vocab_size: int = 128
+    vocab_offset: int = 262_272
+    input_feat_size: int = 128
+    hidden_size: int = 1536
+    rms_norm_eps: float = 1e-6
+    gradient_clipping: float = 1e10
+    conf_num_hidden_layers: int = 12
+    conf_num_attention_heads: int = 8
+    conf_conv_kernel_size: int = 5
+    conf_attention_chunk_size: int = 12
+    conf_attention_context_left: int = 13
+    conf_attention_context_right: int = 0
+    conf_attention_logit_cap: float = 50.0
+    conf_reduction_factor: int = 4
+    conf_residual_weight: float = 0.5
+    sscp_conv_channel_size: tuple[int, int] = (128, 32)
+    sscp_conv_group_norm_eps: float = 1e-3
+    sscp_conv_kernel_size: tuple[tuple[int, int], tuple[int, int]] = ((3, 3), (3, 3))
+    sscp_conv_stride_size: tuple[tuple[int, int], tuple[int, int]] = ((2, 2), (2, 2))
 
 
 @dataclass(kw_only=True)
@@ -41,6 +66,8 @@ class Gemma3nConfig:
     hidden_size_per_layer_input: int = 256
     rms_norm_eps: float = 1e-6
     init_std: float = 0.02
+    audio_config: Gemma3nAudioConfig | None = None
+    """When set, the model carries the audio tower and its embedder; ``forward`` then accepts mel features."""
 
 
 def is_global_layer(layer_idx: int, num_layers: int) -> bool:
@@ -66,12 +93,17 @@ arch = ConfigRegistrar(Gemma3nConfig)
 
 @arch("e4b")
 def gemma3n_e4b() -> Gemma3nConfig:
-    return Gemma3nConfig()
+    return Gemma3nConfig(audio_config=Gemma3nAudioConfig())
 
 
 @arch("e2b")
 def gemma3n_e2b() -> Gemma3nConfig:
-    return Gemma3nConfig(num_layers=30, ffn_inner_dim=8192, num_kv_shared_layers=10)
+    return Gemma3nConfig(num_layers=30, ffn_inner_dim=8192, num_kv_shared_layers=10, audio_config=Gemma3nAudioConfig())
+
+
+@arch("e4b_text")
+def gemma3n_e4b_text() -> Gemma3nConfig:
+    return Gemma3nConfig()
 
 
 @arch("tiny")

@@ -1,6 +1,7 @@
 """Hugging Face <-> fairseq2_b200 state dicts for Gemma 3n (text decoder). Module names follow the Hugging Face
 layout, so conversion is a prefix change: ``model.`` (``Gemma3nForCausalLM``) or ``model.language_model.``
-(``Gemma3nForConditionalGeneration``) is dropped; vision/audio tower entries are skipped
+(``Gemma3nForConditionalGeneration``) is dropped; audio tower entries are kept when the config has an audio
+tower, vision entries are skipped
 (cf. fairseq2 ``models/gemma3n/interop.py:30-267``)."""
 from __future__ import annotations
 
@@ -10,7 +11,8 @@ from torch import Tensor
 
 from fairseq2_b200.models.gemma3n.config import Gemma3nConfig
 
-_SKIP = ("model.vision_tower.", "model.audio_tower.", "model.embed_vision.", "model.embed_audio.")
+_VISION = ("model.vision_tower.", "model.embed_vision.")
+_AUDIO = ("model.audio_tower.", "model.embed_audio.")
 
 
 def convert_gemma3n_state_dict(state_dict: dict[str, Tensor], config: Gemma3nConfig) -> dict[str, Tensor]:
@@ -18,7 +20,11 @@ def convert_gemma3n_state_dict(state_dict: dict[str, Tensor], config: Gemma3nCon
         return state_dict                                        # already in the native layout
     out: dict[str, Tensor] = {}
     for key, value in state_dict.items():
-        if key.startswith(_SKIP):
+        if key.startswith(_VISION) or (config.audio_config is None and key.startswith(_AUDIO)):
+            continue
+        if key.startswith(_AUDIO):
+            if not key.endswith("embedding_post_projection_norm.weight"):
+                out[key[len("model."):]] = value
             continue
         if key.startswith("model.language_model."):
             key = key[len("model.language_model."):]

@@ -245,6 +245,13 @@ class Gemma3nModel(Module):
         self.layers = ModuleList([Gemma3nDecoderLayer(cfg, i, device, dtype) for i in range(L)])
         self.norm = RMSNorm(d, bias=False, eps=cfg.rms_norm_eps, **kw)
         self.lm_head: Linear | None = None if cfg.tied_embeddings else Linear(d, cfg.vocab_size, bias=False, **kw)
+        self.audio_tower: Module | None = None
+        self.embed_audio: Module | None = None
+        if cfg.audio_config is not None:
+            from fairseq2_b200.models.gemma3n.audio import Gemma3nAudioEncoder, Gemma3nMultimodalEmbedder
+
+            self.audio_tower = Gemma3nAudioEncoder(cfg.audio_config, device=device, dtype=dtype)
+            self.embed_audio = Gemma3nMultimodalEmbedder(cfg.audio_config, d, device=device, dtype=dtype)
         self.reset_parameters()
 
     def reset_parameters(self) -> None:
@@ -278,7 +285,44 @@ class Gemma3nModel(Module):
         mag = torch.sqrt(torch.clamp(x.pow(2).mean(-1, keepdim=True), min=1e-5))
         return x * target / mag
 
-    def decode(self, seqs: Tensor, layout: BatchLayout, state_bag: IncrementalStateBag | None = None) -> Tensor:
+    def embed_inputs(self, ids: Tensor, audio_features: Tensor | None = None, audio_invalid: Tensor | None = None,
+                     audio_token_idx: int | None = None, num_audio_tokens: int | None = None) -> Tensor:
+        """Token embeddings ``[T, D]`` for flattened ids. Ids in the audio vocabulary range are embedded by the audio
+        embedder; with ``audio_features`` (``[B, frames, mel_bins]``) the tower's soft tokens -- padded to
+        ``num_audio_tokens`` per clip with the embedding of the last audio id -- replace, in order, the positions
+        whose id is ``audio_token_idx``."""
+        cfg = self.cfg
+        x0 = self.embed_tokens(ids) * cfg.model_dim ** 0.5
+        if self.embed_audio is None:
+            return x0
+        ac = cfg.audio_config
+        assert ac is not None and self.audio_tower is not None
+        hard = ids >= ac.vocab_offset
+        last_id = ac.vocab_offset + ac.vocab_size - 1
+        if bool(hard.any()):
+            emb = self.embed_audio(input_ids=torch.where(hard, ids, torch.full_like(ids, last_id)))
+            x0 = torch.where(hard.unsqueeze(-1), emb.to(x0.dtype), x0)
+        if audio_features is not None:
+            if audio_invalid is None:
+                audio_invalid = torch.zeros(audio_features.shape[:2], dtype=torch.bool, device=audio_features.device)
+            if audio_token_idx is None:
+                raise ValueError("`audio_token_idx` (the placeholder id) must be given with `audio_features`.")
+            enc, invalid = self.audio_tower(audio_features, audio_invalid)
+            soft = self.embed_audio(inputs_embeds=enc)
+            pad = self.embed_audio(input_ids=torch.full((1, 1), last_id, dtype=torch.long, device=ids.device))
+            soft = torch.where(invalid.unsqueeze(-1), pad.to(soft.dtype), soft)
+            if num_audio_tokens is not None and num_audio_tokens > soft.shape[1]:
+                extra = pad.to(soft.dtype).expand(soft.shape[0], num_audio_tokens - soft.shape[1], -1)
+                soft = torch.cat([soft, extra], dim=1)
+            slots = ids == audio_token_idx
+            if int(slots.sum()) != soft.shape[0] * soft.shape[1]:
+                raise ValueError(f"The batch has {int(slots.sum())} audio placeholder tokens for "
+                                 f"{soft.shape[0] * soft.shape[1]} audio soft tokens.")
+            x0 = x0.masked_scatter(slots.unsqueeze(-1), soft.to(x0.dtype).reshape(-1, x0.shape[-1]))
+        return x0
+
+    def decode(self, seqs: Tensor, layout: BatchLayout, state_bag: IncrementalStateBag | None = None,
+               inputs_embeds: Tensor | None = None) -> Tensor:
         """Token ids ``[N, S]`` or packed ``[T]`` -> final hidden states of the same leading shape. With a state bag
         ``seqs`` holds the next ``S`` steps of every sequence (unpadded) and attention also covers the cached steps."""
         cfg = self.cfg
@@ -296,7 +340,7 @@ class Gemma3nModel(Module):
         positions = layout.position_indices.reshape(-1).clamp(min=0)
         if state_bag is not None:
             positions = positions + state_bag.step_nr
-        x0 = self.embed_tokens(ids) * cfg.model_dim ** 0.5
+        x0 = inputs_embeds if inputs_embeds is not None else self.embed_inputs(ids)
         per_layer = self._per_layer_inputs(ids, x0)
         target = x0.pow(2).mean(-1, keepdim=True) ** 0.5
         streams = torch.stack([x0] + [self._match_magnitude(proj(x0), target) for proj in self.altup_projections])
@@ -324,8 +368,13 @@ class Gemma3nModel(Module):
     def forward(self, seqs: Tensor, seqs_layout: BatchLayout, targets: Tensor | None = None, *,
                 state_bag: IncrementalStateBag | None = None,
                 label_smoothing: float = 0.0, target_mask: Tensor | None = None,
-                reduction: Literal["sum", "mean"] = "sum", return_logits: bool = False):  # type: ignore[no-untyped-def]
-        logits = self.project(self.decode(seqs, seqs_layout, state_bag))
+                reduction: Literal["sum", "mean"] = "sum", return_logits: bool = False,
+                audio_features: Tensor | None = None, audio_invalid: Tensor | None = None,
+                audio_token_idx: int | None = None, num_audio_tokens: int | None = None):  # type: ignore[no-untyped-def]
+        embeds = None
+        if audio_features is not None:
+            embeds = self.embed_inputs(seqs.reshape(-1), audio_features, audio_invalid, audio_token_idx, num_audio_tokens)
+        logits = self.project(self.decode(seqs, seqs_layout, state_bag, embeds))
         if targets is None:
             return logits
         loss = cross_entropy(logits, targets, self.pad_idx, label_smoothing=label_smoothing, target_mask=target_mask,

@@ -191,3 +191,67 @@ def test_gemma3n_incremental_decoding_matches_full_forward() -> None:
     gen = SamplingSequenceGenerator(model, eos_idx=2, pad_idx=0, max_gen_len=6)
     out = gen(ids[:, :5], BatchLayout((2, 5), [5, 4]))
     assert len(out.hypotheses) == 2 and all(len(h[0].seq) >= 5 for h in out.hypotheses)
+
+
+def test_gemma3n_audio_tower_and_multimodal_merge_match_hf() -> None:
+    """The conformer audio tower (banded attention formulation) and the multimodal embedder against the Hugging Face
+    modules; the merged text + audio forward against the Hugging Face text model fed with the same embeddings."""
+    from dataclasses import replace
+
+    from transformers.models.gemma3n import Gemma3nAudioConfig as HFAudioConfig
+    from transformers.models.gemma3n import Gemma3nForCausalLM, Gemma3nTextConfig
+    from transformers.models.gemma3n.modeling_gemma3n import Gemma3nAudioEncoder as HFEncoder
+    from transformers.models.gemma3n.modeling_gemma3n import Gemma3nMultimodalEmbedder as HFEmbedder
+
+    from fairseq2_b200.models.gemma3n import convert_gemma3n_state_dict, create_gemma3n_model, export_gemma3n_to_hg
+    from fairseq2_b200.models.gemma3n.config import Gemma3nAudioConfig, gemma3n_tiny
+
+    torch.manual_seed(0)
+    akw = dict(input_feat_size=32, hidden_size=48, conf_num_hidden_layers=2, conf_num_attention_heads=4,
+               conf_attention_chunk_size=4, conf_attention_context_left=5, conf_attention_context_right=0,
+               sscp_conv_channel_size=(16, 8), conf_reduction_factor=2, vocab_size=16, vocab_offset=320)
+    cfg = replace(gemma3n_tiny(), vocab_size=336, audio_config=Gemma3nAudioConfig(**akw))
+    _, hg = export_gemma3n_to_hg({}, cfg)
+    for key in ("architectures", "model_type"):
+        hg.pop(key)
+    text_cfg = Gemma3nTextConfig(**hg, attn_implementation="eager")
+    hf_text = Gemma3nForCausalLM(text_cfg).eval()
+    hf_audio = HFEncoder(HFAudioConfig(**akw)).eval()
+    hf_embed = HFEmbedder(HFAudioConfig(**akw), text_cfg).eval()
+    with torch.no_grad():
+        for mod in (hf_text, hf_audio, hf_embed):
+            for name, p in mod.named_parameters():
+                if "per_dim_scale" in name or "correct_output_scale" in name:
+                    p.normal_(std=0.3)
+                elif "norm" in name and p.dim() == 1:
+                    p.add_(0.1 * torch.randn_like(p))
+    sd = {k: v for k, v in hf_text.state_dict().items()}
+    sd.update({"model.audio_tower." + k: v for k, v in hf_audio.state_dict().items()})
+    sd.update({"model.embed_audio." + k: v for k, v in hf_embed.state_dict().items()})
+    model = create_gemma3n_model(cfg).eval()
+    missing, unexpected = model.load_state_dict(convert_gemma3n_state_dict(sd, cfg), strict=False)
+    assert not missing and not unexpected, (missing, unexpected)
+
+    mel = torch.randn(2, 80, 32)
+    invalid = torch.zeros(2, 80, dtype=torch.bool)
+    invalid[1, 57:] = True
+    with torch.no_grad():
+        ref = hf_audio(mel, invalid)
+        enc, enc_invalid = model.audio_tower(mel, invalid)
+        assert torch.allclose(enc, ref.last_hidden_state, atol=1e-4) and torch.equal(enc_invalid, ref.audio_mel_mask)
+        assert torch.allclose(model.embed_audio(inputs_embeds=enc), hf_embed(inputs_embeds=enc), atol=1e-5)
+        hard = torch.tensor([[320, 327, 335]])
+        assert torch.allclose(model.embed_audio(input_ids=hard), hf_embed(input_ids=hard), atol=1e-5)
+
+        # merged forward: 12 soft tokens per clip (10 from the tower + 2 padding) at the placeholder id 5
+        S, placeholder, per_clip = 24, 5, 12
+        ids = torch.randint(6, 300, (2, S))
+        ids[:, 4:4 + per_clip] = placeholder
+        ids[0, 20] = 330                                       # an audio hard token
+        out = model(ids, BatchLayout((2, S), [S, S]), audio_features=mel, audio_invalid=invalid,
+                    audio_token_idx=placeholder, num_audio_tokens=per_clip)
+        embeds = model.embed_inputs(ids.reshape(-1), mel, invalid, placeholder, per_clip).view(2, S, -1)
+        in_vocab = ids < cfg.vocab_size_per_layer_input
+        per_layer = hf_text.model.get_per_layer_inputs(torch.where(in_vocab, ids, torch.zeros_like(ids)))
+        ref_logits = hf_text(inputs_embeds=embeds, per_layer_inputs=per_layer, use_cache=False).logits
+    assert torch.allclose(out, ref_logits, atol=2e-4), float((out - ref_logits).abs().max())
