@@ -81,7 +81,16 @@ def run_recipe(recipe: Recipe, config: Any, output_dir: Path, *, checkpoint_dir:
     output_dir.mkdir(parents=True, exist_ok=True)
     configure_logging(debug=common.debug, rank=rank, log_file=output_dir / "logs" / f"rank_{rank}.log")
     if common.debug:
+        # per-rank library logs next to the recipe log (fairseq2 ``recipe/internal/logging.py:82-116``)
         os.environ.setdefault("TORCH_DISTRIBUTED_DEBUG", "INFO")
+        nccl_dir = output_dir / "logs" / "nccl"
+        nccl_dir.mkdir(parents=True, exist_ok=True)
+        os.environ.setdefault("NCCL_DEBUG", "INFO")
+        os.environ.setdefault("NCCL_DEBUG_FILE", str(nccl_dir / f"rank_{rank}.log"))
+        aten_dir = output_dir / "logs" / "aten"
+        aten_dir.mkdir(parents=True, exist_ok=True)
+        os.environ.setdefault("TORCH_CPP_LOG_LEVEL", "INFO")
+        os.environ.setdefault("TORCH_SHOW_CPP_STACKTRACES", "1")
     if rank == 0:
         dump_yaml(unstructure(config), output_dir / "config.yaml")
     configure_torch(common, rank)
