@@ -90,7 +90,6 @@ def run_recipe(recipe: Recipe, config: Any, output_dir: Path, *, checkpoint_dir:
         aten_dir = output_dir / "logs" / "aten"
         aten_dir.mkdir(parents=True, exist_ok=True)
         os.environ.setdefault("TORCH_CPP_LOG_LEVEL", "INFO")
-        os.environ.setdefault("TORCH_SHOW_CPP_STACKTRACES", "1")
     if rank == 0:
         dump_yaml(unstructure(config), output_dir / "config.yaml")
     configure_torch(common, rank)
