@@ -1,18 +1,28 @@
 // Flash-attention backward on the 5th-generation tensor cores (sm_100a), head_dim 128.
 //
 // Two deterministic kernels (no atomics), both built like the forward kernel: TMA -> 128B-swizzled
-// shared memory -> tcgen05.mma with accumulators in TMEM -> tcgen05.ld; 192 threads = TMA producer
-// warp, MMA issuer warp, four compute warps whose thread t owns TMEM lane t.
+// shared memory -> tcgen05.mma with accumulators in TMEM -> tcgen05.ld; 320 threads = TMA producer
+// warp, MMA issuer warp and two compute warpgroups. Thread t of a warpgroup owns TMEM lane t; the
+// two warpgroups split the 64 score columns of a tile between them (and the accumulator columns in
+// the epilogue), so every scheduler has two compute warps whose exp2 / tcgen05.ld latencies overlap.
 //
 // dQ kernel: a CTA owns 128 query rows of one head. Q and dO stay resident; per 64-row K/V tile the
 //   issuer computes S = Q K^T and dP = dO V^T into a double-buffered TMEM pair, the compute warps
-//   turn them into dS = P * (dP - delta) (P = exp2(S * scale - lse)) as a bf16 A-operand tile in
-//   shared memory, and dQ += dS K accumulates in TMEM (K read as an MN-major B operand).
+//   turn them into dS = P * (dP - delta) (P = exp2(S * scale - lse)), written back as bf16 over the
+//   dP columns they came from, and dQ += dS K accumulates in TMEM with dS read as the A operand
+//   straight from tensor memory (K read as an MN-major B operand).
 //
 // dK/dV kernel: a CTA owns 128 key/value rows of one KV head. K and V stay resident; it walks the
 //   query heads of the group and their 64-row query tiles, computing S^T = K Q^T and dP^T = V dO^T,
-//   then P^T and dS^T as bf16 tiles, and dV += P^T dO, dK += dS^T Q accumulate in TMEM over the
-//   whole walk (Q and dO read as MN-major B operands).
+//   then P^T and dS^T as bf16 written over the score columns, and dV += P^T dO, dK += dS^T Q
+//   accumulate in TMEM over the whole walk (A operands from tensor memory, Q and dO read as
+//   MN-major B operands).
+//
+// Keeping P^T / dS^T in tensor memory matters because these kernels are bound by shared-memory
+// bandwidth (a 128 x 64 x 16 MMA reads 6 KB of operands for 32 cycles of math): it removes the
+// 32 KB of stores and 32 KB of A-operand reads per tile that a shared-memory staging costs. The
+// tensor pipe executes the MMAs of the issuing thread in order, so the scores of tile i+2 cannot
+// overwrite a buffer before the accumulating MMAs of tile i, issued earlier, have read it.
 //
 // The softmax scale is applied once to the dQ / dK accumulators in the epilogue.
 // Every barrier wait is bounded; a wait that gives up records a code in the host-visible status
@@ -39,41 +49,35 @@ constexpr int BOX128 = 128 * 64 * 2;     // [128 rows][64 cols] bf16 box
 constexpr int BOX64 = 64 * 64 * 2;       // [64 rows][64 cols] bf16 box
 constexpr int BIG_TILE = 2 * BOX128;     // [128][128]
 constexpr int SMALL_TILE = 2 * BOX64;    // [64][128]
-constexpr int OPER_TILE = 128 * 64 * 2;  // thread-written [128][64] A operand
-constexpr int BWD_THREADS = 192;
+constexpr int BWD_WGS = 2;                       // compute warpgroups
+constexpr int BWD_THREADS = 64 + 128 * BWD_WGS;
 constexpr uint32_t BWD_TMEM_COLS = 512;
 
-// Shared memory: two resident [128][128] tiles, a ring of stages (each two [64][128] tiles), operand tiles.
+// Shared memory: two resident [128][128] tiles and a ring of stages (each two [64][128] tiles).
 // A stage is released only after the accumulating MMA that reads it has completed, so the ring must be deep
 // enough for the TMA loads to run ahead of that point.
 constexpr int STAGE_BYTES = 2 * SMALL_TILE;
 constexpr int OFF_RES0 = 0;
 constexpr int OFF_RES1 = OFF_RES0 + BIG_TILE;
 constexpr int OFF_STG = OFF_RES1 + BIG_TILE;
-// dQ kernel: 4 stages, dS double-buffered
-constexpr int DQ_NSTG = 4, DQ_NOP = 2;
-constexpr int DQ_OFF_OPER = OFF_STG + DQ_NSTG * STAGE_BYTES;
-constexpr int DQ_OFF_BAR = DQ_OFF_OPER + DQ_NOP * OPER_TILE;
+constexpr int DQ_NSTG = 5, KV_NSTG = 5;
+constexpr int MAX_NSTG = 6;
+constexpr int DQ_OFF_BAR = OFF_STG + DQ_NSTG * STAGE_BYTES;
 constexpr int DQ_SMEM_BYTES = DQ_OFF_BAR + 256 + 1024;
-// dK/dV kernel: 3 stages, one {P^T, dS^T} pair, per-warp lse/delta staging [4 warps][2 bufs][2][64] floats
-constexpr int KV_NSTG = 3, KV_NOP = 1;
-constexpr int KV_OFF_OPER = OFF_STG + KV_NSTG * STAGE_BYTES;
-constexpr int KV_OFF_VEC = KV_OFF_OPER + KV_NOP * 2 * OPER_TILE;
-constexpr int KV_OFF_BAR = KV_OFF_VEC + 4 * 2 * 2 * 64 * 4;
+constexpr int KV_OFF_BAR = OFF_STG + KV_NSTG * STAGE_BYTES;
 constexpr int KV_SMEM_BYTES = KV_OFF_BAR + 256 + 1024;
 static_assert(DQ_SMEM_BYTES <= 232448 && KV_SMEM_BYTES <= 232448, "shared memory budget of one CTA exceeded");
 
 enum : int {
     B_RES_FULL = 0,
-    B_STG_FULL = 1,    // [4]
-    B_STG_EMPTY = 5,   // [4]
-    B_ACC_FULL = 9,    // [2] score pair in TMEM ready
-    B_ACC_EMPTY = 11,  // [2] score pair consumed
-    B_OP_FULL = 13,    // [2] operand tile(s) written
-    B_OP_EMPTY = 15,   // [2] operand tile(s) consumed by the MMA
-    B_DONE = 17,
-    B_NUM = 18
+    B_STG_FULL = 1,                        // [MAX_NSTG]
+    B_STG_EMPTY = B_STG_FULL + MAX_NSTG,   // [MAX_NSTG]
+    B_ACC_FULL = B_STG_EMPTY + MAX_NSTG,   // [2] score pair in TMEM ready
+    B_OP_FULL = B_ACC_FULL + 2,            // [2] bf16 operand(s) written over the score pair
+    B_DONE = B_OP_FULL + 2,
+    B_NUM = B_DONE + 1
 };
+static_assert(8 * B_NUM + 16 <= 256, "barrier area");
 
 struct Ctx {
     uint32_t base;
@@ -104,15 +108,13 @@ __device__ __forceinline__ void bwd_setup(Ctx& c, uint8_t* smem_raw, int* status
     if (threadIdx.x == 0) {
         mbar_init(c.bar(B_RES_FULL), 1);
         mbar_init(c.bar(B_DONE), 1);
-        for (int s = 0; s < 4; ++s) {
+        for (int s = 0; s < MAX_NSTG; ++s) {
             mbar_init(c.bar(B_STG_FULL + s), 1);
             mbar_init(c.bar(B_STG_EMPTY + s), 1);
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(c.bar(B_ACC_FULL + s), 1);
-            mbar_init(c.bar(B_ACC_EMPTY + s), 128);
-            mbar_init(c.bar(B_OP_FULL + s), 128);
-            mbar_init(c.bar(B_OP_EMPTY + s), 1);
+            mbar_init(c.bar(B_OP_FULL + s), 128 * BWD_WGS);
         }
         *c.abort_flag = 0;
         fence_barrier_init();
@@ -148,20 +150,30 @@ __device__ __forceinline__ void mma_scores(uint32_t d_tmem, uint32_t a_s, uint32
     }
 }
 
-// D[128 x 128] (+)= A[128 x 64 (K-major operand tile)] * B[64 x 128 (row-major [64][128] tile read MN-major)]
-__device__ __forceinline__ void mma_accum(uint32_t d_tmem, uint32_t a_s, uint32_t b_s, uint32_t idesc, bool first) {
+// D[128 x 128] (+)= A[128 x 64] * B[64 x 128 (row-major [64][128] tile read MN-major)]. A is bf16 in tensor memory:
+// warpgroup g wrote K elements [32 g, 32 g + 32) as 16 packed columns starting at column 32 g of `a_tmem`.
+__device__ __forceinline__ void mma_accum(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_s, uint32_t idesc, bool first) {
 #pragma unroll
     for (int k = 0; k < 64 / 16; ++k) {
-        const uint64_t da = make_smem_desc(a_s + k * 32, 16, 1024);
+        const uint32_t ta = a_tmem + static_cast<uint32_t>((k >> 1) * 32 + (k & 1) * 8);
         const uint64_t db = make_smem_desc(b_s + k * 16 * 128, BOX64, 1024);
-        umma_bf16(d_tmem, da, db, idesc, (first && k == 0) ? 0u : 1u);
+        umma_bf16_ts(d_tmem, ta, db, idesc, (first && k == 0) ? 0u : 1u);
     }
 }
 
-// Epilogue: TMEM accumulator [128 lanes][128 cols] * mul -> bf16 row in global memory.
-__device__ __forceinline__ void store_acc_row(uint32_t t_lane_col, float mul, __nv_bfloat16* dst, bool valid) {
+// Packs 32 floats to bf16 pairs and writes them as 16 columns of this thread's TMEM lane.
+__device__ __forceinline__ void store_operand(uint32_t taddr, const float* e) {
+    uint32_t r[16];
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
+    for (int j = 0; j < 16; ++j) r[j] = pack2_bf16(e[2 * j], e[2 * j + 1]);
+    tmem_st_32x16(taddr, r);
+}
+
+// Epilogue: TMEM accumulator [128 lanes][128 cols] * mul -> bf16 row in global memory.
+// Chunks [c0, c1) of 32 columns each.
+__device__ __forceinline__ void store_acc_row(uint32_t t_lane_col, float mul, __nv_bfloat16* dst, bool valid,
+                                              int c0 = 0, int c1 = 4) {
+    for (int c = c0; c < c1; ++c) {
         uint32_t v[32];
         tmem_ld_32x32(t_lane_col + c * 32, v);
         tmem_ld_wait();
@@ -180,14 +192,14 @@ __device__ __forceinline__ void store_acc_row(uint32_t t_lane_col, float mul, __
 }
 
 // ============================================================================ dQ kernel
-// grid (q tiles of 128, seqs, H)
+// grid (H, seqs, q tiles of 128): heads fastest, so the long query tiles of every head are scheduled first
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_do,
                       const __grid_constant__ CUtensorMap tma_k, const __grid_constant__ CUtensorMap tma_v,
                       const AttnParams p, int* status) {
-    const int seq = blockIdx.y, h = blockIdx.z;
+    const int seq = blockIdx.y, h = blockIdx.x;
     const int q_len = p.q_lens[seq], k_len = p.k_lens[seq];
-    const int qblk = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
+    const int qblk = static_cast<int>(gridDim.z) - 1 - static_cast<int>(blockIdx.z);
     const int q0 = qblk * 128;
     if (q0 >= q_len) return;
     const int q_begin = p.q_begins[seq], k_begin = p.k_begins[seq];
@@ -202,7 +214,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_co
 
     if (n_iter == 0) {
         // no visible key: the gradient of these query rows is zero
-        if (warp >= 2) {
+        if (warp >= 2 && warp < 6) {
             const int row = (warp & 3) * 32 + lane;
             if (q0 + row < q_len) {
                 __nv_bfloat16* dst = p.dq + static_cast<size_t>(q_begin + q0 + row) * p.dq_tstride + static_cast<size_t>(h) * HD;
@@ -255,19 +267,18 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_co
             bool ok = c.wait(B_RES_FULL, 0u);
             if (!ok) c.fail(0x42);
             auto accumulate = [&](int j) -> bool {     // dQ += dS_j K_j
-                const int ob = j % DQ_NOP, st = j % DQ_NSTG;
-                if (!c.wait(B_OP_FULL + ob, static_cast<uint32_t>(j / DQ_NOP) & 1u)) return false;
+                const int b = j & 1, st = j % DQ_NSTG;
+                if (!c.wait(B_OP_FULL + b, static_cast<uint32_t>(j >> 1) & 1u)) return false;
                 tcgen05_fence_after();
                 const uint32_t k_s = c.base + OFF_STG + st * STAGE_BYTES;
-                mma_accum(c.tmem_base + 256u, c.base + DQ_OFF_OPER + ob * OPER_TILE, k_s, id_acc, j == 0);
-                umma_commit(c.bar(B_OP_EMPTY + ob));
+                mma_accum(c.tmem_base + 256u, c.tmem_base + static_cast<uint32_t>(b * 128 + 64), k_s, id_acc, j == 0);
                 umma_commit(c.bar(B_STG_EMPTY + st));
                 return true;
             };
             for (int i = 0; i < n_iter && ok; ++i) {
                 const int b = i & 1, st = i % DQ_NSTG;
-                const uint32_t ph = static_cast<uint32_t>(i >> 1) & 1u;
-                ok = c.wait(B_STG_FULL + st, static_cast<uint32_t>(i / DQ_NSTG) & 1u) && c.wait(B_ACC_EMPTY + b, ph ^ 1u);
+                // the score pair b is free: the MMAs that read tile i - 2 from it were issued before this point
+                ok = c.wait(B_STG_FULL + st, static_cast<uint32_t>(i / DQ_NSTG) & 1u);
                 if (!ok) {
                     c.fail(0x43);
                     break;
@@ -289,7 +300,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_co
             if (ok) umma_commit(c.bar(B_DONE));
         }
     } else {
-        const int quad = warp & 3;
+        const int quad = warp & 3;                 // the TMEM lane quarter this warp may read
+        const int cc = (warp - 2) >> 2;            // warpgroup = which half of the score columns
         const int row = quad * 32 + lane;
         const int q_row = q0 + row;
         const bool row_ok = q_row < q_len;
@@ -305,36 +317,29 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_co
             const int b = i & 1;
             const uint32_t ph = static_cast<uint32_t>(i >> 1) & 1u;
             const int kv0 = (it0 + i) * 64;
-            const int ob = i % DQ_NOP;
-            if (!warp_wait(c.bar(B_ACC_FULL + b), ph, c.abort_flag) ||
-                !warp_wait(c.bar(B_OP_EMPTY + ob), (static_cast<uint32_t>(i / DQ_NOP) & 1u) ^ 1u, c.abort_flag)) {
+            if (!warp_wait(c.bar(B_ACC_FULL + b), ph, c.abort_flag)) {
                 ok = false;
                 break;
             }
             tcgen05_fence_after();
             const int rel = lim - kv0, rel_lo = lo - kv0;
             const uint32_t t_s = t_lane + static_cast<uint32_t>(b * 128);
-            const uint32_t ds_tile = c.base + DQ_OFF_OPER + ob * OPER_TILE;
+            // this warpgroup's 32 of the 64 key columns
+            uint32_t s[32], dp[32];
+            tmem_ld_32x32(t_s + cc * 32, s);
+            tmem_ld_32x32(t_s + 64 + cc * 32, dp);
+            tmem_ld_wait();
+            float e[32];
 #pragma unroll
-            for (int cc = 0; cc < 2; ++cc) {
-                uint32_t s[32], dp[32];
-                tmem_ld_32x32(t_s + cc * 32, s);
-                tmem_ld_32x32(t_s + 64 + cc * 32, dp);
-                tmem_ld_wait();
-                float e[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const float pr = ex2_approx(fmaf(__uint_as_float(s[j]), sl2, neg_lse2));
-                    const float ds = pr * (__uint_as_float(dp[j]) - delta);
-                    e[j] = (cc * 32 + j <= rel && cc * 32 + j >= rel_lo) ? ds : 0.f;
-                }
-#pragma unroll
-                for (int g = 0; g < 4; ++g) st_swizzled_chunk(ds_tile, row, static_cast<uint32_t>(cc * 4 + g), e + 8 * g);
+            for (int j = 0; j < 32; ++j) {
+                const float pr = ex2_approx(fmaf(__uint_as_float(s[j]), sl2, neg_lse2));
+                const float ds = pr * (__uint_as_float(dp[j]) - delta);
+                e[j] = (cc * 32 + j <= rel && cc * 32 + j >= rel_lo) ? ds : 0.f;
             }
+            store_operand(t_s + 64 + cc * 32, e);     // dS over the dP columns it came from
+            tmem_st_wait();
             tcgen05_fence_before();
-            mbar_arrive(c.bar(B_ACC_EMPTY + b));
-            fence_proxy_async_smem();
-            mbar_arrive(c.bar(B_OP_FULL + ob));
+            mbar_arrive(c.bar(B_OP_FULL + b));
         }
         if (ok) ok = warp_wait(c.bar(B_DONE), 0u, c.abort_flag);
         if (!ok) {
@@ -342,21 +347,22 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_co
         } else {
             tcgen05_fence_after();
             __nv_bfloat16* dst = p.dq + static_cast<size_t>(q_begin + q_row) * p.dq_tstride + static_cast<size_t>(h) * HD;
-            store_acc_row(t_lane + 256u, p.scale, dst, row_ok);
+            store_acc_row(t_lane + 256u, p.scale, dst, row_ok, 2 * cc, 2 * cc + 2);
         }
     }
     bwd_teardown(c);
 }
 
 // ========================================================================= dK/dV kernel
-// grid (kv tiles of 128, seqs, Hkv)
+// grid (Hkv, seqs, kv tiles of 128): heads fastest, so the early key tiles (seen by the most queries under a causal
+// mask) of every head are scheduled first
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_do,
                        const __grid_constant__ CUtensorMap tma_k, const __grid_constant__ CUtensorMap tma_v,
                        const AttnParams p, int* status) {
-    const int seq = blockIdx.y, kvh = blockIdx.z;
+    const int seq = blockIdx.y, kvh = blockIdx.x;
     const int q_len = p.q_lens[seq], k_len = p.k_lens[seq];
-    const int kv0 = static_cast<int>(blockIdx.x) * 128;
+    const int kv0 = static_cast<int>(blockIdx.z) * 128;
     if (kv0 >= k_len) return;
     const int q_begin = p.q_begins[seq], k_begin = p.k_begins[seq];
     const int shift = k_len - q_len;
@@ -375,7 +381,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
 
     if (n_iter == 0) {
         // no query sees these keys: zero gradients
-        if (warp >= 2) {
+        if (warp >= 2 && warp < 6) {
             const int row = (warp & 3) * 32 + lane;
             if (kv0 + row < k_len) {
                 const size_t t = static_cast<size_t>(k_begin + kv0 + row);
@@ -400,7 +406,6 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
         prefetch_tmap(&tma_v);
     }
     const uint32_t k_s = c.base + OFF_RES0, v_s = c.base + OFF_RES1;
-    float* vec = reinterpret_cast<float*>(smem_raw + (c.base - smem_u32(smem_raw)) + KV_OFF_VEC);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -435,21 +440,20 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
             bool ok = c.wait(B_RES_FULL, 0u);
             if (!ok) c.fail(0x52);
             auto accumulate = [&](int j) -> bool {     // dV += P^T dO_j ; dK += dS^T Q_j
-                const int ob = j % KV_NOP, st = j % KV_NSTG;
-                if (!c.wait(B_OP_FULL + ob, static_cast<uint32_t>(j / KV_NOP) & 1u)) return false;
+                const int b = j & 1, st = j % KV_NSTG;
+                if (!c.wait(B_OP_FULL + b, static_cast<uint32_t>(j >> 1) & 1u)) return false;
                 tcgen05_fence_after();
                 const uint32_t q_s = c.base + OFF_STG + st * STAGE_BYTES, do_s = q_s + SMALL_TILE;
-                const uint32_t pt_s = c.base + KV_OFF_OPER + ob * 2 * OPER_TILE, dst_s = pt_s + OPER_TILE;
-                mma_accum(c.tmem_base + 256u, pt_s, do_s, id_acc, j == 0);
-                mma_accum(c.tmem_base + 384u, dst_s, q_s, id_acc, j == 0);
-                umma_commit(c.bar(B_OP_EMPTY + ob));
+                const uint32_t pt_t = c.tmem_base + static_cast<uint32_t>(b * 128), dst_t = pt_t + 64u;
+                mma_accum(c.tmem_base + 256u, pt_t, do_s, id_acc, j == 0);
+                mma_accum(c.tmem_base + 384u, dst_t, q_s, id_acc, j == 0);
                 umma_commit(c.bar(B_STG_EMPTY + st));
                 return true;
             };
             for (int i = 0; i < n_iter && ok; ++i) {
                 const int b = i & 1, st = i % KV_NSTG;
-                const uint32_t ph = static_cast<uint32_t>(i >> 1) & 1u;
-                ok = c.wait(B_STG_FULL + st, static_cast<uint32_t>(i / KV_NSTG) & 1u) && c.wait(B_ACC_EMPTY + b, ph ^ 1u);
+                // the score pair b is free: the MMAs that read tile i - 2 from it were issued before this point
+                ok = c.wait(B_STG_FULL + st, static_cast<uint32_t>(i / KV_NSTG) & 1u);
                 if (!ok) {
                     c.fail(0x53);
                     break;
@@ -471,32 +475,31 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
             if (ok) umma_commit(c.bar(B_DONE));
         }
     } else {
-        const int quad = warp & 3;
+        const int quad = warp & 3;                 // the TMEM lane quarter this warp may read
+        const int cc = (warp - 2) >> 2;            // warpgroup = which half of the 64 query columns
         const int row = quad * 32 + lane;          // key/value row inside the tile
         const int kv_row = kv0 + row;
         const bool row_ok = kv_row < k_len;
         const uint32_t t_lane = c.tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
         const float sl2 = p.scale * LOG2E;
         bool ok = true;
+        // Lane l holds -lse * log2(e) and delta of query column cc * 32 + l of the current tile; the values of the
+        // next tile are fetched before the wait for the scores.
+        auto load_stats = [&](int i, float& nl, float& dl) {
+            const int h = kvh * G + i / per_head;
+            const int q = (jt_lo + i % per_head) * 64 + cc * 32 + lane;
+            const size_t idx = static_cast<size_t>(h) * p.total_q + q_begin + q;
+            nl = (q < q_len) ? -p.lse[idx] * LOG2E : -INFINITY;   // -inf -> probability 0
+            dl = (q < q_len) ? p.delta[idx] : 0.f;
+        };
+        float nl_next, dl_next;
+        load_stats(0, nl_next, dl_next);
         for (int i = 0; i < n_iter; ++i) {
             const int b = i & 1;
             const uint32_t ph = static_cast<uint32_t>(i >> 1) & 1u;
-            const int h = kvh * G + i / per_head;
             const int qt0 = (jt_lo + i % per_head) * 64;
-            // Every warp stages its own copy of -lse * log2(e) and delta of the 64 query rows of this tile, so
-            // that only a warp-level sync is needed (a CTA-wide named barrier could block after an abort).
-            float* nl = vec + ((quad * 2 + b) * 2) * 64;
-            float* dl = nl + 64;
-#pragma unroll
-            for (int r = 0; r < 2; ++r) {
-                const int j = lane + 32 * r;
-                const int q = qt0 + j;
-                const size_t idx = static_cast<size_t>(h) * p.total_q + q_begin + q;
-                nl[j] = (q < q_len) ? -p.lse[idx] * LOG2E : -INFINITY;   // -inf -> probability 0
-                dl[j] = (q < q_len) ? p.delta[idx] : 0.f;
-            }
-            __syncwarp();
-            const int ob = i % KV_NOP;
+            const float nl = nl_next, dl = dl_next;
+            if (i + 1 < n_iter) load_stats(i + 1, nl_next, dl_next);
             if (!warp_wait(c.bar(B_ACC_FULL + b), ph, c.abort_flag)) {
                 ok = false;
                 break;
@@ -506,42 +509,27 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
             const int jmin = p.causal ? kv_row - shift - qt0 : 0;     // columns below jmin are masked
             const int jmax = windowed ? kv_row - shift + p.window - 1 - qt0 : (1 << 30);   // and above jmax
             const uint32_t t_s = t_lane + static_cast<uint32_t>(b * 128);
-            const uint32_t pt_tile = c.base + KV_OFF_OPER + ob * 2 * OPER_TILE, dst_tile = pt_tile + OPER_TILE;
+            uint32_t s[32], dp[32];
+            tmem_ld_32x32(t_s + cc * 32, s);
+            tmem_ld_32x32(t_s + 64 + cc * 32, dp);
+            tmem_ld_wait();
+            float pe[32], de[32];
 #pragma unroll
-            for (int cc = 0; cc < 2; ++cc) {
-                uint32_t s[32], dp[32];
-                tmem_ld_32x32(t_s + cc * 32, s);
-                tmem_ld_32x32(t_s + 64 + cc * 32, dp);
-                tmem_ld_wait();
-                float pe[32], de[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int col = cc * 32 + j;
-                    float pr = ex2_approx(fmaf(__uint_as_float(s[j]), sl2, nl[col]));
-                    float ds = pr * (__uint_as_float(dp[j]) - dl[col]);
-                    const bool live = row_ok && col >= jmin && col <= jmax;
-                    pe[j] = live ? pr : 0.f;
-                    de[j] = live ? ds : 0.f;
-                }
-                if (cc == 0) {
-                    // the single operand pair is still being read by the MMA of the previous tile until this fires;
-                    // the math above already overlapped with it
-                    if (!warp_wait(c.bar(B_OP_EMPTY + ob), (static_cast<uint32_t>(i / KV_NOP) & 1u) ^ 1u, c.abort_flag)) {
-                        ok = false;
-                        break;
-                    }
-                }
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    st_swizzled_chunk(pt_tile, row, static_cast<uint32_t>(cc * 4 + g), pe + 8 * g);
-                    st_swizzled_chunk(dst_tile, row, static_cast<uint32_t>(cc * 4 + g), de + 8 * g);
-                }
+            for (int j = 0; j < 32; ++j) {
+                const int col = cc * 32 + j;
+                const float nl_j = __shfl_sync(0xffffffffu, nl, j);
+                const float dl_j = __shfl_sync(0xffffffffu, dl, j);
+                float pr = ex2_approx(fmaf(__uint_as_float(s[j]), sl2, nl_j));
+                float ds = pr * (__uint_as_float(dp[j]) - dl_j);
+                const bool live = row_ok && col >= jmin && col <= jmax;
+                pe[j] = live ? pr : 0.f;
+                de[j] = live ? ds : 0.f;
             }
-            if (!ok) break;
+            store_operand(t_s + cc * 32, pe);          // P^T over the S^T columns it came from
+            store_operand(t_s + 64 + cc * 32, de);     // dS^T over the dP^T columns
+            tmem_st_wait();
             tcgen05_fence_before();
-            mbar_arrive(c.bar(B_ACC_EMPTY + b));
-            fence_proxy_async_smem();
-            mbar_arrive(c.bar(B_OP_FULL + ob));
+            mbar_arrive(c.bar(B_OP_FULL + b));
         }
         if (ok) ok = warp_wait(c.bar(B_DONE), 0u, c.abort_flag);
         if (!ok) {
@@ -549,8 +537,10 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
         } else {
             tcgen05_fence_after();
             const size_t t = static_cast<size_t>(k_begin + kv_row);
-            store_acc_row(t_lane + 256u, 1.0f, p.dv + t * p.dv_tstride + static_cast<size_t>(kvh) * HD, row_ok);
-            store_acc_row(t_lane + 384u, p.scale, p.dk + t * p.dk_tstride + static_cast<size_t>(kvh) * HD, row_ok);
+            if (cc == 0)
+                store_acc_row(t_lane + 256u, 1.0f, p.dv + t * p.dv_tstride + static_cast<size_t>(kvh) * HD, row_ok);
+            else
+                store_acc_row(t_lane + 384u, p.scale, p.dk + t * p.dk_tstride + static_cast<size_t>(kvh) * HD, row_ok);
         }
     }
     bwd_teardown(c);
@@ -593,8 +583,8 @@ const char* attn_backward_tc(const AttnParams& p, int* status, cudaStream_t st) 
         if (e != cudaSuccess) return cudaGetErrorString(e);
         configured = true;
     }
-    const dim3 grid_kv((p.max_k + 127) / 128, p.num_seqs, p.Hkv);
-    const dim3 grid_q((p.max_q + 127) / 128, p.num_seqs, p.H);
+    const dim3 grid_kv(p.Hkv, p.num_seqs, (p.max_k + 127) / 128);
+    const dim3 grid_q(p.H, p.num_seqs, (p.max_q + 127) / 128);
     attn_bwd_dkv_tc_kernel<<<grid_kv, BWD_THREADS, KV_SMEM_BYTES, st>>>(q64, do64, k128, v128, p, status);
     attn_bwd_dq_tc_kernel<<<grid_q, BWD_THREADS, DQ_SMEM_BYTES, st>>>(q128, do128, k64, v64, p, status);
     cudaError_t e = cudaGetLastError();

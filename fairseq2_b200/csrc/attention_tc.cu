@@ -84,10 +84,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                    const __grid_constant__ CUtensorMap tma_v, const AttnParams p, int* status) {
     // ------------------------------------------------------------- tile geometry
+    // Heads vary fastest and tiles slowest, so that the block scheduler hands out the long (late) query tiles of ALL
+    // heads before any short one: with tiles fastest, the last head's long tiles start late and the SMs that
+    // finished early idle behind them.
     const int seq = blockIdx.y;
-    const int h = blockIdx.z;
+    const int h = blockIdx.x;
     const int q_len = p.q_lens[seq], k_len = p.k_lens[seq];
-    const int qblk = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);   // long tiles first
+    const int qblk = static_cast<int>(gridDim.z) - 1 - static_cast<int>(blockIdx.z);   // long tiles first
     const int q0 = qblk * TQ;
     if (q0 >= q_len) return;
     const int q_begin = p.q_begins[seq], k_begin = p.k_begins[seq];
@@ -401,7 +404,7 @@ const char* attn_forward_tc(const AttnParams& p, int* status, cudaStream_t st) {
         if (e != cudaSuccess) return cudaGetErrorString(e);
         configured = true;
     }
-    const dim3 grid((p.max_q + TQ - 1) / TQ, p.num_seqs, p.H);
+    const dim3 grid(p.H, p.num_seqs, (p.max_q + TQ - 1) / TQ);
     if (p.causal && p.window > 0)
         attn_fwd_tc_kernel<true><<<grid, TC_THREADS, TC_SMEM_BYTES, st>>>(tq, tk, tv, p, status);
     else
