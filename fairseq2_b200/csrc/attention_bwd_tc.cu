@@ -60,11 +60,14 @@ constexpr int STAGE_BYTES = 2 * SMALL_TILE;
 constexpr int OFF_RES0 = 0;
 constexpr int OFF_RES1 = OFF_RES0 + BIG_TILE;
 constexpr int OFF_STG = OFF_RES1 + BIG_TILE;
-constexpr int DQ_NSTG = 5, KV_NSTG = 5;
+constexpr int DQ_NSTG = 5, KV_NSTG = 4;
 constexpr int MAX_NSTG = 6;
 constexpr int DQ_OFF_BAR = OFF_STG + DQ_NSTG * STAGE_BYTES;
 constexpr int DQ_SMEM_BYTES = DQ_OFF_BAR + 256 + 1024;
-constexpr int KV_OFF_BAR = OFF_STG + KV_NSTG * STAGE_BYTES;
+// dK/dV kernel: per compute warp, -lse * log2(e) and delta of its 32 query columns, double-buffered
+constexpr int KV_OFF_VEC = OFF_STG + KV_NSTG * STAGE_BYTES;
+constexpr int KV_VEC_BYTES = 8 * 2 * 2 * 32 * 4;
+constexpr int KV_OFF_BAR = KV_OFF_VEC + KV_VEC_BYTES;
 constexpr int KV_SMEM_BYTES = KV_OFF_BAR + 256 + 1024;
 static_assert(DQ_SMEM_BYTES <= 232448 && KV_SMEM_BYTES <= 232448, "shared memory budget of one CTA exceeded");
 
@@ -330,11 +333,22 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_co
             tmem_ld_32x32(t_s + 64 + cc * 32, dp);
             tmem_ld_wait();
             float e[32];
+            // Only the tiles that the diagonal (or the window edge) crosses need the per-element mask; rows past
+            // the end of the sequence have lse = +inf and give 0 without it.
+            const int c_lo = cc * 32;
+            if (__all_sync(0xffffffffu, rel >= c_lo + 31 && rel_lo <= c_lo)) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const float pr = ex2_approx(fmaf(__uint_as_float(s[j]), sl2, neg_lse2));
-                const float ds = pr * (__uint_as_float(dp[j]) - delta);
-                e[j] = (cc * 32 + j <= rel && cc * 32 + j >= rel_lo) ? ds : 0.f;
+                for (int j = 0; j < 32; ++j) {
+                    const float pr = ex2_approx(fmaf(__uint_as_float(s[j]), sl2, neg_lse2));
+                    e[j] = pr * (__uint_as_float(dp[j]) - delta);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const float pr = ex2_approx(fmaf(__uint_as_float(s[j]), sl2, neg_lse2));
+                    const float ds = pr * (__uint_as_float(dp[j]) - delta);
+                    e[j] = (c_lo + j <= rel && c_lo + j >= rel_lo) ? ds : 0.f;
+                }
             }
             store_operand(t_s + 64 + cc * 32, e);     // dS over the dP columns it came from
             tmem_st_wait();
@@ -406,6 +420,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
         prefetch_tmap(&tma_v);
     }
     const uint32_t k_s = c.base + OFF_RES0, v_s = c.base + OFF_RES1;
+    float* vec = reinterpret_cast<float*>(smem_raw + (c.base - smem_u32(smem_raw)) + KV_OFF_VEC);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -483,8 +498,9 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
         const uint32_t t_lane = c.tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
         const float sl2 = p.scale * LOG2E;
         bool ok = true;
-        // Lane l holds -lse * log2(e) and delta of query column cc * 32 + l of the current tile; the values of the
-        // next tile are fetched before the wait for the scores.
+        // Every warp stages -lse * log2(e) and delta of its 32 query columns of the NEXT tile in its own slice of
+        // shared memory (a warp-level sync suffices) and reads them back four columns per load.
+        float* my_vec = vec + (warp - 2) * (2 * 2 * 32);
         auto load_stats = [&](int i, float& nl, float& dl) {
             const int h = kvh * G + i / per_head;
             const int q = (jt_lo + i % per_head) * 64 + cc * 32 + lane;
@@ -492,14 +508,21 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
             nl = (q < q_len) ? -p.lse[idx] * LOG2E : -INFINITY;   // -inf -> probability 0
             dl = (q < q_len) ? p.delta[idx] : 0.f;
         };
+        auto stage_stats = [&](int i, float nl, float dl) {
+            float* dst = my_vec + (i & 1) * 64;
+            dst[lane] = nl;
+            dst[32 + lane] = dl;
+        };
         float nl_next, dl_next;
         load_stats(0, nl_next, dl_next);
+        stage_stats(0, nl_next, dl_next);
         for (int i = 0; i < n_iter; ++i) {
             const int b = i & 1;
             const uint32_t ph = static_cast<uint32_t>(i >> 1) & 1u;
             const int qt0 = (jt_lo + i % per_head) * 64;
-            const float nl = nl_next, dl = dl_next;
+            // the loads for the next tile are in flight during this tile's math and staged at its end
             if (i + 1 < n_iter) load_stats(i + 1, nl_next, dl_next);
+            __syncwarp();
             if (!warp_wait(c.bar(B_ACC_FULL + b), ph, c.abort_flag)) {
                 ok = false;
                 break;
@@ -509,27 +532,42 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
             const int jmin = p.causal ? kv_row - shift - qt0 : 0;     // columns below jmin are masked
             const int jmax = windowed ? kv_row - shift + p.window - 1 - qt0 : (1 << 30);   // and above jmax
             const uint32_t t_s = t_lane + static_cast<uint32_t>(b * 128);
+            const float4* nl4 = reinterpret_cast<const float4*>(my_vec + b * 64);
+            const float4* dl4 = nl4 + 8;
             uint32_t s[32], dp[32];
             tmem_ld_32x32(t_s + cc * 32, s);
             tmem_ld_32x32(t_s + 64 + cc * 32, dp);
             tmem_ld_wait();
             float pe[32], de[32];
+            const int c_lo = cc * 32;
+            // only the tiles that the diagonal (or the window edge) crosses need the per-element mask
+            const bool all_live = __all_sync(0xffffffffu, row_ok && jmin <= c_lo && jmax >= c_lo + 31);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const int col = cc * 32 + j;
-                const float nl_j = __shfl_sync(0xffffffffu, nl, j);
-                const float dl_j = __shfl_sync(0xffffffffu, dl, j);
-                float pr = ex2_approx(fmaf(__uint_as_float(s[j]), sl2, nl_j));
-                float ds = pr * (__uint_as_float(dp[j]) - dl_j);
-                const bool live = row_ok && col >= jmin && col <= jmax;
-                pe[j] = live ? pr : 0.f;
-                de[j] = live ? ds : 0.f;
+            for (int g = 0; g < 8; ++g) {
+                const float4 n4 = nl4[g], d4 = dl4[g];
+                const float nl_j[4] = {n4.x, n4.y, n4.z, n4.w}, dl_j[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int j = 4 * g + u;
+                    const float pr = ex2_approx(fmaf(__uint_as_float(s[j]), sl2, nl_j[u]));
+                    pe[j] = pr;
+                    de[j] = pr * (__uint_as_float(dp[j]) - dl_j[u]);
+                }
+            }
+            if (!all_live) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const bool live = row_ok && c_lo + j >= jmin && c_lo + j <= jmax;
+                    pe[j] = live ? pe[j] : 0.f;
+                    de[j] = live ? de[j] : 0.f;
+                }
             }
             store_operand(t_s + cc * 32, pe);          // P^T over the S^T columns it came from
             store_operand(t_s + 64 + cc * 32, de);     // dS^T over the dP^T columns
             tmem_st_wait();
             tcgen05_fence_before();
             mbar_arrive(c.bar(B_OP_FULL + b));
+            if (i + 1 < n_iter) stage_stats(i + 1, nl_next, dl_next);
         }
         if (ok) ok = warp_wait(c.bar(B_DONE), 0u, c.abort_flag);
         if (!ok) {
