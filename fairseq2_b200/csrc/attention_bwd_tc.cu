@@ -6,7 +6,8 @@
 // two warpgroups split the 64 score columns of a tile between them (and the accumulator columns in
 // the epilogue), so every scheduler has two compute warps whose exp2 / tcgen05.ld latencies overlap.
 //
-// dQ kernel: a CTA owns 128 query rows of one head. Q and dO stay resident; per 64-row K/V tile the
+// dQ kernel: a CTA owns 128 query rows of one head. Q and dO are copied once into tensor memory and
+//   are the A operands of every score MMA from there; per 64-row K/V tile the
 //   issuer computes S = Q K^T and dP = dO V^T into a double-buffered TMEM pair, the compute warps
 //   turn them into dS = P * (dP - delta) (P = exp2(S * scale - lse)), written back as bf16 over the
 //   dP columns they came from, and dQ += dS K accumulates in TMEM with dS read as the A operand
@@ -18,9 +19,10 @@
 //   accumulate in TMEM over the whole walk (A operands from tensor memory, Q and dO read as
 //   MN-major B operands).
 //
-// Keeping P^T / dS^T in tensor memory matters because these kernels are bound by shared-memory
-// bandwidth (a 128 x 64 x 16 MMA reads 6 KB of operands for 32 cycles of math): it removes the
-// 32 KB of stores and 32 KB of A-operand reads per tile that a shared-memory staging costs. The
+// Operands in tensor memory matter because these kernels are bound by the rate at which the tensor
+// core reads operands from shared memory: measured here, an MMA costs max(math, operand bytes / 64 B
+// per cycle), so a 128 x 64 x 16 MMA with both operands in shared memory (6 KB) takes 96 cycles for
+// 32 cycles of math, and 32 with A in tensor memory. The
 // tensor pipe executes the MMAs of the issuing thread in order, so the scores of tile i+2 cannot
 // overwrite a buffer before the accumulating MMAs of tile i, issued earlier, have read it.
 //
@@ -78,7 +80,8 @@ enum : int {
     B_ACC_FULL = B_STG_EMPTY + MAX_NSTG,   // [2] score pair in TMEM ready
     B_OP_FULL = B_ACC_FULL + 2,            // [2] bf16 operand(s) written over the score pair
     B_DONE = B_OP_FULL + 2,
-    B_NUM = B_DONE + 1
+    B_RESA_FULL = B_DONE + 1,              // resident A operands copied to tensor memory
+    B_NUM = B_RESA_FULL + 1
 };
 static_assert(8 * B_NUM + 16 <= 256, "barrier area");
 
@@ -111,6 +114,7 @@ __device__ __forceinline__ void bwd_setup(Ctx& c, uint8_t* smem_raw, int* status
     if (threadIdx.x == 0) {
         mbar_init(c.bar(B_RES_FULL), 1);
         mbar_init(c.bar(B_DONE), 1);
+        mbar_init(c.bar(B_RESA_FULL), 128 * BWD_WGS);
         for (int s = 0; s < MAX_NSTG; ++s) {
             mbar_init(c.bar(B_STG_FULL + s), 1);
             mbar_init(c.bar(B_STG_EMPTY + s), 1);
@@ -150,6 +154,37 @@ __device__ __forceinline__ void mma_scores(uint32_t d_tmem, uint32_t a_s, uint32
         const uint64_t da = make_smem_desc(a_s + (k >> 2) * BOX128 + (k & 3) * 32, 16, 1024);
         const uint64_t db = make_smem_desc(b_s + (k >> 2) * BOX64 + (k & 3) * 32, 16, 1024);
         umma_bf16(d_tmem, da, db, idesc, k > 0 ? 1u : 0u);
+    }
+}
+
+// Same with A[128 x 128] as bf16 in tensor memory (64 columns from `a_tmem`).
+__device__ __forceinline__ void mma_scores_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_s, uint32_t idesc) {
+#pragma unroll
+    for (int k = 0; k < HD / 16; ++k) {
+        const uint64_t db = make_smem_desc(b_s + (k >> 2) * BOX64 + (k & 3) * 32, 16, 1024);
+        umma_bf16_ts(d_tmem, a_tmem + static_cast<uint32_t>(k * 8), db, idesc, k > 0 ? 1u : 0u);
+    }
+}
+
+// Copies row `row` of a 128B-swizzled [128][128] bf16 tile (two [128][64] boxes) from shared memory into the 64
+// columns from `taddr` of this thread's TMEM lane: element k of the row lands in column k / 2, half k % 2.
+__device__ __forceinline__ void copy_row_to_tmem(uint32_t tile_s, int row, uint32_t taddr) {
+#pragma unroll
+    for (int bx = 0; bx < 2; ++bx) {
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+            uint32_t r[16];
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) {
+                const uint32_t chunk = static_cast<uint32_t>(hf * 4 + c4);
+                const uint32_t src = tile_s + static_cast<uint32_t>(bx) * BOX128 + static_cast<uint32_t>(row) * 128u +
+                                     (((chunk ^ static_cast<uint32_t>(row & 7)) & 7u) << 4);
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(r[4 * c4]), "=r"(r[4 * c4 + 1]), "=r"(r[4 * c4 + 2]), "=r"(r[4 * c4 + 3])
+                             : "r"(src));
+            }
+            tmem_st_32x16(taddr + static_cast<uint32_t>(bx * 32 + hf * 16), r);
+        }
     }
 }
 
@@ -213,7 +248,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_co
     const int it0 = windowed ? max(0, q0 + shift - p.window + 1) / 64 : 0;     // first key tile inside the window
     const int n_iter = kv_hi > 0 ? max(0, (kv_hi + 63) / 64 - it0) : 0;
     const int kvh = h / (p.H / p.Hkv);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;   // warp-uniform for the compiler
 
     if (n_iter == 0) {
         // no visible key: the gradient of these query rows is zero
@@ -264,44 +299,52 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_co
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            const uint32_t id_s = make_idesc_bf16(128, 64, false);
-            const uint32_t id_acc = make_idesc_bf16(128, 128, true);
-            bool ok = c.wait(B_RES_FULL, 0u);
-            if (!ok) c.fail(0x42);
-            auto accumulate = [&](int j) -> bool {     // dQ += dS_j K_j
-                const int b = j & 1, st = j % DQ_NSTG;
-                if (!c.wait(B_OP_FULL + b, static_cast<uint32_t>(j >> 1) & 1u)) return false;
-                tcgen05_fence_after();
-                const uint32_t k_s = c.base + OFF_STG + st * STAGE_BYTES;
-                mma_accum(c.tmem_base + 256u, c.tmem_base + static_cast<uint32_t>(b * 128 + 64), k_s, id_acc, j == 0);
+        // The whole warp runs the issue loop converged; only the tcgen05 instructions are predicated on one lane.
+        const bool leader = elect_one();
+        const uint32_t tmem = __shfl_sync(0xffffffffu, c.tmem_base, 0);
+        const uint32_t id_s = make_idesc_bf16(128, 64, false);
+        const uint32_t id_acc = make_idesc_bf16(128, 128, true);
+        bool ok = c.wait(B_RESA_FULL, 0u);     // Q and dO are in tensor memory (columns 384.. and 448..)
+        if (!ok && leader) c.fail(0x42);
+        tcgen05_fence_after();
+        const uint32_t q_t = tmem + 384u, do_t = tmem + 448u;
+        auto accumulate = [&](int j) -> bool {     // dQ += dS_j K_j
+            const int b = j & 1, st = j % DQ_NSTG;
+            if (!c.wait(B_OP_FULL + b, static_cast<uint32_t>(j >> 1) & 1u)) return false;
+            tcgen05_fence_after();
+            const uint32_t k_s = c.base + OFF_STG + st * STAGE_BYTES;
+            if (leader) {
+                mma_accum(tmem + 256u, tmem + static_cast<uint32_t>(b * 128 + 64), k_s, id_acc, j == 0);
                 umma_commit(c.bar(B_STG_EMPTY + st));
-                return true;
-            };
-            for (int i = 0; i < n_iter && ok; ++i) {
-                const int b = i & 1, st = i % DQ_NSTG;
-                // the score pair b is free: the MMAs that read tile i - 2 from it were issued before this point
-                ok = c.wait(B_STG_FULL + st, static_cast<uint32_t>(i / DQ_NSTG) & 1u);
-                if (!ok) {
-                    c.fail(0x43);
-                    break;
-                }
-                tcgen05_fence_after();
-                const uint32_t k_s = c.base + OFF_STG + st * STAGE_BYTES, v_s = k_s + SMALL_TILE;
-                mma_scores(c.tmem_base + static_cast<uint32_t>(b * 128), q_s, k_s, id_s);        // S
-                mma_scores(c.tmem_base + static_cast<uint32_t>(b * 128 + 64), do_s, v_s, id_s);  // dP
-                umma_commit(c.bar(B_ACC_FULL + b));
-                if (i > 0 && !accumulate(i - 1)) {
-                    c.fail(0x44);
-                    ok = false;
-                }
             }
-            if (ok && !accumulate(n_iter - 1)) {
-                c.fail(0x45);
+            return true;
+        };
+        for (int i = 0; i < n_iter && ok; ++i) {
+            const int b = i & 1, st = i % DQ_NSTG;
+            // the score pair b is free: the MMAs that read tile i - 2 from it were issued before this point
+            ok = c.wait(B_STG_FULL + st, static_cast<uint32_t>(i / DQ_NSTG) & 1u);
+            if (!ok) {
+                if (leader) c.fail(0x43);
+                break;
+            }
+            tcgen05_fence_after();
+            const uint32_t k_s = c.base + OFF_STG + st * STAGE_BYTES, v_s = k_s + SMALL_TILE;
+            if (leader) {
+                mma_scores_ts(tmem + static_cast<uint32_t>(b * 128), q_t, k_s, id_s);        // S
+                mma_scores_ts(tmem + static_cast<uint32_t>(b * 128 + 64), do_t, v_s, id_s);  // dP
+                umma_commit(c.bar(B_ACC_FULL + b));
+            }
+            if (i > 0 && !accumulate(i - 1)) {
+                if (leader) c.fail(0x44);
                 ok = false;
             }
-            if (ok) umma_commit(c.bar(B_DONE));
         }
+        if (ok && !accumulate(n_iter - 1)) {
+            if (leader) c.fail(0x45);
+            ok = false;
+        }
+        if (ok && leader) umma_commit(c.bar(B_DONE));
+        __syncwarp();
     } else {
         const int quad = warp & 3;                 // the TMEM lane quarter this warp may read
         const int cc = (warp - 2) >> 2;            // warpgroup = which half of the score columns
@@ -315,8 +358,15 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_co
         const float delta = row_ok ? p.delta[stat_idx] : 0.f;
         const int lim = p.causal ? min(k_len - 1, q_row + shift) : k_len - 1;
         const int lo = windowed ? q_row + shift - p.window + 1 : -(1 << 30);
-        bool ok = true;
-        for (int i = 0; i < n_iter; ++i) {
+        // one warpgroup moves Q, the other dO, from the TMA-written tiles into tensor memory
+        bool ok = warp_wait(c.bar(B_RES_FULL), 0u, c.abort_flag);
+        if (ok) {
+            copy_row_to_tmem(cc == 0 ? q_s : do_s, row, t_lane + (cc == 0 ? 384u : 448u));
+            tmem_st_wait();
+            tcgen05_fence_before();
+            mbar_arrive(c.bar(B_RESA_FULL));
+        }
+        for (int i = 0; ok && i < n_iter; ++i) {
             const int b = i & 1;
             const uint32_t ph = static_cast<uint32_t>(i >> 1) & 1u;
             const int kv0 = (it0 + i) * 64;
@@ -391,7 +441,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
     const int jt_hi = (q_hi + 63) / 64;
     const int per_head = max(0, jt_hi - jt_lo);
     const int n_iter = per_head * G;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;   // warp-uniform for the compiler
 
     if (n_iter == 0) {
         // no query sees these keys: zero gradients
@@ -449,46 +499,52 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            const uint32_t id_s = make_idesc_bf16(128, 64, false);
-            const uint32_t id_acc = make_idesc_bf16(128, 128, true);
-            bool ok = c.wait(B_RES_FULL, 0u);
-            if (!ok) c.fail(0x52);
-            auto accumulate = [&](int j) -> bool {     // dV += P^T dO_j ; dK += dS^T Q_j
-                const int b = j & 1, st = j % KV_NSTG;
-                if (!c.wait(B_OP_FULL + b, static_cast<uint32_t>(j >> 1) & 1u)) return false;
-                tcgen05_fence_after();
-                const uint32_t q_s = c.base + OFF_STG + st * STAGE_BYTES, do_s = q_s + SMALL_TILE;
-                const uint32_t pt_t = c.tmem_base + static_cast<uint32_t>(b * 128), dst_t = pt_t + 64u;
-                mma_accum(c.tmem_base + 256u, pt_t, do_s, id_acc, j == 0);
-                mma_accum(c.tmem_base + 384u, dst_t, q_s, id_acc, j == 0);
+        // The whole warp runs the issue loop converged; only the tcgen05 instructions are predicated on one lane.
+        const bool leader = elect_one();
+        const uint32_t tmem = __shfl_sync(0xffffffffu, c.tmem_base, 0);
+        const uint32_t id_s = make_idesc_bf16(128, 64, false);
+        const uint32_t id_acc = make_idesc_bf16(128, 128, true);
+        bool ok = c.wait(B_RES_FULL, 0u);
+        if (!ok && leader) c.fail(0x52);
+        auto accumulate = [&](int j) -> bool {     // dV += P^T dO_j ; dK += dS^T Q_j
+            const int b = j & 1, st = j % KV_NSTG;
+            if (!c.wait(B_OP_FULL + b, static_cast<uint32_t>(j >> 1) & 1u)) return false;
+            tcgen05_fence_after();
+            const uint32_t q_s = c.base + OFF_STG + st * STAGE_BYTES, do_s = q_s + SMALL_TILE;
+            const uint32_t pt_t = tmem + static_cast<uint32_t>(b * 128), dst_t = pt_t + 64u;
+            if (leader) {
+                mma_accum(tmem + 256u, pt_t, do_s, id_acc, j == 0);
+                mma_accum(tmem + 384u, dst_t, q_s, id_acc, j == 0);
                 umma_commit(c.bar(B_STG_EMPTY + st));
-                return true;
-            };
-            for (int i = 0; i < n_iter && ok; ++i) {
-                const int b = i & 1, st = i % KV_NSTG;
-                // the score pair b is free: the MMAs that read tile i - 2 from it were issued before this point
-                ok = c.wait(B_STG_FULL + st, static_cast<uint32_t>(i / KV_NSTG) & 1u);
-                if (!ok) {
-                    c.fail(0x53);
-                    break;
-                }
-                tcgen05_fence_after();
-                const uint32_t q_s = c.base + OFF_STG + st * STAGE_BYTES, do_s = q_s + SMALL_TILE;
-                mma_scores(c.tmem_base + static_cast<uint32_t>(b * 128), k_s, q_s, id_s);         // S^T
-                mma_scores(c.tmem_base + static_cast<uint32_t>(b * 128 + 64), v_s, do_s, id_s);   // dP^T
-                umma_commit(c.bar(B_ACC_FULL + b));
-                if (i > 0 && !accumulate(i - 1)) {
-                    c.fail(0x54);
-                    ok = false;
-                }
             }
-            if (ok && !accumulate(n_iter - 1)) {
-                c.fail(0x55);
+            return true;
+        };
+        for (int i = 0; i < n_iter && ok; ++i) {
+            const int b = i & 1, st = i % KV_NSTG;
+            // the score pair b is free: the MMAs that read tile i - 2 from it were issued before this point
+            ok = c.wait(B_STG_FULL + st, static_cast<uint32_t>(i / KV_NSTG) & 1u);
+            if (!ok) {
+                if (leader) c.fail(0x53);
+                break;
+            }
+            tcgen05_fence_after();
+            const uint32_t q_s = c.base + OFF_STG + st * STAGE_BYTES, do_s = q_s + SMALL_TILE;
+            if (leader) {
+                mma_scores(tmem + static_cast<uint32_t>(b * 128), k_s, q_s, id_s);         // S^T
+                mma_scores(tmem + static_cast<uint32_t>(b * 128 + 64), v_s, do_s, id_s);   // dP^T
+                umma_commit(c.bar(B_ACC_FULL + b));
+            }
+            if (i > 0 && !accumulate(i - 1)) {
+                if (leader) c.fail(0x54);
                 ok = false;
             }
-            if (ok) umma_commit(c.bar(B_DONE));
         }
+        if (ok && !accumulate(n_iter - 1)) {
+            if (leader) c.fail(0x55);
+            ok = false;
+        }
+        if (ok && leader) umma_commit(c.bar(B_DONE));
+        __syncwarp();
     } else {
         const int quad = warp & 3;                 // the TMEM lane quarter this warp may read
         const int cc = (warp - 2) >> 2;            // warpgroup = which half of the 64 query columns

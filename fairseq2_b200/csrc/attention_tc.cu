@@ -115,7 +115,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_ptr + 8 * NUM_BARS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_ptr + 8 * NUM_BARS + 8);
 
-    const int warp = threadIdx.x >> 5;
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);   // warp-uniform for the compiler
     const int lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
@@ -179,25 +179,32 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         }
     } else if (warp == 1) {
         // -------------------------------------------------------------- MMA issuer
-        if (lane == 0) {
-            const uint32_t idesc_s = make_idesc_bf16(128, 128, false);
-            const uint32_t idesc_pv = make_idesc_bf16(128, 128, true);
-            bool ok = mbar_wait_bounded(bar(BAR_Q_FULL), 0u, abort_flag, WAIT_LIMIT_NS);
-            if (!ok) {
-                if (!*abort_flag) report_status(status, kStatusTimeout | (0x21 << 8));
+        // The whole warp runs the issue loop converged and only the tcgen05 instructions are predicated on one lane,
+        // so that descriptors and addresses stay in uniform registers.
+        const bool leader = elect_one();
+        const uint32_t tmem = __shfl_sync(0xffffffffu, tmem_base, 0);
+        auto fail = [&](int code) {
+            if (leader) {
+                if (!*abort_flag) report_status(status, kStatusTimeout | (code << 8));
                 *abort_flag = 1;
             }
-            // PV(j) = P_j V_j into output buffer j & 1
-            auto issue_pv = [&](int j) -> bool {
-                const int b = j & 1;
-                const uint32_t ph = static_cast<uint32_t>(j >> 1) & 1u;
-                if (!mbar_wait_bounded(bar(BAR_V_FULL + b), ph, abort_flag, WAIT_LIMIT_NS)) return false;
-                if (!mbar_wait_bounded(bar(BAR_P_FULL + b), ph, abort_flag, WAIT_LIMIT_NS)) return false;
-                if (!mbar_wait_bounded(bar(BAR_PV_EMPTY + b), ph ^ 1u, abort_flag, WAIT_LIMIT_NS)) return false;
-                tcgen05_fence_after();
-                const uint32_t d_tmem = tmem_base + 256u + static_cast<uint32_t>(b * 128);
-                const uint32_t p_s = base + OFF_P + b * TILE_BYTES;
-                const uint32_t v_s = base + OFF_V + b * TILE_BYTES;
+        };
+        const uint32_t idesc_s = make_idesc_bf16(128, 128, false);
+        const uint32_t idesc_pv = make_idesc_bf16(128, 128, true);
+        bool ok = mbar_wait_bounded(bar(BAR_Q_FULL), 0u, abort_flag, WAIT_LIMIT_NS);
+        if (!ok) fail(0x21);
+        // PV(j) = P_j V_j into output buffer j & 1
+        auto issue_pv = [&](int j) -> bool {
+            const int b = j & 1;
+            const uint32_t ph = static_cast<uint32_t>(j >> 1) & 1u;
+            if (!mbar_wait_bounded(bar(BAR_V_FULL + b), ph, abort_flag, WAIT_LIMIT_NS)) return false;
+            if (!mbar_wait_bounded(bar(BAR_P_FULL + b), ph, abort_flag, WAIT_LIMIT_NS)) return false;
+            if (!mbar_wait_bounded(bar(BAR_PV_EMPTY + b), ph ^ 1u, abort_flag, WAIT_LIMIT_NS)) return false;
+            tcgen05_fence_after();
+            const uint32_t d_tmem = tmem + 256u + static_cast<uint32_t>(b * 128);
+            const uint32_t p_s = base + OFF_P + b * TILE_BYTES;
+            const uint32_t v_s = base + OFF_V + b * TILE_BYTES;
+            if (leader) {
 #pragma unroll
                 for (int k = 0; k < TK / 16; ++k) {
                     const uint64_t da = make_smem_desc(p_s + (k >> 2) * BOX_BYTES + (k & 3) * 32, 16, 1024);
@@ -206,22 +213,23 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
                 }
                 umma_commit(bar(BAR_PV_FULL + b));
                 umma_commit(bar(BAR_V_EMPTY + b));
-                return true;
-            };
-            for (int i = 0; i < n_iter && ok; ++i) {
-                const int b = i & 1;
-                const uint32_t ph = static_cast<uint32_t>(i >> 1) & 1u;
-                ok = mbar_wait_bounded(bar(BAR_K_FULL + b), ph, abort_flag, WAIT_LIMIT_NS) &&
-                     mbar_wait_bounded(bar(BAR_S_EMPTY + b), ph ^ 1u, abort_flag, WAIT_LIMIT_NS);
-                if (!ok) {
-                    if (!*abort_flag) report_status(status, kStatusTimeout | (0x22 << 8));
-                    *abort_flag = 1;
-                    break;
-                }
-                tcgen05_fence_after();
-                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(b * 128);
-                const uint32_t q_s = base + OFF_Q;
-                const uint32_t k_s = base + OFF_K + b * TILE_BYTES;
+            }
+            return true;
+        };
+        for (int i = 0; i < n_iter && ok; ++i) {
+            const int b = i & 1;
+            const uint32_t ph = static_cast<uint32_t>(i >> 1) & 1u;
+            ok = mbar_wait_bounded(bar(BAR_K_FULL + b), ph, abort_flag, WAIT_LIMIT_NS) &&
+                 mbar_wait_bounded(bar(BAR_S_EMPTY + b), ph ^ 1u, abort_flag, WAIT_LIMIT_NS);
+            if (!ok) {
+                fail(0x22);
+                break;
+            }
+            tcgen05_fence_after();
+            const uint32_t d_tmem = tmem + static_cast<uint32_t>(b * 128);
+            const uint32_t q_s = base + OFF_Q;
+            const uint32_t k_s = base + OFF_K + b * TILE_BYTES;
+            if (leader) {
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k) {
                     const uint32_t off = (k >> 2) * BOX_BYTES + (k & 3) * 32;
@@ -230,17 +238,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
                 }
                 umma_commit(bar(BAR_S_FULL + b));
                 umma_commit(bar(BAR_K_EMPTY + b));
-                if (i > 0 && !issue_pv(i - 1)) {
-                    if (!*abort_flag) report_status(status, kStatusTimeout | (0x23 << 8));
-                    *abort_flag = 1;
-                    ok = false;
-                }
             }
-            if (ok && !issue_pv(n_iter - 1)) {
-                if (!*abort_flag) report_status(status, kStatusTimeout | (0x24 << 8));
-                *abort_flag = 1;
+            if (i > 0 && !issue_pv(i - 1)) {
+                fail(0x23);
+                ok = false;
             }
         }
+        if (ok && !issue_pv(n_iter - 1)) fail(0x24);
+        __syncwarp();
     } else {
         // ----------------------------------------------------------------- softmax
         const int quad = warp & 3;                     // TMEM lane quadrant of this warp

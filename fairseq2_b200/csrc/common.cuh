@@ -24,6 +24,22 @@ __device__ __forceinline__ void report_status(int* status, int code) {
     }
 }
 
+// True in exactly one lane of a fully active warp. Code that issues tcgen05 / TMA instructions keeps the whole warp
+// converged and predicates only the instruction on this, so that the compiler can hold descriptors and addresses in
+// uniform registers; inside a divergent `if (lane == 0)` every operand is moved to a uniform register per
+// instruction, which costs tens of cycles per MMA.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 __device__ __forceinline__ uint64_t global_timer_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
