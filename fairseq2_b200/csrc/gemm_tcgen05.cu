@@ -302,7 +302,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_ptr + 8 * (2 * STAGES + 4));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_ptr + 8 * (2 * STAGES + 4) + 8);
 
-    const int warp = threadIdx.x >> 5;
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);   // warp-uniform for the compiler
     const int lane = threadIdx.x & 31;
 
     const int num_m = GROUPED == 1 ? *ga.num_m_tiles : (M + BM - 1) / BM;
@@ -413,39 +413,48 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------- MMA issuer
-        if (lane == 0) {
-            const uint32_t idesc = make_idesc(A_MN, B_MN);
-            int stage = 0;
-            uint32_t phase = 0;
-            int acc = 0;
-            uint32_t acc_phase = 0;
-            bool ok = true;
-            for (int t = first_tile; t < num_tiles && ok; t += tile_stride) {
-                if (!mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
-                    if (!*abort_flag) report_status(status, kStatusTimeout | (2 << 8));
-                    *abort_flag = 1;
+        // The whole warp runs the loop converged and only the tcgen05 instructions are predicated on one elected
+        // lane: descriptors and addresses then stay in uniform registers. Inside a divergent `if (lane == 0)` every
+        // operand is moved to a uniform register per instruction, which costs tens of cycles per MMA.
+        const bool issue = elect_one();
+        const uint32_t tmem = __shfl_sync(0xffffffffu, tmem_base, 0);
+        auto fail = [&](int code) {
+            if (issue) {
+                if (!*abort_flag) report_status(status, kStatusTimeout | (code << 8));
+                *abort_flag = 1;
+            }
+        };
+        const uint32_t idesc = make_idesc(A_MN, B_MN);
+        int stage = 0;
+        uint32_t phase = 0;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int t = first_tile; t < num_tiles && ok; t += tile_stride) {
+            if (!mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
+                fail(2);
+                break;
+            }
+            tcgen05_fence_after();
+            const uint32_t d_tmem = tmem + static_cast<uint32_t>(acc * BN);
+            int kb_begin = (t / num_mn) * kb_per_split;
+            int kb_end = min(num_kb_total, kb_begin + kb_per_split);
+            if constexpr (GROUPED == 1) { kb_begin = 0; kb_end = num_kb_total; }
+            if constexpr (GROUPED == 2) {
+                const GroupedTile gt = grouped_tile<GATHER>(t, num_m, num_n, M, ga);
+                kb_begin = gt.kb_begin;
+                kb_end = gt.kb_end;
+            }
+            for (int kb = kb_begin; kb < kb_end; ++kb) {
+                if (!mbar_wait_bounded(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
+                    fail(3);
+                    ok = false;
                     break;
                 }
                 tcgen05_fence_after();
-                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-                int kb_begin = (t / num_mn) * kb_per_split;
-                int kb_end = min(num_kb_total, kb_begin + kb_per_split);
-                if constexpr (GROUPED == 1) { kb_begin = 0; kb_end = num_kb_total; }
-                if constexpr (GROUPED == 2) {
-                    const GroupedTile gt = grouped_tile<GATHER>(t, num_m, num_n, M, ga);
-                    kb_begin = gt.kb_begin;
-                    kb_end = gt.kb_end;
-                }
-                for (int kb = kb_begin; kb < kb_end; ++kb) {
-                    if (!mbar_wait_bounded(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
-                        if (!*abort_flag) report_status(status, kStatusTimeout | (3 << 8));
-                        *abort_flag = 1;
-                        ok = false;
-                        break;
-                    }
-                    tcgen05_fence_after();
-                    const uint32_t a_s = base + stage * STAGE_BYTES;
-                    const uint32_t b_s = a_s + A_BYTES;
+                const uint32_t a_s = base + stage * STAGE_BYTES;
+                const uint32_t b_s = a_s + A_BYTES;
+                if (issue) {
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         uint64_t da, db;
@@ -456,17 +465,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
                         umma_bf16(d_tmem, da, db, idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
                     }
                     umma_commit(empty_bar(stage));
-                    if (++stage == STAGES) {
-                        stage = 0;
-                        phase ^= 1u;
-                    }
                 }
-                if (!ok) break;
-                umma_commit(tfull_bar(acc));
-                acc ^= 1;
-                if (acc == 0) acc_phase ^= 1u;
+                if (++stage == STAGES) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
             }
+            if (!ok) break;
+            if (issue) umma_commit(tfull_bar(acc));
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1u;
         }
+        __syncwarp();
     } else {
         // ------------------------------------------------------------ epilogue
         const int q = warp & 3;                       // TMEM lane quadrant of this warp
