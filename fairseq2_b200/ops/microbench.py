@@ -14,6 +14,7 @@ from __future__ import annotations
 import argparse
 import json
 import math
+import time
 from typing import Any, Callable
 
 import torch
@@ -41,6 +42,25 @@ def _time(fn: Callable[[], Any], iters: int, warmup: int) -> float:
     return ts[len(ts) // 2]
 
 
+def _time_sustained(fn: Callable[[], Any], seconds: float) -> float:
+    """Average time of `fn` launched back to back for `seconds` (the GPU settles at its power-capped clock)."""
+    fn()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n, t0 = 0, time.perf_counter()
+    s.record()
+    while True:
+        for _ in range(50):
+            fn()
+        n += 50
+        torch.cuda.synchronize()
+        if time.perf_counter() - t0 >= seconds:
+            break
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / n
+
+
 def _emit(case: str, ms: float, *, flops: float | None = None, nbytes: float | None = None, **kw: Any) -> None:
     r: dict[str, Any] = {"case": case, "ms": round(ms, 4), **kw}
     if flops is not None:
@@ -64,6 +84,14 @@ def bench_gemm(a: argparse.Namespace) -> None:
         ref = torch.matmul(A, B)
         r["rel_err"] = float((out.float() - ref.float()).norm() / ref.float().norm())
         r["ms_cublas"] = round(_time(lambda: torch.matmul(A, B, out=ref), a.iters, a.warmup), 4)
+    if a.sustained > 0:
+        # seconds-long loops under the power cap: the figure a kernel reaches inside a long training step
+        fl = 2.0 * M * N * K
+        r["tflops_sustained"] = round(fl / _time_sustained(lambda: ext.gemm_bf16(x, w, out, a.a_mn, a.b_mn, False),
+                                                            a.sustained) / 1e9, 1)
+        if a.compare:
+            r["tflops_cublas_sustained"] = round(fl / _time_sustained(lambda: torch.matmul(A, B, out=ref),
+                                                                      a.sustained) / 1e9, 1)
     _emit("gemm", ms, flops=2.0 * M * N * K, M=M, N=N, K=K, a_mn=a.a_mn, b_mn=a.b_mn, **r)
 
 
@@ -215,6 +243,8 @@ def main() -> None:
     ap.add_argument("--a-mn", action="store_true", help="A is stored [K, M]")
     ap.add_argument("--b-mn", action="store_true", help="B is stored [K, N]")
     ap.add_argument("--compare", action="store_true", help="also time torch.matmul and report the relative error")
+    ap.add_argument("--sustained", type=float, default=0.0,
+                    help="gemm: also loop back to back for this many seconds and report the power-capped throughput")
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--seq-len", type=int, default=8192)
     ap.add_argument("--heads", type=int, default=32)
