@@ -24,13 +24,19 @@
 // Every barrier wait is bounded (2 s); a wait that gives up records a code in
 // a host-visible status word, raises a CTA-wide abort flag, and all roles fall
 // through to the common teardown that frees TMEM.
+//
+// Plain GEMMs with enough tiles run on the CTA-pair variant of this kernel (`gemm_pair_kernel`,
+// `cta_group::2`, 256 x 256 tile per pair of SMs) further down; the fused all-gather / reduce-scatter
+// epilogues and the grouped modes use the single-CTA kernel.
 
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "gemm_tcgen05.h"
@@ -614,6 +620,346 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
     if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+// ================================================================= CTA-pair kernel
+// The plain GEMM on pairs of CTAs (`cta_group::2`): a cluster of two CTAs on neighbouring SMs computes a 256 x 256
+// tile with ONE stream of tcgen05.mma issued by the first CTA of the pair. Each CTA stages its own 128 rows of A and
+// only ITS HALF (128 rows) of the B tile, so per MMA it reads 8 KB of operands from shared memory instead of 12 KB and
+// loads a third less from L2; the accumulator rows of each CTA stay in its own tensor memory and its own epilogue
+// warps write them out. Under the power cap (where a long training step runs) this is what separates the
+// single-CTA kernel from a library GEMM.
+//
+// Synchronisation across the pair: both producers issue their TMA loads against the FIRST CTA's "full" barrier
+// (`cp.async.bulk.tensor ... cta_group::2`, one expect-tx of the pair's bytes by the first CTA); the issuer releases
+// a stage and publishes an accumulator with commits that arrive on the barrier of the same name in both CTAs; the
+// second CTA's epilogue threads arrive on the first CTA's "accumulator drained" barrier through its cluster address.
+// Every wait is bounded as in the single-CTA kernel.
+constexpr int STAGES2 = 6;
+constexpr int B2_BYTES = 128 * BK * 2;               // this CTA's half of the 256-row B tile
+constexpr int STAGE2_BYTES = A_BYTES + B2_BYTES;     // 32 KB
+constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 2 * EPI_BYTES + BAR_BYTES + 1024;
+static_assert(SMEM2_BYTES <= 232448, "shared memory budget of one CTA exceeded");
+
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// The address, in the cluster's shared window, of `addr` in the shared memory of CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t cluster_map(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+// TMA load into this CTA's shared memory whose bytes are counted on a barrier of the pair's first CTA.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const void* tmap, uint32_t bar_cluster_addr, int x,
+                                                 int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_dst), "l"(tmap), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Arrives, once the MMAs issued so far are done, on the barrier at offset `bar` in BOTH CTAs of the pair (two
+// commits: this CTA's barrier and, through its cluster address, the partner's).
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(cluster_map(bar, 1)) : "memory");
+}
+
+__device__ __forceinline__ uint32_t make_idesc_pair(bool a_mn, bool b_mn) {
+    uint32_t d = 0;
+    d |= 1u << 4;                         // D format: f32
+    d |= 1u << 7;                         // A format: bf16
+    d |= 1u << 10;                        // B format: bf16
+    d |= (a_mn ? 1u : 0u) << 15;
+    d |= (b_mn ? 1u : 0u) << 16;
+    d |= static_cast<uint32_t>(256 >> 3) << 17;   // N
+    d |= static_cast<uint32_t>(256 >> 4) << 24;   // M of the pair
+    return d;
+}
+
+template <bool A_MN, bool B_MN, bool OUT_F32>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 const __grid_constant__ CUtensorMap tma_c, int M, int N, int K, int accumulate, int* status) {
+    const uint32_t cta = cluster_cta_rank();          // 0 = the CTA that issues the MMAs
+    const int first_tile = static_cast<int>(blockIdx.x >> 1);
+    const int tile_stride = static_cast<int>(gridDim.x >> 1);
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* smem = smem_raw + (base - raw);
+
+    const uint32_t epi_base = base + STAGES2 * STAGE2_BYTES;
+    uint8_t* bar_ptr = smem + STAGES2 * STAGE2_BYTES + 2 * EPI_BYTES;
+    const uint32_t bar_base = smem_u32(bar_ptr);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES2 + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES2 + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES2 + 2 + a); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_ptr + 8 * (2 * STAGES2 + 4));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_ptr + 8 * (2 * STAGES2 + 4) + 8);
+
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
+    const int lane = threadIdx.x & 31;
+
+    constexpr int PM = 2 * BM;                         // rows of the pair's tile
+    const int num_m = (M + PM - 1) / PM;
+    const int num_n = (N + BN - 1) / BN;
+    const int k_splits = (accumulate >> 8) > 1 ? (accumulate >> 8) : 1;
+    accumulate &= 1;
+    const int num_mn = num_m * num_n;
+    const int num_tiles = num_mn * k_splits;
+    const int num_kb_total = (K + BK - 1) / BK;
+    const int kb_per_split = (num_kb_total + k_splits - 1) / k_splits;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES2; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 256);             // the epilogue threads of both CTAs
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tmap(&tma_a);
+        prefetch_tmap(&tma_b);
+        prefetch_tmap(&tma_c);
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(const_cast<uint32_t*>(tmem_slot))), "r"(static_cast<uint32_t>(TMEM_COLS)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                // the partner's barriers exist before anything signals them
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer (both CTAs)
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = first_tile; t < num_tiles && ok; t += tile_stride) {
+                int mt, nt;
+                tile_coords(t % num_mn, num_m, num_n, mt, nt);
+                const int m0 = mt * PM + static_cast<int>(cta) * BM;       // this CTA's rows of A
+                const int n0 = nt * BN + static_cast<int>(cta) * (BN / 2); // this CTA's half of B
+                const int kb_begin = (t / num_mn) * kb_per_split;
+                const int kb_end = min(num_kb_total, kb_begin + kb_per_split);
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
+                    if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
+                        if (!*abort_flag) report_status(status, kStatusTimeout | (0x11 << 8));
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t a_s = base + stage * STAGE2_BYTES;
+                    const uint32_t b_s = a_s + A_BYTES;
+                    if (cta == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * STAGE2_BYTES);
+                    const uint32_t fb = cluster_map(full_bar(stage), 0);
+                    const int k0 = kb * BK;
+                    if constexpr (!A_MN) {
+                        tma_load_2d_pair(a_s, &tma_a, fb, k0, m0);
+                    } else {
+#pragma unroll
+                        for (int h = 0; h < BM / 64; ++h) tma_load_2d_pair(a_s + h * MN_BLOCK_BYTES, &tma_a, fb, m0 + h * 64, k0);
+                    }
+                    if constexpr (!B_MN) {
+                        tma_load_2d_pair(b_s, &tma_b, fb, k0, n0);
+                    } else {
+#pragma unroll
+                        for (int h = 0; h < BN / 2 / 64; ++h)
+                            tma_load_2d_pair(b_s + h * MN_BLOCK_BYTES, &tma_b, fb, n0 + h * 64, k0);
+                    }
+                    if (++stage == STAGES2) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------- MMA issuer (first CTA of the pair only)
+        if (cta == 0) {
+            const bool issue = elect_one();
+            const uint32_t tmem = __shfl_sync(0xffffffffu, tmem_base, 0);
+            auto fail = [&](int code) {
+                if (issue) {
+                    if (!*abort_flag) report_status(status, kStatusTimeout | (code << 8));
+                    *abort_flag = 1;
+                }
+            };
+            const uint32_t idesc = make_idesc_pair(A_MN, B_MN);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int t = first_tile; t < num_tiles && ok; t += tile_stride) {
+                if (!mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
+                    fail(0x12);
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem + static_cast<uint32_t>(acc * BN);
+                const int kb_begin = (t / num_mn) * kb_per_split;
+                const int kb_end = min(num_kb_total, kb_begin + kb_per_split);
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
+                    if (!mbar_wait_bounded(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
+                        fail(0x13);
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const uint32_t a_s = base + stage * STAGE2_BYTES;
+                    const uint32_t b_s = a_s + A_BYTES;
+                    if (issue) {
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k) {
+                            uint64_t da, db;
+                            if constexpr (!A_MN) da = make_smem_desc(a_s + k * UMMA_K * 2, 16, 1024);
+                            else da = make_smem_desc(a_s + k * UMMA_K * 128, MN_BLOCK_BYTES, 1024);
+                            if constexpr (!B_MN) db = make_smem_desc(b_s + k * UMMA_K * 2, 16, 1024);
+                            else db = make_smem_desc(b_s + k * UMMA_K * 128, MN_BLOCK_BYTES, 1024);
+                            umma_bf16_pair(d_tmem, da, db, idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
+                        }
+                        umma_commit_pair(empty_bar(stage));
+                    }
+                    if (++stage == STAGES2) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                if (issue) umma_commit_pair(tfull_bar(acc));
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1u;
+            }
+            __syncwarp();
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (both CTAs, own accumulator rows)
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        const bool leader = (threadIdx.x == 64);
+        constexpr int CHUNK_COLS = OUT_F32 ? 32 : 64;
+        constexpr int NCHUNK = BN / CHUNK_COLS;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        int buf = 0;
+        for (int t = first_tile; t < num_tiles; t += tile_stride) {
+            int mt, nt;
+            tile_coords(t % num_mn, num_m, num_n, mt, nt);
+            const int m0 = mt * PM + static_cast<int>(cta) * BM, n0 = nt * BN;
+            const bool got = mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS);
+            if (epi_bar_or(!got)) {
+                if (leader && !*abort_flag) report_status(status, kStatusTimeout | (0x14 << 8));
+                *abort_flag = 1;
+                break;
+            }
+            tcgen05_fence_after();
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
+#pragma unroll 1
+            for (int c = 0; c < NCHUNK; ++c) {
+                const int col0 = c * CHUNK_COLS;
+                if (n0 + col0 >= N) break;  // uniform over the CTA
+                if (leader) tma_wait_group_read<1>();
+                epi_bar_sync();
+                const uint32_t sbuf = epi_base + buf * EPI_BYTES;
+                const uint32_t srow = sbuf + row * 128;
+                if constexpr (OUT_F32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(t_row + col0, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const uint32_t dst = srow + (((j ^ (row & 7)) & 7) << 4);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v[4 * j]),
+                                     "r"(v[4 * j + 1]), "r"(v[4 * j + 2]), "r"(v[4 * j + 3])
+                                     : "memory");
+                    }
+                } else {
+                    uint32_t v[64];
+                    tmem_ld_32x32(t_row + col0, v);
+                    tmem_ld_32x32(t_row + col0 + 32, v + 32);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        uint32_t pk[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[8 * j + 2 * e]),
+                                                                      __uint_as_float(v[8 * j + 2 * e + 1]));
+                            pk[e] = *reinterpret_cast<uint32_t*>(&h);
+                        }
+                        const uint32_t dst = srow + (((j ^ (row & 7)) & 7) << 4);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[0]), "r"(pk[1]),
+                                     "r"(pk[2]), "r"(pk[3])
+                                     : "memory");
+                    }
+                }
+                fence_proxy_async_smem();
+                epi_bar_sync();
+                if (leader && m0 < M) {
+                    if (accumulate) tma_reduce_add_2d(&tma_c, sbuf, n0 + col0, m0);
+                    else tma_store_2d(&tma_c, sbuf, n0 + col0, m0);
+                    tma_commit_group();
+                }
+                buf ^= 1;
+            }
+            tcgen05_fence_before();
+            // "accumulator drained" lives in the first CTA of the pair
+            if (cta == 0) mbar_arrive(tempty_bar(acc));
+            else mbar_arrive_cluster(cluster_map(tempty_bar(acc), 0));
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1u;
+        }
+        if (leader) tma_wait_group<0>();
+    }
+
+    // -------------------------------------------------------------- teardown
+    __syncthreads();
+    if (*abort_flag) {
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+        __syncthreads();
+    }
+    cluster_sync_all();       // neither CTA leaves while its partner may still signal its barriers or read its tiles
+    tcgen05_fence_after();
+    if (warp == 1)
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(static_cast<uint32_t>(TMEM_COLS)) : "memory");
+}
+
 // ---------------------------------------------------------------- host side
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -684,6 +1030,54 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
     return cudaGetLastError();
 }
 
+// Launch of the CTA-pair kernel: clusters of two CTAs, as many pairs as the device can keep resident at once (a pair
+// needs two free SMs of one GPC, so this can be fewer than num_sms / 2).
+template <bool A_MN, bool B_MN, bool OUT_F32>
+cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, int M, int N, int K,
+                        int accumulate, int* status, int num_sms, cudaStream_t stream, int k_splits) {
+    auto kern = gemm_pair_kernel<A_MN, B_MN, OUT_F32>;
+    static int max_pairs = 0;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = SMEM2_BYTES;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (max_pairs == 0) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
+        if (e != cudaSuccess) return e;
+        cfg.gridDim = dim3(static_cast<unsigned>(num_sms & ~1));
+        int n = 0;
+        e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+        if (e != cudaSuccess) return e;
+        if (n < 1) return cudaErrorInvalidConfiguration;
+        max_pairs = n;
+    }
+    const int num_kb = (K + BK - 1) / BK;
+    if (k_splits > num_kb) k_splits = num_kb;
+    if (k_splits > 1) {
+        const int per = (num_kb + k_splits - 1) / k_splits;
+        k_splits = (num_kb + per - 1) / per;
+    }
+    if (k_splits < 1) k_splits = 1;
+    const int num_tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN) * k_splits;
+    const int pairs = std::min(std::min(num_tiles, max_pairs), num_sms / 2);
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+    return cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, M, N, K, (accumulate & 1) | (k_splits << 8), status);
+}
+
+// The pair kernel is used for plain GEMMs that are large enough to fill the device with 256 x 256 tiles;
+// FAIRSEQ2_B200_GEMM_PAIR=0 selects the single-CTA kernel for them as well.
+bool pair_kernel_enabled() {
+    const char* e = std::getenv("FAIRSEQ2_B200_GEMM_PAIR");      // read per call: tests switch it
+    return e == nullptr || e[0] != '0';
+}
+
 }  // namespace
 
 const char* gemm_bf16_tcgen05(const void* a, const void* b, void* c, int M, int N, int K, bool a_mn, bool b_mn,
@@ -712,6 +1106,19 @@ const char* gemm_bf16_tcgen05_view(const void* a, long long lda, long long a_row
     if (!ok) return g_tmap_err;
     cudaError_t e;
     const int acc = accumulate ? 1 : 0;
+    const long long tiles256 = static_cast<long long>((M + 255) / 256) * ((N + 255) / 256) * (k_splits > 1 ? k_splits : 1);
+    if (pair_kernel_enabled() && tiles256 >= num_sms / 2) {
+        // each CTA of a pair loads 128 rows of a K-major B
+        if (!b_mn && !make_tmap(&tb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, br, K, 128, BK, ldb)) return g_tmap_err;
+#define FS2_LAUNCH2(AM, BMN, F32) e = launch_pair<AM, BMN, F32>(ta, tb, tc, M, N, K, acc, status, num_sms, stream, k_splits)
+        if (!a_mn && !b_mn) { if (out_f32) FS2_LAUNCH2(false, false, true); else FS2_LAUNCH2(false, false, false); }
+        else if (!a_mn && b_mn) { if (out_f32) FS2_LAUNCH2(false, true, true); else FS2_LAUNCH2(false, true, false); }
+        else if (a_mn && !b_mn) { if (out_f32) FS2_LAUNCH2(true, false, true); else FS2_LAUNCH2(true, false, false); }
+        else { if (out_f32) FS2_LAUNCH2(true, true, true); else FS2_LAUNCH2(true, true, false); }
+#undef FS2_LAUNCH2
+        if (e != cudaSuccess) return cudaGetErrorString(e);
+        return nullptr;
+    }
 #define FS2_LAUNCH(AM, BMN, F32) e = launch<AM, BMN, F32>(ta, tb, tc, M, N, K, acc, status, num_sms, stream, k_splits)
     if (!a_mn && !b_mn) { if (out_f32) FS2_LAUNCH(false, false, true); else FS2_LAUNCH(false, false, false); }
     else if (!a_mn && b_mn) { if (out_f32) FS2_LAUNCH(false, true, true); else FS2_LAUNCH(false, true, false); }

@@ -67,8 +67,11 @@ def test_gemm_accumulate() -> None:
     assert _rel_err(outb, ref) < 1e-2
 
 
-def test_gemm_large_persistent() -> None:
-    """More tiles than SMs: exercises the persistent loop, both accumulators and every stage phase."""
+@pytest.mark.parametrize("pair", ["0", "1"])
+def test_gemm_large_persistent(pair: str, monkeypatch: pytest.MonkeyPatch) -> None:
+    """More tiles than SMs: exercises the persistent loop, both accumulators and every stage phase (single-CTA kernel
+    and CTA-pair kernel)."""
+    monkeypatch.setenv("FAIRSEQ2_B200_GEMM_PAIR", pair)
     torch.manual_seed(2)
     M, N, K = 4096, 4096, 2048
     a = torch.randn((M, K), device=DEV, dtype=torch.bfloat16)
@@ -76,6 +79,27 @@ def test_gemm_large_persistent() -> None:
     out = gemm(a, b)
     ref = torch.matmul(a, b.t())
     assert _rel_err(out, ref) < 5e-3
+
+
+@pytest.mark.parametrize("a_mn", [False, True])
+@pytest.mark.parametrize("b_mn", [False, True])
+def test_gemm_cta_pair_kernel(a_mn: bool, b_mn: bool, monkeypatch: pytest.MonkeyPatch) -> None:
+    """The `cta_group::2` kernel (two CTAs per 256 x 256 tile): all operand layouts, a ragged M and N, bf16 and fp32
+    outputs, accumulation, against an fp32 matmul."""
+    monkeypatch.setenv("FAIRSEQ2_B200_GEMM_PAIR", "1")
+    torch.manual_seed(12)
+    M, N, K = 4096 + 136, 4096 + 72, 576                 # 17 x 17 tiles of 256 x 256, 9 K blocks
+    a = torch.randn((K, M) if a_mn else (M, K), device=DEV, dtype=torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), device=DEV, dtype=torch.bfloat16)
+    ref = gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+    out = torch.empty((M, N), device=DEV, dtype=torch.bfloat16)
+    require_ext().gemm_bf16(a, b, out, a_mn, b_mn, False)
+    assert require_ext().read_status() == 0
+    assert _rel_err(out, ref) < 5e-3
+    out32 = torch.randn((M, N), device=DEV, dtype=torch.float32)
+    base = out32.clone()
+    require_ext().gemm_bf16(a, b, out32, a_mn, b_mn, True)
+    assert _rel_err(out32, base + ref) < 1e-4
 
 
 def test_linear_autograd() -> None:
