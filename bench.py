@@ -97,6 +97,17 @@ def _trace_steps(args: argparse.Namespace, step_fn, batches, rank: int, record: 
     path = f"{args.trace}.rank{rank}.json"
     with open(path, "w") as fp:
         json.dump(rows, fp)
+    # per-kernel totals, milliseconds per step (the trace covers len(batches) steps)
+    totals: dict[str, list[float]] = {}
+    for r in rows:
+        t = totals.setdefault(r["name"], [0.0, 0])
+        t[0] += r["dur"] / 1000.0 / len(batches)
+        t[1] += 1
+    with open(f"{args.trace}.rank{rank}.kernels.txt", "w") as fp:
+        fp.write(f"# kernel time per step (torch.profiler CUDA activity, {len(batches)} steps averaged)\n")
+        fp.write(f"TOTAL {sum(t[0] for t in totals.values()):.1f} ms/step\n")
+        for name, (ms, n) in sorted(totals.items(), key=lambda kv: -kv[1][0])[:40]:
+            fp.write(f"{ms:9.2f} ms {n // len(batches):6d}x  {name}\n")
 
 
 def run_ours(args: argparse.Namespace) -> None:
