@@ -704,7 +704,8 @@ __device__ __forceinline__ uint32_t make_idesc_pair(bool a_mn, bool b_mn) {
 template <bool A_MN, bool B_MN, bool OUT_F32>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                 const __grid_constant__ CUtensorMap tma_c, int M, int N, int K, int accumulate, int* status) {
+                 const __grid_constant__ CUtensorMap tma_c, int M, int N, int K, int accumulate, int tail_splits,
+                 int* status) {
     const uint32_t cta = cluster_cta_rank();          // 0 = the CTA that issues the MMAs
     const int first_tile = static_cast<int>(blockIdx.x >> 1);
     const int tile_stride = static_cast<int>(gridDim.x >> 1);
@@ -732,9 +733,35 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     const int k_splits = (accumulate >> 8) > 1 ? (accumulate >> 8) : 1;
     accumulate &= 1;
     const int num_mn = num_m * num_n;
-    const int num_tiles = num_mn * k_splits;
     const int num_kb_total = (K + BK - 1) / BK;
     const int kb_per_split = (num_kb_total + k_splits - 1) / k_splits;
+    // Work units. Normally unit u is output tile u % num_mn over the K range of split u / num_mn. With
+    // `tail_splits` > 1 (no global split-K) the tiles of the last, partial wave are each cut into `tail_splits`
+    // K slices that are reduce-added into C, so that the pairs which would idle in that wave share its work.
+    const int full_tiles = tail_splits > 1 ? (num_mn / tile_stride) * tile_stride : num_mn;
+    const int kb_per_tail = tail_splits > 1 ? (num_kb_total + tail_splits - 1) / tail_splits : num_kb_total;
+    const int num_tiles = tail_splits > 1 ? full_tiles + (num_mn - full_tiles) * tail_splits : num_mn * k_splits;
+    auto unit = [&](int u, int& tile, int& kb_begin, int& kb_end, int& acc_flag) {
+        if (tail_splits > 1) {
+            if (u < full_tiles) {
+                tile = u;
+                kb_begin = 0;
+                kb_end = num_kb_total;
+                acc_flag = accumulate;
+            } else {
+                const int v = u - full_tiles;
+                tile = full_tiles + v / tail_splits;
+                kb_begin = (v % tail_splits) * kb_per_tail;
+                kb_end = min(num_kb_total, kb_begin + kb_per_tail);
+                acc_flag = 1;
+            }
+        } else {
+            tile = u % num_mn;
+            kb_begin = (u / num_mn) * kb_per_split;
+            kb_end = min(num_kb_total, kb_begin + kb_per_split);
+            acc_flag = accumulate;
+        }
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES2; ++s) {
@@ -769,12 +796,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             uint32_t phase = 0;
             bool ok = true;
             for (int t = first_tile; t < num_tiles && ok; t += tile_stride) {
-                int mt, nt;
-                tile_coords(t % num_mn, num_m, num_n, mt, nt);
+                int tile, kb_begin, kb_end, acc_flag, mt, nt;
+                unit(t, tile, kb_begin, kb_end, acc_flag);
+                tile_coords(tile, num_m, num_n, mt, nt);
                 const int m0 = mt * PM + static_cast<int>(cta) * BM;       // this CTA's rows of A
                 const int n0 = nt * BN + static_cast<int>(cta) * (BN / 2); // this CTA's half of B
-                const int kb_begin = (t / num_mn) * kb_per_split;
-                const int kb_end = min(num_kb_total, kb_begin + kb_per_split);
                 for (int kb = kb_begin; kb < kb_end; ++kb) {
                     if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
                         if (!*abort_flag) report_status(status, kStatusTimeout | (0x11 << 8));
@@ -831,8 +857,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 }
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem + static_cast<uint32_t>(acc * BN);
-                const int kb_begin = (t / num_mn) * kb_per_split;
-                const int kb_end = min(num_kb_total, kb_begin + kb_per_split);
+                int tile, kb_begin, kb_end, acc_flag;
+                unit(t, tile, kb_begin, kb_end, acc_flag);
                 for (int kb = kb_begin; kb < kb_end; ++kb) {
                     if (!mbar_wait_bounded(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
                         fail(0x13);
@@ -877,8 +903,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         uint32_t acc_phase = 0;
         int buf = 0;
         for (int t = first_tile; t < num_tiles; t += tile_stride) {
-            int mt, nt;
-            tile_coords(t % num_mn, num_m, num_n, mt, nt);
+            int tile, kb_begin, kb_end, acc_flag, mt, nt;
+            unit(t, tile, kb_begin, kb_end, acc_flag);
+            tile_coords(tile, num_m, num_n, mt, nt);
             const int m0 = mt * PM + static_cast<int>(cta) * BM, n0 = nt * BN;
             const bool got = mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS);
             if (epi_bar_or(!got)) {
@@ -930,7 +957,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 fence_proxy_async_smem();
                 epi_bar_sync();
                 if (leader && m0 < M) {
-                    if (accumulate) tma_reduce_add_2d(&tma_c, sbuf, n0 + col0, m0);
+                    if (acc_flag) tma_reduce_add_2d(&tma_c, sbuf, n0 + col0, m0);
                     else tma_store_2d(&tma_c, sbuf, n0 + col0, m0);
                     tma_commit_group();
                 }
@@ -1034,7 +1061,8 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
 // needs two free SMs of one GPC, so this can be fewer than num_sms / 2).
 template <bool A_MN, bool B_MN, bool OUT_F32>
 cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, int M, int N, int K,
-                        int accumulate, int* status, int num_sms, cudaStream_t stream, int k_splits) {
+                        int accumulate, int* status, int num_sms, cudaStream_t stream, int k_splits,
+                        void* dense_c, size_t c_elem_bytes) {
     auto kern = gemm_pair_kernel<A_MN, B_MN, OUT_F32>;
     static int max_pairs = 0;
     cudaLaunchAttribute attr[1];
@@ -1065,10 +1093,34 @@ cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUte
         k_splits = (num_kb + per - 1) / per;
     }
     if (k_splits < 1) k_splits = 1;
-    const int num_tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN) * k_splits;
+    const int num_mn = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+    const int num_tiles = num_mn * k_splits;
     const int pairs = std::min(std::min(num_tiles, max_pairs), num_sms / 2);
     cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
-    return cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, M, N, K, (accumulate & 1) | (k_splits << 8), status);
+    // Partial last wave: cut its tiles along K so that every pair has work (see the kernel). Worth it when the
+    // time saved exceeds that of zeroing C, which the reduce-adds of the slices need unless C is accumulated into.
+    int tail_splits = 1;
+    const int rem = num_mn % pairs;
+    if (k_splits == 1 && num_mn > pairs && rem > 0 && (accumulate || dense_c != nullptr)) {
+        int sp = std::min(std::min(pairs / rem, 4), num_kb / 8);
+        if (sp > 1) {
+            const int per = (num_kb + sp - 1) / sp;
+            sp = (num_kb + per - 1) / per;                      // no empty slice
+        }
+        if (sp > 1) {
+            const double tile_us = 2.0 * 256 * 256 * K / (1.35e15 / 74) * 1e6;
+            const double saved_us = tile_us * (1.0 - 1.0 / sp);
+            const double zero_us = accumulate ? 0.0 : 2.0 + static_cast<double>(M) * N * c_elem_bytes / 5.0e6;
+            if (saved_us > 1.5 * zero_us) {
+                tail_splits = sp;
+                if (!accumulate) {
+                    cudaError_t e = cudaMemsetAsync(dense_c, 0, static_cast<size_t>(M) * N * c_elem_bytes, stream);
+                    if (e != cudaSuccess) return e;
+                }
+            }
+        }
+    }
+    return cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, M, N, K, (accumulate & 1) | (k_splits << 8), tail_splits, status);
 }
 
 // The pair kernel is used for plain GEMMs that are large enough to fill the device with 256 x 256 tiles;
@@ -1110,7 +1162,11 @@ const char* gemm_bf16_tcgen05_view(const void* a, long long lda, long long a_row
     if (pair_kernel_enabled() && tiles256 >= num_sms / 2) {
         // each CTA of a pair loads 128 rows of a K-major B
         if (!b_mn && !make_tmap(&tb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, br, K, 128, BK, ldb)) return g_tmap_err;
-#define FS2_LAUNCH2(AM, BMN, F32) e = launch_pair<AM, BMN, F32>(ta, tb, tc, M, N, K, acc, status, num_sms, stream, k_splits)
+        // the tail split zeroes C first unless it accumulates: only for a dense, fully present C
+        void* dense_c = (ldc == 0 || ldc == N) && (c_rows == 0 || c_rows >= M) ? c : nullptr;
+        const size_t c_elem = out_f32 ? 4 : 2;
+#define FS2_LAUNCH2(AM, BMN, F32) \
+    e = launch_pair<AM, BMN, F32>(ta, tb, tc, M, N, K, acc, status, num_sms, stream, k_splits, dense_c, c_elem)
         if (!a_mn && !b_mn) { if (out_f32) FS2_LAUNCH2(false, false, true); else FS2_LAUNCH2(false, false, false); }
         else if (!a_mn && b_mn) { if (out_f32) FS2_LAUNCH2(false, true, true); else FS2_LAUNCH2(false, true, false); }
         else if (a_mn && !b_mn) { if (out_f32) FS2_LAUNCH2(true, false, true); else FS2_LAUNCH2(true, false, false); }

@@ -102,6 +102,28 @@ def test_gemm_cta_pair_kernel(a_mn: bool, b_mn: bool, monkeypatch: pytest.Monkey
     assert _rel_err(out32, base + ref) < 1e-4
 
 
+def test_gemm_cta_pair_tail_split(monkeypatch: pytest.MonkeyPatch) -> None:
+    """A partial last wave of 256 x 256 tiles is cut along K and reduce-added: once into a zeroed bf16 output (long K,
+    where zeroing pays) and once into an accumulated fp32 output."""
+    monkeypatch.setenv("FAIRSEQ2_B200_GEMM_PAIR", "1")
+    torch.manual_seed(13)
+    M, N = 4096, 4096                                    # 256 tiles: three full waves of 74 pairs and 34 more
+    for K, f32 in ((8192, False), (1024, True)):
+        a = torch.randn((M, K), device=DEV, dtype=torch.bfloat16)
+        b = torch.randn((N, K), device=DEV, dtype=torch.bfloat16)
+        ref = gemm_reference(a, b, out_dtype=torch.float32)
+        if f32:
+            out = torch.randn((M, N), device=DEV, dtype=torch.float32)
+            base = out.clone()
+            require_ext().gemm_bf16(a, b, out, False, False, True)
+            assert _rel_err(out, base + ref) < 1e-4
+        else:
+            out = torch.full((M, N), 7.0, device=DEV, dtype=torch.bfloat16)
+            require_ext().gemm_bf16(a, b, out, False, False, False)
+            assert _rel_err(out, ref) < 5e-3
+        assert require_ext().read_status() == 0
+
+
 def test_linear_autograd() -> None:
     torch.manual_seed(3)
     x = torch.randn((4, 96, 256), device=DEV, dtype=torch.bfloat16, requires_grad=True)
