@@ -140,9 +140,6 @@ class FlatParamUnit:
     # ------------------------------------------------------------- arena
     #: "copy": all-gather through the copy engines (no SM); "kernel": the load/store kernel
     allgather_engine = "kernel"
-    #: timing aid (``FAIRSEQ2_B200_FSDP_STUB_COMM=1``): collectives move local data only, so that
-    #: step time with stubs minus the real step time is the communication cost that compute does not hide
-    stub_comm = False
     #: thread blocks of the reduce-scatter kernel
     rs_blocks = 48
     #: local bf16 buffer of (world - 1) shards shared by all units: when set, the NVLink half of the reduce-scatter
@@ -196,12 +193,7 @@ class FlatParamUnit:
         with ctx:
             if self.arena is not None:
                 a = self.arena
-                if self.stub_comm:
-                    # timing aid: only the local shard is copied (no NVLink traffic); values of the other
-                    # ranks' regions are whatever the buffer held
-                    a.ext.comm_allgather_copy([a.peer_ptrs[a.rank]], 0, self.seg_offs, self.seg_numels, self.low_off,
-                                              full[: self.shard_size], 1, 0, a.wait_limit_s)
-                elif self.allgather_engine == "copy":
+                if self.allgather_engine == "copy":
                     a.ext.comm_allgather_copy(a.peer_ptrs, a.rank, self.seg_offs, self.seg_numels, self.low_off, full,
                                               1, param_epoch, a.wait_limit_s)
                 else:
@@ -287,9 +279,7 @@ class FlatParamUnit:
                 if not acc:
                     self.grad_shard = torch.empty(self.shard_size, device=self.device, dtype=torch.float32)
                 self.rs_epoch += 1
-                if self.stub_comm:
-                    self.grad_shard.copy_(self.grad_full[: self.shard_size])      # timing aid: no peer traffic
-                elif self.rs_staging is not None:
+                if self.rs_staging is not None:
                     a.ext.comm_reducescatter_copy(a.peer_ptrs, a.rank, self.seg_offs, self.seg_numels, self.grad_off,
                                                   self.rs_staging, self.grad_shard, (1.0 / W) if average else 1.0, acc,
                                                   2 + self.slot, self.rs_epoch, 4 * self.rs_blocks, a.wait_limit_s)
@@ -481,7 +471,6 @@ class FSDP(Module):
                         u.attach_arena(self.arena, i)
                         u.allgather_engine = engine
                         u.rs_blocks = int(os.environ.get("FAIRSEQ2_B200_FSDP_RS_BLOCKS", rs_blocks))
-                        u.stub_comm = os.environ.get("FAIRSEQ2_B200_FSDP_STUB_COMM", "0") == "1"
                     if os.environ.get("FAIRSEQ2_B200_FSDP_REDUCESCATTER", reducescatter) == "copy":
                         biggest = max(u.shard_size for u in self.all_units)
                         staging = torch.empty((W - 1) * biggest, device=dev, dtype=torch.bfloat16)
