@@ -55,8 +55,66 @@ def get_model_hub(family_name: str) -> ModelHub[Any, Any]:
     return ModelHub(get_model_family(family_name))
 
 
+# One accessor per built-in family, as in the reference (`get_llama_model_hub`, `get_qwen_model_hub`, ...:
+# fairseq2 ``models/<family>/hub.py``).
 def get_llama_model_hub() -> ModelHub[Any, Any]:
     return get_model_hub("llama")
+
+
+def get_llama4_model_hub() -> ModelHub[Any, Any]:
+    return get_model_hub("llama4")
+
+
+def get_mistral_model_hub() -> ModelHub[Any, Any]:
+    return get_model_hub("mistral")
+
+
+def get_qwen_model_hub() -> ModelHub[Any, Any]:
+    return get_model_hub("qwen")
+
+
+def get_olmo_model_hub() -> ModelHub[Any, Any]:
+    return get_model_hub("olmo")
+
+
+def get_gemma3n_model_hub() -> ModelHub[Any, Any]:
+    return get_model_hub("gemma3n")
+
+
+def get_nllb_model_hub() -> ModelHub[Any, Any]:
+    return get_model_hub("nllb")
+
+
+def get_s2t_transformer_model_hub() -> ModelHub[Any, Any]:
+    return get_model_hub("s2t_transformer")
+
+
+def get_s2t_conformer_model_hub() -> ModelHub[Any, Any]:
+    return get_model_hub("s2t_conformer")
+
+
+def get_wav2vec2_model_hub() -> ModelHub[Any, Any]:
+    return get_model_hub("wav2vec2")
+
+
+def get_wav2vec2_asr_model_hub() -> ModelHub[Any, Any]:
+    return get_model_hub("wav2vec2_asr")
+
+
+def get_w2vbert_model_hub() -> ModelHub[Any, Any]:
+    return get_model_hub("w2vbert")
+
+
+def get_jepa_model_hub() -> ModelHub[Any, Any]:
+    return get_model_hub("jepa")
+
+
+def get_jepa_classifier_model_hub() -> ModelHub[Any, Any]:
+    return get_model_hub("jepa_classifier")
+
+
+def get_hg_model_hub() -> ModelHub[Any, Any]:
+    return get_model_hub("hg")
 
 
 def load_model(name_or_card: str | AssetCard, *, gangs: Gangs | None = None, dtype: DataType = torch.float32,
