@@ -78,10 +78,29 @@ for _n, _l in (("nllb", _load_nllb), ("s2t_transformer", _load_s2t_transformer),
     register_tokenizer_family(_n, _l)
 
 
+def resolve_tokenizer_reference(store: AssetStore, card: AssetCard) -> AssetCard:
+    """Follows ``tokenizer_ref`` fields (a model card that names the card of its tokenizer) to the card that holds the
+    tokenizer itself (cf. fairseq2 ``data/tokenizers/ref.py:12-33``)."""
+    first, seen = card.name, {card.name}
+    while True:
+        ref = card.maybe_get_field("tokenizer_ref", str)
+        if ref is None:
+            return card
+        if ref in seen:
+            raise UnknownTokenizerFamilyError(f"The `tokenizer_ref` fields starting at '{first}' form a cycle at '{ref}'.")
+        seen.add(ref)
+        try:
+            card = store.retrieve_card(ref)
+        except LookupError:
+            raise UnknownTokenizerFamilyError(
+                f"The '{ref}' asset referenced by the '{first}' asset card does not exist.") from None
+
+
 def load_tokenizer(name_or_card: str | AssetCard, *, store: AssetStore | None = None,
                    download_manager: AssetDownloadManager | None = None) -> Tokenizer:
     store = store or get_asset_store()
     card = store.retrieve_card(name_or_card) if isinstance(name_or_card, str) else name_or_card
+    card = resolve_tokenizer_reference(store, card)
     family = card.maybe_get_field("tokenizer_family", str)
     if family is None:
         raise UnknownTokenizerFamilyError(f"The '{card.name}' asset card does not have a 'tokenizer_family' field.")

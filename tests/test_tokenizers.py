@@ -101,3 +101,26 @@ def test_model_hub_accessors() -> None:
                  "wav2vec2", "wav2vec2_asr", "w2vbert", "jepa", "jepa_classifier", "hg"):
         h = getattr(hub, f"get_{name}_model_hub")()
         assert isinstance(h.get_archs(), list), name
+
+
+def test_tokenizer_ref_is_followed() -> None:
+    from fairseq2_b200.assets import AssetStore
+    from fairseq2_b200.assets.store import InMemoryAssetMetadataProvider
+    from fairseq2_b200.data.tokenizers.char import CharTokenizer
+    from fairseq2_b200.data.tokenizers.hub import load_tokenizer, resolve_tokenizer_reference
+
+    provider = InMemoryAssetMetadataProvider([
+        {"name": "tok_card", "tokenizer_family": "char"},
+        {"name": "model_a", "model_family": "wav2vec2_asr", "tokenizer_ref": "tok_card"},
+        {"name": "model_b", "tokenizer_ref": "model_a"},
+        {"name": "loop_a", "tokenizer_ref": "loop_b"},
+        {"name": "loop_b", "tokenizer_ref": "loop_a"},
+        {"name": "dangling", "tokenizer_ref": "nowhere"},
+    ])
+    store = AssetStore([provider])
+    assert resolve_tokenizer_reference(store, store.retrieve_card("model_b")).name == "tok_card"
+    assert isinstance(load_tokenizer("model_b", store=store), CharTokenizer)
+    with pytest.raises(LookupError, match="cycle"):
+        load_tokenizer("loop_a", store=store)
+    with pytest.raises(LookupError, match="does not exist"):
+        load_tokenizer("dangling", store=store)
