@@ -14,3 +14,7 @@ from fairseq2_b200.composition.library import compose_library as compose_library
 from fairseq2_b200.composition.library import register_dataset_family as register_dataset_family
 from fairseq2_b200.composition.library import register_model_family as register_model_family
 from fairseq2_b200.composition.library import register_tokenizer_family as register_tokenizer_family
+from fairseq2_b200.composition.library import register_checkpoint_models as register_checkpoint_models
+from fairseq2_b200.composition.library import register_file_assets as register_file_assets
+from fairseq2_b200.composition.library import register_in_memory_assets as register_in_memory_assets
+from fairseq2_b200.composition.library import register_package_assets as register_package_assets

@@ -10,11 +10,13 @@ extension is usable from recipes and from resolver-based code alike.
 from __future__ import annotations
 
 import os
-from typing import Any, Callable, Mapping
+from pathlib import Path
+from typing import Any, Callable, Mapping, Sequence
 
 import torch
 
 from fairseq2_b200.assets import AssetDownloadManager, AssetStore, get_asset_store
+from fairseq2_b200.assets.store import FileAssetMetadataProvider, InMemoryAssetMetadataProvider
 from fairseq2_b200.cluster import ClusterHandler, SlurmHandler
 from fairseq2_b200.datasets.family import DatasetFamily
 from fairseq2_b200.datasets.family import register_dataset_family as _register_dataset_family_global
@@ -56,6 +58,39 @@ def register_tokenizer_family(container: DependencyContainer, name: str, loader:
 
     register_global(name, loader)
     container.register_instance(TokenizerFamily, TokenizerFamily(name, loader), key=name)
+
+
+# ------------------------------------------------------------------ asset sources
+# cf. fairseq2 ``composition/assets.py:37-62``: each helper adds one source of asset cards to the store that the
+# container hands out (and that ``load_model`` / ``load_tokenizer`` / ``open_dataset`` use by default).
+def register_file_assets(container: DependencyContainer, path: Path) -> None:
+    """All ``*.yaml`` cards under ``path`` (a file or a directory)."""
+    container.resolve(AssetStore).add_provider(FileAssetMetadataProvider(Path(path)))
+
+
+def register_package_assets(container: DependencyContainer, package: str) -> None:
+    """The cards shipped inside an importable package, e.g. ``"my_extension.cards"``."""
+    import importlib
+
+    mod = importlib.import_module(package)
+    paths = list(getattr(mod, "__path__", []))
+    if not paths:
+        raise ValueError(f"`package` must be an importable package with a directory, but '{package}' is not.")
+    store = container.resolve(AssetStore)
+    for p in paths:
+        store.add_provider(FileAssetMetadataProvider(Path(p)))
+
+
+def register_in_memory_assets(container: DependencyContainer, source: str,
+                              entries: Sequence[Mapping[str, Any]]) -> None:
+    container.resolve(AssetStore).add_provider(InMemoryAssetMetadataProvider(entries, source=source))
+
+
+def register_checkpoint_models(container: DependencyContainer, checkpoint_dir: Path) -> None:
+    """``checkpoint_step_N`` / ``last_checkpoint`` / ``best_checkpoint`` cards of a training run."""
+    from fairseq2_b200.assets.store import register_checkpoint_models as register
+
+    register(container.resolve(AssetStore), Path(checkpoint_dir))
 
 
 def compose_library(container: DependencyContainer, *, env: Mapping[str, str] | None = None) -> None:

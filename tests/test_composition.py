@@ -96,3 +96,18 @@ def test_init_is_idempotent_and_installs_the_resolver() -> None:
     finally:
         fairseq2_b200._container = None
         set_dependency_resolver(None)
+
+
+def test_asset_sources_added_through_the_container(tmp_path) -> None:  # type: ignore[no-untyped-def]
+    from fairseq2_b200.assets import AssetStore
+    from fairseq2_b200.composition import register_file_assets, register_in_memory_assets
+
+    c = _container()
+    c.register_instance(AssetStore, AssetStore([]))          # a private store: the process-wide one stays untouched
+    (tmp_path / "cards.yaml").write_text("name: file_card\nmodel_family: llama\nmodel_arch: llama3_8b\n---\n"
+                                         "name: file_card_b\nbase: file_card\n")
+    register_file_assets(c, tmp_path)
+    register_in_memory_assets(c, "test", [{"name": "mem_card", "tokenizer_family": "char"}])
+    store = c.resolve(AssetStore)
+    assert store.retrieve_card("file_card_b").maybe_get_field("model_arch", str) == "llama3_8b"
+    assert store.retrieve_card("mem_card").maybe_get_field("tokenizer_family", str) == "char"
