@@ -64,9 +64,11 @@ def generate_sweep_tag(unstructured_config: Mapping[str, Any], world_size: int, 
     if unknown:
         raise SweepFormatPlaceholderError(unknown, sorted(tags))
 
-    class _M(dict):  # type: ignore[type-arg]
-        def __missing__(self, key: str) -> str:
-            return "{" + key + "}"
+    class _WholeKey(string.Formatter):
+        """Looks a placeholder such as ``{model.name}`` or ``{list[0]}`` up as ONE key instead of walking attributes."""
 
-    out = string.Formatter().vformat(sweep_format, (), _M(tags))
+        def get_field(self, field_name: str, args: Any, kwargs: Any) -> tuple[Any, str]:
+            return kwargs[field_name], field_name
+
+    out = _WholeKey().vformat(sweep_format, (), tags)
     return _SAFE.sub("", out.replace(".", "_DOT_")).replace("_DOT_", ".")
