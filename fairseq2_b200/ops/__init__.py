@@ -7,3 +7,4 @@
   gloo) and as the numerical oracle of the kernel tests.
 """
 from fairseq2_b200.ops._ext import ext_available, get_ext, require_ext  # noqa: F401
+from fairseq2_b200.ops._ext import KernelWaitTimeout as KernelWaitTimeout
