@@ -208,5 +208,22 @@ class DDP(Module):
             b.pending = len(b.params)
 
 
+def convert_batch_norms(module: Module, gangs: Gangs) -> Module:
+    """Buffers are not broadcast during training, so batch-norm statistics have to be computed over the whole
+    replicated gang: every ``BatchNorm`` becomes a ``SyncBatchNorm`` over it (cf. fairseq2 ``nn/ddp.py:92-94``).
+    A module without batch norms, or a gang without a process group (single rank, fake gang), is returned as is."""
+    from torch.nn.modules.batchnorm import _BatchNorm
+
+    gang = gangs.rdp
+    if gang.size == 1 or not any(isinstance(m, _BatchNorm) for m in module.modules()):
+        return module
+    try:
+        group = gang.as_process_group()
+    except Exception:  # noqa: BLE001 - fake gangs have no process group
+        return module
+    return torch.nn.SyncBatchNorm.convert_sync_batchnorm(module, group)
+
+
 def to_ddp(module: Module, gangs: Gangs, **kw: Any) -> DDP:
+    module = convert_batch_norms(module, gangs)
     return DDP(module, gangs, **kw)

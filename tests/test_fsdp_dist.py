@@ -110,3 +110,22 @@ def test_two_rank_training_matches_single_rank(kind: str) -> None:
         _, _, shapes = results[0]
         assert shapes["decoder.layers.0.self_attn.q_proj.weight"] == (128, 256)
         assert shapes["decoder_frontend.embed.weight"] == (4096, 256)
+
+
+def _sync_bn_worker(rank: int, world: int):
+    from fairseq2_b200.gang import ProcessGroupGang, create_parallel_gangs
+    from fairseq2_b200.parallel.ddp import convert_batch_norms
+
+    root = ProcessGroupGang.create_default_process_group(torch.device("cpu"))
+    gangs = create_parallel_gangs(root)
+    with_bn = torch.nn.Sequential(torch.nn.Conv1d(2, 2, 1), torch.nn.BatchNorm1d(2))
+    without = torch.nn.Sequential(torch.nn.Linear(2, 2), torch.nn.LayerNorm(2))
+    a, b = convert_batch_norms(with_bn, gangs), convert_batch_norms(without, gangs)
+    root.barrier()
+    return type(a[1]).__name__, b is without
+
+
+def test_ddp_converts_batch_norms_to_sync_batch_norm() -> None:
+    """Buffers are not broadcast during training, so batch norms must reduce their statistics over the gang."""
+    for name, untouched in run_distributed(_sync_bn_worker, 2):
+        assert name == "SyncBatchNorm" and untouched
