@@ -175,6 +175,8 @@ class JsonlMetricRecorder(MetricRecorder):
         for n, v in _sorted_items(values):
             d = get_metric_descriptor(n)
             key = d.display_name if d else n
+            if hasattr(v, "tolist") and not isinstance(v, (str, bytes)):
+                v = v.tolist()                      # tensors and numpy values (0-dim -> Python scalar)
             if isinstance(v, float) and not math.isfinite(v):
                 v = str(v)
             out[key] = v
