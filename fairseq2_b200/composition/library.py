@@ -9,7 +9,6 @@ extension is usable from recipes and from resolver-based code alike.
 
 from __future__ import annotations
 
-import os
 from pathlib import Path
 from typing import Any, Callable, Mapping, Sequence
 
@@ -26,13 +25,10 @@ from fairseq2_b200.models.family import ModelFamily, get_model_families
 from fairseq2_b200.models.family import register_model_family as _register_model_family_global
 from fairseq2_b200.runtime.dependency import DependencyContainer, DependencyResolver
 from fairseq2_b200.sharder import EmbeddingSharder, LinearSharder, ModelSharder, ModuleSharder, StandardModelSharder
+from fairseq2_b200.utils.env import Environment
 from fairseq2_b200.utils.rng import RngBag
 from fairseq2_b200.utils.threading import StandardThreadPool, ThreadPool
 from fairseq2_b200.world_info import WorldInfo
-
-
-class Environment(dict):  # type: ignore[type-arg]
-    """The process environment as seen at composition time (a snapshot that tests can replace)."""
 
 
 class TokenizerFamily:
@@ -95,11 +91,12 @@ def register_checkpoint_models(container: DependencyContainer, checkpoint_dir: P
 
 def compose_library(container: DependencyContainer, *, env: Mapping[str, str] | None = None) -> None:
     """Registers the process-wide services and every built-in family."""
-    environ = Environment(os.environ if env is None else env)
+    # the process environment, or the mapping a test passes in
+    environ = Environment(None if env is None else dict(env))
     container.register_instance(Environment, environ)
 
-    container.register(WorldInfo, lambda r: WorldInfo.from_env(r.resolve(Environment)))
-    container.register(Device, lambda r: detect_default_device(r.resolve(Environment)))
+    container.register(WorldInfo, lambda r: WorldInfo.from_env(r.resolve(Environment).to_dict()))
+    container.register(Device, lambda r: detect_default_device(r.resolve(Environment).to_dict()))
     container.register(FileSystem, lambda r: GlobalFileSystem())
     container.register(ThreadPool, lambda r: StandardThreadPool(max_num_workers=1, num_torch_threads=1))
     container.register(AssetStore, lambda r: get_asset_store())

@@ -4,7 +4,8 @@ from __future__ import annotations
 import pytest
 
 from fairseq2_b200.composition import ExtensionError, compose_library, register_tokenizer_family, run_extensions
-from fairseq2_b200.composition.library import Environment, TokenizerFamily
+from fairseq2_b200.composition.library import TokenizerFamily
+from fairseq2_b200.utils.env import Environment
 from fairseq2_b200.device import Device
 from fairseq2_b200.file_system import FileSystem
 from fairseq2_b200.models.family import ModelFamily
@@ -21,7 +22,7 @@ def _container(env: dict[str, str] | None = None) -> DependencyContainer:
 
 def test_library_services_and_families() -> None:
     c = _container({"FAIRSEQ2_DEVICE": "cpu", "WORLD_SIZE": "4", "RANK": "3", "LOCAL_WORLD_SIZE": "2", "LOCAL_RANK": "1"})
-    assert c.resolve(Environment)["RANK"] == "3"
+    assert c.resolve(Environment).get("RANK") == "3"
     w = c.resolve(WorldInfo)
     assert (w.rank, w.size, w.local_rank, w.local_size) == (3, 4, 1, 2)
     assert c.resolve(Device).type == "cpu"
