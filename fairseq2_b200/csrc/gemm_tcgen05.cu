@@ -1102,7 +1102,9 @@ cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUte
     int tail_splits = 1;
     const int rem = num_mn % pairs;
     if (k_splits == 1 && num_mn > pairs && rem > 0 && (accumulate || dense_c != nullptr)) {
-        int sp = std::min(std::min(pairs / rem, 4), num_kb / 8);
+        // two slices at most: a + b is the same in either order, so the result does not depend on which pair
+        // finishes first (three or more reduce-adds would make the last bit vary from run to run)
+        int sp = std::min(std::min(pairs / rem, 2), num_kb / 8);
         if (sp > 1) {
             const int per = (num_kb + sp - 1) / sp;
             sp = (num_kb + per - 1) / per;                      // no empty slice

@@ -15,8 +15,8 @@ TMEM pipeline (see ``csrc/gemm_tcgen05.cu``). Shapes with at least half a wave
 of 256 x 256 tiles run on pairs of CTAs (``cta_group::2``: one tile per two
 SMs, each CTA stages half of ``b``); ``FAIRSEQ2_B200_GEMM_PAIR=0`` keeps them
 on the single-CTA kernel. When the last wave of tiles is partial, its tiles are
-cut along K and reduce-added, so a bf16 result can differ from the single-pass
-one by one rounding.
+cut into two K slices that are reduce-added (deterministic: a + b in either
+order), so a bf16 result can differ from the single-pass one by one rounding.
 """
 from __future__ import annotations
 
