@@ -238,6 +238,7 @@ class CheckpointManager:
         g.root.barrier()
 
     def load_scores(self) -> list[tuple[float, int]]:
+        """``(score, step_nr)`` pairs, best score first (cf. reference ``checkpoint/manager.py:527-555``)."""
         out = []
         d = self._dir / "scores"
         if d.exists():
@@ -246,7 +247,7 @@ class CheckpointManager:
                     out.append((float(f.read_text().strip()), int(f.stem[5:])))
                 except ValueError:
                     raise CheckpointLoadError(f"The score file '{f}' is corrupt.") from None
-        out.sort()
+        out.sort(reverse=True)
         return out
 
     # --------------------------------------------------------------- listing
@@ -280,7 +281,10 @@ class CheckpointManager:
     def delete_checkpoint(self, step_nr: int, *, keep_model: bool = False) -> None:
         g = self._gangs
         d = self._step_dir(step_nr)
-        exists = d.exists()
+        # every rank must see the same answer: look before rank 0 starts deleting, and let rank 0 decide
+        from fairseq2_b200.gang import broadcast_flag
+
+        exists = broadcast_flag(g.root, d.exists()) if g.root.size > 1 else d.exists()
         if g.root.rank == 0 and exists:
             try:
                 if keep_model:
@@ -298,9 +302,10 @@ class CheckpointManager:
         if not exists:
             raise CheckpointNotFoundError(step_nr)
 
-    def delete_stale_checkpoints(self, *, keep_last_n: int | None = None, keep_best_n: int | None = None,
-                                 keep_every_n_steps: int | None = None, keep_model_only: bool = False) -> list[int]:
-        """Applies the retention policy; returns the step numbers that were removed."""
+    def get_stale_step_numbers(self, keep_last_n: int | None = None, keep_best_n: int | None = None,
+                               keep_every_n_steps: int | None = None) -> list[int]:
+        """Step numbers that the retention policy does not keep, ascending (cf. reference
+        ``checkpoint/manager.py:754-798``). The last checkpoint is always kept."""
         steps = self.get_step_numbers()
         if not steps or (keep_last_n is None and keep_best_n is None):
             return []
@@ -308,15 +313,18 @@ class CheckpointManager:
         if keep_last_n is not None:
             keep.update(steps[-keep_last_n:] if keep_last_n > 0 else [])
         if keep_best_n is not None:
-            scores = self.load_scores()
-            best = [s for _, s in sorted(scores, reverse=True)[:keep_best_n]]
-            keep.update(best)
+            keep.update(s for _, s in self.load_scores()[:keep_best_n])
         if keep_every_n_steps is not None:
             keep.update(s for s in steps if s % keep_every_n_steps == 0)
         keep.add(steps[-1])
+        return [s for s in steps if s not in keep]
+
+    def delete_stale_checkpoints(self, *, keep_last_n: int | None = None, keep_best_n: int | None = None,
+                                 keep_every_n_steps: int | None = None, keep_model_only: bool = False) -> list[int]:
+        """Applies the retention policy; returns the step numbers that were removed."""
         removed = []
-        for s in steps:
-            if s not in keep:
+        for s in self.get_stale_step_numbers(keep_last_n, keep_best_n, keep_every_n_steps):
+            if True:
                 try:
                     self.delete_checkpoint(s, keep_model=keep_model_only)
                     removed.append(s)

@@ -967,7 +967,7 @@ void multi_tensor_adamw(const std::vector<Tensor>& masters, const std::vector<Te
         fs2::adamw(p.data_ptr<float>(), g.data_ptr(), is_bf16(g), ms[i].data_ptr<float>(), vs[i].data_ptr<float>(), low,
                    static_cast<size_t>(p.numel()), static_cast<float>(lr), static_cast<float>(beta1),
                    static_cast<float>(beta2), static_cast<float>(eps), static_cast<float>(wd), static_cast<int>(step),
-                   gs, num_sms(p), stream_of(p));
+                   gs, status_dev_ptr(), num_sms(p), stream_of(p));
         g_launches += 1;
     }
 }
@@ -1092,10 +1092,21 @@ void comm_allgather_copy(const std::vector<int64_t>& ptrs, int64_t rank, const s
     }
 }
 
+// Device scalar that receives a sum of squares, or null.
+float* norm_out_ptr(const std::optional<Tensor>& norm_out, const Tensor& like) {
+    if (!norm_out.has_value()) return nullptr;
+    TORCH_CHECK(norm_out->is_cuda() && norm_out->scalar_type() == at::kFloat && norm_out->numel() == 1 &&
+                    norm_out->device() == like.device(),
+                "comm: `norm_out` must be an fp32 scalar on the device of the output");
+    return norm_out->data_ptr<float>();
+}
+
 void comm_reducescatter_segments(const std::vector<int64_t>& ptrs, int64_t rank, const std::vector<int64_t>& offs,
                                  const std::vector<int64_t>& numels, int64_t full_byte_off, Tensor out, double scale,
-                                 bool accumulate, int64_t slot, int64_t epoch, int64_t blocks, double wait_limit_s) {
+                                 bool accumulate, int64_t slot, int64_t epoch, int64_t blocks, double wait_limit_s,
+                                 const std::optional<Tensor>& norm_out) {
     const int64_t shard_numel = offs.back() + numels.back();
+    float* norm_ptr = norm_out_ptr(norm_out, out);
     TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.numel() == shard_numel && aligned16(out) &&
                     (out.scalar_type() == at::kFloat || is_bf16(out)),
                 "comm_reducescatter_segments: `out` must be a contiguous fp32/bf16 shard-sized CUDA tensor");
@@ -1104,8 +1115,8 @@ void comm_reducescatter_segments(const std::vector<int64_t>& ptrs, int64_t rank,
     fs2::comm_reducescatter_segments(make_peers(ptrs, rank, wait_limit_s), make_segments(offs, numels),
                                      full_byte_off, out.data_ptr(), out.scalar_type() == at::kFloat, shard_numel,
                                      static_cast<float>(scale), accumulate, static_cast<int>(slot),
-                                     static_cast<uint32_t>(epoch), static_cast<int>(blocks), status_dev_ptr(),
-                                     stream_of(out));
+                                     static_cast<uint32_t>(epoch), static_cast<int>(blocks), norm_ptr,
+                                     status_dev_ptr(), stream_of(out));
     g_launches += 1;
 }
 
@@ -1115,9 +1126,10 @@ void comm_reducescatter_segments(const std::vector<int64_t>& ptrs, int64_t rank,
 void comm_reducescatter_copy(const std::vector<int64_t>& ptrs, int64_t rank, const std::vector<int64_t>& offs,
                              const std::vector<int64_t>& numels, int64_t full_byte_off, Tensor staging, Tensor out,
                              double scale, bool accumulate, int64_t slot, int64_t epoch, int64_t blocks,
-                             double wait_limit_s) {
+                             double wait_limit_s, const std::optional<Tensor>& norm_out) {
     const int64_t W = static_cast<int64_t>(ptrs.size());
     const int64_t shard_numel = offs.back() + numels.back();
+    float* norm_ptr = norm_out_ptr(norm_out, out);
     TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.numel() == shard_numel && aligned16(out) &&
                     (out.scalar_type() == at::kFloat || is_bf16(out)),
                 "comm_reducescatter_copy: `out` must be a contiguous fp32/bf16 shard-sized CUDA tensor");
@@ -1145,7 +1157,7 @@ void comm_reducescatter_copy(const std::vector<int64_t>& ptrs, int64_t rank, con
     const char* own = reinterpret_cast<const char*>(ptrs[static_cast<size_t>(rank)]) + full_byte_off;
     fs2::comm_reduce_staged(own, staged, static_cast<int>(W - 1), segs, static_cast<int>(rank), static_cast<int>(W),
                             out.data_ptr(), out.scalar_type() == at::kFloat, static_cast<float>(scale), accumulate,
-                            static_cast<int>(blocks), st);
+                            static_cast<int>(blocks), norm_ptr, st);
     g_launches += 2;
 }
 
@@ -1197,7 +1209,8 @@ void comm_allreduce_inplace(const std::vector<int64_t>& ptrs, int64_t rank, int6
     const int64_t per = f32 ? 4 : 8;
     TORCH_CHECK(byte_off % 16 == 0 && numel % per == 0 && numel > 0, "comm_allreduce_inplace: the bucket must be a "
                 "whole number of 16-byte vectors at a 16-byte aligned offset");
-    TORCH_CHECK(counter_byte_off % 4 == 0 && blocks >= 1 && blocks <= 148, "comm_allreduce_inplace: bad argument");
+    TORCH_CHECK(counter_byte_off % 8 == 0 && blocks >= 1 && blocks <= 148 && epoch >= 1,
+                "comm_allreduce_inplace: bad argument (the counter is two words, 8-byte aligned; epochs start at 1)");
     c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
     auto* counter = reinterpret_cast<unsigned int*>(ptrs[static_cast<size_t>(rank)] + counter_byte_off);
     fs2::comm_allreduce_inplace(make_peers(ptrs, rank, wait_limit_s), byte_off, numel, f32, static_cast<float>(scale),
@@ -1283,8 +1296,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("comm_signal", &comm_signal);
     m.def("comm_allgather_segments", &comm_allgather_segments);
     m.def("comm_allgather_copy", &comm_allgather_copy);
-    m.def("comm_reducescatter_segments", &comm_reducescatter_segments);
-    m.def("comm_reducescatter_copy", &comm_reducescatter_copy);
+    m.def("comm_reducescatter_segments", &comm_reducescatter_segments, py::arg("ptrs"), py::arg("rank"),
+          py::arg("offs"), py::arg("numels"), py::arg("full_byte_off"), py::arg("out"), py::arg("scale"),
+          py::arg("accumulate"), py::arg("slot"), py::arg("epoch"), py::arg("blocks"), py::arg("wait_limit_s"),
+          py::arg("norm_out") = std::nullopt);
+    m.def("comm_reducescatter_copy", &comm_reducescatter_copy, py::arg("ptrs"), py::arg("rank"), py::arg("offs"),
+          py::arg("numels"), py::arg("full_byte_off"), py::arg("staging"), py::arg("out"), py::arg("scale"),
+          py::arg("accumulate"), py::arg("slot"), py::arg("epoch"), py::arg("blocks"), py::arg("wait_limit_s"),
+          py::arg("norm_out") = std::nullopt);
     m.def("comm_reducescatter_adamw", &comm_reducescatter_adamw);
     m.def("comm_allreduce_f32", &comm_allreduce_f32);
     m.def("comm_allreduce_inplace", &comm_allreduce_inplace);

@@ -87,24 +87,39 @@ __global__ void __launch_bounds__(512) allgather_segments_kernel(
 }
 
 // Reduce-scatter: out[off_s + i] = scale * sum_r peer_r.full[W*off_s + rank*numel_s + i]; bf16 in,
-// fp32 accumulate. All W peer loads of RS_UNROLL vectors are issued before the first use.
-constexpr int RS_UNROLL = 2;
+// fp32 accumulate. All W peer loads of the unrolled vectors are issued before the first use.
+// Vectors per thread and peer in flight: few ranks mean few peers per vector, so more vectors are unrolled to keep
+// about the same number of bytes outstanding on NVLink.
+template <int W>
+struct RsUnroll {
+    static constexpr int value = W <= 2 ? 8 : (W <= 4 ? 4 : 2);
+};
 
 // What happens to a reduced (and scaled) vector of 8 gradients at shard element index j.
 template <typename OutT>
 struct StoreSink {
     OutT* out;
     int accumulate;
-    __device__ __forceinline__ void operator()(size_t j, float* acc) const {
+    float sumsq;   // running sum of squares of what this thread stored (the thread's share of the gradient norm)
+    __device__ __forceinline__ void operator()(size_t j, float* acc) {
         if (accumulate) {
             float prev[8];
             load8(out, j, prev);
 #pragma unroll
             for (int e = 0; e < 8; ++e) acc[e] += prev[e];
         }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sumsq = fmaf(acc[e], acc[e], sumsq);
         store8(out, j, acc);
     }
 };
+
+// Adds the block's sum of the per-thread `sumsq` to `*norm_out` (one atomic per block).
+__device__ __forceinline__ void publish_sumsq(float sumsq, float* norm_out) {
+    __shared__ float scratch[32];
+    const float total = block_sum(sumsq, scratch);
+    if (threadIdx.x == 0) atomicAdd(norm_out, total);
+}
 
 // AdamW applied to the freshly reduced gradient while it is still in registers: the fp32 gradient shard is never
 // written to (or re-read from) memory.
@@ -114,7 +129,7 @@ struct AdamWSink {
     float* v;
     __nv_bfloat16* low;   // bf16 copy of the updated parameters (may be null)
     float lr, beta1, beta2, eps, wd, step_size, bc2_sqrt;
-    __device__ __forceinline__ void operator()(size_t j, float* g) const {
+    __device__ __forceinline__ void operator()(size_t j, float* g) {
         float pv[8], mv[8], vv[8];
         load8(p, j, pv);
         load8(m, j, mv);
@@ -135,13 +150,14 @@ struct AdamWSink {
 
 template <typename Sink, int W>
 __device__ __forceinline__ void reducescatter_body(const CommPeers& peers, const CommSegments& segs,
-                                                   long long full_byte_off, const Sink& sink, float scale) {
+                                                   long long full_byte_off, Sink& sink, float scale) {
     const __nv_bfloat16* srcs[W];
 #pragma unroll
     for (int k = 0; k < W; ++k) {
         const int r = (peers.rank + k) % W;
         srcs[k] = reinterpret_cast<const __nv_bfloat16*>(reinterpret_cast<const char*>(peers.base[r]) + full_byte_off);
     }
+    constexpr int RS_UNROLL = RsUnroll<W>::value;
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     for (int s = 0; s < segs.count; ++s) {
         const long long off = segs.off[s];
@@ -183,7 +199,7 @@ __device__ __forceinline__ void reducescatter_body(const CommPeers& peers, const
 
 template <typename Sink>
 __device__ __forceinline__ void reducescatter_dispatch(const CommPeers& peers, const CommSegments& segs,
-                                                       long long full_byte_off, const Sink& sink, float scale) {
+                                                       long long full_byte_off, Sink& sink, float scale) {
     switch (peers.world) {
         case 1: reducescatter_body<Sink, 1>(peers, segs, full_byte_off, sink, scale); break;
         case 2: reducescatter_body<Sink, 2>(peers, segs, full_byte_off, sink, scale); break;
@@ -196,12 +212,18 @@ __device__ __forceinline__ void reducescatter_dispatch(const CommPeers& peers, c
     }
 }
 
+// With `norm_out` the kernel is the whole gradient path of an FSDP unit between backward and optimizer: peer loads of
+// the W bf16 slices, fp32 sum, averaging factor, ONE store of the fp32 shard, and the unit's contribution to the
+// squared global gradient norm (clipping then only needs the tiny all-reduce of that scalar; AdamW takes the clip
+// factor as a device scalar). Without it, a plain reduce-scatter.
 template <typename OutT>
 __global__ void __launch_bounds__(512) reducescatter_segments_kernel(
     CommPeers peers, CommSegments segs, long long full_byte_off, OutT* __restrict__ out, long long shard_numel,
-    float scale, int accumulate, int slot, uint32_t epoch, int* status) {
+    float scale, int accumulate, int slot, uint32_t epoch, float* norm_out, int* status) {
     if (!signal_and_wait(peers, slot, epoch, true, status, 18)) return;
-    reducescatter_dispatch(peers, segs, full_byte_off, StoreSink<OutT>{out, accumulate}, scale);
+    StoreSink<OutT> sink{out, accumulate, 0.f};
+    reducescatter_dispatch(peers, segs, full_byte_off, sink, scale);
+    if (norm_out != nullptr) publish_sumsq(sink.sumsq, norm_out);
 }
 
 // Reduce-scatter fused with the optimizer step of the local shard (no gradient clipping between the two).
@@ -209,7 +231,8 @@ __global__ void __launch_bounds__(512) reducescatter_adamw_kernel(CommPeers peer
                                                                   long long full_byte_off, AdamWSink sink, float scale,
                                                                   int slot, uint32_t epoch, int* status) {
     if (!signal_and_wait(peers, slot, epoch, true, status, 24)) return;
-    reducescatter_dispatch(peers, segs, full_byte_off, sink, scale);
+    AdamWSink local = sink;
+    reducescatter_dispatch(peers, segs, full_byte_off, local, scale);
 }
 
 // Second half of the copy-engine reduce-scatter: the peers' slices of this rank's shard have been copied into local
@@ -223,8 +246,9 @@ struct StagedSlices {
 template <typename OutT>
 __global__ void __launch_bounds__(512) reduce_staged_kernel(const __nv_bfloat16* __restrict__ own_full,
                                                             StagedSlices staged, CommSegments segs, int rank, int world,
-                                                            OutT* __restrict__ out, float scale, int accumulate) {
-    const StoreSink<OutT> sink{out, accumulate};
+                                                            OutT* __restrict__ out, float scale, int accumulate,
+                                                            float* norm_out) {
+    StoreSink<OutT> sink{out, accumulate, 0.f};
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     for (int s = 0; s < segs.count; ++s) {
         const long long off = segs.off[s];
@@ -244,6 +268,7 @@ __global__ void __launch_bounds__(512) reduce_staged_kernel(const __nv_bfloat16*
             sink(static_cast<size_t>(off + v * 8), acc);
         }
     }
+    if (norm_out != nullptr) publish_sumsq(sink.sumsq, norm_out);
 }
 
 template <typename OutT>
@@ -346,7 +371,9 @@ template <typename T>
 __global__ void __launch_bounds__(512) allreduce_inplace_kernel(CommPeers peers, long long byte_off, long long numel,
                                                                 float scale, int slot_in, int slot_mid,
                                                                 uint32_t epoch, unsigned int* counter, int* status) {
-    if (!signal_and_wait(peers, slot_in, epoch, true, status, 22)) return;
+    // slot_in carries two epochs per call: 2 * epoch - 1 = "my bucket holds this call's input",
+    // 2 * epoch = "I have finished reading every peer's bucket" (the trailing handshake below)
+    if (!signal_and_wait(peers, slot_in, 2 * epoch - 1, true, status, 22)) return;
     constexpr int PER = 16 / sizeof(T);
     const int W = peers.world;
     // slices are multiples of one 16-byte vector; `numel` itself is a multiple of PER (host-checked)
@@ -389,6 +416,19 @@ __global__ void __launch_bounds__(512) allreduce_inplace_kernel(CommPeers peers,
         for (long long v = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v < nvec;
              v += static_cast<long long>(gridDim.x) * blockDim.x)
             st16(to + v * 16, ld_peer16(from + v * 16));
+    }
+    // Trailing handshake: the bucket may be overwritten (by the next backward pass) as soon as this kernel has
+    // finished, so the kernel ends only when every peer has pulled what it needs from this rank's bucket. The last
+    // CTA to finish phase 2 announces "done reading" and waits (bounded) for the same announcement of every peer.
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int prev = atomicAdd(counter + 1, 1u);
+        if (prev == gridDim.x - 1) {
+            counter[1] = 0;
+            __threadfence_system();
+            signal_all(peers, slot_in, 2 * epoch);
+            wait_all_one_thread(peers, slot_in, 2 * epoch, status, 28);
+        }
     }
 }
 
@@ -519,15 +559,15 @@ void comm_allgather_segments(const CommPeers& peers, const CommSegments& segs, l
 
 void comm_reducescatter_segments(const CommPeers& peers, const CommSegments& segs, long long full_byte_off, void* out,
                                  bool out_f32, long long shard_numel, float scale, bool accumulate, int slot,
-                                 uint32_t epoch, int blocks, int* status, cudaStream_t st) {
+                                 uint32_t epoch, int blocks, float* norm_out, int* status, cudaStream_t st) {
     if (out_f32)
         reducescatter_segments_kernel<float><<<blocks, 512, 0, st>>>(peers, segs, full_byte_off,
                                                                      static_cast<float*>(out), shard_numel, scale,
-                                                                     accumulate ? 1 : 0, slot, epoch, status);
+                                                                     accumulate ? 1 : 0, slot, epoch, norm_out, status);
     else
         reducescatter_segments_kernel<__nv_bfloat16><<<blocks, 512, 0, st>>>(
             peers, segs, full_byte_off, static_cast<__nv_bfloat16*>(out), shard_numel, scale, accumulate ? 1 : 0,
-            slot, epoch, status);
+            slot, epoch, norm_out, status);
 }
 
 void comm_allreduce_f32(const CommPeers& peers, long long byte_off, float* out, long long numel, int op, int slot,
@@ -578,17 +618,19 @@ void comm_reduce_slices(const void* slices, int world, long long n, void* out, b
 }
 
 void comm_reduce_staged(const void* own_full, const void* const* staged, int count, const CommSegments& segs, int rank,
-                        int world, void* out, bool out_f32, float scale, bool accumulate, int blocks, cudaStream_t st) {
+                        int world, void* out, bool out_f32, float scale, bool accumulate, int blocks, float* norm_out,
+                        cudaStream_t st) {
     StagedSlices sl;
     sl.count = count;
     for (int k = 0; k < count; ++k) sl.p[k] = static_cast<const __nv_bfloat16*>(staged[k]);
     if (out_f32)
         reduce_staged_kernel<float><<<blocks, 512, 0, st>>>(static_cast<const __nv_bfloat16*>(own_full), sl, segs, rank,
-                                                            world, static_cast<float*>(out), scale, accumulate ? 1 : 0);
+                                                            world, static_cast<float*>(out), scale, accumulate ? 1 : 0,
+                                                            norm_out);
     else
         reduce_staged_kernel<__nv_bfloat16><<<blocks, 512, 0, st>>>(static_cast<const __nv_bfloat16*>(own_full), sl,
                                                                     segs, rank, world, static_cast<__nv_bfloat16*>(out),
-                                                                    scale, accumulate ? 1 : 0);
+                                                                    scale, accumulate ? 1 : 0, norm_out);
 }
 
 void comm_allreduce_multimem(const CommPeers& peers, void* multicast_base, long long byte_off, long long numel, bool f32,

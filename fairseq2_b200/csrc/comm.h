@@ -35,16 +35,20 @@ void comm_allreduce_multimem(const CommPeers& peers, void* multicast_base, long 
 // out[i] = sum over w < world of slices[w * n + i] (bf16 in, fp32 sum, bf16 or fp32 out); n a multiple of 8.
 void comm_reduce_slices(const void* slices, int world, long long n, void* out, bool out_f32, cudaStream_t st);
 // out[off_s + i] = scale * (own_full[W * off_s + rank * numel_s + i] + sum_k staged[k][off_s + i]); local memory only.
+// `norm_out` (may be null): the sum of squares of everything stored is added to it.
 void comm_reduce_staged(const void* own_full, const void* const* staged, int count, const CommSegments& segs, int rank,
-                        int world, void* out, bool out_f32, float scale, bool accumulate, int blocks, cudaStream_t st);
+                        int world, void* out, bool out_f32, float scale, bool accumulate, int blocks, float* norm_out,
+                        cudaStream_t st);
 // Waits (bounded) until every peer's flag in `slot` has reached `epoch`, without signalling.
 void comm_wait(const CommPeers& peers, int slot, uint32_t epoch, int* status, cudaStream_t st);
 void comm_allgather_segments(const CommPeers& peers, const CommSegments& segs, long long shard_byte_off, void* full,
                              long long shard_numel, int slot, uint32_t epoch, int blocks, int* status,
                              cudaStream_t st);
+// Reduce-scatter by peer loads: out[off_s + i] = scale * sum_r peer_r.full[W * off_s + rank * numel_s + i]. With
+// `norm_out` (may be null) the sum of squares of the stored shard is added to that device scalar in the same pass.
 void comm_reducescatter_segments(const CommPeers& peers, const CommSegments& segs, long long full_byte_off, void* out,
                                  bool out_f32, long long shard_numel, float scale, bool accumulate, int slot,
-                                 uint32_t epoch, int blocks, int* status, cudaStream_t st);
+                                 uint32_t epoch, int blocks, float* norm_out, int* status, cudaStream_t st);
 void comm_allreduce_f32(const CommPeers& peers, long long byte_off, float* out, long long numel, int op, int slot,
                         uint32_t epoch, int blocks, int* status, cudaStream_t st);
 void comm_pull(const CommPeers& peers, int src_rank, long long byte_off, void* dst, long long bytes, int slot,
@@ -58,8 +62,9 @@ void comm_reducescatter_adamw(const CommPeers& peers, const CommSegments& segs, 
                               float* m, float* v, void* low, float scale, float lr, float beta1, float beta2, float eps,
                               float wd, int step, int slot, uint32_t epoch, int blocks, int* status, cudaStream_t st);
 
-// In-place all-reduce (sum * scale) of `numel` bf16/fp32 elements at `byte_off` of every arena; `counter` is a zeroed
-// device word; at most `blocks` <= number of SMs CTAs.
+// In-place all-reduce (sum * scale) of `numel` bf16/fp32 elements at `byte_off` of every arena; `counter` points at
+// TWO zeroed device words (end of phase 1, end of phase 2); at most `blocks` <= number of SMs CTAs. The kernel ends
+// only after every peer has finished reading this rank's bucket, so the bucket may be rewritten right after it.
 void comm_allreduce_inplace(const CommPeers& peers, long long byte_off, long long numel, bool f32, float scale,
                             int slot_in, int slot_mid, uint32_t epoch, unsigned int* counter, int blocks, int* status,
                             cudaStream_t st);

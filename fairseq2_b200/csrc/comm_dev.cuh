@@ -38,6 +38,31 @@ __device__ __forceinline__ void st16(void* p, uint4 v) {
                  : "memory");
 }
 
+// One thread stores `epoch` into this rank's column of `slot` in every rank's flag page.
+__device__ __forceinline__ void signal_all(const CommPeers& peers, int slot, uint32_t epoch) {
+    for (int r = 0; r < peers.world; ++r) {
+        uint32_t* f = reinterpret_cast<uint32_t*>(peers.base[r]) + slot * kCommMaxRanks + peers.rank;
+        st_release_sys(f, epoch);
+    }
+}
+
+// One thread waits (bounded) until every peer's flag in `slot` reached `epoch`; no block-wide synchronisation.
+__device__ __forceinline__ bool wait_all_one_thread(const CommPeers& peers, int slot, uint32_t epoch, int* status,
+                                                    int site) {
+    const uint32_t* mine = reinterpret_cast<const uint32_t*>(peers.base[peers.rank]) + slot * kCommMaxRanks;
+    const uint64_t t0 = global_timer_ns();
+    for (int r = 0; r < peers.world; ++r) {
+        uint32_t spins = 0;
+        while (static_cast<int32_t>(ld_acquire_sys(mine + r) - epoch) < 0) {
+            if ((++spins & 255u) == 0 && global_timer_ns() - t0 > peers.wait_limit_ns) {
+                report_status(status, kStatusTimeout | (site << 8));
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
 // Thread 0 of the block signals (optionally) and waits until every peer's flag
 // in `slot` reached `epoch`; returns false for the whole block on time-out.
 __device__ __forceinline__ bool signal_and_wait(const CommPeers& peers, int slot, uint32_t epoch, bool do_signal,

@@ -504,7 +504,15 @@ template <typename G>
 __global__ void adamw_kernel(float* __restrict__ p, const G* __restrict__ g, float* __restrict__ m,
                              float* __restrict__ v, __nv_bfloat16* __restrict__ low, size_t n, float lr, float beta1,
                              float beta2, float eps, float wd, float bc1, float bc2_sqrt,
-                             const float* __restrict__ grad_scale) {
+                             const float* __restrict__ grad_scale, const int* __restrict__ guard) {
+    // `guard` is the status word of the bounded waits: a collective that gave up left this step's gradients (or
+    // parameters) incomplete, so the update is skipped and the weights stay as they were; the host raises.
+    if (guard != nullptr) {
+        __shared__ int bad;
+        if (threadIdx.x == 0) bad = *reinterpret_cast<const volatile int*>(guard);
+        __syncthreads();
+        if (bad != 0) return;
+    }
     const float gs = grad_scale ? *grad_scale : 1.f;
     const size_t nvec = n / 8;
     const float step_size = lr / bc1;
@@ -747,7 +755,8 @@ void ce_fwd_bwd(void* logits, const long long* targets, const float* mask, float
 }
 
 void adamw(float* p, const void* g, bool g_bf16, float* m, float* v, void* low, size_t n, float lr, float beta1,
-           float beta2, float eps, float wd, int step, const float* grad_scale, int num_sms, cudaStream_t st) {
+           float beta2, float eps, float wd, int step, const float* grad_scale, const int* guard, int num_sms,
+           cudaStream_t st) {
     if (n == 0) return;
     const float bc1 = 1.f - powf(beta1, static_cast<float>(step));
     const float bc2 = 1.f - powf(beta2, static_cast<float>(step));
@@ -755,11 +764,11 @@ void adamw(float* p, const void* g, bool g_bf16, float* m, float* v, void* low, 
     if (g_bf16)
         adamw_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p, static_cast<const __nv_bfloat16*>(g), m, v,
                                                           static_cast<__nv_bfloat16*>(low), n, lr, beta1, beta2, eps,
-                                                          wd, bc1, sqrtf(bc2), grad_scale);
+                                                          wd, bc1, sqrtf(bc2), grad_scale, guard);
     else
         adamw_kernel<float><<<grid, 256, 0, st>>>(p, static_cast<const float*>(g), m, v,
                                                   static_cast<__nv_bfloat16*>(low), n, lr, beta1, beta2, eps, wd, bc1,
-                                                  sqrtf(bc2), grad_scale);
+                                                  sqrtf(bc2), grad_scale, guard);
 }
 
 void l2_norm_sq(const void* x, bool bf16, size_t n, float* out, int num_sms, cudaStream_t st) {

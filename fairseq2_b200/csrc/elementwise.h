@@ -32,8 +32,10 @@ void rope_inplace(void* x, const float* freqs, const int* pos, size_t tokens, in
                   size_t hstride, int max_pos, bool inverse, int num_sms, cudaStream_t st);
 void ce_fwd_bwd(void* logits, const long long* targets, const float* mask, float* row_loss, int rows, int V,
                 int pad_idx, cudaStream_t st);
+// `guard` (may be null): a device-readable status word; the update is skipped when it is non-zero.
 void adamw(float* p, const void* g, bool g_bf16, float* m, float* v, void* low, size_t n, float lr, float beta1,
-           float beta2, float eps, float wd, int step, const float* grad_scale, int num_sms, cudaStream_t st);
+           float beta2, float eps, float wd, int step, const float* grad_scale, const int* guard, int num_sms,
+           cudaStream_t st);
 void l2_norm_sq(const void* x, bool bf16, size_t n, float* out, int num_sms, cudaStream_t st);
 void scale_inplace(void* x, bool bf16, size_t n, const float* scale, int num_sms, cudaStream_t st);
 

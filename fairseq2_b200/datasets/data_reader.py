@@ -111,7 +111,14 @@ class DataPipelineReader(DataReader[BatchT]):
         self._iter = None
         self._pipeline.reset()
 
+    @property
+    def stateless(self) -> bool:
+        """True if the underlying pipeline cannot record its position (no ``load_state_dict``)."""
+        return not hasattr(self._pipeline, "load_state_dict")
+
     def state_dict(self) -> dict[str, Any]:
+        if self.stateless:
+            return {}
         try:
             return self._pipeline.state_dict(strict=self._strict_state)
         except TypeError:

@@ -89,6 +89,13 @@ class DataParallelFacade:
         if self.kind == "fsdp":
             self.module.after_optimizer_step()  # type: ignore[operator]
 
+    def check_comm_status(self) -> None:
+        """Raises ``KernelWaitTimeout`` if a peer-memory collective of this process gave up waiting for a peer.
+        Costs one read of a host-mapped word; does not synchronise with the device."""
+        arena = getattr(self.module, "arena", None)
+        if arena is not None:
+            arena.ext.check_status()
+
     def summon_full_parameters(self):  # type: ignore[no-untyped-def]
         if self.kind == "fsdp":
             return self.module.summon_full_parameters()  # type: ignore[operator]

@@ -87,11 +87,34 @@ class AdamW(Optimizer):
                 st0 = self.state[unit.shard_params[0]]
                 step = int(st0["step"].item()) + 1 if "_host_step" not in st0 else st0["_host_step"] + 1
                 m, v = self._unit_moments(unit)
-                low = unit.low_shard if unit.low_shard.dtype == torch.bfloat16 else None
-                multi_tensor_adamw([unit.master], [unit.grad_shard], [m], [v], [low], lr=lr, beta1=b1, beta2=b2,
-                                   eps=eps, weight_decay=wd, step=step, grad_scale=grad_scale)
+                offloaded = unit.master.device != unit.low_shard.device
+                low = unit.low_shard if (unit.low_shard.dtype == torch.bfloat16 and not offloaded) else None
+                grad = unit.grad_shard
+                gs = grad_scale
+                if offloaded:            # CPU offload: the update runs where the fp32 state lives
+                    grad = grad.to(unit.master.device)
+                    gs = grad_scale.to(unit.master.device) if grad_scale is not None else None
+                # Parameters that received no gradient since ``zero_grad`` (frozen, or unused in this step) are
+                # left alone -- no weight decay, no moment decay -- as ``torch.optim.AdamW`` leaves parameters
+                # whose ``grad`` is None: one launch per maximal run of adjacent parameters that took part.
+                took = getattr(unit, "took_part", None)
+                if took is None or all(took):
+                    ranges = [(0, unit.shard_size)]
+                else:
+                    ranges = []
+                    for s, t in zip(unit.specs, took):
+                        if not t:
+                            continue
+                        if ranges and ranges[-1][1] == s.shard_off:
+                            ranges[-1] = (ranges[-1][0], s.shard_off + s.shard_numel)
+                        else:
+                            ranges.append((s.shard_off, s.shard_off + s.shard_numel))
+                for lo, hi in ranges:
+                    multi_tensor_adamw([unit.master[lo:hi]], [grad[lo:hi]], [m[lo:hi]], [v[lo:hi]],
+                                       [low[lo:hi] if low is not None else None], lr=lr, beta1=b1, beta2=b2,
+                                       eps=eps, weight_decay=wd, step=step, grad_scale=gs)
                 if low is None:
-                    unit.low_shard.copy_(unit.master)
+                    unit.low_shard.copy_(unit.master, non_blocking=True)
                 for sp in unit.shard_params:
                     st = self.state[sp]
                     st["_host_step"] = step

@@ -31,7 +31,8 @@ class Float16LossScaler:
     def unscale_grads_(self, model: Any) -> None:
         pass
 
-    def run_optimizer_step(self, optimizer: Optimizer, *, grad_scale: Tensor | None = None) -> Float16LossScaleResult:
+    def run_optimizer_step(self, optimizer: Optimizer, *, grad_scale: Tensor | None = None,
+                           grad_norm: Tensor | None = None) -> Float16LossScaleResult:
         if grad_scale is not None:
             optimizer.step(grad_scale=grad_scale)  # type: ignore[call-arg]
         else:
@@ -67,7 +68,17 @@ class StandardFloat16LossScaler(Float16LossScaler):
         (loss * self._scale).backward()
 
     def unscale_grads_(self, model: Any) -> None:
+        """Divides the gradients by the loss scale and looks for non-finite values. A model whose gradients live
+        in flat shards and whose scaling is deferred into the optimizer launch (``scale_grads`` + ``grad_scale``,
+        i.e. FSDP) only records the factor here; its overflow check is the finiteness of the global gradient norm,
+        which :meth:`run_optimizer_step` receives (already reduced over the ranks)."""
         inv = 1.0 / self._scale
+        if getattr(model, "kind", None) == "fsdp":
+            model.scale_grads(inv)
+            self._found_inf = None
+            self._check_norm = True
+            return
+        self._check_norm = False
         found = torch.zeros((), device=self._gang.device)
         params = list(model.parameters())
         for p in params:
@@ -80,8 +91,11 @@ class StandardFloat16LossScaler(Float16LossScaler):
             self._gang.all_reduce(found, ReduceOperation.SUM)
         self._found_inf = found
 
-    def run_optimizer_step(self, optimizer: Optimizer, *, grad_scale: Tensor | None = None) -> Float16LossScaleResult:
+    def run_optimizer_step(self, optimizer: Optimizer, *, grad_scale: Tensor | None = None,
+                           grad_norm: Tensor | None = None) -> Float16LossScaleResult:
         overflow = bool(self._found_inf is not None and float(self._found_inf) > 0)
+        if getattr(self, "_check_norm", False) and grad_norm is not None:
+            overflow = overflow or not bool(torch.isfinite(grad_norm))
         self._found_inf = None
         old = self._scale
         if overflow:

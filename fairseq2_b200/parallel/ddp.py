@@ -51,6 +51,8 @@ class _Bucket:
             off += p.numel()
         self.pending = len(params)
         self.event: torch.cuda.Event | None = None
+        self.epoch = 0            # reductions of this bucket so far (every reduction gets an epoch of its own)
+        self.reduced_in_step = 0  # reductions since the last ``zero_grad``
 
 
 class DDP(Module):
@@ -62,11 +64,20 @@ class DDP(Module):
                  allreduce: str = "auto") -> None:
         """``allreduce`` picks the kernel of the symmetric-memory path: "multimem" reduces inside the NVSwitch
         (``multimem.ld_reduce`` / ``multimem.st`` on the multicast mapping of the arena), "p2p" is the two-shot
-        kernel on plain peer loads and stores and what "auto" selects."""
+        kernel on plain peer loads and stores. "auto" takes "multimem" where the arena has a multicast mapping and
+        "p2p" otherwise; ``FAIRSEQ2_B200_DDP_ALLREDUCE`` overrides it.
+
+        Gradient accumulation: a bucket is reduced whenever all of its gradients have been produced, i.e. once per
+        micro-batch unless the backward pass runs under :meth:`no_sync`. Reducing the running sum again is exact for
+        ``average=True`` (the mean of a value that is already identical on every rank is that value); with
+        ``average=False`` the earlier micro-batches would be counted ``size`` times, so a second reduction of a
+        bucket within one step raises -- accumulate under ``no_sync`` there."""
         super().__init__()
         if allreduce not in ("auto", "multimem", "p2p"):
             raise ValueError(f"`allreduce` must be 'auto', 'multimem' or 'p2p', but is '{allreduce}' instead.")
-        self._allreduce = allreduce
+        import os
+
+        self._allreduce = os.environ.get("FAIRSEQ2_B200_DDP_ALLREDUCE", allreduce)
         self.module = module
         self.gang: Gang = gangs.rdp if gangs.rdp.size > 1 else gangs.dp
         self.average = average
@@ -91,10 +102,10 @@ class DDP(Module):
         if cur:
             groups.append(cur)
         self.arena = self._maybe_create_arena(groups, comm)
-        self._epoch = 0
         self._counter_off = -1
         if self.arena is not None:
-            self._counter_off, c = self.arena.alloc(4 * len(groups), align=16)
+            # two zeroed words per bucket: "last CTA" counters of the two phases of the in-place kernel
+            self._counter_off, c = self.arena.alloc(8 * len(groups), align=16)
             c.zero_()
         self.buckets: list[_Bucket] = [_Bucket(g, self.arena, i) for i, g in enumerate(groups)]
         if self.arena is not None:
@@ -138,12 +149,19 @@ class DDP(Module):
             b.views[i].copy_(p.grad)
             p.grad = b.views[i]
         b.pending -= 1
-        if b.pending == 0 and self._require_sync:
-            self._reduce(b)
+        if b.pending == 0:
+            b.pending = len(b.params)          # the next micro-batch counts from the top again
+            if self._require_sync:
+                self._reduce(b)
 
     def _reduce(self, b: _Bucket) -> None:
         if self.gang.size == 1:
             return
+        b.reduced_in_step += 1
+        if b.reduced_in_step > 1 and not self.average:
+            raise RuntimeError("A gradient bucket was summed over the ranks twice in one step, which counts the "
+                               "earlier micro-batches `size` times; accumulate under `no_sync()` or use "
+                               "`average=True`.")
         if self.arena is not None:
             self._reduce_symm(b)
             return
@@ -158,11 +176,13 @@ class DDP(Module):
     def _reduce_symm(self, b: _Bucket) -> None:
         a = self.arena
         assert a is not None and self.comm_stream is not None
-        # every bucket is reduced once per step, in the same order on every rank: the step counter is the epoch
-        epoch = self._step_epoch
+        # every reduction of a bucket has an epoch of its own (the flags only grow; a repeated epoch would let both
+        # waits of the kernel pass without synchronising); all ranks reduce a bucket equally often
+        b.epoch += 1
+        epoch = b.epoch
         scale = 1.0 / self.gang.size if self.average else 1.0
         blocks = max(1, min(64, b.padded * b.flat.element_size() // (512 * 16 * 4)))
-        use_mm = self._allreduce == "multimem"          # "auto" stays on plain peer loads/stores
+        use_mm = self._allreduce == "multimem" or (self._allreduce == "auto" and a.multicast_ptr != 0)
         if use_mm and a.multicast_ptr == 0:
             raise RuntimeError("The symmetric arena has no NVSwitch multicast mapping; use allreduce='p2p'.")
         self.comm_stream.wait_stream(torch.cuda.current_stream(self.device))
@@ -170,25 +190,26 @@ class DDP(Module):
             fn = a.ext.comm_allreduce_multimem if use_mm else a.ext.comm_allreduce_inplace
             args = (a.multicast_ptr,) if use_mm else ()
             fn(a.peer_ptrs, a.rank, *args, b.byte_off, b.padded, b.flat.dtype == torch.float32, scale,
-               self.SLOT_BASE + 2 * b.index, self.SLOT_BASE + 2 * b.index + 1, epoch, self._counter_off + 4 * b.index,
+               self.SLOT_BASE + 2 * b.index, self.SLOT_BASE + 2 * b.index + 1, epoch, self._counter_off + 8 * b.index,
                a.device_index, blocks, a.wait_limit_s)
-
-    @property
-    def _step_epoch(self) -> int:
-        return self._epoch + 1
 
     def finish_backward(self) -> None:
         for b in self.buckets:
-            if self._require_sync and b.pending != 0 and b.pending != len(b.params):
-                # some parameters of the bucket received no gradient this step
+            if self._require_sync and b.pending != len(b.params):
+                # some parameters of the bucket received no gradient in the last backward pass
+                for i, p in enumerate(b.params):
+                    if p.grad is None:
+                        b.views[i].zero_()
+                        p.grad = b.views[i]
+                self._reduce(b)
+            elif self._require_sync and b.reduced_in_step == 0 and any(p.grad is not None for p in b.params):
+                # gradients accumulated under ``no_sync`` only: reduce them now
                 for i, p in enumerate(b.params):
                     if p.grad is None:
                         b.views[i].zero_()
                         p.grad = b.views[i]
                 self._reduce(b)
             b.pending = len(b.params)
-        if self._require_sync:
-            self._epoch += 1
         if self.comm_stream is not None:
             torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
 
@@ -206,6 +227,7 @@ class DDP(Module):
             for p in b.params:
                 p.grad = None
             b.pending = len(b.params)
+            b.reduced_in_step = 0
 
 
 def convert_batch_norms(module: Module, gangs: Gangs) -> Module:

@@ -77,7 +77,8 @@ class FlatParamUnit:
     """One FSDP unit: the parameters of ``module`` that are not owned by a nested unit."""
 
     def __init__(self, name: str, module: Module, named_params: list[tuple[str, list[tuple[Module, str]], Parameter]],
-                 gang: Gang, *, param_dtype: DataType, reduce_dtype: DataType, reshard_after_forward: bool) -> None:
+                 gang: Gang, *, param_dtype: DataType, reduce_dtype: DataType, reshard_after_forward: bool,
+                 cpu_offload: bool = False) -> None:
         self.name, self.module, self.gang = name, module, gang
         self.world, self.rank = gang.size, gang.rank
         self.param_dtype, self.reduce_dtype = param_dtype, reduce_dtype
@@ -109,6 +110,10 @@ class FlatParamUnit:
                     src = p.detach().reshape(s.d0, s.row)[r * s.chunk: r * s.chunk + s.rows_local]
                     self.master[s.shard_off: s.shard_off + s.rows_local * s.row].copy_(src.reshape(-1))
         self.low_shard = self.master.to(param_dtype)
+        if cpu_offload and dev.type == "cuda":
+            # fp32 master weights (and, through the optimizer, the moments) live in pinned host memory; only the
+            # low-precision shard that feeds the all-gather stays on the device (cf. FSDP2 ``CPUOffloadPolicy``)
+            self.master = self.master.cpu().pin_memory()
         self.full: Tensor | None = self.low_shard if W == 1 else None
         self.grad_full: Tensor | None = None
         self.grad_shard: Tensor | None = None   # reduced gradient of the local shard
@@ -117,6 +122,12 @@ class FlatParamUnit:
         self._ag_event: torch.cuda.Event | None = None
         self.arena: Any = None
         self.needs_reduce = False   # gradients were (or may have been) produced since the last reduction
+        #: per parameter: did it receive a gradient since the last ``zero_grad``? (the optimizer leaves the others
+        #: untouched, as ``torch.optim.AdamW`` does for parameters whose ``grad`` is None)
+        self.took_part: list[bool] = [False] * len(specs)
+        #: device scalar that the reduce-scatter kernels add this unit's squared gradient norm to (set by FSDP)
+        self.norm_slot: Tensor | None = None
+        self.norm_fused = False     # ``norm_slot`` holds the norm of the current ``grad_shard``
 
         # shard parameters handed to the optimizer / state dict
         self.shard_params: list[Parameter] = []
@@ -140,8 +151,13 @@ class FlatParamUnit:
     # ------------------------------------------------------------- arena
     #: "copy": all-gather through the copy engines (no SM); "kernel": the load/store kernel
     allgather_engine = "kernel"
+    #: "copy": peers' slices through the copy engines + local sum kernel; "kernel": ONE kernel that loads the peers'
+    #: slices over NVLink, sums, scales, stores the fp32 shard and adds the unit's squared norm
+    reducescatter_engine = "kernel"
     #: thread blocks of the reduce-scatter kernel
     rs_blocks = 48
+    #: thread blocks of the local sum kernel of the copy-engine reduce-scatter
+    rs_local_blocks = 192
     #: local bf16 buffer of (world - 1) shards shared by all units: when set, the NVLink half of the reduce-scatter
     #: runs on the copy engines and only the final sum runs on SMs
     rs_staging: Tensor | None = None
@@ -255,11 +271,14 @@ class FlatParamUnit:
             return
         self.needs_reduce = False
         self.collect_autograd_grads()
-        for s, cp in zip(self.specs, self.compute_params):
-            if not getattr(cp, "grad_sink_filled", False) and getattr(cp, "grad_sink", None) is not None:
-                cp.grad_sink.zero_()  # type: ignore[attr-defined]  # parameter took no part in this step
+        for i, (s, cp) in enumerate(zip(self.specs, self.compute_params)):
+            if getattr(cp, "grad_sink_filled", False):
+                self.took_part[i] = True
+            elif getattr(cp, "grad_sink", None) is not None:
+                cp.grad_sink.zero_()  # type: ignore[attr-defined]  # parameter took no part in this pass
                 cp.grad_sink_filled = True  # type: ignore[attr-defined]
         W = self.world
+        self.norm_fused = False
         if W == 1:
             self.grad_shard = self.grad_full
             self.grads_ready = True
@@ -279,15 +298,22 @@ class FlatParamUnit:
                 if not acc:
                     self.grad_shard = torch.empty(self.shard_size, device=self.device, dtype=torch.float32)
                 self.rs_epoch += 1
-                if self.rs_staging is not None:
+                # the squared norm of the shard is a by-product of the pass that writes it (not when this pass adds
+                # to an earlier micro-batch's sum: then only a pass over the final sum gives the norm)
+                norm = self.norm_slot if not acc else None
+                if norm is not None:
+                    norm.zero_()
+                if self.rs_staging is not None and self.reducescatter_engine == "copy":
                     a.ext.comm_reducescatter_copy(a.peer_ptrs, a.rank, self.seg_offs, self.seg_numels, self.grad_off,
                                                   self.rs_staging, self.grad_shard, (1.0 / W) if average else 1.0, acc,
-                                                  2 + self.slot, self.rs_epoch, 4 * self.rs_blocks, a.wait_limit_s)
+                                                  2 + self.slot, self.rs_epoch, self.rs_local_blocks, a.wait_limit_s,
+                                                  norm)
                 else:
                     a.ext.comm_reducescatter_segments(a.peer_ptrs, a.rank, self.seg_offs, self.seg_numels,
                                                       self.grad_off, self.grad_shard, (1.0 / W) if average else 1.0,
                                                       acc, 2 + self.slot, self.rs_epoch, self.rs_blocks,
-                                                      a.wait_limit_s)
+                                                      a.wait_limit_s, norm)
+                self.norm_fused = norm is not None
             self.grads_ready = True
             for cp in self.compute_params:
                 cp.grad_sink_filled = False  # type: ignore[attr-defined]
@@ -316,6 +342,8 @@ class FlatParamUnit:
 
     def zero_grad(self) -> None:
         self.grads_ready = False
+        self.norm_fused = False
+        self.took_part = [False] * len(self.specs)
         if self.world == 1:
             if self.grad_full is not None:
                 # keep the buffer, mark every sink as empty: the next wgrad overwrites
@@ -338,6 +366,8 @@ class FlatParamUnit:
     def local_grad_norm_sq(self) -> Tensor | None:
         if not self.grads_ready or self.grad_shard is None:
             return None
+        if self.norm_fused and self.norm_slot is not None:
+            return self.norm_slot
         g = self.grad_shard
         if self.world == 1:
             # padding between regions is zero, so the flat norm is the parameter norm
@@ -395,15 +425,15 @@ class FSDP(Module):
     def __init__(self, module: Module, gangs: Gangs, *, wrap_policy: FSDPWrapPolicy | None = layerwise_wrap_policy,
                  param_dtype: DataType = torch.bfloat16, fp32_reduce: bool = True,
                  reshard_after_forward: bool = True, overlap: bool = True, comm: str = "auto",
-                 allgather: str = "copy", reducescatter: str = "copy", rs_blocks: int = 48) -> None:
+                 allgather: str = "copy", reducescatter: str = "copy", rs_blocks: int = 48,
+                 wait_limit_s: float | None = None, cpu_offload: bool = False) -> None:
         super().__init__()
         self.module = module
         self.gangs = gangs
         self.gang = gangs.sdp if gangs.sdp.size > 1 or gangs.rdp.size > 1 else gangs.dp
-        if gangs.rdp.size > 1 and gangs.sdp.size > 1:
-            self.replica_gang: Gang | None = gangs.rdp
-        else:
-            self.replica_gang = None
+        # gradients are averaged over the replicas after the reduce-scatter whenever there is more than one
+        # replica, also when nothing is sharded (sdp of one rank: the "shard" is the whole parameter)
+        self.replica_gang: Gang | None = gangs.rdp if gangs.rdp.size > 1 else None
         W = self.gang.size
         self.param_dtype = param_dtype
         reduce_dtype = torch.float32 if (fp32_reduce and W > 1) else param_dtype
@@ -432,7 +462,7 @@ class FSDP(Module):
             if not nps:
                 return None
             u = FlatParamUnit(name, m, nps, self.gang, param_dtype=param_dtype, reduce_dtype=reduce_dtype,
-                              reshard_after_forward=reshard)
+                              reshard_after_forward=reshard, cpu_offload=cpu_offload)
             owned.update(id(cp) for cp in u.compute_params)
             return u
 
@@ -448,6 +478,7 @@ class FSDP(Module):
         # cast floating-point buffers (e.g. nothing for RoPE tables which stay fp32 by design)
         dev = self.all_units[0].device if self.all_units else torch.device("cpu")
         self.device = dev
+        self.cpu_offload = cpu_offload
         self.comm_stream = torch.cuda.Stream(dev) if (overlap and dev.type == "cuda" and W > 1) else None
         self._require_sync = True
         self._grad_scale: Tensor | None = None
@@ -462,8 +493,11 @@ class FSDP(Module):
 
             if symmetric_memory_available(self.gang):
                 need = sum((1 + W) * u.shard_size * 2 + 1024 for u in self.all_units) + (1 << 20)
+                if wait_limit_s is None:
+                    # training: ranks may legitimately drift apart by a data-loader stall or a checkpoint write
+                    wait_limit_s = float(os.environ.get("FAIRSEQ2_B200_WAIT_LIMIT_S", "120"))
                 try:
-                    self.arena = SymmetricArena(self.gang, need)  # type: ignore[arg-type]
+                    self.arena = SymmetricArena(self.gang, need, wait_limit_s=wait_limit_s)  # type: ignore[arg-type]
                     engine = os.environ.get("FAIRSEQ2_B200_FSDP_ALLGATHER", allgather)
                     if engine not in ("copy", "kernel"):
                         raise ValueError(f"`allgather` must be 'copy' or 'kernel', but is '{engine}' instead.")
@@ -471,7 +505,16 @@ class FSDP(Module):
                         u.attach_arena(self.arena, i)
                         u.allgather_engine = engine
                         u.rs_blocks = int(os.environ.get("FAIRSEQ2_B200_FSDP_RS_BLOCKS", rs_blocks))
-                    if os.environ.get("FAIRSEQ2_B200_FSDP_REDUCESCATTER", reducescatter) == "copy":
+                    rs_engine = os.environ.get("FAIRSEQ2_B200_FSDP_REDUCESCATTER", reducescatter)
+                    if rs_engine not in ("copy", "kernel"):
+                        raise ValueError(f"`reducescatter` must be 'copy' or 'kernel', but is '{rs_engine}' instead.")
+                    local_blocks = int(os.environ.get("FAIRSEQ2_B200_FSDP_RS_LOCAL_BLOCKS", "192"))
+                    self._norm_slots = torch.zeros(len(self.all_units), device=dev, dtype=torch.float32)
+                    for i, u in enumerate(self.all_units):
+                        u.reducescatter_engine = rs_engine
+                        u.rs_local_blocks = local_blocks
+                        u.norm_slot = self._norm_slots[i]
+                    if rs_engine == "copy":
                         biggest = max(u.shard_size for u in self.all_units)
                         staging = torch.empty((W - 1) * biggest, device=dev, dtype=torch.bfloat16)
                         for u in self.all_units:
@@ -572,6 +615,14 @@ class FSDP(Module):
             for u in self.all_units:
                 if u.grad_shard is not None:
                     self.replica_gang.all_reduce(u.grad_shard, ReduceOperation.MEAN)
+
+    def check_comm_status(self) -> None:
+        """Raises :class:`~fairseq2_b200.ops._ext.KernelWaitTimeout` if a kernel of this process gave up on a
+        bounded wait (a peer that never arrived). Reads a host-mapped word: no synchronisation with the device.
+        The optimizer kernels check the same word on the device and leave the weights untouched once it is set,
+        so a step that ran on incomplete gradients never reaches the parameters."""
+        if self.arena is not None:
+            self.arena.ext.check_status()
 
     def after_optimizer_step(self) -> None:
         """The optimizer wrote new bf16 shards: gathered copies are stale. With the
@@ -695,7 +746,7 @@ class FSDP(Module):
         out: dict[str, Tensor] = {}
         for u in self.all_units:
             for s in u.specs:
-                local = u.master[s.shard_off: s.shard_off + s.chunk * s.row]
+                local = u.master[s.shard_off: s.shard_off + s.chunk * s.row].to(u.device)
                 if u.world > 1:
                     buf = torch.empty((u.world, s.chunk * s.row), device=u.device, dtype=torch.float32)
                     u.gang.all_gather(buf, local.contiguous())
@@ -742,6 +793,9 @@ def _materialize(module: Module, device: Device, memo: dict[int, Parameter]) -> 
 
 def to_fsdp(module: Module, gangs: Gangs, *, wrap_policy: FSDPWrapPolicy | None = layerwise_wrap_policy,
             mixed_precision_dtype: DataType | None = torch.bfloat16, fp32_reduce: bool = True,
-            reshard_after_forward: bool = True, **_: Any) -> FSDP:
+            reshard_after_forward: bool = True, cpu_offload: bool = False, **_: Any) -> FSDP:
+    """``cpu_offload`` keeps the fp32 master weights and the optimizer state in pinned host memory (the
+    reference's ``to_fsdp2(..., cpu_offload=True)``, ``nn/fsdp/fsdp2.py:70,128-131``): the reduced gradient
+    shard is copied to the host, the optimizer runs there and the updated low-precision shard is copied back."""
     return FSDP(module, gangs, wrap_policy=wrap_policy, param_dtype=mixed_precision_dtype or torch.float32,
-                fp32_reduce=fp32_reduce, reshard_after_forward=reshard_after_forward)
+                fp32_reduce=fp32_reduce, reshard_after_forward=reshard_after_forward, cpu_offload=cpu_offload)

@@ -249,7 +249,8 @@ class RecipeContext:
             if policy is None and ts.fsdp.granularity != "model":
                 from fairseq2_b200.parallel.fsdp import layerwise_wrap_policy as policy  # type: ignore[no-redef]
             return FSDP(model, gangs, wrap_policy=policy, param_dtype=param_dtype, fp32_reduce=ts.fsdp.fp32_reduce,
-                        reshard_after_forward=ts.fsdp.reshard_after_forward, comm=ts.fsdp.comm)
+                        reshard_after_forward=ts.fsdp.reshard_after_forward, comm=ts.fsdp.comm,
+                        cpu_offload=ts.fsdp.cpu_offload, wait_limit_s=ts.fsdp.wait_limit)
         model = model.to(self.device)
         if gangs.dp.size > 1:
             return DDP(model, gangs)

@@ -82,6 +82,9 @@ class FSDPSection:
     reshard_after_forward: bool = True
     fp32_reduce: bool = True
     comm: Literal["auto", "symm", "nccl"] = "auto"
+    cpu_offload: bool = False
+    #: seconds a peer-memory collective waits for a peer before it gives up and the step raises
+    wait_limit: float = 120.0
 
 
 @dataclass(kw_only=True)

@@ -72,10 +72,17 @@ class TrainStep:
         self.max_grad_norm, self.lr_scheduler, self.loss_scaler = max_grad_norm, lr_scheduler, loss_scaler
         self.no_sync = no_sync
         self.metric_bag = metric_bag
+        #: outcome of the last optimizer step under fp16 loss scaling (``None`` without a loss scaler)
+        self.last_scale_result: Any | None = None
 
     def __call__(self, batches: Sequence[Any], step_nr: int = 0) -> tuple[Tensor, Tensor]:
         """Returns ``(summed loss, gradient norm)`` as device tensors."""
         model = self.unit.model
+        # a collective kernel of an earlier step that gave up on a peer (bounded wait) surfaces here, before new
+        # work is queued; the optimizer kernels skip their update on the device in the meantime
+        check = getattr(model, "check_comm_status", None)
+        if check is not None:
+            check()
         model.zero_grad()
         n = len(batches)
         total_loss: Tensor | None = None
@@ -116,7 +123,12 @@ class TrainStep:
         with record_function(f"step_{step_nr}_optimizer"):
             scale = model.grad_scale
             if self.loss_scaler is not None:
-                self.loss_scaler.run_optimizer_step(self.optimizer, grad_scale=scale)
+                res = self.loss_scaler.run_optimizer_step(self.optimizer, grad_scale=scale, grad_norm=grad_norm)
+                self.last_scale_result = res
+                if res.overflowed:
+                    # the step did not happen: weights, optimizer state and learning-rate schedule stay where they
+                    # were and the caller repeats the batch with the reduced loss scale
+                    return total_loss, grad_norm
             elif scale is not None:
                 self.optimizer.step(grad_scale=scale)  # type: ignore[call-arg]
             else:
@@ -124,6 +136,8 @@ class TrainStep:
             model.after_optimizer_step()
         if self.lr_scheduler is not None:
             self.lr_scheduler.step()
+        if check is not None:
+            check()
         return total_loss, grad_norm
 
 
@@ -366,7 +380,7 @@ class Trainer(Task):
                           [getattr(getattr(b, 'seqs', None), 'shape', None) for b in batches])
                 raise
         self._compute_watch.stop()
-        res = getattr(self._loss_scaler, "last_result", None)
+        res = self._step_fn.last_scale_result
         if res is not None and res.overflowed:
             self._metric_bag.rollback_updates()
             if res.exploded:
@@ -539,10 +553,13 @@ class Trainer(Task):
         self._ckpt.load_trainer_state(step, self)
         self._ckpt.load_model_state(step, self._unit.model)
         self._ckpt.load_optimizer_state(step, self._optimizer)
-        try:
+        # A reader without position state (synthetic data) restarts from the beginning. That is decided from the
+        # reader itself, identically on every rank; a missing or corrupt state FILE is an error that propagates
+        # (the load contains a barrier, so swallowing it on one rank would leave the others waiting).
+        if getattr(self._reader, "stateless", False):
+            log.warning("The data reader keeps no position; the data restarts from the beginning at step {}.", step)
+        else:
             self._ckpt.load_data_reader_state(step, self._reader)
-        except Exception as ex:  # noqa: BLE001 - readers of synthetic data may be stateless
-            log.warning("The data reader state of step {} cannot be restored ({}).", step, ex)
         self._unit.set_step_nr(self._step_nr)
         self._unit.set_data_epoch_nr(self._data_epoch_nr)
         self._gangs.root.barrier()

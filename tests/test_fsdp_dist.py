@@ -129,3 +129,93 @@ def test_ddp_converts_batch_norms_to_sync_batch_norm() -> None:
     """Buffers are not broadcast during training, so batch norms must reduce their statistics over the gang."""
     for name, untouched in run_distributed(_sync_bn_worker, 2):
         assert name == "SyncBatchNorm" and untouched
+
+
+def _accum_worker(rank: int, world: int, kind: str, no_sync: bool):
+    """Two micro-batches per step: the result must equal one step over the four batches of both ranks."""
+    from fairseq2_b200.gang import ProcessGroupGang, create_fsdp_gangs, create_parallel_gangs
+    from fairseq2_b200.nn import BatchLayout
+    from fairseq2_b200.nn.data_parallel import DataParallelFacade
+    from fairseq2_b200.optim import AdamW
+    from fairseq2_b200.parallel.ddp import DDP
+    from fairseq2_b200.parallel.fsdp import FSDP
+    from fairseq2_b200.trainer import TrainStep, TrainUnit
+
+    root = ProcessGroupGang.create_default_process_group(torch.device("cpu"))
+    gangs = create_parallel_gangs(root)
+    _, model = _build()
+    if kind == "fsdp":
+        gangs = create_fsdp_gangs(gangs)
+        wrapped = FSDP(model, gangs, param_dtype=torch.float32)
+        opt = AdamW(wrapped.parameters(), lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1)
+    else:
+        wrapped = DDP(model, gangs)
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1)
+    facade = DataParallelFacade(wrapped)
+
+    class Unit(TrainUnit):
+        @property
+        def model(self):
+            return facade
+
+        def process_batch(self, batch, metric_bag=None):
+            return wrapped(batch, BatchLayout.of(batch), targets=batch), batch.numel()
+
+    step = TrainStep(Unit(), opt, gangs, max_grad_norm=1.0, no_sync=no_sync)
+    data = _data(2 * world, 2)
+    for i, per_slot in enumerate(data):
+        step([per_slot[2 * rank], per_slot[2 * rank + 1]], i)
+    full = wrapped.full_state_dict() if kind == "fsdp" else {k: v.detach().clone() for k, v in model.state_dict().items()}
+    root.close()
+    return {k: v.numpy() for k, v in full.items()}
+
+
+@pytest.mark.parametrize("kind", ["ddp", "fsdp"])
+@pytest.mark.parametrize("no_sync", [False, True])
+def test_gradient_accumulation_matches_one_big_step(kind: str, no_sync: bool) -> None:
+    world = 2
+    _, ref_sd = _single_rank_reference(2 * world, 2)
+    for full in run_distributed(_accum_worker, world, kind, no_sync):
+        for k, v in ref_sd.items():
+            atol = 3e-3 if "embed" in k else 1e-4
+            assert torch.allclose(torch.from_numpy(full[k]), v, atol=atol, rtol=1e-4), k
+
+
+def test_fsdp_frozen_parameter_is_untouched_by_the_optimizer() -> None:
+    """A parameter without a gradient gets no weight decay and no moment update (``torch.optim.AdamW`` skips
+    parameters whose ``grad`` is None); the flat-unit launch must do the same."""
+    from fairseq2_b200.gang import create_fake_gangs
+    from fairseq2_b200.nn import BatchLayout
+    from fairseq2_b200.optim import AdamW
+    from fairseq2_b200.parallel.fsdp import FSDP
+
+    _, model = _build()
+    model.decoder.layers[0].ffn.gate_proj.weight.requires_grad_(False)
+    before = model.decoder.layers[0].ffn.gate_proj.weight.detach().clone()
+    other = model.decoder.layers[0].ffn.output_proj.weight.detach().clone()
+    fsdp = FSDP(model, create_fake_gangs(torch.device("cpu")), param_dtype=torch.float32)
+    opt = AdamW(fsdp.parameters(), lr=1e-2, weight_decay=0.5)
+    b = _data(1, 1)[0][0]
+    for _ in range(2):
+        fsdp.zero_grad()
+        loss = fsdp(b, BatchLayout.of(b), targets=b)
+        loss.backward()
+        fsdp.finish_backward()
+        opt.step()
+        fsdp.after_optimizer_step()
+    sd = fsdp.full_state_dict()
+    assert torch.equal(sd["decoder.layers.0.ffn.gate_proj.weight"], before)
+    assert not torch.equal(sd["decoder.layers.0.ffn.output_proj.weight"], other)
+
+
+def test_fsdp_replica_only_layout_reduces_over_the_replica_gang() -> None:
+    """With one shard rank and several replicas the gradients still have to be averaged over the replicas."""
+    from fairseq2_b200.gang import FakeGang, Gangs
+    from fairseq2_b200.parallel.fsdp import FSDP
+
+    dev = torch.device("cpu")
+    root = FakeGang(dev, rank=0, size=2)
+    gangs = Gangs(root=root, dp=root, rdp=root, sdp=FakeGang(dev), tp=FakeGang(dev), pp=FakeGang(dev))
+    _, model = _build()
+    fsdp = FSDP(model, gangs, param_dtype=torch.float32)
+    assert fsdp.replica_gang is root and fsdp.gang.size == 1
