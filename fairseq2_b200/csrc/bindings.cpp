@@ -260,10 +260,41 @@ std::tuple<Tensor, Tensor> rms_norm_fwd(const Tensor& x, const Tensor& w, double
     return {y, rstd};
 }
 
-std::tuple<Tensor, Tensor> rms_norm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd) {
+// h = x + res, y = rms_norm(h) * w in one pass; returns (h, y, rstd).
+std::tuple<Tensor, Tensor, Tensor> add_rms_norm_fwd(const Tensor& x, const Tensor& res, const Tensor& w, double eps) {
+    TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous() && w.is_contiguous() && res.is_contiguous() &&
+                    res.sizes() == x.sizes() && res.device() == x.device(),
+                "add_rms_norm_fwd: bad input");
+    TORCH_CHECK(x.scalar_type() == w.scalar_type() && x.scalar_type() == res.scalar_type() &&
+                    (is_bf16(x) || x.scalar_type() == at::kFloat),
+                "add_rms_norm_fwd: dtype must be bf16 or fp32 and match the weight and the residual");
+    const int rows = static_cast<int>(x.size(0)), D = static_cast<int>(x.size(1));
+    TORCH_CHECK(D % 8 == 0 && D <= 65536 && w.numel() == D && aligned16(x) && aligned16(w) && aligned16(res),
+                "add_rms_norm_fwd: bad dim");
+    c10::cuda::CUDAGuard guard(x.device());
+    Tensor h = at::empty_like(x);
+    Tensor y = at::empty_like(x);
+    Tensor rstd = at::empty({rows}, x.options().dtype(at::kFloat));
+    if (rows > 0)
+        fs2::rms_norm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr<float>(), rows, D,
+                          static_cast<float>(eps), is_bf16(x), num_sms(x), stream_of(x), res.data_ptr(),
+                          h.data_ptr());
+    g_launches += 1;
+    return {h, y, rstd};
+}
+
+std::tuple<Tensor, Tensor> rms_norm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd,
+                                        const std::optional<Tensor>& dres) {
     TORCH_CHECK(dy.is_cuda() && dy.is_contiguous() && x.is_contiguous() && dy.sizes() == x.sizes(),
                 "rms_norm_bwd: bad input");
     TORCH_CHECK(dy.scalar_type() == x.scalar_type(), "rms_norm_bwd: dtype mismatch");
+    const void* dres_ptr = nullptr;
+    if (dres.has_value()) {
+        TORCH_CHECK(dres->is_cuda() && dres->is_contiguous() && dres->sizes() == x.sizes() &&
+                        dres->scalar_type() == x.scalar_type() && aligned16(*dres),
+                    "rms_norm_bwd: the residual gradient must match x");
+        dres_ptr = dres->data_ptr();
+    }
     const int rows = static_cast<int>(x.size(0)), D = static_cast<int>(x.size(1));
     c10::cuda::CUDAGuard guard(x.device());
     Tensor dx = at::empty_like(x);
@@ -273,8 +304,10 @@ std::tuple<Tensor, Tensor> rms_norm_bwd(const Tensor& dy, const Tensor& x, const
         Tensor part = at::empty({grid, D}, x.options().dtype(at::kFloat));
         fs2::rms_norm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(),
                           part.data_ptr<float>(), dw.data_ptr<float>(), rows, D, is_bf16(x), num_sms(x),
-                          stream_of(x));
+                          stream_of(x), dres_ptr);
         g_launches += 2;
+    } else if (dres.has_value()) {
+        dx.copy_(*dres);
     }
     return {dx, dw};
 }
@@ -1277,7 +1310,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("gemm_scatter", &gemm_scatter);
     m.def("reduce_slices", &reduce_slices);
     m.def("rms_norm_fwd", &rms_norm_fwd);
-    m.def("rms_norm_bwd", &rms_norm_bwd);
+    m.def("rms_norm_bwd", &rms_norm_bwd, py::arg("dy"), py::arg("x"), py::arg("w"), py::arg("rstd"),
+          py::arg("dres") = std::nullopt);
+    m.def("add_rms_norm_fwd", &add_rms_norm_fwd);
     m.def("layer_norm_fwd", &layer_norm_fwd, py::arg("x"), py::arg("w"), py::arg("b"), py::arg("eps"),
           py::arg("gelu") = false);
     m.def("layer_norm_bwd", &layer_norm_bwd, py::arg("dy"), py::arg("x"), py::arg("w"), py::arg("mean"),

@@ -38,9 +38,12 @@ inline int norm_block(int D) {
 }
 
 // ------------------------------------------------------------------- RMSNorm
+// With `res` the kernel is residual add + norm in one pass: h = x + res (rounded to the activation dtype, as a
+// separate add would) is written to `sum_out` and normalised, so the sum is never re-read from memory.
 template <typename T, int VPT>
 __global__ void rms_norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
-                                    float* __restrict__ rstd, int rows, int D, float eps) {
+                                    float* __restrict__ rstd, int rows, int D, float eps,
+                                    const T* __restrict__ res, T* __restrict__ sum_out) {
     __shared__ float scratch[32];
     const int nvec = D / 8;
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -53,6 +56,17 @@ __global__ void rms_norm_fwd_kernel(const T* __restrict__ x, const T* __restrict
             const int v = threadIdx.x + j * blockDim.x;
             if (v < nvec) {
                 load8(xr, static_cast<size_t>(v) * 8, cache[j]);
+                if (res != nullptr) {
+                    float rv[8];
+                    load8(res + static_cast<size_t>(row) * D, static_cast<size_t>(v) * 8, rv);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        float h = cache[j][e] + rv[e];
+                        if constexpr (sizeof(T) == 2) h = __bfloat162float(__float2bfloat16_rn(h));
+                        cache[j][e] = h;
+                    }
+                    store8(sum_out + static_cast<size_t>(row) * D, static_cast<size_t>(v) * 8, cache[j]);
+                }
 #pragma unroll
                 for (int e = 0; e < 8; ++e) ss += cache[j][e] * cache[j][e];
             }
@@ -107,10 +121,12 @@ struct Raw8<float> {
 
 // dx = rstd * (g - xhat * mean(g * xhat)), g = dy * w, xhat = x * rstd
 // dw partial per block: sum over its rows of dy * xhat
+// `dres` (may be null): a gradient that reaches x by another path (the residual connection); it is added to dx in
+// the same pass, which is the backward of the fused residual add + norm.
 template <typename T, int VPT>
 __global__ void rms_norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
                                     const float* __restrict__ rstd, T* __restrict__ dx, float* __restrict__ dw_part,
-                                    int rows, int D) {
+                                    int rows, int D, const T* __restrict__ dres) {
     __shared__ float scratch[32];
     const int nvec = D / 8;
     float dwacc[VPT][8];
@@ -170,6 +186,12 @@ __global__ void rms_norm_bwd_kernel(const T* __restrict__ dy, const T* __restric
                 float o[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) o[e] = r * (g[j][e] - xh[j][e] * m);
+                if (dres != nullptr) {
+                    float dr[8];
+                    load8(dres + off, static_cast<size_t>(v) * 8, dr);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) o[e] += dr[e];
+                }
                 store8(dx + off, static_cast<size_t>(v) * 8, o);
             }
         }
@@ -630,33 +652,35 @@ int norm_bwd_grid(int rows, int num_sms) {
 }
 
 void rms_norm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int D, float eps, bool bf16,
-                  int num_sms, cudaStream_t st) {
+                  int num_sms, cudaStream_t st, const void* res, void* sum_out) {
     const int threads = norm_block(D);
     const int grid = rows < num_sms * 16 ? rows : num_sms * 16;
     FS2_VPT_DISPATCH(norm_vpt(D, threads),
         if (bf16)
             rms_norm_fwd_kernel<__nv_bfloat16, VPT><<<grid, threads, 0, st>>>(
                 static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
-                static_cast<__nv_bfloat16*>(y), rstd, rows, D, eps);
+                static_cast<__nv_bfloat16*>(y), rstd, rows, D, eps, static_cast<const __nv_bfloat16*>(res),
+                static_cast<__nv_bfloat16*>(sum_out));
         else
             rms_norm_fwd_kernel<float, VPT><<<grid, threads, 0, st>>>(
                 static_cast<const float*>(x), static_cast<const float*>(w), static_cast<float*>(y), rstd, rows, D,
-                eps))
+                eps, static_cast<const float*>(res), static_cast<float*>(sum_out)))
 }
 
 void rms_norm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw_part,
-                  float* dw, int rows, int D, bool bf16, int num_sms, cudaStream_t st) {
+                  float* dw, int rows, int D, bool bf16, int num_sms, cudaStream_t st, const void* dres) {
     const int threads = norm_block_bwd(D);
     const int grid = norm_bwd_grid(rows, num_sms);
     FS2_VPT_DISPATCH(norm_vpt(D, threads),
         if (bf16)
             rms_norm_bwd_kernel<__nv_bfloat16, VPT><<<grid, threads, 0, st>>>(
                 static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
-                static_cast<const __nv_bfloat16*>(w), rstd, static_cast<__nv_bfloat16*>(dx), dw_part, rows, D);
+                static_cast<const __nv_bfloat16*>(w), rstd, static_cast<__nv_bfloat16*>(dx), dw_part, rows, D,
+                static_cast<const __nv_bfloat16*>(dres));
         else
             rms_norm_bwd_kernel<float, VPT><<<grid, threads, 0, st>>>(
                 static_cast<const float*>(dy), static_cast<const float*>(x), static_cast<const float*>(w), rstd,
-                static_cast<float*>(dx), dw_part, rows, D))
+                static_cast<float*>(dx), dw_part, rows, D, static_cast<const float*>(dres)))
     reduce_partials_kernel<<<(D + 255) / 256, 256, 0, st>>>(dw_part, dw, grid, D);
 }
 
@@ -859,11 +883,12 @@ extern "C" int fs2_rms_norm_bwd_no_alloc(const void* dy, const void* x, const vo
         if (is_bf16)
             rms_norm_bwd_kernel<__nv_bfloat16, VPT><<<grid, threads, 0, stream>>>(
                 static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
-                static_cast<const __nv_bfloat16*>(w), rstd, static_cast<__nv_bfloat16*>(dx), scratch, rows, D);
+                static_cast<const __nv_bfloat16*>(w), rstd, static_cast<__nv_bfloat16*>(dx), scratch, rows, D,
+                nullptr);
         else
             rms_norm_bwd_kernel<float, VPT><<<grid, threads, 0, stream>>>(
                 static_cast<const float*>(dy), static_cast<const float*>(x), static_cast<const float*>(w), rstd,
-                static_cast<float*>(dx), scratch, rows, D))
+                static_cast<float*>(dx), scratch, rows, D, nullptr))
     reduce_partials_kernel<<<(D + 255) / 256, 256, 0, stream>>>(scratch, dw, grid, D);
     if (cudaGetLastError() != cudaSuccess) {
         g_no_alloc_error = "kernel launch failed";

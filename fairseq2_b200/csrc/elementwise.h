@@ -9,10 +9,12 @@ namespace fs2 {
 
 int norm_bwd_grid(int rows, int num_sms);
 
+// `res`/`sum_out` (both or neither): y = rms_norm(x + res) and sum_out = x + res in one pass.
 void rms_norm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int D, float eps, bool bf16,
-                  int num_sms, cudaStream_t st);
+                  int num_sms, cudaStream_t st, const void* res = nullptr, void* sum_out = nullptr);
+// `dres` (may be null) is added to dx: the gradient that reaches the normalised tensor through a residual path.
 void rms_norm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw_part,
-                  float* dw, int rows, int D, bool bf16, int num_sms, cudaStream_t st);
+                  float* dw, int rows, int D, bool bf16, int num_sms, cudaStream_t st, const void* dres = nullptr);
 // `gelu` (bf16 only): y = gelu(layer_norm(x)) in one pass; the backward then takes the bias as `b_for_gelu` to
 // rebuild the pre-activation and treats `dy` as the gradient of the GELU output.
 void layer_norm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int rows, int D,

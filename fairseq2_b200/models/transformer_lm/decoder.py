@@ -47,9 +47,27 @@ class StandardTransformerLMDecoder(TransformerLMDecoder):
         self.layers = ModuleList(layers)
         self.layer_norm = layer_norm
 
+    def _can_defer_residuals(self) -> bool:
+        return (not self._layer_hooks and len(self.layers) > 0
+                and all(getattr(layer, "supports_deferred_residual", False) for layer in self.layers))
+
     def forward(self, seqs, seqs_layout, *, state_bag=None):  # type: ignore[override]
         cache = AttentionBiasCache()
         n = len(self.layers)
+        if self._can_defer_residuals():
+            # every residual add is folded into the norm kernel that reads the sum (the next layer's first norm,
+            # or the final norm below)
+            from fairseq2_b200.nn.normalization import RMSNorm
+            from fairseq2_b200.ops.norm import add_rms_norm
+
+            delta = None
+            for layer in self.layers:
+                seqs, delta = layer(seqs, seqs_layout, cache, state_bag=state_bag, delta=delta, defer_residual=True)
+            ln = self.layer_norm
+            if type(ln) is RMSNorm and ln.weight is not None and ln.bias is None and len(ln.normalized_shape) == 1:
+                return add_rms_norm(delta, seqs, ln.weight, ln.eps)[1]
+            seqs = seqs + delta
+            return ln(seqs) if ln is not None else seqs
         for i, layer in enumerate(self.layers):
             seqs = layer(seqs, seqs_layout, cache, state_bag=state_bag)
             stop = False

@@ -36,7 +36,41 @@ class StandardTransformerLMDecoderLayer(TransformerLMDecoderLayer):
         self.self_attn_dropout = Dropout(dropout_p) if dropout_p > 0.0 else None
         self.ffn_dropout = Dropout(dropout_p) if dropout_p > 0.0 else None
 
-    def forward(self, seqs, seqs_layout, bias_cache, *, state_bag=None):  # type: ignore[override]
+    @property
+    def supports_deferred_residual(self) -> bool:
+        """True if both residual adds of this layer can be folded into the RMSNorm that follows them (pre-norm,
+        plain additive residuals, no dropout, RMSNorm with a weight and no bias)."""
+        from fairseq2_b200.nn.normalization import RMSNorm
+
+        def plain_rms(n: LayerNorm) -> bool:
+            return (type(n) is RMSNorm and n.weight is not None and n.bias is None and len(n.normalized_shape) == 1)
+
+        return (self.norm_order == TransformerNormOrder.PRE and type(self.self_attn_residual) is AdditiveResidualConnect
+                and type(self.ffn_residual) is AdditiveResidualConnect and self.self_attn_dropout is None
+                and self.ffn_dropout is None and plain_rms(self.self_attn_layer_norm)
+                and plain_rms(self.ffn_layer_norm))
+
+    def _forward_deferred(self, seqs, seqs_layout, bias_cache, state_bag, delta):  # type: ignore[no-untyped-def]
+        """The hidden state enters as ``seqs + delta`` (``delta`` = the previous layer's feed-forward output, not
+        yet added) and leaves the same way, so that every residual add runs inside the norm kernel that consumes
+        the sum: one pass over the activations instead of an add, a write and a re-read."""
+        from fairseq2_b200.ops.norm import add_rms_norm
+
+        n1, n2 = self.self_attn_layer_norm, self.ffn_layer_norm
+        if delta is not None:
+            residual, y = add_rms_norm(delta, seqs, n1.weight, n1.eps)
+        else:
+            residual, y = seqs, n1(seqs)
+        attn = self.self_attn(y, seqs_layout, y, seqs_layout, y, bias_cache, state_bag=state_bag)
+        hidden, y2 = add_rms_norm(attn, residual, n2.weight, n2.eps)
+        return hidden, self.ffn(y2)
+
+    def forward(self, seqs, seqs_layout, bias_cache, *, state_bag=None, delta=None,  # type: ignore[override]
+                defer_residual=False):
+        if defer_residual:
+            return self._forward_deferred(seqs, seqs_layout, bias_cache, state_bag, delta)
+        if delta is not None:
+            seqs = seqs + delta
         pre = self.norm_order != TransformerNormOrder.POST
         residual = seqs
         if pre:

@@ -48,6 +48,52 @@ class _RMSNormFn(torch.autograd.Function):
         return dx.view(dy.shape), dw.to(weight.dtype), None
 
 
+class _AddRMSNormFn(torch.autograd.Function):
+    """``h = x + res; y = rms_norm(h) * w`` in one kernel; the backward adds the gradient of ``h`` that arrives
+    through the residual path to the norm's input gradient in the same pass."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, res: Tensor, weight: Tensor, eps: float):  # type: ignore[override]
+        ext = require_ext()
+        x2 = x.reshape(-1, x.shape[-1])
+        r2 = res.reshape(-1, res.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        if not r2.is_contiguous():
+            r2 = r2.contiguous()
+        h, y, rstd = ext.add_rms_norm_fwd(x2, r2, weight, eps)
+        ctx.save_for_backward(h, weight, rstd)
+        return h.view(x.shape), y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dh: Tensor | None, dy: Tensor | None):  # type: ignore[override]
+        ext = require_ext()
+        h, weight, rstd = ctx.saved_tensors
+        if dy is None:
+            return dh, dh, None, None
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dh2 = None
+        if dh is not None:
+            dh2 = dh.reshape(-1, dh.shape[-1])
+            if not dh2.is_contiguous():
+                dh2 = dh2.contiguous()
+        dx, dw = ext.rms_norm_bwd(dy2, h, weight, rstd, dh2)
+        dx = dx.view(dy.shape)
+        return dx, dx, dw.to(weight.dtype), None
+
+
+def add_rms_norm(x: Tensor, res: Tensor, weight: Tensor | None, eps: float) -> tuple[Tensor, Tensor]:
+    """Returns ``(x + res, rms_norm(x + res) * weight)``: the residual add and the normalisation that follows it in
+    a pre-norm transformer layer, as one pass over the activations on CUDA."""
+    if (use_kernels(x) and weight is not None and x.dtype in (torch.bfloat16, torch.float32)
+            and weight.dtype == x.dtype and res.dtype == x.dtype and x.shape == res.shape and x.shape[-1] % 8 == 0):
+        return _AddRMSNormFn.apply(x, res, weight, eps)
+    h = x + res
+    return h, rms_norm(h, (h.shape[-1],), weight, eps)
+
+
 def rms_norm(x: Tensor, normalized_shape: Sequence[int], weight: Tensor | None, eps: float,
              bias: Tensor | None = None) -> Tensor:
     if (use_kernels(x) and weight is not None and bias is None and len(normalized_shape) == 1

@@ -129,6 +129,19 @@ class AdamWConfig:
 
 
 @dataclass(kw_only=True)
+class AdafactorConfig:
+    """Hyper-parameters of :class:`fairseq2_b200.optim.Adafactor` (reference ``recipe/config.py:851-897``)."""
+
+    lr: float = 1e-2
+    beta2_decay: float = -0.8
+    eps: tuple[float | None, float] = (None, 0.001)
+    d: float = 1.0
+    weight_decay: float = 0.0
+    foreach: bool | None = None
+    maximize: bool = False
+
+
+@dataclass(kw_only=True)
 class OptimizerSection:
     name: str = "adamw"
     config: dict[str, Any] = field(default_factory=dict)
