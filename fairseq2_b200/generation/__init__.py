@@ -4,4 +4,6 @@ from fairseq2_b200.generation.generator import (BeamSearchAlgorithm, BeamSearchS
 from fairseq2_b200.generation.sampler import Sampler, TopKSampler, TopPSampler
 from fairseq2_b200.generation.step_processor import (BannedSequenceProcessor, NGramRepeatBlockProcessor,
                                                      StepProcessor)
-from fairseq2_b200.generation.text import TextCompleter
+from fairseq2_b200.generation.seq2seq import (BeamSearchSeq2SeqGenerator, SamplingSeq2SeqGenerator,
+                                              Seq2SeqGenerator)
+from fairseq2_b200.generation.text import SequenceToTextConverter, TextCompleter, TextTranslator

@@ -3,7 +3,8 @@ from fairseq2_b200.nn.embedding import (Embedding, ShardedEmbedding, StandardEmb
                                         init_scaled_embedding)
 from fairseq2_b200.nn.incremental_state import IncrementalState, IncrementalStateBag
 from fairseq2_b200.nn.normalization import LayerNorm, RMSNorm, StandardLayerNorm
-from fairseq2_b200.nn.position_encoder import (LearnedPositionEncoder, PositionEncoder, ReferenceRotaryEncoder,
+from fairseq2_b200.nn.position_encoder import (DualRotaryEncoder, LearnedPositionEncoder, PositionEncoder,
+                                               ReferenceRotaryEncoder,
                                                RotaryEncoder, SinusoidalPositionEncoder)
 from fairseq2_b200.nn.projection import (ColumnShardedLinear, IdentityProjection, Linear, Projection,
                                          RowShardedLinear, TiedProjection)

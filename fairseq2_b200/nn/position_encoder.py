@@ -165,6 +165,34 @@ class RotaryEncoder(PositionEncoder):
         return f"encoding_dim={self.encoding_dim}, max_seq_len={self.max_seq_len}, theta={self.theta}"
 
 
+class DualRotaryEncoder(RotaryEncoder):
+    """Rotary encoder with two frequency bands: the first half of the feature dimension rotates with ``theta``,
+    the second half with ``dual_theta`` (short- and long-range positions side by side; used by Gemma 3n's LAuReL
+    blocks, cf. fairseq2 ``nn/position_encoder.py:928-1009``).
+
+    Both bands live in ONE ``(cos, sin)`` table -- the inverse frequencies of the two half-width encoders laid end
+    to end -- so a forward pass is a single rotation over the whole feature dimension instead of two rotations
+    and a concatenation.
+    """
+
+    def __init__(self, encoding_dim: int, max_seq_len: int, *, theta: float = 10_000.0,
+                 dual_theta: float = 100_000.0, device: Device | None = None) -> None:
+        if encoding_dim % 4:
+            raise ValueError(f"`encoding_dim` must be divisible by 4 for dual RoPE, but is {encoding_dim} instead.")
+        self.dual_theta = dual_theta
+
+        def init(enc: RotaryEncoder) -> Tensor:
+            half = enc.encoding_dim // 2
+            idx = torch.arange(0, half, 2, dtype=torch.float32) / half
+            return torch.cat([1.0 / (enc.theta ** idx), 1.0 / (dual_theta ** idx)])
+
+        super().__init__(encoding_dim, max_seq_len, theta=theta, freqs_init_fn=init, device=device)
+
+    def extra_repr(self) -> str:
+        return (f"encoding_dim={self.encoding_dim}, max_seq_len={self.max_seq_len}, theta={self.theta}, "
+                f"dual_theta={self.dual_theta}")
+
+
 class ReferenceRotaryEncoder(PositionEncoder):
     """Half-rotation RoPE (``rotate_half`` as in HF/GPT-NeoX): pairs are
     ``(x[i], x[i + E/2])``."""

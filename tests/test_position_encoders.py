@@ -90,3 +90,29 @@ def test_rotary_incremental_matches_full() -> None:
         outs.append(enc(step, BatchLayout.of(step), state_bag=bag))
         bag.increment_step_nr()
     assert torch.allclose(torch.cat(outs, dim=1), full, atol=1e-6)
+
+
+def test_dual_rotary_encoder_equals_two_half_width_encoders() -> None:
+    """One table with two frequency bands must equal RoPE(theta) on the first half of the features and
+    RoPE(dual_theta) on the second half, concatenated; incremental decoding offsets the positions."""
+    import pytest
+    import torch
+
+    from fairseq2_b200.nn import BatchLayout, DualRotaryEncoder, IncrementalStateBag, RotaryEncoder
+
+    torch.manual_seed(0)
+    E, S = 16, 9
+    enc = DualRotaryEncoder(E, 32, theta=10_000.0, dual_theta=100_000.0)
+    std, long = RotaryEncoder(E // 2, 32, theta=10_000.0), RotaryEncoder(E // 2, 32, theta=100_000.0)
+    x = torch.randn(2, S, 3, E)
+    layout = BatchLayout.of(x[:, :, 0, 0])
+    want = torch.cat([std(x[..., : E // 2], layout), long(x[..., E // 2:], layout)], dim=-1)
+    assert torch.allclose(enc(x, layout), want, atol=1e-6)
+    bag = IncrementalStateBag(32)
+    bag.increment_step_nr(5)
+    step = x[:, :1]
+    one = BatchLayout.of(step[:, :, 0, 0])
+    want = torch.cat([std(step[..., : E // 2], one, state_bag=bag), long(step[..., E // 2:], one, state_bag=bag)], -1)
+    assert torch.allclose(enc(step, one, state_bag=bag), want, atol=1e-6)
+    with pytest.raises(ValueError):
+        DualRotaryEncoder(6, 32)
