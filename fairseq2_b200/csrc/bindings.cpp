@@ -966,6 +966,30 @@ std::tuple<Tensor, Tensor, Tensor> attn_bwd(const Tensor& dout, const Tensor& q,
 }
 
 // ------------------------------------------------------------------ optimizer
+// Device-memory copy of the status word that the optimizer kernels read ("skip the update if a collective gave
+// up"); one word per device, zero until `refresh_status_guard` finds the status word set.
+int* g_guard_dev[64] = {};
+
+int* status_guard_ptr(int device) {
+    TORCH_CHECK(device >= 0 && device < 64, "status guard: bad device index");
+    if (g_guard_dev[device] == nullptr) {
+        c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+        TORCH_CHECK(cudaMalloc(reinterpret_cast<void**>(&g_guard_dev[device]), sizeof(int)) == cudaSuccess,
+                    "status guard: allocation failed");
+        TORCH_CHECK(cudaMemset(g_guard_dev[device], 0, sizeof(int)) == cudaSuccess, "status guard: memset failed");
+    }
+    return g_guard_dev[device];
+}
+
+// Once per optimizer step, on the current stream of `device`: the optimizer launches that follow see the status word
+// as it is at this point of the stream (after the collectives of the step).
+void refresh_status_guard(int64_t device) {
+    c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+    fs2::copy_status(status_dev_ptr(), status_guard_ptr(static_cast<int>(device)),
+                     at::cuda::getCurrentCUDAStream(static_cast<c10::DeviceIndex>(device)).stream());
+    g_launches += 1;
+}
+
 void multi_tensor_adamw(const std::vector<Tensor>& masters, const std::vector<Tensor>& grads,
                         const std::vector<Tensor>& ms, const std::vector<Tensor>& vs, const std::vector<Tensor>& lows,
                         double lr, double beta1, double beta2, double eps, double wd, int64_t step,
@@ -1000,7 +1024,7 @@ void multi_tensor_adamw(const std::vector<Tensor>& masters, const std::vector<Te
         fs2::adamw(p.data_ptr<float>(), g.data_ptr(), is_bf16(g), ms[i].data_ptr<float>(), vs[i].data_ptr<float>(), low,
                    static_cast<size_t>(p.numel()), static_cast<float>(lr), static_cast<float>(beta1),
                    static_cast<float>(beta2), static_cast<float>(eps), static_cast<float>(wd), static_cast<int>(step),
-                   gs, status_dev_ptr(), num_sms(p), stream_of(p));
+                   gs, status_guard_ptr(p.get_device()), num_sms(p), stream_of(p));
         g_launches += 1;
     }
 }
@@ -1325,6 +1349,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("attn_bwd", &attn_bwd);
     m.def("attn_bwd_out", &attn_bwd_out);
     m.def("multi_tensor_adamw", &multi_tensor_adamw);
+    m.def("refresh_status_guard", &refresh_status_guard);
     m.def("multi_tensor_l2_norm_sq", &multi_tensor_l2_norm_sq);
     m.def("multi_tensor_scale", &multi_tensor_scale);
     m.def("comm_barrier", &comm_barrier);

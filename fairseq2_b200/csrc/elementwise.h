@@ -38,6 +38,8 @@ void ce_fwd_bwd(void* logits, const long long* targets, const float* mask, float
 void adamw(float* p, const void* g, bool g_bf16, float* m, float* v, void* low, size_t n, float lr, float beta1,
            float beta2, float eps, float wd, int step, const float* grad_scale, const int* guard, int num_sms,
            cudaStream_t st);
+// Copies the host-mapped status word into a device-memory word (the `guard` of `adamw`).
+void copy_status(const int* host_mapped_status, int* device_guard, cudaStream_t st);
 void l2_norm_sq(const void* x, bool bf16, size_t n, float* out, int num_sms, cudaStream_t st);
 void scale_inplace(void* x, bool bf16, size_t n, const float* scale, int num_sms, cudaStream_t st);
 

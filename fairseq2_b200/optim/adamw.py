@@ -24,6 +24,22 @@ from torch.optim import Optimizer
 from fairseq2_b200.ops.optim import adamw_reference, multi_tensor_adamw
 
 
+def _refresh_status_guard(param_groups: list[dict[str, Any]]) -> None:
+    """The fused update kernels skip their work when a collective of this step gave up on a peer; they read a
+    device-memory copy of the status word, which is brought up to date here, once per step."""
+    for group in param_groups:
+        for p in group["params"]:
+            unit = getattr(p, "_fs2_unit", None)
+            dev = unit.low_shard.device if unit is not None else p.device
+            if dev.type == "cuda":
+                from fairseq2_b200.ops._ext import require_ext, use_kernels
+
+                if use_kernels(unit.low_shard if unit is not None else p):
+                    require_ext().refresh_status_guard(dev.index if dev.index is not None else
+                                                       torch.cuda.current_device())
+            return
+
+
 class AdamW(Optimizer):
     def __init__(self, params: Iterable[Any], lr: float = 1e-3, betas: tuple[float, float] = (0.9, 0.999),
                  eps: float = 1e-8, weight_decay: float = 0.0, *, impl: str = "auto") -> None:
@@ -64,6 +80,7 @@ class AdamW(Optimizer):
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
+        _refresh_status_guard(self.param_groups)
         for group in self.param_groups:
             lr, (b1, b2), eps, wd = group["lr"], group["betas"], group["eps"], group["weight_decay"]
             lr = float(lr)
