@@ -59,13 +59,26 @@ log = LogWriter("fairseq2_b200")
 
 
 def configure_logging(*, debug: bool = False, rank: int | None = None, log_file: Path | None = None,
-                      force: bool = True) -> None:
-    """Console output on rank 0 only, optional per-rank file ``logs/rank_N.log``."""
+                      force: bool = True, no_rich: bool | None = None) -> None:
+    """Console output on rank 0 only, optional per-rank file ``logs/rank_N.log``. The console handler is rich's
+    (colours, wrapped tracebacks) when the stream is a terminal, unless ``no_rich`` (or ``FAIRSEQ2_NO_RICH``)."""
     if rank is None:
         rank = int(os.environ.get("RANK", "0"))
+    if no_rich is None:
+        no_rich = "FAIRSEQ2_NO_RICH" in os.environ
     handlers: list[Handler] = []
     if rank == 0:
-        handlers.append(StreamHandler(sys.stderr))
+        console: Handler | None = None
+        if not no_rich and sys.stderr.isatty():
+            try:
+                from rich.logging import RichHandler
+
+                from fairseq2_b200.utils.rich import get_error_console
+
+                console = RichHandler(console=get_error_console(), show_path=False, keywords=[])
+            except ImportError:
+                console = None
+        handlers.append(console if console is not None else StreamHandler(sys.stderr))
     if log_file is not None:
         log_file.parent.mkdir(parents=True, exist_ok=True)
         handlers.append(FileHandler(log_file))

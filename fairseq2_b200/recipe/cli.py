@@ -3,8 +3,8 @@
     python -m recipes.lm.sft OUTPUT_DIR --config-file cfg.yaml --config trainer.max_grad_norm=1.0 ...
 
 Flags: ``--config-file`` (repeatable), ``--config k=v ...``, ``--dump-config``,
-``--no-sweep-dir``, ``--checkpoint-dir``, ``--no-exit-on-error``, ``--debug``.
-Known failures are mapped to distinct exit codes."""
+``--no-sweep-dir``, ``--checkpoint-dir``, ``--no-rich``, ``--no-exit-on-error``, ``--debug``.
+Failures are mapped to exit codes by the registry in ``recipe/exit_codes.py``."""
 from __future__ import annotations
 
 import argparse
@@ -15,7 +15,7 @@ from typing import Any, Sequence
 
 from fairseq2_b200.logging import configure_logging, log
 from fairseq2_b200.recipe.base import Recipe
-from fairseq2_b200.recipe.error import RecipeError
+from fairseq2_b200.recipe.exit_codes import exit_code_for
 from fairseq2_b200.recipe.run import load_recipe_config, run_recipe
 from fairseq2_b200.utils.config import parse_config_overrides
 from fairseq2_b200.utils.structured import unstructure
@@ -32,6 +32,8 @@ def _parse(argv: Sequence[str] | None) -> argparse.Namespace:
     ap.add_argument("--dump-config", action="store_true", help="print the merged configuration and exit")
     ap.add_argument("--no-sweep-dir", action="store_true", help="do not create a sweep sub-directory")
     ap.add_argument("--checkpoint-dir", type=Path, default=None)
+    ap.add_argument("--no-rich", action="store_true",
+                    help="plain text console output: no rich formatting, no progress bars")
     ap.add_argument("--no-exit-on-error", action="store_true", help="re-raise errors instead of exiting")
     ap.add_argument("--debug", action="store_true")
     return ap.parse_args(argv)
@@ -39,7 +41,12 @@ def _parse(argv: Sequence[str] | None) -> argparse.Namespace:
 
 def main(recipe: Recipe, argv: Sequence[str] | None = None, preset: Any | None = None) -> int:
     args = _parse(argv)
-    configure_logging(debug=args.debug)
+    if args.no_rich:
+        import os
+
+        os.environ["FAIRSEQ2_NO_RICH"] = "1"
+        os.environ["FAIRSEQ2_NO_PROGRESS"] = "1"
+    configure_logging(debug=args.debug, no_rich=args.no_rich)
     try:
         overrides = parse_config_overrides(args.overrides)
         if args.debug:
@@ -54,20 +61,9 @@ def main(recipe: Recipe, argv: Sequence[str] | None = None, preset: Any | None =
         run_recipe(recipe, config, args.output_dir, checkpoint_dir=args.checkpoint_dir,
                    no_sweep_dir=args.no_sweep_dir or None)
         return 0
-    except RecipeError as ex:
-        if args.no_exit_on_error:
+    except BaseException as ex:  # noqa: BLE001 - every failure is mapped to an exit code by the registry
+        if args.no_exit_on_error and not isinstance(ex, SystemExit):
             raise
-        log.error("{}", ex)
-        return ex.exit_code
-    except ValueError as ex:
-        if args.no_exit_on_error:
+        if isinstance(ex, SystemExit):
             raise
-        log.error("{}", ex)
-        return 2
-    except KeyboardInterrupt:
-        return 130
-    except Exception:  # noqa: BLE001
-        if args.no_exit_on_error:
-            raise
-        log.error("The recipe failed with an unexpected error:\n{}", traceback.format_exc())
-        return 1
+        return exit_code_for(ex)
