@@ -40,7 +40,21 @@ def run_reference_arm(args: Namespace) -> None:
     sys.path.insert(0, str(HERE / "ref_shims"))
     sys.path.insert(0, str(ref_dir))
     try:
-        _run(args)
+        config = getattr(args, "config", "llama3_8b_fsdp")
+        if config == "wav2vec2_large_ddp":
+            from baseline.reference_wav2vec2 import run as run_w2v
+
+            run_w2v(args)
+        elif config == "llama3_70b_tp4_fsdp2":
+            from baseline.reference_llama70b import run as run_70b
+
+            run_70b(args)
+        elif config == "moe_ep8":
+            from baseline.reference_moe import run as run_moe
+
+            run_moe(args)
+        else:
+            _run(args)
     except Exception as ex:  # noqa: BLE001 - the arm must always print a line and exit 0
         import traceback
 

@@ -2,6 +2,10 @@
 
     python bench.py --gpus N --steps K --warmup W            # this framework
     python bench.py --impl reference --gpus N ...            # unmodified fairseq2 from baseline/_ref
+    python bench.py --config {llama3_70b_tp4_fsdp2,moe_ep8,wav2vec2_large_ddp} ...   # the other configurations
+
+Without ``--config`` the headline configuration below runs; the others are described in their modules under
+``benchmarks/`` (ours) and ``baseline/`` (reference arms).
 
 Model/config: LLaMA-3-8B architecture (32 layers, dim 4096, 32/8 heads, FFN
 14336, vocab 128256), random init, packed sequences of 8192 tokens per GPU made
@@ -31,44 +35,8 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 
-def _clock_sampler(stop: threading.Event, out: list[dict], gpu_index: int) -> None:
-    q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
-    try:
-        proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "200",
-                                 "-i", str(gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-    except OSError:
-        return
-    assert proc.stdout is not None
-    try:
-        while not stop.is_set():
-            line = proc.stdout.readline()
-            if not line:
-                break
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) >= 7:
-                try:
-                    out.append({"sm": float(parts[0]), "max": float(parts[1]), "power": float(parts[2]),
-                                "hw_slowdown": parts[3], "hw_thermal": parts[4], "sw_thermal": parts[5],
-                                "sw_power_cap": parts[6]})
-                except ValueError:
-                    pass
-    finally:
-        proc.terminate()
-
-
-def _summarize_clocks(samples: list[dict]) -> dict:
-    if not samples:
-        return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-    sm = sorted(s["sm"] for s in samples)
-    reasons = []
-    for key, name in (("hw_slowdown", "hw_slowdown"), ("hw_thermal", "hw_thermal_slowdown"),
-                      ("sw_thermal", "sw_thermal_slowdown"), ("sw_power_cap", "sw_power_cap")):
-        if any(s[key].lower().startswith("active") for s in samples):
-            reasons.append(name)
-    return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": samples[0]["max"], "reasons": reasons,
-            "samples": len(samples), "power_w_max": max(s["power"] for s in samples)}
+from benchmarks.harness import clock_sampler as _clock_sampler  # noqa: E402
+from benchmarks.harness import summarize_clocks as _summarize_clocks  # noqa: E402
 
 
 def _trace_steps(args: argparse.Namespace, step_fn, batches, rank: int, record: bool) -> None:  # type: ignore[no-untyped-def]
@@ -145,7 +113,7 @@ def run_ours(args: argparse.Namespace) -> None:
     with torch.device("meta"):
         model = create_llama_model(cfg, gangs)
     fsdp = FSDP(model, gangs, param_dtype=torch.bfloat16, fp32_reduce=True,
-                reshard_after_forward=bool(args.reshard_after_forward))
+                reshard_after_forward=bool(args.reshard_after_forward), wait_limit_s=30.0)
     facade = DataParallelFacade(fsdp)
     optimizer = AdamW(fsdp.parameters(), lr=1e-5, betas=(0.9, 0.95), weight_decay=0.1)
 
@@ -236,8 +204,14 @@ def run_ours(args: argparse.Namespace) -> None:
     e2e_value = tokens_per_step * args.steps / (e2e_ms * 1e-3)
 
     if rank == 0:
-        n_params = sum(u.shard_size for u in fsdp.all_units) * world
-        flops_per_token = 6 * 8.03e9 if args.model == "llama3_8b" and args.layers is None else None
+        # model FLOPs of a step: 6 x (parameters that are GEMM operands: everything but the embedding table)
+        # per token, plus causal attention (forward 2 GEMMs over half the score matrix, backward twice that)
+        gemm_params = sum(s.d0 * s.row for u in fsdp.all_units for s in u.specs
+                          if len(s.shape) == 2 and "embed" not in s.fqn)
+        attn_flops = sum(6.0 * n * n * cfg.num_attn_heads * (cfg.model_dim // cfg.num_attn_heads)
+                         for ex in examples[args.warmup: args.warmup + args.steps] for n in ex.seq_lens)
+        attn_flops = attn_flops * cfg.num_layers / max(args.steps, 1)
+        flops_per_step = 6.0 * gemm_params * seq_len + attn_flops
         out = {
             "metric": "llama3_8b_fsdp_sft_tokens_per_second", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
@@ -256,8 +230,7 @@ def run_ours(args: argparse.Namespace) -> None:
             "final_loss": last_loss,
             "peak_mem_gb": torch.cuda.max_memory_allocated(device) / 2**30,
         }
-        if flops_per_token is not None:
-            out["model_tflops_per_gpu"] = flops_per_token * value / world / 1e12
+        out["model_tflops_per_gpu"] = flops_per_step / (dev_ms / args.steps * 1e-3) / 1e12
         print(json.dumps(out), flush=True)
     if world > 1:
         root.close()
@@ -269,12 +242,31 @@ def run_reference(args: argparse.Namespace) -> None:
     run_reference_arm(args)
 
 
+CONFIGS = ("llama3_8b_fsdp", "llama3_70b_tp4_fsdp2", "moe_ep8", "wav2vec2_large_ddp")
+
+
+def run_config(args: argparse.Namespace) -> None:
+    """The configurations other than the headline one live in ``benchmarks/``."""
+    if args.config == "wav2vec2_large_ddp":
+        from benchmarks.wav2vec2_ddp import run_ours as fn
+    elif args.config == "llama3_70b_tp4_fsdp2":
+        from benchmarks.llama70b_tp_fsdp import run_ours as fn
+    elif args.config == "moe_ep8":
+        from benchmarks.moe_ep import run_ours as fn
+    else:
+        raise SystemExit(f"unknown --config {args.config}")
+    fn(args)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="llama3_8b_fsdp", choices=list(CONFIGS),
+                    help="benchmark configuration; the default is the headline LLaMA-3-8B FSDP SFT step")
+    ap.add_argument("--tp", type=int, default=None, help="tensor-parallel size (llama3_70b_tp4_fsdp2: default 4)")
     ap.add_argument("--model", default="llama3_8b")
     ap.add_argument("--seq-len", type=int, default=8192)
     ap.add_argument("--reshard-after-forward", type=int, default=1, choices=[0, 1],
@@ -288,6 +280,8 @@ def main() -> None:
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+    elif args.config != "llama3_8b_fsdp":
+        run_config(args)
     else:
         run_ours(args)
 

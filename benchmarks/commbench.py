@@ -3,7 +3,7 @@
 Run one process per GPU::
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
-        -m fairseq2_b200.parallel.commbench [--cases all] [--iters 10]
+        -m benchmarks.commbench [--cases all] [--iters 10]
 
 Every case is timed with CUDA events on the launching stream after warm-up, a barrier on both sides, and reported as
 the MAX over ranks. Rank 0 prints one JSON line per case with the achieved rate and its fraction of the roofline

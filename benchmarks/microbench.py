@@ -1,8 +1,8 @@
 """Per-kernel micro-benchmarks on one GPU.
 
-    python -m fairseq2_b200.ops.microbench gemm --m 8192 --n 6144 --k 4096
-    python -m fairseq2_b200.ops.microbench attention --tokens 8192 --seq-len 8192
-    python -m fairseq2_b200.ops.microbench all
+    python -m benchmarks.microbench gemm --m 8192 --n 6144 --k 4096
+    python -m benchmarks.microbench attention --tokens 8192 --seq-len 8192
+    python -m benchmarks.microbench all
 
 Every case warms up, flushes L2 (a 256 MiB write) between timed iterations,
 times with CUDA events on the launching stream and prints one JSON line with

@@ -16,12 +16,24 @@ from fairseq2_b200.typing import DataType, Device
 
 class Wav2Vec2PositionalConv1d(Conv1d):
     def reset_parameters(self) -> None:
-        if self.weight.device.type == "meta":
-            return
+        from torch.nn.utils import parametrize
+
         model_dim, kernel_size = self.in_channels, self.kernel_size[0]
         std = (4.0 / (kernel_size * model_dim)) ** 0.5
-        torch.nn.init.normal_(self.weight, mean=0.0, std=std)
-        if self.bias is not None:
+        if parametrize.is_parametrized(self, "weight"):
+            # weight-normalised: ``self.weight`` is computed from (magnitude, direction); a fresh weight has to be
+            # assigned so that the parametrisation's right inverse refills both (an in-place init of the computed
+            # tensor would be lost -- this is the path taken when the module was built on the meta device)
+            direction = self.parametrizations.weight.original1
+            if direction.device.type == "meta":
+                return
+            with torch.no_grad():
+                self.weight = torch.empty_like(direction).normal_(mean=0.0, std=std)
+        else:
+            if self.weight.device.type == "meta":
+                return
+            torch.nn.init.normal_(self.weight, mean=0.0, std=std)
+        if self.bias is not None and self.bias.device.type != "meta":
             torch.nn.init.zeros_(self.bias)
 
 

@@ -92,6 +92,10 @@ class DataParallelFacade:
     def check_comm_status(self) -> None:
         """Raises ``KernelWaitTimeout`` if a peer-memory collective of this process gave up waiting for a peer.
         Costs one read of a host-mapped word; does not synchronise with the device."""
+        check = getattr(self.module, "check_comm_status", None)
+        if check is not None:
+            check()
+            return
         arena = getattr(self.module, "arena", None)
         if arena is not None:
             arena.ext.check_status()

@@ -53,6 +53,7 @@ from fairseq2_b200.ops.optim import multi_tensor_l2_norm_sq
 from fairseq2_b200.typing import DataType, Device
 
 _ALIGN = 64  # elements; keeps every region 128-byte aligned (TMA needs 16 B)
+REPLICA_SLOT_BASE = 64  # first epoch-flag slot of the replica all-reduces (two slots per unit)
 
 
 def _round_up(n: int, m: int) -> int:
@@ -128,6 +129,7 @@ class FlatParamUnit:
         #: device scalar that the reduce-scatter kernels add this unit's squared gradient norm to (set by FSDP)
         self.norm_slot: Tensor | None = None
         self.norm_fused = False     # ``norm_slot`` holds the norm of the current ``grad_shard``
+        self.replicated = False     # gradients are averaged over a replica gang after the (trivial) reduction
 
         # shard parameters handed to the optimizer / state dict
         self.shard_params: list[Parameter] = []
@@ -176,6 +178,46 @@ class FlatParamUnit:
         self.seg_offs = [s.shard_off for s in self.specs]
         self.seg_numels = [s.shard_numel for s in self.specs]
         self.rs_epoch = 0
+
+    def attach_replica_arena(self, arena: Any, index: int, counter_off: int, blocks: int, multimem: bool) -> None:
+        """Replicated (unsharded) unit: the flat gradient buffer moves into a symmetric arena over the replica
+        gang, where the in-place all-reduce kernel averages it over the replicas right after the unit's backward
+        pass -- the data-parallel gradient all-reduce fused with its 1/size scaling, overlapped with the rest of
+        the backward pass."""
+        self.replica_arena = arena
+        self.replica_index = index
+        self.replica_counter_off = counter_off
+        self.replica_blocks = blocks
+        self.replica_multimem = multimem
+        per = 8                                             # bf16 elements per 16-byte vector
+        self.replica_numel = (self.shard_size + per - 1) // per * per
+        self.grad_off, gf = arena.alloc_tensor(self.replica_numel, self.param_dtype)
+        gf.zero_()
+        self.grad_full = gf[: self.shard_size]
+        self._bind_grad_sinks(self.grad_full, filled=False)
+        self.replica_epoch = 0
+
+    def _allreduce_replicas(self, comm_stream: "torch.cuda.Stream | None", average: bool) -> None:
+        a = self.replica_arena
+        cur = torch.cuda.current_stream(self.device)
+        if comm_stream is not None:
+            comm_stream.wait_stream(cur)
+            ctx: Any = torch.cuda.stream(comm_stream)
+        else:
+            ctx = _null()
+        self.replica_epoch += 1
+        scale = 1.0 / a.world if average else 1.0
+        slot = REPLICA_SLOT_BASE + 2 * self.replica_index
+        with ctx:
+            if self.replica_multimem:
+                a.ext.comm_allreduce_multimem(a.peer_ptrs, a.rank, a.multicast_ptr, self.grad_off, self.replica_numel,
+                                              False, scale, slot, slot + 1, self.replica_epoch,
+                                              self.replica_counter_off, a.device_index, self.replica_blocks,
+                                              a.wait_limit_s)
+            else:
+                a.ext.comm_allreduce_inplace(a.peer_ptrs, a.rank, self.grad_off, self.replica_numel, False, scale,
+                                             slot, slot + 1, self.replica_epoch, self.replica_counter_off,
+                                             a.device_index, self.replica_blocks, a.wait_limit_s)
 
     # ------------------------------------------------------------- views
     def _region(self, buf: Tensor, s: _ParamSpec) -> Tensor:
@@ -245,9 +287,9 @@ class FlatParamUnit:
         and points every parameter's ``grad_sink`` into it."""
         self.needs_reduce = True
         if self.grad_full is None and self.arena is None:
-            self.grad_full = torch.empty(self.world * self.shard_size, device=self.device, dtype=self.param_dtype)
-            if self.world > 1:
-                self.grad_full.zero_()  # padding rows take part in the reduce-scatter
+            # zeroed: padding rows take part in the reduce-scatter, and the alignment gaps between parameters are
+            # read by the flat gradient-norm pass (with one rank the buffer is allocated once and kept)
+            self.grad_full = torch.zeros(self.world * self.shard_size, device=self.device, dtype=self.param_dtype)
             self._bind_grad_sinks(self.grad_full, filled=False)
 
     def collect_autograd_grads(self) -> None:
@@ -271,8 +313,11 @@ class FlatParamUnit:
             return
         self.needs_reduce = False
         self.collect_autograd_grads()
+        shared = self.world > 1 or getattr(self, "replica_arena", None) is not None or self.replicated
         for i, (s, cp) in enumerate(zip(self.specs, self.compute_params)):
-            if getattr(cp, "grad_sink_filled", False):
+            if getattr(cp, "grad_sink_filled", False) or (shared and s.requires_grad):
+                # with more than one rank a parameter counts as used when ANY rank may have used it: the reduced
+                # gradient then is the mean over the ranks and every rank must apply the same update
                 self.took_part[i] = True
             elif getattr(cp, "grad_sink", None) is not None:
                 cp.grad_sink.zero_()  # type: ignore[attr-defined]  # parameter took no part in this pass
@@ -282,6 +327,11 @@ class FlatParamUnit:
         if W == 1:
             self.grad_shard = self.grad_full
             self.grads_ready = True
+            if getattr(self, "replica_arena", None) is not None:
+                self._allreduce_replicas(comm_stream, average)
+                self.replicas_reduced = True
+                for cp in self.compute_params:
+                    cp.grad_sink_filled = True  # type: ignore[attr-defined]  # later micro-batches accumulate
             return
         gf = self.grad_full
         cur = torch.cuda.current_stream(self.device) if self.device.type == "cuda" else None
@@ -342,6 +392,7 @@ class FlatParamUnit:
 
     def zero_grad(self) -> None:
         self.grads_ready = False
+        self.replicas_reduced = False
         self.norm_fused = False
         self.took_part = [False] * len(self.specs)
         if self.world == 1:
@@ -528,6 +579,37 @@ class FSDP(Module):
                     self.arena = None
             elif comm == "symm":
                 raise RuntimeError("Symmetric-memory communication was requested but is not available.")
+        for u in self.all_units:
+            u.replicated = self.replica_gang is not None
+        self.replica_arena: Any = None
+        if (W == 1 and self.replica_gang is not None and comm != "nccl" and param_dtype == torch.bfloat16
+                and dev.type == "cuda"):
+            from fairseq2_b200.parallel.symm import SymmetricArena, symmetric_memory_available
+
+            if symmetric_memory_available(self.replica_gang):
+                if wait_limit_s is None:
+                    wait_limit_s = float(os.environ.get("FAIRSEQ2_B200_WAIT_LIMIT_S", "120"))
+                need = sum((u.shard_size + 64) * 2 + 64 for u in self.all_units) + (1 << 16)
+                try:
+                    ra = SymmetricArena(self.replica_gang, need, wait_limit_s=wait_limit_s)  # type: ignore[arg-type]
+                    coff, counters = ra.alloc(8 * len(self.all_units), align=16)
+                    counters.zero_()
+                    mode = os.environ.get("FAIRSEQ2_B200_DDP_ALLREDUCE", "auto")
+                    use_mm = mode == "multimem" or (mode == "auto" and ra.multicast_ptr != 0)
+                    for i, u in enumerate(self.all_units):
+                        nbytes = u.shard_size * 2
+                        blocks = max(1, min(64, nbytes // (512 * 16 * 4)))
+                        u.attach_replica_arena(ra, i, coff + 8 * i, blocks, use_mm)
+                    self.replica_arena = ra
+                    if self.comm_stream is None and overlap:
+                        self.comm_stream = torch.cuda.Stream(dev)
+                    torch.cuda.synchronize(dev)
+                    self.replica_gang.barrier()
+                except Exception as ex:  # noqa: BLE001
+                    if comm == "symm":
+                        raise
+                    log.warning("Symmetric memory is not usable ({}); replicas are averaged with NCCL.", ex)
+                    self.replica_arena = None
         self._install_hooks()
         n = sum(u.shard_size for u in self.all_units)
         log.info("FSDP: {} unit(s), {:,} local shard elements, world size {}.", len(self.all_units), n, W)
@@ -604,7 +686,13 @@ class FSDP(Module):
         self._in_backward = False
         self._flush_pending_reduce()
         if self._require_sync:
+            multi = self.gang.size > 1 or self.replica_gang is not None
             for u in self.all_units:
+                if not u.needs_reduce and multi and not u.grads_ready and any(s.requires_grad for s in u.specs):
+                    # The unit did not run on this rank in this step (LayerDrop, an unused expert, a skipped
+                    # branch), but it may have run on a peer: every rank takes part in every unit's reduction,
+                    # contributing zeros, or the peers would wait for it.
+                    u.prepare_grads()
                 if u.needs_reduce:
                     u.reduce_grads(self.comm_stream)
         if self.root_unit is not None and self.root_unit.world > 1 and self._require_sync:
@@ -613,7 +701,7 @@ class FSDP(Module):
             torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
         if self.replica_gang is not None and self._require_sync:
             for u in self.all_units:
-                if u.grad_shard is not None:
+                if u.grad_shard is not None and not getattr(u, "replicas_reduced", False):
                     self.replica_gang.all_reduce(u.grad_shard, ReduceOperation.MEAN)
 
     def check_comm_status(self) -> None:
@@ -621,8 +709,9 @@ class FSDP(Module):
         bounded wait (a peer that never arrived). Reads a host-mapped word: no synchronisation with the device.
         The optimizer kernels check the same word on the device and leave the weights untouched once it is set,
         so a step that ran on incomplete gradients never reaches the parameters."""
-        if self.arena is not None:
-            self.arena.ext.check_status()
+        arena = self.arena if self.arena is not None else self.replica_arena
+        if arena is not None:
+            arena.ext.check_status()
 
     def after_optimizer_step(self) -> None:
         """The optimizer wrote new bf16 shards: gathered copies are stale. With the
@@ -763,12 +852,17 @@ def _materialize(module: Module, device: Device, memo: dict[int, Parameter]) -> 
     ``device`` and initialised module by module (children first), so that a
     model far larger than one GPU can be sharded unit by unit: only one unit
     is ever resident in full precision."""
+    reparametrized: set[int] = set()     # parametrisation containers (e.g. weight norm) that received fresh storage
     for sub in reversed(list(module.modules())):
         metas = [n for n, p in sub._parameters.items() if p is not None and p.is_meta]
         metab = [n for n, b in sub._buffers.items() if b is not None and b.is_meta]
-        if not metas and not metab:
+        # a module whose parametrised tensors were just allocated must re-initialise them through its own
+        # ``reset_parameters`` even if none of its direct parameters is new
+        owns_fresh = any(id(c) in reparametrized for c in getattr(sub, "parametrizations", {}).values()) \
+            if hasattr(sub, "parametrizations") else False
+        if not metas and not metab and not owns_fresh:
             continue
-        fresh = False
+        fresh = owns_fresh
         for n in metas:
             p = sub._parameters[n]
             if id(p) in memo:       # tied parameter that another module already materialised
@@ -783,6 +877,8 @@ def _materialize(module: Module, device: Device, memo: dict[int, Parameter]) -> 
         for n in metab:
             sub._buffers[n] = torch.empty_like(sub._buffers[n], device=device)
         fn = getattr(sub, "reset_parameters", None)
+        if type(sub).__name__ == "ParametrizationList":
+            reparametrized.add(id(sub))
         if callable(fn):
             fn()
         else:

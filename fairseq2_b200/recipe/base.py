@@ -251,6 +251,18 @@ class RecipeContext:
             return FSDP(model, gangs, wrap_policy=policy, param_dtype=param_dtype, fp32_reduce=ts.fsdp.fp32_reduce,
                         reshard_after_forward=ts.fsdp.reshard_after_forward, comm=ts.fsdp.comm,
                         cpu_offload=ts.fsdp.cpu_offload, wait_limit_s=ts.fsdp.wait_limit)
+        mp = ts.mixed_precision
+        if (self.device.type == "cuda" and mp.mode in ("static", "auto") and mp.dtype == torch.bfloat16
+                and family.supports_fsdp and ts.ddp_flat_units):
+            # Replicated data parallelism on flat units: bf16 compute parameters, fp32 master weights and
+            # optimizer state, gradients averaged over the replicas by the in-place all-reduce kernel as each
+            # unit's backward finishes, one fused optimizer launch per unit. (The reference's DDP keeps fp32
+            # parameters under autocast and all-reduces fp32 buckets with NCCL, ``nn/ddp.py:30-152``.)
+            policy = family.fsdp_wrap_policy or None
+            if policy is None:
+                from fairseq2_b200.parallel.fsdp import layerwise_wrap_policy as policy  # type: ignore[no-redef]
+            return FSDP(model, gangs, wrap_policy=policy, param_dtype=torch.bfloat16, comm=ts.fsdp.comm,
+                        wait_limit_s=ts.fsdp.wait_limit)
         model = model.to(self.device)
         if gangs.dp.size > 1:
             return DDP(model, gangs)

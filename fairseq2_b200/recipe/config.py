@@ -108,6 +108,9 @@ class ActivationCheckpointingSection:
 @dataclass(kw_only=True)
 class TrainerSection:
     data_parallelism: Literal["ddp", "fsdp"] = "ddp"
+    #: DDP on CUDA with bf16 mixed precision runs on flat parameter units (bf16 compute copies, fp32 master
+    #: weights, fused all-reduce + optimizer kernels); ``False`` selects the bucketed fp32 DDP
+    ddp_flat_units: bool = True
     fsdp: FSDPSection = field(default_factory=FSDPSection)
     mixed_precision: MixedPrecisionSection = field(default_factory=MixedPrecisionSection)
     grad_accumulation: GradAccumulationSection = field(default_factory=GradAccumulationSection)

@@ -174,9 +174,9 @@ def test_add_rms_norm_fused_residual(dtype: torch.dtype, rows: int, D: int) -> N
     torch.autograd.backward([h, y], [gh, gy])
     xr, rr, wr = (t.detach().double().requires_grad_(True) for t in (x, r, w))
     hr = xr + rr
-    hq = hr.to(dtype).double() + (hr - hr.detach())          # the kernel rounds the sum to the activation dtype
+    hq = hr + (hr.to(dtype).double() - hr).detach()          # the kernel rounds the sum to the activation dtype
     yr = hq * torch.rsqrt(hq.pow(2).mean(dim=-1, keepdim=True) + 1e-5)
-    yr = (yr.to(dtype).double() + (yr - yr.detach())) * wr
+    yr = (yr + (yr.to(dtype).double() - yr).detach()) * wr
     torch.autograd.backward([hr, yr], [gh.double(), gy.double()])
     tol = 1e-2 if dtype == torch.bfloat16 else 1e-5
     assert _rel_err(h, hr) < tol and _rel_err(y, yr) < tol
