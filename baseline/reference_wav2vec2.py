@@ -117,10 +117,12 @@ def run(args: Namespace) -> None:
     barrier()
     t0 = time.perf_counter()
     h2d, last = 0, 0.0
+    losses: list[float] = []
     for i in range(args.steps):
         ex = examples[args.warmup + args.steps + i]
         h2d = ex[0].numel() * 4 + (len(ex[1]) + 1) * 4
         last = float(step(stage(ex), i).item())
+        losses.append(last)
     barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3
     t = torch.tensor([dev_ms, e2e_ms, 0.0], device=device, dtype=torch.float64)
@@ -140,7 +142,7 @@ def run(args: Namespace) -> None:
                           "parallelism": f"ddp{world} (torch DDP, fp32 parameters under autocast bf16)"},
                "e2e": {"value": units * args.steps / (e2e_ms * 1e-3), "unit": "audio samples/s",
                        "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
-               "final_loss": last}
+               "final_loss": last, "losses": losses}
         if cuda:
             out["peak_mem_gb"] = torch.cuda.max_memory_allocated(device) / 2**30
         print(json.dumps(out), flush=True)

@@ -93,10 +93,12 @@ def timed_run(*, steps: int, warmup: int, rank: int, world: int, local_rank: int
     barrier()
     t0 = time.perf_counter()
     h2d, last = 0, 0.0
+    losses: list[float] = []
     for i in range(steps):
         ex = examples[warmup + steps + i]
         h2d = h2d_bytes(ex)
         last = float(step(stage(ex), warmup + steps + i).item())
+        losses.append(last)
     barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3
     stop.set()
@@ -104,7 +106,7 @@ def timed_run(*, steps: int, warmup: int, rank: int, world: int, local_rank: int
     if world > 1:
         all_reduce_max(times)
     out: dict[str, Any] = {"dev_ms": float(times[0]), "e2e_ms": float(times[1]), "h2d_bytes": h2d, "d2h_bytes": 4,
-                           "final_loss": last, "clocks": summarize_clocks(samples)}
+                           "final_loss": last, "losses": losses, "clocks": summarize_clocks(samples)}
     if launches is not None:
         out["gpu_launches"] = int(launches)
     if cuda:
@@ -122,7 +124,7 @@ def result_line(*, metric: str, unit: str, impl: str, units_per_step: float, wor
         "e2e": {"value": units_per_step * steps / (run["e2e_ms"] * 1e-3), "unit": unit,
                 "ms_per_step": run["e2e_ms"] / steps, "h2d_bytes_per_step": run["h2d_bytes"],
                 "d2h_bytes_per_step": run["d2h_bytes"]},
-        "clocks": run["clocks"], "final_loss": run["final_loss"],
+        "clocks": run["clocks"], "final_loss": run["final_loss"], "losses": run.get("losses"),
     }
     if "gpu_launches" in run:
         out["gpu_launches"] = run["gpu_launches"]

@@ -43,12 +43,18 @@ class LLaMAFactory:
     def __init__(self, config: LLaMAConfig, gangs: Gangs | None = None) -> None:
         self._config = config
         self._gangs = gangs if gangs is not None else get_current_gangs()
+        from fairseq2_b200.parallel.tp import sequence_parallel_enabled
+
+        # training-time layout of tensor parallelism: the residual stream is sharded over the tokens
+        self._sequence_parallel = self._gangs.tp.size > 1 and sequence_parallel_enabled()
 
     def create_model(self) -> TransformerLM:
         c = self._config
         embed = self.create_embedding()
-        return TransformerLM(c.model_dim, self.create_decoder_frontend(embed), self.create_decoder(),
-                             self.create_final_projection(embed), c.pad_idx, c.max_seq_len)
+        model = TransformerLM(c.model_dim, self.create_decoder_frontend(embed), self.create_decoder(),
+                              self.create_final_projection(embed), c.pad_idx, c.max_seq_len)
+        model.tp_sequence_parallel = self._sequence_parallel
+        return model
 
     def create_embedding(self) -> Embedding:
         c = self._config
@@ -61,8 +67,12 @@ class LLaMAFactory:
         if tp.size == 1:
             return StandardEmbedding(c.vocab_size, c.model_dim, c.pad_idx, init_fn=init_embed)
         if c.shard_embed_dim:
+            if self._sequence_parallel:
+                raise NotSupportedError("Sequence-parallel tensor parallelism needs a vocabulary-sharded embedding "
+                                        "(`shard_embed_dim=False`).")
             return ShardedEmbedding(tp, c.vocab_size, c.model_dim, c.pad_idx, init_fn=init_embed)
-        return VocabShardedEmbedding(tp, c.vocab_size, c.model_dim, c.pad_idx, init_fn=init_embed)
+        return VocabShardedEmbedding(tp, c.vocab_size, c.model_dim, c.pad_idx,
+                                     sequence_parallel=self._sequence_parallel, init_fn=init_embed)
 
     def create_decoder_frontend(self, embed: Embedding) -> TransformerFrontend:
         c = self._config
@@ -133,7 +143,8 @@ class LLaMAFactory:
 
         if tp.size == 1:
             return Linear(c.model_dim, c.vocab_size, bias=False, init_fn=init)
-        return ColumnShardedLinear(tp, c.model_dim, c.vocab_size, bias=False, gather_output=True, init_fn=init)
+        return ColumnShardedLinear(tp, c.model_dim, c.vocab_size, bias=False, gather_output=True,
+                                   sequence_parallel=self._sequence_parallel, init_fn=init)
 
     def create_layer_norm(self) -> LayerNorm:
         return RMSNorm(self._config.model_dim, bias=False)

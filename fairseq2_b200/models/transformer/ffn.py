@@ -33,14 +33,20 @@ class FeedForwardNetwork(Module, ABC):
 
 def _col(gangs: Gangs | None, i: int, o: int, bias: bool, init_fn, device, dtype) -> Projection:  # type: ignore[no-untyped-def]
     if gangs is not None and gangs.tp.size > 1:
-        return ColumnShardedLinear(gangs.tp, i, o, bias, gather_output=False, init_fn=init_fn, device=device,
+        from fairseq2_b200.parallel.tp import sequence_parallel_enabled
+
+        return ColumnShardedLinear(gangs.tp, i, o, bias, gather_output=False,
+                                   sequence_parallel=sequence_parallel_enabled(), init_fn=init_fn, device=device,
                                    dtype=dtype)
     return Linear(i, o, bias, init_fn=init_fn, device=device, dtype=dtype)
 
 
 def _row(gangs: Gangs | None, i: int, o: int, bias: bool, init_fn, device, dtype) -> Projection:  # type: ignore[no-untyped-def]
     if gangs is not None and gangs.tp.size > 1:
-        return RowShardedLinear(gangs.tp, i, o, bias, scatter_input=False, init_fn=init_fn, device=device,
+        from fairseq2_b200.parallel.tp import sequence_parallel_enabled
+
+        return RowShardedLinear(gangs.tp, i, o, bias, scatter_input=False,
+                                sequence_parallel=sequence_parallel_enabled(), init_fn=init_fn, device=device,
                                 dtype=dtype)
     return Linear(i, o, bias, init_fn=init_fn, device=device, dtype=dtype)
 

@@ -239,10 +239,17 @@ def merged_linear(x: Tensor, projs: list[Projection]) -> Tensor | None:
     ``x``) as one GEMM when their weights are adjacent in memory; returns
     ``None`` when that is not possible."""
     ws = []
+    sp_gang = None
     for p in projs:
         if not isinstance(p, (Linear, ColumnShardedLinear)) or p.bias is not None:
             return None
-        if isinstance(p, ColumnShardedLinear) and (p.gang.size > 1 or p.gather_output and p.gang.size > 1):
+        if isinstance(p, ColumnShardedLinear) and p.gang.size > 1:
+            # tensor parallel: only the sequence-parallel form merges (one all-gather of the token shard inside
+            # ONE GEMM over the adjacent local weight shards instead of one collective per projection)
+            if not p.sequence_parallel or p.gather_output or (sp_gang is not None and p.gang is not sp_gang):
+                return None
+            sp_gang = p.gang
+        elif sp_gang is not None:
             return None
         ws.append(p.weight)
     if not x.is_cuda or x.dtype != torch.bfloat16:
@@ -250,6 +257,15 @@ def merged_linear(x: Tensor, projs: list[Projection]) -> Tensor | None:
     merged = _adjacent([w.detach() for w in ws])
     if merged is None:
         return None
+    if sp_gang is not None:
+        from fairseq2_b200.nn.projection import _fused_ops
+
+        if any(isinstance(p, Linear) for p in projs):
+            return None
+        ops = _fused_ops(sp_gang, x, x.shape[0] if x.ndim == 2 else 0, x.shape[-1], merged)
+        if ops is None:
+            return None
+        return ops.column(x, merged, tuple(ws))
     return _MergedLinearFn.apply(x, merged, *ws)
 
 
@@ -275,10 +291,15 @@ class StandardMultiheadAttention(MultiheadAttention):
         if tp is not None and (num_heads % tp.size or nkv % tp.size):
             raise ValueError("`num_heads` and `num_key_value_heads` must be multiples of the tensor parallel size.")
 
+        from fairseq2_b200.parallel.tp import sequence_parallel_enabled
+
+        sp = tp is not None and sequence_parallel_enabled()
+        self.sequence_parallel = sp
+
         def col(i: int, o: int) -> Projection:
             if tp is not None:
-                return ColumnShardedLinear(tp, i, o, bias, gather_output=False, init_fn=qkv_proj_init_fn,
-                                           device=device, dtype=dtype)
+                return ColumnShardedLinear(tp, i, o, bias, gather_output=False, sequence_parallel=sp,
+                                           init_fn=qkv_proj_init_fn, device=device, dtype=dtype)
             return Linear(i, o, bias, init_fn=qkv_proj_init_fn, device=device, dtype=dtype)
 
         self.q_proj = q_proj if q_proj is not None else col(model_dim, num_heads * hd)
@@ -298,7 +319,8 @@ class StandardMultiheadAttention(MultiheadAttention):
             self.output_proj = output_proj
         elif tp is not None:
             self.output_proj = RowShardedLinear(tp, num_heads * hd, model_dim, ob, scatter_input=False,
-                                                init_fn=output_proj_init_fn, device=device, dtype=dtype)
+                                                sequence_parallel=sp, init_fn=output_proj_init_fn, device=device,
+                                                dtype=dtype)
         else:
             self.output_proj = Linear(num_heads * hd, model_dim, ob, init_fn=output_proj_init_fn, device=device,
                                       dtype=dtype)

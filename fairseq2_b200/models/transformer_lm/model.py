@@ -16,7 +16,7 @@ from fairseq2_b200.models.transformer_lm.decoder import TransformerLMDecoder
 from fairseq2_b200.nn.batch_layout import BatchLayout
 from fairseq2_b200.nn.functional import cross_entropy
 from fairseq2_b200.nn.incremental_state import IncrementalStateBag
-from fairseq2_b200.nn.projection import Linear, Projection, TiedProjection
+from fairseq2_b200.nn.projection import ColumnShardedLinear, Linear, Projection, TiedProjection
 from fairseq2_b200.ops.cross_entropy import fused_linear_cross_entropy
 
 
@@ -54,6 +54,19 @@ class TransformerLM(CausalLM):
         if label_smoothing == 0.0 and isinstance(fp, (Linear, TiedProjection)) and fp.bias is None:
             return fused_linear_cross_entropy(decoder_output, fp.weight, targets, target_mask=target_mask,
                                               pad_idx=self.pad_idx, reduction=reduction)
+        if (label_smoothing == 0.0 and isinstance(fp, ColumnShardedLinear) and fp.bias is None and fp.gang.size > 1
+                and fp.gather_output):
+            # vocabulary-parallel output projection: every rank scores its slice of the vocabulary and only three
+            # numbers per token cross the tensor-parallel gang; the [T, V] logits are never gathered
+            from fairseq2_b200.ops.cross_entropy import vocab_parallel_linear_cross_entropy
+            from fairseq2_b200.ops.tensor_parallel import all_gather_seq, reduce_on_backward
+
+            h = decoder_output
+            if fp.sequence_parallel:
+                h = all_gather_seq(h, fp.gang, dim=-2)     # backward: reduce-scatter of the per-rank partial dh
+            return vocab_parallel_linear_cross_entropy(h, fp.weight, targets, fp.gang, target_mask=target_mask,
+                                                       pad_idx=self.pad_idx, reduction=reduction,
+                                                       reduce_input_grad=not fp.sequence_parallel)
         return self.compute_loss(fp(decoder_output), targets, label_smoothing=label_smoothing,
                                  target_mask=target_mask, reduction=reduction)
 

@@ -59,13 +59,16 @@ class VocabShardedEmbedding(Embedding):
     to zero and the partial results are summed over the gang."""
 
     def __init__(self, gang: Gang, num_embeddings: int, embed_dim: int, pad_idx: int | None = None, *,
-                 init_fn: Callable[[StandardEmbedding], None] | None = None, device: Device | None = None,
-                 dtype: DataType | None = None) -> None:
+                 sequence_parallel: bool = False, init_fn: Callable[[StandardEmbedding], None] | None = None,
+                 device: Device | None = None, dtype: DataType | None = None) -> None:
+        """``sequence_parallel``: the output is this rank's shard of the tokens (``[T / W, D]``), i.e. the partial
+        look-ups are reduce-scattered over the tokens instead of all-reduced."""
         super().__init__(num_embeddings, embed_dim, pad_idx)
         if num_embeddings % gang.size:
             raise ValueError(
                 f"`num_embeddings` must be a multiple of `gang.size` ({gang.size}), but is {num_embeddings} instead.")
         self.gang = gang
+        self.sequence_parallel = sequence_parallel
         self.sharded_num_embeddings = num_embeddings // gang.size
         self.weight = Parameter(torch.empty((self.sharded_num_embeddings, embed_dim), device=device, dtype=dtype))
         self.init_fn = init_fn
@@ -93,7 +96,12 @@ class VocabShardedEmbedding(Embedding):
     def forward(self, x: Tensor) -> Tensor:
         from fairseq2_b200.ops.embedding import embed_vocab_parallel
 
-        y = embed_vocab_parallel(x, self.weight, self.gang.rank * self.sharded_num_embeddings)
+        lo = self.gang.rank * self.sharded_num_embeddings
+        if self.sequence_parallel and self.gang.size > 1:
+            from fairseq2_b200.ops.embedding import embed_vocab_parallel_scatter
+
+            return embed_vocab_parallel_scatter(x, self.weight, lo, self.gang)
+        y = embed_vocab_parallel(x, self.weight, lo)
         return reduce(y, self.gang)
 
     def to_embedding(self, device: Device | None = None) -> StandardEmbedding:

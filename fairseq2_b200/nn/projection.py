@@ -27,6 +27,21 @@ from fairseq2_b200.ops.tensor_parallel import (all_gather_seq, gather, reduce, r
 from fairseq2_b200.typing import DataType, Device
 
 
+def _fused_ops(gang: Gang, x: Tensor, rows: int, model_dim: int, weight: Tensor):  # type: ignore[no-untyped-def]
+    """The fused all-gather / reduce-scatter GEMM operators for token shards of ``rows x model_dim``, if the call
+    is one the sm_100a kernels cover (bf16 on CUDA, 2-D activations, tile-aligned shard) and the gang has a
+    symmetric arena; ``None`` otherwise (the caller then uses the gang's collectives)."""
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and x.ndim == 2 and weight.dtype == torch.bfloat16):
+        return None
+    from fairseq2_b200.ops._ext import use_kernels
+
+    if not use_kernels(x):
+        return None
+    from fairseq2_b200.parallel.tp import get_tp_context
+
+    return get_tp_context(gang).linears(x, rows, model_dim)
+
+
 class Projection(Module, ABC):
     def __init__(self, input_dim: int, output_dim: int) -> None:
         super().__init__()
@@ -129,7 +144,11 @@ class ColumnShardedLinear(Projection):
                               0, self.weight, self.bias)
 
     def forward(self, x: Tensor) -> Tensor:
-        if self.sequence_parallel:
+        if self.sequence_parallel and self.gang.size > 1:
+            # x is this rank's token shard [T / W, D]: the all-gather of the tokens runs inside the GEMM
+            ops = _fused_ops(self.gang, x, x.shape[0] if x.ndim == 2 else 0, self.input_dim, self.weight)
+            if ops is not None and self.bias is None and not self.gather_output:
+                return ops.column(x, self.weight)
             x = all_gather_seq(x, self.gang, dim=-2)
         else:
             x = reduce_on_backward(x, self.gang)
@@ -205,11 +224,16 @@ class RowShardedLinear(Projection):
     def forward(self, x: Tensor) -> Tensor:
         if self.scatter_input:
             x = scatter(x, self.gang, dim=-1)
-        y = _linear(x, self.weight, None)
-        if self.sequence_parallel:
-            y = reduce_scatter_seq(y, self.gang, dim=-2)
+        if self.sequence_parallel and self.gang.size > 1:
+            # the GEMM epilogue sends every output tile to the rank that owns its tokens: y is [T / W, D]
+            rows = x.shape[0] // self.gang.size if x.ndim == 2 and x.shape[0] % self.gang.size == 0 else 0
+            ops = _fused_ops(self.gang, x, rows, self.output_dim, self.weight)
+            if ops is not None:
+                y = ops.row(x if x.is_contiguous() else x.contiguous(), self.weight)
+            else:
+                y = reduce_scatter_seq(_linear(x, self.weight, None), self.gang, dim=-2)
         else:
-            y = reduce(y, self.gang)
+            y = reduce(_linear(x, self.weight, None), self.gang)
         if self.bias is not None:
             y = y + self.bias
         return y

@@ -131,7 +131,7 @@ class _VocabParallelLinearCE(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, h: Tensor, weight: Tensor, targets: Tensor, mask: Tensor | None, pad_idx: int, chunk: int,
-                gang: Any) -> Tensor:  # type: ignore[override]
+                gang: Any, reduce_dh: bool = True) -> Tensor:  # type: ignore[override]
         from fairseq2_b200.gang import ReduceOperation
 
         T, D = h.shape
@@ -168,7 +168,7 @@ class _VocabParallelLinearCE(torch.autograd.Function):
                 if need_dw:
                     dw += g.float().t() @ hc.float()
         ctx.save_for_backward(dh, dw)
-        ctx.gang, ctx.wdtype = gang, weight.dtype
+        ctx.gang, ctx.wdtype, ctx.reduce_dh = gang, weight.dtype, reduce_dh
         return loss
 
     @staticmethod
@@ -179,22 +179,27 @@ class _VocabParallelLinearCE(torch.autograd.Function):
         gdh = gdw = None
         if dh is not None:
             gdh = dh.mul_(g.to(dh.dtype))
-            ctx.gang.all_reduce(gdh, ReduceOperation.SUM)     # every rank contributed its vocabulary slice
+            if ctx.reduce_dh:
+                ctx.gang.all_reduce(gdh, ReduceOperation.SUM)     # every rank contributed its vocabulary slice
         if dw is not None:
             gdw = (dw * g).to(ctx.wdtype)
-        return gdh, gdw, None, None, None, None, None
+        return gdh, gdw, None, None, None, None, None, None
 
 
 def vocab_parallel_linear_cross_entropy(h: Tensor, weight_shard: Tensor, targets: Tensor, gang: Any, *,
                                         target_mask: Tensor | None = None, pad_idx: int | None = None,
-                                        reduction: str = "sum", chunk_size: int = 4096) -> Tensor:
+                                        reduction: str = "sum", chunk_size: int = 4096,
+                                        reduce_input_grad: bool = True) -> Tensor:
     """``cross_entropy(h @ concat_r(weight_shard_r)ᵀ, targets)`` where rank ``r`` of ``gang`` holds rows
-    ``[r·V/W, (r+1)·V/W)`` of the output projection. Returns the same fp32 scalar on every rank."""
+    ``[r·V/W, (r+1)·V/W)`` of the output projection. Returns the same fp32 scalar on every rank.
+    ``reduce_input_grad=False`` leaves the gradient of ``h`` as this rank's partial (its vocabulary slice's
+    contribution) for a caller whose own backward sums over the gang, e.g. the reduce-scatter that is the backward
+    of a sequence-parallel all-gather."""
     h2 = h.reshape(-1, h.shape[-1]).contiguous()
     t = targets.reshape(-1).contiguous()
     m = target_mask.reshape(-1).float() if target_mask is not None else None
     loss = _VocabParallelLinearCE.apply(h2, weight_shard, t, m, -100 if pad_idx is None else pad_idx, chunk_size,
-                                        gang)
+                                        gang, reduce_input_grad)
     if reduction == "mean":
         denom = m.sum() if m is not None else ((t != pad_idx).sum() if pad_idx is not None
                                                else torch.tensor(float(t.numel()), device=h.device))

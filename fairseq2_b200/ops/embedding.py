@@ -38,3 +38,16 @@ def embed_vocab_parallel(ids: Tensor, shard: Tensor, lo: int) -> Tensor:
     if use_kernels(ids, shard) and shard.dtype == torch.bfloat16 and shard.shape[1] % 8 == 0 and ids.dtype == torch.int64:
         return _EmbedVocabParallel.apply(ids.contiguous(), shard, lo)
     return embed_vocab_parallel_reference(ids, shard, lo)
+
+
+def embed_vocab_parallel_scatter(ids: Tensor, shard: Tensor, lo: int, gang) -> Tensor:  # type: ignore[no-untyped-def]
+    """Vocabulary-parallel lookup with a sequence-parallel result: rank ``r`` of ``gang`` gets the embeddings of
+    tokens ``[r * T / W, (r + 1) * T / W)`` (dimension -2 of the result). Every token's row lives on exactly one
+    rank, so the sum over ranks that a reduce-scatter performs has a single non-zero term per row."""
+    from fairseq2_b200.ops.tensor_parallel import reduce_scatter_seq
+
+    if ids.shape[-1] % gang.size:
+        raise ValueError(f"With sequence-parallel tensor parallelism the number of tokens ({ids.shape[-1]}) must be "
+                         f"a multiple of the tensor-parallel size ({gang.size}); pad or pack the batch accordingly.")
+    y = embed_vocab_parallel(ids, shard, lo)
+    return reduce_scatter_seq(y, gang, dim=-2)

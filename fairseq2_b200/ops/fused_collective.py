@@ -151,15 +151,33 @@ class FusedAllGatherGemm:
         return out
 
 
+def _wgrad(dy: Tensor, x: Tensor, owners: tuple[Tensor, ...]) -> tuple[Tensor | None, ...]:
+    """``dW = dy^T @ x`` for one weight or for several weights that were run as one merged GEMM. Weights that carry
+    a ``grad_sink`` (views of a flat data-parallel gradient buffer) receive their gradient there -- one GEMM
+    straight into the merged sink when the sinks are adjacent in memory -- and ``None`` is returned for them."""
+    from fairseq2_b200.models.transformer.multihead_attention import _merged_sink
+
+    rows = [w.shape[0] for w in owners]
+    sink = _merged_sink(owners)
+    if sink is not None and sink[0].is_contiguous():
+        gemm(dy, x, a_mn=True, b_mn=True, out=sink[0], accumulate=sink[1])
+        for w in owners:
+            w.grad_sink_filled = True  # type: ignore[attr-defined]
+        return tuple(None for _ in owners)
+    dw = gemm(dy, x, a_mn=True, b_mn=True)
+    return tuple(dw.split(rows, dim=0)) if len(owners) > 1 else (dw,)
+
+
 class _ColumnSP(torch.autograd.Function):
-    """``y [T, F_local] = all_gather(x_shard) @ w^T``; backward reduce-scatters ``dy @ w`` back to the token shard."""
+    """``y [T, F_local] = all_gather(x_shard) @ w^T``; backward reduce-scatters ``dy @ w`` back to the token shard.
+    ``w`` may be the merged view of several adjacent weights (``owners``), e.g. q|k|v or gate|up."""
 
     @staticmethod
-    def forward(ctx, x_shard: Tensor, weight: Tensor, sp: "SequenceParallelLinears") -> Tensor:  # type: ignore[override]
+    def forward(ctx, x_shard: Tensor, weight: Tensor, sp: "SequenceParallelLinears", *owners: Tensor) -> Tensor:  # type: ignore[override]
         sp.ag.shard.copy_(x_shard)
         y = sp.ag(weight)
         ctx.save_for_backward(x_shard, weight)
-        ctx.sp = sp
+        ctx.sp, ctx.owners = sp, owners
         return y
 
     @staticmethod
@@ -167,11 +185,16 @@ class _ColumnSP(torch.autograd.Function):
         x_shard, weight = ctx.saved_tensors
         sp: SequenceParallelLinears = ctx.sp
         dy = dy.contiguous()
-        dx_shard = sp.rs(dy, weight, weight_kn=True)                 # [T / W, D] = reduce_scatter(dy @ w)
+        dx_shard = sp.rs(dy, weight, weight_kn=True) if ctx.needs_input_grad[0] else None   # reduce_scatter(dy @ w)
+        owners = ctx.owners
+        if owners:
+            dws: tuple[Tensor | None, ...] = (None,) * len(owners)
+            if any(ctx.needs_input_grad[3:]):
+                dws = _wgrad(dy, sp.all_gather_tokens(x_shard), owners)      # [F_local, D] = dy^T @ x
+            return (dx_shard, None, None, *dws)
         dw = None
         if ctx.needs_input_grad[1]:
-            x_full = sp.all_gather_tokens(x_shard)
-            dw = gemm(dy, x_full, a_mn=True, b_mn=True)              # [F_local, D] = dy^T @ x
+            dw = _wgrad(dy, sp.all_gather_tokens(x_shard), (weight,))[0]
         return dx_shard, dw, None
 
 
@@ -193,7 +216,7 @@ class _RowSP(torch.autograd.Function):
         dh = sp.ag(weight, other_kn=True)                            # [T, F_local] = all_gather(dy) @ w
         dw = None
         if ctx.needs_input_grad[1]:
-            dw = gemm(sp.ag.gathered, h, a_mn=True, b_mn=True)       # [D, F_local] = dy^T @ h (dy just gathered)
+            dw = _wgrad(sp.ag.gathered, h, (weight,))[0]             # [D, F_local] = dy^T @ h (dy just gathered)
         return dh, dw, None
 
 
@@ -229,8 +252,10 @@ class SequenceParallelLinears:
         a.barrier_next(FusedAllGatherGemm.SLOT)                      # nobody restages while a peer still reads
         return full.view(a.world * self.tokens_per_rank, self.model_dim)
 
-    def column(self, x_shard: Tensor, weight: Tensor) -> Tensor:
-        return _ColumnSP.apply(x_shard, weight, self)
+    def column(self, x_shard: Tensor, weight: Tensor, owners: tuple[Tensor, ...] = ()) -> Tensor:
+        """``owners``: when ``weight`` is a merged view of several adjacent parameters, those parameters (they
+        receive the weight gradients)."""
+        return _ColumnSP.apply(x_shard, weight, self, *owners)
 
     def row(self, h: Tensor, weight: Tensor) -> Tensor:
         return _RowSP.apply(h, weight, self)

@@ -489,6 +489,15 @@ class FSDP(Module):
         self.param_dtype = param_dtype
         reduce_dtype = torch.float32 if (fp32_reduce and W > 1) else param_dtype
         unit_modules = wrap_policy(module) if wrap_policy is not None else []
+        # tensor parallelism: which parameters are slices of a larger tensor (distinct on every tp rank) and which
+        # are replicated over the tp gang (norm weights, biases of row-parallel layers, ...)
+        self.tp_gang: Gang | None = gangs.tp if gangs.tp.size > 1 else None
+        self.tp_sequence_parallel = bool(getattr(module, "tp_sequence_parallel", False))
+        tp_sharded: set[str] = set()
+        if self.tp_gang is not None:
+            from fairseq2_b200.nn.sharded import get_shard_dims
+
+            tp_sharded = set(get_shard_dims(module))
         owned: set[int] = set()
         self.units: list[FlatParamUnit] = []
 
@@ -581,6 +590,9 @@ class FSDP(Module):
                 raise RuntimeError("Symmetric-memory communication was requested but is not available.")
         for u in self.all_units:
             u.replicated = self.replica_gang is not None
+            # (offset, length) in the unit's shard buffers of the parameters that are replicated over the tp gang
+            u.tp_replicated = [(sp.shard_off, sp.rows_local * sp.row) for sp in u.specs
+                               if sp.fqn not in tp_sharded and sp.requires_grad] if self.tp_gang is not None else []
         self.replica_arena: Any = None
         if (W == 1 and self.replica_gang is not None and comm != "nccl" and param_dtype == torch.bfloat16
                 and dev.type == "cuda"):
@@ -703,6 +715,27 @@ class FSDP(Module):
             for u in self.all_units:
                 if u.grad_shard is not None and not getattr(u, "replicas_reduced", False):
                     self.replica_gang.all_reduce(u.grad_shard, ReduceOperation.MEAN)
+        if self.tp_gang is not None and self.tp_sequence_parallel and self._require_sync:
+            self._sum_tp_partial_grads()
+
+    def _sum_tp_partial_grads(self) -> None:
+        """With sequence-parallel activations every tp rank sees its own tokens only, so the gradient of a
+        parameter that is replicated over the tp gang (a norm weight) is a partial sum: add the partials up.
+        All segments travel in one small all-reduce."""
+        assert self.tp_gang is not None
+        views = [u.grad_shard[off: off + n] for u in self.all_units if u.grad_shard is not None and u.grads_ready
+                 for off, n in u.tp_replicated if n > 0]
+        if not views:
+            return
+        flat = torch.cat([v.float() for v in views])
+        self.tp_gang.all_reduce(flat, ReduceOperation.SUM)
+        pos = 0
+        for v in views:
+            v.copy_(flat[pos: pos + v.numel()])
+            pos += v.numel()
+        for u in self.all_units:
+            if u.tp_replicated:
+                u.norm_fused = False          # the norm that the reduce-scatter pass emitted predates this sum
 
     def check_comm_status(self) -> None:
         """Raises :class:`~fairseq2_b200.ops._ext.KernelWaitTimeout` if a kernel of this process gave up on a
@@ -755,8 +788,16 @@ class FSDP(Module):
         if not parts:
             return torch.zeros((), device=self.device)
         total = torch.stack(parts).sum()
+        if self.tp_gang is not None:
+            # parameters replicated over the tp gang are counted once, sharded ones on every tp rank
+            rep = [u.grad_shard[off: off + n].float().pow(2).sum() for u in self.all_units
+                   if u.grad_shard is not None and u.grads_ready for off, n in u.tp_replicated if n > 0]
+            if rep:
+                total = total - torch.stack(rep).sum() * (1.0 - 1.0 / self.tp_gang.size)
         if self.gang.size > 1:
             self.gang.all_reduce(total, ReduceOperation.SUM)
+        if self.tp_gang is not None:
+            self.tp_gang.all_reduce(total, ReduceOperation.SUM)
         norm = total.sqrt()
         if self._grad_scale is not None:
             norm = norm * self._grad_scale
