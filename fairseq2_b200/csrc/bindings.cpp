@@ -1222,7 +1222,14 @@ void comm_reducescatter_adamw(const std::vector<int64_t>& ptrs, int64_t rank, co
                               const std::vector<int64_t>& numels, int64_t full_byte_off, Tensor master, Tensor m,
                               Tensor v, const std::optional<Tensor>& low, double scale, double lr, double beta1,
                               double beta2, double eps, double wd, int64_t step, int64_t slot, int64_t epoch,
-                              int64_t blocks, double wait_limit_s) {
+                              int64_t blocks, double wait_limit_s, const std::optional<Tensor>& grad_scale) {
+    const float* scale_ptr = nullptr;
+    if (grad_scale.has_value()) {
+        TORCH_CHECK(grad_scale->is_cuda() && grad_scale->scalar_type() == at::kFloat && grad_scale->numel() == 1 &&
+                        grad_scale->device() == master.device(),
+                    "comm_reducescatter_adamw: grad_scale must be an fp32 scalar on the device of the shard");
+        scale_ptr = grad_scale->data_ptr<float>();
+    }
     const int64_t shard_numel = offs.back() + numels.back();
     for (const Tensor* t : {&master, &m, &v})
         TORCH_CHECK(t->is_cuda() && t->is_contiguous() && t->scalar_type() == at::kFloat &&
@@ -1241,8 +1248,9 @@ void comm_reducescatter_adamw(const std::vector<int64_t>& ptrs, int64_t rank, co
                                   master.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), lowp,
                                   static_cast<float>(scale), static_cast<float>(lr), static_cast<float>(beta1),
                                   static_cast<float>(beta2), static_cast<float>(eps), static_cast<float>(wd),
-                                  static_cast<int>(step), static_cast<int>(slot), static_cast<uint32_t>(epoch),
-                                  static_cast<int>(blocks), status_dev_ptr(), stream_of(master));
+                                  static_cast<int>(step), scale_ptr, static_cast<int>(slot),
+                                  static_cast<uint32_t>(epoch), static_cast<int>(blocks), status_dev_ptr(),
+                                  stream_of(master));
     g_launches += 1;
 }
 
@@ -1364,7 +1372,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("numels"), py::arg("full_byte_off"), py::arg("staging"), py::arg("out"), py::arg("scale"),
           py::arg("accumulate"), py::arg("slot"), py::arg("epoch"), py::arg("blocks"), py::arg("wait_limit_s"),
           py::arg("norm_out") = std::nullopt);
-    m.def("comm_reducescatter_adamw", &comm_reducescatter_adamw);
+    m.def("comm_reducescatter_adamw", &comm_reducescatter_adamw, py::arg("ptrs"), py::arg("rank"), py::arg("offs"),
+          py::arg("numels"), py::arg("full_byte_off"), py::arg("master"), py::arg("m"), py::arg("v"), py::arg("low"),
+          py::arg("scale"), py::arg("lr"), py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("wd"),
+          py::arg("step"), py::arg("slot"), py::arg("epoch"), py::arg("blocks"), py::arg("wait_limit_s"),
+          py::arg("grad_scale") = std::nullopt);
     m.def("comm_allreduce_f32", &comm_allreduce_f32);
     m.def("comm_allreduce_inplace", &comm_allreduce_inplace);
     m.def("comm_allreduce_multimem", &comm_allreduce_multimem);

@@ -227,11 +227,15 @@ __global__ void __launch_bounds__(512) reducescatter_segments_kernel(
 }
 
 // Reduce-scatter fused with the optimizer step of the local shard (no gradient clipping between the two).
+// `scale_ptr` (may be null): a device scalar multiplied into `scale` -- the loss normalisation of the step, known only
+// on the device (the all-reduced number of targets) when the kernel is queued.
 __global__ void __launch_bounds__(512) reducescatter_adamw_kernel(CommPeers peers, CommSegments segs,
                                                                   long long full_byte_off, AdamWSink sink, float scale,
-                                                                  int slot, uint32_t epoch, int* status) {
+                                                                  const float* __restrict__ scale_ptr, int slot,
+                                                                  uint32_t epoch, int* status) {
     if (!signal_and_wait(peers, slot, epoch, true, status, 24)) return;
     AdamWSink local = sink;
+    if (scale_ptr != nullptr) scale *= *scale_ptr;
     reducescatter_dispatch(peers, segs, full_byte_off, local, scale);
 }
 
@@ -590,7 +594,8 @@ void comm_alltoall(const CommPeers& peers, long long byte_off, void* dst, const 
 
 void comm_reducescatter_adamw(const CommPeers& peers, const CommSegments& segs, long long full_byte_off, float* p,
                               float* m, float* v, void* low, float scale, float lr, float beta1, float beta2, float eps,
-                              float wd, int step, int slot, uint32_t epoch, int blocks, int* status, cudaStream_t st) {
+                              float wd, int step, const float* scale_ptr, int slot, uint32_t epoch, int blocks,
+                              int* status, cudaStream_t st) {
     AdamWSink sink{};
     sink.p = p;
     sink.m = m;
@@ -603,7 +608,8 @@ void comm_reducescatter_adamw(const CommPeers& peers, const CommSegments& segs, 
     sink.wd = wd;
     sink.step_size = lr / (1.f - powf(beta1, static_cast<float>(step)));
     sink.bc2_sqrt = sqrtf(1.f - powf(beta2, static_cast<float>(step)));
-    reducescatter_adamw_kernel<<<blocks, 512, 0, st>>>(peers, segs, full_byte_off, sink, scale, slot, epoch, status);
+    reducescatter_adamw_kernel<<<blocks, 512, 0, st>>>(peers, segs, full_byte_off, sink, scale, scale_ptr, slot, epoch,
+                                                       status);
 }
 
 void comm_reduce_slices(const void* slices, int world, long long n, void* out, bool out_f32, cudaStream_t st) {

@@ -57,10 +57,12 @@ void comm_alltoall(const CommPeers& peers, long long byte_off, void* dst, const 
                    int slot, uint32_t epoch, int blocks, int* status, cudaStream_t st);
 
 // Reduce-scatter of bf16 gradients fused with the AdamW step of the local fp32 shard (`p`, `m`, `v`: shard-sized
-// fp32; `low`: optional bf16 copy of the updated parameters). `step` is the 1-based step count.
+// fp32; `low`: optional bf16 copy of the updated parameters). `step` is the 1-based step count; `scale_ptr` (may be
+// null) is a device scalar multiplied into `scale`.
 void comm_reducescatter_adamw(const CommPeers& peers, const CommSegments& segs, long long full_byte_off, float* p,
                               float* m, float* v, void* low, float scale, float lr, float beta1, float beta2, float eps,
-                              float wd, int step, int slot, uint32_t epoch, int blocks, int* status, cudaStream_t st);
+                              float wd, int step, const float* scale_ptr, int slot, uint32_t epoch, int blocks,
+                              int* status, cudaStream_t st);
 
 // In-place all-reduce (sum * scale) of `numel` bf16/fp32 elements at `byte_off` of every arena; `counter` points at
 // TWO zeroed device words (end of phase 1, end of phase 2); at most `blocks` <= number of SMs CTAs. The kernel ends

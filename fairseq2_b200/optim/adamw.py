@@ -74,6 +74,36 @@ class AdamW(Optimizer):
                 st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32, memory_format=torch.preserve_format)
         return st
 
+    def prepare_fused_step(self, grad_scale: Tensor | None = None) -> int:
+        """Arms the FSDP units of this optimizer so that their gradient reduce-scatter applies THIS step's update in
+        the same kernel (``comm_reducescatter_adamw``): call before the backward pass, then :meth:`step` as usual
+        afterwards -- it only has to book-keep for the units that were updated on the way. ``grad_scale`` is the
+        device scalar (loss normalisation) multiplied into the averaged gradient. Returns the number of armed
+        units. Only valid when no decision depends on all gradients at once (no clipping by the global norm, no
+        loss-scale overflow check)."""
+        armed = 0
+        _refresh_status_guard(self.param_groups)
+        for group in self.param_groups:
+            b1, b2 = group["betas"]
+            units: dict[int, Any] = {}
+            for p in group["params"]:
+                unit = getattr(p, "_fs2_unit", None)
+                if unit is not None:
+                    units[id(unit)] = unit
+                    self._init_state(p)
+            for unit in units.values():
+                if unit.arena is None or unit.low_shard.dtype != torch.bfloat16 or unit.master.device != unit.device:
+                    continue
+                st0 = self.state[unit.shard_params[0]]
+                step = st0.get("_host_step", int(st0["step"].item())) + 1
+                m, v = self._unit_moments(unit)
+                unit.fused_step = {"m": m, "v": v, "lr": float(group["lr"]), "beta1": b1, "beta2": b2,
+                                   "eps": group["eps"], "weight_decay": group["weight_decay"], "step": step,
+                                   "grad_scale": grad_scale}
+                unit.fused_done = False
+                armed += 1
+        return armed
+
     @torch.no_grad()
     def step(self, closure: Callable[[], Tensor] | None = None, *, grad_scale: Tensor | None = None) -> Tensor | None:  # type: ignore[override]
         loss = None
@@ -97,6 +127,16 @@ class AdamW(Optimizer):
                     plain.append(p)
             # ---- flat units: one launch each
             for uid, unit in units.items():
+                if getattr(unit, "fused_done", False):
+                    # the reduce-scatter of this unit has already applied the update: only the step count moves
+                    step = unit.fused_step["step"]
+                    unit.fused_step, unit.fused_done = None, False
+                    for sp in unit.shard_params:
+                        st = self.state[sp]
+                        st["_host_step"] = step
+                        st["step"].fill_(step)
+                    continue
+                unit.fused_step = None
                 if not unit.grads_ready or unit.grad_shard is None:
                     continue
                 if unit_members[uid] != len(unit.shard_params):

@@ -130,6 +130,13 @@ class FlatParamUnit:
         self.norm_slot: Tensor | None = None
         self.norm_fused = False     # ``norm_slot`` holds the norm of the current ``grad_shard``
         self.replicated = False     # gradients are averaged over a replica gang after the (trivial) reduction
+        #: hyper-parameters and moment buffers of an optimizer step that the reduce-scatter applies itself
+        #: (set per step by the optimizer's ``prepare_fused_step``; ``None`` = reduce only)
+        self.fused_step: dict[str, Any] | None = None
+        self.fused_done = False
+        #: parameters whose gradients are partial sums over the tensor-parallel gang (set by FSDP)
+        self.tp_partial_specs: list[_ParamSpec] = []
+        self.tp_gang: Gang | None = None
 
         # shard parameters handed to the optimizer / state dict
         self.shard_params: list[Parameter] = []
@@ -324,6 +331,8 @@ class FlatParamUnit:
                 cp.grad_sink_filled = True  # type: ignore[attr-defined]
         W = self.world
         self.norm_fused = False
+        if self.tp_partial_specs:
+            self._sum_tp_partial_grads(comm_stream)
         if W == 1:
             self.grad_shard = self.grad_full
             self.grads_ready = True
@@ -348,6 +357,23 @@ class FlatParamUnit:
                 if not acc:
                     self.grad_shard = torch.empty(self.shard_size, device=self.device, dtype=torch.float32)
                 self.rs_epoch += 1
+                fo = self.fused_step
+                if fo is not None and not acc:
+                    # Reduce-scatter fused with the optimizer: the reduced gradient stays in registers through the
+                    # AdamW update of the local shard (fp32 master + moments) and the refreshed bf16 shard is
+                    # written in the same pass; no fp32 gradient shard is ever stored. Possible whenever nothing
+                    # has to look at ALL gradients before the update (no clipping by the global norm).
+                    a.ext.comm_reducescatter_adamw(a.peer_ptrs, a.rank, self.seg_offs, self.seg_numels, self.grad_off,
+                                                   self.master, fo["m"], fo["v"], self.low_shard,
+                                                   (1.0 / W) if average else 1.0, fo["lr"], fo["beta1"], fo["beta2"],
+                                                   fo["eps"], fo["weight_decay"], fo["step"], 2 + self.slot,
+                                                   self.rs_epoch, self.rs_blocks, a.wait_limit_s, fo["grad_scale"])
+                    self.fused_done = True
+                    self.grad_shard = None
+                    self.grads_ready = False
+                    for cp in self.compute_params:
+                        cp.grad_sink_filled = False  # type: ignore[attr-defined]
+                    return
                 # the squared norm of the shard is a by-product of the pass that writes it (not when this pass adds
                 # to an earlier micro-batch's sum: then only a pass over the final sum gives the norm)
                 norm = self.norm_slot if not acc else None
@@ -389,6 +415,28 @@ class FlatParamUnit:
         for cp in self.compute_params:
             cp.grad_sink = None  # type: ignore[attr-defined]
             cp.grad_sink_filled = False  # type: ignore[attr-defined]
+
+    def _sum_tp_partial_grads(self, comm_stream: "torch.cuda.Stream | None") -> None:
+        """With sequence-parallel activations every tensor-parallel rank sees its own tokens only, so the gradient
+        of a parameter that is replicated over the tp gang (a norm weight) is a partial sum. The partials are added
+        up over the tp gang in the flat gradient buffer, BEFORE the data-parallel reduction, so that whatever
+        consumes the reduced gradient (also an optimizer step fused into the reduce-scatter) sees the full sum.
+        All such parameters of the unit travel in one small all-reduce."""
+        assert self.grad_full is not None and self.tp_gang is not None
+        cur = torch.cuda.current_stream(self.device) if self.device.type == "cuda" else None
+        if comm_stream is not None and cur is not None:
+            comm_stream.wait_stream(cur)
+            ctx: Any = torch.cuda.stream(comm_stream)
+        else:
+            ctx = _null()
+        with ctx:
+            views = [self._region(self.grad_full, s)[: s.d0 * s.row] for s in self.tp_partial_specs]
+            flat = torch.cat([v.float() for v in views])
+            self.tp_gang.all_reduce(flat, ReduceOperation.SUM)
+            pos = 0
+            for v in views:
+                v.copy_(flat[pos: pos + v.numel()])
+                pos += v.numel()
 
     def zero_grad(self) -> None:
         self.grads_ready = False
@@ -593,6 +641,9 @@ class FSDP(Module):
             # (offset, length) in the unit's shard buffers of the parameters that are replicated over the tp gang
             u.tp_replicated = [(sp.shard_off, sp.rows_local * sp.row) for sp in u.specs
                                if sp.fqn not in tp_sharded and sp.requires_grad] if self.tp_gang is not None else []
+            if self.tp_gang is not None and self.tp_sequence_parallel:
+                u.tp_gang = self.tp_gang
+                u.tp_partial_specs = [sp for sp in u.specs if sp.fqn not in tp_sharded and sp.requires_grad]
         self.replica_arena: Any = None
         if (W == 1 and self.replica_gang is not None and comm != "nccl" and param_dtype == torch.bfloat16
                 and dev.type == "cuda"):
@@ -715,27 +766,12 @@ class FSDP(Module):
             for u in self.all_units:
                 if u.grad_shard is not None and not getattr(u, "replicas_reduced", False):
                     self.replica_gang.all_reduce(u.grad_shard, ReduceOperation.MEAN)
-        if self.tp_gang is not None and self.tp_sequence_parallel and self._require_sync:
-            self._sum_tp_partial_grads()
 
-    def _sum_tp_partial_grads(self) -> None:
-        """With sequence-parallel activations every tp rank sees its own tokens only, so the gradient of a
-        parameter that is replicated over the tp gang (a norm weight) is a partial sum: add the partials up.
-        All segments travel in one small all-reduce."""
-        assert self.tp_gang is not None
-        views = [u.grad_shard[off: off + n] for u in self.all_units if u.grad_shard is not None and u.grads_ready
-                 for off, n in u.tp_replicated if n > 0]
-        if not views:
-            return
-        flat = torch.cat([v.float() for v in views])
-        self.tp_gang.all_reduce(flat, ReduceOperation.SUM)
-        pos = 0
-        for v in views:
-            v.copy_(flat[pos: pos + v.numel()])
-            pos += v.numel()
-        for u in self.all_units:
-            if u.tp_replicated:
-                u.norm_fused = False          # the norm that the reduce-scatter pass emitted predates this sum
+    @property
+    def supports_fused_optimizer(self) -> bool:
+        """True if the gradient reduce-scatter of every unit can apply the optimizer step itself: sharded over a
+        symmetric arena, bf16 shards, no replica gang."""
+        return self.arena is not None and self.replica_gang is None and not self.cpu_offload
 
     def check_comm_status(self) -> None:
         """Raises :class:`~fairseq2_b200.ops._ext.KernelWaitTimeout` if a kernel of this process gave up on a

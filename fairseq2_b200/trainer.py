@@ -67,7 +67,11 @@ class TrainStep:
 
     def __init__(self, unit: TrainUnit[Any], optimizer: Optimizer, gangs: Gangs, *, max_grad_norm: float | None = None,
                  lr_scheduler: Any | None = None, loss_scaler: Any | None = None, no_sync: bool = False,
-                 metric_bag: Any | None = None) -> None:
+                 metric_bag: Any | None = None, fuse_optimizer: bool = True) -> None:
+        """``fuse_optimizer``: when nothing needs all gradients before the update (no gradient clipping, no loss
+        scaler, one micro-batch) and the unit can tell its number of targets up front (``unit.count_targets``),
+        the optimizer step of every FSDP unit runs inside its gradient reduce-scatter kernel."""
+        self.fuse_optimizer = fuse_optimizer
         self.unit, self.optimizer, self.gangs = unit, optimizer, gangs
         self.max_grad_norm, self.lr_scheduler, self.loss_scaler = max_grad_norm, lr_scheduler, loss_scaler
         self.no_sync = no_sync
@@ -85,6 +89,7 @@ class TrainStep:
             check()
         model.zero_grad()
         n = len(batches)
+        fused = self._maybe_arm_fused_optimizer(model, batches)
         total_loss: Tensor | None = None
         total_targets: Tensor | int | None = 0
         for i, batch in enumerate(batches):
@@ -106,7 +111,9 @@ class TrainStep:
         assert total_loss is not None
         # ---- normalise: gradients hold the data-parallel MEAN of per-rank sums
         dp = self.gangs.dp
-        if total_targets is not None:
+        if fused:
+            pass        # the normalisation factor went into the fused reduce-scatter + update kernels
+        elif total_targets is not None:
             t = total_targets if isinstance(total_targets, Tensor) else \
                 torch.tensor(float(total_targets), device=total_loss.device)
             t = t.to(torch.float32)
@@ -139,6 +146,27 @@ class TrainStep:
         if check is not None:
             check()
         return total_loss, grad_norm
+
+
+def _arm_fused(self: TrainStep, model: Any, batches: Sequence[Any]) -> bool:
+    count = getattr(self.unit, "count_targets", None)
+    inner = getattr(model, "module", None)
+    prepare = getattr(self.optimizer, "prepare_fused_step", None)
+    if (not self.fuse_optimizer or count is None or prepare is None or len(batches) != 1
+            or self.max_grad_norm is not None or self.loss_scaler is not None
+            or not getattr(inner, "supports_fused_optimizer", False)):
+        return False
+    t = count(batches[0])
+    dev = self.gangs.root.device
+    t = t.to(device=dev, dtype=torch.float32) if isinstance(t, Tensor) else torch.tensor(float(t), device=dev)
+    dp = self.gangs.dp
+    if dp.size > 1:
+        t = t.clone()
+        dp.all_reduce(t, ReduceOperation.SUM)
+    return prepare(dp.size / t.clamp(min=1.0)) > 0
+
+
+TrainStep._maybe_arm_fused_optimizer = _arm_fused  # type: ignore[attr-defined]
 
 
 class Validator(ABC):
