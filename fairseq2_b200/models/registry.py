@@ -41,6 +41,12 @@ def _register_lm_families() -> None:
         layerwise_ac_applier=apply_layerwise_ac))
 
 
+    from fairseq2_b200.models.moe_lm import MOE_LM_FAMILY, MoELMConfig, MoETransformerLM, create_moe_lm_model
+
+    register_model_family(ModelFamily(
+        name=MOE_LM_FAMILY, kls=MoETransformerLM, config_kls=MoELMConfig, factory=create_moe_lm_model,
+        fsdp_wrap_policy=layerwise_wrap_policy, layerwise_ac_applier=apply_layerwise_ac))
+
     from fairseq2_b200.models.gemma3n import (GEMMA3N_FAMILY, Gemma3nConfig, Gemma3nModel, convert_gemma3n_state_dict,
                                               create_gemma3n_model, export_gemma3n_to_hg, gemma3n_wrap_policy)
 

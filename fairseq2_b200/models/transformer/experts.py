@@ -103,16 +103,18 @@ class TPShardedExpertNetwork(ExpertNetwork):
         return grouped_mm(h, self.output_proj, group_sizes)
 
 
-def route_tokens(logits: Tensor, top_k: int) -> tuple[Tensor, Tensor, Tensor, list[int]]:
+def route_tokens(logits: Tensor, top_k: int, softmax_gate: bool = False) -> tuple[Tensor, Tensor, Tensor, list[int]]:
     """Token-choice routing. Returns ``(token_idx [R], expert_scores [R], order, group_sizes)`` where the ``R = T·k``
-    routed rows are sorted by expert; ``expert_scores`` is ``sigmoid`` of the selected logits."""
+    routed rows are sorted by expert; ``expert_scores`` is ``sigmoid`` of the selected logits, or their softmax
+    over the ``top_k`` choices of the token with ``softmax_gate``."""
     T, E = logits.shape
     scores, experts = torch.topk(logits, top_k, dim=1)                   # [T, k]
     flat_e = experts.reshape(-1)
     order = torch.argsort(flat_e, stable=True)                           # rows grouped by expert
     token_idx = order // top_k
     sizes = torch.bincount(flat_e, minlength=E).tolist()
-    return token_idx, torch.sigmoid(scores.reshape(-1)[order].float()), order, sizes
+    gates = torch.softmax(scores.float(), dim=1) if softmax_gate else torch.sigmoid(scores.float())
+    return token_idx, gates.reshape(-1)[order], order, sizes
 
 
 class MoE(FeedForwardNetwork):
@@ -121,11 +123,18 @@ class MoE(FeedForwardNetwork):
     def __init__(self, model_dim: int, inner_dim: int, use_shared_expert: bool, num_experts: int,
                  capacity_factor: float, top_k: int, *, moe_activation: Module | None = None,
                  inner_dim_scale: float = 2 / 3, inner_dim_to_multiple: int = 1, auto_scale: bool = True,
-                 tp_gang: Gang | None = None, ep: Any | None = None, device: Device | None = None,
+                 tp_gang: Gang | None = None, ep: Any | None = None, softmax_gate: bool = False,
+                 aux_loss: bool = False, router_init_std: float | None = None, device: Device | None = None,
                  dtype: DataType | None = None) -> None:
         """``ep``: an ``ops.moe_ep.ExpertParallelExchange``. When given, this rank holds only its
         ``num_experts / ep.arena.world`` experts and tokens travel to the owning rank inside the dispatch kernel and
-        back inside the combine kernel; the router and the shared expert stay replicated."""
+        back inside the combine kernel; the router and the shared expert stay replicated.
+
+        ``softmax_gate``: gates are the softmax over the selected ``top_k`` logits (Mixtral / Qwen-MoE style)
+        instead of independent sigmoids (LLaMA 4). ``aux_loss``: every forward pass in training mode leaves the
+        router's load-balancing loss in ``self.last_aux_loss`` (see ``ops.moe.load_balancing_loss``) for the model
+        to add to its objective. ``router_init_std``: normal initialisation of the router (default
+        ``model_dim ** -0.5``, truncated)."""
         super().__init__(model_dim)
         if inner_dim_scale != 1.0:
             inner_dim = int(inner_dim * inner_dim_scale)
@@ -141,6 +150,8 @@ class MoE(FeedForwardNetwork):
             self.shared_expert = GLUFeedForwardNetwork(model_dim, inner_dim, bias=False, inner_dim_scale=1.0,
                                                        device=device, dtype=dtype)
         self.router = Parameter(torch.empty((model_dim, num_experts), device=device, dtype=dtype))
+        self.softmax_gate, self.aux_loss, self.router_init_std = softmax_gate, aux_loss, router_init_std
+        self.last_aux_loss: Tensor | None = None
         self.ep = ep
         if ep is not None:
             if self.tp_gang is not None:
@@ -159,24 +170,41 @@ class MoE(FeedForwardNetwork):
 
     def reset_parameters(self) -> None:
         if self.router.device.type != "meta":
-            torch.nn.init.trunc_normal_(self.router, std=self.model_dim ** -0.5)
+            if self.router_init_std is not None:
+                torch.nn.init.normal_(self.router, std=self.router_init_std)
+            else:
+                torch.nn.init.trunc_normal_(self.router, std=self.model_dim ** -0.5)
+
+    def _router_logits(self, x: Tensor) -> Tensor:
+        """``x @ router`` on the tcgen05 GEMM (the router is stored ``[D, E]``, i.e. as an MN-major B operand)."""
+        from fairseq2_b200.ops.gemm import linear_kn
+
+        return linear_kn(x, self.router, out_dtype=torch.float32 if x.is_cuda else None)
+
+    def _note_aux_loss(self, logits: Tensor, counts: Tensor) -> None:
+        from fairseq2_b200.ops.moe import load_balancing_loss
+
+        self.last_aux_loss = load_balancing_loss(logits, counts, self.top_k) \
+            if (self.aux_loss and self.training) else None
 
     def forward(self, seqs: Tensor) -> Tensor:
         x = seqs.reshape(-1, self.model_dim)
-        logits = x @ self.router
+        logits = self._router_logits(x)
         from fairseq2_b200.ops import moe as moe_ops
 
         if self.ep is not None:
             if not moe_ops.moe_kernels_available(x, logits):
                 raise RuntimeError("Expert parallelism needs the CUDA routing kernels (bf16 activations on a GPU).")
-            ids, gates, counts = moe_ops.moe_route(logits, self.top_k)
+            ids, gates, counts = moe_ops.moe_route(logits, self.top_k, self.softmax_gate)
+            self._note_aux_loss(logits, counts)
             rows, dest, group_sizes = self.ep.dispatch(x, ids, counts, gates=gates)
             rows_out = self.experts(rows, group_sizes.tolist())
             base = self.shared_expert(x) if self.shared_expert is not None else None
             return self.ep.combine(rows_out, dest, x.shape[0], base=base).view(seqs.shape)
         if moe_ops.moe_kernels_available(x, logits):
             # fused top-k gate + histogram, gather/scale into expert order, experts, gather back per token
-            ids, gates, counts = moe_ops.moe_route(logits, self.top_k)
+            ids, gates, counts = moe_ops.moe_route(logits, self.top_k, self.softmax_gate)
+            self._note_aux_loss(logits, counts)
             if isinstance(self.experts, GroupedExpertNetwork) and self.experts.supports_padded_layout(x):
                 # padded layout + device-resident tile tables: the CPU never waits for the routing result
                 routed_in, src_row, inv, layout = moe_ops.moe_dispatch_padded(x, gates, ids, counts)
@@ -189,7 +217,8 @@ class MoE(FeedForwardNetwork):
             if self.tp_gang is not None:
                 out = reduce(out, self.tp_gang)
             return out.view(seqs.shape)
-        token_idx, scores, _, sizes = route_tokens(logits, self.top_k)
+        token_idx, scores, _, sizes = route_tokens(logits, self.top_k, self.softmax_gate)
+        self._note_aux_loss(logits, torch.tensor(sizes, device=logits.device))
         routed_in = x.index_select(0, token_idx) * scores.to(x.dtype).unsqueeze(1)
         routed_out = self.experts(routed_in, sizes)
         out = self.shared_expert(x) if self.shared_expert is not None else torch.zeros_like(x)

@@ -121,3 +121,37 @@ def linear(x: Tensor, weight: Tensor, bias: Tensor | None = None) -> Tensor:
             y = y + bias
         return y
     return torch.nn.functional.linear(x, weight, bias)
+
+
+class _LinearKNFn(torch.autograd.Function):
+    """``y = x @ w`` with ``w`` stored ``[K, N]`` (an MN-major B operand): no transpose is ever materialised."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, weight: Tensor, out_dtype: torch.dtype | None = None) -> Tensor:  # type: ignore[override]
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        ctx.save_for_backward(x2, weight)
+        ctx.x_shape = x.shape
+        return gemm(x2, weight, b_mn=True, out_dtype=out_dtype).view(*x.shape[:-1], weight.shape[1])
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):  # type: ignore[override]
+        x2, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).to(x2.dtype)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = gemm(dy2, weight).view(ctx.x_shape) if ctx.needs_input_grad[0] else None     # dy [M, N] x w [K, N]^T
+        dw = gemm(x2, dy2, a_mn=True, b_mn=True) if ctx.needs_input_grad[1] else None     # x^T dy -> [K, N]
+        return dx, dw, None
+
+
+def linear_kn(x: Tensor, weight: Tensor, out_dtype: torch.dtype | None = None) -> Tensor:
+    """``x @ weight`` for a weight stored ``[in, out]`` (e.g. a mixture-of-experts router); CUDA bf16 inputs run on
+    the tcgen05 GEMM, forward and backward. ``out_dtype=torch.float32`` keeps the fp32 accumulators (router logits
+    decide a discrete choice, so they are not rounded to bf16)."""
+    if use_kernels(x, weight) and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and not _USE_CUBLAS \
+            and weight.is_contiguous() and weight.shape[1] % 8 == 0 and weight.shape[0] % 8 == 0:
+        return _LinearKNFn.apply(x, weight, out_dtype)
+    y = x @ weight
+    return y.to(out_dtype) if out_dtype is not None else y

@@ -127,3 +127,15 @@ def moe_dispatch_padded(x: Tensor, gates: Tensor, expert_ids: Tensor, counts: Te
 
 def moe_combine(routed: Tensor, inv: Tensor, src_row: Tensor, base: Tensor | None = None) -> Tensor:
     return _Combine.apply(routed, inv, src_row, base)
+
+
+def load_balancing_loss(logits: Tensor, counts: Tensor, top_k: int) -> Tensor:
+    """Switch / GShard load-balancing auxiliary loss of one router:
+    ``E * sum_e f_e * P_e`` with ``f_e`` the fraction of the ``T * k`` routing slots that went to expert ``e`` (a
+    constant with respect to the parameters) and ``P_e`` the mean router probability of expert ``e``. It is 1 for a
+    uniform router and grows as load and probability mass concentrate on the same experts. ``logits``: ``[T, E]``;
+    ``counts``: ``[E]`` slots per expert as produced by the routing kernel."""
+    T, E = logits.shape
+    probs = torch.softmax(logits.float(), dim=-1).mean(dim=0)
+    frac = counts.to(torch.float32) / max(T * top_k, 1)
+    return E * (frac.detach() * probs).sum()

@@ -134,6 +134,7 @@ class FlatParamUnit:
         #: (set per step by the optimizer's ``prepare_fused_step``; ``None`` = reduce only)
         self.fused_step: dict[str, Any] | None = None
         self.fused_done = False
+        self.reduced_in_step = False   # the unit's gradients were reduced since the last ``zero_grad``
         #: parameters whose gradients are partial sums over the tensor-parallel gang (set by FSDP)
         self.tp_partial_specs: list[_ParamSpec] = []
         self.tp_gang: Gang | None = None
@@ -319,6 +320,7 @@ class FlatParamUnit:
         if self.grad_full is None or not self.needs_reduce:
             return
         self.needs_reduce = False
+        self.reduced_in_step = True
         self.collect_autograd_grads()
         shared = self.world > 1 or getattr(self, "replica_arena", None) is not None or self.replicated
         for i, (s, cp) in enumerate(zip(self.specs, self.compute_params)):
@@ -440,6 +442,7 @@ class FlatParamUnit:
 
     def zero_grad(self) -> None:
         self.grads_ready = False
+        self.reduced_in_step = False
         self.replicas_reduced = False
         self.norm_fused = False
         self.took_part = [False] * len(self.specs)
@@ -751,7 +754,8 @@ class FSDP(Module):
         if self._require_sync:
             multi = self.gang.size > 1 or self.replica_gang is not None
             for u in self.all_units:
-                if not u.needs_reduce and multi and not u.grads_ready and any(s.requires_grad for s in u.specs):
+                if (not u.needs_reduce and multi and not u.reduced_in_step
+                        and any(s.requires_grad for s in u.specs)):
                     # The unit did not run on this rank in this step (LayerDrop, an unused expert, a skipped
                     # branch), but it may have run on a peer: every rank takes part in every unit's reduction,
                     # contributing zeros, or the peers would wait for it.
