@@ -71,6 +71,34 @@ def _trace_steps(args: argparse.Namespace, step_fn, batches, rank: int, record: 
         t = totals.setdefault(r["name"], [0.0, 0])
         t[0] += r["dur"] / 1000.0 / len(batches)
         t[1] += 1
+    # exposed communication: what the compute stream (the one that runs the GEMMs) spends idle between the first and
+    # the last kernel of the traced steps -- time in which the step waits for a collective, a copy or the host
+    by_stream: dict[object, list[tuple[float, float]]] = {}
+    gemm_us: dict[object, float] = {}
+    for r in rows:
+        by_stream.setdefault(r["stream"], []).append((r["ts"], r["ts"] + r["dur"]))
+        if "gemm" in r["name"]:
+            gemm_us[r["stream"]] = gemm_us.get(r["stream"], 0.0) + r["dur"]
+    stats = {}
+    if gemm_us:
+        cs = max(gemm_us, key=gemm_us.get)  # type: ignore[arg-type]
+        iv = sorted(by_stream[cs])
+        busy, cur_s, cur_e = 0.0, iv[0][0], iv[0][1]
+        for s_, e_ in iv[1:]:
+            if s_ > cur_e:
+                busy += cur_e - cur_s
+                cur_s, cur_e = s_, e_
+            else:
+                cur_e = max(cur_e, e_)
+        busy += cur_e - cur_s
+        span = iv[-1][1] - iv[0][0]
+        stats = {"compute_stream_idle_ms_per_step": (span - busy) / 1000.0 / len(batches),
+                 "compute_stream_busy_ms_per_step": busy / 1000.0 / len(batches),
+                 "gemm_ms_per_step": gemm_us[cs] / 1000.0 / len(batches),
+                 "other_streams_kernel_ms_per_step": sum(e_ - s_ for k_, v in by_stream.items() if k_ != cs
+                                                         for s_, e_ in v) / 1000.0 / len(batches)}
+        with open(f"{args.trace}.rank{rank}.overlap.json", "w") as fp:
+            json.dump(stats, fp)
     with open(f"{args.trace}.rank{rank}.kernels.txt", "w") as fp:
         fp.write(f"# kernel time per step (torch.profiler CUDA activity, {len(batches)} steps averaged)\n")
         fp.write(f"TOTAL {sum(t[0] for t in totals.values()):.1f} ms/step\n")
@@ -190,10 +218,26 @@ def run_ours(args: argparse.Namespace) -> None:
     stop.set()
     ext.check_status()
 
-    if args.trace:
+    # kernel timeline of two more steps, outside every timed region: the source of the exposed-communication figure
+    overlap = None
+    if not args.no_trace:
+        import tempfile
+
+        own_prefix = args.trace is None
+        if own_prefix:
+            args.trace = os.path.join(tempfile.mkdtemp(prefix="fs2_trace_"), "t")
         _trace_steps(args, step_fn, [stage(examples[args.warmup + i]) for i in range(2)], rank,
                      record=rank == 0 or args.trace_all_ranks)
         barrier()
+        try:
+            with open(f"{args.trace}.rank0.overlap.json") as fp:
+                overlap = json.load(fp) if rank == 0 else None
+        except OSError:
+            overlap = None
+        if own_prefix and rank == 0:
+            import shutil
+
+            shutil.rmtree(os.path.dirname(args.trace), ignore_errors=True)
 
     times = torch.tensor([dev_ms, e2e_ms], device=device, dtype=torch.float64)
     if world > 1:
@@ -231,6 +275,12 @@ def run_ours(args: argparse.Namespace) -> None:
             "peak_mem_gb": torch.cuda.max_memory_allocated(device) / 2**30,
         }
         out["model_tflops_per_gpu"] = flops_per_step / (dev_ms / args.steps * 1e-3) / 1e12
+        if overlap:
+            # exposed communication of the step: idle time of the compute stream (kernel timeline of two extra steps
+            # recorded after the timed regions); GEMM time is listed so that runs at different N can be compared
+            out["exposed_comm_ms"] = round(overlap["compute_stream_idle_ms_per_step"], 3)
+            out["gemm_ms_per_step"] = round(overlap["gemm_ms_per_step"], 3)
+            out["comm_stream_kernel_ms_per_step"] = round(overlap["other_streams_kernel_ms_per_step"], 3)
         print(json.dumps(out), flush=True)
     if world > 1:
         root.close()
@@ -274,6 +324,8 @@ def main() -> None:
     ap.add_argument("--trace", default=None, metavar="PREFIX",
                     help="after the timed regions, write a kernel timeline of two steps to PREFIX.rankN.json")
     ap.add_argument("--trace-all-ranks", action="store_true")
+    ap.add_argument("--no-trace", action="store_true",
+                    help="skip the two traced steps after the timed regions (no `exposed_comm_ms` in the result)")
     ap.add_argument("--layers", type=int, default=None, help="debugging only: truncates the model (result is not a valid benchmark)")
     args = ap.parse_args()
     if args.warmup < 3 and args.layers is None:

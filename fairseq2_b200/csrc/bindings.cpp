@@ -598,9 +598,51 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> moe_ep_layout(const std::vector<int64
     return {send_base, cursor, group_sizes, total};
 }
 
+// returns (send_base [E], limit [E], cursor [E], offsets [El + 1], group_sizes [El], tile_row0 [cap / 128],
+//          tile_expert [cap / 128], num_tiles [1], total [1])
+std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor> moe_ep_layout_padded(
+    const std::vector<int64_t>& ptrs, int64_t rank, const Tensor& counts, int64_t table_byte_off, int64_t inbox_byte_off,
+    int64_t cap, int64_t D, int64_t slot, int64_t epoch, double wait_limit_s) {
+    const int64_t W = static_cast<int64_t>(ptrs.size()), E = counts.numel();
+    TORCH_CHECK(counts.is_cuda() && counts.scalar_type() == at::kInt && counts.is_contiguous() && E % W == 0 && E <= 256,
+                "moe_ep_layout_padded: counts must be an int32 CUDA vector whose length is a multiple of the world size");
+    const int64_t El = E / W;
+    TORCH_CHECK(table_byte_off % 16 == 0 && inbox_byte_off % 16 == 0 && cap % 128 == 0 && cap >= 128 * El && D % 8 == 0,
+                "moe_ep_layout_padded: the inbox must hold a multiple of 128 rows and at least 128 per local expert");
+    c10::cuda::CUDAGuard guard(counts.device());
+    auto iopt = counts.options();
+    Tensor send_base = at::empty({E}, iopt), limit = at::empty({E}, iopt), cursor = at::empty({E}, iopt);
+    Tensor offsets = at::empty({El + 1}, iopt), group_sizes = at::empty({El}, iopt);
+    Tensor tile_row0 = at::empty({cap / 128}, iopt), tile_expert = at::empty({cap / 128}, iopt);
+    Tensor num_tiles = at::empty({1}, iopt), total = at::empty({1}, iopt);
+    void* inbox = reinterpret_cast<char*>(ptrs[static_cast<size_t>(rank)]) + inbox_byte_off;
+    fs2::moe_ep_layout_padded(make_peers(ptrs, rank, wait_limit_s), counts.data_ptr<int>(), table_byte_off,
+                              static_cast<int>(E), static_cast<int>(cap), send_base.data_ptr<int>(),
+                              limit.data_ptr<int>(), cursor.data_ptr<int>(), offsets.data_ptr<int>(),
+                              group_sizes.data_ptr<int>(), tile_row0.data_ptr<int>(), tile_expert.data_ptr<int>(),
+                              num_tiles.data_ptr<int>(), total.data_ptr<int>(), inbox, static_cast<int>(D),
+                              static_cast<int>(slot), static_cast<uint32_t>(epoch), status_dev_ptr(),
+                              stream_of(counts));
+    g_launches += 2;
+    return {send_base, limit, cursor, offsets, group_sizes, tile_row0, tile_expert, num_tiles, total};
+}
+
 void moe_ep_push(const std::vector<int64_t>& ptrs, int64_t rank, const Tensor& x, const std::optional<Tensor>& expert_ids,
                  const std::optional<Tensor>& gates, const std::optional<Tensor>& send_base,
-                 const std::optional<Tensor>& cursor, int64_t inbox_byte_off, Tensor dest, int64_t E, int64_t cap) {
+                 const std::optional<Tensor>& cursor, int64_t inbox_byte_off, Tensor dest, int64_t E, int64_t cap,
+                 const std::optional<Tensor>& limit, const std::optional<Tensor>& dropped) {
+    const int* limit_ptr = nullptr;
+    int* dropped_ptr = nullptr;
+    if (limit.has_value()) {
+        TORCH_CHECK(limit->is_cuda() && limit->scalar_type() == at::kInt && limit->is_contiguous() && limit->numel() == E,
+                    "moe_ep_push: limit must be int32 [E]");
+        limit_ptr = limit->data_ptr<int>();
+    }
+    if (dropped.has_value()) {
+        TORCH_CHECK(dropped->is_cuda() && dropped->scalar_type() == at::kInt && dropped->numel() == 1,
+                    "moe_ep_push: dropped must be an int32 device scalar");
+        dropped_ptr = dropped->data_ptr<int>();
+    }
     TORCH_CHECK(x.is_cuda() && is_bf16(x) && x.dim() == 2 && x.is_contiguous() && x.size(1) % 8 == 0 && aligned16(x),
                 "moe_ep_push: x must be a contiguous bf16 [T, D] CUDA tensor with D % 8 == 0");
     TORCH_CHECK(dest.scalar_type() == at::kInt && dest.is_contiguous() && dest.dim() == 2 && dest.size(0) == x.size(0),
@@ -623,7 +665,8 @@ void moe_ep_push(const std::vector<int64_t>& ptrs, int64_t rank, const Tensor& x
     fs2::moe_ep_push(make_peers(ptrs, rank, 1.0), x.data_ptr(), assign ? expert_ids->data_ptr<int>() : nullptr, gp,
                      assign ? send_base->data_ptr<int>() : nullptr, assign ? cursor->data_ptr<int>() : nullptr,
                      inbox_byte_off, dest.data_ptr<int>(), static_cast<int>(x.size(0)), static_cast<int>(dest.size(1)),
-                     static_cast<int>(x.size(1)), static_cast<int>(E), static_cast<int>(cap), assign, stream_of(x));
+                     static_cast<int>(x.size(1)), static_cast<int>(E), static_cast<int>(cap), assign, limit_ptr,
+                     dropped_ptr, stream_of(x));
     g_launches += 1;
 }
 
@@ -1395,7 +1438,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("w2v_quantize_fwd", &w2v_quantize_fwd);
     m.def("w2v_quantize_bwd", &w2v_quantize_bwd);
     m.def("moe_ep_layout", &moe_ep_layout);
-    m.def("moe_ep_push", &moe_ep_push);
+    m.def("moe_ep_push", &moe_ep_push, py::arg("ptrs"), py::arg("rank"), py::arg("x"), py::arg("expert_ids"),
+          py::arg("gates"), py::arg("send_base"), py::arg("cursor"), py::arg("inbox_byte_off"), py::arg("dest"),
+          py::arg("E"), py::arg("cap"), py::arg("limit") = std::nullopt, py::arg("dropped") = std::nullopt);
+    m.def("moe_ep_layout_padded", &moe_ep_layout_padded);
     m.def("moe_ep_pull", &moe_ep_pull);
     m.def("ngram_repeat_block", &ngram_repeat_block);
     m.def("sample_top_p_top_k", &sample_top_p_top_k);

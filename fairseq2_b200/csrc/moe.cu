@@ -246,6 +246,101 @@ __global__ void __launch_bounds__(256) moe_ep_layout_kernel(CommPeers peers, con
     }
 }
 
+// Layout of the inboxes for the single-launch grouped GEMM: at every owner the rows of local expert i occupy a range
+// that starts on a multiple of 128 rows and is padded to one (at least one tile, so that no expert is empty); inside
+// a range rows are ordered by source rank, then by arrival. Every rank derives the layout of EVERY inbox from the
+// exchanged count table, so senders know where their rows go without a second exchange.
+//
+// Overflow: an inbox holds `cap` rows (a multiple of 128, at least 128 per local expert). If the padded ranges of
+// an owner do not fit, the ranges are cut (each later expert keeps one tile) and the rows that do not fit are
+// DROPPED: their `dest` is -1, combine reads zero for them, and the push kernel counts them.
+//
+// One block. Outputs for all E experts: send_base[e] (first inbox row, at the owner of e, of this rank's rows),
+// limit[e] (first row of e's range that holds no accepted row); for the El local experts: offsets[El + 1] (range
+// starts), group_sizes[El] (accepted rows), the tile tables of the grouped GEMM, total[0] = rows in use incl. padding.
+__global__ void __launch_bounds__(256) moe_ep_layout_padded_kernel(
+    CommPeers peers, const int* __restrict__ counts, long long table_byte_off, int E, int El, int cap,
+    int* __restrict__ send_base, int* __restrict__ limit, int* __restrict__ cursor, int* __restrict__ offsets,
+    int* __restrict__ group_sizes, int* __restrict__ tile_row0, int* __restrict__ tile_expert,
+    int* __restrict__ num_tiles, int* __restrict__ total, int slot, uint32_t epoch, int* status) {
+    __shared__ int n_all[256];      // rows for expert e from all ranks
+    __shared__ int n_before[256];   // rows for expert e from the ranks before this one
+    const int W = peers.world;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        const int c = counts[e];
+        for (int r = 0; r < W; ++r) {
+            int* tbl = reinterpret_cast<int*>(static_cast<char*>(peers.base[r]) + table_byte_off);
+            tbl[peers.rank * E + e] = c;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (!signal_and_wait(peers, slot, epoch, true, status, 41)) return;
+    const volatile int* tbl =
+        reinterpret_cast<const volatile int*>(static_cast<char*>(peers.base[peers.rank]) + table_byte_off);
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int n = 0, b = 0;
+        for (int s = 0; s < W; ++s) {
+            const int c = tbl[s * E + e];
+            if (s < peers.rank) b += c;
+            n += c;
+        }
+        n_all[e] = n;
+        n_before[e] = b;
+        cursor[e] = 0;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int tile = 0;
+        for (int o = 0; o < W; ++o) {
+            int row = 0;
+            for (int i = 0; i < El; ++i) {
+                const int e = o * El + i;
+                const int n = n_all[e];
+                int want = (n + 127) / 128;                                   // tiles the expert would like
+                if (want < 1) want = 1;
+                int room = (cap - row) / 128 - (El - 1 - i);                 // tiles left after reserving one per later expert
+                if (room < 1) room = 1;                                      // cap >= 128 * El is checked on the host
+                const int tiles = want < room ? want : room;
+                const int accepted = n < tiles * 128 ? n : tiles * 128;
+                int first = row + n_before[e];
+                send_base[e] = first;
+                limit[e] = row + accepted;
+                if (o == peers.rank) {
+                    offsets[i] = row;
+                    group_sizes[i] = accepted;
+                    for (int t = 0; t < tiles; ++t) {
+                        tile_row0[tile] = row + t * 128;
+                        tile_expert[tile] = i;
+                        ++tile;
+                    }
+                }
+                row += tiles * 128;
+            }
+            if (o == peers.rank) {
+                offsets[El] = row;
+                total[0] = row;
+                num_tiles[0] = tile;
+            }
+        }
+    }
+}
+
+// Zeroes the padding rows [offsets[i] + group_sizes[i], offsets[i + 1]) of every local expert's range in the inbox:
+// the grouped weight-gradient GEMM runs over whole ranges, so rows that no sender wrote must not hold old data.
+__global__ void __launch_bounds__(256) moe_ep_zero_padding_kernel(__nv_bfloat16* __restrict__ inbox,
+                                                                  const int* __restrict__ offsets,
+                                                                  const int* __restrict__ group_sizes, int D) {
+    const int i = blockIdx.x;
+    const int beg = offsets[i] + group_sizes[i], end = offsets[i + 1];
+    const long long nvec = static_cast<long long>(end - beg) * D / 8;
+    __nv_bfloat16* base = inbox + static_cast<size_t>(beg) * D;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    for (long long v = blockIdx.y * static_cast<long long>(blockDim.x) + threadIdx.x; v < nvec;
+         v += static_cast<long long>(gridDim.y) * blockDim.x)
+        st16(base + v * 8, zero);
+}
+
 // One warp per (token, choice): stores x[t] (* gate) into row `dest[t, j] % cap` of the inbox of rank
 // `dest[t, j] / cap`. With `assign` the destination is chosen here (send_base + arrival order) and recorded in
 // `dest`; without it the rows go where an earlier call put them (used by the backward of combine).
@@ -254,7 +349,8 @@ __global__ void __launch_bounds__(256) moe_ep_push_kernel(CommPeers peers, const
                                                           const float* __restrict__ gates,
                                                           const int* __restrict__ send_base, int* __restrict__ cursor,
                                                           long long inbox_byte_off, int* __restrict__ dest, int rows,
-                                                          int k, int D, int El, int cap, int assign) {
+                                                          int k, int D, int El, int cap, int assign,
+                                                          const int* __restrict__ limit, int* __restrict__ dropped) {
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (warp >= rows) return;
@@ -264,7 +360,10 @@ __global__ void __launch_bounds__(256) moe_ep_push_kernel(CommPeers peers, const
         if (assign) {
             const int e = expert_ids[warp];
             const int row = send_base[e] + atomicAdd(&cursor[e], 1);
-            d = row < cap ? (e / El) * cap + row : -1;          // a full inbox drops the row (combine reads zero)
+            // a row beyond the expert's range (or beyond the inbox) is dropped: nothing is stored, combine reads zero
+            const bool fits = row < cap && row >= 0 && (limit == nullptr || row < limit[e]);
+            d = fits ? (e / El) * cap + row : -1;
+            if (!fits && dropped != nullptr) atomicAdd(dropped, 1);
             dest[warp] = d;
         } else {
             d = dest[warp];
@@ -396,13 +495,24 @@ void moe_ep_layout(const CommPeers& peers, const int* counts, long long table_by
 
 void moe_ep_push(const CommPeers& peers, const void* x, const int* expert_ids, const float* gates, const int* send_base,
                  int* cursor, long long inbox_byte_off, int* dest, int T, int k, int D, int E, int cap, bool assign,
-                 cudaStream_t st) {
+                 const int* limit, int* dropped, cudaStream_t st) {
     const int rows = T * k;
     if (rows == 0) return;
     const int blocks = (rows * 32 + 255) / 256;
     moe_ep_push_kernel<<<blocks, 256, 0, st>>>(peers, static_cast<const __nv_bfloat16*>(x), expert_ids, gates, send_base,
                                                cursor, inbox_byte_off, dest, rows, k, D, E / peers.world, cap,
-                                               assign ? 1 : 0);
+                                               assign ? 1 : 0, limit, dropped);
+}
+
+void moe_ep_layout_padded(const CommPeers& peers, const int* counts, long long table_byte_off, int E, int cap,
+                          int* send_base, int* limit, int* cursor, int* offsets, int* group_sizes, int* tile_row0,
+                          int* tile_expert, int* num_tiles, int* total, void* inbox, int D, int slot, uint32_t epoch,
+                          int* status, cudaStream_t st) {
+    const int El = E / peers.world;
+    moe_ep_layout_padded_kernel<<<1, 256, 0, st>>>(peers, counts, table_byte_off, E, El, cap, send_base, limit, cursor,
+                                                   offsets, group_sizes, tile_row0, tile_expert, num_tiles, total, slot,
+                                                   epoch, status);
+    moe_ep_zero_padding_kernel<<<dim3(El, 8), 256, 0, st>>>(static_cast<__nv_bfloat16*>(inbox), offsets, group_sizes, D);
 }
 
 void moe_ep_pull(const CommPeers& peers, long long outbox_byte_off, const int* dest, const float* gates, void* y,

@@ -44,9 +44,19 @@ void moe_ep_layout(const CommPeers& peers, const int* counts, long long table_by
 // moe_ep_push: row (t, j) of x [T, D] (* gate if given) is stored into the inbox (at `inbox_byte_off`, `cap` rows of
 // D bf16) of the rank owning its expert. `assign`: positions are taken from send_base/cursor and written to
 // dest[t, j] = owner * cap + row (-1 if the inbox is full); otherwise dest is read.
+// `limit` (may be null): limit[e] = first inbox row of expert e's range that takes no row (rows at or beyond it are
+// dropped); `dropped` (may be null): device counter of dropped rows.
 void moe_ep_push(const CommPeers& peers, const void* x, const int* expert_ids, const float* gates, const int* send_base,
                  int* cursor, long long inbox_byte_off, int* dest, int T, int k, int D, int E, int cap, bool assign,
-                 cudaStream_t st);
+                 const int* limit, int* dropped, cudaStream_t st);
+
+// Count exchange + inbox layout in the 128-row padded form of the single-launch grouped GEMM (per local expert a
+// range that starts and ends on a tile boundary), with the tile tables of this rank's inbox, and zeroing of the
+// padding rows of `inbox`. `cap`: rows per inbox, a multiple of 128 and at least 128 per local expert.
+void moe_ep_layout_padded(const CommPeers& peers, const int* counts, long long table_byte_off, int E, int cap,
+                          int* send_base, int* limit, int* cursor, int* offsets, int* group_sizes, int* tile_row0,
+                          int* tile_expert, int* num_tiles, int* total, void* inbox, int D, int slot, uint32_t epoch,
+                          int* status, cudaStream_t st);
 
 // moe_ep_pull: y[t] (+)= sum_j gate[t, j] * outbox row dest[t, j] (peer loads); optionally dgate[t, j] = <row, x[t]>.
 void moe_ep_pull(const CommPeers& peers, long long outbox_byte_off, const int* dest, const float* gates, void* y,

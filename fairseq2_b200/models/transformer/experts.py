@@ -197,8 +197,14 @@ class MoE(FeedForwardNetwork):
                 raise RuntimeError("Expert parallelism needs the CUDA routing kernels (bf16 activations on a GPU).")
             ids, gates, counts = moe_ops.moe_route(logits, self.top_k, self.softmax_gate)
             self._note_aux_loss(logits, counts)
-            rows, dest, group_sizes = self.ep.dispatch(x, ids, counts, gates=gates)
-            rows_out = self.experts(rows, group_sizes.tolist())
+            if isinstance(self.experts, GroupedExpertNetwork) and self.experts.supports_padded_layout(x):
+                # tile-aligned inbox + device-resident tile tables: three single-launch grouped GEMMs, and the
+                # host never waits for the routing result
+                rows, dest, layout, _ = self.ep.dispatch_padded(x, ids, counts, gates=gates)
+                rows_out = self.experts.forward_padded(rows, layout)
+            else:
+                rows, dest, group_sizes = self.ep.dispatch(x, ids, counts, gates=gates)
+                rows_out = self.experts(rows, group_sizes.tolist())
             base = self.shared_expert(x) if self.shared_expert is not None else None
             return self.ep.combine(rows_out, dest, x.shape[0], base=base).view(seqs.shape)
         if moe_ops.moe_kernels_available(x, logits):

@@ -118,6 +118,84 @@ class _Pull(torch.autograd.Function):
         return None, d_rows, None, dgates, (dy if ctx.has_base else None), None
 
 
+class _PushPadded(torch.autograd.Function):
+    """Dispatch into the 128-row padded inbox layout of the single-launch grouped GEMM. Nothing returns to the host:
+    the received rows are handed on as a capacity-sized buffer together with device-resident tile tables."""
+
+    @staticmethod
+    def forward(ctx, ep: "ExpertParallelExchange", x: Tensor, gates: Tensor | None, expert_ids: Tensor,  # type: ignore[override]
+                counts: Tensor):
+        a = ep.arena
+        (send_base, limit, cursor, offsets, group_sizes, tile_row0, tile_expert, num_tiles, total) = \
+            a.ext.moe_ep_layout_padded(a.peer_ptrs, a.rank, counts, ep.table_off, ep.inbox_off, ep.capacity,
+                                       ep.model_dim, ep.SLOT, ep.next_epoch(), a.wait_limit_s)
+        dest = torch.empty_like(expert_ids)
+        a.ext.moe_ep_push(a.peer_ptrs, a.rank, x, expert_ids, gates, send_base, cursor, ep.inbox_off, dest,
+                          ep.num_experts, ep.capacity, limit, ep.dropped)
+        a.barrier(ep.SLOT, ep.next_epoch())                     # every rank's rows have landed in my inbox
+        rows = ep.inbox.clone()                                  # the inbox is reused by the next exchange
+        ctx.ep, ctx.has_gates = ep, gates is not None
+        ctx.save_for_backward(x, gates if gates is not None else x.new_empty(0), dest)
+        ctx.mark_non_differentiable(dest, offsets, group_sizes, tile_row0, tile_expert, num_tiles, total)
+        return rows, dest, offsets, group_sizes, tile_row0, tile_expert, num_tiles, total
+
+    @staticmethod
+    def backward(ctx, d_rows: Tensor, *_: Tensor):  # type: ignore[override]
+        ep: ExpertParallelExchange = ctx.ep
+        a = ep.arena
+        x, gates, dest = ctx.saved_tensors
+        ep.outbox.copy_(d_rows)
+        a.barrier(ep.SLOT, ep.next_epoch())                     # every owner has published its row gradients
+        dx = torch.empty_like(x)
+        if ctx.has_gates:
+            dgates = torch.empty(dest.shape, device=x.device, dtype=torch.float32)
+            a.ext.moe_ep_pull(a.peer_ptrs, a.rank, ep.outbox_off, dest, gates, dx, x, dgates, ep.capacity, False)
+        else:
+            dgates = None
+            a.ext.moe_ep_pull(a.peer_ptrs, a.rank, ep.outbox_off, dest, None, dx, None, None, ep.capacity, False)
+        a.barrier(ep.SLOT, ep.next_epoch())                     # outboxes may be overwritten again
+        return None, dx, dgates, None, None
+
+
+class _PullPadded(torch.autograd.Function):
+    """Combine from capacity-sized outboxes (the counterpart of ``_PushPadded``)."""
+
+    @staticmethod
+    def forward(ctx, ep: "ExpertParallelExchange", rows: Tensor, dest: Tensor, gates: Tensor | None,  # type: ignore[override]
+                base: Tensor | None, num_tokens: int) -> Tensor:
+        a = ep.arena
+        ep.outbox.copy_(rows)
+        a.barrier(ep.SLOT, ep.next_epoch())                     # every owner has published its expert outputs
+        y = base.clone() if base is not None else torch.empty((num_tokens, rows.shape[1]), device=rows.device,
+                                                              dtype=rows.dtype)
+        a.ext.moe_ep_pull(a.peer_ptrs, a.rank, ep.outbox_off, dest, gates, y, None, None, ep.capacity, base is not None)
+        a.barrier(ep.SLOT, ep.next_epoch())                     # outboxes may be overwritten again
+        ctx.ep, ctx.has_gates, ctx.has_base = ep, gates is not None, base is not None
+        ctx.save_for_backward(dest, gates if gates is not None else rows.new_empty(0), rows)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):  # type: ignore[override]
+        ep: ExpertParallelExchange = ctx.ep
+        a = ep.arena
+        dest, gates, rows = ctx.saved_tensors
+        dy = dy.contiguous()
+        dgates = None
+        if ctx.has_gates:
+            ep.outbox.copy_(rows)
+            a.barrier(ep.SLOT, ep.next_epoch())
+            dgates = torch.empty(dest.shape, device=dy.device, dtype=torch.float32)
+            scratch = torch.empty_like(dy)
+            a.ext.moe_ep_pull(a.peer_ptrs, a.rank, ep.outbox_off, dest, None, scratch, dy, dgates, ep.capacity, False)
+            a.barrier(ep.SLOT, ep.next_epoch())
+        # d rows: the output gradient travels to the rows the tokens were sent to (dropped rows go nowhere)
+        a.ext.moe_ep_push(a.peer_ptrs, a.rank, dy, None, gates if ctx.has_gates else None, None, None, ep.inbox_off,
+                          dest, ep.num_experts, ep.capacity)
+        a.barrier(ep.SLOT, ep.next_epoch())
+        d_rows = ep.inbox.clone()
+        return None, d_rows, None, dgates, (dy if ctx.has_base else None), None
+
+
 class ExpertParallelExchange:
     """Buffers and epoch bookkeeping of one expert-parallel group; shared by all MoE layers of a model.
 
@@ -136,7 +214,11 @@ class ExpertParallelExchange:
             raise ValueError("`model_dim` must be a multiple of 8.")
         self.arena, self.num_experts, self.model_dim = arena, num_experts, model_dim
         self.num_local_experts = num_experts // W
-        self.capacity = capacity if capacity is not None else W * max_tokens * top_k
+        cap = capacity if capacity is not None else W * max_tokens * top_k
+        # whole 128-row tiles, and room for the padding of the tile-aligned per-expert ranges
+        self.capacity = max((cap + 127) // 128 * 128 + 128 * self.num_local_experts, 128 * self.num_local_experts)
+        #: rows that did not fit into an inbox since creation (device counter; 0 unless ``capacity`` was set too low)
+        self.dropped = torch.zeros(1, dtype=torch.int32, device=arena.device)
         self.table_off, _ = arena.alloc(4 * W * num_experts, align=16)
         self.inbox_off, inbox = arena.alloc(self.capacity * model_dim * 2, align=16)
         self.outbox_off, outbox = arena.alloc(self.capacity * model_dim * 2, align=16)
@@ -163,4 +245,17 @@ class ExpertParallelExchange:
                 base: Tensor | None = None) -> Tensor:
         """``y[t] = base[t] + sum_j gate[t, j] * rows_of_owner[dest[t, j]]`` (gate = 1 if not given)."""
         g = gates.float().contiguous() if gates is not None else None
+        if rows.shape[0] == self.capacity:
+            return _PullPadded.apply(self, rows.contiguous(), dest, g, base, num_tokens)
         return _Pull.apply(self, rows.contiguous(), dest, g, base, num_tokens)
+
+    def dispatch_padded(self, x: Tensor, expert_ids: Tensor, counts: Tensor, gates: Tensor | None = None
+                        ) -> tuple[Tensor, Tensor, tuple[Tensor, Tensor, Tensor, Tensor], Tensor]:
+        """Like :meth:`dispatch`, but the received rows come as the whole ``[capacity, D]`` inbox in the 128-row
+        padded layout of the single-launch grouped GEMM, with its device-resident tables: returns
+        ``(rows, dest, (offsets, tile_row0, tile_expert, num_tiles), group_sizes)``. The host never waits for the
+        routing result. Rows that do not fit into an inbox are dropped and counted in ``self.dropped``."""
+        g = gates.float().contiguous() if gates is not None else None
+        rows, dest, offsets, group_sizes, tile_row0, tile_expert, num_tiles, _ = _PushPadded.apply(
+            self, x.contiguous(), g, expert_ids.contiguous(), counts.contiguous())
+        return rows, dest, (offsets, tile_row0, tile_expert, num_tiles), group_sizes

@@ -130,6 +130,8 @@ class FlatParamUnit:
         self.norm_slot: Tensor | None = None
         self.norm_fused = False     # ``norm_slot`` holds the norm of the current ``grad_shard``
         self.replicated = False     # gradients are averaged over a replica gang after the (trivial) reduction
+        self.local_only = False     # rank-local parameters (expert-parallel experts): no reduction at all
+        self.local_grad_scale: Tensor | None = None
         #: hyper-parameters and moment buffers of an optimizer step that the reduce-scatter applies itself
         #: (set per step by the optimizer's ``prepare_fused_step``; ``None`` = reduce only)
         self.fused_step: dict[str, Any] | None = None
@@ -338,6 +340,10 @@ class FlatParamUnit:
         if W == 1:
             self.grad_shard = self.grad_full
             self.grads_ready = True
+            if self.local_only and self.local_grad_scale is not None:
+                from fairseq2_b200.ops.optim import multi_tensor_scale
+
+                multi_tensor_scale([self.grad_full], self.local_grad_scale)
             if getattr(self, "replica_arena", None) is not None:
                 self._allreduce_replicas(comm_stream, average)
                 self.replicas_reduced = True
@@ -528,7 +534,14 @@ class FSDP(Module):
                  param_dtype: DataType = torch.bfloat16, fp32_reduce: bool = True,
                  reshard_after_forward: bool = True, overlap: bool = True, comm: str = "auto",
                  allgather: str = "copy", reducescatter: str = "copy", rs_blocks: int = 48,
-                 wait_limit_s: float | None = None, cpu_offload: bool = False) -> None:
+                 wait_limit_s: float | None = None, cpu_offload: bool = False,
+                 local_module_filter: Callable[[Module], bool] | None = None) -> None:
+        """``local_module_filter``: sub-modules for which it returns True keep their parameters LOCAL to the rank
+        (not sharded, not reduced over the data-parallel gang): the experts of an expert-parallel mixture-of-experts
+        layer, which differ from rank to rank and whose gradients already cover every rank's tokens. Each such
+        module becomes a flat unit of its own (bf16 compute copy, fp32 master, fused optimizer launch); its
+        gradients are divided by the data-parallel size so that the step's common normalisation factor
+        (``dp.size / num_targets``) applies to them as to the averaged gradients of the shared parameters."""
         super().__init__()
         self.module = module
         self.gangs = gangs
@@ -567,20 +580,33 @@ class FSDP(Module):
                     out.append((f"{mod_name}.{attr}" if mod_name else attr, holders_of(p), p))
             return out
 
-        def make_unit(name: str, m: Module, reshard: bool) -> FlatParamUnit | None:
+        def make_unit(name: str, m: Module, reshard: bool, local: bool = False) -> FlatParamUnit | None:
             _materialize(m, target_device, memo)
             nps = collect(m, name)
             if not nps:
                 return None
-            u = FlatParamUnit(name, m, nps, self.gang, param_dtype=param_dtype, reduce_dtype=reduce_dtype,
+            from fairseq2_b200.gang import FakeGang
+
+            gang = FakeGang(target_device) if local else self.gang
+            u = FlatParamUnit(name, m, nps, gang, param_dtype=param_dtype, reduce_dtype=reduce_dtype,
                               reshard_after_forward=reshard, cpu_offload=cpu_offload)
+            u.local_only = local
             owned.update(id(cp) for cp in u.compute_params)
             return u
 
         names = {id(m): n for n, m in module.named_modules()}
         last = len(unit_modules) - 1
         target_device = gangs.root.device
+        self.local_units: list[FlatParamUnit] = []
         for i, um in enumerate(unit_modules):
+            if local_module_filter is not None:
+                # rank-local sub-modules first: what remains of the layer forms the sharded unit
+                for sub in um.modules():
+                    if sub is not um and local_module_filter(sub):
+                        lu = make_unit(names[id(sub)], sub, False, local=True)
+                        if lu is not None:
+                            self.units.append(lu)
+                            self.local_units.append(lu)
             u = make_unit(names[id(um)], um, reshard_after_forward and i != last)
             if u is not None:
                 self.units.append(u)
@@ -603,7 +629,8 @@ class FSDP(Module):
             from fairseq2_b200.parallel.symm import SymmetricArena, symmetric_memory_available
 
             if symmetric_memory_available(self.gang):
-                need = sum((1 + W) * u.shard_size * 2 + 1024 for u in self.all_units) + (1 << 20)
+                sharded = [u for u in self.all_units if u.world > 1]        # rank-local units stay out of the arena
+                need = sum((1 + W) * u.shard_size * 2 + 1024 for u in sharded) + (1 << 20)
                 if wait_limit_s is None:
                     # training: ranks may legitimately drift apart by a data-loader stall or a checkpoint write
                     wait_limit_s = float(os.environ.get("FAIRSEQ2_B200_WAIT_LIMIT_S", "120"))
@@ -612,7 +639,7 @@ class FSDP(Module):
                     engine = os.environ.get("FAIRSEQ2_B200_FSDP_ALLGATHER", allgather)
                     if engine not in ("copy", "kernel"):
                         raise ValueError(f"`allgather` must be 'copy' or 'kernel', but is '{engine}' instead.")
-                    for i, u in enumerate(self.all_units):
+                    for i, u in enumerate(sharded):
                         u.attach_arena(self.arena, i)
                         u.allgather_engine = engine
                         u.rs_blocks = int(os.environ.get("FAIRSEQ2_B200_FSDP_RS_BLOCKS", rs_blocks))
@@ -620,15 +647,15 @@ class FSDP(Module):
                     if rs_engine not in ("copy", "kernel"):
                         raise ValueError(f"`reducescatter` must be 'copy' or 'kernel', but is '{rs_engine}' instead.")
                     local_blocks = int(os.environ.get("FAIRSEQ2_B200_FSDP_RS_LOCAL_BLOCKS", "192"))
-                    self._norm_slots = torch.zeros(len(self.all_units), device=dev, dtype=torch.float32)
-                    for i, u in enumerate(self.all_units):
+                    self._norm_slots = torch.zeros(len(sharded), device=dev, dtype=torch.float32)
+                    for i, u in enumerate(sharded):
                         u.reducescatter_engine = rs_engine
                         u.rs_local_blocks = local_blocks
                         u.norm_slot = self._norm_slots[i]
                     if rs_engine == "copy":
-                        biggest = max(u.shard_size for u in self.all_units)
+                        biggest = max(u.shard_size for u in sharded)
                         staging = torch.empty((W - 1) * biggest, device=dev, dtype=torch.bfloat16)
-                        for u in self.all_units:
+                        for u in sharded:
                             u.rs_staging = staging
                     torch.cuda.synchronize(dev)
                     self.gang.barrier()
@@ -639,8 +666,12 @@ class FSDP(Module):
                     self.arena = None
             elif comm == "symm":
                 raise RuntimeError("Symmetric-memory communication was requested but is not available.")
+        if self.local_units and gangs.dp.size > 1:
+            inv = torch.tensor(1.0 / gangs.dp.size, device=dev, dtype=torch.float32)
+            for u in self.local_units:
+                u.local_grad_scale = inv
         for u in self.all_units:
-            u.replicated = self.replica_gang is not None
+            u.replicated = self.replica_gang is not None and not u.local_only
             # (offset, length) in the unit's shard buffers of the parameters that are replicated over the tp gang
             u.tp_replicated = [(sp.shard_off, sp.rows_local * sp.row) for sp in u.specs
                                if sp.fqn not in tp_sharded and sp.requires_grad] if self.tp_gang is not None else []
@@ -695,9 +726,19 @@ class FSDP(Module):
             u.wait_unshard()
             if torch.is_grad_enabled():
                 u.prepare_grads()
-            if idx + 1 < len(self.units):           # prefetch the next layer
-                self.units[idx + 1].unshard(self.comm_stream, self.param_epoch)
+            nxt = self._neighbour(idx, +1)           # prefetch the next sharded unit
+            if nxt is not None:
+                nxt.unshard(self.comm_stream, self.param_epoch)
         return hook
+
+    def _neighbour(self, idx: int, step: int) -> "FlatParamUnit | None":
+        """The closest unit after (``step = 1``) or before (``-1``) ``idx`` that has something to all-gather."""
+        i = idx + step
+        while 0 <= i < len(self.units):
+            if self.units[i].world > 1:
+                return self.units[i]
+            i += step
+        return None
 
     def _make_post_forward(self, idx: int):  # type: ignore[no-untyped-def]
         def hook(m: Module, args: Any, out: Any) -> None:
@@ -714,8 +755,9 @@ class FSDP(Module):
             u.unshard(self.comm_stream, self.param_epoch)
             u.wait_unshard()
             u.prepare_grads()
-            if idx - 1 >= 0:
-                self.units[idx - 1].unshard(self.comm_stream, self.param_epoch)
+            prv = self._neighbour(idx, -1)
+            if prv is not None:
+                prv.unshard(self.comm_stream, self.param_epoch)
         return hook
 
     def _make_post_backward(self, idx: int):  # type: ignore[no-untyped-def]
@@ -768,7 +810,7 @@ class FSDP(Module):
             torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
         if self.replica_gang is not None and self._require_sync:
             for u in self.all_units:
-                if u.grad_shard is not None and not getattr(u, "replicas_reduced", False):
+                if u.grad_shard is not None and not getattr(u, "replicas_reduced", False) and not u.local_only:
                     self.replica_gang.all_reduce(u.grad_shard, ReduceOperation.MEAN)
 
     @property

@@ -730,7 +730,9 @@ def test_flat_unit_ddp_symmetric_allreduce_matches_nccl(world: int) -> None:
     for (ra, ma), (rb, mb) in zip(a, b):
         for (la, ga), (lb, gb) in zip(ra, rb):
             assert abs(la - lb) / abs(lb) < 1e-3 and abs(ga - gb) / abs(gb) < 2e-2
-        assert _rel(torch.from_numpy(ma), torch.from_numpy(mb)) < 1e-4
+        # the in-place kernel sums in fp32 and rounds once to bf16, NCCL reduces in bf16: single weights may end a
+        # step on the other side of an Adam sign decision
+        assert _rel(torch.from_numpy(ma), torch.from_numpy(mb)) < 2e-3
     assert _rel(torch.from_numpy(a[0][1]), torch.from_numpy(a[-1][1])) == 0.0     # replicas stay identical
 
 
