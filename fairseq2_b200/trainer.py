@@ -111,8 +111,10 @@ class TrainStep:
         assert total_loss is not None
         # ---- normalise: gradients hold the data-parallel MEAN of per-rank sums
         dp = self.gangs.dp
-        if fused:
-            pass        # the normalisation factor went into the fused reduce-scatter + update kernels
+        if fused is not None:
+            # the factor already went into the fused reduce-scatter + update kernels; units that were not armed
+            # (rank-local ones, units outside a symmetric arena) get it through the regular optimizer launch
+            model.scale_grads(fused)
         elif total_targets is not None:
             t = total_targets if isinstance(total_targets, Tensor) else \
                 torch.tensor(float(total_targets), device=total_loss.device)
@@ -148,14 +150,15 @@ class TrainStep:
         return total_loss, grad_norm
 
 
-def _arm_fused(self: TrainStep, model: Any, batches: Sequence[Any]) -> bool:
+def _arm_fused(self: TrainStep, model: Any, batches: Sequence[Any]) -> Tensor | None:
+    """Returns the loss-normalisation factor (a device scalar) if the optimizer was armed, else ``None``."""
     count = getattr(self.unit, "count_targets", None)
     inner = getattr(model, "module", None)
     prepare = getattr(self.optimizer, "prepare_fused_step", None)
     if (not self.fuse_optimizer or count is None or prepare is None or len(batches) != 1
             or self.max_grad_norm is not None or self.loss_scaler is not None
             or not getattr(inner, "supports_fused_optimizer", False)):
-        return False
+        return None
     t = count(batches[0])
     dev = self.gangs.root.device
     t = t.to(device=dev, dtype=torch.float32) if isinstance(t, Tensor) else torch.tensor(float(t), device=dev)
@@ -163,7 +166,8 @@ def _arm_fused(self: TrainStep, model: Any, batches: Sequence[Any]) -> bool:
     if dp.size > 1:
         t = t.clone()
         dp.all_reduce(t, ReduceOperation.SUM)
-    return prepare(dp.size / t.clamp(min=1.0)) > 0
+    scale = dp.size / t.clamp(min=1.0)
+    return scale if prepare(scale) > 0 else None
 
 
 TrainStep._maybe_arm_fused_optimizer = _arm_fused  # type: ignore[attr-defined]
