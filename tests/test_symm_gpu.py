@@ -794,3 +794,54 @@ def test_tensor_parallel_llama_matches_fp32_single_rank(world: int, fused: bool)
         assert used_fused == fused
         assert abs(loss - ref_loss) / abs(ref_loss) < 5e-3
         assert worst < 5e-2, (name, worst)
+
+
+def _moe_ep_overflow_worker(rank: int, world: int):
+    """An inbox that is too small: the layout cuts the expert ranges, the push kernel drops what does not fit and
+    counts it -- nothing is written out of range, the status word stays clear, the step still runs both ways."""
+    from fairseq2_b200.gang import ProcessGroupGang, ReduceOperation
+    from fairseq2_b200.models.transformer.experts import MoE
+    from fairseq2_b200.ops.moe_ep import ExpertParallelExchange
+    from fairseq2_b200.parallel.symm import SymmetricArena
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    base = ProcessGroupGang.create_default_process_group(dev)
+    D, F, E, K, T = 256, 512, 8, 2, 640
+    El = E // world
+    arena = SymmetricArena(base, (4 * world + 8) << 20, wait_limit_s=20.0)
+    ep = ExpertParallelExchange(arena, E, D, max_tokens=T, top_k=K, capacity=0)      # one 128-row tile per expert
+    assert ep.capacity == 128 * El
+    torch.manual_seed(1)
+    moe = MoE(D, F, False, E, 1.0, K, inner_dim_scale=1.0, ep=ep, softmax_gate=True, aux_loss=True,
+              router_init_std=0.02).to(dev, torch.bfloat16)
+    with torch.no_grad():                                       # every rank routes with the same router
+        moe.router.copy_(torch.randn(D, E, generator=torch.Generator().manual_seed(5)).mul_(0.02))
+    x = torch.randn(T, D, generator=torch.Generator().manual_seed(50 + rank)).to(dev, torch.bfloat16)
+    x.requires_grad_(True)
+    moe.train()
+    y = moe(x)
+    (y.float().pow(2).sum() + moe.last_aux_loss).backward()
+    # expected number of dropped rows, from the global routing counts
+    logits = (x.detach().float() @ moe.router.detach().float())
+    ids = torch.topk(logits, K, dim=1).indices.reshape(-1)
+    counts = torch.bincount(ids, minlength=E).float()
+    base.all_reduce(counts, ReduceOperation.SUM)
+    expected = int(sum(max(int(c) - 128, 0) for c in counts.tolist()))
+    dropped = ep.dropped.clone().float()
+    base.all_reduce(dropped, ReduceOperation.SUM)
+    torch.cuda.synchronize()
+    arena.ext.check_status()
+    out = (int(dropped), expected, bool(torch.isfinite(y).all()), bool(torch.isfinite(x.grad).all()),
+           float(moe.last_aux_loss))
+    base.close()
+    return out
+
+
+@pytest.mark.parametrize("world", WORLDS)
+def test_moe_expert_parallel_overflow_is_dropped_and_counted(world: int) -> None:
+    _need_gpus(world)
+    for dropped, expected, y_ok, dx_ok, aux in run_distributed(_moe_ep_overflow_worker, world):
+        assert expected > 0 and abs(dropped - expected) <= 4      # bf16 router logits may flip a near-tie
+        assert y_ok and dx_ok and 0.9 < aux < 2.0
