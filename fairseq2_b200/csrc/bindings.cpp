@@ -1192,6 +1192,39 @@ void comm_allgather_copy(const std::vector<int64_t>& ptrs, int64_t rank, const s
     }
 }
 
+// Vocabulary-parallel lookup whose rows go straight to the ranks that own the tokens (no reduce-scatter).
+void embed_push(const std::vector<int64_t>& ptrs, int64_t rank, const Tensor& ids, const Tensor& table, int64_t lo,
+                int64_t out_byte_off, int64_t rows_per_rank, double wait_limit_s) {
+    TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous() && table.is_cuda() &&
+                    is_bf16(table) && table.dim() == 2 && table.is_contiguous() && table.size(1) % 8 == 0 &&
+                    aligned16(table),
+                "embed_push: ids must be int64, the table shard a contiguous bf16 [rows, D] with D % 8 == 0");
+    TORCH_CHECK(out_byte_off % 16 == 0 && rows_per_rank > 0 &&
+                    ids.numel() == rows_per_rank * static_cast<int64_t>(ptrs.size()),
+                "embed_push: the tokens must split evenly over the ranks and the output offset be 16-byte aligned");
+    c10::cuda::CUDAGuard guard(table.device());
+    fs2::embed_push(make_peers(ptrs, rank, wait_limit_s), reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()),
+                    table.data_ptr(), lo, table.size(0), out_byte_off, ids.numel(), static_cast<int>(table.size(1)),
+                    rows_per_rank, stream_of(table));
+    g_launches += 1;
+}
+
+Tensor embed_pull_bwd(const std::vector<int64_t>& ptrs, int64_t rank, const Tensor& ids, int64_t dout_byte_off,
+                      int64_t rows, int64_t D, int64_t lo, int64_t rows_per_rank, double wait_limit_s) {
+    TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous(), "embed_pull_bwd: bad ids");
+    TORCH_CHECK(dout_byte_off % 16 == 0 && D % 8 == 0 && rows_per_rank > 0 &&
+                    ids.numel() == rows_per_rank * static_cast<int64_t>(ptrs.size()),
+                "embed_pull_bwd: bad layout");
+    c10::cuda::CUDAGuard guard(ids.device());
+    Tensor dtable = at::zeros({rows, D}, ids.options().dtype(at::kFloat));
+    fs2::embed_pull_bwd(make_peers(ptrs, rank, wait_limit_s),
+                        reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()), dout_byte_off,
+                        dtable.data_ptr<float>(), lo, rows, ids.numel(), static_cast<int>(D), rows_per_rank,
+                        stream_of(ids));
+    g_launches += 1;
+    return dtable;
+}
+
 // Device scalar that receives a sum of squares, or null.
 float* norm_out_ptr(const std::optional<Tensor>& norm_out, const Tensor& like) {
     if (!norm_out.has_value()) return nullptr;
@@ -1424,6 +1457,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("comm_allreduce_inplace", &comm_allreduce_inplace);
     m.def("comm_allreduce_multimem", &comm_allreduce_multimem);
     m.def("comm_pull", &comm_pull);
+    m.def("embed_push", &embed_push);
+    m.def("embed_pull_bwd", &embed_pull_bwd);
     m.def("comm_alltoall", &comm_alltoall);
     m.def("moe_route", &moe_route);
     m.def("moe_dispatch", &moe_dispatch);

@@ -539,6 +539,54 @@ __global__ void alltoall_kernel(CommPeers peers, long long byte_off, char* __res
     }
 }
 
+
+// ------------------------------------------------ vocabulary-parallel embedding, token-sharded result
+// This rank holds rows [lo, lo + rows) of the table. Token t's embedding belongs to rank t / rows_per_rank of the
+// tensor-parallel group (sequence-parallel residual stream), so the rank that owns the row writes it straight into
+// that rank's output buffer over NVLink: every output row has exactly one writer and no reduction is needed. One
+// warp per token. The caller separates the launch from the consumer with a barrier.
+__global__ void __launch_bounds__(256) embed_push_kernel(CommPeers peers, const long long* __restrict__ ids,
+                                                         const __nv_bfloat16* __restrict__ table, long long lo,
+                                                         long long rows, long long out_byte_off, long long tokens,
+                                                         int D, long long rows_per_rank) {
+    const long long t = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (t >= tokens) return;
+    const long long r = ids[t] - lo;
+    if (r < 0 || r >= rows) return;
+    const int owner = static_cast<int>(t / rows_per_rank);
+    char* dst = static_cast<char*>(peers.base[owner]) + out_byte_off + (t - owner * rows_per_rank) * D * 2;
+    const char* src = reinterpret_cast<const char*>(table + r * D);
+    for (int c = lane * 16; c < D * 2; c += 512) st16(dst + c, *reinterpret_cast<const uint4*>(src + c));
+}
+
+// Backward of the above: every rank staged its token shard of d(out) at `dout_byte_off` of its arena; the rank
+// that owns the row of token t reads that token's gradient from rank t / rows_per_rank and adds it to its fp32
+// table gradient (atomics: tokens repeat).
+__global__ void __launch_bounds__(256) embed_pull_bwd_kernel(CommPeers peers, const long long* __restrict__ ids,
+                                                             long long dout_byte_off, float* __restrict__ dtable,
+                                                             long long lo, long long rows, long long tokens, int D,
+                                                             long long rows_per_rank) {
+    const long long t = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (t >= tokens) return;
+    const long long r = ids[t] - lo;
+    if (r < 0 || r >= rows) return;
+    const int owner = static_cast<int>(t / rows_per_rank);
+    const char* src = static_cast<const char*>(peers.base[owner]) + dout_byte_off + (t - owner * rows_per_rank) * D * 2;
+    float* dst = dtable + r * D;
+    for (int c = lane * 8; c < D; c += 256) {
+        const uint4 v = ld_peer16(src + c * 2);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h[e]);
+            atomicAdd(dst + c + 2 * e, f.x);
+            atomicAdd(dst + c + 2 * e + 1, f.y);
+        }
+    }
+}
+
 }  // namespace
 
 void comm_barrier(const CommPeers& peers, int slot, uint32_t epoch, int* status, cudaStream_t st) {
@@ -577,6 +625,22 @@ void comm_reducescatter_segments(const CommPeers& peers, const CommSegments& seg
 void comm_allreduce_f32(const CommPeers& peers, long long byte_off, float* out, long long numel, int op, int slot,
                         uint32_t epoch, int blocks, int* status, cudaStream_t st) {
     allreduce_f32_kernel<<<blocks, 256, 0, st>>>(peers, byte_off, out, numel, op, slot, epoch, status);
+}
+
+void embed_push(const CommPeers& peers, const long long* ids, const void* table, long long lo, long long rows,
+                long long out_byte_off, long long tokens, int D, long long rows_per_rank, cudaStream_t st) {
+    if (tokens == 0) return;
+    const unsigned blocks = static_cast<unsigned>((tokens * 32 + 255) / 256);
+    embed_push_kernel<<<blocks, 256, 0, st>>>(peers, ids, static_cast<const __nv_bfloat16*>(table), lo, rows,
+                                              out_byte_off, tokens, D, rows_per_rank);
+}
+
+void embed_pull_bwd(const CommPeers& peers, const long long* ids, long long dout_byte_off, float* dtable, long long lo,
+                    long long rows, long long tokens, int D, long long rows_per_rank, cudaStream_t st) {
+    if (tokens == 0) return;
+    const unsigned blocks = static_cast<unsigned>((tokens * 32 + 255) / 256);
+    embed_pull_bwd_kernel<<<blocks, 256, 0, st>>>(peers, ids, dout_byte_off, dtable, lo, rows, tokens, D,
+                                                  rows_per_rank);
 }
 
 void comm_pull(const CommPeers& peers, int src_rank, long long byte_off, void* dst, long long bytes, int slot,

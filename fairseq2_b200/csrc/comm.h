@@ -56,6 +56,13 @@ void comm_pull(const CommPeers& peers, int src_rank, long long byte_off, void* d
 void comm_alltoall(const CommPeers& peers, long long byte_off, void* dst, const long long* send_offs, int elem_bytes,
                    int slot, uint32_t epoch, int blocks, int* status, cudaStream_t st);
 
+// Vocabulary-parallel embedding with a token-sharded result: the owner of a row pushes it into the output buffer of
+// the rank that owns the token (forward), and pulls that token's gradient from it (backward).
+void embed_push(const CommPeers& peers, const long long* ids, const void* table, long long lo, long long rows,
+                long long out_byte_off, long long tokens, int D, long long rows_per_rank, cudaStream_t st);
+void embed_pull_bwd(const CommPeers& peers, const long long* ids, long long dout_byte_off, float* dtable, long long lo,
+                    long long rows, long long tokens, int D, long long rows_per_rank, cudaStream_t st);
+
 // Reduce-scatter of bf16 gradients fused with the AdamW step of the local fp32 shard (`p`, `m`, `v`: shard-sized
 // fp32; `low`: optional bf16 copy of the updated parameters). `step` is the 1-based step count; `scale_ptr` (may be
 // null) is a device scalar multiplied into `scale`.

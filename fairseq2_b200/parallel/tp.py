@@ -95,6 +95,27 @@ class TPContext:
         return ops or None
 
 
+    def embedding(self, rows: int, dim: int) -> Any | None:
+        """The row-push operator of the vocabulary-parallel embedding for ``rows`` tokens per rank."""
+        if rows <= 0 or dim % 8:
+            return None
+        key = (-rows, dim)
+        op = self._ops.get(key)
+        if op is None:
+            arena = self._ensure_arena()
+            if arena is None:
+                return None
+            from fairseq2_b200.ops.embedding import EmbeddingPush
+
+            try:
+                op = EmbeddingPush(arena, rows, dim)
+            except MemoryError:
+                self._ops[key] = False
+                return None
+            self._ops[key] = op
+        return op or None
+
+
 _contexts: dict[int, TPContext] = {}
 
 

@@ -455,6 +455,56 @@ def test_sequence_parallel_mlp_from_fused_kernels(world: int) -> None:
         assert all(e < 3e-2 for e in errs), errs
 
 
+def _embed_push_worker(rank: int, world: int):
+    """Vocabulary-parallel embedding whose rows are pushed to the token owners, against the plain lookup in fp32:
+    this rank's tokens of the output and this rank's rows of the table gradient, over two calls (buffer turns)."""
+    from fairseq2_b200.gang import ProcessGroupGang
+    from fairseq2_b200.ops.embedding import embed_vocab_parallel_scatter
+    from fairseq2_b200.ops import require_ext
+    from fairseq2_b200.parallel.tp import get_tp_context
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    os.environ["FAIRSEQ2_B200_TP_ARENA_MB"] = "64"
+    os.environ["FAIRSEQ2_B200_WAIT_LIMIT_S"] = "20"
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    base = ProcessGroupGang.create_default_process_group(dev)
+    V, D, Tl = 1024, 256, 96
+    rows = V // world
+    gen = torch.Generator().manual_seed(5)
+    table = torch.randn(V, D, generator=gen).to(dev, torch.bfloat16)
+    shard = table[rank * rows:(rank + 1) * rows].clone().requires_grad_(True)
+    errs = []
+    for call in range(3):
+        g = torch.Generator().manual_seed(30 + call)
+        ids = torch.randint(0, V, (world * Tl,), generator=g).to(dev)
+        ids[::7] = ids[0]                                            # repeated tokens: the backward accumulates
+        dout = torch.randn(world * Tl, D, generator=g).to(dev, torch.bfloat16)
+        shard.grad = None
+        y = embed_vocab_parallel_scatter(ids, shard, rank * rows, base)
+        sl = slice(rank * Tl, (rank + 1) * Tl)
+        y.backward(dout[sl])
+        tr = table.float().requires_grad_(True)
+        yr = torch.nn.functional.embedding(ids, tr)
+        yr.backward(dout.float())
+        errs.append(float((y.float() - yr[sl]).abs().max()))
+        want = tr.grad[rank * rows:(rank + 1) * rows]
+        errs.append(float((shard.grad.float() - want).norm() / want.norm()))
+    used = get_tp_context(base).arena is not None
+    torch.cuda.synchronize()
+    require_ext().check_status()
+    base.close()
+    return errs, used
+
+
+@pytest.mark.parametrize("world", WORLDS)
+def test_vocab_parallel_embedding_push_matches_lookup(world: int) -> None:
+    _need_gpus(world)
+    for errs, used in run_distributed(_embed_push_worker, world):
+        assert used
+        assert all(e < 1e-2 for e in errs), errs
+
+
 # ------------------------------------------------------------------ whole-model checks against an fp32 oracle
 def _small_llama_cfg():
     from fairseq2_b200.models.llama import LLaMAConfig
