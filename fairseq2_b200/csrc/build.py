@@ -82,9 +82,32 @@ def build_data(verbose: bool = False, force: bool = False) -> Path | None:
     return target
 
 
+def build_data_tests(verbose: bool = False, force: bool = False) -> Path | None:
+    """``_data_tests.so``: the data runtime's sources (without the Python bindings) plus the C++ unit tests of
+    ``csrc/data/tests``; ``run_all()`` of that module returns one row per test case."""
+    from torch.utils import cpp_extension
+
+    src_dir = CSRC / "data"
+    tests = sorted((src_dir / "tests").glob("*.cc")) if (src_dir / "tests").exists() else []
+    if not tests:
+        return None
+    sources = [s for s in sorted(src_dir.glob("*.cc")) if s.name != "bindings.cc"] + tests
+    target = PKG / "_data_tests.so"
+    if not force and not _newer(sources, target):
+        return target
+    build_dir = CSRC / "_build" / "data_tests"
+    build_dir.mkdir(parents=True, exist_ok=True)
+    cpp_extension.load(name="_data_tests", sources=[str(s) for s in sources],
+                       extra_cflags=["-O1", "-std=c++17", "-pthread"], extra_ldflags=["-pthread", "-lz"],
+                       build_directory=str(build_dir), verbose=verbose, is_python_module=False, with_cuda=False)
+    shutil.copy2(build_dir / "_data_tests.so", target)
+    return target
+
+
 def build_all(verbose: bool = False, force: bool = False) -> None:
     build_cuda(verbose=verbose, force=force)
     build_data(verbose=verbose, force=force)
+    build_data_tests(verbose=verbose, force=force)
 
 
 if __name__ == "__main__":

@@ -362,14 +362,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("read_text", [](py::object path, std::optional<std::string> key, std::optional<std::string> encoding,
                           const std::string& line_ending, bool ltrim, bool rtrim, bool skip_empty, bool memory_map,
                           std::optional<size_t> block_size) {
-        if (encoding && !encoding->empty()) {
-            std::string e = *encoding;
-            for (auto& c : e) c = static_cast<char>(std::tolower(c));
-            if (e != "utf-8" && e != "utf8" && e != "ascii")
-                throw std::invalid_argument("Only UTF-8 text files are supported by this build, but `encoding` is '" + *encoding + "'.");
-        }
         return read_text(py::str(path).cast<std::string>(), std::move(key), line_ending, ltrim, rtrim, skip_empty,
-                         memory_map, block_size.value_or(0));
+                         memory_map, block_size.value_or(0), std::move(encoding));
     }, py::arg("path"), py::arg("key") = py::none(), py::arg("encoding") = py::none(),
        py::arg("line_ending") = "infer", py::arg("ltrim") = false, py::arg("rtrim") = false,
        py::arg("skip_empty") = false, py::arg("memory_map") = false, py::arg("block_size") = py::none());

@@ -302,7 +302,8 @@ DataPipelineBuilder read_list(DataList items);
 DataPipelineBuilder list_files(const std::string& path, std::optional<std::string> pattern);
 DataPipelineBuilder read_zipped_records(const std::string& path);
 DataPipelineBuilder read_text(const std::string& path, std::optional<std::string> key, const std::string& line_ending,
-                              bool ltrim, bool rtrim, bool skip_empty, bool memory_map, size_t block_size);
+                              bool ltrim, bool rtrim, bool skip_empty, bool memory_map, size_t block_size,
+                              std::optional<std::string> encoding = std::nullopt);
 DataPipelineBuilder read_py_iterator(py::object iterator, py::object reset_fn, bool infinite);
 
 // length of an example for bucketing/packing: tensor -> size(0), list -> size, int -> itself

@@ -1,5 +1,8 @@
 // Element selectors, collater, file/text/zip sources, file mapper and text
 // converters of the native data pipeline runtime.
+#include <iconv.h>
+
+#include <cerrno>
 #include <dirent.h>
 #include <fnmatch.h>
 #include <sys/stat.h>
@@ -285,13 +288,60 @@ DataPipelineBuilder list_files(const std::string& path, std::optional<std::strin
 // ================================================================== read_text
 namespace {
 
+bool is_utf8_name(const std::string& name) {
+    std::string e;
+    for (char c : name)
+        if (c != '-' && c != '_') e += static_cast<char>(std::tolower(static_cast<unsigned char>(c)));
+    return e.empty() || e == "utf8" || e == "ascii" || e == "usascii";
+}
+
+// Converts a whole text file from `encoding` to UTF-8 with iconv; positions recorded by the reader refer to the
+// converted bytes, which are a pure function of the file. An invalid or truncated multi-byte sequence is an error.
+MemoryBlock reencode_to_utf8(const MemoryBlock& in, const std::string& encoding, const std::string& path) {
+    iconv_t cd = iconv_open("UTF-8", encoding.c_str());
+    if (cd == reinterpret_cast<iconv_t>(-1))
+        throw std::invalid_argument("The text encoding '" + encoding + "' is not known to iconv.");
+    std::vector<char> out(in.size() + in.size() / 2 + 16);
+    char* src = const_cast<char*>(reinterpret_cast<const char*>(in.data()));
+    size_t src_left = in.size();
+    size_t used = 0;
+    while (true) {
+        char* dst = out.data() + used;
+        size_t dst_left = out.size() - used;
+        const size_t rc = src_left > 0 ? iconv(cd, &src, &src_left, &dst, &dst_left)
+                                       : iconv(cd, nullptr, nullptr, &dst, &dst_left);   // flush the shift state
+        used = out.size() - dst_left;
+        if (rc != static_cast<size_t>(-1)) {
+            if (src_left == 0) {
+                char* d2 = out.data() + used;
+                size_t l2 = out.size() - used;
+                iconv(cd, nullptr, nullptr, &d2, &l2);
+                used = out.size() - l2;
+                break;
+            }
+            continue;
+        }
+        if (errno == E2BIG) {
+            out.resize(out.size() * 2);
+            continue;
+        }
+        const size_t at = in.size() - src_left;
+        iconv_close(cd);
+        throw ByteStreamError("'" + path + "' is not valid " + encoding + " text (byte offset " + std::to_string(at) +
+                              (errno == EINVAL ? ", truncated sequence)." : ", invalid sequence)."));
+    }
+    iconv_close(cd);
+    return MemoryBlock::copy_of(out.data(), used);
+}
+
 class TextSource final : public DataSource {
 public:
     TextSource(std::string path, std::optional<std::string> key, std::string ending, bool ltrim, bool rtrim,
-               bool skip_empty, bool memory_map)
+               bool skip_empty, bool memory_map, const std::optional<std::string>& encoding)
         : path_(std::move(path)), key_(std::move(key)), ending_(std::move(ending)), ltrim_(ltrim), rtrim_(rtrim),
           skip_empty_(skip_empty) {
         block_ = memory_map ? MemoryBlock::map_file(path_) : MemoryBlock::read_file(path_);
+        if (encoding && !is_utf8_name(*encoding)) block_ = reencode_to_utf8(block_, *encoding, path_);
     }
     std::optional<Data> next() override {
         const char* base = reinterpret_cast<const char*>(block_.data());
@@ -339,11 +389,12 @@ private:
 }  // namespace
 
 DataPipelineBuilder read_text(const std::string& path, std::optional<std::string> key, const std::string& line_ending,
-                              bool ltrim, bool rtrim, bool skip_empty, bool memory_map, size_t) {
+                              bool ltrim, bool rtrim, bool skip_empty, bool memory_map, size_t,
+                              std::optional<std::string> encoding) {
     if (line_ending != "infer" && line_ending != "lf" && line_ending != "crlf")
         throw std::invalid_argument("`line_ending` must be 'infer', 'lf' or 'crlf'.");
     return DataPipelineBuilder([=]() -> std::unique_ptr<DataSource> {
-        return std::make_unique<TextSource>(path, key, line_ending, ltrim, rtrim, skip_empty, memory_map);
+        return std::make_unique<TextSource>(path, key, line_ending, ltrim, rtrim, skip_empty, memory_map, encoding);
     });
 }
 

@@ -4,6 +4,8 @@
 
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.nn.functional as F
 from torch import Tensor
@@ -92,7 +94,7 @@ class _EmbedPush(torch.autograd.Function):
 
 def _embedding_push_op(ids: Tensor, shard: Tensor, gang) -> EmbeddingPush | None:  # type: ignore[no-untyped-def]
     if not (use_kernels(ids, shard) and shard.dtype == torch.bfloat16 and shard.shape[1] % 8 == 0
-            and ids.dtype == torch.int64):
+            and ids.dtype == torch.int64) or os.environ.get("FAIRSEQ2_B200_TP_EMBED_PUSH", "1") == "0":
         return None
     from fairseq2_b200.parallel.tp import get_tp_context
 

@@ -308,3 +308,18 @@ def test_image_decoder_jpeg_matches_libjpeg() -> None:
         assert np.abs(got.astype(int) - ref.astype(int)).max() <= 4, (mode, kw)
     with pytest.raises(Exception):
         dec(MemoryBlock(b"\xff\xd8\xff\xc2\x00\x0b\x08\x00\x10\x00\x10\x01\x01\x11\x00"))      # progressive
+
+
+def test_read_text_reencodes_with_iconv(tmp_path) -> None:
+    from fairseq2_b200.data.text import read_text
+
+    p = tmp_path / "latin1.txt"
+    p.write_bytes("señor\nmañana\n".encode("latin-1"))
+    assert list(read_text(p, encoding="latin1", rtrim=True).and_return()) == ["señor", "mañana"]
+    q = tmp_path / "sjis.txt"
+    q.write_bytes("日本語\nテキスト".encode("shift_jis"))
+    assert list(read_text(q, encoding="SHIFT_JIS").and_return()) == ["日本語", "テキスト"]
+    with pytest.raises(ValueError):
+        list(read_text(p, encoding="klingon").and_return())
+    with pytest.raises(Exception, match="not valid"):
+        list(read_text(q, encoding="utf-16").and_return())  # 15 bytes: a truncated code unit
