@@ -1,0 +1,180 @@
+"""One contract check per data-pipeline operator: the full output, a ``state_dict`` round trip at every split point
+(into the same pipeline and into a freshly built one), and ``reset()`` (cf. the per-operator files of fairseq2's
+``tests/unit/data/data_pipeline/``)."""
+from __future__ import annotations
+
+import pickle
+from pathlib import Path
+from typing import Any, Callable
+
+import pytest
+import torch
+
+from fairseq2_b200.data import DataPipeline, read_sequence, read_zipped_records
+from fairseq2_b200.data.text import read_text
+
+
+def _norm(x: Any) -> Any:
+    if isinstance(x, torch.Tensor):
+        return ("tensor", tuple(x.shape), x.flatten().tolist())
+    if isinstance(x, (list, tuple)):
+        return [_norm(e) for e in x]
+    if isinstance(x, dict):
+        return {k: _norm(v) for k, v in x.items()}
+    if isinstance(x, memoryview):
+        return bytes(x)
+    return x
+
+
+def _drain(p: DataPipeline) -> list[Any]:
+    return [_norm(x) for x in p]
+
+
+def _seq(n: int, start: int = 0) -> list[int]:
+    return list(range(start, start + n))
+
+
+def _text_file(tmp: Path) -> Path:
+    f = tmp / "lines.txt"
+    f.write_text("".join(f"line {i}\n" for i in range(9)))
+    return f
+
+
+def _zip_file(tmp: Path) -> Path:
+    import zipfile
+
+    f = tmp / "records.zip"
+    with zipfile.ZipFile(f, "w", zipfile.ZIP_DEFLATED) as z:
+        for i in range(5):
+            z.writestr(f"r{i}.bin", bytes([i]) * (i + 1))
+    return f
+
+
+Builders = dict[str, Callable[[Path], DataPipeline]]
+
+OPERATORS: Builders = {
+    "read_sequence": lambda t: read_sequence(_seq(6)).and_return(),
+    "bucket": lambda t: read_sequence(_seq(11)).bucket(4).and_return(),
+    "bucket_drop_remainder": lambda t: read_sequence(_seq(11)).bucket(4, drop_remainder=True).and_return(),
+    "bucket_by_length": lambda t: read_sequence([torch.zeros(n) for n in (1, 3, 2, 4, 1, 2, 3, 4, 1)])
+    .bucket_by_length([(3, 2), (2, 4)]).and_return(),
+    "dynamic_bucket": lambda t: read_sequence(_seq(12, 1)).dynamic_bucket(10, lambda x: float(x)).and_return(),
+    "filter": lambda t: read_sequence(_seq(15)).filter(lambda x: x % 3 != 0).and_return(),
+    "map": lambda t: read_sequence(_seq(9)).map(lambda x: x * x).and_return(),
+    "map_parallel": lambda t: read_sequence(_seq(25)).map(lambda x: x + 1, num_parallel_calls=4).and_return(),
+    "map_selector": lambda t: read_sequence([{"a": i, "b": [i, i]} for i in range(6)])
+    .map(lambda x: x * 10, selector="a,b[1]").and_return(),
+    "pack": lambda t: read_sequence([torch.arange(n) for n in (3, 5, 2, 7, 1, 4, 6)])
+    .pack(num_elements=8, max_seq_len=6, pad_value=0).and_return(),
+    "prefetch": lambda t: read_sequence(_seq(20)).prefetch(3).and_return(),
+    "repeat": lambda t: read_sequence(_seq(3)).repeat(3).and_return(),
+    "shard": lambda t: read_sequence(_seq(13)).shard(1, 3).and_return(),
+    "shard_uneven": lambda t: read_sequence(_seq(13)).shard(0, 3, allow_uneven=True).and_return(),
+    "shuffle": lambda t: read_sequence(_seq(30)).shuffle(8, seed=5).and_return(),
+    "shuffle_full": lambda t: read_sequence(_seq(12)).shuffle(0, seed=5).and_return(),
+    "skip": lambda t: read_sequence(_seq(8)).skip(3).and_return(),
+    "take": lambda t: read_sequence(_seq(8)).take(5).and_return(),
+    "yield_from": lambda t: read_sequence(_seq(4, 1)).yield_from(lambda n: read_sequence(_seq(n, 10 * n)).and_return())
+    .and_return(),
+    "concat": lambda t: DataPipeline.concat([read_sequence(_seq(3)).and_return(),
+                                             read_sequence(_seq(4, 10)).and_return()]).and_return(),
+    "constant": lambda t: DataPipeline.constant(7).take(4).and_return(),
+    "count": lambda t: DataPipeline.count(3, step=2).take(6).and_return(),
+    "round_robin": lambda t: DataPipeline.round_robin([read_sequence(_seq(5)).and_return(),
+                                                       read_sequence(_seq(2, 100)).and_return()]).and_return(),
+    "round_robin_shortest": lambda t: DataPipeline.round_robin(
+        [read_sequence(_seq(5)).and_return(), read_sequence(_seq(2, 100)).and_return()],
+        stop_at_shortest=True).and_return(),
+    "sample": lambda t: DataPipeline.sample([read_sequence(_seq(6)).and_return(),
+                                             read_sequence(_seq(9, 100)).and_return()], weights=[0.3, 0.7],
+                                            seed=11).and_return(),
+    "zip": lambda t: DataPipeline.zip([read_sequence(_seq(5)).and_return(), read_sequence(_seq(5, 50)).and_return()],
+                                      names=["x", "y"]).and_return(),
+    "zip_flatten": lambda t: DataPipeline.zip(
+        [read_sequence([{"a": i} for i in range(4)]).and_return(),
+         read_sequence([{"b": -i} for i in range(4)]).and_return()], flatten=True).and_return(),
+    "read_text": lambda t: read_text(_text_file(t), rtrim=True).and_return(),
+    "read_text_mmap": lambda t: read_text(_text_file(t), rtrim=True, memory_map=True).and_return(),
+    "read_zipped_records": lambda t: read_zipped_records(_zip_file(t)).map(lambda b: bytes(b)).and_return(),
+    "composite": lambda t: read_sequence(_seq(40)).shuffle(10, seed=1).filter(lambda x: x % 5 != 0)
+    .map(lambda x: torch.full((x % 4 + 1,), x), num_parallel_calls=2).bucket(3).prefetch(2).and_return(),
+}
+
+EXPECTED: dict[str, Any] = {
+    "read_sequence": _seq(6),
+    "bucket": [[0, 1, 2, 3], [4, 5, 6, 7], [8, 9, 10]],
+    "bucket_drop_remainder": [[0, 1, 2, 3], [4, 5, 6, 7]],
+    "filter": [x for x in _seq(15) if x % 3],
+    "map": [x * x for x in _seq(9)],
+    "map_parallel": _seq(25, 1),
+    "map_selector": [{"a": i * 10, "b": [i, i * 10]} for i in range(6)],
+    "prefetch": _seq(20),
+    "repeat": _seq(3) * 3,
+    "shard": [1, 4, 7, 10],
+    "shard_uneven": [0, 3, 6, 9, 12],
+    "skip": _seq(5, 3),
+    "take": _seq(5),
+    "yield_from": [10, 20, 21, 30, 31, 32, 40, 41, 42, 43],
+    "concat": [0, 1, 2, 10, 11, 12, 13],
+    "constant": [7] * 4,
+    "count": [3, 5, 7, 9, 11, 13],
+    "round_robin": [0, 100, 1, 101, 2, 100, 3, 101, 4, 100],
+    "round_robin_shortest": [0, 100, 1, 101],
+    "zip": [{"x": i, "y": 50 + i} for i in range(5)],
+    "zip_flatten": [{"a": i, "b": -i} for i in range(4)],
+    "read_text": [f"line {i}" for i in range(9)],
+    "read_text_mmap": [f"line {i}" for i in range(9)],
+    "read_zipped_records": [bytes([i]) * (i + 1) for i in range(5)],
+}
+
+
+@pytest.mark.parametrize("name", sorted(OPERATORS))
+def test_operator_output(name: str, tmp_path: Path) -> None:
+    got = _drain(OPERATORS[name](tmp_path))
+    assert got, name
+    if name in EXPECTED:
+        assert got == _norm(EXPECTED[name])
+    if name in ("shuffle", "shuffle_full"):
+        assert sorted(got) == _seq(len(got)) and got != _seq(len(got))
+    if name == "sample":
+        assert sorted(x for x in got if x < 100) == _seq(6) or sorted(x for x in got if x >= 100) == _seq(9, 100)
+    if name == "dynamic_bucket":
+        assert all(sum(b) >= 10 for b in got[:-1]) and sum(map(sum, got)) == sum(_seq(12, 1))
+    if name == "pack":
+        assert all(len(b["seqs"][2]) == 8 for b in got)
+    if name == "bucket_by_length":
+        assert sum(len(b) for b in got) == 9
+
+
+@pytest.mark.parametrize("name", sorted(OPERATORS))
+def test_operator_state_dict_round_trip(name: str, tmp_path: Path) -> None:
+    make = OPERATORS[name]
+    want = _drain(make(tmp_path))
+    for k in range(len(want) + 1):
+        p = make(tmp_path)
+        it = iter(p)
+        for _ in range(k):
+            next(it)
+        state = pickle.loads(pickle.dumps(p.state_dict()))       # checkpoints pickle it
+        for _ in range(2):
+            next(it, None)
+        p.load_state_dict(state)
+        tail = _drain(p)
+        assert tail == want[k:], (name, k)
+        q = make(tmp_path)
+        q.load_state_dict(state)
+        assert _drain(q) == want[k:], (name, k)
+
+
+@pytest.mark.parametrize("name", sorted(OPERATORS))
+def test_operator_reset(name: str, tmp_path: Path) -> None:
+    p = OPERATORS[name](tmp_path)
+    want = _drain(p)
+    p.reset(reset_rng=True)
+    assert _drain(p) == want
+    it = iter(p)
+    p.reset(reset_rng=True)
+    next(iter(p))
+    p.reset(reset_rng=True)
+    assert _drain(p) == want
+    del it
