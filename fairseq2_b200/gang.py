@@ -116,6 +116,11 @@ class Gang(ABC):
     @abstractmethod
     def supports_process_group(self) -> bool: ...
 
+    def base_gang(self) -> "Gang":
+        """The gang that owns the process group: ``self``, except for gangs that wrap another one to run its
+        collectives on other kernels."""
+        return self
+
     def __enter__(self) -> "Gang":
         return self
 
@@ -632,13 +637,41 @@ def create_fsdp_gangs(gangs: Gangs, intra_node_size: int | None = None) -> Gangs
     return Gangs(root=gangs.root, dp=dp, rdp=rdp, sdp=sdp, tp=gangs.tp, pp=gangs.pp)
 
 
-def setup_root_gang(device: Device, *, timeout: timedelta | None = None, high_priority: bool = False) -> Gang:
-    """Root gang from the environment: fake when ``WORLD_SIZE`` is 1."""
+def setup_root_gang(device: Device, *, timeout: timedelta | None = None, high_priority: bool = False,
+                    collectives: str = "auto") -> Gang:
+    """Root gang from the environment: fake when ``WORLD_SIZE`` is 1.
+
+    ``collectives``: ``"nccl"`` keeps the process-group gang; ``"symm"`` wraps it into a
+    :class:`~fairseq2_b200.parallel.symm.SymmGang`, whose CUDA collectives (loss / metric / gradient-norm
+    reductions, flag broadcasts, data-reader synchronisation) run on the peer-memory kernels of a symmetric arena
+    and raises if that is not possible; ``"auto"`` does so when all ranks sit in one NVSwitch domain (2 to 8 CUDA
+    ranks of one node) and keeps NCCL otherwise."""
+    if collectives not in ("auto", "nccl", "symm"):
+        raise ValueError(f"`collectives` must be 'auto', 'nccl' or 'symm', but is '{collectives}' instead.")
     info = WorldInfo.from_env()
     if info.size == 1:
         return FakeGang(device)
-    return ProcessGroupGang.create_default_process_group(device, timeout=timeout, high_priority=high_priority,
+    root = ProcessGroupGang.create_default_process_group(device, timeout=timeout, high_priority=high_priority,
                                                          world_info=info)
+    if collectives == "nccl" or device.type != "cuda":
+        if collectives == "symm":
+            raise NotSupportedError("`collectives='symm'` needs CUDA devices.")
+        return root
+    from fairseq2_b200.parallel.symm import SymmGang, symmetric_memory_available
+
+    single_node = info.local_size == info.size
+    if not (single_node and symmetric_memory_available(root)):
+        if collectives == "symm":
+            raise NotSupportedError("`collectives='symm'` needs 2 to 8 CUDA ranks on one node with peer access.")
+        return root
+    try:
+        limit = timeout.total_seconds() if timeout is not None else 900.0
+        return SymmGang(root, wait_limit_s=limit)
+    except Exception as ex:  # noqa: BLE001 - no peer access between the devices
+        if collectives == "symm":
+            raise
+        log.warning("Symmetric memory is not usable for the root gang ({}); using NCCL collectives.", ex)
+        return root
 
 
 # --------------------------------------------------------------------- helpers

@@ -123,7 +123,7 @@ class DDP(Module):
         from fairseq2_b200.gang import ProcessGroupGang
 
         usable = (self.device.type == "cuda" and self.gang.size > 1 and self.gang.size <= 8
-                  and isinstance(self.gang, ProcessGroupGang)
+                  and isinstance(self.gang.base_gang(), ProcessGroupGang)
                   and all(g[0].dtype in (torch.float32, torch.bfloat16) for g in groups))
         if comm == "nccl" or not usable:
             if comm == "symm":

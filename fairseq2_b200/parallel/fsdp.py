@@ -491,7 +491,7 @@ def _null() -> Iterator[None]:
 
 
 def _coalesced_all_gather(gang: Gang, outs: Sequence[Tensor], ins: Sequence[Tensor]) -> None:
-    if isinstance(gang, ProcessGroupGang) and gang.device.type == "cuda":
+    if isinstance(gang.base_gang(), ProcessGroupGang) and gang.device.type == "cuda":
         pg = gang.as_process_group()
         with dist._coalescing_manager(group=pg, device=gang.device, async_ops=False):
             for o, i in zip(outs, ins):
@@ -502,7 +502,7 @@ def _coalesced_all_gather(gang: Gang, outs: Sequence[Tensor], ins: Sequence[Tens
 
 
 def _coalesced_reduce_scatter(gang: Gang, outs: Sequence[Tensor], ins: Sequence[Tensor], op: ReduceOperation) -> None:
-    if isinstance(gang, ProcessGroupGang) and gang.device.type == "cuda":
+    if isinstance(gang.base_gang(), ProcessGroupGang) and gang.device.type == "cuda":
         pg = gang.as_process_group()
         top = dist.ReduceOp.AVG if op == ReduceOperation.MEAN else dist.ReduceOp.SUM
         with dist._coalescing_manager(group=pg, device=gang.device, async_ops=False):

@@ -41,6 +41,7 @@ _OPS = {ReduceOperation.SUM: 0, ReduceOperation.MEAN: 1, ReduceOperation.PRODUCT
 
 
 def symmetric_memory_available(gang: Gang) -> bool:
+    gang = gang.base_gang()
     if not isinstance(gang, ProcessGroupGang) or gang.device.type != "cuda" or gang.size > MAX_RANKS:
         return False
     try:
@@ -123,9 +124,13 @@ class SymmGang(Gang):
     """
 
     def __init__(self, base: ProcessGroupGang, *, staging_bytes: int = 64 * 1024 * 1024,
-                 arena: SymmetricArena | None = None) -> None:
+                 arena: SymmetricArena | None = None, wait_limit_s: float = 5.0) -> None:
+        """``wait_limit_s``: how long a collective waits for its slowest peer before it gives up and records a
+        time-out in the status word (the next ``barrier()`` raises); a training job sets it to the gang timeout,
+        since ranks legitimately wait for one another during checkpoint writes and evaluation."""
         self._base = base
-        self.arena = arena if arena is not None else SymmetricArena(base, 2 * staging_bytes + 4096)
+        self.arena = arena if arena is not None else SymmetricArena(base, 2 * staging_bytes + 4096,
+                                                                    wait_limit_s=wait_limit_s)
         self._stage_bytes = staging_bytes
         # two staging halves alternate so that a rank that races ahead into the next collective
         # cannot overwrite data a slower peer is still reading
@@ -147,6 +152,19 @@ class SymmGang(Gang):
     def close(self) -> None:
         self._base.close()
 
+    def base_gang(self) -> Gang:
+        return self._base
+
+    def _on_kernels(self, t: Tensor, *, reduce: bool = False) -> bool:
+        """Whether a collective on ``t`` runs on the peer-memory kernels; otherwise it goes to the wrapped gang:
+        CPU tensors, tensors beyond the staging area, and reductions of types that fp32 cannot hold exactly."""
+        if not t.is_cuda or t.numel() == 0:
+            return False
+        nbytes = t.numel() * (4 if reduce else t.element_size())
+        if nbytes + 16 > self._stage_bytes:
+            return False
+        return not reduce or t.dtype in (torch.float32, torch.bfloat16, torch.float16)
+
     def create_gang(self, ranks: Sequence[int]) -> "Gang | None":
         return self._base.create_gang(ranks)
 
@@ -159,7 +177,7 @@ class SymmGang(Gang):
         self.arena.ext.check_status()
 
     def all_reduce(self, tensor: Tensor, op: ReduceOperation) -> None:
-        if not tensor.is_cuda:
+        if not self._on_kernels(tensor, reduce=True):
             self._base.all_reduce(tensor, op)
             return
         src = tensor if tensor.dtype == torch.float32 else tensor.float()
@@ -171,7 +189,7 @@ class SymmGang(Gang):
         tensor.copy_(out.view_as(tensor))
 
     def all_gather(self, output_tensor: Tensor, input_tensor: Tensor) -> None:
-        if not input_tensor.is_cuda:
+        if not self._on_kernels(input_tensor):
             self._base.all_gather(output_tensor, input_tensor)
             return
         if not output_tensor.is_contiguous():
@@ -196,7 +214,7 @@ class SymmGang(Gang):
             o.copy_(s)
 
     def reduce_scatter(self, output_tensor: Tensor, input_tensor: Tensor, op: ReduceOperation) -> None:
-        if not input_tensor.is_cuda:
+        if not self._on_kernels(input_tensor, reduce=True):
             self._base.reduce_scatter(output_tensor, input_tensor, op)
             return
         tmp = input_tensor.float().contiguous()
@@ -206,7 +224,7 @@ class SymmGang(Gang):
     def all_to_all(self, output_tensor: Tensor, input_tensor: Tensor,
                    output_split_sizes: Sequence[int] | None = None,
                    input_split_sizes: Sequence[int] | None = None) -> None:
-        if not input_tensor.is_cuda:
+        if not self._on_kernels(input_tensor):
             self._base.all_to_all(output_tensor, input_tensor, output_split_sizes, input_split_sizes)
             return
         W = self.size
@@ -223,7 +241,7 @@ class SymmGang(Gang):
     def broadcast(self, tensor: Tensor, source_rank: int = 0) -> None:
         if not 0 <= source_rank < self.size:
             raise ValueError(f"`source_rank` must be in [0, {self.size}), but is {source_rank} instead.")
-        if not tensor.is_cuda:
+        if not self._on_kernels(tensor):
             self._base.broadcast(tensor, source_rank)
             return
         src = tensor.contiguous()

@@ -123,7 +123,8 @@ class RecipeContext:
             gs: GangSection = self._section("gang", GangSection)
             ts: TrainerSection = self._section("trainer", TrainerSection)
             device = get_default_device()
-            root = setup_root_gang(device, timeout=timedelta(minutes=gs.timeout), high_priority=gs.high_priority)
+            root = setup_root_gang(device, timeout=timedelta(minutes=gs.timeout), high_priority=gs.high_priority,
+                                   collectives=gs.collectives)
             if root.size % gs.tensor_parallel_size != 0:
                 raise GangTopologyError(root.size, gs.tensor_parallel_size)
             gangs = create_parallel_gangs(root, tp_size=gs.tensor_parallel_size)

@@ -66,6 +66,9 @@ class GangSection:
     timeout: int = 15
     high_priority: bool = True
     monitored: bool = False
+    #: kernels behind the root gang's CUDA collectives: "symm" = peer-memory kernels over a symmetric arena,
+    #: "nccl", or "auto" (symm inside one NVSwitch domain, NCCL otherwise)
+    collectives: Literal["auto", "nccl", "symm"] = "auto"
 
     def validate(self) -> ValidationResult:
         r = ValidationResult()

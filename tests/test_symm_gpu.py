@@ -22,15 +22,23 @@ def _need_gpus(n: int) -> None:
 
 
 def _collectives_worker(rank: int, world: int):
-    from fairseq2_b200.gang import ProcessGroupGang, ReduceOperation
-    from fairseq2_b200.parallel.symm import SymmGang
+    from datetime import timedelta
+
+    from fairseq2_b200.gang import ProcessGroupGang, ReduceOperation, create_parallel_gangs, setup_root_gang
+    from fairseq2_b200.parallel.symm import SymmGang, symmetric_memory_available
 
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     dev = torch.device("cuda", rank)
     torch.cuda.set_device(dev)
-    base = ProcessGroupGang.create_default_process_group(dev)
-    g = SymmGang(base, staging_bytes=8 << 20)
+    g = setup_root_gang(dev, timeout=timedelta(seconds=30), collectives="symm")   # the factory the recipes use
+    assert isinstance(g, SymmGang) and isinstance(g.base_gang(), ProcessGroupGang)
+    assert symmetric_memory_available(g) and g.arena.wait_limit_s == 30.0
+    assert create_parallel_gangs(g).dp is g                       # tp = 1: the data-parallel gang is the root gang
     out = {}
+    # exact in 64-bit integers (goes to the wrapped gang: fp32 staging would round)
+    big = torch.tensor([2**40 + rank + 1], device=dev)
+    g.all_reduce(big, ReduceOperation.SUM)
+    out["int_sum"] = int(big[0])
     t = torch.full((1000,), float(rank + 1), device=dev)
     g.all_reduce(t, ReduceOperation.SUM)
     out["sum"] = float(t[0]), float(t[-1])
@@ -68,6 +76,7 @@ def test_symm_gang_collectives(world: int) -> None:
     res = run_distributed(_collectives_worker, world)
     for rank, r in enumerate(res):
         assert r["sum"] == (world * (world + 1) / 2,) * 2
+        assert r["int_sum"] == world * 2**40 + world * (world + 1) // 2
         assert r["max"] == float(world)
         assert r["ag"] == [[i + 100 * q for i in range(10)] for q in range(world)]
         assert r["bcast"] == float(world - 1)
