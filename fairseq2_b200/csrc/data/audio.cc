@@ -23,8 +23,23 @@ Data AudioDecoder::operator()(Data&& d) const {
     const MemoryBlock& mb = d.as_memory_block();
     const uint8_t* b = mb.data();
     const size_t n = mb.size();
+    if (is_flac(b, n)) {
+        int rate = 0, bps = 0;
+        at::Tensor pcm = decode_flac(b, n, rate, bps);                                  // int32 [frames, channels]
+        const at::ScalarType out_dtype = dtype_.value_or(bps <= 16 ? at::kShort : at::kInt);
+        at::Tensor out = at::isFloatingType(out_dtype)
+                             ? (pcm.to(at::kDouble) / static_cast<double>(int64_t{1} << (bps - 1))).to(out_dtype)
+                             : pcm.to(out_dtype);
+        if (!keepdim_ && out.size(1) == 1) out = out.squeeze(-1);
+        DataDict res{{"waveform", Data(out)}, {"sample_rate", Data(static_cast<double>(rate))},
+                     {"format", Data("FLAC/PCM_" + std::to_string(bps))}};
+        return Data(std::move(res));
+    }
+    if (n >= 4 && std::memcmp(b, "OggS", 4) == 0)
+        throw std::invalid_argument("Ogg containers (Vorbis/Opus) are lossy codecs that this build does not decode; "
+                                    "convert the audio to FLAC or WAV.");
     if (n < 44 || std::memcmp(b, "RIFF", 4) != 0 || std::memcmp(b + 8, "WAVE", 4) != 0)
-        throw std::invalid_argument("The input audio is not a RIFF/WAVE file (only WAV is supported by this build).");
+        throw std::invalid_argument("The input audio is neither a RIFF/WAVE nor a FLAC stream.");
     size_t p = 12;
     uint16_t fmt = 0, channels = 0, bits = 0;
     uint32_t rate = 0;

@@ -72,7 +72,11 @@ private:
     at::ScalarType dtype_;
 };
 
-// RIFF/WAVE decoder (PCM 8/16/24/32-bit and IEEE float) -> {"waveform", "sample_rate", "format"}.
+// flac.cc
+bool is_flac(const uint8_t* b, size_t n);
+at::Tensor decode_flac(const uint8_t* b, size_t n, int& sample_rate, int& bits_per_sample);
+
+// RIFF/WAVE (PCM 8/16/24/32-bit and IEEE float) and FLAC decoder -> {"waveform", "sample_rate", "format"}.
 class AudioDecoder {
 public:
     AudioDecoder(bool keepdim, std::optional<at::ScalarType> dtype) : keepdim_(keepdim), dtype_(dtype) {}

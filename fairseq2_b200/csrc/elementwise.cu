@@ -886,6 +886,16 @@ extern "C" int fs2_rms_norm_bwd_no_alloc(const void* dy, const void* x, const vo
         g_no_alloc_error = "all pointers must be non-null and 16-byte aligned";
         return 3;
     }
+    // the scratch array is resolved for the current device while the kernels go to `stream`: both must be the same GPU
+    int current = -1, stream_dev = -1;
+    if (cudaGetDevice(&current) == cudaSuccess && cudaStreamGetDevice(stream, &stream_dev) == cudaSuccess) {
+        if (stream_dev != current) {
+            g_no_alloc_error = "the device that owns `stream` must be the current device of the calling thread";
+            return 6;
+        }
+    } else {
+        (void)cudaGetLastError();           // the query is unavailable: the header states the requirement
+    }
     float* scratch = no_alloc_scratch_ptr();
     if (scratch == nullptr) return 4;
     const int threads = norm_block_bwd(D);

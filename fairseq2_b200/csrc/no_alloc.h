@@ -19,6 +19,10 @@
 //     resident until the process exits.
 //
 // Behaviour to know about:
+//   * Call with the device that owns `stream` current on the calling thread
+//     (cudaSetDevice): the scratch array is looked up for the current device
+//     and the kernels are launched into `stream`. A stream of another device is
+//     rejected with return value 6.
 //   * The first call on each device resolves the device address of the scratch
 //     array (cudaGetSymbolAddress). Make that first call outside of any stream
 //     capture; later calls only launch kernels.
