@@ -162,9 +162,12 @@ Data WaveformToFbankConverter::operator()(Data&& d) const {
     return Data(std::move(out));
 }
 
-// ------------------------------------------------------------------ baseline JPEG
-// Sequential (baseline / extended) DCT JPEG with Huffman coding: 8-bit samples, 1 or 3 components, any sampling
-// factors up to 2x2 (4:4:4, 4:2:2, 4:2:0), restart intervals. Progressive and arithmetic-coded files are rejected.
+// ------------------------------------------------------------------------ JPEG
+// DCT JPEG with Huffman coding, sequential (baseline / extended) and progressive (spectral selection + successive
+// approximation), interleaved and non-interleaved scans: 8-bit samples, 1 or 3 components, sampling factors up to
+// 2x2 (4:4:4, 4:2:2, 4:2:0), restart intervals. Scans fill per-component coefficient arrays; dequantisation, the
+// inverse DCT, chroma upsampling and colour conversion run once after the last scan. Arithmetic-coded, lossless
+// and hierarchical files are rejected.
 namespace {
 
 struct JpegHuff {
@@ -258,8 +261,119 @@ void jpeg_idct8x8(const float* in, uint8_t* out, int out_stride) {
 struct JpegComp {
     int id = 0, h = 1, v = 1, tq = 0, td = 0, ta = 0, pred = 0;
     int bw = 0, bh = 0;                  // plane size in pixels (multiple of 8 * sampling)
+    int blocks_w = 0, blocks_h = 0;      // coefficient storage in blocks (padded to whole MCUs)
+    int own_bw = 0, own_bh = 0;          // blocks a non-interleaved scan of this component visits
+    std::vector<int16_t> coef;           // [blocks_h][blocks_w][64] in natural (row-major) order, not dequantised
     std::vector<uint8_t> plane;
 };
+
+// One scan of a progressive frame for one block: spectral band [ss, se], successive-approximation bits ah/al.
+struct JpegScan {
+    int ss = 0, se = 63, ah = 0, al = 0;
+    int eobrun = 0;
+};
+
+void jpeg_refine_nonzero(JpegBits& br, int16_t* c, int p1, int m1) {
+    if (br.get_bit() && (*c & p1) == 0) *c = static_cast<int16_t>(*c >= 0 ? *c + p1 : *c + m1);
+}
+
+void jpeg_decode_block(JpegBits& br, JpegComp& c, const JpegHuff* dc, const JpegHuff* ac, JpegScan& sc, int16_t* blk,
+                       bool progressive) {
+    const auto corrupt = [] { return std::invalid_argument("The JPEG entropy-coded data is corrupt."); };
+    if (!progressive) {
+        const int t = jpeg_decode_symbol(br, dc[c.td]);
+        if (t > 11) throw corrupt();
+        c.pred += jpeg_extend(br.get_bits(t), t);
+        blk[0] = static_cast<int16_t>(c.pred);
+        for (int k = 1; k < 64;) {
+            const int rs = jpeg_decode_symbol(br, ac[c.ta]);
+            const int r = rs >> 4, sz = rs & 15;
+            if (sz == 0) {
+                if (r == 15) { k += 16; continue; }
+                break;
+            }
+            k += r;
+            if (k > 63) throw corrupt();
+            blk[kZigzag[k]] = static_cast<int16_t>(jpeg_extend(br.get_bits(sz), sz));
+            ++k;
+        }
+        return;
+    }
+    if (sc.ss == 0) {                                               // DC scan
+        if (sc.ah == 0) {
+            const int t = jpeg_decode_symbol(br, dc[c.td]);
+            if (t > 11) throw corrupt();
+            c.pred += jpeg_extend(br.get_bits(t), t);
+            blk[0] = static_cast<int16_t>(c.pred * (1 << sc.al));
+        } else if (br.get_bit()) {
+            blk[0] = static_cast<int16_t>(blk[0] | (1 << sc.al));
+        }
+        return;
+    }
+    if (sc.ah == 0) {                                               // AC band, first pass
+        if (sc.eobrun > 0) {
+            --sc.eobrun;
+            return;
+        }
+        for (int k = sc.ss; k <= sc.se;) {
+            const int rs = jpeg_decode_symbol(br, ac[c.ta]);
+            const int r = rs >> 4, sz = rs & 15;
+            if (sz == 0) {
+                if (r < 15) {
+                    sc.eobrun = (1 << r) - 1;
+                    if (r) sc.eobrun += br.get_bits(r);
+                    break;
+                }
+                k += 16;
+                continue;
+            }
+            k += r;
+            if (k > sc.se) throw corrupt();
+            blk[kZigzag[k]] = static_cast<int16_t>(jpeg_extend(br.get_bits(sz), sz) * (1 << sc.al));
+            ++k;
+        }
+        return;
+    }
+    // AC band, refinement pass: every coefficient that is already non-zero reads one correction bit; new
+    // coefficients (magnitude 1 << al) are placed after `r` still-zero positions
+    const int p1 = 1 << sc.al, m1 = -(1 << sc.al);
+    int k = sc.ss;
+    if (sc.eobrun == 0) {
+        for (; k <= sc.se; ++k) {
+            const int rs = jpeg_decode_symbol(br, ac[c.ta]);
+            int r = rs >> 4, value = 0;
+            const int sz = rs & 15;
+            if (sz) {
+                if (sz != 1) throw corrupt();
+                value = br.get_bit() ? p1 : m1;
+            } else if (r != 15) {
+                sc.eobrun = 1 << r;
+                if (r) sc.eobrun += br.get_bits(r);
+                break;
+            }
+            do {
+                int16_t* cf = blk + kZigzag[k];
+                if (*cf != 0) {
+                    jpeg_refine_nonzero(br, cf, p1, m1);
+                } else if (--r < 0) {
+                    break;
+                }
+                ++k;
+            } while (k <= sc.se);
+            if (value) {
+                if (k > sc.se) throw corrupt();
+                blk[kZigzag[k]] = static_cast<int16_t>(value);
+            }
+        }
+    }
+    if (sc.eobrun > 0) {
+        for (; k <= sc.se; ++k) {
+            int16_t* cf = blk + kZigzag[k];
+            if (*cf != 0) jpeg_refine_nonzero(br, cf, p1, m1);
+        }
+        --sc.eobrun;
+    }
+}
 
 at::Tensor decode_jpeg(const uint8_t* b, size_t n) {
     auto be16 = [&](size_t p) { return (static_cast<int>(b[p]) << 8) | b[p + 1]; };
@@ -268,8 +382,9 @@ at::Tensor decode_jpeg(const uint8_t* b, size_t n) {
     JpegHuff dc[4], ac[4];
     std::vector<JpegComp> comps;
     int width = 0, height = 0, restart = 0, hmax = 1, vmax = 1;
+    int mcus_x = 0, mcus_y = 0;
     size_t p = 2;
-    bool got_frame = false;
+    bool got_frame = false, progressive = false, got_scan = false;
     while (p + 4 <= n) {
         if (b[p] != 0xFF) throw std::invalid_argument("The JPEG marker stream is corrupt.");
         while (p < n && b[p] == 0xFF) ++p;
@@ -308,12 +423,14 @@ at::Tensor decode_jpeg(const uint8_t* b, size_t n) {
                 for (int i = 0; i < total; ++i) h.vals[i] = b[q++];
                 h.build();
             }
-        } else if (m == 0xC0 || m == 0xC1) {                        // SOF0 / SOF1
+        } else if (m == 0xC0 || m == 0xC1 || m == 0xC2) {           // SOF0 / SOF1 (sequential), SOF2 (progressive)
+            if (got_frame) throw std::invalid_argument("The JPEG file has more than one frame header.");
             if (b[seg] != 8) throw std::invalid_argument("Only 8-bit JPEG files are supported.");
+            progressive = m == 0xC2;
             height = be16(seg + 1);
             width = be16(seg + 3);
             const int nc = b[seg + 5];
-            if ((nc != 1 && nc != 3) || width <= 0 || height <= 0)
+            if ((nc != 1 && nc != 3) || width <= 0 || height <= 0 || seg + 6 + 3 * static_cast<size_t>(nc) > seg_end)
                 throw std::invalid_argument("Only grayscale and three-component JPEG files are supported.");
             comps.resize(nc);
             for (int i = 0; i < nc; ++i) {
@@ -326,71 +443,118 @@ at::Tensor decode_jpeg(const uint8_t* b, size_t n) {
                 hmax = std::max(hmax, comps[i].h);
                 vmax = std::max(vmax, comps[i].v);
             }
+            if (nc == 1) comps[0].h = comps[0].v = hmax = vmax = 1;  // a single component is never interleaved
+            mcus_x = (width + 8 * hmax - 1) / (8 * hmax);
+            mcus_y = (height + 8 * vmax - 1) / (8 * vmax);
+            for (auto& c : comps) {
+                c.blocks_w = mcus_x * c.h;
+                c.blocks_h = mcus_y * c.v;
+                c.bw = c.blocks_w * 8;
+                c.bh = c.blocks_h * 8;
+                c.own_bw = ((width * c.h + hmax - 1) / hmax + 7) / 8;
+                c.own_bh = ((height * c.v + vmax - 1) / vmax + 7) / 8;
+                c.coef.assign(static_cast<size_t>(c.blocks_w) * c.blocks_h * 64, 0);
+            }
             got_frame = true;
-        } else if (m == 0xC2 || (m >= 0xC5 && m <= 0xCF && m != 0xC8 && m != 0xCC)) {
-            throw std::invalid_argument("Progressive, lossless and arithmetic-coded JPEG files are not supported.");
+        } else if (m >= 0xC3 && m <= 0xCF && m != 0xC8 && m != 0xCC) {
+            throw std::invalid_argument("Lossless, hierarchical and arithmetic-coded JPEG files are not supported.");
         } else if (m == 0xDD) {                                     // DRI
             restart = be16(seg);
-        } else if (m == 0xDA) {                                     // SOS: the entropy-coded scan follows
+        } else if (m == 0xDA) {                                     // SOS: an entropy-coded scan follows
             if (!got_frame) throw std::invalid_argument("The JPEG file has no frame header before its scan.");
             const int ns = b[seg];
-            if (ns != static_cast<int>(comps.size()))
-                throw std::invalid_argument("Only single-scan (interleaved) JPEG files are supported.");
+            if (ns < 1 || ns > static_cast<int>(comps.size()) || seg + 1 + 2 * static_cast<size_t>(ns) + 3 > seg_end)
+                throw std::invalid_argument("The JPEG scan header is corrupt.");
+            std::vector<JpegComp*> in_scan;
             for (int i = 0; i < ns; ++i) {
                 const int cid = b[seg + 1 + 2 * i];
+                JpegComp* found = nullptr;
                 for (auto& c : comps)
-                    if (c.id == cid) {
-                        c.td = b[seg + 2 + 2 * i] >> 4;
-                        c.ta = b[seg + 2 + 2 * i] & 15;
-                    }
+                    if (c.id == cid) found = &c;
+                if (found == nullptr) throw std::invalid_argument("The JPEG scan names an unknown component.");
+                found->td = b[seg + 2 + 2 * i] >> 4;
+                found->ta = b[seg + 2 + 2 * i] & 15;
+                if (found->td > 3 || found->ta > 3) throw std::invalid_argument("The JPEG Huffman table index is invalid.");
+                in_scan.push_back(found);
             }
-            const int mcu_w = 8 * hmax, mcu_h = 8 * vmax;
-            const int mcus_x = (width + mcu_w - 1) / mcu_w, mcus_y = (height + mcu_h - 1) / mcu_h;
-            for (auto& c : comps) {
-                if (!qt_present[c.tq] || !dc[c.td].present || !ac[c.ta].present)
+            JpegScan sc;
+            sc.ss = b[seg + 1 + 2 * ns];
+            sc.se = b[seg + 2 + 2 * ns];
+            sc.ah = b[seg + 3 + 2 * ns] >> 4;
+            sc.al = b[seg + 3 + 2 * ns] & 15;
+            if (!progressive) {
+                sc = JpegScan{};
+            } else if (sc.ss > sc.se || sc.se > 63 || sc.al > 13 || (sc.ss == 0 && sc.se != 0) ||
+                       (sc.ss > 0 && ns != 1)) {
+                throw std::invalid_argument("The JPEG progressive scan parameters are invalid.");
+            }
+            for (JpegComp* c : in_scan) {
+                const bool need_dc = !progressive || (sc.ss == 0 && sc.ah == 0);
+                const bool need_ac = !progressive || sc.ss > 0;
+                if (!qt_present[c->tq] || (need_dc && !dc[c->td].present) || (need_ac && !ac[c->ta].present))
                     throw std::invalid_argument("The JPEG scan refers to a table that was not defined.");
-                c.bw = mcus_x * c.h * 8;
-                c.bh = mcus_y * c.v * 8;
-                c.plane.assign(static_cast<size_t>(c.bw) * c.bh, 0);
-                c.pred = 0;
+                c->pred = 0;
             }
             JpegBits br{b + seg_end, b + n};
             int until_restart = restart;
-            for (int my = 0; my < mcus_y; ++my)
-                for (int mx = 0; mx < mcus_x; ++mx) {
-                    if (restart && until_restart == 0) {
-                        br.reset();
-                        while (br.p + 1 < br.end && !(br.p[0] == 0xFF && br.p[1] >= 0xD0 && br.p[1] <= 0xD7)) ++br.p;
-                        br.p += 2;
-                        for (auto& c : comps) c.pred = 0;
-                        until_restart = restart;
-                    }
-                    for (auto& c : comps)
-                        for (int by = 0; by < c.v; ++by)
-                            for (int bx = 0; bx < c.h; ++bx) {
-                                float blk[64] = {0};
-                                const int t = jpeg_decode_symbol(br, dc[c.td]);
-                                if (t > 11) throw std::invalid_argument("The JPEG entropy-coded data is corrupt.");
-                                c.pred += jpeg_extend(br.get_bits(t), t);
-                                blk[0] = c.pred * qt[c.tq][0];
-                                for (int k = 1; k < 64;) {
-                                    const int rs = jpeg_decode_symbol(br, ac[c.ta]);
-                                    const int r = rs >> 4, sz = rs & 15;
-                                    if (sz == 0) {
-                                        if (r == 15) { k += 16; continue; }
-                                        break;
-                                    }
-                                    k += r;
-                                    if (k > 63) throw std::invalid_argument("The JPEG entropy-coded data is corrupt.");
-                                    const int z = kZigzag[k];
-                                    blk[z] = jpeg_extend(br.get_bits(sz), sz) * qt[c.tq][z];
-                                    ++k;
-                                }
-                                const int px = (mx * c.h + bx) * 8, py = (my * c.v + by) * 8;
-                                jpeg_idct8x8(blk, c.plane.data() + static_cast<size_t>(py) * c.bw + px, c.bw);
-                            }
-                    if (restart) --until_restart;
+            const auto maybe_restart = [&] {
+                if (restart && until_restart == 0) {
+                    br.reset();
+                    while (br.p + 1 < br.end && !(br.p[0] == 0xFF && br.p[1] >= 0xD0 && br.p[1] <= 0xD7)) ++br.p;
+                    br.p += 2;
+                    for (JpegComp* c : in_scan) c->pred = 0;
+                    sc.eobrun = 0;
+                    until_restart = restart;
                 }
+            };
+            if (ns == 1) {
+                // non-interleaved: the component's own blocks in raster order, one block per "MCU"
+                JpegComp& c = *in_scan[0];
+                for (int by = 0; by < c.own_bh; ++by)
+                    for (int bx = 0; bx < c.own_bw; ++bx) {
+                        maybe_restart();
+                        jpeg_decode_block(br, c, dc, ac, sc,
+                                          c.coef.data() + (static_cast<size_t>(by) * c.blocks_w + bx) * 64, progressive);
+                        if (restart) --until_restart;
+                    }
+            } else {
+                for (int my = 0; my < mcus_y; ++my)
+                    for (int mx = 0; mx < mcus_x; ++mx) {
+                        maybe_restart();
+                        for (JpegComp* c : in_scan)
+                            for (int by = 0; by < c->v; ++by)
+                                for (int bx = 0; bx < c->h; ++bx)
+                                    jpeg_decode_block(br, *c, dc, ac, sc,
+                                                      c->coef.data() + (static_cast<size_t>(my * c->v + by) * c->blocks_w +
+                                                                        mx * c->h + bx) * 64,
+                                                      progressive);
+                        if (restart) --until_restart;
+                    }
+            }
+            got_scan = true;
+            // the next marker sits after the entropy-coded bytes: skip stuffed 0xFF00 pairs and restart markers
+            size_t q = static_cast<size_t>(br.p - b);
+            if (q > seg_end && br.cnt == 0 && b[q - 1] == 0xFF) --q;   // the reader stopped on a marker's 0xFF
+            while (q + 1 < n && !(b[q] == 0xFF && b[q + 1] != 0 && !(b[q + 1] >= 0xD0 && b[q + 1] <= 0xD7))) ++q;
+            p = q;
+            continue;
+        }
+        p = seg_end;
+    }
+    if (!got_frame || !got_scan) throw std::invalid_argument("The JPEG file has no image scan.");
+    {
+        {
+            // dequantisation and inverse DCT of every block
+            for (auto& c : comps) {
+                c.plane.assign(static_cast<size_t>(c.bw) * c.bh, 0);
+                for (int by = 0; by < c.blocks_h; ++by)
+                    for (int bx = 0; bx < c.blocks_w; ++bx) {
+                        const int16_t* src = c.coef.data() + (static_cast<size_t>(by) * c.blocks_w + bx) * 64;
+                        float blk[64];
+                        for (int i = 0; i < 64; ++i) blk[i] = static_cast<float>(src[i]) * qt[c.tq][i];
+                        jpeg_idct8x8(blk, c.plane.data() + static_cast<size_t>(by) * 8 * c.bw + bx * 8, c.bw);
+                    }
+            }
             // chroma upsampling with the triangle filter ("3/4 near + 1/4 far", separable) on the valid part of each
             // plane, then colour conversion
             const int nc = static_cast<int>(comps.size());
@@ -445,9 +609,7 @@ at::Tensor decode_jpeg(const uint8_t* b, size_t n) {
                 }
             return out;
         }
-        p = seg_end;
     }
-    throw std::invalid_argument("The JPEG file has no image scan.");
 }
 
 }  // namespace

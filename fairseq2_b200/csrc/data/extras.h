@@ -103,7 +103,8 @@ private:
     std::optional<at::ScalarType> dtype_;
 };
 
-// PNG decoder (8/16-bit gray, gray+alpha, RGB, RGBA, palette; non-interlaced) -> {"image", "bit_depth", "format"}.
+// PNG (8/16-bit gray, gray+alpha, RGB, RGBA, palette; non-interlaced) and JPEG (sequential and progressive)
+// decoder -> {"image", "bit_depth", "format"}.
 class ImageDecoder {
 public:
     ImageDecoder() = default;

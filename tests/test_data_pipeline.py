@@ -307,7 +307,42 @@ def test_image_decoder_jpeg_matches_libjpeg() -> None:
         assert got.shape == ref.shape and out["bit_depth"] == 8.0
         assert np.abs(got.astype(int) - ref.astype(int)).max() <= 4, (mode, kw)
     with pytest.raises(Exception):
-        dec(MemoryBlock(b"\xff\xd8\xff\xc2\x00\x0b\x08\x00\x10\x00\x10\x01\x01\x11\x00"))      # progressive
+        dec(MemoryBlock(b"\xff\xd8\xff\xc2\x00\x0b\x08\x00\x10\x00\x10\x01\x01\x11\x00"))      # no scan
+
+
+def test_image_decoder_progressive_jpeg_matches_libjpeg() -> None:
+    """Progressive JPEG (DC/AC first and refinement scans, non-interleaved AC scans, optimised tables, restart
+    intervals) vs Pillow; the same pixels through the sequential and the progressive path agree exactly because
+    both reconstruct the same coefficients."""
+    import io
+
+    import numpy as np
+
+    PIL = pytest.importorskip("PIL.Image")
+    from fairseq2_b200.data.data_pipeline import MemoryBlock
+    from fairseq2_b200.data.image import ImageDecoder
+
+    rng = np.random.default_rng(0)
+    y, x = np.mgrid[0:131, 0:157]
+    rgb = np.stack([(x * 2 + y) % 256, (x + y * 3) % 256, (x * y // 7) % 256], -1).astype(np.float64)
+    rgb = np.clip(0.6 * rgb + 0.4 * np.roll(rgb, 5, 1) + rng.normal(0, 6, rgb.shape), 0, 255).astype(np.uint8)
+    dec = ImageDecoder()
+    cases = [("RGB", 0, 90, {}), ("RGB", 1, 75, {}), ("RGB", 2, 95, {}), ("L", 0, 85, {}),
+             ("RGB", 2, 60, {"restart_marker_blocks": 3}), ("L", 0, 98, {"restart_marker_rows": 2})]
+    for mode, sub, quality, extra in cases:
+        im = PIL.fromarray(rgb if mode == "RGB" else rgb[..., 1])
+        kw = {"subsampling": sub} if mode == "RGB" else {}
+        prog, seq = io.BytesIO(), io.BytesIO()
+        im.save(prog, format="JPEG", quality=quality, progressive=True, **kw, **extra)
+        im.save(seq, format="JPEG", quality=quality, progressive=False, **kw)
+        assert b"\xff\xc2" in prog.getvalue()
+        got = dec(MemoryBlock(prog.getvalue()))["image"].numpy()
+        ref = np.asarray(PIL.open(io.BytesIO(prog.getvalue())).convert(mode))
+        ref = ref if ref.ndim == 3 else ref[..., None]
+        assert got.shape == ref.shape
+        assert np.abs(got.astype(int) - ref.astype(int)).max() <= 4, (mode, sub, quality)
+        same = dec(MemoryBlock(seq.getvalue()))["image"].numpy()
+        assert np.array_equal(got, same), (mode, sub, quality)
 
 
 def test_read_text_reencodes_with_iconv(tmp_path) -> None:
