@@ -59,6 +59,9 @@ class ModelFamily(Generic[ModelT, ConfigT]):
     hg_exporter: Callable[[Mapping[str, Any], Any], tuple[dict[str, Any], dict[str, Any]]] | None = None
     supports_meta: bool = True
     supports_fsdp: bool = True
+    #: the factory builds every tensor-parallel layer (embedding, projections, output projection and loss) for
+    #: token-sharded activations when ``parallel.tp.sequence_parallel()`` is active
+    supports_sequence_parallel: bool = False
     restrict: bool = True
 
     # ------------------------------------------------------------------ config

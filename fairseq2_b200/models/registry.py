@@ -14,7 +14,7 @@ from fairseq2_b200.parallel.fsdp import layerwise_wrap_policy
 register_model_family(ModelFamily(
     name=LLAMA_FAMILY, kls=TransformerLM, config_kls=LLaMAConfig, factory=create_llama_model,
     state_dict_converter=convert_llama_state_dict, fsdp_wrap_policy=layerwise_wrap_policy,
-    layerwise_ac_applier=apply_layerwise_ac, hg_exporter=export_llama_to_hg))
+    layerwise_ac_applier=apply_layerwise_ac, hg_exporter=export_llama_to_hg, supports_sequence_parallel=True))
 
 
 def _register_lm_families() -> None:

@@ -204,22 +204,28 @@ class RecipeContext:
         except UnknownModelArchitectureError as ex:
             raise ModelArchitectureNotKnownError(str(ex)) from None
 
+        from fairseq2_b200.parallel.tp import sequence_parallel
+
+        gsec: GangSection = self._section("gang", GangSection)
+        seq_par = sequence_parallel(train and gangs.tp.size > 1 and gsec.sequence_parallel
+                                    and family.supports_sequence_parallel)
         use_fsdp = train and ts.data_parallelism == "fsdp" and gangs.dp.size >= 1
         static_mp = ts.mixed_precision.mode == "static" and use_fsdp
         build_dtype = ms.dtype
         load_weights = (card is not None and card.has_field("checkpoint")) or ms.path is not None
         new_init = not load_weights
-        if load_weights and not has_ckpt:
-            if ms.path is not None:
-                model = family.create_new_model(config, gangs, build_dtype)
-                family.load_into(model, Path(ms.path), config, gangs, mmap=ms.mmap)
+        with seq_par:
+            if load_weights and not has_ckpt:
+                if ms.path is not None:
+                    model = family.create_new_model(config, gangs, build_dtype)
+                    family.load_into(model, Path(ms.path), config, gangs, mmap=ms.mmap)
+                else:
+                    model = family.load_model(card, gangs, build_dtype, config=config, mmap=ms.mmap, store=store)
+                log.info("Model '{}' loaded.", ms.name or ms.path)
             else:
-                model = family.load_model(card, gangs, build_dtype, config=config, mmap=ms.mmap, store=store)
-            log.info("Model '{}' loaded.", ms.name or ms.path)
-        else:
-            # fresh weights (or weights that the training checkpoint will overwrite): build on the meta
-            # device when FSDP will materialise it unit by unit
-            model = family.create_new_model(config, gangs, build_dtype, meta=use_fsdp and family.supports_meta)
+                # fresh weights (or weights that the training checkpoint will overwrite): build on the meta
+                # device when FSDP will materialise it unit by unit
+                model = family.create_new_model(config, gangs, build_dtype, meta=use_fsdp and family.supports_meta)
         if recipe is not None:
             model = recipe.setup_model(self, model, new_init)
         if train:
@@ -497,4 +503,4 @@ class RecipeContext:
             publish_metrics_every_n_data_epochs=regime.publish_metrics_every_n_data_epochs,
             profiler=self.create_profiler(), garbage_collector=gc,
             device_stat_tracker=create_device_stat_tracker(self.device), anomaly_detection=ts.anomaly_detection,
-            hg_exporter=hg_exporter)
+            hg_exporter=hg_exporter, fuse_optimizer=ts.fuse_optimizer)

@@ -69,6 +69,11 @@ class GangSection:
     #: kernels behind the root gang's CUDA collectives: "symm" = peer-memory kernels over a symmetric arena,
     #: "nccl", or "auto" (symm inside one NVSwitch domain, NCCL otherwise)
     collectives: Literal["auto", "nccl", "symm"] = "auto"
+    #: training layout of tensor parallelism: the residual stream is sharded over the tokens between the blocks
+    #: and the column / row projections all-gather / reduce-scatter inside their GEMM kernels. The number of tokens
+    #: of a batch (its padded length) must then be a multiple of `tensor_parallel_size`. Evaluation and generation
+    #: models always keep their activations replicated.
+    sequence_parallel: bool = True
 
     def validate(self) -> ValidationResult:
         r = ValidationResult()
@@ -119,6 +124,9 @@ class TrainerSection:
     grad_accumulation: GradAccumulationSection = field(default_factory=GradAccumulationSection)
     activation_checkpointing: ActivationCheckpointingSection = field(default_factory=ActivationCheckpointingSection)
     max_grad_norm: float | None = None
+    #: without gradient clipping, loss scaling and gradient accumulation, FSDP runs each unit's optimizer step
+    #: inside the unit's gradient reduce-scatter kernel; ``False`` keeps the separate optimizer launches
+    fuse_optimizer: bool = True
     fp16_loss_scale: tuple[float, float] = (128.0, 0.0001)
     gc_every_n_steps: int | None = 1000
     grad_check: bool = False

@@ -236,7 +236,7 @@ class Trainer(Task):
                  publish_metrics_every_n_data_epochs: int | None = None, profiler: Any | None = None,
                  garbage_collector: Any | None = None, device_stat_tracker: Any | None = None,
                  anomaly_detection: bool = False, wall_watch: Stopwatch | None = None,
-                 hg_exporter: Any | None = None) -> None:
+                 hg_exporter: Any | None = None, fuse_optimizer: bool = True) -> None:
         from fairseq2_b200.metrics import MetricBag
 
         self._unit, self._reader, self._gangs = unit, data_reader, gangs
@@ -266,7 +266,7 @@ class Trainer(Task):
         self._metric_bag = MetricBag(device)
         self._step_fn = TrainStep(unit, optimizer, gangs, max_grad_norm=max_grad_norm, lr_scheduler=lr_scheduler,
                                   loss_scaler=loss_scaler, no_sync=no_sync_grad_accumulation,
-                                  metric_bag=self._metric_bag)
+                                  metric_bag=self._metric_bag, fuse_optimizer=fuse_optimizer)
         self._rng_bag = RngBag.from_device_defaults(torch.device("cpu"), device) if device.type == "cuda" \
             else RngBag.from_device_defaults(device)
         self._state = _State.NOT_STARTED
