@@ -35,6 +35,12 @@ class MoELMConfig:
     init_std: float | None = 0.02
     #: rows an expert-parallel inbox can hold, as a multiple of the mean load ``tokens * top_k`` per rank
     ep_capacity_factor: float = 2.0
+    #: expert parallelism over the data-parallel gang: every rank builds ``num_experts / size`` experts and the
+    #: tokens travel to them through the peer-memory dispatch / combine kernels (CUDA, 2 to 8 ranks of one node);
+    #: ``False`` replicates the experts like any other parameter
+    expert_parallel: bool = False
+    #: most tokens one rank routes per forward pass when ``expert_parallel`` (sizes the dispatch buffers)
+    ep_max_tokens: int = 16_384
 
 
 arch = ConfigRegistrar(MoELMConfig)

@@ -58,7 +58,32 @@ class MoELMFactory:
     def __init__(self, config: MoELMConfig, gangs: Gangs | None = None, *, ep: Any | None = None) -> None:
         self._config = config
         self._gangs = gangs if gangs is not None else get_current_gangs()
-        self._ep = ep
+        self._ep = ep if ep is not None else self._maybe_create_exchange()
+
+    def _maybe_create_exchange(self) -> Any | None:
+        """The expert-parallel exchange over the data-parallel gang when ``config.expert_parallel`` asks for it."""
+        c, dp = self._config, self._gangs.dp
+        if not c.expert_parallel or dp.size == 1:
+            return None
+        from fairseq2_b200.error import NotSupportedError
+        from fairseq2_b200.parallel.symm import SymmetricArena, symmetric_memory_available
+
+        if self._gangs.tp.size > 1:
+            raise NotSupportedError("Expert parallelism cannot be combined with tensor parallelism.")
+        if c.num_experts % dp.size:
+            raise NotSupportedError(f"`num_experts` ({c.num_experts}) must be a multiple of the data-parallel size "
+                                    f"({dp.size}) for expert parallelism.")
+        if not symmetric_memory_available(dp):
+            raise NotSupportedError("Expert parallelism needs 2 to 8 CUDA ranks with peer access (one NVSwitch domain).")
+        from fairseq2_b200.ops.moe_ep import ExpertParallelExchange
+
+        rows = c.ep_max_tokens * c.top_k
+        cap = int(c.ep_capacity_factor * rows)
+        per_box = (cap + 128 * (c.num_experts // dp.size + 2)) * c.model_dim * 2
+        with torch.device(dp.device):                       # the model itself may be under construction on "meta"
+            arena = SymmetricArena(dp.base_gang(), 2 * per_box + (8 << 20), wait_limit_s=120.0)  # type: ignore[arg-type]
+            return ExpertParallelExchange(arena, c.num_experts, c.model_dim, max_tokens=c.ep_max_tokens,
+                                          top_k=c.top_k, capacity=cap)
 
     def _init(self, p: Linear) -> None:
         std = self._config.init_std or p.weight.shape[1] ** -0.5
@@ -82,6 +107,12 @@ class MoELMFactory:
         final = Linear(c.model_dim, c.vocab_size, bias=False, init_fn=self._init)
         model = MoETransformerLM(c.model_dim, frontend, decoder, final, c.pad_idx, c.max_seq_len)
         model.aux_loss_coef = c.aux_loss_coef
+        if self._ep is not None:
+            from fairseq2_b200.models.transformer.experts import GroupedExpertNetwork
+
+            # each rank's experts are its own: the sharded data-parallel wrapper keeps them as rank-local units
+            model.fsdp_local_module_filter = lambda m: isinstance(m, GroupedExpertNetwork)
+            model.expert_parallel_exchange = self._ep
         return model
 
     def create_layer(self, idx: int, pe: RotaryEncoder) -> StandardTransformerLMDecoderLayer:

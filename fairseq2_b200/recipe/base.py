@@ -257,7 +257,8 @@ class RecipeContext:
                 from fairseq2_b200.parallel.fsdp import layerwise_wrap_policy as policy  # type: ignore[no-redef]
             return FSDP(model, gangs, wrap_policy=policy, param_dtype=param_dtype, fp32_reduce=ts.fsdp.fp32_reduce,
                         reshard_after_forward=ts.fsdp.reshard_after_forward, comm=ts.fsdp.comm,
-                        cpu_offload=ts.fsdp.cpu_offload, wait_limit_s=ts.fsdp.wait_limit)
+                        cpu_offload=ts.fsdp.cpu_offload, wait_limit_s=ts.fsdp.wait_limit,
+                        local_module_filter=getattr(model, "fsdp_local_module_filter", None))
         mp = ts.mixed_precision
         if (self.device.type == "cuda" and mp.mode in ("static", "auto") and mp.dtype == torch.bfloat16
                 and family.supports_fsdp and ts.ddp_flat_units):

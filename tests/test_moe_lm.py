@@ -78,3 +78,39 @@ def test_training_with_rank_local_expert_units() -> None:
         fsdp.after_optimizer_step()
         losses.append(float(loss))
     assert losses[-1] < 0.8 * losses[0]
+
+
+def test_expert_parallel_option_without_peers_keeps_replicated_experts() -> None:
+    from fairseq2_b200.gang import create_fake_gangs
+    from fairseq2_b200.models.moe_lm import create_moe_lm_model
+    from fairseq2_b200.models.moe_lm.config import tiny
+
+    cfg = tiny()
+    cfg.expert_parallel = True
+    model = create_moe_lm_model(cfg, create_fake_gangs(torch.device("cpu")))
+    assert not hasattr(model, "fsdp_local_module_filter")          # one rank: nothing to exchange
+
+
+def _ep_cpu_worker(rank: int, world: int):
+    from fairseq2_b200.error import NotSupportedError
+    from fairseq2_b200.gang import ProcessGroupGang, create_parallel_gangs
+    from fairseq2_b200.models.moe_lm import create_moe_lm_model
+    from fairseq2_b200.models.moe_lm.config import tiny
+
+    root = ProcessGroupGang.create_default_process_group(torch.device("cpu"))
+    cfg = tiny()
+    cfg.expert_parallel = True
+    try:
+        create_moe_lm_model(cfg, create_parallel_gangs(root))
+        out = "built"
+    except NotSupportedError as ex:
+        out = str(ex)
+    root.close()
+    return out
+
+
+def test_expert_parallel_option_on_cpu_ranks_is_refused() -> None:
+    from tests.dist_utils import run_distributed
+
+    for msg in run_distributed(_ep_cpu_worker, 2):
+        assert "peer access" in msg
