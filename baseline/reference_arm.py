@@ -32,6 +32,33 @@ def _unavailable(why: str) -> None:
         print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
 
 
+def _abort_marker() -> Path:
+    """One file per launch: all workers of a ``torch.distributed.run`` share their parent process."""
+    return Path("/tmp") / f"fs2_ref_abort_{os.environ.get('MASTER_PORT', '0')}_{os.getppid()}"
+
+
+def _watch_for_abort() -> None:
+    """A rank that fails (say, out of memory) leaves its peers inside collectives that never complete. It writes the
+    reason to the marker file; this thread, running on every rank, sees the file, lets rank 0 print the
+    ``unavailable`` line, and ends the process with exit code 0 so that the launcher returns at once."""
+    marker = _abort_marker()
+
+    def loop() -> None:
+        while True:
+            time.sleep(0.5)
+            try:
+                why = marker.read_text()
+            except OSError:
+                continue
+            if not why.endswith("\n"):
+                continue                                    # still being written
+            _unavailable(why.strip())
+            sys.stdout.flush()
+            os._exit(0)
+
+    threading.Thread(target=loop, daemon=True).start()
+
+
 def run_reference_arm(args: Namespace) -> None:
     ref_dir = HERE / "_ref"
     if not (ref_dir / "fairseq2").exists():
@@ -39,6 +66,13 @@ def run_reference_arm(args: Namespace) -> None:
         return
     sys.path.insert(0, str(HERE / "ref_shims"))
     sys.path.insert(0, str(ref_dir))
+    multi = int(os.environ.get("WORLD_SIZE", "1")) > 1
+    if multi:
+        try:
+            _abort_marker().unlink()
+        except OSError:
+            pass
+        _watch_for_abort()
     try:
         config = getattr(args, "config", "llama3_8b_fsdp")
         if config == "wav2vec2_large_ddp":
@@ -59,7 +93,17 @@ def run_reference_arm(args: Namespace) -> None:
         import traceback
 
         traceback.print_exc()
-        _unavailable(f"{type(ex).__name__}: {str(ex).splitlines()[0][:300] if str(ex) else ''}")
+        why = f"{type(ex).__name__}: {str(ex).splitlines()[0][:300] if str(ex) else ''}"
+        if multi:
+            # the peers are stuck in collectives: tell them (and rank 0, which prints the line) and leave
+            tmp = _abort_marker().with_suffix(f".{os.getpid()}")
+            tmp.write_text(why + "\n")
+            try:
+                os.replace(tmp, _abort_marker())
+            except OSError:
+                pass
+            time.sleep(3.0)                                 # the watcher thread of this rank ends the process
+        _unavailable(why)
 
 
 def _make_example(rng, seq_len: int, vocab: int):  # type: ignore[no-untyped-def]
@@ -140,7 +184,7 @@ def _run(args: Namespace) -> None:
 
     torch.manual_seed(2)
     if world > 1:
-        with torch.device("meta"), set_gangs(gangs), set_dtype(torch.float32):
+        with torch.device("meta"), set_gangs(gangs, meta=True), set_dtype(torch.float32):
             model = LLaMAFactory(cfg).create_model()
 
         def applier(m, wrapper):  # type: ignore[no-untyped-def]

@@ -77,8 +77,16 @@ def run(args: Namespace) -> None:
                       num_key_value_heads=8, ffn_inner_dim=int(8192 * 4 * 1.3), ffn_inner_dim_multiple_of=4096,
                       rope_theta=500_000.0, shard_embed_dim=False)
     torch.manual_seed(2)
-    with torch.device("meta"), set_gangs(gangs), set_dtype(torch.float32):
+    # as in the reference's own `ModelFamily._do_create_model`: the gangs must also be registered for the meta device,
+    # otherwise the layers built there see single-rank gangs and come out unsharded
+    with torch.device("meta"), set_gangs(gangs, meta=True), set_dtype(torch.float32):
         model = LLaMAFactory(cfg).create_model()
+    if tp > 1:
+        from fairseq2.nn import ColumnShardedLinear
+
+        q = model.decoder.layers[0].self_attn.q_proj
+        if not (isinstance(q, ColumnShardedLinear) and q.weight.shape[0] == cfg.model_dim // tp):
+            raise RuntimeError(f"the reference model is not tensor-parallel: q_proj weight {tuple(q.weight.shape)}")
     apply_ac_to_transformer_lm(model, every_nth_layer=1)
 
     def applier(m, wrapper):  # type: ignore[no-untyped-def]

@@ -141,6 +141,15 @@ def run(args: Namespace) -> None:
         model = TransformerLM(D, frontend, decoder, Linear(D, V, bias=False, init_fn=init), pad_idx=None,
                               max_seq_len=4096)
     model.train()
+    # Without activation checkpointing the full-size model does not fit this formulation (48 layers of padded
+    # per-expert batches and their fp32 autocast copies: out of memory at 177 GiB on a B200), so from 32 layers on
+    # every layer is checkpointed the way the reference recipes do it; the result line says so.
+    use_ac = L >= 32 or os.environ.get("FS2_BENCH_REF_AC") == "1"
+    if use_ac:
+        from fairseq2.models.transformer_lm.ac import apply_ac_to_transformer_lm
+
+        apply_ac_to_transformer_lm(model, every_nth_layer=1)
+        layers = list(model.decoder.layers)
     # FSDP2 on the dense parts, the way the reference's `to_fsdp2` applies `fully_shard` (bf16 parameters, fp32
     # reduction, one unit per layer, the root last); the expert weights differ from rank to rank and stay local
     mesh = torch.distributed.device_mesh.DeviceMesh.from_group(pg, "cuda")
@@ -214,6 +223,7 @@ def run(args: Namespace) -> None:
                "config": {"model": "moe_48l_2048d_128e_top8" if args.layers is None else f"moe[layers={L}]",
                           "global_batch": seqs_per_gpu * world, "seq_len": seq_len,
                           "parallelism": f"ep{world} (NCCL all_to_all_single + torch.bmm experts) + fsdp2 (dense parts)",
+                          "activation_checkpointing": "per layer (does not fit without)" if use_ac else False,
                           "note": "NCCL-only formulation: the reference has no expert parallelism of its own"},
                "e2e": {"value": units * args.steps / (e2e_ms * 1e-3), "unit": "tokens/s",
                        "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": examples[0].numel() * 8,

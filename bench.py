@@ -40,70 +40,9 @@ from benchmarks.harness import summarize_clocks as _summarize_clocks  # noqa: E4
 
 
 def _trace_steps(args: argparse.Namespace, step_fn, batches, rank: int, record: bool) -> None:  # type: ignore[no-untyped-def]
-    """Kernel timeline of two more steps (outside every timed region): one JSON row per kernel with stream, start
-    and duration in microseconds, for overlap analysis of the compute and communication streams."""
-    import torch
-    from torch.profiler import ProfilerActivity, profile
+    from benchmarks.harness import trace_steps
 
-    if not record:                       # the other ranks only take part in the collectives
-        for i, b in enumerate(batches):
-            step_fn([b], 10_000 + i)
-        torch.cuda.synchronize()
-        return
-    with profile(activities=[ProfilerActivity.CUDA]) as prof:
-        for i, b in enumerate(batches):
-            step_fn([b], 10_000 + i)
-        torch.cuda.synchronize()
-    raw = f"{args.trace}.rank{rank}.raw.json"
-    os.makedirs(os.path.dirname(os.path.abspath(raw)), exist_ok=True)
-    prof.export_chrome_trace(raw)
-    with open(raw) as fp:
-        events = json.load(fp)["traceEvents"]
-    os.remove(raw)
-    rows = [{"name": e["name"][:96], "ts": e["ts"], "dur": e["dur"], "stream": e.get("args", {}).get("stream")}
-            for e in events if e.get("cat") in ("kernel", "gpu_memcpy", "gpu_memset")]
-    path = f"{args.trace}.rank{rank}.json"
-    with open(path, "w") as fp:
-        json.dump(rows, fp)
-    # per-kernel totals, milliseconds per step (the trace covers len(batches) steps)
-    totals: dict[str, list[float]] = {}
-    for r in rows:
-        t = totals.setdefault(r["name"], [0.0, 0])
-        t[0] += r["dur"] / 1000.0 / len(batches)
-        t[1] += 1
-    # exposed communication: what the compute stream (the one that runs the GEMMs) spends idle between the first and
-    # the last kernel of the traced steps -- time in which the step waits for a collective, a copy or the host
-    by_stream: dict[object, list[tuple[float, float]]] = {}
-    gemm_us: dict[object, float] = {}
-    for r in rows:
-        by_stream.setdefault(r["stream"], []).append((r["ts"], r["ts"] + r["dur"]))
-        if "gemm" in r["name"]:
-            gemm_us[r["stream"]] = gemm_us.get(r["stream"], 0.0) + r["dur"]
-    stats = {}
-    if gemm_us:
-        cs = max(gemm_us, key=gemm_us.get)  # type: ignore[arg-type]
-        iv = sorted(by_stream[cs])
-        busy, cur_s, cur_e = 0.0, iv[0][0], iv[0][1]
-        for s_, e_ in iv[1:]:
-            if s_ > cur_e:
-                busy += cur_e - cur_s
-                cur_s, cur_e = s_, e_
-            else:
-                cur_e = max(cur_e, e_)
-        busy += cur_e - cur_s
-        span = iv[-1][1] - iv[0][0]
-        stats = {"compute_stream_idle_ms_per_step": (span - busy) / 1000.0 / len(batches),
-                 "compute_stream_busy_ms_per_step": busy / 1000.0 / len(batches),
-                 "gemm_ms_per_step": gemm_us[cs] / 1000.0 / len(batches),
-                 "other_streams_kernel_ms_per_step": sum(e_ - s_ for k_, v in by_stream.items() if k_ != cs
-                                                         for s_, e_ in v) / 1000.0 / len(batches)}
-        with open(f"{args.trace}.rank{rank}.overlap.json", "w") as fp:
-            json.dump(stats, fp)
-    with open(f"{args.trace}.rank{rank}.kernels.txt", "w") as fp:
-        fp.write(f"# kernel time per step (torch.profiler CUDA activity, {len(batches)} steps averaged)\n")
-        fp.write(f"TOTAL {sum(t[0] for t in totals.values()):.1f} ms/step\n")
-        for name, (ms, n) in sorted(totals.items(), key=lambda kv: -kv[1][0])[:40]:
-            fp.write(f"{ms:9.2f} ms {n // len(batches):6d}x  {name}\n")
+    trace_steps(args.trace, lambda i: step_fn([batches[i]], 10_000 + i), len(batches), rank, record)
 
 
 def run_ours(args: argparse.Namespace) -> None:
@@ -332,10 +271,18 @@ def main() -> None:
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
-    elif args.config != "llama3_8b_fsdp":
-        run_config(args)
-    else:
-        run_ours(args)
+        return
+    from benchmarks.harness import abort_peers, watch_for_abort
+
+    watch_for_abort()
+    try:
+        if args.config != "llama3_8b_fsdp":
+            run_config(args)
+        else:
+            run_ours(args)
+    except BaseException as ex:
+        abort_peers(f"{type(ex).__name__}: {ex}")
+        raise
 
 
 if __name__ == "__main__":

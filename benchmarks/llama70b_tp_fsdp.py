@@ -54,6 +54,10 @@ def run_ours(args: argparse.Namespace) -> None:
     apply_layerwise_ac(model, 1)
     fsdp = FSDP(model, gangs, param_dtype=torch.bfloat16, fp32_reduce=True, reshard_after_forward=True,
                 wait_limit_s=60.0)
+    if tp > 1:
+        from fairseq2_b200.parallel.tp import get_tp_context
+
+        get_tp_context(gangs.tp).prepare()                   # the tensor-parallel arena, before the optimizer state
     facade = DataParallelFacade(fsdp)
     optimizer = AdamW(fsdp.parameters(), lr=1e-5, betas=(0.9, 0.95), weight_decay=0.1)
 
@@ -96,7 +100,7 @@ def run_ours(args: argparse.Namespace) -> None:
                     examples=examples,
                     h2d_bytes=lambda ex: ex.tokens.numel() * 8 + ex.target_mask.numel() * 4
                     + (2 * len(ex.seq_lens) + 1 + seq_len) * 4,
-                    launch_counter=ext.launch_count, reset_launch_counter=ext.reset_launch_count)
+                    launch_counter=ext.launch_count, reset_launch_counter=ext.reset_launch_count, trace=args)
     ext.check_status()
     if rank == 0:
         fused_tp = bool(tp > 1 and __import__("fairseq2_b200.parallel.tp", fromlist=["x"]).get_tp_context(gangs.tp).arena)

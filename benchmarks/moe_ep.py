@@ -98,7 +98,7 @@ def run_ours(args: argparse.Namespace) -> None:
                     all_reduce_max=lambda t: root.all_reduce(t, ReduceOperation.MAX),
                     stage=lambda ex: ex.to(device, non_blocking=True), step=step, examples=examples,
                     h2d_bytes=lambda ex: ex.numel() * 8,
-                    launch_counter=ext.launch_count, reset_launch_counter=ext.reset_launch_count)
+                    launch_counter=ext.launch_count, reset_launch_counter=ext.reset_launch_count, trace=args)
     ext.check_status()
     dropped = ep.dropped.clone()
     root.all_reduce(dropped, ReduceOperation.SUM)

@@ -114,7 +114,7 @@ def run_ours(args: argparse.Namespace) -> None:
                     device=device, barrier=barrier,
                     all_reduce_max=lambda t: root.all_reduce(t, ReduceOperation.MAX), stage=stage, step=step,
                     examples=examples, h2d_bytes=lambda ex: ex[0].numel() * 4 + (len(ex[1]) + 1) * 4,
-                    launch_counter=ext.launch_count, reset_launch_counter=ext.reset_launch_count)
+                    launch_counter=ext.launch_count, reset_launch_counter=ext.reset_launch_count, trace=args)
     ext.check_status()
     tot = torch.tensor([samples_per_step], device=device, dtype=torch.float64)
     if world > 1:

@@ -524,6 +524,72 @@ std::tuple<Tensor, Tensor> w2v_contrastive_bwd(const Tensor& x, const Tensor& tg
     return {dx, dtgt};
 }
 
+// First wav2vec 2.0 feature-extractor layer: conv (1 input channel, kernel width 10) + bias [+ LayerNorm + GELU],
+// channels-last output [B, t_pad, C] with rows >= t_valid zeroed.
+bool w2v_first_conv_supported(int64_t C, int64_t kernel_width) {
+    return fs2::w2v_first_conv_supported(static_cast<int>(C), static_cast<int>(kernel_width));
+}
+
+namespace {
+const void* opt_ptr(const std::optional<Tensor>& t, int64_t C, const Tensor& like, const char* what) {
+    if (!t.has_value()) return nullptr;
+    TORCH_CHECK(t->is_cuda() && is_bf16(*t) && t->is_contiguous() && t->numel() == C && t->device() == like.device(),
+                "w2v_first_conv: `", what, "` must be a contiguous bf16 CUDA tensor of C elements");
+    return t->data_ptr();
+}
+}  // namespace
+
+Tensor w2v_first_conv_fwd(const Tensor& x, const Tensor& w, const std::optional<Tensor>& bias,
+                          const std::optional<Tensor>& lnw, const std::optional<Tensor>& lnb, int64_t stride,
+                          int64_t t_pad, double eps) {
+    TORCH_CHECK(x.is_cuda() && is_bf16(x) && x.dim() == 2 && x.is_contiguous() && w.is_cuda() && is_bf16(w) &&
+                    w.is_contiguous() && w.dim() == 2,
+                "w2v_first_conv_fwd: x must be a contiguous bf16 [B, L] waveform, w a contiguous bf16 [C, 10]");
+    const int64_t B = x.size(0), L = x.size(1), C = w.size(0), KW = w.size(1);
+    TORCH_CHECK(fs2::w2v_first_conv_supported(static_cast<int>(C), static_cast<int>(KW)) && stride >= 1 && L >= KW,
+                "w2v_first_conv_fwd: unsupported shape");
+    TORCH_CHECK(lnw.has_value() == lnb.has_value(), "w2v_first_conv_fwd: LayerNorm weight and bias come together");
+    const int64_t t_valid = (L - KW) / stride + 1;
+    TORCH_CHECK(t_pad >= t_valid, "w2v_first_conv_fwd: `t_pad` is smaller than the number of output positions");
+    c10::cuda::CUDAGuard guard(x.device());
+    Tensor y = at::empty({B, t_pad, C}, x.options());
+    fs2::w2v_first_conv_fwd(x.data_ptr(), w.data_ptr(), opt_ptr(bias, C, x, "bias"), opt_ptr(lnw, C, x, "ln weight"),
+                            opt_ptr(lnb, C, x, "ln bias"), y.data_ptr(), static_cast<int>(B), static_cast<int>(L),
+                            static_cast<int>(t_valid), static_cast<int>(t_pad), static_cast<int>(C),
+                            static_cast<int>(stride), static_cast<float>(eps), num_sms(x), stream_of(x));
+    g_launches += 1;
+    return y;
+}
+
+// returns fp32 (dw [C, 10], dbias [C], dlnw [C], dlnb [C]); entries for absent inputs are empty tensors
+std::tuple<Tensor, Tensor, Tensor, Tensor> w2v_first_conv_bwd(const Tensor& dy, const Tensor& x, const Tensor& w,
+                                                              const std::optional<Tensor>& bias,
+                                                              const std::optional<Tensor>& lnw,
+                                                              const std::optional<Tensor>& lnb, int64_t stride,
+                                                              double eps) {
+    TORCH_CHECK(dy.is_cuda() && is_bf16(dy) && dy.dim() == 3 && dy.is_contiguous() && x.is_contiguous() &&
+                    dy.size(0) == x.size(0) && dy.size(2) == w.size(0),
+                "w2v_first_conv_bwd: dy must be a contiguous bf16 [B, t_pad, C] tensor");
+    const int64_t B = x.size(0), L = x.size(1), C = w.size(0), KW = w.size(1), t_pad = dy.size(1);
+    const int64_t t_valid = (L - KW) / stride + 1;
+    TORCH_CHECK(t_pad >= t_valid, "w2v_first_conv_bwd: dy has fewer rows than output positions");
+    c10::cuda::CUDAGuard guard(x.device());
+    auto fopt = x.options().dtype(at::kFloat);
+    Tensor dw = at::zeros({C, KW}, fopt);
+    Tensor db = bias.has_value() ? at::zeros({C}, fopt) : at::empty({0}, fopt);
+    Tensor dlw = lnw.has_value() ? at::zeros({C}, fopt) : at::empty({0}, fopt);
+    Tensor dlb = lnb.has_value() ? at::zeros({C}, fopt) : at::empty({0}, fopt);
+    fs2::w2v_first_conv_bwd(x.data_ptr(), w.data_ptr(), opt_ptr(bias, C, x, "bias"), opt_ptr(lnw, C, x, "ln weight"),
+                            opt_ptr(lnb, C, x, "ln bias"), dy.data_ptr(), dw.data_ptr<float>(),
+                            bias.has_value() ? db.data_ptr<float>() : nullptr,
+                            lnw.has_value() ? dlw.data_ptr<float>() : nullptr,
+                            lnb.has_value() ? dlb.data_ptr<float>() : nullptr, static_cast<int>(B), static_cast<int>(L),
+                            static_cast<int>(t_valid), static_cast<int>(t_pad), static_cast<int>(C),
+                            static_cast<int>(stride), static_cast<float>(eps), num_sms(x), stream_of(x));
+    g_launches += 1;
+    return {dw, db, dlw, dlb};
+}
+
 // returns (q [R, E], hard_idx [R], sel [R], prob_sum [G, V], hard_count [G, V], y_soft [R, V] or empty)
 std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor, Tensor> w2v_quantize_fwd(const Tensor& logits,
                                                                             const std::optional<Tensor>& noise,
@@ -1470,6 +1536,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("grouped_gemm_wgrad", &grouped_gemm_wgrad);
     m.def("w2v_contrastive_fwd", &w2v_contrastive_fwd);
     m.def("w2v_contrastive_bwd", &w2v_contrastive_bwd);
+    m.def("w2v_first_conv_supported", &w2v_first_conv_supported);
+    m.def("w2v_first_conv_fwd", &w2v_first_conv_fwd);
+    m.def("w2v_first_conv_bwd", &w2v_first_conv_bwd);
     m.def("w2v_quantize_fwd", &w2v_quantize_fwd);
     m.def("w2v_quantize_bwd", &w2v_quantize_bwd);
     m.def("moe_ep_layout", &moe_ep_layout);

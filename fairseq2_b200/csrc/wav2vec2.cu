@@ -279,6 +279,257 @@ __global__ void __launch_bounds__(256) quantize_bwd_kernel(const T* __restrict__
     for (int e = lane; e < E; e += 32) atomicAdd(&de[e], to_f(dqr[e]));
 }
 
+
+// ------------------------------------------------- first feature-extractor layer (1 input channel)
+// y[b, t, :] = GELU(LayerNorm_c(conv1d(x[b, :], w, stride)[t, :] + bias)) written channels-last, or the bare
+// convolution + bias when the layer has no LayerNorm. With one input channel the layer is bound by writing its
+// output (C values per KW input samples), so everything between the waveform and the first channels-last
+// activation happens in registers: one warp per output position, lane l owns channels [(v * 32 + l) * 8, +8) for
+// v < NV; the weights sit transposed ([tap][channel], fp32) in shared memory. Rows t >= t_valid (padding that makes
+// later strides divide) are written as zeros.
+__device__ __forceinline__ float gelu_f(float u) { return 0.5f * u * (1.f + erff(u * 0.70710678118654752f)); }
+__device__ __forceinline__ float gelu_grad_f(float u) {
+    return 0.5f * (1.f + erff(u * 0.70710678118654752f)) + u * 0.3989422804014327f * __expf(-0.5f * u * u);
+}
+
+template <int NV, int KW>
+__device__ __forceinline__ void first_conv_row(const float* __restrict__ sw, const float* xk, int C, int lane,
+                                               float (*z)[8]) {
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        const int c0 = (v * 32 + lane) * 8;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) z[v][e] = 0.f;
+        if (c0 < C) {
+#pragma unroll
+            for (int k = 0; k < KW; ++k) {
+                const float4 a = *reinterpret_cast<const float4*>(sw + k * C + c0);
+                const float4 b = *reinterpret_cast<const float4*>(sw + k * C + c0 + 4);
+                z[v][0] += xk[k] * a.x; z[v][1] += xk[k] * a.y; z[v][2] += xk[k] * a.z; z[v][3] += xk[k] * a.w;
+                z[v][4] += xk[k] * b.x; z[v][5] += xk[k] * b.y; z[v][6] += xk[k] * b.z; z[v][7] += xk[k] * b.w;
+            }
+        }
+    }
+}
+
+template <int NV, int KW>
+__global__ void __launch_bounds__(256) first_conv_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                             const __nv_bfloat16* __restrict__ w,
+                                                             const __nv_bfloat16* __restrict__ bias,
+                                                             const __nv_bfloat16* __restrict__ lnw,
+                                                             const __nv_bfloat16* __restrict__ lnb,
+                                                             __nv_bfloat16* __restrict__ y, int B, int L, int t_valid,
+                                                             int t_pad, int C, int stride, float eps) {
+    extern __shared__ float sw[];                        // [KW][C]
+    for (int i = threadIdx.x; i < C * KW; i += blockDim.x) sw[(i % KW) * C + i / KW] = __bfloat162float(w[i]);
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const long long warp = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+    const long long nwarps = (gridDim.x * static_cast<long long>(blockDim.x)) >> 5;
+    float bv[NV][8], gw[NV][8], gb[NV][8];
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        const int c0 = (v * 32 + lane) * 8;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) bv[v][e] = gb[v][e] = 0.f, gw[v][e] = 1.f;
+        if (c0 < C) {
+            if (bias) load8(bias, c0, bv[v]);
+            if (lnw) load8(lnw, c0, gw[v]);
+            if (lnb) load8(lnb, c0, gb[v]);
+        }
+    }
+    const long long total = static_cast<long long>(B) * t_pad;
+    for (long long pos = warp; pos < total; pos += nwarps) {
+        const int b = static_cast<int>(pos / t_pad), t = static_cast<int>(pos % t_pad);
+        __nv_bfloat16* out = y + pos * C;
+        float z[NV][8];
+        if (t >= t_valid) {
+#pragma unroll
+            for (int v = 0; v < NV; ++v) {
+                const int c0 = (v * 32 + lane) * 8;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) z[v][e] = 0.f;
+                if (c0 < C) store8(out, c0, z[v]);
+            }
+            continue;
+        }
+        const float mine = lane < KW ? __bfloat162float(x[static_cast<long long>(b) * L + static_cast<long long>(t) * stride + lane]) : 0.f;
+        float xk[KW];
+#pragma unroll
+        for (int k = 0; k < KW; ++k) xk[k] = __shfl_sync(0xffffffffu, mine, k);
+        first_conv_row<NV, KW>(sw, xk, C, lane, z);
+        float sum = 0.f;
+#pragma unroll
+        for (int v = 0; v < NV; ++v)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                z[v][e] += bv[v][e];
+                sum += z[v][e];                           // lanes without channels hold zeros
+            }
+        if (lnw != nullptr) {
+            const float mean = warp_sum(sum) / C;
+            float var = 0.f;
+#pragma unroll
+            for (int v = 0; v < NV; ++v)
+                if ((v * 32 + lane) * 8 < C)
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) var += (z[v][e] - mean) * (z[v][e] - mean);
+            const float rstd = rsqrtf(warp_sum(var) / C + eps);
+#pragma unroll
+            for (int v = 0; v < NV; ++v)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) z[v][e] = gelu_f((z[v][e] - mean) * rstd * gw[v][e] + gb[v][e]);
+        }
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+            const int c0 = (v * 32 + lane) * 8;
+            if (c0 < C) store8(out, c0, z[v]);
+        }
+    }
+}
+
+// Backward of the above for channel slot blockIdx.y (the 256 channels whose gradients this pass accumulates): the
+// row is recomputed from the waveform, so the forward pass saves nothing but its inputs. Accumulators per lane:
+// dW [8][KW], dbias, dlnw, dlnb [8]; they are summed over the block in shared memory and added to the fp32 outputs.
+template <int NV, int KW>
+__global__ void __launch_bounds__(256) first_conv_bwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                             const __nv_bfloat16* __restrict__ w,
+                                                             const __nv_bfloat16* __restrict__ bias,
+                                                             const __nv_bfloat16* __restrict__ lnw,
+                                                             const __nv_bfloat16* __restrict__ lnb,
+                                                             const __nv_bfloat16* __restrict__ dy,
+                                                             float* __restrict__ dw, float* __restrict__ dbias,
+                                                             float* __restrict__ dlnw, float* __restrict__ dlnb, int B,
+                                                             int L, int t_valid, int t_pad, int C, int stride,
+                                                             float eps) {
+    extern __shared__ float sw[];                        // [KW][C] weights, then [(KW + 3)][256] block sums
+    float* sacc = sw + KW * C;
+    for (int i = threadIdx.x; i < C * KW; i += blockDim.x) sw[(i % KW) * C + i / KW] = __bfloat162float(w[i]);
+    for (int i = threadIdx.x; i < (KW + 3) * 256; i += blockDim.x) sacc[i] = 0.f;
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int slot = blockIdx.y;
+    const long long warp = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+    const long long nwarps = (gridDim.x * static_cast<long long>(blockDim.x)) >> 5;
+    float bv[NV][8], gw[NV][8], gb[NV][8];
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        const int c0 = (v * 32 + lane) * 8;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) bv[v][e] = gb[v][e] = 0.f, gw[v][e] = 1.f;
+        if (c0 < C) {
+            if (bias) load8(bias, c0, bv[v]);
+            if (lnw) load8(lnw, c0, gw[v]);
+            if (lnb) load8(lnb, c0, gb[v]);
+        }
+    }
+    float a_dw[8][KW], a_db[8], a_gw[8], a_gb[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        a_db[e] = a_gw[e] = a_gb[e] = 0.f;
+#pragma unroll
+        for (int k = 0; k < KW; ++k) a_dw[e][k] = 0.f;
+    }
+    const long long total = static_cast<long long>(B) * t_pad;
+    for (long long pos = warp; pos < total; pos += nwarps) {
+        const int b = static_cast<int>(pos / t_pad), t = static_cast<int>(pos % t_pad);
+        if (t >= t_valid) continue;
+        const float mine = lane < KW ? __bfloat162float(x[static_cast<long long>(b) * L + static_cast<long long>(t) * stride + lane]) : 0.f;
+        float xk[KW];
+#pragma unroll
+        for (int k = 0; k < KW; ++k) xk[k] = __shfl_sync(0xffffffffu, mine, k);
+        float z[NV][8], g[NV][8];
+        first_conv_row<NV, KW>(sw, xk, C, lane, z);
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+            const int c0 = (v * 32 + lane) * 8;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) g[v][e] = 0.f;
+            if (c0 < C) load8(dy + pos * C, c0, g[v]);
+        }
+        float dzs[8], xhs[8], gs[8];                     // this slot's dz, xhat and dLN-output
+        if (lnw != nullptr) {
+            float sum = 0.f;
+#pragma unroll
+            for (int v = 0; v < NV; ++v)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    z[v][e] += bv[v][e];
+                    sum += z[v][e];
+                }
+            const float mean = warp_sum(sum) / C;
+            float var = 0.f;
+#pragma unroll
+            for (int v = 0; v < NV; ++v)
+                if ((v * 32 + lane) * 8 < C)
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) var += (z[v][e] - mean) * (z[v][e] - mean);
+            const float rstd = rsqrtf(warp_sum(var) / C + eps);
+            float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+            for (int v = 0; v < NV; ++v)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float xh = (z[v][e] - mean) * rstd;
+                    const float go = g[v][e] * gelu_grad_f(xh * gw[v][e] + gb[v][e]);   // grad of the LN output
+                    z[v][e] = xh;
+                    g[v][e] = go;
+                    s1 += go * gw[v][e];
+                    s2 += go * gw[v][e] * xh;
+                }
+            s1 = warp_sum(s1) / C;
+            s2 = warp_sum(s2) / C;
+#pragma unroll
+            for (int v = 0; v < NV; ++v)
+                if (v == slot)
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        xhs[e] = z[v][e];
+                        gs[e] = g[v][e];
+                        dzs[e] = rstd * (g[v][e] * gw[v][e] - s1 - z[v][e] * s2);
+                    }
+        } else {
+#pragma unroll
+            for (int v = 0; v < NV; ++v)
+                if (v == slot)
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        xhs[e] = 0.f;
+                        gs[e] = 0.f;
+                        dzs[e] = g[v][e];
+                    }
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            a_db[e] += dzs[e];
+            a_gw[e] += gs[e] * xhs[e];
+            a_gb[e] += gs[e];
+#pragma unroll
+            for (int k = 0; k < KW; ++k) a_dw[e][k] += dzs[e] * xk[k];
+        }
+    }
+    // block sums in shared memory (lane l, element e -> column l * 8 + e of the slot), then one atomic per value
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        const int col = lane * 8 + e;
+#pragma unroll
+        for (int k = 0; k < KW; ++k) atomicAdd(sacc + k * 256 + col, a_dw[e][k]);
+        atomicAdd(sacc + KW * 256 + col, a_db[e]);
+        atomicAdd(sacc + (KW + 1) * 256 + col, a_gw[e]);
+        atomicAdd(sacc + (KW + 2) * 256 + col, a_gb[e]);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+        const int c = slot * 256 + i;
+        if (c >= C) continue;
+#pragma unroll
+        for (int k = 0; k < KW; ++k) atomicAdd(dw + c * KW + k, sacc[k * 256 + i]);
+        if (dbias) atomicAdd(dbias + c, sacc[KW * 256 + i]);
+        if (dlnw) atomicAdd(dlnw + c, sacc[(KW + 1) * 256 + i]);
+        if (dlnb) atomicAdd(dlnb + c, sacc[(KW + 2) * 256 + i]);
+    }
+}
+
 }  // namespace
 
 void w2v_contrastive_fwd(const void* x, const void* tgt, bool bf16, const int* distractors, int P, int K, int M,
@@ -340,6 +591,61 @@ void w2v_quantize_bwd(const void* dq, const void* entries, bool bf16, const floa
         quantize_bwd_kernel<float><<<blocks, 256, 0, st>>>(static_cast<const float*>(dq),
                                                            static_cast<const float*>(entries), y_soft, sel, R, G, V, E,
                                                            1.f / tau, dlogits, dentries);
+}
+
+
+namespace {
+
+template <int NV>
+void first_conv_fwd_nv(const void* x, const void* w, const void* bias, const void* lnw, const void* lnb, void* y, int B,
+                       int L, int t_valid, int t_pad, int C, int stride, float eps, int num_sms, cudaStream_t st) {
+    constexpr int KW = 10;
+    const size_t smem = static_cast<size_t>(KW) * C * sizeof(float);
+    auto kernel = first_conv_fwd_kernel<NV, KW>;
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    kernel<<<num_sms * 2, 256, smem, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+                                           static_cast<const __nv_bfloat16*>(bias),
+                                           static_cast<const __nv_bfloat16*>(lnw),
+                                           static_cast<const __nv_bfloat16*>(lnb), static_cast<__nv_bfloat16*>(y), B, L,
+                                           t_valid, t_pad, C, stride, eps);
+}
+
+template <int NV>
+void first_conv_bwd_nv(const void* x, const void* w, const void* bias, const void* lnw, const void* lnb, const void* dy,
+                       float* dw, float* dbias, float* dlnw, float* dlnb, int B, int L, int t_valid, int t_pad, int C,
+                       int stride, float eps, int num_sms, cudaStream_t st) {
+    constexpr int KW = 10;
+    const size_t smem = (static_cast<size_t>(KW) * C + (KW + 3) * 256) * sizeof(float);
+    auto kernel = first_conv_bwd_kernel<NV, KW>;
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    dim3 grid(num_sms, NV);
+    kernel<<<grid, 256, smem, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+                                    static_cast<const __nv_bfloat16*>(bias), static_cast<const __nv_bfloat16*>(lnw),
+                                    static_cast<const __nv_bfloat16*>(lnb), static_cast<const __nv_bfloat16*>(dy), dw,
+                                    dbias, dlnw, dlnb, B, L, t_valid, t_pad, C, stride, eps);
+}
+
+}  // namespace
+
+bool w2v_first_conv_supported(int C, int kernel_width) { return kernel_width == 10 && C % 8 == 0 && C >= 8 && C <= 1024; }
+
+void w2v_first_conv_fwd(const void* x, const void* w, const void* bias, const void* lnw, const void* lnb, void* y, int B,
+                        int L, int t_valid, int t_pad, int C, int stride, float eps, int num_sms, cudaStream_t st) {
+    const int nv = (C / 8 + 31) / 32;
+    if (nv == 1) first_conv_fwd_nv<1>(x, w, bias, lnw, lnb, y, B, L, t_valid, t_pad, C, stride, eps, num_sms, st);
+    else if (nv == 2) first_conv_fwd_nv<2>(x, w, bias, lnw, lnb, y, B, L, t_valid, t_pad, C, stride, eps, num_sms, st);
+    else if (nv == 3) first_conv_fwd_nv<3>(x, w, bias, lnw, lnb, y, B, L, t_valid, t_pad, C, stride, eps, num_sms, st);
+    else first_conv_fwd_nv<4>(x, w, bias, lnw, lnb, y, B, L, t_valid, t_pad, C, stride, eps, num_sms, st);
+}
+
+void w2v_first_conv_bwd(const void* x, const void* w, const void* bias, const void* lnw, const void* lnb, const void* dy,
+                        float* dw, float* dbias, float* dlnw, float* dlnb, int B, int L, int t_valid, int t_pad, int C,
+                        int stride, float eps, int num_sms, cudaStream_t st) {
+    const int nv = (C / 8 + 31) / 32;
+    if (nv == 1) first_conv_bwd_nv<1>(x, w, bias, lnw, lnb, dy, dw, dbias, dlnw, dlnb, B, L, t_valid, t_pad, C, stride, eps, num_sms, st);
+    else if (nv == 2) first_conv_bwd_nv<2>(x, w, bias, lnw, lnb, dy, dw, dbias, dlnw, dlnb, B, L, t_valid, t_pad, C, stride, eps, num_sms, st);
+    else if (nv == 3) first_conv_bwd_nv<3>(x, w, bias, lnw, lnb, dy, dw, dbias, dlnw, dlnb, B, L, t_valid, t_pad, C, stride, eps, num_sms, st);
+    else first_conv_bwd_nv<4>(x, w, bias, lnw, lnb, dy, dw, dbias, dlnw, dlnb, B, L, t_valid, t_pad, C, stride, eps, num_sms, st);
 }
 
 }  // namespace fs2

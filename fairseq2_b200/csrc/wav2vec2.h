@@ -27,4 +27,15 @@ void w2v_quantize_fwd(const void* logits, const float* noise, const void* entrie
 void w2v_quantize_bwd(const void* dq, const void* entries, bool bf16, const float* y_soft, const int* sel, int R, int G,
                       int V, int E, float tau, float* dlogits, float* dentries, cudaStream_t st);
 
+// First layer of the wav2vec 2.0 feature extractor (one input channel, kernel width 10): x [B, L] bf16 waveform,
+// w [C, 10], optional bias / LayerNorm weight and bias [C] -> y [B, t_pad, C] bf16 channels-last =
+// GELU(LayerNorm(conv + bias)) (bare conv + bias without LayerNorm); rows t >= t_valid are zero. The backward
+// recomputes the row from the waveform and accumulates into zero-initialised fp32 dw [C, 10], dbias, dlnw, dlnb [C].
+bool w2v_first_conv_supported(int C, int kernel_width);
+void w2v_first_conv_fwd(const void* x, const void* w, const void* bias, const void* lnw, const void* lnb, void* y, int B,
+                        int L, int t_valid, int t_pad, int C, int stride, float eps, int num_sms, cudaStream_t st);
+void w2v_first_conv_bwd(const void* x, const void* w, const void* bias, const void* lnw, const void* lnb, const void* dy,
+                        float* dw, float* dbias, float* dlnw, float* dlnb, int B, int L, int t_valid, int t_pad, int C,
+                        int stride, float eps, int num_sms, cudaStream_t st);
+
 }  // namespace fs2

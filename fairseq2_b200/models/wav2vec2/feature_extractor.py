@@ -131,22 +131,35 @@ class Wav2Vec2FeatureExtractor(SequenceFeatureExtractor):
                    and layer.group_norm is None for layer in self.layers[1:])
 
     def _forward_channels_last(self, x: Tensor) -> Tensor:
-        """The first convolution (few input channels) runs as usual; from then on activations stay channels-last
+        """The first layer (one input channel) is one fused kernel when it has a LayerNorm, else it runs as usual;
+        from then on activations stay channels-last
         ``(N, S, C)`` and every strided convolution is one tcgen05 GEMM over an overlapping-row view, followed by
         one fused LayerNorm+GELU kernel. Time steps are padded once so that every stride divides evenly; rows
         past the true output length are meaningless and cut off at the end."""
         from fairseq2_b200.ops.conv import conv1d_channels_last
         from fairseq2_b200.ops.norm import layer_norm_gelu
 
-        valid = x.shape[-1]
-        x = self.layers[0](x)                        # (N, C, S1)
-        valid = (valid - self.layers[0].conv.kernel_size[0]) // self.layers[0].conv.stride[0] + 1
+        from fairseq2_b200.ops.conv import first_conv_ln_gelu, first_conv_supported
+
+        first = self.layers[0]
+        valid = (x.shape[-1] - first.conv.kernel_size[0]) // first.conv.stride[0] + 1
         total_stride = 1
         for layer in self.layers[1:]:
             total_stride *= layer.conv.stride[0]
-        pad = (-x.shape[-1]) % total_stride
-        x = x.transpose(1, 2)
-        x = torch.nn.functional.pad(x, (0, 0, 0, pad)) if pad else x.contiguous()
+        pad = (-valid) % total_stride
+        wave = x[:, 0] if x.shape[1] == 1 else None
+        if (wave is not None and first.group_norm is None and first.layer_norm is not None
+                and first.layer_norm.weight is not None and first.layer_norm.bias is not None
+                and (first.dropout is None or not self.training or first.dropout.p == 0.0)
+                and first_conv_supported(wave, first.conv.weight)):
+            # one kernel: waveform -> conv + bias -> LayerNorm over the channels -> GELU -> channels-last, padded
+            ln = first.layer_norm
+            x = first_conv_ln_gelu(wave, first.conv.weight, first.conv.bias, ln.weight, ln.bias,
+                                   first.conv.stride[0], valid + pad, ln.eps)
+        else:
+            x = first(x)                             # (N, C, S1)
+            x = x.transpose(1, 2)
+            x = torch.nn.functional.pad(x, (0, 0, 0, pad)) if pad else x.contiguous()
         for layer in self.layers[1:]:
             k, s = layer.conv.kernel_size[0], layer.conv.stride[0]
             x = conv1d_channels_last(x, layer.conv.weight, layer.conv.bias, s)

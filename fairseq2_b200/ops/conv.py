@@ -93,3 +93,58 @@ def conv1d_channels_last(x: Tensor, weight: Tensor, bias: Tensor | None, stride:
         y = _Conv1dCL.apply(x, weight, stride)
         return y if bias is None else y + bias
     return conv1d_cl_reference(x, weight, bias, stride).to(x.dtype)
+
+
+# ---------------------------------------------------------------- first feature-extractor layer
+def first_conv_reference(x: Tensor, weight: Tensor, bias: Tensor | None, ln_weight: Tensor | None,
+                         ln_bias: Tensor | None, stride: int, t_pad: int, eps: float) -> Tensor:
+    """fp32 formulation of :func:`first_conv_ln_gelu` (any device): ``[B, L]`` -> ``[B, t_pad, C]``."""
+    y = F.conv1d(x.float().unsqueeze(1), weight.float(), None if bias is None else bias.float(), stride=stride)
+    y = y.transpose(1, 2)
+    if ln_weight is not None:
+        y = F.gelu(F.layer_norm(y, (y.shape[-1],), ln_weight.float(), None if ln_bias is None else ln_bias.float(), eps))
+    return F.pad(y, (0, 0, 0, t_pad - y.shape[1]))
+
+
+class _FirstConv(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, ln_weight, ln_bias, stride, t_pad, eps):  # type: ignore[no-untyped-def]
+        ext = require_ext()
+        w2 = weight.reshape(weight.shape[0], weight.shape[2]).contiguous()
+        ctx.save_for_backward(x, w2, bias, ln_weight, ln_bias)
+        ctx.meta = (stride, eps, weight.shape)
+        return ext.w2v_first_conv_fwd(x, w2, bias, ln_weight, ln_bias, stride, t_pad, eps)
+
+    @staticmethod
+    def backward(ctx, dy):  # type: ignore[no-untyped-def]
+        x, w2, bias, ln_weight, ln_bias = ctx.saved_tensors
+        stride, eps, wshape = ctx.meta
+        dw, db, dlw, dlb = require_ext().w2v_first_conv_bwd(dy.contiguous(), x, w2, bias, ln_weight, ln_bias, stride, eps)
+        return (None, dw.view(wshape).to(w2.dtype), None if bias is None else db.to(bias.dtype),
+                None if ln_weight is None else dlw.to(ln_weight.dtype),
+                None if ln_bias is None else dlb.to(ln_bias.dtype), None, None, None)
+
+
+def first_conv_supported(x: Tensor, weight: Tensor) -> bool:
+    return (use_kernels(x, weight) and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2
+            and weight.dim() == 3 and weight.shape[1] == 1 and not x.requires_grad
+            and require_ext().w2v_first_conv_supported(weight.shape[0], weight.shape[2])
+            and x.shape[1] >= weight.shape[2])
+
+
+def first_conv_ln_gelu(x: Tensor, weight: Tensor, bias: Tensor | None, ln_weight: Tensor | None,
+                       ln_bias: Tensor | None, stride: int, t_pad: int | None = None, eps: float = 1e-5) -> Tensor:
+    """First layer of the wav2vec 2.0 feature extractor in one kernel: ``x`` ``[B, L]`` waveform, ``weight``
+    ``[C, 1, k]`` -> channels-last ``[B, t_pad, C]`` = ``GELU(LayerNorm(conv1d(x) + bias))`` (the bare convolution
+    + bias when ``ln_weight`` is ``None``); rows past the ``(L - k) // stride + 1`` true outputs are zero. The layer
+    is bound by writing its output, so the convolution, the normalisation over the channels and the activation run
+    in registers between one read of the waveform and one write of the result; the backward recomputes the row from
+    the waveform (nothing but the inputs is saved) and produces the four parameter gradients. Replaces cuDNN
+    ``Conv1d`` + transpose + LayerNorm + GELU + transpose + pad
+    (fairseq2 ``models/wav2vec2/feature_extractor.py:129-172``)."""
+    t_valid = (x.shape[1] - weight.shape[2]) // stride + 1
+    if t_pad is None:
+        t_pad = t_valid
+    if first_conv_supported(x, weight):
+        return _FirstConv.apply(x.contiguous(), weight, bias, ln_weight, ln_bias, stride, t_pad, eps)
+    return first_conv_reference(x, weight, bias, ln_weight, ln_bias, stride, t_pad, eps).to(x.dtype)

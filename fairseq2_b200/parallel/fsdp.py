@@ -629,6 +629,9 @@ class FSDP(Module):
             from fairseq2_b200.parallel.symm import SymmetricArena, symmetric_memory_available
 
             if symmetric_memory_available(self.gang):
+                # the arena is allocated outside the caching allocator: hand back what materialising the units left
+                # cached (tens of GB for a 70B model), or the driver cannot find room for it
+                torch.cuda.empty_cache()
                 sharded = [u for u in self.all_units if u.world > 1]        # rank-local units stay out of the arena
                 need = sum((1 + W) * u.shard_size * 2 + 1024 for u in sharded) + (1 << 20)
                 if wait_limit_s is None:
@@ -658,6 +661,7 @@ class FSDP(Module):
                         for u in sharded:
                             u.rs_staging = staging
                     torch.cuda.synchronize(dev)
+                    torch.cuda.empty_cache()              # the private bf16 shards that moved into the arena
                     self.gang.barrier()
                 except Exception as ex:  # noqa: BLE001
                     if comm == "symm":

@@ -61,6 +61,7 @@ class TPContext:
         if not symmetric_memory_available(self.gang):
             return None
         mb = int(os.environ.get("FAIRSEQ2_B200_TP_ARENA_MB", "1536"))
+        torch.cuda.empty_cache()              # symmetric memory is allocated outside the caching allocator
         try:
             wait = float(os.environ.get("FAIRSEQ2_B200_WAIT_LIMIT_S", "120"))
             self.arena = SymmetricArena(self.gang, mb << 20, wait_limit_s=wait)  # type: ignore[arg-type]
@@ -68,6 +69,11 @@ class TPContext:
             log.warning("Symmetric memory is not usable for tensor parallelism ({}); using gang collectives.", ex)
             self.arena = None
         return self.arena
+
+    def prepare(self) -> bool:
+        """Creates the arena now (a collective call: every rank of the gang must make it) instead of inside the
+        first forward pass, e.g. while memory is still plentiful; returns whether the fused operators are usable."""
+        return self._ensure_arena() is not None
 
     def linears(self, like: Tensor, rows: int, dim: int) -> Any | None:
         """The fused operator set for token shards ``[rows, dim]`` (``like``: a bf16 CUDA tensor of the call), or

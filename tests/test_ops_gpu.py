@@ -556,6 +556,42 @@ def test_conv1d_channels_last_view_gemm(B: int, L: int, C: int, C_out: int, k: i
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("B,L,C,stride,with_ln,with_bias", [(3, 4003, 512, 5, True, True), (2, 1500, 256, 5, True, False),
+                                                            (2, 977, 768, 4, False, True), (1, 50_000, 512, 5, True, True)])
+def test_wav2vec2_first_conv_fused(B: int, L: int, C: int, stride: int, with_ln: bool, with_bias: bool) -> None:
+    """conv (1 input channel, width 10) + bias + LayerNorm + GELU in one kernel and its recomputing backward against
+    the fp32 formulation on the CPU: output (valid rows and zeroed padding) and all parameter gradients."""
+    from fairseq2_b200.ops.conv import first_conv_ln_gelu, first_conv_reference, first_conv_supported
+
+    torch.manual_seed(0)
+    k = 10
+    x = torch.randn(B, L, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(C, 1, k, device="cuda") * (2.0 / k) ** 0.5).to(torch.bfloat16).requires_grad_(True)
+    b = (0.1 * torch.randn(C, device="cuda")).to(torch.bfloat16).requires_grad_(True) if with_bias else None
+    lw = (1 + 0.1 * torch.randn(C, device="cuda")).to(torch.bfloat16).requires_grad_(True) if with_ln else None
+    lb = (0.1 * torch.randn(C, device="cuda")).to(torch.bfloat16).requires_grad_(True) if with_ln else None
+    assert first_conv_supported(x, w)
+    t_valid = (L - k) // stride + 1
+    t_pad = (t_valid + 63) // 64 * 64
+    y = first_conv_ln_gelu(x, w, b, lw, lb, stride, t_pad, 1e-5)
+    assert y.shape == (B, t_pad, C) and y.dtype == torch.bfloat16
+    params = [t for t in (w, b, lw, lb) if t is not None]
+    cpu = [t.detach().float().cpu().requires_grad_(True) for t in params]
+    it = iter(cpu)
+    wr = next(it)
+    br = next(it) if with_bias else None
+    lwr, lbr = (next(it), next(it)) if with_ln else (None, None)
+    ref = first_conv_reference(x.float().cpu(), wr, br, lwr, lbr, stride, t_pad, 1e-5)
+    assert _rel_err(y[:, :t_valid].float().cpu(), ref[:, :t_valid].detach()) < 1e-2
+    assert float(y[:, t_valid:].abs().max()) == 0.0 if t_pad > t_valid else True
+    g = torch.randn(B, t_pad, C, device="cuda", dtype=torch.bfloat16)
+    y.backward(g)
+    ref[:, :t_valid].backward(g[:, :t_valid].float().cpu())
+    for got, want in zip(params, cpu):
+        assert _rel_err(got.grad.float().cpu(), want.grad) < 2e-2, (got.shape, _rel_err(got.grad.float().cpu(), want.grad))
+
+
+@pytest.mark.gpu
 def test_layer_norm_gelu_fused() -> None:
     from fairseq2_b200.ops.norm import layer_norm_gelu
 
