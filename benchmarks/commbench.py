@@ -67,14 +67,14 @@ def main() -> None:
     peak = args.gemm_tflops
     if peak is None:
         try:
-            with open(os.path.join(os.path.dirname(__file__), "..", "..", "MEASURED_PEAKS.json")) as fp:
+            with open(os.path.join(os.path.dirname(__file__), "..", "MEASURED_PEAKS.json")) as fp:
                 peak = float(json.load(fp)["bf16_tflops"])
         except (OSError, KeyError, ValueError):
             peak = 1590.0
     link = args.link_gbs * 1e9
     hbm = 6.5e12
     try:
-        with open(os.path.join(os.path.dirname(__file__), "..", "..", "MEASURED_PEAKS.json")) as fp:
+        with open(os.path.join(os.path.dirname(__file__), "..", "MEASURED_PEAKS.json")) as fp:
             hbm = float(json.load(fp)["hbm_gbs"]) * 1e9
     except (OSError, KeyError, ValueError):
         pass
@@ -310,6 +310,67 @@ def main() -> None:
             emit("tp_mlp_70b_fwd_bwd_sequence_parallel_fused", ms, flops=flops,
                  nvlink_bytes=4 * (W - 1) / W * T * D2 * 2, baseline_ms=base_ms, tokens=T, model_dim=D2, inner_dim=F2,
                  note="baseline = replicated activations, same GEMM kernel, NCCL all-reduce forward and backward")
+
+    if want("moe_ep"):
+        # Expert-parallel dispatch and combine of one MoE layer of the 128-expert top-8 model: 8192 tokens per GPU,
+        # model dim 2048, near-uniform routing. ours: counts exchange + layout + rows stored straight into the
+        # owners' tile-aligned inboxes (dispatch), outputs loaded from the owners' outboxes and gate-weighted
+        # (combine). baseline: sort by expert + two NCCL all_to_all_single (counts, rows) and the inverse.
+        from fairseq2_b200.ops.moe import moe_route
+        from fairseq2_b200.ops.moe_ep import ExpertParallelExchange
+        from fairseq2_b200.parallel.symm import SymmetricArena as _Arena
+
+        E, k, Dm, Tm = 128, 8, 2048, 8192
+        if E % W == 0:
+            rows_total = Tm * k
+            cap = 2 * rows_total
+            ep_arena = _Arena(base, 2 * (cap + 128 * (E // W + 2)) * Dm * 2 + (8 << 20))
+            ep = ExpertParallelExchange(ep_arena, E, Dm, max_tokens=Tm, top_k=k, capacity=cap)
+            xm = torch.randn(Tm, Dm, device=dev, dtype=torch.bfloat16)
+            logits = torch.randn(Tm, E, device=dev) * 0.02
+            ids, gates, counts = moe_route(logits, k, softmax_gate=True)
+            state: dict[str, object] = {}
+
+            def disp() -> None:
+                state["out"] = ep.dispatch_padded(xm, ids, counts)
+
+            def comb() -> None:
+                rows, dest = state["out"][0], state["out"][1]     # type: ignore[index]
+                ep.combine(rows, dest, Tm, gates)
+
+            disp()
+            ms_d = _time(disp, barrier, args.iters)
+            ms_c = _time(comb, barrier, args.iters)
+            # NCCL formulation
+            El = E // W
+            flat = ids.reshape(-1).long()
+            def nccl_disp() -> None:
+                order = torch.argsort(flat, stable=True)
+                rows = xm.index_select(0, order // k)
+                per = torch.bincount(flat, minlength=E)
+                recv_per = torch.empty_like(per)
+                dist.all_to_all_single(recv_per, per, group=pg)
+                send = per.view(W, El).sum(1).tolist()
+                recv = recv_per.view(W, El).sum(1).tolist()
+                got = rows.new_empty((sum(recv), Dm))
+                dist.all_to_all_single(got, rows, recv, send, group=pg)
+                state["nccl"] = (got, order, send, recv)
+
+            def nccl_comb() -> None:
+                got, order, send, recv = state["nccl"]            # type: ignore[misc]
+                back = got.new_empty((sum(send), Dm))
+                dist.all_to_all_single(back, got, send, recv, group=pg)
+                w = gates.reshape(-1)[order].unsqueeze(1).to(back.dtype)
+                torch.zeros_like(xm).index_add_(0, order // k, back * w)
+
+            nccl_disp()
+            nd = _time(nccl_disp, barrier, args.iters)
+            nc = _time(nccl_comb, barrier, args.iters)
+            link_bytes = (W - 1) / W * rows_total * Dm * 2
+            emit("moe_ep_dispatch_128e_top8", ms_d, nvlink_bytes=link_bytes, hbm_bytes=2.0 * rows_total * Dm * 2,
+                 baseline_ms=nd, rows=rows_total, model_dim=Dm)
+            emit("moe_ep_combine_128e_top8", ms_c, nvlink_bytes=link_bytes, hbm_bytes=2.0 * rows_total * Dm * 2,
+                 baseline_ms=nc, rows=rows_total, model_dim=Dm)
 
     barrier()
     ext.check_status()

@@ -125,6 +125,23 @@ struct SeqInfo {
     int qb, ql, kb, kl, shift;
 };
 
+// Stateless dropout mask: the forward kernel and both backward kernels evaluate the same hash of (seed, head, global
+// query token, global key token), so no mask is stored. Two rounds of the murmur3 finaliser.
+__device__ __forceinline__ uint32_t mix32(uint32_t a) {
+    a ^= a >> 16;
+    a *= 0x85EBCA6Bu;
+    a ^= a >> 13;
+    a *= 0xC2B2AE35u;
+    a ^= a >> 16;
+    return a;
+}
+__device__ __forceinline__ bool dropout_keep(const AttnParams& p, int h, int qtok, int ktok) {
+    uint32_t a = mix32(static_cast<uint32_t>(qtok) ^ static_cast<uint32_t>(p.seed));
+    a = mix32(a + static_cast<uint32_t>(ktok) * 0x9E3779B1u + static_cast<uint32_t>(h) * 0x7F4A7C15u +
+              static_cast<uint32_t>(p.seed >> 32));
+    return a >= p.drop_threshold;
+}
+
 __device__ __forceinline__ SeqInfo seq_info(const AttnParams& p, int s) {
     SeqInfo i;
     i.qb = p.q_begins[s];
@@ -255,6 +272,19 @@ __global__ void __launch_bounds__(256, 1) attn_fwd_kernel(const AttnParams p) {
             }
         }
 
+        if (p.drop_threshold) {
+            // the normaliser above keeps every probability; only the product with V sees the dropped ones as zero
+#pragma unroll
+            for (int nb = 0; nb < BN / 8; ++nb) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int col = j * BN + nb * 8 + (lane & 3) * 2 + (e & 1);
+                    const int row = r_lo + (e >> 1) * 8;
+                    if (!dropout_keep(p, h, si.qb + row, si.kb + col)) acc_s[nb][e] = 0.f;
+                }
+            }
+        }
+
         // O += P V
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ++ks) {
@@ -287,7 +317,7 @@ __global__ void __launch_bounds__(256, 1) attn_fwd_kernel(const AttnParams p) {
     for (int r = 0; r < 2; ++r) {
         const int row = r_lo + r * 8;
         if (row >= si.ql) continue;
-        const float inv = row_sum[r] > 0.f ? 1.f / row_sum[r] : 0.f;
+        const float inv = (row_sum[r] > 0.f ? 1.f / row_sum[r] : 0.f) * (p.drop_threshold ? p.keep_scale : 1.f);
         __nv_bfloat16* og = p.o + static_cast<size_t>(si.qb + row) * p.o_tstride + static_cast<size_t>(h) * D;
 #pragma unroll
         for (int nb = 0; nb < NB_D; ++nb) {
@@ -401,6 +431,7 @@ __global__ void __launch_bounds__(128, 1) attn_bwd_dkv_kernel(const AttnParams p
         const float* delta = sDelta + buf * BM;
         const int mb = mb_start + it % iters_per_head;
         const int q0 = mb * BM;
+        const int h_cur = hk * G + it / iters_per_head;
 
         // S^T = K Q^T  (16 keys x 64 queries per warp)
         float acc_s[BM / 8][4];
@@ -436,8 +467,10 @@ __global__ void __launch_bounds__(128, 1) attn_bwd_dkv_kernel(const AttnParams p
                 const int qrow = q0 + qc;
                 const bool dead = key >= si.kl || (p.causal && key > qrow + si.shift);
                 const float pr = dead ? 0.f : exp2f(acc_s[nb][e] * sl2 - lse[qc] * LOG2E);
-                acc_s[nb][e] = pr;
-                acc_dp[nb][e] = pr * (acc_dp[nb][e] - delta[qc]) * p.scale;
+                float m = 1.f;
+                if (p.drop_threshold) m = dropout_keep(p, h_cur, si.qb + qrow, si.kb + key) ? p.keep_scale : 0.f;
+                acc_s[nb][e] = pr * m;                                   // dV sees the dropped probabilities
+                acc_dp[nb][e] = pr * (acc_dp[nb][e] * m - delta[qc]) * p.scale;
             }
         }
         // dV += P^T dO ; dK += dS^T Q      (k = query index)
@@ -582,7 +615,9 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_dq_kernel(const AttnParams p)
                 const int row = r_lo + r * 8;
                 const bool dead = col >= si.kl || (p.causal && col > row + si.shift);
                 const float pr = dead ? 0.f : exp2f(acc_s[nb][e] * sl2 - lse_r[r] * LOG2E);
-                acc_dp[nb][e] = pr * (acc_dp[nb][e] - delta_r[r]) * p.scale;
+                float m = 1.f;
+                if (p.drop_threshold) m = dropout_keep(p, h, si.qb + row, si.kb + col) ? p.keep_scale : 0.f;
+                acc_dp[nb][e] = pr * (acc_dp[nb][e] * m - delta_r[r]) * p.scale;
             }
         }
         // dQ += dS K   (k = key index)

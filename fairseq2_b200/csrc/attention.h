@@ -30,6 +30,12 @@ struct AttnParams {
     int causal;
     int window;    // > 0 (causal only): query i sees keys j with i + shift - window < j <= i + shift; 0 = no limit
     float scale;
+    // Dropout on the attention probabilities (mma.sync kernels only): an element (head, query token, key token) is
+    // kept iff hash(seed, head, q, k) >= drop_threshold, and kept elements are scaled by keep_scale = 1 / (1 - p).
+    // drop_threshold = 0 switches dropout off.
+    unsigned int drop_threshold;
+    float keep_scale;
+    unsigned long long seed;
 };
 
 // Return nullptr on success, else a static error string.

@@ -409,6 +409,55 @@ Tensor swiglu_fwd(const Tensor& gu) {
     return y;
 }
 
+// SwiGLU of separate gate / up matrices, bounded by a device-resident tile count (rows beyond stay untouched).
+namespace {
+const int* tiles_ptr(const std::optional<Tensor>& num_tiles, const Tensor& like) {
+    if (!num_tiles.has_value()) return nullptr;
+    TORCH_CHECK(num_tiles->is_cuda() && num_tiles->scalar_type() == at::kInt && num_tiles->numel() >= 1 &&
+                    num_tiles->device() == like.device(),
+                "`num_tiles` must be an int32 CUDA tensor on the same device");
+    return num_tiles->data_ptr<int>();
+}
+}  // namespace
+
+Tensor swiglu2_fwd(const Tensor& g, const Tensor& u, const std::optional<Tensor>& num_tiles) {
+    TORCH_CHECK(g.is_cuda() && is_bf16(g) && is_bf16(u) && g.dim() == 2 && g.is_contiguous() && u.is_contiguous() &&
+                    g.sizes() == u.sizes() && g.size(1) % 8 == 0 && aligned16(g) && aligned16(u),
+                "swiglu2_fwd: expects two contiguous bf16 [rows, F] matrices with F % 8 == 0");
+    c10::cuda::CUDAGuard guard(g.device());
+    Tensor y = at::empty_like(g);
+    fs2::swiglu2_fwd(g.data_ptr(), u.data_ptr(), y.data_ptr(), static_cast<size_t>(g.size(0)),
+                     static_cast<int>(g.size(1)), tiles_ptr(num_tiles, g), num_sms(g), stream_of(g));
+    g_launches += 1;
+    return y;
+}
+
+std::tuple<Tensor, Tensor> swiglu2_bwd(const Tensor& dy, const Tensor& g, const Tensor& u,
+                                       const std::optional<Tensor>& num_tiles) {
+    TORCH_CHECK(dy.is_cuda() && is_bf16(dy) && dy.is_contiguous() && g.is_contiguous() && u.is_contiguous() &&
+                    dy.sizes() == g.sizes() && g.sizes() == u.sizes() && aligned16(dy),
+                "swiglu2_bwd: bad input");
+    c10::cuda::CUDAGuard guard(g.device());
+    Tensor dg = at::empty_like(g), du = at::empty_like(u);
+    fs2::swiglu2_bwd(dy.data_ptr(), g.data_ptr(), u.data_ptr(), dg.data_ptr(), du.data_ptr(),
+                     static_cast<size_t>(g.size(0)), static_cast<int>(g.size(1)), tiles_ptr(num_tiles, g), num_sms(g),
+                     stream_of(g));
+    g_launches += 1;
+    return {dg, du};
+}
+
+void copy_rows_bounded(Tensor dst, const Tensor& src, const std::optional<Tensor>& num_tiles) {
+    TORCH_CHECK(dst.is_cuda() && src.is_cuda() && dst.dim() == 2 && dst.is_contiguous() && src.is_contiguous() &&
+                    dst.sizes() == src.sizes() && dst.scalar_type() == src.scalar_type() &&
+                    (dst.size(1) * dst.element_size()) % 16 == 0 && aligned16(dst) && aligned16(src),
+                "copy_rows_bounded: two contiguous [rows, D] matrices of the same type with 16-byte rows");
+    c10::cuda::CUDAGuard guard(dst.device());
+    fs2::copy_rows_bounded(dst.data_ptr(), src.data_ptr(), static_cast<size_t>(dst.size(0)),
+                           static_cast<size_t>(dst.size(1) * dst.element_size()), tiles_ptr(num_tiles, dst),
+                           num_sms(dst), stream_of(dst));
+    g_launches += 1;
+}
+
 Tensor swiglu_bwd(const Tensor& dy, const Tensor& gu) {
     TORCH_CHECK(dy.is_cuda() && is_bf16(dy) && dy.is_contiguous() && gu.is_contiguous() && dy.dim() == 2 &&
                     gu.size(0) == dy.size(0) && gu.size(1) == 2 * dy.size(1),
@@ -817,8 +866,9 @@ Tensor grouped_gemm(const Tensor& x, const Tensor& w, bool w_kn, const Tensor& t
                 "grouped_gemm: bad tile tables");
     check_status();
     c10::cuda::CUDAGuard guard(x.device());
-    // rows past the last tile (the buffer is sized for the worst case) are never written by the kernel
-    Tensor y = at::zeros({rows, N}, x.options());
+    // rows past the last tile (the buffer is sized for the worst case) are never written by the kernel and never read
+    // by a consumer: everything downstream is bounded by the same tile tables or indexes rows explicitly
+    Tensor y = at::empty({rows, N}, x.options());
     const char* err = fs2::gemm_grouped_bf16_tcgen05(
         x.data_ptr(), w.data_ptr(), y.data_ptr(), static_cast<int>(rows), static_cast<int>(N), static_cast<int>(K), w_kn,
         static_cast<int>(E), tile_row0.data_ptr<int>(), tile_expert.data_ptr<int>(), num_tiles.data_ptr<int>(),
@@ -994,9 +1044,21 @@ fs2::AttnParams make_attn_params(const Tensor& q, const Tensor& k, const Tensor&
     return p;
 }
 
+// Dropout on the attention probabilities; only the mma.sync kernels implement it.
+bool set_attn_dropout(fs2::AttnParams& p, double dropout_p, int64_t seed) {
+    TORCH_CHECK(dropout_p >= 0.0 && dropout_p < 1.0, "attention: `dropout_p` must be in [0, 1)");
+    if (dropout_p == 0.0) return false;
+    TORCH_CHECK(p.window == 0, "attention: dropout cannot be combined with a sliding window");
+    p.drop_threshold = static_cast<unsigned int>(std::min(4294967295.0, std::max(1.0, dropout_p * 4294967296.0)));
+    p.keep_scale = static_cast<float>(1.0 / (1.0 - dropout_p));
+    p.seed = static_cast<unsigned long long>(seed);
+    return true;
+}
+
 std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& qb,
                                     const Tensor& ql, const Tensor& kb, const Tensor& kl, int64_t max_q,
-                                    int64_t max_k, bool causal, double scale, int64_t window) {
+                                    int64_t max_k, bool causal, double scale, int64_t window, double dropout_p,
+                                    int64_t seed) {
     fs2::AttnParams p = make_attn_params(q, k, v, qb, ql, kb, kl, max_q, max_k, causal, scale);
     TORCH_CHECK(window >= 0 && (window == 0 || (causal && p.D == 128)),
                 "attn_fwd: a sliding window needs causal attention with head_dim 128");
@@ -1013,8 +1075,10 @@ std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tens
         const char* e = std::getenv("FAIRSEQ2_B200_ATTN");
         return e == nullptr || std::string(e) != "mma";
     }();
-    const char* err = ((use_tc || p.window > 0) && p.D == 128) ? fs2::attn_forward_tc(p, status_dev_ptr(), stream_of(q))
-                                                               : fs2::attn_forward(p, stream_of(q));
+    const bool dropout = set_attn_dropout(p, dropout_p, seed);
+    const char* err = ((use_tc || p.window > 0) && p.D == 128 && !dropout)
+                          ? fs2::attn_forward_tc(p, status_dev_ptr(), stream_of(q))
+                          : fs2::attn_forward(p, stream_of(q));
     TORCH_CHECK(err == nullptr, "attn_fwd: ", err);
     g_launches += 1;
     return {out, lse};
@@ -1023,7 +1087,7 @@ std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tens
 void attn_bwd_out(const Tensor& dout, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out,
                   const Tensor& lse, const Tensor& qb, const Tensor& ql, const Tensor& kb, const Tensor& kl,
                   int64_t max_q, int64_t max_k, bool causal, double scale, Tensor dq, Tensor dk, Tensor dv,
-                  int64_t window) {
+                  int64_t window, double dropout_p, int64_t seed) {
     fs2::AttnParams p = make_attn_params(q, k, v, qb, ql, kb, kl, max_q, max_k, causal, scale);
     TORCH_CHECK(window >= 0 && (window == 0 || (causal && p.D == 128)),
                 "attn_bwd: a sliding window needs causal attention with head_dim 128");
@@ -1056,8 +1120,10 @@ void attn_bwd_out(const Tensor& dout, const Tensor& q, const Tensor& k, const Te
         const char* e = std::getenv("FAIRSEQ2_B200_ATTN");
         return e == nullptr || (std::string(e) != "mma" && std::string(e) != "mma_bwd");
     }();
-    const char* err = ((use_tc || p.window > 0) && p.D == 128) ? fs2::attn_backward_tc(p, status_dev_ptr(), stream_of(q))
-                                                               : fs2::attn_backward(p, stream_of(q));
+    const bool dropout = set_attn_dropout(p, dropout_p, seed);
+    const char* err = ((use_tc || p.window > 0) && p.D == 128 && !dropout)
+                          ? fs2::attn_backward_tc(p, status_dev_ptr(), stream_of(q))
+                          : fs2::attn_backward(p, stream_of(q));
     TORCH_CHECK(err == nullptr, "attn_bwd: ", err);
     g_launches += 3;
 }
@@ -1065,12 +1131,14 @@ void attn_bwd_out(const Tensor& dout, const Tensor& q, const Tensor& k, const Te
 std::tuple<Tensor, Tensor, Tensor> attn_bwd(const Tensor& dout, const Tensor& q, const Tensor& k, const Tensor& v,
                                             const Tensor& out, const Tensor& lse, const Tensor& qb, const Tensor& ql,
                                             const Tensor& kb, const Tensor& kl, int64_t max_q, int64_t max_k,
-                                            bool causal, double scale, int64_t window) {
+                                            bool causal, double scale, int64_t window, double dropout_p,
+                                            int64_t seed) {
     // tokens outside every sequence (padding) receive zero gradients
     Tensor dq = at::zeros({q.size(0), q.size(1), q.size(2)}, q.options());
     Tensor dk = at::zeros({k.size(0), k.size(1), k.size(2)}, k.options());
     Tensor dv = at::zeros({v.size(0), v.size(1), v.size(2)}, v.options());
-    attn_bwd_out(dout, q, k, v, out, lse, qb, ql, kb, kl, max_q, max_k, causal, scale, dq, dk, dv, window);
+    attn_bwd_out(dout, q, k, v, out, lse, qb, ql, kb, kl, max_q, max_k, causal, scale, dq, dk, dv, window, dropout_p,
+                 seed);
     return {dq, dk, dv};
 }
 
@@ -1493,11 +1561,22 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("rstd"), py::arg("b_for_gelu") = std::nullopt);
     m.def("swiglu_fwd", &swiglu_fwd);
     m.def("swiglu_bwd", &swiglu_bwd);
+    m.def("swiglu2_fwd", &swiglu2_fwd, py::arg("g"), py::arg("u"), py::arg("num_tiles") = std::nullopt);
+    m.def("swiglu2_bwd", &swiglu2_bwd, py::arg("dy"), py::arg("g"), py::arg("u"), py::arg("num_tiles") = std::nullopt);
+    m.def("copy_rows_bounded", &copy_rows_bounded, py::arg("dst"), py::arg("src"), py::arg("num_tiles") = std::nullopt);
     m.def("rope_inplace", &rope_inplace);
     m.def("ce_fwd_bwd_inplace", &ce_fwd_bwd_inplace);
-    m.def("attn_fwd", &attn_fwd);
-    m.def("attn_bwd", &attn_bwd);
-    m.def("attn_bwd_out", &attn_bwd_out);
+    m.def("attn_fwd", &attn_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("q_begins"), py::arg("q_lens"),
+          py::arg("k_begins"), py::arg("k_lens"), py::arg("max_q"), py::arg("max_k"), py::arg("causal"),
+          py::arg("scale"), py::arg("window"), py::arg("dropout_p") = 0.0, py::arg("seed") = 0);
+    m.def("attn_bwd", &attn_bwd, py::arg("dout"), py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"),
+          py::arg("lse"), py::arg("q_begins"), py::arg("q_lens"), py::arg("k_begins"), py::arg("k_lens"),
+          py::arg("max_q"), py::arg("max_k"), py::arg("causal"), py::arg("scale"), py::arg("window"),
+          py::arg("dropout_p") = 0.0, py::arg("seed") = 0);
+    m.def("attn_bwd_out", &attn_bwd_out, py::arg("dout"), py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"),
+          py::arg("lse"), py::arg("q_begins"), py::arg("q_lens"), py::arg("k_begins"), py::arg("k_lens"),
+          py::arg("max_q"), py::arg("max_k"), py::arg("causal"), py::arg("scale"), py::arg("dq"), py::arg("dk"),
+          py::arg("dv"), py::arg("window"), py::arg("dropout_p") = 0.0, py::arg("seed") = 0);
     m.def("multi_tensor_adamw", &multi_tensor_adamw);
     m.def("refresh_status_guard", &refresh_status_guard);
     m.def("multi_tensor_l2_norm_sq", &multi_tensor_l2_norm_sq);

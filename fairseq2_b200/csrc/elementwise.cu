@@ -373,6 +373,57 @@ __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfl
     }
 }
 
+// Two-input form for operands that come from separate GEMMs (the experts' gate and up projections), bounded by a
+// device-resident row count: only the first `num_tiles[0] * 128` rows of the capacity-sized buffers hold data.
+__global__ void swiglu2_fwd_kernel(const __nv_bfloat16* __restrict__ g_, const __nv_bfloat16* __restrict__ u_,
+                                   __nv_bfloat16* __restrict__ y, size_t rows, int F, const int* __restrict__ num_tiles) {
+    if (num_tiles != nullptr) rows = min(rows, static_cast<size_t>(*num_tiles) * 128);
+    const size_t total = rows * (F / 8);
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        float g[8], u[8], o[8];
+        load8(g_, i * 8, g);
+        load8(u_, i * 8, u);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = g[e] * fast_sigmoid(g[e]) * u[e];
+        store8(y, i * 8, o);
+    }
+}
+
+__global__ void swiglu2_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ g_,
+                                   const __nv_bfloat16* __restrict__ u_, __nv_bfloat16* __restrict__ dg_,
+                                   __nv_bfloat16* __restrict__ du_, size_t rows, int F,
+                                   const int* __restrict__ num_tiles) {
+    if (num_tiles != nullptr) rows = min(rows, static_cast<size_t>(*num_tiles) * 128);
+    const size_t total = rows * (F / 8);
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        float g[8], u[8], d[8], dg[8], du[8];
+        load8(g_, i * 8, g);
+        load8(u_, i * 8, u);
+        load8(dy, i * 8, d);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float sg = fast_sigmoid(g[e]);
+            const float silu = g[e] * sg;
+            du[e] = d[e] * silu;
+            dg[e] = d[e] * u[e] * (sg + silu * (1.f - sg));
+        }
+        store8(dg_, i * 8, dg);
+        store8(du_, i * 8, du);
+    }
+}
+
+// dst[r] = src[r] for the first min(rows, num_tiles[0] * 128) rows (16-byte vectors).
+__global__ void copy_rows_bounded_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, size_t rows,
+                                         size_t vec_per_row, const int* __restrict__ num_tiles) {
+    if (num_tiles != nullptr) rows = min(rows, static_cast<size_t>(*num_tiles) * 128);
+    const size_t total = rows * vec_per_row;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x)
+        dst[i] = src[i];
+}
+
 __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ gu,
                                   __nv_bfloat16* __restrict__ dgu, size_t rows, int F) {
     const size_t nvec_row = F / 8;
@@ -738,6 +789,33 @@ void layer_norm_bwd(const void* dy, const void* x, const void* w, const float* m
     }
     reduce_partials_kernel<<<(D + 255) / 256, 256, 0, st>>>(dw_part, dw, grid, D);
     reduce_partials_kernel<<<(D + 255) / 256, 256, 0, st>>>(db_part, db, grid, D);
+}
+
+void swiglu2_fwd(const void* g, const void* u, void* y, size_t rows, int F, const int* num_tiles, int num_sms,
+                 cudaStream_t st) {
+    const size_t work = rows * (F / 8);
+    if (work == 0) return;
+    swiglu2_fwd_kernel<<<stream_grid(work, 256, num_sms), 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(g), static_cast<const __nv_bfloat16*>(u), static_cast<__nv_bfloat16*>(y), rows,
+        F, num_tiles);
+}
+
+void swiglu2_bwd(const void* dy, const void* g, const void* u, void* dg, void* du, size_t rows, int F,
+                 const int* num_tiles, int num_sms, cudaStream_t st) {
+    const size_t work = rows * (F / 8);
+    if (work == 0) return;
+    swiglu2_bwd_kernel<<<stream_grid(work, 256, num_sms), 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(g),
+        static_cast<const __nv_bfloat16*>(u), static_cast<__nv_bfloat16*>(dg), static_cast<__nv_bfloat16*>(du), rows, F,
+        num_tiles);
+}
+
+void copy_rows_bounded(void* dst, const void* src, size_t rows, size_t row_bytes, const int* num_tiles, int num_sms,
+                       cudaStream_t st) {
+    const size_t work = rows * (row_bytes / 16);
+    if (work == 0) return;
+    copy_rows_bounded_kernel<<<stream_grid(work, 512, num_sms), 512, 0, st>>>(
+        static_cast<uint4*>(dst), static_cast<const uint4*>(src), rows, row_bytes / 16, num_tiles);
 }
 
 void swiglu_fwd(const void* gu, void* y, size_t rows, int F, int num_sms, cudaStream_t st) {

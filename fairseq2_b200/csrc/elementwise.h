@@ -30,6 +30,15 @@ void embed_vocab_parallel_bwd(const long long* ids, const void* dout, float* dta
                               long long rows, float scale, cudaStream_t st);
 void swiglu_fwd(const void* gu, void* y, size_t rows, int F, int num_sms, cudaStream_t st);
 void swiglu_bwd(const void* dy, const void* gu, void* dgu, size_t rows, int F, int num_sms, cudaStream_t st);
+// SwiGLU on separate gate / up operands [rows, F]; `num_tiles` (device int, may be null) bounds the rows that hold
+// data to num_tiles[0] * 128. Same bound for the row copy (`row_bytes` a multiple of 16).
+void swiglu2_fwd(const void* g, const void* u, void* y, size_t rows, int F, const int* num_tiles, int num_sms,
+                 cudaStream_t st);
+void swiglu2_bwd(const void* dy, const void* g, const void* u, void* dg, void* du, size_t rows, int F,
+                 const int* num_tiles, int num_sms, cudaStream_t st);
+void copy_rows_bounded(void* dst, const void* src, size_t rows, size_t row_bytes, const int* num_tiles, int num_sms,
+                       cudaStream_t st);
+
 void rope_inplace(void* x, const float* freqs, const int* pos, size_t tokens, int heads, int D, size_t tstride,
                   size_t hstride, int max_pos, bool inverse, int num_sms, cudaStream_t st);
 void ce_fwd_bwd(void* logits, const long long* targets, const float* mask, float* row_loss, int rows, int V,

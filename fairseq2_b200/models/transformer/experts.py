@@ -66,7 +66,13 @@ class GroupedExpertNetwork(ExpertNetwork):
 
     def forward_padded(self, x: Tensor, layout: tuple[Tensor, Tensor, Tensor, Tensor]) -> Tensor:
         """``x`` in the 128-row padded expert-sorted layout: three single-launch grouped GEMMs, no host-side sizes."""
-        h = self.activation(grouped_mm_device(x, self.gate_proj, layout)) * grouped_mm_device(x, self.inner_proj, layout)
+        g, u = grouped_mm_device(x, self.gate_proj, layout), grouped_mm_device(x, self.inner_proj, layout)
+        if isinstance(self.activation, SiLU):
+            from fairseq2_b200.ops.moe import swiglu_gate_up
+
+            h = swiglu_gate_up(g, u, layout[3])                  # one pass over the rows that hold data
+        else:
+            h = self.activation(g) * u
         return grouped_mm_device(h, self.output_proj, layout)
 
 
@@ -202,11 +208,13 @@ class MoE(FeedForwardNetwork):
                 # host never waits for the routing result
                 rows, dest, layout, _ = self.ep.dispatch_padded(x, ids, counts, gates=gates)
                 rows_out = self.experts.forward_padded(rows, layout)
+                num_tiles = layout[3]
             else:
                 rows, dest, group_sizes = self.ep.dispatch(x, ids, counts, gates=gates)
                 rows_out = self.experts(rows, group_sizes.tolist())
+                num_tiles = None
             base = self.shared_expert(x) if self.shared_expert is not None else None
-            return self.ep.combine(rows_out, dest, x.shape[0], base=base).view(seqs.shape)
+            return self.ep.combine(rows_out, dest, x.shape[0], base=base, num_tiles=num_tiles).view(seqs.shape)
         if moe_ops.moe_kernels_available(x, logits):
             # fused top-k gate + histogram, gather/scale into expert order, experts, gather back per token
             ids, gates, counts = moe_ops.moe_route(logits, self.top_k, self.softmax_gate)

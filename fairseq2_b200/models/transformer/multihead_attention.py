@@ -402,7 +402,8 @@ class StandardMultiheadAttention(MultiheadAttention):
         window = getattr(bias, "attn_window_len", None)
         if window and self.head_dim != 128:        # the sliding window lives in the tcgen05 kernels only
             return None
-        if self.training and self.sdpa.dropout_p > 0.0:
+        drop = self.sdpa.dropout_p if self.training else 0.0
+        if drop > 0.0 and window:                  # dropout lives in the mma.sync kernels, the window in the others
             return None
         pe = self.pos_encoder
         if pe is not None and type(pe) is not RotaryEncoder:
@@ -419,7 +420,8 @@ class StandardMultiheadAttention(MultiheadAttention):
         out = qkv_rope_attention(flat, freqs, pos, layout.seq_begin_indices_pt[:-1], layout.seq_lens_pt,
                                  layout.max_seq_len, num_heads=H, num_kv_heads=Hkv,
                                  causal=isinstance(bias, CausalAttentionBias),
-                                 has_padding=layout.padded or sum(layout.seq_lens) < flat.shape[0], window=window)
+                                 has_padding=layout.padded or sum(layout.seq_lens) < flat.shape[0], window=window,
+                                 dropout_p=drop)
         out = out.flatten(-2, -1)
         if not layout.packed:
             out = out.view(*qkv.shape[:2], H * self.head_dim)

@@ -24,6 +24,7 @@ from torch.nn import Module
 from fairseq2_b200.models.transformer.attention_bias import (AttentionBias, AttentionBiasCache, CausalAttentionBias,
                                                               IdentityBias, materialize_attention_bias)
 from fairseq2_b200.nn.batch_layout import BatchLayout
+from fairseq2_b200.ops._ext import use_kernels
 from fairseq2_b200.ops.attention import varlen_attention
 
 
@@ -115,7 +116,10 @@ class VarlenSDPA(SDPA):
 
     def forward(self, q, q_layout, k, k_layout, v, bias_cache, *, needs_weights=False):  # type: ignore[override]
         supported = isinstance(self.bias, (IdentityBias, CausalAttentionBias))
-        if needs_weights or not supported or (self.training and self.dropout_p > 0.0):
+        drop = self.dropout_p if self.training else 0.0
+        kernel_dropout = (drop == 0.0 or (use_kernels(q) and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128)
+                                          and getattr(self.bias, "attn_window_len", None) is None))
+        if needs_weights or not supported or not kernel_dropout:
             return self._naive(q, q_layout, k, k_layout, v, bias_cache, needs_weights=needs_weights)
         causal = isinstance(self.bias, CausalAttentionBias)
         window = self.bias.attn_window_len if causal else None
@@ -126,7 +130,7 @@ class VarlenSDPA(SDPA):
             q2, k2, v2 = q.flatten(0, 1), k.flatten(0, 1), v.flatten(0, 1)
         out = varlen_attention(q2, k2, v2, q_layout.seq_begin_indices_pt[:-1], q_layout.seq_lens_pt,
                                k_layout.seq_begin_indices_pt[:-1], k_layout.seq_lens_pt, q_layout.max_seq_len,
-                               k_layout.max_seq_len, causal=causal, window=window)
+                               k_layout.max_seq_len, causal=causal, window=window, dropout_p=drop)
         if not packed:
             out = out.view(q.shape)
         return out, None

@@ -34,11 +34,25 @@ class Wav2Vec2Masker(Module):
     def forward(self, seqs: Tensor, seqs_layout: BatchLayout) -> tuple[Tensor, Tensor]:
         """Returns the masked sequences and the boolean temporal mask ``(N, S)`` (True = masked)."""
         n, s, m = seqs.shape
-        temporal = compute_row_mask((n, s), self.temporal_span_len, self.max_temporal_mask_prob,
-                                    row_lens=seqs_layout.seq_lens_pt, min_num_spans=self.min_num_temporal_mask_spans,
-                                    device=seqs.device)
-        if temporal is None:
-            raise ValueError("The temporal mask span length is too long for the given sequences.")
+        if seqs.is_cuda:
+            # The mask is a few thousand booleans whose construction needs several data-dependent sizes (spans per
+            # row, masked steps per row). Built on the device, each of them stalls the host until the feature
+            # extractor has finished, and the encoder behind it starts with an empty launch queue. The sequence
+            # lengths are known on the host, so the mask and the positions it selects are made there and copied.
+            host = compute_row_mask((n, s), self.temporal_span_len, self.max_temporal_mask_prob,
+                                    row_lens=torch.tensor(list(seqs_layout.seq_lens), dtype=torch.int64),
+                                    min_num_spans=self.min_num_temporal_mask_spans, device=torch.device("cpu"))
+            if host is None:
+                raise ValueError("The temporal mask span length is too long for the given sequences.")
+            temporal = host.to(seqs.device, non_blocking=True)
+            idx = host.flatten().nonzero().squeeze(1)
+            temporal._fs2_masked_rows = idx.to(seqs.device, non_blocking=True)  # type: ignore[attr-defined]
+        else:
+            temporal = compute_row_mask((n, s), self.temporal_span_len, self.max_temporal_mask_prob,
+                                        row_lens=seqs_layout.seq_lens_pt,
+                                        min_num_spans=self.min_num_temporal_mask_spans, device=seqs.device)
+            if temporal is None:
+                raise ValueError("The temporal mask span length is too long for the given sequences.")
         seqs = torch.where(temporal.unsqueeze(-1), self.temporal_mask_embed.to(seqs.dtype), seqs)
         if self.max_spatial_mask_prob > 0.0:
             spatial = compute_row_mask((n, m), self.spatial_span_len, self.max_spatial_mask_prob,
@@ -52,6 +66,10 @@ class Wav2Vec2Masker(Module):
     def extract_masked_elements(seqs: Tensor, temporal_mask: Tensor) -> Tensor:
         """``(N, S, M)`` -> ``(N, S_masked, M)``; every row of the mask selects the same number of steps."""
         n = seqs.shape[0]
+        rows = getattr(temporal_mask, "_fs2_masked_rows", None)
+        if rows is not None and rows.device == seqs.device:
+            # positions computed on the host together with the mask: a gather, no `nonzero` round trip
+            return seqs.flatten(0, 1).index_select(0, rows).unflatten(0, (n, -1))
         return seqs[temporal_mask].unflatten(0, (n, -1))
 
     def extra_repr(self) -> str:

@@ -88,9 +88,17 @@ class GumbelVectorQuantizer(VectorQuantizer):
         return VectorQuantizerOutput(q.view(bsz, tsz, -1), cb, G, V, code_perplexity, prob_perplexity, temp)
 
     def _current_temperature(self) -> float:
-        temp = max(self.max_temp * self.temp_decay ** int(self.num_updates), self.min_temp)
+        # `num_updates` lives on the device for checkpoints; reading it every step would stall the host until the
+        # whole forward pass has run. A host-side mirror is read instead and refreshed whenever the buffer may have
+        # changed behind our back (first use, checkpoint load, reset, a move to another device).
+        key = (self.num_updates.data_ptr(), self.num_updates._version)
+        if getattr(self, "_updates_key", None) != key:
+            self._updates_host = int(self.num_updates)
+        temp = max(self.max_temp * self.temp_decay ** self._updates_host, self.min_temp)
         if self.training:
             self.num_updates.add_(1)
+            self._updates_host += 1
+        self._updates_key = (self.num_updates.data_ptr(), self.num_updates._version)
         return temp
 
 

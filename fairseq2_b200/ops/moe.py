@@ -139,3 +139,27 @@ def load_balancing_loss(logits: Tensor, counts: Tensor, top_k: int) -> Tensor:
     probs = torch.softmax(logits.float(), dim=-1).mean(dim=0)
     frac = counts.to(torch.float32) / max(T * top_k, 1)
     return E * (frac.detach() * probs).sum()
+
+
+class _SwiGLU2(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, g: Tensor, u: Tensor, num_tiles: Tensor | None) -> Tensor:  # type: ignore[override]
+        g, u = g.contiguous(), u.contiguous()
+        ctx.save_for_backward(g, u, num_tiles if num_tiles is not None else g.new_empty(0))
+        ctx.bounded = num_tiles is not None
+        return require_ext().swiglu2_fwd(g, u, num_tiles)
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):  # type: ignore[override]
+        g, u, nt = ctx.saved_tensors
+        dg, du = require_ext().swiglu2_bwd(dy.contiguous(), g, u, nt if ctx.bounded else None)
+        return dg, du, None
+
+
+def swiglu_gate_up(g: Tensor, u: Tensor, num_tiles: Tensor | None = None) -> Tensor:
+    """``silu(g) * u`` for the separate gate / up outputs of the grouped expert GEMMs in one pass (and one pass
+    backward). ``num_tiles`` (device int32): only the first ``num_tiles * 128`` rows of the capacity-sized buffers
+    hold data; the rest is neither read nor written."""
+    if use_kernels(g, u) and g.dtype == torch.bfloat16 and g.dim() == 2 and g.shape[1] % 8 == 0:
+        return _SwiGLU2.apply(g, u, num_tiles)
+    return torch.nn.functional.silu(g) * u

@@ -133,9 +133,10 @@ class _PushPadded(torch.autograd.Function):
         a.ext.moe_ep_push(a.peer_ptrs, a.rank, x, expert_ids, gates, send_base, cursor, ep.inbox_off, dest,
                           ep.num_experts, ep.capacity, limit, ep.dropped)
         a.barrier(ep.SLOT, ep.next_epoch())                     # every rank's rows have landed in my inbox
-        rows = ep.inbox.clone()                                  # the inbox is reused by the next exchange
+        rows = torch.empty_like(ep.inbox)                        # the inbox is reused by the next exchange
+        a.ext.copy_rows_bounded(rows, ep.inbox, num_tiles)       # (only the rows that hold data are copied)
         ctx.ep, ctx.has_gates = ep, gates is not None
-        ctx.save_for_backward(x, gates if gates is not None else x.new_empty(0), dest)
+        ctx.save_for_backward(x, gates if gates is not None else x.new_empty(0), dest, num_tiles)
         ctx.mark_non_differentiable(dest, offsets, group_sizes, tile_row0, tile_expert, num_tiles, total)
         return rows, dest, offsets, group_sizes, tile_row0, tile_expert, num_tiles, total
 
@@ -143,8 +144,8 @@ class _PushPadded(torch.autograd.Function):
     def backward(ctx, d_rows: Tensor, *_: Tensor):  # type: ignore[override]
         ep: ExpertParallelExchange = ctx.ep
         a = ep.arena
-        x, gates, dest = ctx.saved_tensors
-        ep.outbox.copy_(d_rows)
+        x, gates, dest, num_tiles = ctx.saved_tensors
+        a.ext.copy_rows_bounded(ep.outbox, d_rows.contiguous(), num_tiles)
         a.barrier(ep.SLOT, ep.next_epoch())                     # every owner has published its row gradients
         dx = torch.empty_like(x)
         if ctx.has_gates:
@@ -162,27 +163,30 @@ class _PullPadded(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, ep: "ExpertParallelExchange", rows: Tensor, dest: Tensor, gates: Tensor | None,  # type: ignore[override]
-                base: Tensor | None, num_tokens: int) -> Tensor:
+                base: Tensor | None, num_tokens: int, num_tiles: Tensor | None = None) -> Tensor:
         a = ep.arena
-        ep.outbox.copy_(rows)
+        a.ext.copy_rows_bounded(ep.outbox, rows, num_tiles)
         a.barrier(ep.SLOT, ep.next_epoch())                     # every owner has published its expert outputs
         y = base.clone() if base is not None else torch.empty((num_tokens, rows.shape[1]), device=rows.device,
                                                               dtype=rows.dtype)
         a.ext.moe_ep_pull(a.peer_ptrs, a.rank, ep.outbox_off, dest, gates, y, None, None, ep.capacity, base is not None)
         a.barrier(ep.SLOT, ep.next_epoch())                     # outboxes may be overwritten again
-        ctx.ep, ctx.has_gates, ctx.has_base = ep, gates is not None, base is not None
-        ctx.save_for_backward(dest, gates if gates is not None else rows.new_empty(0), rows)
+        ctx.ep, ctx.has_gates, ctx.has_base, ctx.bounded = ep, gates is not None, base is not None, num_tiles is not None
+        ctx.save_for_backward(dest, gates if gates is not None else rows.new_empty(0),
+                              rows if gates is not None else rows.new_empty(0),
+                              num_tiles if num_tiles is not None else dest.new_empty(0))
         return y
 
     @staticmethod
     def backward(ctx, dy: Tensor):  # type: ignore[override]
         ep: ExpertParallelExchange = ctx.ep
         a = ep.arena
-        dest, gates, rows = ctx.saved_tensors
+        dest, gates, rows, num_tiles = ctx.saved_tensors
+        nt = num_tiles if ctx.bounded else None
         dy = dy.contiguous()
         dgates = None
         if ctx.has_gates:
-            ep.outbox.copy_(rows)
+            a.ext.copy_rows_bounded(ep.outbox, rows, nt)
             a.barrier(ep.SLOT, ep.next_epoch())
             dgates = torch.empty(dest.shape, device=dy.device, dtype=torch.float32)
             scratch = torch.empty_like(dy)
@@ -192,8 +196,10 @@ class _PullPadded(torch.autograd.Function):
         a.ext.moe_ep_push(a.peer_ptrs, a.rank, dy, None, gates if ctx.has_gates else None, None, None, ep.inbox_off,
                           dest, ep.num_experts, ep.capacity)
         a.barrier(ep.SLOT, ep.next_epoch())
-        d_rows = ep.inbox.clone()
-        return None, d_rows, None, dgates, (dy if ctx.has_base else None), None
+        # The row gradients are consumed straight from the inbox: the experts' backward runs before this rank
+        # reaches the barriers of the dispatch's backward, and no peer can start the exchange that next writes
+        # this inbox before it has passed those barriers.
+        return None, ep.inbox, None, dgates, (dy if ctx.has_base else None), None, None
 
 
 class ExpertParallelExchange:
@@ -242,11 +248,12 @@ class ExpertParallelExchange:
         return _Push.apply(self, x.contiguous(), g, expert_ids.contiguous(), counts.contiguous())
 
     def combine(self, rows: Tensor, dest: Tensor, num_tokens: int, gates: Tensor | None = None,
-                base: Tensor | None = None) -> Tensor:
-        """``y[t] = base[t] + sum_j gate[t, j] * rows_of_owner[dest[t, j]]`` (gate = 1 if not given)."""
+                base: Tensor | None = None, num_tiles: Tensor | None = None) -> Tensor:
+        """``y[t] = base[t] + sum_j gate[t, j] * rows_of_owner[dest[t, j]]`` (gate = 1 if not given). ``num_tiles``
+        (from the layout of :meth:`dispatch_padded`): only that many 128-row tiles of ``rows`` hold data."""
         g = gates.float().contiguous() if gates is not None else None
         if rows.shape[0] == self.capacity:
-            return _PullPadded.apply(self, rows.contiguous(), dest, g, base, num_tokens)
+            return _PullPadded.apply(self, rows.contiguous(), dest, g, base, num_tokens, num_tiles)
         return _Pull.apply(self, rows.contiguous(), dest, g, base, num_tokens)
 
     def dispatch_padded(self, x: Tensor, expert_ids: Tensor, counts: Tensor, gates: Tensor | None = None

@@ -307,15 +307,27 @@ class FlatParamUnit:
         are moved into the flat buffer; sinks written by GEMM epilogues are
         already in place."""
         assert self.grad_full is not None
+        copy_dst: list[Tensor] = []
+        copy_src: list[Tensor] = []
+        add_dst: list[Tensor] = []
+        add_src: list[Tensor] = []
         for s, cp in zip(self.specs, self.compute_params):
             if cp.grad is not None:
                 sink = cp.grad_sink  # type: ignore[attr-defined]
+                g = cp.grad if cp.grad.shape == sink.shape else cp.grad.view(sink.shape)
                 if cp.grad_sink_filled:  # type: ignore[attr-defined]
-                    sink.add_(cp.grad.to(sink.dtype))
+                    add_dst.append(sink)
+                    add_src.append(g if g.dtype == sink.dtype else g.to(sink.dtype))
                 else:
-                    sink.copy_(cp.grad)
+                    copy_dst.append(sink)
+                    copy_src.append(g)
                 cp.grad_sink_filled = True  # type: ignore[attr-defined]
                 cp.grad = None
+        # one multi-tensor launch per unit instead of one copy per bias / norm weight
+        if copy_dst:
+            torch._foreach_copy_(copy_dst, copy_src)
+        if add_dst:
+            torch._foreach_add_(add_dst, add_src)
 
     def reduce_grads(self, comm_stream: "torch.cuda.Stream | None", *, average: bool = True) -> None:
         """Reduce-scatters the flat gradient into ``grad_shard`` (mean over ranks)."""

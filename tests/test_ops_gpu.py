@@ -269,6 +269,74 @@ def test_attention_fwd_bwd(causal: bool, D: int, H: int, Hkv: int, lens: list[in
     assert _rel_err(v.grad, vr.grad) < 2e-2
 
 
+def _dropout_keep_mask(seed: int, H: int, q_tok: torch.Tensor, k_tok: torch.Tensor, p: float) -> torch.Tensor:
+    """Host restatement of the kernels' stateless dropout hash -> bool [H, Lq, Lk] (True = kept)."""
+    import numpy as np
+
+    def mix(a):  # type: ignore[no-untyped-def]
+        a = a.astype(np.uint32)
+        a ^= a >> np.uint32(16)
+        a = (a.astype(np.uint64) * np.uint64(0x85EBCA6B)).astype(np.uint32)
+        a ^= a >> np.uint32(13)
+        a = (a.astype(np.uint64) * np.uint64(0xC2B2AE35)).astype(np.uint32)
+        a ^= a >> np.uint32(16)
+        return a
+
+    lo, hi = np.uint32(seed & 0xFFFFFFFF), np.uint32((seed >> 32) & 0xFFFFFFFF)
+    q = q_tok.cpu().numpy().astype(np.uint32)[None, :, None]
+    k = k_tok.cpu().numpy().astype(np.uint64)[None, None, :]
+    h = np.arange(H, dtype=np.uint64)[:, None, None]
+    a = mix(q ^ lo).astype(np.uint64)
+    a = (a + k * np.uint64(0x9E3779B1) + h * np.uint64(0x7F4A7C15) + np.uint64(hi)).astype(np.uint32)   # mod 2^32
+    a = mix(a)
+    thr = np.uint32(min(4294967295.0, max(1.0, p * 4294967296.0)))
+    return torch.from_numpy(a >= thr)
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("D,H,Hkv", [(64, 4, 4), (128, 8, 2)])
+def test_attention_dropout_matches_masked_reference(causal: bool, D: int, H: int, Hkv: int) -> None:
+    """Dropout inside the attention kernels: forward and all gradients against the fp32 formulation that applies
+    the same (hash-derived) mask, plus the keep rate."""
+    torch.manual_seed(3)
+    lens, p_drop, seed = [150, 70, 257], 0.25, 0x1234_5678_9ABC
+    T = sum(lens)
+    q = torch.randn((T, H, D), device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn((T, Hkv, D), device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn((T, Hkv, D), device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    b, l = _seqs(lens)
+    out = varlen_attention(q, k, v, b, l, b, l, max(lens), max(lens), causal=causal, dropout_p=p_drop, seed=seed)
+    g = torch.randn_like(out)
+    out.backward(g)
+    qr, kr, vr = (t.detach().float().cpu().requires_grad_(True) for t in (q, k, v))
+    ref = torch.zeros(T, H, D)
+    kept = total = 0
+    off = 0
+    for n in lens:
+        tok = torch.arange(off, off + n)
+        mask = _dropout_keep_mask(seed, H, tok, tok, p_drop)
+        qs = qr[off:off + n].transpose(0, 1)
+        ks = kr[off:off + n].transpose(0, 1).repeat_interleave(H // Hkv, 0)
+        vs = vr[off:off + n].transpose(0, 1).repeat_interleave(H // Hkv, 0)
+        s = qs @ ks.transpose(1, 2) * D ** -0.5
+        if causal:
+            s = s.masked_fill(torch.triu(torch.ones(n, n, dtype=torch.bool), 1), float("-inf"))
+        pr = torch.softmax(s, -1) * mask / (1 - p_drop)
+        ref = ref + torch.nn.functional.pad((pr @ vs).transpose(0, 1), (0, 0, 0, 0, off, T - off - n))
+        kept += int(mask.sum())
+        total += mask.numel()
+        off += n
+    ref.backward(g.float().cpu())
+    assert abs(kept / total - (1 - p_drop)) < 0.01
+    assert _rel_err(out.float().cpu(), ref.detach()) < 1.5e-2
+    assert _rel_err(q.grad.float().cpu(), qr.grad) < 2.5e-2
+    assert _rel_err(k.grad.float().cpu(), kr.grad) < 2.5e-2
+    assert _rel_err(v.grad.float().cpu(), vr.grad) < 2.5e-2
+    # another seed gives another mask; p = 0 is the plain kernel
+    out2 = varlen_attention(q, k, v, b, l, b, l, max(lens), max(lens), causal=causal, dropout_p=p_drop, seed=seed + 1)
+    assert _rel_err(out2.float(), out.float()) > 0.1
+
+
 @pytest.mark.parametrize("causal", [True, False])
 def test_attention_long_sequences(causal: bool) -> None:
     """Many key/value tiles per query tile: exercises the ring phases of the tcgen05 forward kernel."""
@@ -744,3 +812,37 @@ def test_embed_vocab_parallel_kernel() -> None:
     out.backward(g)
     ref.backward(g.float())
     assert _rel_err(shard.grad.float(), sr.grad) < 1e-2
+
+
+@pytest.mark.gpu
+def test_swiglu_gate_up_and_bounded_copy() -> None:
+    """Two-input SwiGLU bounded by a device-resident tile count (fp32 oracle on the rows that hold data; rows beyond
+    the bound are neither read nor written) and the bounded row copy."""
+    from fairseq2_b200.ops import require_ext
+    from fairseq2_b200.ops.moe import swiglu_gate_up
+
+    torch.manual_seed(0)
+    rows, F, tiles = 1024, 768, 5
+    g = torch.randn(rows, F, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    u = torch.randn(rows, F, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    with torch.no_grad():
+        g[tiles * 128:] = float("nan")                          # must never be looked at
+    nt = torch.tensor([tiles], device="cuda", dtype=torch.int32)
+    y = swiglu_gate_up(g, u, nt)
+    n = tiles * 128
+    gr, ur = g.detach()[:n].float().cpu().requires_grad_(True), u.detach()[:n].float().cpu().requires_grad_(True)
+    ref = torch.nn.functional.silu(gr) * ur
+    assert _rel_err(y[:n].float().cpu(), ref.detach()) < 1e-2
+    dy = torch.randn(rows, F, device="cuda", dtype=torch.bfloat16)
+    y.backward(dy)
+    ref.backward(dy[:n].float().cpu())
+    assert _rel_err(g.grad[:n].float().cpu(), gr.grad) < 1.5e-2 and _rel_err(u.grad[:n].float().cpu(), ur.grad) < 1.5e-2
+    # unbounded form
+    y2 = swiglu_gate_up(g.detach()[:n], u.detach()[:n])
+    assert torch.equal(y2, y[:n])
+    src = torch.randn(rows, 256, device="cuda", dtype=torch.bfloat16)
+    dst = torch.full_like(src, 7.0)
+    require_ext().copy_rows_bounded(dst, src, nt)
+    assert torch.equal(dst[:n], src[:n]) and bool((dst[n:] == 7.0).all())
+    require_ext().copy_rows_bounded(dst, src)
+    assert torch.equal(dst, src)
