@@ -137,6 +137,7 @@ class FlatParamUnit:
         self.fused_step: dict[str, Any] | None = None
         self.fused_done = False
         self.reduced_in_step = False   # the unit's gradients were reduced since the last ``zero_grad``
+        self.ran_forward = False       # the unit's module ran in the current forward pass
         #: parameters whose gradients are partial sums over the tensor-parallel gang (set by FSDP)
         self.tp_partial_specs: list[_ParamSpec] = []
         self.tp_gang: Gang | None = None
@@ -337,14 +338,22 @@ class FlatParamUnit:
         self.reduced_in_step = True
         self.collect_autograd_grads()
         shared = self.world > 1 or getattr(self, "replica_arena", None) is not None or self.replicated
+        if not any(getattr(cp, "grad_sink_filled", False) for cp in self.compute_params):
+            # nothing of this unit ran on this rank in this pass (LayerDrop, an expert without tokens): the buffer
+            # is reused from step to step, so what it holds is the previous step's gradient
+            self.grad_full.zero_()
+            for cp in self.compute_params:
+                if getattr(cp, "grad_sink", None) is not None:
+                    cp.grad_sink_filled = True  # type: ignore[attr-defined]
         for i, (s, cp) in enumerate(zip(self.specs, self.compute_params)):
-            if getattr(cp, "grad_sink_filled", False) or (shared and s.requires_grad):
+            filled = getattr(cp, "grad_sink_filled", False)
+            if not filled and getattr(cp, "grad_sink", None) is not None:
+                cp.grad_sink.zero_()  # type: ignore[attr-defined]  # parameter took no part in this pass
+                cp.grad_sink_filled = True  # type: ignore[attr-defined]
+            if filled or (shared and s.requires_grad):
                 # with more than one rank a parameter counts as used when ANY rank may have used it: the reduced
                 # gradient then is the mean over the ranks and every rank must apply the same update
                 self.took_part[i] = True
-            elif getattr(cp, "grad_sink", None) is not None:
-                cp.grad_sink.zero_()  # type: ignore[attr-defined]  # parameter took no part in this pass
-                cp.grad_sink_filled = True  # type: ignore[attr-defined]
         W = self.world
         self.norm_fused = False
         if self.tp_partial_specs:
@@ -624,6 +633,8 @@ class FSDP(Module):
                 self.units.append(u)
         self.root_unit: FlatParamUnit | None = make_unit("", module, False)
         self.all_units = ([self.root_unit] if self.root_unit is not None else []) + self.units
+        self._unit_pos = {id(u): i for i, u in enumerate(self.units)}
+        self._canon_cursor = len(self.units) - 1
         # cast floating-point buffers (e.g. nothing for RoPE tables which stay fp32 by design)
         dev = self.all_units[0].device if self.all_units else torch.device("cpu")
         self.device = dev
@@ -738,6 +749,7 @@ class FSDP(Module):
     def _make_pre_forward(self, idx: int):  # type: ignore[no-untyped-def]
         def hook(m: Module, args: Any) -> None:
             u = self.units[idx]
+            u.ran_forward = True
             u.unshard(self.comm_stream, self.param_epoch)
             u.wait_unshard()
             if torch.is_grad_enabled():
@@ -787,14 +799,39 @@ class FSDP(Module):
     def _flush_pending_reduce(self) -> None:
         for u in self._pending_reduce:
             if self._require_sync:
+                self._reduce_skipped_units(self._unit_pos[id(u)])
                 u.reduce_grads(self.comm_stream)
             if u.world > 1:
                 u.reshard()
         self._pending_reduce.clear()
 
+    def _reduce_skipped_units(self, down_to: int) -> None:
+        """Every rank issues the units' gradient reductions in the same order -- last unit first -- although ranks
+        may run different subsets of the units in a step (LayerDrop with per-rank random numbers, experts no token
+        of this rank reached). The reductions are kernels that wait for their peers on one communication stream:
+        issued in different orders on two ranks, each rank's first kernel would wait for a peer kernel that is
+        queued behind the other rank's first one. So before unit ``down_to`` is reduced, the units after it that did
+        not run in this rank's forward pass (and therefore get no backward hook) take their turn with zero
+        gradients. The backward pass visits the units that did run in reverse order, which completes the order."""
+        if self.gang.size == 1 and self.replica_gang is None:
+            return
+        while self._canon_cursor > down_to:
+            v = self.units[self._canon_cursor]
+            self._canon_cursor -= 1
+            shared = (v.world > 1 or v.replicated) and not v.local_only
+            if (shared and not v.ran_forward and not v.reduced_in_step and v not in self._pending_reduce
+                    and any(sp.requires_grad for sp in v.specs)):
+                if not v.needs_reduce:
+                    v.prepare_grads()
+                v.reduce_grads(self.comm_stream)
+        self._canon_cursor = min(self._canon_cursor, down_to - 1)
+
     # ---------------------------------------------------------------- forward
     def forward(self, *args: Any, **kwargs: Any) -> Any:
         self._in_backward = False
+        self._canon_cursor = len(self.units) - 1
+        for u in self.units:
+            u.ran_forward = False
         if self.root_unit is not None:
             self.root_unit.unshard(self.comm_stream, self.param_epoch)
             self.root_unit.wait_unshard()
@@ -811,7 +848,8 @@ class FSDP(Module):
         self._flush_pending_reduce()
         if self._require_sync:
             multi = self.gang.size > 1 or self.replica_gang is not None
-            for u in self.all_units:
+            self._reduce_skipped_units(-1)            # units before the first one that ran, last to first
+            for u in self.units[::-1] + ([self.root_unit] if self.root_unit is not None else []):
                 if (not u.needs_reduce and multi and not u.reduced_in_step
                         and any(s.requires_grad for s in u.specs)):
                     # The unit did not run on this rank in this step (LayerDrop, an unused expert, a skipped

@@ -219,3 +219,68 @@ def test_fsdp_replica_only_layout_reduces_over_the_replica_gang() -> None:
     _, model = _build()
     fsdp = FSDP(model, gangs, param_dtype=torch.float32)
     assert fsdp.replica_gang is root and fsdp.gang.size == 1
+
+
+def _skipping_units_cpu_worker(rank: int, world: int, sharded: bool):
+    """Ranks run different subsets of the layers (LayerDrop with per-rank random numbers): the per-unit gradient
+    reductions are blocking collectives, so they only complete if every rank issues them in the same order."""
+    import torch.distributed as dist
+
+    from fairseq2_b200.gang import ProcessGroupGang, create_fsdp_gangs, create_parallel_gangs
+    from fairseq2_b200.parallel.fsdp import FSDP
+
+    dev = torch.device("cpu")
+    root = ProcessGroupGang.create_default_process_group(dev)
+    gangs = create_parallel_gangs(root)
+    if sharded:
+        gangs = create_fsdp_gangs(gangs)
+
+    class Net(torch.nn.Module):
+        def __init__(self) -> None:
+            super().__init__()
+            self.inp = torch.nn.Linear(16, 16)
+            self.layers = torch.nn.ModuleList(torch.nn.Linear(16, 16) for _ in range(6))
+            self.skip: set[int] = set()
+
+        def forward(self, x):  # type: ignore[no-untyped-def]
+            x = self.inp(x)
+            for i, layer in enumerate(self.layers):
+                if i not in self.skip:
+                    x = x + torch.tanh(layer(x))
+            return x
+
+    torch.manual_seed(0)
+    plain = Net()
+    model = Net()
+    model.load_state_dict(plain.state_dict())
+    fsdp = FSDP(model, gangs, param_dtype=torch.float32)
+    worst = 0.0
+    plans = [{0: {1, 4}, 1: {0, 4, 5}}, {0: {0, 1, 2, 3, 4, 5}, 1: set()}, {0: {5}, 1: {0}}]
+    for step, plan in enumerate(plans):
+        model.skip = plain.skip = plan.get(rank, set())
+        x = torch.randn(8, 16, generator=torch.Generator().manual_seed(10 * step + rank))
+        fsdp.zero_grad()
+        plain.zero_grad()
+        fsdp(x).pow(2).mean().backward()
+        fsdp.finish_backward()
+        plain(x).pow(2).mean().backward()
+        for u in fsdp.all_units:
+            for sp in u.specs:
+                if sp.rows_local == 0:
+                    continue
+                p = dict(plain.named_parameters())[sp.fqn]
+                g = (p.grad if p.grad is not None else torch.zeros_like(p)).clone()
+                dist.all_reduce(g)
+                want = (g / world).reshape(sp.d0, sp.row)[u.rank * sp.chunk: u.rank * sp.chunk + sp.rows_local]
+                got = u.grad_shard[sp.shard_off: sp.shard_off + sp.rows_local * sp.row].view(want.shape)
+                worst = max(worst, float((got - want).abs().max()))
+    root.close()
+    return worst
+
+
+def test_ranks_running_different_units_reduce_in_one_order() -> None:
+    """Replicated units only: with sharded units over process-group collectives the forward all-gathers are
+    collectives too, and ranks that skip different layers cannot pair them up (as with torch's FSDP); over the
+    symmetric arena the all-gathers are one-sided and the sharded case works (GPU test of the same name)."""
+    for worst in run_distributed(_skipping_units_cpu_worker, 2, False, timeout=120.0):
+        assert worst < 1e-5, worst

@@ -786,7 +786,9 @@ def test_grouped_gemm_single_launch_padded_layout() -> None:
     for e in range(E):
         ref[offsets[e]:offsets[e + 1]] = rr[offsets[e]:offsets[e + 1]] @ wr[e]
     ref.backward(g.float())
-    assert _rel_err(y.float(), ref.detach()) < 1e-2
+    used = int(layout[3]) * 128                # rows past the last tile are never written (nor read by a consumer)
+    assert offsets[-1] == used
+    assert _rel_err(y[:used].float(), ref[:used].detach()) < 1e-2
     assert _rel_err(w.grad.float(), wr.grad) < 1.5e-2
     assert float(w.grad[E - 1].abs().max()) == 0.0                                 # the empty expert gets a zero gradient
     # gradient reaching x through dispatch: sum_j gate * d_routed[inv]

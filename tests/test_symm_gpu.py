@@ -514,6 +514,86 @@ def test_vocab_parallel_embedding_push_matches_lookup(world: int) -> None:
         assert all(e < 1e-2 for e in errs), errs
 
 
+def _skipping_units_worker(rank: int, world: int, sharded: bool):
+    """Ranks run DIFFERENT subsets of the layers in a step (LayerDrop with per-rank random numbers): the per-unit
+    reductions must still pair up across ranks. Gradients after the reduction against the mean of the per-rank
+    gradients of a plain copy of the model."""
+    import torch.distributed as dist
+
+    from fairseq2_b200.gang import ProcessGroupGang, create_fsdp_gangs, create_parallel_gangs
+    from fairseq2_b200.ops import require_ext
+    from fairseq2_b200.parallel.fsdp import FSDP
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    os.environ["FAIRSEQ2_B200_DDP_ALLREDUCE"] = "p2p"
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    root = ProcessGroupGang.create_default_process_group(dev)
+    gangs = create_parallel_gangs(root)
+    if sharded:
+        gangs = create_fsdp_gangs(gangs)
+
+    class Net(torch.nn.Module):
+        def __init__(self) -> None:
+            super().__init__()
+            self.inp = torch.nn.Linear(256, 256)
+            self.layers = torch.nn.ModuleList(torch.nn.Linear(256, 256) for _ in range(6))
+            self.skip: set[int] = set()
+
+        def forward(self, x):  # type: ignore[no-untyped-def]
+            x = self.inp(x)
+            for i, layer in enumerate(self.layers):
+                if i not in self.skip:
+                    x = x + torch.tanh(layer(x))
+            return x
+
+    torch.manual_seed(0)
+    plain = Net().to(dev)
+    model = Net().to(dev)
+    model.load_state_dict(plain.state_dict())
+    fsdp = FSDP(model, gangs, param_dtype=torch.bfloat16, wait_limit_s=20.0)
+    errs = []
+    # step 0: rank 0 drops {1, 4}, rank 1 drops {0, 4, 5}, others nothing; step 1: rank-dependent single drops
+    plans = [{0: {1, 4}, 1: {0, 4, 5}}, {r: {(r + 2) % 6} for r in range(world)}]
+    for step, plan in enumerate(plans):
+        skip = plan.get(rank, set())
+        model.skip = plain.skip = skip
+        x = torch.randn(64, 256, generator=torch.Generator().manual_seed(10 * step + rank)).to(dev)
+        fsdp.zero_grad()
+        plain.zero_grad()
+        fsdp(x.to(torch.bfloat16)).float().pow(2).mean().backward()
+        fsdp.finish_backward()
+        plain.to(torch.bfloat16)(x.to(torch.bfloat16)).float().pow(2).mean().backward()
+        plain.float()
+        want = {}
+        for n, p in plain.named_parameters():
+            g = (p.grad if p.grad is not None else torch.zeros_like(p)).float()
+            dist.all_reduce(g)
+            want[n] = g / world
+        for u in fsdp.all_units:
+            for sp in u.specs:
+                if sp.rows_local == 0:
+                    continue
+                full = want[sp.fqn].reshape(sp.d0, sp.row)[u.rank * sp.chunk: u.rank * sp.chunk + sp.rows_local]
+                got = u.grad_shard[sp.shard_off: sp.shard_off + sp.rows_local * sp.row].float().view(full.shape)
+                if float(full.norm()) > 0:
+                    errs.append(_rel(got, full))
+                else:
+                    errs.append(float(got.abs().max()))
+    torch.cuda.synchronize()
+    require_ext().check_status()
+    root.close()
+    return max(errs)
+
+
+@pytest.mark.parametrize("world", WORLDS)
+@pytest.mark.parametrize("sharded", [False, True])
+def test_ranks_running_different_units_reduce_in_one_order(world: int, sharded: bool) -> None:
+    _need_gpus(world)
+    for worst in run_distributed(_skipping_units_worker, world, sharded):
+        assert worst < 2e-2, worst
+
+
 # ------------------------------------------------------------------ whole-model checks against an fp32 oracle
 def _small_llama_cfg():
     from fairseq2_b200.models.llama import LLaMAConfig
