@@ -59,7 +59,18 @@ class Wav2Vec2PositionEncoder(PositionEncoder):
         if state_bag is not None:
             raise ValueError("`Wav2Vec2PositionEncoder` does not support incremental decoding.")
         seqs = _zero_padding(seqs, seqs_layout)      # padding must not leak into the convolution
-        enc = self.conv(seqs.transpose(1, 2))
+        from fairseq2_b200.ops.conv import grouped_conv1d_channels_last, grouped_conv1d_supported
+
+        conv = self.conv
+        weight = conv.weight                         # evaluates the weight-norm parametrisation once
+        if grouped_conv1d_supported(seqs, weight, conv.groups):
+            # channels-last all the way: one tcgen05 GEMM per group over an overlapping-row view
+            enc = grouped_conv1d_channels_last(seqs, weight, conv.bias, conv.groups, conv.padding[0])
+            if self.remove_pad:
+                enc = enc[:, :-1]
+            return seqs + self.activation(enc)
+        enc = torch.nn.functional.conv1d(seqs.transpose(1, 2), weight, conv.bias, padding=conv.padding[0],
+                                         groups=conv.groups)
         if self.remove_pad:
             enc = enc[:, :, :-1]
         return seqs + self.activation(enc).transpose(1, 2)

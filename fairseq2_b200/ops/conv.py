@@ -148,3 +148,35 @@ def first_conv_ln_gelu(x: Tensor, weight: Tensor, bias: Tensor | None, ln_weight
     if first_conv_supported(x, weight):
         return _FirstConv.apply(x.contiguous(), weight, bias, ln_weight, ln_bias, stride, t_pad, eps)
     return first_conv_reference(x, weight, bias, ln_weight, ln_bias, stride, t_pad, eps).to(x.dtype)
+
+
+# ------------------------------------------------------------------------ grouped convolution
+def grouped_conv1d_supported(x: Tensor, weight: Tensor, groups: int) -> bool:
+    C_out, Cg, k = weight.shape
+    return (use_kernels(x, weight) and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 3
+            and groups > 1 and x.shape[2] == Cg * groups and C_out % groups == 0 and Cg % 8 == 0
+            and (C_out // groups) % 8 == 0)
+
+
+def grouped_conv1d_channels_last(x: Tensor, weight: Tensor, bias: Tensor | None, groups: int, padding: int) -> Tensor:
+    """Stride-1 grouped convolution over a channels-last signal: ``x`` ``[B, T, C]``, ``weight``
+    ``[C_out, C / groups, k]`` (the ``torch.nn.Conv1d`` layout), zero padding on both sides ->
+    ``[B, T + 2 * padding - k + 1, C_out]``.
+
+    The signal is copied once into a group-major, zero-padded layout ``[groups, B, T_p, C / groups]``; there the
+    patch matrix of a group is an overlapping-row view (row pitch ``C / groups``, row length ``k * C / groups``) and
+    the group's convolution is one tcgen05 GEMM of :func:`conv1d_channels_last`, as are its two gradients. For the
+    positional convolution of wav2vec 2.0 (k = 128, 16 groups of 64 channels) that is a ``[B * T_p, 8192] x [8192,
+    64]`` GEMM per group instead of cuDNN's grouped implicit-GEMM kernels
+    (fairseq2 ``models/wav2vec2/position_encoder.py:69-107``)."""
+    B, T, C = x.shape
+    C_out, Cg, k = weight.shape
+    if not grouped_conv1d_supported(x, weight, groups):
+        y = F.conv1d(x.transpose(1, 2), weight, bias, padding=padding, groups=groups)
+        return y.transpose(1, 2)
+    Og = C_out // groups
+    Tp = T + 2 * padding
+    xg = F.pad(x, (0, 0, padding, padding)).view(B, Tp, groups, Cg).permute(2, 0, 1, 3).contiguous()
+    outs = [conv1d_channels_last(xg[g], weight[g * Og:(g + 1) * Og], None, 1) for g in range(groups)]
+    y = torch.stack(outs, dim=2)[:, : Tp - k + 1].reshape(B, Tp - k + 1, C_out)      # rows past that are not outputs
+    return y if bias is None else y + bias

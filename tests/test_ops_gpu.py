@@ -848,3 +848,28 @@ def test_swiglu_gate_up_and_bounded_copy() -> None:
     assert torch.equal(dst[:n], src[:n]) and bool((dst[n:] == 7.0).all())
     require_ext().copy_rows_bounded(dst, src)
     assert torch.equal(dst, src)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,T,C,G,k", [(3, 200, 1024, 16, 128), (2, 77, 256, 4, 9)])
+def test_grouped_conv1d_channels_last(B: int, T: int, C: int, G: int, k: int) -> None:
+    """The grouped same-padded convolution of the wav2vec 2.0 position encoder as one view GEMM per group: output
+    and all gradients against ``F.conv1d`` in fp32 on the CPU."""
+    from fairseq2_b200.ops.conv import grouped_conv1d_channels_last, grouped_conv1d_supported
+
+    torch.manual_seed(0)
+    x = torch.randn(B, T, C, device="cuda", dtype=torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(C, C // G, k, device="cuda") * (k * C // G) ** -0.5).to(torch.bfloat16).requires_grad_(True)
+    b = (0.1 * torch.randn(C, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    assert grouped_conv1d_supported(x, w, G)
+    y = grouped_conv1d_channels_last(x, w, b, G, k // 2)
+    xr, wr, br = (t.detach().float().cpu().requires_grad_(True) for t in (x, w, b))
+    ref = torch.nn.functional.conv1d(xr.transpose(1, 2), wr, br, padding=k // 2, groups=G).transpose(1, 2)
+    assert y.shape == ref.shape
+    assert _rel_err(y.float().cpu(), ref.detach()) < 1e-2
+    g = torch.randn_like(y)
+    y.backward(g)
+    ref.backward(g.float().cpu())
+    assert _rel_err(x.grad.float().cpu(), xr.grad) < 2e-2
+    assert _rel_err(w.grad.float().cpu(), wr.grad) < 2e-2
+    assert _rel_err(b.grad.float().cpu(), br.grad) < 2e-2
