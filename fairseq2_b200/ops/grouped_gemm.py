@@ -74,6 +74,7 @@ class _GroupedMMDevice(torch.autograd.Function):
 
         y = require_ext().grouped_gemm(x.contiguous(), w, True, tile_row0, tile_expert, num_tiles)
         ctx.save_for_backward(x, w, offsets, tile_row0, tile_expert, num_tiles)
+        ctx.weight_ref = w if hasattr(w, "grad_sink") else None
         return y
 
     @staticmethod
@@ -87,7 +88,19 @@ class _GroupedMMDevice(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = ext.grouped_gemm(dy, w, False, tile_row0, tile_expert, num_tiles)      # dy @ w[e]^T: w read as [E, K, N] K-major
         if ctx.needs_input_grad[1]:
-            dw = ext.grouped_gemm_wgrad(x.contiguous(), dy, offsets).to(w.dtype)          # [E, K, N]
+            dw32 = ext.grouped_gemm_wgrad(x.contiguous(), dy, offsets)                    # [E, K, N] fp32
+            wref = ctx.weight_ref
+            sink = getattr(wref, "grad_sink", None) if wref is not None else None
+            if sink is not None and sink.numel() == dw32.numel():
+                # data-parallel wrappers point `grad_sink` into their flat gradient buffer: one conversion pass
+                # straight into it instead of a bf16 temporary that is copied again later
+                if getattr(wref, "grad_sink_filled", False):
+                    sink.view(dw32.shape).add_(dw32)
+                else:
+                    sink.view(dw32.shape).copy_(dw32)
+                wref.grad_sink_filled = True
+            else:
+                dw = dw32.to(w.dtype)
         return dx, dw, None, None, None, None
 
 
