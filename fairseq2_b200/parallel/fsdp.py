@@ -934,6 +934,11 @@ class FSDP(Module):
             self.gang.all_reduce(total, ReduceOperation.SUM)
         if self.tp_gang is not None:
             self.tp_gang.all_reduce(total, ReduceOperation.SUM)
+        if self.replica_gang is not None:
+            # Replicas hold the same gradients, but the squared norm is accumulated with floating-point atomics
+            # whose order differs from run to run: the last bits of the norm, and with them the clipping factor,
+            # could differ between replicas and let their weights drift apart. They agree on the maximum.
+            self.replica_gang.all_reduce(total, ReduceOperation.MAX)
         norm = total.sqrt()
         if self._grad_scale is not None:
             norm = norm * self._grad_scale
