@@ -96,9 +96,23 @@ def bench_gemm(a: argparse.Namespace) -> None:
 
 
 def _attn_inputs(a: argparse.Namespace):  # type: ignore[no-untyped-def]
+    """``--doc-lens LO,HI``: the tokens are packed documents with lengths uniform in [LO, HI] (the SFT benchmark's
+    workload: 128,4096) instead of equal sequences of ``--seq-len``."""
     T, S, H, Hkv, D = a.tokens, a.seq_len, a.heads, a.kv_heads, a.head_dim
-    nseq = T // S
     qkv = torch.randn(T, H + 2 * Hkv, D, device=_DEV, dtype=torch.bfloat16)
+    if a.doc_lens:
+        import numpy as np
+
+        lo, hi = (int(v) for v in a.doc_lens.split(","))
+        rng, doc, total = np.random.default_rng(0), [], 0
+        while total < T:
+            n = min(int(rng.integers(lo, hi + 1)), T - total)
+            doc.append(n)
+            total += n
+        lens = torch.tensor(doc, device=_DEV, dtype=torch.int32)
+        begins = (torch.cumsum(lens, 0) - lens).to(torch.int32)
+        return qkv, begins, lens
+    nseq = T // S
     begins = torch.arange(nseq, device=_DEV, dtype=torch.int32) * S
     lens = torch.full((nseq,), S, device=_DEV, dtype=torch.int32)
     return qkv, begins, lens
@@ -110,19 +124,23 @@ def bench_attention(a: argparse.Namespace) -> None:
     qkv, begins, lens = _attn_inputs(a)
     q, k, v = qkv[:, :H], qkv[:, H:H + Hkv], qkv[:, H + Hkv:]
     scale = 1.0 / math.sqrt(D)
-    fl_fwd = 4.0 * (T // S) * H * D * S * S / 2      # causal: half of the score matrix
-    out, lse = ext.attn_fwd(q, k, v, begins, lens, begins, lens, S, S, True, scale, 0)
-    ms = _time(lambda: ext.attn_fwd(q, k, v, begins, lens, begins, lens, S, S, True, scale, 0), a.iters, a.warmup)
-    _emit("attention_fwd", ms, flops=fl_fwd, tokens=T, seq_len=S, heads=H, kv_heads=Hkv, head_dim=D)
+    S = int(lens.max())
+    fl_fwd = 4.0 * H * D * float((lens.double() ** 2).sum()) / 2      # causal: half of the score matrix
+    drop, seed = a.dropout, 1234
+    tag = {"docs": a.doc_lens or None, "dropout": drop or None}
+    out, lse = ext.attn_fwd(q, k, v, begins, lens, begins, lens, S, S, True, scale, 0, drop, seed)
+    ms = _time(lambda: ext.attn_fwd(q, k, v, begins, lens, begins, lens, S, S, True, scale, 0, drop, seed), a.iters,
+               a.warmup)
+    _emit("attention_fwd", ms, flops=fl_fwd, tokens=T, seq_len=S, heads=H, kv_heads=Hkv, head_dim=D, **tag)
     dout = torch.randn_like(out)
     dqkv = torch.empty_like(qkv)
 
     def bwd() -> None:
         ext.attn_bwd_out(dout, q, k, v, out, lse, begins, lens, begins, lens, S, S, True, scale, dqkv[:, :H],
-                         dqkv[:, H:H + Hkv], dqkv[:, H + Hkv:], 0)
+                         dqkv[:, H:H + Hkv], dqkv[:, H + Hkv:], 0, drop, seed)
 
     ms = _time(bwd, a.iters, a.warmup)
-    _emit("attention_bwd", ms, flops=2.5 * fl_fwd, tokens=T, seq_len=S, heads=H, kv_heads=Hkv, head_dim=D)
+    _emit("attention_bwd", ms, flops=2.5 * fl_fwd, tokens=T, seq_len=S, heads=H, kv_heads=Hkv, head_dim=D, **tag)
 
 
 def bench_norm(a: argparse.Namespace) -> None:
@@ -228,7 +246,54 @@ def bench_conv(a: argparse.Namespace) -> None:
     _emit("layer_norm_then_gelu_torch_fwd", ms, nbytes=2.0 * rows * C * 2)
 
 
-_CASES = {"conv": bench_conv, "gemm": bench_gemm, "attention": bench_attention, "norm": bench_norm, "swiglu": bench_swiglu,
+def bench_first_conv(a: argparse.Namespace) -> None:
+    """First wav2vec 2.0 feature-extractor layer in one kernel: ~1.4 M samples per step in the SSL benchmark."""
+    from fairseq2_b200.ops.conv import first_conv_ln_gelu
+
+    B, L, C, k, s = 8, a.samples // 8, 512, 10, 5
+    x = (torch.randn(B, L, device=_DEV) * 0.1).to(torch.bfloat16)
+    w = (torch.randn(C, 1, k, device=_DEV) * 0.3).to(torch.bfloat16).requires_grad_(True)
+    b = torch.zeros(C, device=_DEV, dtype=torch.bfloat16, requires_grad=True)
+    lw = torch.ones(C, device=_DEV, dtype=torch.bfloat16, requires_grad=True)
+    lb = torch.zeros(C, device=_DEV, dtype=torch.bfloat16, requires_grad=True)
+    T = (L - k) // s + 1
+    ms = _time(lambda: first_conv_ln_gelu(x, w.detach(), b.detach(), lw.detach(), lb.detach(), s, T), a.iters, a.warmup)
+    _emit("wav2vec2_first_conv_ln_gelu_fwd", ms, nbytes=B * T * C * 2.0 + B * L * 2.0, samples=B * L, channels=C)
+    y = first_conv_ln_gelu(x, w, b, lw, lb, s, T)
+    g = torch.randn_like(y)
+    ms = _time(lambda: torch.autograd.grad(y, (w, b, lw, lb), g, retain_graph=True), a.iters, a.warmup)
+    _emit("wav2vec2_first_conv_ln_gelu_bwd", ms, nbytes=B * T * C * 2.0 + B * L * 2.0, samples=B * L, channels=C)
+
+
+def bench_swiglu2(a: argparse.Namespace) -> None:
+    """Two-input SwiGLU of the expert path: capacity-sized buffers of which half the rows hold data."""
+    from fairseq2_b200.ops.moe import swiglu_gate_up
+
+    rows, F = 131072, 768
+    g = torch.randn(rows, F, device=_DEV, dtype=torch.bfloat16, requires_grad=True)
+    u = torch.randn(rows, F, device=_DEV, dtype=torch.bfloat16, requires_grad=True)
+    nt = torch.tensor([rows // 256], device=_DEV, dtype=torch.int32)
+    used = rows // 2
+    ms = _time(lambda: swiglu_gate_up(g.detach(), u.detach(), nt), a.iters, a.warmup)
+    _emit("swiglu_gate_up_bounded_fwd", ms, nbytes=3.0 * used * F * 2, rows_with_data=used, inner_dim=F)
+    y = swiglu_gate_up(g, u, nt)
+    dy = torch.randn_like(y)
+    ms = _time(lambda: torch.autograd.grad(y, (g, u), dy, retain_graph=True), a.iters, a.warmup)
+    _emit("swiglu_gate_up_bounded_bwd", ms, nbytes=5.0 * used * F * 2, rows_with_data=used, inner_dim=F)
+
+
+def bench_add_norm(a: argparse.Namespace) -> None:
+    from fairseq2_b200.ops.norm import add_rms_norm
+
+    T, Dm = a.tokens, a.dim
+    x = torch.randn(T, Dm, device=_DEV, dtype=torch.bfloat16)
+    r = torch.randn(T, Dm, device=_DEV, dtype=torch.bfloat16)
+    w = torch.ones(Dm, device=_DEV, dtype=torch.bfloat16)
+    ms = _time(lambda: add_rms_norm(x, r, w, 1e-5), a.iters, a.warmup)
+    _emit("add_rms_norm_fwd", ms, nbytes=4.0 * T * Dm * 2, tokens=T, dim=Dm)
+
+
+_CASES = {"first_conv": bench_first_conv, "swiglu2": bench_swiglu2, "add_norm": bench_add_norm, "conv": bench_conv, "gemm": bench_gemm, "attention": bench_attention, "norm": bench_norm, "swiglu": bench_swiglu,
           "adamw": bench_adamw, "ce": bench_ce}
 
 
@@ -254,6 +319,9 @@ def main() -> None:
     ap.add_argument("--ffn-dim", type=int, default=14336)
     ap.add_argument("--vocab", type=int, default=128256)
     ap.add_argument("--numel", type=int, default=1 << 28)
+    ap.add_argument("--doc-lens", default="", metavar="LO,HI", help="attention: packed documents of these lengths")
+    ap.add_argument("--dropout", type=float, default=0.0, help="attention: dropout probability (mma.sync kernels)")
+    ap.add_argument("--samples", type=int, default=1_400_000, help="first_conv: waveform samples per step")
     a = ap.parse_args()
     torch.manual_seed(0)
     for name in (_CASES if a.case == "all" else [a.case]):
