@@ -22,6 +22,8 @@ from fairseq2_b200.metrics import MetricBag, sync_and_compute_metrics
 from fairseq2_b200.metrics.common import extend_batch_metric_values
 from fairseq2_b200.task import Task, TaskStopException
 from fairseq2_b200.trainer import Validator
+from fairseq2_b200.utils.progress import create_progress_reporter
+from fairseq2_b200.utils.rng import RngBag
 from fairseq2_b200.utils.stopwatch import Stopwatch
 
 BatchT = TypeVar("BatchT")
@@ -30,6 +32,9 @@ BatchT = TypeVar("BatchT")
 class EvalUnit(ABC, Generic[BatchT]):
     @abstractmethod
     def process_batch(self, batch: BatchT, metric_bag: MetricBag) -> None: ...
+
+    def prepare_metric_bag(self, metric_bag: MetricBag) -> None:
+        """Called once before the first batch: register the metrics the unit will update."""
 
     def set_train_step_nr(self, train_step_nr: int) -> None:
         pass
@@ -70,11 +75,15 @@ class _EvalLoop:
         self._seed = seed
         self._step_nr = 0
         self._stop = False
+        device = gangs.root.device
+        self._rng_bag = RngBag.from_device_defaults(torch.device("cpu"), device) if device.type == "cuda" \
+            else RngBag.from_device_defaults(device)
 
     def _run_unit(self, unit: EvalUnit[Any], reader: Any, train_step_nr: int | None) -> dict[str, Any] | None:
         g = self._gangs
         device = g.root.device
         bag = MetricBag(device)
+        unit.prepare_metric_bag(bag)
         if train_step_nr is not None:
             unit.set_train_step_nr(train_step_nr)
         watch = Stopwatch()
@@ -84,8 +93,13 @@ class _EvalLoop:
         module = unit.model.module if hasattr(unit.model, "module") else unit.model
         was_training = getattr(module, "training", False)
         module.train(False)
+        label = self._category if unit.name is None else f"{self._category}/{unit.name}"
+        task = create_progress_reporter().create_task(label, None) if g.root.rank == 0 else None
         try:
-            with torch.no_grad(), _autocast(device, self._amp, self._amp_dtype):
+            # The random state of the surrounding job (dropout and masking of the training step that follows a
+            # validation) must not depend on whether, or on how much data, was evaluated in between.
+            with self._rng_bag.temporary_manual_seed(self._seed + g.root.rank), torch.no_grad(), \
+                    _autocast(device, self._amp, self._amp_dtype):
                 for batches in reader:
                     if self._stop:
                         raise TaskStopException()
@@ -95,7 +109,11 @@ class _EvalLoop:
                             batch = batch.to(device, non_blocking=True)
                         unit.process_batch(batch, bag)
                         num_batches += 1
+                    if task is not None:
+                        task.step(1)
         finally:
+            if task is not None:
+                task.close()
             module.train(was_training)
             reader.reset()
         values = sync_and_compute_metrics(bag, g.dp) if g.tp.rank == 0 else None
@@ -153,18 +171,47 @@ class Generator(Evaluator):
 
 class StandardValidator(Validator, _EvalLoop):
     """Validation inside training. ``score_metric`` names the metric that becomes the checkpoint score;
-    ``lower_better`` negates it so that a higher score is always better."""
+    ``lower_better`` negates it so that a higher score is always better. The best score and its step are tracked
+    across runs (and picked up from the scores of the saved checkpoints after a restart when a
+    ``checkpoint_manager`` is given), and logged next to the last one."""
 
     def __init__(self, units: Sequence[EvalUnit[Any]], data_readers: Sequence[Any], gangs: Gangs, *,
-                 score_metric: str | None = None, lower_better: bool = False, **kw: Any) -> None:
+                 score_metric: str | None = None, lower_better: bool = False, checkpoint_manager: Any | None = None,
+                 **kw: Any) -> None:
         kw.setdefault("category", "valid")
         _EvalLoop.__init__(self, units, data_readers, gangs, **kw)
         self._score_metric, self._lower_better = score_metric, lower_better
+        self._ckpt = checkpoint_manager
+        self._best_score = float("-inf")
+        self._best_step_nr = -1                     # -1: not yet compared with the checkpoints on disk
+
+    @property
+    def best_score(self) -> float | None:
+        """The best score so far in the metric's own direction (``None`` before the first scored run)."""
+        if self._best_step_nr <= 0:
+            return None
+        return -self._best_score if self._lower_better else self._best_score
+
+    @property
+    def best_step_nr(self) -> int | None:
+        return self._best_step_nr if self._best_step_nr > 0 else None
+
+    def _maybe_restore_best(self) -> None:
+        if self._score_metric is None or self._best_step_nr >= 0:
+            return
+        self._best_step_nr = 0
+        if self._ckpt is not None:
+            scored = self._ckpt.load_scores()       # best first, higher is better
+            if scored:
+                self._best_score, self._best_step_nr = float(scored[0][0]), int(scored[0][1])
 
     def run(self, train_step_nr: int) -> float | None:
         log.info("Validation at step {} starting.", train_step_nr)
+        self._maybe_restore_best()
         scores = []
         for unit, reader in zip(self._units, self._readers):
+            if unit.name:
+                log.info("Validating {}.", unit.name)
             values = self._run_unit(unit, reader, train_step_nr)
             if self._score_metric is not None and values is not None and self._score_metric in values:
                 scores.append(float(values[self._score_metric]))
@@ -178,8 +225,19 @@ class StandardValidator(Validator, _EvalLoop):
             v = float(t.item())
             if v == v:
                 score = -v if self._lower_better else v
+                if score > self._best_score:
+                    self._best_score, self._best_step_nr = score, train_step_nr
+                log.info("Score - Metric: {} | Last: {:.6g} (step {}) | Best: {:.6g} (step {})", self._score_metric, v,
+                         train_step_nr, -self._best_score if self._lower_better else self._best_score,
+                         self._best_step_nr)
         log.info("Validation finished.")
         return score
+
+    def reset(self) -> None:
+        self._step_nr = 0
+        self._stop = False
+        for reader in self._readers:
+            reader.reset()
 
     def close(self) -> None:
         pass

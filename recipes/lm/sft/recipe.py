@@ -59,7 +59,7 @@ class LMSFTRecipe(TrainRecipe):
                 target_encode_mode=ds.target_encode_mode, chat_mode=ds.chat_mode, sync_batches=True)
             vreader = dataset.create_reader(ds.valid_split, tokenizer, context.gangs, ds.min_seq_len, ds.max_seq_len,
                                             vopts)
-            validator = StandardValidator([LMLossEvalUnit(model)], [vreader], context.gangs,
+            validator = StandardValidator([LMLossEvalUnit(model)], [vreader], context.gangs, checkpoint_manager=context.checkpoint_manager,
                                           score_metric="nll_loss", lower_better=True,
                                           metric_recorder=context.create_metric_recorder())
         return context.create_trainer(LMSFTUnit(model, config.label_smoothing), reader, validator)

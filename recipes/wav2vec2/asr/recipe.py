@@ -203,7 +203,7 @@ class Wav2Vec2AsrRecipe(TrainRecipe):
         if splits:
             units = [Wav2Vec2AsrEvalUnit(model, tokenizer, s if len(splits) > 1 else None) for s in splits]
             readers = [dataset.create_reader(s, context.gangs, ds, tokenizer=tokenizer, train=False) for s in splits]
-            validator = StandardValidator(units, readers, context.gangs, score_metric="wer", lower_better=True,
+            validator = StandardValidator(units, readers, context.gangs, checkpoint_manager=context.checkpoint_manager, score_metric="wer", lower_better=True,
                                           metric_recorder=context.create_metric_recorder())
         unit = Wav2Vec2AsrTrainUnit(model, config.trainer.freeze_encoder_for_n_steps)
         return context.create_trainer(unit, reader, validator)

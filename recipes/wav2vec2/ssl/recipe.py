@@ -144,7 +144,7 @@ class Wav2Vec2SslRecipe(TrainRecipe):
         if splits:
             units = [Wav2Vec2SslEvalUnit(model, config.loss, s if len(splits) > 1 else None) for s in splits]
             readers = [dataset.create_reader(s, context.gangs, ds, train=False) for s in splits]
-            validator = StandardValidator(units, readers, context.gangs, score_metric="loss", lower_better=True,
+            validator = StandardValidator(units, readers, context.gangs, checkpoint_manager=context.checkpoint_manager, score_metric="loss", lower_better=True,
                                           metric_recorder=context.create_metric_recorder())
         return context.create_trainer(Wav2Vec2SslTrainUnit(model, config.loss), reader, validator)
 

@@ -220,3 +220,58 @@ def test_kernel_wait_timeout_aborts_the_step() -> None:
     assert ei.value.site == 18
     after = fsdp.full_state_dict()
     assert all(torch.equal(before[k], after[k]) for k in before)   # raised before the step touched the weights
+
+
+def test_validator_tracks_best_score_and_leaves_rng_alone(tmp_path) -> None:
+    """The validator reports the best score so far (restored from checkpoint scores after a restart) and the random
+    state of the surrounding job is the same whether or not a validation ran."""
+    from fairseq2_b200.evaluator import EvalUnit, StandardValidator
+    from fairseq2_b200.gang import create_fake_gangs
+    from fairseq2_b200.metrics import Mean
+
+    gangs = create_fake_gangs(torch.device("cpu"))
+    model = torch.nn.Linear(2, 2)
+
+    class Unit(EvalUnit):
+        def __init__(self) -> None:
+            self.values = iter([3.0, 1.0, 2.0])
+            self.prepared = 0
+
+        @property
+        def model(self):  # type: ignore[no-untyped-def]
+            return model
+
+        def prepare_metric_bag(self, bag) -> None:  # type: ignore[no-untyped-def]
+            self.prepared += 1
+            bag.add("loss", Mean(device=torch.device("cpu")))
+
+        def process_batch(self, batch, bag) -> None:  # type: ignore[no-untyped-def]
+            torch.rand(3)                                 # consumes random numbers
+            bag.get("loss", Mean).update(torch.tensor(self.current), weight=1)
+
+    class Reader:
+        def __iter__(self):  # type: ignore[no-untyped-def]
+            return iter([[torch.zeros(1)], [torch.zeros(1)]])
+
+        def reset(self) -> None:
+            pass
+
+    class Scores:
+        def load_scores(self):  # type: ignore[no-untyped-def]
+            return [(-0.5, 7), (-4.0, 3)]               # best first; the metric is lower-better, scores negated
+
+    unit = Unit()
+    v = StandardValidator([unit], [Reader()], gangs, score_metric="loss", lower_better=True, checkpoint_manager=Scores())
+    torch.manual_seed(5)
+    expected_next = torch.rand(2)
+    torch.manual_seed(5)
+    unit.current = 3.0
+    assert v.run(10) == -3.0
+    assert torch.equal(torch.rand(2), expected_next)      # validation did not advance the generator
+    assert (v.best_score, v.best_step_nr) == (0.5, 7)     # the restored checkpoint is still the best
+    unit.current = 0.25
+    assert v.run(20) == -0.25 and (v.best_score, v.best_step_nr) == (0.25, 20)
+    unit.current = 2.0
+    assert v.run(30) == -2.0 and (v.best_score, v.best_step_nr) == (0.25, 20)
+    assert unit.prepared == 3
+    v.reset()
