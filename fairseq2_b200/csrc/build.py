@@ -50,7 +50,7 @@ def build_cuda(verbose: bool = False, force: bool = False) -> Path:
                        # the C++ runtime is named explicitly: the toolchain's link driver leaves it out of DT_NEEDED,
                        # and the extension would then bind `__cxa_throw` and friends to whichever copy the process
                        # happens to have loaded first
-                       extra_ldflags=["-lstdc++"],
+                       extra_ldflags=["-l:libstdc++.so.6"],
                        build_directory=str(build_dir), verbose=verbose, is_python_module=False,
                        with_cuda=True)
     shutil.copy2(build_dir / "_C.so", target)
@@ -72,7 +72,7 @@ def build_data(verbose: bool = False, force: bool = False) -> Path | None:
     sanitize = os.environ.get("FAIRSEQ2_B200_SANITIZE", "")
     if sanitize and sanitize not in ("address", "undefined", "thread"):
         raise ValueError(f"FAIRSEQ2_B200_SANITIZE must be address, undefined or thread, but is '{sanitize}'.")
-    cflags, ldflags, tag = ["-O2", "-std=c++17", "-pthread"], ["-pthread", "-lz", "-lstdc++"], "data"
+    cflags, ldflags, tag = ["-O2", "-std=c++17", "-pthread"], ["-pthread", "-lz", "-l:libstdc++.so.6"], "data"
     if sanitize:
         cflags += [f"-fsanitize={sanitize}", "-fno-omit-frame-pointer", "-g"]
         ldflags += [f"-fsanitize={sanitize}"]
@@ -102,7 +102,7 @@ def build_data_tests(verbose: bool = False, force: bool = False) -> Path | None:
     build_dir = CSRC / "_build" / "data_tests"
     build_dir.mkdir(parents=True, exist_ok=True)
     cpp_extension.load(name="_data_tests", sources=[str(s) for s in sources],
-                       extra_cflags=["-O1", "-std=c++17", "-pthread"], extra_ldflags=["-pthread", "-lz", "-lstdc++"],
+                       extra_cflags=["-O1", "-std=c++17", "-pthread"], extra_ldflags=["-pthread", "-lz", "-l:libstdc++.so.6"],
                        build_directory=str(build_dir), verbose=verbose, is_python_module=False, with_cuda=False)
     shutil.copy2(build_dir / "_data_tests.so", target)
     return target
