@@ -20,6 +20,26 @@ from fairseq2_b200.nn.projection import ColumnShardedLinear, Linear, Projection,
 from fairseq2_b200.ops.cross_entropy import fused_linear_cross_entropy
 
 
+def _widen_batch(seqs: Tensor, layout: BatchLayout, targets: Tensor | None, target_mask: Tensor | None, pad: int,
+                 pad_idx: int | None):  # type: ignore[no-untyped-def]
+    """``pad`` more positions at the end of the token dimension: padding in the layout, masked out of the loss."""
+    import torch
+    import torch.nn.functional as F
+
+    fill = pad_idx if pad_idx is not None else 0
+    seqs = F.pad(seqs, (0, pad), value=fill)
+    if layout.packed:
+        layout = BatchLayout((seqs.shape[-1],), list(layout.seq_lens), packed=True, device=seqs.device)
+    else:
+        layout = BatchLayout(tuple(seqs.shape[:2]), list(layout.seq_lens), device=seqs.device)
+    if targets is not None:
+        if target_mask is None:
+            target_mask = torch.ones(targets.shape, device=targets.device, dtype=torch.bool)
+        targets = F.pad(targets, (0, pad), value=fill)
+        target_mask = F.pad(target_mask, (0, pad), value=0)
+    return seqs, layout, targets, target_mask
+
+
 class TransformerLM(CausalLM):
     def __init__(self, model_dim: int, decoder_frontend: TransformerFrontend, decoder: TransformerLMDecoder,
                  final_proj: Projection, pad_idx: int | None, max_seq_len: int) -> None:
@@ -30,18 +50,33 @@ class TransformerLM(CausalLM):
 
     def forward(self, seqs, seqs_layout, targets=None, *, state_bag=None, label_smoothing=0.0, target_mask=None,
                 reduction="sum", return_logits=False):  # type: ignore[override]
+        num_tokens = seqs.shape[-1]
+        pad = self._sequence_parallel_padding(num_tokens) if state_bag is None else 0
+        if pad:
+            # token-sharded activations need a token count that the tensor-parallel ranks can split evenly: the
+            # batch is widened by up to size - 1 padding positions that no sequence owns and no target counts
+            seqs, seqs_layout, targets, target_mask = _widen_batch(seqs, seqs_layout, targets, target_mask, pad,
+                                                                   self.pad_idx)
         seqs, seqs_layout = self.decoder_frontend(seqs, seqs_layout, state_bag=state_bag)
         out = self.decoder(seqs, seqs_layout, state_bag=state_bag)
         del seqs
         if targets is None:
-            return self.final_proj(out)
+            logits = self.final_proj(out)
+            return logits[..., :num_tokens, :] if pad else logits
         if not return_logits:
             return self.compute_fused_loss(out, targets, label_smoothing=label_smoothing, target_mask=target_mask,
                                            reduction=reduction)
         logits = self.final_proj(out)
         loss = self.compute_loss(logits, targets, label_smoothing=label_smoothing, target_mask=target_mask,
                                  reduction=reduction)
-        return loss, logits
+        return loss, (logits[..., :num_tokens, :] if pad else logits)
+
+    def _sequence_parallel_padding(self, num_tokens: int) -> int:
+        if not getattr(self, "tp_sequence_parallel", False):
+            return 0
+        gang = getattr(self.final_proj, "gang", None)
+        size = gang.size if gang is not None else 1
+        return (-num_tokens) % size
 
     def compute_loss(self, logits: Tensor, targets: Tensor, *, label_smoothing: float = 0.0,
                      target_mask: Tensor | None = None, reduction: Literal["sum", "mean"] = "sum") -> Tensor:

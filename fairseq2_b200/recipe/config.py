@@ -70,9 +70,9 @@ class GangSection:
     #: "nccl", or "auto" (symm inside one NVSwitch domain, NCCL otherwise)
     collectives: Literal["auto", "nccl", "symm"] = "auto"
     #: training layout of tensor parallelism: the residual stream is sharded over the tokens between the blocks
-    #: and the column / row projections all-gather / reduce-scatter inside their GEMM kernels. The number of tokens
-    #: of a batch (its padded length) must then be a multiple of `tensor_parallel_size`. Evaluation and generation
-    #: models always keep their activations replicated.
+    #: and the column / row projections all-gather / reduce-scatter inside their GEMM kernels (the model widens a
+    #: batch by up to `tensor_parallel_size - 1` masked padding positions where the token count does not divide).
+    #: Evaluation and generation models always keep their activations replicated.
     sequence_parallel: bool = True
 
     def validate(self) -> ValidationResult:

@@ -253,3 +253,26 @@ def test_lm_dpo_recipe(tmp_path: Path) -> None:
     assert main(LMDPORecipe(), args) == 0
     rows = [json.loads(l) for l in open(tmp_path / "out" / "metrics" / "train.jsonl")]
     assert len(rows) == 4 and all(math.isfinite(r["dpo_loss"]) for r in rows)
+
+
+def _tp_sft_worker(rank: int, world: int, root: str, seq_par: bool):
+    from recipes.lm.sft.recipe import LMSFTRecipe
+
+    tmp = Path(root)
+    data = tmp / "data"
+    args = _sft_args(tmp, data, ["regime.num_steps=3", "dataset.packed=true", "gang.tensor_parallel_size=2",
+                                 f"gang.sequence_parallel={str(seq_par).lower()}", "trainer.data_parallelism=fsdp",
+                                 "regime.validate_every_n_steps=null", "regime.checkpoint_every_n_steps=null"])
+    return main(LMSFTRecipe(), args)
+
+
+@pytest.mark.parametrize("seq_par", [True, False])
+def test_lm_sft_recipe_with_tensor_parallelism(tmp_path: Path, seq_par: bool) -> None:
+    """Two gloo ranks, TP=2: the recipe builds the LLaMA model sequence parallel (token-sharded residual stream,
+    vocabulary-parallel embedding and loss) or with replicated activations, and the loss goes down either way."""
+    from tests.dist_utils import run_distributed
+
+    _write_sft_data(tmp_path)
+    assert run_distributed(_tp_sft_worker, 2, str(tmp_path), seq_par, timeout=300.0) == [0, 0]
+    lines = [json.loads(l) for l in open(tmp_path / "out" / "metrics" / "train.jsonl")]
+    assert len(lines) == 3 and lines[-1]["NLL Loss"] < lines[0]["NLL Loss"]
