@@ -65,6 +65,14 @@ MapFn as_map_fn(py::object o) {
         auto c = o.cast<ImageDecoder>();
         return [c](Data&& d) { return c(std::move(d)); };
     }
+    if (py::isinstance<SentencePieceEncoder>(o)) {
+        auto c = o.cast<SentencePieceEncoder>();
+        return [c](Data&& d) { return c(std::move(d)); };
+    }
+    if (py::isinstance<SentencePieceDecoder>(o)) {
+        auto c = o.cast<SentencePieceDecoder>();
+        return [c](Data&& d) { return c(std::move(d)); };
+    }
     PyCallable pc(std::move(o));
     return [pc](Data&& d) {
         py::gil_scoped_acquire gil;
@@ -347,6 +355,70 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     py::class_<ImageDecoder>(m, "ImageDecoder")
         .def(py::init<>())
         .def("__call__", [](const ImageDecoder& a, Data d) { return a(std::move(d)); });
+
+    py::class_<SentencePieceModel>(m, "SentencePieceModel")
+        .def(py::init([](py::object path, std::vector<std::string> control_symbols) {
+            return SentencePieceModel::from_file(py::str(path).cast<std::string>(), control_symbols);
+        }), py::arg("path"), py::arg("control_symbols") = std::vector<std::string>{})
+        .def_static("from_serialized", [](py::bytes blob, std::vector<std::string> control_symbols) {
+            std::string s = blob;
+            return SentencePieceModel(s, control_symbols);
+        }, py::arg("serialized"), py::arg("control_symbols") = std::vector<std::string>{})
+        .def_property_readonly("vocabulary_size", &SentencePieceModel::size)
+        .def_property_readonly("unk_idx", &SentencePieceModel::unk_id)
+        .def_property_readonly("bos_idx", [](const SentencePieceModel& s) -> std::optional<int> {
+            return s.bos_id() < 0 ? std::nullopt : std::optional<int>(s.bos_id());
+        })
+        .def_property_readonly("eos_idx", [](const SentencePieceModel& s) -> std::optional<int> {
+            return s.eos_id() < 0 ? std::nullopt : std::optional<int>(s.eos_id());
+        })
+        .def_property_readonly("pad_idx", [](const SentencePieceModel& s) -> std::optional<int> {
+            return s.pad_id() < 0 ? std::nullopt : std::optional<int>(s.pad_id());
+        })
+        .def("token_to_index", [](const SentencePieceModel& s, const std::string& t) { return s.piece_to_id(t); })
+        .def("index_to_token", [](const SentencePieceModel& s, int i) { return s.id_to_piece(i); })
+        .def("is_control", &SentencePieceModel::is_control)
+        .def("normalize", [](const SentencePieceModel& s, const std::string& t) { return s.normalize(t); })
+        .def("encode", [](const SentencePieceModel& s, const std::string& t) { return s.encode(t); })
+        .def("encode_as_tokens", [](const SentencePieceModel& s, const std::string& t) {
+            std::vector<std::string> out;
+            for (auto& p : s.encode_as_pieces(t)) out.push_back(std::move(p.first));
+            return out;
+        })
+        .def("nbest_encode", [](const SentencePieceModel& s, const std::string& t, size_t n) {
+            std::vector<std::pair<std::vector<int>, float>> out;
+            for (auto& r : s.nbest_encode(t, n)) {
+                std::vector<int> ids;
+                for (auto& p : r.first) ids.push_back(p.second);
+                out.emplace_back(std::move(ids), r.second);
+            }
+            return out;
+        })
+        .def("decode", [](const SentencePieceModel& s, const std::vector<int64_t>& ids) { return s.decode(ids); })
+        .def("decode_from_tokens", [](const SentencePieceModel& s, const std::vector<std::string>& toks) {
+            return s.decode_tokens(toks);
+        });
+
+    py::class_<SentencePieceEncoder>(m, "SentencePieceEncoder")
+        .def(py::init([](SentencePieceModel model, std::vector<std::string> prefix, std::vector<std::string> suffix,
+                         bool reverse, bool enable_sampling, int nbest_size, float alpha,
+                         std::optional<std::string> device, bool pin_memory, uint64_t seed) {
+            std::optional<at::Device> dev;
+            if (device) dev = at::Device(*device);
+            return SentencePieceEncoder(std::move(model), std::move(prefix), std::move(suffix), reverse,
+                                        enable_sampling, nbest_size, alpha, dev, pin_memory, seed);
+        }), py::arg("model"), py::arg("prefix_tokens") = std::vector<std::string>{},
+           py::arg("suffix_tokens") = std::vector<std::string>{}, py::arg("reverse") = false,
+           py::arg("enable_sampling") = false, py::arg("nbest_size") = -1, py::arg("alpha") = 0.1f,
+           py::arg("device") = py::none(), py::arg("pin_memory") = false, py::arg("seed") = 0)
+        .def("__call__", [](const SentencePieceEncoder& e, const std::string& text) { return e.encode(text); })
+        .def("encode_as_tokens", [](const SentencePieceEncoder& e, const std::string& text) {
+            return e.encode_as_tokens(text);
+        });
+
+    py::class_<SentencePieceDecoder>(m, "SentencePieceDecoder")
+        .def(py::init<SentencePieceModel, bool>(), py::arg("model"), py::arg("reverse") = false)
+        .def("__call__", [](const SentencePieceDecoder& d, const at::Tensor& t) { return d.decode(t); });
 
     m.def("read_sequence", [](py::sequence seq) {
         DataList items;

@@ -1,6 +1,10 @@
 // Declarations of the pipeline helpers implemented in extras.cc / audio.cc.
 #pragma once
 
+#include <mutex>
+#include <random>
+#include <string_view>
+
 #include "data.h"
 
 namespace fs2d {
@@ -109,6 +113,75 @@ class ImageDecoder {
 public:
     ImageDecoder() = default;
     Data operator()(Data&& d) const;
+};
+
+// sentencepiece.cc: a SentencePiece runtime (model reader, normalizer, unigram / BPE / char / word segmentation).
+struct SamplingOptions {
+    int nbest_size = -1;   // < 0: sample from the whole lattice; > 1: sample among the n best; else the best path
+    float alpha = 0.1f;    // unigram: inverse temperature; BPE: merge dropout probability
+};
+
+class SentencePieceModel {
+public:
+    // `control_symbols`: appended as control pieces unless the model holds them; "<sym>@0" is inserted at index 0.
+    SentencePieceModel(std::string_view serialized, const std::vector<std::string>& control_symbols);
+    static SentencePieceModel from_file(const std::string& path, const std::vector<std::string>& control_symbols);
+
+    size_t size() const;
+    int unk_id() const;
+    int bos_id() const;   // -1 where the model has no such control piece
+    int eos_id() const;
+    int pad_id() const;
+    int piece_to_id(std::string_view piece) const;   // the unknown id for a piece that is not in the vocabulary
+    const std::string& id_to_piece(int id) const;
+    bool is_control(int id) const;
+
+    std::string normalize(std::string_view text) const;
+    std::vector<int64_t> encode(std::string_view text, const SamplingOptions* sampling = nullptr,
+                                std::mt19937_64* rng = nullptr) const;
+    std::vector<std::pair<std::string, int>> encode_as_pieces(std::string_view text,
+                                                              const SamplingOptions* sampling = nullptr,
+                                                              std::mt19937_64* rng = nullptr) const;
+    std::vector<std::pair<std::vector<std::pair<std::string, int>>, float>> nbest_encode(std::string_view text,
+                                                                                         size_t nbest) const;
+    std::string decode(const std::vector<int64_t>& ids) const;
+    std::string decode_tokens(const std::vector<std::string>& tokens) const;
+
+private:
+    std::string decode_pieces(const std::vector<std::pair<std::string, int>>& pieces) const;
+    struct Impl;
+    std::shared_ptr<Impl> impl_;
+};
+
+// str -> int64 tensor: prefix tokens + pieces (optionally reversed, optionally sampled) + suffix tokens.
+class SentencePieceEncoder {
+public:
+    SentencePieceEncoder(SentencePieceModel model, std::vector<std::string> prefix_tokens,
+                         std::vector<std::string> suffix_tokens, bool reverse, bool enable_sampling, int nbest_size,
+                         float alpha, std::optional<at::Device> device, bool pin_memory, uint64_t seed);
+    at::Tensor encode(std::string_view text) const;
+    std::vector<std::string> encode_as_tokens(std::string_view text) const;
+    Data operator()(Data&& d) const;
+
+private:
+    SentencePieceModel model_;
+    std::vector<int64_t> prefix_, suffix_;
+    bool reverse_, sampling_;
+    SamplingOptions options_;
+    std::optional<at::Device> device_;
+    bool pin_;
+    std::shared_ptr<std::pair<std::mutex, std::mt19937_64>> rng_;
+};
+
+class SentencePieceDecoder {
+public:
+    SentencePieceDecoder(SentencePieceModel model, bool reverse) : model_(std::move(model)), reverse_(reverse) {}
+    std::string decode(const at::Tensor& indices) const;
+    Data operator()(Data&& d) const;
+
+private:
+    SentencePieceModel model_;
+    bool reverse_;
 };
 
 }  // namespace fs2d

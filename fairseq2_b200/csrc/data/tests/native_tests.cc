@@ -7,6 +7,7 @@
 
 #include <cstdio>
 #include <fstream>
+#include <random>
 #include <sstream>
 #include <thread>
 
@@ -554,6 +555,118 @@ TEST(pipeline_text_reader_reencodes) {
     // UTF-8 spellings bypass the converter
     DataPipeline u = read_text(latin.path, std::nullopt, "infer", false, false, false, false, 0, "utf_8").and_return();
     CHECK(u.next()->as_string() == "caf\xe9");
+}
+
+// A serialized SentencePiece model written field by field (protobuf wire format).
+struct ProtoWriter {
+    std::string out;
+    void varint(uint64_t v) {
+        while (v >= 0x80) {
+            out.push_back(static_cast<char>((v & 0x7f) | 0x80));
+            v >>= 7;
+        }
+        out.push_back(static_cast<char>(v));
+    }
+    void bytes(int field, const std::string& b) {
+        varint(static_cast<uint64_t>(field) << 3 | 2);
+        varint(b.size());
+        out += b;
+    }
+    void integer(int field, uint64_t v) {
+        varint(static_cast<uint64_t>(field) << 3);
+        varint(v);
+    }
+    void f32(int field, float f) {
+        varint(static_cast<uint64_t>(field) << 3 | 5);
+        out.append(reinterpret_cast<const char*>(&f), 4);
+    }
+};
+
+std::string tiny_sentencepiece_model(int model_type, bool byte_fallback) {
+    const std::string sp = "\xe2\x96\x81";
+    ProtoWriter m;
+    auto piece = [&](const std::string& text, float score, int type) {
+        ProtoWriter p;
+        p.bytes(1, text);
+        p.f32(2, score);
+        p.integer(3, static_cast<uint64_t>(type));
+        m.bytes(1, p.out);
+    };
+    piece("<unk>", 0.f, 2);
+    piece("<s>", 0.f, 3);
+    piece("</s>", 0.f, 3);
+    piece(sp + "a", -1.0f, 1);
+    piece(sp + "b", -1.5f, 1);
+    piece("a", -2.0f, 1);
+    piece("b", -2.5f, 1);
+    piece(sp + "ab", -1.2f, 1);
+    piece(sp, -3.0f, 1);
+    piece("ab", -2.2f, 1);
+    if (byte_fallback)
+        for (int b = 0; b < 256; ++b) {
+            char name[8];
+            std::snprintf(name, sizeof name, "<0x%02X>", b);
+            piece(name, 0.f, 6);
+        }
+    ProtoWriter t;
+    t.integer(3, static_cast<uint64_t>(model_type));
+    t.integer(35, byte_fallback ? 1 : 0);
+    m.bytes(2, t.out);
+    ProtoWriter n;
+    n.bytes(1, "identity");
+    m.bytes(3, n.out);
+    return m.out;
+}
+
+TEST(sentencepiece_unigram_viterbi_and_decode) {
+    SentencePieceModel m(tiny_sentencepiece_model(1, false), {});
+    CHECK(m.size() == 10 && m.unk_id() == 0 && m.bos_id() == 1 && m.eos_id() == 2 && m.pad_id() == -1);
+    CHECK(m.normalize("  ab   a ") == "\xe2\x96\x81" "ab" "\xe2\x96\x81" "a");
+    // "_ab" (-1.2) beats "_a" + "b" (-3.5); the second word is one piece
+    CHECK(m.encode("ab a") == (std::vector<int64_t>{7, 3}));
+    CHECK(m.decode({1, 7, 3, 2}) == "ab a");
+    // an unknown run merges into one unknown token and decodes to the unknown surface
+    auto pieces = m.encode_as_pieces("a xyz");
+    CHECK(pieces.size() == 3 && pieces[2].second == 0 && pieces[2].first == "xyz");
+    CHECK(m.decode({3, 8, 0}) == "a  \xe2\x81\x87 ");
+    auto best = m.nbest_encode("ab", 3);
+    CHECK(best.size() == 3 && best[0].second >= best[1].second && best[1].second >= best[2].second);
+    CHECK(best[0].first.size() == 1 && best[0].first[0].second == 7);
+    CHECK_THROWS(m.id_to_piece(99), std::out_of_range);
+    CHECK_THROWS(SentencePieceModel(std::string("\x0a\x05zz"), {}), std::invalid_argument);
+}
+
+TEST(sentencepiece_bpe_byte_fallback_and_control_symbols) {
+    SentencePieceModel m(tiny_sentencepiece_model(2, true), {"<pad>@0", "<lang>"});
+    CHECK(m.size() == 10 + 256 + 2 && m.pad_id() == 0 && m.unk_id() == 1 && m.piece_to_id("<lang>") == 267);
+    // merges by score: (_ a) -1.0 first, then (_a b) -1.2
+    CHECK(m.encode("ab") == (std::vector<int64_t>{8}));
+    // 'z' is unknown: one byte piece; the euro sign: three
+    auto ids = m.encode("a z\xe2\x82\xac");
+    CHECK(ids.size() == 1 + 1 + 4 && ids[0] == 4 && ids[1] == 9);
+    CHECK(m.id_to_piece(static_cast<int>(ids[2])) == "<0x7A>" && m.id_to_piece(static_cast<int>(ids[3])) == "<0xE2>");
+    CHECK(m.decode(ids) == "a z\xe2\x82\xac");
+    CHECK(m.decode({0, 4, 267}) == "a");
+    // a torn multi-byte character decodes to the replacement character
+    CHECK(m.decode({ids[3]}) == "\xef\xbf\xbd");
+    std::mt19937_64 rng(1);
+    SamplingOptions drop;
+    drop.alpha = 1.0f;   // every merge dropped: characters only
+    CHECK(m.encode("ab", &drop, &rng) == (std::vector<int64_t>{9, 6, 7}));
+}
+
+TEST(sentencepiece_encoder_tensor_layout) {
+    SentencePieceModel m(tiny_sentencepiece_model(1, false), {});
+    SentencePieceEncoder enc(m, {"<s>"}, {"</s>"}, /*reverse=*/true, false, -1, 0.1f, std::nullopt, false, 0);
+    at::Tensor t = enc.encode("ab a");
+    CHECK(t.scalar_type() == at::kLong && t.numel() == 4);
+    CHECK(t[0].item<int64_t>() == 1 && t[1].item<int64_t>() == 3 && t[2].item<int64_t>() == 7 && t[3].item<int64_t>() == 2);
+    SentencePieceDecoder dec(m, /*reverse=*/true);
+    CHECK(dec.decode(t) == "ab a");
+    CHECK_THROWS(SentencePieceEncoder(m, {"<nope>"}, {}, false, false, -1, 0.1f, std::nullopt, false, 0),
+                 std::invalid_argument);
+    Data out = enc(Data(std::string("a")));
+    CHECK(out.is_tensor() && out.as_tensor().numel() == 3);
 }
 
 TEST(pipeline_broken_after_error_and_reset_recovers_nothing) {

@@ -1,92 +1,100 @@
-"""SentencePiece tokenizers over the ``sentencepiece`` runtime (cf. fairseq2
-``data/tokenizers/sentencepiece.py:19-110``): ``SentencePieceModel`` with extra
-control symbols, encoder with prefix/suffix tokens, sampling and reversal,
-decoder."""
+"""SentencePiece tokenizers on the native runtime of the data pipeline (``csrc/data/sentencepiece.cc``: model reader,
+normalizer, unigram / BPE / character / word segmentation; no dependency on the ``sentencepiece`` package).
+Cf. fairseq2 ``data/tokenizers/sentencepiece.py:19-110``: ``SentencePieceModel`` with extra control symbols, encoder
+with prefix/suffix tokens, sampling and reversal, decoder. Encoders and decoders are native callables, so a
+``DataPipeline.map`` runs them on its worker threads without the interpreter lock."""
 from __future__ import annotations
 
 from pathlib import Path
 from typing import Sequence
 
+import torch
 from torch import Tensor
 
-from fairseq2_b200.data.tokenizers.tokenizer import (TokenDecoder, TokenEncoder, Tokenizer, VocabularyInfo,
-                                                     _to_tensor)
+from fairseq2_b200.data.tokenizers.tokenizer import TokenDecoder, TokenEncoder, Tokenizer, VocabularyInfo
 from fairseq2_b200.typing import Device
+
+
+def _native():  # type: ignore[no-untyped-def]
+    from fairseq2_b200.data.data_pipeline import _n
+
+    return _n
 
 
 class SentencePieceModel:
     """A SentencePiece model with extra control symbols.
 
-    A symbol that the model does not know is appended after the model's pieces. A symbol written ``"<sym>@0"`` is
-    instead INSERTED at index 0 and every piece of the model moves up by one (the reference's native model does the
-    same for NLLB, whose SentencePiece model has no pad symbol: fairseq2 ``models/nllb/tokenizer.py:149-159``)."""
+    A symbol that the model does not know is appended after the model's pieces as a control piece. A symbol written
+    ``"<sym>@0"`` is instead INSERTED at index 0, every piece of the model moves up by one, and the symbol becomes
+    the pad symbol (the reference's native model does the same for NLLB, whose SentencePiece model has no pad
+    symbol: fairseq2 ``models/nllb/tokenizer.py:149-159``)."""
 
     def __init__(self, path: Path | str, control_symbols: Sequence[str] | None = None) -> None:
-        try:
-            import sentencepiece as spm
-        except ImportError as ex:
-            raise RuntimeError("The `sentencepiece` package is required for SentencePiece tokenizers.") from ex
-        self._sp = spm.SentencePieceProcessor()
-        self._sp.Load(str(path))
-        base = self._sp.GetPieceSize()
-        self._front: str | None = None
-        for s in control_symbols or []:
-            if s.endswith("@0"):
-                if self._front is not None:
-                    raise ValueError("Only one control symbol can be inserted at index 0.")
-                self._front = s[:-2]
-        self._shift = 0 if self._front is None else 1
-        self._extra: dict[str, int] = {}
-        for s in control_symbols or []:
-            if s.endswith("@0"):
-                continue
-            idx = self._sp.PieceToId(s)
-            known = idx != self._sp.unk_id() or s == self._sp.IdToPiece(self._sp.unk_id())
-            if not known and s not in self._extra:
-                self._extra[s] = self._shift + base + len(self._extra)
-        self._extra_by_index = {i: s for s, i in self._extra.items()}
+        self._path = str(path)
+        self._control_symbols = list(control_symbols or [])
+        self._m = _native().SentencePieceModel(self._path, self._control_symbols)
+
+    def __getstate__(self) -> dict[str, object]:
+        return {"path": self._path, "control_symbols": self._control_symbols}
+
+    def __setstate__(self, state: dict[str, object]) -> None:
+        self.__init__(state["path"], state["control_symbols"])  # type: ignore[misc, arg-type]
 
     @property
-    def processor(self):  # type: ignore[no-untyped-def]
-        return self._sp
+    def native(self):  # type: ignore[no-untyped-def]
+        return self._m
 
-    @property
-    def index_shift(self) -> int:
-        """What is added to the model's own piece indices (1 if a symbol was inserted at index 0)."""
-        return self._shift
+    def encode(self, text: str) -> list[int]:
+        return list(self._m.encode(text))
 
-    def encode(self, text: str, **kwargs: object) -> list[int]:
-        ids = self._sp.Encode(text, **kwargs)
-        return [int(i) + self._shift for i in ids] if self._shift else [int(i) for i in ids]
+    def encode_as_tokens(self, text: str) -> list[str]:
+        return list(self._m.encode_as_tokens(text))
+
+    def nbest_encode(self, text: str, nbest_size: int) -> list[tuple[list[int], float]]:
+        """The ``nbest_size`` best segmentations of a unigram model with their scores, best first."""
+        return [(list(ids), float(score)) for ids, score in self._m.nbest_encode(text, nbest_size)]
 
     def decode(self, indices: Sequence[int]) -> str:
-        n, sh = self._sp.GetPieceSize(), self._shift
-        return str(self._sp.Decode([i - sh for i in indices if sh <= i < n + sh]))
+        n = self._m.vocabulary_size
+        return str(self._m.decode([int(i) for i in indices if 0 <= int(i) < n]))
+
+    def decode_from_tokens(self, tokens: Sequence[str]) -> str:
+        return str(self._m.decode_from_tokens(list(tokens)))
+
+    def normalize(self, text: str) -> str:
+        return str(self._m.normalize(text))
 
     def token_to_index(self, token: str) -> int:
-        if token == self._front:
-            return 0
-        if token in self._extra:
-            return self._extra[token]
-        return int(self._sp.PieceToId(token)) + self._shift
+        return int(self._m.token_to_index(token))
 
     def index_to_token(self, idx: int) -> str:
-        if idx == 0 and self._front is not None:
-            return self._front
-        if idx in self._extra_by_index:
-            return self._extra_by_index[idx]
-        return str(self._sp.IdToPiece(idx - self._shift))
+        return str(self._m.index_to_token(idx))
+
+    @property
+    def vocabulary_size(self) -> int:
+        return int(self._m.vocabulary_size)
+
+    @property
+    def unk_idx(self) -> int | None:
+        return self._m.unk_idx
+
+    @property
+    def bos_idx(self) -> int | None:
+        return self._m.bos_idx
+
+    @property
+    def eos_idx(self) -> int | None:
+        return self._m.eos_idx
+
+    @property
+    def pad_idx(self) -> int | None:
+        return self._m.pad_idx
 
     @property
     def vocab_info(self) -> VocabularyInfo:
-        sp, sh = self._sp, self._shift
-
-        def opt(i: int) -> int | None:
-            return i + sh if i >= 0 else None
-
-        pad = 0 if self._front is not None else opt(sp.pad_id())
-        return VocabularyInfo(size=sp.GetPieceSize() + sh + len(self._extra), unk_idx=opt(sp.unk_id()),
-                              bos_idx=opt(sp.bos_id()), eos_idx=opt(sp.eos_id()), pad_idx=pad)
+        m = self._m
+        return VocabularyInfo(size=m.vocabulary_size, unk_idx=m.unk_idx, bos_idx=m.bos_idx, eos_idx=m.eos_idx,
+                              pad_idx=m.pad_idx)
 
 
 def load_sentencepiece_model(path: Path | str, control_symbols: Sequence[str] | None = None) -> SentencePieceModel:
@@ -94,24 +102,28 @@ def load_sentencepiece_model(path: Path | str, control_symbols: Sequence[str] | 
 
 
 class SentencePieceEncoder(TokenEncoder):
+    """``enable_sampling``: unigram models sample a segmentation (``nbest_size`` < 0: from all of them, with inverse
+    temperature ``alpha``; > 1: among the n best), BPE models drop merges with probability ``alpha``. The sampler is
+    seeded from the CPU generator, so ``torch.manual_seed`` makes it repeatable."""
+
     def __init__(self, model: SentencePieceModel, *, prefix_tokens: Sequence[str] | None = None,
                  suffix_tokens: Sequence[str] | None = None, reverse: bool = False, enable_sampling: bool = False,
                  nbest_size: int = -1, alpha: float = 0.1, device: Device | None = None, pin_memory: bool = False) -> None:
-        self._m = model
-        self._prefix = [model.token_to_index(t) for t in (prefix_tokens or [])]
-        self._suffix = [model.token_to_index(t) for t in (suffix_tokens or [])]
-        self._reverse, self._sampling, self._nbest, self._alpha = reverse, enable_sampling, nbest_size, alpha
-        self._device, self._pin = device, pin_memory
+        seed = int(torch.randint(0, 2**62, (1,), device="cpu")) if enable_sampling else 0
+        self._e = _native().SentencePieceEncoder(
+            model.native, list(prefix_tokens or []), list(suffix_tokens or []), reverse, enable_sampling, nbest_size,
+            alpha, None if device is None else str(device), pin_memory, seed)
+
+    @property
+    def native(self):  # type: ignore[no-untyped-def]
+        """The native callable: hand it to ``DataPipelineBuilder.map`` to tokenize on the worker threads."""
+        return self._e
 
     def __call__(self, text: str) -> Tensor:
-        ids = self._m.encode(text, enable_sampling=self._sampling, nbest_size=self._nbest, alpha=self._alpha)
-        if self._reverse:
-            ids = ids[::-1]
-        return _to_tensor(self._prefix + list(ids) + self._suffix, self._device, self._pin)
+        return self._e(text)
 
     def encode_as_tokens(self, text: str) -> list[str]:
-        toks = self._m.processor.EncodeAsPieces(text)
-        return toks[::-1] if self._reverse else toks
+        return list(self._e.encode_as_tokens(text))
 
 
 class SentencePieceDecoder(TokenDecoder):
@@ -125,7 +137,8 @@ class SentencePieceDecoder(TokenDecoder):
         return self._m.decode(ids)
 
     def decode_from_tokens(self, tokens: Sequence[str]) -> str:
-        return str(self._m.processor.DecodePieces(list(tokens)))
+        tokens = list(tokens)
+        return self._m.decode_from_tokens(tokens[::-1] if self._reverse else tokens)
 
 
 class BasicSentencePieceTokenizer(Tokenizer):

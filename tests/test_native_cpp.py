@@ -15,10 +15,9 @@ _SO = Path(__file__).resolve().parent.parent / "fairseq2_b200" / "_data_tests.so
 def _rows():  # type: ignore[no-untyped-def]
     import torch  # noqa: F401  (the library links against libtorch)
 
-    if not _SO.exists():
-        from fairseq2_b200.csrc.build import build_data_tests
+    from fairseq2_b200.csrc.build import build_data_tests
 
-        build_data_tests()
+    build_data_tests()   # a no-op unless a source is newer than the library
     name = "_data_tests"
     mod = sys.modules.get(name)
     if mod is None:

@@ -43,7 +43,7 @@ def test_basic_modes_and_round_trip(spm_path: Path) -> None:
 def test_front_inserted_symbol_shifts_every_piece(spm_path: Path) -> None:
     plain = SentencePieceModel(spm_path)
     shifted = SentencePieceModel(spm_path, control_symbols=["__eng__", "<pad>@0"])
-    assert shifted.index_shift == 1 and shifted.token_to_index("<pad>") == 0 and shifted.index_to_token(0) == "<pad>"
+    assert shifted.pad_idx == 0 and shifted.token_to_index("<pad>") == 0 and shifted.index_to_token(0) == "<pad>"
     assert shifted.encode("lazy dog") == [i + 1 for i in plain.encode("lazy dog")]
     assert shifted.token_to_index("</s>") == plain.token_to_index("</s>") + 1
     vi = shifted.vocab_info
