@@ -150,3 +150,36 @@ def test_malformed_models_are_refused(tmp_path, trained: dict[str, tuple]) -> No
             SentencePieceModel(bad)
     with pytest.raises((ValueError, RuntimeError)):
         SentencePieceModel(tmp_path / "absent.model")
+
+
+def test_random_unicode_matches_the_package(trained: dict[str, tuple]) -> None:
+    """Random code points from every UTF-8 length class, odd whitespace, literal control-symbol spellings."""
+    rng = random.Random(1)
+
+    def text() -> str:
+        out = []
+        for _ in range(rng.randint(0, 30)):
+            r = rng.random()
+            if r < 0.3:
+                out.append(rng.choice("abcdefghijklmnopqrstuvwxyz ABC 012"))
+            elif r < 0.4:
+                out.append(rng.choice([" ", "  ", "\t", "\n", " ", "　", "​", "▁", "﻿", "­"]))
+            elif r < 0.5:
+                out.append(rng.choice(["<sep>", "<ctl>", "<s>", "</s>", "<unk>", "<0x41>"]))
+            else:
+                cp = 0xd800
+                while 0xd800 <= cp <= 0xdfff:
+                    cp = rng.choice([rng.randint(0, 0x7f), rng.randint(0x80, 0x7ff), rng.randint(0x800, 0xffff),
+                                     rng.randint(0x10000, 0x10ffff)])
+                out.append(chr(cp))
+        return "".join(out)
+
+    texts = [text() for _ in range(600)]
+    for name in ("unigram", "bpe_byte_fallback", "unigram_case_folding", "bpe_keep_whitespace"):
+        path, ref = trained[name]
+        model = SentencePieceModel(path)
+        for t in texts:
+            ids = ref.EncodeAsIds(t)
+            assert model.encode(t) == ids, (name, t)
+            assert model.encode_as_tokens(t) == ref.EncodeAsPieces(t), (name, t)
+            assert model.decode(ids) == ref.DecodeIds(ids), (name, t)
