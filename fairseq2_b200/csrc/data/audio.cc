@@ -1,5 +1,5 @@
-// WAV decoding, Kaldi-style filter bank features and PNG decoding for the
-// native data pipeline (no external codec libraries are required).
+// Audio decoding front (FLAC in flac.cc, WAV / AIFF / AU in pcm.cc), Kaldi-style filter bank features and PNG /
+// JPEG decoding for the native data pipeline (no external codec libraries are required).
 #include <zlib.h>
 
 #include <cmath>
@@ -11,8 +11,6 @@ namespace fs2d {
 
 namespace {
 
-uint32_t le32(const uint8_t* p) { return p[0] | (p[1] << 8) | (p[2] << 16) | (static_cast<uint32_t>(p[3]) << 24); }
-uint16_t le16(const uint8_t* p) { return static_cast<uint16_t>(p[0] | (p[1] << 8)); }
 uint32_t be32(const uint8_t* p) { return (static_cast<uint32_t>(p[0]) << 24) | (p[1] << 16) | (p[2] << 8) | p[3]; }
 
 }  // namespace
@@ -38,63 +36,11 @@ Data AudioDecoder::operator()(Data&& d) const {
     if (n >= 4 && std::memcmp(b, "OggS", 4) == 0)
         throw std::invalid_argument("Ogg containers (Vorbis/Opus) are lossy codecs that this build does not decode; "
                                     "convert the audio to FLAC or WAV.");
-    if (n < 44 || std::memcmp(b, "RIFF", 4) != 0 || std::memcmp(b + 8, "WAVE", 4) != 0)
-        throw std::invalid_argument("The input audio is neither a RIFF/WAVE nor a FLAC stream.");
-    size_t p = 12;
-    uint16_t fmt = 0, channels = 0, bits = 0;
-    uint32_t rate = 0;
-    const uint8_t* data = nullptr;
-    size_t data_len = 0;
-    while (p + 8 <= n) {
-        const uint32_t len = le32(b + p + 4);
-        if (std::memcmp(b + p, "fmt ", 4) == 0 && p + 8 + 16 <= n) {
-            fmt = le16(b + p + 8);
-            channels = le16(b + p + 10);
-            rate = le32(b + p + 12);
-            bits = le16(b + p + 22);
-            if (fmt == 0xFFFE && len >= 26) fmt = le16(b + p + 8 + 24);  // WAVE_FORMAT_EXTENSIBLE sub-format
-        } else if (std::memcmp(b + p, "data", 4) == 0) {
-            data = b + p + 8;
-            data_len = std::min<size_t>(len, n - (p + 8));
-            break;
-        }
-        p += 8 + len + (len & 1);
-    }
-    if (data == nullptr || channels == 0 || bits == 0) throw std::invalid_argument("The WAV file has no fmt/data chunk.");
-    const size_t bytes = bits / 8;
-    const int64_t frames = static_cast<int64_t>(data_len / (bytes * channels));
-    at::ScalarType out_dtype = dtype_.value_or(fmt == 3 ? at::kFloat : (bits <= 16 ? at::kShort : at::kInt));
-    at::Tensor wav = at::empty({frames, channels}, at::kFloat);
-    float* w = wav.data_ptr<float>();
-    const bool to_float = at::isFloatingType(out_dtype);
-    for (int64_t i = 0; i < frames * channels; ++i) {
-        const uint8_t* s = data + i * bytes;
-        float v;
-        if (fmt == 3 && bits == 32) {
-            std::memcpy(&v, s, 4);
-        } else if (fmt == 1 && bits == 16) {
-            v = static_cast<int16_t>(le16(s));
-            if (to_float) v /= 32768.f;
-        } else if (fmt == 1 && bits == 8) {
-            v = static_cast<float>(s[0]) - 128.f;
-            if (to_float) v /= 128.f;
-        } else if (fmt == 1 && bits == 24) {
-            int32_t x = (s[0] | (s[1] << 8) | (s[2] << 16));
-            if (x & 0x800000) x |= ~0xFFFFFF;
-            v = static_cast<float>(x);
-            if (to_float) v /= 8388608.f;
-        } else if (fmt == 1 && bits == 32) {
-            v = static_cast<float>(static_cast<int32_t>(le32(s)));
-            if (to_float) v /= 2147483648.f;
-        } else {
-            throw std::invalid_argument("The WAV sample format is not supported.");
-        }
-        w[i] = v;
-    }
-    at::Tensor out = wav.to(out_dtype);
-    if (!keepdim_ && channels == 1) out = out.squeeze(-1);
-    std::string format = std::string("WAV/") + (fmt == 3 ? "FLOAT" : "PCM_") + (fmt == 3 ? "" : std::to_string(bits));
-    DataDict res{{"waveform", Data(out)}, {"sample_rate", Data(static_cast<double>(rate))}, {"format", Data(format)}};
+    double rate = 0.0;
+    std::string format;
+    at::Tensor out = decode_pcm_container(b, n, dtype_, rate, format);               // [frames, channels]
+    if (!keepdim_ && out.size(1) == 1) out = out.squeeze(-1);
+    DataDict res{{"waveform", Data(out)}, {"sample_rate", Data(rate)}, {"format", Data(format)}};
     return Data(std::move(res));
 }
 

@@ -80,7 +80,12 @@ private:
 bool is_flac(const uint8_t* b, size_t n);
 at::Tensor decode_flac(const uint8_t* b, size_t n, int& sample_rate, int& bits_per_sample);
 
-// RIFF/WAVE (PCM 8/16/24/32-bit and IEEE float) and FLAC decoder -> {"waveform", "sample_rate", "format"}.
+// pcm.cc: WAV / AIFF / AIFF-C / AU with integer, float, mu-law and A-law samples -> [frames, channels]
+bool is_pcm_container(const uint8_t* b, size_t n);
+at::Tensor decode_pcm_container(const uint8_t* b, size_t n, std::optional<at::ScalarType> dtype, double& rate,
+                                std::string& format);
+
+// WAV, AIFF, AU and FLAC decoder -> {"waveform", "sample_rate", "format"}.
 class AudioDecoder {
 public:
     AudioDecoder(bool keepdim, std::optional<at::ScalarType> dtype) : keepdim_(keepdim), dtype_(dtype) {}
