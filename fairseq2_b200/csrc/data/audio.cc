@@ -1,7 +1,5 @@
 // Audio decoding front (FLAC in flac.cc, WAV / AIFF / AU in pcm.cc), Kaldi-style filter bank features and PNG /
 // JPEG decoding for the native data pipeline (no external codec libraries are required).
-#include <zlib.h>
-
 #include <cmath>
 #include <cstring>
 
@@ -568,96 +566,24 @@ Data ImageDecoder::operator()(Data&& d) const {
     const size_t n = mb.size();
     if (n >= 4 && b[0] == 0xFF && b[1] == 0xD8) {
         at::Tensor img = decode_jpeg(b, n);
+        if (pin_memory_) img = img.pin_memory();
         const double channels = static_cast<double>(img.size(2));
-        DataDict res{{"bit_depth", Data(8.0)}, {"format", Data(channels)}, {"image", Data(img)}};
+        DataDict res{{"channels", Data(channels)}, {"height", Data(static_cast<double>(img.size(0)))},
+                     {"width", Data(static_cast<double>(img.size(1)))}, {"bit_depth", Data(8.0)},
+                     {"format", Data(channels)}};
+        if (device_.has_value() && !device_->is_cpu()) img = img.to(*device_, /*non_blocking=*/pin_memory_);
+        res.emplace_back("image", Data(img));
         return Data(std::move(res));
     }
-    static const uint8_t sig[8] = {0x89, 'P', 'N', 'G', 0x0D, 0x0A, 0x1A, 0x0A};
-    if (n < 8 || std::memcmp(b, sig, 8) != 0)
-        throw std::invalid_argument("The input image is neither a PNG nor a JPEG file.");
-    size_t p = 8;
-    uint32_t width = 0, height = 0;
-    int depth = 0, color = 0, interlace = 0;
-    std::vector<uint8_t> idat, palette;
-    while (p + 12 <= n) {
-        const uint32_t len = be32(b + p);
-        const uint8_t* type = b + p + 4;
-        const uint8_t* body = b + p + 8;
-        if (p + 12 + len > n) throw std::invalid_argument("The PNG file is truncated.");
-        if (std::memcmp(type, "IHDR", 4) == 0) {
-            width = be32(body);
-            height = be32(body + 4);
-            depth = body[8];
-            color = body[9];
-            interlace = body[12];
-        } else if (std::memcmp(type, "PLTE", 4) == 0) {
-            palette.assign(body, body + len);
-        } else if (std::memcmp(type, "IDAT", 4) == 0) {
-            idat.insert(idat.end(), body, body + len);
-        } else if (std::memcmp(type, "IEND", 4) == 0) {
-            break;
-        }
-        p += 12 + len;
-    }
-    if (width == 0 || height == 0) throw std::invalid_argument("The PNG file has no IHDR chunk.");
-    if (interlace != 0) throw std::invalid_argument("Interlaced PNG files are not supported.");
-    int channels = color == 0 ? 1 : color == 2 ? 3 : color == 3 ? 1 : color == 4 ? 2 : 4;
-    if (depth != 8 && depth != 16) throw std::invalid_argument("Only 8- and 16-bit PNG files are supported.");
-    const size_t bpp = static_cast<size_t>(channels) * depth / 8;
-    const size_t stride = width * bpp;
-    std::vector<uint8_t> raw((stride + 1) * height);
-    uLongf out_len = raw.size();
-    if (uncompress(raw.data(), &out_len, idat.data(), idat.size()) != Z_OK || out_len != raw.size())
-        throw std::invalid_argument("The PNG image data cannot be inflated.");
-    std::vector<uint8_t> img(stride * height);
-    for (uint32_t y = 0; y < height; ++y) {
-        const uint8_t ft = raw[y * (stride + 1)];
-        const uint8_t* src = raw.data() + y * (stride + 1) + 1;
-        uint8_t* dst = img.data() + y * stride;
-        const uint8_t* up = y > 0 ? dst - stride : nullptr;
-        for (size_t x = 0; x < stride; ++x) {
-            const int a = x >= bpp ? dst[x - bpp] : 0;
-            const int bb = up ? up[x] : 0;
-            const int c = (up && x >= bpp) ? up[x - bpp] : 0;
-            int pred = 0;
-            switch (ft) {
-                case 0: pred = 0; break;
-                case 1: pred = a; break;
-                case 2: pred = bb; break;
-                case 3: pred = (a + bb) / 2; break;
-                case 4: {
-                    const int pp = a + bb - c, pa = std::abs(pp - a), pb = std::abs(pp - bb), pc = std::abs(pp - c);
-                    pred = (pa <= pb && pa <= pc) ? a : (pb <= pc ? bb : c);
-                    break;
-                }
-                default: throw std::invalid_argument("The PNG file uses an unknown filter type.");
-            }
-            dst[x] = static_cast<uint8_t>(src[x] + pred);
-        }
-    }
-    at::Tensor out;
-    if (color == 3) {
-        out = at::empty({static_cast<int64_t>(height), static_cast<int64_t>(width), 3}, at::kByte);
-        uint8_t* o = out.data_ptr<uint8_t>();
-        for (size_t i = 0; i < static_cast<size_t>(width) * height; ++i) {
-            const size_t idx = static_cast<size_t>(img[i]) * 3;
-            if (idx + 2 >= palette.size())
-                throw std::invalid_argument("The PNG palette index is out of range.");
-            o[3 * i] = palette[idx];
-            o[3 * i + 1] = palette[idx + 1];
-            o[3 * i + 2] = palette[idx + 2];
-        }
-        channels = 3;
-    } else if (depth == 8) {
-        out = at::empty({static_cast<int64_t>(height), static_cast<int64_t>(width), channels}, at::kByte);
-        std::memcpy(out.data_ptr<uint8_t>(), img.data(), img.size());
-    } else {
-        out = at::empty({static_cast<int64_t>(height), static_cast<int64_t>(width), channels}, at::kShort);
-        int16_t* o = out.data_ptr<int16_t>();
-        for (size_t i = 0; i < img.size() / 2; ++i) o[i] = static_cast<int16_t>((img[2 * i] << 8) | img[2 * i + 1]);
-    }
-    DataDict res{{"bit_depth", Data(static_cast<double>(depth))}, {"format", Data(static_cast<double>(channels))},
-                 {"image", Data(out)}};
+    if (!is_png(b, n)) throw std::invalid_argument("The input image is neither a PNG nor a JPEG file.");
+    int depth = 0, color = 0;
+    at::Tensor out = decode_png(b, n, pin_memory_, depth, color);
+    const double channels = static_cast<double>(out.size(2));
+    DataDict res{{"bit_depth", Data(static_cast<double>(depth))}, {"color_type", Data(static_cast<double>(color))},
+                 {"channels", Data(channels)}, {"height", Data(static_cast<double>(out.size(0)))},
+                 {"width", Data(static_cast<double>(out.size(1)))}, {"format", Data(channels)}};
+    if (device_.has_value() && !device_->is_cpu()) out = out.to(*device_, /*non_blocking=*/pin_memory_);
+    res.emplace_back("image", Data(out));
     return Data(std::move(res));
 }
 

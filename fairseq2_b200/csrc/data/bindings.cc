@@ -353,7 +353,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("__call__", [](const WaveformToFbankConverter& a, Data d) { return a(std::move(d)); });
 
     py::class_<ImageDecoder>(m, "ImageDecoder")
-        .def(py::init<>())
+        .def(py::init([](std::optional<std::string> device, bool pin_memory) {
+            std::optional<at::Device> dev;
+            if (device) dev = at::Device(*device);
+            return ImageDecoder(dev, pin_memory);
+        }), py::arg("device") = py::none(), py::arg("pin_memory") = false)
         .def("__call__", [](const ImageDecoder& a, Data d) { return a(std::move(d)); });
 
     py::class_<SentencePieceModel>(m, "SentencePieceModel")

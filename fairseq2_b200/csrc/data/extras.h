@@ -112,12 +112,21 @@ private:
     std::optional<at::ScalarType> dtype_;
 };
 
-// PNG (8/16-bit gray, gray+alpha, RGB, RGBA, palette; non-interlaced) and JPEG (sequential and progressive)
-// decoder -> {"image", "bit_depth", "format"}.
+// png.cc: every colour type and bit depth, Adam7 interlacing, palette transparency, chunk checksums
+bool is_png(const uint8_t* b, size_t n);
+at::Tensor decode_png(const uint8_t* b, size_t n, bool pin_memory, int& bit_depth, int& color_type);
+
+// PNG and JPEG (sequential and progressive) decoder ->
+// {"image" [H, W, C], "channels", "height", "width", "bit_depth", "format" (= channels)}; PNG adds "color_type".
 class ImageDecoder {
 public:
     ImageDecoder() = default;
+    ImageDecoder(std::optional<at::Device> device, bool pin_memory) : device_(device), pin_memory_(pin_memory) {}
     Data operator()(Data&& d) const;
+
+private:
+    std::optional<at::Device> device_;
+    bool pin_memory_ = false;
 };
 
 // sentencepiece.cc: a SentencePiece runtime (model reader, normalizer, unigram / BPE / char / word segmentation).
