@@ -782,7 +782,7 @@ class MapSource final : public DataSource {
 public:
     MapSource(std::unique_ptr<DataSource> in, std::vector<MapFn> fns, std::optional<std::string> selector,
               size_t num_parallel)
-        : in_(std::move(in)), fns_(std::move(fns)), selector_(std::move(selector)), n_(num_parallel) {
+        : in_(std::move(in)), fns_(std::move(fns)), selector_(std::move(selector)), n_(num_parallel), window_(num_parallel) {
         if (n_ > 1) pool_ = std::make_unique<WorkerPool>(n_);
     }
     std::optional<Data> next() override {
@@ -801,6 +801,7 @@ public:
     void reset(bool r) override {
         out_.clear();
         out_pos_ = 0;
+        window_ = n_;
         in_->reset(r);
     }
     void record_position(Tape& t, bool s) const override {
@@ -829,26 +830,37 @@ private:
         for (const auto& fn : fns_) cur = apply_selected(std::move(cur), selector_, fn);
         return cur;
     }
+    // Reads a window of inputs and maps it on the workers, one contiguous slice per worker (output order = input
+    // order). The window starts at `num_parallel_calls` items, so a short or interactive pipeline reads no further
+    // ahead than it asks for, and doubles on every refill up to kMaxItemsPerWorker per worker, so that the cost of
+    // handing work over is spread over many items when the function is cheap.
+    static constexpr size_t kMaxItemsPerWorker = 32;
     bool fill() {
         out_.clear();
         out_pos_ = 0;
         DataList in;
-        while (in.size() < n_) {
+        while (in.size() < window_) {
             auto d = in_->next();
             if (!d) break;
             in.push_back(std::move(*d));
         }
         if (in.empty()) return false;
+        if (in.size() == window_) window_ = std::min(window_ * 2, n_ * kMaxItemsPerWorker);
         out_.resize(in.size());
+        const size_t tasks = std::min(n_, in.size());
+        const size_t per_task = (in.size() + tasks - 1) / tasks;
         std::mutex m;
         std::condition_variable cv;
-        size_t pending = in.size();
-        for (size_t i = 0; i < in.size(); ++i) {
-            pool_->submit([&, i] {
-                try {
-                    out_[i].value = invoke(std::move(in[i]));
-                } catch (...) {
-                    out_[i].error = std::current_exception();
+        size_t pending = tasks;
+        for (size_t k = 0; k < tasks; ++k) {
+            pool_->submit([&, k] {
+                const size_t lo = k * per_task, hi = std::min(in.size(), lo + per_task);
+                for (size_t i = lo; i < hi; ++i) {
+                    try {
+                        out_[i].value = invoke(std::move(in[i]));
+                    } catch (...) {
+                        out_[i].error = std::current_exception();
+                    }
                 }
                 std::lock_guard<std::mutex> lk(m);
                 if (--pending == 0) cv.notify_one();
@@ -876,6 +888,7 @@ private:
     std::optional<std::string> selector_;
     size_t n_;
     std::unique_ptr<WorkerPool> pool_;
+    size_t window_ = 0;
     std::vector<Slot> out_;
     size_t out_pos_ = 0;
 };
