@@ -9,6 +9,8 @@ clipping in this configuration). Random init, synthetic data."""
 from __future__ import annotations
 
 import argparse
+import os
+import sys
 
 import numpy as np
 
@@ -39,9 +41,20 @@ def run_ours(args: argparse.Namespace) -> None:
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
     ext = require_ext()
+    # NCCL only carries control traffic here (barriers, a few scalars; the data moves through the peer-memory
+    # kernels), so its communicators go without NVLS buffers, and they are brought up now, while the device is
+    # empty: the model state below fills most of the device, and a communicator that initialises lazily at the
+    # first barrier after that finds no room (that is how the first 8-GPU attempt of this configuration ended).
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     root = FakeGang(device) if world == 1 else ProcessGroupGang.create_default_process_group(device)
     gangs = create_fsdp_gangs(create_parallel_gangs(root, tp_size=tp))
     dp = gangs.dp
+    if world > 1:
+        warmed: set[int] = set()
+        for g in (root, gangs.dp, gangs.tp, gangs.sdp, gangs.rdp):
+            if g.size > 1 and id(g) not in warmed:
+                warmed.add(id(g))
+                g.barrier()
 
     cfg = get_llama_config("llama3_70b")
     seq_len = args.seq_len if args.seq_len != 8192 else 4096
@@ -75,6 +88,11 @@ def run_ours(args: argparse.Namespace) -> None:
             return loss, num_targets
 
     step_fn = TrainStep(SFTUnit(), optimizer, gangs, max_grad_norm=None)
+    torch.cuda.empty_cache()
+    if rank == 0:
+        free, total = torch.cuda.mem_get_info(device)
+        print(f"model state in place: {torch.cuda.memory_allocated(device) / 2**30:.1f} GiB in tensors, "
+              f"{(total - free) / 2**30:.1f} of {total / 2**30:.1f} GiB of the device in use", file=sys.stderr, flush=True)
 
     rng = np.random.default_rng(1234 + dp.rank)              # tensor-parallel peers read the same sequence
     examples = [make_packed_sft_example(rng, seq_len, cfg.vocab_size, doc_len_range=(128, 2048))
