@@ -67,9 +67,9 @@ class _ParamSpec:
     shape: tuple[int, ...]
     d0: int
     row: int            # elements per dim-0 row
-    chunk: int          # dim-0 rows per rank (ceil)
+    chunk: int          # dim-0 rows per rank (ceil, rounded up so that chunk * row is aligned when sharded)
     shard_off: int      # offset into the flat shard buffers
-    shard_numel: int    # padded elements per rank (chunk * row, aligned)
+    shard_numel: int    # elements per rank: chunk * row (padded at the end only when there is one rank)
     rows_local: int     # real rows owned by this rank
     requires_grad: bool
 
@@ -95,6 +95,12 @@ class FlatParamUnit:
             d0 = shape[0]
             row = int(math.prod(shape[1:])) if len(shape) > 1 else 1
             chunk = (d0 + W - 1) // W
+            if W > 1:
+                # The gathered parameter is the [W * chunk, row] region itself, so a rank's piece must be exactly
+                # chunk * row elements (padding inside the region would shift every later rank's rows) and must
+                # start aligned: round the rows per rank up until chunk * row is a multiple of the alignment.
+                # The last ranks then own fewer rows, or none (a bias of 256 over 8 ranks: 64 rows on four ranks).
+                chunk = _round_up(chunk, _ALIGN // math.gcd(row, _ALIGN))
             shard_numel = _round_up(chunk * row, _ALIGN)
             rows_local = max(0, min(d0, (r + 1) * chunk) - r * chunk)
             specs.append(_ParamSpec(fqn, owners, shape, d0, row, chunk, off, shard_numel, rows_local,

@@ -284,3 +284,82 @@ def test_ranks_running_different_units_reduce_in_one_order() -> None:
     symmetric arena the all-gathers are one-sided and the sharded case works (GPU test of the same name)."""
     for worst in run_distributed(_skipping_units_cpu_worker, 2, False, timeout=120.0):
         assert worst < 1e-5, worst
+
+
+def _odd_shapes_worker(rank: int, world: int):
+    """Parameters whose rows do not divide evenly, and whose per-rank piece is smaller than the alignment of the
+    flat buffers (a bias of 40 over 3 ranks): outputs, reduced gradients and the gathered state must equal a plain
+    copy of the model. Some ranks own no row of the small parameters."""
+    import torch.distributed as dist
+
+    from fairseq2_b200.gang import ProcessGroupGang, create_fsdp_gangs, create_parallel_gangs
+    from fairseq2_b200.optim import AdamW
+    from fairseq2_b200.parallel.fsdp import FSDP
+
+    dev = torch.device("cpu")
+    root = ProcessGroupGang.create_default_process_group(dev)
+    gangs = create_fsdp_gangs(create_parallel_gangs(root))
+
+    class Net(torch.nn.Module):
+        def __init__(self) -> None:
+            super().__init__()
+            self.inp = torch.nn.Linear(24, 40)
+            self.layers = torch.nn.ModuleList(torch.nn.Linear(40, 40) for _ in range(2))
+            self.scale = torch.nn.Parameter(torch.ones(5, 3, 7))           # 21 elements per row
+
+        def forward(self, x):  # type: ignore[no-untyped-def]
+            x = self.inp(x)
+            for layer in self.layers:
+                x = x + torch.tanh(layer(x))
+            return x * self.scale.sum()
+
+    torch.manual_seed(0)
+    plain = Net()
+    model = Net()
+    model.load_state_dict(plain.state_dict())
+    fsdp = FSDP(model, gangs, param_dtype=torch.float32)
+    layout = {s.fqn: (s.chunk, s.row, s.shard_numel, s.rows_local) for u in fsdp.all_units for s in u.specs}
+    opt = AdamW(fsdp.parameters(), lr=1e-2, weight_decay=0.0)
+    ref_opt = torch.optim.AdamW(plain.parameters(), lr=1e-2, weight_decay=0.0)
+    out = {"layout": layout, "fwd": 0.0, "grad": 0.0, "state": 0.0}
+    for step in range(2):
+        x = torch.randn(8, 24, generator=torch.Generator().manual_seed(10 * step + rank))
+        fsdp.zero_grad()
+        plain.zero_grad()
+        y, yp = fsdp(x), plain(x)
+        out["fwd"] = max(out["fwd"], float((y - yp).abs().max()))
+        y.pow(2).mean().backward()
+        fsdp.finish_backward()
+        yp.pow(2).mean().backward()
+        want = {}
+        for n, p in plain.named_parameters():
+            g = p.grad.clone()
+            dist.all_reduce(g)
+            p.grad = g / world
+            want[n] = p.grad
+        for u in fsdp.all_units:
+            for sp in u.specs:
+                if sp.rows_local == 0:
+                    continue
+                w = want[sp.fqn].reshape(sp.d0, sp.row)[u.rank * sp.chunk: u.rank * sp.chunk + sp.rows_local]
+                got = u.grad_shard[sp.shard_off: sp.shard_off + sp.rows_local * sp.row].view(w.shape)
+                out["grad"] = max(out["grad"], float((got - w).abs().max()))
+        opt.step()
+        fsdp.after_optimizer_step()
+        ref_opt.step()
+        full = fsdp.full_state_dict()
+        for n, p in plain.named_parameters():
+            out["state"] = max(out["state"], float((full[n] - p.detach()).abs().max()))
+    root.close()
+    return out
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_shards_smaller_than_the_buffer_alignment(world: int) -> None:
+    for out in run_distributed(_odd_shapes_worker, world, timeout=120.0):
+        assert out["fwd"] < 1e-4 and out["grad"] < 1e-3 and out["state"] < 1e-5, out   # outputs are O(100)
+        for chunk, row, shard_numel, _ in out["layout"].values():
+            assert shard_numel == chunk * row and shard_numel % 64 == 0      # no padding inside a gathered region
+    owners = [sum(1 for o in run_distributed(_odd_shapes_worker, world, timeout=120.0)
+                  if o["layout"]["layers.0.bias"][3] > 0)]
+    assert owners[0] < world                                                 # the 40-element bias: not every rank owns rows
