@@ -286,7 +286,7 @@ def test_ranks_running_different_units_reduce_in_one_order() -> None:
         assert worst < 1e-5, worst
 
 
-def _odd_shapes_worker(rank: int, world: int):
+def _odd_shapes_worker(rank: int, world: int, intra: int | None = None):
     """Parameters whose rows do not divide evenly, and whose per-rank piece is smaller than the alignment of the
     flat buffers (a bias of 40 over 3 ranks): outputs, reduced gradients and the gathered state must equal a plain
     copy of the model. Some ranks own no row of the small parameters."""
@@ -298,7 +298,7 @@ def _odd_shapes_worker(rank: int, world: int):
 
     dev = torch.device("cpu")
     root = ProcessGroupGang.create_default_process_group(dev)
-    gangs = create_fsdp_gangs(create_parallel_gangs(root))
+    gangs = create_fsdp_gangs(create_parallel_gangs(root), intra)      # `intra`: hybrid, shards inside groups of it
 
     class Net(torch.nn.Module):
         def __init__(self) -> None:
@@ -354,12 +354,12 @@ def _odd_shapes_worker(rank: int, world: int):
     return out
 
 
-@pytest.mark.parametrize("world", [2, 3])
-def test_shards_smaller_than_the_buffer_alignment(world: int) -> None:
-    for out in run_distributed(_odd_shapes_worker, world, timeout=120.0):
+@pytest.mark.parametrize("world,intra", [(2, None), (3, None), (4, 2)])
+def test_shards_smaller_than_the_buffer_alignment(world: int, intra: int | None) -> None:
+    outs = run_distributed(_odd_shapes_worker, world, intra, timeout=120.0)
+    for out in outs:
         assert out["fwd"] < 1e-4 and out["grad"] < 1e-3 and out["state"] < 1e-5, out   # outputs are O(100)
         for chunk, row, shard_numel, _ in out["layout"].values():
             assert shard_numel == chunk * row and shard_numel % 64 == 0      # no padding inside a gathered region
-    owners = [sum(1 for o in run_distributed(_odd_shapes_worker, world, timeout=120.0)
-                  if o["layout"]["layers.0.bias"][3] > 0)]
-    assert owners[0] < world                                                 # the 40-element bias: not every rank owns rows
+    # the 40-element bias: 64 rows per rank after rounding, so one rank of every shard group owns all of it
+    assert sum(1 for o in outs if o["layout"]["layers.0.bias"][3] > 0) == world // (intra or world)
