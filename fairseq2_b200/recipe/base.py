@@ -94,6 +94,63 @@ class RecipeModel:
         self.facade = DataParallelFacade(dp_module)
 
 
+class RecipeDataset:
+    """A dataset as a recipe sees it (cf. fairseq2 ``recipe/dataset.py:17-44``; kept for recipes written against
+    the older context API): the opened dataset with the config and family it came from."""
+
+    def __init__(self, inner_dataset: object, config: object, family: object) -> None:
+        self._inner, self._config, self._family = inner_dataset, config, family
+
+    def as_(self, kls: type) -> Any:
+        if not isinstance(self._inner, kls):
+            raise TypeError(f"Dataset is expected to be of type `{kls}`, but is of type `{type(self._inner)}` instead.")
+        return self._inner
+
+    @property
+    def config(self) -> object:
+        return self._config
+
+    @property
+    def family(self) -> object:
+        return self._family
+
+
+class RecipeTokenizer:
+    """A tokenizer as a recipe sees it (cf. fairseq2 ``recipe/tokenizer.py:26-82``): delegates the ``Tokenizer``
+    interface to the loaded tokenizer and carries its config and family."""
+
+    def __init__(self, inner_tokenizer: Any, config: object, family: object) -> None:
+        self._inner, self._config, self._family = inner_tokenizer, config, family
+
+    def create_encoder(self, *, task: str | None = None, lang: str | None = None, mode: str | None = None,
+                       device: Any = None, pin_memory: bool = False) -> Any:
+        return self._inner.create_encoder(task=task, lang=lang, mode=mode, device=device, pin_memory=pin_memory)
+
+    def create_raw_encoder(self, *, device: Any = None, pin_memory: bool = False) -> Any:
+        return self._inner.create_raw_encoder(device=device, pin_memory=pin_memory)
+
+    def create_decoder(self, *, skip_special_tokens: bool = False) -> Any:
+        return self._inner.create_decoder(skip_special_tokens=skip_special_tokens)
+
+    def as_(self, kls: type) -> Any:
+        if not isinstance(self._inner, kls):
+            raise TypeError(
+                f"Tokenizer is expected to be of type `{kls}`, but is of type `{type(self._inner)}` instead.")
+        return self._inner
+
+    @property
+    def config(self) -> object:
+        return self._config
+
+    @property
+    def family(self) -> object:
+        return self._family
+
+    @property
+    def vocab_info(self) -> Any:
+        return self._inner.vocab_info
+
+
 class RecipeContext:
     def __init__(self, config: Any, output_dir: Path, *, checkpoint_dir: Path | None = None,
                  gangs: Gangs | None = None) -> None:

@@ -67,3 +67,20 @@ def test_read_pickle_wrapped_iterator_state_dict() -> None:
     assert list(pipeline) == [3, 4, 5]
     pipeline.reset()
     assert list(pipeline) == [0, 1, 2, 3, 4, 5]
+
+
+def test_recipe_dataset_and_tokenizer_wrappers() -> None:
+    from fairseq2_b200.data.tokenizers.char import CharTokenizer
+    from fairseq2_b200.recipe import RecipeDataset, RecipeTokenizer
+
+    ds = RecipeDataset([1, 2], {"a": 1}, "family")
+    assert ds.as_(list) == [1, 2] and ds.config == {"a": 1} and ds.family == "family"
+    with pytest.raises(TypeError, match="expected to be of type"):
+        ds.as_(dict)
+    inner = CharTokenizer()
+    tok = RecipeTokenizer(inner, None, "char")
+    assert tok.as_(CharTokenizer) is inner and tok.vocab_info == inner.vocab_info
+    ids = tok.create_encoder()("ab")
+    assert tok.create_decoder()(ids[1:-1]) == "ab" and tok.create_raw_encoder()("ab").tolist() == ids[1:-1].tolist()
+    with pytest.raises(TypeError):
+        tok.as_(dict)
