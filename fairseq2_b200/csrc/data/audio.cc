@@ -329,6 +329,8 @@ at::Tensor decode_jpeg(const uint8_t* b, size_t n) {
     int mcus_x = 0, mcus_y = 0;
     size_t p = 2;
     bool got_frame = false, progressive = false, got_scan = false;
+    bool saw_jfif = false, saw_adobe = false;
+    int adobe_transform = 0;
     while (p + 4 <= n) {
         if (b[p] != 0xFF) throw std::invalid_argument("The JPEG marker stream is corrupt.");
         while (p < n && b[p] == 0xFF) ++p;
@@ -339,7 +341,12 @@ at::Tensor decode_jpeg(const uint8_t* b, size_t n) {
         const size_t len = static_cast<size_t>(be16(p));
         if (len < 2 || p + len > n) throw std::invalid_argument("The JPEG file is truncated.");
         const size_t seg = p + 2, seg_end = p + len;
-        if (m == 0xDB) {                                            // DQT
+        if (m == 0xE0 && len >= 7 && std::memcmp(b + seg, "JFIF\0", 5) == 0) {
+            saw_jfif = true;
+        } else if (m == 0xEE && len >= 14 && std::memcmp(b + seg, "Adobe", 5) == 0) {
+            saw_adobe = true;
+            adobe_transform = b[seg + 11];                           // 0: as stored, 1: YCbCr, 2: YCCK
+        } else if (m == 0xDB) {                                     // DQT
             size_t q = seg;
             while (q < seg_end) {
                 const int pq = b[q] >> 4, tq = b[q] & 15;
@@ -374,8 +381,9 @@ at::Tensor decode_jpeg(const uint8_t* b, size_t n) {
             height = be16(seg + 1);
             width = be16(seg + 3);
             const int nc = b[seg + 5];
-            if ((nc != 1 && nc != 3) || width <= 0 || height <= 0 || seg + 6 + 3 * static_cast<size_t>(nc) > seg_end)
-                throw std::invalid_argument("Only grayscale and three-component JPEG files are supported.");
+            if ((nc != 1 && nc != 3 && nc != 4) || width <= 0 || height <= 0 ||
+                seg + 6 + 3 * static_cast<size_t>(nc) > seg_end)
+                throw std::invalid_argument("Only JPEG files with one, three or four components are supported.");
             comps.resize(nc);
             for (int i = 0; i < nc; ++i) {
                 comps[i].id = b[seg + 6 + 3 * i];
@@ -537,18 +545,40 @@ at::Tensor decode_jpeg(const uint8_t* b, size_t n) {
             }
             auto sample = [&](int ci, int x, int y) { return static_cast<int>(full[ci][static_cast<size_t>(y) * width + x]); };
             auto clamp8 = [](float v) { const int i = static_cast<int>(std::lround(v)); return static_cast<uint8_t>(i < 0 ? 0 : (i > 255 ? 255 : i)); };
+            // What the stored components mean (the rules of the JFIF / Adobe conventions): three components are
+            // YCbCr unless an Adobe marker says "no transform" or, without any marker, the component ids spell
+            // "RGB"; four components are CMYK as stored unless the Adobe marker says YCCK. Output: gray, RGB, or
+            // CMYK with the file's polarity (Adobe files store inverted ink values; they are passed on unchanged).
+            bool ycc = false;
+            if (nc == 3) {
+                if (saw_jfif) ycc = true;
+                else if (saw_adobe) ycc = adobe_transform != 0;
+                else ycc = !(comps[0].id == 'R' && comps[1].id == 'G' && comps[2].id == 'B');
+            } else if (nc == 4) {
+                ycc = saw_adobe && adobe_transform == 2;
+            }
             for (int y = 0; y < height; ++y)
                 for (int x = 0; x < width; ++x) {
                     uint8_t* px = o + (static_cast<size_t>(y) * width + x) * nc;
                     if (nc == 1) {
                         px[0] = static_cast<uint8_t>(sample(0, x, y));
-                    } else {
-                        const float Y = static_cast<float>(sample(0, x, y));
-                        const float cb = static_cast<float>(sample(1, x, y)) - 128.f;
-                        const float cr = static_cast<float>(sample(2, x, y)) - 128.f;
-                        px[0] = clamp8(Y + 1.402f * cr);
-                        px[1] = clamp8(Y - 0.344136f * cb - 0.714136f * cr);
-                        px[2] = clamp8(Y + 1.772f * cb);
+                        continue;
+                    }
+                    if (!ycc) {
+                        for (int ci = 0; ci < nc; ++ci) px[ci] = static_cast<uint8_t>(sample(ci, x, y));
+                        continue;
+                    }
+                    const float Y = static_cast<float>(sample(0, x, y));
+                    const float cb = static_cast<float>(sample(1, x, y)) - 128.f;
+                    const float cr = static_cast<float>(sample(2, x, y)) - 128.f;
+                    const uint8_t r = clamp8(Y + 1.402f * cr);
+                    const uint8_t g = clamp8(Y - 0.344136f * cb - 0.714136f * cr);
+                    const uint8_t bl = clamp8(Y + 1.772f * cb);
+                    if (nc == 3) {
+                        px[0] = r, px[1] = g, px[2] = bl;
+                    } else {   // YCCK -> CMYK: the first three planes are the YCbCr form of (255 - C, 255 - M, 255 - Y)
+                        px[0] = static_cast<uint8_t>(255 - r), px[1] = static_cast<uint8_t>(255 - g);
+                        px[2] = static_cast<uint8_t>(255 - bl), px[3] = static_cast<uint8_t>(sample(3, x, y));
                     }
                 }
             return out;

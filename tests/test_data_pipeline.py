@@ -358,3 +358,42 @@ def test_read_text_reencodes_with_iconv(tmp_path) -> None:
         list(read_text(p, encoding="klingon").and_return())
     with pytest.raises(Exception, match="not valid"):
         list(read_text(q, encoding="utf-16").and_return())  # 15 bytes: a truncated code unit
+
+
+def test_image_decoder_jpeg_colour_spaces() -> None:
+    """Four-component files (CMYK as stored; YCCK converted to CMYK) and three-component files stored without a
+    colour transform, against Pillow. Pillow inverts Adobe ink values when it loads a file; the decoder passes
+    them on with the polarity of the file, as libjpeg does."""
+    import io
+
+    import numpy as np
+
+    PIL = pytest.importorskip("PIL.Image")
+    from fairseq2_b200.data.data_pipeline import MemoryBlock
+    from fairseq2_b200.data.image import ImageDecoder
+
+    y, x = np.mgrid[0:67, 0:93]
+    rgb = np.stack([(x * 2 + y) % 256, (x + y * 3) % 256, (x * y // 7) % 256], -1).astype(np.uint8)
+    rgb = (0.5 * rgb + 0.5 * np.roll(rgb, 3, 0)).astype(np.uint8)
+    cmyk = np.concatenate([rgb, ((x + 2 * y) % 256).astype(np.uint8)[..., None]], -1)
+    dec = ImageDecoder()
+    for progressive in (False, True):
+        buf = io.BytesIO()
+        PIL.fromarray(cmyk, mode="CMYK").save(buf, format="JPEG", quality=92, progressive=progressive)
+        data = buf.getvalue()
+        out = dec(MemoryBlock(data))
+        ref = 255 - np.asarray(PIL.open(io.BytesIO(data))).astype(int)
+        assert out["channels"] == 4 and out["image"].shape == (67, 93, 4)
+        assert np.abs(out["image"].numpy().astype(int) - ref).max() <= 2
+        # the same scan data declared as YCCK: byte 11 of the Adobe segment is the transform flag
+        at = data.index(b"Adobe")
+        assert data[at + 11] == 0
+        ycck = data[: at + 11] + b"\x02" + data[at + 12:]
+        out = dec(MemoryBlock(ycck))
+        ref = 255 - np.asarray(PIL.open(io.BytesIO(ycck))).astype(int)
+        assert np.abs(out["image"].numpy().astype(int) - ref).max() <= 4
+    buf = io.BytesIO()
+    PIL.fromarray(rgb).save(buf, format="JPEG", quality=92, keep_rgb=True)       # RGB planes, no YCbCr transform
+    out = dec(MemoryBlock(buf.getvalue()))
+    ref = np.asarray(PIL.open(io.BytesIO(buf.getvalue())).convert("RGB")).astype(int)
+    assert out["channels"] == 3 and np.abs(out["image"].numpy().astype(int) - ref).max() <= 2
