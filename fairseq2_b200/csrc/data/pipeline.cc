@@ -893,6 +893,127 @@ private:
     size_t out_pos_ = 0;
 };
 
+// map with `deterministic=False`: up to 2 x `num_parallel_calls` elements are in flight on the workers at any
+// time and results are handed out in the order in which they finish, so one slow element never holds back the
+// others and the workers never wait for a window to drain. The position of such a stage is the set of finished,
+// not yet returned results plus the position of its input (recording it waits for the elements in flight).
+class AsyncMapSource final : public DataSource {
+public:
+    AsyncMapSource(std::unique_ptr<DataSource> in, std::vector<MapFn> fns, std::optional<std::string> selector,
+                   size_t num_parallel)
+        : in_(std::move(in)), fns_(std::move(fns)), selector_(std::move(selector)), n_(num_parallel),
+          st_(std::make_shared<Shared>()), pool_(std::make_unique<WorkerPool>(num_parallel)) {}
+    ~AsyncMapSource() override {
+        pool_.reset();   // joins the workers: no task outlives the state it writes to
+    }
+    std::optional<Data> next() override {
+        while (true) {
+            top_up();
+            MaybeRelease rel;   // workers running Python callables need the interpreter lock
+            std::unique_lock<std::mutex> lk(st_->m);
+            st_->cv.wait(lk, [&] { return !st_->done.empty() || st_->in_flight == 0; });
+            if (!st_->done.empty()) {
+                Slot slot = std::move(st_->done.front());
+                st_->done.pop_front();
+                lk.unlock();
+                if (slot.error) std::rethrow_exception(slot.error);
+                return std::move(slot.value);
+            }
+            if (eod_) return std::nullopt;
+            // nothing finished, nothing in flight and the input still has elements: read more
+        }
+    }
+    void reset(bool r) override {
+        drain();
+        st_->done.clear();
+        eod_ = false;
+        in_->reset(r);
+    }
+    void record_position(Tape& t, bool s) const override {
+        const_cast<AsyncMapSource*>(this)->drain();
+        DataList rest;
+        for (const Slot& slot : st_->done)
+            if (!slot.error) rest.push_back(slot.value);
+        t.record(Data(std::move(rest)));
+        in_->record_position(t, s);
+    }
+    void reload_position(Tape& t, bool s) override {
+        drain();
+        st_->done.clear();
+        eod_ = false;
+        for (auto& e : t.read().as_list()) st_->done.push_back(Slot{e, nullptr});
+        in_->reload_position(t, s);
+    }
+    Finitude finitude() const override { return in_->finitude(); }
+
+private:
+    struct Slot {
+        Data value;
+        std::exception_ptr error;
+    };
+    struct Shared {
+        std::mutex m;
+        std::condition_variable cv;
+        std::deque<Slot> done;
+        size_t in_flight = 0;
+    };
+    struct MaybeRelease {
+        PyThreadState* st = nullptr;
+        MaybeRelease() {
+            if (PyGILState_Check()) st = PyEval_SaveThread();
+        }
+        ~MaybeRelease() {
+            if (st) PyEval_RestoreThread(st);
+        }
+    };
+    void top_up() {
+        while (!eod_) {
+            {
+                std::lock_guard<std::mutex> lk(st_->m);
+                if (st_->in_flight + st_->done.size() >= 2 * n_) return;
+            }
+            auto d = in_->next();
+            if (!d) {
+                eod_ = true;
+                return;
+            }
+            {
+                std::lock_guard<std::mutex> lk(st_->m);
+                ++st_->in_flight;
+            }
+            auto st = st_;
+            auto item = std::make_shared<Data>(std::move(*d));
+            pool_->submit([this, st, item] {
+                Slot slot;
+                try {
+                    Data cur = std::move(*item);
+                    for (const auto& fn : fns_) cur = apply_selected(std::move(cur), selector_, fn);
+                    slot.value = std::move(cur);
+                } catch (...) {
+                    slot.error = std::current_exception();
+                }
+                std::lock_guard<std::mutex> lk(st->m);
+                st->done.push_back(std::move(slot));
+                --st->in_flight;
+                st->cv.notify_all();
+            });
+        }
+    }
+    void drain() {
+        MaybeRelease rel;
+        std::unique_lock<std::mutex> lk(st_->m);
+        st_->cv.wait(lk, [&] { return st_->in_flight == 0; });
+    }
+
+    std::unique_ptr<DataSource> in_;
+    std::vector<MapFn> fns_;
+    std::optional<std::string> selector_;
+    size_t n_;
+    bool eod_ = false;
+    std::shared_ptr<Shared> st_;
+    std::unique_ptr<WorkerPool> pool_;
+};
+
 // Packs 1-D tensors into fixed-size buffers of `num_elements` elements.
 class PackSource final : public DataSource {
 public:
@@ -1408,8 +1529,10 @@ DataPipelineBuilder DataPipelineBuilder::filter(PredicateFn fn) && {
 }
 
 DataPipelineBuilder DataPipelineBuilder::map(std::vector<MapFn> fns, std::optional<std::string> selector,
-                                              size_t num_parallel_calls, bool) && {
+                                              size_t num_parallel_calls, bool deterministic) && {
     if (num_parallel_calls == 0) throw std::invalid_argument("`num_parallel_calls` must be greater than zero.");
+    if (!deterministic && num_parallel_calls > 1)
+        return DataPipelineBuilder(chain<AsyncMapSource>(std::move(factory_), fns, selector, num_parallel_calls));
     return DataPipelineBuilder(chain<MapSource>(std::move(factory_), fns, selector, num_parallel_calls));
 }
 

@@ -11,6 +11,7 @@ import pytest
 import torch
 
 from fairseq2_b200.data import DataPipeline, read_sequence, read_zipped_records
+from fairseq2_b200.data.data_pipeline import DataPipelineError
 from fairseq2_b200.data.text import read_text
 
 
@@ -178,3 +179,60 @@ def test_operator_reset(name: str, tmp_path: Path) -> None:
     p.reset(reset_rng=True)
     assert _drain(p) == want
     del it
+
+
+# ------------------------------------------------------------------ map(deterministic=False)
+def test_unordered_parallel_map_returns_every_element_once() -> None:
+    import time
+
+    def slow_for_some(x: int) -> int:
+        if x % 7 == 0:
+            time.sleep(0.02)
+        return x * 2
+
+    p = read_sequence(list(range(100))).map(slow_for_some, num_parallel_calls=4, deterministic=False).and_return()
+    out = list(p)
+    assert sorted(out) == [2 * i for i in range(100)]
+    assert out != sorted(out)                          # the slow elements were overtaken
+    p.reset()
+    assert sorted(p) == [2 * i for i in range(100)]
+    # one call at a time, or deterministic (the default): input order
+    assert list(read_sequence(list(range(20))).map(slow_for_some, num_parallel_calls=1, deterministic=False)
+                .and_return()) == [2 * i for i in range(20)]
+    ordered = read_sequence(list(range(20))).map(slow_for_some, num_parallel_calls=4).and_return()
+    assert list(ordered) == [2 * i for i in range(20)]
+
+
+def test_unordered_parallel_map_position_and_errors() -> None:
+    def fn(x: int) -> int:
+        return x + 1000
+
+    def build():  # type: ignore[no-untyped-def]
+        return read_sequence(list(range(50))).map(fn, num_parallel_calls=3, deterministic=False).and_return()
+
+    p = build()
+    it = iter(p)
+    head = [next(it) for _ in range(17)]
+    state = p.state_dict()
+    tail = list(it)
+    assert sorted(head + tail) == [i + 1000 for i in range(50)]
+    q = build()
+    q.load_state_dict(state)
+    assert sorted(q) == sorted(tail)                   # what was finished but not handed out is part of the position
+
+    def boom(x: int) -> int:
+        if x == 13:
+            raise ValueError("thirteen")
+        return x
+
+    r = read_sequence(list(range(30))).map(boom, num_parallel_calls=4, deterministic=False).and_return()
+    with pytest.raises(Exception, match="thirteen"):
+        list(r)
+    with pytest.raises(DataPipelineError):
+        next(iter(r))                                  # broken until reset
+    # native callables run on the workers without the interpreter lock
+    from fairseq2_b200.data.text import StrToIntConverter
+
+    s = read_sequence([str(i) for i in range(200)]).map(StrToIntConverter(), num_parallel_calls=8,
+                                                         deterministic=False).and_return()
+    assert sorted(s) == list(range(200))
