@@ -1,12 +1,10 @@
-"""Evaluation and generation loops (cf. fairseq2 ``evaluator.py:44-345``,
-``validator.py:45-341``, ``generator.py:42-315``).
+"""The evaluation task and the loop it shares with validation and generation (cf. fairseq2 ``evaluator.py:44-345``).
 
 * :class:`EvalUnit` computes metrics of one batch into a metric bag.
-* :class:`Evaluator` is the task that runs a list of ``(unit, data_reader)``
-  pairs under ``no_grad`` + inference autocast and publishes the synced metrics.
-* :class:`StandardValidator` is the same loop packaged as the trainer's
-  validator; it derives a score (higher is better) from a named metric.
-* :class:`GeneratorUnit`/:class:`Generator` run a generation job over a reader.
+* :class:`Evaluator` is the task that runs a list of ``(unit, data_reader)`` pairs under ``no_grad`` + inference
+  autocast and publishes the synced metrics.
+* ``_EvalLoop`` is that loop; :mod:`fairseq2_b200.validator` packages it as the trainer's validator and
+  :mod:`fairseq2_b200.generator` as the generation task (both are re-exported here).
 """
 from __future__ import annotations
 
@@ -21,7 +19,6 @@ from fairseq2_b200.logging import log
 from fairseq2_b200.metrics import MetricBag, sync_and_compute_metrics
 from fairseq2_b200.metrics.common import extend_batch_metric_values
 from fairseq2_b200.task import Task, TaskStopException
-from fairseq2_b200.trainer import Validator
 from fairseq2_b200.utils.progress import create_progress_reporter
 from fairseq2_b200.utils.rng import RngBag
 from fairseq2_b200.utils.stopwatch import Stopwatch
@@ -52,10 +49,6 @@ class EvalUnit(ABC, Generic[BatchT]):
     @property
     @abstractmethod
     def model(self) -> Any: ...
-
-
-class GeneratorUnit(EvalUnit[BatchT]):
-    """Same contract as :class:`EvalUnit`; ``process_batch`` generates and writes its outputs."""
 
 
 def _autocast(device: torch.device, amp: bool, dtype: torch.dtype) -> Any:
@@ -161,83 +154,14 @@ class Evaluator(Task, _EvalLoop):
         return self._step_nr
 
 
-class Generator(Evaluator):
-    """The generation task: identical control flow, metrics published under ``generation``."""
+def __getattr__(name: str) -> Any:
+    # the validator and the generator build on this module: resolve them lazily for importers of the old location
+    if name == "StandardValidator":
+        from fairseq2_b200.validator import StandardValidator
 
-    def __init__(self, unit: GeneratorUnit[Any], data_reader: Any, gangs: Gangs, **kw: Any) -> None:
-        kw.setdefault("category", "generation")
-        super().__init__([unit], [data_reader], gangs, **kw)
+        return StandardValidator
+    if name in ("Generator", "GeneratorUnit"):
+        import fairseq2_b200.generator as g
 
-
-class StandardValidator(Validator, _EvalLoop):
-    """Validation inside training. ``score_metric`` names the metric that becomes the checkpoint score;
-    ``lower_better`` negates it so that a higher score is always better. The best score and its step are tracked
-    across runs (and picked up from the scores of the saved checkpoints after a restart when a
-    ``checkpoint_manager`` is given), and logged next to the last one."""
-
-    def __init__(self, units: Sequence[EvalUnit[Any]], data_readers: Sequence[Any], gangs: Gangs, *,
-                 score_metric: str | None = None, lower_better: bool = False, checkpoint_manager: Any | None = None,
-                 **kw: Any) -> None:
-        kw.setdefault("category", "valid")
-        _EvalLoop.__init__(self, units, data_readers, gangs, **kw)
-        self._score_metric, self._lower_better = score_metric, lower_better
-        self._ckpt = checkpoint_manager
-        self._best_score = float("-inf")
-        self._best_step_nr = -1                     # -1: not yet compared with the checkpoints on disk
-
-    @property
-    def best_score(self) -> float | None:
-        """The best score so far in the metric's own direction (``None`` before the first scored run)."""
-        if self._best_step_nr <= 0:
-            return None
-        return -self._best_score if self._lower_better else self._best_score
-
-    @property
-    def best_step_nr(self) -> int | None:
-        return self._best_step_nr if self._best_step_nr > 0 else None
-
-    def _maybe_restore_best(self) -> None:
-        if self._score_metric is None or self._best_step_nr >= 0:
-            return
-        self._best_step_nr = 0
-        if self._ckpt is not None:
-            scored = self._ckpt.load_scores()       # best first, higher is better
-            if scored:
-                self._best_score, self._best_step_nr = float(scored[0][0]), int(scored[0][1])
-
-    def run(self, train_step_nr: int) -> float | None:
-        log.info("Validation at step {} starting.", train_step_nr)
-        self._maybe_restore_best()
-        scores = []
-        for unit, reader in zip(self._units, self._readers):
-            if unit.name:
-                log.info("Validating {}.", unit.name)
-            values = self._run_unit(unit, reader, train_step_nr)
-            if self._score_metric is not None and values is not None and self._score_metric in values:
-                scores.append(float(values[self._score_metric]))
-        score: float | None = None
-        if self._score_metric is not None:
-            g = self._gangs
-            # the score is computed where tp.rank == 0 and shared so that every rank takes the same decisions
-            t = torch.tensor([sum(scores) / len(scores) if scores else float("nan")], device=g.root.device,
-                             dtype=torch.float64)
-            g.root.broadcast(t, 0)
-            v = float(t.item())
-            if v == v:
-                score = -v if self._lower_better else v
-                if score > self._best_score:
-                    self._best_score, self._best_step_nr = score, train_step_nr
-                log.info("Score - Metric: {} | Last: {:.6g} (step {}) | Best: {:.6g} (step {})", self._score_metric, v,
-                         train_step_nr, -self._best_score if self._lower_better else self._best_score,
-                         self._best_step_nr)
-        log.info("Validation finished.")
-        return score
-
-    def reset(self) -> None:
-        self._step_nr = 0
-        self._stop = False
-        for reader in self._readers:
-            reader.reset()
-
-    def close(self) -> None:
-        pass
+        return getattr(g, name)
+    raise AttributeError(f"module 'fairseq2_b200.evaluator' has no attribute '{name}'")

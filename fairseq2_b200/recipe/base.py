@@ -515,7 +515,7 @@ class RecipeContext:
         return Evaluator(list(units), list(data_readers), self.gangs, **self._eval_kwargs("evaluator"))
 
     def create_generator(self, unit: Any, data_reader: Any) -> Task:
-        from fairseq2_b200.evaluator import Generator
+        from fairseq2_b200.generator import Generator
 
         return Generator(unit, data_reader, self.gangs, **self._eval_kwargs("generator"))
 

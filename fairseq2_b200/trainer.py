@@ -36,6 +36,7 @@ from fairseq2_b200.nn.data_parallel import DataParallelFacade
 from fairseq2_b200.task import Task, TaskStopException
 from fairseq2_b200.utils.rng import RngBag
 from fairseq2_b200.utils.stopwatch import DeviceStopwatch, Stopwatch
+from fairseq2_b200.validator import NoopValidator, Validator
 
 BatchT = TypeVar("BatchT")
 
@@ -171,24 +172,6 @@ def _arm_fused(self: TrainStep, model: Any, batches: Sequence[Any]) -> Tensor | 
 
 
 TrainStep._maybe_arm_fused_optimizer = _arm_fused  # type: ignore[attr-defined]
-
-
-class Validator(ABC):
-    """Runs validation and returns a score (higher is better) or ``None``."""
-
-    @abstractmethod
-    def run(self, train_step_nr: int) -> float | None: ...
-
-    def reset(self) -> None:
-        pass
-
-    def close(self) -> None:
-        pass
-
-
-class NoopValidator(Validator):
-    def run(self, train_step_nr: int) -> float | None:
-        return None
 
 
 class _State(Enum):

@@ -7,7 +7,7 @@ from typing import Any, TextIO
 
 from fairseq2_b200.datasets import DataReadError, SequenceBatch
 from fairseq2_b200.datasets.family import register_dataset_family
-from fairseq2_b200.evaluator import GeneratorUnit
+from fairseq2_b200.generator import GeneratorUnit
 from fairseq2_b200.metrics import MetricBag
 from fairseq2_b200.metrics.aggregation import Sum
 from fairseq2_b200.recipe.base import GenerationRecipe, RecipeContext, RecipeModel

@@ -11,7 +11,8 @@ from torch import Tensor
 
 from fairseq2_b200.datasets import SequenceBatch
 from fairseq2_b200.datasets.family import register_dataset_family
-from fairseq2_b200.evaluator import EvalUnit, StandardValidator
+from fairseq2_b200.evaluator import EvalUnit
+from fairseq2_b200.validator import StandardValidator
 from fairseq2_b200.metrics import MetricBag
 from fairseq2_b200.metrics.common import update_nll_loss_metric, update_seq_batch_metrics
 from fairseq2_b200.recipe.base import RecipeContext, RecipeModel, TrainRecipe

@@ -14,7 +14,8 @@ from torch.nn import Module
 
 from fairseq2_b200.datasets import Seq2SeqBatch
 from fairseq2_b200.datasets.family import register_dataset_family
-from fairseq2_b200.evaluator import EvalUnit, StandardValidator
+from fairseq2_b200.evaluator import EvalUnit
+from fairseq2_b200.validator import StandardValidator
 from fairseq2_b200.logging import log
 from fairseq2_b200.metrics import MetricBag
 from fairseq2_b200.metrics.aggregation import Mean, Sum

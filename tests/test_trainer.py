@@ -225,7 +225,8 @@ def test_kernel_wait_timeout_aborts_the_step() -> None:
 def test_validator_tracks_best_score_and_leaves_rng_alone(tmp_path) -> None:
     """The validator reports the best score so far (restored from checkpoint scores after a restart) and the random
     state of the surrounding job is the same whether or not a validation ran."""
-    from fairseq2_b200.evaluator import EvalUnit, StandardValidator
+    from fairseq2_b200.evaluator import EvalUnit
+    from fairseq2_b200.validator import StandardValidator
     from fairseq2_b200.gang import create_fake_gangs
     from fairseq2_b200.metrics import Mean
 
