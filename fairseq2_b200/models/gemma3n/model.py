@@ -2,6 +2,12 @@
 residuals, per-layer input embeddings, local/global attention with two RoPE bases, query/key/value RMS norms,
 key/value sharing across the last layers, Gaussian top-k activation sparsity and final logit soft-capping
 (cf. fairseq2 ``models/gemma3n/{altup,decoder_layer,decoder,frontend,model}.py``).
+
+Tensor parallelism (``tp_gang`` of size > 1): the attention heads and the FFN inner dimension are split over the gang
+(q/k/v and gate/up column-sharded, o and down row-sharded with an all-reduce of their outputs); everything that is
+``model_dim`` wide -- embeddings, AltUp, LAuReL, per-layer inputs, norms, the output projection -- is replicated and
+sees identical activations on every rank. The cut-off of the activation sparsity is a statistic over the whole
+inner dimension: its two moments are summed over the gang.
 """
 from __future__ import annotations
 
@@ -13,13 +19,16 @@ import torch.nn.functional as F
 from torch import Tensor
 from torch.nn import Module, ModuleList, Parameter
 
+from fairseq2_b200.gang import Gang, ReduceOperation
 from fairseq2_b200.models.gemma3n.config import Gemma3nConfig, is_global_layer, kv_source_layer
 from fairseq2_b200.nn import BatchLayout
 from fairseq2_b200.nn.functional import cross_entropy
 from fairseq2_b200.nn.incremental_state import IncrementalState, IncrementalStateBag
 from fairseq2_b200.nn.normalization import RMSNorm
-from fairseq2_b200.nn.projection import Linear
+from fairseq2_b200.nn.projection import ColumnShardedLinear, Linear, Projection, RowShardedLinear
+from fairseq2_b200.ops import norm as _norm_ops
 from fairseq2_b200.ops.attention import varlen_attention
+from fairseq2_b200.ops.tensor_parallel import reduce_on_backward
 from fairseq2_b200.typing import DataType, Device
 
 
@@ -27,6 +36,36 @@ def _rms(x: Tensor, eps: float) -> Tensor:
     """Scale-free RMS normalisation in fp32."""
     xf = x.float()
     return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).type_as(x)
+
+
+class _SumOverGang(torch.autograd.Function):
+    """Sum over the gang in the forward AND the backward pass: for a value that every rank then uses in its own
+    shard of a computation (so the gradients of all ranks' uses add up)."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, gang: Gang) -> Tensor:  # type: ignore[override]
+        ctx.gang = gang
+        y = x.clone()
+        gang.all_reduce(y, ReduceOperation.SUM)
+        return y
+
+    @staticmethod
+    def backward(ctx, g: Tensor):  # type: ignore[override]
+        g = g.clone()
+        ctx.gang.all_reduce(g, ReduceOperation.SUM)
+        return g, None
+
+
+def _column(tp: Gang | None, input_dim: int, output_dim: int, kw: dict) -> Projection:
+    if tp is None or tp.size == 1:
+        return Linear(input_dim, output_dim, bias=False, **kw)
+    return ColumnShardedLinear(tp, input_dim, output_dim, False, gather_output=False, **kw)
+
+
+def _row(tp: Gang | None, input_dim: int, output_dim: int, kw: dict) -> Projection:
+    if tp is None or tp.size == 1:
+        return Linear(input_dim, output_dim, bias=False, **kw)
+    return RowShardedLinear(tp, input_dim, output_dim, False, scatter_input=False, **kw)
 
 
 class AltUp(Module):
@@ -85,12 +124,15 @@ class Laurel(Module):
 
 
 class Gemma3nFFN(Module):
-    def __init__(self, cfg: Gemma3nConfig, sparsity: float, device: Device | None, dtype: DataType | None) -> None:
+    def __init__(self, cfg: Gemma3nConfig, sparsity: float, device: Device | None, dtype: DataType | None,
+                 tp_gang: Gang | None = None) -> None:
         super().__init__()
         kw = {"device": device, "dtype": dtype}
-        self.gate_proj = Linear(cfg.model_dim, cfg.ffn_inner_dim, bias=False, **kw)
-        self.up_proj = Linear(cfg.model_dim, cfg.ffn_inner_dim, bias=False, **kw)
-        self.down_proj = Linear(cfg.ffn_inner_dim, cfg.model_dim, bias=False, **kw)
+        self.tp = tp_gang if tp_gang is not None and tp_gang.size > 1 else None
+        self.inner_dim = cfg.ffn_inner_dim
+        self.gate_proj = _column(self.tp, cfg.model_dim, cfg.ffn_inner_dim, kw)
+        self.up_proj = _column(self.tp, cfg.model_dim, cfg.ffn_inner_dim, kw)
+        self.down_proj = _row(self.tp, cfg.ffn_inner_dim, cfg.model_dim, kw)
         self.sparsity = sparsity
         # standard-normal quantile of the target sparsity: entries below mean + z * std are zeroed
         self.std_multiplier = math.sqrt(2.0) * float(torch.erfinv(torch.tensor(2.0 * sparsity - 1.0))) if sparsity > 0 else 0.0
@@ -98,8 +140,16 @@ class Gemma3nFFN(Module):
     def forward(self, x: Tensor) -> Tensor:
         gate = self.gate_proj(x)
         if self.sparsity > 0.0:
-            mean = gate.mean(dim=-1, keepdim=True)
-            std = gate.std(dim=-1, keepdim=True, unbiased=False)
+            if self.tp is None:
+                mean = gate.mean(dim=-1, keepdim=True)
+                std = gate.std(dim=-1, keepdim=True, unbiased=False)
+            else:
+                # this rank holds a slice of the inner dimension: first and second moment over all slices
+                gf = gate.float()
+                moments = _SumOverGang.apply(torch.stack([gf.sum(-1), gf.pow(2).sum(-1)], dim=-1), self.tp)
+                mean = (moments[..., :1] / self.inner_dim)
+                std = (moments[..., 1:] / self.inner_dim - mean.pow(2)).clamp_min(0.0).sqrt()
+                mean, std = mean.type_as(gate), std.type_as(gate)
             gate = F.relu(gate - (mean + std * self.std_multiplier))
         return self.down_proj(F.gelu(gate, approximate="tanh") * self.up_proj(x))
 
@@ -147,31 +197,48 @@ class _AttnGeometry:
 
 
 class Gemma3nAttention(Module):
-    def __init__(self, cfg: Gemma3nConfig, layer_idx: int, device: Device | None, dtype: DataType | None) -> None:
+    def __init__(self, cfg: Gemma3nConfig, layer_idx: int, device: Device | None, dtype: DataType | None,
+                 tp_gang: Gang | None = None) -> None:
         super().__init__()
         kw = {"device": device, "dtype": dtype}
         H, Hkv, D = cfg.num_attn_heads, cfg.num_key_value_heads, cfg.head_dim
-        self.H, self.Hkv, self.D, self.eps = H, Hkv, D, cfg.rms_norm_eps
+        tp = tp_gang if tp_gang is not None and tp_gang.size > 1 else None
+        if tp is not None and (H % tp.size or Hkv % tp.size):
+            raise ValueError(f"The tensor parallel size ({tp.size}) must divide the number of attention heads ({H}) "
+                             f"and of key-value heads ({Hkv}).")
+        shards = 1 if tp is None else tp.size
+        # heads of this rank
+        self.H, self.Hkv, self.D, self.eps = H // shards, Hkv // shards, D, cfg.rms_norm_eps
         self.is_global = is_global_layer(layer_idx, cfg.num_layers)
         self.window = None if self.is_global else cfg.sliding_window
         self.kv_source = kv_source_layer(layer_idx, cfg.num_layers, cfg.num_kv_shared_layers)
-        self.q_proj = Linear(cfg.model_dim, H * D, bias=False, **kw)
-        self.k_proj = Linear(cfg.model_dim, Hkv * D, bias=False, **kw)
-        self.v_proj = Linear(cfg.model_dim, Hkv * D, bias=False, **kw)
-        self.o_proj = Linear(H * D, cfg.model_dim, bias=False, **kw)
+        self.q_proj = _column(tp, cfg.model_dim, H * D, kw)
+        self.k_proj = _column(tp, cfg.model_dim, Hkv * D, kw)
+        self.v_proj = _column(tp, cfg.model_dim, Hkv * D, kw)
+        self.o_proj = _row(tp, H * D, cfg.model_dim, kw)
         self.q_norm = RMSNorm(D, bias=False, eps=cfg.rms_norm_eps, **kw)
         self.k_norm = RMSNorm(D, bias=False, eps=cfg.rms_norm_eps, **kw)
+        self.tp = tp
+
+    def _head_norm(self, norm: RMSNorm, x: Tensor) -> Tensor:
+        """The per-head norms have one weight vector for all heads. With the heads split over ranks every rank
+        only sees the gradient of its own heads: the weight enters through an identity whose backward pass sums
+        over the gang, so the replicated weight gets the whole gradient on every rank."""
+        if self.tp is None:
+            return norm(x)
+        return _norm_ops.rms_norm(x, norm.normalized_shape, reduce_on_backward(norm.weight, self.tp), norm.eps,
+                                  bias=None)
 
     def forward(self, x: Tensor, cos: Tensor, sin: Tensor, geo: _AttnGeometry,
                 shared_kv: dict[int, tuple[Tensor, Tensor]], layer_idx: int,
                 state_bag: IncrementalStateBag | None = None) -> Tensor:
         """``x``: ``[T, D_model]`` (tokens of all sequences, flattened)."""
         T = x.shape[0]
-        q = _rope_half(self.q_norm(self.q_proj(x).view(T, self.H, self.D)), cos, sin)
+        q = _rope_half(self._head_norm(self.q_norm, self.q_proj(x).view(T, self.H, self.D)), cos, sin)
         if self.kv_source is not None and self.kv_source in shared_kv:
             k, v = shared_kv[self.kv_source]
         else:
-            k = _rope_half(self.k_norm(self.k_proj(x).view(T, self.Hkv, self.D)), cos, sin)
+            k = _rope_half(self._head_norm(self.k_norm, self.k_proj(x).view(T, self.Hkv, self.D)), cos, sin)
             v = _rms(self.v_proj(x).view(T, self.Hkv, self.D), self.eps)
             if state_bag is not None:
                 # keys/values of the earlier steps come from the cache; the new ones are appended
@@ -192,13 +259,15 @@ class Gemma3nAttention(Module):
 
 
 class Gemma3nDecoderLayer(Module):
-    def __init__(self, cfg: Gemma3nConfig, layer_idx: int, device: Device | None, dtype: DataType | None) -> None:
+    def __init__(self, cfg: Gemma3nConfig, layer_idx: int, device: Device | None, dtype: DataType | None,
+                 tp_gang: Gang | None = None) -> None:
         super().__init__()
         kw = {"device": device, "dtype": dtype}
         d, p = cfg.model_dim, cfg.hidden_size_per_layer_input
         self.layer_idx, self.active, self.correct_scale = layer_idx, cfg.altup_active_idx, cfg.altup_correct_scale
-        self.self_attn = Gemma3nAttention(cfg, layer_idx, device, dtype)
-        self.mlp = Gemma3nFFN(cfg, cfg.activation_sparsity if layer_idx < cfg.num_sparse_layers else 0.0, device, dtype)
+        self.self_attn = Gemma3nAttention(cfg, layer_idx, device, dtype, tp_gang)
+        self.mlp = Gemma3nFFN(cfg, cfg.activation_sparsity if layer_idx < cfg.num_sparse_layers else 0.0, device, dtype,
+                              tp_gang)
         norm = lambda: RMSNorm(d, bias=False, eps=cfg.rms_norm_eps, **kw)  # noqa: E731
         self.input_layernorm, self.post_attention_layernorm = norm(), norm()
         self.pre_feedforward_layernorm, self.post_feedforward_layernorm = norm(), norm()
@@ -230,7 +299,8 @@ class Gemma3nDecoderLayer(Module):
 class Gemma3nModel(Module):
     """Decoder-only LM with the ``TransformerLM`` calling convention: ``forward(seqs, layout, targets=None, ...)``."""
 
-    def __init__(self, cfg: Gemma3nConfig, *, device: Device | None = None, dtype: DataType | None = None) -> None:
+    def __init__(self, cfg: Gemma3nConfig, *, device: Device | None = None, dtype: DataType | None = None,
+                 tp_gang: Gang | None = None) -> None:
         super().__init__()
         kw = {"device": device, "dtype": dtype}
         self.cfg = cfg
@@ -242,7 +312,7 @@ class Gemma3nModel(Module):
         self.per_layer_projection_norm = RMSNorm(p, bias=False, eps=cfg.rms_norm_eps, **kw)
         self.altup_projections = ModuleList([Linear(d, d, bias=False, **kw) for _ in range(1, cfg.altup_num_inputs)])
         self.altup_unembed_projections = ModuleList([Linear(d, d, bias=False, **kw) for _ in range(1, cfg.altup_num_inputs)])
-        self.layers = ModuleList([Gemma3nDecoderLayer(cfg, i, device, dtype) for i in range(L)])
+        self.layers = ModuleList([Gemma3nDecoderLayer(cfg, i, device, dtype, tp_gang) for i in range(L)])
         self.norm = RMSNorm(d, bias=False, eps=cfg.rms_norm_eps, **kw)
         self.lm_head: Linear | None = None if cfg.tied_embeddings else Linear(d, cfg.vocab_size, bias=False, **kw)
         self.audio_tower: Module | None = None

@@ -111,3 +111,94 @@ def test_tensor_parallel_training_matches_single_rank(world: int, tp: int, sp: b
                 assert torch.allclose(p, parts[0], atol=1e-6), f"{k}: replicas over the tp gang differ"
         atol = 3e-3 if "embed" in k else 2e-4
         assert torch.allclose(got, v, atol=atol, rtol=1e-3), k
+
+
+# ------------------------------------------------------------------ Gemma 3n
+def _gemma_cfg():
+    from dataclasses import replace
+
+    from fairseq2_b200.models.gemma3n.config import gemma3n_tiny
+
+    return replace(gemma3n_tiny(), num_kv_shared_layers=2, num_layers=6)
+
+
+def _gemma_batches(steps: int):
+    g = torch.Generator().manual_seed(5)
+    return [torch.randint(1, 320, (2, 18), generator=g) for _ in range(steps)]
+
+
+def _gemma_reference(steps: int):
+    from fairseq2_b200.models.gemma3n import create_gemma3n_model
+    from fairseq2_b200.nn import BatchLayout
+
+    torch.manual_seed(17)
+    model = create_gemma3n_model(_gemma_cfg())
+    with torch.no_grad():                                    # zero-initialised upstream: would hide the AltUp scale
+        for n, p in model.named_parameters():
+            if "correct_output_scale" in n:
+                p.fill_(0.3)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-3, weight_decay=0.0)
+    losses = []
+    for ids in _gemma_batches(steps):
+        opt.zero_grad()
+        loss = model(ids[:, :-1], BatchLayout.of(ids[:, :-1]), targets=ids[:, 1:], reduction="mean")
+        loss.backward()
+        opt.step()
+        losses.append(float(loss.detach()))
+    with torch.no_grad():
+        logits = model(_gemma_batches(1)[0][:, :-1], BatchLayout.of(_gemma_batches(1)[0][:, :-1]))
+    return losses, logits
+
+
+def _gemma_worker(rank: int, world: int, steps: int):
+    from fairseq2_b200.gang import ProcessGroupGang, create_parallel_gangs
+    from fairseq2_b200.models.gemma3n import create_gemma3n_model
+    from fairseq2_b200.nn import BatchLayout
+    from fairseq2_b200.nn.sharded import get_shard_dims
+
+    root = ProcessGroupGang.create_default_process_group(torch.device("cpu"))
+    gangs = create_parallel_gangs(root, tp_size=world)
+    torch.manual_seed(17)
+    model = create_gemma3n_model(_gemma_cfg(), gangs)
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if "correct_output_scale" in n:
+                p.fill_(0.3)
+    dims = get_shard_dims(model)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-3, weight_decay=0.0)
+    losses = []
+    for ids in _gemma_batches(steps):
+        opt.zero_grad()
+        loss = model(ids[:, :-1], BatchLayout.of(ids[:, :-1]), targets=ids[:, 1:], reduction="mean")
+        loss.backward()
+        opt.step()
+        losses.append(float(loss.detach()))
+    with torch.no_grad():
+        logits = model(_gemma_batches(1)[0][:, :-1], BatchLayout.of(_gemma_batches(1)[0][:, :-1]))
+    heads = (model.layers[0].self_attn.H, model.layers[0].self_attn.Hkv)
+    root.close()
+    return losses, logits.numpy(), dims, heads
+
+
+def test_gemma3n_tensor_parallel_training_matches_single_rank() -> None:
+    """Heads and the FFN inner dimension split over two ranks (including the layers with activation sparsity, whose
+    cut-off needs moments over the whole inner dimension, and the layers that reuse earlier keys / values): losses of
+    three optimizer steps and the logits afterwards equal the single-process model's."""
+    steps = 3
+    want_losses, want_logits = _gemma_reference(steps)
+    for losses, logits, dims, heads in run_distributed(_gemma_worker, 2, steps, timeout=180.0):
+        assert heads == (2, 1)
+        assert losses == pytest.approx(want_losses, rel=2e-4)
+        logits = torch.from_numpy(logits)
+        assert torch.allclose(logits, want_logits, atol=2e-3), float((logits - want_logits).abs().max())
+        assert dims["layers.0.self_attn.q_proj.weight"] == 0 and dims["layers.0.self_attn.o_proj.weight"] == 1
+        assert dims["layers.1.mlp.gate_proj.weight"] == 0 and dims["layers.1.mlp.down_proj.weight"] == 1
+        assert "layers.0.laurel.linear_left.weight" not in dims
+    from fairseq2_b200.gang import FakeGang, Gangs
+    from fairseq2_b200.models.gemma3n import create_gemma3n_model
+
+    dev = torch.device("cpu")
+    one = FakeGang(dev)
+    four = Gangs(root=FakeGang(dev, rank=0, size=4), dp=one, rdp=one, sdp=one, tp=FakeGang(dev, rank=0, size=4), pp=one)
+    with pytest.raises(ValueError, match="key-value heads"):
+        create_gemma3n_model(_gemma_cfg(), four)
