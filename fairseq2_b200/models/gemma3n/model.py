@@ -26,7 +26,6 @@ from fairseq2_b200.nn.functional import cross_entropy
 from fairseq2_b200.nn.incremental_state import IncrementalState, IncrementalStateBag
 from fairseq2_b200.nn.normalization import RMSNorm
 from fairseq2_b200.nn.projection import ColumnShardedLinear, Linear, Projection, RowShardedLinear
-from fairseq2_b200.ops import norm as _norm_ops
 from fairseq2_b200.ops.attention import varlen_attention
 from fairseq2_b200.ops.tensor_parallel import reduce_on_backward
 from fairseq2_b200.typing import DataType, Device
@@ -226,8 +225,7 @@ class Gemma3nAttention(Module):
         over the gang, so the replicated weight gets the whole gradient on every rank."""
         if self.tp is None:
             return norm(x)
-        return _norm_ops.rms_norm(x, norm.normalized_shape, reduce_on_backward(norm.weight, self.tp), norm.eps,
-                                  bias=None)
+        return norm.apply_with(x, reduce_on_backward(norm.weight, self.tp), None)
 
     def forward(self, x: Tensor, cos: Tensor, sin: Tensor, geo: _AttnGeometry,
                 shared_kv: dict[int, tuple[Tensor, Tensor]], layer_idx: int,

@@ -26,6 +26,7 @@ from fairseq2_b200.nn.normalization import LayerNorm
 from fairseq2_b200.nn.position_encoder import PositionEncoder
 from fairseq2_b200.nn.projection import ColumnShardedLinear, Linear, Projection, RowShardedLinear
 from fairseq2_b200.ops.gemm import linear as _linear
+from fairseq2_b200.ops.tensor_parallel import reduce_on_backward
 from fairseq2_b200.typing import DataType, Device
 
 
@@ -288,6 +289,7 @@ class StandardMultiheadAttention(MultiheadAttention):
         self.num_key_value_heads, self.head_dim, self.kv_dim = nkv, hd, kv_dim
         tp = gangs.tp if gangs is not None and gangs.tp.size > 1 else None
         self.tp_size = tp.size if tp is not None else 1
+        self._tp_gang = tp
         if tp is not None and (num_heads % tp.size or nkv % tp.size):
             raise ValueError("`num_heads` and `num_key_value_heads` must be multiples of the tensor parallel size.")
 
@@ -326,6 +328,18 @@ class StandardMultiheadAttention(MultiheadAttention):
                                       dtype=dtype)
         self.state_factory = state_factory
 
+    def _head_norm(self, norm: LayerNorm, x: Tensor) -> Tensor:
+        """A per-head q/k norm has ONE weight vector for all heads. With the heads split over tensor-parallel ranks
+        and replicated activations, a rank's gradient of that weight only covers its own heads, and nothing
+        downstream sums replicated parameters over the gang: the weight therefore enters through an identity whose
+        backward pass does. (With sequence-parallel activations every replicated parameter has a partial gradient
+        and the data-parallel engine sums them all, this one included.)"""
+        if self._tp_gang is None or self.sequence_parallel or norm.weight is None or not torch.is_grad_enabled():
+            return norm(x)
+        weight = reduce_on_backward(norm.weight, self._tp_gang)
+        bias = reduce_on_backward(norm.bias, self._tp_gang) if norm.bias is not None else None
+        return norm.apply_with(x, weight, bias)
+
     # ------------------------------------------------------------------ forward
     def forward(self, seqs, seqs_layout, keys, keys_layout, values, bias_cache, *, state_bag=None):  # type: ignore[override]
         H = self.num_heads // self.tp_size
@@ -347,7 +361,7 @@ class StandardMultiheadAttention(MultiheadAttention):
                 q = self.q_norm(q)
             q = q.unflatten(-1, (H, D))
             if self.q_norm is not None and not self.qk_norm_over_heads:
-                q = self.q_norm(q)
+                q = self._head_norm(self.q_norm, q)
         if self.pos_encoder is not None:
             q = self.pos_encoder(q, seqs_layout, state_bag=state_bag)
 
@@ -363,7 +377,7 @@ class StandardMultiheadAttention(MultiheadAttention):
                 k = k.unflatten(-1, (Hkv, D))
                 v = self.v_proj(values).unflatten(-1, (Hkv, D))
                 if self.k_norm is not None and not self.qk_norm_over_heads:
-                    k = self.k_norm(k)
+                    k = self._head_norm(self.k_norm, k)
             if self.pos_encoder is not None:
                 k = self.pos_encoder(k, keys_layout, state_bag=state_bag)
             if state_bag is not None and not self.training:

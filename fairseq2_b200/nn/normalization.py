@@ -53,6 +53,11 @@ class LayerNorm(Module, ABC):
     @abstractmethod
     def forward(self, x: Tensor) -> Tensor: ...
 
+    @abstractmethod
+    def apply_with(self, x: Tensor, weight: Tensor | None, bias: Tensor | None) -> Tensor:
+        """The same normalisation with ``weight`` / ``bias`` given by the caller instead of the module's own
+        (tensor-parallel callers pass the parameters through an identity whose backward sums over the gang)."""
+
     def extra_repr(self) -> str:
         s = f"normalized_shape={self.normalized_shape}, eps={self.eps:G}, elementwise_affine={self.elementwise_affine}"
         return s
@@ -64,12 +69,17 @@ class StandardLayerNorm(LayerNorm):
         super().__init__(*a, **kw)
 
     def forward(self, x: Tensor) -> Tensor:
-        return _norm_ops.layer_norm(x, self.normalized_shape, self.weight, self.bias, self.eps,
-                                    cast_fp32=self.cast_fp32)
+        return self.apply_with(x, self.weight, self.bias)
+
+    def apply_with(self, x: Tensor, weight: Tensor | None, bias: Tensor | None) -> Tensor:
+        return _norm_ops.layer_norm(x, self.normalized_shape, weight, bias, self.eps, cast_fp32=self.cast_fp32)
 
 
 class RMSNorm(LayerNorm):
     """Root-mean-square norm: ``x * rsqrt(mean(x^2) + eps) * w``, statistics in fp32."""
 
     def forward(self, x: Tensor) -> Tensor:
-        return _norm_ops.rms_norm(x, self.normalized_shape, self.weight, self.eps, bias=self.bias)
+        return self.apply_with(x, self.weight, self.bias)
+
+    def apply_with(self, x: Tensor, weight: Tensor | None, bias: Tensor | None) -> Tensor:
+        return _norm_ops.rms_norm(x, self.normalized_shape, weight, self.eps, bias=bias)

@@ -202,3 +202,63 @@ def test_gemma3n_tensor_parallel_training_matches_single_rank() -> None:
     four = Gangs(root=FakeGang(dev, rank=0, size=4), dp=one, rdp=one, sdp=one, tp=FakeGang(dev, rank=0, size=4), pp=one)
     with pytest.raises(ValueError, match="key-value heads"):
         create_gemma3n_model(_gemma_cfg(), four)
+
+
+# ------------------------------------------------------------------ per-head q/k norms (Qwen 3) with replicated activations
+def _qwen_cfg():  # type: ignore[no-untyped-def]
+    from dataclasses import replace
+
+    from fairseq2_b200.models.qwen.config import qwen_tiny
+
+    return replace(qwen_tiny(), tied_embeddings=False)
+
+
+def _qwen_train(model, steps: int):  # type: ignore[no-untyped-def]
+    from fairseq2_b200.nn import BatchLayout
+
+    with torch.no_grad():                                    # norm weights start at one: make their gradients matter
+        for n, p in model.named_parameters():
+            if n.endswith("q_norm.weight") or n.endswith("k_norm.weight"):
+                p.copy_(torch.linspace(0.5, 1.5, p.numel()))
+    opt = torch.optim.SGD(model.parameters(), lr=0.05)
+    g = torch.Generator().manual_seed(3)
+    losses = []
+    for _ in range(steps):
+        ids = torch.randint(0, 512, (2, 17), generator=g)
+        opt.zero_grad()
+        loss = model(ids[:, :-1], BatchLayout.of(ids[:, :-1]), targets=ids[:, 1:], reduction="mean")
+        loss.backward()
+        opt.step()
+        losses.append(float(loss.detach()))
+    norms = {n: p.detach().clone() for n, p in model.named_parameters() if "_norm.weight" in n and "self_attn" in n}
+    return losses, norms
+
+
+def _qwen_worker(rank: int, world: int, steps: int):
+    from fairseq2_b200.gang import ProcessGroupGang, create_parallel_gangs
+    from fairseq2_b200.models.qwen.factory import create_qwen_model
+    from fairseq2_b200.parallel.tp import sequence_parallel
+
+    root = ProcessGroupGang.create_default_process_group(torch.device("cpu"))
+    gangs = create_parallel_gangs(root, tp_size=world)
+    torch.manual_seed(23)
+    with sequence_parallel(False):
+        model = create_qwen_model(_qwen_cfg(), gangs)
+    losses, norms = _qwen_train(model, steps)
+    root.close()
+    return losses, {k: v.numpy() for k, v in norms.items()}
+
+
+def test_per_head_norm_weights_get_the_whole_gradient_under_tensor_parallelism() -> None:
+    """Qwen 3 normalises every query / key head with one shared weight vector. With the heads split over two ranks and
+    replicated activations each rank computes the gradient of its own heads only; the weight must still move as in
+    the single-process model, and identically on both ranks."""
+    from fairseq2_b200.models.qwen.factory import create_qwen_model
+
+    torch.manual_seed(23)
+    want_losses, want_norms = _qwen_train(create_qwen_model(_qwen_cfg()), 3)
+    results = run_distributed(_qwen_worker, 2, 3, timeout=180.0)
+    for losses, norms in results:
+        assert losses == pytest.approx(want_losses, rel=1e-4)
+        for k, v in want_norms.items():
+            assert torch.allclose(torch.from_numpy(norms[k]), v, atol=1e-5), k
