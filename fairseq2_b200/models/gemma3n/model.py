@@ -19,7 +19,7 @@ import torch.nn.functional as F
 from torch import Tensor
 from torch.nn import Module, ModuleList, Parameter
 
-from fairseq2_b200.gang import Gang, ReduceOperation
+from fairseq2_b200.gang import Gang
 from fairseq2_b200.models.gemma3n.config import Gemma3nConfig, is_global_layer, kv_source_layer
 from fairseq2_b200.nn import BatchLayout
 from fairseq2_b200.nn.functional import cross_entropy
@@ -27,7 +27,7 @@ from fairseq2_b200.nn.incremental_state import IncrementalState, IncrementalStat
 from fairseq2_b200.nn.normalization import RMSNorm
 from fairseq2_b200.nn.projection import ColumnShardedLinear, Linear, Projection, RowShardedLinear
 from fairseq2_b200.ops.attention import varlen_attention
-from fairseq2_b200.ops.tensor_parallel import reduce_on_backward
+from fairseq2_b200.ops.tensor_parallel import reduce_both_ways, reduce_on_backward
 from fairseq2_b200.typing import DataType, Device
 
 
@@ -35,24 +35,6 @@ def _rms(x: Tensor, eps: float) -> Tensor:
     """Scale-free RMS normalisation in fp32."""
     xf = x.float()
     return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).type_as(x)
-
-
-class _SumOverGang(torch.autograd.Function):
-    """Sum over the gang in the forward AND the backward pass: for a value that every rank then uses in its own
-    shard of a computation (so the gradients of all ranks' uses add up)."""
-
-    @staticmethod
-    def forward(ctx, x: Tensor, gang: Gang) -> Tensor:  # type: ignore[override]
-        ctx.gang = gang
-        y = x.clone()
-        gang.all_reduce(y, ReduceOperation.SUM)
-        return y
-
-    @staticmethod
-    def backward(ctx, g: Tensor):  # type: ignore[override]
-        g = g.clone()
-        ctx.gang.all_reduce(g, ReduceOperation.SUM)
-        return g, None
 
 
 def _column(tp: Gang | None, input_dim: int, output_dim: int, kw: dict) -> Projection:
@@ -145,7 +127,7 @@ class Gemma3nFFN(Module):
             else:
                 # this rank holds a slice of the inner dimension: first and second moment over all slices
                 gf = gate.float()
-                moments = _SumOverGang.apply(torch.stack([gf.sum(-1), gf.pow(2).sum(-1)], dim=-1), self.tp)
+                moments = reduce_both_ways(torch.stack([gf.sum(-1), gf.pow(2).sum(-1)], dim=-1), self.tp)
                 mean = (moments[..., :1] / self.inner_dim)
                 std = (moments[..., 1:] / self.inner_dim - mean.pow(2)).clamp_min(0.0).sqrt()
                 mean, std = mean.type_as(gate), std.type_as(gate)

@@ -94,6 +94,30 @@ class _ReduceScatter(torch.autograd.Function):
         return _all_gather_dim(g, ctx.gang, ctx.dim), None, None
 
 
+class _ReduceBothWays(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x: Tensor, gang: Gang) -> Tensor:  # type: ignore[override]
+        ctx.gang = gang
+        y = x.clone()
+        gang.all_reduce(y, ReduceOperation.SUM)
+        return y
+
+    @staticmethod
+    def backward(ctx, g: Tensor):  # type: ignore[override]
+        g = g.clone()
+        ctx.gang.all_reduce(g, ReduceOperation.SUM)
+        return g, None
+
+
+def reduce_both_ways(x: Tensor, gang: Gang) -> Tensor:
+    """Sum over the gang in the forward AND the backward pass: for a value that every rank computes a part of and
+    then uses in its own shard of a computation (a statistic over a dimension that is split over the ranks), so that
+    both the parts and the gradients of the uses add up."""
+    if gang.size == 1:
+        return x
+    return _ReduceBothWays.apply(x, gang)
+
+
 def reduce(x: Tensor, gang: Gang) -> Tensor:
     return x if gang.size == 1 else _Reduce.apply(x, gang)
 

@@ -262,3 +262,43 @@ def test_per_head_norm_weights_get_the_whole_gradient_under_tensor_parallelism()
         assert losses == pytest.approx(want_losses, rel=1e-4)
         for k, v in want_norms.items():
             assert torch.allclose(torch.from_numpy(norms[k]), v, atol=1e-5), k
+
+
+# ------------------------------------------------------------------ FFN with activation sparsity
+def _altup_ffn_worker(rank: int, world: int):
+    from fairseq2_b200.gang import ProcessGroupGang, create_parallel_gangs
+    from fairseq2_b200.models.transformer.ffn import AltUpFeedForwardNetwork
+
+    root = ProcessGroupGang.create_default_process_group(torch.device("cpu"))
+    gangs = create_parallel_gangs(root, tp_size=world)
+    torch.manual_seed(4)
+    ffn = AltUpFeedForwardNetwork(32, 96, bias=True, activation_sparsity=0.7, gangs=gangs)
+    x = torch.randn(5, 32, generator=torch.Generator().manual_seed(8), requires_grad=True)
+    y = ffn(x)
+    y.pow(2).sum().backward()
+    out = (y.detach().numpy(), x.grad.numpy(), ffn.output_proj.bias.grad.numpy(), gangs.tp.rank,
+           ffn.gate_proj.weight.grad.numpy())
+    root.close()
+    return out
+
+
+def test_altup_ffn_activation_sparsity_under_tensor_parallelism() -> None:
+    """The cut-off of the Gaussian top-k is a statistic over the whole inner dimension: with the dimension split
+    over two ranks, outputs, input gradients and weight gradients equal the unsplit module's."""
+    from fairseq2_b200.models.transformer.ffn import AltUpFeedForwardNetwork, gaussian_topk
+
+    torch.manual_seed(4)
+    ffn = AltUpFeedForwardNetwork(32, 96, bias=True, activation_sparsity=0.7)
+    x = torch.randn(5, 32, generator=torch.Generator().manual_seed(8), requires_grad=True)
+    y = ffn(x)
+    y.pow(2).sum().backward()
+    for got_y, got_dx, got_db, tp_rank, got_dw in run_distributed(_altup_ffn_worker, 2, timeout=120.0):
+        assert torch.allclose(torch.from_numpy(got_y), y.detach(), atol=1e-5)
+        assert torch.allclose(torch.from_numpy(got_dx), x.grad, atol=1e-4)
+        assert torch.allclose(torch.from_numpy(got_db), ffn.output_proj.bias.grad, atol=1e-4)
+        assert torch.allclose(torch.from_numpy(got_dw), ffn.gate_proj.weight.grad[tp_rank * 48:(tp_rank + 1) * 48], atol=1e-4)
+    g = torch.randn(1000, 512)
+    kept = (gaussian_topk(g, 0.9) > 0).float().mean()
+    assert 0.08 < float(kept) < 0.12                       # about a tenth of a normal sample survives
+    with pytest.raises(ValueError):
+        AltUpFeedForwardNetwork(8, 8, False, activation_sparsity=1.0)
