@@ -21,7 +21,7 @@ from torch.nn import Module, Parameter, SiLU
 from fairseq2_b200.gang import Gang
 from fairseq2_b200.models.transformer.ffn import FeedForwardNetwork, GLUFeedForwardNetwork
 from fairseq2_b200.ops.grouped_gemm import grouped_mm, grouped_mm_device, grouped_mm_device_supported
-from fairseq2_b200.ops.tensor_parallel import reduce
+from fairseq2_b200.ops.tensor_parallel import reduce, reduce_on_backward
 from fairseq2_b200.typing import DataType, Device
 
 
@@ -91,7 +91,24 @@ class TPShardedExpertNetwork(ExpertNetwork):
         self.inner_proj = Parameter(torch.empty((num_experts, model_dim, f), **kw))
         self.output_proj = Parameter(torch.empty((num_experts, f, model_dim), **kw))
         self.activation = activation if activation is not None else SiLU()
-        GroupedExpertNetwork.reset_parameters(self)  # type: ignore[arg-type]
+        self.reset_parameters()
+
+    def reset_parameters(self) -> None:
+        """This rank's slice of the unsplit initialisation, so that a tensor-parallel model equals its one-rank
+        counterpart built from the same seed (as the sharded projections do)."""
+        if self.gate_proj.device.type == "meta":
+            return
+        full = GroupedExpertNetwork(self.num_experts, self.model_dim, self.inner_dim, device=self.gate_proj.device,
+                                    dtype=self.gate_proj.dtype)
+        f, r = self.inner_dim // self.gang.size, self.gang.rank
+        with torch.no_grad():
+            self.gate_proj.copy_(full.gate_proj[:, :, r * f:(r + 1) * f])
+            self.inner_proj.copy_(full.inner_proj[:, :, r * f:(r + 1) * f])
+            self.output_proj.copy_(full.output_proj[:, r * f:(r + 1) * f, :])
+
+    def get_shard_dims(self) -> list[tuple[Parameter, int]]:
+        """(parameter, dimension split over the gang): what checkpoint resharding and the data-parallel engine go by."""
+        return [(self.gate_proj, 2), (self.inner_proj, 2), (self.output_proj, 1)]
 
     @staticmethod
     def from_grouped_expert_network(net: GroupedExpertNetwork, gang: Gang) -> "TPShardedExpertNetwork":
@@ -153,8 +170,16 @@ class MoE(FeedForwardNetwork):
         self.tp_gang = tp_gang if tp_gang is not None and tp_gang.size > 1 else None
         self.shared_expert: GLUFeedForwardNetwork | None = None
         if use_shared_expert:
+            shared_gangs = None
+            if self.tp_gang is not None:
+                # the shared expert is split over the inner dimension like any FFN (its output projection sums over
+                # the gang itself)
+                from fairseq2_b200.gang import FakeGang, Gangs
+
+                one = FakeGang(self.tp_gang.device)
+                shared_gangs = Gangs(root=self.tp_gang, dp=one, rdp=one, sdp=one, tp=self.tp_gang, pp=one)
             self.shared_expert = GLUFeedForwardNetwork(model_dim, inner_dim, bias=False, inner_dim_scale=1.0,
-                                                       device=device, dtype=dtype)
+                                                       gangs=shared_gangs, device=device, dtype=dtype)
         self.router = Parameter(torch.empty((model_dim, num_experts), device=device, dtype=dtype))
         self.softmax_gate, self.aux_loss, self.router_init_std = softmax_gate, aux_loss, router_init_std
         self.last_aux_loss: Tensor | None = None
@@ -215,30 +240,40 @@ class MoE(FeedForwardNetwork):
                 num_tiles = None
             base = self.shared_expert(x) if self.shared_expert is not None else None
             return self.ep.combine(rows_out, dest, x.shape[0], base=base, num_tiles=num_tiles).view(seqs.shape)
+        # Tensor-parallel experts: every rank holds a slice of each expert's inner dimension, so the routed output is
+        # a partial sum (summed over the gang below) and so is the gradient that the experts send back into `x`
+        # (summed over the gang in the backward pass of `xe`). The shared expert does both inside its own sharded
+        # projections and is added after the sum, not before: its output is already whole on every rank.
+        xe = reduce_on_backward(x, self.tp_gang) if self.tp_gang is not None else x
         if moe_ops.moe_kernels_available(x, logits):
             # fused top-k gate + histogram, gather/scale into expert order, experts, gather back per token
             ids, gates, counts = moe_ops.moe_route(logits, self.top_k, self.softmax_gate)
             self._note_aux_loss(logits, counts)
+            if self.tp_gang is not None:
+                gates = reduce_on_backward(gates, self.tp_gang)      # the gates scale the experts' inputs: same story
             if isinstance(self.experts, GroupedExpertNetwork) and self.experts.supports_padded_layout(x):
                 # padded layout + device-resident tile tables: the CPU never waits for the routing result
-                routed_in, src_row, inv, layout = moe_ops.moe_dispatch_padded(x, gates, ids, counts)
+                routed_in, src_row, inv, layout = moe_ops.moe_dispatch_padded(xe, gates, ids, counts)
                 routed_out = self.experts.forward_padded(routed_in, layout)
             else:
-                routed_in, src_row, inv = moe_ops.moe_dispatch(x, gates, ids, counts)
+                routed_in, src_row, inv = moe_ops.moe_dispatch(xe, gates, ids, counts)
                 routed_out = self.experts(routed_in, counts.tolist())
             base = self.shared_expert(x) if self.shared_expert is not None else None
-            out = moe_ops.moe_combine(routed_out, inv, src_row, base)
-            if self.tp_gang is not None:
-                out = reduce(out, self.tp_gang)
-            return out.view(seqs.shape)
+            if self.tp_gang is None:
+                return moe_ops.moe_combine(routed_out, inv, src_row, base).view(seqs.shape)
+            out = reduce(moe_ops.moe_combine(routed_out, inv, src_row, None), self.tp_gang)
+            return (out if base is None else out + base).view(seqs.shape)
         token_idx, scores, _, sizes = route_tokens(logits, self.top_k, self.softmax_gate)
         self._note_aux_loss(logits, torch.tensor(sizes, device=logits.device))
-        routed_in = x.index_select(0, token_idx) * scores.to(x.dtype).unsqueeze(1)
+        if self.tp_gang is not None:
+            scores = reduce_on_backward(scores, self.tp_gang)        # the gates scale the experts' inputs: same story
+        routed_in = xe.index_select(0, token_idx) * scores.to(x.dtype).unsqueeze(1)
         routed_out = self.experts(routed_in, sizes)
-        out = self.shared_expert(x) if self.shared_expert is not None else torch.zeros_like(x)
-        out = out.index_add(0, token_idx, routed_out)
+        out = torch.zeros_like(x).index_add(0, token_idx, routed_out)
         if self.tp_gang is not None:
             out = reduce(out, self.tp_gang)
+        if self.shared_expert is not None:
+            out = out + self.shared_expert(x)
         return out.view(seqs.shape)
 
     def extra_repr(self) -> str:

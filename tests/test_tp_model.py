@@ -302,3 +302,64 @@ def test_altup_ffn_activation_sparsity_under_tensor_parallelism() -> None:
     assert 0.08 < float(kept) < 0.12                       # about a tenth of a normal sample survives
     with pytest.raises(ValueError):
         AltUpFeedForwardNetwork(8, 8, False, activation_sparsity=1.0)
+
+
+# ------------------------------------------------------------------ LLaMA 4 (MoE layers with tensor-parallel experts)
+def _llama4_train(model, steps: int):  # type: ignore[no-untyped-def]
+    from fairseq2_b200.nn import BatchLayout
+
+    opt = torch.optim.SGD(model.parameters(), lr=0.05)
+    g = torch.Generator().manual_seed(6)
+    losses = []
+    for _ in range(steps):
+        ids = torch.randint(1, 500, (2, 41), generator=g)
+        layout = BatchLayout((2, 40), [40, 33])
+        opt.zero_grad()
+        loss = model(ids[:, :-1], layout, targets=ids[:, 1:], reduction="mean")
+        loss.backward()
+        opt.step()
+        losses.append(float(loss.detach()))
+    return losses
+
+
+def _llama4_worker(rank: int, world: int, steps: int):
+    from fairseq2_b200.gang import ProcessGroupGang, create_parallel_gangs
+    from fairseq2_b200.models.llama4.config import llama4_tiny
+    from fairseq2_b200.models.llama4.factory import create_llama4_model
+    from fairseq2_b200.parallel.tp import sequence_parallel
+
+    root = ProcessGroupGang.create_default_process_group(torch.device("cpu"))
+    gangs = create_parallel_gangs(root, tp_size=world)
+    from fairseq2_b200.nn.sharded import get_shard_dims
+
+    with sequence_parallel(False):
+        model = create_llama4_model(llama4_tiny(), gangs)
+    # the same weights as the single-process model: its state, cut along every parameter's tensor-parallel dimension
+    torch.manual_seed(29)
+    full = create_llama4_model(llama4_tiny()).state_dict()
+    dims = get_shard_dims(model)
+    own = model.state_dict()
+    assert set(own) == set(full)
+    with torch.no_grad():
+        for k, v in own.items():
+            src = full[k]
+            if k in dims:
+                src = src.chunk(world, dim=dims[k])[gangs.tp.rank]
+            assert src.shape == v.shape, (k, tuple(src.shape), tuple(v.shape))
+            v.copy_(src)
+    losses = _llama4_train(model, steps)
+    root.close()
+    return losses, sorted(dims)
+
+
+def test_llama4_tensor_parallel_training_matches_single_rank() -> None:
+    """Dense and MoE layers (router, routed experts and the shared expert split over the inner dimension), chunked
+    and NoPE attention, q/k norms without weights: three SGD steps on two ranks give the single-process losses."""
+    from fairseq2_b200.models.llama4.config import llama4_tiny
+    from fairseq2_b200.models.llama4.factory import create_llama4_model
+
+    torch.manual_seed(29)
+    want = _llama4_train(create_llama4_model(llama4_tiny()), 3)
+    for losses, sharded in run_distributed(_llama4_worker, 2, 3, timeout=180.0):
+        assert losses == pytest.approx(want, rel=2e-4)
+        assert any("experts" in k for k in sharded) and any("shared_expert" in k for k in sharded)
