@@ -23,6 +23,7 @@ import torch
 from torch import Tensor
 from torch.nn import Module
 
+from fairseq2_b200.error import NotSupportedError
 from fairseq2_b200.gang import Gang, Gangs, ReduceOperation
 from fairseq2_b200.nn.utils.module import broadcast_module
 
@@ -78,6 +79,11 @@ class DDP(Module):
         import os
 
         self._allreduce = os.environ.get("FAIRSEQ2_B200_DDP_ALLREDUCE", allreduce)
+        if any(getattr(m, "sequence_parallel", False) for m in module.modules()):
+            # token-sharded activations leave partial gradients on every parameter that is replicated over the
+            # tensor-parallel gang; only the flat-unit engine adds them up
+            raise NotSupportedError("A model built with sequence-parallel activations needs the flat-unit engine "
+                                    "(`fairseq2_b200.parallel.fsdp.FSDP`), not `DDP`.")
         self.module = module
         self.gang: Gang = gangs.rdp if gangs.rdp.size > 1 else gangs.dp
         self.average = average

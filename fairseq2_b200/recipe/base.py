@@ -264,9 +264,19 @@ class RecipeContext:
         from fairseq2_b200.parallel.tp import sequence_parallel
 
         gsec: GangSection = self._section("gang", GangSection)
-        seq_par = sequence_parallel(train and gangs.tp.size > 1 and gsec.sequence_parallel
-                                    and family.supports_sequence_parallel)
         use_fsdp = train and ts.data_parallelism == "fsdp" and gangs.dp.size >= 1
+        # With token-sharded activations every parameter that is replicated over the tensor-parallel gang (norm
+        # weights, biases of row projections) only sees its rank's tokens: its gradient is a partial sum that the
+        # flat-unit engine adds up over the gang. The bucketed DDP wrapper and a bare module do not, so those
+        # configurations keep replicated activations.
+        mp = ts.mixed_precision
+        flat_units = use_fsdp or (train and self.device.type == "cuda" and mp.mode in ("static", "auto")
+                                  and mp.dtype == torch.bfloat16 and family.supports_fsdp and ts.ddp_flat_units)
+        want_sp = train and gangs.tp.size > 1 and gsec.sequence_parallel and family.supports_sequence_parallel
+        if want_sp and not flat_units:
+            log.info("Sequence-parallel activations need the flat-unit data-parallel engine (`trainer.data_parallelism: "
+                     "fsdp`, or bf16 `ddp` on GPUs); this run keeps replicated activations.")
+        seq_par = sequence_parallel(want_sp and flat_units)
         static_mp = ts.mixed_precision.mode == "static" and use_fsdp
         build_dtype = ms.dtype
         load_weights = (card is not None and card.has_field("checkpoint")) or ms.path is not None

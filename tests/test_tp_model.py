@@ -363,3 +363,25 @@ def test_llama4_tensor_parallel_training_matches_single_rank() -> None:
     for losses, sharded in run_distributed(_llama4_worker, 2, 3, timeout=180.0):
         assert losses == pytest.approx(want, rel=2e-4)
         assert any("experts" in k for k in sharded) and any("shared_expert" in k for k in sharded)
+
+
+def test_sequence_parallel_model_is_refused_by_the_bucketed_ddp_wrapper() -> None:
+    """Token-sharded activations leave partial gradients on replicated parameters; only the flat-unit engine sums
+    them over the tensor-parallel gang, so the bucketed wrapper must not accept such a model silently."""
+    from fairseq2_b200.error import NotSupportedError
+    from fairseq2_b200.gang import FakeGang, Gangs
+    from fairseq2_b200.models.llama import create_llama_model
+    from fairseq2_b200.parallel.ddp import DDP
+    from fairseq2_b200.parallel.tp import sequence_parallel
+
+    dev = torch.device("cpu")
+    one = FakeGang(dev)
+    gangs = Gangs(root=FakeGang(dev, rank=0, size=4), dp=FakeGang(dev, rank=0, size=2), rdp=FakeGang(dev, rank=0, size=2),
+                  sdp=one, tp=FakeGang(dev, rank=0, size=2), pp=one)
+    with sequence_parallel(True):
+        model = create_llama_model(_cfg(), gangs)
+    with pytest.raises(NotSupportedError, match="sequence-parallel"):
+        DDP(model, gangs, broadcast_parameters=False)
+    with sequence_parallel(False):
+        plain = create_llama_model(_cfg(), gangs)
+    DDP(plain, gangs, broadcast_parameters=False)
