@@ -42,11 +42,46 @@ def normalize_grads(module: Module, gang: Gang, num_targets: int | Tensor, *, fo
     return factor
 
 
+def _tensor_parallel_split(module: Module) -> tuple[Gang | None, set[int]]:
+    """The tensor-parallel gang of ``module`` (``None`` if it has none) and the ids of the parameters that are
+    split over it."""
+    from fairseq2_b200.nn.sharded import Sharded
+
+    gang: Gang | None = None
+    split: set[int] = set()
+    for m in module.modules():
+        if isinstance(m, Sharded):
+            g = getattr(m, "gang", None)
+            if g is not None and g.size > 1:
+                gang = g
+                split.update(id(p) for p, _ in m.get_shard_dims())
+    return gang, split
+
+
 def clip_grad_norm(module: Module, max_norm: float | None, norm_type: float = 2.0) -> Tensor:
-    """Global gradient norm; clips in place when ``max_norm`` is given."""
+    """Global gradient norm; clips in place when ``max_norm`` is given. In a tensor-parallel model the norm covers
+    the whole model: the squared norms of the parameters that are split over the gang are summed over it, those of
+    the replicated parameters count once, so every rank scales by the same factor."""
     gs = _grads(module)
     if not gs:
         return torch.zeros(())
+    tp, split = _tensor_parallel_split(module)
+    if tp is not None:
+        if norm_type != 2.0:
+            raise ValueError("Only the 2-norm is supported for tensor-parallel models.")
+        dev = gs[0].device
+        parts = torch.zeros(2, device=dev, dtype=torch.float32)        # [split over the gang, replicated]
+        for p in module.parameters():
+            if p.grad is not None:
+                parts[0 if id(p) in split else 1] += p.grad.detach().float().pow(2).sum()
+        shared = parts[:1].clone()
+        tp.all_reduce(shared, ReduceOperation.SUM)
+        total = (shared[0] + parts[1]).sqrt()
+        if max_norm is not None:
+            coef = (max_norm / (total + 1e-6)).clamp(max=1.0)
+            for g in gs:
+                g.mul_(coef.to(g.dtype))
+        return total
     if norm_type == 2.0 and gs[0].is_cuda and all(g.is_contiguous() and g.data_ptr() % 16 == 0 for g in gs):
         total = multi_tensor_l2_norm_sq(gs).sqrt()
         if max_norm is not None:

@@ -385,3 +385,42 @@ def test_sequence_parallel_model_is_refused_by_the_bucketed_ddp_wrapper() -> Non
     with sequence_parallel(False):
         plain = create_llama_model(_cfg(), gangs)
     DDP(plain, gangs, broadcast_parameters=False)
+
+
+def _clip_worker(rank: int, world: int):
+    from fairseq2_b200.gang import ProcessGroupGang, create_parallel_gangs
+    from fairseq2_b200.models.llama import create_llama_model
+    from fairseq2_b200.nn import BatchLayout
+    from fairseq2_b200.nn.utils.grad import clip_grad_norm
+    from fairseq2_b200.parallel.tp import sequence_parallel
+
+    root = ProcessGroupGang.create_default_process_group(torch.device("cpu"))
+    gangs = create_parallel_gangs(root, tp_size=world)
+    torch.manual_seed(13)
+    with sequence_parallel(False):
+        model = create_llama_model(_cfg(), gangs)
+    b = _data(1, 1)[0][0]
+    model(b[:-1], BatchLayout((32,), [18, 14], packed=True), targets=b[1:]).backward()
+    total = float(clip_grad_norm(model, 1.0))
+    after = float(clip_grad_norm(model, None))
+    norm_w = model.decoder.layers[0].self_attn_layer_norm.weight.grad.clone().numpy()
+    root.close()
+    return total, after, norm_w
+
+
+def test_gradient_clipping_of_a_tensor_parallel_model_uses_the_whole_model_norm() -> None:
+    """Without a data-parallel wrapper: both ranks must arrive at the single-process norm (split parameters summed
+    over the gang, replicated ones counted once) and scale by the same factor."""
+    from fairseq2_b200.models.llama import create_llama_model
+    from fairseq2_b200.nn import BatchLayout
+
+    torch.manual_seed(13)
+    model = create_llama_model(_cfg())
+    b = _data(1, 1)[0][0]
+    model(b[:-1], BatchLayout((32,), [18, 14], packed=True), targets=b[1:]).backward()
+    want = float(torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0))
+    want_w = model.decoder.layers[0].self_attn_layer_norm.weight.grad
+    assert want > 1.0
+    for total, after, norm_w in run_distributed(_clip_worker, 2, timeout=120.0):
+        assert total == pytest.approx(want, rel=1e-4) and after == pytest.approx(1.0, rel=1e-3)
+        assert torch.allclose(torch.from_numpy(norm_w), want_w, rtol=1e-3, atol=1e-7)
