@@ -149,8 +149,14 @@ class ModelFamily(Generic[ModelT, ConfigT]):
 
         state = dict(model.state_dict())
         seen: set[str] = set()
+        # `model` holds whole (tensor-parallel-local) parameters at this point: the data-parallel engine shards them
+        # later, unit by unit. The loader must therefore cut along the tensor-parallel dimension only.
+        from fairseq2_b200.gang import FakeGang
+
+        one = FakeGang(gangs.root.device)
+        load_gangs = Gangs(root=gangs.root, dp=gangs.dp, rdp=gangs.rdp, sdp=one, tp=gangs.tp, pp=gangs.pp)
         with torch.no_grad():
-            for key, tensor in loader.lazy_load(path, shard_dims, gangs=gangs, mmap=mmap, restrict=restrict,
+            for key, tensor in loader.lazy_load(path, shard_dims, gangs=load_gangs, mmap=mmap, restrict=restrict,
                                                 state_dict_converter=conv):
                 tgt = state.get(key)
                 if tgt is None:

@@ -115,3 +115,39 @@ def test_save_at_dp2_load_at_dp1_dp3_and_tp2(tmp_path: Path) -> None:
         for k, v in full.items():
             want = v.chunk(2, dim=dims[k])[r] if k in dims else v
             assert torch.equal(got[k], want), k
+
+
+def _load_then_shard_worker(rank: int, world: int, full_file: str, sharded_dir: str):
+    """What a fine-tuning job does: build the model, load pretrained weights into it, then hand it to the
+    data-parallel engine. The model holds whole parameters while it is loaded, whatever the FSDP size."""
+    from fairseq2_b200.gang import ProcessGroupGang, create_fsdp_gangs, create_parallel_gangs
+    from fairseq2_b200.models.family import get_model_family
+    from fairseq2_b200.parallel.fsdp import FSDP
+
+    root = ProcessGroupGang.create_default_process_group(torch.device("cpu"))
+    gangs = create_fsdp_gangs(create_parallel_gangs(root))
+    fam = get_model_family("llama")
+    cfg = fam.get_arch_config("tiny")
+    cfg.num_layers = 1
+    cfg.vocab_size = 8191
+    out = []
+    for path in (full_file, sharded_dir):
+        model = fam.create_new_model(cfg, gangs)
+        fam.load_into(model, Path(path), cfg, gangs)
+        fsdp = FSDP(model, gangs, param_dtype=torch.float32)
+        out.append({k: v.numpy() for k, v in fsdp.full_state_dict().items()})
+    root.close()
+    return out
+
+
+def test_pretrained_weights_load_into_a_model_that_fsdp_shards_afterwards(tmp_path: Path) -> None:
+    results = run_distributed(_save_worker, 2, str(tmp_path / "ckpt"))
+    full = {k: torch.from_numpy(v) for k, v in results[0][1].items()}
+    full_file = tmp_path / "consolidated.pt"
+    torch.save({"model": full}, full_file)
+    sharded_dir = tmp_path / "ckpt" / "step_1" / "model"
+    for per_source in run_distributed(_load_then_shard_worker, 2, str(full_file), str(sharded_dir)):
+        for got in per_source:                              # a single file, then a directory written at dp = 2
+            assert set(got) == set(full)
+            for k, v in full.items():
+                assert torch.equal(torch.from_numpy(got[k]), v), k
