@@ -276,3 +276,37 @@ def test_lm_sft_recipe_with_tensor_parallelism(tmp_path: Path, seq_par: bool) ->
     assert run_distributed(_tp_sft_worker, 2, str(tmp_path), seq_par, timeout=300.0) == [0, 0]
     lines = [json.loads(l) for l in open(tmp_path / "out" / "metrics" / "train.jsonl")]
     assert len(lines) == 3 and lines[-1]["NLL Loss"] < lines[0]["NLL Loss"]
+
+
+def _pretrained_sft_worker(rank: int, world: int, root: str, ckpt: str):
+    from recipes.lm.sft.recipe import LMSFTRecipe
+
+    tmp = Path(root)
+    args = _sft_args(tmp, tmp / "data", ["regime.num_steps=2", "dataset.packed=true", "trainer.data_parallelism=fsdp",
+                                         f"model.path={ckpt}", "optimizer.config.lr=1e-6",
+                                         "regime.validate_every_n_steps=null", "regime.checkpoint_every_n_steps=null"])
+    return main(LMSFTRecipe(), args)
+
+
+def test_lm_sft_recipe_fine_tunes_pretrained_weights_on_two_fsdp_ranks(tmp_path: Path) -> None:
+    """`model.path` points at a consolidated checkpoint; the job runs on two ranks with FSDP. The model is loaded
+    whole and sharded afterwards, and the first loss is the pretrained model's, not a fresh one's."""
+    import torch
+
+    from fairseq2_b200.models.family import get_model_family
+    from tests.dist_utils import run_distributed
+
+    _write_sft_data(tmp_path)
+    fam = get_model_family("llama")
+    cfg = fam.get_arch_config("tiny")
+    torch.manual_seed(1)
+    model = fam.create_new_model(cfg, None)
+    with torch.no_grad():
+        # "pretrained" in a way the loss can tell: the output projection is zero, so every token is equally likely
+        model.final_proj.weight.zero_()
+    ckpt = tmp_path / "pretrained.pt"
+    torch.save({"model": model.state_dict()}, ckpt)
+    assert run_distributed(_pretrained_sft_worker, 2, str(tmp_path), str(ckpt), timeout=300.0) == [0, 0]
+    lines = [json.loads(l) for l in open(tmp_path / "out" / "metrics" / "train.jsonl")]
+    uniform = math.log2(cfg.vocab_size)                   # the metric is in bits
+    assert abs(lines[0]["NLL Loss"] - uniform) < 1e-2 * uniform, (lines[0]["NLL Loss"], uniform)
