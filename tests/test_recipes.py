@@ -310,3 +310,30 @@ def test_lm_sft_recipe_fine_tunes_pretrained_weights_on_two_fsdp_ranks(tmp_path:
     lines = [json.loads(l) for l in open(tmp_path / "out" / "metrics" / "train.jsonl")]
     uniform = math.log2(cfg.vocab_size)                   # the metric is in bits
     assert abs(lines[0]["NLL Loss"] - uniform) < 1e-2 * uniform, (lines[0]["NLL Loss"], uniform)
+
+
+def _continue_worker(rank: int, world: int, root: str, prev: str):
+    from recipes.lm.sft.recipe import LMSFTRecipe
+
+    tmp = Path(root)
+    args = _sft_args(tmp, Path(prev) / "data", [
+        "regime.num_steps=2", "dataset.packed=true", "trainer.data_parallelism=fsdp", "model.name=last_checkpoint",
+        "model.family=null", "model.arch=null", f"common.assets.prev_checkpoint_dir={prev}/out/checkpoints",
+        "optimizer.config.lr=1e-6", "regime.validate_every_n_steps=null", "regime.checkpoint_every_n_steps=null"])
+    return main(LMSFTRecipe(), args)
+
+
+def test_checkpoint_of_one_run_is_the_model_asset_of_the_next_at_another_world_size(tmp_path: Path) -> None:
+    """A run on one process writes checkpoints; a second job on two FSDP ranks names `last_checkpoint` of that
+    directory as its model and starts from the trained weights (its first loss is near the first run's last)."""
+    from recipes.lm.sft.recipe import LMSFTRecipe
+    from tests.dist_utils import run_distributed
+
+    first_dir, second_dir = tmp_path / "first", tmp_path / "second"
+    first_dir.mkdir(), second_dir.mkdir()
+    data = _write_sft_data(first_dir)
+    assert main(LMSFTRecipe(), _sft_args(first_dir, data, ["regime.num_steps=4", "dataset.packed=true"])) == 0
+    first = [json.loads(l) for l in open(first_dir / "out" / "metrics" / "train.jsonl")]
+    assert run_distributed(_continue_worker, 2, str(second_dir), str(first_dir), timeout=300.0) == [0, 0]
+    second = [json.loads(l) for l in open(second_dir / "out" / "metrics" / "train.jsonl")]
+    assert first[0]["NLL Loss"] > 10 and second[0]["NLL Loss"] < first[-1]["NLL Loss"] + 1.0
