@@ -515,6 +515,9 @@ class Trainer(Task):
             "_rng_bag": self._rng_bag.state_dict(), "_metric_bag": self._metric_bag.state_dict(),
             "_base_wall_time": self._base_wall_time + self._wall_watch.get_elapsed_time(),
             "_best_score": self._best_score,
+            # whether the current data epoch has produced a batch: a run that resumes exactly at the end of an epoch
+            # reads nothing before the reader reports the end, and must not mistake that for an empty dataset
+            "_has_read_any": self._has_read_any,
         }
         if self._lr_scheduler is not None:
             sd["_lr_scheduler"] = self._lr_scheduler.state_dict()
@@ -529,6 +532,7 @@ class Trainer(Task):
         self._metric_bag.load_state_dict(sd.get("_metric_bag", {}))
         self._base_wall_time = float(sd.get("_base_wall_time", 0.0))
         self._best_score = sd.get("_best_score")
+        self._has_read_any = bool(sd.get("_has_read_any", self._step_nr > 0))
         if self._lr_scheduler is not None and "_lr_scheduler" in sd:
             self._lr_scheduler.load_state_dict(sd["_lr_scheduler"])
         if self._loss_scaler is not None and "_fp16_loss_scaler" in sd:

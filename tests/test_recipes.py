@@ -337,3 +337,32 @@ def test_checkpoint_of_one_run_is_the_model_asset_of_the_next_at_another_world_s
     assert run_distributed(_continue_worker, 2, str(second_dir), str(first_dir), timeout=300.0) == [0, 0]
     second = [json.loads(l) for l in open(second_dir / "out" / "metrics" / "train.jsonl")]
     assert first[0]["NLL Loss"] > 10 and second[0]["NLL Loss"] < first[-1]["NLL Loss"] + 1.0
+
+
+def _resume_worker(rank: int, world: int, root: str, steps: int):
+    from recipes.lm.sft.recipe import LMSFTRecipe
+
+    tmp = Path(root)
+    args = _sft_args(tmp, tmp / "data", [
+        f"regime.num_steps={steps}", "dataset.packed=true", "trainer.data_parallelism=fsdp",
+        "lr_scheduler.config.cycle_len=8",                 # the schedule must not depend on where a run stops
+        "regime.validate_every_n_steps=null", "regime.checkpoint_every_n_steps=2"])
+    return main(LMSFTRecipe(), args)
+
+
+def test_two_rank_fsdp_run_resumes_where_it_stopped(tmp_path: Path) -> None:
+    """Four steps on two FSDP ranks, then the same command with six: the second job restores model, optimizer,
+    trainer and data position from the checkpoint of step 4 -- which here falls exactly on the end of the first data
+    epoch -- and its steps 5 and 6 equal those of a job that ran six steps in one go."""
+    from tests.dist_utils import run_distributed
+
+    once, twice = tmp_path / "once", tmp_path / "twice"
+    once.mkdir(), twice.mkdir()
+    _write_sft_data(once), _write_sft_data(twice)
+    assert run_distributed(_resume_worker, 2, str(once), 6, timeout=300.0) == [0, 0]
+    assert run_distributed(_resume_worker, 2, str(twice), 4, timeout=300.0) == [0, 0]
+    assert run_distributed(_resume_worker, 2, str(twice), 6, timeout=300.0) == [0, 0]
+    want = [json.loads(l)["NLL Loss"] for l in open(once / "out" / "metrics" / "train.jsonl")]
+    got = [json.loads(l)["NLL Loss"] for l in open(twice / "out" / "metrics" / "train.jsonl")]
+    assert len(want) == 6 and len(got) == 6
+    assert got == pytest.approx(want, rel=1e-4)
