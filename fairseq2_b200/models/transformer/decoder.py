@@ -4,6 +4,7 @@ from __future__ import annotations
 from abc import ABC, abstractmethod
 from typing import Iterable
 
+import torch
 from torch import Tensor
 from torch.nn import Module, ModuleList
 
@@ -32,11 +33,15 @@ class StandardTransformerDecoder(TransformerDecoder):
         self.layers = ModuleList(layers)
         self.layer_norm = layer_norm
         self.layer_drop_p = layer_drop_p
+        #: source of the LayerDrop decisions (``None``: the global CPU generator, which jobs seed differently on
+        #: every rank). A data-parallel engine whose collectives need every rank to run the same layers installs a
+        #: generator that is seeded identically everywhere.
+        self.layer_drop_generator: torch.Generator | None = None
 
     def forward(self, seqs, seqs_layout, encoder_output, encoder_output_layout, *, state_bag=None):  # type: ignore[override]
         self_cache, cross_cache = AttentionBiasCache(), AttentionBiasCache()
         n = len(self.layers)
-        for i, layer in drop_iter(self.layers, self.layer_drop_p, self.training):
+        for i, layer in drop_iter(self.layers, self.layer_drop_p, self.training, self.layer_drop_generator):
             seqs = layer(seqs, seqs_layout, encoder_output, encoder_output_layout, self_cache, cross_cache,
                          state_bag=state_bag)
             stop = False

@@ -63,11 +63,15 @@ class StandardTransformerEncoder(TransformerEncoder):
         self.layers = ModuleList(layers)
         self.layer_norm = layer_norm
         self.layer_drop_p = layer_drop_p
+        #: source of the LayerDrop decisions (``None``: the global CPU generator, which jobs seed differently on
+        #: every rank). A data-parallel engine whose collectives need every rank to run the same layers installs a
+        #: generator that is seeded identically everywhere.
+        self.layer_drop_generator: torch.Generator | None = None
 
     def forward(self, seqs: Tensor, seqs_layout: BatchLayout) -> Tensor:
         cache = AttentionBiasCache()
         n = len(self.layers)
-        for i, layer in drop_iter(self.layers, self.layer_drop_p, self.training):
+        for i, layer in drop_iter(self.layers, self.layer_drop_p, self.training, self.layer_drop_generator):
             seqs = layer(seqs, seqs_layout, cache)
             stop = False
             for hook in self._layer_hooks.values():

@@ -740,6 +740,18 @@ class FSDP(Module):
                         raise
                     log.warning("Symmetric memory is not usable ({}); replicas are averaged with NCCL.", ex)
                     self.replica_arena = None
+        if W > 1 and self.arena is None:
+            # Over process-group collectives the all-gather of a sharded unit is a collective too: a layer that one
+            # rank drops and another runs would leave the second waiting. LayerDrop therefore draws from generators
+            # that are seeded identically on every rank here (over the peer-memory arena the gathers are one-sided and
+            # the reductions keep one canonical order, so ranks may differ).
+            k = 0
+            for m in module.modules():
+                if getattr(m, "layer_drop_p", 0.0) and hasattr(m, "layer_drop_generator"):
+                    g = torch.Generator()
+                    g.manual_seed(0x1A7E5D0 + k)
+                    m.layer_drop_generator = g
+                    k += 1
         self._install_hooks()
         n = sum(u.shard_size for u in self.all_units)
         log.info("FSDP: {} unit(s), {:,} local shard elements, world size {}.", len(self.all_units), n, W)

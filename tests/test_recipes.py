@@ -366,3 +366,29 @@ def test_two_rank_fsdp_run_resumes_where_it_stopped(tmp_path: Path) -> None:
     got = [json.loads(l)["NLL Loss"] for l in open(twice / "out" / "metrics" / "train.jsonl")]
     assert len(want) == 6 and len(got) == 6
     assert got == pytest.approx(want, rel=1e-4)
+
+
+def _ssl_layerdrop_worker(rank: int, world: int, root: str, man: str, data_parallelism: str):
+    from recipes.wav2vec2.ssl.recipe import Wav2Vec2SslRecipe
+
+    args = [str(Path(root) / "ssl"), "--no-sweep-dir", "--no-exit-on-error", "--config", "model.arch=tiny",
+            "model.config_overrides={encoder_config: {layer_drop_p: 0.5}}", f"dataset.config_overrides={{path: {man}}}",
+            "dataset.min_audio_len=1000", "dataset.max_audio_len=8000", "dataset.max_num_elements=16000", "dataset.npc=1",
+            "trainer.mixed_precision.mode=off", f"trainer.data_parallelism={data_parallelism}", "regime.num_steps=4",
+            "regime.validate_every_n_steps=null", "regime.checkpoint_every_n_steps=null",
+            "regime.publish_metrics_every_n_steps=1", "common.metric_recorders.jsonl=true",
+            "lr_scheduler.config.num_warmup_steps=1", "optimizer.config.lr=1e-4"]
+    return main(Wav2Vec2SslRecipe(), args)
+
+
+@pytest.mark.parametrize("data_parallelism", ["ddp", "fsdp"])
+def test_wav2vec2_ssl_with_layer_drop_on_two_ranks(tmp_path: Path, data_parallelism: str) -> None:
+    """LayerDrop really skips layers. Jobs seed every rank differently, so two ranks would drop different layers:
+    fine for replicated parameters (missing gradients count as zero), but with sharded units over process-group
+    collectives every rank has to run the same layers -- the engine then makes the decisions identical."""
+    from tests.dist_utils import run_distributed
+
+    man = _write_speech_data(tmp_path)
+    assert run_distributed(_ssl_layerdrop_worker, 2, str(tmp_path), str(man), data_parallelism, timeout=240.0) == [0, 0]
+    rows = [json.loads(l) for l in open(tmp_path / "ssl" / "metrics" / "train.jsonl")]
+    assert len(rows) == 4
