@@ -307,11 +307,34 @@ class StandardMultiheadAttention(MultiheadAttention):
         self.q_proj = q_proj if q_proj is not None else col(model_dim, num_heads * hd)
         self.k_proj = k_proj if k_proj is not None else col(kv_dim, nkv * hd)
         self.v_proj = v_proj if v_proj is not None else col(kv_dim, nkv * hd)
-        self.q_norm, self.k_norm = q_norm, k_norm
         # OLMo-2 style: q/k norms span the whole projection (all heads) rather than one head
         self.qk_norm_over_heads = qk_norm_over_heads
+        self._norm_full_dims: tuple[int, int] | None = None
         if qk_norm_over_heads and tp is not None:
-            raise NotSupportedError("`qk_norm_over_heads` is not supported when tensor parallelism is enabled.")
+            # The normalised vector is split over the ranks together with the heads: every rank keeps its slice of
+            # the weight, and the mean of squares is taken over all slices (summed over the gang, see
+            # `_norm_over_heads`). Only a norm without mean subtraction and bias can be split this way.
+            from fairseq2_b200.nn.normalization import RMSNorm
+
+            for norm in (q_norm, k_norm):
+                if norm is not None and (not isinstance(norm, RMSNorm) or norm.bias is not None):
+                    raise NotSupportedError(
+                        "`qk_norm_over_heads` with tensor parallelism needs RMS norms without bias.")
+            self._norm_full_dims = (num_heads * hd, nkv * hd)
+
+            def split(norm: LayerNorm | None, full: int) -> LayerNorm | None:
+                if norm is None:
+                    return None
+                if norm.normalized_shape != (full,):
+                    raise ValueError(f"The q/k norm must span the whole projection ({full}), but spans "
+                                     f"{norm.normalized_shape}.")
+                w = norm.weight
+                return RMSNorm(full // tp.size, bias=False, eps=norm.eps, elementwise_affine=w is not None,
+                               init_fn=norm.init_fn, device=w.device if w is not None else device,
+                               dtype=w.dtype if w is not None else dtype)
+
+            q_norm, k_norm = split(q_norm, num_heads * hd), split(k_norm, nkv * hd)
+        self.q_norm, self.k_norm = q_norm, k_norm
         if pos_encoder is not None and pos_encoder.encoding_dim != hd:
             raise ValueError(f"`pos_encoder.encoding_dim` must equal the head dimension ({hd}).")
         self.pos_encoder = pos_encoder
@@ -327,6 +350,29 @@ class StandardMultiheadAttention(MultiheadAttention):
             self.output_proj = Linear(num_heads * hd, model_dim, ob, init_fn=output_proj_init_fn, device=device,
                                       dtype=dtype)
         self.state_factory = state_factory
+
+    @property
+    def gang(self):  # type: ignore[no-untyped-def]
+        """The tensor-parallel gang (``None`` without tensor parallelism)."""
+        return self._tp_gang
+
+    def get_shard_dims(self) -> list[tuple[Parameter, int]]:
+        """Parameters of this module itself (not of its projections) that are split over the tensor-parallel gang:
+        the weights of q/k norms that span all heads."""
+        if self._norm_full_dims is None:
+            return []
+        return [(n.weight, 0) for n in (self.q_norm, self.k_norm) if n is not None and n.weight is not None]
+
+    def _norm_over_heads(self, norm: LayerNorm, x: Tensor, full_dim: int) -> Tensor:
+        """RMS norm over a vector of ``full_dim`` entries of which this rank holds a slice."""
+        if self._norm_full_dims is None:
+            return norm(x)
+        from fairseq2_b200.ops.tensor_parallel import reduce_both_ways
+
+        xf = x.float()
+        sq = reduce_both_ways(xf.pow(2).sum(dim=-1, keepdim=True), self._tp_gang)
+        y = (xf * torch.rsqrt(sq / full_dim + norm.eps)).type_as(x)
+        return y * norm.weight if norm.weight is not None else y
 
     def _head_norm(self, norm: LayerNorm, x: Tensor) -> Tensor:
         """A per-head q/k norm has ONE weight vector for all heads. With the heads split over tensor-parallel ranks
@@ -358,7 +404,7 @@ class StandardMultiheadAttention(MultiheadAttention):
         if q is None:
             q = self.q_proj(seqs)
             if self.q_norm is not None and self.qk_norm_over_heads:
-                q = self.q_norm(q)
+                q = self._norm_over_heads(self.q_norm, q, self.num_heads * self.head_dim)
             q = q.unflatten(-1, (H, D))
             if self.q_norm is not None and not self.qk_norm_over_heads:
                 q = self._head_norm(self.q_norm, q)
@@ -373,7 +419,7 @@ class StandardMultiheadAttention(MultiheadAttention):
             if k is None:
                 k = self.k_proj(keys)
                 if self.k_norm is not None and self.qk_norm_over_heads:
-                    k = self.k_norm(k)
+                    k = self._norm_over_heads(self.k_norm, k, self.num_key_value_heads * self.head_dim)
                 k = k.unflatten(-1, (Hkv, D))
                 v = self.v_proj(values).unflatten(-1, (Hkv, D))
                 if self.k_norm is not None and not self.qk_norm_over_heads:

@@ -424,3 +424,63 @@ def test_gradient_clipping_of_a_tensor_parallel_model_uses_the_whole_model_norm(
     for total, after, norm_w in run_distributed(_clip_worker, 2, timeout=120.0):
         assert total == pytest.approx(want, rel=1e-4) and after == pytest.approx(1.0, rel=1e-3)
         assert torch.allclose(torch.from_numpy(norm_w), want_w, rtol=1e-3, atol=1e-7)
+
+
+# ------------------------------------------------------------------ OLMo 2 (q/k norms that span all heads)
+def _olmo_train(model, steps: int):  # type: ignore[no-untyped-def]
+    from fairseq2_b200.nn import BatchLayout
+
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if n.endswith("q_norm.weight") or n.endswith("k_norm.weight"):
+                p.copy_(torch.linspace(0.5, 1.5, 128)[: p.numel()] if p.numel() == 128 else
+                        torch.linspace(0.5, 1.5, 128).chunk(2)[_olmo_train.rank])
+    opt = torch.optim.SGD(model.parameters(), lr=0.05)
+    g = torch.Generator().manual_seed(11)
+    losses = []
+    for _ in range(steps):
+        ids = torch.randint(1, 512, (2, 25), generator=g)
+        opt.zero_grad()
+        loss = model(ids[:, :-1], BatchLayout.of(ids[:, :-1]), targets=ids[:, 1:], reduction="mean")
+        loss.backward()
+        opt.step()
+        losses.append(float(loss.detach()))
+    return losses
+
+
+_olmo_train.rank = 0  # type: ignore[attr-defined]
+
+
+def _olmo_worker(rank: int, world: int, steps: int):
+    from fairseq2_b200.gang import ProcessGroupGang, create_parallel_gangs
+    from fairseq2_b200.models.olmo.config import olmo_tiny
+    from fairseq2_b200.models.olmo.factory import create_olmo_model
+    from fairseq2_b200.nn.sharded import get_shard_dims
+    from fairseq2_b200.parallel.tp import sequence_parallel
+
+    root = ProcessGroupGang.create_default_process_group(torch.device("cpu"))
+    gangs = create_parallel_gangs(root, tp_size=world)
+    torch.manual_seed(31)
+    with sequence_parallel(False):
+        model = create_olmo_model(olmo_tiny(), gangs)
+    _olmo_train.rank = gangs.tp.rank  # type: ignore[attr-defined]
+    dims = get_shard_dims(model)
+    q_norm_shape = tuple(model.decoder.layers[0].self_attn.q_norm.weight.shape)
+    losses = _olmo_train(model, steps)
+    root.close()
+    return losses, dims.get("decoder.layers.0.self_attn.q_norm.weight"), q_norm_shape
+
+
+def test_olmo_norms_over_all_heads_under_tensor_parallelism() -> None:
+    """OLMo 2 normalises the whole query / key projection. With the heads split over two ranks every rank holds
+    half of the vector and of the norm weight; the mean of squares is taken over both halves."""
+    from fairseq2_b200.gang import create_fake_gangs
+    from fairseq2_b200.models.olmo.config import olmo_tiny
+    from fairseq2_b200.models.olmo.factory import create_olmo_model
+
+    torch.manual_seed(31)
+    _olmo_train.rank = 0  # type: ignore[attr-defined]
+    want = _olmo_train(create_olmo_model(olmo_tiny(), create_fake_gangs(torch.device("cpu"))), 3)
+    for losses, dim, shape in run_distributed(_olmo_worker, 2, 3, timeout=180.0):
+        assert dim == 0 and shape == (64,)
+        assert losses == pytest.approx(want, rel=2e-4)
