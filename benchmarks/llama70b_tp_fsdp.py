@@ -46,6 +46,9 @@ def run_ours(args: argparse.Namespace) -> None:
     # empty: the model state below fills most of the device, and a communicator that initialises lazily at the
     # first barrier after that finds no room (that is how the first 8-GPU attempt of this configuration ended).
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    # Nothing in this configuration uses `multimem` (no replicated gradient buffers), so the arenas (49 GiB for the
+    # flat units) need no NVSwitch multicast binding either; torch's symmetric-memory rendezvous skips it when told.
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
     root = FakeGang(device) if world == 1 else ProcessGroupGang.create_default_process_group(device)
     gangs = create_fsdp_gangs(create_parallel_gangs(root, tp_size=tp))
     dp = gangs.dp
