@@ -184,7 +184,8 @@ def _run(args: Namespace) -> None:
 
     torch.manual_seed(2)
     if world > 1:
-        with torch.device("meta"), set_gangs(gangs, meta=True), set_dtype(torch.float32):
+        # tensor parallel size 1 here: the factory needs no gangs on the meta device (the 70B arm registers them)
+        with torch.device("meta"), set_gangs(gangs), set_dtype(torch.float32):
             model = LLaMAFactory(cfg).create_model()
 
         def applier(m, wrapper):  # type: ignore[no-untyped-def]
