@@ -236,3 +236,88 @@ def test_unordered_parallel_map_position_and_errors() -> None:
     s = read_sequence([str(i) for i in range(200)]).map(StrToIntConverter(), num_parallel_calls=8,
                                                          deterministic=False).and_return()
     assert sorted(s) == list(range(200))
+
+
+# ------------------------------------------------------------------ random operator chains
+def _random_chain(rng):  # type: ignore[no-untyped-def]
+    chain, bucketed = [], False
+    for _ in range(rng.randint(1, 5)):
+        k = rng.choice(["map", "pmap", "filter", "shuffle", "bucket", "take", "skip", "prefetch", "shard", "repeat",
+                        "unbucket"])
+        if bucketed and k in ("map", "pmap", "bucket"):      # the elements are lists now
+            k = "unbucket"
+        if k == "unbucket" and not bucketed:
+            k = "prefetch"
+        if k == "pmap":
+            chain.append((k, rng.choice([2, 3, 4])))
+        elif k == "shuffle":
+            chain.append((k, rng.choice([0, 1, 4, 16]), rng.randint(0, 5)))
+        elif k == "bucket":
+            chain.append((k, rng.choice([1, 2, 5]), rng.random() < 0.5))
+            bucketed = True
+        elif k == "take":
+            chain.append((k, rng.randint(0, 30)))
+        elif k == "skip":
+            chain.append((k, rng.randint(0, 10)))
+        elif k == "prefetch":
+            chain.append((k, rng.choice([1, 3])))
+        elif k == "shard":
+            chain.append((k, rng.randint(0, 1), 2))
+        elif k == "repeat":
+            chain.append((k, rng.choice([1, 2])))
+        else:
+            if k == "unbucket":
+                bucketed = False
+            chain.append((k,))
+    return chain
+
+
+def _build_chain(chain, n: int) -> DataPipeline:  # type: ignore[no-untyped-def]
+    b = read_sequence(list(range(n)))
+    for op in chain:
+        k = op[0]
+        if k == "map":
+            b = b.map(lambda x: x + 1)
+        elif k == "pmap":
+            b = b.map(lambda x: x * 2, num_parallel_calls=op[1])
+        elif k == "filter":
+            b = b.filter(lambda x: (x if isinstance(x, int) else len(x)) % 3 != 0)
+        elif k == "shuffle":
+            b = b.shuffle(op[1], seed=op[2])
+        elif k == "bucket":
+            b = b.bucket(op[1], drop_remainder=op[2])
+        elif k == "take":
+            b = b.take(op[1])
+        elif k == "skip":
+            b = b.skip(op[1])
+        elif k == "prefetch":
+            b = b.prefetch(op[1])
+        elif k == "shard":
+            b = b.shard(op[1], op[2], allow_uneven=True)
+        elif k == "repeat":
+            b = b.repeat(op[1])
+        else:
+            b = b.yield_from(lambda xs: read_sequence(list(xs)).and_return())
+    return b.and_return()
+
+
+def test_random_operator_chains_save_and_restore_their_position() -> None:
+    """300 random chains of up to five operators: stopping anywhere, saving the position, loading it into a freshly
+    built pipeline and reading on gives the uninterrupted output; a reset with the generators rewound does too."""
+    import random
+
+    rng = random.Random(0)
+    for _ in range(300):
+        chain, n = _random_chain(rng), rng.randint(0, 40)
+        want = list(_build_chain(chain, n))
+        for _ in range(2):
+            k = rng.randint(0, len(want))
+            p = _build_chain(chain, n)
+            it = iter(p)
+            head = [next(it) for _ in range(k)]
+            state = p.state_dict()
+            q = _build_chain(chain, n)
+            q.load_state_dict(state)
+            assert head + list(q) == want, (chain, n, k)
+            p.reset(True)
+            assert list(p) == want, (chain, n)
