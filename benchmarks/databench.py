@@ -62,7 +62,7 @@ def main() -> None:
             t0 = time.perf_counter()
             tokens = batches = 0
             for batch in pipeline:
-                tokens += int(batch["seq_lens"].sum()) if isinstance(batch, dict) else 0
+                tokens += sum(batch["seq_lens"]) if isinstance(batch, dict) else 0
                 batches += 1
             dt = time.perf_counter() - t0
             print(json.dumps({"case": name, "workers": workers, "lines": len(lines), "batches": batches,

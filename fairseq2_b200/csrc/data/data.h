@@ -114,6 +114,7 @@ public:
     Data(DataDict v) : v_(std::make_shared<DataDict>(std::move(v))) {}
     Data(PyObjectHolder v) : v_(std::move(v)) {}
 
+    size_t index() const { return v_.index(); }   // which alternative is held: equal for values of one type
     bool is_none() const { return std::holds_alternative<std::monostate>(v_); }
     bool is_bool() const { return std::holds_alternative<bool>(v_); }
     bool is_int() const { return std::holds_alternative<int64_t>(v_); }

@@ -156,7 +156,10 @@ Data collate_tensors(const std::vector<at::Tensor>& ts, const std::optional<int6
         if (n != max_len) ragged = true;
         out[static_cast<int64_t>(i)].narrow(0, 0, n).copy_(ts[i]);
     }
-    DataDict d{{"is_ragged", Data(ragged)}, {"seqs", Data(out)}, {"seq_lens", Data(at::tensor(lens, at::kLong))}};
+    DataList lens_l;
+    lens_l.reserve(lens.size());
+    for (int64_t n : lens) lens_l.emplace_back(n);
+    DataDict d{{"is_ragged", Data(ragged)}, {"seqs", Data(out)}, {"seq_lens", Data(std::move(lens_l))}};
     return Data(std::move(d));
 }
 
@@ -166,63 +169,135 @@ Collater::Collater(std::optional<int64_t> pad_value, int64_t pad_to_multiple, st
     : pad_value_(pad_value), pad_to_multiple_(pad_to_multiple), overrides_(std::move(overrides)) {
     if (pad_to_multiple_ > 1 && !pad_value_)
         throw std::invalid_argument("`pad_value` must be set when `pad_to_multiple` is greater than 1.");
+    for (const auto& ov : overrides_)
+        if (ov.pad_to_multiple > 1 && !ov.pad_value)
+            throw std::invalid_argument("`pad_value` of the selector '" + ov.selector +
+                                        "' must be set when `pad_to_multiple` is greater than 1.");
 }
 
+namespace {
+
+const char* collate_type_name(const Data& d) {
+    if (d.is_none()) return "none";
+    if (d.is_bool()) return "bool";
+    if (d.is_int()) return "int";
+    if (d.is_float()) return "float";
+    if (d.is_string()) return "string";
+    if (d.is_tensor()) return "torch.Tensor";
+    if (d.is_memory_block()) return "memory_block";
+    if (d.is_list()) return "list";
+    if (d.is_dict()) return "dict";
+    return "pyobj";
+}
+
+// "The bucket item 1 ..." at the root, "The element at path 'a[0]' in the bucket item 1 ..." below it.
+std::string item_ref(const char* what, const std::string& path, size_t item) {
+    if (path.empty()) return "The bucket item " + std::to_string(item);
+    return std::string("The ") + what + " at path '" + path + "' in the bucket item " + std::to_string(item);
+}
+
+// An override selector matches a path segment by segment; `[*]` stands for any list index.
+bool selector_matches(const std::string& selector, const std::string& path) {
+    size_t i = 0, j = 0;
+    while (i < selector.size() && j < path.size()) {
+        if (selector.compare(i, 3, "[*]") == 0 && path[j] == '[') {
+            const size_t close = path.find(']', j);
+            if (close == std::string::npos) return false;
+            i += 3;
+            j = close + 1;
+        } else if (selector[i] == path[j]) {
+            ++i;
+            ++j;
+        } else {
+            return false;
+        }
+    }
+    return i == selector.size() && j == path.size();
+}
+
+}  // namespace
+
 Data Collater::operator()(Data&& bucket) const {
-    if (!bucket.is_list()) throw std::invalid_argument("The collater expects a list of examples (a bucket).");
+    if (!bucket.is_list()) {
+        // a single example is a bucket of one
+        DataList one;
+        one.push_back(std::move(bucket));
+        return collate(one, "");
+    }
     DataList& items = bucket.as_list();
-    if (items.empty()) throw std::invalid_argument("The bucket must contain at least one element.");
+    if (items.empty()) throw std::invalid_argument("The bucket must contain at least one element, but is empty instead.");
     return collate(items, "");
 }
 
 Data Collater::collate(DataList& items, const std::string& path) const {
     const Data& first = items[0];
+    for (size_t i = 1; i < items.size(); ++i)
+        if (items[i].index() != first.index())
+            throw std::invalid_argument(item_ref("element", path, i) + " must be of type `" + collate_type_name(first) +
+                                        "`, but is of type `" + collate_type_name(items[i]) + "` instead.");
     if (first.is_dict()) {
+        const size_t n = first.as_dict().size();
+        for (size_t i = 1; i < items.size(); ++i)
+            if (items[i].as_dict().size() != n)
+                throw std::invalid_argument(item_ref("`dict`", path, i) + " must have a length of " + std::to_string(n) +
+                                            ", but has a length of " + std::to_string(items[i].as_dict().size()) +
+                                            " instead.");
         DataDict out;
         for (const auto& kv : first.as_dict()) {
+            const std::string sub = path.empty() ? kv.first : path + "." + kv.first;
             DataList column;
             column.reserve(items.size());
-            for (auto& it : items) {
-                if (!it.is_dict()) throw std::invalid_argument("The bucket items at path '" + path + "' must all be dicts.");
-                const Data* e = it.find(kv.first);
-                if (e == nullptr || it.as_dict().size() != first.as_dict().size())
-                    throw std::invalid_argument("The dicts in the bucket at path '" + path + "' must all have the same keys.");
+            for (size_t i = 0; i < items.size(); ++i) {
+                const Data* e = items[i].find(kv.first);
+                if (e == nullptr)
+                    throw std::invalid_argument("The bucket item " + std::to_string(i) +
+                                                " does not have an element at path '" + sub + "'.");
                 column.push_back(*e);
             }
-            out.emplace_back(kv.first, collate(column, path.empty() ? kv.first : path + "." + kv.first));
+            out.emplace_back(kv.first, collate(column, sub));
         }
         return Data(std::move(out));
     }
     if (first.is_list()) {
         const size_t n = first.as_list().size();
+        for (size_t i = 1; i < items.size(); ++i)
+            if (items[i].as_list().size() != n)
+                throw std::invalid_argument(item_ref("`list`", path, i) + " must have a length of " + std::to_string(n) +
+                                            ", but has a length of " + std::to_string(items[i].as_list().size()) +
+                                            " instead.");
         DataList out;
-        for (size_t i = 0; i < n; ++i) {
+        for (size_t k = 0; k < n; ++k) {
             DataList column;
-            for (auto& it : items) {
-                if (!it.is_list() || it.as_list().size() != n)
-                    throw std::invalid_argument("The lists in the bucket at path '" + path + "' must all have the same length.");
-                column.push_back(it.as_list()[i]);
-            }
-            out.push_back(collate(column, path + "[" + std::to_string(i) + "]"));
+            column.reserve(items.size());
+            for (auto& it : items) column.push_back(it.as_list()[k]);
+            out.push_back(collate(column, path + "[" + std::to_string(k) + "]"));
         }
         return Data(std::move(out));
     }
     if (first.is_tensor()) {
         std::vector<at::Tensor> ts;
-        for (auto& it : items) {
-            if (!it.is_tensor()) throw std::invalid_argument("The bucket items at path '" + path + "' must all be tensors.");
-            ts.push_back(it.as_tensor());
-        }
+        ts.reserve(items.size());
+        for (auto& it : items) ts.push_back(it.as_tensor());
         std::optional<int64_t> pad = pad_value_;
         int64_t mult = pad_to_multiple_;
         for (const auto& ov : overrides_)
-            if (ov.selector == path) {
+            if (selector_matches(ov.selector, path)) {
                 pad = ov.pad_value;
                 mult = ov.pad_to_multiple;
             }
+        if (!pad) {
+            try {
+                return Data(at::stack(ts));
+            } catch (const c10::Error& ex) {
+                std::throw_with_nested(std::invalid_argument(
+                    (path.empty() ? std::string("The tensors in the bucket")
+                                  : "The tensors at path '" + path + "' in the bucket") +
+                    " cannot be stacked. See nested exception for details."));
+            }
+        }
         return collate_tensors(ts, pad, mult, path);
     }
-    return Data(DataList(items));  // non-tensor leaves stay a list
+    return Data(DataList(items));  // other leaves stay a list
 }
 
 // ================================================================= list_files

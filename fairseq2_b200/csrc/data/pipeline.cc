@@ -1082,8 +1082,10 @@ public:
         }
         if (fill == 0) return std::nullopt;
         if (fill < capacity_ && eod_ && drop_) return std::nullopt;
-        at::Tensor lens_t = at::tensor(lens, at::kLong);
-        DataDict out{{"seqs", Data(buf)}, {"seq_lens", Data(lens_t)}};
+        DataList lens_l;
+        lens_l.reserve(lens.size());
+        for (int64_t n : lens) lens_l.emplace_back(n);
+        DataDict out{{"seqs", Data(buf)}, {"seq_lens", Data(std::move(lens_l))}};
         return Data(std::move(out));
     }
     void reset(bool r) override {

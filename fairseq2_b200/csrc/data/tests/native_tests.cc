@@ -270,8 +270,8 @@ TEST(collater_pads_and_stacks) {
     const at::Tensor& seqs = out.find("seqs")->as_tensor();
     CHECK(seqs.size(0) == 2 && seqs.size(1) == 8);               // padded to a multiple of 4
     CHECK(seqs[0][3].item<int64_t>() == 0 && seqs[1][4].item<int64_t>() == 1);
-    const at::Tensor& lens = out.find("seq_lens")->as_tensor();
-    CHECK(lens[0].item<int64_t>() == 3 && lens[1].item<int64_t>() == 5);
+    const DataList& lens = out.find("seq_lens")->as_list();                // plain integers, as the batch types expect
+    CHECK(lens.size() == 2 && lens[0].as_int() == 3 && lens[1].as_int() == 5);
     Collater stack(std::nullopt, 1, {});
     Data st = stack(Data(DataList{Data(at::zeros({2, 2})), Data(at::ones({2, 2}))}));
     CHECK(st.is_tensor() && st.as_tensor().size(0) == 2 && st.as_tensor()[1][0][0].item<float>() == 1.f);

@@ -54,7 +54,7 @@ class SequenceData(TypedDict):
     """Output of the collater for padded sequences."""
 
     seqs: Tensor
-    seq_lens: Tensor
+    seq_lens: list[int]
     is_ragged: bool
 
 

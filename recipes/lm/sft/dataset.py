@@ -165,7 +165,7 @@ class LMSFTDataset:
                 folded = ex["seqs"]
                 mask = folded >= 0
                 seqs = torch.where(mask, folded, -folded - 1)
-                return SequenceBatch(seqs, ex["seq_lens"].tolist(), packed=True, target_mask=mask)
+                return SequenceBatch(seqs, list(ex["seq_lens"]), packed=True, target_mask=mask)
 
             b.map(to_packed)
         else:

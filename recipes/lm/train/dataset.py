@@ -65,7 +65,7 @@ class LMTrainDataset:
         b.pack(max_num_tokens + 1, max_seq_len, truncate=True, drop_remainder=True,
                pinned_memory=torch.cuda.is_available())
         b.prefetch(prefetch)
-        b.map(lambda ex: SequenceBatch(ex["seqs"], ex["seq_lens"].tolist(), packed=True))
+        b.map(lambda ex: SequenceBatch(ex["seqs"], list(ex["seq_lens"]), packed=True))
         return DataPipelineReader(self._name, split, b.and_return(), gangs.dp, num_accumulate=num_accumulate,
                                   sync=sync_ranks, sync_mode=SyncMode.UNTIL_FIRST)
 
