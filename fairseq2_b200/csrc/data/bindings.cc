@@ -244,7 +244,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                         bool truncate, bool drop, bool pinned) -> DataPipelineBuilder& {
             b = std::move(b).pack(num_elements, max_seq_len, pad_value, truncate, drop, pinned);
             return b;
-        }, py::arg("num_elements"), py::arg("max_seq_len"), py::arg("pad_value") = 0, py::arg("truncate") = false,
+        }, py::arg("num_elements"), py::arg("max_seq_len"), py::arg("pad_value") = 0, py::arg("truncate") = true,
            py::arg("drop_remainder") = true, py::arg("pinned_memory") = false,
            py::return_value_policy::reference_internal)
         .def("prefetch", [](DataPipelineBuilder& b, size_t n) -> DataPipelineBuilder& {

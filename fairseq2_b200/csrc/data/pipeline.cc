@@ -487,6 +487,9 @@ private:
 // Wraps a Python iterator; its state is the pickled iterator itself.
 class PyIteratorSource final : public DataSource {
 public:
+    // The iterator is handed to `reset_fn` before its first element is read, here and after every reset: a source
+    // built anew over an iterator that an earlier pass used up (a `yield_from` callback after a reset of the outer
+    // pipeline) starts from the beginning like any other source.
     PyIteratorSource(py::object it, py::object reset_fn, bool infinite)
         : it_(std::move(it)), reset_fn_(std::move(reset_fn)), infinite_(infinite) {}
     ~PyIteratorSource() override {
@@ -496,6 +499,10 @@ public:
     }
     std::optional<Data> next() override {
         py::gil_scoped_acquire gil;
+        if (pending_reset_) {
+            pending_reset_ = false;
+            it_ = reset_fn_(it_);
+        }
         PyObject* item = PyIter_Next(it_.ptr());
         if (item == nullptr) {
             if (PyErr_Occurred()) throw py::error_already_set();
@@ -503,26 +510,26 @@ public:
         }
         return data_from_py(py::reinterpret_steal<py::object>(item));
     }
-    void reset(bool) override {
-        py::gil_scoped_acquire gil;
-        it_ = reset_fn_(it_);
-    }
+    void reset(bool) override { pending_reset_ = true; }
     void record_position(Tape& t, bool) const override {
         py::gil_scoped_acquire gil;
         py::object dumps = py::module_::import("pickle").attr("dumps");
         t.record(Data(PyObjectHolder(dumps(it_))));
+        t.record(Data(pending_reset_));
     }
     void reload_position(Tape& t, bool) override {
         py::gil_scoped_acquire gil;
         Data d = t.read();
         py::object loads = py::module_::import("pickle").attr("loads");
         it_ = loads(data_to_py(d));
+        pending_reset_ = t.read_bool();
     }
     Finitude finitude() const override { return infinite_ ? Finitude::Infinite : Finitude::Finite; }
 
 private:
     py::object it_, reset_fn_;
     bool infinite_;
+    bool pending_reset_ = true;
 };
 
 // ===================================================================== operators
@@ -1021,71 +1028,66 @@ public:
                bool truncate, bool drop_remainder, bool pinned)
         : in_(std::move(in)), capacity_(num_elements), max_seq_len_(max_seq_len), pad_(pad_value),
           truncate_(truncate), drop_(drop_remainder), pinned_(pinned) {}
+    // Rules (those of fairseq2n's packed_data_source.cc:19-122):
+    //  * a piece of a sequence is at most `max_seq_len` long and never crosses the end of the buffer;
+    //  * `truncate`: a sequence that is longer than the room it gets is cut. Cut at the end of the buffer, the next
+    //    buffer starts again with the last token that went in (so that no next-token target is lost); cut by
+    //    `max_seq_len` inside a buffer, the rest follows as its own piece;
+    //  * without `truncate` a sequence that does not fit (or is longer than `max_seq_len`) closes the buffer and
+    //    opens the next one; alone in an empty buffer it is an error;
+    //  * a last, partly filled buffer is dropped only with `truncate` and `drop_remainder`.
     std::optional<Data> next() override {
-        if (eod_) return std::nullopt;
         at::Tensor buf;
-        std::vector<int64_t> lens;
+        DataList lens;
         int64_t fill = 0;
-        auto ensure_buf = [&](const at::Tensor& like) {
-            if (!buf.defined()) {
-                auto opts = like.options().device(at::kCPU);
-                if (pinned_) opts = opts.pinned_memory(true);
-                buf = at::full({capacity_}, pad_, opts);
-            }
-        };
-        auto append = [&](const at::Tensor& seq) {
-            ensure_buf(seq);
-            const int64_t n = seq.size(0);
-            buf.narrow(0, fill, n).copy_(seq);
-            lens.push_back(n);
-            fill += n;
-        };
-        while (fill < capacity_) {
+        bool filled = false;
+        while (true) {
             at::Tensor seq;
+            std::optional<Data> example;
             if (remainder_.defined()) {
                 seq = remainder_;
                 remainder_ = at::Tensor();
             } else {
-                auto d = in_->next();
-                if (!d) {
-                    eod_ = true;
+                example = in_->next();
+                if (!example) break;
+                if (!example->is_tensor())
+                    throw DataPipelineError("The pack operation can only be used with tensor inputs.", /*recoverable=*/true);
+                seq = example->as_tensor();
+                if (seq.dim() != 1)
+                    throw DataPipelineError("The input tensors to the pack operation must be one-dimensional.",
+                                            /*recoverable=*/true);
+            }
+            if (!buf.defined()) {
+                buf = at::full({capacity_}, pad_, seq.options().pinned_memory(pinned_));
+            } else {
+                seq = seq.to(buf.device());
+            }
+            const int64_t numel = seq.numel();
+            if (numel == 0) continue;
+            const int64_t piece = std::min(numel, std::min(capacity_ - fill, max_seq_len_));
+            if (numel > piece) {
+                if (truncate_) {
+                    const bool at_buffer_end = fill + piece == capacity_;
+                    remainder_ = seq.slice(0, at_buffer_end ? piece - 1 : piece);
+                    seq = seq.slice(0, 0, piece);
+                } else {
+                    if (fill == 0)
+                        throw DataPipelineError("The input tensor is too long to pack.", /*recoverable=*/true);
+                    remainder_ = seq;
                     break;
                 }
-                if (!d->is_tensor() || d->as_tensor().dim() != 1)
-                    throw DataPipelineError("`pack()` expects one-dimensional tensors.");
-                seq = d->as_tensor();
             }
-            if (seq.size(0) == 0) continue;
-            if (seq.size(0) > max_seq_len_) {
-                if (!truncate_) {
-                    // split long sequences into max_seq_len pieces; the rest is carried over
-                    remainder_ = seq.narrow(0, max_seq_len_, seq.size(0) - max_seq_len_);
-                }
-                seq = seq.narrow(0, 0, max_seq_len_);
-            }
-            const int64_t room = capacity_ - fill;
-            if (seq.size(0) <= room) {
-                append(seq);
-            } else if (truncate_) {
-                append(seq.narrow(0, 0, room));
-                // carry the remainder, overlapping by one token so that no next-token target is lost
-                const int64_t start = room > 0 ? room - 1 : 0;
-                at::Tensor rest = seq.narrow(0, start, seq.size(0) - start);
-                if (remainder_.defined()) remainder_ = at::cat({rest, remainder_});
-                else remainder_ = rest;
-            } else {
-                // does not fit: close this buffer, keep the sequence for the next one
-                if (remainder_.defined()) remainder_ = at::cat({seq, remainder_});
-                else remainder_ = seq;
+            buf.slice(0, fill, fill + piece).copy_(seq);
+            lens.emplace_back(piece);
+            fill += piece;
+            if (fill == capacity_) {
+                filled = true;
                 break;
             }
         }
-        if (fill == 0) return std::nullopt;
-        if (fill < capacity_ && eod_ && drop_) return std::nullopt;
-        DataList lens_l;
-        lens_l.reserve(lens.size());
-        for (int64_t n : lens) lens_l.emplace_back(n);
-        DataDict out{{"seqs", Data(buf)}, {"seq_lens", Data(std::move(lens_l))}};
+        if (truncate_ && !filled && drop_) return std::nullopt;
+        if (!buf.defined()) return std::nullopt;
+        DataDict out{{"seqs", Data(buf)}, {"seq_lens", Data(std::move(lens))}};
         return Data(std::move(out));
     }
     void reset(bool r) override {
@@ -1650,8 +1652,15 @@ DataPipelineBuilder DataPipeline::zip(std::vector<DataPipeline> pipelines, std::
 }
 
 DataPipelineBuilder read_py_iterator(py::object iterator, py::object reset_fn, bool infinite) {
-    auto it = std::make_shared<py::object>(std::move(iterator));
-    auto rf = std::make_shared<py::object>(std::move(reset_fn));
+    // The factory may be destroyed on any thread and without the interpreter lock (a pipeline built inside a
+    // `yield_from` callback dies in the middle of a `next()` that runs unlocked): the references are dropped under
+    // the lock, whoever drops them.
+    auto release = [](py::object* o) {
+        py::gil_scoped_acquire gil;
+        delete o;
+    };
+    std::shared_ptr<py::object> it(new py::object(std::move(iterator)), release);
+    std::shared_ptr<py::object> rf(new py::object(std::move(reset_fn)), release);
     return DataPipelineBuilder([it, rf, infinite]() -> std::unique_ptr<DataSource> {
         py::gil_scoped_acquire gil;
         return std::make_unique<PyIteratorSource>(*it, *rf, infinite);

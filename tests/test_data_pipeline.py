@@ -163,14 +163,21 @@ def test_prefetch_preserves_order_and_errors() -> None:
 
 def test_pack() -> None:
     seqs = [torch.full((n,), i + 1) for i, n in enumerate((3, 4, 2, 5))]
-    p = read_sequence(seqs).pack(num_elements=8, max_seq_len=8, pad_value=0, drop_remainder=False).and_return()
-    out = list(p)
+    p = read_sequence(seqs).pack(num_elements=8, max_seq_len=8, pad_value=0, truncate=False).and_return()
+    out = list(p)                                           # whole sequences only; the last buffer is kept
     assert out[0]["seqs"].tolist() == [1, 1, 1, 2, 2, 2, 2, 0] and out[0]["seq_lens"] == [3, 4]
     assert out[1]["seqs"].tolist() == [3, 3, 4, 4, 4, 4, 4, 0] and out[1]["seq_lens"] == [2, 5]
-    p = read_sequence(seqs).pack(num_elements=8, max_seq_len=8, truncate=True, drop_remainder=False).and_return()
+    p = read_sequence(seqs).pack(num_elements=8, max_seq_len=8, drop_remainder=False).and_return()   # truncating
     out = list(p)
-    assert out[0]["seq_lens"] == [3, 4, 1]
-    assert sum(out[0]["seq_lens"]) == 8
+    assert out[0]["seqs"].tolist() == [1, 1, 1, 2, 2, 2, 2, 3] and out[0]["seq_lens"] == [3, 4, 1]
+    # the next buffer starts again with the last token that went in
+    assert out[1]["seqs"].tolist() == [3, 3, 4, 4, 4, 4, 4, 0] and out[1]["seq_lens"] == [2, 5]
+    # pieces are at most `max_seq_len` long; the rest of a sequence follows as its own piece
+    p = read_sequence([torch.arange(1, 8)]).pack(num_elements=8, max_seq_len=3, drop_remainder=False).and_return()
+    out = list(p)
+    assert out[0]["seqs"].tolist() == [1, 2, 3, 4, 5, 6, 7, 0] and out[0]["seq_lens"] == [3, 3, 1]
+    with pytest.raises(DataPipelineError, match="too long to pack"):
+        list(read_sequence([torch.arange(9)]).pack(num_elements=8, max_seq_len=8, truncate=False).and_return())
 
 
 def test_collater_pads_and_stacks() -> None:
