@@ -224,7 +224,7 @@ public:
         : ps_(std::move(ps)), stop_at_shortest_(stop_at_shortest), allow_repeats_(allow_repeats) {
         fin_ = max_finitude_of(ps_);
         buffer_.resize(ps_.size());
-        done_.assign(ps_.size(), false);
+        mark_endless_done();
     }
     std::optional<Data> next() override {
         if (ps_.empty() || eod_) return std::nullopt;
@@ -260,7 +260,7 @@ public:
     void reset(bool r) override {
         for (auto& p : ps_) p.reset(r);
         std::fill(buffer_.begin(), buffer_.end(), std::nullopt);
-        std::fill(done_.begin(), done_.end(), false);
+        mark_endless_done();
         idx_ = 0;
         filled_ = false;
         eod_ = false;
@@ -290,8 +290,20 @@ public:
     Finitude finitude() const override { return fin_; }
 
 private:
+    // A pipeline that never ends by construction (`constant`, `count`) has no epoch to finish: it takes its turns
+    // but the round ends when the pipelines that do end have all been through once. (A pipeline made endless with
+    // `repeat()` keeps the whole round going for ever.)
+    void mark_endless_done() {
+        done_.assign(ps_.size(), false);
+        for (size_t i = 0; i < ps_.size(); ++i)
+            if (ps_[i].finitude() == Finitude::PseudoInfinite) done_[i] = true;
+    }
     bool finished() const {
-        if (stop_at_shortest_) return std::any_of(done_.begin(), done_.end(), [](bool b) { return b; });
+        if (stop_at_shortest_) {
+            for (size_t i = 0; i < ps_.size(); ++i)
+                if (done_[i] && ps_[i].finitude() != Finitude::PseudoInfinite) return true;
+            return false;
+        }
         return std::all_of(done_.begin(), done_.end(), [](bool b) { return b; });
     }
     std::vector<DataPipeline> ps_;
@@ -310,7 +322,7 @@ public:
         : ps_(std::move(ps)), weights_(std::move(w)), seed_(seed), allow_repeats_(allow_repeats), gen_(seed) {
         fin_ = max_finitude_of(ps_);
         buffer_.resize(ps_.size());
-        done_.assign(ps_.size(), false);
+        mark_endless_done();
         blocked_.assign(ps_.size(), false);
     }
     std::optional<Data> next() override {
@@ -362,7 +374,7 @@ public:
     void reset(bool r) override {
         for (auto& p : ps_) p.reset(r);
         std::fill(buffer_.begin(), buffer_.end(), std::nullopt);
-        std::fill(done_.begin(), done_.end(), false);
+        mark_endless_done();
         std::fill(blocked_.begin(), blocked_.end(), false);
         filled_ = eod_ = false;
         if (r) gen_.seed(seed_);
@@ -394,6 +406,13 @@ public:
     Finitude finitude() const override { return fin_; }
 
 private:
+    // `constant` / `count` pipelines have no epoch to finish: sampling ends when the pipelines that do end have all
+    // been through once
+    void mark_endless_done() {
+        done_.assign(ps_.size(), false);
+        for (size_t i = 0; i < ps_.size(); ++i)
+            if (ps_[i].finitude() == Finitude::PseudoInfinite) done_[i] = true;
+    }
     bool all_done() const {
         return std::all_of(done_.begin(), done_.end(), [](bool b) { return b; });
     }
@@ -1273,7 +1292,7 @@ public:
         in_->reload_position(t, s);
     }
     Finitude finitude() const override {
-        return n_ ? in_->finitude() : max_finitude(in_->finitude(), Finitude::PseudoInfinite);
+        return n_ ? in_->finitude() : Finitude::Infinite;   // repeated without a count: endless for good
     }
 
 private:
