@@ -251,6 +251,8 @@ public:
                     ps_[i].reset(false);
                     buffer_[i] = ps_[i].next();
                 }
+            } else if (ps_[i].finitude() == Finitude::PseudoInfinite) {
+                done_[i] = true;
             }
             return out;
         }
@@ -290,14 +292,10 @@ public:
     Finitude finitude() const override { return fin_; }
 
 private:
-    // A pipeline that never ends by construction (`constant`, `count`) has no epoch to finish: it takes its turns
-    // but the round ends when the pipelines that do end have all been through once. (A pipeline made endless with
-    // `repeat()` keeps the whole round going for ever.)
-    void mark_endless_done() {
-        done_.assign(ps_.size(), false);
-        for (size_t i = 0; i < ps_.size(); ++i)
-            if (ps_[i].finitude() == Finitude::PseudoInfinite) done_[i] = true;
-    }
+    // A pipeline that never ends by construction (`constant`, `count`) has no epoch to finish: it counts as
+    // through once it has been read, so the round ends when the pipelines that do end have all been through once.
+    // (A pipeline made endless with `repeat()` keeps the whole round going for ever.)
+    void mark_endless_done() { done_.assign(ps_.size(), false); }
     bool finished() const {
         if (stop_at_shortest_) {
             for (size_t i = 0; i < ps_.size(); ++i)
@@ -367,6 +365,8 @@ public:
                 } else {
                     blocked_[pick] = true;
                 }
+            } else if (ps_[pick].finitude() == Finitude::PseudoInfinite) {
+                done_[pick] = true;
             }
             return out;
         }
@@ -406,13 +406,9 @@ public:
     Finitude finitude() const override { return fin_; }
 
 private:
-    // `constant` / `count` pipelines have no epoch to finish: sampling ends when the pipelines that do end have all
-    // been through once
-    void mark_endless_done() {
-        done_.assign(ps_.size(), false);
-        for (size_t i = 0; i < ps_.size(); ++i)
-            if (ps_[i].finitude() == Finitude::PseudoInfinite) done_[i] = true;
-    }
+    // `constant` / `count` pipelines have no epoch to finish: they count as through once they have been drawn from,
+    // so sampling ends when every pipeline has been through once
+    void mark_endless_done() { done_.assign(ps_.size(), false); }
     bool all_done() const {
         return std::all_of(done_.begin(), done_.end(), [](bool b) { return b; });
     }

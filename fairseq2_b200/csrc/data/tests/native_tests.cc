@@ -421,8 +421,9 @@ TEST(pipeline_round_robin) {
 
 TEST(pipeline_sample_follows_weights) {
     auto make = [] {
-        return DataPipeline::sample({DataPipeline::constant(Data(0), std::nullopt).and_return(),
-                                     DataPipeline::constant(Data(1), std::nullopt).and_return()},
+        // repeated without a count: endless for good (a bare `constant` counts as through after one draw)
+        return DataPipeline::sample({read_list(DataList{Data(0)}).repeat(std::nullopt, false).and_return(),
+                                     read_list(DataList{Data(1)}).repeat(std::nullopt, false).and_return()},
                                     std::vector<float>{0.8f, 0.2f}, 3, true)
             .take(2000)
             .and_return();
