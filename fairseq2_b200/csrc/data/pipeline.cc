@@ -41,8 +41,15 @@ std::optional<Data> DataPipeline::next() {
                 ++s_->warning_count;
                 continue;  // skip the faulty example
             }
-            s_->broken = true;
+            // only an error that cannot be recovered from makes every later read fail
+            if (!ex.recoverable()) s_->broken = true;
             throw;
+        } catch (const ByteStreamError& ex) {
+            s_->broken = true;
+            throw DataPipelineError(ex.what());
+        } catch (const RecordError& ex) {
+            s_->broken = true;
+            throw DataPipelineError(ex.what());
         } catch (...) {
             s_->broken = true;
             throw;
@@ -433,31 +440,39 @@ public:
         if (ps_.empty()) return std::nullopt;
         DataList items;
         items.reserve(ps_.size());
-        size_t num_ended = 0;
-        for (auto& p : ps_) {
-            auto d = p.next();
+        // Pipelines that are endless by construction (`constant`, `count`) ride along: the zip ends with the others.
+        bool only_endless = true;
+        for (auto& p : ps_)
+            if (p.finitude() != Finitude::PseudoInfinite) only_endless = false;
+        if (only_endless) throw DataPipelineError("Cannot zip only pseudo-infinite pipelines.");
+        std::vector<size_t> ended, going;
+        for (size_t i = 0; i < ps_.size(); ++i) {
+            auto d = ps_[i].next();
             if (!d) {
-                ++num_ended;
+                ended.push_back(i);
                 items.emplace_back();
             } else {
+                if (ps_[i].finitude() != Finitude::PseudoInfinite) going.push_back(i);
                 items.push_back(std::move(*d));
             }
         }
-        if (num_ended == ps_.size()) return std::nullopt;
-        if (num_ended > 0) {
-            if (to_shortest_) return std::nullopt;
-            throw DataPipelineError("The zipped data pipelines must all have the same number of examples.");
+        if (!ended.empty()) {
+            if (to_shortest_ || going.empty()) return std::nullopt;
+            std::string idx;
+            for (size_t i : going) idx += (idx.empty() ? "" : ", ") + std::to_string(i);
+            throw DataPipelineError("The zipped data pipelines must all have the same number of examples, but the data "
+                                    "pipelines at the indices [" + idx + "] have more examples than the others.");
         }
         if (flatten_) {
             if (items[0].is_dict()) {
                 DataDict out;
                 for (auto& it : items) {
                     if (!it.is_dict())
-                        throw DataPipelineError("The zipped pipelines must all return only dicts, or only non-dicts when `flatten` is set.");
+                        throw DataPipelineError("The zipped data pipelines must all return only dicts or only non-dicts when `flatten` is set.");
                     for (auto& kv : it.as_dict()) {
                         for (const auto& e : out)
                             if (e.first == kv.first)
-                                throw DataPipelineError("The zipped dicts must have unique keys when `flatten` is set; '" + kv.first + "' is not unique.");
+                                throw DataPipelineError("The zipped data pipelines must all return unique keys when `flatten` is set, but the key '" + kv.first + "' is not unique.");
                         out.push_back(kv);
                     }
                 }
@@ -466,7 +481,7 @@ public:
             DataList out;
             for (auto& it : items) {
                 if (it.is_dict())
-                    throw DataPipelineError("The zipped pipelines must all return only dicts, or only non-dicts when `flatten` is set.");
+                    throw DataPipelineError("The zipped data pipelines must all return only dicts or only non-dicts when `flatten` is set.");
                 if (it.is_list())
                     for (auto& e : it.as_list()) out.push_back(e);
                 else
@@ -1620,7 +1635,19 @@ std::shared_ptr<std::vector<DataPipeline>> share(std::vector<DataPipeline> ps) {
 }
 }  // namespace
 
+namespace {
+
+void refuse_broken(const std::vector<DataPipeline>& pipelines, const char* what) {
+    for (const auto& p : pipelines)
+        if (p.is_broken())
+            throw std::invalid_argument(std::string("At least one of the specified data pipelines is broken and cannot be ") +
+                                        what + ".");
+}
+
+}  // namespace
+
 DataPipelineBuilder DataPipeline::concat(std::vector<DataPipeline> pipelines) {
+    refuse_broken(pipelines, "concatenated");
     auto sp = share(std::move(pipelines));
     return DataPipelineBuilder([sp]() -> std::unique_ptr<DataSource> {
         return std::make_unique<ConcatSource>(std::move(*sp));
@@ -1629,6 +1656,7 @@ DataPipelineBuilder DataPipeline::concat(std::vector<DataPipeline> pipelines) {
 
 DataPipelineBuilder DataPipeline::round_robin(std::vector<DataPipeline> pipelines, bool stop_at_shortest,
                                               bool allow_repeats) {
+    refuse_broken(pipelines, "used in round robin");
     auto sp = share(std::move(pipelines));
     return DataPipelineBuilder([sp, stop_at_shortest, allow_repeats]() -> std::unique_ptr<DataSource> {
         return std::make_unique<RoundRobinSource>(std::move(*sp), stop_at_shortest, allow_repeats);
@@ -1637,6 +1665,7 @@ DataPipelineBuilder DataPipeline::round_robin(std::vector<DataPipeline> pipeline
 
 DataPipelineBuilder DataPipeline::sample(std::vector<DataPipeline> pipelines, std::optional<std::vector<float>> weights,
                                          uint64_t seed, bool allow_repeats) {
+    refuse_broken(pipelines, "sampled");
     std::vector<float> w = weights ? *weights : std::vector<float>(pipelines.size(), 1.0f);
     if (w.size() != pipelines.size())
         throw std::invalid_argument("The number of `pipelines` and `weights` must be equal.");
@@ -1650,18 +1679,21 @@ DataPipelineBuilder DataPipeline::sample(std::vector<DataPipeline> pipelines, st
 
 DataPipelineBuilder DataPipeline::zip(std::vector<DataPipeline> pipelines, std::vector<std::string> names,
                                       bool zip_to_shortest, bool flatten, bool) {
+    refuse_broken(pipelines, "zipped");
     if (!names.empty() && names.size() != pipelines.size())
-        throw std::invalid_argument("The number of `pipelines` and `names` must be equal.");
-    if (!names.empty() && flatten) throw std::invalid_argument("`names` and `flatten` are mutually exclusive.");
+        throw std::invalid_argument("The number of `pipelines` and the number of `names` must be equal, but are " +
+                                    std::to_string(pipelines.size()) + " and " + std::to_string(names.size()) +
+                                    " instead.");
+    if (!names.empty() && flatten)
+        throw std::invalid_argument("`names` and `flatten` are mutually exclusive and cannot be specified at the same time.");
+    bool any_inf = false, any_fin = false;
+    for (const auto& p : pipelines) {
+        if (p.finitude() == Finitude::Infinite) any_inf = true;
+        else if (p.finitude() == Finitude::Finite) any_fin = true;
+    }
+    if (any_inf && any_fin && !zip_to_shortest) throw DataPipelineError("Cannot mix finite and infinite pipelines in zip.");
     auto sp = share(std::move(pipelines));
     return DataPipelineBuilder([sp, names, zip_to_shortest, flatten]() -> std::unique_ptr<DataSource> {
-        bool any_inf = false, any_fin = false;
-        for (const auto& p : *sp) {
-            if (p.finitude() == Finitude::Infinite) any_inf = true;
-            else if (p.finitude() == Finitude::Finite) any_fin = true;
-        }
-        if (any_inf && any_fin && !zip_to_shortest)
-            throw DataPipelineError("Finite and infinite data pipelines cannot be zipped unless `zip_to_shortest` is set.");
         return std::make_unique<ZipSource>(std::move(*sp), names, zip_to_shortest, flatten);
     });
 }
