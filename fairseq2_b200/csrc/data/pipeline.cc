@@ -22,6 +22,9 @@ void DataPipeline::ensure_initialized() const {
         if (!s_->factory) return;  // an empty pipeline yields nothing
         try {
             s_->source = s_->factory();
+        } catch (const ByteStreamError& ex) {
+            s_->broken = true;
+            throw DataPipelineError(ex.what());
         } catch (...) {
             s_->broken = true;
             throw;
@@ -678,8 +681,9 @@ public:
             ready_.pop_front();
             return out;
         }
-        double cost = 0;
-        for (const auto& e : buffer_) cost += cost_(e);
+        // the cost runs over the examples added since the last bucket was cut: what a creation function hands back
+        // as the remainder starts the next bucket at cost zero (fairseq2n's dynamic_bucket_data_source.cc does so)
+        double& cost = acc_cost_;
         auto full = [&]() {
             const bool cost_ok = cost >= threshold_;
             const bool min_ok = !min_n_ || buffer_.size() >= *min_n_;
@@ -693,17 +697,17 @@ public:
                     if (res) {
                         for (auto& b : res->first) ready_.push_back(b.is_list() ? b.as_list() : DataList{b});
                         buffer_ = std::move(res->second);
+                        cost = 0;
                         if (!ready_.empty()) {
                             Data out(std::move(ready_.front()));
                             ready_.pop_front();
                             return out;
                         }
-                        cost = 0;
-                        for (const auto& e : buffer_) cost += cost_(e);
                     }
                 } else {
                     DataList out = std::move(buffer_);
                     buffer_.clear();
+                    cost = 0;
                     return Data(std::move(out));
                 }
             }
@@ -712,6 +716,7 @@ public:
             cost += cost_(*d);
             buffer_.push_back(std::move(*d));
         }
+        cost = 0;
         if (buffer_.empty() || drop_) {
             buffer_.clear();
             return std::nullopt;
@@ -723,9 +728,11 @@ public:
     void reset(bool r) override {
         buffer_.clear();
         ready_.clear();
+        acc_cost_ = 0;
         in_->reset(r);
     }
     void record_position(Tape& t, bool s) const override {
+        t.record(Data(acc_cost_));
         t.record(Data(DataList(buffer_)));
         DataList rd;
         for (const auto& b : ready_) rd.emplace_back(DataList(b));
@@ -733,6 +740,7 @@ public:
         in_->record_position(t, s);
     }
     void reload_position(Tape& t, bool s) override {
+        acc_cost_ = t.read().as_float();
         buffer_ = t.read().as_list();
         ready_.clear();
         for (auto& b : t.read().as_list()) ready_.push_back(b.as_list());
@@ -741,6 +749,7 @@ public:
     Finitude finitude() const override { return in_->finitude(); }
 
 private:
+    double acc_cost_ = 0;
     std::unique_ptr<DataSource> in_;
     double threshold_;
     CostFn cost_;
@@ -1483,7 +1492,7 @@ public:
             if (!ex) return std::nullopt;
             example_ = *ex;
             sub_ = std::make_unique<DataPipeline>(fn_(*ex));
-            if (sub_->finitude() == Finitude::Infinite)
+            if (sub_->finitude() != Finitude::Finite)
                 throw DataPipelineError("The data pipeline to yield from cannot be infinite.");
         }
     }
@@ -1680,12 +1689,12 @@ DataPipelineBuilder DataPipeline::sample(std::vector<DataPipeline> pipelines, st
 DataPipelineBuilder DataPipeline::zip(std::vector<DataPipeline> pipelines, std::vector<std::string> names,
                                       bool zip_to_shortest, bool flatten, bool) {
     refuse_broken(pipelines, "zipped");
+    if (!names.empty() && flatten)
+        throw std::invalid_argument("`names` and `flatten` are mutually exclusive and cannot be specified at the same time.");
     if (!names.empty() && names.size() != pipelines.size())
         throw std::invalid_argument("The number of `pipelines` and the number of `names` must be equal, but are " +
                                     std::to_string(pipelines.size()) + " and " + std::to_string(names.size()) +
                                     " instead.");
-    if (!names.empty() && flatten)
-        throw std::invalid_argument("`names` and `flatten` are mutually exclusive and cannot be specified at the same time.");
     bool any_inf = false, any_fin = false;
     for (const auto& p : pipelines) {
         if (p.finitude() == Finitude::Infinite) any_inf = true;

@@ -547,8 +547,9 @@ TEST(pipeline_text_reader_reencodes) {
     CHECK(w.next()->as_string() == "hi");
     CHECK(w.next()->as_string() == "\xe2\x82\xac");
     TempFile odd("utf16-truncated", std::string("h\0i", 3));
+    // a stream error reaches the caller of the pipeline as a pipeline error, and the pipeline stays broken
     CHECK_THROWS(read_text(odd.path, std::nullopt, "infer", false, false, false, false, 0, "UTF-16LE").and_return().next(),
-                 ByteStreamError);
+                 DataPipelineError);
     CHECK_THROWS(read_text(latin.path, std::nullopt, "infer", false, false, false, false, 0, "no-such-charset")
                      .and_return()
                      .next(),
