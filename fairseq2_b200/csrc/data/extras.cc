@@ -30,45 +30,52 @@ struct PathStep {
     size_t index = 0;
 };
 
-std::vector<PathStep> parse_path(const std::string& s) {
-    std::vector<PathStep> out;
+// One element path: keys separated by dots, list positions in brackets after a key or another position
+// ("a.b[0]", "[*].c"). No empty keys, no blanks, a dot only between a key or position and a following key.
+bool parse_path(const std::string& s, std::vector<PathStep>& out) {
     size_t i = 0;
-    auto fail = [&]() -> void {
-        throw std::invalid_argument("`selector` must be a well-formatted element path, but is '" + s + "' instead.");
-    };
-    if (s.empty()) fail();
+    if (s.empty()) return false;
+    bool need_key = false;              // the previous character was a dot
     while (i < s.size()) {
         if (s[i] == '[') {
+            if (need_key) return false;                              // "foo.[0]"
             size_t j = s.find(']', i);
-            if (j == std::string::npos) fail();
+            if (j == std::string::npos) return false;
             std::string inner = s.substr(i + 1, j - i - 1);
             if (inner == "*") {
                 out.push_back({PathStep::Wildcard, "", 0});
             } else {
-                if (inner.empty() || !std::all_of(inner.begin(), inner.end(), ::isdigit)) fail();
+                if (inner.empty() || inner.size() > 18 || !std::all_of(inner.begin(), inner.end(), ::isdigit)) return false;
                 out.push_back({PathStep::Index, "", static_cast<size_t>(std::stoull(inner))});
             }
             i = j + 1;
-            if (i < s.size() && s[i] == '.') {
-                ++i;
-                if (i >= s.size()) fail();
-            }
         } else {
             size_t j = i;
-            while (j < s.size() && s[j] != '.' && s[j] != '[') ++j;
-            if (j == i) fail();
+            while (j < s.size() && s[j] != '.' && s[j] != '[') {
+                if (s[j] == ' ' || s[j] == ']' || s[j] == ',') return false;
+                ++j;
+            }
+            if (j == i) return false;
             out.push_back({PathStep::Key, s.substr(i, j - i), 0});
             i = j;
-            if (i < s.size() && s[i] == '.') {
-                ++i;
-                if (i >= s.size() || s[i] == '.' ) fail();
-            }
+            need_key = false;
+        }
+        if (i < s.size() && s[i] == '.') {
+            ++i;
+            need_key = true;
+            if (i >= s.size()) return false;                         // "foo."
+        } else if (i < s.size() && s[i] != '[') {
+            return false;
         }
     }
-    return out;
+    return !need_key;
 }
 
 std::vector<std::vector<PathStep>> parse_selector(const std::string& s) {
+    auto fail = [&]() {
+        throw std::invalid_argument("`selector` must contain one or more well-formatted element paths, but is '" + s +
+                                    "' instead.");
+    };
     std::vector<std::vector<PathStep>> out;
     size_t start = 0;
     while (true) {
@@ -76,38 +83,72 @@ std::vector<std::vector<PathStep>> parse_selector(const std::string& s) {
         std::string part = s.substr(start, c == std::string::npos ? std::string::npos : c - start);
         size_t a = part.find_first_not_of(' ');
         size_t b = part.find_last_not_of(' ');
-        if (a == std::string::npos) throw std::invalid_argument("`selector` must not contain empty paths.");
-        out.push_back(parse_path(part.substr(a, b - a + 1)));
+        if (a == std::string::npos) fail();
+        std::vector<PathStep> path;
+        if (!parse_path(part.substr(a, b - a + 1), path)) fail();
+        out.push_back(std::move(path));
         if (c == std::string::npos) break;
         start = c + 1;
     }
     return out;
 }
 
-void visit_path(Data& d, const std::vector<PathStep>& path, size_t pos, const std::function<void(Data&)>& fn,
-                const std::string& sel) {
+// The path as it reads for one concrete element: wildcards up to `upto` replaced by the positions in `taken`.
+std::string concrete_path(const std::vector<PathStep>& path, const std::vector<size_t>& taken) {
+    std::string out;
+    size_t w = 0;
+    for (const PathStep& st : path) {
+        if (st.kind == PathStep::Key) {
+            if (!out.empty()) out += ".";
+            out += st.key;
+        } else if (st.kind == PathStep::Index) {
+            out += "[" + std::to_string(st.index) + "]";
+        } else {
+            out += w < taken.size() ? "[" + std::to_string(taken[w]) + "]" : "[*]";
+            ++w;
+        }
+    }
+    return out;
+}
+
+void visit_path_at(Data& d, const std::vector<PathStep>& path, size_t pos, const std::function<void(Data&)>& fn,
+                   std::vector<size_t>& taken) {
     if (pos == path.size()) {
         fn(d);
         return;
     }
     const PathStep& st = path[pos];
     auto missing = [&]() {
-        throw std::invalid_argument("The input data does not have an element at path '" + sel + "'.");
+        throw std::invalid_argument("The input data does not have an element at path '" + concrete_path(path, taken) +
+                                    "'.");
     };
     if (st.kind == PathStep::Key) {
         Data* e = d.find(st.key);
         if (e == nullptr) missing();
-        visit_path(*e, path, pos + 1, fn, sel);
+        visit_path_at(*e, path, pos + 1, fn, taken);
     } else if (st.kind == PathStep::Index) {
         if (!d.is_list() || st.index >= d.as_list().size()) missing();
-        visit_path(d.as_list()[st.index], path, pos + 1, fn, sel);
+        visit_path_at(d.as_list()[st.index], path, pos + 1, fn, taken);
     } else {
         if (!d.is_list()) missing();
-        for (auto& e : d.as_list()) visit_path(e, path, pos + 1, fn, sel);
+        DataList& items = d.as_list();
+        for (size_t i = 0; i < items.size(); ++i) {
+            taken.push_back(i);
+            visit_path_at(items[i], path, pos + 1, fn, taken);
+            taken.pop_back();
+        }
     }
 }
 
+void visit_path(Data& d, const std::vector<PathStep>& path, size_t pos, const std::function<void(Data&)>& fn,
+                const std::string&) {
+    std::vector<size_t> taken;
+    visit_path_at(d, path, pos, fn, taken);
+}
+
 }  // namespace
+
+void validate_selector(const std::string& selector) { parse_selector(selector); }
 
 Data apply_selected(Data&& d, const std::optional<std::string>& selector, const MapFn& fn) {
     if (!selector) return fn(std::move(d));

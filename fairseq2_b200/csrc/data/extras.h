@@ -9,6 +9,8 @@
 
 namespace fs2d {
 
+// Throws std::invalid_argument unless `selector` is a comma-separated list of well-formed element paths.
+void validate_selector(const std::string& selector);
 Data apply_selected(Data&& d, const std::optional<std::string>& selector, const MapFn& fn);
 const Data& select_single(const Data& d, const std::optional<std::string>& selector);
 

@@ -1574,6 +1574,7 @@ DataPipelineBuilder DataPipelineBuilder::filter(PredicateFn fn) && {
 DataPipelineBuilder DataPipelineBuilder::map(std::vector<MapFn> fns, std::optional<std::string> selector,
                                               size_t num_parallel_calls, bool deterministic) && {
     if (num_parallel_calls == 0) throw std::invalid_argument("`num_parallel_calls` must be greater than zero.");
+    if (selector) validate_selector(*selector);
     if (!deterministic && num_parallel_calls > 1)
         return DataPipelineBuilder(chain<AsyncMapSource>(std::move(factory_), fns, selector, num_parallel_calls));
     return DataPipelineBuilder(chain<MapSource>(std::move(factory_), fns, selector, num_parallel_calls));

@@ -81,24 +81,15 @@ def create_bucket_sizes(*, max_num_elements: int, max_seq_len: int, min_seq_len:
         raise ValueError(f"`max_num_elements` must be equal to a multiple of `max_seq_len`, but is {max_num_elements} instead.")
     if max_num_elements < max_seq_len * num_seqs_multiple_of:
         raise ValueError("`max_num_elements` must be greater than or equal to `max_seq_len * num_seqs_multiple_of`.")
+    # One entry per distinct value of `max_num_elements // seq_len`, at the longest `seq_len` that still allows that
+    # many rows; the row count is then rounded down to the multiple (so two entries may share a row count).
     sizes: list[tuple[int, int]] = []
     seq_len = min_seq_len
-    bucket_size = max_num_elements // seq_len
-    while seq_len < max_seq_len:
-        if seq_len > max_num_elements // bucket_size or True:
-            pass
-        # largest batch that fits `seq_len`, rounded down to the multiple
-        bs = max_num_elements // seq_len
-        bs -= bs % num_seqs_multiple_of
-        if bs < 1:
-            break
-        # longest sequence that still allows `bs` rows
-        seq_len = max_num_elements // bs
-        if seq_len >= max_seq_len:
-            break
-        sizes.append((bs, seq_len))
-        seq_len += 1
-    bs = max_num_elements // max_seq_len
-    bs -= bs % num_seqs_multiple_of
-    sizes.append((max(bs, num_seqs_multiple_of), max_seq_len))
+    while seq_len <= max_seq_len:
+        rows = max_num_elements // seq_len
+        last = min(max_num_elements // rows, max_seq_len)          # longest length with the same number of rows
+        rounded = rows - rows % num_seqs_multiple_of
+        if rounded > 0:
+            sizes.append((rounded, last))
+        seq_len = last + 1
     return sizes
