@@ -851,10 +851,11 @@ public:
         in_->reset(r);
     }
     void record_position(Tape& t, bool s) const override {
-        // remaining mapped-but-unread outputs are part of the position
+        // remaining mapped-but-unread outputs are part of the position (left out of a state that is not strict)
         DataList rest;
-        for (size_t i = out_pos_; i < out_.size(); ++i)
-            if (!out_[i].error) rest.push_back(out_[i].value);
+        if (s)
+            for (size_t i = out_pos_; i < out_.size(); ++i)
+                if (!out_[i].error) rest.push_back(out_[i].value);
         t.record(Data(std::move(rest)));
         in_->record_position(t, s);
     }
@@ -978,8 +979,9 @@ public:
     void record_position(Tape& t, bool s) const override {
         const_cast<AsyncMapSource*>(this)->drain();
         DataList rest;
-        for (const Slot& slot : st_->done)
-            if (!slot.error) rest.push_back(slot.value);
+        if (s)
+            for (const Slot& slot : st_->done)
+                if (!slot.error) rest.push_back(slot.value);
         t.record(Data(std::move(rest)));
         in_->record_position(t, s);
     }
@@ -1192,7 +1194,7 @@ public:
         self->stop_thread();  // quiesce: the queue and the inner position are then consistent
         {
             std::lock_guard<std::mutex> lk(m_);
-            t.record(Data(DataList(q_.begin(), q_.end())));
+            t.record(Data(s ? DataList(q_.begin(), q_.end()) : DataList{}));   // not strict: without the queue
             t.record_bool(state_ == State::Eod);
         }
         in_->record_position(t, s);
@@ -1396,8 +1398,10 @@ public:
         in_->reset(r);
     }
     void record_position(Tape& t, bool s) const override {
-        t.record(Data(DataList(buf_)));
-        t.record_bool(filled_);
+        // not strict: the buffered examples are left out of the state (smaller, and the run goes on with what the
+        // input still holds); the buffer is filled again from there
+        t.record(Data(s ? DataList(buf_) : DataList{}));
+        t.record_bool(s ? filled_ : false);
         t.record_bool(inner_done_);
         t.record_int(static_cast<int64_t>(gen_.state));
         in_->record_position(t, s);
