@@ -838,7 +838,7 @@ SentencePieceModel::SentencePieceModel(std::string_view serialized, const std::v
 SentencePieceModel SentencePieceModel::from_file(const std::string& path,
                                                  const std::vector<std::string>& control_symbols) {
     std::ifstream fp(path, std::ios::binary);
-    if (!fp) throw std::invalid_argument("The SentencePiece model '" + path + "' cannot be opened.");
+    if (!fp) throw std::runtime_error("The SentencePiece model '" + path + "' cannot be opened: No such file or directory.");
     std::stringstream ss;
     ss << fp.rdbuf();
     std::string blob = ss.str();
@@ -854,7 +854,8 @@ int SentencePieceModel::piece_to_id(std::string_view piece) const { return impl_
 
 const std::string& SentencePieceModel::id_to_piece(int id) const {
     if (id < 0 || static_cast<size_t>(id) >= impl_->pieces.size())
-        throw std::out_of_range("The index " + std::to_string(id) + " is outside the SentencePiece vocabulary.");
+        throw std::invalid_argument("`idx` must be less than vocabulary size (" + std::to_string(impl_->pieces.size()) +
+                                    "), but is " + std::to_string(id) + " instead.");
     return impl_->pieces[id].text;
 }
 
@@ -1007,13 +1008,13 @@ at::Tensor SentencePieceEncoder::encode(std::string_view text) const {
     } else {
         ids = model_.encode(text);
     }
-    if (reverse_) std::reverse(ids.begin(), ids.end());
     const int64_t n = static_cast<int64_t>(prefix_.size() + ids.size() + suffix_.size());
     at::Tensor t = at::empty({n}, at::TensorOptions().dtype(at::kLong).pinned_memory(pin_ && device_.has_value() && device_->is_cuda()));
     int64_t* p = t.data_ptr<int64_t>();
-    p = std::copy(prefix_.begin(), prefix_.end(), p);
-    p = std::copy(ids.begin(), ids.end(), p);
-    std::copy(suffix_.begin(), suffix_.end(), p);
+    int64_t* q = std::copy(prefix_.begin(), prefix_.end(), p);
+    q = std::copy(ids.begin(), ids.end(), q);
+    std::copy(suffix_.begin(), suffix_.end(), q);
+    if (reverse_) std::reverse(p, p + n);            // the whole sequence, prefix and suffix tokens included
     if (device_.has_value() && !device_->is_cpu()) t = t.to(*device_, /*non_blocking=*/pin_);
     return t;
 }
@@ -1021,10 +1022,10 @@ at::Tensor SentencePieceEncoder::encode(std::string_view text) const {
 std::vector<std::string> SentencePieceEncoder::encode_as_tokens(std::string_view text) const {
     std::vector<std::string> out;
     auto pieces = model_.encode_as_pieces(text);
-    if (reverse_) std::reverse(pieces.begin(), pieces.end());
     for (const int64_t id : prefix_) out.push_back(model_.id_to_piece(static_cast<int>(id)));
     for (auto& p : pieces) out.push_back(std::move(p.first));
     for (const int64_t id : suffix_) out.push_back(model_.id_to_piece(static_cast<int>(id)));
+    if (reverse_) std::reverse(out.begin(), out.end());
     return out;
 }
 
@@ -1034,7 +1035,11 @@ Data SentencePieceEncoder::operator()(Data&& d) const {
 }
 
 std::string SentencePieceDecoder::decode(const at::Tensor& indices) const {
-    if (indices.dim() != 1) throw std::invalid_argument("The input of a SentencePiece decoder must be one-dimensional.");
+    if (indices.dim() != 1)
+        throw std::invalid_argument("The input tensor must be one dimensional, but has " + std::to_string(indices.dim()) +
+                                    " dimension(s) instead.");
+    if (indices.scalar_type() != at::kShort && indices.scalar_type() != at::kInt && indices.scalar_type() != at::kLong)
+        throw std::invalid_argument("`sp_decoder` supports only `torch.int16`, `torch.int32`, and `torch.int64` data types.");
     at::Tensor t = indices.to(at::kCPU, at::kLong).contiguous();
     const int64_t* p = t.data_ptr<int64_t>();
     std::vector<int64_t> ids(p, p + t.numel());

@@ -634,7 +634,7 @@ TEST(sentencepiece_unigram_viterbi_and_decode) {
     auto best = m.nbest_encode("ab", 3);
     CHECK(best.size() == 3 && best[0].second >= best[1].second && best[1].second >= best[2].second);
     CHECK(best[0].first.size() == 1 && best[0].first[0].second == 7);
-    CHECK_THROWS(m.id_to_piece(99), std::out_of_range);
+    CHECK_THROWS(m.id_to_piece(99), std::invalid_argument);
     CHECK_THROWS(SentencePieceModel(std::string("\x0a\x05zz"), {}), std::invalid_argument);
 }
 
@@ -662,7 +662,8 @@ TEST(sentencepiece_encoder_tensor_layout) {
     SentencePieceEncoder enc(m, {"<s>"}, {"</s>"}, /*reverse=*/true, false, -1, 0.1f, std::nullopt, false, 0);
     at::Tensor t = enc.encode("ab a");
     CHECK(t.scalar_type() == at::kLong && t.numel() == 4);
-    CHECK(t[0].item<int64_t>() == 1 && t[1].item<int64_t>() == 3 && t[2].item<int64_t>() == 7 && t[3].item<int64_t>() == 2);
+    // reversed as a whole: </s>, the pieces back to front, <s>
+    CHECK(t[0].item<int64_t>() == 2 && t[1].item<int64_t>() == 3 && t[2].item<int64_t>() == 7 && t[3].item<int64_t>() == 1);
     SentencePieceDecoder dec(m, /*reverse=*/true);
     CHECK(dec.decode(t) == "ab a");
     CHECK_THROWS(SentencePieceEncoder(m, {"<nope>"}, {}, false, false, -1, 0.1f, std::nullopt, false, 0),

@@ -131,6 +131,11 @@ class SentencePieceDecoder(TokenDecoder):
         self._m, self._reverse = model, reverse
 
     def __call__(self, token_indices: Tensor) -> str:
+        if token_indices.dim() != 1:
+            raise ValueError(
+                f"The input tensor must be one dimensional, but has {token_indices.dim()} dimension(s) instead.")
+        if token_indices.dtype not in (torch.int16, torch.int32, torch.int64):
+            raise ValueError("`sp_decoder` supports only `torch.int16`, `torch.int32`, and `torch.int64` data types.")
         ids = [int(i) for i in token_indices.tolist()]
         if self._reverse:
             ids = ids[::-1]

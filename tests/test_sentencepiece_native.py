@@ -126,8 +126,8 @@ def test_encoder_options_and_pipeline_use(trained: dict[str, tuple]) -> None:
     assert model.vocabulary_size == ref.GetPieceSize() + 1 and model.token_to_index("<extra>") == ref.GetPieceSize()
     enc = SentencePieceEncoder(model, prefix_tokens=["<s>", "<extra>"], suffix_tokens=["</s>"], reverse=True)
     ids = enc("hello world")
-    assert ids.dtype == torch.int64 and ids.tolist() == [1, ref.GetPieceSize(), *ref.EncodeAsIds("hello world")[::-1], 2]
-    assert enc.encode_as_tokens("hello world") == ["<s>", "<extra>", *ref.EncodeAsPieces("hello world")[::-1], "</s>"]
+    assert ids.dtype == torch.int64 and ids.tolist() == [2, *ref.EncodeAsIds("hello world")[::-1], ref.GetPieceSize(), 1]
+    assert enc.encode_as_tokens("hello world") == ["</s>", *ref.EncodeAsPieces("hello world")[::-1], "<extra>", "<s>"]  # reversed as a whole
     dec = SentencePieceDecoder(model, reverse=True)
     assert dec(ids) == "hello world"                                 # control symbols decode to nothing
     with pytest.raises(ValueError):
