@@ -127,10 +127,28 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
 
     py::class_<MemoryBlock>(m, "MemoryBlock", py::buffer_protocol())
         .def(py::init<>())
-        .def(py::init([](py::buffer b) {
-            py::buffer_info info = b.request();
-            return MemoryBlock::copy_of(info.ptr, static_cast<size_t>(info.size * info.itemsize));
-        }))
+        .def(py::init([](py::buffer b, bool copy) {
+            // Shares the exporter's bytes unless a copy is asked for: the buffer view stays held, which
+            // keeps the exporter alive and unresizable, and is released under the GIL with the last reference.
+            auto info = std::make_unique<py::buffer_info>(b.request());
+            const size_t n = static_cast<size_t>(info->size * info->itemsize);
+            if (info->view() != nullptr && PyBuffer_IsContiguous(info->view(), 'C') == 0)
+                throw std::invalid_argument("`buffer` must be contiguous in memory.");
+            if (copy) return MemoryBlock::copy_of(info->ptr, n);
+            const auto* data = static_cast<const uint8_t*>(info->ptr);
+            std::shared_ptr<const void> owner(info.release(), [](const void* held) {
+                py::gil_scoped_acquire gil;
+                delete static_cast<const py::buffer_info*>(held);
+            });
+            return MemoryBlock(std::move(owner), data, n);
+        }), py::arg("buffer"), py::arg("copy") = false)
+        .def("__reduce_ex__", [](py::object self, int protocol) {
+            // protocol 5 hands the bytes over as a PickleBuffer (out-of-band capable), older ones as bytes
+            py::object cls = self.attr("__class__");
+            if (protocol >= 5)
+                return py::make_tuple(cls, py::make_tuple(py::module_::import("pickle").attr("PickleBuffer")(self)));
+            return py::make_tuple(cls, py::make_tuple(py::bytes(self)));
+        })
         .def("__len__", &MemoryBlock::size)
         .def("__bytes__", [](const MemoryBlock& b) {
             return py::bytes(reinterpret_cast<const char*>(b.data()), b.size());
@@ -313,11 +331,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                          std::optional<py::object> indices, bool exclude) {
             if (sep.size() != 1) throw std::invalid_argument("`sep` must be of length 1.");
             std::vector<size_t> idx;
+            bool single = false;
             if (indices && !indices->is_none()) {
-                if (py::isinstance<py::int_>(*indices)) idx.push_back(indices->cast<size_t>());
+                single = py::isinstance<py::int_>(*indices);
+                if (single) idx.push_back(indices->cast<size_t>());
                 else idx = indices->cast<std::vector<size_t>>();
             }
-            return StrSplitter(sep[0], std::move(names), std::move(idx), exclude);
+            return StrSplitter(sep[0], std::move(names), std::move(idx), exclude, single);
         }), py::arg("sep") = "\t", py::arg("names") = py::none(), py::arg("indices") = py::none(),
            py::arg("exclude") = false)
         .def("__call__", [](const StrSplitter& s, Data d) { return s(std::move(d)); });

@@ -9,6 +9,7 @@
 #include <zlib.h>
 
 #include <algorithm>
+#include <limits>
 #include <cctype>
 #include <cstring>
 #include <fstream>
@@ -610,26 +611,65 @@ FileMapper::FileMapper(std::optional<std::string> root_dir, size_t cached_fd_cou
     : root_(std::move(root_dir)), capacity_(cached_fd_count == 0 ? 100 : cached_fd_count),
       cache_(std::make_shared<Cache>()) {}
 
-Data FileMapper::operator()(Data&& d) const {
-    if (!d.is_string()) throw std::invalid_argument("The input data must be a path string.");
-    std::string spec = d.as_string();
-    // "path[:offset[:length]]"
-    std::string path = spec;
-    std::optional<size_t> off, len;
-    size_t c2 = spec.rfind(':');
-    if (c2 != std::string::npos) {
-        size_t c1 = c2 > 0 ? spec.rfind(':', c2 - 1) : std::string::npos;
-        auto is_num = [](const std::string& s) { return !s.empty() && std::all_of(s.begin(), s.end(), ::isdigit); };
-        std::string last = spec.substr(c2 + 1);
-        if (c1 != std::string::npos && is_num(last) && is_num(spec.substr(c1 + 1, c2 - c1 - 1))) {
-            off = std::stoull(spec.substr(c1 + 1, c2 - c1 - 1));
-            len = std::stoull(last);
-            path = spec.substr(0, c1);
-        } else if (is_num(last)) {
-            off = std::stoull(last);
-            path = spec.substr(0, c2);
-        }
+namespace {
+
+std::string trimmed(const std::string& s) {
+    size_t b = 0, e = s.size();
+    while (b < e && std::isspace(static_cast<unsigned char>(s[b]))) ++b;
+    while (e > b && std::isspace(static_cast<unsigned char>(s[e - 1]))) --e;
+    return s.substr(b, e - b);
+}
+
+// 1234567 -> "1,234,567"
+std::string with_thousands(size_t v) {
+    std::string digits = std::to_string(v), out;
+    for (size_t i = 0; i < digits.size(); ++i) {
+        if (i != 0 && (digits.size() - i) % 3 == 0) out.push_back(',');
+        out.push_back(digits[i]);
     }
+    return out;
+}
+
+// The offset or size specifier of "path:offset:size": decimal digits only, and it has to fit a size_t.
+size_t parse_specifier(const char* what, const std::string& spec, const std::string& text) {
+    if (text.empty() || !std::all_of(text.begin(), text.end(), [](unsigned char c) { return std::isdigit(c) != 0; }))
+        throw std::invalid_argument(std::string("The ") + what + " specifier of '" + spec + "' must be an integer, but is '" +
+                                    text + "' instead.");
+    size_t v = 0;
+    for (const char c : text) {
+        const size_t digit = static_cast<size_t>(c - '0');
+        if (v > (std::numeric_limits<size_t>::max() - digit) / 10)
+            throw std::invalid_argument(std::string("The ") + what + " specifier of '" + spec +
+                                        "' must be a machine-representable integer, but is '" + text +
+                                        "' instead, which is out of range.");
+        v = v * 10 + digit;
+    }
+    return v;
+}
+
+}  // namespace
+
+Data FileMapper::operator()(Data&& d) const {
+    if (!d.is_string()) {
+        const char* tn = d.is_none() ? "pyobj" : collate_type_name(d);
+        throw std::invalid_argument(std::string("The input data must be of type `string`, but is of type `") + tn + "` instead.");
+    }
+    std::string spec = d.as_string();
+    // "path[:offset[:size]]": one to three fields between colons, none of them blank
+    std::vector<std::string> fields;
+    for (size_t pos = 0;;) {
+        const size_t c = spec.find(':', pos);
+        fields.push_back(trimmed(spec.substr(pos, c == std::string::npos ? std::string::npos : c - pos)));
+        if (c == std::string::npos) break;
+        pos = c + 1;
+    }
+    if (fields.size() > 3 || std::any_of(fields.begin(), fields.end(), [](const std::string& f) { return f.empty(); }))
+        throw std::invalid_argument("The input string must be a pathname with optional offset and size specifiers, but is '" +
+                                    spec + "' instead.");
+    const std::string& path = fields[0];
+    std::optional<size_t> off, len;
+    if (fields.size() >= 2) off = parse_specifier("offset", spec, fields[1]);
+    if (fields.size() == 3) len = parse_specifier("size", spec, fields[2]);
     std::string full = (root_ && !path.empty() && path[0] != '/') ? *root_ + "/" + path : path;
     MemoryBlock block;
     {
@@ -651,9 +691,14 @@ Data FileMapper::operator()(Data&& d) const {
         }
     }
     if (off) {
-        if (*off > block.size()) throw std::invalid_argument("The offset in '" + spec + "' is beyond the end of the file.");
+        if (*off > block.size())
+            throw std::invalid_argument("The specified offset within '" + spec + "' must be less than or equal to the file size (" +
+                                        with_thousands(block.size()) + " bytes), but is " + with_thousands(*off) + " instead.");
         const size_t l = len ? *len : block.size() - *off;
-        if (l > block.size() - *off) throw std::invalid_argument("The length in '" + spec + "' is beyond the end of the file.");
+        if (l > block.size() - *off)
+            throw std::invalid_argument("The end of the specified region within '" + spec +
+                                        "' must be less than or equal to the file size (" + with_thousands(block.size()) +
+                                        " bytes), but is " + with_thousands(*off + l) + " instead.");
         block = block.slice(*off, l);
     }
     DataDict out{{"path", Data(spec)}, {"data", Data(block)}};
@@ -661,14 +706,43 @@ Data FileMapper::operator()(Data&& d) const {
 }
 
 // ============================================================= text converters
+namespace {
+
+[[noreturn]] void refuse_non_string(const Data& d) {
+    const char* tn = d.is_none() ? "pyobj" : collate_type_name(d);
+    throw std::invalid_argument(std::string("The input data must be of type `string`, but is of type `") + tn + "` instead.");
+}
+
+struct IntegralType {
+    const char* name;
+    int64_t lo, hi;
+};
+
+IntegralType integral_type(at::ScalarType t) {
+    switch (t) {
+        case at::kByte: return {"torch.uint8", 0, 255};
+        case at::kChar: return {"torch.int8", -128, 127};
+        case at::kShort: return {"torch.int16", -32768, 32767};
+        case at::kInt: return {"torch.int32", std::numeric_limits<int32_t>::min(), std::numeric_limits<int32_t>::max()};
+        default: return {"torch.int64", std::numeric_limits<int64_t>::min(), std::numeric_limits<int64_t>::max()};
+    }
+}
+
+}  // namespace
+
 StrSplitter::StrSplitter(char sep, std::optional<std::vector<std::string>> names, std::vector<size_t> indices,
-                         bool exclude)
-    : sep_(sep), names_(std::move(names)), indices_(std::move(indices)), exclude_(exclude) {
+                         bool exclude, bool single_index)
+    : sep_(sep), names_(std::move(names)), indices_(std::move(indices)), exclude_(exclude),
+      single_index_(single_index && !exclude) {
+    // with kept (not excluded) indices every kept field gets one name
+    if (names_ && !indices_.empty() && !exclude_ && names_->size() != indices_.size())
+        throw std::invalid_argument("`names` and `indices` must have the same length, but have the lengths " +
+                                    std::to_string(names_->size()) + " and " + std::to_string(indices_.size()) + " instead.");
     std::sort(indices_.begin(), indices_.end());
 }
 
 Data StrSplitter::operator()(Data&& d) const {
-    if (!d.is_string()) throw std::invalid_argument("The input data must be of type `str`.");
+    if (!d.is_string()) refuse_non_string(d);
     const std::string& s = d.as_string();
     std::vector<std::string> fields;
     size_t start = 0;
@@ -679,81 +753,84 @@ Data StrSplitter::operator()(Data&& d) const {
         start = p + 1;
     }
     if (!indices_.empty()) {
+        // kept or excluded, the highest index has to exist in the line
+        if (indices_.back() >= fields.size())
+            throw std::invalid_argument("The input string must have at least " + std::to_string(indices_.back()) +
+                                        " field(s), but has " + std::to_string(fields.size()) + " instead.");
         std::vector<std::string> kept;
         if (exclude_) {
             for (size_t i = 0; i < fields.size(); ++i)
                 if (!std::binary_search(indices_.begin(), indices_.end(), i)) kept.push_back(fields[i]);
         } else {
-            for (size_t i : indices_) {
-                if (i >= fields.size())
-                    throw std::invalid_argument("The input string must have at least " + std::to_string(i + 1) +
-                                                " field(s), but has " + std::to_string(fields.size()) + " instead.");
-                kept.push_back(fields[i]);
-            }
+            for (size_t i : indices_) kept.push_back(fields[i]);
         }
         fields = std::move(kept);
     }
     if (names_) {
         if (names_->size() != fields.size())
-            throw std::invalid_argument("The number of fields (" + std::to_string(fields.size()) +
-                                        ") must match the number of names (" + std::to_string(names_->size()) + ").");
+            throw std::invalid_argument("The number of fields must match the number of names (" +
+                                        std::to_string(names_->size()) + "), but is " + std::to_string(fields.size()) +
+                                        " instead.");
         DataDict out;
         for (size_t i = 0; i < fields.size(); ++i) out.emplace_back((*names_)[i], Data(std::move(fields[i])));
         return Data(std::move(out));
     }
+    // one kept index given as an int yields the field itself rather than a list of one
+    if (single_index_ && fields.size() == 1) return Data(std::move(fields[0]));
     DataList out;
     for (auto& f : fields) out.emplace_back(std::move(f));
     return Data(std::move(out));
 }
 
 Data StrToIntConverter::operator()(Data&& d) const {
-    if (!d.is_string()) throw std::invalid_argument("The input data must be of type `str`.");
+    if (!d.is_string()) refuse_non_string(d);
     const std::string& s = d.as_string();
+    const std::string head = "The input string must represent a 64-bit integer, but is '" + s + "' instead";
     try {
         size_t idx = 0;
         long long v = std::stoll(s, &idx, base_);
         if (idx != s.size()) throw std::invalid_argument("trailing characters");
         return Data(static_cast<int64_t>(v));
+    } catch (const std::out_of_range&) {
+        throw std::invalid_argument(head + ", which is out of range.");
     } catch (const std::exception&) {
-        throw std::invalid_argument("The input string must represent an integer, but is '" + s + "' instead.");
+        throw std::invalid_argument(head + ".");
     }
 }
 
 Data StrToTensorConverter::operator()(Data&& d) const {
-    if (!d.is_string()) throw std::invalid_argument("The input data must be of type `str`.");
+    if (!d.is_string()) refuse_non_string(d);
     const std::string& s = d.as_string();
-    std::vector<double> fvals;
-    std::vector<int64_t> ivals;
-    const bool is_float = at::isFloatingType(dtype_);
+    const IntegralType type = integral_type(dtype_);
+    const std::string head = std::string("The input string must be a space-separated list representing values of type `") +
+                             type.name + "`, but contains an element with value '";
+    std::vector<int64_t> vals;
     size_t i = 0;
     while (i < s.size()) {
         while (i < s.size() && std::isspace(static_cast<unsigned char>(s[i]))) ++i;
         if (i >= s.size()) break;
         size_t j = i;
         while (j < s.size() && !std::isspace(static_cast<unsigned char>(s[j]))) ++j;
-        std::string tok = s.substr(i, j - i);
+        const std::string tok = s.substr(i, j - i);
+        bool parsed = false, in_range = true;
+        long long v = 0;
         try {
             size_t idx = 0;
-            if (is_float) {
-                fvals.push_back(std::stod(tok, &idx));
-            } else {
-                ivals.push_back(std::stoll(tok, &idx));
-            }
-            if (idx != tok.size()) throw std::invalid_argument("bad token");
+            v = std::stoll(tok, &idx);
+            parsed = idx == tok.size();
+        } catch (const std::out_of_range&) {
+            parsed = true;
+            in_range = false;
         } catch (const std::exception&) {
-            throw std::invalid_argument("The input string must be a space-separated list of numbers, but contains '" + tok + "'.");
         }
+        if (!parsed) throw std::invalid_argument(head + tok + "' that cannot be parsed as `" + type.name + "`.");
+        if (!in_range || v < type.lo || v > type.hi)
+            throw std::invalid_argument(head + tok + "' that is out of range for `" + type.name + "`.");
+        vals.push_back(v);
         i = j;
     }
-    at::Tensor t = is_float ? at::tensor(fvals, at::kDouble).to(dtype_) : at::tensor(ivals, at::kLong).to(dtype_);
-    if (size_) {
-        int64_t n = 1;
-        for (auto x : *size_) n *= x;
-        if (n != t.numel())
-            throw std::invalid_argument("The number of parsed elements (" + std::to_string(t.numel()) +
-                                        ") does not match the requested size.");
-        t = t.view(*size_);
-    }
+    at::Tensor t = at::tensor(vals, at::kLong).to(dtype_);
+    if (size_) t = t.view(*size_);                   // a -1 extent is inferred; a mismatch raises torch's shape error
     return Data(t);
 }
 

@@ -48,7 +48,7 @@ private:
 
 class StrSplitter {
 public:
-    StrSplitter(char sep, std::optional<std::vector<std::string>> names, std::vector<size_t> indices, bool exclude);
+    StrSplitter(char sep, std::optional<std::vector<std::string>> names, std::vector<size_t> indices, bool exclude, bool single_index = false);
     Data operator()(Data&& d) const;
 
 private:
@@ -56,6 +56,7 @@ private:
     std::optional<std::vector<std::string>> names_;
     std::vector<size_t> indices_;
     bool exclude_;
+    bool single_index_;  // `indices` was one int, not a list: the field itself is returned
 };
 
 class StrToIntConverter {
@@ -70,7 +71,10 @@ private:
 class StrToTensorConverter {
 public:
     StrToTensorConverter(std::optional<std::vector<int64_t>> size, at::ScalarType dtype)
-        : size_(std::move(size)), dtype_(dtype) {}
+        : size_(std::move(size)), dtype_(dtype) {
+        if (!at::isIntegralType(dtype, /*includeBool=*/false))
+            throw std::invalid_argument("Only integral types are supported.");
+    }
     Data operator()(Data&& d) const;
 
 private:

@@ -50,6 +50,15 @@ read_zipped_records = _n.read_zipped_records
 read_iterator = _n.read_iterator
 
 
+class FileMapperOutput(TypedDict):
+    """What a :class:`FileMapper` returns for one pathname: the path relative to
+    the mapper's root and the bytes of the file, or of the requested slice of it
+    (cf. fairseq2 ``data/data_pipeline.py``, ``FileMapperOutput``)."""
+
+    path: str
+    data: "MemoryBlock"
+
+
 class SequenceData(TypedDict):
     """Output of the collater for padded sequences."""
 
