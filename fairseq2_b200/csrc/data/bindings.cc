@@ -468,8 +468,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
             try {
                 py::module_::import("pickle").attr("dumps")(iterator);
             } catch (py::error_already_set&) {
-                throw std::invalid_argument(
-                    "`iterator` is not pickleable; set `skip_pickling_check` to True to bypass (not recommended).");
+                throw py::type_error(
+                    "`iterator` is not pickleable; set `skip_pickling_check` to True to bypass (see `read_iterator` documentation for details).");
             }
         }
         return read_py_iterator(std::move(iterator), std::move(reset_fn), infinite);

@@ -1566,7 +1566,7 @@ DataPipelineBuilder DataPipelineBuilder::dynamic_bucket(double threshold, CostFn
     if (max_num_examples && *max_num_examples == 0)
         throw std::invalid_argument("`max_num_examples` must be greater than zero.");
     if (min_num_examples && max_num_examples && *min_num_examples > *max_num_examples)
-        throw std::invalid_argument("`min_num_examples` must be less than or equal to `max_num_examples`.");
+        throw std::invalid_argument("`max_num_examples` must be greater than or equal to `min_num_examples`.");
     return DataPipelineBuilder(chain<DynamicBucketSource>(std::move(factory_), threshold, cost_fn, creation_fn,
                                                           min_num_examples, max_num_examples, drop_remainder));
 }
